@@ -1,0 +1,7 @@
+"""pmetal_b200 — LLM fine-tuning, RL and serving on NVIDIA B200 (sm_100a).
+
+PyTorch is the framework layer; the hot operators are hand-written CUDA kernels in
+``pmetal_b200/csrc`` (tcgen05/TMEM GEMMs fed by TMA, flash attention, fused
+normalisation/activation/loss/optimizer kernels and peer-memory collectives).
+"""
+__version__ = "0.1.0"

@@ -1,0 +1,367 @@
+"""Decoder-only transformer (Qwen3 / Qwen2 / Llama / Mistral family, dense or MoE).
+
+Behaviour follows the reference's Qwen3 implementation
+(crates/pmetal-models/src/architectures/qwen3.rs:235-545): pre-norm blocks, GQA,
+optional per-head RMSNorm on q and k before half-split RoPE, SwiGLU MLP, optional
+tied output embedding; the MoE variant follows qwen3_moe.rs:390-640.
+
+Physical layout differs from the Hugging Face checkpoint layout on purpose: q, k, v
+are one row-stacked weight (one GEMM), as are gate and up, and every frozen weight
+can keep a transposed copy so that the input-gradient GEMM reads a K-major operand.
+Activations are a flat token stream [T, hidden] with ``cu_seqlens`` document
+boundaries; a padded batch is the special case of equal-length documents.
+``load_hf_state_dict`` / ``hf_state_dict`` translate to and from checkpoint names.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import functional as ops
+from .config import ModelArgs
+
+ATTN_PROJ = ("q_proj", "k_proj", "v_proj", "o_proj")
+MLP_PROJ = ("gate_proj", "up_proj", "down_proj")
+ALL_PROJ = ATTN_PROJ + MLP_PROJ
+
+
+class FusedLinear(nn.Module):
+    """A row-stacked group of projections sharing one input, with optional LoRA.
+
+    ``weight`` is [sum(seg_sizes), in]. LoRA factors are stored stacked as
+    ``lora_a`` [n_seg·r, in] and ``lora_b`` [sum(seg_sizes), r] in fp32 (the reference keeps
+    adapters in f32, crates/pmetal-lora/src/lora.rs:268-289). ``active`` marks which
+    segments are LoRA targets; inactive ones keep zero factors and receive no update.
+    """
+
+    def __init__(self, in_features: int, seg_names: Sequence[str], seg_sizes: Sequence[int], bias: bool = False,
+                 dtype=torch.float32, device=None):
+        super().__init__()
+        self.in_features = in_features
+        self.seg_names = tuple(seg_names)
+        self.seg_sizes = tuple(int(s) for s in seg_sizes)
+        self.out_features = sum(self.seg_sizes)
+        self.weight = nn.Parameter(torch.empty(self.out_features, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(self.out_features, dtype=dtype, device=device)) if bias else None
+        self.weight_t: Optional[torch.Tensor] = None
+        self.lora_a: Optional[nn.Parameter] = None
+        self.lora_b: Optional[nn.Parameter] = None
+        self.r = 0
+        self.scale = 0.0
+        self.active: Tuple[bool, ...] = tuple(False for _ in self.seg_sizes)
+
+    # -- LoRA management
+    def add_lora(self, r: int, scale: float, active: Sequence[bool], use_rslora: bool = False,
+                 generator: Optional[torch.Generator] = None) -> None:
+        if r <= 0 or not any(active):
+            return
+        dev = self.weight.device
+        n = len(self.seg_sizes)
+        a = torch.zeros(n * r, self.in_features, dtype=torch.float32)
+        # A ~ U(±sqrt(3/in)) (rsLoRA: ±sqrt(1/r)), B = 0  (crates/pmetal-lora/src/lora.rs:268-289)
+        bound = math.sqrt(1.0 / r) if use_rslora else math.sqrt(3.0 / self.in_features)
+        for i, on in enumerate(active):
+            if on:
+                a[i * r:(i + 1) * r].uniform_(-bound, bound, generator=generator)
+        self.lora_a = nn.Parameter(a.to(dev))
+        self.lora_b = nn.Parameter(torch.zeros(self.out_features, r, dtype=torch.float32, device=dev))
+        self.r, self.scale, self.active = r, float(scale), tuple(bool(x) for x in active)
+        if not all(self.active):
+            mask_a = torch.zeros(n * r, 1, device=dev)
+            mask_b = torch.zeros(self.out_features, 1, device=dev)
+            o = 0
+            for i, (on, sz) in enumerate(zip(self.active, self.seg_sizes)):
+                if on:
+                    mask_a[i * r:(i + 1) * r] = 1
+                    mask_b[o:o + sz] = 1
+                o += sz
+            self.lora_a.register_hook(lambda g, m=mask_a: g * m)
+            self.lora_b.register_hook(lambda g, m=mask_b: g * m)
+
+    def seg_slice(self, name: str) -> Tuple[int, slice]:
+        i = self.seg_names.index(name)
+        o = sum(self.seg_sizes[:i])
+        return i, slice(o, o + self.seg_sizes[i])
+
+    def prepare_transposed(self) -> None:
+        """Keep Wᵀ for the input-gradient GEMM (frozen weights only)."""
+        if self.weight.is_cuda and not self.weight.requires_grad:
+            self.weight_t = self.weight.detach().t().contiguous()
+
+    def merged_weight(self) -> torch.Tensor:
+        w = self.weight.detach().float()
+        if self.lora_a is not None:
+            o = 0
+            for i, sz in enumerate(self.seg_sizes):
+                a = self.lora_a[i * self.r:(i + 1) * self.r].float()
+                w[o:o + sz] += self.scale * (self.lora_b[o:o + sz].float() @ a)
+                o += sz
+        return w
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.bias is not None or self.weight.requires_grad:
+            y = F.linear(x, self.weight, self.bias)
+            if self.lora_a is not None:
+                y = y + self._lora_delta(x)
+            return y if residual is None else y + residual
+        return ops.lora_linear(x, self.weight, self.weight_t, self.lora_a, self.lora_b, self.seg_sizes, self.r,
+                               self.scale, residual, getattr(self, "lora_a_c", None), getattr(self, "lora_b_c", None))
+
+    def _lora_delta(self, x: torch.Tensor) -> torch.Tensor:
+        outs, o = [], 0
+        for i, sz in enumerate(self.seg_sizes):
+            t = F.linear(x, self.lora_a[i * self.r:(i + 1) * self.r].to(x.dtype))
+            outs.append(self.scale * F.linear(t, self.lora_b[o:o + sz].to(x.dtype)))
+            o += sz
+        return torch.cat(outs, -1)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelArgs, layer_idx: int, dtype, device):
+        super().__init__()
+        self.cfg, self.layer_idx = cfg, layer_idx
+        d = cfg.head_dim
+        self.qkv_proj = FusedLinear(cfg.hidden_size, ("q_proj", "k_proj", "v_proj"),
+                                    (cfg.q_size, cfg.kv_size, cfg.kv_size), cfg.attention_bias, dtype, device)
+        self.o_proj = FusedLinear(cfg.q_size, ("o_proj",), (cfg.hidden_size,), False, dtype, device)
+        if cfg.qk_norm:
+            self.q_norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
+            self.k_norm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
+        else:
+            self.q_norm = self.k_norm = None
+        self.window = cfg.sliding_window if cfg.uses_sliding_window(layer_idx) else 0
+
+    def forward(self, x_normed, residual, positions, cu_seqlens, seq_start):
+        cfg = self.cfg
+        qkv = self.qkv_proj(x_normed)
+        o = ops.attention_block(qkv, self.q_norm, self.k_norm, positions, cu_seqlens, seq_start,
+                                cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rope_theta,
+                                cfg.rms_norm_eps, cfg.rope_scale, None, self.window, cfg.attn_logit_softcap)
+        return self.o_proj(o, residual)
+
+
+class MLP(nn.Module):
+    def __init__(self, cfg: ModelArgs, inter: int, dtype, device):
+        super().__init__()
+        self.gate_up_proj = FusedLinear(cfg.hidden_size, ("gate_proj", "up_proj"), (inter, inter), cfg.mlp_bias,
+                                        dtype, device)
+        self.down_proj = FusedLinear(inter, ("down_proj",), (cfg.hidden_size,), cfg.mlp_bias, dtype, device)
+
+    def forward(self, x_normed, residual):
+        return self.down_proj(ops.swiglu(self.gate_up_proj(x_normed)), residual)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelArgs, layer_idx: int, dtype, device):
+        super().__init__()
+        self.cfg = cfg
+        self.self_attn = Attention(cfg, layer_idx, dtype, device)
+        if cfg.is_moe_layer(layer_idx):
+            from .moe import SparseMoeBlock
+            self.mlp = SparseMoeBlock(cfg, dtype, device)
+        else:
+            self.mlp = MLP(cfg, cfg.intermediate_size, dtype, device)
+        self.input_layernorm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
+        self.post_attention_layernorm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
+
+    def forward(self, x, pending, positions, cu_seqlens, seq_start):
+        """``pending`` is a branch output not yet added to the residual stream ``x`` (the add is fused
+        into the next RMSNorm). Returns the new (x, pending)."""
+        eps = self.cfg.rms_norm_eps
+        n1, h = ops.add_rms_norm(x, pending, self.input_layernorm, eps)
+        h2 = self.self_attn(n1, h, positions, cu_seqlens, seq_start)     # h + attn(n1)
+        n2, h2 = ops.add_rms_norm(h2, None, self.post_attention_layernorm, eps)
+        out = self.mlp(n2, h2)                                            # h2 + mlp(n2)
+        return out, None
+
+
+class DecoderLM(nn.Module):
+    def __init__(self, cfg: ModelArgs, dtype=torch.float32, device=None):
+        super().__init__()
+        self.cfg = cfg
+        self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
+        self.layers = nn.ModuleList([DecoderLayer(cfg, i, dtype, device) for i in range(cfg.num_hidden_layers)])
+        self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
+        self.lm_head = None if cfg.tie_word_embeddings else nn.Parameter(
+            torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
+        self.head_t: Optional[torch.Tensor] = None
+        self.gradient_checkpointing = 0
+
+    # ------------------------------------------------------------------ init / freeze
+    @torch.no_grad()
+    def init_weights(self, std: float = 0.02, seed: int = 0) -> "DecoderLM":
+        """N(0, std) for every matrix, ones for norms. Drawn on CPU in fp32 in parameter order so the
+        result is identical for any target device/dtype."""
+        g = torch.Generator().manual_seed(seed)
+        for name, p in self.named_parameters():
+            if "lora_" in name:
+                continue
+            if p.dim() >= 2:
+                p.copy_(torch.empty(p.shape, dtype=torch.float32).normal_(0.0, std, generator=g).to(p.dtype))
+            elif name.endswith("bias"):
+                p.zero_()
+            else:
+                p.fill_(1.0)
+        return self
+
+    def freeze_base(self) -> None:
+        for name, p in self.named_parameters():
+            p.requires_grad_("lora_" in name or "magnitude" in name)
+
+    def fused_linears(self):
+        for i, layer in enumerate(self.layers):
+            yield i, "self_attn", layer.self_attn.qkv_proj
+            yield i, "self_attn", layer.self_attn.o_proj
+            if isinstance(layer.mlp, MLP):
+                yield i, "mlp", layer.mlp.gate_up_proj
+                yield i, "mlp", layer.mlp.down_proj
+
+    def prepare_for_training(self) -> None:
+        """Build the transposed copies the input-gradient GEMMs read."""
+        for _, _, fl in self.fused_linears():
+            fl.prepare_transposed()
+        hw = self.head_weight()
+        if hw.is_cuda and not hw.requires_grad:
+            self.head_t = hw.detach().t().contiguous()
+
+    def head_weight(self) -> torch.Tensor:
+        return self.embed_tokens if self.lm_head is None else self.lm_head
+
+    # ------------------------------------------------------------------ forward
+    def forward_hidden(self, input_ids: torch.Tensor, positions: Optional[torch.Tensor] = None,
+                       cu_seqlens: Optional[torch.Tensor] = None, seq_start: Optional[torch.Tensor] = None,
+                       layer_range: Optional[Tuple[int, int]] = None,
+                       hidden_in: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """input_ids [T] (flat packed stream) or [B, L] → final-normed hidden [T, H]."""
+        if input_ids.dim() == 2:
+            B, L = input_ids.shape
+            input_ids = input_ids.reshape(-1)
+            if cu_seqlens is None:
+                cu_seqlens = torch.arange(0, (B + 1) * L, L, dtype=torch.int32, device=input_ids.device)
+            if positions is None:
+                positions = torch.arange(L, device=input_ids.device, dtype=torch.int32).repeat(B)
+        T = input_ids.shape[0]
+        if cu_seqlens is None:
+            cu_seqlens = torch.tensor([0, T], dtype=torch.int32, device=input_ids.device)
+        if positions is None:
+            from ..ops.reference import seq_starts_from_cu
+            ss = seq_start if seq_start is not None else seq_starts_from_cu(cu_seqlens, T)
+            positions = torch.arange(T, device=input_ids.device, dtype=torch.int32) - ss
+        lo, hi = layer_range if layer_range is not None else (0, len(self.layers))
+        x = hidden_in if hidden_in is not None else F.embedding(input_ids, self.embed_tokens)
+        pending = None
+        for i in range(lo, hi):
+            layer = self.layers[i]
+            if self.gradient_checkpointing and self.training and (i % self.gradient_checkpointing == 0):
+                from torch.utils.checkpoint import checkpoint
+                x, pending = checkpoint(layer, x, pending, positions, cu_seqlens, seq_start, use_reentrant=False)
+            else:
+                x, pending = layer(x, pending, positions, cu_seqlens, seq_start)
+        if hi < len(self.layers):
+            return x
+        return ops.rms_norm(x, self.norm, self.cfg.rms_norm_eps)
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        out = F.linear(hidden, self.head_weight())
+        cap = self.cfg.final_logit_softcap
+        return cap * torch.tanh(out / cap) if cap > 0 else out
+
+    def forward(self, input_ids, positions=None, cu_seqlens=None, seq_start=None) -> torch.Tensor:
+        shape = input_ids.shape
+        h = self.forward_hidden(input_ids, positions, cu_seqlens, seq_start)
+        return self.logits(h).view(*shape, -1)
+
+    def loss(self, input_ids: torch.Tensor, labels: torch.Tensor, positions=None, cu_seqlens=None,
+             seq_start=None) -> torch.Tensor:
+        """Causal-LM loss. ``labels`` are unshifted (label[t] is the id at t, −100 = ignore); the shift by
+        one happens here (crates/pmetal-bridge/src/training.rs:120). In a packed stream the caller masks
+        the first token of each non-first document so no prediction crosses a boundary."""
+        h = self.forward_hidden(input_ids, positions, cu_seqlens, seq_start)
+        flat = labels.reshape(-1)
+        if input_ids.dim() == 2:
+            B, L = input_ids.shape
+            tgt = torch.full_like(labels, -100)
+            tgt[:, :-1] = labels[:, 1:]
+            tgt = tgt.reshape(-1)
+        else:
+            tgt = torch.full_like(flat, -100)
+            tgt[:-1] = flat[1:]
+        return ops.causal_lm_loss(h, self.head_weight(), tgt, -100, self.head_t, self.cfg.final_logit_softcap)
+
+    # ------------------------------------------------------------------ checkpoint name mapping
+    def hf_state_dict(self, merged: bool = False) -> Dict[str, torch.Tensor]:
+        sd: Dict[str, torch.Tensor] = {"model.embed_tokens.weight": self.embed_tokens.detach(),
+                                       "model.norm.weight": self.norm.detach()}
+        if self.lm_head is not None:
+            sd["lm_head.weight"] = self.lm_head.detach()
+        for i, layer in enumerate(self.layers):
+            p = f"model.layers.{i}."
+            sd[p + "input_layernorm.weight"] = layer.input_layernorm.detach()
+            sd[p + "post_attention_layernorm.weight"] = layer.post_attention_layernorm.detach()
+            at = layer.self_attn
+            if at.q_norm is not None:
+                sd[p + "self_attn.q_norm.weight"] = at.q_norm.detach()
+                sd[p + "self_attn.k_norm.weight"] = at.k_norm.detach()
+            groups = [("self_attn.", at.qkv_proj), ("self_attn.", at.o_proj)]
+            if isinstance(layer.mlp, MLP):
+                groups += [("mlp.", layer.mlp.gate_up_proj), ("mlp.", layer.mlp.down_proj)]
+            else:
+                sd.update({p + "mlp." + k: v for k, v in layer.mlp.hf_state_dict().items()})
+            for pre, fl in groups:
+                w = fl.merged_weight().to(fl.weight.dtype) if merged else fl.weight.detach()
+                o = 0
+                for nm, sz in zip(fl.seg_names, fl.seg_sizes):
+                    sd[p + pre + nm + ".weight"] = w[o:o + sz]
+                    if fl.bias is not None:
+                        sd[p + pre + nm + ".bias"] = fl.bias.detach()[o:o + sz]
+                    o += sz
+        return sd
+
+    @torch.no_grad()
+    def load_hf_state_dict(self, sd: Dict[str, torch.Tensor], strict: bool = True) -> List[str]:
+        """Copy tensors named like a Hugging Face checkpoint into the fused layout. Returns unused keys."""
+        used = set()
+
+        def take(name, dst):
+            if name not in sd:
+                if strict:
+                    raise KeyError(f"missing weight {name}")
+                return
+            dst.copy_(sd[name].to(dst.dtype))
+            used.add(name)
+
+        take("model.embed_tokens.weight", self.embed_tokens)
+        take("model.norm.weight", self.norm)
+        if self.lm_head is not None:
+            if "lm_head.weight" in sd:
+                take("lm_head.weight", self.lm_head)
+            else:
+                self.lm_head.copy_(self.embed_tokens)
+        for i, layer in enumerate(self.layers):
+            p = f"model.layers.{i}."
+            take(p + "input_layernorm.weight", layer.input_layernorm)
+            take(p + "post_attention_layernorm.weight", layer.post_attention_layernorm)
+            at = layer.self_attn
+            if at.q_norm is not None:
+                take(p + "self_attn.q_norm.weight", at.q_norm)
+                take(p + "self_attn.k_norm.weight", at.k_norm)
+            groups = [("self_attn.", at.qkv_proj), ("self_attn.", at.o_proj)]
+            if isinstance(layer.mlp, MLP):
+                groups += [("mlp.", layer.mlp.gate_up_proj), ("mlp.", layer.mlp.down_proj)]
+            else:
+                used |= layer.mlp.load_hf_state_dict(sd, p + "mlp.", strict)
+            for pre, fl in groups:
+                o = 0
+                for nm, sz in zip(fl.seg_names, fl.seg_sizes):
+                    take(p + pre + nm + ".weight", fl.weight[o:o + sz])
+                    if fl.bias is not None:
+                        take(p + pre + nm + ".bias", fl.bias[o:o + sz])
+                    o += sz
+        return [k for k in sd if k not in used]
+
+    def num_parameters(self, trainable_only: bool = False) -> int:
+        return sum(p.numel() for p in self.parameters() if p.requires_grad or not trainable_only)

@@ -1,0 +1,247 @@
+"""Differentiable operators used by the models.
+
+Each function runs the hand-written sm_100a kernel (``ops.native``) when its inputs
+live on a CUDA device and falls back to the PyTorch statement in ``ops.reference``
+on CPU. A CUDA tensor with the native library missing raises instead of silently
+taking the slow path, unless ``PMETAL_ALLOW_TORCH_FALLBACK=1`` is set.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import reference as ref
+
+_FORCE_REF = os.environ.get("PMETAL_FORCE_REFERENCE", "0") == "1"
+
+
+def _native():
+    from . import native
+    return native
+
+
+def use_native(t: torch.Tensor) -> bool:
+    if _FORCE_REF or not t.is_cuda:
+        return False
+    nat = _native()
+    if nat.available():
+        return t.dtype == torch.bfloat16
+    if os.environ.get("PMETAL_ALLOW_TORCH_FALLBACK", "0") == "1":
+        return False
+    raise RuntimeError("pmetal_b200 native CUDA library is not built/loaded; run __graft_entry__.build() "
+                       f"({nat.load_error()})")
+
+
+# --------------------------------------------------------------------------- RMSNorm (+ residual add)
+class _RmsNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps, residual):
+        nat = _native()
+        h, y, rstd = nat.rmsnorm_fwd(x, weight, eps, residual)
+        ctx.save_for_backward(h, weight, rstd)
+        ctx.has_res = residual is not None
+        ctx.w_grad = weight.requires_grad
+        ctx.mark_non_differentiable(rstd)
+        return y, h
+
+    @staticmethod
+    def backward(ctx, dy, dh):
+        h, weight, rstd = ctx.saved_tensors
+        nat = _native()
+        dx, dw = nat.rmsnorm_bwd(dy.contiguous(), h, weight, rstd, dh, ctx.w_grad)
+        return dx, dw, None, (dx if ctx.has_res else None)
+
+
+def add_rms_norm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, eps: float):
+    """h = x + residual (or x); returns (rms_norm(h)·w, h)."""
+    if use_native(x):
+        y, h = _RmsNormFn.apply(x, weight, eps, residual)
+        return y, h
+    h = x if residual is None else x + residual
+    return ref.rms_norm(h, weight, eps), h
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    return add_rms_norm(x, None, weight, eps)[0]
+
+
+# --------------------------------------------------------------------------- SwiGLU
+class _SwigluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate_up):
+        ctx.save_for_backward(gate_up)
+        return _native().swiglu_fwd(gate_up)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gate_up,) = ctx.saved_tensors
+        return _native().swiglu_bwd(dout.contiguous(), gate_up)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    if use_native(gate_up):
+        return _SwigluFn.apply(gate_up)
+    return ref.swiglu(gate_up)
+
+
+# --------------------------------------------------------------------------- attention block
+class _AttnBlockFn(torch.autograd.Function):
+    """fused projection [T,(hq+2hkv)·d] → per-head RMSNorm(q,k) → RoPE → varlen causal attention → [T,hq·d].
+
+    Backward writes dv straight into the v slice of the fused gradient, so the
+    gradient of the fused projection is assembled without a zero-fill or a concat.
+    """
+
+    @staticmethod
+    def forward(ctx, qkv, qw, kw, positions, seq_start, hq, hkv, d, theta, eps, rope_scale, scale, window):
+        nat = _native()
+        q, k = nat.qknorm_rope_fwd(qkv, qw, kw, positions, hq, hkv, d, theta, eps, rope_scale)
+        T = qkv.shape[0]
+        v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        o, lse = nat.attn_fwd(q, k, v, seq_start, scale, window)
+        ctx.save_for_backward(qkv, qw, kw, positions, seq_start, q, k, o, lse)
+        ctx.cfg = (hq, hkv, d, theta, eps, rope_scale, scale, window)
+        return o.view(T, hq * d)
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, qw, kw, positions, seq_start, q, k, o, lse = ctx.saved_tensors
+        hq, hkv, d, theta, eps, rope_scale, scale, window = ctx.cfg
+        nat = _native()
+        T = qkv.shape[0]
+        dqkv = torch.empty_like(qkv)
+        v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        dv = dqkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        dq, dk = nat.attn_bwd(do.contiguous().view(T, hq, d), q, k, v, o, lse, seq_start, scale, window, dv)
+        nat.qknorm_rope_bwd(dq, dk, qkv, qw, kw, positions, hq, hkv, d, theta, eps, rope_scale, dqkv)
+        return (dqkv,) + (None,) * 12
+
+
+def attention_block(qkv: torch.Tensor, q_weight, k_weight, positions: torch.Tensor, cu_seqlens: torch.Tensor,
+                    seq_start: Optional[torch.Tensor], hq: int, hkv: int, d: int, theta: float, eps: float,
+                    rope_scale: float = 1.0, scale: Optional[float] = None, window: int = 0,
+                    softcap: float = 0.0) -> torch.Tensor:
+    """Packed-sequence self-attention on a fused q|k|v projection. Returns [T, hq·d]."""
+    T = qkv.shape[0]
+    scale = scale if scale is not None else d ** -0.5
+    if use_native(qkv) and d == 128 and softcap == 0.0:
+        if seq_start is None:
+            seq_start = ref.seq_starts_from_cu(cu_seqlens, T)
+        return _AttnBlockFn.apply(qkv, q_weight, k_weight, positions, seq_start, hq, hkv, d, theta, eps, rope_scale,
+                                  scale, window)
+    q = qkv[:, :hq * d].view(T, hq, d)
+    k = qkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+    q, k = ref.qk_norm_rope(q, k, q_weight, k_weight, positions, theta, eps, rope_scale)
+    return ref.varlen_attention(q, k, v, cu_seqlens, scale, True, window, softcap).reshape(T, hq * d)
+
+
+# --------------------------------------------------------------------------- fused base + LoRA linear
+class _LoraLinearFn(torch.autograd.Function):
+    """y = x Wᵀ + Σ_seg s·(x A_segᵀ) B_segᵀ over a row-stacked group of projections.
+
+    ``a`` is [n_seg·r, K] (segments stacked), ``b`` is [N, r] (rows stacked), both in
+    the compute dtype; gradients for them are returned in fp32.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w, w_t, a32, b32, a, b, seg_sizes, r, scale, residual):
+        # a32/b32 are the fp32 parameters (autograd edges only); a/b are their bf16 compute copies.
+        nat = _native()
+        t = None
+        if a is not None:
+            t = nat.gemm(x, a, alpha=scale)                       # [M, n_seg·r] = s·x Aᵀ
+        y = nat.gemm_lora(x, w, t, b, seg_sizes, r, residual)
+        ctx.save_for_backward(x, w, w_t, a, b, t)
+        ctx.cfg = (seg_sizes, r, scale, residual is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, w_t, a, b, t = ctx.saved_tensors
+        seg_sizes, r, scale, has_res = ctx.cfg
+        nat = _native()
+        dy = dy.contiguous()
+        da = db = dx = None
+        if a is not None:
+            dt = nat.lora_dt(dy, b, seg_sizes, r, scale)          # [M, n_seg·r] = s·dY_seg B_seg
+            if ctx.needs_input_grad[0]:
+                dx = nat.gemm_lora_dx(dy, w, w_t, dt, a)
+            da = nat.gemm_tn_f32(dt, x)                           # [n_seg·r, K]
+            db = nat.lora_db(dy, t, seg_sizes, r)                 # [N, r]
+        elif ctx.needs_input_grad[0]:
+            dx = nat.gemm_lora_dx(dy, w, w_t, None, None)
+        return dx, None, None, da, db, None, None, None, None, None, (dy if has_res else None)
+
+
+def lora_linear(x: torch.Tensor, w: torch.Tensor, w_t: Optional[torch.Tensor], a: Optional[torch.Tensor],
+                b: Optional[torch.Tensor], seg_sizes: Sequence[int], r: int, scale: float,
+                residual: Optional[torch.Tensor] = None, a_c: Optional[torch.Tensor] = None,
+                b_c: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if use_native(x):
+        if a is not None:
+            a_c = a_c if a_c is not None else a.detach().to(torch.bfloat16)
+            b_c = b_c if b_c is not None else b.detach().to(torch.bfloat16)
+        return _LoraLinearFn.apply(x, w, w_t, a, b, a_c, b_c, tuple(seg_sizes), r, scale, residual)
+    y = F.linear(x, w)
+    if a is not None:
+        outs, n0 = [], 0
+        for i, n in enumerate(seg_sizes):
+            t = F.linear(x, a[i * r:(i + 1) * r].to(x.dtype))
+            outs.append(scale * F.linear(t, b[n0:n0 + n].to(x.dtype)))
+            n0 += n
+        y = y + torch.cat(outs, dim=-1)
+    if residual is not None:
+        y = y + residual
+    return y
+
+
+# --------------------------------------------------------------------------- linear + cross-entropy
+class _LinearCeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, weight_t, labels, ignore_index, chunk):
+        loss_sum, n_valid, dh = _native().linear_ce(hidden, weight, weight_t, labels, ignore_index, chunk,
+                                                    hidden.requires_grad)
+        ctx.save_for_backward(dh)
+        ctx.mark_non_differentiable(n_valid)
+        return loss_sum, n_valid
+
+    @staticmethod
+    def backward(ctx, dloss, _dn):
+        (dh,) = ctx.saved_tensors
+        return (dh * dloss.to(dh.dtype)) if dh is not None else None, None, None, None, None, None
+
+
+def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
+                         chunk: int = 4096, weight_t: Optional[torch.Tensor] = None, softcap: float = 0.0):
+    """Returns (Σ loss over valid tokens, number of valid tokens). The head weight is treated as frozen on
+    the native path (LoRA fine-tuning); full fine-tuning of the head uses the reference path."""
+    if use_native(hidden) and softcap == 0.0 and not weight.requires_grad:
+        return _LinearCeFn.apply(hidden, weight, weight_t, labels, ignore_index, chunk)
+    return ref.linear_cross_entropy(hidden, weight, labels, ignore_index, chunk, softcap)
+
+
+def causal_lm_loss(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
+                   weight_t: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
+    """Mean over non-ignored tokens; ``labels`` must already be shifted/aligned with ``hidden``."""
+    s, n = linear_cross_entropy(hidden, weight, labels, ignore_index, weight_t=weight_t, softcap=softcap)
+    return s / n.clamp(min=1).to(s.dtype)
+
+
+# --------------------------------------------------------------------------- grouped expert MLP
+def grouped_mlp(xs: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    """Rows of ``xs`` are grouped by expert (``offsets`` [E+1]); returns down_e(swiglu(gate_up_e(x))) per row."""
+    if use_native(xs) and not gate_up.requires_grad and not torch.is_grad_enabled():
+        nat = _native()
+        h = nat.grouped_gemm(xs, gate_up, offsets)
+        return nat.grouped_gemm(nat.swiglu_fwd(h), down, offsets)
+    out = torch.empty(xs.shape[0], down.shape[1], dtype=xs.dtype, device=xs.device)
+    off = offsets.tolist()
+    for e in range(gate_up.shape[0]):
+        s, t = off[e], off[e + 1]
+        if t > s:
+            out[s:t] = F.linear(ref.swiglu(F.linear(xs[s:t], gate_up[e])), down[e])
+    return out
