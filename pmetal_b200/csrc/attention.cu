@@ -1,0 +1,626 @@
+// Varlen (packed-sequence) causal flash attention, forward and backward, head_dim 128, GQA.
+//
+// The token stream is a concatenation of documents; `seq_start[t]` is the index of the first
+// token of the document that token t belongs to. Query i may attend key j iff
+// seq_start[i] <= j <= i (and i - j < window when a sliding window is set), i.e. a
+// block-diagonal causal mask that is never materialised. The reference has a varlen forward
+// only (flash_attention_varlen_forward_d128, crates/pmetal-metal/src/kernels/metal/
+// flash_attention.metal:1093-1130) and falls back to a dense [T,T] mask for packed training;
+// here forward, dQ and dK/dV all work from the boundaries.
+//
+// Tiles are 64 queries x 64 keys, 4 warps per CTA, mma.sync.m16n8k16 bf16 with fp32 accumulation,
+// online softmax in base 2, K/V (or Q/dO) tiles double-buffered with cp.async, shared memory rows
+// XOR-swizzled in 16-byte chunks. The backward is two kernels, both deterministic:
+//   dQ  : one CTA per (query tile, head), loops over key tiles (recomputes S and dP)
+//   dKV : one CTA per (key tile, kv head), loops over the query heads of the group and query tiles
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pm {
+
+constexpr int kD = 128;     // head dim
+constexpr int kTile = 64;   // rows per tile (queries or keys)
+constexpr int kAttnThreads = 128;
+constexpr int kTileBytes = kTile * kD * 2;   // 16 KB
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// byte offset of element (row, col) in a swizzled [rows][128] bf16 tile
+__device__ __forceinline__ uint32_t sw_off(int row, int col) {
+  return static_cast<uint32_t>(row * 256 + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1)));
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copy a [64][128] bf16 tile (rows row0.., clamped to < T) from a strided global tensor into swizzled smem.
+__device__ __forceinline__ void load_tile(uint8_t* smem_tile, const __nv_bfloat16* base, long long row_stride, int row0,
+                                          int T) {
+  const uint32_t sbase = smem_addr(smem_tile);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int idx = threadIdx.x + i * kAttnThreads;   // 0..1023
+    const int r = idx >> 4, c = idx & 15;
+    int gr = row0 + r;
+    gr = gr < T ? gr : T - 1;
+    cp_async16(sbase + r * 256 + ((c ^ (r & 7)) << 4), base + static_cast<long long>(gr) * row_stride + c * 8);
+  }
+}
+
+// A-operand fragments (16 rows x 16 k) of a row-major swizzled tile: rows r0.., k columns k0..
+__device__ __forceinline__ void load_a_frag(uint32_t tile, int r0, int k0, int lane, uint32_t (&a)[4]) {
+  const int row = r0 + (lane & 15), col = k0 + ((lane >> 4) << 3);
+  ldsm_x4(tile + sw_off(row, col), a[0], a[1], a[2], a[3]);
+}
+// B-operand fragments for C = A * X^T where X is a row-major tile [n][k]: two n-tiles (n0, n0+8), k0..k0+15.
+__device__ __forceinline__ void load_b_frag_nt(uint32_t tile, int n0, int k0, int lane, uint32_t (&b)[4]) {
+  const int id = lane >> 3, r = lane & 7;
+  const int row = n0 + ((id >> 1) << 3) + r, col = k0 + ((id & 1) << 3);
+  ldsm_x4(tile + sw_off(row, col), b[0], b[1], b[2], b[3]);
+}
+// B-operand fragments for C = A * X where X is a row-major tile [k][n]: two n-tiles (n0, n0+8), k0..k0+15.
+__device__ __forceinline__ void load_b_frag_nn(uint32_t tile, int k0, int n0, int lane, uint32_t (&b)[4]) {
+  const int id = lane >> 3, r = lane & 7;
+  const int row = k0 + ((id & 1) << 3) + r, col = n0 + ((id >> 1) << 3);
+  ldsm_x4_t(tile + sw_off(row, col), b[0], b[1], b[2], b[3]);
+}
+
+struct AttnParams {
+  const __nv_bfloat16 *q, *k, *v, *o, *dout;
+  __nv_bfloat16 *out, *dq, *dk, *dv;
+  long long q_stride, k_stride, v_stride, o_stride, dq_stride, dk_stride, dv_stride;   // per-token strides (elements)
+  const int* seq_start;
+  float* lse;          // [Hq][T], natural log
+  const float* delta;  // [Hq][T]
+  int T, hq, hkv;
+  float scale;
+  int window;
+};
+
+// ================================================================================= forward
+__global__ void __launch_bounds__(kAttnThreads) attn_fwd_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + kTileBytes;               // 2 buffers
+  uint8_t* sV = smem + 3 * kTileBytes;           // 2 buffers
+  int* sStart = reinterpret_cast<int*>(smem + 5 * kTileBytes);
+
+  const int qt = gridDim.x - 1 - blockIdx.x;     // longest (latest) tiles first
+  const int h = blockIdx.y;
+  const int hk = h / (p.hq / p.hkv);
+  const int q0 = qt * kTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  if (threadIdx.x < kTile) {
+    const int i = q0 + threadIdx.x;
+    sStart[threadIdx.x] = p.seq_start[i < p.T ? i : p.T - 1];
+  }
+  const int first_start = p.seq_start[q0];
+  int kv_lo = first_start;
+  if (p.window > 0) kv_lo = max(kv_lo, q0 - p.window + 1);
+  kv_lo = (kv_lo / kTile) * kTile;
+  const int kv_hi = min(q0 + kTile, p.T);
+  const int n_tiles = (kv_hi - kv_lo + kTile - 1) / kTile;
+
+  const __nv_bfloat16* qb = p.q + static_cast<long long>(h) * kD;
+  const __nv_bfloat16* kb = p.k + static_cast<long long>(hk) * kD;
+  const __nv_bfloat16* vb = p.v + static_cast<long long>(hk) * kD;
+
+  load_tile(sQ, qb, p.q_stride, q0, p.T);
+  load_tile(sK, kb, p.k_stride, kv_lo, p.T);
+  load_tile(sV, vb, p.v_stride, kv_lo, p.T);
+  cp_async_commit();
+
+  float o_acc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float sl2 = p.scale * kLog2e;
+  const uint32_t q_tile = smem_addr(sQ);
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int buf = it & 1;
+    const int j0 = kv_lo + it * kTile;
+    if (it + 1 < n_tiles) {
+      load_tile(sK + (buf ^ 1) * kTileBytes, kb, p.k_stride, j0 + kTile, p.T);
+      load_tile(sV + (buf ^ 1) * kTileBytes, vb, p.v_stride, j0 + kTile, p.T);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t k_tile = smem_addr(sK + buf * kTileBytes);
+    const uint32_t v_tile = smem_addr(sV + buf * kTileBytes);
+
+    // S = Q K^T  (16 x 64 per warp)
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      uint32_t a[4];
+      load_a_frag(q_tile, warp * 16, kk * 16, lane, a);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b[4];
+        load_b_frag_nt(k_tile, np * 16, kk * 16, lane, b);
+        mma_bf16(s[2 * np], a[0], a[1], a[2], a[3], b[0], b[1]);
+        mma_bf16(s[2 * np + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
+      }
+    }
+    // mask + online softmax. Thread holds rows r0 = warp*16+g and r0+8, columns nt*8 + 2*t4 + {0,1}.
+    const int r_lo = warp * 16 + g;
+    const int i_lo = q0 + r_lo, i_hi = i_lo + 8;
+    const int st_lo = sStart[r_lo], st_hi = sStart[r_lo + 8];
+    const bool need_mask = (j0 + kTile - 1 > q0) || (j0 < sStart[kTile - 1]) ||
+                           (p.window > 0 && j0 < q0 + kTile - p.window);
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = s[nt][e] * sl2;
+        if (need_mask) {
+          const int j = j0 + nt * 8 + 2 * t4 + (e & 1);
+          const int i = (e < 2) ? i_lo : i_hi;
+          const int st = (e < 2) ? st_lo : st_hi;
+          bool ok = (j <= i) && (j >= st);
+          if (p.window > 0) ok = ok && (i - j < p.window);
+          if (!ok) v = -INFINITY;
+        }
+        s[nt][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+      corr[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_use[r]);
+      m_run[r] = m_new;
+      l_run[r] *= corr[r];
+    }
+    float rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = exp2f(s[nt][e] - m_use[e >> 1]);
+        s[nt][e] = pv;
+        rs[e >> 1] += pv;
+      }
+    }
+    l_run[0] += rs[0];
+    l_run[1] += rs[1];
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      o_acc[nt][0] *= corr[0];
+      o_acc[nt][1] *= corr[0];
+      o_acc[nt][2] *= corr[1];
+      o_acc[nt][3] *= corr[1];
+    }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const uint32_t a0 = pack2(s[2 * kk][0], s[2 * kk][1]);
+      const uint32_t a1 = pack2(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t a2 = pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      const uint32_t a3 = pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        uint32_t b[4];
+        load_b_frag_nn(v_tile, kk * 16, np * 16, lane, b);
+        mma_bf16(o_acc[2 * np], a0, a1, a2, a3, b[0], b[1]);
+        mma_bf16(o_acc[2 * np + 1], a0, a1, a2, a3, b[2], b[3]);
+      }
+    }
+    __syncthreads();   // all warps done with this K/V buffer before it is refilled
+  }
+
+  // finalise: divide by the row sum, write O and LSE
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  const int r_lo = warp * 16 + g;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int i = q0 + r_lo + r * 8;
+    if (i >= p.T) continue;
+    const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+    __nv_bfloat16* orow = p.out + static_cast<long long>(i) * p.o_stride + static_cast<long long>(h) * kD;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      *reinterpret_cast<uint32_t*>(orow + nt * 8 + 2 * t4) =
+          pack2(o_acc[nt][2 * r] * inv, o_acc[nt][2 * r + 1] * inv);
+    }
+    if (t4 == 0) p.lse[static_cast<long long>(h) * p.T + i] = (m_run[r] + log2f(l_run[r])) / kLog2e;
+  }
+}
+
+// ================================================================================= backward: dQ
+// Same tiling as the forward. P = exp2(S*scale*log2e - lse*log2e); dP = dO V^T; dS = P (dP - delta) scale;
+// dQ = sum_j dS K.
+__global__ void __launch_bounds__(kAttnThreads) attn_bwd_dq_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sdO = smem + kTileBytes;
+  uint8_t* sK = smem + 2 * kTileBytes;   // 2 buffers
+  uint8_t* sV = smem + 4 * kTileBytes;   // 2 buffers
+  int* sStart = reinterpret_cast<int*>(smem + 6 * kTileBytes);
+
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y;
+  const int hk = h / (p.hq / p.hkv);
+  const int q0 = qt * kTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  if (threadIdx.x < kTile) {
+    const int i = q0 + threadIdx.x;
+    sStart[threadIdx.x] = p.seq_start[i < p.T ? i : p.T - 1];
+  }
+  int kv_lo = p.seq_start[q0];
+  if (p.window > 0) kv_lo = max(kv_lo, q0 - p.window + 1);
+  kv_lo = (kv_lo / kTile) * kTile;
+  const int kv_hi = min(q0 + kTile, p.T);
+  const int n_tiles = (kv_hi - kv_lo + kTile - 1) / kTile;
+
+  const __nv_bfloat16* kb = p.k + static_cast<long long>(hk) * kD;
+  const __nv_bfloat16* vb = p.v + static_cast<long long>(hk) * kD;
+  load_tile(sQ, p.q + static_cast<long long>(h) * kD, p.q_stride, q0, p.T);
+  load_tile(sdO, p.dout + static_cast<long long>(h) * kD, p.o_stride, q0, p.T);
+  load_tile(sK, kb, p.k_stride, kv_lo, p.T);
+  load_tile(sV, vb, p.v_stride, kv_lo, p.T);
+  cp_async_commit();
+
+  const int r_lo = warp * 16 + g;
+  const int i_lo = q0 + r_lo, i_hi = i_lo + 8;
+  const int ic_lo = min(i_lo, p.T - 1), ic_hi = min(i_hi, p.T - 1);
+  const float lse2[2] = {p.lse[static_cast<long long>(h) * p.T + ic_lo] * kLog2e,
+                         p.lse[static_cast<long long>(h) * p.T + ic_hi] * kLog2e};
+  const float dl[2] = {p.delta[static_cast<long long>(h) * p.T + ic_lo],
+                       p.delta[static_cast<long long>(h) * p.T + ic_hi]};
+  const float sl2 = p.scale * kLog2e;
+
+  float dq_acc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dq_acc[i][j] = 0.f;
+  const uint32_t q_tile = smem_addr(sQ), do_tile = smem_addr(sdO);
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int buf = it & 1;
+    const int j0 = kv_lo + it * kTile;
+    if (it + 1 < n_tiles) {
+      load_tile(sK + (buf ^ 1) * kTileBytes, kb, p.k_stride, j0 + kTile, p.T);
+      load_tile(sV + (buf ^ 1) * kTileBytes, vb, p.v_stride, j0 + kTile, p.T);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t k_tile = smem_addr(sK + buf * kTileBytes);
+    const uint32_t v_tile = smem_addr(sV + buf * kTileBytes);
+
+    float s[8][4], dp[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { s[i][j] = 0.f; dp[i][j] = 0.f; }
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      uint32_t a[4], ad[4];
+      load_a_frag(q_tile, warp * 16, kk * 16, lane, a);
+      load_a_frag(do_tile, warp * 16, kk * 16, lane, ad);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b[4];
+        load_b_frag_nt(k_tile, np * 16, kk * 16, lane, b);
+        mma_bf16(s[2 * np], a[0], a[1], a[2], a[3], b[0], b[1]);
+        mma_bf16(s[2 * np + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
+        load_b_frag_nt(v_tile, np * 16, kk * 16, lane, b);
+        mma_bf16(dp[2 * np], ad[0], ad[1], ad[2], ad[3], b[0], b[1]);
+        mma_bf16(dp[2 * np + 1], ad[0], ad[1], ad[2], ad[3], b[2], b[3]);
+      }
+    }
+    const int st_lo = sStart[r_lo], st_hi = sStart[r_lo + 8];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + nt * 8 + 2 * t4 + (e & 1);
+        const int i = (e < 2) ? i_lo : i_hi;
+        const int st = (e < 2) ? st_lo : st_hi;
+        bool ok = (j <= i) && (j >= st) && (i < p.T);
+        if (p.window > 0) ok = ok && (i - j < p.window);
+        const float pv = ok ? exp2f(s[nt][e] * sl2 - lse2[e >> 1]) : 0.f;
+        s[nt][e] = pv * (dp[nt][e] - dl[e >> 1]) * p.scale;   // dS
+      }
+    }
+    // dQ += dS K
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const uint32_t a0 = pack2(s[2 * kk][0], s[2 * kk][1]);
+      const uint32_t a1 = pack2(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t a2 = pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      const uint32_t a3 = pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        uint32_t b[4];
+        load_b_frag_nn(k_tile, kk * 16, np * 16, lane, b);
+        mma_bf16(dq_acc[2 * np], a0, a1, a2, a3, b[0], b[1]);
+        mma_bf16(dq_acc[2 * np + 1], a0, a1, a2, a3, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int i = q0 + r_lo + r * 8;
+    if (i >= p.T) continue;
+    __nv_bfloat16* drow = p.dq + static_cast<long long>(i) * p.dq_stride + static_cast<long long>(h) * kD;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+      *reinterpret_cast<uint32_t*>(drow + nt * 8 + 2 * t4) = pack2(dq_acc[nt][2 * r], dq_acc[nt][2 * r + 1]);
+  }
+}
+
+// ================================================================================= backward: dK, dV
+// One CTA per (key tile, kv head). Works on the transposed score tile S^T = K Q^T so that each warp owns
+// 16 key rows and accumulates dV += P^T dO and dK += dS^T Q in registers over every query tile that can
+// see these keys and every query head of the GQA group.
+__global__ void __launch_bounds__(kAttnThreads) attn_bwd_dkv_kernel(const AttnParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + kTileBytes;
+  uint8_t* sQ = smem + 2 * kTileBytes;    // 2 buffers
+  uint8_t* sdO = smem + 4 * kTileBytes;   // 2 buffers
+  float* sLse = reinterpret_cast<float*>(smem + 6 * kTileBytes);   // [2][64]
+  float* sDelta = sLse + 2 * kTile;                                 // [2][64]
+  int* sStart = reinterpret_cast<int*>(sDelta + 2 * kTile);         // [2][64]
+
+  const int jt = blockIdx.x;
+  const int hk = blockIdx.y;
+  const int rep = p.hq / p.hkv;
+  const int j0 = jt * kTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int j_last = min(j0 + kTile, p.T) - 1;
+
+  // query tiles m0 = j0, j0+64, ... while the tile's first row belongs to a document that started at or
+  // before the last key of this tile (later tiles cannot see these keys)
+  int n_q_tiles = 0;
+  for (bool done = false; !done;) {
+    const int m0 = j0 + (n_q_tiles + lane) * kTile;
+    bool ok = m0 < p.T;
+    if (ok) ok = p.seq_start[m0] <= j_last && !(p.window > 0 && m0 - j_last >= p.window);
+    const unsigned b = __ballot_sync(0xffffffffu, ok);
+    const int cnt = (b == 0xffffffffu) ? 32 : (__ffs(~b) - 1);
+    n_q_tiles += cnt;
+    done = cnt < 32;
+  }
+  const int total = n_q_tiles * rep;
+
+  load_tile(sK, p.k + static_cast<long long>(hk) * kD, p.k_stride, j0, p.T);
+  load_tile(sV, p.v + static_cast<long long>(hk) * kD, p.v_stride, j0, p.T);
+
+  auto issue = [&](int w, int buf) {
+    const int hh = hk * rep + (w / n_q_tiles);
+    const int m0 = j0 + (w % n_q_tiles) * kTile;
+    load_tile(sQ + buf * kTileBytes, p.q + static_cast<long long>(hh) * kD, p.q_stride, m0, p.T);
+    load_tile(sdO + buf * kTileBytes, p.dout + static_cast<long long>(hh) * kD, p.o_stride, m0, p.T);
+    if (threadIdx.x < kTile) {
+      const int i = min(m0 + static_cast<int>(threadIdx.x), p.T - 1);
+      sLse[buf * kTile + threadIdx.x] = p.lse[static_cast<long long>(hh) * p.T + i] * kLog2e;
+      sDelta[buf * kTile + threadIdx.x] = p.delta[static_cast<long long>(hh) * p.T + i];
+      sStart[buf * kTile + threadIdx.x] = p.seq_start[i];
+    }
+  };
+  if (total > 0) issue(0, 0);
+  cp_async_commit();
+
+  float dk_acc[16][4], dv_acc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { dk_acc[i][j] = 0.f; dv_acc[i][j] = 0.f; }
+  const float sl2 = p.scale * kLog2e;
+  const uint32_t k_tile = smem_addr(sK), v_tile = smem_addr(sV);
+  const int jr_lo = j0 + warp * 16 + g, jr_hi = jr_lo + 8;   // key rows owned by this thread
+
+  for (int w = 0; w < total; ++w) {
+    const int buf = w & 1;
+    const int m0 = j0 + (w % n_q_tiles) * kTile;
+    if (w + 1 < total) {
+      issue(w + 1, buf ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t q_tile = smem_addr(sQ + buf * kTileBytes);
+    const uint32_t do_tile = smem_addr(sdO + buf * kTileBytes);
+    const float* lse2 = sLse + buf * kTile;
+    const float* dl = sDelta + buf * kTile;
+    const int* st = sStart + buf * kTile;
+
+    // S^T = K Q^T and dP^T = V dO^T  (16 keys x 64 queries per warp)
+    float s[8][4], dp[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { s[i][j] = 0.f; dp[i][j] = 0.f; }
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+      uint32_t a[4], av[4];
+      load_a_frag(k_tile, warp * 16, kk * 16, lane, a);
+      load_a_frag(v_tile, warp * 16, kk * 16, lane, av);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b[4];
+        load_b_frag_nt(q_tile, np * 16, kk * 16, lane, b);
+        mma_bf16(s[2 * np], a[0], a[1], a[2], a[3], b[0], b[1]);
+        mma_bf16(s[2 * np + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
+        load_b_frag_nt(do_tile, np * 16, kk * 16, lane, b);
+        mma_bf16(dp[2 * np], av[0], av[1], av[2], av[3], b[0], b[1]);
+        mma_bf16(dp[2 * np + 1], av[0], av[1], av[2], av[3], b[2], b[3]);
+      }
+    }
+    // element (key row, query col): P^T and dS^T
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int c = nt * 8 + 2 * t4 + (e & 1);   // query index within tile
+        const int i = m0 + c;
+        const int j = (e < 2) ? jr_lo : jr_hi;
+        bool ok = (j <= i) && (j >= st[c]) && (i < p.T);
+        if (p.window > 0) ok = ok && (i - j < p.window);
+        const float pv = ok ? exp2f(s[nt][e] * sl2 - lse2[c]) : 0.f;
+        s[nt][e] = pv;                                           // P^T
+        dp[nt][e] = pv * (dp[nt][e] - dl[c]) * p.scale;          // dS^T
+      }
+    }
+    // dV += P^T dO ; dK += dS^T Q   (reduction over the 64 queries)
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const uint32_t pa0 = pack2(s[2 * kk][0], s[2 * kk][1]);
+      const uint32_t pa1 = pack2(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t pa2 = pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      const uint32_t pa3 = pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      const uint32_t sa0 = pack2(dp[2 * kk][0], dp[2 * kk][1]);
+      const uint32_t sa1 = pack2(dp[2 * kk][2], dp[2 * kk][3]);
+      const uint32_t sa2 = pack2(dp[2 * kk + 1][0], dp[2 * kk + 1][1]);
+      const uint32_t sa3 = pack2(dp[2 * kk + 1][2], dp[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < 8; ++np) {
+        uint32_t b[4];
+        load_b_frag_nn(do_tile, kk * 16, np * 16, lane, b);
+        mma_bf16(dv_acc[2 * np], pa0, pa1, pa2, pa3, b[0], b[1]);
+        mma_bf16(dv_acc[2 * np + 1], pa0, pa1, pa2, pa3, b[2], b[3]);
+        load_b_frag_nn(q_tile, kk * 16, np * 16, lane, b);
+        mma_bf16(dk_acc[2 * np], sa0, sa1, sa2, sa3, b[0], b[1]);
+        mma_bf16(dk_acc[2 * np + 1], sa0, sa1, sa2, sa3, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  if (total == 0) cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int j = j0 + warp * 16 + g + r * 8;
+    if (j >= p.T) continue;
+    __nv_bfloat16* krow = p.dk + static_cast<long long>(j) * p.dk_stride + static_cast<long long>(hk) * kD;
+    __nv_bfloat16* vrow = p.dv + static_cast<long long>(j) * p.dv_stride + static_cast<long long>(hk) * kD;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      *reinterpret_cast<uint32_t*>(krow + nt * 8 + 2 * t4) = pack2(dk_acc[nt][2 * r], dk_acc[nt][2 * r + 1]);
+      *reinterpret_cast<uint32_t*>(vrow + nt * 8 + 2 * t4) = pack2(dv_acc[nt][2 * r], dv_acc[nt][2 * r + 1]);
+    }
+  }
+}
+
+}  // namespace pm
+
+using namespace pm;
+
+static int set_smem(const void* fn, int bytes) {
+  return static_cast<int>(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+}
+
+// q:[T,hq,128] k:[T,hkv,128] v:[T,hkv,128] with per-token strides; out:[T,hq,128]; lse:[hq,T]
+extern "C" int pm_attn_fwd(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
+                           long long v_stride, void* out, long long o_stride, float* lse, const int* seq_start, int T,
+                           int hq, int hkv, float scale, int window, cudaStream_t st) {
+  if (hq % hkv || T <= 0) return -1;
+  if ((q_stride | k_stride | v_stride | o_stride) % 8) return -2;
+  AttnParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q); p.k = static_cast<const __nv_bfloat16*>(k);
+  p.v = static_cast<const __nv_bfloat16*>(v); p.out = static_cast<__nv_bfloat16*>(out);
+  p.q_stride = q_stride; p.k_stride = k_stride; p.v_stride = v_stride; p.o_stride = o_stride;
+  p.seq_start = seq_start; p.lse = lse; p.T = T; p.hq = hq; p.hkv = hkv; p.scale = scale; p.window = window;
+  const int smem = 5 * kTileBytes + 256;
+  static bool once = false;
+  if (!once) { int e = set_smem(reinterpret_cast<const void*>(attn_fwd_kernel), smem); if (e) return e; once = true; }
+  dim3 grid((T + kTile - 1) / kTile, hq);
+  attn_fwd_kernel<<<grid, kAttnThreads, smem, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dq:[T,hq,128] dk,dv:[T,hkv,128] (strided). delta:[hq,T] = rowsum(dO*O) computed beforehand.
+extern "C" int pm_attn_bwd(const void* dout, const void* q, long long q_stride, const void* k, long long k_stride,
+                           const void* v, long long v_stride, long long o_stride, const float* lse, const float* delta,
+                           void* dq, long long dq_stride, void* dk, long long dk_stride, void* dv, long long dv_stride,
+                           const int* seq_start, int T, int hq, int hkv, float scale, int window, cudaStream_t st) {
+  if (hq % hkv || T <= 0) return -1;
+  if ((q_stride | k_stride | v_stride | o_stride | dq_stride | dk_stride | dv_stride) % 8) return -2;
+  AttnParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q); p.k = static_cast<const __nv_bfloat16*>(k);
+  p.v = static_cast<const __nv_bfloat16*>(v); p.dout = static_cast<const __nv_bfloat16*>(dout);
+  p.dq = static_cast<__nv_bfloat16*>(dq); p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.q_stride = q_stride; p.k_stride = k_stride; p.v_stride = v_stride; p.o_stride = o_stride;
+  p.dq_stride = dq_stride; p.dk_stride = dk_stride; p.dv_stride = dv_stride;
+  p.seq_start = seq_start; p.lse = const_cast<float*>(lse); p.delta = delta;
+  p.T = T; p.hq = hq; p.hkv = hkv; p.scale = scale; p.window = window;
+  const int smem_dq = 6 * kTileBytes + 256;
+  const int smem_dkv = 6 * kTileBytes + 6 * kTile * 4;
+  static bool once = false;
+  if (!once) {
+    int e = set_smem(reinterpret_cast<const void*>(attn_bwd_dq_kernel), smem_dq);
+    if (e) return e;
+    e = set_smem(reinterpret_cast<const void*>(attn_bwd_dkv_kernel), smem_dkv);
+    if (e) return e;
+    once = true;
+  }
+  dim3 gq((T + kTile - 1) / kTile, hq);
+  attn_bwd_dq_kernel<<<gq, kAttnThreads, smem_dq, st>>>(p);
+  int e = static_cast<int>(cudaGetLastError());
+  if (e) return e;
+  dim3 gk((T + kTile - 1) / kTile, hkv);
+  attn_bwd_dkv_kernel<<<gk, kAttnThreads, smem_dkv, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,573 @@
+// Bandwidth-bound fused kernels: RMSNorm (+residual add) fwd/bwd, per-head QK-RMSNorm + RoPE
+// fwd/bwd, SwiGLU fwd/bwd, softmax-cross-entropy over a logits chunk (loss + gradient in place),
+// sum of squares, and the flat multi-tensor AdamW update with global-norm clipping.
+//
+// They restate the reference's Metal kernels for sm_100a: fused_norm_lora.metal (RMSNorm),
+// fused_rope.metal (rope_qk_with_positions), fused_swiglu.metal, fused_cross_entropy.metal and
+// fused_training.metal (fused_adamw_update_bias_corrected, gradient_norm_squared_partial),
+// all under crates/pmetal-metal/src/kernels/metal/.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pm {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const bf16x8 t = *reinterpret_cast<const bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 a = __bfloat1622float2(t.v[i]);
+    f[2 * i] = a.x;
+    f[2 * i + 1] = a.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  bf16x8 t;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) t.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<bf16x8*>(p) = t;
+}
+
+// ------------------------------------------------------------------------------------ RMSNorm
+// One warp per row. h = x (+ res); y = h * rsqrt(mean(h^2) + eps) * w. H % 8 == 0.
+__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                   __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd, int T, int H,
+                                   float eps) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= T) return;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
+  const __nv_bfloat16* rr = res ? res + static_cast<size_t>(row) * H : nullptr;
+  __nv_bfloat16* hr = h_out ? h_out + static_cast<size_t>(row) * H : nullptr;
+  float ss = 0.f;
+  for (int c = lane * 8; c < H; c += 256) {
+    float f[8];
+    load8(xr + c, f);
+    if (rr) {
+      float g[8];
+      load8(rr + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] += g[i];
+      // the residual stream is kept in bf16: round before use so that y matches norm(h_out)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(__float2bfloat16(f[i]));
+      store8(hr + c, f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = warp_sum(ss);
+  const float rs = rsqrtf(ss / H + eps);
+  if (lane == 0) rstd[row] = rs;
+  const __nv_bfloat16* src = rr ? hr : xr;
+  __nv_bfloat16* yr = y + static_cast<size_t>(row) * H;
+  for (int c = lane * 8; c < H; c += 256) {
+    float f[8], g[8];
+    load8(src + c, f);
+    load8(w + c, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * rs * g[i];
+    store8(yr + c, f);
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dh_add);  optional dw += sum_rows dy * xhat
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                                   const __nv_bfloat16* __restrict__ dh_add, __nv_bfloat16* __restrict__ dx,
+                                   float* __restrict__ dw, int T, int H) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= T) return;
+  const size_t off = static_cast<size_t>(row) * H;
+  const float rs = rstd[row];
+  float dot = 0.f;
+  for (int c = lane * 8; c < H; c += 256) {
+    float a[8], b[8], g[8];
+    load8(dy + off + c, a);
+    load8(h + off + c, b);
+    load8(w + c, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dot += a[i] * g[i] * b[i] * rs;
+  }
+  dot = warp_sum(dot) / H;
+  for (int c = lane * 8; c < H; c += 256) {
+    float a[8], b[8], g[8], o[8];
+    load8(dy + off + c, a);
+    load8(h + off + c, b);
+    load8(w + c, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = rs * (a[i] * g[i] - b[i] * rs * dot);
+    if (dh_add) {
+      float e[8];
+      load8(dh_add + off + c, e);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] += e[i];
+    }
+    store8(dx + off + c, o);
+    if (dw) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(dw + c + i, a[i] * b[i] * rs);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------ RoPE table
+__global__ void rope_table_kernel(const int* __restrict__ pos, float* __restrict__ cs, float* __restrict__ sn, int T,
+                                  int half, float theta, float inv_scale) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * half) return;
+  const int t = i / half, j = i - t * half;
+  const float inv_freq = powf(theta, -static_cast<float>(j) / half) * inv_scale;
+  float s, c;
+  sincosf(static_cast<float>(pos[t]) * inv_freq, &s, &c);
+  cs[i] = c;
+  sn[i] = s;
+}
+
+// ------------------------------------------------------------------------------------ QK-norm + RoPE (D = 128)
+// One warp per (token, head). Lane l owns elements {4l..4l+3} of the vector: the first 16 lanes hold
+// the first half (j < 64), the last 16 the second half; rotation partners are exchanged by shuffle.
+__global__ void qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, int ld,
+                                       const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+                                       const float* __restrict__ cs, const float* __restrict__ sn,
+                                       __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out, int T,
+                                       int hq, int hkv, float eps) {
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = hq + hkv;
+  if (gw >= T * heads) return;
+  const int t = gw / heads, hh = gw - t * heads;
+  const bool is_q = hh < hq;
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ld + hh * 128 + lane * 4;
+  const __nv_bfloat16* wv = is_q ? qw : kw;
+  const uint2 raw = *reinterpret_cast<const uint2*>(src);
+  float x[4];
+  {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  }
+  if (wv) {
+    float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / 128.f + eps);
+    const uint2 wr = *reinterpret_cast<const uint2*>(wv + lane * 4);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wr.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wr.y));
+    x[0] *= rs * a.x; x[1] *= rs * a.y; x[2] *= rs * b.x; x[3] *= rs * b.y;
+  }
+  const int j = (lane & 15) * 4;
+  const float4 c = *reinterpret_cast<const float4*>(cs + static_cast<size_t>(t) * 64 + j);
+  const float4 s = *reinterpret_cast<const float4*>(sn + static_cast<size_t>(t) * 64 + j);
+  const float cc[4] = {c.x, c.y, c.z, c.w}, ssn[4] = {s.x, s.y, s.z, s.w};
+  float o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float partner = __shfl_xor_sync(0xffffffffu, x[i], 16);
+    // first half: x1*c - x2*s ; second half: x2*c + x1*s
+    o[i] = (lane < 16) ? (x[i] * cc[i] - partner * ssn[i]) : (x[i] * cc[i] + partner * ssn[i]);
+  }
+  __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(t) * hq + hh) * 128 + lane * 4
+                            : k_out + (static_cast<size_t>(t) * hkv + (hh - hq)) * 128 + lane * 4;
+  uint2 ov;
+  *reinterpret_cast<__nv_bfloat162*>(&ov.x) = __floats2bfloat162_rn(o[0], o[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&ov.y) = __floats2bfloat162_rn(o[2], o[3]);
+  *reinterpret_cast<uint2*>(dst) = ov;
+}
+
+__global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
+                                       const __nv_bfloat16* __restrict__ qkv, int ld,
+                                       const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+                                       const float* __restrict__ cs, const float* __restrict__ sn,
+                                       __nv_bfloat16* __restrict__ dqkv, int T, int hq, int hkv, float eps) {
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = hq + hkv;
+  if (gw >= T * heads) return;
+  const int t = gw / heads, hh = gw - t * heads;
+  const bool is_q = hh < hq;
+  const __nv_bfloat16* gsrc = is_q ? dq + (static_cast<size_t>(t) * hq + hh) * 128 + lane * 4
+                                   : dk + (static_cast<size_t>(t) * hkv + (hh - hq)) * 128 + lane * 4;
+  const uint2 graw = *reinterpret_cast<const uint2*>(gsrc);
+  float g[4];
+  {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&graw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&graw.y));
+    g[0] = a.x; g[1] = a.y; g[2] = b.x; g[3] = b.y;
+  }
+  const int j = (lane & 15) * 4;
+  const float4 c = *reinterpret_cast<const float4*>(cs + static_cast<size_t>(t) * 64 + j);
+  const float4 s = *reinterpret_cast<const float4*>(sn + static_cast<size_t>(t) * 64 + j);
+  const float cc[4] = {c.x, c.y, c.z, c.w}, ssn[4] = {s.x, s.y, s.z, s.w};
+  float dn[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float partner = __shfl_xor_sync(0xffffffffu, g[i], 16);
+    // transpose of the rotation: dn1 = dy1*c + dy2*s ; dn2 = dy2*c - dy1*s
+    dn[i] = (lane < 16) ? (g[i] * cc[i] + partner * ssn[i]) : (g[i] * cc[i] - partner * ssn[i]);
+  }
+  const size_t off = static_cast<size_t>(t) * ld + hh * 128 + lane * 4;
+  const __nv_bfloat16* wv = is_q ? qw : kw;
+  float o[4];
+  if (wv) {
+    const uint2 xr = *reinterpret_cast<const uint2*>(qkv + off);
+    const uint2 wr = *reinterpret_cast<const uint2*>(wv + lane * 4);
+    float x[4], w4[4];
+    {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xr.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xr.y));
+      x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+      const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wr.x));
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wr.y));
+      w4[0] = e.x; w4[1] = e.y; w4[2] = f.x; w4[3] = f.y;
+    }
+    float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / 128.f + eps);
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dot += dn[i] * w4[i] * x[i] * rs;
+    dot = warp_sum(dot) / 128.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = rs * (dn[i] * w4[i] - x[i] * rs * dot);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = dn[i];
+  }
+  uint2 ov;
+  *reinterpret_cast<__nv_bfloat162*>(&ov.x) = __floats2bfloat162_rn(o[0], o[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&ov.y) = __floats2bfloat162_rn(o[2], o[3]);
+  *reinterpret_cast<uint2*>(dqkv + off) = ov;
+}
+
+// ------------------------------------------------------------------------------------ SwiGLU
+// gate_up [T, 2I] (gate | up) -> out [T, I]
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long T,
+                                  int I) {
+  const long long n8 = T * (I / 8);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / (I / 8);
+    const int c = static_cast<int>(i - t * (I / 8)) * 8;
+    float g[8], u[8], o[8];
+    load8(gu + t * 2 * I + c, g);
+    load8(gu + t * 2 * I + I + c, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+    store8(out + t * I + c, o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gu,
+                                  __nv_bfloat16* __restrict__ dgu, long long T, int I) {
+  const long long n8 = T * (I / 8);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / (I / 8);
+    const int c = static_cast<int>(i - t * (I / 8)) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + t * 2 * I + c, g);
+    load8(gu + t * 2 * I + I + c, u);
+    load8(dout + t * I + c, d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float sg = 1.f / (1.f + __expf(-g[k]));
+      dg[k] = d[k] * u[k] * sg * (1.f + g[k] * (1.f - sg));
+      du[k] = d[k] * g[k] * sg;
+    }
+    store8(dgu + t * 2 * I + c, dg);
+    store8(dgu + t * 2 * I + I + c, du);
+  }
+}
+
+// ------------------------------------------------------------------------------------ cross-entropy on a logits chunk
+// One block per row. logits (bf16, [n, ldl]) are replaced in place by d(loss_sum)/dlogits * grad_scale,
+// where grad_scale = *inv_n (1 / number of valid tokens of the whole batch). Adds the row's
+// loss (lse - logit[label]) to loss_sum. Rows whose label is ignore_index get a zero gradient.
+__global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ labels,
+                                  float* __restrict__ loss_sum, const float* __restrict__ inv_n, int V,
+                                  long long ignore_index, int write_grad) {
+  __shared__ float red[32];
+  __shared__ float bcast[2];
+  const int row = blockIdx.x;
+  __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ldl;
+  const long long label = labels[row];
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  const int V8 = V & ~7;
+  if (label == ignore_index || label < 0 || label >= V) {
+    if (write_grad) {
+      const bf16x8 z = {};
+      for (int c = tid * 8; c < V8; c += nthr * 8) *reinterpret_cast<bf16x8*>(lr + c) = z;
+      for (int c = V8 + tid; c < V; c += nthr) lr[c] = __float2bfloat16(0.f);
+    }
+    return;
+  }
+  // pass 1: online max / sum-exp
+  float m = -INFINITY, s = 0.f;
+  for (int c = tid * 8; c < V8; c += nthr * 8) {
+    float f[8];
+    load8(lr + c, f);
+    float lm = f[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) lm = fmaxf(lm, f[i]);
+    if (lm > m) { s *= __expf(m - lm); m = lm; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += __expf(f[i] - m);
+  }
+  for (int c = V8 + tid; c < V; c += nthr) {
+    const float f = __bfloat162float(lr[c]);
+    if (f > m) { s *= __expf(m - f); m = f; }
+    s += __expf(f - m);
+  }
+  // block reduce (m, s)
+  const float wm = warp_max(m);
+  s = (m == -INFINITY) ? 0.f : s * __expf(m - wm);
+  s = warp_sum(s);
+  if ((tid & 31) == 0) { red[tid >> 5] = wm; }
+  __syncthreads();
+  float bm = -INFINITY;
+  const int nw = nthr >> 5;
+  for (int i = 0; i < nw; ++i) bm = fmaxf(bm, red[i]);
+  __syncthreads();
+  s = (wm == -INFINITY) ? 0.f : s * __expf(wm - bm);
+  if ((tid & 31) == 0) red[tid >> 5] = s;
+  __syncthreads();
+  if (tid == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < nw; ++i) tot += red[i];
+    const float lse = bm + logf(tot);
+    bcast[0] = lse;
+    atomicAdd(loss_sum, lse - __bfloat162float(lr[label]));
+  }
+  __syncthreads();
+  if (!write_grad) return;
+  const float lse = bcast[0];
+  const float gs = *inv_n;
+  for (int c = tid * 8; c < V8; c += nthr * 8) {
+    float f[8];
+    load8(lr + c, f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = (__expf(f[i] - lse) - ((c + i) == label ? 1.f : 0.f)) * gs;
+    store8(lr + c, f);
+  }
+  for (int c = V8 + tid; c < V; c += nthr) {
+    const float f = __bfloat162float(lr[c]);
+    lr[c] = __float2bfloat16((__expf(f - lse) - (c == label ? 1.f : 0.f)) * gs);
+  }
+}
+
+// ------------------------------------------------------------------------------------ sum of squares
+__global__ void sumsq_kernel(const float* __restrict__ x, long long n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float acc = 0.f;
+  const long long n4 = n >> 2;
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 v = x4[i];
+    acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (long long i = n4 << 2; i < n; ++i) acc += x[i] * x[i];
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) atomicAdd(out, v);
+  }
+}
+
+// ------------------------------------------------------------------------------------ flat AdamW
+// Reference semantics (crates/pmetal-bridge/src/optimizer.rs:295-336): bias-corrected step, then
+// decoupled decay applied to the updated parameter. Per-1024-element chunk lr multiplier and decay.
+// gnorm_sq holds the squared global norm of the *unscaled* gradient buffer.
+struct AdamwArgs {
+  float lr, beta1, beta2, eps, bc1, bc2, grad_scale, max_norm;
+};
+__global__ void adamw_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                                  float* __restrict__ v, __nv_bfloat16* __restrict__ shadow,
+                                  const float* __restrict__ lr_mult, const float* __restrict__ wd,
+                                  const float* __restrict__ gnorm_sq, long long n, AdamwArgs a) {
+  float coef = a.grad_scale;
+  if (a.max_norm > 0.f) {
+    const float norm = sqrtf(*gnorm_sq) * a.grad_scale;
+    coef *= fminf(1.f, a.max_norm / (norm + 1e-6f));
+  }
+  for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 4; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x * 4) {
+    const int chunk = static_cast<int>(i >> 10);
+    const float lr = a.lr * lr_mult[chunk];
+    const float decay = wd[chunk] * lr;
+    const float4 g4 = *reinterpret_cast<const float4*>(g + i);
+    float4 m4 = *reinterpret_cast<float4*>(m + i);
+    float4 v4 = *reinterpret_cast<float4*>(v + i);
+    float4 p4 = *reinterpret_cast<float4*>(p + i);
+    float gg[4] = {g4.x * coef, g4.y * coef, g4.z * coef, g4.w * coef};
+    float mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w}, pp[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      mm[k] = a.beta1 * mm[k] + (1.f - a.beta1) * gg[k];
+      vv[k] = a.beta2 * vv[k] + (1.f - a.beta2) * gg[k] * gg[k];
+      const float mh = mm[k] / a.bc1, vh = vv[k] / a.bc2;
+      pp[k] -= lr * mh / (sqrtf(vh) + a.eps);
+      pp[k] -= decay * pp[k];
+    }
+    *reinterpret_cast<float4*>(m + i) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    *reinterpret_cast<float4*>(p + i) = make_float4(pp[0], pp[1], pp[2], pp[3]);
+    if (shadow) {
+      uint2 o;
+      *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(pp[0], pp[1]);
+      *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(pp[2], pp[3]);
+      *reinterpret_cast<uint2*>(shadow + i) = o;
+    }
+  }
+}
+
+// rowsum(dO * O) per (token, head): the delta term of the attention backward. One warp per row of 128.
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                  float* __restrict__ delta, int T, int H) {
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (gw >= T * H) return;
+  const int t = gw / H, h = gw - t * H;
+  const size_t off = static_cast<size_t>(gw) * 128 + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(o + off);
+  const uint2 b = *reinterpret_cast<const uint2*>(dout + off);
+  const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+  const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+  const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.x));
+  const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.y));
+  float s = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+  s = warp_sum(s);
+  if (lane == 0) delta[static_cast<size_t>(h) * T + t] = s;
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long n) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    out[i] = __float2bfloat16(in[i]);
+}
+
+}  // namespace pm
+
+using namespace pm;
+
+static inline int grid_for(long long work, int per_block, int cap = 148 * 16) {
+  long long g = (work + per_block - 1) / per_block;
+  if (g < 1) g = 1;
+  return static_cast<int>(g > cap ? cap : g);
+}
+#define PM_LAUNCH_CHECK() static_cast<int>(cudaGetLastError())
+
+extern "C" int pm_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd, int T,
+                              int H, float eps, cudaStream_t st) {
+  if (H % 8) return -1;
+  rmsnorm_fwd_kernel<<<(T + 7) / 8, 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
+      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(h_out), rstd, T,
+      H, eps);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dh_add,
+                              void* dx, float* dw, int T, int H, cudaStream_t st) {
+  if (H % 8) return -1;
+  rmsnorm_bwd_kernel<<<(T + 7) / 8, 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(h),
+      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dh_add),
+      static_cast<__nv_bfloat16*>(dx), dw, T, H);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_rope_table(const int* pos, float* cs, float* sn, int T, int half, float theta, float rope_scale,
+                             cudaStream_t st) {
+  const long long n = static_cast<long long>(T) * half;
+  rope_table_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, st>>>(pos, cs, sn, T, half, theta, 1.f / rope_scale);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_qknorm_rope_fwd(const void* qkv, int ld, const void* qw, const void* kw, const float* cs,
+                                  const float* sn, void* q_out, void* k_out, int T, int hq, int hkv, float eps,
+                                  cudaStream_t st) {
+  const long long warps = static_cast<long long>(T) * (hq + hkv);
+  qknorm_rope_fwd_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(qkv), ld, static_cast<const __nv_bfloat16*>(qw),
+      static_cast<const __nv_bfloat16*>(kw), cs, sn, static_cast<__nv_bfloat16*>(q_out),
+      static_cast<__nv_bfloat16*>(k_out), T, hq, hkv, eps);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_qknorm_rope_bwd(const void* dq, const void* dk, const void* qkv, int ld, const void* qw,
+                                  const void* kw, const float* cs, const float* sn, void* dqkv, int T, int hq, int hkv,
+                                  float eps, cudaStream_t st) {
+  const long long warps = static_cast<long long>(T) * (hq + hkv);
+  qknorm_rope_bwd_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(dq), static_cast<const __nv_bfloat16*>(dk),
+      static_cast<const __nv_bfloat16*>(qkv), ld, static_cast<const __nv_bfloat16*>(qw),
+      static_cast<const __nv_bfloat16*>(kw), cs, sn, static_cast<__nv_bfloat16*>(dqkv), T, hq, hkv, eps);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_swiglu_fwd(const void* gu, void* out, long long T, int I, cudaStream_t st) {
+  if (I % 8) return -1;
+  swiglu_fwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gu),
+                                                               static_cast<__nv_bfloat16*>(out), T, I);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_swiglu_bwd(const void* dout, const void* gu, void* dgu, long long T, int I, cudaStream_t st) {
+  if (I % 8) return -1;
+  swiglu_bwd_kernel<<<grid_for(T * (I / 8), 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(dgu),
+      T, I);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_ce_fwd_bwd(void* logits, long long ldl, const long long* labels, float* loss_sum, const float* inv_n,
+                             int n_rows, int V, long long ignore_index, int write_grad, cudaStream_t st) {
+  if (ldl % 8) return -1;
+  ce_fwd_bwd_kernel<<<n_rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ldl, labels, loss_sum, inv_n, V,
+                                             ignore_index, write_grad);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_sumsq(const float* x, long long n, float* out, cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(out, 0, sizeof(float), st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  sumsq_kernel<<<grid_for(n / 4 + 1, 256, 148 * 4), 256, 0, st>>>(x, n, out);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_adamw_flat(float* p, const float* g, float* m, float* v, void* shadow, const float* lr_mult,
+                             const float* wd, const float* gnorm_sq, long long n, float lr, float beta1, float beta2,
+                             float eps, int step, float grad_scale, float max_norm, cudaStream_t st) {
+  if (n % 1024) return -1;
+  AdamwArgs a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps;
+  a.bc1 = 1.f - powf(beta1, static_cast<float>(step));
+  a.bc2 = 1.f - powf(beta2, static_cast<float>(step));
+  a.grad_scale = grad_scale; a.max_norm = max_norm;
+  adamw_flat_kernel<<<grid_for(n / 4, 256, 148 * 8), 256, 0, st>>>(p, g, m, v, static_cast<__nv_bfloat16*>(shadow),
+                                                                  lr_mult, wd, gnorm_sq, n, a);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_attn_delta(const void* o, const void* dout, float* delta, int T, int H, cudaStream_t st) {
+  const long long warps = static_cast<long long>(T) * H;
+  attn_delta_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), delta, T, H);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_f32_to_bf16(const float* in, void* out, long long n, cudaStream_t st) {
+  f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, st>>>(in, static_cast<__nv_bfloat16*>(out), n);
+  return PM_LAUNCH_CHECK();
+}

@@ -135,12 +135,12 @@ class Attention(nn.Module):
             self.q_norm = self.k_norm = None
         self.window = cfg.sliding_window if cfg.uses_sliding_window(layer_idx) else 0
 
-    def forward(self, x_normed, residual, positions, cu_seqlens, seq_start):
+    def forward(self, x_normed, residual, rope, cu_seqlens, seq_start):
         cfg = self.cfg
         qkv = self.qkv_proj(x_normed)
-        o = ops.attention_block(qkv, self.q_norm, self.k_norm, positions, cu_seqlens, seq_start,
-                                cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rope_theta,
-                                cfg.rms_norm_eps, cfg.rope_scale, None, self.window, cfg.attn_logit_softcap)
+        o = ops.attention_block(qkv, self.q_norm, self.k_norm, rope[0], rope[1], cu_seqlens, seq_start,
+                                cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps,
+                                None, self.window, cfg.attn_logit_softcap)
         return self.o_proj(o, residual)
 
 
@@ -168,15 +168,14 @@ class DecoderLayer(nn.Module):
         self.input_layernorm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
         self.post_attention_layernorm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
 
-    def forward(self, x, pending, positions, cu_seqlens, seq_start):
-        """``pending`` is a branch output not yet added to the residual stream ``x`` (the add is fused
-        into the next RMSNorm). Returns the new (x, pending)."""
+    def forward(self, x, rope, cu_seqlens, seq_start):
+        """x -> x + attn(norm(x)) -> (+ mlp(norm(.))). The residual adds run in the epilogue of the
+        o_proj / down_proj GEMMs."""
         eps = self.cfg.rms_norm_eps
-        n1, h = ops.add_rms_norm(x, pending, self.input_layernorm, eps)
-        h2 = self.self_attn(n1, h, positions, cu_seqlens, seq_start)     # h + attn(n1)
-        n2, h2 = ops.add_rms_norm(h2, None, self.post_attention_layernorm, eps)
-        out = self.mlp(n2, h2)                                            # h2 + mlp(n2)
-        return out, None
+        n1 = ops.rms_norm(x, self.input_layernorm, eps)
+        h = self.self_attn(n1, x, rope, cu_seqlens, seq_start)
+        n2 = ops.rms_norm(h, self.post_attention_layernorm, eps)
+        return self.mlp(n2, h)
 
 
 class DecoderLM(nn.Module):
@@ -253,14 +252,14 @@ class DecoderLM(nn.Module):
             positions = torch.arange(T, device=input_ids.device, dtype=torch.int32) - ss
         lo, hi = layer_range if layer_range is not None else (0, len(self.layers))
         x = hidden_in if hidden_in is not None else F.embedding(input_ids, self.embed_tokens)
-        pending = None
+        rope = ops.rope_table(positions, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scale)
         for i in range(lo, hi):
             layer = self.layers[i]
             if self.gradient_checkpointing and self.training and (i % self.gradient_checkpointing == 0):
                 from torch.utils.checkpoint import checkpoint
-                x, pending = checkpoint(layer, x, pending, positions, cu_seqlens, seq_start, use_reentrant=False)
+                x = checkpoint(layer, x, rope, cu_seqlens, seq_start, use_reentrant=False)
             else:
-                x, pending = layer(x, pending, positions, cu_seqlens, seq_start)
+                x = layer(x, rope, cu_seqlens, seq_start)
         if hi < len(self.layers):
             return x
         return ops.rms_norm(x, self.norm, self.cfg.rms_norm_eps)

@@ -23,6 +23,19 @@ def _native():
     return native
 
 
+class force_reference:
+    """Context manager: run every op through the PyTorch reference path (tests, debugging)."""
+
+    def __enter__(self):
+        global _FORCE_REF
+        self._old = _FORCE_REF
+        _FORCE_REF = True
+
+    def __exit__(self, *a):
+        global _FORCE_REF
+        _FORCE_REF = self._old
+
+
 def use_native(t: torch.Tensor) -> bool:
     if _FORCE_REF or not t.is_cuda:
         return False
@@ -88,90 +101,106 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------- attention block
+def rope_table(positions: torch.Tensor, head_dim: int, theta: float, rope_scale: float = 1.0):
+    """cos/sin [T, head_dim/2] in fp32 for the positions of this batch (shared by every layer)."""
+    if positions.is_cuda and not _FORCE_REF and _native().available():
+        return _native().rope_table(positions, head_dim, theta, rope_scale)
+    return ref.rope_cos_sin(positions, head_dim, theta, rope_scale)
+
+
 class _AttnBlockFn(torch.autograd.Function):
-    """fused projection [T,(hq+2hkv)·d] → per-head RMSNorm(q,k) → RoPE → varlen causal attention → [T,hq·d].
+    """fused projection [T,(hq+2hkv)*d] -> per-head RMSNorm(q,k) -> RoPE -> varlen causal attention -> [T,hq*d].
 
     Backward writes dv straight into the v slice of the fused gradient, so the
     gradient of the fused projection is assembled without a zero-fill or a concat.
     """
 
     @staticmethod
-    def forward(ctx, qkv, qw, kw, positions, seq_start, hq, hkv, d, theta, eps, rope_scale, scale, window):
+    def forward(ctx, qkv, qw, kw, cos, sin, seq_start, hq, hkv, d, eps, scale, window):
         nat = _native()
-        q, k = nat.qknorm_rope_fwd(qkv, qw, kw, positions, hq, hkv, d, theta, eps, rope_scale)
+        q, k = nat.qknorm_rope_fwd(qkv, qw, kw, cos, sin, hq, hkv, eps)
         T = qkv.shape[0]
         v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
         o, lse = nat.attn_fwd(q, k, v, seq_start, scale, window)
-        ctx.save_for_backward(qkv, qw, kw, positions, seq_start, q, k, o, lse)
-        ctx.cfg = (hq, hkv, d, theta, eps, rope_scale, scale, window)
+        ctx.save_for_backward(qkv, qw, kw, cos, sin, seq_start, q, k, o, lse)
+        ctx.cfg = (hq, hkv, d, eps, scale, window)
         return o.view(T, hq * d)
 
     @staticmethod
     def backward(ctx, do):
-        qkv, qw, kw, positions, seq_start, q, k, o, lse = ctx.saved_tensors
-        hq, hkv, d, theta, eps, rope_scale, scale, window = ctx.cfg
+        qkv, qw, kw, cos, sin, seq_start, q, k, o, lse = ctx.saved_tensors
+        hq, hkv, d, eps, scale, window = ctx.cfg
         nat = _native()
         T = qkv.shape[0]
         dqkv = torch.empty_like(qkv)
         v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
         dv = dqkv[:, (hq + hkv) * d:].view(T, hkv, d)
         dq, dk = nat.attn_bwd(do.contiguous().view(T, hq, d), q, k, v, o, lse, seq_start, scale, window, dv)
-        nat.qknorm_rope_bwd(dq, dk, qkv, qw, kw, positions, hq, hkv, d, theta, eps, rope_scale, dqkv)
-        return (dqkv,) + (None,) * 12
+        nat.qknorm_rope_bwd(dq, dk, qkv, qw, kw, cos, sin, hq, hkv, eps, dqkv)
+        return (dqkv,) + (None,) * 11
 
 
-def attention_block(qkv: torch.Tensor, q_weight, k_weight, positions: torch.Tensor, cu_seqlens: torch.Tensor,
-                    seq_start: Optional[torch.Tensor], hq: int, hkv: int, d: int, theta: float, eps: float,
-                    rope_scale: float = 1.0, scale: Optional[float] = None, window: int = 0,
-                    softcap: float = 0.0) -> torch.Tensor:
-    """Packed-sequence self-attention on a fused q|k|v projection. Returns [T, hq·d]."""
+def attention_block(qkv: torch.Tensor, q_weight, k_weight, cos: torch.Tensor, sin: torch.Tensor,
+                    cu_seqlens: torch.Tensor, seq_start: Optional[torch.Tensor], hq: int, hkv: int, d: int,
+                    eps: float, scale: Optional[float] = None, window: int = 0, softcap: float = 0.0) -> torch.Tensor:
+    """Packed-sequence self-attention on a fused q|k|v projection. Returns [T, hq*d]."""
     T = qkv.shape[0]
     scale = scale if scale is not None else d ** -0.5
     if use_native(qkv) and d == 128 and softcap == 0.0:
         if seq_start is None:
             seq_start = ref.seq_starts_from_cu(cu_seqlens, T)
-        return _AttnBlockFn.apply(qkv, q_weight, k_weight, positions, seq_start, hq, hkv, d, theta, eps, rope_scale,
-                                  scale, window)
+        return _AttnBlockFn.apply(qkv, q_weight, k_weight, cos, sin, seq_start, hq, hkv, d, eps, scale, window)
     q = qkv[:, :hq * d].view(T, hq, d)
     k = qkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d)
     v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
-    q, k = ref.qk_norm_rope(q, k, q_weight, k_weight, positions, theta, eps, rope_scale)
+    if q_weight is not None:
+        q, k = ref.rms_norm(q, q_weight, eps), ref.rms_norm(k, k_weight, eps)
+    q, k = ref.apply_rope(q, cos, sin), ref.apply_rope(k, cos, sin)
     return ref.varlen_attention(q, k, v, cu_seqlens, scale, True, window, softcap).reshape(T, hq * d)
 
 
 # --------------------------------------------------------------------------- fused base + LoRA linear
 class _LoraLinearFn(torch.autograd.Function):
-    """y = x Wᵀ + Σ_seg s·(x A_segᵀ) B_segᵀ over a row-stacked group of projections.
+    """y = x W^T + sum_seg s (x A_seg^T) B_seg^T over a row-stacked group of projections (+ residual).
 
-    ``a`` is [n_seg·r, K] (segments stacked), ``b`` is [N, r] (rows stacked), both in
-    the compute dtype; gradients for them are returned in fp32.
+    ``a32``/``b32`` are the fp32 parameters (autograd edges); ``a``/``b`` their bf16 compute copies,
+    ``a`` stacked [n_seg*r, K] and ``b`` stacked [N, r]. Factor gradients are accumulated in fp32
+    straight into ``.grad`` when that buffer already exists (the flat optimizer pre-binds it).
     """
 
     @staticmethod
     def forward(ctx, x, w, w_t, a32, b32, a, b, seg_sizes, r, scale, residual):
-        # a32/b32 are the fp32 parameters (autograd edges only); a/b are their bf16 compute copies.
         nat = _native()
-        t = None
-        if a is not None:
-            t = nat.gemm(x, a, alpha=scale)                       # [M, n_seg·r] = s·x Aᵀ
+        t = nat.lora_t(x, a, scale) if a is not None else None    # [M, 64-padded] = s x A^T
         y = nat.gemm_lora(x, w, t, b, seg_sizes, r, residual)
         ctx.save_for_backward(x, w, w_t, a, b, t)
+        ctx.params = (a32, b32)
         ctx.cfg = (seg_sizes, r, scale, residual is not None)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, w, w_t, a, b, t = ctx.saved_tensors
+        a32, b32 = ctx.params
         seg_sizes, r, scale, has_res = ctx.cfg
         nat = _native()
         dy = dy.contiguous()
         da = db = dx = None
         if a is not None:
-            dt = nat.lora_dt(dy, b, seg_sizes, r, scale)          # [M, n_seg·r] = s·dY_seg B_seg
+            dt = nat.lora_dt(dy, b, seg_sizes, r, scale)          # [M, 64-padded] = s dY_seg B_seg
             if ctx.needs_input_grad[0]:
                 dx = nat.gemm_lora_dx(dy, w, w_t, dt, a)
-            da = nat.gemm_tn_f32(dt, x)                           # [n_seg·r, K]
-            db = nat.lora_db(dy, t, seg_sizes, r)                 # [N, r]
+
+            def target(p32):
+                g = p32.grad
+                if g is not None and g.dtype == torch.float32 and g.is_contiguous():
+                    return g, None
+                z = torch.zeros(p32.shape, dtype=torch.float32, device=p32.device)
+                return z, z
+            ga, da = target(a32)
+            gb, db = target(b32)
+            nat.lora_da(dt, x, a.shape[0], ga)
+            nat.lora_db(dy, t, seg_sizes, r, gb)
         elif ctx.needs_input_grad[0]:
             dx = nat.gemm_lora_dx(dy, w, w_t, None, None)
         return dx, None, None, da, db, None, None, None, None, None, (dy if has_res else None)

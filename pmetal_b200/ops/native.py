@@ -1,0 +1,369 @@
+"""ctypes bindings for the sm_100a kernel library (``pmetal_b200/lib/libpmetal_b200.so``).
+
+The library is plain CUDA C++ with ``extern "C"`` launchers that take raw device
+pointers and a stream; tensors are allocated here with PyTorch and every launch
+goes to PyTorch's current stream, so the kernels compose with autograd, CUDA graphs
+and NCCL streams. Launchers return 0 or an error code, which is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+_LIB = None
+_ERR: Optional[str] = None
+_STATUS = {}
+LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libpmetal_b200.so")
+
+# The transposed LoRA products read token-major tensors through MN-major tcgen05 descriptors.
+# PMETAL_MN_MAJOR=0 routes them through explicit transposes instead.
+MN_MAJOR = os.environ.get("PMETAL_MN_MAJOR", "1") == "1"
+LAUNCHES = 0   # number of kernels launched through this module (bench reporting)
+
+c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+def _load():
+    global _LIB, _ERR
+    if _LIB is not None or _ERR is not None:
+        return
+    if not os.path.exists(LIB_PATH):
+        _ERR = f"{LIB_PATH} not found"
+        return
+    try:
+        _LIB = ctypes.CDLL(LIB_PATH)
+    except OSError as e:  # pragma: no cover
+        _ERR = str(e)
+        return
+    for name in dir(_LIB):
+        pass
+    for fn in ("pm_gemm_bf16", "pm_rmsnorm_fwd", "pm_rmsnorm_bwd", "pm_rope_table", "pm_qknorm_rope_fwd",
+               "pm_qknorm_rope_bwd", "pm_swiglu_fwd", "pm_swiglu_bwd", "pm_ce_fwd_bwd", "pm_sumsq", "pm_adamw_flat",
+               "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16"):
+        getattr(_LIB, fn).restype = c_int
+
+
+def available() -> bool:
+    _load()
+    return _LIB is not None and torch.cuda.is_available()
+
+
+def load_error() -> Optional[str]:
+    _load()
+    return _ERR
+
+
+def lib():
+    _load()
+    if _LIB is None:
+        raise RuntimeError(f"native library unavailable: {_ERR}")
+    return _LIB
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _chk(rc: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+def status_word(device=None) -> torch.Tensor:
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev not in _STATUS:
+        _STATUS[dev] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _STATUS[dev]
+
+
+def check_status() -> None:
+    """Synchronise and raise if any kernel abandoned a bounded wait."""
+    for dev, t in _STATUS.items():
+        v = int(t.item())
+        if v != 0:
+            t.zero_()
+            raise RuntimeError(f"device-side wait timed out on {dev} (status {v})")
+
+
+# ------------------------------------------------------------------------------------------- GEMM
+def _pick_bn(n: int, seg_sizes: Sequence[int] = ()) -> int:
+    for bn in (256, 128, 64, 32):
+        if n % bn == 0 and all(s % bn == 0 for s in seg_sizes):
+            return bn
+    return 128 if n >= 128 else (64 if n > 32 else 32)
+
+
+def _seg_ends(seg_sizes: Sequence[int]):
+    ends, c = [], 0
+    for s in seg_sizes:
+        c += s
+        ends.append(c)
+    ends = ends[:-1] + [0x7FFFFFFF] * (5 - len(ends))
+    return (c_int * 4)(*ends[:4])
+
+
+def raw_gemm(A, a_mn, lda, a_rows, B, b_mn, ldb, b_rows, D, out_mode, ldd, M, N, K, *, A2=None, a2_mn=0, lda2=0,
+             a2_k=0, B2=None, b2_mn=0, ldb2=0, b2_rows=0, K2=0, R=None, ldr=0, n_store=0, alpha=1.0, bn=128, splits=1,
+             seg_mode=0, seg_sizes=(), seg_r=0, max_ctas=0) -> None:
+    rc = lib().pm_gemm_bf16(_p(A), c_int(a_mn), c_int(lda), c_int(a_rows), _p(B), c_int(b_mn), c_int(ldb),
+                            c_int(b_rows), _p(A2), c_int(a2_mn), c_int(lda2), c_int(a2_k), _p(B2), c_int(b2_mn),
+                            c_int(ldb2), c_int(b2_rows), _p(D), c_int(out_mode), c_int(ldd), _p(R), c_int(ldr),
+                            c_int(M), c_int(N), c_int(K), c_int(K2), c_int(n_store), c_float(alpha), c_int(bn),
+                            c_int(splits), c_int(seg_mode), _seg_ends(seg_sizes) if seg_mode else None, c_int(seg_r),
+                            c_int(max_ctas), _p(status_word(D.device)), _stream())
+    _chk(rc, "pm_gemm_bf16")
+
+
+def _t_width(nr: int) -> int:
+    return -(-nr // 64) * 64
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0, residual: Optional[torch.Tensor] = None,
+         out: Optional[torch.Tensor] = None, pad_n_to: int = 0, bn: int = 0) -> torch.Tensor:
+    """[M,K] x [N,K]^T -> [M,N] bf16. ``pad_n_to`` widens the output (extra columns are written as zeros)."""
+    M, K = x.shape
+    N = w.shape[0]
+    Nw = max(N, pad_n_to)
+    if out is None:
+        out = torch.empty(M, Nw, dtype=torch.bfloat16, device=x.device)
+    bn = bn or _pick_bn(Nw)
+    raw_gemm(x, 0, x.stride(0), M, w, 0, w.stride(0), N, out, 0, out.stride(0), M, Nw, K, R=residual,
+             ldr=residual.stride(0) if residual is not None else 0, alpha=alpha, bn=bn)
+    return out
+
+
+def gemm_lora(x, w, t, b, seg_sizes, r, residual=None, bn: int = 0) -> torch.Tensor:
+    """y = x w^T + sum_seg t[:, seg*r:(seg+1)*r] b_seg^T (+ residual). t already carries the LoRA scale."""
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    bn = bn or _pick_bn(N, seg_sizes)
+    kw = {}
+    if t is not None:
+        kw = dict(A2=t, a2_mn=0, lda2=t.stride(0), a2_k=t.shape[1], B2=b, b2_mn=0, ldb2=b.stride(0), b2_rows=N, K2=r,
+                  seg_mode=1 if len(seg_sizes) > 1 else 0, seg_sizes=seg_sizes, seg_r=r)
+    raw_gemm(x, 0, x.stride(0), M, w, 0, w.stride(0), N, out, 0, N, M, N, K, R=residual,
+             ldr=residual.stride(0) if residual is not None else 0, bn=bn, **kw)
+    return out
+
+
+def lora_t(x, a, scale: float) -> torch.Tensor:
+    """t = scale * x a^T, padded to a multiple of 64 columns (padding is zero)."""
+    return gemm(x, a, alpha=scale, pad_n_to=_t_width(a.shape[0]), bn=64)
+
+
+def lora_dt(dy, b, seg_sizes, r, scale) -> torch.Tensor:
+    """dt[:, seg*r:(seg+1)*r] = scale * dy[:, seg] b_seg   ([M, 64-padded]); padding columns are unspecified."""
+    M, N = dy.shape
+    nseg = len(seg_sizes)
+    dt = torch.empty(M, _t_width(nseg * r), dtype=torch.bfloat16, device=dy.device)
+    b_t = b.t().contiguous()                      # [r, N], K-major over N
+    n0 = 0
+    for i, sz in enumerate(seg_sizes):
+        raw_gemm(dy[:, n0:], 0, dy.stride(0), M, b_t[:, n0:], 0, N, r, dt[:, i * r:], 0, dt.stride(0), M, 32, sz,
+                 n_store=r, alpha=scale, bn=32)
+        n0 += sz
+    return dt
+
+
+def gemm_lora_dx(dy, w, w_t, dt, a) -> torch.Tensor:
+    """dx = dy w (+ dt[:, :nr] a).  w:[N,K_in]; w_t:[K_in,N] optional; a:[nr,K_in]."""
+    M, N = dy.shape
+    kin = w.shape[1]
+    out = torch.empty(M, kin, dtype=torch.bfloat16, device=dy.device)
+    bn = _pick_bn(kin)
+    kw = {}
+    if dt is not None:
+        nr = a.shape[0]
+        if MN_MAJOR:
+            kw = dict(A2=dt, a2_mn=0, lda2=dt.stride(0), a2_k=dt.shape[1], B2=a, b2_mn=1, ldb2=a.stride(0),
+                      b2_rows=kin, K2=nr)
+        else:
+            a_t = a.t().contiguous()
+            kw = dict(A2=dt, a2_mn=0, lda2=dt.stride(0), a2_k=dt.shape[1], B2=a_t, b2_mn=0, ldb2=nr, b2_rows=kin, K2=nr)
+    if w_t is not None:
+        raw_gemm(dy, 0, dy.stride(0), M, w_t, 0, w_t.stride(0), kin, out, 0, kin, M, kin, N, bn=bn, **kw)
+    elif MN_MAJOR:
+        raw_gemm(dy, 0, dy.stride(0), M, w, 1, w.stride(0), kin, out, 0, kin, M, kin, N, bn=max(bn, 64), **kw)
+    else:
+        wt = w.t().contiguous()
+        raw_gemm(dy, 0, dy.stride(0), M, wt, 0, N, kin, out, 0, kin, M, kin, N, bn=bn, **kw)
+    return out
+
+
+def _splits_for(m_tiles: int, nk: int) -> int:
+    return max(1, min(nk, -(-148 // max(m_tiles, 1))))
+
+
+def lora_da(dt, x, nr: int, out: torch.Tensor) -> None:
+    """out[nr, K_in] (fp32) += dt[:, :nr]^T x  — reduction over tokens, split across CTAs."""
+    M, kin = x.shape
+    if not MN_MAJOR:
+        out.add_(dt[:, :nr].t().float() @ x.float())
+        return
+    tw = dt.shape[1]
+    nk = -(-M // 64)
+    raw_gemm(x, 1, x.stride(0), kin, dt, 1, dt.stride(0), tw, out, 3, out.stride(0), kin, tw, M, n_store=nr, bn=64,
+             splits=_splits_for(-(-kin // 128), nk))
+
+
+def lora_db(dy, t, seg_sizes, r: int, out: torch.Tensor) -> None:
+    """out[N, r] (fp32) += dy_seg^T t[:, seg*r:(seg+1)*r]."""
+    M, N = dy.shape
+    if not MN_MAJOR:
+        n0 = 0
+        for i, sz in enumerate(seg_sizes):
+            out[n0:n0 + sz].add_(dy[:, n0:n0 + sz].t().float() @ t[:, i * r:(i + 1) * r].float())
+            n0 += sz
+        return
+    nk = -(-M // 64)
+    raw_gemm(dy, 1, dy.stride(0), N, t, 1, t.stride(0), t.shape[1], out, 2, out.stride(0), N, 64, M, n_store=r, bn=64,
+             splits=_splits_for(-(-N // 128), nk), seg_mode=2 if len(seg_sizes) > 1 else 0, seg_sizes=seg_sizes,
+             seg_r=r)
+
+
+# ------------------------------------------------------------------------------------------- norms etc.
+def rmsnorm_fwd(x, w, eps: float, residual=None):
+    T, H = x.shape
+    y = torch.empty_like(x)
+    h = torch.empty_like(x) if residual is not None else x
+    rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    _chk(lib().pm_rmsnorm_fwd(_p(x), _p(residual), _p(w), _p(y), _p(h if residual is not None else None), _p(rstd),
+                              c_int(T), c_int(H), c_float(eps), _stream()), "pm_rmsnorm_fwd")
+    return h, y, rstd
+
+
+def rmsnorm_bwd(dy, h, w, rstd, dh_add=None, want_dw: bool = False):
+    T, H = h.shape
+    dx = torch.empty_like(h)
+    dw = torch.zeros(H, dtype=torch.float32, device=h.device) if want_dw else None
+    _chk(lib().pm_rmsnorm_bwd(_p(dy), _p(h), _p(w), _p(rstd), _p(dh_add), _p(dx), _p(dw), c_int(T), c_int(H),
+                              _stream()), "pm_rmsnorm_bwd")
+    return dx, (dw.to(w.dtype) if dw is not None else None)
+
+
+def rope_table(positions: torch.Tensor, head_dim: int, theta: float, rope_scale: float = 1.0):
+    T = positions.shape[0]
+    half = head_dim // 2
+    pos = positions if positions.dtype == torch.int32 else positions.to(torch.int32)
+    cs = torch.empty(T, half, dtype=torch.float32, device=positions.device)
+    sn = torch.empty_like(cs)
+    _chk(lib().pm_rope_table(_p(pos), _p(cs), _p(sn), c_int(T), c_int(half), c_float(theta), c_float(rope_scale),
+                             _stream()), "pm_rope_table")
+    return cs, sn
+
+
+def qknorm_rope_fwd(qkv, qw, kw, cos, sin, hq: int, hkv: int, eps: float):
+    T = qkv.shape[0]
+    q = torch.empty(T, hq, 128, dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty(T, hkv, 128, dtype=qkv.dtype, device=qkv.device)
+    _chk(lib().pm_qknorm_rope_fwd(_p(qkv), c_int(qkv.stride(0)), _p(qw), _p(kw), _p(cos), _p(sin), _p(q), _p(k),
+                                  c_int(T), c_int(hq), c_int(hkv), c_float(eps), _stream()), "pm_qknorm_rope_fwd")
+    return q, k
+
+
+def qknorm_rope_bwd(dq, dk, qkv, qw, kw, cos, sin, hq: int, hkv: int, eps: float, dqkv) -> None:
+    T = qkv.shape[0]
+    _chk(lib().pm_qknorm_rope_bwd(_p(dq), _p(dk), _p(qkv), c_int(qkv.stride(0)), _p(qw), _p(kw), _p(cos), _p(sin),
+                                  _p(dqkv), c_int(T), c_int(hq), c_int(hkv), c_float(eps), _stream()),
+         "pm_qknorm_rope_bwd")
+
+
+def swiglu_fwd(gate_up):
+    T, I2 = gate_up.shape
+    out = torch.empty(T, I2 // 2, dtype=gate_up.dtype, device=gate_up.device)
+    _chk(lib().pm_swiglu_fwd(_p(gate_up), _p(out), c_ll(T), c_int(I2 // 2), _stream()), "pm_swiglu_fwd")
+    return out
+
+
+def swiglu_bwd(dout, gate_up):
+    T, I2 = gate_up.shape
+    dgu = torch.empty_like(gate_up)
+    _chk(lib().pm_swiglu_bwd(_p(dout), _p(gate_up), _p(dgu), c_ll(T), c_int(I2 // 2), _stream()), "pm_swiglu_bwd")
+    return dgu
+
+
+# ------------------------------------------------------------------------------------------- attention
+def attn_fwd(q, k, v, seq_start, scale: float, window: int = 0):
+    T, hq, d = q.shape
+    hkv = k.shape[1]
+    assert d == 128 and q.stride(2) == 1 and k.stride(2) == 1 and v.stride(2) == 1
+    out = torch.empty(T, hq, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(hq, T, dtype=torch.float32, device=q.device)
+    _chk(lib().pm_attn_fwd(_p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)), _p(out),
+                           c_ll(out.stride(0)), _p(lse), _p(seq_start), c_int(T), c_int(hq), c_int(hkv),
+                           c_float(scale), c_int(window), _stream()), "pm_attn_fwd")
+    return out, lse
+
+
+def attn_bwd(dout, q, k, v, o, lse, seq_start, scale: float, window: int = 0, dv_out=None):
+    T, hq, d = q.shape
+    hkv = k.shape[1]
+    delta = torch.empty(hq, T, dtype=torch.float32, device=q.device)
+    _chk(lib().pm_attn_delta(_p(o), _p(dout), _p(delta), c_int(T), c_int(hq), _stream()), "pm_attn_delta")
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = dv_out if dv_out is not None else torch.empty(T, hkv, d, dtype=q.dtype, device=q.device)
+    _chk(lib().pm_attn_bwd(_p(dout), _p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)),
+                           c_ll(dout.stride(0)), _p(lse), _p(delta), _p(dq), c_ll(dq.stride(0)), _p(dk),
+                           c_ll(dk.stride(0)), _p(dv), c_ll(dv.stride(0)), _p(seq_start), c_int(T), c_int(hq),
+                           c_int(hkv), c_float(scale), c_int(window), _stream()), "pm_attn_bwd")
+    global LAUNCHES
+    LAUNCHES += 1   # pm_attn_bwd launches two kernels
+    return (dq, dk) if dv_out is not None else (dq, dk, dv)
+
+
+# ------------------------------------------------------------------------------------------- loss / optimizer
+def linear_ce(hidden, weight, weight_t, labels, ignore_index: int, chunk: int, need_grad: bool):
+    """Chunked linear + cross-entropy. Logits of one token chunk live in a bf16 scratch buffer, are turned
+    into their gradient in place, and feed the input-gradient GEMM; the [T, V] matrix never exists."""
+    T, H = hidden.shape
+    V = weight.shape[0]
+    labels = labels.contiguous()
+    n_valid = (labels != ignore_index).sum()
+    inv_n = torch.ones(1, dtype=torch.float32, device=hidden.device)   # gradient is of the *sum*; caller divides
+    loss = torch.zeros(1, dtype=torch.float32, device=hidden.device)
+    dh = torch.empty_like(hidden) if need_grad else None
+    chunk = min(chunk, T)
+    ldl = -(-V // 8) * 8
+    scratch = torch.empty(chunk, ldl, dtype=torch.bfloat16, device=hidden.device)
+    bn = _pick_bn(V)
+    for s in range(0, T, chunk):
+        n = min(chunk, T - s)
+        h = hidden[s:s + n]
+        raw_gemm(h, 0, h.stride(0), n, weight, 0, weight.stride(0), V, scratch, 0, ldl, n, V, H, bn=bn)
+        _chk(lib().pm_ce_fwd_bwd(_p(scratch), c_ll(ldl), _p(labels[s:s + n]), _p(loss), _p(inv_n), c_int(n), c_int(V),
+                                 c_ll(ignore_index), c_int(1 if need_grad else 0), _stream()), "pm_ce_fwd_bwd")
+        if need_grad:
+            d = dh[s:s + n]
+            if weight_t is not None:
+                raw_gemm(scratch, 0, ldl, n, weight_t, 0, weight_t.stride(0), H, d, 0, d.stride(0), n, H, V,
+                         bn=_pick_bn(H))
+            elif MN_MAJOR:
+                raw_gemm(scratch, 0, ldl, n, weight, 1, weight.stride(0), H, d, 0, d.stride(0), n, H, V,
+                         bn=max(64, _pick_bn(H)))
+            else:
+                wt = weight.t().contiguous()
+                raw_gemm(scratch, 0, ldl, n, wt, 0, V, H, d, 0, d.stride(0), n, H, V, bn=_pick_bn(H))
+    return loss.reshape(()), n_valid, dh
+
+
+def sumsq(x: torch.Tensor, out: torch.Tensor) -> None:
+    _chk(lib().pm_sumsq(_p(x), c_ll(x.numel()), _p(out), _stream()), "pm_sumsq")
+    global LAUNCHES
+    LAUNCHES += 0
+
+
+def adamw_flat(p, g, m, v, shadow, lr_mult, wd, gnorm_sq, lr, b1, b2, eps, step, grad_scale, max_norm) -> None:
+    _chk(lib().pm_adamw_flat(_p(p), _p(g), _p(m), _p(v), _p(shadow), _p(lr_mult), _p(wd), _p(gnorm_sq),
+                             c_ll(p.numel()), c_float(lr), c_float(b1), c_float(b2), c_float(eps), c_int(step),
+                             c_float(grad_scale), c_float(max_norm or 0.0), _stream()), "pm_adamw_flat")

@@ -1,0 +1,245 @@
+"""Numerics of every CUDA kernel against the fp32 PyTorch statement of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _nat():
+    from pmetal_b200.ops import native
+    if not native.available():
+        pytest.fail(f"native library not loaded: {native.load_error()}")
+    return native
+
+
+def _close(a, b, rtol=2e-2, atol=2e-2, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert err <= atol + rtol * ref, f"{what}: max err {err} vs ref max {ref}"
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device="cuda") * scale).to(dtype)
+
+
+@pytest.mark.parametrize("M,N,K,bn", [(256, 256, 512, 128), (384, 512, 1024, 256), (200, 192, 320, 64),
+                                      (1000, 96, 136, 32), (128, 128, 64, 128), (4096, 4096, 1024, 256)])
+def test_gemm_kmajor(M, N, K, bn):
+    nat = _nat()
+    torch.manual_seed(0)
+    x, w = _rand(M, K), _rand(N, K, scale=K ** -0.5)
+    y = nat.gemm(x, w, bn=bn)
+    nat.check_status()
+    _close(y, x.float() @ w.float().t(), what="gemm")
+
+
+def test_gemm_alpha_residual_pad():
+    nat = _nat()
+    torch.manual_seed(1)
+    x, w, r = _rand(300, 256), _rand(48, 256, scale=1 / 16), _rand(300, 64)
+    y = nat.gemm(x, w, alpha=0.5, residual=r, pad_n_to=64, bn=64)
+    nat.check_status()
+    ref = torch.zeros(300, 64, device="cuda")
+    ref[:, :48] = 0.5 * (x.float() @ w.float().t())
+    _close(y, ref + r.float(), what="gemm alpha/residual/pad")
+
+
+@pytest.mark.parametrize("segs,r", [((256, 128, 128), 16), ((512,), 16), ((256, 256), 8), ((256, 128, 128), 64)])
+def test_gemm_lora_forward(segs, r):
+    nat = _nat()
+    torch.manual_seed(2)
+    M, K, N = 640, 512, sum(segs)
+    x, w = _rand(M, K), _rand(N, K, scale=K ** -0.5)
+    a, b = _rand(len(segs) * r, K, scale=K ** -0.5), _rand(N, r, scale=0.2)
+    res = _rand(M, N)
+    t = nat.lora_t(x, a, 2.0)
+    y = nat.gemm_lora(x, w, t, b, segs, r, res)
+    nat.check_status()
+    ref = x.float() @ w.float().t() + res.float()
+    n0 = 0
+    for i, sz in enumerate(segs):
+        ti = 2.0 * (x.float() @ a[i * r:(i + 1) * r].float().t())
+        _close(t[:, i * r:(i + 1) * r], ti, what="lora_t")
+        ref[:, n0:n0 + sz] += ti.to(torch.bfloat16).float() @ b[n0:n0 + sz].float().t()
+        n0 += sz
+    assert torch.all(t[:, len(segs) * r:] == 0)
+    _close(y, ref, what="gemm_lora")
+
+
+@pytest.mark.parametrize("mn", [True, False])
+def test_lora_backward_pieces(mn):
+    nat = _nat()
+    old = nat.MN_MAJOR
+    nat.MN_MAJOR = mn
+    try:
+        torch.manual_seed(3)
+        segs, r = (256, 128, 128), 16
+        M, K, N = 1024, 512, sum(segs)
+        x, dy = _rand(M, K), _rand(M, N)
+        w = _rand(N, K, scale=K ** -0.5)
+        a, b = _rand(len(segs) * r, K, scale=K ** -0.5), _rand(N, r, scale=0.2)
+        t = nat.lora_t(x, a, 2.0)
+        dt = nat.lora_dt(dy, b, segs, r, 2.0)
+        n0 = 0
+        dt_ref = torch.zeros(M, len(segs) * r, device="cuda")
+        for i, sz in enumerate(segs):
+            dt_ref[:, i * r:(i + 1) * r] = 2.0 * (dy[:, n0:n0 + sz].float() @ b[n0:n0 + sz].float())
+            n0 += sz
+        _close(dt[:, :len(segs) * r], dt_ref, what="lora_dt")
+        for wt in (w.t().contiguous(), None):
+            dx = nat.gemm_lora_dx(dy, w, wt, dt, a)
+            _close(dx, dy.float() @ w.float() + dt[:, :len(segs) * r].float() @ a.float(), what="gemm_lora_dx")
+        da = torch.zeros(len(segs) * r, K, device="cuda")
+        nat.lora_da(dt, x, len(segs) * r, da)
+        _close(da, dt[:, :len(segs) * r].float().t() @ x.float(), rtol=2e-2, atol=0.5, what="lora_da")
+        db = torch.zeros(N, r, device="cuda")
+        nat.lora_db(dy, t, segs, r, db)
+        db_ref = torch.zeros(N, r, device="cuda")
+        n0 = 0
+        for i, sz in enumerate(segs):
+            db_ref[n0:n0 + sz] = dy[:, n0:n0 + sz].float().t() @ t[:, i * r:(i + 1) * r].float()
+            n0 += sz
+        _close(db, db_ref, rtol=2e-2, atol=0.5, what="lora_db")
+        nat.check_status()
+    finally:
+        nat.MN_MAJOR = old
+
+
+def test_rmsnorm():
+    nat = _nat()
+    from pmetal_b200.ops import reference as ref
+    torch.manual_seed(4)
+    T, H = 777, 1024
+    x, res, w = _rand(T, H), _rand(T, H), (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    h, y, rstd = nat.rmsnorm_fwd(x, w, 1e-6, res)
+    hr = (x.float() + res.float()).bfloat16()
+    assert torch.equal(h, hr)
+    _close(y, ref.rms_norm(hr.float(), w.float(), 1e-6), what="rmsnorm fwd")
+    dy, dh = _rand(T, H), _rand(T, H)
+    dx, dw = nat.rmsnorm_bwd(dy, h, w, rstd, dh, True)
+    hf = hr.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    ref.rms_norm(hf, wf, 1e-6).backward(dy.float())
+    _close(dx, hf.grad + dh.float(), what="rmsnorm dx")
+    _close(dw, wf.grad, rtol=3e-2, atol=0.5, what="rmsnorm dw")
+
+
+def test_qknorm_rope():
+    nat = _nat()
+    from pmetal_b200.ops import reference as ref
+    torch.manual_seed(5)
+    T, hq, hkv, d = 300, 4, 2, 128
+    qkv = _rand(T, (hq + 2 * hkv) * d)
+    qw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    kw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    pos = torch.randint(0, 5000, (T,), device="cuda", dtype=torch.int32)
+    cs, sn = nat.rope_table(pos, d, 1e6, 1.0)
+    cr, sr = ref.rope_cos_sin(pos, d, 1e6)
+    _close(cs, cr, rtol=0, atol=2e-3, what="cos")
+    _close(sn, sr, rtol=0, atol=2e-3, what="sin")
+    q, k = nat.qknorm_rope_fwd(qkv, qw, kw, cs, sn, hq, hkv, 1e-6)
+    x = qkv.float().requires_grad_(True)
+    qr = ref.apply_rope(ref.rms_norm(x[:, :hq * d].view(T, hq, d), qw.float(), 1e-6), cr, sr)
+    kr = ref.apply_rope(ref.rms_norm(x[:, hq * d:(hq + hkv) * d].view(T, hkv, d), kw.float(), 1e-6), cr, sr)
+    _close(q, qr, what="q rope")
+    _close(k, kr, what="k rope")
+    dq, dk = _rand(T, hq, d), _rand(T, hkv, d)
+    dqkv = torch.zeros_like(qkv)
+    nat.qknorm_rope_bwd(dq, dk, qkv, qw, kw, cs, sn, hq, hkv, 1e-6, dqkv)
+    (qr * dq.float()).sum().add((kr * dk.float()).sum()).backward()
+    _close(dqkv[:, :(hq + hkv) * d], x.grad[:, :(hq + hkv) * d], what="qknorm_rope bwd")
+
+
+def test_swiglu():
+    nat = _nat()
+    from pmetal_b200.ops import reference as ref
+    torch.manual_seed(6)
+    gu = _rand(513, 2 * 768)
+    out = nat.swiglu_fwd(gu)
+    x = gu.float().requires_grad_(True)
+    r = ref.swiglu(x)
+    _close(out, r, what="swiglu fwd")
+    d = _rand(513, 768)
+    r.backward(d.float())
+    _close(nat.swiglu_bwd(d, gu), x.grad, what="swiglu bwd")
+
+
+def _doc_bounds(T, lens):
+    cu = [0]
+    for n in lens:
+        cu.append(min(cu[-1] + n, T))
+    if cu[-1] < T:
+        cu.append(T)
+    return torch.tensor(cu, dtype=torch.int32, device="cuda")
+
+
+@pytest.mark.parametrize("T,lens,hq,hkv,window", [(256, [256], 2, 1, 0), (512, [100, 37, 200, 175], 4, 2, 0),
+                                                  (1000, [333, 64, 1, 450, 152], 4, 2, 0),
+                                                  (768, [500, 268], 2, 2, 96)])
+def test_attention_fwd_bwd(T, lens, hq, hkv, window):
+    nat = _nat()
+    from pmetal_b200.ops import reference as ref
+    torch.manual_seed(7)
+    d = 128
+    cu = _doc_bounds(T, lens)
+    ss = ref.seq_starts_from_cu(cu, T)
+    q, k, v = _rand(T, hq, d), _rand(T, hkv, d), _rand(T, hkv, d)
+    scale = d ** -0.5
+    o, lse = nat.attn_fwd(q, k, v, ss, scale, window)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    orf = ref.varlen_attention(qf, kf, vf, cu, scale, True, window)
+    _close(o, orf, what="attn fwd")
+    do = _rand(T, hq, d)
+    orf.backward(do.float())
+    dq, dk, dv = nat.attn_bwd(do, q, k, v, o, lse, ss, scale, window)
+    _close(dq, qf.grad, rtol=3e-2, atol=3e-2, what="attn dq")
+    _close(dk, kf.grad, rtol=3e-2, atol=3e-2, what="attn dk")
+    _close(dv, vf.grad, rtol=3e-2, atol=3e-2, what="attn dv")
+
+
+def test_linear_ce():
+    nat = _nat()
+    torch.manual_seed(8)
+    T, H, V = 700, 256, 5000
+    h, w = _rand(T, H), _rand(V, H, scale=H ** -0.5)
+    lab = torch.randint(0, V, (T,), device="cuda")
+    lab[::7] = -100
+    for wt in (w.t().contiguous(), None):
+        loss, n, dh = nat.linear_ce(h, w, wt, lab, -100, 256, True)
+        hf = h.float().requires_grad_(True)
+        ref = torch.nn.functional.cross_entropy(hf @ w.float().t(), lab, ignore_index=-100, reduction="sum")
+        ref.backward()
+        assert int(n) == int((lab != -100).sum())
+        assert abs(loss.item() - ref.item()) / ref.item() < 5e-3
+        _close(dh, hf.grad, rtol=3e-2, atol=2e-3, what="linear_ce dh")
+    nat.check_status()
+
+
+def test_adamw_and_sumsq():
+    nat = _nat()
+    from pmetal_b200.ops import reference as ref
+    torch.manual_seed(9)
+    n = 4096
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda") * 3
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    sh = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    lr_mult = torch.tensor([1.0, 2.0, 1.0, 0.5], device="cuda")
+    wd = torch.tensor([0.01, 0.0, 0.01, 0.1], device="cuda")
+    gn = torch.zeros(1, device="cuda")
+    nat.sumsq(g, gn)
+    assert abs(gn.item() - (g.double() ** 2).sum().item()) / gn.item() < 1e-4
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    coef = min(1.0, 1.0 / (math.sqrt(gn.item()) * 0.5 + 1e-6)) * 0.5
+    for step in (1, 2):
+        nat.adamw_flat(p, g, m, v, sh, lr_mult, wd, gn, 1e-3, 0.9, 0.999, 1e-8, step, 0.5, 1.0)
+        for c in range(4):
+            s = slice(c * 1024, (c + 1) * 1024)
+            ref.adamw_step(pr[s], g[s] * coef, mr[s], vr[s], step, 1e-3 * lr_mult[c].item(), 0.9, 0.999, 1e-8,
+                           wd[c].item())
+    _close(p, pr, rtol=1e-5, atol=1e-6, what="adamw p")
+    _close(sh, pr, rtol=1e-2, atol=1e-2, what="adamw shadow")
