@@ -1,0 +1,269 @@
+#!/usr/bin/env python
+"""Headline benchmark: LoRA SFT training throughput, Qwen3-0.6B architecture, bf16, packed sequences.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Config (the reference's LoRA SFT benchmark re-stated for one NVSwitch box): 28 layers, hidden 1024,
+16/8 heads of 128 with QK-norm, SwiGLU 3072, vocab 151936, tied embeddings, random init N(0, 0.02);
+LoRA r=16 alpha=32 on all seven projections; synthetic documents with lengths uniform in [64, 2048]
+packed to 4096 tokens with per-document causal masking; 4 packs per GPU per step; data parallel over N GPUs.
+
+Prints one JSON line on rank 0. ``value`` is whole-job tokens/s over K device-timed steps (CUDA events,
+max over ranks); ``e2e`` is the same step driven through the public training-loop API with the batch
+copied from pinned host memory and the loss read back every step.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_TOK_S = 2400.0   # best published single-machine LoRA SFT figure of the reference (Qwen3-0.6B)
+METRIC = "lora_sft_train_tokens_per_sec"
+
+
+def reference_arm(args) -> None:
+    """The reference is a macOS-only Rust/Metal/MLX workspace; it has no Python build that can be installed
+    here (no cargo/rustc, no Metal toolchain, MLX is fetched from the network at build time)."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    why = "reference is a Rust+Metal+MLX (macOS-only) workspace: pip install fails offline (no cargo, no Metal SDK)"
+    note = os.path.join(ROOT, "baseline", "install_outcome.txt")
+    if os.path.exists(note):
+        with open(note, "r", encoding="utf-8") as fh:
+            first = fh.readline().strip()
+        if first:
+            why = first
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why, "installed_dir_exists": os.path.isdir(ref_dir)}))
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.idx), "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for ts, line in self.rows:
+            if ts < t0 or ts > t1 + 0.3:
+                continue
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--model", default="qwen3-0.6b")
+    ap.add_argument("--packs", type=int, default=4)
+    ap.add_argument("--pack-len", type=int, default=4096)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--dp", default="fused", choices=["fused", "nccl"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    from pmetal_b200.core.config import LoraConfig, TrainingConfig
+    from pmetal_b200.data.dataloader import synthetic_documents
+    from pmetal_b200.data.packing import PackerConfig, SequencePacker, collate_packs
+    from pmetal_b200.lora import apply_lora
+    from pmetal_b200.models.config import preset
+    from pmetal_b200.models.decoder import DecoderLM
+    from pmetal_b200.ops import native
+    from pmetal_b200.trainer.loop import TrainingLoop
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not native.available():
+        raise SystemExit(f"native kernel library missing: {native.load_error()}")
+    dctx = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        if args.dp == "fused":
+            from pmetal_b200.parallel.fused_dp import FusedDataParallel
+            dctx = FusedDataParallel()
+        else:
+            from pmetal_b200.parallel.dp import DistContext
+            dctx = DistContext()
+
+    cfg = preset(args.model)
+    model = DecoderLM(cfg).init_weights(0.02, 0)
+    lcfg = LoraConfig(r=16, alpha=32.0, target_modules=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj",
+                                                        "up_proj", "down_proj"])
+    apply_lora(model, lcfg, seed=42)
+    model = model.to(dev)
+    for n, p in model.named_parameters():
+        if "lora_" not in n:
+            p.data = p.data.to(torch.bfloat16)
+    model.prepare_for_training()
+    tcfg = TrainingConfig(learning_rate=2e-4, gradient_accumulation_steps=1, warmup_steps=0, max_grad_norm=1.0,
+                          lr_scheduler="cosine")
+    loop = TrainingLoop(model, tcfg, dist=dctx, total_steps=10_000)
+
+    # synthetic packed data, a distinct batch for every step, staged in pinned host memory
+    n_steps_total = args.warmup + 2 * args.steps + 2
+    docs = synthetic_documents(int(n_steps_total * args.packs * args.pack_len / 1056 * 1.15) + 64, 64, 2048,
+                               cfg.vocab_size, seed=1000 + rank)
+    packs = SequencePacker(PackerConfig(max_length=args.pack_len, max_seq_length=args.pack_len)).pack(docs)
+    packs = [p for p in packs if p.total_tokens() >= int(0.9 * args.pack_len)] or packs
+    batches = []
+    for i in range(n_steps_total):
+        grp = [packs[(i * args.packs + j) % len(packs)] for j in range(args.packs)]
+        batches.append(collate_packs(grp, args.pack_len).pin())
+    h2d = sum(t.numel() * t.element_size() for t in (batches[0].input_ids, batches[0].labels, batches[0].position_ids,
+                                                     batches[0].seq_start))
+
+    use_graph = not args.no_graph
+    if use_graph:
+        loop.enable_cuda_graph(batches[0])
+        step_fn = loop.train_step_graphed
+    else:
+        step_fn = lambda b: loop.train_step(b.to(dev))      # noqa: E731
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    bi = 1
+    for _ in range(args.warmup):
+        step_fn(batches[bi]); bi += 1
+    barrier()
+    native.check_status()
+
+    # ---- region A: device-timed steps, inputs already resident on the device
+    dev_batches = [batches[bi + i].to(dev) for i in range(args.steps)]
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    barrier()
+    l0 = native.LAUNCHES
+    t_wall0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step_fn(dev_batches[i])
+    e1.record()
+    barrier()
+    t_wall1 = time.time()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop(t_wall0, t_wall1)
+    launches = (loop.launches_per_graph * args.steps) if use_graph else (native.LAUNCHES - l0)
+    tokens_a = sum(b.total_tokens for b in dev_batches)
+    bi += args.steps
+
+    # ---- region B: end to end — pinned host batch -> device every step, loss read back every step
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    tokens_b = 0
+    last_loss = 0.0
+    for i in range(args.steps):
+        b = batches[bi + i]
+        loss, _ = step_fn(b)
+        last_loss = float(loss)          # device -> host read of the step's result
+        tokens_b += b.total_tokens
+    f1.record()
+    barrier()
+    ms_b = f0.elapsed_time(f1)
+    native.check_status()
+
+    def reduce_max(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def reduce_sum(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t)
+        return float(t.item())
+
+    ms = reduce_max(ms)
+    ms_b = reduce_max(ms_b)
+    tok_a = reduce_sum(float(tokens_a))
+    tok_b = reduce_sum(float(tokens_b))
+    value = tok_a / (ms / 1e3)
+    e2e = tok_b / (ms_b / 1e3)
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": round(value / BASELINE_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": "Qwen3-0.6B architecture (random init)", "global_batch": args.packs * world,
+                       "seq_len": args.pack_len, "parallelism": f"dp{world}", "lora": "r16 alpha32 all-7",
+                       "packing": "docs U[64,2048] packed to 4096, varlen per-document causal attention",
+                       "tokens_per_step": int(tok_a / args.steps),
+                       "l2": "per-step working set (~1.2 GB weights + >10 GB activations) far exceeds the 126 MB L2",
+                       "cuda_graph": use_graph, "dp_impl": (args.dp if world > 1 else "none")},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+                    "d2h_bytes_per_step": 4, "ms_per_step": round(ms_b / args.steps, 3)},
+            "gpu_launches": int(launches),
+            "final_loss": round(last_loss, 4),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -405,7 +405,13 @@ struct AdamwArgs {
 __global__ void adamw_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
                                   float* __restrict__ v, __nv_bfloat16* __restrict__ shadow,
                                   const float* __restrict__ lr_mult, const float* __restrict__ wd,
-                                  const float* __restrict__ gnorm_sq, long long n, AdamwArgs a) {
+                                  const float* __restrict__ gnorm_sq, const float* __restrict__ hp, long long n,
+                                  AdamwArgs a) {
+  if (hp) {   // step-dependent scalars kept on the device so that a captured graph can be replayed
+    a.lr = hp[0];
+    a.bc1 = hp[1];
+    a.bc2 = hp[2];
+  }
   float coef = a.grad_scale;
   if (a.max_norm > 0.f) {
     const float norm = sqrtf(*gnorm_sq) * a.grad_scale;
@@ -549,8 +555,9 @@ extern "C" int pm_sumsq(const float* x, long long n, float* out, cudaStream_t st
   return PM_LAUNCH_CHECK();
 }
 extern "C" int pm_adamw_flat(float* p, const float* g, float* m, float* v, void* shadow, const float* lr_mult,
-                             const float* wd, const float* gnorm_sq, long long n, float lr, float beta1, float beta2,
-                             float eps, int step, float grad_scale, float max_norm, cudaStream_t st) {
+                             const float* wd, const float* gnorm_sq, const float* hp, long long n, float lr,
+                             float beta1, float beta2, float eps, int step, float grad_scale, float max_norm,
+                             cudaStream_t st) {
   if (n % 1024) return -1;
   AdamwArgs a;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps;
@@ -558,7 +565,7 @@ extern "C" int pm_adamw_flat(float* p, const float* g, float* m, float* v, void*
   a.bc2 = 1.f - powf(beta2, static_cast<float>(step));
   a.grad_scale = grad_scale; a.max_norm = max_norm;
   adamw_flat_kernel<<<grid_for(n / 4, 256, 148 * 8), 256, 0, st>>>(p, g, m, v, static_cast<__nv_bfloat16*>(shadow),
-                                                                  lr_mult, wd, gnorm_sq, n, a);
+                                                                  lr_mult, wd, gnorm_sq, hp, n, a);
   return PM_LAUNCH_CHECK();
 }
 extern "C" int pm_attn_delta(const void* o, const void* dout, float* delta, int T, int H, cudaStream_t st) {

@@ -363,7 +363,9 @@ def sumsq(x: torch.Tensor, out: torch.Tensor) -> None:
     LAUNCHES += 0
 
 
-def adamw_flat(p, g, m, v, shadow, lr_mult, wd, gnorm_sq, lr, b1, b2, eps, step, grad_scale, max_norm) -> None:
-    _chk(lib().pm_adamw_flat(_p(p), _p(g), _p(m), _p(v), _p(shadow), _p(lr_mult), _p(wd), _p(gnorm_sq),
+def adamw_flat(p, g, m, v, shadow, lr_mult, wd, gnorm_sq, lr, b1, b2, eps, step, grad_scale, max_norm,
+               hp=None) -> None:
+    """``hp`` (optional device tensor [lr, 1-b1^t, 1-b2^t]) overrides the scalar arguments (CUDA-graph replay)."""
+    _chk(lib().pm_adamw_flat(_p(p), _p(g), _p(m), _p(v), _p(shadow), _p(lr_mult), _p(wd), _p(gnorm_sq), _p(hp),
                              c_ll(p.numel()), c_float(lr), c_float(b1), c_float(b2), c_float(eps), c_int(step),
                              c_float(grad_scale), c_float(max_norm or 0.0), _stream()), "pm_adamw_flat")

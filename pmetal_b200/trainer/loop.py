@@ -107,6 +107,52 @@ class TrainingLoop:
             return loss, self.optimizer_step()
         return loss, None
 
+    # ------------------------------------------------------------------ CUDA-graph step
+    def enable_cuda_graph(self, example: PackedTensors) -> None:
+        """Capture forward + backward + (reduce) + optimizer of one fixed-shape packed batch into a CUDA graph.
+
+        One eager step on ``example`` runs first (it is a real optimizer step). Later calls of
+        ``train_step_graphed`` copy the batch into the static input buffers, stage the learning rate and
+        bias corrections on the device and replay the graph. Requires gradient_accumulation_steps == 1.
+        """
+        assert self.device.type == "cuda" and self.cfg.gradient_accumulation_steps == 1
+        ex = example.to(self.device)
+        self._g_in = PackedTensors(ex.input_ids.clone(), ex.labels.clone(), ex.position_ids.clone(),
+                                   ex.cu_seqlens.clone(), ex.seq_start.clone(), ex.total_tokens, ex.num_sequences,
+                                   ex.max_seqlen)
+        self.opt.device_hparams = True
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.opt.set_lr(self.current_lr())
+            self.opt.push_hparams(self.opt.step_count + 1)
+            self.train_step(self._g_in)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self._graph = torch.cuda.CUDAGraph()
+        from ..ops import native
+        n0 = native.LAUNCHES
+        with torch.cuda.graph(self._graph):
+            loss = self.micro_step(self._g_in)
+            gn = self.optimizer_step()
+        self.launches_per_graph = native.LAUNCHES - n0
+        self.opt.step_count -= 1          # capture records the work without running it
+        self.state.step -= 1
+        self._g_loss, self._g_gnorm = loss, gn
+
+    def train_step_graphed(self, batch: PackedTensors):
+        gi = self._g_in
+        gi.input_ids.copy_(batch.input_ids, non_blocking=True)
+        gi.labels.copy_(batch.labels, non_blocking=True)
+        gi.position_ids.copy_(batch.position_ids, non_blocking=True)
+        gi.seq_start.copy_(batch.seq_start, non_blocking=True)
+        self.opt.set_lr(self.current_lr())
+        self.opt.step_count += 1
+        self.opt.push_hparams(self.opt.step_count)
+        self._graph.replay()
+        self.state.step += 1
+        return self._g_loss, self._g_gnorm
+
     # ------------------------------------------------------------------ evaluation
     @torch.no_grad()
     def evaluate(self, batches: Iterable) -> EvalMetrics:

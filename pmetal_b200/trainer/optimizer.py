@@ -86,7 +86,10 @@ class FlatAdamW:
         self.lr_mult = lr_mult.to(dev)
         self.wd_tab = wd_tab.to(dev)
         self.grad_norm = torch.zeros(1, dtype=torch.float32, device=dev)
-        self._hp = torch.zeros(8, dtype=torch.float32, device=dev) if dev.type == "cuda" else None
+        # [lr, 1-beta1^t, 1-beta2^t] on the device; used instead of scalars while replaying a CUDA graph
+        self._hp = torch.zeros(4, dtype=torch.float32, device=dev) if dev.type == "cuda" else None
+        self._hp_host = torch.zeros(4, dtype=torch.float32).pin_memory() if dev.type == "cuda" else None
+        self.device_hparams = False
 
     # ---------------------------------------------------------------- helpers
     def zero_grad(self) -> None:
@@ -123,7 +126,7 @@ class FlatAdamW:
             native.sumsq(self.flat_g, self.grad_norm)
             native.adamw_flat(self.flat_p, self.flat_g, self.flat_m, self.flat_v, self.flat_shadow, self.lr_mult,
                               self.wd_tab, self.grad_norm, self.lr, b1, b2, self.eps, self.step_count, grad_scale,
-                              self.max_grad_norm)
+                              self.max_grad_norm, self._hp if self.device_hparams else None)
             return self.grad_norm.sqrt() * grad_scale
         if grad_scale != 1.0:
             self.flat_g.mul_(grad_scale)
@@ -139,6 +142,12 @@ class FlatAdamW:
         if self.flat_shadow is not None:
             self.flat_shadow.copy_(self.flat_p)
         return norm.reshape(1)
+
+    def push_hparams(self, step: int) -> None:
+        """Stage lr and the bias corrections of ``step`` on the device (call before replaying a captured step)."""
+        b1, b2 = self.betas
+        self._hp_host[0], self._hp_host[1], self._hp_host[2] = self.lr, 1 - b1 ** step, 1 - b2 ** step
+        self._hp.copy_(self._hp_host, non_blocking=True)
 
     # ---------------------------------------------------------------- state
     def state_dict(self) -> dict:
