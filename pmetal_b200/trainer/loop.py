@@ -59,10 +59,10 @@ class TrainingLoop:
         self.opt = FlatAdamW(model.named_parameters(), lr=cfg.learning_rate, weight_decay=cfg.weight_decay,
                              embedding_lr=cfg.embedding_learning_rate or 5e-5, loraplus_ratio=loraplus_ratio,
                              max_grad_norm=cfg.max_grad_norm, shadow_dtype=shadow)
-        if shadow is not None:
-            attach_shadows(model, self.opt)
         if fused_dist:
             dist.bind_optimizer(self.opt)
+        if shadow is not None:
+            attach_shadows(model, self.opt)
         self.sched = LearningRateScheduler.from_training_config(cfg, total_steps)
         self.state = LoopState()
         self.lr_override: Optional[float] = None

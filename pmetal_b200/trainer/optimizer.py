@@ -91,6 +91,17 @@ class FlatAdamW:
         self._hp_host = torch.zeros(4, dtype=torch.float32).pin_memory() if dev.type == "cuda" else None
         self.device_hparams = False
 
+    def rehome(self, flat_p: torch.Tensor, flat_g: torch.Tensor, flat_shadow: Optional[torch.Tensor]) -> None:
+        """Adopt externally allocated flat buffers (e.g. symmetric memory); contents must already be copied."""
+        self.flat_p, self.flat_g = flat_p, flat_g
+        if flat_shadow is not None:
+            self.flat_shadow = flat_shadow
+        for (n, p), o in zip(self.named, self.offsets):
+            p.data = self.flat_p[o:o + p.numel()].view(p.shape)
+            p.grad = self.flat_g[o:o + p.numel()].view(p.shape)
+            if self.flat_shadow is not None:
+                self.shadows[n] = self.flat_shadow[o:o + p.numel()].view(p.shape)
+
     # ---------------------------------------------------------------- helpers
     def zero_grad(self) -> None:
         self.flat_g.zero_()

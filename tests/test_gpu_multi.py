@@ -1,0 +1,24 @@
+"""Multi-GPU tests (skipped with fewer than two devices): run workers under torch.distributed.run."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(worker: str, nproc: int, timeout: int = 600, port: int = 29541):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "workers", worker)]
+    return subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_fused_dp_matches_nccl_baseline():
+    n = min(torch.cuda.device_count(), 4)
+    r = _run("dp_worker.py", n)
+    assert r.returncode == 0 and "DP_WORKER_OK" in r.stdout, r.stdout[-4000:]
