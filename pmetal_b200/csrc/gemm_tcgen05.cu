@@ -12,43 +12,9 @@
 // Roles inside a 192-thread CTA: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
 // owner, warps 2..5 = epilogue (TMEM -> registers -> global). Two accumulator buffers
 // in TMEM let the epilogue of tile i overlap the MMAs of tile i+1.
-#include "common.cuh"
-
-#include <stdio.h>
+#include "gemm_common.cuh"
 
 namespace pm {
-
-constexpr int kBM = 128;
-constexpr int kBK = 64;
-constexpr int kThreads = 192;
-constexpr int kMaxStages = 8;
-
-struct GemmParams {
-  int M, N, K, K2;
-  int bn;          // tile width in N: 32, 64, 128 or 256
-  int a_mn, b_mn, a2_mn, b2_mn;
-  int nk1, nk2;    // number of 64-wide K blocks in the first / second product
-  int splits;      // split-K factor (out_mode must be atomic when > 1)
-  int stages;
-  int out_mode;    // 0: bf16 store, 1: f32 store, 2: f32 atomic add, 3: f32 atomic add, transposed
-  int ldd, ldr;
-  int n_store;     // columns >= n_store are computed but not written
-  float alpha;
-  void* D;
-  const void* R;
-  int seg_mode;    // 0 none; 1: A2 K-offset = seg(n0)*seg_r; 2: B mn-offset = seg(m0)*seg_r
-  int seg_end[4];
-  int seg_r;
-  int tmem_cols;
-  int* status;
-};
-
-__device__ __forceinline__ int seg_of(const GemmParams& p, int x) {
-  int s = 0;
-#pragma unroll
-  for (int i = 0; i < 3; ++i) s += (x >= p.seg_end[i]) ? 1 : 0;
-  return s;
-}
 
 // Issue the TMA copies that bring one operand tile (rows x 64 K) into shared memory.
 //   K-major : one box [rows][64 k], coordinates (k0, row0)
@@ -181,7 +147,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           const uint64_t db = make_smem_desc(sb, bmn ? 8192u : 16u, 1024u);
           const uint32_t astep = amn ? 128u : 2u;   // 16 K elements: 2048 B (MN-major) or 32 B (K-major), >> 4
           const uint32_t bstep = bmn ? 128u : 2u;
-          for (int j = 0; j < nmma; ++j) {
+          for (int j = 0; j < ((p.debug & 2) ? 0 : nmma); ++j) {
             umma_f16(d_tmem, da + static_cast<uint64_t>(astep * j), db + static_cast<uint64_t>(bstep * j), idesc,
                      accumulate);
             accumulate = 1;
@@ -213,58 +179,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         tmem_ld_32x32b_x32(tmem_base + buf * p.bn + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
         tmem_ld_wait();
         const int col0 = nb * p.bn + c * 32;
-        if (!row_ok || col0 >= p.n_store) continue;
-        if (p.out_mode == 0) {
-          __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd;
-          const __nv_bfloat16* rrow =
-              p.R ? static_cast<const __nv_bfloat16*>(p.R) + static_cast<size_t>(row) * p.ldr : nullptr;
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = col0 + v * 8;
-            if (col + 8 <= p.n_store) {
-              float f[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v * 8 + e]) * p.alpha;
-              if (rrow) {
-                const uint4 rv = *reinterpret_cast<const uint4*>(rrow + col);
-                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  f[2 * e] += bf16_bits_to_float(rw[e] & 0xFFFFu);
-                  f[2 * e + 1] += bf16_bits_to_float(rw[e] >> 16);
-                }
-              }
-              uint4 o;
-              o.x = pack_bf16x2(f[0], f[1]);
-              o.y = pack_bf16x2(f[2], f[3]);
-              o.z = pack_bf16x2(f[4], f[5]);
-              o.w = pack_bf16x2(f[6], f[7]);
-              *reinterpret_cast<uint4*>(drow + col) = o;
-            } else {
-              for (int e = 0; e < 8 && col + e < p.n_store; ++e) {
-                float f = __uint_as_float(r[v * 8 + e]) * p.alpha;
-                if (rrow) f += __bfloat162float(rrow[col + e]);
-                drow[col + e] = __float2bfloat16(f);
-              }
-            }
-          }
-        } else if (p.out_mode == 1) {
-          float* drow = static_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd;
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (col0 + e < p.n_store) drow[col0 + e] = __uint_as_float(r[e]) * p.alpha;
-        } else if (p.out_mode == 2) {
-          float* drow = static_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd;
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (col0 + e < p.n_store) atomicAdd(drow + col0 + e, __uint_as_float(r[e]) * p.alpha);
-        } else {
-          float* d = static_cast<float*>(p.D);
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (col0 + e < p.n_store)
-              atomicAdd(d + static_cast<size_t>(col0 + e) * p.ldd + row, __uint_as_float(r[e]) * p.alpha);
-        }
+        if (!row_ok || col0 >= p.n_store || (p.debug & 1)) continue;
+        epilogue_store_chunk(p, r, row, col0);
       }
       tc_fence_before();
       __syncwarp();
@@ -288,47 +204,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   }
 }
 
-// ======================================================================= host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// 2-D bf16 tensor map with 128-byte swizzle. inner = contiguous extent (elements).
-static int make_map(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld_elems,
-                    uint32_t box_inner, uint32_t box_outer) {
-  EncodeTiledFn enc = get_encode();
-  if (!enc) return -1;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld_elems * 2};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
-}
-
-static int operand_map(CUtensorMap* map, const void* ptr, int mn_major, int rows_total, int k_total, int ld,
-                       int tile_rows) {
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld % 8)) return -2;
-  if (!mn_major) return make_map(map, ptr, k_total, rows_total, ld, kBK, tile_rows);
-  return make_map(map, ptr, rows_total, k_total, ld, 64, kBK);
-}
-
-static int g_num_sms = 0;
-
 }  // namespace pm
 
 using namespace pm;
@@ -339,7 +214,7 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
                             const void* A2, int a2_mn, int lda2, int a2_k, const void* B2, int b2_mn, int ldb2,
                             int b2_rows, void* D, int out_mode, int ldd, const void* R, int ldr, int M, int N, int K,
                             int K2, int n_store, float alpha, int bn, int splits, int seg_mode, const int* seg_end,
-                            int seg_r, int max_ctas, int* status, cudaStream_t stream) {
+                            int seg_r, int max_ctas, int debug, int* status, cudaStream_t stream) {
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return -10;
   if ((b_mn || (K2 > 0 && b2_mn)) && (bn % 64)) return -11;
   if (splits < 1 || (splits > 1 && out_mode < 2)) return -12;
@@ -357,9 +232,11 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
   p.seg_mode = seg_mode; p.seg_r = seg_r;
   for (int i = 0; i < 4; ++i) p.seg_end[i] = (seg_mode && seg_end) ? seg_end[i] : 0x7fffffff;
   p.status = status;
+  p.debug = debug & 3;
   const int stage_bytes = kBM * kBK * 2 + bn * kBK * 2;
   int stages = (227 * 1024 - 2048) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
+  if ((debug >> 4) > 0 && (debug >> 4) < stages) stages = debug >> 4;   // stage-count experiments
   p.stages = stages;
   int cols = 32;
   while (cols < 2 * bn) cols *= 2;
@@ -375,11 +252,6 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
   } else {
     ma2 = ma; mb2 = mb;
   }
-  if (!g_num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024 /*align*/ + 256 /*barriers*/;
   static size_t configured = 0;
   if (smem > configured) {
@@ -390,7 +262,7 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
   }
   const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + bn - 1) / bn;
   int grid = m_tiles * n_tiles * splits;
-  int cap = max_ctas > 0 ? max_ctas : g_num_sms;
+  int cap = max_ctas > 0 ? max_ctas : num_sms();
   if (grid > cap) grid = cap;
   gemm_bf16_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(ma, mb, ma2, mb2, p);
   return static_cast<int>(cudaGetLastError());

@@ -21,6 +21,8 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__
 # The transposed LoRA products read token-major tensors through MN-major tcgen05 descriptors.
 # PMETAL_MN_MAJOR=0 routes them through explicit transposes instead.
 MN_MAJOR = os.environ.get("PMETAL_MN_MAJOR", "1") == "1"
+USE_2SM = os.environ.get("PMETAL_GEMM_2SM", "1") == "1"   # CTA-pair kernel for 256-wide tiles
+GEMM_DEBUG = int(os.environ.get("PMETAL_GEMM_DEBUG", "0"))   # timing experiments only (see gemm_tcgen05.cu)
 LAUNCHES = 0   # number of kernels launched through this module (bench reporting)
 
 c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
@@ -40,7 +42,7 @@ def _load():
         return
     for name in dir(_LIB):
         pass
-    for fn in ("pm_gemm_bf16", "pm_rmsnorm_fwd", "pm_rmsnorm_bwd", "pm_rope_table", "pm_qknorm_rope_fwd",
+    for fn in ("pm_gemm_bf16", "pm_gemm_bf16_2sm", "pm_rmsnorm_fwd", "pm_rmsnorm_bwd", "pm_rope_table", "pm_qknorm_rope_fwd",
                "pm_qknorm_rope_bwd", "pm_swiglu_fwd", "pm_swiglu_bwd", "pm_ce_fwd_bwd", "pm_sumsq", "pm_adamw_flat",
                "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16"):
         getattr(_LIB, fn).restype = c_int
@@ -96,10 +98,12 @@ def check_status() -> None:
 
 # ------------------------------------------------------------------------------------------- GEMM
 def _pick_bn(n: int, seg_sizes: Sequence[int] = ()) -> int:
+    """Widest tile whose boundaries respect the LoRA segments; a ragged last tile is fine (TMA zero-fills)."""
+    segs = seg_sizes[:-1] if len(seg_sizes) > 1 else ()
     for bn in (256, 128, 64, 32):
-        if n % bn == 0 and all(s % bn == 0 for s in seg_sizes):
+        if n >= bn and all(s % bn == 0 for s in segs):
             return bn
-    return 128 if n >= 128 else (64 if n > 32 else 32)
+    return 32
 
 
 def _seg_ends(seg_sizes: Sequence[int]):
@@ -114,12 +118,23 @@ def _seg_ends(seg_sizes: Sequence[int]):
 def raw_gemm(A, a_mn, lda, a_rows, B, b_mn, ldb, b_rows, D, out_mode, ldd, M, N, K, *, A2=None, a2_mn=0, lda2=0,
              a2_k=0, B2=None, b2_mn=0, ldb2=0, b2_rows=0, K2=0, R=None, ldr=0, n_store=0, alpha=1.0, bn=128, splits=1,
              seg_mode=0, seg_sizes=(), seg_r=0, max_ctas=0) -> None:
+    """One GEMM launch. 256-wide tiles on at least 256 rows go to the CTA-pair (cta_group::2) kernel."""
+    segs = _seg_ends(seg_sizes) if seg_mode else None
+    if USE_2SM and bn == 256 and M >= 256 and (seg_mode != 2 or all(s % 256 == 0 for s in seg_sizes[:-1])):
+        rc = lib().pm_gemm_bf16_2sm(_p(A), c_int(a_mn), c_int(lda), c_int(a_rows), _p(B), c_int(b_mn), c_int(ldb),
+                                    c_int(b_rows), _p(A2), c_int(a2_mn), c_int(lda2), c_int(a2_k), _p(B2),
+                                    c_int(b2_mn), c_int(ldb2), c_int(b2_rows), _p(D), c_int(out_mode), c_int(ldd),
+                                    _p(R), c_int(ldr), c_int(M), c_int(N), c_int(K), c_int(K2), c_int(n_store),
+                                    c_float(alpha), c_int(splits), c_int(seg_mode), segs, c_int(seg_r),
+                                    c_int(max_ctas), c_int(GEMM_DEBUG), _p(status_word(D.device)), _stream())
+        _chk(rc, "pm_gemm_bf16_2sm")
+        return
     rc = lib().pm_gemm_bf16(_p(A), c_int(a_mn), c_int(lda), c_int(a_rows), _p(B), c_int(b_mn), c_int(ldb),
                             c_int(b_rows), _p(A2), c_int(a2_mn), c_int(lda2), c_int(a2_k), _p(B2), c_int(b2_mn),
                             c_int(ldb2), c_int(b2_rows), _p(D), c_int(out_mode), c_int(ldd), _p(R), c_int(ldr),
                             c_int(M), c_int(N), c_int(K), c_int(K2), c_int(n_store), c_float(alpha), c_int(bn),
-                            c_int(splits), c_int(seg_mode), _seg_ends(seg_sizes) if seg_mode else None, c_int(seg_r),
-                            c_int(max_ctas), _p(status_word(D.device)), _stream())
+                            c_int(splits), c_int(seg_mode), segs, c_int(seg_r),
+                            c_int(max_ctas), c_int(GEMM_DEBUG), _p(status_word(D.device)), _stream())
     _chk(rc, "pm_gemm_bf16")
 
 

@@ -1,0 +1,183 @@
+"""End-to-end training job: config merge → model → tokenizer → dataset → loop → adapter files.
+
+Phase order and artefacts follow the reference orchestrator
+(crates/pmetal-trainer/src/orchestrator.rs:379-1332): explicit CLI values override YAML,
+``max_seq_len`` auto = min(max_position_embeddings, 8192), checkpoints under
+``<output>/checkpoints`` (keep 3), adaptive-LR control file ``.lr_control.json``, packed
+loop preferred over the padded loop, ``lora_weights.safetensors`` + ``adapter_config.json``
+written at the end by rank 0. Unlike the reference, sequence packing and the captured
+(CUDA-graph) step stay enabled in data-parallel runs.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+import logging
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional
+
+import torch
+
+from ..core.callbacks import LoggingCallback, MetricsJsonCallback, TrainingCallback
+from ..core.config import DatasetConfig, FullTrainingConfig, LoraConfig, ModelConfig, TrainingConfig
+from ..core.events import JobEvent, NullSink
+
+log = logging.getLogger("pmetal")
+
+
+@dataclass
+class TrainingJobConfig:
+    model: str = ""
+    dataset: str = ""
+    eval_dataset: Optional[str] = None
+    output: str = "./output"
+    lora: LoraConfig = field(default_factory=LoraConfig)
+    training: TrainingConfig = field(default_factory=TrainingConfig)
+    quantization: str = "none"          # none | nf4 | fp4 | int8
+    quant_block_size: int = 64
+    double_quant: bool = False
+    use_packing: bool = True
+    pack_max_seq_len: Optional[int] = None
+    packs_per_batch: Optional[int] = None
+    use_cuda_graph: bool = True
+    gradient_checkpointing_layers: int = 0
+    log_metrics: Optional[str] = None
+    resume: bool = False
+    adaptive_lr: bool = True
+    dataset_format: str = "auto"
+    custom_columns: Optional[object] = None
+    max_samples: Optional[int] = None
+    device: Optional[str] = None
+    dtype: str = "bfloat16"
+    distributed: bool = False
+    dp_impl: str = "fused"
+    cut_cross_entropy: bool = True
+    job_id: str = "train"
+
+    @classmethod
+    def from_yaml(cls, path: str) -> "TrainingJobConfig":
+        full = FullTrainingConfig.from_yaml(path)
+        return cls(model=full.model.model_id, dataset=full.dataset.dataset_id, output=full.training.output_dir,
+                   lora=full.lora, training=full.training, quantization=full.model.quantization,
+                   use_packing=full.training.use_packing, max_samples=full.dataset.max_samples)
+
+
+def run_training(job: TrainingJobConfig, phase_cb: Optional[Callable[[str], None]] = None,
+                 callbacks: Optional[List[TrainingCallback]] = None, sink=None) -> dict:
+    from ..data.chat_templates import ChatTemplate
+    from ..data.dataloader import DataLoader, PackedDataLoader
+    from ..data.dataset import TrainingDataset
+    from ..data.packing import compute_pack_seq_len
+    from ..data.tokenizer import ByteTokenizer, Tokenizer
+    from ..lora import apply_lora, load_adapter, save_adapter
+    from ..models.loader import load_pretrained
+    from .adaptive_lr import AdaptiveLrController
+    from .checkpoint import CheckpointManager
+    from .loop import TrainingLoop
+
+    sink = sink or NullSink()
+    sink.emit(JobEvent.started(job.job_id, "train"))
+
+    def phase(name: str):
+        sink.emit(JobEvent.phase(job.job_id, name))
+        if phase_cb:
+            phase_cb(name)
+        log.info("phase: %s", name)
+
+    t_start = time.time()
+    try:
+        out_dir = os.path.abspath(job.output)
+        os.makedirs(out_dir, exist_ok=True)
+        tcfg = job.training
+        tcfg.output_dir = out_dir
+        torch.manual_seed(tcfg.seed)
+        # ---- distributed context
+        dctx = None
+        if job.distributed or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            if job.dp_impl == "fused" and torch.cuda.is_available():
+                from ..parallel.dp import DistContext
+                DistContext.from_env()
+                from ..parallel.fused_dp import FusedDataParallel
+                dctx = FusedDataParallel()
+            else:
+                from ..parallel.dp import DistContext
+                dctx = DistContext.from_env()
+        rank = dctx.rank if dctx else 0
+        world = dctx.world_size if dctx else 1
+        dev = torch.device(job.device) if job.device else (
+            torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
+        dtype = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}[job.dtype]
+        if dev.type == "cpu":
+            dtype = torch.float32
+        # ---- model
+        phase("resolving_model")
+        phase("loading_model")
+        model, margs, model_dir = load_pretrained(job.model, dtype, dev, seed=tcfg.seed)
+        max_seq = tcfg.max_seq_len if tcfg.max_seq_len and tcfg.max_seq_len != 8192 else min(
+            margs.max_position_embeddings, 8192)
+        # ---- tokenizer + dataset
+        phase("loading_tokenizer")
+        tok = Tokenizer.from_model_dir(model_dir) if model_dir else ByteTokenizer()
+        template = ChatTemplate.from_model_dir(model_dir, job.model) if model_dir else None
+        phase("tokenizing_dataset")
+        ds = TrainingDataset.from_file_tokenized(job.dataset, tok, max_seq, job.dataset_format, template,
+                                                 job.custom_columns, job.max_samples)
+        stats = ds.stats()
+        log.info("dataset: %s", stats)
+        eval_ds = None
+        if job.eval_dataset:
+            eval_ds = TrainingDataset.from_file_tokenized(job.eval_dataset, tok, max_seq, job.dataset_format, template,
+                                                          job.custom_columns)
+        # ---- adapters
+        if job.quantization != "none":
+            from ..lora.qlora import quantize_base
+            quantize_base(model, job.quantization, job.quant_block_size, job.double_quant)
+        apply_lora(model, job.lora, seed=tcfg.seed)
+        if job.gradient_checkpointing_layers:
+            model.gradient_checkpointing = job.gradient_checkpointing_layers
+        model.prepare_for_training()
+        cbs = list(callbacks or []) + [LoggingCallback(tcfg.logging_steps)]
+        if job.log_metrics and rank == 0:
+            cbs.append(MetricsJsonCallback(job.log_metrics, config={"lora": dataclasses.asdict(job.lora),
+                                                                    "training": dataclasses.asdict(tcfg)}))
+        ckpt = CheckpointManager(os.path.join(out_dir, "checkpoints"), keep=3) if rank == 0 else None
+        adaptive = AdaptiveLrController.lora_preset(os.path.join(out_dir, ".lr_control.json")) if job.adaptive_lr else None
+        # ---- loaders
+        use_pack = job.use_packing and tcfg.use_packing
+        if use_pack:
+            pack_len = job.pack_max_seq_len or compute_pack_seq_len([len(s) for s in ds.samples], max_seq)
+            loader = PackedDataLoader(ds.samples, pack_len, job.packs_per_batch or tcfg.batch_size, True, tcfg.seed,
+                                      rank, world, tok.pad_token_id or 0)
+            log.info("packing: %s", loader.stats.summary())
+            if loader.stats.max_sequences_per_batch <= 1:     # nothing gained: fall back (run_packed.rs:99-105)
+                use_pack = False
+        if not use_pack:
+            loader = DataLoader(ds.samples, tcfg.batch_size, True, tcfg.seed, tok.pad_token_id or 0, max_seq, rank, world)
+        eval_loader = None
+        if eval_ds is not None:
+            eval_loader = DataLoader(eval_ds.samples, tcfg.batch_size, False, tcfg.seed, tok.pad_token_id or 0, max_seq)
+        per_epoch = max(len(loader) // max(tcfg.gradient_accumulation_steps, 1), 1)
+        total_steps = tcfg.max_steps or per_epoch * tcfg.num_epochs
+        loop = TrainingLoop(model, tcfg, cbs, dctx, job.lora.loraplus_lr_ratio, checkpoint_manager=ckpt,
+                            adaptive_lr=adaptive, total_steps=total_steps)
+        if job.resume and ckpt is not None and ckpt.latest_path():
+            loop.resume(ckpt.latest_path())
+            log.info("resumed from %s at step %d", ckpt.latest_path(), loop.state.step)
+        phase("training")
+        state = loop.run(loader, eval_loader)
+        # ---- save
+        phase("saving")
+        adapter_path = None
+        if rank == 0:
+            adapter_path = save_adapter(model, out_dir, job.lora, base_model=job.model)
+        if dctx:
+            dctx.barrier()
+        summary = {"steps": state.step, "final_loss": state.running_loss, "tokens": state.tokens_seen,
+                   "seconds": time.time() - t_start, "adapter": adapter_path, "output": out_dir}
+        sink.emit(JobEvent.completed(job.job_id, **summary))
+        return summary
+    except BaseException as e:
+        sink.emit(JobEvent.failed(job.job_id, f"{type(e).__name__}: {e}"))
+        raise
