@@ -624,3 +624,301 @@ extern "C" int pm_attn_bwd(const void* dout, const void* q, long long q_stride, 
   attn_bwd_dkv_kernel<<<gk, kAttnThreads, smem_dkv, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ================================================================================= paged-KV decode / verify attention
+// Attention of a few new query tokens per sequence against a block-paged KV cache (block = 64 tokens =
+// one key tile). Used for single-token decode (q_len 1), speculative verification (q_len = k+1) and
+// chunked prefill continuation. The rows of the 64-row query tile are the (query token, head-in-group)
+// pairs of one (sequence, kv head): row = i * rep + g. Key position t is visible to query token i iff
+// t <= seq_len - q_len + i. With n_split > 1 each CTA covers a slice of the key blocks and writes an
+// unnormalised partial (o, m, l) to scratch; `paged_attn_combine_kernel` merges the slices.
+// The reference has no paged attention kernel: its paged cache is gathered and concatenated into a dense
+// tensor before every SDPA call (crates/pmetal-mlx/src/kv_cache/paged.rs:262-530).
+namespace pm {
+
+struct PagedParams {
+  const __nv_bfloat16* q;        // [total_q, hq, 128]
+  const __nv_bfloat16* k_cache;  // [num_blocks, 64, hkv, 128]
+  const __nv_bfloat16* v_cache;
+  __nv_bfloat16* out;            // [total_q, hq, 128]
+  const int* block_table;        // [num_seqs, max_blocks]
+  const int* seq_lens;           // [num_seqs] keys available (new tokens included)
+  const int* q_start;            // [num_seqs] first query row of the sequence in q
+  const int* q_lens;             // [num_seqs]
+  float* part_o;                 // [n_split, total_q, hq, 128] (only when n_split > 1)
+  float* part_ml;                // [n_split, total_q, hq, 2]
+  int max_blocks, hq, hkv, n_split, total_q;
+  float scale;
+  int window;
+};
+
+__global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + kTileBytes;       // 2 buffers
+  uint8_t* sV = smem + 3 * kTileBytes;   // 2 buffers
+  const int seq = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+  const int rep = p.hq / p.hkv;
+  const int q_len = p.q_lens[seq], q0 = p.q_start[seq], kv_len = p.seq_lens[seq];
+  const int nq = q_len * rep;           // valid rows (<= 64)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  if (q_len <= 0 || kv_len <= 0) return;
+
+  const int n_blocks = (kv_len + kTile - 1) / kTile;
+  const int per = (n_blocks + p.n_split - 1) / p.n_split;
+  const int b0 = split * per, b1 = min(n_blocks, b0 + per);
+
+  // gather the query rows into the swizzled tile (rows >= nq are zero)
+  {
+    const uint32_t sbase = smem_addr(sQ);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = threadIdx.x + i * kAttnThreads;
+      const int r = idx >> 4, c = idx & 15;
+      const uint32_t dst = sbase + r * 256 + ((c ^ (r & 7)) << 4);
+      if (r < nq) {
+        const int qi = r / rep, gh = r - qi * rep;
+        cp_async16(dst, p.q + (static_cast<long long>(q0 + qi) * p.hq + hk * rep + gh) * kD + c * 8);
+      } else {
+        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0) : "memory");
+      }
+    }
+  }
+  const long long row_stride = static_cast<long long>(p.hkv) * kD;
+  const int* bt = p.block_table + static_cast<long long>(seq) * p.max_blocks;
+  auto kv_base = [&](const __nv_bfloat16* cache, int blk) {
+    return cache + (static_cast<long long>(bt[blk]) * kTile * p.hkv + hk) * kD;
+  };
+  if (b0 < b1) {
+    load_tile(sK, kv_base(p.k_cache, b0), row_stride, 0, kTile);
+    load_tile(sV, kv_base(p.v_cache, b0), row_stride, 0, kTile);
+  }
+  cp_async_commit();
+
+  float o_acc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o_acc[i][j] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float sl2 = p.scale * kLog2e;
+  const uint32_t q_tile = smem_addr(sQ);
+  const bool warp_active = warp * 16 < nq;
+  const int r_lo = warp * 16 + g;
+  // visible-key limit (inclusive) for the two rows this thread owns
+  const int lim_lo = kv_len - q_len + (r_lo / rep), lim_hi = kv_len - q_len + ((r_lo + 8) / rep);
+
+  for (int b = b0; b < b1; ++b) {
+    const int buf = (b - b0) & 1;
+    if (b + 1 < b1) {
+      load_tile(sK + (buf ^ 1) * kTileBytes, kv_base(p.k_cache, b + 1), row_stride, 0, kTile);
+      load_tile(sV + (buf ^ 1) * kTileBytes, kv_base(p.v_cache, b + 1), row_stride, 0, kTile);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (warp_active) {
+      const uint32_t k_tile = smem_addr(sK + buf * kTileBytes);
+      const uint32_t v_tile = smem_addr(sV + buf * kTileBytes);
+      float s[8][4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        uint32_t a[4];
+        load_a_frag(q_tile, warp * 16, kk * 16, lane, a);
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          uint32_t bb[4];
+          load_b_frag_nt(k_tile, np * 16, kk * 16, lane, bb);
+          mma_bf16(s[2 * np], a[0], a[1], a[2], a[3], bb[0], bb[1]);
+          mma_bf16(s[2 * np + 1], a[0], a[1], a[2], a[3], bb[2], bb[3]);
+        }
+      }
+      const int j0 = b * kTile;
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j0 + nt * 8 + 2 * t4 + (e & 1);
+          const int lim = (e < 2) ? lim_lo : lim_hi;
+          bool ok = j <= lim;
+          if (p.window > 0) ok = ok && (lim - j < p.window);
+          const float v = ok ? s[nt][e] * sl2 : -INFINITY;
+          s[nt][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+      }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);
+        m_use[r] = (m_new == -INFINITY) ? 0.f : m_new;
+        corr[r] = (m_run[r] == -INFINITY) ? 0.f : exp2f(m_run[r] - m_use[r]);
+        m_run[r] = m_new;
+        l_run[r] *= corr[r];
+      }
+      float rs[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pv = exp2f(s[nt][e] - m_use[e >> 1]);
+          s[nt][e] = pv;
+          rs[e >> 1] += pv;
+        }
+      l_run[0] += rs[0];
+      l_run[1] += rs[1];
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) {
+        o_acc[nt][0] *= corr[0]; o_acc[nt][1] *= corr[0];
+        o_acc[nt][2] *= corr[1]; o_acc[nt][3] *= corr[1];
+      }
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const uint32_t a0 = pack2(s[2 * kk][0], s[2 * kk][1]);
+        const uint32_t a1 = pack2(s[2 * kk][2], s[2 * kk][3]);
+        const uint32_t a2 = pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        const uint32_t a3 = pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int np = 0; np < 8; ++np) {
+          uint32_t bb[4];
+          load_b_frag_nn(v_tile, kk * 16, np * 16, lane, bb);
+          mma_bf16(o_acc[2 * np], a0, a1, a2, a3, bb[0], bb[1]);
+          mma_bf16(o_acc[2 * np + 1], a0, a1, a2, a3, bb[2], bb[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (!warp_active) return;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = r_lo + r * 8;
+    if (row >= nq) continue;
+    const int qi = row / rep, gh = row - qi * rep;
+    const long long orow = (static_cast<long long>(q0 + qi) * p.hq + hk * rep + gh);
+    if (p.n_split == 1) {
+      const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+      __nv_bfloat16* o = p.out + orow * kD;
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt)
+        *reinterpret_cast<uint32_t*>(o + nt * 8 + 2 * t4) = pack2(o_acc[nt][2 * r] * inv, o_acc[nt][2 * r + 1] * inv);
+    } else {
+      float* o = p.part_o + (static_cast<long long>(split) * p.total_q * p.hq + orow) * kD;
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt)
+        *reinterpret_cast<float2*>(o + nt * 8 + 2 * t4) = make_float2(o_acc[nt][2 * r], o_acc[nt][2 * r + 1]);
+      if (t4 == 0) {
+        float* ml = p.part_ml + (static_cast<long long>(split) * p.total_q * p.hq + orow) * 2;
+        ml[0] = m_run[r];
+        ml[1] = l_run[r];
+      }
+    }
+  }
+}
+
+// Merge the per-slice partials: one warp per (query row, head).
+__global__ void paged_attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                          __nv_bfloat16* __restrict__ out, int rows, int n_split) {
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (gw >= rows) return;
+  float m = -INFINITY;
+  for (int s = 0; s < n_split; ++s) m = fmaxf(m, part_ml[(static_cast<long long>(s) * rows + gw) * 2]);
+  float l = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < n_split; ++s) {
+    const float ms = part_ml[(static_cast<long long>(s) * rows + gw) * 2];
+    const float ls = part_ml[(static_cast<long long>(s) * rows + gw) * 2 + 1];
+    if (ms == -INFINITY) continue;
+    const float w = exp2f(ms - m);
+    l += ls * w;
+    const float4 o = *reinterpret_cast<const float4*>(part_o + (static_cast<long long>(s) * rows + gw) * kD + lane * 4);
+    acc[0] += o.x * w; acc[1] += o.y * w; acc[2] += o.z * w; acc[3] += o.w * w;
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  uint2 ov;
+  *reinterpret_cast<__nv_bfloat162*>(&ov.x) = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+  *reinterpret_cast<__nv_bfloat162*>(&ov.y) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+  *reinterpret_cast<uint2*>(out + static_cast<long long>(gw) * kD + lane * 4) = ov;
+}
+
+// Append new keys/values to the paged cache: slot[t] = block_id * 64 + offset for each new token.
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, long long k_stride,
+                                 const __nv_bfloat16* __restrict__ v, long long v_stride,
+                                 __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                 const long long* __restrict__ slots, int n_tokens, int hkv) {
+  const int per_tok = hkv * (kD / 8);   // 16-byte chunks per token
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+       i < static_cast<long long>(n_tokens) * per_tok; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / per_tok), c = static_cast<int>(i - static_cast<long long>(t) * per_tok);
+    const long long slot = slots[t];
+    if (slot < 0) continue;
+    const uint4 kv = *reinterpret_cast<const uint4*>(k + t * k_stride + c * 8);
+    const uint4 vv = *reinterpret_cast<const uint4*>(v + t * v_stride + c * 8);
+    *reinterpret_cast<uint4*>(k_cache + slot * hkv * kD + c * 8) = kv;
+    *reinterpret_cast<uint4*>(v_cache + slot * hkv * kD + c * 8) = vv;
+  }
+}
+
+}  // namespace pm
+
+// Scratch (part_o / part_ml) is needed only when n_split > 1:
+//   part_o  : n_split * total_q * hq * 128 floats,  part_ml : n_split * total_q * hq * 2 floats
+extern "C" int pm_paged_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                             const int* seq_lens, const int* q_start, const int* q_lens, float* part_o, float* part_ml,
+                             int num_seqs, int max_blocks, int total_q, int hq, int hkv, int n_split, float scale,
+                             int window, cudaStream_t st) {
+  if (hq % hkv || num_seqs <= 0) return -1;
+  if (n_split < 1 || (n_split > 1 && (!part_o || !part_ml))) return -2;
+  PagedParams p{};
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.block_table = block_table; p.seq_lens = seq_lens; p.q_start = q_start; p.q_lens = q_lens;
+  p.part_o = part_o; p.part_ml = part_ml;
+  p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.n_split = n_split; p.total_q = total_q;
+  p.scale = scale; p.window = window;
+  const int smem = 5 * kTileBytes;
+  static bool once = false;
+  if (!once) {
+    int e = set_smem(reinterpret_cast<const void*>(paged_attn_kernel), smem);
+    if (e) return e;
+    once = true;
+  }
+  dim3 grid(num_seqs, hkv, n_split);
+  paged_attn_kernel<<<grid, kAttnThreads, smem, st>>>(p);
+  int e = static_cast<int>(cudaGetLastError());
+  if (e || n_split == 1) return e;
+  const int rows = total_q * hq;
+  paged_attn_combine_kernel<<<(rows + 7) / 8, 256, 0, st>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), rows,
+                                                            n_split);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int pm_kv_append(const void* k, long long k_stride, const void* v, long long v_stride, void* k_cache,
+                            void* v_cache, const long long* slots, int n_tokens, int hkv, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  const long long work = static_cast<long long>(n_tokens) * hkv * 16;
+  int grid = static_cast<int>((work + 255) / 256);
+  if (grid > 148 * 8) grid = 148 * 8;
+  kv_append_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k), k_stride,
+                                         static_cast<const __nv_bfloat16*>(v), v_stride,
+                                         static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), slots,
+                                         n_tokens, hkv);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -59,13 +59,59 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtens
       "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
       : "memory");
 }
-__device__ __forceinline__ void load_operand_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int mn_major,
-                                                  int rows, int row0, int k0) {
+__device__ __forceinline__ void tma_load_2d_local(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar_addr, int c0,
+                                                  int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          dst_smem),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+template <bool kLocal>
+__device__ __forceinline__ void load_operand_pair_t(uint32_t dst, const CUtensorMap* map, uint32_t bar, int mn_major,
+                                                    int rows, int row0, int k0) {
   if (!mn_major) {
-    tma_load_2d_pair(dst, map, bar, k0, row0);
+    if (kLocal) tma_load_2d_local(dst, map, bar, k0, row0); else tma_load_2d_pair(dst, map, bar, k0, row0);
   } else {
-    for (int j = 0; j < rows / 64; ++j) tma_load_2d_pair(dst + j * 8192, map, bar, row0 + 64 * j, k0);
+    for (int j = 0; j < rows / 64; ++j) {
+      if (kLocal) tma_load_2d_local(dst + j * 8192, map, bar, row0 + 64 * j, k0);
+      else tma_load_2d_pair(dst + j * 8192, map, bar, row0 + 64 * j, k0);
+    }
   }
+}
+__device__ __forceinline__ void load_operand_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int mn_major,
+                                                  int rows, int row0, int k0, int local) {
+  if (local) load_operand_pair_t<true>(dst, map, bar, mn_major, rows, row0, k0);
+  else load_operand_pair_t<false>(dst, map, bar, mn_major, rows, row0, k0);
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// bounded wait on a barrier that the partner CTA arrives on
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* g_status, int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++spins & 255u) == 0u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (g_status) atomicCAS(g_status, 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
@@ -92,6 +138,16 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                : "memory");
 }
+// One commit that arrives on the barrier at the same shared-memory offset in both CTAs of the pair
+// (a barrier signal, not a data copy).
+__device__ __forceinline__ void umma_commit_both(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
 // kind::f16, bf16 x bf16 -> fp32, M = 256 across the pair
 __device__ __forceinline__ uint32_t make_idesc_bf16_m256(uint32_t n, uint32_t a_mn, uint32_t b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (a_mn << 15) | (b_mn << 16) | ((n >> 3) << 17) | ((256u >> 4) << 24);
@@ -114,7 +170,8 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint64_t* empty_bar = full_bar + kMaxStages;
   uint64_t* tfull_bar = empty_bar + kMaxStages;   // [2]
   uint64_t* tempty_bar = tfull_bar + 2;           // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* pfull_bar = tempty_bar + 2;           // [kMaxStages] leader only: "the partner's half has landed"
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pfull_bar + kMaxStages);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -126,6 +183,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     for (int i = 0; i < p.stages; ++i) {
       mbar_init(&full_bar[i], 1);     // leader producer's expect_tx arrive; bytes from both CTAs
       mbar_init(&empty_bar[i], 1);    // one tcgen05.commit
+      mbar_init(&pfull_bar[i], 1);    // one remote arrive from the partner's forwarder
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull_bar[i], 1);    // one tcgen05.commit
@@ -177,26 +235,47 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const int s = it % p.stages;
           const uint32_t ph = (it / p.stages) & 1;
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.status, kTimeoutProducer)) { ok = false; break; }
-          const uint32_t fb = map_to_cta(smem_u32(&full_bar[s]), 0);   // the leader's full barrier
           const int nsub = min(kps, kb1 - kb);
-          if (leader) mbar_expect_tx(&full_bar[s], 2 * nsub * kPairStageBytes);
+          uint32_t fb;
+          if (p.fwd_full) {   // every CTA counts its own bytes on its own barrier
+            fb = smem_u32(&full_bar[s]);
+            mbar_expect_tx(&full_bar[s], nsub * kPairStageBytes);
+          } else {            // both CTAs' bytes are counted on the leader's barrier
+            fb = map_to_cta(smem_u32(&full_bar[s]), 0);
+            if (leader) mbar_expect_tx(&full_bar[s], 2 * nsub * kPairStageBytes);
+          }
           for (int j = 0; j < nsub; ++j) {
             const uint32_t sa = smem_u32(smem + s * stage_bytes + j * kPairStageBytes);
             const uint32_t sb = sa + a_bytes;
             const int kbj = kb + j;
             if (kbj < p.nk1) {
-              load_operand_pair(sa, &map_a, fb, p.a_mn, kBM, m0, kbj * kBK);
-              load_operand_pair(sb, &map_b, fb, p.b_mn, kHalfBN, n0 + b_off, kbj * kBK);
+              load_operand_pair(sa, &map_a, fb, p.a_mn, kBM, m0, kbj * kBK, p.fwd_full);
+              load_operand_pair(sb, &map_b, fb, p.b_mn, kHalfBN, n0 + b_off, kbj * kBK, p.fwd_full);
             } else {
               const int k0 = (kbj - p.nk1) * kBK;
-              load_operand_pair(sa, &map_a2, fb, p.a2_mn, kBM, m0, k0 + a2_off);
-              load_operand_pair(sb, &map_b2, fb, p.b2_mn, kHalfBN, n0, k0);
+              load_operand_pair(sa, &map_a2, fb, p.a2_mn, kBM, m0, k0 + a2_off, p.fwd_full);
+              load_operand_pair(sb, &map_b2, fb, p.b2_mn, kHalfBN, n0, k0, p.fwd_full);
             }
           }
         }
       }
     }
   } else if (warp == 1) {
+    // ------------------------------------------------------------------ partner CTA: forward "stage landed"
+    if (lane == 0 && !leader && p.fwd_full) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = first; w < total && ok; w += stride) {
+        const int split = w % p.splits;
+        const int kb0 = split * per_split, kb1 = min(nk, kb0 + per_split);
+        for (int kb = kb0; kb < kb1; kb += kps, ++it) {
+          const int s = it % p.stages;
+          const uint32_t ph = (it / p.stages) & 1;
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
+          mbar_arrive_cluster(map_to_cta(smem_u32(&pfull_bar[s]), 0));
+        }
+      }
+    }
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && leader) {
       uint32_t it = 0, acc_it = 0;
@@ -207,7 +286,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (kb0 >= kb1) continue;
         const int buf = acc_it & 1;
         const uint32_t aph = (acc_it >> 1) & 1;
-        if (!mbar_wait(&tempty_bar[buf], aph ^ 1, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
+        if (!mbar_wait_cluster(&tempty_bar[buf], aph ^ 1, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kPairBN;
         uint32_t accumulate = 0;
@@ -215,6 +294,10 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const int s = it % p.stages;
           const uint32_t ph = (it / p.stages) & 1;
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
+          if (p.fwd_full && !mbar_wait_cluster(&pfull_bar[s], ph, abort_flag, p.status, kTimeoutMma)) {
+            ok = false;
+            break;
+          }
           tc_fence_after();
           const int nsub = min(kps, kb1 - kb);
           for (int js = 0; js < nsub; ++js) {
@@ -241,12 +324,20 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             }
           }
           // the stage is free in both CTAs once these MMAs have read it
-          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 0));
-          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 1));
+          if (p.commit_both) {
+            umma_commit_both(&empty_bar[s]);
+          } else {
+            umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 0));
+            umma_commit_pair(map_to_cta(smem_u32(&empty_bar[s]), 1));
+          }
         }
         if (ok) {
-          umma_commit_pair(map_to_cta(smem_u32(&tfull_bar[buf]), 0));
-          umma_commit_pair(map_to_cta(smem_u32(&tfull_bar[buf]), 1));
+          if (p.commit_both) {
+            umma_commit_both(&tfull_bar[buf]);
+          } else {
+            umma_commit_pair(map_to_cta(smem_u32(&tfull_bar[buf]), 0));
+            umma_commit_pair(map_to_cta(smem_u32(&tfull_bar[buf]), 1));
+          }
         }
         ++acc_it;
       }
@@ -325,6 +416,8 @@ extern "C" int pm_gemm_bf16_2sm(const void* A, int a_mn, int lda, int a_rows, co
   p.status = status;
   p.debug = debug & 3;
   p.kps = (debug & 4) ? 1 : 2;
+  p.commit_both = 0;
+  p.fwd_full = (debug & 8) ? 1 : 0;
   int stages = (227 * 1024 - 2048) / (p.kps * kPairStageBytes);
   if (stages > kMaxStages) stages = kMaxStages;
   if ((debug >> 4) > 0 && (debug >> 4) < stages) stages = debug >> 4;
@@ -341,7 +434,7 @@ extern "C" int pm_gemm_bf16_2sm(const void* A, int a_mn, int lda, int a_rows, co
   } else {
     ma2 = ma; mb2 = mb;
   }
-  const size_t smem = static_cast<size_t>(stages) * p.kps * kPairStageBytes + 1024 + 256;
+  const size_t smem = static_cast<size_t>(stages) * p.kps * kPairStageBytes + 1024 + 512;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);

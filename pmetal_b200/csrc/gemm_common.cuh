@@ -28,6 +28,8 @@ struct GemmParams {
   int seg_r;
   int tmem_cols;
   int kps;         // K blocks per pipeline stage (CTA-pair kernel)
+  int fwd_full;    // CTA-pair kernel: each CTA counts its own TMA bytes; the partner forwards one arrive per stage
+  int commit_both; // CTA-pair kernel: signal both CTAs' barriers with one commit
   int debug;       // bit 0: skip epilogue stores, bit 1: skip MMA issue (timing experiments only)
   int* status;
 };

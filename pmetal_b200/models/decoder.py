@@ -291,6 +291,81 @@ class DecoderLM(nn.Module):
             tgt[:-1] = flat[1:]
         return ops.causal_lm_loss(h, self.head_weight(), tgt, -100, self.head_t, self.cfg.final_logit_softcap)
 
+    # ------------------------------------------------------------------ cached (paged) forward
+    @torch.no_grad()
+    def forward_paged(self, input_ids: torch.Tensor, cache, meta, all_logits: bool = False,
+                      return_hidden: bool = False) -> torch.Tensor:
+        """Forward over the new tokens of several sequences with a paged KV cache.
+
+        ``input_ids`` [total_q] are the new tokens in ``meta`` order; keys/values are appended to ``cache`` and
+        attention reads the block table directly. Returns logits for the last new token of every sequence
+        ([n_seq, V]) or for every new token ([total_q, V], speculative verification)."""
+        cfg = self.cfg
+        hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        x = F.embedding(input_ids, self.embed_tokens)
+        native = ops.use_native(x) and d == 128
+        rope = ops.rope_table(meta.positions, d, cfg.rope_theta, cfg.rope_scale)
+        T = x.shape[0]
+        for li, layer in enumerate(self.layers):
+            at = layer.self_attn
+            n1 = ops.rms_norm(x, layer.input_layernorm, cfg.rms_norm_eps)
+            qkv = at.qkv_proj(n1)
+            if native:
+                from ..ops import native as nat
+                q, k = nat.qknorm_rope_fwd(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, cfg.rms_norm_eps)
+                v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+                nat.kv_append(k, v, cache.k[li], cache.v[li], meta.slots)
+                o = nat.paged_attn(q, cache.k[li], cache.v[li], meta, d ** -0.5, at.window).view(T, hq * d)
+            else:
+                o = self._paged_attention_reference(qkv, at, rope, cache, meta, li)
+            h = at.o_proj(o, x)
+            n2 = ops.rms_norm(h, layer.post_attention_layernorm, cfg.rms_norm_eps)
+            x = layer.mlp(n2, h)
+        x = ops.rms_norm(x, self.norm, cfg.rms_norm_eps)
+        if not all_logits:
+            last = (meta.q_start + meta.q_lens - 1).long()
+            x = x[last]
+        return x if return_hidden else self.logits(x)
+
+    def _paged_attention_reference(self, qkv, at, rope, cache, meta, li):
+        from ..ops import reference as ref
+        cfg = self.cfg
+        hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        T = qkv.shape[0]
+        q = qkv[:, :hq * d].view(T, hq, d)
+        k = qkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d)
+        v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+        if at.q_norm is not None:
+            q, k = ref.rms_norm(q, at.q_norm, cfg.rms_norm_eps), ref.rms_norm(k, at.k_norm, cfg.rms_norm_eps)
+        q, k = ref.apply_rope(q, rope[0], rope[1]), ref.apply_rope(k, rope[0], rope[1])
+        kc, vc = cache.k[li].view(-1, hkv, d), cache.v[li].view(-1, hkv, d)
+        kc[meta.slots] = k.to(kc.dtype)
+        vc[meta.slots] = v.to(vc.dtype)
+        out = torch.empty(T, hq, d, dtype=qkv.dtype, device=qkv.device)
+        qs, ql = meta.q_start.tolist(), meta.q_lens.tolist()
+        rep = hq // hkv
+        for i, sid in enumerate(meta.seq_ids):
+            K, V = cache.gather(li, sid)
+            L, n = K.shape[0], ql[i]
+            qq = q[qs[i]:qs[i] + n].transpose(0, 1).float()
+            kk = K.transpose(0, 1).float().repeat_interleave(rep, 0)
+            vv = V.transpose(0, 1).float().repeat_interleave(rep, 0)
+            sc = torch.matmul(qq, kk.transpose(1, 2)) * d ** -0.5
+            qpos = torch.arange(L - n, L, device=qkv.device)[:, None]
+            kpos = torch.arange(L, device=qkv.device)[None, :]
+            mask = kpos <= qpos
+            if at.window > 0:
+                mask &= kpos > qpos - at.window
+            sc = sc.masked_fill(~mask, float("-inf"))
+            out[qs[i]:qs[i] + n] = torch.matmul(sc.softmax(-1), vv).transpose(0, 1).to(out.dtype)
+        return out.view(T, hq * d)
+
+    def new_cache(self, num_blocks: int, dtype=None, device=None):
+        from .kv_cache import PagedKVCache
+        p = self.embed_tokens
+        return PagedKVCache(self.cfg.num_hidden_layers, self.cfg.num_key_value_heads, self.cfg.head_dim, num_blocks,
+                            dtype or p.dtype, device or p.device)
+
     # ------------------------------------------------------------------ checkpoint name mapping
     def hf_state_dict(self, merged: bool = False) -> Dict[str, torch.Tensor]:
         sd: Dict[str, torch.Tensor] = {"model.embed_tokens.weight": self.embed_tokens.detach(),

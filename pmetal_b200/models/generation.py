@@ -1,0 +1,199 @@
+"""Text generation on the paged KV cache.
+
+``Generator`` runs any number of sequences in lock-step: chunked prefill (2048 tokens per chunk,
+crates/pmetal-models/src/generation.rs:316-355), then batched single-token decode steps with
+per-row sampling, stop tokens and length limits. It is the engine under ``pmetal infer``, the
+batched RL rollouts (the reference decodes the G rollouts of a group one by one,
+rl_generation.rs:285-420; here they share the prompt blocks and decode as one batch) and
+speculative decoding (``speculative.py``).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Iterator, List, Optional, Sequence
+
+import torch
+
+from .kv_cache import BLOCK, PagedKVCache
+from .sampling import Sampler, SamplingParams
+
+PREFILL_CHUNK = 2048
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[List[int]]
+    logprobs: Optional[List[List[float]]] = None
+    finish_reasons: List[str] = field(default_factory=list)
+    prompt_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_seconds: float = 0.0
+
+    @property
+    def generated_tokens(self) -> int:
+        return sum(len(t) for t in self.tokens)
+
+    @property
+    def decode_tok_per_s(self) -> float:
+        return self.generated_tokens / self.decode_seconds if self.decode_seconds > 0 else 0.0
+
+    @property
+    def prefill_tok_per_s(self) -> float:
+        return self.prompt_tokens / self.prefill_seconds if self.prefill_seconds > 0 else 0.0
+
+
+class Generator:
+    def __init__(self, model, cache: Optional[PagedKVCache] = None, num_blocks: Optional[int] = None):
+        self.model = model
+        self.device = model.embed_tokens.device
+        if cache is None:
+            cache = model.new_cache(num_blocks or 4096)
+        self.cache = cache
+        self._next_id = 0
+
+    def new_seq(self) -> int:
+        sid = self._next_id
+        self._next_id += 1
+        self.cache.add_sequence(sid)
+        return sid
+
+    # ------------------------------------------------------------------ prefill / decode primitives
+    @torch.no_grad()
+    def prefill(self, seq_ids: Sequence[int], prompts: Sequence[Sequence[int]], chunk: int = PREFILL_CHUNK):
+        """Feed whole prompts (chunked); returns logits of each prompt's last token [n, V]."""
+        n = len(seq_ids)
+        offs = [0] * n
+        last_logits = [None] * n
+        while True:
+            ids, sids, counts = [], [], []
+            budget = chunk
+            for i in range(n):
+                rem = len(prompts[i]) - offs[i]
+                if rem <= 0 or budget <= 0:
+                    continue
+                take = min(rem, budget)
+                ids.extend(prompts[i][offs[i]:offs[i] + take])
+                sids.append(i)
+                counts.append(take)
+                budget -= take
+            if not sids:
+                break
+            meta = self.cache.prepare([seq_ids[i] for i in sids], counts)
+            t = torch.tensor(ids, dtype=torch.int64, device=self.device)
+            logits = self.model.forward_paged(t, self.cache, meta)
+            for j, i in enumerate(sids):
+                offs[i] += counts[j]
+                if offs[i] == len(prompts[i]):
+                    last_logits[i] = logits[j]
+        return torch.stack(last_logits)
+
+    @torch.no_grad()
+    def decode_step(self, seq_ids: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
+        """One new token per sequence → next-token logits [n, V]."""
+        meta = self.cache.prepare(seq_ids, [1] * len(seq_ids))
+        return self.model.forward_paged(tokens, self.cache, meta)
+
+    # ------------------------------------------------------------------ full loop
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[SamplingParams] = None,
+                 eos_ids: Sequence[int] = (), num_return_sequences: int = 1, return_logprobs: bool = False,
+                 on_token: Optional[Callable[[int, int], None]] = None, keep_sequences: bool = False,
+                 track_history: bool = True) -> GenerationResult:
+        """Generate for every prompt (``num_return_sequences`` samples each, sharing the prompt's KV blocks)."""
+        p = params or SamplingParams()
+        sampler = Sampler(p, self.device)
+        stop = set(eos_ids) | set(p.stop_token_ids)
+        G = num_return_sequences
+        t0 = time.perf_counter()
+        base_ids = [self.new_seq() for _ in prompts]
+        logits = self.prefill(base_ids, prompts)
+        seq_ids: List[int] = []
+        for b in base_ids:
+            seq_ids.append(b)
+            for _ in range(G - 1):
+                sid = self._next_id
+                self._next_id += 1
+                self.cache.fork(b, sid)
+                seq_ids.append(sid)
+        if G > 1:
+            logits = logits.repeat_interleave(G, dim=0)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        n = len(seq_ids)
+        V = logits.shape[-1]
+        counts = None
+        if track_history and (p.repetition_penalty != 1.0 or p.frequency_penalty or p.presence_penalty):
+            counts = torch.zeros(n, V, dtype=torch.int32, device=self.device)
+            for i, pr in enumerate(prompts):
+                c = torch.bincount(torch.tensor(pr, device=self.device), minlength=V).to(torch.int32)
+                counts[i * G:(i + 1) * G] = c
+        out: List[List[int]] = [[] for _ in range(n)]
+        lps: List[List[float]] = [[] for _ in range(n)]
+        reasons = ["length"] * n
+        alive = list(range(n))
+        for step in range(p.max_tokens):
+            cur_counts = counts[alive] if counts is not None else None
+            if return_logprobs:
+                ids, lp = sampler.sample(logits, cur_counts, True)
+                lp_l = lp.tolist()
+            else:
+                ids = sampler.sample(logits, cur_counts)
+            id_l = ids.tolist()
+            keep = []
+            for j, i in enumerate(alive):
+                tok = id_l[j]
+                out[i].append(tok)
+                if return_logprobs:
+                    lps[i].append(lp_l[j])
+                if on_token:
+                    on_token(i, tok)
+                if tok in stop:
+                    reasons[i] = "stop"
+                else:
+                    keep.append(j)
+            if counts is not None:
+                counts[alive, ids] += 1
+            if not keep or step == p.max_tokens - 1:
+                break
+            if len(keep) != len(alive):
+                sel = torch.tensor(keep, device=self.device)
+                ids = ids[sel]
+                alive = [alive[j] for j in keep]
+            logits = self.decode_step([seq_ids[i] for i in alive], ids)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        if not keep_sequences:
+            for sid in seq_ids:
+                self.cache.free_sequence(sid)
+        res = GenerationResult(out, lps if return_logprobs else None, reasons, sum(len(x) for x in prompts),
+                               t1 - t0, t2 - t1)
+        res.seq_ids = seq_ids
+        return res
+
+    def stream(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+               eos_ids: Sequence[int] = ()) -> Iterator[int]:
+        """Yield tokens of a single sequence as they are sampled."""
+        p = params or SamplingParams()
+        sampler = Sampler(p, self.device)
+        stop = set(eos_ids) | set(p.stop_token_ids)
+        sid = self.new_seq()
+        try:
+            logits = self.prefill([sid], [prompt])
+            counts = None
+            if p.repetition_penalty != 1.0 or p.frequency_penalty or p.presence_penalty:
+                counts = torch.bincount(torch.tensor(list(prompt), device=self.device),
+                                        minlength=logits.shape[-1]).to(torch.int32)[None]
+            for _ in range(p.max_tokens):
+                ids = sampler.sample(logits, counts)
+                tok = int(ids[0])
+                yield tok
+                if tok in stop:
+                    break
+                if counts is not None:
+                    counts[0, tok] += 1
+                logits = self.decode_step([sid], ids)
+        finally:
+            self.cache.free_sequence(sid)

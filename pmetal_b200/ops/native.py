@@ -44,7 +44,7 @@ def _load():
         pass
     for fn in ("pm_gemm_bf16", "pm_gemm_bf16_2sm", "pm_rmsnorm_fwd", "pm_rmsnorm_bwd", "pm_rope_table", "pm_qknorm_rope_fwd",
                "pm_qknorm_rope_bwd", "pm_swiglu_fwd", "pm_swiglu_bwd", "pm_ce_fwd_bwd", "pm_sumsq", "pm_adamw_flat",
-               "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16"):
+               "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16", "pm_paged_attn", "pm_kv_append"):
         getattr(_LIB, fn).restype = c_int
 
 
@@ -384,3 +384,32 @@ def adamw_flat(p, g, m, v, shadow, lr_mult, wd, gnorm_sq, lr, b1, b2, eps, step,
     _chk(lib().pm_adamw_flat(_p(p), _p(g), _p(m), _p(v), _p(shadow), _p(lr_mult), _p(wd), _p(gnorm_sq), _p(hp),
                              c_ll(p.numel()), c_float(lr), c_float(b1), c_float(b2), c_float(eps), c_int(step),
                              c_float(grad_scale), c_float(max_norm or 0.0), _stream()), "pm_adamw_flat")
+
+
+# ------------------------------------------------------------------------------------------- paged KV
+def kv_append(k, v, k_cache, v_cache, slots) -> None:
+    """k, v: [n, hkv, 128] (token stride arbitrary) -> cache [num_blocks, 64, hkv, 128] at ``slots``."""
+    n, hkv, _ = k.shape
+    _chk(lib().pm_kv_append(_p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)), _p(k_cache), _p(v_cache), _p(slots),
+                            c_int(n), c_int(hkv), _stream()), "pm_kv_append")
+
+
+def paged_attn(q, k_cache, v_cache, meta, scale: float, window: int = 0, n_split: int = 0):
+    """q: [total_q, hq, 128]; ``meta`` is a ``BatchMeta``. Long single sequences are split over key blocks."""
+    total_q, hq, _ = q.shape
+    hkv = k_cache.shape[2]
+    n_seq = meta.block_table.shape[0]
+    if n_split <= 0:
+        ctas = n_seq * hkv
+        n_blocks = -(-meta.max_kv // 64)
+        n_split = max(1, min(n_blocks // 4, 296 // max(ctas, 1), 32)) if ctas < 148 else 1
+    out = torch.empty_like(q)
+    po = pml = None
+    if n_split > 1:
+        po = torch.empty(n_split, total_q, hq, 128, dtype=torch.float32, device=q.device)
+        pml = torch.empty(n_split, total_q, hq, 2, dtype=torch.float32, device=q.device)
+    _chk(lib().pm_paged_attn(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(meta.block_table), _p(meta.seq_lens),
+                             _p(meta.q_start), _p(meta.q_lens), _p(po), _p(pml), c_int(n_seq),
+                             c_int(meta.block_table.shape[1]), c_int(total_q), c_int(hq), c_int(hkv), c_int(n_split),
+                             c_float(scale), c_int(window), _stream()), "pm_paged_attn")
+    return out

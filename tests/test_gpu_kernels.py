@@ -243,3 +243,66 @@ def test_adamw_and_sumsq():
                            wd[c].item())
     _close(p, pr, rtol=1e-5, atol=1e-6, what="adamw p")
     _close(sh, pr, rtol=1e-2, atol=1e-2, what="adamw shadow")
+
+
+@pytest.mark.parametrize("hq,hkv,lens,qlens", [(4, 2, [70, 1, 300], [1, 1, 1]), (8, 1, [200, 64], [5, 3]),
+                                               (2, 2, [5000], [1]), (4, 2, [130, 257], [130, 2])])
+def test_paged_attention_and_append(hq, hkv, lens, qlens):
+    nat = _nat()
+    from pmetal_b200.models.kv_cache import PagedKVCache
+    torch.manual_seed(11)
+    d = 128
+    cache = PagedKVCache(1, hkv, d, 256, torch.bfloat16, "cuda")
+    ks, vs = [], []
+    for i, (L, n) in enumerate(zip(lens, qlens)):
+        cache.add_sequence(i)
+        k, v = _rand(L, hkv, d), _rand(L, hkv, d)
+        ks.append(k); vs.append(v)
+        if L - n > 0:
+            slots = torch.tensor(cache.reserve(i, L - n), device="cuda")
+            nat.kv_append(k[:L - n], v[:L - n], cache.k[0], cache.v[0], slots)
+    meta = cache.prepare(list(range(len(lens))), qlens)
+    knew = torch.cat([k[L - n:] for k, L, n in zip(ks, lens, qlens)])
+    vnew = torch.cat([v[L - n:] for v, L, n in zip(vs, lens, qlens)])
+    nat.kv_append(knew, vnew, cache.k[0], cache.v[0], meta.slots)
+    for i in range(len(lens)):
+        kk, vv = cache.gather(0, i)
+        assert torch.equal(kk, ks[i]) and torch.equal(vv, vs[i])
+    q = _rand(meta.total_q, hq, d)
+    scale = d ** -0.5
+    outs = [nat.paged_attn(q, cache.k[0], cache.v[0], meta, scale, 0, n_split=s) for s in (1, 3)]
+    rep = hq // hkv
+    qs = meta.q_start.tolist()
+    for i, (L, n) in enumerate(zip(lens, qlens)):
+        qq = q[qs[i]:qs[i] + n].float().transpose(0, 1)
+        kk = ks[i].float().transpose(0, 1).repeat_interleave(rep, 0)
+        vv = vs[i].float().transpose(0, 1).repeat_interleave(rep, 0)
+        sc = qq @ kk.transpose(1, 2) * scale
+        qpos = torch.arange(L - n, L, device="cuda")[:, None]
+        sc = sc.masked_fill(torch.arange(L, device="cuda")[None, :] > qpos, float("-inf"))
+        ref = (sc.softmax(-1) @ vv).transpose(0, 1)
+        for o in outs:
+            _close(o[qs[i]:qs[i] + n], ref, what=f"paged attn seq {i}")
+
+
+def test_generation_native_matches_reference_path():
+    _nat()
+    from pmetal_b200.models.config import ModelArgs
+    from pmetal_b200.models.decoder import DecoderLM
+    from pmetal_b200.models.generation import Generator
+    from pmetal_b200.models.sampling import SamplingParams
+    from pmetal_b200.ops import functional as F
+    cfg = ModelArgs(vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                    num_attention_heads=2, num_key_value_heads=1, head_dim=128)
+    m = DecoderLM(cfg).init_weights(0.05, 0).to("cuda").to(torch.bfloat16).eval()
+    for p in m.parameters():
+        p.requires_grad_(False)
+    prompts = [torch.randint(0, 2048, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (7, 150)]
+    g = Generator(m, num_blocks=64)
+    meta_logits = g.prefill([g.new_seq(), g.new_seq()], prompts)
+    with F.force_reference():
+        g2 = Generator(m, num_blocks=64)
+        ref_logits = g2.prefill([g2.new_seq(), g2.new_seq()], prompts)
+    _close(meta_logits, ref_logits, rtol=5e-2, atol=5e-2, what="prefill logits")
+    out = Generator(m, num_blocks=64).generate(prompts, SamplingParams.greedy(8))
+    assert all(len(t) == 8 for t in out.tokens)
