@@ -261,8 +261,13 @@ def main() -> None:
             "final_loss": round(last_loss, 4),
         }
         print(json.dumps(out))
+    sys.stdout.flush()
     if world > 1:
-        dist.destroy_process_group()
+        # leave without the collective teardown: destroying a communicator whose collectives were captured in a
+        # CUDA graph can block for minutes, and nothing after this point needs it
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -110,8 +110,9 @@ def make_cases(T: int = 16384):
         inv = torch.ones(1, device="cuda")
         from ctypes import c_int, c_longlong
         L = nat.lib()
-        return (lambda: L.pm_ce_fwd_bwd(nat._p(lg), c_longlong(V), nat._p(lab), nat._p(loss), nat._p(inv), c_int(2048),
-                                        c_int(V), c_longlong(-100), c_int(1), nat._stream())), 0.0, 2.0 * 2048 * V * 3
+        return (lambda: L.pm_ce_fwd_bwd(nat._p(lg), c_longlong(V), nat._p(lab), nat._p(loss), nat._p(inv), nat._p(None),
+                                        nat._p(None), c_int(2048), c_int(V), c_longlong(-100), c_int(1),
+                                        nat._stream())), 0.0, 2.0 * 2048 * V * 3
 
     def adam():
         n = 10 * 1024 * 1024

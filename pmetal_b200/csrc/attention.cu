@@ -647,7 +647,7 @@ struct PagedParams {
   const int* q_lens;             // [num_seqs]
   float* part_o;                 // [n_split, total_q, hq, 128] (only when n_split > 1)
   float* part_ml;                // [n_split, total_q, hq, 2]
-  int max_blocks, hq, hkv, n_split, total_q;
+  int max_blocks, hq, hkv, n_split, total_q, q_tiles;
   float scale;
   int window;
 };
@@ -657,15 +657,18 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
   uint8_t* sQ = smem;
   uint8_t* sK = smem + kTileBytes;       // 2 buffers
   uint8_t* sV = smem + 3 * kTileBytes;   // 2 buffers
-  const int seq = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+  const int seq = blockIdx.x / p.q_tiles, row_base = (blockIdx.x % p.q_tiles) * kTile;
+  const int hk = blockIdx.y, split = blockIdx.z;
   const int rep = p.hq / p.hkv;
   const int q_len = p.q_lens[seq], q0 = p.q_start[seq], kv_len = p.seq_lens[seq];
-  const int nq = q_len * rep;           // valid rows (<= 64)
+  const int nq = q_len * rep - row_base;   // valid rows of this 64-row tile
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
-  if (q_len <= 0 || kv_len <= 0) return;
+  if (q_len <= 0 || kv_len <= 0 || nq <= 0) return;
 
-  const int n_blocks = (kv_len + kTile - 1) / kTile;
+  // keys visible to the last row of this tile bound the block range (causal)
+  const int last_row = min(row_base + kTile, q_len * rep) - 1;
+  const int n_blocks = (kv_len - q_len + last_row / rep) / kTile + 1;
   const int per = (n_blocks + p.n_split - 1) / p.n_split;
   const int b0 = split * per, b1 = min(n_blocks, b0 + per);
 
@@ -678,7 +681,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
       const int r = idx >> 4, c = idx & 15;
       const uint32_t dst = sbase + r * 256 + ((c ^ (r & 7)) << 4);
       if (r < nq) {
-        const int qi = r / rep, gh = r - qi * rep;
+        const int gr = row_base + r;
+        const int qi = gr / rep, gh = gr - qi * rep;
         cp_async16(dst, p.q + (static_cast<long long>(q0 + qi) * p.hq + hk * rep + gh) * kD + c * 8);
       } else {
         asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0) : "memory");
@@ -707,7 +711,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
   const bool warp_active = warp * 16 < nq;
   const int r_lo = warp * 16 + g;
   // visible-key limit (inclusive) for the two rows this thread owns
-  const int lim_lo = kv_len - q_len + (r_lo / rep), lim_hi = kv_len - q_len + ((r_lo + 8) / rep);
+  const int lim_lo = kv_len - q_len + ((row_base + r_lo) / rep), lim_hi = kv_len - q_len + ((row_base + r_lo + 8) / rep);
 
   for (int b = b0; b < b1; ++b) {
     const int buf = (b - b0) & 1;
@@ -807,8 +811,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
   }
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    const int row = r_lo + r * 8;
-    if (row >= nq) continue;
+    if (r_lo + r * 8 >= nq) continue;
+    const int row = row_base + r_lo + r * 8;
     const int qi = row / rep, gh = row - qi * rep;
     const long long orow = (static_cast<long long>(q0 + qi) * p.hq + hk * rep + gh);
     if (p.n_split == 1) {
@@ -880,8 +884,8 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, long long 
 //   part_o  : n_split * total_q * hq * 128 floats,  part_ml : n_split * total_q * hq * 2 floats
 extern "C" int pm_paged_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                              const int* seq_lens, const int* q_start, const int* q_lens, float* part_o, float* part_ml,
-                             int num_seqs, int max_blocks, int total_q, int hq, int hkv, int n_split, float scale,
-                             int window, cudaStream_t st) {
+                             int num_seqs, int max_blocks, int total_q, int max_q, int hq, int hkv, int n_split,
+                             float scale, int window, cudaStream_t st) {
   if (hq % hkv || num_seqs <= 0) return -1;
   if (n_split < 1 || (n_split > 1 && (!part_o || !part_ml))) return -2;
   PagedParams p{};
@@ -893,6 +897,8 @@ extern "C" int pm_paged_attn(const void* q, const void* k_cache, const void* v_c
   p.part_o = part_o; p.part_ml = part_ml;
   p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.n_split = n_split; p.total_q = total_q;
   p.scale = scale; p.window = window;
+  p.q_tiles = (max_q * (hq / hkv) + kTile - 1) / kTile;
+  if (p.q_tiles < 1) p.q_tiles = 1;
   const int smem = 5 * kTileBytes;
   static bool once = false;
   if (!once) {
@@ -900,7 +906,7 @@ extern "C" int pm_paged_attn(const void* q, const void* k_cache, const void* v_c
     if (e) return e;
     once = true;
   }
-  dim3 grid(num_seqs, hkv, n_split);
+  dim3 grid(num_seqs * p.q_tiles, hkv, n_split);
   paged_attn_kernel<<<grid, kAttnThreads, smem, st>>>(p);
   int e = static_cast<int>(cudaGetLastError());
   if (e || n_split == 1) return e;

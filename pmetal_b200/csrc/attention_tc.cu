@@ -1,0 +1,317 @@
+// Varlen causal flash attention forward on tcgen05 tensor cores (head_dim 128, GQA).
+//
+// One CTA per (128-query tile, head). Q, K and V tiles arrive by TMA into 128-byte-swizzled shared
+// memory; S = Q K^T and O_j = P V are tcgen05.mma instructions with fp32 accumulators in TMEM:
+//
+//   TMEM columns   [0,128) S buffer 0   [128,256) S buffer 1   [256,384) O buffer 0   [384,512) O buffer 1
+//
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (owns TMEM), warps 2..5 softmax. A softmax thread
+// owns one query row (TMEM lane), so row max and row sum need no shuffles. Per key tile it reads the row
+// of S from TMEM twice (max pass, exp pass), writes P as bf16 into shared memory in the layout the
+// P·V MMA reads, and folds the previous tile's O_j into its register accumulator with the online-softmax
+// correction. QK^T of tile j+1 is issued before the softmax of tile j finishes, so tensor cores and the
+// exp pipeline overlap. Same masking rule as attention.cu: key j is visible to query i iff
+// seq_start[i] <= j <= i.
+#include "attention_tc.cuh"
+
+namespace pm {
+
+// barrier indices inside the shared barrier array
+enum {
+  kBarQ = 0, kBarK = 1 /*2*/, kBarV = 3 /*2*/, kBarKvFree = 5 /*2*/, kBarSFull = 7 /*2*/, kBarSFree = 9 /*2*/,
+  kBarP = 11, kBarOFull = 12 /*2*/, kBarOFree = 14 /*2*/, kBarCount = 16
+};
+
+__global__ void __launch_bounds__(kFaThreads, 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const FaParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                          // 32 KB
+  uint8_t* sK = smem + kFaTileBytes;           // 2 x 32 KB
+  uint8_t* sV = smem + 3 * kFaTileBytes;       // 2 x 32 KB
+  uint8_t* sP = smem + 5 * kFaTileBytes;       // 32 KB
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + 6 * kFaTileBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + kBarCount);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;   // late (long) tiles first
+  const int h = blockIdx.y;
+  const int hk = h / (p.hq / p.hkv);
+  const int q0 = qt * kFaTile;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar[kBarQ], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar[kBarK + i], 1);
+      mbar_init(&bar[kBarV + i], 1);
+      mbar_init(&bar[kBarKvFree + i], 1);
+      mbar_init(&bar[kBarSFull + i], 1);
+      mbar_init(&bar[kBarSFree + i], 4);
+      mbar_init(&bar[kBarOFull + i], 1);
+      mbar_init(&bar[kBarOFree + i], 4);
+    }
+    mbar_init(&bar[kBarP], 4);
+    *abort_flag = 0;
+    mbar_init_fence();
+    tma_prefetch_desc(&map_q);
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // key range of this query tile: from the document start of its first row up to its last row
+  int kv_lo = (p.seq_start[q0] / kFaTile) * kFaTile;
+  const int kv_hi = min(q0 + kFaTile, p.T);
+  const int n_tiles = (kv_hi - kv_lo + kFaTile - 1) / kFaTile;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&bar[kBarQ], kFaTileBytes);
+      tma_load_2d(sQ, &map_q, &bar[kBarQ], h * 128, q0);
+      tma_load_2d(sQ + kFaBox, &map_q, &bar[kBarQ], h * 128 + 64, q0);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bar[kBarKvFree + b], ph ^ 1, abort_flag, p.status, kTimeoutProducer)) break;
+        const int j0 = kv_lo + j * kFaTile;
+        mbar_expect_tx(&bar[kBarK + b], kFaTileBytes);
+        tma_load_2d(sK + b * kFaTileBytes, &map_k, &bar[kBarK + b], hk * 128, j0);
+        tma_load_2d(sK + b * kFaTileBytes + kFaBox, &map_k, &bar[kBarK + b], hk * 128 + 64, j0);
+        mbar_expect_tx(&bar[kBarV + b], kFaTileBytes);
+        tma_load_2d(sV + b * kFaTileBytes, &map_v, &bar[kBarV + b], hk * 128, j0);
+        tma_load_2d(sV + b * kFaTileBytes + kFaBox, &map_v, &bar[kBarV + b], hk * 128 + 64, j0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_qk = make_idesc_bf16(128, 0, 0);   // A = Q (K-major), B = K (K-major)
+      const uint32_t idesc_pv = make_idesc_bf16(128, 0, 1);   // A = P (K-major), B = V (MN-major: rows are keys)
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      bool ok = mbar_wait(&bar[kBarQ], 0, abort_flag, p.status, kTimeoutMma);
+      auto issue_qk = [&](int j) -> bool {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bar[kBarK + b], ph, abort_flag, p.status, kTimeoutMma)) return false;
+        if (!mbar_wait(&bar[kBarSFree + b], ph ^ 1, abort_flag, p.status, kTimeoutMma)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + b * kFaTileBytes);
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          const uint32_t off = (s >> 2) * kFaBox + (s & 3) * 32;
+          umma_f16(tmem_base + b * 128, make_smem_desc(q_addr + off, 16u, 1024u),
+                   make_smem_desc(k_addr + off, 16u, 1024u), idesc_qk, s > 0);
+        }
+        umma_commit(&bar[kBarSFull + b]);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);   // overlaps the softmax of tile j
+        if (!ok) break;
+        if (!mbar_wait(&bar[kBarV + b], ph, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
+        if (!mbar_wait(&bar[kBarP], j & 1, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
+        if (!mbar_wait(&bar[kBarOFree + b], ph ^ 1, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sV + b * kFaTileBytes);
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          // A: P[128 q][128 keys], K-major in two 64-key boxes; B: V[128 keys][128 d], MN-major: 16 keys = 2048 B,
+          // the two 64-wide d chunks are the two boxes (LBO = 16 KB)
+          umma_f16(tmem_base + 256 + b * 128,
+                   make_smem_desc(p_addr + (s >> 2) * kFaBox + (s & 3) * 32, 16u, 1024u),
+                   make_smem_desc(v_addr + s * 2048, static_cast<uint32_t>(kFaBox), 1024u), idesc_pv, s > 0);
+        }
+        umma_commit(&bar[kBarOFull + b]);    // O_j ready; also: P and this K/V stage have been consumed
+        umma_commit(&bar[kBarKvFree + b]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax (one thread per query row)
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;
+    const int i = q0 + r;
+    const int ic = min(i, p.T - 1);
+    const int st = p.seq_start[ic];
+    const int st_max = p.seq_start[min(q0 + kFaTile - 1, p.T - 1)];
+    const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
+    const float sl2 = p.scale * kFaLog2e;
+    float o_reg[128];
+#pragma unroll
+    for (int c = 0; c < 128; ++c) o_reg[c] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
+    const uint32_t p_row = smem_u32(sP) + r * 128;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int b = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      const int j0 = kv_lo + j * kFaTile;
+      const bool need_mask = (j0 + kFaTile - 1 > q0) || (j0 < st_max);
+      if (!mbar_wait(&bar[kBarSFull + b], ph, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
+      tc_fence_after();
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + b * 128 + c * 32 + lane_off, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          float x = __uint_as_float(v[e]);
+          if (need_mask) {
+            const int jj = j0 + c * 32 + e;
+            if (jj > i || jj < st) x = -INFINITY;
+          }
+          mx = fmaxf(mx, x);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx * sl2);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
+      m_run = m_new;
+      // P of the previous tile must have been consumed before it is overwritten
+      if (j > 0 && !mbar_wait(&bar[kBarOFull + (b ^ 1)], ((j - 1) >> 1) & 1, abort_flag, p.status, kTimeoutEpilogue)) {
+        ok = false;
+        break;
+      }
+      // pass 2: p = exp2(s - m), row sum, bf16 P into shared memory (128B-swizzled, two 64-key boxes)
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + b * 128 + c * 32 + lane_off, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float x0 = __uint_as_float(v[e]) * sl2 - m_use, x1 = __uint_as_float(v[e + 1]) * sl2 - m_use;
+          if (need_mask) {
+            const int jj = j0 + c * 32 + e;
+            if (jj > i || jj < st) x0 = -INFINITY;
+            if (jj + 1 > i || jj + 1 < st) x1 = -INFINITY;
+          }
+          const float p0 = exp2f(x0), p1 = exp2f(x1);
+          rs += p0 + p1;
+          pk[e >> 1] = pack_bf16x2(p0, p1);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (c & 1) * 4 + g;   // 16-byte chunk within the 128-byte row of this box
+          const uint32_t addr = p_row + (c >> 1) * kFaBox + ((chunk ^ (r & 7)) << 4);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(pk[4 * g]), "r"(pk[4 * g + 1]),
+                       "r"(pk[4 * g + 2]), "r"(pk[4 * g + 3])
+                       : "memory");
+        }
+      }
+      l_run = l_run * corr + rs;
+      fence_async_smem();        // generic-proxy writes of P -> visible to the tensor-core (async) proxy
+      tc_fence_before();         // this thread's TMEM reads of S are complete
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bar[kBarP]);
+        mbar_arrive(&bar[kBarSFree + b]);
+      }
+      // fold the previous tile's O into the running accumulator (its MMA finished: waited above)
+      if (j > 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_base + 256 + (b ^ 1) * 128 + c * 32 + lane_off, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o_reg[c * 32 + e] = o_reg[c * 32 + e] * corr_prev + __uint_as_float(v[e]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar[kBarOFree + (b ^ 1)]);
+      }
+      corr_prev = corr;
+    }
+    if (ok && n_tiles > 0) {
+      const int jl = n_tiles - 1, b = jl & 1;
+      if (mbar_wait(&bar[kBarOFull + b], (jl >> 1) & 1, abort_flag, p.status, kTimeoutEpilogue)) {
+        tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* orow = p.out + static_cast<long long>(ic) * p.o_stride + static_cast<long long>(h) * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_base + 256 + b * 128 + c * 32 + lane_off, v);
+          tmem_ld_wait();
+          if (i < p.T) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                f[e] = (o_reg[c * 32 + g * 8 + e] * corr_prev + __uint_as_float(v[g * 8 + e])) * inv;
+              o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+              o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+              *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = o;
+            }
+          }
+        }
+        if (i < p.T) p.lse[static_cast<long long>(h) * p.T + i] = (m_run + log2f(l_run)) / kFaLog2e;
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace pm
+
+using namespace pm;
+
+// q:[T, hq*128 (+...)] with token stride q_stride, k/v likewise (v may be a strided view). out:[T,hq,128], lse:[hq,T]
+extern "C" int pm_attn_fwd_tc(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
+                              long long v_stride, void* out, long long o_stride, float* lse, const int* seq_start, int T,
+                              int hq, int hkv, float scale, int* status, cudaStream_t st) {
+  if (hq % hkv || T <= 0) return -1;
+  if ((q_stride | k_stride | v_stride | o_stride) % 8) return -2;
+  CUtensorMap mq, mk, mv;
+  int rc;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return -3;
+  if ((rc = make_map(&mq, q, static_cast<uint64_t>(hq) * 128, T, q_stride, 64, kFaTile))) return rc;
+  if ((rc = make_map(&mk, k, static_cast<uint64_t>(hkv) * 128, T, k_stride, 64, kFaTile))) return rc;
+  if ((rc = make_map(&mv, v, static_cast<uint64_t>(hkv) * 128, T, v_stride, 64, kFaTile))) return rc;
+  FaParams p{};
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.o_stride = o_stride; p.lse = lse; p.seq_start = seq_start;
+  p.T = T; p.hq = hq; p.hkv = hkv; p.scale = scale; p.status = status;
+  const int smem = 6 * kFaTileBytes + 1024 + 256;
+  static bool once = false;
+  if (!once) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    once = true;
+  }
+  dim3 grid((T + kFaTile - 1) / kFaTile, hq);
+  attn_fwd_tc_kernel<<<grid, kFaThreads, smem, st>>>(mq, mk, mv, p);
+  return static_cast<int>(cudaGetLastError());
+}

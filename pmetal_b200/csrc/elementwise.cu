@@ -301,7 +301,8 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const 
 // where grad_scale = *inv_n (1 / number of valid tokens of the whole batch). Adds the row's
 // loss (lse - logit[label]) to loss_sum. Rows whose label is ignore_index get a zero gradient.
 __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ labels,
-                                  float* __restrict__ loss_sum, const float* __restrict__ inv_n, int V,
+                                  float* __restrict__ loss_sum, const float* __restrict__ inv_n,
+                                  float* __restrict__ row_loss, const float* __restrict__ row_scale, int V,
                                   long long ignore_index, int write_grad) {
   __shared__ float red[32];
   __shared__ float bcast[2];
@@ -311,6 +312,7 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int V8 = V & ~7;
   if (label == ignore_index || label < 0 || label >= V) {
+    if (row_loss && tid == 0) row_loss[row] = 0.f;
     if (write_grad) {
       const bf16x8 z = {};
       for (int c = tid * 8; c < V8; c += nthr * 8) *reinterpret_cast<bf16x8*>(lr + c) = z;
@@ -353,12 +355,14 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
     for (int i = 0; i < nw; ++i) tot += red[i];
     const float lse = bm + logf(tot);
     bcast[0] = lse;
-    atomicAdd(loss_sum, lse - __bfloat162float(lr[label]));
+    const float rl = lse - __bfloat162float(lr[label]);
+    if (row_loss) row_loss[row] = rl;
+    if (loss_sum) atomicAdd(loss_sum, rl);
   }
   __syncthreads();
   if (!write_grad) return;
   const float lse = bcast[0];
-  const float gs = *inv_n;
+  const float gs = row_scale ? row_scale[row] : *inv_n;
   for (int c = tid * 8; c < V8; c += nthr * 8) {
     float f[8];
     load8(lr + c, f);
@@ -473,6 +477,49 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* 
     out[i] = __float2bfloat16(in[i]);
 }
 
+// ------------------------------------------------------------------------------------ 4-bit block dequantisation
+// NF4 / FP4 codes (two per byte, first element in the high nibble) with per-block absmax, optionally
+// double-quantised (u8 * scale + offset)  ->  bf16. Layout of crates/pmetal-mlx/src/quantization/nf4.rs.
+__constant__ float kNf4Lut[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                  -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                  0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+                                  0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+__constant__ float kFp4Lut[16] = {0.0f, 0.0052083333f, 0.6666667f, 1.0f, 0.3333333f, 0.5f, 0.1666667f, 0.25f,
+                                  -0.0f, -0.0052083333f, -0.6666667f, -1.0f, -0.3333333f, -0.5f, -0.1666667f, -0.25f};
+
+__global__ void dequant_4bit_kernel(const uint8_t* __restrict__ data, const float* __restrict__ absmax,
+                                    const uint8_t* __restrict__ absmax_q, float am_scale, float am_offset,
+                                    __nv_bfloat16* __restrict__ out, long long n, int block_size, int fp4) {
+  __shared__ float lut[16];
+  if (threadIdx.x < 16) lut[threadIdx.x] = fp4 ? kFp4Lut[threadIdx.x] : kNf4Lut[threadIdx.x];
+  __syncthreads();
+  const long long n8 = n >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint32_t packed = *reinterpret_cast<const uint32_t*>(data + i * 4);
+    const long long blk = (i * 8) / block_size;
+    const float am = absmax ? absmax[blk] : (static_cast<float>(absmax_q[blk]) * am_scale + am_offset);
+    float f[8];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const uint32_t byte = (packed >> (8 * b)) & 0xFFu;
+      f[2 * b] = lut[byte >> 4] * am;
+      f[2 * b + 1] = lut[byte & 0xFu] * am;
+    }
+    store8(out + i * 8, f);
+  }
+  // tail (n not a multiple of 8)
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (long long e = n8 << 3; e < n; ++e) {
+      const uint8_t byte = data[e >> 1];
+      const uint32_t code = (e & 1) ? (byte & 0xFu) : (byte >> 4);
+      const long long blk = e / block_size;
+      const float am = absmax ? absmax[blk] : (static_cast<float>(absmax_q[blk]) * am_scale + am_offset);
+      out[e] = __float2bfloat16(lut[code] * am);
+    }
+  }
+}
+
 }  // namespace pm
 
 using namespace pm;
@@ -541,11 +588,13 @@ extern "C" int pm_swiglu_bwd(const void* dout, const void* gu, void* dgu, long l
       T, I);
   return PM_LAUNCH_CHECK();
 }
+// row_loss (optional): per-row loss out. row_scale (optional): per-row gradient scale replacing *inv_n.
 extern "C" int pm_ce_fwd_bwd(void* logits, long long ldl, const long long* labels, float* loss_sum, const float* inv_n,
-                             int n_rows, int V, long long ignore_index, int write_grad, cudaStream_t st) {
+                             float* row_loss, const float* row_scale, int n_rows, int V, long long ignore_index,
+                             int write_grad, cudaStream_t st) {
   if (ldl % 8) return -1;
-  ce_fwd_bwd_kernel<<<n_rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ldl, labels, loss_sum, inv_n, V,
-                                             ignore_index, write_grad);
+  ce_fwd_bwd_kernel<<<n_rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ldl, labels, loss_sum, inv_n, row_loss,
+                                             row_scale, V, ignore_index, write_grad);
   return PM_LAUNCH_CHECK();
 }
 extern "C" int pm_sumsq(const float* x, long long n, float* out, cudaStream_t st) {
@@ -576,5 +625,13 @@ extern "C" int pm_attn_delta(const void* o, const void* dout, float* delta, int 
 }
 extern "C" int pm_f32_to_bf16(const float* in, void* out, long long n, cudaStream_t st) {
   f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, st>>>(in, static_cast<__nv_bfloat16*>(out), n);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_dequant_4bit(const void* data, const float* absmax, const void* absmax_q, float am_scale,
+                               float am_offset, void* out, long long n, int block_size, int fp4, cudaStream_t st) {
+  if (block_size % 8) return -1;
+  dequant_4bit_kernel<<<grid_for(n / 8 + 1, 256), 256, 0, st>>>(
+      static_cast<const uint8_t*>(data), absmax, static_cast<const uint8_t*>(absmax_q), am_scale, am_offset,
+      static_cast<__nv_bfloat16*>(out), n, block_size, fp4);
   return PM_LAUNCH_CHECK();
 }

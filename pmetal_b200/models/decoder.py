@@ -93,7 +93,12 @@ class FusedLinear(nn.Module):
             self.weight_t = self.weight.detach().t().contiguous()
 
     def merged_weight(self) -> torch.Tensor:
-        w = self.weight.detach().float()
+        q = getattr(self, "qweight", None)
+        if q is not None:
+            from ..lora.nf4 import dequantize
+            w = dequantize(q, torch.float32)
+        else:
+            w = self.weight.detach().float()
         if self.lora_a is not None:
             o = 0
             for i, sz in enumerate(self.seg_sizes):
@@ -109,7 +114,8 @@ class FusedLinear(nn.Module):
                 y = y + self._lora_delta(x)
             return y if residual is None else y + residual
         return ops.lora_linear(x, self.weight, self.weight_t, self.lora_a, self.lora_b, self.seg_sizes, self.r,
-                               self.scale, residual, getattr(self, "lora_a_c", None), getattr(self, "lora_b_c", None))
+                               self.scale, residual, getattr(self, "lora_a_c", None), getattr(self, "lora_b_c", None),
+                               getattr(self, "qweight", None))
 
     def _lora_delta(self, x: torch.Tensor) -> torch.Tensor:
         outs, o = [], 0

@@ -169,12 +169,16 @@ class _LoraLinearFn(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, w, w_t, a32, b32, a, b, seg_sizes, r, scale, residual):
+    def forward(ctx, x, w, w_t, a32, b32, a, b, seg_sizes, r, scale, residual, qweight=None):
         nat = _native()
+        if qweight is not None:      # QLoRA: dequantise into a transient buffer; only the packed weight is kept
+            from ..lora.qlora import dequantize_weight
+            w, w_t = dequantize_weight(qweight), None
         t = nat.lora_t(x, a, scale) if a is not None else None    # [M, 64-padded] = s x A^T
         y = nat.gemm_lora(x, w, t, b, seg_sizes, r, residual)
-        ctx.save_for_backward(x, w, w_t, a, b, t)
+        ctx.save_for_backward(x, None if qweight is not None else w, w_t, a, b, t)
         ctx.params = (a32, b32)
+        ctx.qweight = qweight
         ctx.cfg = (seg_sizes, r, scale, residual is not None)
         return y
 
@@ -184,6 +188,9 @@ class _LoraLinearFn(torch.autograd.Function):
         a32, b32 = ctx.params
         seg_sizes, r, scale, has_res = ctx.cfg
         nat = _native()
+        if ctx.qweight is not None:
+            from ..lora.qlora import dequantize_weight
+            w = dequantize_weight(ctx.qweight)
         dy = dy.contiguous()
         da = db = dx = None
         if a is not None:
@@ -203,18 +210,21 @@ class _LoraLinearFn(torch.autograd.Function):
             nat.lora_db(dy, t, seg_sizes, r, gb)
         elif ctx.needs_input_grad[0]:
             dx = nat.gemm_lora_dx(dy, w, w_t, None, None)
-        return dx, None, None, da, db, None, None, None, None, None, (dy if has_res else None)
+        return dx, None, None, da, db, None, None, None, None, None, (dy if has_res else None), None
 
 
 def lora_linear(x: torch.Tensor, w: torch.Tensor, w_t: Optional[torch.Tensor], a: Optional[torch.Tensor],
                 b: Optional[torch.Tensor], seg_sizes: Sequence[int], r: int, scale: float,
                 residual: Optional[torch.Tensor] = None, a_c: Optional[torch.Tensor] = None,
-                b_c: Optional[torch.Tensor] = None) -> torch.Tensor:
+                b_c: Optional[torch.Tensor] = None, qweight=None) -> torch.Tensor:
     if use_native(x):
         if a is not None:
             a_c = a_c if a_c is not None else a.detach().to(torch.bfloat16)
             b_c = b_c if b_c is not None else b.detach().to(torch.bfloat16)
-        return _LoraLinearFn.apply(x, w, w_t, a, b, a_c, b_c, tuple(seg_sizes), r, scale, residual)
+        return _LoraLinearFn.apply(x, w, w_t, a, b, a_c, b_c, tuple(seg_sizes), r, scale, residual, qweight)
+    if qweight is not None:
+        from ..lora.nf4 import dequantize
+        w = dequantize(qweight, x.dtype)
     y = F.linear(x, w)
     if a is not None:
         outs, n0 = [], 0
@@ -274,3 +284,37 @@ def grouped_mlp(xs: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, off
         if t > s:
             out[s:t] = F.linear(ref.swiglu(F.linear(xs[s:t], gate_up[e])), down[e])
     return out
+
+
+# --------------------------------------------------------------------------- per-token log-probabilities
+class _TokenLogpFn(torch.autograd.Function):
+    """log p(token_t | hidden_t) for a frozen output head; the backward recomputes each logits chunk."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, weight_t, tokens, chunk):
+        nll, _ = _native().token_nll(hidden, weight, tokens, chunk)
+        ctx.save_for_backward(hidden, weight, weight_t, tokens)
+        ctx.chunk = chunk
+        return -nll
+
+    @staticmethod
+    def backward(ctx, dlogp):
+        hidden, weight, weight_t, tokens = ctx.saved_tensors
+        # d/dh of (-nll) with upstream dlogp  ==  d/dh of nll scaled by -dlogp
+        _, dh = _native().token_nll(hidden, weight, tokens, ctx.chunk, (-dlogp).float().contiguous(), weight_t)
+        return dh, None, None, None, None
+
+
+def token_logprobs(hidden: torch.Tensor, weight: torch.Tensor, tokens: torch.Tensor, chunk: int = 4096,
+                   weight_t: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Selective log-softmax: log-probability of ``tokens`` [T] under the head applied to ``hidden`` [T, H].
+    (reference: crates/pmetal-trainer/src/logprob_utils.rs)"""
+    if use_native(hidden) and not weight.requires_grad:
+        return _TokenLogpFn.apply(hidden, weight, weight_t, tokens, chunk)
+    out = []
+    for s in range(0, hidden.shape[0], chunk):
+        lg = F.linear(hidden[s:s + chunk], weight).float()
+        t = tokens[s:s + chunk]
+        lp = torch.log_softmax(lg, -1).gather(-1, t.clamp(min=0)[:, None])[:, 0]
+        out.append(torch.where(t >= 0, lp, torch.zeros_like(lp)))
+    return torch.cat(out)

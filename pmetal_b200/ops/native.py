@@ -21,6 +21,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__
 # The transposed LoRA products read token-major tensors through MN-major tcgen05 descriptors.
 # PMETAL_MN_MAJOR=0 routes them through explicit transposes instead.
 MN_MAJOR = os.environ.get("PMETAL_MN_MAJOR", "1") == "1"
+ATTN_TC = os.environ.get("PMETAL_ATTN_TC", "1") == "1"      # tcgen05 attention kernels
 USE_2SM = os.environ.get("PMETAL_GEMM_2SM", "1") == "1"   # CTA-pair kernel for 256-wide tiles
 GEMM_DEBUG = int(os.environ.get("PMETAL_GEMM_DEBUG", "0"))   # timing experiments only (see gemm_tcgen05.cu)
 LAUNCHES = 0   # number of kernels launched through this module (bench reporting)
@@ -44,7 +45,7 @@ def _load():
         pass
     for fn in ("pm_gemm_bf16", "pm_gemm_bf16_2sm", "pm_rmsnorm_fwd", "pm_rmsnorm_bwd", "pm_rope_table", "pm_qknorm_rope_fwd",
                "pm_qknorm_rope_bwd", "pm_swiglu_fwd", "pm_swiglu_bwd", "pm_ce_fwd_bwd", "pm_sumsq", "pm_adamw_flat",
-               "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16", "pm_paged_attn", "pm_kv_append"):
+               "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16", "pm_paged_attn", "pm_kv_append", "pm_attn_fwd_tc", "pm_attn_bwd_tc", "pm_dequant_4bit"):
         getattr(_LIB, fn).restype = c_int
 
 
@@ -309,11 +310,18 @@ def swiglu_bwd(dout, gate_up):
 
 # ------------------------------------------------------------------------------------------- attention
 def attn_fwd(q, k, v, seq_start, scale: float, window: int = 0):
+    """Varlen causal attention forward. The tcgen05 kernel handles the common case; sliding windows use the
+    mma.sync kernel."""
     T, hq, d = q.shape
     hkv = k.shape[1]
     assert d == 128 and q.stride(2) == 1 and k.stride(2) == 1 and v.stride(2) == 1
     out = torch.empty(T, hq, d, dtype=q.dtype, device=q.device)
     lse = torch.empty(hq, T, dtype=torch.float32, device=q.device)
+    if ATTN_TC and window == 0 and q.stride(1) == d and k.stride(1) == d and v.stride(1) == d:
+        _chk(lib().pm_attn_fwd_tc(_p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)),
+                                  _p(out), c_ll(out.stride(0)), _p(lse), _p(seq_start), c_int(T), c_int(hq),
+                                  c_int(hkv), c_float(scale), _p(status_word(q.device)), _stream()), "pm_attn_fwd_tc")
+        return out, lse
     _chk(lib().pm_attn_fwd(_p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)), _p(out),
                            c_ll(out.stride(0)), _p(lse), _p(seq_start), c_int(T), c_int(hq), c_int(hkv),
                            c_float(scale), c_int(window), _stream()), "pm_attn_fwd")
@@ -328,10 +336,16 @@ def attn_bwd(dout, q, k, v, o, lse, seq_start, scale: float, window: int = 0, dv
     dq = torch.empty_like(q)
     dk = torch.empty_like(k)
     dv = dv_out if dv_out is not None else torch.empty(T, hkv, d, dtype=q.dtype, device=q.device)
-    _chk(lib().pm_attn_bwd(_p(dout), _p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)),
-                           c_ll(dout.stride(0)), _p(lse), _p(delta), _p(dq), c_ll(dq.stride(0)), _p(dk),
-                           c_ll(dk.stride(0)), _p(dv), c_ll(dv.stride(0)), _p(seq_start), c_int(T), c_int(hq),
-                           c_int(hkv), c_float(scale), c_int(window), _stream()), "pm_attn_bwd")
+    if ATTN_TC and window == 0 and all(t.stride(1) == d for t in (q, k, v, dout, dv)):
+        _chk(lib().pm_attn_bwd_tc(_p(dout), c_ll(dout.stride(0)), _p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)),
+                                  _p(v), c_ll(v.stride(0)), _p(lse), _p(delta), _p(dq), c_ll(dq.stride(0)), _p(dk),
+                                  c_ll(dk.stride(0)), _p(dv), c_ll(dv.stride(0)), _p(seq_start), c_int(T), c_int(hq),
+                                  c_int(hkv), c_float(scale), _p(status_word(q.device)), _stream()), "pm_attn_bwd_tc")
+    else:
+        _chk(lib().pm_attn_bwd(_p(dout), _p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)),
+                               c_ll(dout.stride(0)), _p(lse), _p(delta), _p(dq), c_ll(dq.stride(0)), _p(dk),
+                               c_ll(dk.stride(0)), _p(dv), c_ll(dv.stride(0)), _p(seq_start), c_int(T), c_int(hq),
+                               c_int(hkv), c_float(scale), c_int(window), _stream()), "pm_attn_bwd")
     global LAUNCHES
     LAUNCHES += 1   # pm_attn_bwd launches two kernels
     return (dq, dk) if dv_out is not None else (dq, dk, dv)
@@ -356,8 +370,9 @@ def linear_ce(hidden, weight, weight_t, labels, ignore_index: int, chunk: int, n
         n = min(chunk, T - s)
         h = hidden[s:s + n]
         raw_gemm(h, 0, h.stride(0), n, weight, 0, weight.stride(0), V, scratch, 0, ldl, n, V, H, bn=bn)
-        _chk(lib().pm_ce_fwd_bwd(_p(scratch), c_ll(ldl), _p(labels[s:s + n]), _p(loss), _p(inv_n), c_int(n), c_int(V),
-                                 c_ll(ignore_index), c_int(1 if need_grad else 0), _stream()), "pm_ce_fwd_bwd")
+        _chk(lib().pm_ce_fwd_bwd(_p(scratch), c_ll(ldl), _p(labels[s:s + n]), _p(loss), _p(inv_n), _p(None), _p(None),
+                                 c_int(n), c_int(V), c_ll(ignore_index), c_int(1 if need_grad else 0), _stream()),
+             "pm_ce_fwd_bwd")
         if need_grad:
             d = dh[s:s + n]
             if weight_t is not None:
@@ -410,6 +425,51 @@ def paged_attn(q, k_cache, v_cache, meta, scale: float, window: int = 0, n_split
         pml = torch.empty(n_split, total_q, hq, 2, dtype=torch.float32, device=q.device)
     _chk(lib().pm_paged_attn(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(meta.block_table), _p(meta.seq_lens),
                              _p(meta.q_start), _p(meta.q_lens), _p(po), _p(pml), c_int(n_seq),
-                             c_int(meta.block_table.shape[1]), c_int(total_q), c_int(hq), c_int(hkv), c_int(n_split),
+                             c_int(meta.block_table.shape[1]), c_int(total_q), c_int(meta.max_q), c_int(hq), c_int(hkv), c_int(n_split),
                              c_float(scale), c_int(window), _stream()), "pm_paged_attn")
     return out
+
+
+# ------------------------------------------------------------------------------------------- QLoRA
+def dequant_4bit(q) -> torch.Tensor:
+    """``QuantizedTensor`` (nf4/fp4) -> bf16 tensor of its shape."""
+    n = 1
+    for d in q.shape:
+        n *= d
+    out = torch.empty(q.shape, dtype=torch.bfloat16, device=q.data.device)
+    _chk(lib().pm_dequant_4bit(_p(q.data), _p(q.absmax), _p(q.absmax_q), c_float(q.absmax_scale),
+                               c_float(q.absmax_offset), _p(out), c_ll(n), c_int(q.block_size),
+                               c_int(1 if q.scheme == "fp4" else 0), _stream()), "pm_dequant_4bit")
+    return out
+
+
+def token_nll(hidden, weight, tokens, chunk: int = 4096, row_scale=None, weight_t=None):
+    """Per-token negative log-likelihood of ``tokens`` under softmax(hidden @ weight^T), chunked over tokens.
+
+    With ``row_scale`` (per-token upstream gradient of the NLL) it also returns d/d hidden; logits of a chunk
+    exist only in a transient bf16 buffer. Tokens equal to -100 give 0."""
+    T, H = hidden.shape
+    V = weight.shape[0]
+    tokens = tokens.contiguous()
+    nll = torch.empty(T, dtype=torch.float32, device=hidden.device)
+    dh = torch.empty_like(hidden) if row_scale is not None else None
+    chunk = min(chunk, T)
+    ldl = -(-V // 8) * 8
+    scratch = torch.empty(chunk, ldl, dtype=torch.bfloat16, device=hidden.device)
+    bn = _pick_bn(V)
+    for s in range(0, T, chunk):
+        n = min(chunk, T - s)
+        h = hidden[s:s + n]
+        raw_gemm(h, 0, h.stride(0), n, weight, 0, weight.stride(0), V, scratch, 0, ldl, n, V, H, bn=bn)
+        _chk(lib().pm_ce_fwd_bwd(_p(scratch), c_ll(ldl), _p(tokens[s:s + n]), _p(None), _p(None), _p(nll[s:s + n]),
+                                 _p(row_scale[s:s + n] if row_scale is not None else None), c_int(n), c_int(V),
+                                 c_ll(-100), c_int(1 if row_scale is not None else 0), _stream()), "pm_ce_fwd_bwd")
+        if row_scale is not None:
+            d = dh[s:s + n]
+            if weight_t is not None:
+                raw_gemm(scratch, 0, ldl, n, weight_t, 0, weight_t.stride(0), H, d, 0, d.stride(0), n, H, V,
+                         bn=_pick_bn(H))
+            else:
+                raw_gemm(scratch, 0, ldl, n, weight, 1, weight.stride(0), H, d, 0, d.stride(0), n, H, V,
+                         bn=max(64, _pick_bn(H)))
+    return nll, dh

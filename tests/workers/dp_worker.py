@@ -64,9 +64,11 @@ def main():
           f"nccl {results['nccl'][1]:.4f})", flush=True)
     assert diff < 2e-4, diff
     dist.barrier()
-    dist.destroy_process_group()
+    torch.cuda.synchronize()
     if rank == 0:
         print("DP_WORKER_OK", flush=True)
+    sys.stdout.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":
