@@ -71,12 +71,12 @@ def make_cases(T: int = 16384):
     cases["gemm_lm_head_chunk"] = lambda: gemm_case(4096, 151936, 1024)
     cases["gemm_square_8192"] = lambda: gemm_case(8192, 8192, 8192)
 
-    def attn(which):
+    def attn(which, one_doc=False):
         hq, hkv, d = 16, 8, 128
         g = torch.Generator().manual_seed(0)
         lens, tot = [], 0
         while tot < T:
-            n = int(torch.randint(64, 2049, (1,), generator=g))
+            n = T if one_doc else int(torch.randint(64, 2049, (1,), generator=g))
             n = min(n, T - tot)
             lens.append(n)
             tot += n
@@ -93,6 +93,8 @@ def make_cases(T: int = 16384):
 
     cases["attn_varlen_fwd"] = lambda: attn("fwd")
     cases["attn_varlen_bwd"] = lambda: attn("bwd")
+    cases["attn_onedoc_fwd"] = lambda: attn("fwd", True)
+    cases["attn_onedoc_bwd"] = lambda: attn("bwd", True)
 
     def rms():
         x, res, w = _r(T, 1024), _r(T, 1024), _r(1024)

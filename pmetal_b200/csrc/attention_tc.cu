@@ -22,6 +22,53 @@ enum {
   kBarP = 11, kBarOFull = 12 /*2*/, kBarOFree = 14 /*2*/, kBarCount = 16
 };
 
+// Row maximum of 128 fp32 TMEM columns of this thread's lane; with kMask only columns in [lo, lo+span] count.
+template <bool kMask>
+__device__ __forceinline__ float row_max(uint32_t taddr, int lo, int span) {
+  float mx = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + c * 32, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      float x = __uint_as_float(v[e]);
+      if (kMask) x = (static_cast<unsigned>(c * 32 + e - lo) <= static_cast<unsigned>(span) && span >= 0) ? x : -INFINITY;
+      mx = fmaxf(mx, x);
+    }
+  }
+  return mx;
+}
+
+// p = exp2(s * a + b) for the 128 columns of this row, written as bf16 into the swizzled P tile; returns the row sum.
+template <bool kMask>
+__device__ __forceinline__ float exp_rows(uint32_t taddr, uint32_t tile_addr, int r, float a, float b, int lo,
+                                          int span) {
+  float rs = 0.f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + c * 32, v);
+    tmem_ld_wait();
+    uint32_t pk[16];
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      float p0 = fast_exp2(fmaf(__uint_as_float(v[e]), a, b));
+      float p1 = fast_exp2(fmaf(__uint_as_float(v[e + 1]), a, b));
+      if (kMask) {
+        const bool any = span >= 0;
+        p0 = (any && static_cast<unsigned>(c * 32 + e - lo) <= static_cast<unsigned>(span)) ? p0 : 0.f;
+        p1 = (any && static_cast<unsigned>(c * 32 + e + 1 - lo) <= static_cast<unsigned>(span)) ? p1 : 0.f;
+      }
+      rs += p0 + p1;
+      pk[e >> 1] = pack_bf16x2(p0, p1);
+    }
+    store_row_chunk_sw128(tile_addr, r, c, pk);
+  }
+  return rs;
+}
+
 __global__ void __launch_bounds__(kFaThreads, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const FaParams p) {
@@ -152,7 +199,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
     for (int c = 0; c < 128; ++c) o_reg[c] = 0.f;
     float m_run = -INFINITY, l_run = 0.f, corr_prev = 1.f;
-    const uint32_t p_row = smem_u32(sP) + r * 128;
+    const uint32_t sP_addr = smem_u32(sP);
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int b = j & 1;
@@ -161,61 +208,24 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const bool need_mask = (j0 + kFaTile - 1 > q0) || (j0 < st_max);
       if (!mbar_wait(&bar[kBarSFull + b], ph, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after();
+      // valid key columns of this row inside the tile: [lo, lo + span]; span < 0 means none
+      const int lo = max(st - j0, 0);
+      const int span = min(i - j0, kFaTile - 1) - lo;
       // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + b * 128 + c * 32 + lane_off, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float x = __uint_as_float(v[e]);
-          if (need_mask) {
-            const int jj = j0 + c * 32 + e;
-            if (jj > i || jj < st) x = -INFINITY;
-          }
-          mx = fmaxf(mx, x);
-        }
-      }
+      const float mx = need_mask ? row_max<true>(tmem_base + b * 128 + lane_off, lo, span)
+                                 : row_max<false>(tmem_base + b * 128 + lane_off, 0, 0);
       const float m_new = fmaxf(m_run, mx * sl2);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
+      const float corr = (m_run == -INFINITY) ? 0.f : fast_exp2(m_run - m_use);
       m_run = m_new;
       // P of the previous tile must have been consumed before it is overwritten
       if (j > 0 && !mbar_wait(&bar[kBarOFull + (b ^ 1)], ((j - 1) >> 1) & 1, abort_flag, p.status, kTimeoutEpilogue)) {
         ok = false;
         break;
       }
-      // pass 2: p = exp2(s - m), row sum, bf16 P into shared memory (128B-swizzled, two 64-key boxes)
-      float rs = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + b * 128 + c * 32 + lane_off, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float x0 = __uint_as_float(v[e]) * sl2 - m_use, x1 = __uint_as_float(v[e + 1]) * sl2 - m_use;
-          if (need_mask) {
-            const int jj = j0 + c * 32 + e;
-            if (jj > i || jj < st) x0 = -INFINITY;
-            if (jj + 1 > i || jj + 1 < st) x1 = -INFINITY;
-          }
-          const float p0 = exp2f(x0), p1 = exp2f(x1);
-          rs += p0 + p1;
-          pk[e >> 1] = pack_bf16x2(p0, p1);
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int chunk = (c & 1) * 4 + g;   // 16-byte chunk within the 128-byte row of this box
-          const uint32_t addr = p_row + (c >> 1) * kFaBox + ((chunk ^ (r & 7)) << 4);
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(pk[4 * g]), "r"(pk[4 * g + 1]),
-                       "r"(pk[4 * g + 2]), "r"(pk[4 * g + 3])
-                       : "memory");
-        }
-      }
+      // pass 2: p = exp2(s * scale - m), row sum, bf16 P into shared memory (128B-swizzled, two 64-key boxes)
+      const float rs = need_mask ? exp_rows<true>(tmem_base + b * 128 + lane_off, sP_addr, r, sl2, -m_use, lo, span)
+                                 : exp_rows<false>(tmem_base + b * 128 + lane_off, sP_addr, r, sl2, -m_use, 0, 0);
       l_run = l_run * corr + rs;
       fence_async_smem();        // generic-proxy writes of P -> visible to the tensor-core (async) proxy
       tc_fence_before();         // this thread's TMEM reads of S are complete

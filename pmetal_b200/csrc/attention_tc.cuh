@@ -22,6 +22,13 @@ struct FaParams {
   int* status;
 };
 
+// 2^x on the SFU; -inf gives 0
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Store 32 bf16 (packed in pk[16]) of row r into a [128][128] bf16 tile made of two 128B-swizzled

@@ -20,6 +20,33 @@ enum {
   kDqBarDsFree = 8, kDqBarDqFull = 9, kDqBarCount = 10
 };
 
+// dS row for the dQ kernel: p = exp2(s*a + b); ds = p * (dp - delta) * scale, written as bf16 into the swizzled tile.
+// S is at taddr, dP at taddr + 128.
+template <bool kMask>
+__device__ __forceinline__ void dq_ds_rows(uint32_t taddr, uint32_t tile_addr, int r, float a, float b, float delta,
+                                           float scale, int lo, int span) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t sv[32], dv[32];
+    tmem_ld_32x32b_x32(taddr + c * 32, sv);
+    tmem_ld_32x32b_x32(taddr + 128 + c * 32, dv);
+    tmem_ld_wait();
+    uint32_t pk[16];
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      float d2[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), a, b));
+        if (kMask) pv = (span >= 0 && static_cast<unsigned>(c * 32 + e + u - lo) <= static_cast<unsigned>(span)) ? pv : 0.f;
+        d2[u] = pv * (__uint_as_float(dv[e + u]) - delta) * scale;
+      }
+      pk[e >> 1] = pack_bf16x2(d2[0], d2[1]);
+    }
+    store_row_chunk_sw128(tile_addr, r, c, pk);
+  }
+}
+
 // TMEM columns: [0,128) S   [128,256) dP   [256,384) dQ accumulator
 __global__ void __launch_bounds__(kFaThreads, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -139,6 +166,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const float sl2 = p.scale * kFaLog2e;
     const float lse2 = p.lse[static_cast<long long>(h) * p.T + ic] * kFaLog2e;
     const float dl = p.delta[static_cast<long long>(h) * p.T + ic];
+    const int st_max = p.seq_start[min(q0 + kFaTile - 1, p.T - 1)];
     const uint32_t ds_addr = smem_u32(sdS);
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
@@ -150,26 +178,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ok = false;
         break;
       }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem_base + c * 32 + lane_off, sv);
-        tmem_ld_32x32b_x32(tmem_base + 128 + c * 32 + lane_off, dv);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float d2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int jj = j0 + c * 32 + e + u;
-            const bool vis = (jj <= i) && (jj >= st) && (i < p.T);
-            const float pv = vis ? exp2f(__uint_as_float(sv[e + u]) * sl2 - lse2) : 0.f;
-            d2[u] = pv * (__uint_as_float(dv[e + u]) - dl) * p.scale;
-          }
-          pk[e >> 1] = pack_bf16x2(d2[0], d2[1]);
-        }
-        store_row_chunk_sw128(ds_addr, r, c, pk);
+      {
+        const int lo = max(st - j0, 0);
+        const int span = (i < p.T) ? (min(i - j0, kFaTile - 1) - lo) : -1;
+        const bool need_mask = (j0 + kFaTile - 1 > q0) || (j0 < st_max) || (q0 + kFaTile > p.T);
+        if (need_mask) dq_ds_rows<true>(tmem_base + lane_off, ds_addr, r, sl2, -lse2, dl, p.scale, lo, span);
+        else dq_ds_rows<false>(tmem_base + lane_off, ds_addr, r, sl2, -lse2, dl, p.scale, 0, 0);
       }
       fence_async_smem();
       tc_fence_before();
@@ -384,6 +398,10 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (w > 0) PM_KV_WAIT(kKvBarXFree2, (w - 1) & 1);
       if (!ok) continue;
       tc_fence_after();
+      // a tile needs no mask when every key precedes every query, every query's document began at or
+      // before the first key, and all rows are in range
+      const bool need_mask = (j0 + kFaTile - 1 > m0) || (sStart[kFaTile - 1] > j0) || (m0 + kFaTile > p.T) ||
+                             (j0 + kFaTile > p.T);
       uint32_t dsk[64];                    // dS^T row of this key, packed bf16, written after dV's MMA has read P^T
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -399,8 +417,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           for (int u = 0; u < 2; ++u) {
             const int cq = c * 32 + e + u;
             const int i = m0 + cq;
-            const bool vis = (jrow <= i) && (jrow >= sStart[cq]) && (i < p.T);
-            p2[u] = vis ? exp2f(__uint_as_float(sv[e + u]) * sl2 - sLse[cq]) : 0.f;
+            float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), sl2, -sLse[cq]));
+            if (need_mask) pv = ((jrow <= i) && (jrow >= sStart[cq]) && (i < p.T)) ? pv : 0.f;
+            p2[u] = pv;
             d2[u] = p2[u] * (__uint_as_float(dv[e + u]) - sDelta[cq]) * p.scale;
           }
           pk[e >> 1] = pack_bf16x2(p2[0], p2[1]);
