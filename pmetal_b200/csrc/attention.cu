@@ -928,3 +928,58 @@ extern "C" int pm_kv_append(const void* k, long long k_stride, const void* v, lo
                                          n_tokens, hkv);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ------------------------------------------------------------------ allocation-free split-KV entry point
+// Same kernels as pm_paged_attn; the partials live in a static device array (see paged_attn_static.h).
+#include "paged_attn_static.h"
+
+namespace pm {
+// [rows][128] partial outputs followed by [rows][2] (max, sum); rows = n_split * total_q * hq
+static __device__ __align__(256) float g_paged_static_scratch[PM_PAGED_STATIC_MAX_ROWS * (kD + 2)];
+constexpr int kMaxStaticDevices = 64;
+static float* g_paged_static_ptr[kMaxStaticDevices] = {};
+}  // namespace pm
+
+extern "C" int pm_paged_attn_static_max_rows(void) { return PM_PAGED_STATIC_MAX_ROWS; }
+
+extern "C" const char* pm_paged_attn_static_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case PM_PAGED_STATIC_E_BAD_HEADS: return "hq must be a multiple of hkv and num_seqs must be positive";
+    case PM_PAGED_STATIC_E_BAD_SPLIT: return "n_split must be at least 1";
+    case PM_PAGED_STATIC_E_TOO_LARGE:
+      return "n_split * total_q * hq exceeds PM_PAGED_STATIC_MAX_ROWS (4096): use pm_paged_attn with caller scratch";
+    case PM_PAGED_STATIC_E_DEVICE: return "current device index is outside the per-device scratch table";
+    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown error";
+  }
+}
+
+extern "C" int pm_paged_attn_static(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                    const int* block_table, const int* seq_lens, const int* q_start, const int* q_lens,
+                                    int num_seqs, int max_blocks, int total_q, int max_q, int hq, int hkv, int n_split,
+                                    float scale, int window, cudaStream_t st) {
+  using namespace pm;
+  if (hkv <= 0 || hq % hkv || num_seqs <= 0) return PM_PAGED_STATIC_E_BAD_HEADS;
+  if (n_split < 1) return PM_PAGED_STATIC_E_BAD_SPLIT;
+  const long long rows_all = static_cast<long long>(n_split) * total_q * hq;
+  if (total_q <= 0 || rows_all > PM_PAGED_STATIC_MAX_ROWS) return PM_PAGED_STATIC_E_TOO_LARGE;
+  int dev = 0;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  if (dev < 0 || dev >= kMaxStaticDevices) return PM_PAGED_STATIC_E_DEVICE;
+  if (!g_paged_static_ptr[dev]) {   // once per device; not a capturable call, so it must precede any capture
+    float* ptr = nullptr;
+    ce = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_paged_static_scratch);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+    if (!ptr) return static_cast<int>(cudaErrorInvalidSymbol);
+    g_paged_static_ptr[dev] = ptr;
+  }
+  float* part_o = g_paged_static_ptr[dev];
+  float* part_ml = part_o + static_cast<long long>(PM_PAGED_STATIC_MAX_ROWS) * kD;
+  if (n_split > 1) {
+    ce = cudaMemsetAsync(part_ml, 0, static_cast<size_t>(rows_all) * 2 * sizeof(float), st);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+  }
+  return pm_paged_attn(q, k_cache, v_cache, out, block_table, seq_lens, q_start, q_lens, part_o, part_ml, num_seqs,
+                       max_blocks, total_q, max_q, hq, hkv, n_split, scale, window, st);
+}
