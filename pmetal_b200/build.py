@@ -21,7 +21,7 @@ LIBDIR = os.path.join(ROOT, "lib")
 OBJDIR = os.path.join(LIBDIR, "obj")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
-CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-march=x86-64-v3", "-fopenmp"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-ffp-contract=off", "-pthread"]   # no FMA contraction: byte-exact quantisers
 
 
 def _nvcc() -> str:

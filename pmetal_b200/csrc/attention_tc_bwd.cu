@@ -231,13 +231,38 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
 
 enum {
-  kKvBarKv = 0, kKvBarQdoFull = 1 /*2*/, kKvBarQdoFree = 3 /*2*/, kKvBarSpFull = 5, kKvBarSpFree = 6, kKvBarPReady = 7,
-  kKvBarXFree = 8, kKvBarDsReady = 9, kKvBarXFree2 = 10, kKvBarAccFull = 11, kKvBarCount = 12
+  kKvBarKv = 0, kKvBarQdoFull = 1 /*2*/, kKvBarQdoFree = 3 /*2*/, kKvBarSFull = 5, kKvBarSFree = 6, kKvBarDpFull = 7,
+  kKvBarDpFree = 8, kKvBarPReady = 9, kKvBarPFree = 10, kKvBarDsReady = 11, kKvBarDsFree = 12, kKvBarAccFull = 13,
+  kKvBarCount = 14
 };
 
-__device__ __forceinline__ void compute_group_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// P row for the dK/dV kernel: p = exp2(s*a + b) (masked), packed bf16 into pk[64].
+template <bool kMask>
+__device__ __forceinline__ void kv_p_row(uint32_t taddr, float a, float b, int lo, int span, uint32_t (&pk)[64]) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t sv[32];
+    tmem_ld_32x32b_x32(taddr + c * 32, sv);
+    tmem_ld_wait();
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      float p2[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), a, b));
+        if (kMask) pv = (span >= 0 && static_cast<unsigned>(c * 32 + e + u - lo) <= static_cast<unsigned>(span)) ? pv : 0.f;
+        p2[u] = pv;
+      }
+      pk[c * 16 + (e >> 1)] = pack_bf16x2(p2[0], p2[1]);
+    }
+  }
+}
 
-// TMEM columns: [0,128) S^T   [128,256) dP^T   [256,384) dV accumulator   [384,512) dK accumulator
+// One CTA per (key tile, kv head). For every query tile that can see the key tile, and every query head of the
+// group: S = Q K^T and dP = dO V^T (rows = queries, as in the dQ kernel), P and dS are formed per query row, and
+// the same [query][key] smem tile is then read as an MN-major A operand: dV += P^T dO, dK += dS^T Q.
+// S and dP have separate full/free barriers so that S of the next pair is computed while dS of this one is formed.
+// TMEM columns: [0,128) S   [128,256) dP   [256,384) dV accumulator   [384,512) dK accumulator
 __global__ void __launch_bounds__(kFaThreads, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -248,11 +273,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint8_t* sV = smem + kFaTileBytes;
   uint8_t* sQ = smem + 2 * kFaTileBytes;    // 2 buffers
   uint8_t* sdO = smem + 4 * kFaTileBytes;   // 2 buffers
-  uint8_t* sX = smem + 6 * kFaTileBytes;    // P^T, then dS^T
-  float* sLse = reinterpret_cast<float*>(smem + 7 * kFaTileBytes);   // [128] lse * log2e of the query tile
-  float* sDelta = sLse + kFaTile;
-  int* sStart = reinterpret_cast<int*>(sDelta + kFaTile);
-  uint64_t* bar = reinterpret_cast<uint64_t*>(sStart + kFaTile);
+  uint8_t* sX = smem + 6 * kFaTileBytes;    // P[query][key], then dS[query][key]
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + 7 * kFaTileBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + kKvBarCount);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -268,12 +290,14 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&bar[kKvBarQdoFull + i], 1);
       mbar_init(&bar[kKvBarQdoFree + i], 1);
     }
-    mbar_init(&bar[kKvBarSpFull], 1);
-    mbar_init(&bar[kKvBarSpFree], 4);
+    mbar_init(&bar[kKvBarSFull], 1);
+    mbar_init(&bar[kKvBarSFree], 4);
+    mbar_init(&bar[kKvBarDpFull], 1);
+    mbar_init(&bar[kKvBarDpFree], 4);
     mbar_init(&bar[kKvBarPReady], 4);
-    mbar_init(&bar[kKvBarXFree], 1);
+    mbar_init(&bar[kKvBarPFree], 1);
     mbar_init(&bar[kKvBarDsReady], 4);
-    mbar_init(&bar[kKvBarXFree2], 1);
+    mbar_init(&bar[kKvBarDsFree], 1);
     mbar_init(&bar[kKvBarAccFull], 1);
     *abort_flag = 0;
     mbar_init_fence();
@@ -327,129 +351,132 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t id_kk = make_idesc_bf16(128, 0, 0);
-      const uint32_t id_kmn = make_idesc_bf16(128, 0, 1);
+      const uint32_t id_mm = make_idesc_bf16(128, 1, 1);
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), x_addr = smem_u32(sX);
       bool ok = mbar_wait(&bar[kKvBarKv], 0, abort_flag, p.status, kTimeoutMma);
-      auto issue_s_dp = [&](int w) -> bool {
+      auto issue_s = [&](int w) -> bool {
         const int b = w & 1;
         if (!mbar_wait(&bar[kKvBarQdoFull + b], (w >> 1) & 1, abort_flag, p.status, kTimeoutMma)) return false;
-        if (!mbar_wait(&bar[kKvBarSpFree], (w & 1) ^ 1, abort_flag, p.status, kTimeoutMma)) return false;
+        if (!mbar_wait(&bar[kKvBarSFree], (w & 1) ^ 1, abort_flag, p.status, kTimeoutMma)) return false;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQ + b * kFaTileBytes), do_addr = smem_u32(sdO + b * kFaTileBytes);
+        const uint32_t q_addr = smem_u32(sQ + b * kFaTileBytes);
 #pragma unroll
-        for (int s = 0; s < 8; ++s)   // S^T = K Q^T
-          umma_f16(tmem_base, desc_kmajor(k_addr, s), desc_kmajor(q_addr, s), id_kk, s > 0);
-#pragma unroll
-        for (int s = 0; s < 8; ++s)   // dP^T = V dO^T
-          umma_f16(tmem_base + 128, desc_kmajor(v_addr, s), desc_kmajor(do_addr, s), id_kk, s > 0);
-        umma_commit(&bar[kKvBarSpFull]);
+        for (int s = 0; s < 8; ++s)   // S = Q K^T
+          umma_f16(tmem_base, desc_kmajor(q_addr, s), desc_kmajor(k_addr, s), id_kk, s > 0);
+        umma_commit(&bar[kKvBarSFull]);
         return true;
       };
-      if (ok && total > 0) ok = issue_s_dp(0);
+      auto issue_dp = [&](int w) -> bool {   // the Q/dO buffer of w was already seen full by issue_s(w)
+        const int b = w & 1;
+        if (!mbar_wait(&bar[kKvBarDpFree], (w & 1) ^ 1, abort_flag, p.status, kTimeoutMma)) return false;
+        tc_fence_after();
+        const uint32_t do_addr = smem_u32(sdO + b * kFaTileBytes);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)   // dP = dO V^T
+          umma_f16(tmem_base + 128, desc_kmajor(do_addr, s), desc_kmajor(v_addr, s), id_kk, s > 0);
+        umma_commit(&bar[kKvBarDpFull]);
+        return true;
+      };
+      if (ok && total > 0) ok = issue_s(0) && issue_dp(0);
       for (int w = 0; w < total && ok; ++w) {
         const int b = w & 1;
         const uint32_t q_addr = smem_u32(sQ + b * kFaTileBytes), do_addr = smem_u32(sdO + b * kFaTileBytes);
         if (!mbar_wait(&bar[kKvBarPReady], w & 1, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int s = 0; s < 8; ++s)   // dV += P^T[keys][q] * dO[q][d]: dO tile read as an MN-major operand
-          umma_f16(tmem_base + 256, desc_kmajor(x_addr, s), desc_mnmajor(do_addr, s), id_kmn, (w > 0) || (s > 0));
-        umma_commit(&bar[kKvBarXFree]);
-        if (w + 1 < total) ok = issue_s_dp(w + 1);
+        for (int s = 0; s < 8; ++s)   // dV[key][d] += P[q][key]^T dO[q][d]: both operands MN-major
+          umma_f16(tmem_base + 256, desc_mnmajor(x_addr, s), desc_mnmajor(do_addr, s), id_mm, (w > 0) || (s > 0));
+        umma_commit(&bar[kKvBarPFree]);
+        if (w + 1 < total) ok = issue_s(w + 1);
         if (!ok) break;
         if (!mbar_wait(&bar[kKvBarDsReady], w & 1, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int s = 0; s < 8; ++s)   // dK += dS^T[keys][q] * Q[q][d]
-          umma_f16(tmem_base + 384, desc_kmajor(x_addr, s), desc_mnmajor(q_addr, s), id_kmn, (w > 0) || (s > 0));
-        umma_commit(&bar[kKvBarXFree2]);
+        for (int s = 0; s < 8; ++s)   // dK[key][d] += dS[q][key]^T Q[q][d]
+          umma_f16(tmem_base + 384, desc_mnmajor(x_addr, s), desc_mnmajor(q_addr, s), id_mm, (w > 0) || (s > 0));
+        umma_commit(&bar[kKvBarDsFree]);
         umma_commit(&bar[kKvBarQdoFree + b]);
+        if (w + 1 < total) ok = issue_dp(w + 1);
       }
       if (ok) umma_commit(&bar[kKvBarAccFull]);
     }
   } else {
     const int qd = warp & 3;
-    const int r = qd * 32 + lane;          // key row owned by this thread
-    const int jrow = j0 + r;
-    const int t128 = threadIdx.x - 64;     // 0..127 within the compute group
+    const int r = qd * 32 + lane;          // query row within the tile; key row in the epilogue
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     const float sl2 = p.scale * kFaLog2e;
     const uint32_t x_addr = smem_u32(sX);
-    // A failed wait must not leave the named barrier short of arrivals: threads keep iterating with
-    // ok == false (warp-uniform), skipping the work.
     bool ok = true;
-#define PM_KV_WAIT(B, PAR)                                                             \
-  do {                                                                                 \
-    if (ok) ok = mbar_wait(&bar[B], PAR, abort_flag, p.status, kTimeoutEpilogue);      \
-    ok = __all_sync(0xffffffffu, ok);                                                  \
-  } while (0)
-    for (int w = 0; w < total; ++w) {
+    for (int w = 0; w < total && ok; ++w) {
       const int hh = hk * rep + w / n_q_tiles;
       const int m0 = j0 + (w % n_q_tiles) * kFaTile;
-      compute_group_sync();                // everyone is done with the previous tile's per-query arrays
-      {
-        const int qi = min(m0 + t128, p.T - 1);
-        sLse[t128] = p.lse[static_cast<long long>(hh) * p.T + qi] * kFaLog2e;
-        sDelta[t128] = p.delta[static_cast<long long>(hh) * p.T + qi];
-        sStart[t128] = p.seq_start[qi];
-      }
-      compute_group_sync();
-      PM_KV_WAIT(kKvBarSpFull, w & 1);
-      if (w > 0) PM_KV_WAIT(kKvBarXFree2, (w - 1) & 1);
-      if (!ok) continue;
+      const int i = m0 + r, ic = min(i, p.T - 1);
+      // per-row values of this pair; the loads are in flight while the S barrier is waited on
+      const int st = p.seq_start[ic];
+      const int st_max = p.seq_start[min(m0 + kFaTile - 1, p.T - 1)];
+      const float lse2 = p.lse[static_cast<long long>(hh) * p.T + ic] * kFaLog2e;
+      const float dl = p.delta[static_cast<long long>(hh) * p.T + ic];
+      const int lo = max(st - j0, 0);
+      const int span = (i < p.T) ? (min(i - j0, kFaTile - 1) - lo) : -1;
+      const bool need_mask = (j0 + kFaTile - 1 > m0) || (j0 < st_max) || (m0 + kFaTile > p.T);
+
+      if (!mbar_wait(&bar[kKvBarSFull], w & 1, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after();
-      // a tile needs no mask when every key precedes every query, every query's document began at or
-      // before the first key, and all rows are in range
-      const bool need_mask = (j0 + kFaTile - 1 > m0) || (sStart[kFaTile - 1] > j0) || (m0 + kFaTile > p.T) ||
-                             (j0 + kFaTile > p.T);
-      uint32_t dsk[64];                    // dS^T row of this key, packed bf16, written after dV's MMA has read P^T
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem_base + c * 32 + lane_off, sv);
-        tmem_ld_32x32b_x32(tmem_base + 128 + c * 32 + lane_off, dv);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p2[2], d2[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int cq = c * 32 + e + u;
-            const int i = m0 + cq;
-            float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), sl2, -sLse[cq]));
-            if (need_mask) pv = ((jrow <= i) && (jrow >= sStart[cq]) && (i < p.T)) ? pv : 0.f;
-            p2[u] = pv;
-            d2[u] = p2[u] * (__uint_as_float(dv[e + u]) - sDelta[cq]) * p.scale;
-          }
-          pk[e >> 1] = pack_bf16x2(p2[0], p2[1]);
-          dsk[c * 16 + (e >> 1)] = pack_bf16x2(d2[0], d2[1]);
-        }
-        store_row_chunk_sw128(x_addr, r, c, pk);
-      }
-      fence_async_smem();
+      uint32_t pk[64];
+      if (need_mask) kv_p_row<true>(tmem_base + lane_off, sl2, -lse2, lo, span, pk);
+      else kv_p_row<false>(tmem_base + lane_off, sl2, -lse2, 0, 0, pk);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bar[kKvBarPReady]);
-        mbar_arrive(&bar[kKvBarSpFree]);
+      if (lane == 0) mbar_arrive(&bar[kKvBarSFree]);
+      // the previous pair's dK MMA must be done with the shared P/dS tile
+      if (w > 0 && !mbar_wait(&bar[kKvBarDsFree], (w - 1) & 1, abort_flag, p.status, kTimeoutEpilogue)) {
+        ok = false;
+        break;
       }
-      PM_KV_WAIT(kKvBarXFree, w & 1);
-      if (!ok) continue;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+        uint32_t ck[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) pk[e] = dsk[c * 16 + e];
-        store_row_chunk_sw128(x_addr, r, c, pk);
+        for (int e = 0; e < 16; ++e) ck[e] = pk[c * 16 + e];
+        store_row_chunk_sw128(x_addr, r, c, ck);
+      }
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[kKvBarPReady]);
+
+      if (!mbar_wait(&bar[kKvBarDpFull], w & 1, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {        // dS = P * (dP - delta) * scale, in place over the packed P row
+        uint32_t dv[32];
+        tmem_ld_32x32b_x32(tmem_base + 128 + c * 32 + lane_off, dv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const uint32_t pp = pk[c * 16 + e];
+          const float p0 = __uint_as_float(pp << 16), p1 = __uint_as_float(pp & 0xffff0000u);
+          pk[c * 16 + e] = pack_bf16x2(p0 * (__uint_as_float(dv[2 * e]) - dl) * p.scale,
+                                       p1 * (__uint_as_float(dv[2 * e + 1]) - dl) * p.scale);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar[kKvBarDpFree]);
+      if (!mbar_wait(&bar[kKvBarPFree], w & 1, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t ck[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) ck[e] = pk[c * 16 + e];
+        store_row_chunk_sw128(x_addr, r, c, ck);
       }
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[kKvBarDsReady]);
     }
-#undef PM_KV_WAIT
     if (ok && total > 0 && mbar_wait(&bar[kKvBarAccFull], 0, abort_flag, p.status, kTimeoutEpilogue)) {
       tc_fence_after();
+      const int jrow = j0 + r;
       const int jc = min(jrow, p.T - 1);
       __nv_bfloat16* krow = p.out + static_cast<long long>(jc) * p.o_stride + static_cast<long long>(hk) * 128;
       __nv_bfloat16* vrow = p.out2 + static_cast<long long>(jc) * p.o2_stride + static_cast<long long>(hk) * 128;

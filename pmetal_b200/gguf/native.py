@@ -1,0 +1,88 @@
+"""ctypes binding of the host C++ block codecs (``csrc/host/gguf_quant.cpp``).
+
+The library is built on first use when it is missing or older than its source (g++, about two seconds)."""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+import threading
+
+import numpy as np
+
+from .types import BLOCK_GEOMETRY, GgmlType, tensor_nbytes
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_SRC = os.path.join(_ROOT, "csrc", "host", "gguf_quant.cpp")
+_SO = os.path.join(_ROOT, "lib", "libpmetal_host.so")
+_LOCK = threading.Lock()
+_LIB = None
+# -ffp-contract=off: a fused multiply-add would change results in the last bit and break byte compatibility
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-ffp-contract=off", "-pthread"]
+
+
+def build(force: bool = False) -> str:
+    os.makedirs(os.path.dirname(_SO), exist_ok=True)
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(_SRC):
+        tmp = _SO + f".{os.getpid()}.tmp"
+        r = subprocess.run(["g++"] + CXX_FLAGS + ["-shared", "-o", tmp, _SRC], stdout=subprocess.PIPE,
+                           stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("host library build failed:\n" + r.stdout)
+        os.replace(tmp, _SO)
+    return _SO
+
+
+def lib():
+    global _LIB
+    with _LOCK:
+        if _LIB is None:
+            L = ctypes.CDLL(build())
+            L.pm_gguf_quantize.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
+            L.pm_gguf_dequantize.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
+            L.pm_gguf_row_bytes.restype = ctypes.c_int64
+            L.pm_gguf_row_bytes.argtypes = [ctypes.c_int, ctypes.c_int64]
+            _LIB = L
+    return _LIB
+
+
+def can_quantize(t: GgmlType) -> bool:
+    return t in (GgmlType.F32, GgmlType.F16, GgmlType.BF16, GgmlType.Q4_0, GgmlType.Q4_1, GgmlType.Q5_0, GgmlType.Q5_1,
+                 GgmlType.Q8_0, GgmlType.Q8_1, GgmlType.Q2K, GgmlType.Q3K, GgmlType.Q4K, GgmlType.Q5K, GgmlType.Q6K,
+                 GgmlType.Q8K, GgmlType.MXFP4)
+
+
+def can_dequantize(t: GgmlType) -> bool:
+    return can_quantize(t) or t in (GgmlType.IQ4_NL, GgmlType.IQ4_XS)
+
+
+def quantize(x: np.ndarray, t: GgmlType, threads: int = 0) -> np.ndarray:
+    """float32 array (any shape, row-major) -> uint8 array of block bytes."""
+    t = GgmlType(t)
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    out = np.zeros(tensor_nbytes(t, x.size), dtype=np.uint8)
+    rc = lib().pm_gguf_quantize(int(t), x.ctypes.data, out.ctypes.data, x.size, threads)
+    if rc == -2:
+        raise NotImplementedError(f"quantisation to {t.name} is not implemented (dequantise-only type)")
+    if rc != 0:
+        raise ValueError(f"unknown ggml type {int(t)}")
+    return out
+
+
+def dequantize(buf, t: GgmlType, n_elements: int, threads: int = 0) -> np.ndarray:
+    t = GgmlType(t)
+    raw = np.frombuffer(buf, dtype=np.uint8) if not isinstance(buf, np.ndarray) else buf.reshape(-1).view(np.uint8)
+    need = tensor_nbytes(t, n_elements)
+    if raw.size < need:
+        raise ValueError(f"{t.name}: need {need} bytes for {n_elements} elements, got {raw.size}")
+    raw = np.ascontiguousarray(raw[:need])
+    out = np.empty(n_elements, dtype=np.float32)
+    rc = lib().pm_gguf_dequantize(int(t), raw.ctypes.data, out.ctypes.data, n_elements, threads)
+    if rc == -2:
+        raise NotImplementedError(f"dequantisation of {t.name} is not implemented")
+    if rc != 0:
+        raise ValueError(f"unknown ggml type {int(t)}")
+    return out
+
+
+__all__ = ["build", "lib", "quantize", "dequantize", "can_quantize", "can_dequantize", "BLOCK_GEOMETRY"]
