@@ -202,7 +202,7 @@ def quantize_model(model_dir: str, output: str, method: str = "q4_k_m", imatrix_
                    dynamic: Optional[DynamicConfig] = None, threads: int = 0,
                    progress: Optional[Callable[[str, GgmlType], None]] = None) -> dict:
     """Reads ``model_dir`` (safetensors, single file or sharded) and writes a GGUF file. Returns a summary."""
-    from ..utils.safetensors_io import load_checkpoint_dir
+    from ..models.loader import read_state_dict
     method = method.lower()
     if method not in QUANT_METHODS:
         raise ValueError(f"unknown quantisation method {method!r}; choose from {sorted(QUANT_METHODS)}")
@@ -212,7 +212,7 @@ def quantize_model(model_dir: str, output: str, method: str = "q4_k_m", imatrix_
         with open(cp, "r", encoding="utf-8") as fh:
             config = json.load(fh)
     arch = architecture_of(config)
-    state = load_checkpoint_dir(model_dir)
+    state = read_state_dict(model_dir)
     w = GgufWriter()
     w.add_string("general.architecture", arch)
     w.add_string("general.name", "quantized-model")

@@ -60,3 +60,16 @@ def load_gguf_state_dict(path: str, threads: int = 0) -> Tuple[Dict[str, np.ndar
         if "lm_head.weight" not in out and "model.embed_tokens.weight" in out:
             cfg.setdefault("tie_word_embeddings", True)
     return out, cfg
+
+
+def load_gguf_model(path: str, threads: int = 0):
+    """Builds a ``DecoderLM`` from a GGUF file. Returns (model, ModelArgs)."""
+    import torch
+
+    from ..models.config import ModelArgs
+    from ..models.decoder import DecoderLM
+    sd, cfg = load_gguf_state_dict(path, threads)
+    args = ModelArgs.from_dict(cfg)
+    m = DecoderLM(args)
+    m.load_hf_state_dict({k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in sd.items()}, strict=False)
+    return m, args

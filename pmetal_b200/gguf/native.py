@@ -59,6 +59,8 @@ def can_dequantize(t: GgmlType) -> bool:
 def quantize(x: np.ndarray, t: GgmlType, threads: int = 0) -> np.ndarray:
     """float32 array (any shape, row-major) -> uint8 array of block bytes."""
     t = GgmlType(t)
+    if not can_quantize(t):
+        raise NotImplementedError(f"quantisation to {t.name} is not implemented (dequantise-only or unsupported type)")
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
     out = np.zeros(tensor_nbytes(t, x.size), dtype=np.uint8)
     rc = lib().pm_gguf_quantize(int(t), x.ctypes.data, out.ctypes.data, x.size, threads)
@@ -71,6 +73,8 @@ def quantize(x: np.ndarray, t: GgmlType, threads: int = 0) -> np.ndarray:
 
 def dequantize(buf, t: GgmlType, n_elements: int, threads: int = 0) -> np.ndarray:
     t = GgmlType(t)
+    if not can_dequantize(t):
+        raise NotImplementedError(f"dequantisation of {t.name} is not implemented")
     raw = np.frombuffer(buf, dtype=np.uint8) if not isinstance(buf, np.ndarray) else buf.reshape(-1).view(np.uint8)
     need = tensor_nbytes(t, n_elements)
     if raw.size < need:

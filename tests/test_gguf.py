@@ -1,0 +1,231 @@
+"""GGUF: block codecs against plain numpy restatements, file round trips, recipe, imatrix, reader hardening."""
+import io
+import json
+import os
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from pmetal_b200.gguf import native
+from pmetal_b200.gguf.convert import gguf_to_hf_name, hf_to_gguf_name, quantize_model
+from pmetal_b200.gguf.imatrix import IMatrix
+from pmetal_b200.gguf.reader import GgufError, GgufFile
+from pmetal_b200.gguf.recipe import DynamicConfig, DynamicQuantizer, tensor_type, use_more_bits
+from pmetal_b200.gguf.types import BLOCK_GEOMETRY, GgmlType, tensor_nbytes
+from pmetal_b200.gguf.writer import GgufWriter
+
+T = GgmlType
+
+
+def _rnd(v):      # round half away from zero, as the quantisers do
+    return np.sign(v) * np.floor(np.abs(v) + 0.5)
+
+
+def _data(n=256 * 12, seed=0, scale=0.05):
+    return (np.random.default_rng(seed).standard_normal(n) * scale).astype(np.float32)
+
+
+def test_q8_0_matches_numpy_restatement():
+    x = _data(32 * 7 + 5)                      # ragged tail is zero-padded
+    raw = native.quantize(x, T.Q8_0)
+    assert raw.size == 8 * 34
+    xp = np.concatenate([x, np.zeros(27, np.float32)]).reshape(8, 32)
+    amax = np.abs(xp).max(1)
+    d = (amax / np.float32(127)).astype(np.float16)
+    inv = np.where(amax == 0, 0, np.float32(127) / amax).astype(np.float32)
+    q = np.clip(_rnd(xp * inv[:, None]), -127, 127).astype(np.int8)
+    blocks = raw.reshape(8, 34)
+    assert np.array_equal(blocks[:, :2].copy().view(np.float16).reshape(-1), d)
+    assert np.array_equal(blocks[:, 2:].view(np.int8), q)
+    y = native.dequantize(raw, T.Q8_0, x.size)
+    assert np.allclose(y, (q * d.astype(np.float32)[:, None]).reshape(-1)[:x.size])
+
+
+def test_q4_0_layout_and_signed_scale():
+    x = np.zeros(32, np.float32)
+    x[3] = -2.0                                 # largest magnitude is negative -> d = -2 / -8 = 0.25
+    x[20] = 1.0
+    raw = native.quantize(x, T.Q4_0)
+    assert raw[:2].view(np.float16)[0] == np.float16(0.25)
+    qs = raw[2:]
+    assert qs[3] & 15 == 1                      # round(-2/0.25 + 8.5) = round(0.5) = 1 (half away from zero)
+    assert qs[4] >> 4 == 13                     # element 20 sits in the high nibble of byte 4: round(4 + 8.5) = 13
+    y = native.dequantize(raw, T.Q4_0, 32)
+    assert abs(y[3] - (1 - 8) * 0.25) < 1e-6
+
+
+@pytest.mark.parametrize("t,tol", [(T.Q4_0, 0.25), (T.Q4_1, 0.12), (T.Q5_0, 0.13), (T.Q5_1, 0.06), (T.Q8_0, 0.01),
+                                   (T.Q8_1, 0.01), (T.Q2K, 0.40), (T.Q3K, 0.22), (T.Q4K, 0.11), (T.Q5K, 0.06),
+                                   (T.Q6K, 0.03), (T.Q8K, 0.012), (T.MXFP4, 0.18), (T.F16, 1e-3), (T.BF16, 5e-3)])
+def test_round_trip_error(t, tol):
+    x = _data()
+    raw = native.quantize(x, t)
+    assert raw.size == tensor_nbytes(t, x.size)
+    y = native.dequantize(raw, t, x.size)
+    assert np.linalg.norm(y - x) / np.linalg.norm(x) < tol
+    # deterministic and independent of the thread count
+    assert np.array_equal(raw, native.quantize(x, t, threads=3))
+
+
+def test_k_quant_ragged_tail_is_zero_and_constant_block():
+    x = _data(256 + 100)
+    raw = native.quantize(x, T.Q4K)
+    assert raw.size == 2 * 144 and not raw[144:].any()
+    const = np.full(256, 0.5, np.float32)       # max == min in every sub-block -> all scales zero
+    y = native.dequantize(native.quantize(const, T.Q4K), T.Q4K, 256)
+    assert not y.any()
+    z = native.dequantize(native.quantize(np.zeros(256, np.float32), T.Q6K), T.Q6K, 256)
+    assert not z.any() and np.isfinite(z).all()
+
+
+def test_q6k_block_fields():
+    x = _data(256, seed=3)
+    raw = native.quantize(x, T.Q6K)
+    sc = raw[192:208].view(np.int8)
+    d = raw[208:210].view(np.float16)[0]
+    assert np.abs(sc).max() in (127, 128 - 1) or np.abs(sc).max() > 100      # scales use the int8 range
+    assert d != 0
+
+
+def test_iq4_and_unknown_types():
+    blk = np.zeros(18, np.uint8)
+    blk[:2] = np.frombuffer(np.float16(2.0).tobytes(), np.uint8)
+    blk[2] = 0x0F                               # element 0 -> code 15 (113), element 16 -> code 0 (-127)
+    y = native.dequantize(blk, T.IQ4_NL, 32)
+    assert y[0] == 226.0 and y[16] == -254.0
+    with pytest.raises(NotImplementedError):
+        native.quantize(_data(256), T.IQ4_XS)
+    with pytest.raises(NotImplementedError):
+        native.dequantize(np.zeros(66, np.uint8), T.IQ2_XXS, 256)
+
+
+def test_writer_layout_and_reader_round_trip(tmp_path):
+    w = GgufWriter()
+    w.add_string("general.architecture", "qwen3").add_u32("qwen3.block_count", 2).add_f32("qwen3.rope.freq_base", 1e6)
+    w.add_array("tokenizer.ggml.tokens", 8, ["<a>", "b", "c"])
+    a = _data(64 * 256).reshape(64, 256)
+    w.add_tensor_f32("blk.0.attn_q.weight", a, T.Q4K)
+    w.add_tensor_f32("output_norm.weight", a[0], T.F32)
+    w.add_tensor_f32("blk.0.ffn_down.weight", a[:3, :96], T.F16)      # 576 bytes: last tensor is not padded
+    p = str(tmp_path / "m.gguf")
+    n = w.write_to(p)
+    assert os.path.getsize(p) == n
+    raw = open(p, "rb").read()
+    magic, ver, nt, nkv = struct.unpack_from("<IIQQ", raw, 0)
+    assert (magic, ver, nt, nkv) == (0x46554747, 3, 3, 6)
+    # metadata keys appear in sorted order
+    first_key_len = struct.unpack_from("<Q", raw, 24)[0]
+    assert raw[32:32 + first_key_len] == b"general.alignment"
+    with GgufFile(p) as f:
+        assert f.metadata["qwen3.block_count"] == 2 and f.metadata["tokenizer.ggml.tokens"] == ["<a>", "b", "c"]
+        assert f.data_start % 32 == 0
+        assert f.tensors["blk.0.attn_q.weight"].shape == (64, 256)
+        assert f.tensors["output_norm.weight"].offset % 32 == 0
+        assert np.array_equal(f.tensor_f32("output_norm.weight"), a[0])
+        q = f.tensor_f32("blk.0.attn_q.weight")
+        assert np.linalg.norm(q - a) / np.linalg.norm(a) < 0.11
+        assert f.tensor_f32("blk.0.ffn_down.weight").shape == (3, 96)
+        assert f.data_start + f.tensors["blk.0.ffn_down.weight"].offset + 576 == len(raw)
+
+
+def test_reader_rejects_malformed_files():
+    w = GgufWriter()
+    w.add_tensor_f32("t", _data(256), T.Q8_0)
+    b = io.BytesIO()
+    w.write(b)
+    good = b.getvalue()
+    GgufFile.from_bytes(good)
+    with pytest.raises(GgufError):
+        GgufFile.from_bytes(b"GGML" + good[4:])
+    with pytest.raises(GgufError):
+        GgufFile.from_bytes(good[:8] + struct.pack("<Q", 1 << 40) + good[16:])       # absurd tensor count
+    with pytest.raises(GgufError):
+        GgufFile.from_bytes(good[:-50])                                              # tensor data cut short
+    with pytest.raises(GgufError):
+        GgufFile.from_bytes(good[:24] + struct.pack("<Q", 1 << 60) + good[32:])      # string length overflow
+    rng = np.random.default_rng(1)
+    for _ in range(200):                                                             # random corruption never crashes
+        m = bytearray(good)
+        for _ in range(4):
+            m[rng.integers(0, min(len(m), 200))] = rng.integers(0, 256)
+        try:
+            GgufFile.from_bytes(bytes(m))
+        except (GgufError, UnicodeDecodeError, struct.error, OverflowError, MemoryError, ValueError):
+            pass
+
+
+def test_name_mapping_and_recipe():
+    assert hf_to_gguf_name("model.layers.7.self_attn.q_proj.weight") == "blk.7.attn_q.weight"
+    assert hf_to_gguf_name("model.embed_tokens.weight") == "token_embd.weight"
+    assert hf_to_gguf_name("model.layers.1.mlp.experts.down_proj.weight") == "blk.1.ffn_down_exps.weight"
+    assert gguf_to_hf_name("blk.3.attn_k_norm.weight") == "model.layers.3.self_attn.k_norm.weight"
+    assert gguf_to_hf_name(hf_to_gguf_name("model.layers.0.mlp.up_proj.weight")) == "model.layers.0.mlp.up_proj.weight"
+    cfg = {"num_hidden_layers": 32, "num_attention_heads": 32, "num_key_value_heads": 8}
+    assert [use_more_bits(i, 32) for i in (0, 3, 4, 5, 6, 26, 28)] == [True, True, False, False, True, False, True]
+    assert tensor_type("q4_k_m", "blk.0.attn_v.weight", (1024, 4096), cfg) == T.Q6K
+    assert tensor_type("q4_k_m", "blk.5.attn_v.weight", (1024, 4096), cfg) == T.Q4K
+    assert tensor_type("q4_k_m", "output.weight", (32000, 4096), cfg) == T.Q6K
+    assert tensor_type("q2_k", "blk.9.attn_v.weight", (1024, 4096), cfg) == T.Q4K       # n_gqa >= 4
+    assert tensor_type("q3_k_m", "blk.1.ffn_down.weight", (4096, 11008), cfg) == T.Q5K
+    assert tensor_type("q4_k_m", "blk.2.attn_norm.weight", (4096,), cfg) == T.F16
+    assert tensor_type("q8_0", "token_embd.weight", (32000, 4096), cfg) == T.Q8_0
+    assert tensor_type("mxfp4", "token_embd.weight", (32000, 4096), cfg) == T.F16
+    assert tensor_type("f16", "blk.0.attn_q.weight", (8, 8), cfg) == T.F16
+
+
+def test_imatrix_round_trip_and_dynamic(tmp_path):
+    im = IMatrix()
+    im.accumulate("blk.0.attn_q.weight", np.ones((4, 8), np.float32) * 3)
+    im.accumulate("blk.0.attn_q.weight", np.ones((4, 8), np.float32))
+    im.accumulate("blk.1.ffn_up.weight", np.ones((2, 8), np.float32) * 0.1)
+    for i in range(2, 10):
+        im.accumulate(f"blk.{i}.ffn_up.weight", np.ones((2, 8), np.float32) * 0.01)
+    p = str(tmp_path / "im.dat")
+    im.save(p)
+    back = IMatrix.load(p)
+    assert back.ncalls["blk.0.attn_q.weight"] == 2
+    assert np.allclose(back.data["blk.0.attn_q.weight"], 5.0)
+    dq = DynamicQuantizer(DynamicConfig(), back)
+    assert dq.propose("blk.0.attn_q.weight") == T.Q6K           # top 20 % by importance
+    assert dq.propose("blk.5.ffn_up.weight") == T.Q4K
+    assert dq.propose("output.weight") == T.Q6K                 # critical -> fallback
+    assert DynamicQuantizer(DynamicConfig()).propose("blk.0.attn_q.weight") == T.Q4K
+    with pytest.raises(ValueError):
+        IMatrix.from_bytes(struct.pack("<i", -1))
+    x = _data(4096)
+    t = DynamicQuantizer(DynamicConfig(kl_calibrate=True, error_budget=0.05)).calibrate("blk.0.x.weight", x)
+    assert t in (T.Q5K, T.Q6K)
+    plan = {"a": (T.Q6K, 1000, 5.0), "b": (T.Q6K, 1000, 1.0), "output.weight": (T.Q6K, 10, 9.0)}
+    out = DynamicQuantizer(DynamicConfig(target_bpw=5.6)).fit_target_bpw(plan)
+    assert out["output.weight"] == T.Q6K and out["b"] != T.Q6K
+
+
+def test_quantize_model_and_load_back(tmp_path):
+    from pmetal_b200.models.config import ModelArgs
+    from pmetal_b200.models.decoder import DecoderLM
+    from pmetal_b200.models.loader import load_pretrained, save_pretrained
+    cfg = ModelArgs(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                    num_attention_heads=2, num_key_value_heads=1, head_dim=128, tie_word_embeddings=False)
+    m = DecoderLM(cfg).init_weights(0.05, 0)
+    src = str(tmp_path / "hf")
+    save_pretrained(m, src)
+    out = str(tmp_path / "m.gguf")
+    info = quantize_model(src, out, "q8_0")
+    assert info["architecture"] == "qwen3" and info["types"]["Q8_0"] >= 14
+    with GgufFile(out) as f:
+        assert f.metadata["general.name"] == "quantized-model"
+        assert f.metadata["qwen3.block_count"] == 2 and f.metadata["qwen3.attention.head_count_kv"] == 1
+        assert f.tensors["blk.0.attn_norm.weight"].dtype == T.F32
+        names = f.tensor_order
+        assert names == sorted(names, key=lambda n: gguf_to_hf_name(n))        # plain tensors in HF-name order
+    m2, args2, _ = load_pretrained(out, dtype=torch.float32)
+    assert args2.num_hidden_layers == 2 and args2.head_dim == 128
+    ids = torch.randint(0, 512, (1, 16))
+    with torch.no_grad():
+        a = m.float().loss(ids, ids.clone())
+        b = m2.loss(ids, ids.clone())
+    assert abs(float(a) - float(b)) < 0.05
+    info2 = quantize_model(src, str(tmp_path / "k.gguf"), "q4_k_m")
+    assert info2["types"].get("Q6K", 0) >= 1 and info2["compression"] > 3
