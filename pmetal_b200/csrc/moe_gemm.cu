@@ -1,0 +1,380 @@
+// Grouped expert GEMMs for mixture-of-experts layers, with expert-parallel dispatch and combine fused in.
+//
+// Every rank holds E_loc = E / world experts and T_loc tokens. After local routing the (token, slot) rows are sorted
+// by expert into `sorted_x` (symmetric memory) with `offsets[E+1]` (symmetric memory as well). Then, per rank:
+//
+//   ep_prepare_kernel   publishes "my sorted tokens and offsets are ready", waits for every peer's flag (bounded),
+//                       reads the peers' offsets and builds the tile lists: one tile per 128 rows of each
+//                       (source rank, local expert) segment.
+//   moe_gemm_kernel #1  gate/up projection: the TMA producer pulls every tile's token rows straight out of the
+//                       *source rank's* sorted buffer (non-multicast TMA through a per-rank tensor map) -- this is
+//                       the dispatch all-to-all -- and the epilogue applies SwiGLU, writing h locally.
+//   moe_gemm_kernel #2  down projection on h; the epilogue stores every output row straight into the *source rank's*
+//                       result buffer at the row's sorted position (16-byte peer stores) -- this is the combine
+//                       all-to-all. The launch ends only after every peer has signalled that its pushes are complete,
+//                       so the local weighted combine that follows on the stream sees all rows.
+//
+// With world = 1 the same kernels are the local grouped GEMM. This replaces the reference's per-destination
+// send/recv dispatcher (crates/pmetal-distributed/src/expert_parallel/dispatch.rs:66-214) and its grouped-GEMM Metal
+// kernels (crates/pmetal-metal/src/kernels/metal/grouped_gemm.metal:125-465, fused_moe.metal).
+//
+// GEMM core: persistent 128x256x64 tcgen05 tiles over a device-side tile list (warp 0 TMA, warp 1 MMA, warps 2-5
+// epilogue, TMEM double-buffered). Gate/up weights are stored per expert in blocks of 256 rows: 128 gate rows followed
+// by the matching 128 up rows, so one accumulator tile holds both halves of 128 outputs.
+// All cross-rank waits are bounded and report through the status word; plain peer loads/stores only.
+#include "gemm_common.cuh"
+
+namespace pm {
+
+constexpr int kEpMaxRanks = 8;
+constexpr int kEpBN = 256;
+constexpr int kEpStages = 4;
+constexpr int kStatusEpPeer = 107;
+
+constexpr int kEpReady = 0;     // [8] rank r's sorted tokens + offsets of this epoch are published
+constexpr int kEpPushed = 8;    // [8] rank r has stored all its down-projection rows
+constexpr int kEpEpoch = 16;    // local epoch (bumped by ep_prepare_kernel)
+constexpr int kEpArrive = 17;   // local CTA arrival counter
+
+struct MoeTile {
+  int a_src;      // index of the A tensor map (source rank; own rank for the down projection)
+  int a_row0;     // first row in that buffer
+  int rows;       // valid rows (<= 128)
+  int expert;     // local expert index (selects the weight rows)
+  int out_dst;    // rank whose buffer receives the output rows
+  int out_row0;   // first output row there
+};
+
+struct MoeMaps {
+  CUtensorMap a[kEpMaxRanks];
+  CUtensorMap b;      // stacked weights [E_loc * n_per_expert, K]
+};
+
+struct MoeGemmParams {
+  const MoeTile* tiles;
+  const int* n_tiles;
+  int N, K;                 // per-expert output rows of the weight (2*I for gate/up, H for down) and reduction size
+  int swiglu;               // 1: out[:, j] = silu(acc[:, j]) * acc[:, j + 128] per 256 block, output width N / 2
+  __nv_bfloat16* out[kEpMaxRanks];
+  int ldd;
+  int rank, world;
+  int signal_pushed;        // 1: set pushed[rank] on all peers at the end and wait for all peers' flags
+  uint32_t* pads[kEpMaxRanks];
+  unsigned long long timeout_ns;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t ep_ld_acquire(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void ep_st_release(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool ep_wait_flag(const uint32_t* flag, uint32_t epoch, unsigned long long timeout_ns,
+                                             int* status) {
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ep_ld_acquire(flag) - epoch) < 0) {
+    if ((++spins & 31u) == 0u) {
+      if (globaltimer_ns() - t0 > timeout_ns) {
+        atomicCAS(status, 0, kStatusEpPeer);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+  return true;
+}
+
+// One CTA. offsets[r] points at rank r's [E+1] expert offsets into its sorted token buffer.
+// tiles1: gate/up tiles (A pulled from the source rank, output to local h rows, packed densely in 128-row blocks);
+// tiles2: down tiles (A = local h rows, output to the source rank's result rows). counts_out[0] = number of tiles,
+// counts_out[1] = h rows used.
+__global__ void ep_prepare_kernel(const int* const* offsets, uint32_t* const* pads, int rank, int world, int e_loc,
+                                  MoeTile* tiles1, MoeTile* tiles2, int max_tiles, int* counts_out,
+                                  unsigned long long timeout_ns, int* status) {
+  __shared__ int s_ok;
+  uint32_t* my_pad = pads[rank];
+  const uint32_t epoch = my_pad[kEpEpoch] + 1;
+  if (threadIdx.x == 0) {
+    s_ok = 1;
+    __threadfence_system();
+    for (int r = 0; r < world; ++r) ep_st_release(pads[r] + kEpReady + rank, epoch);
+  }
+  __syncthreads();
+  if (threadIdx.x < world) {
+    if (!ep_wait_flag(my_pad + kEpReady + threadIdx.x, epoch, timeout_ns, status)) s_ok = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int n = 0, hrow = 0;
+    if (s_ok) {
+      for (int e = 0; e < e_loc; ++e) {
+        const int ge = rank * e_loc + e;
+        for (int s = 0; s < world; ++s) {
+          const int src = (rank + s) % world;    // local tokens first: their rows need no NVLink traffic
+          const int lo = offsets[src][ge], hi = offsets[src][ge + 1];
+          for (int r0 = lo; r0 < hi; r0 += kBM) {
+            if (n >= max_tiles) break;
+            const int rows = min(kBM, hi - r0);
+            tiles1[n] = MoeTile{src, r0, rows, e, rank, hrow};
+            tiles2[n] = MoeTile{rank, hrow, rows, e, src, r0};
+            hrow += kBM;
+            ++n;
+          }
+        }
+      }
+    }
+    counts_out[0] = n;
+    counts_out[1] = hrow;
+    __threadfence();
+    my_pad[kEpEpoch] = epoch;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int a_bytes = kBM * kBK * 2, b_bytes = kEpBN * kBK * 2, stage_bytes = a_bytes + b_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kEpStages * stage_bytes);
+  uint64_t* empty_bar = full_bar + kEpStages;
+  uint64_t* tfull_bar = empty_bar + kEpStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_last = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t* my_pad = p.pads[p.rank];
+  const uint32_t epoch = my_pad[kEpEpoch];   // ep_prepare_kernel already advanced it for this layer call
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kEpStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 4);
+    }
+    *abort_flag = 0;
+    *s_last = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_blocks = (p.N + kEpBN - 1) / kEpBN;
+  const int total = *p.n_tiles * n_blocks;
+  const int nk = (p.K + kBK - 1) / kBK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+        const MoeTile t = p.tiles[w / n_blocks];
+        const int nb = w % n_blocks;
+        const int b_row = t.expert * p.N + nb * kEpBN;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % kEpStages;
+          if (!mbar_wait(&empty_bar[s], ((it / kEpStages) & 1) ^ 1, abort_flag, p.status, kTimeoutProducer)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * stage_bytes;
+          mbar_expect_tx(&full_bar[s], stage_bytes);
+          tma_load_2d(sa, &maps.a[t.a_src], &full_bar[s], kb * kBK, t.a_row0);
+          tma_load_2d(sa + a_bytes, &maps.b, &full_bar[s], kb * kBK, b_row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(kEpBN, 0, 0);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++acc_it) {
+        const int buf = acc_it & 1;
+        if (!mbar_wait(&tempty_bar[buf], ((acc_it >> 1) & 1) ^ 1, abort_flag, p.status, kTimeoutMma)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * kEpBN;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % kEpStages;
+          if (!mbar_wait(&full_bar[s], (it / kEpStages) & 1, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * stage_bytes);
+          const uint64_t da = make_smem_desc(sa, 16u, 1024u), db = make_smem_desc(sa + a_bytes, 16u, 1024u);
+          const int nmma = min(4, (p.K - kb * kBK + 15) / 16);
+          for (int j = 0; j < nmma; ++j)
+            umma_f16(d_tmem, da + static_cast<uint64_t>(2 * j), db + static_cast<uint64_t>(2 * j), idesc,
+                     (kb > 0 || j > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+        }
+        if (ok) umma_commit(&tfull_bar[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t acc_it = 0;
+    for (int w = blockIdx.x; w < total; w += gridDim.x, ++acc_it) {
+      const MoeTile t = p.tiles[w / n_blocks];
+      const int nb = w % n_blocks;
+      const int buf = acc_it & 1;
+      if (!mbar_wait(&tfull_bar[buf], (acc_it >> 1) & 1, abort_flag, p.status, kTimeoutEpilogue)) break;
+      tc_fence_after();
+      const int lrow = q * 32 + lane;
+      const bool row_ok = lrow < t.rows;
+      __nv_bfloat16* drow = p.out[t.out_dst] + static_cast<long long>(t.out_row0 + lrow) * p.ldd;
+      const uint32_t tbase = tmem_base + buf * kEpBN + (static_cast<uint32_t>(q * 32) << 16);
+      if (p.swiglu) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32b_x32(tbase + c * 32, g);
+          tmem_ld_32x32b_x32(tbase + 128 + c * 32, u);
+          tmem_ld_wait();
+          const int col0 = nb * 128 + c * 32;
+          if (!row_ok) continue;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = col0 + v * 8;
+            if (col + 8 > p.N / 2) continue;
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float gv = __uint_as_float(g[v * 8 + e]);
+              f[e] = gv / (1.f + __expf(-gv)) * __uint_as_float(u[v * 8 + e]);
+            }
+            uint4 o;
+            o.x = pack_bf16x2(f[0], f[1]);
+            o.y = pack_bf16x2(f[2], f[3]);
+            o.z = pack_bf16x2(f[4], f[5]);
+            o.w = pack_bf16x2(f[6], f[7]);
+            *reinterpret_cast<uint4*>(drow + col) = o;
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < kEpBN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tbase + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = nb * kEpBN + c * 32;
+          if (!row_ok) continue;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = col0 + v * 8;
+            if (col + 8 > p.N) continue;
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[v * 8]), __uint_as_float(r[v * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+            *reinterpret_cast<uint4*>(drow + col) = o;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+    }
+    if (p.signal_pushed) __threadfence_system();
+  }
+
+  __syncwarp();
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (!p.signal_pushed) return;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(my_pad + kEpArrive, 1u);
+    if (prev == gridDim.x - 1) {
+      my_pad[kEpArrive] = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r) ep_st_release(p.pads[r] + kEpPushed + p.rank, epoch);
+      *s_last = 1;
+    }
+  }
+  __syncthreads();
+  // the last CTA keeps the launch alive until every peer's rows have landed in this rank's result buffer
+  if (*s_last && threadIdx.x < p.world)
+    ep_wait_flag(my_pad + kEpPushed + threadIdx.x, epoch, p.timeout_ns, p.status);
+}
+
+}  // namespace pm
+
+using namespace pm;
+
+extern "C" int pm_ep_prepare(const unsigned long long* offset_ptrs, const unsigned long long* pad_ptrs, int rank,
+                             int world, int e_loc, void* tiles1, void* tiles2, int max_tiles, int* counts_out,
+                             double timeout_s, int* status, void* dev_ptr_scratch, cudaStream_t st) {
+  // dev_ptr_scratch: device buffer of 16 pointers (offsets[8], pads[8]) written here once per call
+  if (world < 1 || world > kEpMaxRanks || rank < 0 || rank >= world || e_loc < 1) return -1;
+  unsigned long long host[16];
+  for (int r = 0; r < 8; ++r) {
+    host[r] = offset_ptrs[r < world ? r : rank];
+    host[8 + r] = pad_ptrs[r < world ? r : rank];
+  }
+  cudaError_t e = cudaMemcpyAsync(dev_ptr_scratch, host, sizeof(host), cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  ep_prepare_kernel<<<1, 32, 0, st>>>(reinterpret_cast<const int* const*>(dev_ptr_scratch),
+                                      reinterpret_cast<uint32_t* const*>(static_cast<unsigned long long*>(dev_ptr_scratch) + 8),
+                                      rank, world, e_loc, static_cast<MoeTile*>(tiles1), static_cast<MoeTile*>(tiles2),
+                                      max_tiles, counts_out, static_cast<unsigned long long>(timeout_s * 1e9), status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// a_ptrs[r]: A buffer of map index r ([a_rows, K], row stride lda); w: [e_loc * N, K]; out_ptrs[r]: output base of rank r.
+extern "C" int pm_moe_gemm(const unsigned long long* a_ptrs, int a_rows, int lda, const void* w, int ldw, int e_loc,
+                           const unsigned long long* out_ptrs, int ldd, const void* tiles, const int* n_tiles,
+                           int max_tiles, int N, int K, int swiglu, int rank, int world, int signal_pushed,
+                           const unsigned long long* pad_ptrs, double timeout_s, int* status, cudaStream_t st) {
+  if (world < 1 || world > kEpMaxRanks || rank < 0 || rank >= world) return -1;
+  if (N <= 0 || K <= 0 || (N % 8) || (ldd % 8) || (swiglu && (N % 256))) return -2;
+  MoeMaps maps;
+  MoeGemmParams p{};
+  int rc;
+  for (int r = 0; r < kEpMaxRanks; ++r) {
+    const int rr = r < world ? r : rank;
+    if ((rc = operand_map(&maps.a[r], reinterpret_cast<const void*>(a_ptrs[rr]), 0, a_rows, K, lda, kBM))) return rc * 10 - 5;
+    p.out[r] = reinterpret_cast<__nv_bfloat16*>(out_ptrs[rr]);
+    p.pads[r] = reinterpret_cast<uint32_t*>(pad_ptrs[rr]);
+  }
+  if ((rc = operand_map(&maps.b, w, 0, e_loc * N, K, ldw, kEpBN))) return rc * 10 - 6;
+  p.tiles = static_cast<const MoeTile*>(tiles);
+  p.n_tiles = n_tiles;
+  p.N = N; p.K = K; p.swiglu = swiglu; p.ldd = ldd; p.rank = rank; p.world = world;
+  p.signal_pushed = signal_pushed;
+  p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
+  p.status = status;
+  const size_t smem = static_cast<size_t>(kEpStages) * (kBM * kBK * 2 + kEpBN * kBK * 2) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const long long work = static_cast<long long>(max_tiles) * ((N + kEpBN - 1) / kEpBN);
+  int grid = num_sms();
+  if (work < grid) grid = static_cast<int>(work < 1 ? 1 : work);
+  moe_gemm_kernel<<<grid, kThreads, smem, st>>>(maps, p);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,371 @@
+// Tensor-parallel linear layers fused with their collective, over NVLink peer memory (one launch per rank).
+//
+//   mode 0  all-gather -> GEMM (column-parallel):  Y[M, N_loc] = concat_r(X_r)[M, K] * W_loc[N_loc, K]^T
+//           X is sharded by rows across ranks (sequence-parallel activations, M_r = M / world rows each, in
+//           symmetric memory). The TMA producer reads each A tile straight from the owning rank's buffer (a
+//           non-multicast TMA load through a per-rank tensor map), starting with the local shard and walking the
+//           ranks in ring order, so no gathered copy of X is ever materialised and remote traffic overlaps the
+//           MMAs of earlier tiles.
+//   mode 1  GEMM -> reduce-scatter (row-parallel): Y_r[M_r, N] = sum_q ( X_q[M, K_loc] * W_q[N, K_loc]^T )[rows of r]
+//           Each rank computes all M rows of its partial product; the epilogue pushes every finished tile as bf16
+//           straight into the owner's staging slot [parity][source rank] with 16-byte peer stores (remote owners
+//           first, own rows last); once every rank has signalled, each rank sums the `world` slots of its rows in
+//           fixed rank order (deterministic) and writes Y_r.
+//
+// This replaces the reference's all_to_sharded_forward / sharded_to_all_forward (an all_sum around a local matmul,
+// crates/pmetal-distributed/src/tensor_parallel/sharded_linear.rs:41-106).
+//
+// GEMM core: persistent 128x256x64 tiles, warp 0 = TMA producer, warp 1 = tcgen05.mma issuer (accumulators
+// double-buffered in TMEM), warps 2-5 = epilogue. Cross-rank ordering uses epoch-valued flags in each rank's signal
+// pad (system-scope release/acquire); every wait is bounded and reports through the status word. Plain peer
+// loads/stores only: no multimem and no multicast loads.
+#include "gemm_common.cuh"
+
+namespace pm {
+
+constexpr int kTpMaxRanks = 8;
+constexpr int kTpBN = 256;
+constexpr int kTpStages = 4;
+constexpr int kStatusTpPeer = 106;
+
+// signal pad words
+constexpr int kTpReady = 0;     // [8] mode 0: rank r's X shard of this epoch is complete
+constexpr int kTpDone = 8;      // [8] mode 0: rank r finished reading everyone's shard
+constexpr int kTpPushed = 16;   // [8] mode 1: rank r finished pushing its partial tiles
+constexpr int kTpEpoch = 24;    // local epoch counter
+constexpr int kTpArrive = 25;   // local CTA arrival counter (phase 1)
+constexpr int kTpArrive2 = 26;  // local CTA arrival counter (phase 2)
+
+struct TpMaps {
+  CUtensorMap a[kTpMaxRanks];   // mode 0: per-rank X shard; mode 1: a[0] = local X
+  CUtensorMap b;
+};
+
+struct TpParams {
+  int mode, rank, world;
+  int M, N, K;            // M = total rows (all ranks)
+  int rows_per_rank;      // M / world, multiple of 128
+  __nv_bfloat16* D;       // mode 0: Y [M, ldd]; mode 1: Y_r [rows_per_rank, ldd]
+  int ldd;
+  __nv_bfloat16* stage[kTpMaxRanks];   // mode 1: peer-mapped staging, [2][world][rows_per_rank][N] bf16 each
+  uint32_t* pads[kTpMaxRanks];
+  unsigned long long timeout_ns;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t tp_ld_acquire(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tp_st_release(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// bounded wait for *flag >= epoch (wrap-safe); false on expiry
+__device__ __forceinline__ bool tp_wait_flag(const uint32_t* flag, uint32_t epoch, unsigned long long timeout_ns,
+                                             int* status) {
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(tp_ld_acquire(flag) - epoch) < 0) {
+    if ((++spins & 31u) == 0u) {
+      if (globaltimer_ns() - t0 > timeout_ns) {
+        atomicCAS(status, 0, kStatusTpPeer);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+  return true;
+}
+
+// work item -> (rank whose rows these are, row block within that rank, column block)
+__device__ __forceinline__ void tp_tile(const TpParams& p, int w, int n_tiles, int tpr, int* owner, int* mb, int* nb) {
+  *nb = w % n_tiles;
+  const int mseq = w / n_tiles;
+  const int s = mseq / tpr;
+  *mb = mseq % tpr;
+  // mode 0: local shard first, then ring order; mode 1: remote owners first, own rows last
+  *owner = (p.mode == 0) ? (p.rank + s) % p.world : (p.rank + 1 + s) % p.world;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int a_bytes = kBM * kBK * 2, b_bytes = kTpBN * kBK * 2, stage_bytes = a_bytes + b_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kTpStages * stage_bytes);
+  uint64_t* empty_bar = full_bar + kTpStages;
+  uint64_t* tfull_bar = empty_bar + kTpStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_last = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t* my_pad = p.pads[p.rank];
+  const uint32_t epoch = my_pad[kTpEpoch] + 1;   // bumped by the last CTA at the very end of the launch
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kTpStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 4);
+    }
+    *abort_flag = 0;
+    *s_last = 0;
+    mbar_init_fence();
+    // mode 0: everything written to the local X shard by earlier kernels of this stream is complete; tell the peers
+    if (p.mode == 0 && blockIdx.x == 0) {
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r) tp_st_release(p.pads[r] + kTpReady + p.rank, epoch);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tpr = p.rows_per_rank / kBM;
+  const int n_tiles = (p.N + kTpBN - 1) / kTpBN;
+  const int total = tpr * p.world * n_tiles;
+  const int nk = (p.K + kBK - 1) / kBK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0, seen = 1u << p.rank;   // ranks whose ready flag has been observed
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+        int owner, mb, nb;
+        tp_tile(p, w, n_tiles, tpr, &owner, &mb, &nb);
+        const CUtensorMap* ma = (p.mode == 0) ? &maps.a[owner] : &maps.a[0];
+        const int m0 = (p.mode == 0) ? mb * kBM : (owner * tpr + mb) * kBM;
+        if (p.mode == 0 && !(seen & (1u << owner))) {
+          if (!tp_wait_flag(my_pad + kTpReady + owner, epoch, p.timeout_ns, p.status)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          seen |= 1u << owner;
+        }
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % kTpStages;
+          if (!mbar_wait(&empty_bar[s], ((it / kTpStages) & 1) ^ 1, abort_flag, p.status, kTimeoutProducer)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * stage_bytes;
+          mbar_expect_tx(&full_bar[s], stage_bytes);
+          tma_load_2d(sa, ma, &full_bar[s], kb * kBK, m0);
+          tma_load_2d(sa + a_bytes, &maps.b, &full_bar[s], kb * kBK, nb * kTpBN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(kTpBN, 0, 0);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++acc_it) {
+        const int buf = acc_it & 1;
+        if (!mbar_wait(&tempty_bar[buf], ((acc_it >> 1) & 1) ^ 1, abort_flag, p.status, kTimeoutMma)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * kTpBN;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+          const int s = it % kTpStages;
+          if (!mbar_wait(&full_bar[s], (it / kTpStages) & 1, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * stage_bytes);
+          const uint64_t da = make_smem_desc(sa, 16u, 1024u), db = make_smem_desc(sa + a_bytes, 16u, 1024u);
+          const int rem = p.K - kb * kBK;
+          const int nmma = min(4, (rem + 15) / 16);
+          for (int j = 0; j < nmma; ++j)
+            umma_f16(d_tmem, da + static_cast<uint64_t>(2 * j), db + static_cast<uint64_t>(2 * j), idesc,
+                     (kb > 0 || j > 0) ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+        }
+        if (ok) umma_commit(&tfull_bar[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t acc_it = 0;
+    for (int w = blockIdx.x; w < total; w += gridDim.x, ++acc_it) {
+      int owner, mb, nb;
+      tp_tile(p, w, n_tiles, tpr, &owner, &mb, &nb);
+      const int buf = acc_it & 1;
+      if (!mbar_wait(&tfull_bar[buf], (acc_it >> 1) & 1, abort_flag, p.status, kTimeoutEpilogue)) break;
+      tc_fence_after();
+      const int lrow = mb * kBM + q * 32 + lane;     // row within the owner's shard
+      __nv_bfloat16* drow;
+      if (p.mode == 0) {
+        drow = p.D + (static_cast<long long>(owner) * p.rows_per_rank + lrow) * p.ldd;
+      } else {
+        const long long slot = (static_cast<long long>(epoch & 1) * p.world + p.rank) * p.rows_per_rank + lrow;
+        drow = p.stage[owner] + slot * p.N;
+      }
+#pragma unroll 1
+      for (int c = 0; c < kTpBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + buf * kTpBN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
+        tmem_ld_wait();
+        const int col0 = nb * kTpBN + c * 32;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int col = col0 + v * 8;
+          if (col + 8 <= p.N) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(r[v * 8]), __uint_as_float(r[v * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+            *reinterpret_cast<uint4*>(drow + col) = o;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+    }
+    if (p.mode == 1) __threadfence_system();   // this thread's peer stores are ordered before the flag below
+  }
+
+  // ---------------------------------------------------------------- phase boundary
+  __syncwarp();
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(my_pad + kTpArrive, 1u);
+    if (prev == gridDim.x - 1) {
+      // every CTA of this rank has finished its tiles (and, in mode 0, its reads of the peers' shards)
+      my_pad[kTpArrive] = 0;
+      __threadfence_system();
+      const int off = (p.mode == 0) ? kTpDone : kTpPushed;
+      for (int r = 0; r < p.world; ++r) tp_st_release(p.pads[r] + off + p.rank, epoch);
+      *s_last = 1;
+    }
+  }
+  __syncthreads();
+
+  if (p.mode == 0) {
+    // the last CTA keeps the launch alive until every peer has stopped reading this rank's shard, so that whatever
+    // runs next on this stream may overwrite it
+    if (*s_last && threadIdx.x < p.world) {
+      if (!tp_wait_flag(my_pad + kTpDone + threadIdx.x, epoch, p.timeout_ns, p.status)) *abort_flag = 1;
+    }
+    __syncthreads();
+    if (*s_last && threadIdx.x == 0) {
+      __threadfence();
+      my_pad[kTpEpoch] = epoch;
+    }
+    return;
+  }
+
+  // ---------------------------------------------------------------- mode 1, phase 2: sum the staged partials
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    if (!tp_wait_flag(my_pad + kTpPushed + threadIdx.x, epoch, p.timeout_ns, p.status)) s_ok = 0;
+  }
+  __syncthreads();
+  if (s_ok) {
+    const long long per_slot = static_cast<long long>(p.rows_per_rank) * p.N;
+    const __nv_bfloat16* base = p.stage[p.rank] + static_cast<long long>(epoch & 1) * p.world * per_slot;
+    const int vec_per_row = p.N / 8;
+    const long long n_vec = static_cast<long long>(p.rows_per_rank) * vec_per_row;
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n_vec;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < p.world; ++r) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(base + r * per_slot + i * 8);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
+      }
+      const long long row = i / vec_per_row;
+      const int col = static_cast<int>(i - row * vec_per_row) * 8;
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(p.D + row * p.ldd + col) = o;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(my_pad + kTpArrive2, 1u);
+    if (prev == gridDim.x - 1) {
+      my_pad[kTpArrive2] = 0;
+      __threadfence();
+      my_pad[kTpEpoch] = epoch;
+    }
+  }
+}
+
+}  // namespace pm
+
+using namespace pm;
+
+// mode 0: x_ptrs[r] = rank r's X shard [rows_per_rank, K] (ldx), w = W_loc [N, K] (ldw), out = Y [M, ldd].
+// mode 1: x_ptrs[rank] = local X [M, K] (ldx), w = W_loc [N, K], stage_ptrs[r] = rank r's staging buffer,
+//         out = Y_r [rows_per_rank, ldd]. K and N are the local extents. Returns 0, a negative argument error,
+//         or a CUDA error code.
+extern "C" int pm_tp_gemm(int mode, const unsigned long long* x_ptrs, int ldx, const void* w, int ldw, void* out,
+                          int ldd, const unsigned long long* stage_ptrs, const unsigned long long* pad_ptrs, int rank,
+                          int world, int M, int N, int K, double timeout_s, int max_ctas, int* status,
+                          cudaStream_t stream) {
+  if (mode != 0 && mode != 1) return -1;
+  if (world < 1 || world > kTpMaxRanks || rank < 0 || rank >= world) return -2;
+  if (M <= 0 || N <= 0 || K <= 0 || M % world || (M / world) % kBM) return -3;
+  if ((N % 8) || (ldd % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) return -4;
+  TpMaps maps;
+  TpParams p{};
+  p.mode = mode; p.rank = rank; p.world = world; p.M = M; p.N = N; p.K = K; p.rows_per_rank = M / world;
+  p.D = static_cast<__nv_bfloat16*>(out); p.ldd = ldd;
+  p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
+  p.status = status;
+  int rc;
+  for (int r = 0; r < kTpMaxRanks; ++r) {
+    const int src = (mode == 0) ? (r < world ? r : rank) : rank;
+    const int rows = (mode == 0) ? p.rows_per_rank : M;
+    if ((rc = operand_map(&maps.a[r], reinterpret_cast<const void*>(x_ptrs[src]), 0, rows, K, ldx, kBM))) return rc * 10 - 5;
+    p.pads[r] = reinterpret_cast<uint32_t*>(pad_ptrs[r < world ? r : rank]);
+    p.stage[r] = (mode == 1) ? reinterpret_cast<__nv_bfloat16*>(stage_ptrs[r < world ? r : rank]) : nullptr;
+  }
+  if ((rc = operand_map(&maps.b, w, 0, N, K, ldw, kTpBN))) return rc * 10 - 6;
+  const size_t smem = static_cast<size_t>(kTpStages) * (kBM * kBK * 2 + kTpBN * kBK * 2) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  const int total = (M / kBM) * ((N + kTpBN - 1) / kTpBN);
+  int grid = total;
+  const int cap = max_ctas > 0 ? max_ctas : num_sms();
+  if (grid > cap) grid = cap;
+  tp_gemm_kernel<<<grid, kThreads, smem, stream>>>(maps, p);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -45,7 +45,9 @@ def _load():
         pass
     for fn in ("pm_gemm_bf16", "pm_gemm_bf16_2sm", "pm_rmsnorm_fwd", "pm_rmsnorm_bwd", "pm_rope_table", "pm_qknorm_rope_fwd",
                "pm_qknorm_rope_bwd", "pm_swiglu_fwd", "pm_swiglu_bwd", "pm_ce_fwd_bwd", "pm_sumsq", "pm_adamw_flat",
-               "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16", "pm_paged_attn", "pm_kv_append", "pm_attn_fwd_tc", "pm_attn_bwd_tc", "pm_dequant_4bit"):
+               "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16", "pm_paged_attn", "pm_kv_append", "pm_attn_fwd_tc", "pm_attn_bwd_tc", "pm_dequant_4bit", "pm_sample", "pm_spec_verify", "pm_count_tokens",
+               "pm_moe_route", "pm_moe_gather", "pm_moe_combine", "pm_gguf_dequant_bf16", "pm_fp8_quant", "pm_fp8_dequant",
+               "pm_kd_fwd_bwd", "pm_merge_fused", "pm_dot_norms"):
         getattr(_LIB, fn).restype = c_int
 
 
@@ -473,3 +475,144 @@ def token_nll(hidden, weight, tokens, chunk: int = 4096, row_scale=None, weight_
                 raw_gemm(scratch, 0, ldl, n, weight, 1, weight.stride(0), H, d, 0, d.stride(0), n, H, V,
                          bn=max(64, _pick_bn(H)))
     return nll, dh
+
+
+# ------------------------------------------------------------------------------------------- sampling
+c_ull = ctypes.c_ulonglong
+
+
+def sample(logits, temperature, top_k=None, top_p=None, min_p=None, counts=None, rep_pen=None, freq_pen=None,
+           pres_pen=None, seeds=None, step: int = 0, want_logprob: bool = True):
+    """logits [rows, V] fp32 or bf16 (row stride arbitrary); per-row parameter tensors on the device.
+    Returns (tokens int32 [rows], logprobs fp32 [rows] or None)."""
+    rows, V = logits.shape
+    assert logits.stride(1) == 1 and logits.dtype in (torch.float32, torch.bfloat16)
+    tok = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    lp = torch.empty(rows, dtype=torch.float32, device=logits.device) if want_logprob else None
+    _chk(lib().pm_sample(_p(logits), c_int(int(logits.dtype == torch.bfloat16)), c_ll(logits.stride(0)), c_int(rows),
+                         c_int(V), _p(counts), _p(temperature), _p(top_k), _p(top_p), _p(min_p), _p(rep_pen),
+                         _p(freq_pen), _p(pres_pen), _p(seeds), c_ull(step), _p(tok), _p(lp), _stream()), "pm_sample")
+    return tok, lp
+
+
+def spec_verify(target_logits, draft_logits, draft_tokens, temperature: float = 0.0, seeds=None, step: int = 0):
+    """target_logits [n, K+1, V] fp32, draft_logits [n, K, V] fp32 (None for greedy), draft_tokens [n, K] int32.
+    Returns (n_accepted int32 [n], next_token int32 [n])."""
+    n, k1, V = target_logits.shape
+    K = k1 - 1
+    assert target_logits.is_contiguous() and target_logits.dtype == torch.float32
+    if draft_logits is not None:
+        assert draft_logits.is_contiguous() and draft_logits.dtype == torch.float32
+    acc = torch.empty(n, dtype=torch.int32, device=target_logits.device)
+    nxt = torch.empty(n, dtype=torch.int32, device=target_logits.device)
+    _chk(lib().pm_spec_verify(_p(target_logits), _p(draft_logits), _p(draft_tokens.contiguous()), c_int(n), c_int(K),
+                              c_int(V), c_float(temperature), _p(seeds), c_ull(step), _p(acc), _p(nxt), _stream()),
+         "pm_spec_verify")
+    return acc, nxt
+
+
+def count_tokens(counts, tokens) -> None:
+    _chk(lib().pm_count_tokens(_p(counts), _p(tokens), c_int(tokens.numel()), c_int(counts.shape[1]), _stream()),
+         "pm_count_tokens")
+
+
+# ------------------------------------------------------------------------------------------- MoE routing
+def moe_route(router_logits, k: int, renorm: bool = True):
+    """router_logits [T, E] (bf16 or fp32). Returns dict(topk_idx [T,k], topk_w [T,k], counts [E], offsets [E+1],
+    perm [T*k] (sorted position -> token*k+slot), inv [T*k] (token*k+slot -> sorted position))."""
+    T, E = router_logits.shape
+    dev = router_logits.device
+    x = router_logits.contiguous()
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        x = x.float()
+    out = dict(topk_idx=torch.empty(T, k, dtype=torch.int32, device=dev), topk_w=torch.empty(T, k, dtype=torch.float32, device=dev),
+               counts=torch.empty(E, dtype=torch.int32, device=dev), offsets=torch.empty(E + 1, dtype=torch.int32, device=dev),
+               perm=torch.empty(T * k, dtype=torch.int32, device=dev), inv=torch.empty(T * k, dtype=torch.int32, device=dev))
+    _chk(lib().pm_moe_route(_p(x), c_int(int(x.dtype == torch.float32)), c_int(T), c_int(E), c_int(k), c_int(int(renorm)),
+                            _p(out["topk_idx"]), _p(out["topk_w"]), _p(out["counts"]), _p(out["offsets"]),
+                            _p(out["perm"]), _p(out["inv"]), _stream()), "pm_moe_route")
+    return out
+
+
+def moe_gather(x, perm, k: int):
+    n, H = perm.numel(), x.shape[1]
+    out = torch.empty(n, H, dtype=torch.bfloat16, device=x.device)
+    _chk(lib().pm_moe_gather(_p(x.contiguous()), _p(perm), c_int(k), _p(out), c_ll(n), c_int(H), _stream()), "pm_moe_gather")
+    return out
+
+
+def moe_combine(z, inv, w, k: int):
+    T, H = inv.numel() // k, z.shape[1]
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=z.device)
+    _chk(lib().pm_moe_combine(_p(z.contiguous()), _p(inv), _p(w.contiguous()), c_int(k), _p(y), c_ll(T), c_int(H), _stream()),
+         "pm_moe_combine")
+    return y
+
+
+# ------------------------------------------------------------------------------------------- GGUF / FP8
+def gguf_dequant_bf16(raw, ggml_type: int, shape):
+    """raw: uint8 device tensor of GGUF blocks (Q4_0=2, Q8_0=8, Q4_K=12, Q6_K=14) -> bf16 tensor of ``shape``."""
+    n = 1
+    for d in shape:
+        n *= d
+    out = torch.empty(shape, dtype=torch.bfloat16, device=raw.device)
+    _chk(lib().pm_gguf_dequant_bf16(_p(raw), _p(out), c_ll(n), c_int(int(ggml_type)), _stream()), "pm_gguf_dequant_bf16")
+    return out
+
+
+def fp8_quant(x):
+    """bf16 tensor (numel % 128 == 0) -> (uint8 E4M3 codes of the same shape, fp32 scales per 128 elements)."""
+    x = x.contiguous()
+    n = x.numel()
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    sc = torch.empty(n // 128, dtype=torch.float32, device=x.device)
+    _chk(lib().pm_fp8_quant(_p(x), _p(q), _p(sc), c_ll(n), _stream()), "pm_fp8_quant")
+    return q, sc
+
+
+def fp8_dequant(q, scales):
+    y = torch.empty(q.shape, dtype=torch.bfloat16, device=q.device)
+    _chk(lib().pm_fp8_dequant(_p(q), _p(scales), _p(y), c_ll(q.numel()), _stream()), "pm_fp8_dequant")
+    return y
+
+
+# ------------------------------------------------------------------------------------------- distillation / merge
+KD_KINDS = {"kl": 0, "forward_kl": 0, "reverse_kl": 1, "js": 2, "jsd": 2, "soft_ce": 3, "tvd": 4}
+
+
+def kd_fwd_bwd(student_logits, teacher_logits, temperature: float, kind: str = "kl", beta: float = 0.5, row_scale=None,
+               write_grad: bool = True):
+    """student_logits [rows, V] bf16 is overwritten with the gradient (times row_scale); returns per-row losses."""
+    rows, V = student_logits.shape
+    assert student_logits.dtype == torch.bfloat16 and teacher_logits.dtype == torch.bfloat16
+    assert student_logits.stride(1) == 1 and teacher_logits.stride(1) == 1
+    row_loss = torch.empty(rows, dtype=torch.float32, device=student_logits.device)
+    _chk(lib().pm_kd_fwd_bwd(_p(student_logits), c_ll(student_logits.stride(0)), _p(teacher_logits),
+                             c_ll(teacher_logits.stride(0)), c_int(rows), c_int(V), c_float(temperature),
+                             c_int(KD_KINDS[kind]), c_float(beta), _p(row_scale), _p(row_loss), _p(None),
+                             c_int(int(write_grad)), _stream()), "pm_kd_fwd_bwd")
+    return row_loss
+
+
+def merge_fused(models, base, weights, thresholds=None, densities=None, consensus=False, rescale=True, lam=1.0, seed=0,
+                out_dtype=torch.float32):
+    """Fused task-vector merge of up to 8 same-shaped tensors (all bf16 or all fp32)."""
+    m0 = models[0]
+    bf = m0.dtype == torch.bfloat16
+    ms = [m.contiguous() for m in models]
+    assert all(m.dtype == m0.dtype and m.shape == m0.shape for m in ms)
+    b = base.contiguous().to(m0.dtype) if base is not None else None
+    out = torch.empty(m0.shape, dtype=out_dtype, device=m0.device)
+    ptrs = (c_void_p * len(ms))(*[m.data_ptr() for m in ms])
+    fa = lambda v: (c_float * len(ms))(*[float(x) for x in v]) if v is not None else None     # noqa: E731
+    _chk(lib().pm_merge_fused(ptrs, _p(b), fa(weights), fa(thresholds), fa(densities), c_int(len(ms)), c_int(int(bf)),
+                              c_int(int(out_dtype == torch.bfloat16)), c_int(int(consensus)), c_int(int(rescale)),
+                              c_float(lam), c_ull(seed), _p(out), c_ll(m0.numel()), _stream()), "pm_merge_fused")
+    return out
+
+
+def dot_norms(a, b):
+    out = torch.empty(3, dtype=torch.float32, device=a.device)
+    _chk(lib().pm_dot_norms(_p(a.contiguous()), _p(b.contiguous()), c_int(int(a.dtype == torch.bfloat16)), c_ll(a.numel()),
+                            _p(out), _stream()), "pm_dot_norms")
+    return out

@@ -1,0 +1,265 @@
+"""GPU numerics for the sampler, speculative verifier, MoE routing, GGUF / FP8 dequantisation, distillation and merge
+kernels; each is compared with a plain PyTorch fp32 restatement of the same op."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _nat():
+    from pmetal_b200.ops import native
+    if not native.available():
+        pytest.fail(f"native library missing: {native.load_error()}")
+    return native
+
+
+def _f(dev, *vals, dtype=torch.float32):
+    return torch.tensor(vals, dtype=dtype, device=dev)
+
+
+def test_sampler_greedy_topk_topp_minp_distribution():
+    nat = _nat()
+    dev = "cuda"
+    torch.manual_seed(0)
+    V = 5000
+    logits = torch.randn(4, V, device=dev) * 2
+    # greedy
+    tok, lp = nat.sample(logits, torch.zeros(4, device=dev))
+    assert torch.equal(tok.long(), logits.argmax(-1))
+    ref_lp = torch.log_softmax(logits, -1).gather(1, tok.long()[:, None])[:, 0]
+    assert torch.allclose(lp, ref_lp, atol=1e-3)
+    # top-k = 1 at any temperature is greedy too
+    tok, _ = nat.sample(logits, torch.full((4,), 0.7, device=dev), top_k=torch.ones(4, dtype=torch.int32, device=dev),
+                        seeds=torch.arange(4, dtype=torch.int64, device=dev))
+    assert torch.equal(tok.long(), logits.argmax(-1))
+    # empirical distribution under temperature + top-k + top-p + min-p on one row, many draws
+    row = torch.randn(1, 64, device=dev) * 1.5
+    n = 20000
+    rows = row.expand(n, 64).contiguous()
+    temp, k, p_, mp = 0.8, 12, 0.9, 0.02
+    tok, _ = nat.sample(rows, torch.full((n,), temp, device=dev), top_k=torch.full((n,), k, dtype=torch.int32, device=dev),
+                        top_p=torch.full((n,), p_, device=dev), min_p=torch.full((n,), mp, device=dev),
+                        seeds=torch.arange(n, dtype=torch.int64, device=dev) + 17, step=3)
+    probs = torch.softmax(row[0] / temp, -1)
+    sp, si = probs.sort(descending=True)
+    keep = torch.zeros(64, dtype=torch.bool, device=dev)
+    keep[si[:k]] = True
+    pk = torch.where(keep, probs, torch.zeros_like(probs))
+    pk = pk / pk.sum()
+    spk, sik = pk.sort(descending=True)
+    cum = spk.cumsum(0)
+    n_keep = int((cum < p_).sum().item()) + 1
+    keep2 = torch.zeros(64, dtype=torch.bool, device=dev)
+    keep2[sik[:n_keep]] = True
+    keep2 &= probs >= mp * probs.max()
+    target = torch.where(keep2, probs, torch.zeros_like(probs))
+    target = target / target.sum()
+    emp = torch.bincount(tok.long(), minlength=64).float() / n
+    assert emp[~keep2].sum() == 0
+    assert (emp - target).abs().max() < 0.015
+    # different seeds give different draws, same seed the same draw
+    a, _ = nat.sample(rows[:8], torch.ones(8, device=dev), seeds=torch.full((8,), 5, dtype=torch.int64, device=dev))
+    assert len(set(a.tolist())) == 1
+
+
+def test_sampler_penalties_and_bf16():
+    nat = _nat()
+    dev = "cuda"
+    V = 1000
+    logits = torch.zeros(2, V, device=dev)
+    logits[:, 10] = 5.0
+    logits[:, 20] = 4.0
+    counts = torch.zeros(2, V, dtype=torch.int32, device=dev)
+    counts[1, 10] = 3
+    tok, _ = nat.sample(logits.bfloat16(), torch.zeros(2, device=dev), counts=counts, rep_pen=_f(dev, 1.0, 2.0),
+                        freq_pen=_f(dev, 0.0, 0.1), pres_pen=_f(dev, 0.0, 0.1))
+    assert tok.tolist() == [10, 20]           # 5/2 - 0.3 - 0.1 = 2.1 < 4
+    nat.count_tokens(counts, tok)
+    assert counts[0, 10].item() == 1 and counts[1, 20].item() == 1
+
+
+def test_spec_verify_greedy_and_stochastic():
+    nat = _nat()
+    dev = "cuda"
+    torch.manual_seed(1)
+    n, K, V = 3, 4, 300
+    target = torch.randn(n, K + 1, V, device=dev)
+    am = target.argmax(-1)
+    draft = am[:, :K].clone().int()
+    draft[1, 2] = (draft[1, 2] + 1) % V        # mismatch at position 2
+    draft[2, 0] = (draft[2, 0] + 1) % V        # mismatch at position 0
+    acc, nxt = nat.spec_verify(target, None, draft, 0.0)
+    assert acc.tolist() == [4, 2, 0]
+    assert nxt.tolist() == [am[0, 4].item(), am[1, 2].item(), am[2, 0].item()]
+    # stochastic: identical draft and target distributions -> everything is accepted
+    dl = target[:, :K].contiguous()
+    toks = torch.distributions.Categorical(logits=dl).sample().int()
+    acc, nxt = nat.spec_verify(target, dl, toks, 1.0, seeds=torch.arange(n, dtype=torch.int64, device=dev))
+    assert acc.tolist() == [K] * n
+    # the emitted token follows the target distribution: one position, many trials
+    trials, V2 = 30000, 16
+    tl = torch.randn(1, 2, V2, device=dev).expand(trials, 2, V2).contiguous()
+    dlog = torch.randn(1, 1, V2, device=dev).expand(trials, 1, V2).contiguous()
+    dt = torch.distributions.Categorical(logits=dlog[:, 0]).sample().int()[:, None]
+    acc, nxt = nat.spec_verify(tl, dlog, dt, 1.0, seeds=torch.arange(trials, dtype=torch.int64, device=dev) * 7 + 1)
+    first = torch.where(acc >= 1, dt[:, 0], nxt)       # token emitted at position 0
+    emp = torch.bincount(first.long(), minlength=V2).float() / trials
+    assert (emp - torch.softmax(tl[0, 0], -1)).abs().max() < 0.015
+
+
+def test_moe_route_sort_gather_combine():
+    nat = _nat()
+    dev = "cuda"
+    torch.manual_seed(2)
+    T, E, k, H = 777, 64, 4, 256
+    logits = torch.randn(T, E, device=dev)
+    r = nat.moe_route(logits, k, renorm=True)
+    p = torch.softmax(logits, -1)
+    tw, ti = p.topk(k, -1)
+    assert torch.equal(r["topk_idx"].long(), ti)
+    assert torch.allclose(r["topk_w"], tw / tw.sum(-1, keepdim=True), atol=1e-5)
+    flat = ti.reshape(-1)
+    assert torch.equal(r["counts"].long(), torch.bincount(flat, minlength=E))
+    assert r["offsets"][-1].item() == T * k
+    perm = r["perm"].long()
+    assert torch.equal(flat[perm], flat[perm].sort().values)            # grouped by expert
+    stable = torch.sort(flat, stable=True).indices
+    assert torch.equal(perm, stable)                                     # and stable within an expert
+    assert torch.equal(r["inv"].long()[perm], torch.arange(T * k, device=dev))
+    x = torch.randn(T, H, device=dev).bfloat16()
+    g = nat.moe_gather(x, r["perm"], k)
+    assert torch.equal(g, x[perm // k])
+    y = nat.moe_combine(g, r["inv"], r["topk_w"], k)                      # identity experts -> y = x * sum(w) = x
+    assert torch.allclose(y.float(), x.float(), atol=2e-2, rtol=2e-2)
+    r2 = nat.moe_route(logits.bfloat16(), 2, renorm=False)
+    p2 = torch.softmax(logits.bfloat16().float(), -1).topk(2, -1)
+    assert torch.allclose(r2["topk_w"], p2.values, atol=1e-5)
+
+
+@pytest.mark.parametrize("name,tid", [("Q4_0", 2), ("Q8_0", 8), ("Q4K", 12), ("Q6K", 14)])
+def test_gguf_dequant_kernel_matches_host(name, tid):
+    nat = _nat()
+    from pmetal_b200.gguf import native as host
+    from pmetal_b200.gguf.types import GgmlType
+    x = (np.random.default_rng(3).standard_normal(256 * 40) * 0.1).astype(np.float32)
+    raw = host.quantize(x, GgmlType(tid))
+    ref = host.dequantize(raw, GgmlType(tid), x.size)
+    out = nat.gguf_dequant_bf16(torch.from_numpy(raw).cuda(), tid, (40, 256))
+    want = torch.from_numpy(ref).reshape(40, 256).bfloat16()
+    assert torch.equal(out.cpu(), want)
+
+
+def test_fp8_block_quant_round_trip():
+    nat = _nat()
+    torch.manual_seed(4)
+    x = (torch.randn(64, 512, device="cuda") * 3).bfloat16()
+    x[0, :128] = 0
+    q, sc = nat.fp8_quant(x)
+    amax = x.float().reshape(-1, 128).abs().amax(-1)
+    assert torch.allclose(sc, torch.where(amax > 0, amax / 448, torch.ones_like(amax)), rtol=1e-6)
+    y = nat.fp8_dequant(q, sc)
+    ref = (x.float().reshape(-1, 128) / sc[:, None]).to(torch.float8_e4m3fn).float() * sc[:, None]
+    close = torch.isclose(y.float().reshape(-1, 128), ref.bfloat16().float(), atol=1e-6, rtol=1e-2)
+    assert close.float().mean().item() > 0.995       # x * (1/scale) vs x / scale can differ on exact rounding ties
+    assert (y.float() - x.float()).abs().max() <= 0.07 * x.float().abs().max()
+
+
+@pytest.mark.parametrize("kind", ["kl", "reverse_kl", "js", "soft_ce", "tvd"])
+def test_distill_kernel_loss_and_grad(kind):
+    nat = _nat()
+    torch.manual_seed(5)
+    rows, V, temp, beta = 6, 3001, 2.0, 0.3
+    s0 = (torch.randn(rows, V, device="cuda") * 2).bfloat16()
+    t0 = (torch.randn(rows, V, device="cuda") * 2).bfloat16()
+    scale = torch.tensor([1.0, 0.5, 0.0, 1.0, 2.0, 1.0], device="cuda")
+    s = s0.float().requires_grad_(True)
+    ls, lt = torch.log_softmax(s / temp, -1), torch.log_softmax(t0.float() / temp, -1)
+    ps, pt = ls.exp(), lt.exp()
+    if kind == "kl":
+        loss = (pt * (lt - ls)).sum(-1)
+    elif kind == "reverse_kl":
+        loss = (ps * (ls - lt)).sum(-1)
+    elif kind == "js":
+        m = beta * pt + (1 - beta) * ps
+        loss = (beta * pt * (lt - m.log()) + (1 - beta) * ps * (ls - m.log())).sum(-1)
+    elif kind == "soft_ce":
+        loss = -(pt * ls).sum(-1)
+    else:
+        loss = 0.5 * (pt - ps).abs().sum(-1)
+    (loss * scale).sum().backward()
+    sg = s0.clone()
+    row_loss = nat.kd_fwd_bwd(sg, t0, temp, kind, beta, row_scale=scale)
+    want = torch.where(scale > 0, loss.detach(), torch.zeros_like(loss))
+    assert torch.allclose(row_loss, want, atol=2e-3, rtol=2e-3)
+    g = s.grad
+    assert (sg.float() - g).abs().max() <= 0.02 * g.abs().max() + 1e-6
+
+
+def test_merge_kernels_match_torch_methods():
+    nat = _nat()
+    from pmetal_b200.merge import methods as M
+    torch.manual_seed(6)
+    n = 100_003
+    base = torch.randn(n, device="cuda")
+    models = [base + 0.1 * torch.randn(n, device="cuda") for _ in range(3)]
+    w = [0.5, 0.3, 0.2]
+    out = nat.merge_fused(models, base, w, lam=0.8)
+    assert torch.allclose(out, M.task_arithmetic(models, base, w, 0.8), atol=1e-5)
+    out = nat.merge_fused(models, None, w)
+    assert torch.allclose(out, M.linear(models, w, normalize=False), atol=1e-5)
+    dens = [0.3, 0.5, 0.7]
+    thr = []
+    for m, d in zip(models, dens):
+        flat = (m - base).abs()
+        kk = min(int(math.ceil((1 - d) * n)), n - 1)
+        thr.append(torch.kthvalue(flat, kk + 1).values.item())
+    out = nat.merge_fused(models, base, w, thresholds=thr, consensus=True, lam=1.0)
+    assert torch.allclose(out, M.ties(models, base, w, dens, 1.0), atol=1e-5)
+    # DARE on one model: a `density` fraction survives and survivors are rescaled by 1/density
+    one = nat.merge_fused(models[:1], base, [1.0], densities=[0.3], rescale=True, seed=9) - base
+    tau = models[0] - base
+    kept = one != 0
+    assert abs(kept.float().mean().item() - 0.3) < 0.01
+    assert torch.allclose(one[kept], tau[kept] / 0.3, rtol=1e-5, atol=1e-6)
+    again = nat.merge_fused(models[:1], base, [1.0], densities=[0.3], rescale=True, seed=9) - base
+    assert torch.equal(one, again)                                  # same seed, same mask
+    other = nat.merge_fused(models[:1], base, [1.0], densities=[0.3], rescale=True, seed=10) - base
+    assert not torch.equal(one != 0, other != 0)
+    # three models: unbiased estimate of task arithmetic
+    out = nat.merge_fused(models, base, w, densities=dens, rescale=True, seed=9)
+    diff = (out - base) - (M.task_arithmetic(models, base, w, 1.0) - base)
+    assert abs(diff.mean().item()) < 5 * diff.std().item() / math.sqrt(n)
+    d3 = nat.dot_norms(models[0], models[1])
+    assert torch.allclose(d3, torch.stack([(models[0] * models[1]).sum(), models[0].pow(2).sum(), models[1].pow(2).sum()]),
+                          rtol=1e-3)
+    ob = nat.merge_fused([m.bfloat16() for m in models], base.bfloat16(), w, out_dtype=torch.bfloat16)
+    assert ob.dtype == torch.bfloat16 and (ob.float() - M.task_arithmetic(models, base, w, 1.0)).abs().max() < 0.05
+
+
+def test_local_grouped_moe_engine_matches_dense_reference():
+    nat = _nat()
+    from pmetal_b200.parallel.ep import FusedExpertMoE
+    torch.manual_seed(8)
+    E, k, H, I, T = 8, 2, 256, 384, 1000
+    gate_up = (torch.randn(E, 2 * I, H, device="cuda") * 0.05).bfloat16()
+    down = (torch.randn(E, H, I, device="cuda") * 0.05).bfloat16()
+    eng = FusedExpertMoE(gate_up, down, E, k, max_tokens=1024)
+    for _ in range(2):
+        x = torch.randn(T, H, device="cuda").bfloat16()
+        logits = torch.randn(T, E, device="cuda")
+        y = eng.forward(x, logits)
+        torch.cuda.synchronize()
+        nat.check_status()
+        p = torch.softmax(logits, -1)
+        w, idx = p.topk(k, -1)
+        w = w / w.sum(-1, keepdim=True)
+        ref = torch.zeros(T, H, device="cuda")
+        for e in range(E):
+            tok, slot = (idx == e).nonzero(as_tuple=True)
+            h = x[tok].float() @ gate_up[e].float().t()
+            h = (torch.nn.functional.silu(h[:, :I]) * h[:, I:]).bfloat16().float()
+            ref.index_add_(0, tok, (h @ down[e].float().t()).bfloat16().float() * w[tok, slot][:, None])
+        assert (y.float() - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 2e-3

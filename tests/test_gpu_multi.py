@@ -22,3 +22,17 @@ def test_fused_dp_matches_nccl_baseline():
     n = min(torch.cuda.device_count(), 4)
     r = _run("dp_worker.py", n)
     assert r.returncode == 0 and "DP_WORKER_OK" in r.stdout, r.stdout[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_fused_tensor_parallel_kernels():
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    r = _run("tp_worker.py", n, port=29543)
+    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_fused_expert_parallel_moe():
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    r = _run("ep_worker.py", n, port=29545)
+    assert r.returncode == 0 and "EP_WORKER_OK" in r.stdout, r.stdout[-4000:]
