@@ -358,7 +358,7 @@ extern "C" int pm_tp_gemm(int mode, const unsigned long long* x_ptrs, int ldx, c
   const size_t smem = static_cast<size_t>(kTpStages) * (kBM * kBK * 2 + kTpBN * kBK * 2) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }

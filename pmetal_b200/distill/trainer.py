@@ -1,0 +1,115 @@
+"""Knowledge-distillation trainer: online (teacher forward every step), offline (cached, compressed teacher logits) and
+progressive (temperature annealed from ``temperature`` to ``final_temperature``).
+
+loss = alpha * soft(student, teacher; T) + (1 - alpha) * CE(student, labels); defaults alpha 0.5, T 2.0 as in the
+reference CLI (crates/pmetal/src/cli/distill.rs; trainer crates/pmetal-trainer/src/distillation.rs, config
+crates/pmetal-distill/src/config.rs). On CUDA the soft term of the KL family runs through the fused chunked kernel, so
+neither model's full logits are materialised."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import losses as L
+from .offline import LogitCache
+from .taid import TaidConfig, TaidDistiller
+
+
+@dataclass
+class DistillConfig:
+    method: str = "online"            # online | offline | progressive
+    loss_type: str = "kl"             # any key of losses.LOSSES, or "taid"
+    alpha: float = 0.5
+    temperature: float = 2.0
+    final_temperature: float = 1.0
+    hidden_loss_weight: float = 0.0
+    hidden_loss_kind: str = "mse"
+    learning_rate: float = 2e-5
+    max_grad_norm: float = 1.0
+    total_steps: int = 1000
+    chunk: int = 2048
+    cache_dir: Optional[str] = None
+
+
+class DistillTrainer:
+    def __init__(self, student, teacher, cfg: DistillConfig, optimizer=None, taid: Optional[TaidConfig] = None):
+        from ..trainer.optimizer import FlatAdamW, attach_shadows
+        self.student, self.teacher, self.cfg = student, teacher, cfg
+        self.device = student.embed_tokens.device
+        shadow = torch.bfloat16 if self.device.type == "cuda" else None
+        self.opt = optimizer or FlatAdamW(student.named_parameters(), lr=cfg.learning_rate, weight_decay=0.0,
+                                          max_grad_norm=cfg.max_grad_norm, shadow_dtype=shadow)
+        if shadow is not None:
+            attach_shadows(student, self.opt)
+        self.taid = TaidDistiller(taid or TaidConfig(temperature=cfg.temperature)) if cfg.loss_type == "taid" else None
+        self.cache = LogitCache.load(cfg.cache_dir) if (cfg.method == "offline" and cfg.cache_dir) else None
+        self.step_count = 0
+
+    def temperature(self) -> float:
+        c = self.cfg
+        if c.method != "progressive":
+            return c.temperature
+        p = min(self.step_count / max(c.total_steps, 1), 1.0)
+        return c.temperature + (c.final_temperature - c.temperature) * p
+
+    def _hidden(self, model, ids, grad):
+        T = ids.numel()
+        pos = torch.arange(T, dtype=torch.int32, device=ids.device)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=ids.device)
+        with (torch.enable_grad() if grad else torch.no_grad()):
+            return model.forward_hidden(ids.reshape(-1), pos, cu, torch.zeros(T, dtype=torch.int32, device=ids.device))
+
+    def loss(self, input_ids: torch.Tensor, labels: torch.Tensor, seq_id: Optional[int] = None):
+        """One sequence [T] (callers pack or loop). Labels -100 are ignored; position t predicts labels[t+1]."""
+        c = self.cfg
+        T = self.temperature()
+        hs = self._hidden(self.student, input_ids, True)[:-1]
+        tgt = labels.reshape(-1)[1:]
+        mask = tgt != -100
+        ws = self.student.head_weight()
+        stats = {}
+        if self.cache is not None and seq_id is not None and self.cache.has_sequence(seq_id):
+            t_logits = self.cache.load_sequence(seq_id).to(self.device)[:-1]
+            s_logits = hs.float() @ ws.float().t()
+            soft = L.LOSSES[c.loss_type](s_logits, t_logits, T, mask)
+        else:
+            ht = self._hidden(self.teacher, input_ids, False)[:-1]
+            wt = self.teacher.head_weight()
+            if self.taid is not None:
+                s_logits = (hs.float() @ ws.float().t()).unsqueeze(0)
+                t_logits = (ht.float() @ wt.float().t()).unsqueeze(0)
+                soft, a = self.taid.loss(t_logits, s_logits, self.step_count, c.total_steps, mask=mask.unsqueeze(0))
+                stats["taid_alpha"] = a
+            elif c.loss_type in ("kl", "forward_kl", "reverse_kl", "js", "jsd", "soft_ce", "tvd"):
+                soft = L.fused_kd_loss(hs, ws, ht, wt, mask, T, c.loss_type, 0.5, c.chunk)
+            else:
+                soft = L.LOSSES[c.loss_type](hs.float() @ ws.float().t(), ht.float() @ wt.float().t(), T, mask)
+            if c.hidden_loss_weight > 0 and hs.shape[-1] == ht.shape[-1]:
+                soft = soft + c.hidden_loss_weight * L.hidden_state_loss(hs, ht, c.hidden_loss_kind, mask=mask)
+        from ..ops import functional as ops
+        hard = ops.causal_lm_loss(hs, ws, tgt) if mask.any() else hs.sum() * 0
+        total = c.alpha * soft + (1 - c.alpha) * hard
+        stats.update(soft=float(soft.detach()), hard=float(hard.detach()), temperature=T)
+        return total, stats
+
+    def step(self, input_ids, labels, seq_id: Optional[int] = None) -> dict:
+        self.opt.zero_grad()
+        loss, stats = self.loss(input_ids.to(self.device), labels.to(self.device), seq_id)
+        loss.backward()
+        gn = self.opt.step(1.0)
+        self.step_count += 1
+        stats.update(loss=float(loss.detach()), grad_norm=float(gn))
+        return stats
+
+    @torch.no_grad()
+    def build_cache(self, sequences, cache_dir: str, compression: str = "topk", top_k: int = 64) -> LogitCache:
+        cache = LogitCache(cache_dir, compression, top_k)
+        for i, ids in enumerate(sequences):
+            ids = torch.as_tensor(ids, dtype=torch.int64, device=self.device)
+            h = self._hidden(self.teacher, ids, False)
+            cache.cache_sequence(i, h.float() @ self.teacher.head_weight().float().t())
+        cache.save_metadata()
+        return cache
