@@ -1,9 +1,10 @@
 // On-device token sampling and speculative verification.
 //
-//   sample_kernel        one CTA per row of logits: penalties (from a per-row token-count table), temperature,
-//                        top-k, top-p (nucleus, applied to the top-k survivors), min-p, then an exact categorical
-//                        draw by the Gumbel-max trick; temperature 0 means greedy. Also returns the log-probability
-//                        of the drawn token under the unfiltered distribution.
+//   sample_kernel        one CTA per row of logits: penalties (from a per-row token-count table), then top-k, top-p
+//                        (nucleus, applied to the top-k survivors) and min-p on the temperature-1 distribution, then an
+//                        exact categorical draw from softmax(logit / T) over the survivors by the Gumbel-max trick;
+//                        temperature 0 means greedy. Also returns the log-probability of the drawn token under the
+//                        filtered, tempered distribution it was drawn from.
 //   spec_verify_kernel   one CTA per sequence: walks the K drafted tokens, accepts token i with probability
 //                        min(1, p_target/p_draft) (greedy mode: iff it equals the target argmax), on the first
 //                        rejection draws from normalize(max(0, p_target - p_draft)), and draws the bonus token from
@@ -80,7 +81,7 @@ struct RowView {
         x -= freq * static_cast<float>(c) + pres;
       }
     }
-    return x * inv_t;
+    return x;
   }
 };
 
@@ -233,21 +234,25 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const SampleParams
   }
   const float mp = p.min_p ? p.min_p[r] : 0.f;
   if (mp > 0.f) floor_key = max(floor_key, order_key(m + __logf(mp)));
-  // Gumbel-max over the survivors
+  // Gumbel-max over the survivors at temperature T, and their tempered partition function for the log-probability
   const unsigned long long seed = p.seeds ? p.seeds[r] : 0ull;
-  float bv = -INFINITY;
+  const float inv_t = row.inv_t;
+  float bv = -INFINITY, zt = 0.f;
   int bi = 0x7fffffff;
   for (int i = threadIdx.x; i < p.vocab; i += blockDim.x) {
     const float x = row.at(i);
     if (order_key(x) >= floor_key) {
-      const float g = x + gumbel(uniform01(seed, p.step, static_cast<uint64_t>(i)));
+      const float xt = (x - m) * inv_t;
+      zt += __expf(xt);
+      const float g = xt + gumbel(uniform01(seed, p.step, static_cast<uint64_t>(i)));
       if (g > bv) { bv = g; bi = i; }
     }
   }
   block_argmax(bv, bi, red, redi);
+  zt = block_sum(zt, red);
   if (threadIdx.x == 0) {
     p.out_token[r] = bi;
-    if (p.out_logprob) p.out_logprob[r] = row.at(bi) - m - __logf(z);
+    if (p.out_logprob) p.out_logprob[r] = (row.at(bi) - m) * inv_t - __logf(zt);
   }
 }
 

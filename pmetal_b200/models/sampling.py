@@ -83,10 +83,40 @@ class Sampler:
         if self.params.seed is not None:
             self.gen = torch.Generator(device=device or "cpu").manual_seed(self.params.seed)
 
+    def _native_sample(self, logits, token_counts, return_logprobs):
+        """Fused sampling kernel (csrc/sampling.cu): one launch for penalties, filters and the draw."""
+        from ..ops import native
+        p = self.params
+        B = logits.shape[0]
+        key = (B, logits.device)
+        if getattr(self, "_nat_key", None) != key:
+            dev = logits.device
+            f = lambda v: torch.full((B,), float(v), dtype=torch.float32, device=dev)      # noqa: E731
+            self._nat = dict(temp=f(0.0 if p.is_greedy else p.temperature),
+                             top_k=torch.full((B,), int(p.top_k), dtype=torch.int32, device=dev), top_p=f(p.top_p),
+                             min_p=f(p.min_p), rep=f(p.repetition_penalty), freq=f(p.frequency_penalty),
+                             pres=f(p.presence_penalty))
+            base = p.seed if p.seed is not None else int(torch.empty((), dtype=torch.int64).random_().item())
+            self._nat["seeds"] = (torch.arange(B, dtype=torch.int64, device=dev) * 0x9E3779B1 + base)
+            self._nat_key, self._nat_step = key, 0
+        n = self._nat
+        self._nat_step += 1
+        if logits.stride(-1) != 1:
+            logits = logits.contiguous()
+        ids, lp = native.sample(logits, n["temp"], n["top_k"], n["top_p"], n["min_p"], token_counts, n["rep"], n["freq"],
+                                n["pres"], n["seeds"], self._nat_step, return_logprobs)
+        ids = ids.long()
+        return (ids, lp) if return_logprobs else ids
+
     def sample(self, logits: torch.Tensor, token_counts: Optional[torch.Tensor] = None,
                return_logprobs: bool = False):
         """logits [B, V] -> ids [B] (and the log-probability of each chosen id under the filtered distribution)."""
         p = self.params
+        if logits.is_cuda and logits.dim() == 2 and logits.dtype in (torch.float32, torch.bfloat16) and \
+                (token_counts is None or token_counts.dtype == torch.int32):
+            from ..ops import functional as _ops
+            if _ops.native_enabled(logits):
+                return self._native_sample(logits, token_counts, return_logprobs)
         logits = apply_penalties(logits.float(), token_counts, p)
         if p.is_greedy:
             ids = logits.argmax(dim=-1)

@@ -36,6 +36,11 @@ class force_reference:
         _FORCE_REF = self._old
 
 
+def native_enabled(t: torch.Tensor) -> bool:
+    """CUDA tensor, native library loaded and the reference path not forced (any dtype)."""
+    return (not _FORCE_REF) and t.is_cuda and _native().available()
+
+
 def use_native(t: torch.Tensor) -> bool:
     if _FORCE_REF or not t.is_cuda:
         return False

@@ -43,20 +43,11 @@ def test_sampler_greedy_topk_topp_minp_distribution():
     tok, _ = nat.sample(rows, torch.full((n,), temp, device=dev), top_k=torch.full((n,), k, dtype=torch.int32, device=dev),
                         top_p=torch.full((n,), p_, device=dev), min_p=torch.full((n,), mp, device=dev),
                         seeds=torch.arange(n, dtype=torch.int64, device=dev) + 17, step=3)
-    probs = torch.softmax(row[0] / temp, -1)
-    sp, si = probs.sort(descending=True)
-    keep = torch.zeros(64, dtype=torch.bool, device=dev)
-    keep[si[:k]] = True
-    pk = torch.where(keep, probs, torch.zeros_like(probs))
-    pk = pk / pk.sum()
-    spk, sik = pk.sort(descending=True)
-    cum = spk.cumsum(0)
-    n_keep = int((cum < p_).sum().item()) + 1
-    keep2 = torch.zeros(64, dtype=torch.bool, device=dev)
-    keep2[sik[:n_keep]] = True
-    keep2 &= probs >= mp * probs.max()
-    target = torch.where(keep2, probs, torch.zeros_like(probs))
-    target = target / target.sum()
+    from pmetal_b200.models.sampling import SamplingParams, filtered_logprobs
+    sp = SamplingParams(temperature=temp, top_k=k, top_p=p_, min_p=mp, repetition_penalty=1.0)
+    logp = filtered_logprobs(row, sp)[0]              # filters act on the temperature-1 distribution
+    keep2 = torch.isfinite(logp)
+    target = torch.softmax(logp / temp, -1)
     emp = torch.bincount(tok.long(), minlength=64).float() / n
     assert emp[~keep2].sum() == 0
     assert (emp - target).abs().max() < 0.015

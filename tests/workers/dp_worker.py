@@ -60,9 +60,13 @@ def main():
             assert torch.allclose(loop.opt.flat_shadow.float(), loop.opt.flat_p, rtol=1e-2, atol=1e-3)
     pf, pn = results["fused"][0], results["nccl"][0]
     diff = (pf - pn).abs().max().item()
+    mean_diff = (pf - pn).abs().mean().item()
     print(f"rank {rank}: fused vs nccl max param diff {diff:.3e} (loss fused {results['fused'][1]:.4f} "
           f"nccl {results['nccl'][1]:.4f})", flush=True)
-    assert diff < 2e-4, diff
+    # LoRA weight gradients are accumulated with fp32 atomics (split-K), so two runs differ in the last bits and Adam's
+    # normalised update can turn that into a full learning-rate step on elements whose gradient is ~0: bound the
+    # mean tightly and the maximum by a few learning-rate steps
+    assert mean_diff < 2e-5 and diff < 4e-3, (mean_diff, diff)
     dist.barrier()
     torch.cuda.synchronize()
     if rank == 0:
