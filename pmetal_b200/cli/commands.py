@@ -144,3 +144,491 @@ def cmd_dataset(a) -> int:
         return 0
     print("dataset download needs network access, which this machine does not have", file=sys.stderr)
     return 2
+
+
+# ------------------------------------------------------------------------------------------- shared helpers
+def _load_for_inference(a):
+    """(model, tokenizer, template, eos ids, model_dir) for commands that generate text."""
+    import torch
+
+    from ..data.chat_templates import ChatTemplate
+    from ..data.tokenizer import ByteTokenizer, Tokenizer
+    from ..models.loader import load_pretrained
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    dtype = torch.bfloat16 if dev.startswith("cuda") else torch.float32
+    model, args, mdir = load_pretrained(a.model, dtype=dtype, device=dev, seed=getattr(a, "seed", 0) or 0)
+    lora = getattr(a, "lora", None)
+    if lora:
+        from ..lora import apply_lora
+        from ..lora.adapter import load_adapter, load_adapter_config
+        apply_lora(model, load_adapter_config(lora))
+        model.to(dev)
+        load_adapter(model, lora)
+    if getattr(a, "fp8", False) and dev.startswith("cuda"):
+        from ..models.fp8 import quantize_model_fp8
+        quantize_model_fp8(model)
+    model.eval()
+    for p in model.parameters():
+        p.requires_grad_(False)
+    if mdir and os.path.exists(os.path.join(mdir, "tokenizer.json")):
+        tok = Tokenizer.from_model_dir(mdir)
+        tpl = ChatTemplate.from_model_dir(mdir)
+    else:
+        tok, tpl = ByteTokenizer(), ChatTemplate("chatml")
+    eos = [i for i in (tok.eos_id,) if i is not None]
+    return model, tok, tpl, eos, mdir
+
+
+def _sampling_from_args(a):
+    from ..models.sampling import SamplingParams
+    if getattr(a, "greedy", False) or a.temperature <= 0:
+        return SamplingParams.greedy(a.max_tokens)
+    return SamplingParams(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p, min_p=a.min_p,
+                          repetition_penalty=a.repetition_penalty, frequency_penalty=a.frequency_penalty,
+                          presence_penalty=a.presence_penalty, max_tokens=a.max_tokens, seed=a.seed)
+
+
+def _add_sampling_flags(p):
+    p.add_argument("--temperature", type=float, default=0.7)
+    p.add_argument("--top-k", type=int, default=40)
+    p.add_argument("--top-p", type=float, default=0.95)
+    p.add_argument("--min-p", type=float, default=0.05)
+    p.add_argument("--repetition-penalty", type=float, default=1.1)
+    p.add_argument("--frequency-penalty", type=float, default=0.0)
+    p.add_argument("--presence-penalty", type=float, default=0.0)
+    p.add_argument("--max-tokens", type=int, default=256)
+    p.add_argument("--seed", type=int, default=None)
+    p.add_argument("--greedy", action="store_true")
+
+
+# ------------------------------------------------------------------------------------------- infer
+def _infer_args(sp):
+    p = sp.add_parser("infer", help="generate text (paged KV cache, optional LoRA, speculative draft)")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("-l", "--lora")
+    p.add_argument("-p", "--prompt", required=True)
+    p.add_argument("--system")
+    p.add_argument("--chat", action="store_true", help="apply the chat template")
+    p.add_argument("--no-thinking", action="store_true")
+    p.add_argument("--stream", action="store_true")
+    p.add_argument("--draft-model", help="two-model speculative decoding with this draft")
+    p.add_argument("--speculative-k", type=int, default=5)
+    p.add_argument("--fp8", action="store_true", help="block-scaled FP8 weights")
+    p.add_argument("--kv-blocks", type=int, default=4096)
+    p.add_argument("--device")
+    p.add_argument("--json", action="store_true")
+    _add_sampling_flags(p)
+    return p
+
+
+@_command(_infer_args)
+def cmd_infer(a) -> int:
+    from ..data.chat_templates import Message
+    from ..data.tokenizer import StreamDecoder
+    from ..models.generation import Generator
+    model, tok, tpl, eos, _ = _load_for_inference(a)
+    if a.chat or a.system:
+        msgs = ([Message("system", a.system)] if a.system else []) + [Message("user", a.prompt)]
+        ids = tok.encode_with_special_tokens(tpl.apply_inference(msgs, a.no_thinking))
+    else:
+        ids = tok.encode(a.prompt)
+    sp_ = _sampling_from_args(a)
+    if a.draft_model:
+        from ..models.loader import load_pretrained
+        from ..models.speculative import SpeculativeConfig, SpeculativeDecoder
+        draft, _, _ = load_pretrained(a.draft_model, dtype=next(model.parameters()).dtype,
+                                      device=str(model.embed_tokens.device))
+        draft.eval()
+        sg = SpeculativeDecoder(model, draft, SpeculativeConfig(num_draft_tokens=a.speculative_k,
+                                                                  temperature=0.0 if sp_.is_greedy else sp_.temperature))
+        out = sg.generate([ids], a.max_tokens, eos)
+        text = tok.decode([t for t in out[0] if t not in eos])
+        info = {"text": text, "tokens": len(out[0]), "acceptance_rate": sg.stats.acceptance_rate,
+                "tokens_per_round": sg.stats.tokens_per_round}
+        print(json.dumps(info) if a.json else text)
+        return 0
+    gen = Generator(model, num_blocks=a.kv_blocks)
+    if a.stream and not a.json:
+        dec = StreamDecoder(tok)
+        for t in gen.stream(ids, sp_, eos):
+            if t not in eos:
+                sys.stdout.write(dec.push(t))
+                sys.stdout.flush()
+        sys.stdout.write("\n")
+        return 0
+    res = gen.generate([ids], sp_, eos)
+    text = tok.decode([t for t in res.tokens[0] if t not in eos])
+    if a.json:
+        print(json.dumps({"text": text, "prompt_tokens": res.prompt_tokens, "generated_tokens": res.generated_tokens,
+                          "prefill_tok_per_s": round(res.prefill_tok_per_s, 1), "decode_tok_per_s": round(res.decode_tok_per_s, 1),
+                          "finish_reason": res.finish_reasons[0]}))
+    else:
+        print(text)
+    return 0
+
+
+# ------------------------------------------------------------------------------------------- serve
+def _serve_args(sp):
+    p = sp.add_parser("serve", help="OpenAI / Anthropic compatible server with continuous batching")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("-l", "--lora")
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=8080)
+    p.add_argument("--max-slots", type=int, default=64)
+    p.add_argument("--kv-blocks", type=int, default=8192)
+    p.add_argument("--fp8", action="store_true")
+    p.add_argument("--device")
+    return p
+
+
+@_command(_serve_args)
+def cmd_serve(a) -> int:
+    from ..serve.server import serve
+    model, tok, tpl, eos, mdir = _load_for_inference(a)
+    serve(model, tok, tpl, a.host, a.port, eos, os.path.basename(os.path.normpath(mdir or a.model)), a.max_slots, a.kv_blocks)
+    return 0
+
+
+# ------------------------------------------------------------------------------------------- fuse / merge / quantize
+def _fuse_args(sp):
+    p = sp.add_parser("fuse", help="merge a LoRA adapter into its base model")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("-l", "--lora", required=True)
+    p.add_argument("-o", "--output", required=True)
+    p.add_argument("--dtype", default="bfloat16")
+    return p
+
+
+@_command(_fuse_args)
+def cmd_fuse(a) -> int:
+    from ..merge.merge import merge_lora_into_base
+    from ..models.loader import resolve_model_path
+    print(json.dumps(merge_lora_into_base(resolve_model_path(a.model), a.lora, a.output, a.dtype)))
+    return 0
+
+
+def _merge_args(sp):
+    p = sp.add_parser("merge", help="merge models (linear, slerp, ties, dare, della, ...) from a YAML recipe or flags")
+    p.add_argument("-c", "--config")
+    p.add_argument("--models", nargs="*")
+    p.add_argument("--base")
+    p.add_argument("--method", default="linear")
+    p.add_argument("--weights", nargs="*", type=float)
+    p.add_argument("--density", type=float, default=1.0)
+    p.add_argument("-o", "--output", required=True)
+    p.add_argument("--dtype", default="bfloat16")
+    p.add_argument("--device")
+    return p
+
+
+@_command(_merge_args)
+def cmd_merge(a) -> int:
+    from ..merge.merge import MergeConfig, run_merge
+    if a.config:
+        cfg = MergeConfig.from_yaml(a.config)
+    else:
+        if not a.models:
+            print("error: --config or --models is required", file=sys.stderr)
+            return 2
+        ws = a.weights or [1.0 / len(a.models)] * len(a.models)
+        cfg = MergeConfig.from_dict({"merge_method": a.method, "base_model": a.base, "dtype": a.dtype,
+                                     "models": [{"model": m, "parameters": {"weight": w, "density": a.density}}
+                                                for m, w in zip(a.models, ws)]})
+    cfg.output = a.output
+    print(json.dumps(run_merge(cfg, a.device)))
+    return 0
+
+
+def _quantize_args(sp):
+    from ..gguf.types import QUANT_METHODS
+    p = sp.add_parser("quantize", help="export a model as GGUF (K-quants, legacy quants, dynamic with imatrix)")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("-o", "--output", required=True)
+    p.add_argument("--method", default="q4_k_m", choices=sorted(QUANT_METHODS))
+    p.add_argument("--imatrix")
+    p.add_argument("--kl-calibrate", action="store_true")
+    p.add_argument("--target-bpw", type=float)
+    p.add_argument("--threads", type=int, default=0)
+    p.add_argument("--format", default="gguf", choices=["gguf", "fp8"])
+    return p
+
+
+@_command(_quantize_args)
+def cmd_quantize(a) -> int:
+    from ..models.loader import resolve_model_path
+    mdir = resolve_model_path(a.model)
+    if a.format == "fp8":
+        from ..models.fp8 import export_fp8_checkpoint
+        print(json.dumps(export_fp8_checkpoint(mdir, a.output)))
+        return 0
+    from ..gguf.convert import quantize_model
+    from ..gguf.recipe import DynamicConfig
+    dyn = DynamicConfig(kl_calibrate=a.kl_calibrate, target_bpw=a.target_bpw) if a.method == "dynamic" else None
+    print(json.dumps(quantize_model(mdir, a.output, a.method, a.imatrix, dyn, a.threads)))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------- distill / grpo / rlkd
+def _read_prompts(path: str, tok, limit=None, key_order=("prompt", "question", "text", "instruction")):
+    out = []
+    with open(path, "r", encoding="utf-8") as fh:
+        for line in fh:
+            line = line.strip()
+            if not line:
+                continue
+            try:
+                d = json.loads(line)
+                text = next((d[k] for k in key_order if isinstance(d.get(k), str)), None) if isinstance(d, dict) else str(d)
+            except json.JSONDecodeError:
+                text = line
+            if text:
+                out.append(tok.encode(text))
+            if limit and len(out) >= limit:
+                break
+    return out
+
+
+def _distill_args(sp):
+    p = sp.add_parser("distill", help="knowledge distillation (online / offline / progressive, TAID)")
+    p.add_argument("--teacher", required=True)
+    p.add_argument("--student", required=True)
+    p.add_argument("-d", "--dataset", required=True)
+    p.add_argument("-o", "--output", default="./distill-output")
+    p.add_argument("--method", default="online", choices=["online", "offline", "progressive"])
+    p.add_argument("--loss-type", default="kl")
+    p.add_argument("--alpha", type=float, default=0.5)
+    p.add_argument("--temperature", type=float, default=2.0)
+    p.add_argument("--learning-rate", type=float, default=2e-5)
+    p.add_argument("--max-steps", type=int, default=100)
+    p.add_argument("--max-seq-len", type=int, default=1024)
+    p.add_argument("--cache-dir")
+    p.add_argument("--lora-r", type=int, default=0, help="train a LoRA adapter on the student instead of all weights")
+    p.add_argument("--device")
+    return p
+
+
+@_command(_distill_args)
+def cmd_distill(a) -> int:
+    import torch
+
+    from ..distill.trainer import DistillConfig, DistillTrainer
+    from ..models.loader import load_pretrained, save_pretrained
+    a.model = a.student
+    student, tok, _, _, sdir = _load_for_inference(a)
+    dev = str(student.embed_tokens.device)
+    teacher, _, _ = load_pretrained(a.teacher, dtype=next(student.parameters()).dtype, device=dev)
+    teacher.eval()
+    for p in teacher.parameters():
+        p.requires_grad_(False)
+    if a.lora_r > 0:
+        from ..core.config import LoraConfig
+        from ..lora import apply_lora
+        apply_lora(student, LoraConfig(r=a.lora_r, alpha=2.0 * a.lora_r))
+        student.to(dev)
+    else:
+        for p in student.parameters():
+            p.requires_grad_(True)
+    student.train()
+    seqs = [s[: a.max_seq_len] for s in _read_prompts(a.dataset, tok) if len(s) > 1]
+    cfg = DistillConfig(method=a.method, loss_type=a.loss_type, alpha=a.alpha, temperature=a.temperature,
+                        learning_rate=a.learning_rate, total_steps=a.max_steps, cache_dir=a.cache_dir)
+    tr = DistillTrainer(student, teacher, cfg)
+    if a.method == "offline" and a.cache_dir and not os.path.exists(os.path.join(a.cache_dir, "metadata.json")):
+        tr.cache = tr.build_cache(seqs, a.cache_dir)
+    last = {}
+    for step in range(a.max_steps):
+        i = step % len(seqs)
+        ids = torch.tensor(seqs[i], dtype=torch.int64)
+        last = tr.step(ids, ids.clone(), seq_id=i)
+        if step % 10 == 0:
+            print(json.dumps({"step": step, **{k: round(v, 5) for k, v in last.items()}}), file=sys.stderr)
+    os.makedirs(a.output, exist_ok=True)
+    if a.lora_r > 0:
+        from ..core.config import LoraConfig
+        from ..lora.adapter import save_adapter
+        save_adapter(student, a.output, LoraConfig(r=a.lora_r, alpha=2.0 * a.lora_r), a.student)
+    else:
+        save_pretrained(student, a.output, copy_from=sdir)
+    print(json.dumps({"output": a.output, "steps": a.max_steps, **last}))
+    return 0
+
+
+def _grpo_args(sp):
+    p = sp.add_parser("grpo", help="GRPO / DAPO reinforcement learning with batched paged rollouts")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("-d", "--dataset", required=True)
+    p.add_argument("-o", "--output", default="./grpo-output")
+    p.add_argument("--dapo", action="store_true")
+    p.add_argument("--num-generations", type=int, default=8)
+    p.add_argument("--beta", type=float, default=0.001)
+    p.add_argument("--max-completion-length", type=int, default=512)
+    p.add_argument("--max-prompt-length", type=int, default=512)
+    p.add_argument("--learning-rate", type=float, default=1e-6)
+    p.add_argument("--max-steps", type=int, default=100)
+    p.add_argument("--prompts-per-step", type=int, default=1)
+    p.add_argument("--lora-r", type=int, default=16)
+    p.add_argument("--reward", default="format", choices=["format", "length", "accuracy"])
+    p.add_argument("--teacher", help="with --rlkd-alpha: add a KD term against this teacher (RLKD)")
+    p.add_argument("--rlkd-alpha", type=float, default=0.0)
+    p.add_argument("--device")
+    return p
+
+
+@_command(_grpo_args)
+def cmd_grpo(a) -> int:
+    from ..core.config import LoraConfig
+    from ..lora import apply_lora
+    from ..lora.adapter import save_adapter
+    from ..trainer.grpo import GrpoConfig, GrpoTrainer
+    from ..trainer.rewards import make_reward
+    model, tok, _, eos, _ = _load_for_inference(a)
+    dev = str(model.embed_tokens.device)
+    lcfg = LoraConfig(r=a.lora_r, alpha=2.0 * a.lora_r)
+    apply_lora(model, lcfg)
+    model.to(dev).train()
+    kw = dict(num_generations=a.num_generations, beta=a.beta, max_completion_length=a.max_completion_length,
+              max_prompt_length=a.max_prompt_length, learning_rate=a.learning_rate)
+    cfg = GrpoConfig.dapo(**kw) if a.dapo else GrpoConfig(**kw)
+    reward = make_reward(a.reward, tok)
+    if a.teacher and a.rlkd_alpha > 0:
+        from ..models.loader import load_pretrained
+        from ..trainer.gspo import RlkdTrainer
+        teacher, _, _ = load_pretrained(a.teacher, dtype=next(model.parameters()).dtype, device=dev)
+        tr = RlkdTrainer(model, cfg, reward, teacher.eval(), a.rlkd_alpha, eos_ids=eos)
+    else:
+        tr = GrpoTrainer(model, cfg, reward, eos_ids=eos)
+    prompts = _read_prompts(a.dataset, tok)
+    if not prompts:
+        print("error: no prompts in dataset", file=sys.stderr)
+        return 2
+    for step in range(a.max_steps):
+        batch = [prompts[(step * a.prompts_per_step + j) % len(prompts)] for j in range(a.prompts_per_step)]
+        st = tr.step(batch)
+        d = st if isinstance(st, dict) else st.__dict__
+        print(json.dumps({"step": step, **{k: (round(v, 5) if isinstance(v, float) else v) for k, v in d.items()}}),
+              file=sys.stderr)
+    save_adapter(model, a.output, lcfg, a.model)
+    print(json.dumps({"output": a.output, "steps": a.max_steps}))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------- eval / bench / cluster
+def _eval_args(sp):
+    p = sp.add_parser("eval", help="loss / perplexity / token accuracy on a dataset")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("-l", "--lora")
+    p.add_argument("-d", "--dataset", required=True)
+    p.add_argument("--max-samples", type=int, default=200)
+    p.add_argument("--max-seq-len", type=int, default=2048)
+    p.add_argument("--device")
+    return p
+
+
+@_command(_eval_args)
+def cmd_eval(a) -> int:
+    import math
+
+    import torch
+    model, tok, _, _, _ = _load_for_inference(a)
+    seqs = [s[: a.max_seq_len] for s in _read_prompts(a.dataset, tok, a.max_samples) if len(s) > 1]
+    tot, n, correct = 0.0, 0, 0
+    dev = model.embed_tokens.device
+    with torch.no_grad():
+        for s in seqs:
+            ids = torch.tensor(s, dtype=torch.int64, device=dev)
+            T = ids.numel()
+            h = model.forward_hidden(ids, torch.arange(T, dtype=torch.int32, device=dev),
+                                     torch.tensor([0, T], dtype=torch.int32, device=dev),
+                                     torch.zeros(T, dtype=torch.int32, device=dev))
+            logits = h[:-1].float() @ model.head_weight().float().t()
+            tot += float(torch.nn.functional.cross_entropy(logits, ids[1:], reduction="sum"))
+            correct += int((logits.argmax(-1) == ids[1:]).sum())
+            n += T - 1
+    loss = tot / max(n, 1)
+    print(json.dumps({"samples": len(seqs), "tokens": n, "loss": round(loss, 5), "perplexity": round(math.exp(min(loss, 50)), 4),
+                      "token_accuracy": round(correct / max(n, 1), 5)}))
+    return 0
+
+
+def _bench_args(sp):
+    p = sp.add_parser("bench", help="kernel corpus / training workload / generation benchmarks")
+    p.add_argument("what", nargs="?", default="corpus", choices=["corpus", "workload", "gen"])
+    p.add_argument("--case", nargs="*")
+    p.add_argument("--iters", type=int, default=10)
+    p.add_argument("-m", "--model", default="random:qwen3-0.6b")
+    p.add_argument("--json")
+    p.add_argument("--device")
+    return p
+
+
+@_command(_bench_args)
+def cmd_bench(a) -> int:
+    if a.what == "corpus":
+        from ..bench import kernels
+        argv = ["--iters", str(a.iters)] + (["--case"] + a.case if a.case else []) + (["--json", a.json] if a.json else [])
+        return kernels.main(argv) or 0
+    from ..bench import workload
+    return workload.main(a) or 0
+
+
+def _cluster_args(sp):
+    p = sp.add_parser("cluster", help="multi-GPU node: status, collective bench, pipeline bench, train, serve")
+    p.add_argument("action", choices=["status", "up", "bench", "pipeline-bench", "train", "serve"])
+    p.add_argument("--gpus", type=int, default=0)
+    p.add_argument("--mb", type=int, default=64)
+    p.add_argument("--iters", type=int, default=20)
+    p.add_argument("rest", nargs=argparse_remainder())
+    return p
+
+
+def argparse_remainder():
+    import argparse
+    return argparse.REMAINDER
+
+
+@_command(_cluster_args)
+def cmd_cluster(a) -> int:
+    from ..parallel import cluster_cli
+    return cluster_cli.run(a) or 0
+
+
+def _dl_args(sp):
+    p = sp.add_parser("download", help="resolve a model from the local Hugging Face cache (this machine is offline)")
+    p.add_argument("model")
+    return p
+
+
+@_command(_dl_args)
+def cmd_download(a) -> int:
+    from ..models.loader import resolve_model_path
+    try:
+        print(resolve_model_path(a.model))
+        return 0
+    except FileNotFoundError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
+
+
+def _ollama_args(sp):
+    p = sp.add_parser("ollama", help="write an Ollama Modelfile for a GGUF export")
+    p.add_argument("action", choices=["modelfile", "templates"])
+    p.add_argument("--gguf")
+    p.add_argument("--template", default="chatml")
+    p.add_argument("--system")
+    p.add_argument("-o", "--output", default="Modelfile")
+    _add_sampling_flags(p)
+    return p
+
+
+@_command(_ollama_args)
+def cmd_ollama(a) -> int:
+    from ..utils.ollama import TEMPLATES, write_modelfile
+    if a.action == "templates":
+        print("\n".join(sorted(TEMPLATES)))
+        return 0
+    if not a.gguf:
+        print("error: --gguf is required", file=sys.stderr)
+        return 2
+    print(write_modelfile(a.gguf, a.output, a.template, a.system, temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
+                          repeat_penalty=a.repetition_penalty))
+    return 0

@@ -101,6 +101,10 @@ def dequantize(q: QuantizedTensor, dtype=torch.float32) -> torch.Tensor:
     for s in q.shape:
         n *= s
     absmax = q.block_absmax().float()
+    if q.scheme == "fp8":         # E4M3 codes with one scale per block of 128 (models/fp8.py)
+        vals = q.data.view(torch.float8_e4m3fn).float().reshape(-1)
+        idx = torch.arange(n, device=q.data.device) // q.block_size
+        return (vals[:n] * absmax[idx]).view(q.shape).to(dtype)
     if q.scheme == "int8":
         vals = q.data.view(torch.int8).float() / 127.0
     else:

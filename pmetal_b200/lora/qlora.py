@@ -18,6 +18,10 @@ def dequantize_weight(q: QuantizedTensor, dtype=torch.bfloat16) -> torch.Tensor:
         from ..ops import native
         if native.available():
             return native.dequant_4bit(q)
+    if q.data.is_cuda and q.scheme == "fp8" and dtype == torch.bfloat16:
+        from ..ops import native
+        if native.available():
+            return native.fp8_dequant(q.data, q.absmax).view(q.shape)
     return dequantize(q, dtype)
 
 
