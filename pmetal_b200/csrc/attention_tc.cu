@@ -117,8 +117,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   // key range of this query tile: from the document start of its first row up to its last row
   int kv_lo = (p.seq_start[q0] / kFaTile) * kFaTile;
-  const int kv_hi = min(q0 + kFaTile, p.T);
-  const int n_tiles = (kv_hi - kv_lo + kFaTile - 1) / kFaTile;
+  const int kv_hi = max(min(q0 + kFaTile + p.shift, p.Tk), 0);
+  const int n_tiles = max((kv_hi - kv_lo + kFaTile - 1) / kFaTile, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -205,12 +205,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const int b = j & 1;
       const uint32_t ph = (j >> 1) & 1;
       const int j0 = kv_lo + j * kFaTile;
-      const bool need_mask = (j0 + kFaTile - 1 > q0) || (j0 < st_max);
+      const bool need_mask = (j0 + kFaTile - 1 > q0 + p.shift) || (j0 < st_max) || (j0 + kFaTile > p.Tk);
       if (!mbar_wait(&bar[kBarSFull + b], ph, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after();
       // valid key columns of this row inside the tile: [lo, lo + span]; span < 0 means none
       const int lo = max(st - j0, 0);
-      const int span = min(i - j0, kFaTile - 1) - lo;
+      const int span = min(min(i + p.shift, p.Tk - 1) - j0, kFaTile - 1) - lo;
       // pass 1: row maximum
       const float mx = need_mask ? row_max<true>(tmem_base + b * 128 + lane_off, lo, span)
                                  : row_max<false>(tmem_base + b * 128 + lane_off, 0, 0);
@@ -298,22 +298,25 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 using namespace pm;
 
-// q:[T, hq*128 (+...)] with token stride q_stride, k/v likewise (v may be a strided view). out:[T,hq,128], lse:[hq,T]
-extern "C" int pm_attn_fwd_tc(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
-                              long long v_stride, void* out, long long o_stride, float* lse, const int* seq_start, int T,
-                              int hq, int hkv, float scale, int* status, cudaStream_t st) {
-  if (hq % hkv || T <= 0) return -1;
+// q:[T, hq*128 (+...)] with token stride q_stride, k/v:[Tk, ...] likewise (v may be a strided view). out:[T,hq,128],
+// lse:[hq,T]. Key j is visible to query i iff seq_start[i] <= j <= i + shift.
+extern "C" int pm_attn_fwd_tc_rect(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
+                                   long long v_stride, void* out, long long o_stride, float* lse, const int* seq_start,
+                                   int T, int Tk, int shift, int hq, int hkv, float scale, int* status,
+                                   cudaStream_t st) {
+  if (hq % hkv || T <= 0 || Tk <= 0) return -1;
   if ((q_stride | k_stride | v_stride | o_stride) % 8) return -2;
   CUtensorMap mq, mk, mv;
   int rc;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return -3;
   if ((rc = make_map(&mq, q, static_cast<uint64_t>(hq) * 128, T, q_stride, 64, kFaTile))) return rc;
-  if ((rc = make_map(&mk, k, static_cast<uint64_t>(hkv) * 128, T, k_stride, 64, kFaTile))) return rc;
-  if ((rc = make_map(&mv, v, static_cast<uint64_t>(hkv) * 128, T, v_stride, 64, kFaTile))) return rc;
+  if ((rc = make_map(&mk, k, static_cast<uint64_t>(hkv) * 128, Tk, k_stride, 64, kFaTile))) return rc;
+  if ((rc = make_map(&mv, v, static_cast<uint64_t>(hkv) * 128, Tk, v_stride, 64, kFaTile))) return rc;
   FaParams p{};
   p.out = static_cast<__nv_bfloat16*>(out);
   p.o_stride = o_stride; p.lse = lse; p.seq_start = seq_start;
   p.T = T; p.hq = hq; p.hkv = hkv; p.scale = scale; p.status = status;
+  p.Tk = Tk; p.shift = shift;
   const int smem = 6 * kFaTileBytes + 1024 + 256;
   static bool once = false;
   if (!once) {
@@ -324,4 +327,11 @@ extern "C" int pm_attn_fwd_tc(const void* q, long long q_stride, const void* k, 
   dim3 grid((T + kFaTile - 1) / kFaTile, hq);
   attn_fwd_tc_kernel<<<grid, kFaThreads, smem, st>>>(mq, mk, mv, p);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int pm_attn_fwd_tc(const void* q, long long q_stride, const void* k, long long k_stride, const void* v,
+                              long long v_stride, void* out, long long o_stride, float* lse, const int* seq_start, int T,
+                              int hq, int hkv, float scale, int* status, cudaStream_t st) {
+  return pm_attn_fwd_tc_rect(q, q_stride, k, k_stride, v, v_stride, out, o_stride, lse, seq_start, T, T, 0, hq, hkv, scale,
+                             status, st);
 }

@@ -20,6 +20,10 @@ struct FaParams {
   int T, hq, hkv;
   float scale;
   int* status;
+  // forward kernel only: number of key rows and the causal offset; key j is visible to query i iff
+  // seq_start[i] <= j <= i + shift (and j < Tk). Tk = T, shift = 0 is ordinary causal attention; shift >= Tk - 1
+  // makes every key visible (a block of ring attention that lies entirely in the past).
+  int Tk, shift;
 };
 
 // 2^x on the SFU; -inf gives 0

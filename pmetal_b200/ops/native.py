@@ -47,7 +47,7 @@ def _load():
                "pm_qknorm_rope_bwd", "pm_swiglu_fwd", "pm_swiglu_bwd", "pm_ce_fwd_bwd", "pm_sumsq", "pm_adamw_flat",
                "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16", "pm_paged_attn", "pm_kv_append", "pm_attn_fwd_tc", "pm_attn_bwd_tc", "pm_dequant_4bit", "pm_sample", "pm_spec_verify", "pm_count_tokens",
                "pm_moe_route", "pm_moe_gather", "pm_moe_combine", "pm_gguf_dequant_bf16", "pm_fp8_quant", "pm_fp8_dequant",
-               "pm_kd_fwd_bwd", "pm_merge_fused", "pm_dot_norms"):
+               "pm_kd_fwd_bwd", "pm_merge_fused", "pm_dot_norms", "pm_attn_fwd_tc_rect"):
         getattr(_LIB, fn).restype = c_int
 
 
@@ -327,6 +327,22 @@ def attn_fwd(q, k, v, seq_start, scale: float, window: int = 0):
     _chk(lib().pm_attn_fwd(_p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)), _p(out),
                            c_ll(out.stride(0)), _p(lse), _p(seq_start), c_int(T), c_int(hq), c_int(hkv),
                            c_float(scale), c_int(window), _stream()), "pm_attn_fwd")
+    return out, lse
+
+
+def attn_fwd_rect(q, k, v, seq_start, scale: float, shift: int):
+    """Attention of Tq queries over Tk keys where key j is visible to query i iff seq_start[i] <= j <= i + shift
+    (shift >= Tk - 1: every key). q [Tq, hq, 128], k/v [Tk, hkv, 128] (k/v may live in a peer GPU's memory: the
+    kernel's TMA loads read them in place). Returns (out bf16 [Tq, hq, 128], lse fp32 [hq, Tq])."""
+    T, hq, d = q.shape
+    Tk, hkv = k.shape[0], k.shape[1]
+    assert d == 128 and q.stride(1) == d and k.stride(1) == d and v.stride(1) == d
+    out = torch.empty(T, hq, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(hq, T, dtype=torch.float32, device=q.device)
+    _chk(lib().pm_attn_fwd_tc_rect(_p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)), _p(out),
+                                   c_ll(out.stride(0)), _p(lse), _p(seq_start), c_int(T), c_int(Tk), c_int(shift),
+                                   c_int(hq), c_int(hkv), c_float(scale), _p(status_word(q.device)), _stream()),
+         "pm_attn_fwd_tc_rect")
     return out, lse
 
 

@@ -262,3 +262,34 @@ def test_cluster_state_machines():
     m.inc("bytes", 10); m.inc("bytes", 5)
     snap = m.snapshot()
     assert snap["counters"]["bytes"] == 15 and snap["histograms"]["all_reduce_ms"]["p95"] == 95.0
+
+
+def test_ring_attention_pipeline_and_1f1b_over_gloo():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for n in (2, 3):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+               "127.0.0.1", "--master-port", str(29720 + n), os.path.join(root, "tests", "workers", "cp_pp_worker.py")]
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=120)
+        assert r.returncode == 0 and "CP_PP_WORKER_OK" in r.stdout, r.stdout[-3000:]
+
+
+def test_activation_message_wire_format():
+    import struct
+
+    import torch
+    from pmetal_b200.parallel.pipeline import ActivationMessage
+    t = torch.arange(6, dtype=torch.float32).reshape(1, 2, 3).to(torch.bfloat16)
+    raw = ActivationMessage(9, 3, t).serialize()
+    assert raw[:16] == struct.pack("<QII", 9, 3, 3) and raw[16:28] == struct.pack("<3I", 1, 2, 3) and raw[28] == 2
+    assert len(raw) == 8 + 4 + 4 + 12 + 1 + 12
+    back = ActivationMessage.deserialize(raw)
+    assert back.nonce == 9 and back.layer_id == 3 and torch.equal(back.tensor, t)
+    import pytest
+    with pytest.raises(ValueError):
+        ActivationMessage.deserialize(raw[:-1])
+    with pytest.raises(ValueError):
+        ActivationMessage.deserialize(raw[:28] + bytes([9]) + raw[29:])
+    with pytest.raises(ValueError):
+        ActivationMessage.deserialize(b"short")
