@@ -175,7 +175,7 @@ def _load_for_inference(a):
         tpl = ChatTemplate.from_model_dir(mdir)
     else:
         tok, tpl = ByteTokenizer(), ChatTemplate("chatml")
-    eos = [i for i in (tok.eos_id,) if i is not None]
+    eos = [i for i in (tok.eos_token_id,) if i is not None]
     return model, tok, tpl, eos, mdir
 
 
@@ -334,7 +334,7 @@ def cmd_merge(a) -> int:
         cfg = MergeConfig.from_dict({"merge_method": a.method, "base_model": a.base, "dtype": a.dtype,
                                      "models": [{"model": m, "parameters": {"weight": w, "density": a.density}}
                                                 for m, w in zip(a.models, ws)]})
-    cfg.output = a.output
+    cfg.output_path = a.output
     print(json.dumps(run_merge(cfg, a.device)))
     return 0
 

@@ -1,0 +1,85 @@
+"""End-to-end CLI runs on CPU with a tiny random checkpoint written to a temp directory."""
+import json
+import os
+
+import pytest
+import torch
+
+from pmetal_b200.cli.main import main
+
+
+@pytest.fixture(scope="module")
+def model_dir(tmp_path_factory):
+    from pmetal_b200.models.config import ModelArgs
+    from pmetal_b200.models.decoder import DecoderLM
+    from pmetal_b200.models.loader import save_pretrained
+    d = str(tmp_path_factory.mktemp("m"))
+    cfg = ModelArgs(vocab_size=300, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                    num_key_value_heads=1, head_dim=64, tie_word_embeddings=False)
+    save_pretrained(DecoderLM(cfg).init_weights(0.05, 0), d)
+    return d
+
+
+def _json_out(capsys):
+    return json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+
+
+def test_infer_eval_and_speculative(model_dir, capsys, tmp_path):
+    assert main(["infer", "-m", model_dir, "-p", "hello", "--max-tokens", "5", "--greedy", "--json", "--device", "cpu"]) == 0
+    j = _json_out(capsys)
+    assert j["generated_tokens"] == 5 and j["prompt_tokens"] == 5
+    assert main(["infer", "-m", model_dir, "-p", "hi", "--chat", "--system", "s", "--max-tokens", "3", "--greedy", "--device", "cpu"]) == 0
+    capsys.readouterr()
+    assert main(["infer", "-m", model_dir, "-p", "hello", "--max-tokens", "6", "--greedy", "--json", "--draft-model", model_dir,
+                 "--speculative-k", "3", "--device", "cpu"]) == 0
+    j2 = _json_out(capsys)
+    assert j2["acceptance_rate"] == 1.0 and j2["tokens"] == 6          # draft == target -> everything accepted
+    data = tmp_path / "d.jsonl"
+    data.write_text("\n".join(json.dumps({"text": "the quick brown fox " * 3}) for _ in range(3)))
+    assert main(["eval", "-m", model_dir, "-d", str(data), "--device", "cpu"]) == 0
+    e = _json_out(capsys)
+    assert e["samples"] == 3 and e["perplexity"] > 1
+
+
+def test_quantize_merge_fuse_ollama(model_dir, capsys, tmp_path):
+    gg = str(tmp_path / "m.gguf")
+    assert main(["quantize", "-m", model_dir, "-o", gg, "--method", "q8_0"]) == 0
+    q = _json_out(capsys)
+    assert q["tensors"] > 10 and os.path.getsize(gg) == q["bytes"]
+    assert main(["infer", "-m", gg, "-p", "hello", "--max-tokens", "3", "--greedy", "--json", "--device", "cpu"]) == 0
+    assert _json_out(capsys)["generated_tokens"] == 3
+    out = str(tmp_path / "merged")
+    assert main(["merge", "--models", model_dir, model_dir, "--method", "linear", "-o", out, "--dtype", "float32"]) == 0
+    capsys.readouterr()
+    from pmetal_b200.models.loader import read_state_dict
+    a, b = read_state_dict(model_dir), read_state_dict(out)
+    k = "model.layers.0.mlp.down_proj.weight"
+    assert torch.allclose(a[k].float(), b[k].float(), atol=1e-3)
+    fp8 = str(tmp_path / "fp8")
+    assert main(["quantize", "-m", model_dir, "-o", fp8, "--format", "fp8"]) == 0
+    f = _json_out(capsys)
+    assert f["quantized_tensors"] > 0
+    from pmetal_b200.models.fp8 import dequantize_fp8_state_dict
+    from pmetal_b200.utils.safetensors_io import load_file
+    back = dequantize_fp8_state_dict(load_file(os.path.join(fp8, "model.safetensors")), torch.float32)
+    assert (back[k] - a[k].float()).abs().max() < 0.07 * a[k].float().abs().max()
+    mf = str(tmp_path / "Modelfile")
+    assert main(["ollama", "modelfile", "--gguf", gg, "-o", mf, "--template", "chatml", "--system", "be nice"]) == 0
+    text = open(mf).read()
+    assert text.startswith("FROM ") and 'SYSTEM """be nice"""' in text and "PARAMETER stop" in text
+    assert main(["download", "/nonexistent/x"]) == 1
+
+
+def test_distill_and_grpo_commands(model_dir, capsys, tmp_path):
+    data = tmp_path / "p.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"question {i} about things"}) for i in range(4)))
+    out = str(tmp_path / "dist")
+    assert main(["distill", "--teacher", model_dir, "--student", model_dir, "-d", str(data), "-o", out, "--max-steps", "2",
+                 "--lora-r", "4", "--device", "cpu"]) == 0
+    assert os.path.exists(os.path.join(out, "lora_weights.safetensors"))
+    capsys.readouterr()
+    out2 = str(tmp_path / "grpo")
+    assert main(["grpo", "-m", model_dir, "-d", str(data), "-o", out2, "--max-steps", "1", "--num-generations", "2",
+                 "--max-completion-length", "4", "--lora-r", "4", "--device", "cpu", "--reward", "length"]) == 0
+    assert os.path.exists(os.path.join(out2, "adapter_config.json"))
+    assert main(["cluster", "status"]) == 0

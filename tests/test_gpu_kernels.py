@@ -306,3 +306,39 @@ def test_generation_native_matches_reference_path():
     _close(meta_logits, ref_logits, rtol=5e-2, atol=5e-2, what="prefill logits")
     out = Generator(m, num_blocks=64).generate(prompts, SamplingParams.greedy(8))
     assert all(len(t) == 8 for t in out.tokens)
+
+
+@pytest.mark.parametrize("tq,tk,shift", [(256, 384, 384), (300, 200, 0), (128, 500, 100), (260, 260, 0)])
+def test_attention_rectangular_blocks(tq, tk, shift):
+    """Key j visible to query i iff j <= i + shift: full past blocks (ring attention) and offset causal blocks."""
+    nat = _nat()
+    torch.manual_seed(3)
+    hq, hkv, d = 4, 2, 128
+    q, k, v = _rand(tq, hq, d), _rand(tk, hkv, d), _rand(tk, hkv, d)
+    ss = torch.zeros(tq, dtype=torch.int32, device="cuda")
+    out, lse = nat.attn_fwd_rect(q, k, v, ss, d ** -0.5, shift)
+    kk = k.float().repeat_interleave(2, 1).permute(1, 0, 2)
+    vv = v.float().repeat_interleave(2, 1).permute(1, 0, 2)
+    s = torch.einsum("thd,hsd->hts", q.float(), kk) * d ** -0.5
+    i = torch.arange(tq, device="cuda")[:, None]
+    j = torch.arange(tk, device="cuda")[None, :]
+    s = s.masked_fill(j > i + shift, float("-inf"))
+    ref = torch.einsum("hts,hsd->thd", torch.softmax(s, -1), vv)
+    _close(out, ref, what="rect attention out")
+    assert torch.allclose(lse, torch.logsumexp(s, -1), atol=2e-2, rtol=2e-3)
+
+
+def test_ring_attention_partial_merge_matches_full():
+    """Two chunks on one device: diagonal causal block + full past block merged by log-sum-exp."""
+    _nat()
+    from pmetal_b200.parallel import cp
+    torch.manual_seed(4)
+    T, hq, hkv, d = 256, 4, 2, 128
+    q, k, v = _rand(2 * T, hq, d), _rand(2 * T, hkv, d), _rand(2 * T, hkv, d)
+    o1, l1 = cp._block_attention(q[T:], k[T:], v[T:], d ** -0.5, True)
+    o0, l0 = cp._block_attention(q[T:], k[:T], v[:T], d ** -0.5, False)
+    out, _ = cp.merge_partials([o1, o0], [l1, l0])
+    ss = torch.zeros(2 * T, dtype=torch.int32, device="cuda")
+    from pmetal_b200.ops import native
+    full, _ = native.attn_fwd(q, k, v, ss, d ** -0.5)
+    _close(out, full[T:].float(), what="merged ring partials")
