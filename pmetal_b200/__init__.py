@@ -5,3 +5,10 @@ PyTorch is the framework layer; the hot operators are hand-written CUDA kernels 
 normalisation/activation/loss/optimizer kernels and peer-memory collectives).
 """
 __version__ = "0.1.0"
+
+
+def __getattr__(name):          # lazy: importing the package must not import torch-heavy modules
+    if name in ("finetune", "infer", "Model"):
+        from . import api
+        return getattr(api, name)
+    raise AttributeError(name)

@@ -632,3 +632,93 @@ def cmd_ollama(a) -> int:
     print(write_modelfile(a.gguf, a.output, a.template, a.system, temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
                           repeat_penalty=a.repetition_penalty))
     return 0
+
+
+def _mcp_args(sp):
+    return sp.add_parser("mcp", help="Model Context Protocol server on stdio (tools for training, inference, jobs)")
+
+
+@_command(_mcp_args)
+def cmd_mcp(a) -> int:
+    from ..mcp import McpServer
+    McpServer().serve_stdio()
+    return 0
+
+
+def _pretrain_args(sp):
+    p = sp.add_parser("pretrain", help="full-parameter pre-training on token shards")
+    p.add_argument("-m", "--model", required=True, help="model directory or random:<preset> for a fresh model")
+    p.add_argument("--shards", required=True, help="glob of *.bin token shards")
+    p.add_argument("-o", "--output", default="./pretrain-output")
+    p.add_argument("--seq-len", type=int, default=2048)
+    p.add_argument("--micro-batch", type=int, default=4)
+    p.add_argument("--max-steps", type=int, default=100)
+    p.add_argument("--learning-rate", type=float, default=3e-4)
+    p.add_argument("--warmup-steps", type=int, default=10)
+    p.add_argument("--z-loss", type=float, default=1e-4)
+    p.add_argument("--resume")
+    p.add_argument("--device")
+    return p
+
+
+@_command(_pretrain_args)
+def cmd_pretrain(a) -> int:
+    import torch
+
+    from ..data.streaming import TokenShardDataset
+    from ..models.loader import load_pretrained
+    from ..trainer.pretrain import PretrainConfig, PretrainTrainer
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    model, _, _ = load_pretrained(a.model, dtype=torch.float32, device=dev)
+    cfg = PretrainConfig(learning_rate=a.learning_rate, warmup_steps=a.warmup_steps, max_steps=a.max_steps,
+                         z_loss_coef=a.z_loss, seq_len=a.seq_len, micro_batch=a.micro_batch, output=a.output)
+    tr = PretrainTrainer(model.train(), cfg)
+    if a.resume:
+        tr.load_checkpoint(a.resume)
+    ds = TokenShardDataset(a.shards, a.seq_len, int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)))
+    last = tr.run(ds, on_step=lambda s: print(json.dumps(s), file=sys.stderr))
+    tr.save_checkpoint(os.path.join(a.output, "final"))
+    print(json.dumps({"output": a.output, **last}))
+    return 0
+
+
+def _embed_args(sp):
+    p = sp.add_parser("embed-train", help="contrastive fine-tuning of an embedding model (InfoNCE / triplet / CoSENT)")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("-d", "--dataset", required=True, help="JSONL with anchor/positive[/negative][/label]")
+    p.add_argument("-o", "--output", default="./embed-output")
+    p.add_argument("--loss", default="infonce", choices=["infonce", "triplet", "cosent"])
+    p.add_argument("--batch-size", type=int, default=8)
+    p.add_argument("--max-steps", type=int, default=100)
+    p.add_argument("--learning-rate", type=float, default=2e-5)
+    p.add_argument("--lora-r", type=int, default=16)
+    p.add_argument("--device")
+    return p
+
+
+@_command(_embed_args)
+def cmd_embed_train(a) -> int:
+    from ..core.config import LoraConfig
+    from ..lora import apply_lora
+    from ..lora.adapter import save_adapter
+    from ..trainer.embedding import EmbeddingConfig, EmbeddingTrainer
+    model, tok, _, _, _ = _load_for_inference(a)
+    dev = str(model.embed_tokens.device)
+    lcfg = LoraConfig(r=a.lora_r, alpha=2.0 * a.lora_r)
+    apply_lora(model, lcfg)
+    model.to(dev).train()
+    rows = []
+    with open(a.dataset, "r", encoding="utf-8") as fh:
+        for line in fh:
+            if line.strip():
+                rows.append(json.loads(line))
+    tr = EmbeddingTrainer(model, EmbeddingConfig(loss=a.loss, learning_rate=a.learning_rate))
+    last = {}
+    for step in range(a.max_steps):
+        b = [rows[(step * a.batch_size + j) % len(rows)] for j in range(a.batch_size)]
+        enc = lambda k: [tok.encode(r[k]) for r in b]        # noqa: E731
+        last = tr.step(enc("anchor"), enc("positive"), enc("negative") if "negative" in b[0] else None,
+                       [r.get("label", 1.0) for r in b] if a.loss == "cosent" else None)
+    save_adapter(model, a.output, lcfg, a.model)
+    print(json.dumps({"output": a.output, **last}))
+    return 0

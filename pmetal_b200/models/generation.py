@@ -15,7 +15,7 @@ from typing import Callable, Iterator, List, Optional, Sequence
 
 import torch
 
-from .kv_cache import BLOCK, PagedKVCache
+from .kv_cache import BLOCK, BatchMeta, PagedKVCache
 from .sampling import Sampler, SamplingParams
 
 PREFILL_CHUNK = 2048
@@ -43,14 +43,136 @@ class GenerationResult:
         return self.prompt_tokens / self.prefill_seconds if self.prefill_seconds > 0 else 0.0
 
 
+def _bucket(n: int, lo: int = 1) -> int:
+    b = lo
+    while b < n:
+        b *= 2
+    return b
+
+
+class GraphedDecoder:
+    """Single-token decode steps replayed from CUDA graphs.
+
+    A decode step is a few hundred small launches (28 layers of norm, projections, rope, cache append, paged attention,
+    MLP): eager execution is bound by launch and interpreter overhead, not by the GPU. One graph is captured per
+    (batch bucket, block-table width bucket); every step copies the step's slots, positions, lengths and block tables
+    into the graph's static buffers from pinned host memory (two async copies) and replays it. Batches are padded to the
+    bucket with rows that point at a private scratch block, so a shrinking batch does not trigger new captures.
+    The reference compiles its decode layers with ``mx::compile`` for the same reason
+    (crates/pmetal-bridge/cpp/bridge_compiled.cpp:213-400; "~7x" in crates/pmetal-bridge/src/compile.rs:3-8)."""
+
+    PAD_SEQ = -(1 << 40)
+
+    def __init__(self, model, cache: PagedKVCache):
+        self.model, self.cache, self.device = model, cache, cache.device
+        self.graphs = {}
+        if self.PAD_SEQ not in cache.seqs:
+            cache.add_sequence(self.PAD_SEQ)
+            cache.reserve(self.PAD_SEQ, 1)
+        self.pad_block = cache.seqs[self.PAD_SEQ].blocks[0]
+
+    def _state(self, nb: int, mb: int):
+        key = (nb, mb)
+        st = self.graphs.get(key)
+        if st is not None:
+            return st
+        dev = self.device
+        st = {
+            "h64": torch.zeros(2 * nb, dtype=torch.int64).pin_memory(),              # slots | tokens
+            "h32": torch.zeros(2 * nb + nb * mb, dtype=torch.int32).pin_memory(),    # positions | seq_lens | table
+            "d64": torch.zeros(2 * nb, dtype=torch.int64, device=dev),
+            "d32": torch.zeros(2 * nb + nb * mb, dtype=torch.int32, device=dev),
+        }
+        d64, d32 = st["d64"], st["d32"]
+        st["meta"] = BatchMeta(list(range(nb)), d32[2 * nb:].view(nb, mb), d32[nb:2 * nb],
+                               torch.arange(nb, dtype=torch.int32, device=dev), torch.ones(nb, dtype=torch.int32, device=dev),
+                               d64[:nb], d32[:nb], nb, 1, mb * BLOCK)
+        st["tokens"] = d64[nb:]
+        self._fill(st, nb, mb, [], [], [], [], [])
+        self._copy(st)
+        # warm-up outside capture (lazy initialisations), then capture
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.model.forward_paged(st["tokens"], self.cache, st["meta"])
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            st["logits"] = self.model.forward_paged(st["tokens"], self.cache, st["meta"])
+        st["graph"] = g
+        self.graphs[key] = st
+        return st
+
+    def _fill(self, st, nb, mb, slots, pos, lens, tables, tokens):
+        """Write one step's metadata into the pinned host buffers (numpy views; no tensor constructions)."""
+        if "n64" not in st:
+            st["n64"], st["n32"] = st["h64"].numpy(), st["h32"].numpy()
+            st["rows"] = [None] * nb               # (first block, block count) last written per row
+            st["n32"][2 * nb:] = self.pad_block
+        a64, a32 = st["n64"], st["n32"]
+        n = len(slots)
+        a64[:n] = slots
+        a64[n:nb] = self.pad_block * BLOCK
+        a64[nb:nb + n] = tokens
+        a64[nb + n:] = 0
+        a32[:n] = pos
+        a32[n:nb] = 0
+        a32[nb:nb + n] = lens
+        a32[nb + n:2 * nb] = 1
+        tab = a32[2 * nb:].reshape(nb, mb)
+        rows = st["rows"]
+        for i in range(nb):
+            bl = tables[i] if i < n else None
+            sig = None if bl is None else (bl[0], len(bl), bl[-1])
+            if rows[i] == sig:
+                continue
+            rows[i] = sig
+            if bl is None:
+                tab[i, :] = self.pad_block
+            else:
+                tab[i, :len(bl)] = bl
+                tab[i, len(bl):] = self.pad_block
+
+    def _copy(self, st):
+        st["d64"].copy_(st["h64"], non_blocking=True)
+        st["d32"].copy_(st["h32"], non_blocking=True)
+
+    @torch.no_grad()
+    def step(self, seq_ids: Sequence[int], tokens) -> torch.Tensor:
+        n = len(seq_ids)
+        cache = self.cache
+        slots, pos, lens, tables = [], [], [], []
+        for sid in seq_ids:
+            start = cache.seqs[sid].length
+            slots.extend(cache.reserve(sid, 1))
+            pos.append(start)
+            lens.append(start + 1)
+            tables.append(cache.seqs[sid].blocks)
+        nb, mb = _bucket(n), _bucket(max(len(t) for t in tables), 8)
+        st = self._state(nb, mb)
+        toks = tokens.tolist() if isinstance(tokens, torch.Tensor) else list(tokens)
+        self._fill(st, nb, mb, slots, pos, lens, tables, toks)
+        self._copy(st)
+        st["graph"].replay()
+        return st["logits"][:n].clone()      # the static buffer is overwritten by the next replay
+
+
 class Generator:
-    def __init__(self, model, cache: Optional[PagedKVCache] = None, num_blocks: Optional[int] = None):
+    def __init__(self, model, cache: Optional[PagedKVCache] = None, num_blocks: Optional[int] = None,
+                 cuda_graphs: Optional[bool] = None):
         self.model = model
         self.device = model.embed_tokens.device
         if cache is None:
             cache = model.new_cache(num_blocks or 4096)
         self.cache = cache
         self._next_id = 0
+        self._graphed: Optional[GraphedDecoder] = None
+        if cuda_graphs is None:
+            import os
+            cuda_graphs = os.environ.get("PMETAL_DECODE_GRAPHS", "1") == "1"
+        self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda"
 
     def new_seq(self) -> int:
         sid = self._next_id
@@ -91,6 +213,12 @@ class Generator:
     @torch.no_grad()
     def decode_step(self, seq_ids: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
         """One new token per sequence → next-token logits [n, V]."""
+        if self.cuda_graphs:
+            from ..ops import functional as ops
+            if ops.native_enabled(self.model.embed_tokens) and self.model.cfg.head_dim == 128:
+                if self._graphed is None:
+                    self._graphed = GraphedDecoder(self.model, self.cache)
+                return self._graphed.step(seq_ids, tokens)
         meta = self.cache.prepare(seq_ids, [1] * len(seq_ids))
         return self.model.forward_paged(tokens, self.cache, meta)
 

@@ -100,9 +100,17 @@ def check_status() -> None:
 
 
 # ------------------------------------------------------------------------------------------- GEMM
-def _pick_bn(n: int, seg_sizes: Sequence[int] = ()) -> int:
-    """Widest tile whose boundaries respect the LoRA segments; a ragged last tile is fine (TMA zero-fills)."""
+def _pick_bn(n: int, seg_sizes: Sequence[int] = (), m: int = 1 << 30) -> int:
+    """Widest tile whose boundaries respect the LoRA segments; a ragged last tile is fine (TMA zero-fills).
+    A single row block (decode: m <= 128) is bandwidth-bound on the weight read, so narrow tiles are used there to
+    spread the columns over as many SMs as possible."""
     segs = seg_sizes[:-1] if len(seg_sizes) > 1 else ()
+    widths = (256, 128, 64, 32)
+    if m <= 128:
+        widths = tuple(b for b in (32, 64, 128, 256) if -(-n // b) <= 4 * 148) or (256,)
+        for bn in widths:
+            if all(s % bn == 0 for s in segs):
+                return bn
     for bn in (256, 128, 64, 32):
         if n >= bn and all(s % bn == 0 for s in segs):
             return bn
@@ -153,7 +161,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0, residual: Optiona
     Nw = max(N, pad_n_to)
     if out is None:
         out = torch.empty(M, Nw, dtype=torch.bfloat16, device=x.device)
-    bn = bn or _pick_bn(Nw)
+    bn = bn or _pick_bn(Nw, (), M)
     raw_gemm(x, 0, x.stride(0), M, w, 0, w.stride(0), N, out, 0, out.stride(0), M, Nw, K, R=residual,
              ldr=residual.stride(0) if residual is not None else 0, alpha=alpha, bn=bn)
     return out
@@ -164,7 +172,7 @@ def gemm_lora(x, w, t, b, seg_sizes, r, residual=None, bn: int = 0) -> torch.Ten
     M, K = x.shape
     N = w.shape[0]
     out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
-    bn = bn or _pick_bn(N, seg_sizes)
+    bn = bn or _pick_bn(N, seg_sizes, M)
     kw = {}
     if t is not None:
         kw = dict(A2=t, a2_mn=0, lda2=t.stride(0), a2_k=t.shape[1], B2=b, b2_mn=0, ldb2=b.stride(0), b2_rows=N, K2=r,

@@ -1,0 +1,137 @@
+"""Full-parameter pre-training loop over token shards (crates/pmetal-trainer/src/pretrain/*).
+
+Every parameter trains (bf16 compute shadows of fp32 masters in the flat AdamW buffer), the loss is next-token
+cross-entropy plus an optional z-loss ``z_coef * mean(logsumexp(logits)^2)`` that keeps the softmax normaliser near one,
+and a checkpoint holds model, optimiser state, step and data position so a run resumes exactly."""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import asdict, dataclass
+from typing import Iterable, Optional
+
+import torch
+
+from ..core.scheduler import LearningRateScheduler
+
+
+@dataclass
+class PretrainConfig:
+    learning_rate: float = 3e-4
+    min_lr: float = 3e-5
+    warmup_steps: int = 100
+    max_steps: int = 1000
+    weight_decay: float = 0.1
+    max_grad_norm: float = 1.0
+    z_loss_coef: float = 1e-4
+    seq_len: int = 2048
+    micro_batch: int = 4
+    gradient_accumulation_steps: int = 1
+    lr_scheduler: str = "cosine"
+    checkpoint_every: int = 0
+    output: str = "./pretrain-output"
+
+
+def z_loss(hidden: torch.Tensor, head: torch.Tensor, chunk: int = 4096) -> torch.Tensor:
+    tot = hidden.new_zeros((), dtype=torch.float32)
+    for a in range(0, hidden.shape[0], chunk):
+        lse = torch.logsumexp(hidden[a:a + chunk].float() @ head.float().t(), -1)
+        tot = tot + (lse ** 2).sum()
+    return tot / hidden.shape[0]
+
+
+class PretrainTrainer:
+    def __init__(self, model, cfg: PretrainConfig, dist=None):
+        from .optimizer import FlatAdamW, attach_shadows
+        self.model, self.cfg, self.dist = model, cfg, dist
+        self.device = model.embed_tokens.device
+        for p in model.parameters():
+            p.requires_grad_(True)
+        shadow = torch.bfloat16 if self.device.type == "cuda" else None
+        self.opt = FlatAdamW(model.named_parameters(), lr=cfg.learning_rate, weight_decay=cfg.weight_decay,
+                             max_grad_norm=cfg.max_grad_norm, shadow_dtype=shadow)
+        if dist is not None and getattr(dist, "fused", False):
+            dist.bind_optimizer(self.opt)
+        if shadow is not None:
+            attach_shadows(model, self.opt)
+        self.sched = LearningRateScheduler(cfg.learning_rate, cfg.max_steps, cfg.warmup_steps, cfg.lr_scheduler,
+                                           min_lr=cfg.min_lr)
+        self.step_count = 0
+        self.tokens_seen = 0
+
+    def _batch(self, windows):
+        import numpy as np
+        ids = torch.as_tensor(np.asarray(windows), dtype=torch.int64, device=self.device)
+        return ids if ids.dim() == 2 else ids[None]
+
+    def train_step(self, windows) -> dict:
+        c = self.cfg
+        self.opt.set_lr(self.sched.get_lr(self.step_count))
+        self.opt.zero_grad()
+        ids = self._batch(windows)
+        B, L = ids.shape
+        tgt = torch.full_like(ids, -100)
+        tgt[:, :-1] = ids[:, 1:]
+        from ..ops import functional as ops
+        import contextlib
+        # every weight trains, so the masters are the fp32 views of the flat optimiser buffer: run the PyTorch operator
+        # path, under bf16 autocast on the GPU
+        amp = torch.autocast("cuda", dtype=torch.bfloat16) if self.device.type == "cuda" else contextlib.nullcontext()
+        with ops.force_reference(), amp:
+            h = self.model.forward_hidden(ids)
+            ce = ops.causal_lm_loss(h, self.model.head_weight(), tgt.reshape(-1), -100, None)
+            loss = ce
+            zl = None
+            if c.z_loss_coef > 0:
+                zl = z_loss(h, self.model.head_weight())
+                loss = loss + c.z_loss_coef * zl
+        loss.backward()
+        if self.dist is not None and self.dist.world_size > 1:
+            gn = self.dist.reduce_and_step(self.opt, 1.0)
+        else:
+            gn = self.opt.step(1.0)
+        self.step_count += 1
+        self.tokens_seen += B * L
+        return {"step": self.step_count, "loss": float(ce.detach()), "z_loss": float(zl.detach()) if zl is not None else 0.0,
+                "grad_norm": float(gn), "lr": self.opt.lr, "tokens": self.tokens_seen}
+
+    def run(self, dataset: Iterable, on_step=None) -> dict:
+        c = self.cfg
+        batch, last = [], {}
+        for window in dataset:
+            batch.append(window)
+            if len(batch) < c.micro_batch:
+                continue
+            last = self.train_step(batch)
+            batch = []
+            if on_step:
+                on_step(last)
+            if c.checkpoint_every and self.step_count % c.checkpoint_every == 0:
+                self.save_checkpoint(os.path.join(c.output, f"step_{self.step_count}"))
+            if self.step_count >= c.max_steps:
+                break
+        return last
+
+    def save_checkpoint(self, path: str) -> None:
+        from ..utils import safetensors_io as st
+        os.makedirs(path, exist_ok=True)
+        sd = {k: v.detach().cpu().contiguous() for k, v in self.model.hf_state_dict(merged=False).items()}
+        st.save_file(sd, os.path.join(path, "model.safetensors"), metadata={"format": "pt"})
+        o = self.opt.state_dict()
+        st.save_file({k: v.detach().cpu().contiguous() for k, v in o.items() if isinstance(v, torch.Tensor)},
+                     os.path.join(path, "optimizer.safetensors"))
+        with open(os.path.join(path, "trainer_state.json"), "w", encoding="utf-8") as fh:
+            json.dump({"step": self.step_count, "tokens_seen": self.tokens_seen, "config": asdict(self.cfg),
+                       "optimizer_scalars": {k: v for k, v in o.items() if not isinstance(v, torch.Tensor)}}, fh, indent=2)
+
+    def load_checkpoint(self, path: str) -> None:
+        from ..utils import safetensors_io as st
+        # parameters are views of the optimiser's flat fp32 buffer, so loading into the model updates the masters
+        self.model.load_hf_state_dict(st.load_file(os.path.join(path, "model.safetensors")), strict=False)
+        with open(os.path.join(path, "trainer_state.json"), "r", encoding="utf-8") as fh:
+            state = json.load(fh)
+        o = dict(st.load_file(os.path.join(path, "optimizer.safetensors")))
+        o.update(state.get("optimizer_scalars", {}))
+        self.opt.load_state_dict(o)
+        self.opt.sync_shadow()
+        self.step_count, self.tokens_seen = state["step"], state["tokens_seen"]

@@ -1,0 +1,121 @@
+"""Embedding objectives, token shards, pre-training with checkpoint resume, MCP protocol, Python API (CPU)."""
+import io
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from pmetal_b200.data.streaming import ShardWriter, TokenShardDataset
+from pmetal_b200.trainer import embedding as E
+
+
+def tiny(seed=0, vocab=97):
+    from pmetal_b200.models.config import ModelArgs
+    from pmetal_b200.models.decoder import DecoderLM
+    cfg = ModelArgs(vocab_size=vocab, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                    num_attention_heads=2, num_key_value_heads=1, head_dim=16)
+    return DecoderLM(cfg).init_weights(0.1, seed)
+
+
+def test_contrastive_losses():
+    a = torch.nn.functional.normalize(torch.tensor([[1.0, 0.0], [0.0, 1.0]]), dim=-1)
+    assert float(E.info_nce(a, a, 0.05)) < 1e-6
+    assert float(E.info_nce(a, a.flip(0), 0.05)) > 10
+    assert float(E.triplet_loss(a, a, a.flip(0), 0.5)) == 0.0
+    assert float(E.triplet_loss(a, a.flip(0), a, 0.5)) == pytest.approx(1.5)
+    cos_ok = E.cosent_loss(a, torch.stack([a[1], a[1]]), torch.tensor([0.0, 1.0]))      # cos 0 (label 0) < cos 1 (label 1)
+    cos_bad = E.cosent_loss(a, torch.stack([a[0], a[0]]), torch.tensor([0.0, 1.0]))     # order violated
+    assert float(cos_ok) < float(cos_bad)
+    h = torch.arange(12, dtype=torch.float32).reshape(6, 2)
+    p = E.pool(h, [0, 2, 6], "mean", normalize=False)
+    assert torch.allclose(p, torch.stack([h[:2].mean(0), h[2:].mean(0)]))
+    assert torch.allclose(E.pool(h, [0, 2, 6], "last", False), torch.stack([h[1], h[5]]))
+
+
+def test_embedding_trainer_improves():
+    torch.manual_seed(0)
+    tr = E.EmbeddingTrainer(tiny(1), E.EmbeddingConfig(learning_rate=1e-2, temperature=1.0))
+    anchors = [[1, 2, 3], [40, 41, 42, 43], [1, 2, 5], [40, 41, 45]]
+    positives = [[1, 2, 4], [40, 41, 44], [1, 2, 6], [40, 41, 46]]
+    a = tr.step(anchors, positives)["loss"]
+    for _ in range(10):
+        b = tr.step(anchors, positives)["loss"]
+    assert b < a
+    e = tr.encode(anchors)
+    assert e.shape == (4, 32) and torch.allclose(e.norm(dim=-1), torch.ones(4), atol=1e-5)
+
+
+def test_token_shards(tmp_path):
+    p = str(tmp_path / "s0.bin")
+    with ShardWriter(p) as w:
+        w.add_document(list(range(100)))
+        w.add_document(list(range(100, 130)))
+    assert os.path.getsize(p) == 130 * 4
+    ds = TokenShardDataset(str(tmp_path / "*.bin"), 16, shuffle=False)
+    wins = list(ds)
+    assert len(wins) == 8 and wins[0].tolist() == list(range(16)) and ds.total_tokens() == 130
+    assert ds.documents(0).tolist() == [0, 100, 130]
+    r0 = [w[0] for w in TokenShardDataset(str(tmp_path / "*.bin"), 16, 0, 2, shuffle=True, seed=1)]
+    r1 = [w[0] for w in TokenShardDataset(str(tmp_path / "*.bin"), 16, 1, 2, shuffle=True, seed=1)]
+    assert sorted(r0 + r1) == [i * 16 for i in range(8)] and not set(r0) & set(r1)
+    with pytest.raises(FileNotFoundError):
+        TokenShardDataset(str(tmp_path / "none*.bin"), 16)
+
+
+def test_pretrain_loss_falls_and_checkpoint_resumes(tmp_path):
+    from pmetal_b200.trainer.pretrain import PretrainConfig, PretrainTrainer, z_loss
+    torch.manual_seed(0)
+    cfg = PretrainConfig(learning_rate=5e-3, min_lr=5e-3, warmup_steps=0, max_steps=6, micro_batch=2, seq_len=16,
+                         z_loss_coef=1e-3, lr_scheduler="constant")
+    data = [np.arange(i, i + 16) % 97 for i in range(40)]
+    tr = PretrainTrainer(tiny(2), cfg)
+    first = tr.train_step(data[:2])
+    last = tr.run(iter(data))
+    assert last["loss"] < first["loss"] and last["z_loss"] > 0 and tr.step_count == 6
+    assert float(z_loss(torch.zeros(3, 4), torch.zeros(5, 4))) == pytest.approx(math.log(5) ** 2)
+    ck = str(tmp_path / "ck")
+    tr.save_checkpoint(ck)
+    tr2 = PretrainTrainer(tiny(3), cfg)
+    tr2.load_checkpoint(ck)
+    assert tr2.step_count == 6 and torch.allclose(tr2.opt.flat_p, tr.opt.flat_p) and torch.allclose(tr2.opt.flat_m, tr.opt.flat_m)
+    a, b = tr.train_step(data[2:4]), tr2.train_step(data[2:4])
+    assert a["loss"] == pytest.approx(b["loss"], rel=1e-5)
+
+
+def test_mcp_protocol(tmp_path):
+    from pmetal_b200.mcp import McpServer
+    srv = McpServer()
+    msgs = [{"jsonrpc": "2.0", "id": 1, "method": "initialize", "params": {}},
+            {"jsonrpc": "2.0", "method": "notifications/initialized"},
+            {"jsonrpc": "2.0", "id": 2, "method": "tools/list"},
+            {"jsonrpc": "2.0", "id": 3, "method": "tools/call", "params": {"name": "set_learning_rate",
+                                                                           "arguments": {"output_dir": str(tmp_path), "lr": 1e-5}}},
+            {"jsonrpc": "2.0", "id": 4, "method": "tools/call", "params": {"name": "job_status", "arguments": {"id": "nope"}}},
+            {"jsonrpc": "2.0", "id": 5, "method": "tools/call", "params": {"name": "infer", "arguments": {}}},
+            {"jsonrpc": "2.0", "id": 6, "method": "bogus"}]
+    fin = io.StringIO("\n".join(json.dumps(m) for m in msgs) + "\nnot json\n")
+    fout = io.StringIO()
+    srv.serve_stdio(fin, fout)
+    out = [json.loads(l) for l in fout.getvalue().splitlines()]
+    by_id = {o["id"]: o for o in out}
+    assert by_id[1]["result"]["serverInfo"]["name"] == "pmetal-b200"
+    names = {t["name"] for t in by_id[2]["result"]["tools"]}
+    assert {"start_train", "start_grpo", "job_status", "infer", "set_learning_rate", "graceful_stop"} <= names and len(names) >= 20
+    assert by_id[3]["result"]["isError"] is False
+    assert json.load(open(tmp_path / ".lr_control.json")) == {"command": "set_lr", "lr": 1e-5}
+    assert by_id[4]["result"]["isError"] is True and by_id[5]["result"]["isError"] is True
+    assert by_id[6]["error"]["code"] == -32601 and by_id[None]["error"]["code"] == -32700
+
+
+def test_python_api_generate(tmp_path):
+    import pmetal_b200 as pm
+    from pmetal_b200.models.loader import save_pretrained
+    d = str(tmp_path / "m")
+    save_pretrained(tiny(4, vocab=300), d)
+    m = pm.Model.load(d, device="cpu")
+    text = m.generate("hello", max_tokens=4, temperature=0)
+    assert isinstance(text, str)
+    assert "".join(m.stream("hello", max_tokens=4, temperature=0)) == text
