@@ -93,6 +93,44 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def measure_decode(cfg, dev, reduce_max, reduce_sum) -> dict:
+    """Greedy decode throughput of a fresh bf16 model of the benchmark architecture on the paged KV cache."""
+    import torch
+    from pmetal_b200.models.decoder import DecoderLM
+    from pmetal_b200.models.generation import Generator
+    from pmetal_b200.models.sampling import SamplingParams
+    m = DecoderLM(cfg).init_weights(0.02, 1).to(dev).to(torch.bfloat16).eval()
+    for p in m.parameters():
+        p.requires_grad_(False)
+    out = {}
+    g = torch.Generator().manual_seed(5)
+    for name, batch, new in (("single_stream", 1, 128), ("batch16", 16, 64)):
+        gen = Generator(m, num_blocks=1024)
+        prompts = [torch.randint(0, cfg.vocab_size, (128,), generator=g).tolist() for _ in range(batch)]
+        gen.generate(prompts, SamplingParams.greedy(8))                     # warm-up: graph capture, lazy inits
+        torch.cuda.synchronize()
+        seqs = [gen.new_seq() for _ in prompts]
+        logits = gen.prefill(seqs, prompts)
+        ids = logits.argmax(-1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(new):
+            logits = gen.decode_step(seqs, ids)
+            ids = logits.argmax(-1)
+            _ = ids.tolist()                                                # tokens reach the host every step
+        e1.record()
+        torch.cuda.synchronize()
+        ms = reduce_max(e0.elapsed_time(e1))
+        out[name] = {"tokens_per_s": round(reduce_sum(float(batch * new)) / (ms / 1e3), 1),
+                     "ms_per_step": round(ms / new, 3), "batch_per_gpu": batch, "new_tokens": new}
+        for s_ in seqs:
+            gen.cache.free_sequence(s_)
+    del m
+    torch.cuda.empty_cache()
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -104,6 +142,7 @@ def main() -> None:
     ap.add_argument("--pack-len", type=int, default=4096)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--dp", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode tok/s measurement appended to the report")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -236,6 +275,12 @@ def main() -> None:
         dist.all_reduce(t)
         return float(t.item())
 
+    # ---- decode tok/s of the same architecture (second half of the headline metric): every rank serves its own
+    # replica; single-stream and 16-stream greedy decode from 128-token prompts, device-timed, summed over ranks
+    decode = None
+    if not args.no_decode:
+        decode = measure_decode(cfg, dev, reduce_max, reduce_sum)
+
     ms = reduce_max(ms)
     ms_b = reduce_max(ms_b)
     tok_a = reduce_sum(float(tokens_a))
@@ -260,6 +305,8 @@ def main() -> None:
             "gpu_launches": int(launches),
             "final_loss": round(last_loss, 4),
         }
+        if decode is not None:
+            out["decode"] = decode
         print(json.dumps(out))
     sys.stdout.flush()
     if world > 1:

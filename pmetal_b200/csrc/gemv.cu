@@ -1,0 +1,244 @@
+// Skinny linear layers for decode: y[M, N] = f(x)[M, K] * W[N, K]^T for M <= 16 rows.
+//
+// A decode step multiplies a handful of token rows by every weight matrix of the model: the work is one pass over the
+// weights and is bound by HBM bandwidth, so tensor cores (and the 128-row tiles they want) buy nothing. Each warp owns
+// a few output columns and streams their weight rows with 16-byte loads while all M activations sit in shared memory;
+// partial sums are reduced with warp shuffles. Around that core the kernel fuses what a decoder layer needs, so a layer
+// is six launches instead of a dozen:
+//   * RMSNorm prologue: x is normalised (and scaled by the norm weight) while it is staged into shared memory
+//   * SwiGLU epilogue: with gate rows [0, I) and up rows [I, 2I) a warp computes column j of both and stores
+//     silu(g) * u, so the [M, 2I] intermediate never exists
+//   * residual add
+//   * LoRA: y += t[:, seg*r : (seg+1)*r] . B[n, :] with t = s * x A^T from a small launch of this same kernel
+// The reference's decode path has the same shape (compiled fused layers, crates/pmetal-bridge/cpp/bridge_compiled.cpp:213-400;
+// fused gate/up + SwiGLU and dequant mat-vec Metal kernels, crates/pmetal-metal/src/kernels/metal/fused_moe.metal).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pm {
+
+constexpr int kGvThreads = 256;
+constexpr int kGvWarps = kGvThreads / 32;
+
+struct GemvParams {
+  const __nv_bfloat16* x;        // [M, ldx]
+  int ldx;
+  const __nv_bfloat16* w;        // [N_w, K] row-major (N_w = 2 * N when swiglu)
+  int ldw;
+  const __nv_bfloat16* norm_w;   // [K] or null: RMSNorm prologue
+  float eps;
+  const __nv_bfloat16* residual; // [M, ldr] or null
+  int ldr;
+  __nv_bfloat16* y;              // [M, ldy]
+  int ldy;
+  int M, N, K;                   // N = output columns
+  int swiglu;                    // 1: y[:, j] = silu(x w_j) * (x w_{N + j})
+  float alpha;
+  // LoRA (all null / 0 when unused): t [M, ldt] bf16 (scale folded in), lora_b [N_w, r] fp32
+  const __nv_bfloat16* t;
+  int ldt;
+  const float* lora_b;
+  int r;
+  int seg_end[4];                // cumulative output-row boundaries of the stacked projections (0x7fffffff padding)
+};
+
+__device__ __forceinline__ float gv_silu(float v) { return v / (1.f + __expf(-v)); }
+
+template <int MR, int C>
+__global__ void __launch_bounds__(kGvThreads) gemv_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) uint8_t gv_smem[];
+  __nv_bfloat16* sx = reinterpret_cast<__nv_bfloat16*>(gv_smem);   // [MR][K] (rows >= M are zero)
+  __shared__ float s_rstd[MR];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = p.K;
+
+  // ---- stage x (optionally RMS-normalised) into shared memory
+  if (p.norm_w) {
+    for (int m = warp; m < MR; m += kGvWarps) {
+      float ss = 0.f;
+      if (m < p.M)
+        for (int k = lane * 8; k < K; k += 256) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(p.x + static_cast<long long>(m) * p.ldx + k);
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            ss += f.x * f.x + f.y * f.y;
+          }
+        }
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s_rstd[m] = rsqrtf(ss / static_cast<float>(K) + p.eps);
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < MR * (K / 8); i += kGvThreads) {
+    const int m = i / (K / 8), k = (i - m * (K / 8)) * 8;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (m < p.M) {
+      raw = *reinterpret_cast<const uint4*>(p.x + static_cast<long long>(m) * p.ldx + k);
+      if (p.norm_w) {
+        const uint4 nw = *reinterpret_cast<const uint4*>(p.norm_w + k);
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+        const __nv_bfloat162* n2 = reinterpret_cast<const __nv_bfloat162*>(&nw);
+        const float rs = s_rstd[m];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]), g = __bfloat1622float2(n2[e]);
+          // same rounding points as the stand-alone RMSNorm kernel: bf16(x * rstd) * w
+          const float a = __bfloat162float(__float2bfloat16(f.x * rs)) * g.x;
+          const float b = __bfloat162float(__float2bfloat16(f.y * rs)) * g.y;
+          h2[e] = __floats2bfloat162_rn(a, b);
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(sx + static_cast<long long>(m) * K + k) = raw;
+  }
+  __syncthreads();
+
+  // ---- each warp walks groups of C output columns
+  const int n_groups = (p.N + C - 1) / C;
+  for (int g = blockIdx.x * kGvWarps + warp; g < n_groups; g += gridDim.x * kGvWarps) {
+    float acc[MR][C], acc2[MR][C];
+#pragma unroll
+    for (int m = 0; m < MR; ++m)
+#pragma unroll
+      for (int c = 0; c < C; ++c) { acc[m][c] = 0.f; acc2[m][c] = 0.f; }
+    const int n0 = g * C;
+    for (int k = lane * 8; k < K; k += 256) {
+      uint4 wv[C], wv2[C];
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const int n = min(n0 + c, p.N - 1);
+        wv[c] = __ldg(reinterpret_cast<const uint4*>(p.w + static_cast<long long>(n) * p.ldw + k));
+        if (p.swiglu) wv2[c] = __ldg(reinterpret_cast<const uint4*>(p.w + static_cast<long long>(n + p.N) * p.ldw + k));
+      }
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(sx + m * K + k);
+        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+        float xf[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(x2[e]);
+          xf[2 * e] = f.x;
+          xf[2 * e + 1] = f.y;
+        }
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv[c]);
+          float s = 0.f;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(w2[e]);
+            s = fmaf(xf[2 * e], f.x, s);
+            s = fmaf(xf[2 * e + 1], f.y, s);
+          }
+          acc[m][c] += s;
+          if (p.swiglu) {
+            const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&wv2[c]);
+            float s2 = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(u2[e]);
+              s2 = fmaf(xf[2 * e], f.x, s2);
+              s2 = fmaf(xf[2 * e + 1], f.y, s2);
+            }
+            acc2[m][c] += s2;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; ++m)
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        float v = acc[m][c], v2 = acc2[m][c];
+        for (int o = 16; o > 0; o >>= 1) {
+          v += __shfl_xor_sync(0xffffffffu, v, o);
+          if (p.swiglu) v2 += __shfl_xor_sync(0xffffffffu, v2, o);
+        }
+        acc[m][c] = v;
+        acc2[m][c] = v2;
+      }
+    // lanes 0 .. M*C-1 each finish one output element
+    const int e = lane;
+    if (e < p.M * C) {
+      const int m = e / C, c = e - m * C, n = n0 + c;
+      if (n < p.N) {
+        // pick this lane's values without dynamic register indexing
+        float v = 0.f, v2 = 0.f;
+#pragma unroll
+        for (int mm = 0; mm < MR; ++mm)
+#pragma unroll
+          for (int cc = 0; cc < C; ++cc)
+            if (mm == m && cc == c) { v = acc[mm][cc]; v2 = acc2[mm][cc]; }
+        if (p.t) {
+          auto lora = [&](int row) {
+            int seg = 0;
+#pragma unroll
+            for (int i = 0; i < 3; ++i) seg += (row >= p.seg_end[i]) ? 1 : 0;
+            const __nv_bfloat16* tr = p.t + static_cast<long long>(m) * p.ldt + seg * p.r;
+            const float* br = p.lora_b + static_cast<long long>(row) * p.r;
+            float s = 0.f;
+            for (int j = 0; j < p.r; ++j) s = fmaf(__bfloat162float(tr[j]), br[j], s);
+            return s;
+          };
+          v += lora(n);
+          if (p.swiglu) v2 += lora(n + p.N);
+        }
+        v *= p.alpha;
+        if (p.swiglu) v = gv_silu(v) * (v2 * p.alpha);
+        if (p.residual) v += __bfloat162float(p.residual[static_cast<long long>(m) * p.ldr + n]);
+        p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16(v);
+      }
+    }
+  }
+}
+
+template <int MR, int C>
+static int launch_gemv(const GemvParams& p, cudaStream_t st) {
+  const size_t smem = static_cast<size_t>(MR) * p.K * 2;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<MR, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = 200 * 1024;
+  }
+  const int groups = (p.N + C - 1) / C;
+  int grid = (groups + kGvWarps - 1) / kGvWarps;
+  const int cap = 148 * 4;
+  if (grid > cap) grid = cap;
+  gemv_kernel<MR, C><<<grid, kGvThreads, smem, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace pm
+
+using namespace pm;
+
+// Returns 0, a negative argument error, or a CUDA error code. K % 8 == 0, row strides % 8 == 0, M <= 16,
+// M * cols-per-warp <= 32.
+extern "C" int pm_gemv(const void* x, int ldx, const void* w, int ldw, const void* norm_w, float eps, const void* residual,
+                       int ldr, void* y, int ldy, int M, int N, int K, int swiglu, float alpha, const void* t, int ldt,
+                       const float* lora_b, int r, const int* seg_end, cudaStream_t st) {
+  if (M < 1 || M > 16 || N < 1 || K < 8 || (K % 8) || (ldx % 8) || (ldw % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -2;
+  if (norm_w && (reinterpret_cast<uintptr_t>(norm_w) & 15)) return -2;
+  if (static_cast<size_t>(M <= 4 ? 4 : (M <= 8 ? 8 : 16)) * K * 2 > 200 * 1024) return -3;
+  GemvParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx;
+  p.w = static_cast<const __nv_bfloat16*>(w); p.ldw = ldw;
+  p.norm_w = static_cast<const __nv_bfloat16*>(norm_w); p.eps = eps;
+  p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+  p.y = static_cast<__nv_bfloat16*>(y); p.ldy = ldy;
+  p.M = M; p.N = N; p.K = K; p.swiglu = swiglu; p.alpha = alpha;
+  p.t = static_cast<const __nv_bfloat16*>(t); p.ldt = ldt; p.lora_b = lora_b; p.r = r;
+  for (int i = 0; i < 4; ++i) p.seg_end[i] = seg_end ? seg_end[i] : 0x7fffffff;
+  // wide outputs: several columns per warp for more loads in flight; narrow outputs: one column per warp so that
+  // every SM gets work
+  const bool wide = N >= 148 * kGvWarps * 2;
+  if (M <= 4) return wide ? launch_gemv<4, 4>(p, st) : launch_gemv<4, 1>(p, st);
+  if (M <= 8) return wide ? launch_gemv<8, 2>(p, st) : launch_gemv<8, 1>(p, st);
+  return wide ? launch_gemv<16, 2>(p, st) : launch_gemv<16, 1>(p, st);
+}

@@ -117,6 +117,25 @@ class FusedLinear(nn.Module):
                                self.scale, residual, getattr(self, "lora_a_c", None), getattr(self, "lora_b_c", None),
                                getattr(self, "qweight", None))
 
+    def gemv_ok(self, m: int) -> bool:
+        """Decode fast path: a few rows, plain bf16 weight, no bias."""
+        return (m <= 16 and self.bias is None and getattr(self, "qweight", None) is None and self.weight.is_cuda
+                and self.weight.dtype == torch.bfloat16 and not self.weight.requires_grad and self.in_features % 8 == 0)
+
+    def gemv_forward(self, x: torch.Tensor, norm_w=None, eps: float = 1e-6, residual=None, swiglu: bool = False):
+        """y = norm(x) W^T (+ LoRA) (+ residual), optionally SwiGLU over the (gate, up) halves; one or two launches of
+        the skinny mat-vec kernel."""
+        from ..ops import native as nat
+        t = None
+        if self.lora_a is not None:
+            a_c = getattr(self, "lora_a_c", None)
+            if a_c is None:
+                a_c = self.lora_a.detach().to(torch.bfloat16)
+            t = nat.gemv(x, a_c, norm_w, eps, alpha=self.scale)
+            return nat.gemv(x, self.weight, norm_w, eps, residual, swiglu, t=t, lora_b=self.lora_b.detach(), r=self.r,
+                            seg_sizes=self.seg_sizes)
+        return nat.gemv(x, self.weight, norm_w, eps, residual, swiglu)
+
     def _lora_delta(self, x: torch.Tensor) -> torch.Tensor:
         outs, o = [], 0
         for i, sz in enumerate(self.seg_sizes):
@@ -312,8 +331,23 @@ class DecoderLM(nn.Module):
         native = ops.use_native(x) and d == 128
         rope = ops.rope_table(meta.positions, d, cfg.rope_theta, cfg.rope_scale)
         T = x.shape[0]
+        skinny = native and T <= 16
         for li, layer in enumerate(self.layers):
             at = layer.self_attn
+            if skinny and isinstance(layer.mlp, MLP) and at.qkv_proj.gemv_ok(T) and layer.mlp.gate_up_proj.gemv_ok(T):
+                # decode: six launches per layer (norm+qkv, qk-norm+rope, cache append, attention, o+residual,
+                # norm+gate/up+SwiGLU, down+residual)
+                from ..ops import native as nat
+                eps = cfg.rms_norm_eps
+                qkv = at.qkv_proj.gemv_forward(x, layer.input_layernorm, eps)
+                q, k = nat.qknorm_rope_fwd(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps)
+                v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+                nat.kv_append(k, v, cache.k[li], cache.v[li], meta.slots)
+                o = nat.paged_attn(q, cache.k[li], cache.v[li], meta, d ** -0.5, at.window).view(T, hq * d)
+                h = at.o_proj.gemv_forward(o, residual=x)
+                act = layer.mlp.gate_up_proj.gemv_forward(h, layer.post_attention_layernorm, eps, swiglu=True)
+                x = layer.mlp.down_proj.gemv_forward(act, residual=h)
+                continue
             n1 = ops.rms_norm(x, layer.input_layernorm, cfg.rms_norm_eps)
             qkv = at.qkv_proj(n1)
             if native:
@@ -327,10 +361,15 @@ class DecoderLM(nn.Module):
             h = at.o_proj(o, x)
             n2 = ops.rms_norm(h, layer.post_attention_layernorm, cfg.rms_norm_eps)
             x = layer.mlp(n2, h)
-        x = ops.rms_norm(x, self.norm, cfg.rms_norm_eps)
         if not all_logits:
             last = (meta.q_start + meta.q_lens - 1).long()
-            x = x[last]
+            x = x[last]               # RMSNorm is per row, so selecting rows first is equivalent
+        head = self.head_weight()
+        if (skinny and not return_hidden and x.shape[0] <= 16 and cfg.final_logit_softcap <= 0
+                and head.dtype == torch.bfloat16 and not head.requires_grad):
+            from ..ops import native as nat
+            return nat.gemv(x.contiguous(), head, self.norm, cfg.rms_norm_eps)      # final norm fused into the head
+        x = ops.rms_norm(x, self.norm, cfg.rms_norm_eps)
         return x if return_hidden else self.logits(x)
 
     def _paged_attention_reference(self, qkv, at, rope, cache, meta, li):

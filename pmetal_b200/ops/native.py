@@ -47,7 +47,7 @@ def _load():
                "pm_qknorm_rope_bwd", "pm_swiglu_fwd", "pm_swiglu_bwd", "pm_ce_fwd_bwd", "pm_sumsq", "pm_adamw_flat",
                "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16", "pm_paged_attn", "pm_kv_append", "pm_attn_fwd_tc", "pm_attn_bwd_tc", "pm_dequant_4bit", "pm_sample", "pm_spec_verify", "pm_count_tokens",
                "pm_moe_route", "pm_moe_gather", "pm_moe_combine", "pm_gguf_dequant_bf16", "pm_fp8_quant", "pm_fp8_dequant",
-               "pm_kd_fwd_bwd", "pm_merge_fused", "pm_dot_norms", "pm_attn_fwd_tc_rect"):
+               "pm_kd_fwd_bwd", "pm_merge_fused", "pm_dot_norms", "pm_attn_fwd_tc_rect", "pm_gemv"):
         getattr(_LIB, fn).restype = c_int
 
 
@@ -640,3 +640,20 @@ def dot_norms(a, b):
     _chk(lib().pm_dot_norms(_p(a.contiguous()), _p(b.contiguous()), c_int(int(a.dtype == torch.bfloat16)), c_ll(a.numel()),
                             _p(out), _stream()), "pm_dot_norms")
     return out
+
+
+# ------------------------------------------------------------------------------------------- decode mat-vec
+def gemv(x, w, norm_w=None, eps: float = 1e-6, residual=None, swiglu: bool = False, alpha: float = 1.0, t=None,
+         lora_b=None, r: int = 0, seg_sizes: Sequence[int] = ()):
+    """x [M <= 16, K] bf16, w [N_w, K] bf16 -> [M, N] bf16 (N = N_w / 2 with ``swiglu``). Optional fused RMSNorm of x,
+    residual add, SwiGLU over (gate rows, up rows) and LoRA term t . lora_b^T (t carries the scale)."""
+    M, K = x.shape
+    Nw = w.shape[0]
+    N = Nw // 2 if swiglu else Nw
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    ends = _seg_ends(seg_sizes) if len(seg_sizes) > 1 else (c_int * 4)(*([0x7FFFFFFF] * 4))
+    _chk(lib().pm_gemv(_p(x), c_int(x.stride(0)), _p(w), c_int(w.stride(0)), _p(norm_w), c_float(eps), _p(residual),
+                       c_int(residual.stride(0) if residual is not None else 0), _p(y), c_int(N), c_int(M), c_int(N),
+                       c_int(K), c_int(int(swiglu)), c_float(alpha), _p(t), c_int(t.stride(0) if t is not None else 0),
+                       _p(lora_b), c_int(r), ends, _stream()), "pm_gemv")
+    return y

@@ -254,3 +254,52 @@ def test_local_grouped_moe_engine_matches_dense_reference():
             h = (torch.nn.functional.silu(h[:, :I]) * h[:, I:]).bfloat16().float()
             ref.index_add_(0, tok, (h @ down[e].float().t()).bfloat16().float() * w[tok, slot][:, None])
         assert (y.float() - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 2e-3
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 1024), (4, 1024, 3072), (7, 6144, 1024), (16, 1000, 2048), (3, 151936, 1024)])
+def test_gemv_plain_norm_residual(M, N, K):
+    nat = _nat()
+    torch.manual_seed(M + N)
+    x = (torch.randn(M, K, device="cuda")).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * K ** -0.5).bfloat16()
+    nw = (1 + 0.1 * torch.randn(K, device="cuda")).bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    y = nat.gemv(x, w)
+    ref = x.float() @ w.float().t()
+    assert (y.float() - ref).abs().max() <= 0.02 * ref.abs().max() + 1e-2
+    y = nat.gemv(x, w, norm_w=nw, eps=1e-6, residual=res, alpha=0.5)
+    xn = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)
+    ref = 0.5 * ((xn.bfloat16().float() * nw.float()).bfloat16().float() @ w.float().t()) + res.float()
+    assert (y.float() - ref).abs().max() <= 0.02 * ref.abs().max() + 2e-2
+
+
+def test_gemv_swiglu_and_lora():
+    nat = _nat()
+    torch.manual_seed(9)
+    M, K, I, r = 5, 1024, 3072, 16
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(2 * I, K, device="cuda") * K ** -0.5).bfloat16()
+    a = (torch.randn(2 * r, K, device="cuda") * K ** -0.5).bfloat16()
+    b = torch.randn(2 * I, r, device="cuda") * 0.1
+    scale = 2.0
+    t = nat.gemv(x, a, alpha=scale)
+    assert (t.float() - scale * (x.float() @ a.float().t())).abs().max() < 0.05
+    y = nat.gemv(x, w, swiglu=True, t=t, lora_b=b, r=r, seg_sizes=(I, I))
+    full = x.float() @ w.float().t()
+    full[:, :I] += t.float()[:, :r] @ b[:I].t()
+    full[:, I:] += t.float()[:, r:2 * r] @ b[I:].t()
+    ref = torch.nn.functional.silu(full[:, :I]) * full[:, I:]
+    assert (y.float() - ref).abs().max() <= 0.03 * ref.abs().max() + 2e-2
+    # stacked q/k/v style segments without swiglu
+    segs = (2048, 1024, 1024)
+    w3 = (torch.randn(sum(segs), K, device="cuda") * K ** -0.5).bfloat16()
+    a3 = (torch.randn(3 * r, K, device="cuda") * K ** -0.5).bfloat16()
+    b3 = torch.randn(sum(segs), r, device="cuda") * 0.1
+    t3 = nat.gemv(x, a3, alpha=scale)
+    y3 = nat.gemv(x, w3, t=t3, lora_b=b3, r=r, seg_sizes=segs)
+    ref3 = x.float() @ w3.float().t()
+    o = 0
+    for i, sz in enumerate(segs):
+        ref3[:, o:o + sz] += t3.float()[:, i * r:(i + 1) * r] @ b3[o:o + sz].t()
+        o += sz
+    assert (y3.float() - ref3).abs().max() <= 0.03 * ref3.abs().max() + 2e-2
