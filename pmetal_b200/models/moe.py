@@ -48,10 +48,16 @@ class SparseMoeBlock(nn.Module):
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         cfg = self.cfg
-        w, idx = route_topk(F.linear(x, self.router), cfg.num_experts_per_tok, cfg.norm_topk_prob)
+        logits = F.linear(x, self.router)
+        eng = getattr(self, "ep_engine", None)
+        if eng is not None and x.is_cuda and not torch.is_grad_enabled() and x.shape[0] * eng.k <= eng.max_rows:
+            # fused routing + (expert-parallel) dispatch + grouped GEMMs + combine (parallel/ep.py)
+            out = eng.forward(x.to(torch.bfloat16), logits).to(x.dtype)
+            return out if residual is None else out + residual
+        w, idx = route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
         if self.ep_group is not None:
-            from ..parallel.ep import ep_moe_forward
-            out = ep_moe_forward(self, x, w, idx)
+            from ..parallel.ep import ep_moe_forward_nccl
+            out = ep_moe_forward_nccl(self, x, w, idx)
         else:
             out = self.experts_forward(x, w, idx)
         return out if residual is None else out + residual
