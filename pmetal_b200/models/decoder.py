@@ -79,8 +79,9 @@ class FusedLinear(nn.Module):
                     mask_a[i * r:(i + 1) * r] = 1
                     mask_b[o:o + sz] = 1
                 o += sz
-            self.lora_a.register_hook(lambda g, m=mask_a: g * m)
-            self.lora_b.register_hook(lambda g, m=mask_b: g * m)
+            # the fused backward accumulates straight into .grad and hands autograd None
+            self.lora_a.register_hook(lambda g, m=mask_a: None if g is None else g * m)
+            self.lora_b.register_hook(lambda g, m=mask_b: None if g is None else g * m)
 
     def seg_slice(self, name: str) -> Tuple[int, slice]:
         i = self.seg_names.index(name)
@@ -119,7 +120,7 @@ class FusedLinear(nn.Module):
 
     def gemv_ok(self, m: int) -> bool:
         """Decode fast path: a few rows, plain bf16 weight, no bias."""
-        return (m <= 16 and self.bias is None and getattr(self, "qweight", None) is None and self.weight.is_cuda
+        return (m <= 8 and self.bias is None and getattr(self, "qweight", None) is None and self.weight.is_cuda
                 and self.weight.dtype == torch.bfloat16 and not self.weight.requires_grad and self.in_features % 8 == 0)
 
     def gemv_forward(self, x: torch.Tensor, norm_w=None, eps: float = 1e-6, residual=None, swiglu: bool = False):
@@ -331,7 +332,7 @@ class DecoderLM(nn.Module):
         native = ops.use_native(x) and d == 128
         rope = ops.rope_table(meta.positions, d, cfg.rope_theta, cfg.rope_scale)
         T = x.shape[0]
-        skinny = native and T <= 16
+        skinny = native and T <= 8
         for li, layer in enumerate(self.layers):
             at = layer.self_attn
             if skinny and isinstance(layer.mlp, MLP) and at.qkv_proj.gemv_ok(T) and layer.mlp.gate_up_proj.gemv_ok(T):
@@ -365,7 +366,7 @@ class DecoderLM(nn.Module):
             last = (meta.q_start + meta.q_lens - 1).long()
             x = x[last]               # RMSNorm is per row, so selecting rows first is equivalent
         head = self.head_weight()
-        if (skinny and not return_hidden and x.shape[0] <= 16 and cfg.final_logit_softcap <= 0
+        if (skinny and not return_hidden and x.shape[0] <= 8 and cfg.final_logit_softcap <= 0
                 and head.dtype == torch.bfloat16 and not head.requires_grad):
             from ..ops import native as nat
             return nat.gemv(x.contiguous(), head, self.norm, cfg.rms_norm_eps)      # final norm fused into the head

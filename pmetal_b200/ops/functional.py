@@ -278,10 +278,8 @@ def causal_lm_loss(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Ten
 # --------------------------------------------------------------------------- grouped expert MLP
 def grouped_mlp(xs: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
     """Rows of ``xs`` are grouped by expert (``offsets`` [E+1]); returns down_e(swiglu(gate_up_e(x))) per row."""
-    if use_native(xs) and not gate_up.requires_grad and not torch.is_grad_enabled():
-        nat = _native()
-        h = nat.grouped_gemm(xs, gate_up, offsets)
-        return nat.grouped_gemm(nat.swiglu_fwd(h), down, offsets)
+    # Library path (training and the oracle). Inference goes through parallel.ep.FusedExpertMoE, whose grouped tcgen05
+    # GEMMs also do the routing sort, SwiGLU and the weighted combine.
     out = torch.empty(xs.shape[0], down.shape[1], dtype=xs.dtype, device=xs.device)
     off = offsets.tolist()
     for e in range(gate_up.shape[0]):

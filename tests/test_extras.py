@@ -1,0 +1,97 @@
+"""Library-level extras: 8-bit Adam, schedule-free AdamW, parameter groups, GaLore, NEFTune, mHC, gated delta-net."""
+import math
+
+import pytest
+import torch
+
+from pmetal_b200.lora.galore import GaLoreProjector, neftune_noise
+from pmetal_b200.models import gdn, mhc
+from pmetal_b200.trainer.extra_optimizers import Adam8bit, ScheduleFreeAdamW, build_param_groups
+
+
+def _quadratic(opt_cls, steps=200, **kw):
+    torch.manual_seed(0)
+    w = torch.nn.Parameter(torch.randn(8192))
+    target = torch.randn(8192)
+    opt = opt_cls([w], **kw)
+    for _ in range(steps):
+        opt.zero_grad()
+        loss = ((w - target) ** 2).mean()
+        loss.backward()
+        opt.step()
+    return float(((w - target) ** 2).mean().detach()), opt
+
+
+def test_adam8bit_tracks_adam_and_saves_memory():
+    l8, opt = _quadratic(Adam8bit, lr=0.05)
+    lref, _ = _quadratic(torch.optim.Adam, lr=0.05)
+    assert l8 < 0.05 and abs(l8 - lref) < 0.05
+    assert opt.state_bytes() < 8192 * 8 * 0.3          # vs two fp32 moments
+
+
+def test_schedule_free_converges_and_eval_swaps():
+    loss, opt = _quadratic(ScheduleFreeAdamW, lr=0.1, steps=300)
+    assert loss < 0.05
+    p = opt.param_groups[0]["params"][0]
+    y = p.detach().clone()
+    opt.eval()
+    x = p.detach().clone()
+    opt.train()
+    assert torch.allclose(p, y, atol=1e-5) and not torch.equal(x, y)
+
+
+def test_param_groups():
+    m = torch.nn.ModuleDict({"embed_tokens": torch.nn.Embedding(4, 4), "norm": torch.nn.LayerNorm(4), "lin": torch.nn.Linear(4, 4)})
+    named = list(m.named_parameters()) + [("layers.0.q_proj.lora_b", torch.nn.Parameter(torch.zeros(2, 2)))]
+    groups = {g["name"]: g for g in build_param_groups(named, 1e-3, 0.1, 5e-5, 16.0)}
+    assert groups["embedding"]["lr"] == 5e-5 and groups["no_decay"]["weight_decay"] == 0.0
+    assert groups["lora_b"]["lr"] == pytest.approx(1.6e-2) and groups["regular"]["weight_decay"] == 0.1
+
+
+def test_galore_and_neftune():
+    torch.manual_seed(0)
+    g = torch.randn(64, 8) @ torch.randn(8, 256)          # rank-8 gradient
+    pr = GaLoreProjector(rank=8, update_gap=10, scale=1.0)
+    low = pr.project(g)
+    assert low.shape == (8, 256)
+    assert torch.allclose(pr.project_back(low), g, atol=1e-3)
+    basis = pr.ortho.clone()
+    for _ in range(9):
+        pr.project(g + 0.01)
+    assert torch.equal(basis, pr.ortho)
+    pr.project(torch.randn(64, 256))
+    assert not torch.equal(basis, pr.ortho)               # refreshed at the gap
+    e = torch.zeros(2, 10, 16)
+    n = neftune_noise(e, 5.0)
+    assert n.abs().max() <= 5.0 / math.sqrt(160) + 1e-6 and n.abs().max() > 0
+    assert torch.equal(neftune_noise(e, 5.0, training=False), e)
+
+
+def test_mhc_sinkhorn_and_layer():
+    torch.manual_seed(0)
+    m = mhc.sinkhorn_knopp(torch.randn(4, 4), 50)
+    assert torch.allclose(m.sum(-1), torch.ones(4), atol=1e-4) and torch.allclose(m.sum(-2), torch.ones(4), atol=1e-4)
+    layer = mhc.MhcLayer(4)
+    x = torch.randn(5, 8)
+    xs = mhc.expand_streams(x, 4)
+    out = layer(xs, lambda h: torch.zeros_like(h))
+    assert torch.allclose(mhc.collapse_streams(out), x, atol=1e-4)      # doubly stochastic mixing keeps the mean
+    out = layer(xs, lambda h: h * 2)
+    assert torch.allclose(mhc.collapse_streams(out), x + 2 * x, atol=1e-4)     # pre sums to 1, post starts at 1
+    dyn = mhc.MhcLayer(4, dynamic=True, hidden=8)
+    o = dyn(xs, lambda h: h)
+    o.sum().backward()
+    assert dyn.dynamic.weight.grad is not None and o.shape == xs.shape
+
+
+def test_gdn_chunked_equals_recurrent():
+    torch.manual_seed(0)
+    T, H, dk, dv = 150, 3, 16, 24
+    q, k = torch.randn(T, H, dk) * 0.3, torch.nn.functional.normalize(torch.randn(T, H, dk), dim=-1)
+    v = torch.randn(T, H, dv)
+    g, beta = torch.rand(T, H) * 0.3 + 0.7, torch.rand(T, H)
+    y1, s1 = gdn.gdn_recurrent(q, k, v, g, beta)
+    y2, s2 = gdn.gdn_chunked(q, k, v, g, beta, chunk=32)
+    assert torch.allclose(y1, y2, atol=1e-4) and torch.allclose(s1, s2, atol=1e-4)
+    y3, s3 = gdn.gdn_chunked(q[100:], k[100:], v[100:], g[100:], beta[100:], S0=gdn.gdn_recurrent(q[:100], k[:100], v[:100], g[:100], beta[:100])[1])
+    assert torch.allclose(y3, y1[100:], atol=1e-4)
