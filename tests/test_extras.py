@@ -95,3 +95,57 @@ def test_gdn_chunked_equals_recurrent():
     assert torch.allclose(y1, y2, atol=1e-4) and torch.allclose(s1, s2, atol=1e-4)
     y3, s3 = gdn.gdn_chunked(q[100:], k[100:], v[100:], g[100:], beta[100:], S0=gdn.gdn_recurrent(q[:100], k[:100], v[:100], g[:100], beta[:100])[1])
     assert torch.allclose(y3, y1[100:], atol=1e-4)
+
+
+def test_turboquant_rotation_codebook_and_attention():
+    from pmetal_b200.models import turboquant as tq
+    torch.manual_seed(0)
+    x = torch.randn(7, 128)
+    assert torch.allclose(tq.fwht(tq.fwht(x)) / 128, x, atol=1e-4)
+    c, t = tq.lloyd_max_normal(2)
+    assert torch.allclose(c, torch.tensor([-1.5104, -0.4528, 0.4528, 1.5104]), atol=2e-3) and t.numel() == 3
+    c1, _ = tq.lloyd_max_normal(1)
+    assert torch.allclose(c1.abs(), torch.full((2,), math.sqrt(2 / math.pi)), atol=1e-3)
+    codes = torch.randint(0, 4, (5, 128), dtype=torch.uint8)
+    assert torch.equal(tq.unpack_bits(tq.pack_bits(codes, 2), 2, 128), codes)
+    T = tq.TurboQuant(128, bits=4)
+    assert torch.allclose(T.unrotate(T.rotate(x)), x, atol=1e-4)
+    keys = torch.randn(300, 128) * 2
+    ck = T.encode(keys)
+    rel = (T.decode(ck) - keys).norm() / keys.norm()
+    assert rel < 0.12 and T.compression_ratio(ck, 300) > 3.8
+    rel2 = (tq.TurboQuant(128, bits=2).decode(tq.TurboQuant(128, bits=2).encode(keys)) - keys).norm() / keys.norm()
+    assert rel < rel2 < 0.4
+    q = torch.randn(4, 128)
+    s = T.scores(q, ck)
+    assert torch.allclose(s, q @ keys.t(), atol=0.15 * (q @ keys.t()).abs().max())
+    vals = torch.randn(300, 128)
+    out = T.attention(q, ck, T.encode(vals), 128 ** -0.5)
+    ref = torch.softmax(q @ keys.t() * 128 ** -0.5, -1) @ vals
+    assert torch.nn.functional.cosine_similarity(out, ref, dim=-1).min() > 0.9
+    # QJL residual sketch: inner-product estimates stay unbiased on average over many keys at 2 bits
+    Tq = tq.TurboQuant(128, bits=2, qjl=True, seed=1)
+    cq = Tq.encode(keys)
+    err_q = (Tq.scores(q, cq) - q @ keys.t()).mean().abs()
+    assert err_q < 0.1 and cq.qjl is not None
+
+
+def test_tuner_cache(tmp_path):
+    from pmetal_b200.utils.tuna import Tuner
+    import time
+    p = str(tmp_path / "t" / "tuna.json")
+    t = Tuner(p, iters=3, warmup=1)
+    calls = []
+
+    def run(c):
+        calls.append(c)
+        if c == "bad":
+            raise ValueError("invalid")
+        time.sleep(0.004 if c == "slow" else 0.0005)
+    key = Tuner.make_key("gemm", 128, 4096, 1024)
+    assert t.tune(key, ["slow", "fast", "bad"], run) == "fast"
+    n = len(calls)
+    assert Tuner(p).tune(key, ["slow", "fast"], run) == "fast" and len(calls) == n      # served from the cache file
+    assert Tuner(p).lookup(key) == "fast"
+    with pytest.raises(RuntimeError):
+        t.tune("other", ["bad"], run)
