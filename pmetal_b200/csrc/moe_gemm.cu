@@ -6,9 +6,12 @@
 //   ep_prepare_kernel   publishes "my sorted tokens and offsets are ready", waits for every peer's flag (bounded),
 //                       reads the peers' offsets and builds the tile lists: one tile per 128 rows of each
 //                       (source rank, local expert) segment.
-//   moe_gemm_kernel #1  gate/up projection: the TMA producer pulls every tile's token rows straight out of the
-//                       *source rank's* sorted buffer (non-multicast TMA through a per-rank tensor map) -- this is
-//                       the dispatch all-to-all -- and the epilogue applies SwiGLU, writing h locally.
+//   moe_gemm_kernel #1  gate/up projection with the dispatch all-to-all inside: at kernel start the four epilogue warps
+//                       of every CTA pull their share of the tiles' token rows out of the *source ranks'* sorted
+//                       buffers (16-byte peer loads over NVLink) into a local staging buffer and publish a flag per
+//                       tile; the TMA producer waits on a tile's flag before loading it. Every token row crosses
+//                       NVLink once (peer memory is not cached in the local L2, so reading remote rows in place would
+//                       re-fetch them once per column block). The epilogue applies SwiGLU, writing h locally.
 //   moe_gemm_kernel #2  down projection on h; the epilogue stores every output row straight into the *source rank's*
 //                       result buffer at the row's sorted position (16-byte peer stores) -- this is the combine
 //                       all-to-all. The launch ends only after every peer has signalled that its pushes are complete,
@@ -43,6 +46,8 @@ struct MoeTile {
   int expert;     // local expert index (selects the weight rows)
   int out_dst;    // rank whose buffer receives the output rows
   int out_row0;   // first output row there
+  int c_src;      // stage-in: rank whose sorted buffer holds the rows (copied to a_row0 of the local staging buffer)
+  int c_row0;     // stage-in: first row there
 };
 
 struct MoeMaps {
@@ -62,6 +67,11 @@ struct MoeGemmParams {
   uint32_t* pads[kEpMaxRanks];
   unsigned long long timeout_ns;
   int* status;
+  // stage-in (gate/up launch): peers' sorted token buffers, the local staging buffer the A map covers, per-tile flags
+  int stage_in;
+  const __nv_bfloat16* x_peer[kEpMaxRanks];
+  __nv_bfloat16* xin;
+  uint32_t* tile_ready;
 };
 
 __device__ __forceinline__ uint32_t ep_ld_acquire(const uint32_t* p) {
@@ -119,8 +129,8 @@ __global__ void ep_prepare_kernel(const int* const* offsets, uint32_t* const* pa
           for (int r0 = lo; r0 < hi; r0 += kBM) {
             if (n >= max_tiles) break;
             const int rows = min(kBM, hi - r0);
-            tiles1[n] = MoeTile{src, r0, rows, e, rank, hrow};
-            tiles2[n] = MoeTile{rank, hrow, rows, e, src, r0};
+            tiles1[n] = MoeTile{rank, hrow, rows, e, rank, hrow, src, r0};
+            tiles2[n] = MoeTile{rank, hrow, rows, e, src, r0, rank, hrow};
             hrow += kBM;
             ++n;
           }
@@ -185,6 +195,25 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
         const MoeTile t = p.tiles[w / n_blocks];
         const int nb = w % n_blocks;
         const int b_row = t.expert * p.N + nb * kEpBN;
+        if (p.stage_in) {   // the tile's rows must have landed in the staging buffer
+          const uint32_t* flag = p.tile_ready + w / n_blocks;
+          const unsigned long long t0 = globaltimer_ns();
+          uint32_t spins = 0, v;
+          do {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (static_cast<int32_t>(v - epoch) >= 0) break;
+            if ((++spins & 31u) == 0u) {
+              if (*abort_flag || globaltimer_ns() - t0 > p.timeout_ns) {
+                atomicCAS(p.status, 0, kStatusEpPeer);
+                *abort_flag = 1;
+                ok = false;
+              }
+              __nanosleep(64);
+            }
+          } while (ok);
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = 0; kb < nk; ++kb, ++it) {
           const int s = it % kEpStages;
           if (!mbar_wait(&empty_bar[s], ((it / kEpStages) & 1) ^ 1, abort_flag, p.status, kTimeoutProducer)) {
@@ -225,6 +254,30 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
     }
   } else {
     const int q = warp & 3;
+    if (p.stage_in) {
+      // ---- dispatch: copy this CTA's share of the tiles' rows from their source ranks into the staging buffer
+      const int t128 = threadIdx.x - 64;
+      const int vec_per_row = p.K / 8;
+      const int n_t = *p.n_tiles;
+      for (int ti = blockIdx.x; ti < n_t; ti += gridDim.x) {
+        const MoeTile t = p.tiles[ti];
+        const __nv_bfloat16* from = p.x_peer[t.c_src] + static_cast<long long>(t.c_row0) * p.K;
+        __nv_bfloat16* to = p.xin + static_cast<long long>(t.a_row0) * p.K;
+        const int n_vec = t.rows * vec_per_row;
+        for (int i0 = t128; i0 < n_vec; i0 += 128 * 4) {
+          uint4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (i0 + u * 128 < n_vec) v[u] = reinterpret_cast<const uint4*>(from)[i0 + u * 128];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (i0 + u * 128 < n_vec) reinterpret_cast<uint4*>(to)[i0 + u * 128] = v[u];
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (t128 == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.tile_ready + ti), "r"(epoch) : "memory");
+      }
+    }
     uint32_t acc_it = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++acc_it) {
       const MoeTile t = p.tiles[w / n_blocks];
@@ -343,10 +396,13 @@ extern "C" int pm_ep_prepare(const unsigned long long* offset_ptrs, const unsign
 }
 
 // a_ptrs[r]: A buffer of map index r ([a_rows, K], row stride lda); w: [e_loc * N, K]; out_ptrs[r]: output base of rank r.
+// copy_src_ptrs (gate/up launch): rank r's sorted token buffer [*, K] (row stride K) that tiles are staged in from;
+// tile_ready: uint32 [max_tiles], zero-initialised once. Both null for the down projection.
 extern "C" int pm_moe_gemm(const unsigned long long* a_ptrs, int a_rows, int lda, const void* w, int ldw, int e_loc,
                            const unsigned long long* out_ptrs, int ldd, const void* tiles, const int* n_tiles,
                            int max_tiles, int N, int K, int swiglu, int rank, int world, int signal_pushed,
-                           const unsigned long long* pad_ptrs, double timeout_s, int* status, cudaStream_t st) {
+                           const unsigned long long* pad_ptrs, const unsigned long long* copy_src_ptrs, void* tile_ready,
+                           double timeout_s, int* status, cudaStream_t st) {
   if (world < 1 || world > kEpMaxRanks || rank < 0 || rank >= world) return -1;
   if (N <= 0 || K <= 0 || (N % 8) || (ldd % 8) || (swiglu && (N % 256))) return -2;
   MoeMaps maps;
@@ -363,6 +419,15 @@ extern "C" int pm_moe_gemm(const unsigned long long* a_ptrs, int a_rows, int lda
   p.n_tiles = n_tiles;
   p.N = N; p.K = K; p.swiglu = swiglu; p.ldd = ldd; p.rank = rank; p.world = world;
   p.signal_pushed = signal_pushed;
+  // stage-in: a_ptrs[rank] is the local staging buffer that all A maps cover; rows come from copy_src_ptrs[r]
+  p.stage_in = copy_src_ptrs != nullptr;
+  if (p.stage_in) {
+    if (!tile_ready || (K % 8)) return -3;
+    for (int r = 0; r < kEpMaxRanks; ++r)
+      p.x_peer[r] = reinterpret_cast<const __nv_bfloat16*>(copy_src_ptrs[r < world ? r : rank]);
+    p.xin = reinterpret_cast<__nv_bfloat16*>(a_ptrs[rank]);
+    p.tile_ready = static_cast<uint32_t*>(tile_ready);
+  }
   p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
   p.status = status;
   const size_t smem = static_cast<size_t>(kEpStages) * (kBM * kBK * 2 + kEpBN * kBK * 2) + 1024 + 256;

@@ -2,10 +2,12 @@
 //
 //   mode 0  all-gather -> GEMM (column-parallel):  Y[M, N_loc] = concat_r(X_r)[M, K] * W_loc[N_loc, K]^T
 //           X is sharded by rows across ranks (sequence-parallel activations, M_r = M / world rows each, in
-//           symmetric memory). The TMA producer reads each A tile straight from the owning rank's buffer (a
-//           non-multicast TMA load through a per-rank tensor map), starting with the local shard and walking the
-//           ranks in ring order, so no gathered copy of X is ever materialised and remote traffic overlaps the
-//           MMAs of earlier tiles.
+//           symmetric memory). The kernel starts on the tiles of its own shard at once; meanwhile the four epilogue
+//           warps of every CTA pull the remote shards, 128-row block by block, over NVLink into a local buffer with
+//           16-byte peer loads and publish a per-block flag; the TMA producer reaches the remote row blocks last and
+//           waits on those flags. Each remote byte crosses NVLink once (reading remote tiles directly would re-fetch
+//           a row block once per column tile, since peer memory is not cached in the local L2), and the transfer
+//           overlaps the MMAs of the local tiles.
 //   mode 1  GEMM -> reduce-scatter (row-parallel): Y_r[M_r, N] = sum_q ( X_q[M, K_loc] * W_q[N, K_loc]^T )[rows of r]
 //           Each rank computes all M rows of its partial product; the epilogue pushes every finished tile as bf16
 //           straight into the owner's staging slot [parity][source rank] with 16-byte peer stores (remote owners
@@ -37,9 +39,18 @@ constexpr int kTpArrive = 25;   // local CTA arrival counter (phase 1)
 constexpr int kTpArrive2 = 26;  // local CTA arrival counter (phase 2)
 
 struct TpMaps {
-  CUtensorMap a[kTpMaxRanks];   // mode 0: per-rank X shard; mode 1: a[0] = local X
+  CUtensorMap a[2];   // mode 0: a[0] = local X shard, a[1] = gathered buffer [M, K]; mode 1: a[0] = local X
   CUtensorMap b;
 };
+
+__device__ __forceinline__ uint32_t tp_ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tp_st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 struct TpParams {
   int mode, rank, world;
@@ -51,6 +62,12 @@ struct TpParams {
   uint32_t* pads[kTpMaxRanks];
   unsigned long long timeout_ns;
   int* status;
+  // mode 0 stage-in: peers' shards (raw pointers, row stride ldx), the local gathered buffer [M, K] that the remote
+  // tiles are read from, and one flag per 128-row block of it
+  const __nv_bfloat16* x_peer[kTpMaxRanks];
+  int ldx;
+  __nv_bfloat16* gathered;
+  uint32_t* blk_ready;
 };
 
 __device__ __forceinline__ uint32_t tp_ld_acquire(const uint32_t* p) {
@@ -139,20 +156,31 @@ tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
 
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t it = 0, seen = 1u << p.rank;   // ranks whose ready flag has been observed
+      uint32_t it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
         int owner, mb, nb;
         tp_tile(p, w, n_tiles, tpr, &owner, &mb, &nb);
-        const CUtensorMap* ma = (p.mode == 0) ? &maps.a[owner] : &maps.a[0];
-        const int m0 = (p.mode == 0) ? mb * kBM : (owner * tpr + mb) * kBM;
-        if (p.mode == 0 && !(seen & (1u << owner))) {
-          if (!tp_wait_flag(my_pad + kTpReady + owner, epoch, p.timeout_ns, p.status)) {
-            *abort_flag = 1;
-            ok = false;
-            break;
+        const bool remote = p.mode == 0 && owner != p.rank;
+        const CUtensorMap* ma = remote ? &maps.a[1] : &maps.a[0];
+        const int m0 = (p.mode == 0) ? (remote ? owner * p.rows_per_rank + mb * kBM : mb * kBM) : (owner * tpr + mb) * kBM;
+        if (remote) {   // the row block must have been copied into the gathered buffer (by some CTA's copy warps)
+          const uint32_t* flag = p.blk_ready + owner * tpr + mb;
+          const unsigned long long t0 = globaltimer_ns();
+          uint32_t spins = 0;
+          while (static_cast<int32_t>(tp_ld_acquire_gpu(flag) - epoch) < 0 && ok) {
+            if ((++spins & 31u) == 0u) {
+              if (*abort_flag || globaltimer_ns() - t0 > p.timeout_ns) {
+                atomicCAS(p.status, 0, kStatusTpPeer);
+                *abort_flag = 1;
+                ok = false;
+              }
+              __nanosleep(64);
+            }
           }
-          seen |= 1u << owner;
+          if (!ok) break;
+          // order the flag read (generic proxy) before the TMA reads of the copied rows (async proxy)
+          asm volatile("fence.proxy.async.global;" ::: "memory");
         }
         for (int kb = 0; kb < nk; ++kb, ++it) {
           const int s = it % kTpStages;
@@ -195,6 +223,43 @@ tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
     }
   } else {
     const int q = warp & 3;
+    if (p.mode == 0 && p.world > 1) {
+      // ---- stage-in: this CTA's share of the remote row blocks, pulled over NVLink by its 128 epilogue threads
+      const int t128 = threadIdx.x - 64;
+      const int vec_per_row = p.K / 8;
+      bool copy_ok = true;
+      for (int s = 1; s < p.world && copy_ok; ++s) {
+        const int src = (p.rank + s) % p.world;
+        if (t128 == 0 && !tp_wait_flag(my_pad + kTpReady + src, epoch, p.timeout_ns, p.status)) *abort_flag = 1;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*abort_flag) { copy_ok = false; break; }
+        for (int b = 0; b < tpr; ++b) {
+          if ((s * tpr + b) % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
+          const __nv_bfloat16* from = p.x_peer[src] + static_cast<long long>(b) * kBM * p.ldx;
+          __nv_bfloat16* to = p.gathered + (static_cast<long long>(src) * p.rows_per_rank + b * kBM) * p.K;
+          const int n_vec = kBM * vec_per_row;
+          for (int i0 = t128; i0 < n_vec; i0 += 128 * 4) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i = i0 + u * 128;
+              if (i < n_vec) {
+                const int r = i / vec_per_row, c = i - r * vec_per_row;
+                v[u] = *reinterpret_cast<const uint4*>(from + static_cast<long long>(r) * p.ldx + c * 8);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i = i0 + u * 128;
+              if (i < n_vec) *reinterpret_cast<uint4*>(to + static_cast<long long>(i) * 8) = v[u];
+            }
+          }
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (t128 == 0) tp_st_release_gpu(p.blk_ready + src * tpr + b, epoch);
+        }
+      }
+    }
     uint32_t acc_it = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++acc_it) {
       int owner, mb, nb;
@@ -330,12 +395,13 @@ using namespace pm;
 
 // mode 0: x_ptrs[r] = rank r's X shard [rows_per_rank, K] (ldx), w = W_loc [N, K] (ldw), out = Y [M, ldd].
 // mode 1: x_ptrs[rank] = local X [M, K] (ldx), w = W_loc [N, K], stage_ptrs[r] = rank r's staging buffer,
-//         out = Y_r [rows_per_rank, ldd]. K and N are the local extents. Returns 0, a negative argument error,
-//         or a CUDA error code.
+//         out = Y_r [rows_per_rank, ldd]. K and N are the local extents. mode 0 also takes `gathered` (local bf16
+//         [M, K] scratch) and `blk_ready` (uint32 [M / 128], zero-initialised once). Returns 0, a negative argument
+//         error, or a CUDA error code.
 extern "C" int pm_tp_gemm(int mode, const unsigned long long* x_ptrs, int ldx, const void* w, int ldw, void* out,
                           int ldd, const unsigned long long* stage_ptrs, const unsigned long long* pad_ptrs, int rank,
-                          int world, int M, int N, int K, double timeout_s, int max_ctas, int* status,
-                          cudaStream_t stream) {
+                          int world, int M, int N, int K, void* gathered, void* blk_ready, double timeout_s, int max_ctas,
+                          int* status, cudaStream_t stream) {
   if (mode != 0 && mode != 1) return -1;
   if (world < 1 || world > kTpMaxRanks || rank < 0 || rank >= world) return -2;
   if (M <= 0 || N <= 0 || K <= 0 || M % world || (M / world) % kBM) return -3;
@@ -348,12 +414,20 @@ extern "C" int pm_tp_gemm(int mode, const unsigned long long* x_ptrs, int ldx, c
   p.status = status;
   int rc;
   for (int r = 0; r < kTpMaxRanks; ++r) {
-    const int src = (mode == 0) ? (r < world ? r : rank) : rank;
-    const int rows = (mode == 0) ? p.rows_per_rank : M;
-    if ((rc = operand_map(&maps.a[r], reinterpret_cast<const void*>(x_ptrs[src]), 0, rows, K, ldx, kBM))) return rc * 10 - 5;
-    p.pads[r] = reinterpret_cast<uint32_t*>(pad_ptrs[r < world ? r : rank]);
-    p.stage[r] = (mode == 1) ? reinterpret_cast<__nv_bfloat16*>(stage_ptrs[r < world ? r : rank]) : nullptr;
+    const int rr = r < world ? r : rank;
+    p.pads[r] = reinterpret_cast<uint32_t*>(pad_ptrs[rr]);
+    p.stage[r] = (mode == 1) ? reinterpret_cast<__nv_bfloat16*>(stage_ptrs[rr]) : nullptr;
+    p.x_peer[r] = reinterpret_cast<const __nv_bfloat16*>(x_ptrs[rr]);
   }
+  p.ldx = ldx;
+  p.gathered = static_cast<__nv_bfloat16*>(gathered);
+  p.blk_ready = static_cast<uint32_t*>(blk_ready);
+  if (mode == 0 && world > 1 && (!gathered || !blk_ready || (K % 8))) return -7;
+  if ((rc = operand_map(&maps.a[0], reinterpret_cast<const void*>(x_ptrs[rank]), 0, mode == 0 ? p.rows_per_rank : M, K, ldx,
+                        kBM)))
+    return rc * 10 - 5;
+  maps.a[1] = maps.a[0];
+  if (mode == 0 && world > 1 && (rc = operand_map(&maps.a[1], gathered, 0, M, K, K, kBM))) return rc * 10 - 5;
   if ((rc = operand_map(&maps.b, w, 0, N, K, ldw, kTpBN))) return rc * 10 - 6;
   const size_t smem = static_cast<size_t>(kTpStages) * (kBM * kBK * 2 + kTpBN * kBK * 2) + 1024 + 256;
   static bool configured = false;

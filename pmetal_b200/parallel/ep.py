@@ -123,8 +123,11 @@ class FusedExpertMoE:
         self.h = torch.empty(self.max_tiles * 128, self.I, dtype=torch.bfloat16, device=dev)
         arr = ctypes.c_ulonglong * self.world
         self._h_ptrs = arr(*([self.h.data_ptr()] * self.world))
-        self.tiles1 = torch.zeros(self.max_tiles * 6, dtype=torch.int32, device=dev)
-        self.tiles2 = torch.zeros(self.max_tiles * 6, dtype=torch.int32, device=dev)
+        self.xin = torch.empty(self.max_tiles * 128, self.H, dtype=torch.bfloat16, device=dev)     # staged-in token rows
+        self._xin_ptrs = arr(*([self.xin.data_ptr()] * self.world))
+        self.tile_ready = torch.zeros(self.max_tiles, dtype=torch.int32, device=dev)
+        self.tiles1 = torch.zeros(self.max_tiles * 8, dtype=torch.int32, device=dev)
+        self.tiles2 = torch.zeros(self.max_tiles * 8, dtype=torch.int32, device=dev)
         self.counts = torch.zeros(2, dtype=torch.int32, device=dev)
         self.ptr_scratch = torch.zeros(16, dtype=torch.int64, device=dev)
         if self.distributed:
@@ -163,18 +166,20 @@ class FusedExpertMoE:
                                       ctypes.c_int(self.e_loc), native._p(self.tiles1), native._p(self.tiles2),
                                       ctypes.c_int(self.max_tiles), native._p(self.counts), ctypes.c_double(self.timeout_s),
                                       native._p(st), native._p(self.ptr_scratch), native._stream()), "pm_ep_prepare")
-        native._chk(lib.pm_moe_gemm(self._x_ptrs, ctypes.c_int(self.max_rows), ctypes.c_int(self.H), native._p(self.w1),
-                                    ctypes.c_int(self.H), ctypes.c_int(self.e_loc), self._h_ptrs, ctypes.c_int(self.I),
-                                    native._p(self.tiles1), native._p(self.counts), ctypes.c_int(self.max_tiles),
-                                    ctypes.c_int(2 * self.I), ctypes.c_int(self.H), ctypes.c_int(1), ctypes.c_int(self.rank),
-                                    ctypes.c_int(self.world), ctypes.c_int(0), self._pad_ptrs,
+        native._chk(lib.pm_moe_gemm(self._xin_ptrs, ctypes.c_int(self.max_tiles * 128), ctypes.c_int(self.H),
+                                    native._p(self.w1), ctypes.c_int(self.H), ctypes.c_int(self.e_loc), self._h_ptrs,
+                                    ctypes.c_int(self.I), native._p(self.tiles1), native._p(self.counts),
+                                    ctypes.c_int(self.max_tiles), ctypes.c_int(2 * self.I), ctypes.c_int(self.H),
+                                    ctypes.c_int(1), ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(0),
+                                    self._pad_ptrs, self._x_ptrs, native._p(self.tile_ready),
                                     ctypes.c_double(self.timeout_s), native._p(st), native._stream()), "pm_moe_gemm")
         native._chk(lib.pm_moe_gemm(self._h_ptrs, ctypes.c_int(self.max_tiles * 128), ctypes.c_int(self.I),
                                     native._p(self.w2), ctypes.c_int(self.I), ctypes.c_int(self.e_loc), self._z_ptrs,
                                     ctypes.c_int(self.H), native._p(self.tiles2), native._p(self.counts),
                                     ctypes.c_int(self.max_tiles), ctypes.c_int(self.H), ctypes.c_int(self.I), ctypes.c_int(0),
                                     ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(1), self._pad_ptrs,
-                                    ctypes.c_double(self.timeout_s), native._p(st), native._stream()), "pm_moe_gemm")
+                                    None, None, ctypes.c_double(self.timeout_s), native._p(st), native._stream()),
+                    "pm_moe_gemm")
         zz = self.z[: n * self.H].view(n, self.H)
         return native.moe_combine(zz, r["inv"], r["topk_w"], self.k)
 

@@ -40,14 +40,14 @@ class _FusedTpBase:
         torch.cuda.synchronize()
         dist.barrier(self.group)
 
-    def _launch(self, mode, x_ptrs, ldx, w, out, stage_ptrs, M, N, K):
+    def _launch(self, mode, x_ptrs, ldx, w, out, stage_ptrs, M, N, K, gathered=None, blk_ready=None):
         from ..ops import native
         lib = native.lib()
         lib.pm_tp_gemm.restype = ctypes.c_int
         rc = lib.pm_tp_gemm(ctypes.c_int(mode), x_ptrs, ctypes.c_int(ldx), native._p(w), ctypes.c_int(w.stride(0)),
                             native._p(out), ctypes.c_int(out.stride(0)), stage_ptrs, self._pads, ctypes.c_int(self.rank),
                             ctypes.c_int(self.world), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
-                            ctypes.c_double(self.timeout_s), ctypes.c_int(self.max_ctas),
+                            native._p(gathered), native._p(blk_ready), ctypes.c_double(self.timeout_s), ctypes.c_int(self.max_ctas),
                             native._p(native.status_word()), native._stream())
         native._chk(rc, "pm_tp_gemm")
 
@@ -65,6 +65,9 @@ class ColumnParallelLinear(_FusedTpBase):
         self.input_buffer = x.view(rows_per_rank, self.K)
         self._x_ptrs = self._arr(*[int(p) for p in hx.buffer_ptrs])
         self._keep.append(hx)
+        # remote shards are staged into this local buffer by the kernel's copy warps; one flag per 128-row block
+        self.gathered = torch.empty(rows_per_rank * self.world, self.K, dtype=torch.bfloat16, device=weight.device)
+        self.blk_ready = torch.zeros(rows_per_rank * self.world // 128, dtype=torch.int32, device=weight.device)
         self._sync_setup()
 
     def forward(self, x_local: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -72,7 +75,8 @@ class ColumnParallelLinear(_FusedTpBase):
             self.input_buffer.copy_(x_local)
         M = self.rows * self.world
         out = torch.empty(M, self.weight.shape[0], dtype=torch.bfloat16, device=self.weight.device)
-        self._launch(0, self._x_ptrs, self.K, self.weight, out, None, M, self.weight.shape[0], self.K)
+        self._launch(0, self._x_ptrs, self.K, self.weight, out, None, M, self.weight.shape[0], self.K, self.gathered,
+                     self.blk_ready)
         return out
 
     def forward_nccl(self, x_local: torch.Tensor) -> torch.Tensor:
