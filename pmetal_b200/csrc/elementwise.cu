@@ -192,6 +192,59 @@ __global__ void qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, in
   *reinterpret_cast<uint2*>(dst) = ov;
 }
 
+// Decode variant: q heads go to q_out; k heads are normalised, rotated and written straight into the paged key cache
+// at the token's slot; v heads are copied into the value cache. One warp per (token, head) over hq + 2 hkv heads.
+__global__ void qknorm_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, int ld,
+                                         const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+                                         const float* __restrict__ cs, const float* __restrict__ sn,
+                                         __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+                                         __nv_bfloat16* __restrict__ v_cache, const long long* __restrict__ slots, int T,
+                                         int hq, int hkv, float eps) {
+  const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = hq + 2 * hkv;
+  if (gw >= T * heads) return;
+  const int t = gw / heads, hh = gw - t * heads;
+  const long long slot = slots[t];
+  const uint2 raw = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(t) * ld + hh * 128 + lane * 4);
+  if (hh >= hq + hkv) {   // value head: plain copy into the cache
+    if (slot >= 0) *reinterpret_cast<uint2*>(v_cache + (slot * hkv + (hh - hq - hkv)) * 128 + lane * 4) = raw;
+    return;
+  }
+  const bool is_q = hh < hq;
+  const __nv_bfloat16* wv = is_q ? qw : kw;
+  float x[4];
+  {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  }
+  if (wv) {
+    float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / 128.f + eps);
+    const uint2 wr = *reinterpret_cast<const uint2*>(wv + lane * 4);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wr.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wr.y));
+    x[0] *= rs * a.x; x[1] *= rs * a.y; x[2] *= rs * b.x; x[3] *= rs * b.y;
+  }
+  const int j = (lane & 15) * 4;
+  const float4 c = *reinterpret_cast<const float4*>(cs + static_cast<size_t>(t) * 64 + j);
+  const float4 s = *reinterpret_cast<const float4*>(sn + static_cast<size_t>(t) * 64 + j);
+  const float cc[4] = {c.x, c.y, c.z, c.w}, ssn[4] = {s.x, s.y, s.z, s.w};
+  float o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float partner = __shfl_xor_sync(0xffffffffu, x[i], 16);
+    o[i] = (lane < 16) ? (x[i] * cc[i] - partner * ssn[i]) : (x[i] * cc[i] + partner * ssn[i]);
+  }
+  uint2 ov;
+  *reinterpret_cast<__nv_bfloat162*>(&ov.x) = __floats2bfloat162_rn(o[0], o[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&ov.y) = __floats2bfloat162_rn(o[2], o[3]);
+  if (is_q) *reinterpret_cast<uint2*>(q_out + (static_cast<size_t>(t) * hq + hh) * 128 + lane * 4) = ov;
+  else if (slot >= 0) *reinterpret_cast<uint2*>(k_cache + (slot * hkv + (hh - hq)) * 128 + lane * 4) = ov;
+}
+
 __global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
                                        const __nv_bfloat16* __restrict__ qkv, int ld,
                                        const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
@@ -563,6 +616,16 @@ extern "C" int pm_qknorm_rope_fwd(const void* qkv, int ld, const void* qw, const
       static_cast<const __nv_bfloat16*>(qkv), ld, static_cast<const __nv_bfloat16*>(qw),
       static_cast<const __nv_bfloat16*>(kw), cs, sn, static_cast<__nv_bfloat16*>(q_out),
       static_cast<__nv_bfloat16*>(k_out), T, hq, hkv, eps);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_qknorm_rope_cache(const void* qkv, int ld, const void* qw, const void* kw, const float* cs,
+                                    const float* sn, void* q_out, void* k_cache, void* v_cache, const long long* slots,
+                                    int T, int hq, int hkv, float eps, cudaStream_t st) {
+  const long long warps = static_cast<long long>(T) * (hq + 2 * hkv);
+  qknorm_rope_cache_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(qkv), ld, static_cast<const __nv_bfloat16*>(qw),
+      static_cast<const __nv_bfloat16*>(kw), cs, sn, static_cast<__nv_bfloat16*>(q_out),
+      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), slots, T, hq, hkv, eps);
   return PM_LAUNCH_CHECK();
 }
 extern "C" int pm_qknorm_rope_bwd(const void* dq, const void* dk, const void* qkv, int ld, const void* qw,

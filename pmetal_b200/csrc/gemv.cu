@@ -45,7 +45,8 @@ struct GemvParams {
 
 __device__ __forceinline__ float gv_silu(float v) { return v / (1.f + __expf(-v)); }
 
-template <int MR, int C>
+// MR rows of x, C output columns per warp at a time, KU 16-byte weight loads in flight per column and lane.
+template <int MR, int C, int KU, bool SWIGLU>
 __global__ void __launch_bounds__(kGvThreads) gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(16) uint8_t gv_smem[];
   __nv_bfloat16* sx = reinterpret_cast<__nv_bfloat16*>(gv_smem);   // [MR][K] (rows >= M are zero)
@@ -105,46 +106,58 @@ __global__ void __launch_bounds__(kGvThreads) gemv_kernel(const GemvParams p) {
 #pragma unroll
       for (int c = 0; c < C; ++c) { acc[m][c] = 0.f; acc2[m][c] = 0.f; }
     const int n0 = g * C;
-    for (int k = lane * 8; k < K; k += 256) {
-      uint4 wv[C], wv2[C];
+    for (int k0 = lane * 8; k0 < K; k0 += 256 * KU) {
+      // issue every load of this chunk before any arithmetic: the kernel lives on bytes in flight
+      uint4 wv[KU][C], wv2[SWIGLU ? KU : 1][SWIGLU ? C : 1];
 #pragma unroll
-      for (int c = 0; c < C; ++c) {
-        const int n = min(n0 + c, p.N - 1);
-        wv[c] = __ldg(reinterpret_cast<const uint4*>(p.w + static_cast<long long>(n) * p.ldw + k));
-        if (p.swiglu) wv2[c] = __ldg(reinterpret_cast<const uint4*>(p.w + static_cast<long long>(n + p.N) * p.ldw + k));
-      }
-#pragma unroll
-      for (int m = 0; m < MR; ++m) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(sx + m * K + k);
-        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
-        float xf[8];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(x2[e]);
-          xf[2 * e] = f.x;
-          xf[2 * e + 1] = f.y;
-        }
+      for (int u = 0; u < KU; ++u) {
+        const int k = k0 + u * 256;
 #pragma unroll
         for (int c = 0; c < C; ++c) {
-          const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv[c]);
-          float s = 0.f;
+          const int n = min(n0 + c, p.N - 1);
+          if (k < K) {
+            wv[u][c] = __ldg(reinterpret_cast<const uint4*>(p.w + static_cast<long long>(n) * p.ldw + k));
+            if (SWIGLU) wv2[u][c] = __ldg(reinterpret_cast<const uint4*>(p.w + static_cast<long long>(n + p.N) * p.ldw + k));
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < KU; ++u) {
+        const int k = k0 + u * 256;
+        if (k >= K) break;
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(sx + m * K + k);
+          const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+          float xf[8];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(w2[e]);
-            s = fmaf(xf[2 * e], f.x, s);
-            s = fmaf(xf[2 * e + 1], f.y, s);
+            const float2 f = __bfloat1622float2(x2[e]);
+            xf[2 * e] = f.x;
+            xf[2 * e + 1] = f.y;
           }
-          acc[m][c] += s;
-          if (p.swiglu) {
-            const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&wv2[c]);
-            float s2 = 0.f;
+#pragma unroll
+          for (int c = 0; c < C; ++c) {
+            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv[u][c]);
+            float s = 0.f;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float2 f = __bfloat1622float2(u2[e]);
-              s2 = fmaf(xf[2 * e], f.x, s2);
-              s2 = fmaf(xf[2 * e + 1], f.y, s2);
+              const float2 f = __bfloat1622float2(w2[e]);
+              s = fmaf(xf[2 * e], f.x, s);
+              s = fmaf(xf[2 * e + 1], f.y, s);
             }
-            acc2[m][c] += s2;
+            acc[m][c] += s;
+            if (SWIGLU) {
+              const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&wv2[u][c]);
+              float s2 = 0.f;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(u2[e]);
+                s2 = fmaf(xf[2 * e], f.x, s2);
+                s2 = fmaf(xf[2 * e + 1], f.y, s2);
+              }
+              acc2[m][c] += s2;
+            }
           }
         }
       }
@@ -156,7 +169,7 @@ __global__ void __launch_bounds__(kGvThreads) gemv_kernel(const GemvParams p) {
         float v = acc[m][c], v2 = acc2[m][c];
         for (int o = 16; o > 0; o >>= 1) {
           v += __shfl_xor_sync(0xffffffffu, v, o);
-          if (p.swiglu) v2 += __shfl_xor_sync(0xffffffffu, v2, o);
+          if (SWIGLU) v2 += __shfl_xor_sync(0xffffffffu, v2, o);
         }
         acc[m][c] = v;
         acc2[m][c] = v2;
@@ -185,10 +198,10 @@ __global__ void __launch_bounds__(kGvThreads) gemv_kernel(const GemvParams p) {
             return s;
           };
           v += lora(n);
-          if (p.swiglu) v2 += lora(n + p.N);
+          if (SWIGLU) v2 += lora(n + p.N);
         }
         v *= p.alpha;
-        if (p.swiglu) v = gv_silu(v) * (v2 * p.alpha);
+        if (SWIGLU) v = gv_silu(v) * (v2 * p.alpha);
         if (p.residual) v += __bfloat162float(p.residual[static_cast<long long>(m) * p.ldr + n]);
         p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16(v);
       }
@@ -196,12 +209,13 @@ __global__ void __launch_bounds__(kGvThreads) gemv_kernel(const GemvParams p) {
   }
 }
 
-template <int MR, int C>
+template <int MR, int C, int KU, bool SWIGLU>
 static int launch_gemv(const GemvParams& p, cudaStream_t st) {
   const size_t smem = static_cast<size_t>(MR) * p.K * 2;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<MR, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemv_kernel<MR, C, KU, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         200 * 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = 200 * 1024;
   }
@@ -209,7 +223,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t st) {
   int grid = (groups + kGvWarps - 1) / kGvWarps;
   const int cap = 148 * 4;
   if (grid > cap) grid = cap;
-  gemv_kernel<MR, C><<<grid, kGvThreads, smem, st>>>(p);
+  gemv_kernel<MR, C, KU, SWIGLU><<<grid, kGvThreads, smem, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -235,10 +249,15 @@ extern "C" int pm_gemv(const void* x, int ldx, const void* w, int ldw, const voi
   p.M = M; p.N = N; p.K = K; p.swiglu = swiglu; p.alpha = alpha;
   p.t = static_cast<const __nv_bfloat16*>(t); p.ldt = ldt; p.lora_b = lora_b; p.r = r;
   for (int i = 0; i < 4; ++i) p.seg_end[i] = seg_end ? seg_end[i] : 0x7fffffff;
-  // wide outputs: several columns per warp for more loads in flight; narrow outputs: one column per warp so that
-  // every SM gets work
+  // wide outputs: several columns per warp; narrow outputs: one column per warp (so that every SM gets work) with a
+  // deeper load pipeline instead
   const bool wide = N >= 148 * kGvWarps * 2;
-  if (M <= 4) return wide ? launch_gemv<4, 4>(p, st) : launch_gemv<4, 1>(p, st);
-  if (M <= 8) return wide ? launch_gemv<8, 2>(p, st) : launch_gemv<8, 1>(p, st);
-  return wide ? launch_gemv<16, 2>(p, st) : launch_gemv<16, 1>(p, st);
+  if (swiglu) {
+    if (M <= 4) return launch_gemv<4, 2, 4, true>(p, st);
+    if (M <= 8) return launch_gemv<8, 1, 4, true>(p, st);
+    return launch_gemv<16, 1, 2, true>(p, st);
+  }
+  if (M <= 4) return wide ? launch_gemv<4, 4, 4, false>(p, st) : launch_gemv<4, 1, 8, false>(p, st);
+  if (M <= 8) return wide ? launch_gemv<8, 2, 4, false>(p, st) : launch_gemv<8, 1, 8, false>(p, st);
+  return wide ? launch_gemv<16, 2, 2, false>(p, st) : launch_gemv<16, 1, 4, false>(p, st);
 }

@@ -15,6 +15,7 @@ boundaries; a padded batch is the special case of equal-length documents.
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -27,6 +28,10 @@ from .config import ModelArgs
 ATTN_PROJ = ("q_proj", "k_proj", "v_proj", "o_proj")
 MLP_PROJ = ("gate_proj", "up_proj", "down_proj")
 ALL_PROJ = ATTN_PROJ + MLP_PROJ
+
+
+# rows up to which linear layers run on the bandwidth-bound mat-vec kernel instead of tensor-core tiles (decode)
+GEMV_MAX_ROWS = int(os.environ.get("PMETAL_GEMV_MAX_ROWS", "8"))
 
 
 class FusedLinear(nn.Module):
@@ -120,7 +125,7 @@ class FusedLinear(nn.Module):
 
     def gemv_ok(self, m: int) -> bool:
         """Decode fast path: a few rows, plain bf16 weight, no bias."""
-        return (m <= 8 and self.bias is None and getattr(self, "qweight", None) is None and self.weight.is_cuda
+        return (m <= GEMV_MAX_ROWS and self.bias is None and getattr(self, "qweight", None) is None and self.weight.is_cuda
                 and self.weight.dtype == torch.bfloat16 and not self.weight.requires_grad and self.in_features % 8 == 0)
 
     def gemv_forward(self, x: torch.Tensor, norm_w=None, eps: float = 1e-6, residual=None, swiglu: bool = False):
@@ -332,18 +337,17 @@ class DecoderLM(nn.Module):
         native = ops.use_native(x) and d == 128
         rope = ops.rope_table(meta.positions, d, cfg.rope_theta, cfg.rope_scale)
         T = x.shape[0]
-        skinny = native and T <= 8
+        skinny = native and T <= GEMV_MAX_ROWS
         for li, layer in enumerate(self.layers):
             at = layer.self_attn
             if skinny and isinstance(layer.mlp, MLP) and at.qkv_proj.gemv_ok(T) and layer.mlp.gate_up_proj.gemv_ok(T):
-                # decode: six launches per layer (norm+qkv, qk-norm+rope, cache append, attention, o+residual,
+                # decode: six launches per layer (norm+qkv, qk-norm+rope+cache append, attention, o+residual,
                 # norm+gate/up+SwiGLU, down+residual)
                 from ..ops import native as nat
                 eps = cfg.rms_norm_eps
                 qkv = at.qkv_proj.gemv_forward(x, layer.input_layernorm, eps)
-                q, k = nat.qknorm_rope_fwd(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps)
-                v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
-                nat.kv_append(k, v, cache.k[li], cache.v[li], meta.slots)
+                q = nat.qknorm_rope_cache(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps, cache.k[li],
+                                          cache.v[li], meta.slots)
                 o = nat.paged_attn(q, cache.k[li], cache.v[li], meta, d ** -0.5, at.window).view(T, hq * d)
                 h = at.o_proj.gemv_forward(o, residual=x)
                 act = layer.mlp.gate_up_proj.gemv_forward(h, layer.post_attention_layernorm, eps, swiglu=True)
@@ -366,7 +370,7 @@ class DecoderLM(nn.Module):
             last = (meta.q_start + meta.q_lens - 1).long()
             x = x[last]               # RMSNorm is per row, so selecting rows first is equivalent
         head = self.head_weight()
-        if (skinny and not return_hidden and x.shape[0] <= 8 and cfg.final_logit_softcap <= 0
+        if (skinny and not return_hidden and x.shape[0] <= GEMV_MAX_ROWS and cfg.final_logit_softcap <= 0
                 and head.dtype == torch.bfloat16 and not head.requires_grad):
             from ..ops import native as nat
             return nat.gemv(x.contiguous(), head, self.norm, cfg.rms_norm_eps)      # final norm fused into the head

@@ -47,7 +47,7 @@ def _load():
                "pm_qknorm_rope_bwd", "pm_swiglu_fwd", "pm_swiglu_bwd", "pm_ce_fwd_bwd", "pm_sumsq", "pm_adamw_flat",
                "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16", "pm_paged_attn", "pm_kv_append", "pm_attn_fwd_tc", "pm_attn_bwd_tc", "pm_dequant_4bit", "pm_sample", "pm_spec_verify", "pm_count_tokens",
                "pm_moe_route", "pm_moe_gather", "pm_moe_combine", "pm_gguf_dequant_bf16", "pm_fp8_quant", "pm_fp8_dequant",
-               "pm_kd_fwd_bwd", "pm_merge_fused", "pm_dot_norms", "pm_attn_fwd_tc_rect", "pm_gemv"):
+               "pm_kd_fwd_bwd", "pm_merge_fused", "pm_dot_norms", "pm_attn_fwd_tc_rect", "pm_gemv", "pm_qknorm_rope_cache"):
         getattr(_LIB, fn).restype = c_int
 
 
@@ -295,6 +295,16 @@ def qknorm_rope_fwd(qkv, qw, kw, cos, sin, hq: int, hkv: int, eps: float):
     _chk(lib().pm_qknorm_rope_fwd(_p(qkv), c_int(qkv.stride(0)), _p(qw), _p(kw), _p(cos), _p(sin), _p(q), _p(k),
                                   c_int(T), c_int(hq), c_int(hkv), c_float(eps), _stream()), "pm_qknorm_rope_fwd")
     return q, k
+
+
+def qknorm_rope_cache(qkv, qw, kw, cos, sin, hq: int, hkv: int, eps: float, k_cache, v_cache, slots):
+    """Decode: q = rope(norm(q)) returned; rope(norm(k)) and v are written into the paged caches at ``slots``."""
+    T = qkv.shape[0]
+    q = torch.empty(T, hq, 128, dtype=qkv.dtype, device=qkv.device)
+    _chk(lib().pm_qknorm_rope_cache(_p(qkv), c_int(qkv.stride(0)), _p(qw), _p(kw), _p(cos), _p(sin), _p(q), _p(k_cache),
+                                    _p(v_cache), _p(slots), c_int(T), c_int(hq), c_int(hkv), c_float(eps), _stream()),
+         "pm_qknorm_rope_cache")
+    return q
 
 
 def qknorm_rope_bwd(dq, dk, qkv, qw, kw, cos, sin, hq: int, hkv: int, eps: float, dqkv) -> None:
