@@ -140,6 +140,8 @@ def main() -> None:
     ap.add_argument("--model", default="qwen3-0.6b")
     ap.add_argument("--packs", type=int, default=4)
     ap.add_argument("--pack-len", type=int, default=4096)
+    ap.add_argument("--quant", default="none", choices=["none", "nf4", "fp4", "int8"],
+                    help="QLoRA: quantise the frozen base (block 64, double-quantised absmax)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--dp", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-decode", action="store_true", help="skip the decode tok/s measurement appended to the report")
@@ -183,11 +185,16 @@ def main() -> None:
     model = DecoderLM(cfg).init_weights(0.02, 0)
     lcfg = LoraConfig(r=16, alpha=32.0, target_modules=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj",
                                                         "up_proj", "down_proj"])
-    apply_lora(model, lcfg, seed=42)
     model = model.to(dev)
     for n, p in model.named_parameters():
-        if "lora_" not in n:
-            p.data = p.data.to(torch.bfloat16)
+        p.data = p.data.to(torch.bfloat16)
+    if args.quant != "none":
+        from pmetal_b200.lora.qlora import quantize_base
+        for p in model.parameters():
+            p.requires_grad_(False)
+        quantize_base(model, args.quant, 64, True)
+    apply_lora(model, lcfg, seed=42)
+    model = model.to(dev)
     model.prepare_for_training()
     tcfg = TrainingConfig(learning_rate=2e-4, gradient_accumulation_steps=1, warmup_steps=0, max_grad_norm=1.0,
                           lr_scheduler="cosine")
@@ -293,7 +300,8 @@ def main() -> None:
             "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": round(value / BASELINE_TOK_S, 2), "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
-            "config": {"model": "Qwen3-0.6B architecture (random init)", "global_batch": args.packs * world,
+            "config": {"model": f"{args.model} architecture (random init)" + (f", base quantised to {args.quant}" if args.quant != "none" else ""),
+                       "global_batch": args.packs * world,
                        "seq_len": args.pack_len, "parallelism": f"dp{world}", "lora": "r16 alpha32 all-7",
                        "packing": "docs U[64,2048] packed to 4096, varlen per-document causal attention",
                        "tokens_per_step": int(tok_a / args.steps),

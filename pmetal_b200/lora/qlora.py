@@ -31,7 +31,10 @@ def quantize_base(model, scheme: str = "nf4", block_size: int = 64, double_quant
     saved = 0
     for _, _, fl in model.fused_linears():
         w = fl.weight
-        q = quantize(w.detach().float().cpu(), scheme, block_size, double_quant).to(w.device)
+        # quantise where the weight lives (GPU when available: the codebook search is plain tensor ops)
+        q = quantize(w.detach(), scheme, block_size, double_quant)
+        if q.data.device != w.device:
+            q = q.to(w.device)
         saved += w.numel() * w.element_size() - q.nbytes()
         fl.qweight = q
         fl.weight = torch.nn.Parameter(torch.empty(0, dtype=w.dtype, device=w.device), requires_grad=False)

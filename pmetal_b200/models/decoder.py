@@ -31,7 +31,7 @@ ALL_PROJ = ATTN_PROJ + MLP_PROJ
 
 
 # rows up to which linear layers run on the bandwidth-bound mat-vec kernel instead of tensor-core tiles (decode)
-GEMV_MAX_ROWS = int(os.environ.get("PMETAL_GEMV_MAX_ROWS", "8"))
+GEMV_MAX_ROWS = int(os.environ.get("PMETAL_GEMV_MAX_ROWS", "16"))
 
 
 class FusedLinear(nn.Module):
