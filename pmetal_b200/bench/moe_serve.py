@@ -1,0 +1,113 @@
+"""Mixture-of-experts serving benchmark: concurrent requests on a Qwen3-30B-A3B-shaped model with expert parallelism.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29660 \
+        -m pmetal_b200.bench.moe_serve [--requests 64] [--prompt-len 512] [--new-tokens 256] [--model qwen3-30b-a3b]
+
+Parallelism: every rank holds the attention weights and serves ``requests / N`` of the requests (data-parallel attention
+with its own paged KV cache); the experts are split across ranks and every MoE layer runs the fused
+routing + dispatch + grouped-GEMM + combine kernels over NVLink peer memory (parallel/ep.py). All ranks step in
+lock-step (same number of requests, prompt lengths and greedy decode steps), which the device-side flags require.
+Reported: prefill tokens/s, decode tokens/s and requests/s for the whole job, device-timed, maximum over ranks."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+
+import torch
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--model", default="qwen3-30b-a3b")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the architecture's own)")
+    a = ap.parse_args(argv)
+    import torch.distributed as dist
+
+    from ..models.config import preset
+    from ..models.decoder import DecoderLM
+    from ..models.generation import Generator
+    from ..ops import native
+    from ..parallel.ep import shard_experts
+    world, rank, local = int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = preset(a.model)
+    if a.layers:
+        cfg.num_hidden_layers = a.layers
+    t0 = time.time()
+    model = DecoderLM(cfg, dtype=torch.bfloat16, device=dev).init_weights_on_device(0.02, 0).eval()
+    for p in model.parameters():
+        p.requires_grad_(False)
+    per_rank = a.requests // world
+    chunk = 2048
+    for layer in model.layers:
+        if hasattr(layer.mlp, "router"):
+            shard_experts(layer.mlp, None if world == 1 else dist.group.WORLD, max_tokens=chunk)
+            # the engine holds this rank's experts; the stacked originals are no longer needed
+            layer.mlp.gate_up = torch.nn.Parameter(torch.empty(0, dtype=torch.bfloat16, device=dev), requires_grad=False)
+            layer.mlp.down = torch.nn.Parameter(torch.empty(0, dtype=torch.bfloat16, device=dev), requires_grad=False)
+    torch.cuda.empty_cache()
+    build_s = time.time() - t0
+    blocks = per_rank * ((a.prompt_len + a.new_tokens) // 64 + 2) + 64
+    gen = Generator(model, num_blocks=blocks)
+    g = torch.Generator().manual_seed(10 + rank)
+    prompts = [torch.randint(0, cfg.vocab_size, (a.prompt_len,), generator=g).tolist() for _ in range(per_rank)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run(new_tokens: int):
+        seqs = [gen.new_seq() for _ in prompts]
+        barrier()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        logits = gen.prefill(seqs, prompts, chunk)
+        ids = logits.argmax(-1)
+        e1.record()
+        for _ in range(new_tokens - 1):
+            logits = gen.decode_step(seqs, ids)
+            ids = logits.argmax(-1)
+            _ = ids.tolist()
+        e2.record()
+        barrier()
+        for s in seqs:
+            gen.cache.free_sequence(s)
+        return e0.elapsed_time(e1), e1.elapsed_time(e2)
+    run(8)                                    # warm-up: graph captures, lazy initialisation
+    pre_ms, dec_ms = run(a.new_tokens)
+    native.check_status()
+
+    def mx(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    pre_ms, dec_ms = mx(pre_ms), mx(dec_ms)
+    if rank == 0:
+        total = per_rank * world
+        print(json.dumps({"bench": "moe_serve", "model": a.model, "layers": cfg.num_hidden_layers, "n_gpus": world,
+                          "requests": total, "prompt_len": a.prompt_len, "new_tokens": a.new_tokens,
+                          "parallelism": f"dp-attention x ep{world}", "build_s": round(build_s, 1),
+                          "prefill_tok_s": round(total * a.prompt_len / (pre_ms / 1e3), 1),
+                          "decode_tok_s": round(total * (a.new_tokens - 1) / (dec_ms / 1e3), 1),
+                          "decode_ms_per_step": round(dec_ms / (a.new_tokens - 1), 3),
+                          "requests_per_s": round(total / ((pre_ms + dec_ms) / 1e3), 3)}), flush=True)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -99,7 +99,7 @@ inline void finite_min_max(const float* x, int n, float* mn, float* mx) {
 enum : int {
   T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q8_1 = 9,
   T_Q2K = 10, T_Q3K = 11, T_Q4K = 12, T_Q5K = 13, T_Q6K = 14, T_Q8K = 15, T_IQ4_NL = 20, T_IQ4_XS = 23,
-  T_BF16 = 30, T_MXFP4 = 39,
+  T_BF16 = 30, T_TQ1_0 = 34, T_TQ2_0 = 35, T_MXFP4 = 39, T_NVFP4 = 40, T_Q1_0 = 41,
 };
 
 struct Fmt { int type, elems, bytes; };
@@ -107,6 +107,7 @@ constexpr Fmt kFormats[] = {
     {T_F32, 1, 4},     {T_F16, 1, 2},     {T_BF16, 1, 2},    {T_Q4_0, 32, 18},  {T_Q4_1, 32, 20},  {T_Q5_0, 32, 22},
     {T_Q5_1, 32, 24},  {T_Q8_0, 32, 34},  {T_Q8_1, 32, 36},  {T_Q2K, 256, 84},  {T_Q3K, 256, 110}, {T_Q4K, 256, 144},
     {T_Q5K, 256, 176}, {T_Q6K, 256, 210}, {T_Q8K, 256, 292}, {T_IQ4_NL, 32, 18}, {T_IQ4_XS, 256, 136}, {T_MXFP4, 32, 17},
+    {T_TQ1_0, 256, 54}, {T_TQ2_0, 256, 66}, {T_NVFP4, 64, 36},  {T_Q1_0, 128, 18},
 };
 const Fmt* find_fmt(int type) {
   for (const Fmt& f : kFormats)
@@ -263,6 +264,156 @@ void enc_mxfp4(const float* x, int n, uint8_t* o) {
     const float a = i < n ? x[i] : 0.f, b = i + 16 < n ? x[i + 16] : 0.f;
     o[1 + i] = static_cast<uint8_t>(code(a) | (code(b) << 4));
   }
+}
+
+// ---------------------------------------------------------------------------------------- NVFP4 / ternary / 1-bit
+// UE4M3 scale byte (unsigned E4M3 with an extra factor 1/2 on decode), as the reference's fp4.rs defines it.
+inline float ue4m3_to_f32(uint8_t x) {
+  if (x == 0 || x == 0x7f) return 0.f;
+  const int e = (x >> 3) & 15, m = x & 7;
+  const float raw = e == 0 ? static_cast<float>(m) * std::ldexp(1.f, -9) : (1.f + static_cast<float>(m) / 8.f) * std::ldexp(1.f, e - 7);
+  return raw * 0.5f;
+}
+inline uint8_t f32_to_ue4m3(float x) {
+  if (!(x > 0.f) || !std::isfinite(x)) return 0;
+  if (x > 448.f) x = 448.f;
+  uint32_t bits;
+  std::memcpy(&bits, &x, 4);
+  const int fe = static_cast<int>((bits >> 23) & 0xff) - 127, fm = static_cast<int>((bits >> 20) & 7);
+  int e = fe + 7;
+  if (e <= 0) {
+    const int man = static_cast<int>(x * 512.f + 0.5f);
+    return static_cast<uint8_t>(man > 7 ? 7 : (man < 1 ? 0 : man));
+  }
+  if (e >= 15) return 0x7e;
+  int m = fm + static_cast<int>((bits >> 19) & 1);
+  if (m > 7) {
+    m = 0;
+    if (++e >= 15) return 0x7e;
+  }
+  return static_cast<uint8_t>((e << 3) | m);
+}
+inline int nearest_e2m1(float v, float d) {
+  int best = 0;
+  float err = std::fabs(kE2M1[0] * d - v);
+  for (int c = 1; c < 16; ++c) {
+    const float e2 = std::fabs(kE2M1[c] * d - v);
+    if (e2 < err) { err = e2; best = c; }
+  }
+  return best;
+}
+// NVFP4: 64 elements = 4 sub-blocks of 16; bytes 0-3 scales, then 4 x 8 nibble bytes (element i low, i + 8 high)
+void enc_nvfp4(const float* x, int n, uint8_t* o) {
+  std::memset(o, 0, 36);
+  for (int sub = 0; sub < 4; ++sub) {
+    const int s0 = sub * 16;
+    float amax = 0.f;
+    for (int i = s0; i < std::min(s0 + 16, n); ++i)
+      if (std::isfinite(x[i])) amax = std::max(amax, std::fabs(x[i]));
+    const uint8_t sb = f32_to_ue4m3(amax / 6.f);
+    const float d = ue4m3_to_f32(sb);
+    o[sub] = sb;
+    for (int i = 0; i < 8; ++i) {
+      const float a = s0 + i < n ? x[s0 + i] : 0.f, b = s0 + i + 8 < n ? x[s0 + i + 8] : 0.f;
+      o[4 + sub * 8 + i] = static_cast<uint8_t>(nearest_e2m1(a, d) | (nearest_e2m1(b, d) << 4));
+    }
+  }
+}
+void dec_nvfp4(const uint8_t* b, float* y) {
+  for (int sub = 0; sub < 4; ++sub) {
+    const float d = ue4m3_to_f32(b[sub]);
+    for (int i = 0; i < 8; ++i) {
+      y[sub * 16 + i] = d * kE2M1[b[4 + sub * 8 + i] & 15];
+      y[sub * 16 + i + 8] = d * kE2M1[b[4 + sub * 8 + i] >> 4];
+    }
+  }
+}
+inline int trit(float v, float inv) {
+  float q = std::round(v * inv);
+  q = q < -1.f ? -1.f : (q > 1.f ? 1.f : q);
+  return static_cast<int>(q) + 1;
+}
+inline float finite_amax(const float* x, int n) {
+  float amax = 0.f;
+  for (int i = 0; i < n; ++i)
+    if (std::isfinite(x[i])) amax = std::max(amax, std::fabs(x[i]));
+  return amax;
+}
+// TQ1_0 {qs[48], qh[4], d}: five trits per byte stored as ceil(q * 256 / 243); strides 32, then 16, then 4
+void enc_tq1_0(const float* x, int n, uint8_t* o) {
+  const float amax = finite_amax(x, n), inv = amax > 0.f ? 1.f / amax : 0.f;
+  auto at = [&](int i) { return i < n ? x[i] : 0.f; };
+  int base = 0;
+  for (int m = 0; m < 32; ++m) {
+    int q = 0;
+    for (int k = 0; k < 5; ++k) q = q * 3 + trit(at(base + m + k * 32), inv);
+    o[m] = static_cast<uint8_t>((q * 256 + 242) / 243);
+  }
+  base += 160;
+  for (int m = 0; m < 16; ++m) {
+    int q = 0;
+    for (int k = 0; k < 5; ++k) q = q * 3 + trit(at(base + m + k * 16), inv);
+    o[32 + m] = static_cast<uint8_t>((q * 256 + 242) / 243);
+  }
+  base += 80;
+  for (int j = 0; j < 4; ++j) {
+    int q = 0;
+    for (int m = 0; m < 4; ++m) q = q * 3 + trit(at(base + j + m * 4), inv);
+    q = std::min(q * 3, 255);
+    o[48 + j] = static_cast<uint8_t>((q * 256 + 242) / 243);
+  }
+  put16(o + 52, f32_to_f16(amax));
+}
+inline int trit_of(uint8_t packed, int k) {     // k-th most significant of five trits
+  static const int pow3[5] = {1, 3, 9, 27, 81};
+  const uint16_t q = static_cast<uint16_t>(packed * pow3[k]);      // shifts the wanted trit to the top
+  return ((q & 0xff) * 3) >> 8;
+}
+void dec_tq1_0(const uint8_t* b, float* y) {
+  const float d = f16_to_f32(get16(b + 52));
+  int base = 0;
+  for (int k = 0; k < 5; ++k)
+    for (int m = 0; m < 32; ++m) y[base + k * 32 + m] = d * static_cast<float>(trit_of(b[m], k) - 1);
+  base += 160;
+  for (int k = 0; k < 5; ++k)
+    for (int m = 0; m < 16; ++m) y[base + k * 16 + m] = d * static_cast<float>(trit_of(b[32 + m], k) - 1);
+  base += 80;
+  for (int m = 0; m < 4; ++m)
+    for (int j = 0; j < 4; ++j) y[base + m * 4 + j] = d * static_cast<float>(trit_of(b[48 + j], m) - 1);
+}
+// TQ2_0 {qs[64], d}: two bits per trit, four elements 32 apart per byte
+void enc_tq2_0(const float* x, int n, uint8_t* o) {
+  const float amax = finite_amax(x, n), inv = amax > 0.f ? 1.f / amax : 0.f;
+  for (int h = 0; h < 2; ++h)
+    for (int m = 0; m < 32; ++m) {
+      int q = 0;
+      for (int k = 0; k < 4; ++k) {
+        const int i = h * 128 + m + k * 32;
+        q |= (trit(i < n ? x[i] : 0.f, inv) & 3) << (2 * k);
+      }
+      o[h * 32 + m] = static_cast<uint8_t>(q);
+    }
+  put16(o + 64, f32_to_f16(amax));
+}
+void dec_tq2_0(const uint8_t* b, float* y) {
+  const float d = f16_to_f32(get16(b + 64));
+  for (int h = 0; h < 2; ++h)
+    for (int k = 0; k < 4; ++k)
+      for (int m = 0; m < 32; ++m) y[h * 128 + k * 32 + m] = d * static_cast<float>(((b[h * 32 + m] >> (2 * k)) & 3) - 1);
+}
+// Q1_0 {d f16 = mean |x| over 128, 16 bytes of sign bits (bit set = non-negative)}
+void enc_q1_0(const float* x, int n, uint8_t* o) {
+  float sum = 0.f;
+  for (int i = 0; i < n; ++i)
+    if (std::isfinite(x[i])) sum += std::fabs(x[i]);
+  put16(o, f32_to_f16(sum / 128.f));
+  std::memset(o + 2, 0, 16);
+  for (int i = 0; i < 128; ++i)
+    if ((i < n ? x[i] : 0.f) >= 0.f) o[2 + i / 8] |= static_cast<uint8_t>(1u << (i % 8));
+}
+void dec_q1_0(const uint8_t* b, float* y) {
+  const float d = f16_to_f32(get16(b));
+  for (int i = 0; i < 128; ++i) y[i] = ((b[2 + i / 8] >> (i % 8)) & 1) ? d : -d;
 }
 
 // ---------------------------------------------------------------------------------------- K-quant helpers
@@ -678,7 +829,8 @@ EncFn encoder(int type) {
     case T_Q5_1: return enc_q5_1;  case T_Q8_0: return enc_q8_0;  case T_Q8_1: return enc_q8_1;
     case T_Q2K: return enc_q2k;    case T_Q3K: return enc_q3k;    case T_Q4K: return enc_q4k;
     case T_Q5K: return enc_q5k;    case T_Q6K: return enc_q6k;    case T_Q8K: return enc_q8k;
-    case T_MXFP4: return enc_mxfp4;
+    case T_MXFP4: return enc_mxfp4;  case T_NVFP4: return enc_nvfp4;  case T_TQ1_0: return enc_tq1_0;
+    case T_TQ2_0: return enc_tq2_0;  case T_Q1_0: return enc_q1_0;
     default: return nullptr;
   }
 }
@@ -689,6 +841,8 @@ DecFn decoder(int type) {
     case T_Q2K: return dec_q2k;    case T_Q3K: return dec_q3k;    case T_Q4K: return dec_q4k;
     case T_Q5K: return dec_q5k;    case T_Q6K: return dec_q6k;    case T_Q8K: return dec_q8k;
     case T_IQ4_NL: return dec_iq4_nl;  case T_IQ4_XS: return dec_iq4_xs;  case T_MXFP4: return dec_mxfp4;
+    case T_NVFP4: return dec_nvfp4;  case T_TQ1_0: return dec_tq1_0;  case T_TQ2_0: return dec_tq2_0;
+    case T_Q1_0: return dec_q1_0;
     default: return nullptr;
   }
 }
@@ -740,7 +894,7 @@ int pm_gguf_quantize(int type, const float* src, void* dst, int64_t n, int threa
   const EncFn enc = encoder(type);
   if (!enc) return -2;
   const int64_t nb = (n + f->elems - 1) / f->elems;
-  const bool k_quant = f->elems == 256;
+  const bool k_quant = type >= T_Q2K && type <= T_Q8K;   // only these leave a ragged tail block zeroed; the rest pad
   parallel_blocks(nb, threads, [&](int64_t a, int64_t b) {
     for (int64_t i = a; i < b; ++i) {
       const int64_t left = n - i * f->elems;

@@ -102,10 +102,16 @@ __device__ __forceinline__ bool ep_wait_flag(const uint32_t* flag, uint32_t epoc
 // tiles1: gate/up tiles (A pulled from the source rank, output to local h rows, packed densely in 128-row blocks);
 // tiles2: down tiles (A = local h rows, output to the source rank's result rows). counts_out[0] = number of tiles,
 // counts_out[1] = h rows used.
-__global__ void ep_prepare_kernel(const int* const* offsets, uint32_t* const* pads, int rank, int world, int e_loc,
-                                  MoeTile* tiles1, MoeTile* tiles2, int max_tiles, int* counts_out,
-                                  unsigned long long timeout_ns, int* status) {
+struct EpPtrs {                  // passed by value, so the launch needs no staging copy and can be captured in a graph
+  const int* offsets[kEpMaxRanks];
+  uint32_t* pads[kEpMaxRanks];
+};
+
+__global__ void ep_prepare_kernel(const EpPtrs ptrs, int rank, int world, int e_loc, MoeTile* tiles1, MoeTile* tiles2,
+                                  int max_tiles, int* counts_out, unsigned long long timeout_ns, int* status) {
   __shared__ int s_ok;
+  const int* const* offsets = ptrs.offsets;
+  uint32_t* const* pads = ptrs.pads;
   uint32_t* my_pad = pads[rank];
   const uint32_t epoch = my_pad[kEpEpoch] + 1;
   if (threadIdx.x == 0) {
@@ -378,19 +384,14 @@ using namespace pm;
 
 extern "C" int pm_ep_prepare(const unsigned long long* offset_ptrs, const unsigned long long* pad_ptrs, int rank,
                              int world, int e_loc, void* tiles1, void* tiles2, int max_tiles, int* counts_out,
-                             double timeout_s, int* status, void* dev_ptr_scratch, cudaStream_t st) {
-  // dev_ptr_scratch: device buffer of 16 pointers (offsets[8], pads[8]) written here once per call
+                             double timeout_s, int* status, cudaStream_t st) {
   if (world < 1 || world > kEpMaxRanks || rank < 0 || rank >= world || e_loc < 1) return -1;
-  unsigned long long host[16];
-  for (int r = 0; r < 8; ++r) {
-    host[r] = offset_ptrs[r < world ? r : rank];
-    host[8 + r] = pad_ptrs[r < world ? r : rank];
+  EpPtrs ptrs;
+  for (int r = 0; r < kEpMaxRanks; ++r) {
+    ptrs.offsets[r] = reinterpret_cast<const int*>(offset_ptrs[r < world ? r : rank]);
+    ptrs.pads[r] = reinterpret_cast<uint32_t*>(pad_ptrs[r < world ? r : rank]);
   }
-  cudaError_t e = cudaMemcpyAsync(dev_ptr_scratch, host, sizeof(host), cudaMemcpyHostToDevice, st);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  ep_prepare_kernel<<<1, 32, 0, st>>>(reinterpret_cast<const int* const*>(dev_ptr_scratch),
-                                      reinterpret_cast<uint32_t* const*>(static_cast<unsigned long long*>(dev_ptr_scratch) + 8),
-                                      rank, world, e_loc, static_cast<MoeTile*>(tiles1), static_cast<MoeTile*>(tiles2),
+  ep_prepare_kernel<<<1, 32, 0, st>>>(ptrs, rank, world, e_loc, static_cast<MoeTile*>(tiles1), static_cast<MoeTile*>(tiles2),
                                       max_tiles, counts_out, static_cast<unsigned long long>(timeout_s * 1e9), status);
   return static_cast<int>(cudaGetLastError());
 }

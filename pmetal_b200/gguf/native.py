@@ -49,7 +49,7 @@ def lib():
 def can_quantize(t: GgmlType) -> bool:
     return t in (GgmlType.F32, GgmlType.F16, GgmlType.BF16, GgmlType.Q4_0, GgmlType.Q4_1, GgmlType.Q5_0, GgmlType.Q5_1,
                  GgmlType.Q8_0, GgmlType.Q8_1, GgmlType.Q2K, GgmlType.Q3K, GgmlType.Q4K, GgmlType.Q5K, GgmlType.Q6K,
-                 GgmlType.Q8K, GgmlType.MXFP4)
+                 GgmlType.Q8K, GgmlType.MXFP4, GgmlType.NVFP4, GgmlType.TQ1_0, GgmlType.TQ2_0, GgmlType.Q1_0)
 
 
 def can_dequantize(t: GgmlType) -> bool:

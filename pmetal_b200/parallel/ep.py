@@ -129,7 +129,6 @@ class FusedExpertMoE:
         self.tiles1 = torch.zeros(self.max_tiles * 8, dtype=torch.int32, device=dev)
         self.tiles2 = torch.zeros(self.max_tiles * 8, dtype=torch.int32, device=dev)
         self.counts = torch.zeros(2, dtype=torch.int32, device=dev)
-        self.ptr_scratch = torch.zeros(16, dtype=torch.int64, device=dev)
         if self.distributed:
             torch.cuda.synchronize()
             dist.barrier(group)
@@ -165,7 +164,7 @@ class FusedExpertMoE:
         native._chk(lib.pm_ep_prepare(self._off_ptrs, self._pad_ptrs, ctypes.c_int(self.rank), ctypes.c_int(self.world),
                                       ctypes.c_int(self.e_loc), native._p(self.tiles1), native._p(self.tiles2),
                                       ctypes.c_int(self.max_tiles), native._p(self.counts), ctypes.c_double(self.timeout_s),
-                                      native._p(st), native._p(self.ptr_scratch), native._stream()), "pm_ep_prepare")
+                                      native._p(st), native._stream()), "pm_ep_prepare")
         native._chk(lib.pm_moe_gemm(self._xin_ptrs, ctypes.c_int(self.max_tiles * 128), ctypes.c_int(self.H),
                                     native._p(self.w1), ctypes.c_int(self.H), ctypes.c_int(self.e_loc), self._h_ptrs,
                                     ctypes.c_int(self.I), native._p(self.tiles1), native._p(self.counts),

@@ -101,6 +101,47 @@ def test_iq4_and_unknown_types():
         native.dequantize(np.zeros(66, np.uint8), T.IQ2_XXS, 256)
 
 
+def test_ternary_one_bit_and_nvfp4_codecs():
+    # ternary inputs survive TQ1_0 / TQ2_0 exactly up to the f16 scale, including a ragged (padded) tail
+    tern = np.random.default_rng(3).integers(-1, 2, 256 * 3 + 40).astype(np.float32) * 0.75
+    for t, blk in ((T.TQ1_0, 54), (T.TQ2_0, 66)):
+        q = native.quantize(tern, t)
+        assert q.size == 4 * blk
+        assert np.abs(native.dequantize(q, t, tern.size) - tern).max() < 1e-3
+    # TQ2_0 layout: element m + 32 k of each 128-half sits in bits 2k of byte m; the scale is the last f16
+    x = np.zeros(256, np.float32)
+    x[0], x[32], x[64], x[96] = 1.0, -1.0, 0.0, 1.0
+    q = native.quantize(x, T.TQ2_0)
+    assert q[0] == (2 | (0 << 2) | (1 << 4) | (2 << 6)) and q[1] == 0x55
+    assert np.frombuffer(q[64:66].tobytes(), np.float16)[0] == 1.0
+    # TQ1_0: five trits base 3, most significant first, stored as ceil(v * 256 / 243)
+    x = np.zeros(256, np.float32)
+    x[0], x[32], x[64], x[96], x[128] = 1.0, 1.0, -1.0, 0.0, 1.0           # trits 2 2 0 1 2 -> 221
+    q = native.quantize(x, T.TQ1_0)
+    assert q[0] == -(-(221 * 256) // 243)
+    # Q1_0: scale = mean |x| over the 128-element block, one sign bit per element (zero counts as positive)
+    x = _data(128, seed=5)
+    q = native.quantize(x, T.Q1_0)
+    assert q.size == 18
+    d = np.frombuffer(q[:2].tobytes(), np.float16)[0]
+    assert abs(float(d) - np.abs(x).mean()) < 1e-3 * np.abs(x).mean() + 1e-4
+    bits = np.unpackbits(q[2:], bitorder="little").astype(bool)
+    assert (bits == (x >= 0)).all()
+    y = native.dequantize(q, T.Q1_0, 128)
+    assert np.allclose(np.abs(y), float(d)) and (np.sign(y) == np.where(x >= 0, 1, -1)).all()
+    # NVFP4: 4 sub-blocks of 16 with an unsigned e4m3 scale each (decoded with a factor one half)
+    x = _data(64 * 5 + 9, seed=6)
+    q = native.quantize(x, T.NVFP4)
+    assert q.size == 6 * 36
+    y = native.dequantize(q, T.NVFP4, x.size)
+    assert np.linalg.norm(y - x) / np.linalg.norm(x) < 0.13
+    one = np.zeros(64, np.float32)
+    one[:16] = 6.0                                         # amax / 6 = 1.0 -> e = 7, m = 0; decodes to 0.5 x code 7 (12)
+    q = native.quantize(one, T.NVFP4)
+    assert q[0] == (7 << 3) and q[1] == 0 and q[4] == 0x77
+    assert np.allclose(native.dequantize(q, T.NVFP4, 64)[:16], 6.0)
+
+
 def test_writer_layout_and_reader_round_trip(tmp_path):
     w = GgufWriter()
     w.add_string("general.architecture", "qwen3").add_u32("qwen3.block_count", 2).add_f32("qwen3.rope.freq_base", 1e6)
