@@ -4,8 +4,10 @@
 // by expert into `sorted_x` (symmetric memory) with `offsets[E+1]` (symmetric memory as well). Then, per rank:
 //
 //   ep_prepare_kernel   publishes "my sorted tokens and offsets are ready", waits for every peer's flag (bounded),
-//                       reads the peers' offsets and builds the tile lists: one tile per 128 rows of each
-//                       (source rank, local expert) segment.
+//                       reads the peers' offsets and builds the tile list: for every local expert the rows routed to
+//                       it by all ranks are concatenated (own rows first) and cut into 128-row tiles, so a tile may
+//                       hold rows of several source ranks ("runs"). With few tokens per expert (decode, or many
+//                       ranks) this streams each expert's weights through the SMs once instead of once per source.
 //   moe_gemm_kernel #1  gate/up projection with the dispatch all-to-all inside: at kernel start the four epilogue warps
 //                       of every CTA pull their share of the tiles' token rows out of the *source ranks'* sorted
 //                       buffers (16-byte peer loads over NVLink) into a local staging buffer and publish a flag per
@@ -13,7 +15,8 @@
 //                       NVLink once (peer memory is not cached in the local L2, so reading remote rows in place would
 //                       re-fetch them once per column block). The epilogue applies SwiGLU, writing h locally.
 //   moe_gemm_kernel #2  down projection on h; the epilogue stores every output row straight into the *source rank's*
-//                       result buffer at the row's sorted position (16-byte peer stores) -- this is the combine
+//                       result buffer at the row's sorted position (16-byte peer stores, destination looked up in
+//                       the tile's runs) -- this is the combine
 //                       all-to-all. The launch ends only after every peer has signalled that its pushes are complete,
 //                       so the local weighted combine that follows on the stream sees all rows.
 //
@@ -40,28 +43,35 @@ constexpr int kEpEpoch = 16;    // local epoch (bumped by ep_prepare_kernel)
 constexpr int kEpArrive = 17;   // local CTA arrival counter
 
 struct MoeTile {
-  int a_src;      // index of the A tensor map (source rank; own rank for the down projection)
-  int a_row0;     // first row in that buffer
+  int a_row0;     // first row of the tile in the local staging / hidden buffers (128 rows reserved)
   int rows;       // valid rows (<= 128)
   int expert;     // local expert index (selects the weight rows)
-  int out_dst;    // rank whose buffer receives the output rows
-  int out_row0;   // first output row there
-  int c_src;      // stage-in: rank whose sorted buffer holds the rows (copied to a_row0 of the local staging buffer)
-  int c_row0;     // stage-in: first row there
+  int run0;       // first entry of this tile in the run list
+  int nruns;      // number of runs (<= world)
+  int pad[3];
+};
+
+struct MoeRun {
+  int src;        // rank whose sorted buffer holds the rows (and receives the results)
+  int src_row0;   // first row there
+  int tile_row0;  // first row inside the tile
+  int rows;
 };
 
 struct MoeMaps {
-  CUtensorMap a[kEpMaxRanks];
+  CUtensorMap a;      // local A buffer: staged-in token rows (gate/up) or the hidden rows (down)
   CUtensorMap b;      // stacked weights [E_loc * n_per_expert, K]
 };
 
 struct MoeGemmParams {
   const MoeTile* tiles;
+  const MoeRun* runs;
   const int* n_tiles;
   int N, K;                 // per-expert output rows of the weight (2*I for gate/up, H for down) and reduction size
   int swiglu;               // 1: out[:, j] = silu(acc[:, j]) * acc[:, j + 128] per 256 block, output width N / 2
-  __nv_bfloat16* out[kEpMaxRanks];
+  __nv_bfloat16* out[kEpMaxRanks];   // push = 0: out[rank] is the local output; push = 1: every rank's result buffer
   int ldd;
+  int push;                 // 1: output rows go to their source ranks' buffers at the rows' sorted positions
   int rank, world;
   int signal_pushed;        // 1: set pushed[rank] on all peers at the end and wait for all peers' flags
   uint32_t* pads[kEpMaxRanks];
@@ -98,19 +108,21 @@ __device__ __forceinline__ bool ep_wait_flag(const uint32_t* flag, uint32_t epoc
   return true;
 }
 
-// One CTA. offsets[r] points at rank r's [E+1] expert offsets into its sorted token buffer.
-// tiles1: gate/up tiles (A pulled from the source rank, output to local h rows, packed densely in 128-row blocks);
-// tiles2: down tiles (A = local h rows, output to the source rank's result rows). counts_out[0] = number of tiles,
-// counts_out[1] = h rows used.
+// One CTA. offsets[r] points at rank r's [E+1] expert offsets into its sorted token buffer. Writes the tile list and
+// the run list; counts_out[0] = number of tiles, counts_out[1] = buffer rows used (128 per tile).
 struct EpPtrs {                  // passed by value, so the launch needs no staging copy and can be captured in a graph
   const int* offsets[kEpMaxRanks];
   uint32_t* pads[kEpMaxRanks];
 };
 
-__global__ void ep_prepare_kernel(const EpPtrs ptrs, int rank, int world, int e_loc, MoeTile* tiles1, MoeTile* tiles2,
-                                  int max_tiles, int* counts_out, unsigned long long timeout_ns, int* status) {
+constexpr int kEpMaxLocal = 512;     // local experts per rank
+constexpr int kStatusEpOverflow = 108;
+
+__global__ void ep_prepare_kernel(const EpPtrs ptrs, int rank, int world, int e_loc, MoeTile* tiles, MoeRun* runs,
+                                  int max_tiles, int max_runs, int* counts_out, unsigned long long timeout_ns,
+                                  int* status) {
   __shared__ int s_ok;
-  const int* const* offsets = ptrs.offsets;
+  __shared__ int s_off[kEpMaxRanks][kEpMaxLocal + 1];
   uint32_t* const* pads = ptrs.pads;
   uint32_t* my_pad = pads[rank];
   const uint32_t epoch = my_pad[kEpEpoch] + 1;
@@ -124,27 +136,50 @@ __global__ void ep_prepare_kernel(const EpPtrs ptrs, int rank, int world, int e_
     if (!ep_wait_flag(my_pad + kEpReady + threadIdx.x, epoch, timeout_ns, status)) s_ok = 0;
   }
   __syncthreads();
+  if (s_ok) {   // all peers' offsets in parallel: a serial scan over peer memory would pay the NVLink latency per load
+    for (int i = threadIdx.x; i < world * (e_loc + 1); i += blockDim.x) {
+      const int s = i / (e_loc + 1), e = i % (e_loc + 1);
+      s_off[s][e] = ptrs.offsets[(rank + s) % world][rank * e_loc + e];
+    }
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
-    int n = 0, hrow = 0;
+    int n = 0, nr = 0;
+    bool overflow = false;
     if (s_ok) {
-      for (int e = 0; e < e_loc; ++e) {
-        const int ge = rank * e_loc + e;
-        for (int s = 0; s < world; ++s) {
-          const int src = (rank + s) % world;    // local tokens first: their rows need no NVLink traffic
-          const int lo = offsets[src][ge], hi = offsets[src][ge + 1];
-          for (int r0 = lo; r0 < hi; r0 += kBM) {
-            if (n >= max_tiles) break;
-            const int rows = min(kBM, hi - r0);
-            tiles1[n] = MoeTile{rank, hrow, rows, e, rank, hrow, src, r0};
-            tiles2[n] = MoeTile{rank, hrow, rows, e, src, r0, rank, hrow};
-            hrow += kBM;
-            ++n;
+      for (int e = 0; e < e_loc && !overflow; ++e) {
+        MoeTile cur{};
+        int filled = kBM;            // forces a new tile at the start of every expert
+        for (int s = 0; s < world && !overflow; ++s) {
+          const int src = (rank + s) % world;    // own tokens first
+          int lo = s_off[s][e];
+          const int hi = s_off[s][e + 1];
+          while (lo < hi) {
+            if (filled == kBM) {
+              if (n > 0 && cur.rows > 0) tiles[n - 1] = cur;
+              if (n >= max_tiles) { overflow = true; break; }
+              cur = MoeTile{};
+              cur.a_row0 = n * kBM;
+              cur.expert = e;
+              cur.run0 = nr;
+              filled = 0;
+              ++n;
+            }
+            if (nr >= max_runs) { overflow = true; break; }
+            const int take = min(hi - lo, kBM - filled);
+            runs[nr++] = MoeRun{src, lo, filled, take};
+            cur.rows += take;
+            cur.nruns += 1;
+            filled += take;
+            lo += take;
           }
         }
+        if (n > 0 && cur.rows > 0) tiles[n - 1] = cur;
       }
     }
-    counts_out[0] = n;
-    counts_out[1] = hrow;
+    if (overflow) atomicCAS(status, 0, kStatusEpOverflow);
+    counts_out[0] = overflow ? 0 : n;
+    counts_out[1] = n * kBM;
     __threadfence();
     my_pad[kEpEpoch] = epoch;
   }
@@ -228,7 +263,7 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
           }
           uint8_t* sa = smem + s * stage_bytes;
           mbar_expect_tx(&full_bar[s], stage_bytes);
-          tma_load_2d(sa, &maps.a[t.a_src], &full_bar[s], kb * kBK, t.a_row0);
+          tma_load_2d(sa, &maps.a, &full_bar[s], kb * kBK, t.a_row0);
           tma_load_2d(sa + a_bytes, &maps.b, &full_bar[s], kb * kBK, b_row);
         }
       }
@@ -267,17 +302,20 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
       const int n_t = *p.n_tiles;
       for (int ti = blockIdx.x; ti < n_t; ti += gridDim.x) {
         const MoeTile t = p.tiles[ti];
-        const __nv_bfloat16* from = p.x_peer[t.c_src] + static_cast<long long>(t.c_row0) * p.K;
-        __nv_bfloat16* to = p.xin + static_cast<long long>(t.a_row0) * p.K;
-        const int n_vec = t.rows * vec_per_row;
-        for (int i0 = t128; i0 < n_vec; i0 += 128 * 4) {
-          uint4 v[4];
+        for (int ri = 0; ri < t.nruns; ++ri) {
+          const MoeRun rn = p.runs[t.run0 + ri];
+          const __nv_bfloat16* from = p.x_peer[rn.src] + static_cast<long long>(rn.src_row0) * p.K;
+          __nv_bfloat16* to = p.xin + static_cast<long long>(t.a_row0 + rn.tile_row0) * p.K;
+          const int n_vec = rn.rows * vec_per_row;
+          for (int i0 = t128; i0 < n_vec; i0 += 128 * 4) {
+            uint4 v[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (i0 + u * 128 < n_vec) v[u] = reinterpret_cast<const uint4*>(from)[i0 + u * 128];
+            for (int u = 0; u < 4; ++u)
+              if (i0 + u * 128 < n_vec) v[u] = reinterpret_cast<const uint4*>(from)[i0 + u * 128];
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (i0 + u * 128 < n_vec) reinterpret_cast<uint4*>(to)[i0 + u * 128] = v[u];
+            for (int u = 0; u < 4; ++u)
+              if (i0 + u * 128 < n_vec) reinterpret_cast<uint4*>(to)[i0 + u * 128] = v[u];
+          }
         }
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -293,7 +331,16 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
       tc_fence_after();
       const int lrow = q * 32 + lane;
       const bool row_ok = lrow < t.rows;
-      __nv_bfloat16* drow = p.out[t.out_dst] + static_cast<long long>(t.out_row0 + lrow) * p.ldd;
+      __nv_bfloat16* drow = p.out[p.rank] + static_cast<long long>(t.a_row0 + lrow) * p.ldd;
+      if (p.push && row_ok) {       // the row's source rank and sorted position there
+        for (int ri = 0; ri < t.nruns; ++ri) {
+          const MoeRun rn = p.runs[t.run0 + ri];
+          if (lrow >= rn.tile_row0 && lrow < rn.tile_row0 + rn.rows) {
+            drow = p.out[rn.src] + static_cast<long long>(rn.src_row0 + lrow - rn.tile_row0) * p.ldd;
+            break;
+          }
+        }
+      }
       const uint32_t tbase = tmem_base + buf * kEpBN + (static_cast<uint32_t>(q * 32) << 16);
       if (p.swiglu) {
 #pragma unroll 1
@@ -383,25 +430,27 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
 using namespace pm;
 
 extern "C" int pm_ep_prepare(const unsigned long long* offset_ptrs, const unsigned long long* pad_ptrs, int rank,
-                             int world, int e_loc, void* tiles1, void* tiles2, int max_tiles, int* counts_out,
+                             int world, int e_loc, void* tiles, void* runs, int max_tiles, int max_runs, int* counts_out,
                              double timeout_s, int* status, cudaStream_t st) {
-  if (world < 1 || world > kEpMaxRanks || rank < 0 || rank >= world || e_loc < 1) return -1;
+  if (world < 1 || world > kEpMaxRanks || rank < 0 || rank >= world || e_loc < 1 || e_loc > kEpMaxLocal) return -1;
   EpPtrs ptrs;
   for (int r = 0; r < kEpMaxRanks; ++r) {
     ptrs.offsets[r] = reinterpret_cast<const int*>(offset_ptrs[r < world ? r : rank]);
     ptrs.pads[r] = reinterpret_cast<uint32_t*>(pad_ptrs[r < world ? r : rank]);
   }
-  ep_prepare_kernel<<<1, 32, 0, st>>>(ptrs, rank, world, e_loc, static_cast<MoeTile*>(tiles1), static_cast<MoeTile*>(tiles2),
-                                      max_tiles, counts_out, static_cast<unsigned long long>(timeout_s * 1e9), status);
+  ep_prepare_kernel<<<1, 256, 0, st>>>(ptrs, rank, world, e_loc, static_cast<MoeTile*>(tiles), static_cast<MoeRun*>(runs),
+                                       max_tiles, max_runs, counts_out, static_cast<unsigned long long>(timeout_s * 1e9),
+                                       status);
   return static_cast<int>(cudaGetLastError());
 }
 
-// a_ptrs[r]: A buffer of map index r ([a_rows, K], row stride lda); w: [e_loc * N, K]; out_ptrs[r]: output base of rank r.
+// a: local A buffer [a_rows, K] (row stride lda): the staging buffer of the gate/up launch or the hidden rows of the
+// down launch; w: [e_loc * N, K]; out_ptrs[r]: output base of rank r (push = 0 uses out_ptrs[rank] only).
 // copy_src_ptrs (gate/up launch): rank r's sorted token buffer [*, K] (row stride K) that tiles are staged in from;
 // tile_ready: uint32 [max_tiles], zero-initialised once. Both null for the down projection.
-extern "C" int pm_moe_gemm(const unsigned long long* a_ptrs, int a_rows, int lda, const void* w, int ldw, int e_loc,
-                           const unsigned long long* out_ptrs, int ldd, const void* tiles, const int* n_tiles,
-                           int max_tiles, int N, int K, int swiglu, int rank, int world, int signal_pushed,
+extern "C" int pm_moe_gemm(const void* a, int a_rows, int lda, const void* w, int ldw, int e_loc,
+                           const unsigned long long* out_ptrs, int ldd, const void* tiles, const void* runs,
+                           const int* n_tiles, int max_tiles, int N, int K, int swiglu, int rank, int world, int push,
                            const unsigned long long* pad_ptrs, const unsigned long long* copy_src_ptrs, void* tile_ready,
                            double timeout_s, int* status, cudaStream_t st) {
   if (world < 1 || world > kEpMaxRanks || rank < 0 || rank >= world) return -1;
@@ -409,24 +458,25 @@ extern "C" int pm_moe_gemm(const unsigned long long* a_ptrs, int a_rows, int lda
   MoeMaps maps;
   MoeGemmParams p{};
   int rc;
+  if ((rc = operand_map(&maps.a, a, 0, a_rows, K, lda, kBM))) return rc * 10 - 5;
   for (int r = 0; r < kEpMaxRanks; ++r) {
     const int rr = r < world ? r : rank;
-    if ((rc = operand_map(&maps.a[r], reinterpret_cast<const void*>(a_ptrs[rr]), 0, a_rows, K, lda, kBM))) return rc * 10 - 5;
     p.out[r] = reinterpret_cast<__nv_bfloat16*>(out_ptrs[rr]);
     p.pads[r] = reinterpret_cast<uint32_t*>(pad_ptrs[rr]);
   }
   if ((rc = operand_map(&maps.b, w, 0, e_loc * N, K, ldw, kEpBN))) return rc * 10 - 6;
   p.tiles = static_cast<const MoeTile*>(tiles);
+  p.runs = static_cast<const MoeRun*>(runs);
   p.n_tiles = n_tiles;
   p.N = N; p.K = K; p.swiglu = swiglu; p.ldd = ldd; p.rank = rank; p.world = world;
-  p.signal_pushed = signal_pushed;
-  // stage-in: a_ptrs[rank] is the local staging buffer that all A maps cover; rows come from copy_src_ptrs[r]
+  p.push = push;
+  p.signal_pushed = push;
   p.stage_in = copy_src_ptrs != nullptr;
   if (p.stage_in) {
     if (!tile_ready || (K % 8)) return -3;
     for (int r = 0; r < kEpMaxRanks; ++r)
       p.x_peer[r] = reinterpret_cast<const __nv_bfloat16*>(copy_src_ptrs[r < world ? r : rank]);
-    p.xin = reinterpret_cast<__nv_bfloat16*>(a_ptrs[rank]);
+    p.xin = reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(a));
     p.tile_ready = static_cast<uint32_t*>(tile_ready);
   }
   p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);

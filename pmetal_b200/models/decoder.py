@@ -356,9 +356,9 @@ class DecoderLM(nn.Module):
         skinny = native and T <= GEMV_MAX_ROWS
         for li, layer in enumerate(self.layers):
             at = layer.self_attn
-            if skinny and isinstance(layer.mlp, MLP) and at.qkv_proj.gemv_ok(T) and layer.mlp.gate_up_proj.gemv_ok(T):
-                # decode: six launches per layer (norm+qkv, qk-norm+rope+cache append, attention, o+residual,
-                # norm+gate/up+SwiGLU, down+residual)
+            if skinny and at.qkv_proj.gemv_ok(T) and at.o_proj.gemv_ok(T):
+                # decode: six launches per dense layer (norm+qkv, qk-norm+rope+cache append, attention, o+residual,
+                # norm+gate/up+SwiGLU, down+residual); mixture-of-experts layers share the attention half
                 from ..ops import native as nat
                 eps = cfg.rms_norm_eps
                 qkv = at.qkv_proj.gemv_forward(x, layer.input_layernorm, eps)
@@ -366,8 +366,11 @@ class DecoderLM(nn.Module):
                                           cache.v[li], meta.slots)
                 o = nat.paged_attn(q, cache.k[li], cache.v[li], meta, d ** -0.5, at.window).view(T, hq * d)
                 h = at.o_proj.gemv_forward(o, residual=x)
-                act = layer.mlp.gate_up_proj.gemv_forward(h, layer.post_attention_layernorm, eps, swiglu=True)
-                x = layer.mlp.down_proj.gemv_forward(act, residual=h)
+                if isinstance(layer.mlp, MLP) and layer.mlp.gate_up_proj.gemv_ok(T):
+                    act = layer.mlp.gate_up_proj.gemv_forward(h, layer.post_attention_layernorm, eps, swiglu=True)
+                    x = layer.mlp.down_proj.gemv_forward(act, residual=h)
+                else:
+                    x = layer.mlp(ops.rms_norm(h, layer.post_attention_layernorm, eps), h)
                 continue
             n1 = ops.rms_norm(x, layer.input_layernorm, cfg.rms_norm_eps)
             qkv = at.qkv_proj(n1)

@@ -111,8 +111,9 @@ class FusedExpertMoE:
         self.w1 = interleave_gate_up(gate_up_local.to(torch.bfloat16)).reshape(self.e_loc * 2 * self.I, self.H)
         self.w2 = down_local.to(torch.bfloat16).contiguous().reshape(self.e_loc * self.H, self.I)
         self.max_rows = max_tokens * top_k
-        # worst case every peer routes everything here; tiles are 128-row blocks per (source, expert) segment
-        self.max_tiles = self.world * (self.max_rows // 128 + self.e_loc) + self.e_loc
+        # worst case every peer routes everything here; an expert's rows from all sources share 128-row tiles
+        self.max_tiles = self.world * self.max_rows // 128 + self.e_loc + 1
+        self.max_runs = self.max_tiles + self.world * self.e_loc
         self._keep = []
         self.sorted_x, self._x_ptrs = self._buf(self.max_rows * self.H, torch.bfloat16)
         self.z, self._z_ptrs = self._buf(self.max_rows * self.H, torch.bfloat16)
@@ -124,10 +125,9 @@ class FusedExpertMoE:
         arr = ctypes.c_ulonglong * self.world
         self._h_ptrs = arr(*([self.h.data_ptr()] * self.world))
         self.xin = torch.empty(self.max_tiles * 128, self.H, dtype=torch.bfloat16, device=dev)     # staged-in token rows
-        self._xin_ptrs = arr(*([self.xin.data_ptr()] * self.world))
         self.tile_ready = torch.zeros(self.max_tiles, dtype=torch.int32, device=dev)
-        self.tiles1 = torch.zeros(self.max_tiles * 8, dtype=torch.int32, device=dev)
-        self.tiles2 = torch.zeros(self.max_tiles * 8, dtype=torch.int32, device=dev)
+        self.tiles = torch.zeros(self.max_tiles * 8, dtype=torch.int32, device=dev)
+        self.runs = torch.zeros(self.max_runs * 4, dtype=torch.int32, device=dev)
         self.counts = torch.zeros(2, dtype=torch.int32, device=dev)
         if self.distributed:
             torch.cuda.synchronize()
@@ -162,23 +162,23 @@ class FusedExpertMoE:
         lib.pm_ep_prepare.restype = ctypes.c_int
         lib.pm_moe_gemm.restype = ctypes.c_int
         native._chk(lib.pm_ep_prepare(self._off_ptrs, self._pad_ptrs, ctypes.c_int(self.rank), ctypes.c_int(self.world),
-                                      ctypes.c_int(self.e_loc), native._p(self.tiles1), native._p(self.tiles2),
-                                      ctypes.c_int(self.max_tiles), native._p(self.counts), ctypes.c_double(self.timeout_s),
-                                      native._p(st), native._stream()), "pm_ep_prepare")
-        native._chk(lib.pm_moe_gemm(self._xin_ptrs, ctypes.c_int(self.max_tiles * 128), ctypes.c_int(self.H),
+                                      ctypes.c_int(self.e_loc), native._p(self.tiles), native._p(self.runs),
+                                      ctypes.c_int(self.max_tiles), ctypes.c_int(self.max_runs), native._p(self.counts),
+                                      ctypes.c_double(self.timeout_s), native._p(st), native._stream()), "pm_ep_prepare")
+        native._chk(lib.pm_moe_gemm(native._p(self.xin), ctypes.c_int(self.max_tiles * 128), ctypes.c_int(self.H),
                                     native._p(self.w1), ctypes.c_int(self.H), ctypes.c_int(self.e_loc), self._h_ptrs,
-                                    ctypes.c_int(self.I), native._p(self.tiles1), native._p(self.counts),
-                                    ctypes.c_int(self.max_tiles), ctypes.c_int(2 * self.I), ctypes.c_int(self.H),
-                                    ctypes.c_int(1), ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(0),
-                                    self._pad_ptrs, self._x_ptrs, native._p(self.tile_ready),
+                                    ctypes.c_int(self.I), native._p(self.tiles), native._p(self.runs),
+                                    native._p(self.counts), ctypes.c_int(self.max_tiles), ctypes.c_int(2 * self.I),
+                                    ctypes.c_int(self.H), ctypes.c_int(1), ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                    ctypes.c_int(0), self._pad_ptrs, self._x_ptrs, native._p(self.tile_ready),
                                     ctypes.c_double(self.timeout_s), native._p(st), native._stream()), "pm_moe_gemm")
-        native._chk(lib.pm_moe_gemm(self._h_ptrs, ctypes.c_int(self.max_tiles * 128), ctypes.c_int(self.I),
+        native._chk(lib.pm_moe_gemm(native._p(self.h), ctypes.c_int(self.max_tiles * 128), ctypes.c_int(self.I),
                                     native._p(self.w2), ctypes.c_int(self.I), ctypes.c_int(self.e_loc), self._z_ptrs,
-                                    ctypes.c_int(self.H), native._p(self.tiles2), native._p(self.counts),
-                                    ctypes.c_int(self.max_tiles), ctypes.c_int(self.H), ctypes.c_int(self.I), ctypes.c_int(0),
-                                    ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(1), self._pad_ptrs,
-                                    None, None, ctypes.c_double(self.timeout_s), native._p(st), native._stream()),
-                    "pm_moe_gemm")
+                                    ctypes.c_int(self.H), native._p(self.tiles), native._p(self.runs),
+                                    native._p(self.counts), ctypes.c_int(self.max_tiles), ctypes.c_int(self.H),
+                                    ctypes.c_int(self.I), ctypes.c_int(0), ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                    ctypes.c_int(1), self._pad_ptrs, None, None, ctypes.c_double(self.timeout_s),
+                                    native._p(st), native._stream()), "pm_moe_gemm")
         zz = self.z[: n * self.H].view(n, self.H)
         return native.moe_combine(zz, r["inv"], r["topk_w"], self.k)
 

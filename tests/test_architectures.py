@@ -1,0 +1,92 @@
+"""Portable architecture implementations against the Hugging Face implementations of the same families: tiny random
+models, identical weights (the checkpoint keys load as they are), logits compared; plus cache-consistency checks."""
+import pytest
+import torch
+
+tf = pytest.importorskip("transformers")
+
+from pmetal_b200.models.architectures.generic import GenericDecoderLM, arch_config_from_hf
+
+BASE = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=4, num_attention_heads=4,
+            num_key_value_heads=2, max_position_embeddings=256)
+
+CASES = {
+    "llama": ("LlamaForCausalLM", "LlamaConfig", dict(BASE)),
+    "llama3_scaled": ("LlamaForCausalLM", "LlamaConfig", dict(BASE, rope_parameters=dict(
+        rope_type="llama3", rope_theta=10000.0, factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+        original_max_position_embeddings=32))),
+    "mistral": ("MistralForCausalLM", "MistralConfig", dict(BASE, sliding_window=8)),
+    "mixtral": ("MixtralForCausalLM", "MixtralConfig", dict(BASE, num_local_experts=4, num_experts_per_tok=2)),
+    "qwen2": ("Qwen2ForCausalLM", "Qwen2Config", dict(BASE)),
+    "gemma": ("GemmaForCausalLM", "GemmaConfig", dict(BASE, head_dim=16)),
+    "gemma2": ("Gemma2ForCausalLM", "Gemma2Config", dict(BASE, head_dim=16, sliding_window=8, query_pre_attn_scalar=24)),
+    "gemma3": ("Gemma3ForCausalLM", "Gemma3TextConfig", dict(BASE, head_dim=16, sliding_window=8)),
+    "phi3": ("Phi3ForCausalLM", "Phi3Config", dict(BASE, pad_token_id=0)),
+    "phi": ("PhiForCausalLM", "PhiConfig", dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=2,
+                                                  num_attention_heads=4)),
+    "cohere": ("CohereForCausalLM", "CohereConfig", dict(BASE, use_qk_norm=True)),
+    "cohere2": ("Cohere2ForCausalLM", "Cohere2Config", dict(BASE, sliding_window=8)),
+    "granite": ("GraniteForCausalLM", "GraniteConfig", dict(BASE, embedding_multiplier=3.0, residual_multiplier=0.5,
+                                                            attention_multiplier=0.2, logits_scaling=2.0)),
+    "granitemoe": ("GraniteMoeForCausalLM", "GraniteMoeConfig", dict(BASE, num_local_experts=4, num_experts_per_tok=2,
+                                                                      attention_multiplier=0.2)),
+    "olmo2": ("Olmo2ForCausalLM", "Olmo2Config", dict(BASE)),
+    "gpt_oss": ("GptOssForCausalLM", "GptOssConfig", dict(BASE, head_dim=16, num_local_experts=4, num_experts_per_tok=2,
+                                                          sliding_window=8)),
+    "llama4": ("Llama4ForCausalLM", "Llama4TextConfig", dict(BASE, head_dim=16, intermediate_size_mlp=96,
+                                                             num_local_experts=4, num_experts_per_tok=1,
+                                                             attention_chunk_size=8, interleave_moe_layer_step=2,
+                                                             floor_scale=4, attn_scale=0.1)),
+    "deepseek_v2": ("DeepseekV2ForCausalLM", "DeepseekV2Config", dict(
+        BASE, num_key_value_heads=4, moe_intermediate_size=32, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
+        first_k_dense_replace=1, q_lora_rank=None, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16)),
+    "deepseek_v3": ("DeepseekV3ForCausalLM", "DeepseekV3Config", dict(
+        BASE, num_key_value_heads=4, moe_intermediate_size=32, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, n_group=2,
+        topk_group=1, first_k_dense_replace=1, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8,
+        v_head_dim=16)),
+}
+
+
+def _pair(name):
+    cls, cfg_cls, kw = CASES[name]
+    torch.manual_seed(0)
+    cfg = getattr(tf, cfg_cls)(**kw, attn_implementation="eager")
+    hf = getattr(tf, cls)(cfg).eval()
+    with torch.no_grad():                       # move every parameter off its initial value (norm weights, biases, sinks)
+        for p in hf.parameters():
+            if p.dim() < 2:
+                p.add_(torch.randn_like(p) * 0.1)
+        for n, b in hf.named_buffers():
+            if "e_score_correction_bias" in n:
+                b.copy_(torch.randn_like(b) * 0.1)
+    ours = GenericDecoderLM(arch_config_from_hf(cfg.to_dict())).eval()
+    missing, unexpected = ours.load_state_dict(hf.state_dict(), strict=False)
+    missing = [m for m in missing if "inv_freq" not in m]
+    unexpected = [u for u in unexpected if "inv_freq" not in u and not (ours.c.tie_embeddings and u == "lm_head.weight")]
+    assert not missing and not unexpected, (missing, unexpected)
+    return hf, ours
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_matches_hugging_face(name):
+    hf, ours = _pair(name)
+    ids = torch.randint(0, 128, (2, 24), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(input_ids=ids).logits.float()
+        got = ours(ids).float()
+    assert got.shape == ref.shape
+    assert torch.allclose(got, ref, atol=2e-4, rtol=2e-3), float((got - ref).abs().max())
+
+
+@pytest.mark.parametrize("name", ["llama", "gemma3", "cohere2", "gpt_oss", "llama4", "deepseek_v3"])
+def test_cached_decode_equals_full_forward(name):
+    _, ours = _pair(name)
+    ids = torch.randint(0, 128, (1, 20), generator=torch.Generator().manual_seed(2))
+    with torch.no_grad():
+        full = ours(ids)
+        cache = ours.new_cache()
+        a = ours(ids[:, :13], cache)
+        steps = [ours(ids[:, t:t + 1], cache) for t in range(13, 20)]
+    inc = torch.cat([a] + steps, 1)
+    assert torch.allclose(inc, full, atol=2e-4, rtol=2e-3), float((inc - full).abs().max())
+    assert len(ours.generate(ids[0, :5].tolist(), max_new_tokens=4)) == 4
