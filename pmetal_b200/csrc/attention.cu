@@ -17,6 +17,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 namespace pm {
 
 constexpr int kD = 128;     // head dim
@@ -653,6 +655,8 @@ struct PagedParams {
 };
 
 __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sK = smem + kTileBytes;       // 2 buffers
@@ -838,6 +842,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
 // Merge the per-slice partials: one warp per (query row, head).
 __global__ void paged_attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                           __nv_bfloat16* __restrict__ out, int rows, int n_split) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (gw >= rows) return;
@@ -907,13 +913,12 @@ extern "C" int pm_paged_attn(const void* q, const void* k_cache, const void* v_c
     once = true;
   }
   dim3 grid(num_seqs * p.q_tiles, hkv, n_split);
-  paged_attn_kernel<<<grid, kAttnThreads, smem, st>>>(p);
-  int e = static_cast<int>(cudaGetLastError());
+  int e = static_cast<int>(launch_pdl(paged_attn_kernel, grid, dim3(kAttnThreads), static_cast<size_t>(smem), st, p));
   if (e || n_split == 1) return e;
   const int rows = total_q * hq;
-  paged_attn_combine_kernel<<<(rows + 7) / 8, 256, 0, st>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), rows,
-                                                            n_split);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(paged_attn_combine_kernel, dim3((rows + 7) / 8), dim3(256), 0, st,
+                                     static_cast<const float*>(part_o), static_cast<const float*>(part_ml),
+                                     static_cast<__nv_bfloat16*>(out), rows, n_split));
 }
 
 extern "C" int pm_kv_append(const void* k, long long k_stride, const void* v, long long v_stride, void* k_cache,

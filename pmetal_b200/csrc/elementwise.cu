@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 namespace pm {
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -200,6 +202,8 @@ __global__ void qknorm_rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, 
                                          __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
                                          __nv_bfloat16* __restrict__ v_cache, const long long* __restrict__ slots, int T,
                                          int hq, int hkv, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int heads = hq + 2 * hkv;
@@ -622,11 +626,11 @@ extern "C" int pm_qknorm_rope_cache(const void* qkv, int ld, const void* qw, con
                                     const float* sn, void* q_out, void* k_cache, void* v_cache, const long long* slots,
                                     int T, int hq, int hkv, float eps, cudaStream_t st) {
   const long long warps = static_cast<long long>(T) * (hq + 2 * hkv);
-  qknorm_rope_cache_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, st>>>(
+  return static_cast<int>(launch_pdl(
+      qknorm_rope_cache_kernel, dim3(static_cast<unsigned>((warps + 7) / 8)), dim3(256), 0, st,
       static_cast<const __nv_bfloat16*>(qkv), ld, static_cast<const __nv_bfloat16*>(qw),
       static_cast<const __nv_bfloat16*>(kw), cs, sn, static_cast<__nv_bfloat16*>(q_out),
-      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), slots, T, hq, hkv, eps);
-  return PM_LAUNCH_CHECK();
+      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), slots, T, hq, hkv, eps));
 }
 extern "C" int pm_qknorm_rope_bwd(const void* dq, const void* dk, const void* qkv, int ld, const void* qw,
                                   const void* kw, const float* cs, const float* sn, void* dqkv, int T, int hq, int hkv,

@@ -16,6 +16,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "pdl.cuh"
+
 namespace pm {
 
 constexpr int kGvThreads = 256;
@@ -41,6 +43,7 @@ struct GemvParams {
   const float* lora_b;
   int r;
   int seg_end[4];                // cumulative output-row boundaries of the stacked projections (0x7fffffff padding)
+  int prefetch_iters;            // groups per warp whose weight rows are pulled into L2 before the dependency wait
 };
 
 __device__ __forceinline__ float gv_silu(float v) { return v / (1.f + __expf(-v)); }
@@ -53,6 +56,23 @@ __global__ void __launch_bounds__(kGvThreads) gemv_kernel(const GemvParams p) {
   __shared__ float s_rstd[MR];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int K = p.K;
+  const int n_groups = (p.N + C - 1) / C;
+
+  // ---- before the previous kernel's output is needed: let the next kernel be scheduled, and start pulling this
+  // warp's first weight rows into L2 (weights do not depend on the previous kernel)
+  pdl_launch_dependents();
+  {
+    const int per_group = C * (SWIGLU ? 2 : 1);
+    const unsigned row_bytes = static_cast<unsigned>(K) * 2u;
+    for (int idx = lane; idx < p.prefetch_iters * per_group; idx += 32) {
+      const int it = idx / per_group, j = idx - it * per_group;
+      const int g = blockIdx.x * kGvWarps + warp + it * gridDim.x * kGvWarps;
+      if (g >= n_groups) continue;
+      const int n = min(g * C + (j % C), p.N - 1) + (j >= C ? p.N : 0);
+      l2_prefetch_bulk(p.w + static_cast<long long>(n) * p.ldw, row_bytes);
+    }
+  }
+  pdl_wait();
 
   // ---- stage x (optionally RMS-normalised) into shared memory
   if (p.norm_w) {
@@ -98,7 +118,6 @@ __global__ void __launch_bounds__(kGvThreads) gemv_kernel(const GemvParams p) {
   __syncthreads();
 
   // ---- each warp walks groups of C output columns
-  const int n_groups = (p.N + C - 1) / C;
   for (int g = blockIdx.x * kGvWarps + warp; g < n_groups; g += gridDim.x * kGvWarps) {
     float acc[MR][C], acc2[MR][C];
 #pragma unroll
@@ -209,6 +228,164 @@ __global__ void __launch_bounds__(kGvThreads) gemv_kernel(const GemvParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core variant for up to 16 rows (no LoRA term): the rows of x are the 16-row A operand of mma.m16n8k16, eight
+// weight rows are the B operand, so the arithmetic per weight byte drops from ~4 CUDA-core instructions per row to a
+// fraction of one and the kernel is bound by the weight stream for every M <= 16.
+//
+// A CTA owns 8 output columns at a time; its 8 warps split K (warp w takes the 32-wide k chunks w, w + 8, ...), all
+// weight loads of a warp are issued before the activations are even staged, and the partial accumulators are summed
+// through shared memory. Each lane's 16-byte weight load (8 consecutive k of column lane / 4) feeds two MMAs: the MMA
+// only needs A and B to agree on which k sits in which fragment slot, so the slots are assigned to match the load
+// (lane group g = lane % 4 owns k = 8 g .. 8 g + 7 of the chunk; MMA j uses k = 8 g + 4 j + {0, 1} and {2, 3}), and
+// the A fragments are read from the staged x with the same assignment: one 16-byte shared load per row half.
+constexpr int kTcThreads = 256;
+constexpr int kTcWarps = 8;
+constexpr int kTcKU = 8;            // 16-byte weight loads in flight per lane (per gate/up half)
+constexpr int kTcPad = 32;          // row padding of the staged activations (bank spread for the fragment loads)
+
+__device__ __forceinline__ void mma_16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kTcThreads) gemv_tc_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) uint8_t gv_smem[];
+  const int K = p.K, lds = K + kTcPad;
+  __nv_bfloat16* sx = reinterpret_cast<__nv_bfloat16*>(gv_smem);                      // [16][lds]
+  float* red = reinterpret_cast<float*>(gv_smem + static_cast<size_t>(16) * lds * 2);   // [warps][2][128]
+  __shared__ float s_rstd[16];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane & 3, col = lane >> 2;
+  const int n_tiles = (p.N + 7) / 8;
+  const int rounds = (K + 255) / 256;            // 32-wide k chunks per warp
+
+  auto load_batch = [&](int tile, int r0, uint4 wv[kTcKU], uint4 wv2[SWIGLU ? kTcKU : 1]) {
+    const int n = min(tile * 8 + col, p.N - 1);
+    const __nv_bfloat16* wr = p.w + static_cast<long long>(n) * p.ldw;
+#pragma unroll
+    for (int u = 0; u < kTcKU; ++u) {
+      const int k = ((r0 + u) * kTcWarps + warp) * 32 + g * 8;
+      if (r0 + u < rounds && k < K) {
+        wv[u] = __ldg(reinterpret_cast<const uint4*>(wr + k));
+        if (SWIGLU) wv2[u] = __ldg(reinterpret_cast<const uint4*>(wr + static_cast<long long>(p.N) * p.ldw + k));
+      } else {
+        wv[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (SWIGLU) wv2[u] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+
+  // the first tile's weights are requested before anything that depends on the previous kernel's output
+  uint4 wv[kTcKU], wv2[SWIGLU ? kTcKU : 1];
+  int tile = blockIdx.x;
+  if (tile < n_tiles) load_batch(tile, 0, wv, wv2);
+
+  // ---- stage x (optionally RMS-normalised) as [16][K + pad]; rows >= M are zero
+  if (p.norm_w) {
+    for (int m = warp; m < p.M; m += kTcWarps) {
+      float ss = 0.f;
+      for (int k = lane * 8; k < K; k += 256) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p.x + static_cast<long long>(m) * p.ldx + k);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]);
+          ss += f.x * f.x + f.y * f.y;
+        }
+      }
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s_rstd[m] = rsqrtf(ss / static_cast<float>(K) + p.eps);
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < 16 * (K / 8); i += kTcThreads) {
+    const int m = i / (K / 8), k = (i - m * (K / 8)) * 8;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (m < p.M) {
+      raw = *reinterpret_cast<const uint4*>(p.x + static_cast<long long>(m) * p.ldx + k);
+      if (p.norm_w) {
+        const uint4 nw = *reinterpret_cast<const uint4*>(p.norm_w + k);
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+        const __nv_bfloat162* n2 = reinterpret_cast<const __nv_bfloat162*>(&nw);
+        const float rs = s_rstd[m];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]), gg = __bfloat1622float2(n2[e]);
+          const float a = __bfloat162float(__float2bfloat16(f.x * rs)) * gg.x;
+          const float b = __bfloat162float(__float2bfloat16(f.y * rs)) * gg.y;
+          h2[e] = __floats2bfloat162_rn(a, b);
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(sx + static_cast<long long>(m) * lds + k) = raw;
+  }
+  __syncthreads();
+
+  for (; tile < n_tiles; tile += gridDim.x) {
+    float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r0 = 0; r0 < rounds; r0 += kTcKU) {
+      if (r0 > 0) load_batch(tile, r0, wv, wv2);
+#pragma unroll
+      for (int u = 0; u < kTcKU; ++u) {
+        const int k = ((r0 + u) * kTcWarps + warp) * 32 + g * 8;
+        if (r0 + u >= rounds || k >= K) break;
+        const uint4 xa = *reinterpret_cast<const uint4*>(sx + col * lds + k);
+        const uint4 xb = *reinterpret_cast<const uint4*>(sx + (col + 8) * lds + k);
+        mma_16816(c, xa.x, xb.x, xa.y, xb.y, wv[u].x, wv[u].y);
+        mma_16816(c, xa.z, xb.z, xa.w, xb.w, wv[u].z, wv[u].w);
+        if (SWIGLU) {
+          mma_16816(c2, xa.x, xb.x, xa.y, xb.y, wv2[u].x, wv2[u].y);
+          mma_16816(c2, xa.z, xb.z, xa.w, xb.w, wv2[u].z, wv2[u].w);
+        }
+      }
+    }
+    // the next tile's first batch goes out before the reduction of this one
+    const int next = tile + gridDim.x;
+    if (next < n_tiles) load_batch(next, 0, wv, wv2);
+    float* my = red + (warp * 2) * 128;
+    *reinterpret_cast<float4*>(my + lane * 4) = make_float4(c[0], c[1], c[2], c[3]);
+    if (SWIGLU) *reinterpret_cast<float4*>(my + 128 + lane * 4) = make_float4(c2[0], c2[1], c2[2], c2[3]);
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      const int e = threadIdx.x;
+      float v = 0.f, v2 = 0.f;
+#pragma unroll
+      for (int w = 0; w < kTcWarps; ++w) {
+        v += red[(w * 2) * 128 + e];
+        if (SWIGLU) v2 += red[(w * 2 + 1) * 128 + e];
+      }
+      const int src = e >> 2, reg = e & 3;
+      const int m = (src >> 2) + ((reg & 2) ? 8 : 0), n = tile * 8 + (src & 3) * 2 + (reg & 1);
+      if (m < p.M && n < p.N) {
+        v *= p.alpha;
+        if (SWIGLU) v = gv_silu(v) * (v2 * p.alpha);
+        if (p.residual) v += __bfloat162float(p.residual[static_cast<long long>(m) * p.ldr + n]);
+        p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16(v);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+template <bool SWIGLU>
+static int launch_gemv_tc(const GemvParams& p, cudaStream_t st) {
+  const size_t smem = static_cast<size_t>(16) * (p.K + kTcPad) * 2 + kTcWarps * 2 * 128 * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 40 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = 200 * 1024;
+  }
+  const int n_tiles = (p.N + 7) / 8;
+  const int grid = n_tiles < 148 * 8 ? n_tiles : 148 * 8;
+  return static_cast<int>(launch_pdl(gemv_tc_kernel<SWIGLU>, dim3(grid), dim3(kTcThreads), smem, st, p));
+}
+
 template <int MR, int C, int KU, bool SWIGLU>
 static int launch_gemv(const GemvParams& p, cudaStream_t st) {
   const size_t smem = static_cast<size_t>(MR) * p.K * 2;
@@ -223,8 +400,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t st) {
   int grid = (groups + kGvWarps - 1) / kGvWarps;
   const int cap = 148 * 4;
   if (grid > cap) grid = cap;
-  gemv_kernel<MR, C, KU, SWIGLU><<<grid, kGvThreads, smem, st>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_pdl(gemv_kernel<MR, C, KU, SWIGLU>, dim3(grid), dim3(kGvThreads), smem, st, p));
 }
 
 }  // namespace pm
@@ -249,6 +425,19 @@ extern "C" int pm_gemv(const void* x, int ldx, const void* w, int ldw, const voi
   p.M = M; p.N = N; p.K = K; p.swiglu = swiglu; p.alpha = alpha;
   p.t = static_cast<const __nv_bfloat16*>(t); p.ldt = ldt; p.lora_b = lora_b; p.r = r;
   for (int i = 0; i < 4; ++i) p.seg_end[i] = seg_end ? seg_end[i] : 0x7fffffff;
+  static int prefetch = -1;
+  if (prefetch < 0) {
+    const char* e = getenv("PMETAL_GEMV_PREFETCH");
+    prefetch = e ? atoi(e) : 2;
+  }
+  p.prefetch_iters = prefetch;
+  static int use_tc = -1;
+  if (use_tc < 0) {
+    const char* e = getenv("PMETAL_GEMV_TC");
+    use_tc = e ? atoi(e) : 1;
+  }
+  if (use_tc && !t && (K % 32) == 0 && static_cast<size_t>(16) * (K + kTcPad) * 2 + 8192 <= 200 * 1024)
+    return swiglu ? launch_gemv_tc<true>(p, st) : launch_gemv_tc<false>(p, st);
   // wide outputs: several columns per warp; narrow outputs: one column per warp (so that every SM gets work) with a
   // deeper load pipeline instead
   const bool wide = N >= 148 * kGvWarps * 2;

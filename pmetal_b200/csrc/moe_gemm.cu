@@ -143,43 +143,73 @@ __global__ void ep_prepare_kernel(const EpPtrs ptrs, int rank, int world, int e_
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int n = 0, nr = 0;
-    bool overflow = false;
-    if (s_ok) {
-      for (int e = 0; e < e_loc && !overflow; ++e) {
-        MoeTile cur{};
-        int filled = kBM;            // forces a new tile at the start of every expert
-        for (int s = 0; s < world && !overflow; ++s) {
-          const int src = (rank + s) % world;    // own tokens first
-          int lo = s_off[s][e];
-          const int hi = s_off[s][e + 1];
-          while (lo < hi) {
-            if (filled == kBM) {
-              if (n > 0 && cur.rows > 0) tiles[n - 1] = cur;
-              if (n >= max_tiles) { overflow = true; break; }
-              cur = MoeTile{};
-              cur.a_row0 = n * kBM;
-              cur.expert = e;
-              cur.run0 = nr;
-              filled = 0;
-              ++n;
-            }
-            if (nr >= max_runs) { overflow = true; break; }
-            const int take = min(hi - lo, kBM - filled);
-            runs[nr++] = MoeRun{src, lo, filled, take};
-            cur.rows += take;
-            cur.nruns += 1;
-            filled += take;
-            lo += take;
-          }
+  // one thread per local expert: count its tiles and runs, scan, then write them at the expert's offsets
+  __shared__ int s_tiles[kEpMaxLocal], s_runs[kEpMaxLocal];
+  auto walk = [&](int e, int n, int nr, bool write) {
+    MoeTile cur{};
+    int filled = kBM, tiles_e = 0, runs_e = 0;
+    for (int s = 0; s < world; ++s) {
+      const int src = (rank + s) % world;    // own tokens first
+      int lo = s_off[s][e];
+      const int hi = s_off[s][e + 1];
+      while (lo < hi) {
+        if (filled == kBM) {
+          if (write && tiles_e > 0) tiles[n + tiles_e - 1] = cur;
+          cur = MoeTile{};
+          cur.a_row0 = (n + tiles_e) * kBM;
+          cur.expert = e;
+          cur.run0 = nr + runs_e;
+          filled = 0;
+          ++tiles_e;
         }
-        if (n > 0 && cur.rows > 0) tiles[n - 1] = cur;
+        const int take = min(hi - lo, kBM - filled);
+        if (write) runs[nr + runs_e] = MoeRun{src, lo, filled, take};
+        ++runs_e;
+        cur.rows += take;
+        cur.nruns += 1;
+        filled += take;
+        lo += take;
       }
     }
+    if (write && tiles_e > 0) tiles[n + tiles_e - 1] = cur;
+    if (!write) {
+      s_tiles[e] = tiles_e;
+      s_runs[e] = runs_e;
+    }
+  };
+  for (int e = threadIdx.x; e < e_loc; e += blockDim.x) {
+    if (s_ok) {
+      walk(e, 0, 0, false);
+    } else {
+      s_tiles[e] = 0;
+      s_runs[e] = 0;
+    }
+  }
+  __syncthreads();
+  for (int off = 1; off < e_loc; off <<= 1) {       // inclusive scan over the local experts
+    int t[2] = {0, 0}, r[2] = {0, 0};
+    for (int j = 0, e = threadIdx.x; e < e_loc && j < 2; e += blockDim.x, ++j)
+      if (e >= off) {
+        t[j] = s_tiles[e - off];
+        r[j] = s_runs[e - off];
+      }
+    __syncthreads();
+    for (int j = 0, e = threadIdx.x; e < e_loc && j < 2; e += blockDim.x, ++j) {
+      s_tiles[e] += t[j];
+      s_runs[e] += r[j];
+    }
+    __syncthreads();
+  }
+  const int n_total = s_tiles[e_loc - 1], r_total = s_runs[e_loc - 1];
+  const bool overflow = n_total > max_tiles || r_total > max_runs;
+  if (!overflow && s_ok)
+    for (int e = threadIdx.x; e < e_loc; e += blockDim.x)
+      walk(e, e ? s_tiles[e - 1] : 0, e ? s_runs[e - 1] : 0, true);
+  __syncthreads();
+  if (threadIdx.x == 0) {
     if (overflow) atomicCAS(status, 0, kStatusEpOverflow);
-    counts_out[0] = overflow ? 0 : n;
-    counts_out[1] = n * kBM;
+    counts_out[0] = overflow ? 0 : n_total;
+    counts_out[1] = n_total * kBM;
     __threadfence();
     my_pad[kEpEpoch] = epoch;
   }

@@ -31,6 +31,7 @@ ALL_PROJ = ATTN_PROJ + MLP_PROJ
 
 
 # rows up to which linear layers run on the bandwidth-bound mat-vec kernel instead of tensor-core tiles (decode)
+DECODE_MEGA = os.environ.get("PMETAL_DECODE_MEGA", "1") == "1"
 GEMV_MAX_ROWS = int(os.environ.get("PMETAL_GEMV_MAX_ROWS", "16"))
 
 
@@ -354,7 +355,20 @@ class DecoderLM(nn.Module):
         rope = ops.rope_table(meta.positions, d, cfg.rope_theta, cfg.rope_scale)
         T = x.shape[0]
         skinny = native and T <= GEMV_MAX_ROWS
-        for li, layer in enumerate(self.layers):
+        layers = self.layers
+        if skinny and DECODE_MEGA and meta.max_q == 1 and T == meta.block_table.shape[0] and self._mega_ok(T):
+            # every layer of the step in one cooperative launch (csrc/decode_mega.cu)
+            from ..ops import native as nat
+            table = self._mega_table(cache)
+            ns = nat.decode_splits(T, hkv, meta.max_kv)
+            sc = self._mega_scratch.get((T, ns))
+            if sc is None:
+                sc = self._mega_scratch[(T, ns)] = nat.decode_scratch(T, cfg.hidden_size, hq, hkv, cfg.intermediate_size,
+                                                                      ns, x.device)
+            x = nat.decode_layers(table, len(self.layers), x.contiguous(), sc, rope[0], rope[1], meta, hq, hkv,
+                                  cfg.intermediate_size, cfg.rms_norm_eps, d ** -0.5)
+            layers = ()
+        for li, layer in enumerate(layers):
             at = layer.self_attn
             if skinny and at.qkv_proj.gemv_ok(T) and at.o_proj.gemv_ok(T):
                 # decode: six launches per dense layer (norm+qkv, qk-norm+rope+cache append, attention, o+residual,
@@ -395,6 +409,46 @@ class DecoderLM(nn.Module):
             return nat.gemv(x.contiguous(), head, self.norm, cfg.rms_norm_eps)      # final norm fused into the head
         x = ops.rms_norm(x, self.norm, cfg.rms_norm_eps)
         return x if return_hidden else self.logits(x)
+
+    def _mega_ok(self, T: int) -> bool:
+        """The whole-step kernel covers dense layers with plain bf16 weights: no adapters, biases, sliding windows or
+        soft-capping."""
+        ok = getattr(self, "_mega_ok_cached", None)
+        if ok is None:
+            cfg = self.cfg
+            ok = cfg.attn_logit_softcap <= 0 and cfg.head_dim == 128
+            for layer in self.layers:
+                at = layer.self_attn
+                if not isinstance(layer.mlp, MLP) or at.window:
+                    ok = False
+                    break
+                for lin in (at.qkv_proj, at.o_proj, layer.mlp.gate_up_proj, layer.mlp.down_proj):
+                    if not lin.gemv_ok(1) or lin.lora_a is not None or not lin.weight.is_contiguous():
+                        ok = False
+            self._mega_ok_cached = ok
+            self._mega_scratch = {}
+            self._mega_tables = {}
+        if not ok:
+            return False
+        from ..ops import native as nat
+        cfg = self.cfg
+        return nat.decode_layers_supported(T, cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads,
+                                           cfg.intermediate_size)
+
+    def _mega_table(self, cache) -> torch.Tensor:
+        t = self._mega_tables.get(id(cache))
+        if t is None:
+            rows = []
+            for li, layer in enumerate(self.layers):
+                at, mlp = layer.self_attn, layer.mlp
+                rows.append([layer.input_layernorm.data_ptr(), at.qkv_proj.weight.data_ptr(),
+                             at.q_norm.data_ptr() if at.q_norm is not None else 0,
+                             at.k_norm.data_ptr() if at.k_norm is not None else 0, at.o_proj.weight.data_ptr(),
+                             layer.post_attention_layernorm.data_ptr(), mlp.gate_up_proj.weight.data_ptr(),
+                             mlp.down_proj.weight.data_ptr(), cache.k[li].data_ptr(), cache.v[li].data_ptr()])
+            t = torch.tensor(rows, dtype=torch.int64, device=self.embed_tokens.device)
+            self._mega_tables[id(cache)] = t
+        return t
 
     def _paged_attention_reference(self, qkv, at, rope, cache, meta, li):
         from ..ops import reference as ref

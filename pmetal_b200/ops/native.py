@@ -667,3 +667,39 @@ def gemv(x, w, norm_w=None, eps: float = 1e-6, residual=None, swiglu: bool = Fal
                        c_int(K), c_int(int(swiglu)), c_float(alpha), _p(t), c_int(t.stride(0) if t is not None else 0),
                        _p(lora_b), c_int(r), ends, _stream()), "pm_gemv")
     return y
+
+
+# ------------------------------------------------------------------------------------------- whole-step decode kernel
+def decode_layers_supported(M: int, H: int, hq: int, hkv: int, I: int) -> bool:
+    return bool(lib().pm_decode_layers_supported(c_int(M), c_int(H), c_int(hq), c_int(hkv), c_int(I)))
+
+
+def decode_layers(table, n_layers: int, x, scratch: dict, cos, sin, meta, hq: int, hkv: int, I: int, eps: float,
+                  scale: float):
+    """All decoder layers of one decode step in a single cooperative launch (csrc/decode_mega.cu). ``table`` is the
+    int64 device tensor of per-layer pointers, ``x`` [M, H] bf16 is updated in place, ``scratch`` holds the work
+    buffers made by ``decode_scratch``."""
+    M, H = x.shape
+    scratch["bar"].zero_()
+    _chk(lib().pm_decode_layers(_p(table), c_int(n_layers), c_int(M), c_int(H), c_int(hq), c_int(hkv), c_int(I),
+                                c_float(eps), c_float(scale), _p(x), _p(scratch["h"]), _p(scratch["qkv"]),
+                                _p(scratch["attn"]), _p(scratch["act"]), _p(scratch["part_o"]), _p(scratch["part_ml"]),
+                                _p(scratch["counters"]), _p(cos), _p(sin), _p(meta.block_table), _p(meta.seq_lens),
+                                _p(meta.slots), c_int(meta.block_table.shape[1]), c_int(scratch["n_split"]),
+                                _p(scratch["bar"]), _p(status_word(x.device)), _p(scratch.get("trace")), _stream()),
+         "pm_decode_layers")
+    return x
+
+
+def decode_splits(M: int, hkv: int, max_kv: int) -> int:
+    """CTAs per (row, kv head) in the attention phase: fill the grid, at least 64 keys per CTA, at most 16."""
+    return max(1, min(148 // max(M * hkv, 1), 16, max(max_kv // 64, 1)))
+
+
+def decode_scratch(M: int, H: int, hq: int, hkv: int, I: int, n_split: int, device) -> dict:
+    bf = dict(dtype=torch.bfloat16, device=device)
+    return dict(h=torch.empty(M, H, **bf), qkv=torch.empty(M, (hq + 2 * hkv) * 128, **bf), attn=torch.empty(M, hq * 128, **bf),
+                act=torch.empty(M, I, **bf), part_o=torch.empty(n_split, M, hq, 128, dtype=torch.float32, device=device),
+                part_ml=torch.empty(n_split, M, hq, 2, dtype=torch.float32, device=device),
+                counters=torch.zeros(M * hkv, dtype=torch.int32, device=device),
+                bar=torch.zeros(2, dtype=torch.int32, device=device), n_split=n_split)

@@ -303,3 +303,19 @@ def test_gemv_swiglu_and_lora():
         ref3[:, o:o + sz] += t3.float()[:, i * r:(i + 1) * r] @ b3[o:o + sz].t()
         o += sz
     assert (y3.float() - ref3).abs().max() <= 0.03 * ref3.abs().max() + 2e-2
+
+
+@pytest.mark.parametrize("M,K,I", [(1, 1024, 3072), (11, 2048, 768), (16, 1024, 1000)])
+def test_gemv_tensor_core_swiglu(M, K, I):
+    """SwiGLU epilogue of the tensor-core mat-vec (no LoRA term): gate rows [0, I), up rows [I, 2I)."""
+    nat = _nat()
+    torch.manual_seed(M)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(2 * I, K, device="cuda") * K ** -0.5).bfloat16()
+    nw = (1 + 0.1 * torch.randn(K, device="cuda")).bfloat16()
+    y = nat.gemv(x, w, norm_w=nw, eps=1e-6, swiglu=True)
+    xn = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)
+    full = (xn.bfloat16().float() * nw.float()).bfloat16().float() @ w.float().t()
+    ref = torch.nn.functional.silu(full[:, :I]) * full[:, I:]
+    assert y.shape == (M, I)
+    assert (y.float() - ref).abs().max() <= 0.03 * ref.abs().max() + 2e-2
