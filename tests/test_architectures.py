@@ -90,3 +90,86 @@ def test_cached_decode_equals_full_forward(name):
     inc = torch.cat([a] + steps, 1)
     assert torch.allclose(inc, full, atol=2e-4, rtol=2e-3), float((inc - full).abs().max())
     assert len(ours.generate(ids[0, :5].tolist(), max_new_tokens=4)) == 4
+
+
+# ---------------------------------------------------------------------------------------------- encoders
+def _load(ours, hf, allow_unexpected=()):
+    missing, unexpected = ours.load_state_dict(hf.state_dict(), strict=False)
+    unexpected = [u for u in unexpected if not any(a in u for a in allow_unexpected)]
+    assert not missing and not unexpected, (missing, unexpected)
+
+
+def test_bert_matches_hugging_face_and_pools():
+    from pmetal_b200.models.architectures.encoders import BertModel
+    torch.manual_seed(0)
+    cfg = tf.BertConfig(vocab_size=100, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                        max_position_embeddings=64, attn_implementation="eager")
+    hf = tf.BertModel(cfg).eval()
+    ours = BertModel(cfg.to_dict()).eval()
+    _load(ours, hf, ("position_ids",))
+    ids = torch.randint(0, 100, (2, 12))
+    mask = torch.ones(2, 12, dtype=torch.long)
+    mask[1, 8:] = 0
+    with torch.no_grad():
+        ref = hf(input_ids=ids, attention_mask=mask)
+        got = ours(ids, mask)
+    assert torch.allclose(got[0], ref.last_hidden_state[0], atol=1e-5)
+    assert torch.allclose(got[1, :8], ref.last_hidden_state[1, :8], atol=1e-5)
+    assert torch.allclose(ours.pool(got, mask, "pooler", normalize=False), ref.pooler_output, atol=1e-5)
+    mean = ours.pool(got, mask, "mean")
+    assert torch.allclose(mean.norm(dim=-1), torch.ones(2), atol=1e-5)
+    assert torch.allclose(ours.pool(got, mask, "last", False)[1], got[1, 7])
+
+
+def test_t5_matches_hugging_face():
+    from pmetal_b200.models.architectures.encoders import T5Model
+    torch.manual_seed(0)
+    for proj, tie in (("gated-gelu", False), ("relu", True)):
+        cfg = tf.T5Config(vocab_size=100, d_model=32, d_kv=8, d_ff=64, num_layers=2, num_heads=4, feed_forward_proj=proj,
+                          tie_word_embeddings=tie, decoder_start_token_id=0)
+        hf = tf.T5ForConditionalGeneration(cfg).eval()
+        ours = T5Model(dict(cfg.to_dict(), tie_word_embeddings=tie)).eval()
+        _load(ours, hf, ("lm_head",) if tie else ())
+        src, tgt = torch.randint(0, 100, (2, 11)), torch.randint(0, 100, (2, 7))
+        with torch.no_grad():
+            ref = hf(input_ids=src, decoder_input_ids=tgt).logits
+            got = ours(src, tgt)
+        assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), float((got - ref).abs().max())
+
+
+def test_clip_matches_hugging_face():
+    from pmetal_b200.models.architectures.encoders import ClipModel
+    torch.manual_seed(0)
+    cfg = tf.CLIPConfig(text_config=dict(vocab_size=100, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                         num_attention_heads=4, max_position_embeddings=16, eos_token_id=2),
+                        vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                                           num_attention_heads=4, image_size=32, patch_size=8), projection_dim=24)
+    hf = tf.CLIPModel(cfg).eval()
+    ours = ClipModel(cfg.to_dict()).eval()
+    _load(ours, hf, ("position_ids",))
+    ids = torch.randint(3, 99, (3, 9))
+    ids[:, -1] = 99                                  # the end-of-text token has the highest id
+    px = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        ref = hf(input_ids=ids, pixel_values=px)
+        per_image, per_text = ours(ids, px)
+    assert torch.allclose(per_image, ref.logits_per_image, atol=1e-4)
+    assert torch.allclose(per_text, ref.logits_per_text, atol=1e-4)
+
+
+def test_whisper_matches_hugging_face():
+    from pmetal_b200.models.architectures.encoders import WhisperModel
+    torch.manual_seed(0)
+    cfg = tf.WhisperConfig(vocab_size=100, d_model=32, encoder_layers=2, decoder_layers=2, encoder_attention_heads=4,
+                           decoder_attention_heads=4, encoder_ffn_dim=64, decoder_ffn_dim=64, num_mel_bins=16,
+                           max_source_positions=50, max_target_positions=32, pad_token_id=0, bos_token_id=1,
+                           eos_token_id=2, decoder_start_token_id=1, suppress_tokens=None, begin_suppress_tokens=None)
+    hf = tf.WhisperForConditionalGeneration(cfg).eval()
+    ours = WhisperModel(cfg.to_dict()).eval()
+    _load(ours, hf, ("proj_out",))
+    mel, tgt = torch.randn(2, 16, 100), torch.randint(0, 100, (2, 6))
+    with torch.no_grad():
+        ref = hf(input_features=mel, decoder_input_ids=tgt).logits
+        got = ours(mel, tgt)
+    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), float((got - ref).abs().max())
+    assert len(ours.transcribe(mel[:1], [1], max_new_tokens=3)) == 4
