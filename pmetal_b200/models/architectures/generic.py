@@ -93,6 +93,14 @@ class ArchConfig:
     n_shared_experts: int = 0
     shared_name: str = "shared_experts"
     shared_gate: bool = False         # qwen: sigmoid gate on the shared expert
+    shared_intermediate: int = 0      # size of the shared expert when it is not n_shared_experts * moe_intermediate
+    # gated attention output and gated-delta-net layers (qwen3-next)
+    attn_output_gate: bool = False
+    lin_v_heads: int = 0
+    lin_k_heads: int = 0
+    lin_k_dim: int = 0
+    lin_v_dim: int = 0
+    lin_conv: int = 4
     # multi-head latent attention (deepseek)
     mla: bool = False
     q_lora_rank: int = 0
@@ -148,8 +156,8 @@ def arch_config_from_hf(d: dict) -> ArchConfig:
     c.o_bias = c.attn_bias
     lt = d.get("layer_types")
     if lt:
-        c.layer_types = [{"full_attention": "full", "sliding_attention": "sliding", "chunked_attention": "chunked"}.get(t, t)
-                         for t in lt]
+        c.layer_types = [{"full_attention": "full", "sliding_attention": "sliding", "chunked_attention": "chunked",
+                          "linear_attention": "linear"}.get(t, t) for t in lt]
     sw = d.get("sliding_window") or 0
     if mt in ("llama", "llama3"):
         pass
@@ -172,6 +180,29 @@ def arch_config_from_hf(d: dict) -> ArchConfig:
             c.num_experts, c.top_k = d["num_experts"], d["num_experts_per_tok"]
             c.moe_intermediate = d["moe_intermediate_size"]
             c.norm_topk_prob = bool(d.get("norm_topk_prob", False))
+            step, only = d.get("decoder_sparse_step", 1), set(d.get("mlp_only_layers") or [])
+            c.mlp_types = ["moe" if (i not in only and (i + 1) % step == 0) else "dense" for i in range(L)]
+    elif mt in ("qwen3_next", "qwen3_5", "qwen3.5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text"):
+        c.norm, c.qk_norm, c.attn_output_gate = "rms_plus1", "head", True
+        c.norm_eps = d.get("rms_norm_eps", 1e-6)
+        prf = (d.get("rope_parameters") or {}).get("partial_rotary_factor", d.get("partial_rotary_factor", 0.25))
+        c.rope_dim = int(c.head_dim * prf)
+        if c.rope_scaling:
+            c.rope_scaling = {k: v for k, v in c.rope_scaling.items() if k != "partial_rotary_factor"}
+            if c.rope_scaling.get("rope_type", "default") == "default":
+                c.rope_scaling = None
+        if not lt:
+            step = d.get("full_attention_interval", 4)
+            c.layer_types = ["full" if (i + 1) % step == 0 else "linear" for i in range(L)]
+        c.lin_v_heads, c.lin_k_heads = d.get("linear_num_value_heads", 32), d.get("linear_num_key_heads", 16)
+        c.lin_k_dim, c.lin_v_dim = d.get("linear_key_head_dim", 128), d.get("linear_value_head_dim", 128)
+        c.lin_conv = d.get("linear_conv_kernel_dim", 4)
+        c.num_experts, c.top_k = d.get("num_experts", 0), d.get("num_experts_per_tok", 0)
+        c.moe_intermediate = d.get("moe_intermediate_size", 0)
+        c.norm_topk_prob = bool(d.get("norm_topk_prob", True))
+        if c.num_experts:
+            c.n_shared_experts, c.shared_name, c.shared_gate = 1, "shared_expert", True
+            c.shared_intermediate = d.get("shared_expert_intermediate_size", c.moe_intermediate)
             step, only = d.get("decoder_sparse_step", 1), set(d.get("mlp_only_layers") or [])
             c.mlp_types = ["moe" if (i not in only and (i + 1) % step == 0) else "dense" for i in range(L)]
     elif mt in ("gemma", "gemma2", "gemma3", "gemma3_text"):
@@ -432,7 +463,7 @@ class Attention(nn.Module):
         if c.fused_qkv:
             self.qkv_proj = nn.Linear(H, (c.n_heads + 2 * c.n_kv_heads) * d, bias=c.attn_bias)
         else:
-            self.q_proj = nn.Linear(H, c.n_heads * d, bias=c.attn_bias)
+            self.q_proj = nn.Linear(H, c.n_heads * d * (2 if c.attn_output_gate else 1), bias=c.attn_bias)
             self.k_proj = nn.Linear(H, c.n_kv_heads * d, bias=c.attn_bias)
             self.v_proj = nn.Linear(H, c.n_kv_heads * d, bias=c.attn_bias)
         setattr(self, c.attn_out_name, nn.Linear(c.n_heads * d, H, bias=c.o_bias))
@@ -456,6 +487,10 @@ class Attention(nn.Module):
             q, k, v = self.qkv_proj(x).split((c.n_heads * d, c.n_kv_heads * d, c.n_kv_heads * d), -1)
         else:
             q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        gate = None
+        if c.attn_output_gate:          # per head: [query (d) | gate (d)]
+            q, gate = q.view(B, T, c.n_heads, 2 * d).chunk(2, -1)
+            q, gate = q.reshape(B, T, c.n_heads * d), gate.reshape(B, T, c.n_heads * d)
         if self.qn_kind == "flat":
             q, k = self.q_norm(q), self.k_norm(k)
         q, k, v = q.view(B, T, c.n_heads, d), k.view(B, T, c.n_kv_heads, d), v.view(B, T, c.n_kv_heads, d)
@@ -477,7 +512,74 @@ class Attention(nn.Module):
         mask = build_mask(self.kind, positions, k_positions, c.sliding_window, c.chunk_size)
         scale = (c.attn_scale or d ** -0.5) * rope.get("attention_factor", 1.0) ** 2
         o = attend(q, k, v, mask, scale, c.attn_softcap, self.sinks if c.sinks else None)
-        return getattr(self, c.attn_out_name)(o.transpose(1, 2).reshape(B, T, c.n_heads * d))
+        o = o.transpose(1, 2).reshape(B, T, c.n_heads * d)
+        if gate is not None:
+            o = o * torch.sigmoid(gate)
+        return getattr(self, c.attn_out_name)(o)
+
+
+class GatedDeltaNet(nn.Module):
+    """Linear-attention layer of the Qwen3-Next hybrids: short causal depthwise convolution over (q, k, v), gated delta
+    rule recurrence per value head, gated RMSNorm of the read-out (crates/pmetal-models/src/architectures/qwen3_next.rs;
+    the recurrence itself is models/gdn.py)."""
+
+    def __init__(self, c: ArchConfig, idx: int):
+        super().__init__()
+        self.c, self.idx = c, idx
+        self.key_dim, self.value_dim = c.lin_k_dim * c.lin_k_heads, c.lin_v_dim * c.lin_v_heads
+        conv_dim = 2 * self.key_dim + self.value_dim
+        self.conv1d = nn.Conv1d(conv_dim, conv_dim, c.lin_conv, groups=conv_dim, padding=c.lin_conv - 1, bias=False)
+        self.in_proj_qkvz = nn.Linear(c.hidden_size, 2 * self.key_dim + 2 * self.value_dim, bias=False)
+        self.in_proj_ba = nn.Linear(c.hidden_size, 2 * c.lin_v_heads, bias=False)
+        self.dt_bias = nn.Parameter(torch.ones(c.lin_v_heads))
+        self.A_log = nn.Parameter(torch.log(torch.empty(c.lin_v_heads).uniform_(0, 16)))
+        self.norm = Norm(c.lin_v_dim, "rms", c.norm_eps)
+        self.out_proj = nn.Linear(self.value_dim, c.hidden_size, bias=False)
+
+    def forward(self, x, rope, positions, cache: Optional[KVCache], k_positions):
+        from ..gdn import gdn_chunked, gdn_recurrent
+        c = self.c
+        B, T, _ = x.shape
+        hk, hv, dk, dv = c.lin_k_heads, c.lin_v_heads, c.lin_k_dim, c.lin_v_dim
+        r = hv // hk
+        qkvz = self.in_proj_qkvz(x).view(B, T, hk, 2 * dk + 2 * r * dv)
+        ba = self.in_proj_ba(x).view(B, T, hk, 2 * r)
+        q, k, v, z = qkvz.split((dk, dk, r * dv, r * dv), -1)
+        b, a = ba.split((r, r), -1)
+        v, z = v.reshape(B, T, hv, dv), z.reshape(B, T, hv, dv)
+        b, a = b.reshape(B, T, hv), a.reshape(B, T, hv)
+        mixed = torch.cat((q.reshape(B, T, -1), k.reshape(B, T, -1), v.reshape(B, T, -1)), -1).transpose(1, 2)
+        st = cache.state.get(self.idx) if cache is not None else None
+        kw = c.lin_conv
+        prev = st[0] if st is not None else mixed.new_zeros(B, mixed.shape[1], kw - 1)
+        full = torch.cat((prev, mixed), -1)
+        conv = F.silu(F.conv1d(full, self.conv1d.weight, None, groups=full.shape[1]))[:, :, -T:].transpose(1, 2)
+        q, k, v = conv.split((self.key_dim, self.key_dim, self.value_dim), -1)
+        q, k, v = q.reshape(B, T, hk, dk), k.reshape(B, T, hk, dk), v.reshape(B, T, hv, dv)
+        beta = torch.sigmoid(b)
+        g = torch.exp(-self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias))
+        if r > 1:
+            q, k = q.repeat_interleave(r, 2), k.repeat_interleave(r, 2)
+        qf, kf = q.float(), k.float()
+        qf = qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
+        kf = kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
+        outs, states = [], []
+        for i in range(B):
+            S0 = st[1][i] if st is not None else None
+            fn = gdn_recurrent if T <= 4 else gdn_chunked
+            y, S = fn(qf[i], kf[i], v[i].float(), g[i], beta[i].float(), S0)
+            outs.append(y)
+            states.append(S)
+        if cache is not None:
+            cache.state[self.idx] = (full[:, :, -(kw - 1):].detach(), torch.stack(states))
+            cache.state["length"] = int(cache.state.get("length", 0)) if self.idx != self._first_linear() else \
+                int(cache.state.get("length", 0)) + T
+        y = torch.stack(outs).to(x.dtype)                                          # [B, T, hv, dv]
+        y = (self.norm(y).float() * F.silu(z.float())).to(x.dtype)
+        return self.out_proj(y.reshape(B, T, hv * dv))
+
+    def _first_linear(self) -> int:
+        return next(i for i in range(self.c.num_layers) if self.c.layer_type(i) == "linear")
 
 
 class LatentAttention(nn.Module):
@@ -647,7 +749,7 @@ class MoE(nn.Module):
         else:
             self.experts = Experts(c)
         if c.n_shared_experts:
-            shared = MLP(_dense_view(c), c.moe_intermediate * c.n_shared_experts)
+            shared = MLP(_dense_view(c), c.shared_intermediate or c.moe_intermediate * c.n_shared_experts)
             setattr(self, c.shared_name, shared)
             if c.shared_gate:
                 self.shared_expert_gate = nn.Linear(c.hidden_size, 1, bias=False)
@@ -695,7 +797,11 @@ class Block(nn.Module):
     def __init__(self, c: ArchConfig, idx: int):
         super().__init__()
         self.c = c
-        self.self_attn = LatentAttention(c, idx) if c.mla else Attention(c, idx)
+        if c.layer_type(idx) == "linear":
+            self.linear_attn = GatedDeltaNet(c, idx)
+        else:
+            self.self_attn = LatentAttention(c, idx) if c.mla else Attention(c, idx)
+        self._mix = lambda: self.linear_attn if c.layer_type(idx) == "linear" else self.self_attn
         if c.mlp_type(idx) == "moe":
             setattr(self, c.moe_name, MoE(c))
             self._ff = lambda: getattr(self, c.moe_name)
@@ -718,14 +824,14 @@ class Block(nn.Module):
         ff = self._ff()
         if c.block == "parallel":
             n = self.input_layernorm(x)
-            return x + self.self_attn(n, rope, positions, cache, k_positions) + ff(n)
+            return x + self._mix()(n, rope, positions, cache, k_positions) + ff(n)
         if c.block == "sandwich":
-            x = x + self.post_attention_layernorm(self.self_attn(self.input_layernorm(x), rope, positions, cache, k_positions))
+            x = x + self.post_attention_layernorm(self._mix()(self.input_layernorm(x), rope, positions, cache, k_positions))
             return x + self.post_feedforward_layernorm(ff(self.pre_feedforward_layernorm(x)))
         if c.block == "post":
-            x = x + self.post_attention_layernorm(self.self_attn(x, rope, positions, cache, k_positions))
+            x = x + self.post_attention_layernorm(self._mix()(x, rope, positions, cache, k_positions))
             return x + self.post_feedforward_layernorm(ff(x))
-        x = x + rm * self.self_attn(self.input_layernorm(x), rope, positions, cache, k_positions)
+        x = x + rm * self._mix()(self.input_layernorm(x), rope, positions, cache, k_positions)
         return x + rm * ff(self.post_attention_layernorm(x))
 
 

@@ -45,7 +45,10 @@ def gdn_chunked(q, k, v, g, beta, S0=None, chunk: int = 64):
         logg = torch.log(gc.clamp(min=1e-30))
         cum = torch.cumsum(logg, -1)                                                # log prod_{s<=t} g_s
         # decay from token s (exclusive) to token t (inclusive): exp(cum_t - cum_s) for s <= t
-        dec = torch.exp(cum[:, :, None] - cum[:, None, :])                          # [H, C(t), C(s)]
+        # [H, C(t), C(s)]; entries above the diagonal are never used and would overflow for strong decay, so they are
+        # forced to exp(-inf) = 0 before the exponential
+        causal = torch.ones(C, C, device=q.device, dtype=torch.bool).tril(0)
+        dec = torch.exp((cum[:, :, None] - cum[:, None, :]).masked_fill(~causal, float("-inf")))
         tri = torch.ones(C, C, device=q.device).tril(-1)
         # u_t = beta_t (v_t - k_t S_{t-1} g-decayed), with S_{t-1} = dec * S_in + sum_{s<t} dec(t-1.. ) k_s^T u_s
         # k_t (state before write t, after decay t) = exp(cum_t) k_t S_in + sum_{s<t} exp(cum_t - cum_s) (k_t . k_s) u_s

@@ -37,6 +37,10 @@ CASES = {
                                                              num_local_experts=4, num_experts_per_tok=1,
                                                              attention_chunk_size=8, interleave_moe_layer_step=2,
                                                              floor_scale=4, attn_scale=0.1)),
+    "qwen3_next": ("Qwen3NextForCausalLM", "Qwen3NextConfig", dict(
+        BASE, head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
+        shared_expert_intermediate_size=48, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16,
+        linear_value_head_dim=8)),
     "deepseek_v2": ("DeepseekV2ForCausalLM", "DeepseekV2Config", dict(
         BASE, num_key_value_heads=4, moe_intermediate_size=32, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
         first_k_dense_replace=1, q_lora_rank=None, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16)),
@@ -78,7 +82,7 @@ def test_matches_hugging_face(name):
     assert torch.allclose(got, ref, atol=2e-4, rtol=2e-3), float((got - ref).abs().max())
 
 
-@pytest.mark.parametrize("name", ["llama", "gemma3", "cohere2", "gpt_oss", "llama4", "deepseek_v3"])
+@pytest.mark.parametrize("name", ["llama", "gemma3", "cohere2", "gpt_oss", "llama4", "deepseek_v3", "qwen3_next"])
 def test_cached_decode_equals_full_forward(name):
     _, ours = _pair(name)
     ids = torch.randint(0, 128, (1, 20), generator=torch.Generator().manual_seed(2))
@@ -173,3 +177,73 @@ def test_whisper_matches_hugging_face():
         got = ours(mel, tgt)
     assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3), float((got - ref).abs().max())
     assert len(ours.transcribe(mel[:1], [1], max_new_tokens=3)) == 4
+
+
+def test_nemotron_h_matches_hugging_face_and_cache():
+    from pmetal_b200.models.architectures.hybrid import NemotronHLM
+    torch.manual_seed(0)
+    cfg = tf.NemotronHConfig(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=6,
+                             layers_block_type=["mamba", "moe", "attention", "moe", "mamba", "moe"],
+                             n_routed_experts=8, num_experts_per_tok=2, n_group=2, topk_group=1, moe_intermediate_size=32,
+                             moe_shared_expert_intermediate_size=48, num_attention_heads=4, num_key_value_heads=2, head_dim=16, mamba_num_heads=8,
+                             mamba_head_dim=8, ssm_state_size=16, n_groups=2, chunk_size=8, attn_implementation="eager")
+    hf = tf.NemotronHForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() < 2:
+                p.add_(torch.randn_like(p) * 0.05)
+        for n, b in hf.named_buffers():
+            if "e_score_correction_bias" in n:
+                b.copy_(torch.randn_like(b) * 0.1)
+    ours = NemotronHLM(cfg.to_dict()).eval()
+    missing, unexpected = ours.load_hf_state_dict(hf.state_dict(), strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    ids = torch.randint(0, 128, (2, 19))
+    with torch.no_grad():
+        ref = hf(input_ids=ids).logits
+        got = ours(ids)
+        cache = ours.new_cache()
+        inc = torch.cat([ours(ids[:, :11], cache)] + [ours(ids[:, t:t + 1], cache) for t in range(11, 19)], 1)
+    assert torch.allclose(got, ref, atol=3e-4, rtol=2e-3), float((got - ref).abs().max())
+    assert torch.allclose(inc, got, atol=3e-4, rtol=2e-3), float((inc - got).abs().max())
+    # the plain squared-ReLU block type (no counterpart in the installed Hugging Face version)
+    mlp_only = NemotronHLM(dict(cfg.to_dict(), layers_block_type=["mamba", "mlp"])).eval()
+    assert mlp_only(ids).shape == (2, 19, 128)
+
+
+def test_registry_resolves_families_and_loads_from_disk(tmp_path):
+    import json
+    from pmetal_b200.models.architectures import build_model, family_of, load_pretrained
+    from pmetal_b200.utils.safetensors_io import save_file
+    assert family_of({"model_type": "qwen3"}) == "fast" and family_of({"model_type": "gemma2"}) == "generic"
+    assert family_of({"model_type": "nemotron_h"}) == "nemotron_h" and family_of({"model_type": "roberta"}) == "bert"
+    assert family_of({"architectures": ["Phi3ForCausalLM"]}) == "generic" and family_of({"model_type": "nope"}) is None
+    assert family_of({"model_type": "gemma3", "text_config": {"model_type": "gemma3_text"}}) == "generic"
+    with pytest.raises(ValueError):
+        build_model({"model_type": "nope"})
+    # a Mixtral checkpoint with one tensor per expert (the layout of the published files) loads into the stacked form
+    cfg = tf.MixtralConfig(**dict(BASE, num_local_experts=4, num_experts_per_tok=2))
+    hf = tf.MixtralForCausalLM(cfg).eval()
+    sd = {}
+    for k, v in hf.state_dict().items():
+        if k.endswith("mlp.experts.gate_up_proj"):
+            pre = k[: -len("mlp.experts.gate_up_proj")]
+            for e in range(4):
+                sd[f"{pre}block_sparse_moe.experts.{e}.w1.weight"] = v[e, :96].clone()
+                sd[f"{pre}block_sparse_moe.experts.{e}.w3.weight"] = v[e, 96:].clone()
+        elif k.endswith("mlp.experts.down_proj"):
+            pre = k[: -len("mlp.experts.down_proj")]
+            for e in range(4):
+                sd[f"{pre}block_sparse_moe.experts.{e}.w2.weight"] = v[e].clone()
+        elif k.endswith("mlp.gate.weight"):
+            sd[k.replace("mlp.gate.", "block_sparse_moe.gate.")] = v.clone()
+        else:
+            sd[k] = v.clone()
+    d = tmp_path / "mixtral"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(cfg.to_dict()))
+    save_file(sd, str(d / "model.safetensors"))
+    ours = load_pretrained(str(d)).eval()
+    ids = torch.randint(0, 128, (1, 9))
+    with torch.no_grad():
+        assert torch.allclose(ours(ids), hf(input_ids=ids).logits, atol=2e-4, rtol=2e-3)
