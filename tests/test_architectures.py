@@ -247,3 +247,49 @@ def test_registry_resolves_families_and_loads_from_disk(tmp_path):
     ids = torch.randint(0, 128, (1, 9))
     with torch.no_grad():
         assert torch.allclose(ours(ids), hf(input_ids=ids).logits, atol=2e-4, rtol=2e-3)
+
+
+def test_vision_towers_match_hugging_face_and_wrapper_splices_features():
+    from pmetal_b200.models.architectures.vision import PixtralVision, Qwen2VLVision, build_vision_language
+    torch.manual_seed(0)
+    pc = tf.PixtralVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                image_size=32, patch_size=8, head_dim=8, attn_implementation="eager")
+    hf = tf.PixtralVisionModel(pc).eval()
+    ours = PixtralVision(pc.to_dict()).eval()
+    _load(ours, hf)
+    imgs = [torch.randn(3, 32, 32), torch.randn(3, 16, 24)]
+    with torch.no_grad():
+        ref = hf(pixel_values=torch.stack([imgs[0]]), image_sizes=[(32, 32)]).last_hidden_state[0]
+        got = ours(imgs[:1])
+        both = ours(imgs)
+    assert torch.allclose(got, ref, atol=2e-5), float((got - ref).abs().max())
+    assert torch.allclose(both[:16], got, atol=2e-5) and both.shape == (16 + 6, 32)    # images do not see each other
+
+    from transformers.models.qwen2_vl.configuration_qwen2_vl import Qwen2VLVisionConfig
+    from transformers.models.qwen2_vl.modeling_qwen2_vl import Qwen2VisionTransformerPretrainedModel
+    vc = Qwen2VLVisionConfig(depth=2, embed_dim=32, hidden_size=48, mlp_ratio=2, num_heads=4, patch_size=4,
+                             spatial_merge_size=2, temporal_patch_size=2)
+    vc._attn_implementation = "eager"
+    hv = Qwen2VisionTransformerPretrainedModel(vc).eval()
+    ov = Qwen2VLVision(vc.to_dict()).eval()
+    _load(ov, hv)
+    grid = [(1, 4, 6), (1, 2, 2)]
+    patches = torch.randn(4 * 6 + 2 * 2, 3 * 2 * 4 * 4)
+    with torch.no_grad():
+        ref = hv(patches, grid_thw=torch.tensor(grid))
+        ref = ref.pooler_output if hasattr(ref, "pooler_output") else ref
+        got = ov(patches, grid)
+    assert got.shape == (7, 48) and torch.allclose(got, ref, atol=2e-5), float((got - ref).abs().max())
+
+    vlm = build_vision_language({"model_type": "pixtral", "image_token_index": 5, "vision_config": pc.to_dict(),
+                                 "text_config": dict(BASE, model_type="mistral")}).eval()
+    ids = torch.randint(6, 128, (1, 30))
+    ids[0, 3:19] = 5                                           # sixteen placeholders for a 4 x 4 patch image
+    with torch.no_grad():
+        feats = vlm.vision_tower([torch.randn(3, 32, 32)])
+        out = vlm(ids, feats)
+        out2 = vlm(ids, feats * 2)
+    assert out.shape == (1, 30, 128) and not torch.allclose(out[0, 20:], out2[0, 20:])
+    assert torch.allclose(out[0, :3], out2[0, :3])             # causal: tokens before the image are unaffected
+    with pytest.raises(ValueError):
+        vlm(ids, feats[:5])
