@@ -293,3 +293,25 @@ def test_vision_towers_match_hugging_face_and_wrapper_splices_features():
     assert torch.allclose(out[0, :3], out2[0, :3])             # causal: tokens before the image are unaffected
     with pytest.raises(ValueError):
         vlm(ids, feats[:5])
+
+
+def test_dflash_block_drafting_equals_greedy_decoding():
+    from pmetal_b200.models.dflash import DFlashConfig, DFlashDecoder, DFlashDraftModel
+    torch.manual_seed(0)
+    target = GenericDecoderLM.from_hf_config(dict(BASE, model_type="qwen3", head_dim=16)).init_weights(0.05, 1).eval()
+    dc = DFlashConfig.from_dict(dict(hidden_size=64, num_hidden_layers=2, intermediate_size=96, num_attention_heads=4,
+                                     num_key_value_heads=2, head_dim=16, vocab_size=128, block_size=6,
+                                     dflash_config=dict(target_layer_ids=[1, 3], mask_token_id=127)))
+    draft = DFlashDraftModel(dc).eval()
+    assert draft.fc.weight.shape == (64, 128)
+    prompt = torch.randint(0, 120, (11,)).tolist()
+    greedy = target.generate(prompt, max_new_tokens=24)
+    dec = DFlashDecoder(target, draft)
+    out = dec.generate(prompt, max_new_tokens=24)
+    dec.close()
+    assert out == greedy                                       # whatever the untrained draft proposes
+    assert dec.stats.total_drafted > 0 and all(1 <= a <= 6 for a in dec.stats.acceptance_lengths)
+    # a draft that cannot be wrong: block size 1 degenerates to one verified token per step
+    dec1 = DFlashDecoder(target, draft)
+    assert dec1.generate(prompt, 10, block_size=1) == greedy[:10] and dec1.stats.total_accepted == 0
+    dec1.close()
