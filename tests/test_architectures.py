@@ -315,3 +315,58 @@ def test_dflash_block_drafting_equals_greedy_decoding():
     dec1 = DFlashDecoder(target, draft)
     assert dec1.generate(prompt, 10, block_size=1) == greedy[:10] and dec1.stats.total_accepted == 0
     dec1.close()
+
+
+def test_flux_transformer_and_autoencoder():
+    from pmetal_b200.models.architectures import build_model
+    from pmetal_b200.models.architectures.diffusion import (AutoencoderKL, FluxTransformer, flow_match_sample, flow_sigmas,
+                                                            pack_latents, rope_nd, timestep_embedding, unpack_latents)
+    torch.manual_seed(0)
+    cfg = dict(model_type="flux", num_attention_heads=2, attention_head_dim=16, axes_dims_rope=(4, 6, 6), in_channels=16,
+               joint_attention_dim=24, pooled_projection_dim=12, num_layers=2, num_single_layers=2, guidance_embeds=True)
+    m = build_model(cfg).eval()
+    assert isinstance(m, FluxTransformer)
+    names = set(m.state_dict())
+    for key in ("x_embedder.weight", "time_text_embed.guidance_embedder.linear_1.weight",
+                "transformer_blocks.0.attn.add_k_proj.weight", "transformer_blocks.1.ff.net.0.proj.weight",
+                "transformer_blocks.0.norm1_context.linear.bias", "single_transformer_blocks.1.proj_out.weight",
+                "single_transformer_blocks.0.attn.norm_q.weight", "norm_out.linear.weight", "proj_out.bias"):
+        assert key in names, key
+    z = torch.randn(1, 4, 8, 12)
+    p, ids = pack_latents(z)
+    assert p.shape == (1, 24, 16) and torch.equal(unpack_latents(p, 8, 12), z) and ids[7].tolist() == [0, 1, 1]
+    text, pooled = torch.randn(1, 5, 24), torch.randn(1, 12)
+    t = torch.tensor([0.7])
+    with torch.no_grad():
+        v = m(p, text, pooled, t, ids, torch.zeros(5, 3), torch.tensor([3.5]))
+        # permuting the image tokens together with their position ids permutes the output the same way
+        perm = torch.randperm(24)
+        v2 = m(p[:, perm], text, pooled, t, ids[perm], torch.zeros(5, 3), torch.tensor([3.5]))
+    assert v.shape == (1, 24, 16) and torch.allclose(v[:, perm], v2, atol=1e-5)
+    # zero gates (adaptive-norm projections at zero) make every block the identity on the residual stream
+    with torch.no_grad():
+        for n, prm in m.named_parameters():
+            if "norm1" in n or ".norm.linear" in n:
+                prm.zero_()
+        x0 = m.x_embedder(p)
+        emb = m.time_text_embed(t * 1000, torch.tensor([3500.0]), pooled)
+        cos, sin = rope_nd(torch.cat((torch.zeros(5, 3), ids)), m.axes_dim)
+        x1, _ = m.transformer_blocks[0](x0, m.context_embedder(text), emb, cos, sin)
+    assert torch.allclose(x0, x1)
+    e = timestep_embedding(torch.tensor([0.0, 500.0]), 8)
+    assert torch.allclose(e[0], torch.tensor([1.0, 1, 1, 1, 0, 0, 0, 0])) and abs(float(e[1, 4]) - float(torch.sin(torch.tensor(500.0)))) < 1e-4
+    s = flow_sigmas(4, 3.0)
+    assert s[0] == 1 and s[-1] == 0 and (s[:-1] > s[1:]).all() and s[2] > 0.5      # the shift spends more steps at high noise
+    out = flow_match_sample(m, torch.randn(1, 4, 8, 12), text, pooled, steps=2, guidance=3.5)
+    assert out.shape == (1, 4, 8, 12) and torch.isfinite(out).all()
+
+    vae = AutoencoderKL(dict(block_out_channels=(8, 16), layers_per_block=1, latent_channels=4, norm_num_groups=4)).eval()
+    for key in ("encoder.down_blocks.0.downsamplers.0.conv.weight", "decoder.up_blocks.0.upsamplers.0.conv.weight",
+                "decoder.mid_block.attentions.0.to_q.weight", "encoder.conv_out.weight", "decoder.up_blocks.1.resnets.0.conv_shortcut.weight"):
+        assert key in vae.state_dict(), key
+    img = torch.randn(2, 3, 16, 16)
+    with torch.no_grad():
+        lat = vae.encode(img)
+        rec = vae.decode(lat)
+    assert lat.shape == (2, 4, 8, 8) and rec.shape == img.shape
+    assert vae.encoder.conv_out.out_channels == 8                                 # mean and log-variance
