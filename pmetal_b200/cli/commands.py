@@ -722,3 +722,320 @@ def cmd_embed_train(a) -> int:
     save_adapter(model, a.output, lcfg, a.model)
     print(json.dumps({"output": a.output, **last}))
     return 0
+
+
+# ------------------------------------------------------------------------------------------- rlkd
+def _rlkd_args(sp):
+    p = sp.add_parser("rlkd", help="GRPO with an added distillation term against a teacher (RLKD)")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("-t", "--teacher", required=True)
+    p.add_argument("-d", "--dataset", required=True)
+    p.add_argument("-o", "--output", default="./rlkd-output")
+    p.add_argument("--alpha", type=float, default=0.5, help="weight of the KD term")
+    p.add_argument("--num-generations", type=int, default=8)
+    p.add_argument("--beta", type=float, default=0.001)
+    p.add_argument("--max-completion-length", type=int, default=512)
+    p.add_argument("--max-prompt-length", type=int, default=512)
+    p.add_argument("--learning-rate", type=float, default=1e-6)
+    p.add_argument("--max-steps", type=int, default=100)
+    p.add_argument("--prompts-per-step", type=int, default=1)
+    p.add_argument("--lora-r", type=int, default=16)
+    p.add_argument("--reward", default="format", choices=["format", "length", "accuracy"])
+    p.add_argument("--device")
+    return p
+
+
+@_command(_rlkd_args)
+def cmd_rlkd(a) -> int:
+    a.dapo, a.rlkd_alpha = False, a.alpha
+    return cmd_grpo(a)
+
+
+# ------------------------------------------------------------------------------------------- search (offline)
+def _search_args(sp):
+    p = sp.add_parser("search", help="search models in the local Hugging Face cache (this machine is offline)")
+    p.add_argument("query", nargs="?", default="")
+    p.add_argument("--limit", type=int, default=20)
+    return p
+
+
+def local_model_index():
+    """[(repo id, snapshot dir, bytes)] of every model in the local hub cache."""
+    cache = os.path.join(os.environ.get("HF_HOME", os.path.expanduser("~/.cache/huggingface")), "hub")
+    out = []
+    if not os.path.isdir(cache):
+        return out
+    for name in sorted(os.listdir(cache)):
+        if not name.startswith("models--"):
+            continue
+        snaps = os.path.join(cache, name, "snapshots")
+        if not os.path.isdir(snaps) or not os.listdir(snaps):
+            continue
+        snap = os.path.join(snaps, sorted(os.listdir(snaps))[-1])
+        size = 0
+        for root, _, files in os.walk(snap):
+            for f in files:
+                try:
+                    size += os.path.getsize(os.path.join(root, f))
+                except OSError:
+                    pass
+        out.append((name[len("models--"):].replace("--", "/"), snap, size))
+    return out
+
+
+@_command(_search_args)
+def cmd_search(a) -> int:
+    from ..utils.sysinfo import estimate_fit
+    q = a.query.lower()
+    rows = []
+    for repo, snap, size in local_model_index():
+        if q and q not in repo.lower():
+            continue
+        row = {"id": repo, "path": snap, "size_gb": round(size / 1e9, 3)}
+        try:
+            fit = estimate_fit(snap, 4096, 1, 16, "none")
+            row["fits"] = fit.get("fits")
+        except Exception:
+            pass
+        rows.append(row)
+    print(json.dumps({"query": a.query, "source": "local cache", "results": rows[: a.limit]}, indent=2))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------- dflash
+def _dflash_args(sp):
+    p = sp.add_parser("dflash", help="speculative decoding with a DFlash block-diffusion draft model")
+    p.add_argument("-m", "--model", required=True, help="target model directory or random:<preset>")
+    p.add_argument("--draft", required=True, help="draft directory (config.json + safetensors) or 'random'")
+    p.add_argument("--prompt", default="Hello")
+    p.add_argument("--max-tokens", type=int, default=64)
+    p.add_argument("--block-size", type=int, default=0)
+    p.add_argument("--device")
+    return p
+
+
+@_command(_dflash_args)
+def cmd_dflash(a) -> int:
+    import time
+
+    import torch
+
+    from ..models.architectures.generic import GenericDecoderLM
+    from ..models.dflash import DFlashConfig, DFlashDecoder, DFlashDraftModel
+    from ..models.loader import read_state_dict
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    if a.model.startswith("random:"):
+        from ..models.config import preset
+        cfg = preset(a.model.split(":", 1)[1]).to_hf_dict()
+        target = GenericDecoderLM.from_hf_config(cfg).init_weights(0.02, 0)
+        tok = None
+    else:
+        from ..data.tokenizer import load_tokenizer
+        with open(os.path.join(a.model, "config.json"), "r", encoding="utf-8") as fh:
+            cfg = json.load(fh)
+        target = GenericDecoderLM.from_hf_config(cfg)
+        target.load_state_dict(read_state_dict(a.model), strict=False)
+        tok = load_tokenizer(a.model)
+    target = target.to(dev).eval()
+    c = target.c
+    if a.draft == "random":
+        n = c.num_layers
+        dc = DFlashConfig(c.hidden_size, 2, c.intermediate_size, c.n_heads, c.n_kv_heads, c.head_dim, c.vocab_size,
+                          sorted({n // 3, (2 * n) // 3, n - 1}), c.vocab_size - 1, c.norm_eps, c.rope_theta, 8)
+        draft = DFlashDraftModel(dc)
+    else:
+        with open(os.path.join(a.draft, "config.json"), "r", encoding="utf-8") as fh:
+            dc = DFlashConfig.from_dict(json.load(fh))
+        draft = DFlashDraftModel(dc)
+        draft.load_hf_state_dict(read_state_dict(a.draft), strict=False)
+    draft = draft.to(dev).eval()
+    prompt = tok.encode(a.prompt) if tok is not None else [min(ord(ch), c.vocab_size - 2) for ch in a.prompt]
+    dec = DFlashDecoder(target, draft)
+    t0 = time.time()
+    out = dec.generate(prompt, a.max_tokens, a.block_size or None)
+    dt = time.time() - t0
+    dec.close()
+    print(json.dumps({"tokens": out, "text": tok.decode(out) if tok is not None else None,
+                      "tokens_per_s": round(len(out) / max(dt, 1e-9), 2),
+                      "avg_acceptance_length": round(dec.stats.avg_acceptance_length, 3),
+                      "acceptance_rate": round(dec.stats.acceptance_rate, 3)}))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------- pack-experts
+def _pack_args(sp):
+    p = sp.add_parser("pack-experts", help="split a mixture-of-experts checkpoint into one file per (layer, expert)")
+    p.add_argument("-m", "--model", required=True)
+    p.add_argument("-o", "--output", required=True)
+    return p
+
+
+def pack_experts(sd, out_dir: str) -> dict:
+    """Write ``experts/layer_{L:03d}_expert_{E:03d}.safetensors`` (gate_up / down of one expert) and ``dense.safetensors``
+    (everything else) plus ``expert_index.json``; stacked ``...mlp.experts.gate_up_proj`` tensors and per-expert
+    ``...experts.E.{gate,up,down}_proj.weight`` layouts are both understood
+    (reference: crates/pmetal/src/pack_experts.rs, expert files for streaming from disk)."""
+    import re
+
+    import torch
+
+    from ..utils.safetensors_io import save_file
+    os.makedirs(os.path.join(out_dir, "experts"), exist_ok=True)
+    dense, experts = {}, {}
+    per = re.compile(r"^(?:model\.)?layers\.(\d+)\.(?:mlp|block_sparse_moe)\.experts\.(\d+)\.(\w+)\.weight$")
+    stacked = re.compile(r"^(?:model\.)?layers\.(\d+)\.(?:mlp|block_sparse_moe)\.experts\.(gate_up_proj|down_proj)$")
+    for k, v in sd.items():
+        m = per.match(k)
+        if m:
+            experts.setdefault((int(m.group(1)), int(m.group(2))), {})[m.group(3)] = v
+            continue
+        m = stacked.match(k)
+        if m:
+            for e in range(v.shape[0]):
+                experts.setdefault((int(m.group(1)), e), {})[m.group(2)] = v[e].contiguous()
+            continue
+        dense[k] = v
+    index = {"experts": {}, "dense": "dense.safetensors"}
+    for (layer, e), tensors in sorted(experts.items()):
+        name = f"experts/layer_{layer:03d}_expert_{e:03d}.safetensors"
+        save_file({n: t.contiguous() for n, t in tensors.items()}, os.path.join(out_dir, name))
+        index["experts"][f"{layer}.{e}"] = {"file": name, "bytes": sum(t.numel() * t.element_size() for t in tensors.values())}
+    save_file({k: v.contiguous() if isinstance(v, torch.Tensor) else v for k, v in dense.items()},
+              os.path.join(out_dir, "dense.safetensors"))
+    with open(os.path.join(out_dir, "expert_index.json"), "w", encoding="utf-8") as fh:
+        json.dump(index, fh, indent=1)
+    return index
+
+
+@_command(_pack_args)
+def cmd_pack_experts(a) -> int:
+    from ..models.loader import read_state_dict
+    idx = pack_experts(read_state_dict(a.model), a.output)
+    print(json.dumps({"output": a.output, "expert_files": len(idx["experts"])}))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------- dashboard / tui (headless)
+def _dash_args(sp):
+    for name in ("dashboard", "tui"):
+        p = sp.add_parser(name, help="follow a job-event file (--log-events output) and print progress lines")
+        p.add_argument("events", help="JSON-lines event file")
+        p.add_argument("--once", action="store_true", help="print the summary of what is there and exit")
+        p.add_argument("--interval", type=float, default=1.0)
+        p.set_defaults(func=cmd_dashboard)
+    return p
+
+
+def summarise_events(lines) -> dict:
+    """Fold job events into {job_id: {kind, state, step, loss, tokens_per_s, ...}}."""
+    jobs = {}
+    for ln in lines:
+        ln = ln.strip()
+        if not ln:
+            continue
+        try:
+            ev = json.loads(ln)
+        except ValueError:
+            continue
+        j = jobs.setdefault(ev.get("job_id", "?"), {"state": "running"})
+        kind = ev.get("event")
+        if kind == "started":
+            j["kind"] = ev.get("kind")
+        elif kind == "metric":
+            pl = ev.get("payload") or {}
+            for k in ("step", "loss", "lr", "tokens_per_s", "tok_per_s", "grad_norm", "eval_loss"):
+                if k in pl:
+                    j[k] = pl[k]
+        elif kind in ("finished", "completed"):
+            j["state"] = "finished"
+        elif kind in ("failed", "error"):
+            j["state"], j["error"] = "failed", ev.get("message") or (ev.get("payload") or {}).get("message")
+        elif kind == "cancelled":
+            j["state"] = "cancelled"
+    return jobs
+
+
+def cmd_dashboard(a) -> int:
+    import time
+    seen = 0
+    lines = []
+    while True:
+        if os.path.exists(a.events):
+            with open(a.events, "r", encoding="utf-8") as fh:
+                lines = fh.readlines()
+        if len(lines) != seen or a.once:
+            seen = len(lines)
+            for job, st in summarise_events(lines).items():
+                print(json.dumps({"job": job, **st}), flush=True)
+        if a.once or all(s["state"] != "running" for s in summarise_events(lines).values()) and lines:
+            return 0
+        time.sleep(a.interval)
+
+
+cmd_dashboard._register = lambda sp: _dash_args(sp)
+
+
+# ------------------------------------------------------------------------------------------- bench-* aliases
+def _bench_alias_args(sp):
+    for name, what in (("bench-corpus", "corpus"), ("bench-workload", "workload"), ("bench-gen", "gen")):
+        p = sp.add_parser(name, help=f"same as: bench {what}")
+        p.add_argument("--case", nargs="*")
+        p.add_argument("--iters", type=int, default=10)
+        p.add_argument("-m", "--model", default="random:qwen3-0.6b")
+        p.add_argument("--json")
+        p.add_argument("--device")
+        p.set_defaults(func=cmd_bench, what=what)
+    p = sp.add_parser("bench-gdn", help="gated delta rule: chunked against token-by-token evaluation")
+    p.add_argument("--tokens", type=int, default=512)
+    p.add_argument("--heads", type=int, default=8)
+    p.add_argument("--device")
+    p.set_defaults(func=cmd_bench_gdn)
+    p = sp.add_parser("bench-ffi", help="cost of one call into the native host library")
+    p.add_argument("--calls", type=int, default=200000)
+    p.set_defaults(func=cmd_bench_ffi)
+    return p
+
+
+def cmd_bench_gdn(a) -> int:
+    import time
+
+    import torch
+
+    from ..models.gdn import gdn_chunked, gdn_recurrent
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    T, H, d = a.tokens, a.heads, 64
+    g = torch.Generator().manual_seed(0)
+    q, k = (torch.nn.functional.normalize(torch.randn(T, H, d, generator=g), dim=-1).to(dev) for _ in range(2))
+    v = torch.randn(T, H, d, generator=g).to(dev)
+    gate, beta = torch.rand(T, H, generator=g).mul(0.2).add(0.8).to(dev), torch.rand(T, H, generator=g).to(dev)
+    res = {}
+    for name, fn in (("recurrent", gdn_recurrent), ("chunked", gdn_chunked)):
+        fn(q[:8], k[:8], v[:8], gate[:8], beta[:8])
+        if dev == "cuda":
+            torch.cuda.synchronize()
+        t0 = time.time()
+        y, _ = fn(q, k, v, gate, beta)
+        if dev == "cuda":
+            torch.cuda.synchronize()
+        res[name] = {"ms": round((time.time() - t0) * 1e3, 3)}
+        res[name + "_out"] = y
+    err = float((res.pop("recurrent_out") - res.pop("chunked_out")).abs().max())
+    print(json.dumps({"tokens": T, "heads": H, "device": dev, **res, "max_abs_diff": err}))
+    return 0
+
+
+def cmd_bench_ffi(a) -> int:
+    import time
+
+    from ..gguf import native
+    from ..gguf.types import GgmlType
+    fn = native.lib().pm_gguf_block_elems
+    t0 = time.perf_counter()
+    for _ in range(a.calls):
+        fn(int(GgmlType.Q4K))
+    dt = time.perf_counter() - t0
+    print(json.dumps({"calls": a.calls, "ns_per_call": round(dt / a.calls * 1e9, 1)}))
+    return 0
+
+
+cmd_bench_gdn._register = lambda sp: _bench_alias_args(sp)

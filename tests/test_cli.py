@@ -83,3 +83,39 @@ def test_distill_and_grpo_commands(model_dir, capsys, tmp_path):
                  "--max-completion-length", "4", "--lora-r", "4", "--device", "cpu", "--reward", "length"]) == 0
     assert os.path.exists(os.path.join(out2, "adapter_config.json"))
     assert main(["cluster", "status"]) == 0
+
+
+def test_new_subcommands(tmp_path, capsys):
+    import json
+
+    import torch
+
+    from pmetal_b200.cli import commands
+    from pmetal_b200.cli.main import main
+    from pmetal_b200.utils.safetensors_io import load_file
+    # dashboard folds an event file
+    ev = tmp_path / "events.jsonl"
+    ev.write_text("\n".join(json.dumps(e) for e in [
+        {"event": "started", "job_id": "j1", "kind": "train", "ts": 1},
+        {"event": "metric", "job_id": "j1", "payload": {"kind": "step", "step": 3, "loss": 1.5, "tokens_per_s": 10.0}},
+        {"event": "finished", "job_id": "j1"}]) + "\n")
+    assert main(["dashboard", str(ev), "--once"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out == {"job": "j1", "state": "finished", "kind": "train", "step": 3, "loss": 1.5, "tokens_per_s": 10.0}
+    # pack-experts understands both expert layouts
+    sd = {"model.embed_tokens.weight": torch.randn(8, 4),
+          "model.layers.0.mlp.experts.gate_up_proj": torch.randn(3, 6, 4), "model.layers.0.mlp.experts.down_proj": torch.randn(3, 4, 3),
+          "model.layers.1.mlp.experts.0.gate_proj.weight": torch.randn(3, 4), "model.layers.1.mlp.experts.0.down_proj.weight": torch.randn(4, 3)}
+    idx = commands.pack_experts(sd, str(tmp_path / "packed"))
+    assert set(idx["experts"]) == {"0.0", "0.1", "0.2", "1.0"}
+    one = load_file(str(tmp_path / "packed" / idx["experts"]["0.2"]["file"]))
+    assert torch.equal(one["gate_up_proj"], sd["model.layers.0.mlp.experts.gate_up_proj"][2])
+    assert "model.embed_tokens.weight" in load_file(str(tmp_path / "packed" / "dense.safetensors"))
+    # offline search, native call overhead, delta-rule micro-benchmark, DFlash on a random target
+    assert main(["search", "nothing-matches-this"]) == 0 and json.loads(capsys.readouterr().out)["results"] == []
+    assert main(["bench-ffi", "--calls", "2000"]) == 0 and json.loads(capsys.readouterr().out)["ns_per_call"] > 0
+    assert main(["bench-gdn", "--tokens", "48", "--heads", "2", "--device", "cpu"]) == 0
+    assert json.loads(capsys.readouterr().out)["max_abs_diff"] < 1e-3
+    assert main(["dflash", "-m", "random:tiny-qwen3", "--draft", "random", "--max-tokens", "12", "--device", "cpu"]) == 0
+    res = json.loads(capsys.readouterr().out)
+    assert len(res["tokens"]) == 12 and res["avg_acceptance_length"] >= 1
