@@ -190,3 +190,59 @@ def run_schedule(schedule: Sequence[Tuple[str, Optional[int]]], stage_fn: Callab
     for r in pending:
         r.wait()
     return losses
+
+
+# ------------------------------------------------------------------------------------------- local in-memory pipeline
+def plan_local_pipeline(num_layers: int, stages: int) -> List[Tuple[int, int]]:
+    """Contiguous, near-equal layer ranges for a pipeline whose stages live in one process and hand activations over
+    in-memory channels (the reference plans such a pipeline across the two dies of an Ultra chip,
+    crates/pmetal-distributed/src/ultrafusion.rs)."""
+    stages = max(1, min(stages, num_layers))
+    base, extra = divmod(num_layers, stages)
+    out, start = [], 0
+    for s in range(stages):
+        n = base + (1 if s < extra else 0)
+        out.append((start, start + n))
+        start += n
+    return out
+
+
+def run_local_pipeline(stage_fns: Sequence, micro_batches: Sequence):
+    """Run ``stage_fns[s](x)`` as a pipeline of threads connected by queues; results come back in input order."""
+    import queue
+    import threading
+    qs = [queue.Queue(maxsize=2) for _ in range(len(stage_fns) + 1)]
+    errors: List[BaseException] = []
+
+    def worker(s):
+        while True:
+            item = qs[s].get()
+            if item is None:
+                qs[s + 1].put(None)
+                return
+            try:
+                qs[s + 1].put(stage_fns[s](item))
+            except BaseException as e:                      # the failure travels down the pipe instead of hanging it
+                errors.append(e)
+                qs[s + 1].put(None)
+                return
+    threads = [threading.Thread(target=worker, args=(s,), daemon=True) for s in range(len(stage_fns))]
+    for t in threads:
+        t.start()
+
+    def feed():
+        for mb in micro_batches:
+            qs[0].put(mb)
+        qs[0].put(None)
+    threading.Thread(target=feed, daemon=True).start()
+    out = []
+    while True:
+        item = qs[-1].get()
+        if item is None:
+            break
+        out.append(item)
+    for t in threads:
+        t.join(timeout=5)
+    if errors:
+        raise errors[0]
+    return out

@@ -293,3 +293,47 @@ def test_activation_message_wire_format():
         ActivationMessage.deserialize(raw[:28] + bytes([9]) + raw[29:])
     with pytest.raises(ValueError):
         ActivationMessage.deserialize(b"short")
+
+
+def test_identity_fabric_discovery_and_bundle(tmp_path):
+    import torch
+
+    from pmetal_b200.parallel import cloud_bridge, discovery
+    from pmetal_b200.parallel.pipeline import plan_local_pipeline, run_local_pipeline
+    ident = discovery.NodeIdentity.load_or_create(str(tmp_path / "id" / "node_keypair"))
+    again = discovery.NodeIdentity.load_or_create(str(tmp_path / "id" / "node_keypair"))
+    assert ident.peer_id == again.peer_id and (tmp_path / "id" / "node_keypair").stat().st_mode & 0o777 == 0o600
+    sig = ident.sign(b"hello")
+    assert discovery.NodeIdentity.verify(ident.public_bytes, sig, b"hello")
+    assert not discovery.NodeIdentity.verify(ident.public_bytes, sig, b"hellp")
+    fab = discovery.probe_fabric(4, lambda i, j: (i // 2) == (j // 2))      # two NVLink islands joined over PCIe
+    assert fab[0][1].name == "nvlink5" and fab[0][2].name == "pcie5" and fab[3][3].name == "self"
+    assert discovery.ring_bandwidth(fab, [0, 1, 2, 3]) == 64.0 and discovery.ring_bandwidth(fab, [0, 1]) == 900.0
+    assert discovery.link_score(discovery.NVLINK5) < discovery.link_score(discovery.PCIE5) < discovery.link_score(discovery.HOST_TCP)
+    peers = [discovery.Peer("b"), discovery.Peer("c"), discovery.Peer("a")]
+    assert [p.peer_id for p in discovery.ring_order(peers)] == ["a", "b", "c"]
+    prev, nxt = discovery.ring_neighbours(peers, "a")
+    assert (prev.peer_id, nxt.peer_id) == ("c", "b")
+    (tmp_path / "peers.json").write_text('[{"peer_id": "x", "addresses": ["10.0.0.1:52416"], "device": 1}]')
+    p = discovery.load_static_peers(str(tmp_path / "peers.json"))[0]
+    assert p.addresses == [("10.0.0.1", 52416)] and p.device == 1
+    # run bundle round trip
+    torch.manual_seed(3)
+    params = {"w": torch.randn(4, 3), "b": torch.randn(3)}
+    opt = {"w.m": torch.zeros(4, 3), "w.v": torch.ones(4, 3)}
+    meta = cloud_bridge.export_bundle(str(tmp_path / "bundle"), params, opt, step=17, config={"lr": 1e-4}, world_size=8)
+    expect = torch.rand(3)
+    torch.rand(10)
+    p2, o2, m2 = cloud_bridge.import_bundle(str(tmp_path / "bundle"))
+    assert torch.equal(torch.rand(3), expect)                                  # the generator state came back
+    assert torch.equal(p2["w"], params["w"]) and torch.equal(o2["w.v"], opt["w.v"]) and m2["step"] == 17 == meta["step"]
+    assert (tmp_path / "bundle" / "bootstrap_cluster.py").exists() and m2["num_params"] == 15
+    # in-process pipeline over queues keeps order and surfaces a stage failure
+    assert plan_local_pipeline(10, 3) == [(0, 4), (4, 7), (7, 10)] and plan_local_pipeline(2, 5) == [(0, 1), (1, 2)]
+    assert run_local_pipeline([lambda x: x + 1, lambda x: x * 2], range(6)) == [2, 4, 6, 8, 10, 12]
+
+    def boom(x):
+        raise RuntimeError("stage failed")
+    import pytest
+    with pytest.raises(RuntimeError):
+        run_local_pipeline([lambda x: x, boom], range(3))
