@@ -23,12 +23,9 @@ namespace pm {
 
 // ------------------------------------------------------------------------------------------------ MoE routing
 // One warp per token. E <= 1024 experts (32 per lane), k <= 16.
-__global__ void moe_router_kernel(const __nv_bfloat16* __restrict__ logits_bf16, const float* __restrict__ logits_f32,
-                                  int T, int E, int k, int renorm, int* __restrict__ topk_idx,
-                                  float* __restrict__ topk_w) {
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (t >= T) return;
+__device__ __forceinline__ void moe_route_token(const __nv_bfloat16* __restrict__ logits_bf16,
+                                                const float* __restrict__ logits_f32, int t, int E, int k, int renorm,
+                                                int* __restrict__ topk_idx, float* __restrict__ topk_w, int lane) {
   float v[32];
   float mx = -INFINITY;
 #pragma unroll
@@ -76,6 +73,57 @@ __global__ void moe_router_kernel(const __nv_bfloat16* __restrict__ logits_bf16,
   if (lane < k) {
     topk_idx[static_cast<long long>(t) * k + lane] = my_idx;
     topk_w[static_cast<long long>(t) * k + lane] = renorm ? my_w / wsum : my_w;
+  }
+}
+
+__global__ void moe_router_kernel(const __nv_bfloat16* __restrict__ logits_bf16, const float* __restrict__ logits_f32,
+                                  int T, int E, int k, int renorm, int* __restrict__ topk_idx,
+                                  float* __restrict__ topk_w) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  moe_route_token(logits_bf16, logits_f32, t, E, k, renorm, topk_idx, topk_w, threadIdx.x & 31);
+}
+
+// Few tokens (T * k <= 1024): routing, counting, offsets and the stable sort in one CTA, so that a decode step pays one
+// launch instead of four. Thread e owns expert e and walks the (token, slot) list in order, which keeps the sort stable
+// and deterministic. offsets2 (optional) receives a second copy of the offsets (the expert-parallel exchange buffer).
+constexpr int kRouteSmallMax = 1024;
+__global__ void __launch_bounds__(1024) moe_route_small_kernel(const __nv_bfloat16* __restrict__ logits_bf16,
+                                                               const float* __restrict__ logits_f32, int T, int E, int k,
+                                                               int renorm, int* __restrict__ topk_idx,
+                                                               float* __restrict__ topk_w, int* __restrict__ counts,
+                                                               int* __restrict__ offsets, int* __restrict__ offsets2,
+                                                               int* __restrict__ perm, int* __restrict__ inv) {
+  __shared__ int s_idx[kRouteSmallMax];
+  __shared__ int s_off[1024 + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = T * k;
+  for (int t = warp; t < T; t += 32) moe_route_token(logits_bf16, logits_f32, t, E, k, renorm, topk_idx, topk_w, lane);
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s_idx[i] = topk_idx[i];
+  __syncthreads();
+  const int e = threadIdx.x;
+  int c = 0;
+  if (e < E)
+    for (int i = 0; i < n; ++i) c += (s_idx[i] == e);
+  if (e < E) s_off[e + 1] = c;
+  if (e == 0) s_off[0] = 0;
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int j = 1; j <= E; ++j) s_off[j] += s_off[j - 1];
+  __syncthreads();
+  if (e <= E) {
+    offsets[e] = s_off[e];
+    if (offsets2) offsets2[e] = s_off[e];
+  }
+  if (e < E) {
+    counts[e] = c;
+    int pos = s_off[e];
+    for (int i = 0; i < n; ++i)
+      if (s_idx[i] == e) {
+        perm[pos] = i;
+        inv[i] = pos;
+        ++pos;
+      }
   }
 }
 
@@ -147,8 +195,8 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int
   }
 }
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ z, const int* __restrict__ inv,
-                                   const float* __restrict__ w, int k, __nv_bfloat16* __restrict__ y, long long T,
-                                   int H) {
+                                   const float* __restrict__ w, int k, const __nv_bfloat16* __restrict__ residual,
+                                   __nv_bfloat16* __restrict__ y, long long T, int H) {
   const int per_row = H / 8;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < T * per_row;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -170,6 +218,12 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ z, const in
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
     for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+    if (residual) {      // y = bf16(sum) + residual, the rounding an unfused add would make
+      const uint4 rr = reinterpret_cast<const uint4*>(residual + t * H)[c];
+      const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) o2[q] = __hadd2(o2[q], r2[q]);
+    }
     reinterpret_cast<uint4*>(y + t * H)[c] = o;
   }
 }
@@ -296,17 +350,34 @@ static inline int grid_cap(long long work, int per_block, int cap = 148 * 16) {
 
 using namespace pm;
 
-extern "C" int pm_moe_route(const void* logits, int is_f32, int T, int E, int k, int renorm, int* topk_idx,
-                            float* topk_w, int* counts, int* offsets, int* perm, int* inv, cudaStream_t st) {
+// offsets2: optional second destination for the [E + 1] offsets (may be null).
+extern "C" int pm_moe_route2(const void* logits, int is_f32, int T, int E, int k, int renorm, int* topk_idx,
+                             float* topk_w, int* counts, int* offsets, int* offsets2, int* perm, int* inv,
+                             cudaStream_t st) {
   if (T <= 0 || E <= 0 || E > 1024 || k <= 0 || k > 16 || k > E) return -1;
+  const long long n = static_cast<long long>(T) * k;
+  if (n <= kRouteSmallMax && E < 1024) {
+    moe_route_small_kernel<<<1, 1024, 0, st>>>(is_f32 ? nullptr : static_cast<const __nv_bfloat16*>(logits),
+                                               is_f32 ? static_cast<const float*>(logits) : nullptr, T, E, k, renorm,
+                                               topk_idx, topk_w, counts, offsets, offsets2, perm, inv);
+    return static_cast<int>(cudaGetLastError());
+  }
   moe_router_kernel<<<(T + 7) / 8, 256, 0, st>>>(is_f32 ? nullptr : static_cast<const __nv_bfloat16*>(logits),
                                                  is_f32 ? static_cast<const float*>(logits) : nullptr, T, E, k, renorm,
                                                  topk_idx, topk_w);
-  const long long n = static_cast<long long>(T) * k;
   moe_count_kernel<<<E, 256, 0, st>>>(topk_idx, n, counts);
   moe_scan_kernel<<<1, 32, 0, st>>>(counts, E, offsets);
   moe_sort_kernel<<<E, 256, 0, st>>>(topk_idx, n, offsets, perm, inv);
+  if (offsets2) {
+    cudaError_t e = cudaMemcpyAsync(offsets2, offsets, sizeof(int) * (E + 1), cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int pm_moe_route(const void* logits, int is_f32, int T, int E, int k, int renorm, int* topk_idx,
+                            float* topk_w, int* counts, int* offsets, int* perm, int* inv, cudaStream_t st) {
+  return pm_moe_route2(logits, is_f32, T, E, k, renorm, topk_idx, topk_w, counts, offsets, nullptr, perm, inv, st);
 }
 
 extern "C" int pm_moe_gather(const void* x, const int* perm, int k, void* out, long long n, int H, cudaStream_t st) {
@@ -317,13 +388,19 @@ extern "C" int pm_moe_gather(const void* x, const int* perm, int k, void* out, l
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int pm_moe_combine(const void* z, const int* inv, const float* w, int k, void* y, long long T, int H,
-                              cudaStream_t st) {
+extern "C" int pm_moe_combine2(const void* z, const int* inv, const float* w, int k, const void* residual, void* y,
+                               long long T, int H, cudaStream_t st) {
   if (H % 8) return -1;
   if (T <= 0) return 0;
   moe_combine_kernel<<<grid_cap(T * (H / 8), 256), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(z), inv, w, k,
+                                                                 static_cast<const __nv_bfloat16*>(residual),
                                                                  static_cast<__nv_bfloat16*>(y), T, H);
   return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int pm_moe_combine(const void* z, const int* inv, const float* w, int k, void* y, long long T, int H,
+                              cudaStream_t st) {
+  return pm_moe_combine2(z, inv, w, k, nullptr, y, T, H, st);
 }
 
 extern "C" int pm_gguf_dequant_bf16(const void* src, void* dst, long long n, int type, cudaStream_t st) {

@@ -52,6 +52,8 @@ class SparseMoeBlock(nn.Module):
         eng = getattr(self, "ep_engine", None)
         if eng is not None and x.is_cuda and not torch.is_grad_enabled() and x.shape[0] * eng.k <= eng.max_rows:
             # fused routing + (expert-parallel) dispatch + grouped GEMMs + combine (parallel/ep.py)
+            if residual is not None and x.dtype == torch.bfloat16:
+                return eng.forward(x, logits, residual)          # residual add fused into the combine kernel
             out = eng.forward(x.to(torch.bfloat16), logits).to(x.dtype)
             return out if residual is None else out + residual
         w, idx = route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)

@@ -551,7 +551,7 @@ def count_tokens(counts, tokens) -> None:
 
 
 # ------------------------------------------------------------------------------------------- MoE routing
-def moe_route(router_logits, k: int, renorm: bool = True):
+def moe_route(router_logits, k: int, renorm: bool = True, offsets_out=None):
     """router_logits [T, E] (bf16 or fp32). Returns dict(topk_idx [T,k], topk_w [T,k], counts [E], offsets [E+1],
     perm [T*k] (sorted position -> token*k+slot), inv [T*k] (token*k+slot -> sorted position))."""
     T, E = router_logits.shape
@@ -562,9 +562,9 @@ def moe_route(router_logits, k: int, renorm: bool = True):
     out = dict(topk_idx=torch.empty(T, k, dtype=torch.int32, device=dev), topk_w=torch.empty(T, k, dtype=torch.float32, device=dev),
                counts=torch.empty(E, dtype=torch.int32, device=dev), offsets=torch.empty(E + 1, dtype=torch.int32, device=dev),
                perm=torch.empty(T * k, dtype=torch.int32, device=dev), inv=torch.empty(T * k, dtype=torch.int32, device=dev))
-    _chk(lib().pm_moe_route(_p(x), c_int(int(x.dtype == torch.float32)), c_int(T), c_int(E), c_int(k), c_int(int(renorm)),
-                            _p(out["topk_idx"]), _p(out["topk_w"]), _p(out["counts"]), _p(out["offsets"]),
-                            _p(out["perm"]), _p(out["inv"]), _stream()), "pm_moe_route")
+    _chk(lib().pm_moe_route2(_p(x), c_int(int(x.dtype == torch.float32)), c_int(T), c_int(E), c_int(k), c_int(int(renorm)),
+                             _p(out["topk_idx"]), _p(out["topk_w"]), _p(out["counts"]), _p(out["offsets"]),
+                             _p(offsets_out), _p(out["perm"]), _p(out["inv"]), _stream()), "pm_moe_route2")
     return out
 
 
@@ -575,11 +575,12 @@ def moe_gather(x, perm, k: int):
     return out
 
 
-def moe_combine(z, inv, w, k: int):
+def moe_combine(z, inv, w, k: int, residual=None):
+    """y[t] = sum_j w[t, j] * z[inv[t * k + j]] (+ residual[t]); residual is a contiguous bf16 [T, H] tensor."""
     T, H = inv.numel() // k, z.shape[1]
     y = torch.empty(T, H, dtype=torch.bfloat16, device=z.device)
-    _chk(lib().pm_moe_combine(_p(z.contiguous()), _p(inv), _p(w.contiguous()), c_int(k), _p(y), c_ll(T), c_int(H), _stream()),
-         "pm_moe_combine")
+    _chk(lib().pm_moe_combine2(_p(z.contiguous()), _p(inv), _p(w.contiguous()), c_int(k), _p(residual), _p(y), c_ll(T),
+                               c_int(H), _stream()), "pm_moe_combine2")
     return y
 
 

@@ -30,8 +30,14 @@ def run(a) -> int:
     if a.action in ("status", "up"):
         from ..utils.sysinfo import system_info
         info = system_info()
+        from . import discovery
+        fabric = discovery.probe_fabric(n) if torch.cuda.is_available() else []
+        peers = discovery.discover_local(num_devices=n)
         info["cluster"] = {"world_size": n, "topology": "nvswitch-all-to-all" if n > 1 else "single",
-                           "ring_order": list(range(n))}
+                           "ring_order": [p.device for p in discovery.ring_order(peers)],
+                           "links": [[link.name for link in row] for row in fabric],
+                           "ring_bandwidth_gbs": discovery.ring_bandwidth(fabric, list(range(n))) if fabric else 0.0,
+                           "ports": {"gradients": discovery.GRADIENT_PORT, "discovery": discovery.DISCOVERY_PORT}}
         print(json.dumps(info, indent=2))
         return 0
     if n < 1:

@@ -146,15 +146,14 @@ class FusedExpertMoE:
         return t, arr(*[int(p) for p in h.buffer_ptrs])
 
     @torch.no_grad()
-    def forward(self, x: torch.Tensor, router_logits: torch.Tensor) -> torch.Tensor:
-        """x [T, H] bf16 local tokens, router_logits [T, E]. Returns [T, H] bf16."""
+    def forward(self, x: torch.Tensor, router_logits: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x [T, H] bf16 local tokens, router_logits [T, E]. Returns [T, H] bf16 (+ residual when given)."""
         from ..ops import native
         T = x.shape[0]
         n = T * self.k
         assert n <= self.max_rows and x.dtype == torch.bfloat16
         lib = native.lib()
-        r = native.moe_route(router_logits, self.k, self.renorm)
-        self.offsets.copy_(r["offsets"])
+        r = native.moe_route(router_logits, self.k, self.renorm, offsets_out=self.offsets)
         sx = self.sorted_x[: n * self.H].view(n, self.H)
         native._chk(lib.pm_moe_gather(native._p(x.contiguous()), native._p(r["perm"]), ctypes.c_int(self.k), native._p(sx),
                                       ctypes.c_longlong(n), ctypes.c_int(self.H), native._stream()), "pm_moe_gather")
@@ -180,7 +179,9 @@ class FusedExpertMoE:
                                     ctypes.c_int(1), self._pad_ptrs, None, None, ctypes.c_double(self.timeout_s),
                                     native._p(st), native._stream()), "pm_moe_gemm")
         zz = self.z[: n * self.H].view(n, self.H)
-        return native.moe_combine(zz, r["inv"], r["topk_w"], self.k)
+        res = residual.contiguous() if residual is not None and residual.dtype == torch.bfloat16 else None
+        y = native.moe_combine(zz, r["inv"], r["topk_w"], self.k, res)
+        return y if res is not None or residual is None else y + residual
 
 
 def shard_experts(block, group=None, max_tokens: int = 16384) -> FusedExpertMoE:

@@ -130,6 +130,26 @@ def test_moe_route_sort_gather_combine():
     assert torch.allclose(r2["topk_w"], p2.values, atol=1e-5)
 
 
+@pytest.mark.parametrize("T,E,k", [(1, 128, 8), (32, 128, 8), (100, 64, 4), (9, 8, 2)])
+def test_moe_route_single_launch_path(T, E, k):
+    """Few tokens take the one-CTA kernel (routing + counts + offsets + stable sort); same contract as the large path."""
+    nat = _nat()
+    torch.manual_seed(T)
+    logits = torch.randn(T, E, device="cuda")
+    extra = torch.full((E + 1,), -1, dtype=torch.int32, device="cuda")
+    r = nat.moe_route(logits, k, renorm=True, offsets_out=extra)
+    tw, ti = torch.softmax(logits, -1).topk(k, -1)
+    assert torch.equal(r["topk_idx"].long(), ti)
+    assert torch.allclose(r["topk_w"], tw / tw.sum(-1, keepdim=True), atol=1e-5)
+    flat = ti.reshape(-1)
+    counts = torch.bincount(flat, minlength=E)
+    assert torch.equal(r["counts"].long(), counts)
+    off = torch.cat((torch.zeros(1, dtype=torch.long, device="cuda"), counts.cumsum(0)))
+    assert torch.equal(r["offsets"].long(), off) and torch.equal(extra.long(), off)
+    assert torch.equal(r["perm"].long(), torch.sort(flat, stable=True).indices)
+    assert torch.equal(r["inv"].long()[r["perm"].long()], torch.arange(T * k, device="cuda"))
+
+
 @pytest.mark.parametrize("name,tid", [("Q4_0", 2), ("Q8_0", 8), ("Q4K", 12), ("Q6K", 14)])
 def test_gguf_dequant_kernel_matches_host(name, tid):
     nat = _nat()
