@@ -44,6 +44,13 @@ struct GemvParams {
   int r;
   int seg_end[4];                // cumulative output-row boundaries of the stacked projections (0x7fffffff padding)
   int prefetch_iters;            // groups per warp whose weight rows are pulled into L2 before the dependency wait
+  // 4-bit weights (NF4 / FP4 codes, two per byte, first element in the high nibble; w is null then)
+  const uint8_t* qdata;          // [N_w * K / 2]
+  const float* absmax;           // per block, or null when double-quantised
+  const uint8_t* absmax_q;
+  float am_scale, am_offset;
+  int qblock;                    // elements per absmax block (multiple of 32)
+  int fp4;
 };
 
 __device__ __forceinline__ float gv_silu(float v) { return v / (1.f + __expf(-v)); }
@@ -252,40 +259,21 @@ __device__ __forceinline__ void mma_16816(float c[4], uint32_t a0, uint32_t a1, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <bool SWIGLU>
-__global__ void __launch_bounds__(kTcThreads) gemv_tc_kernel(const GemvParams p) {
-  extern __shared__ __align__(16) uint8_t gv_smem[];
-  const int K = p.K, lds = K + kTcPad;
-  __nv_bfloat16* sx = reinterpret_cast<__nv_bfloat16*>(gv_smem);                      // [16][lds]
-  float* red = reinterpret_cast<float*>(gv_smem + static_cast<size_t>(16) * lds * 2);   // [warps][2][128]
-  __shared__ float s_rstd[16];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane & 3, col = lane >> 2;
-  const int n_tiles = (p.N + 7) / 8;
-  const int rounds = (K + 255) / 256;            // 32-wide k chunks per warp
-
-  auto load_batch = [&](int tile, int r0, uint4 wv[kTcKU], uint4 wv2[SWIGLU ? kTcKU : 1]) {
-    const int n = min(tile * 8 + col, p.N - 1);
-    const __nv_bfloat16* wr = p.w + static_cast<long long>(n) * p.ldw;
+// LoRA term of one output element: t[m, seg * r ..] . lora_b[row, :], seg from the stacked-projection boundaries.
+__device__ __forceinline__ float gv_lora(const GemvParams& p, int m, int row) {
+  int seg = 0;
 #pragma unroll
-    for (int u = 0; u < kTcKU; ++u) {
-      const int k = ((r0 + u) * kTcWarps + warp) * 32 + g * 8;
-      if (r0 + u < rounds && k < K) {
-        wv[u] = __ldg(reinterpret_cast<const uint4*>(wr + k));
-        if (SWIGLU) wv2[u] = __ldg(reinterpret_cast<const uint4*>(wr + static_cast<long long>(p.N) * p.ldw + k));
-      } else {
-        wv[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (SWIGLU) wv2[u] = make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
-  };
+  for (int i = 0; i < 3; ++i) seg += (row >= p.seg_end[i]) ? 1 : 0;
+  const __nv_bfloat16* tr = p.t + static_cast<long long>(m) * p.ldt + seg * p.r;
+  const float* br = p.lora_b + static_cast<long long>(row) * p.r;
+  float s = 0.f;
+  for (int j = 0; j < p.r; ++j) s = fmaf(__bfloat162float(tr[j]), br[j], s);
+  return s;
+}
 
-  // the first tile's weights are requested before anything that depends on the previous kernel's output
-  uint4 wv[kTcKU], wv2[SWIGLU ? kTcKU : 1];
-  int tile = blockIdx.x;
-  if (tile < n_tiles) load_batch(tile, 0, wv, wv2);
-
-  // ---- stage x (optionally RMS-normalised) as [16][K + pad]; rows >= M are zero
+// Stage x (optionally RMS-normalised) as [16][lds] bf16; rows >= M are zero. Shared by the tensor-core kernels.
+__device__ __forceinline__ void gv_stage16(const GemvParams& p, __nv_bfloat16* sx, int lds, float* s_rstd) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, K = p.K;
   if (p.norm_w) {
     for (int m = warp; m < p.M; m += kTcWarps) {
       float ss = 0.f;
@@ -325,6 +313,68 @@ __global__ void __launch_bounds__(kTcThreads) gemv_tc_kernel(const GemvParams p)
     *reinterpret_cast<uint4*>(sx + static_cast<long long>(m) * lds + k) = raw;
   }
   __syncthreads();
+}
+
+// Sum the 8 warps' partial accumulators of one 8-column tile and finish the outputs (scale, LoRA, SwiGLU, residual).
+template <bool SWIGLU>
+__device__ __forceinline__ void gv_tile_epilogue(const GemvParams& p, const float* red, int tile) {
+  if (threadIdx.x < 128) {
+    const int e = threadIdx.x;
+    float v = 0.f, v2 = 0.f;
+#pragma unroll
+    for (int w = 0; w < kTcWarps; ++w) {
+      v += red[(w * 2) * 128 + e];
+      if (SWIGLU) v2 += red[(w * 2 + 1) * 128 + e];
+    }
+    const int src = e >> 2, reg = e & 3;
+    const int m = (src >> 2) + ((reg & 2) ? 8 : 0), n = tile * 8 + (src & 3) * 2 + (reg & 1);
+    if (m < p.M && n < p.N) {
+      if (p.t) {
+        v += gv_lora(p, m, n);
+        if (SWIGLU) v2 += gv_lora(p, m, n + p.N);
+      }
+      v *= p.alpha;
+      if (SWIGLU) v = gv_silu(v) * (v2 * p.alpha);
+      if (p.residual) v += __bfloat162float(p.residual[static_cast<long long>(m) * p.ldr + n]);
+      p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16(v);
+    }
+  }
+}
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kTcThreads) gemv_tc_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) uint8_t gv_smem[];
+  const int K = p.K, lds = K + kTcPad;
+  __nv_bfloat16* sx = reinterpret_cast<__nv_bfloat16*>(gv_smem);                      // [16][lds]
+  float* red = reinterpret_cast<float*>(gv_smem + static_cast<size_t>(16) * lds * 2);   // [warps][2][128]
+  __shared__ float s_rstd[16];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane & 3, col = lane >> 2;
+  const int n_tiles = (p.N + 7) / 8;
+  const int rounds = (K + 255) / 256;            // 32-wide k chunks per warp
+
+  auto load_batch = [&](int tile, int r0, uint4 wv[kTcKU], uint4 wv2[SWIGLU ? kTcKU : 1]) {
+    const int n = min(tile * 8 + col, p.N - 1);
+    const __nv_bfloat16* wr = p.w + static_cast<long long>(n) * p.ldw;
+#pragma unroll
+    for (int u = 0; u < kTcKU; ++u) {
+      const int k = ((r0 + u) * kTcWarps + warp) * 32 + g * 8;
+      if (r0 + u < rounds && k < K) {
+        wv[u] = __ldg(reinterpret_cast<const uint4*>(wr + k));
+        if (SWIGLU) wv2[u] = __ldg(reinterpret_cast<const uint4*>(wr + static_cast<long long>(p.N) * p.ldw + k));
+      } else {
+        wv[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (SWIGLU) wv2[u] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+
+  // the first tile's weights are requested before anything that depends on the previous kernel's output
+  uint4 wv[kTcKU], wv2[SWIGLU ? kTcKU : 1];
+  int tile = blockIdx.x;
+  if (tile < n_tiles) load_batch(tile, 0, wv, wv2);
+
+  gv_stage16(p, sx, lds, s_rstd);
 
   for (; tile < n_tiles; tile += gridDim.x) {
     float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};
@@ -351,25 +401,123 @@ __global__ void __launch_bounds__(kTcThreads) gemv_tc_kernel(const GemvParams p)
     *reinterpret_cast<float4*>(my + lane * 4) = make_float4(c[0], c[1], c[2], c[3]);
     if (SWIGLU) *reinterpret_cast<float4*>(my + 128 + lane * 4) = make_float4(c2[0], c2[1], c2[2], c2[3]);
     __syncthreads();
-    if (threadIdx.x < 128) {
-      const int e = threadIdx.x;
-      float v = 0.f, v2 = 0.f;
-#pragma unroll
-      for (int w = 0; w < kTcWarps; ++w) {
-        v += red[(w * 2) * 128 + e];
-        if (SWIGLU) v2 += red[(w * 2 + 1) * 128 + e];
-      }
-      const int src = e >> 2, reg = e & 3;
-      const int m = (src >> 2) + ((reg & 2) ? 8 : 0), n = tile * 8 + (src & 3) * 2 + (reg & 1);
-      if (m < p.M && n < p.N) {
-        v *= p.alpha;
-        if (SWIGLU) v = gv_silu(v) * (v2 * p.alpha);
-        if (p.residual) v += __bfloat162float(p.residual[static_cast<long long>(m) * p.ldr + n]);
-        p.y[static_cast<long long>(m) * p.ldy + n] = __float2bfloat16(v);
-      }
-    }
+    gv_tile_epilogue<SWIGLU>(p, red, tile);
     __syncthreads();
   }
+}
+
+// 4-bit weights: the same tiling, but a lane's 16-byte load holds 32 consecutive codes of one column (lane group g owns
+// k = 32 g .. 32 g + 31 of a 128-wide chunk); they are expanded to bf16 in registers (table lookup times the block's
+// absmax) eight at a time, each eight feeding two MMAs. The weight stream is a quarter of the bf16 one.
+__constant__ float kGvNf4[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                 -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                 0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f, 0.33791524171829224f,
+                                 0.44070982933044434f, 0.5626170039176941f, 0.7229568362236023f, 1.0f};
+__constant__ float kGvFp4[16] = {0.0f, 0.0052083333f, 0.6666667f, 1.0f, 0.3333333f, 0.5f, 0.1666667f, 0.25f,
+                                 -0.0f, -0.0052083333f, -0.6666667f, -1.0f, -0.3333333f, -0.5f, -0.1666667f, -0.25f};
+constexpr int kQ4KU = 4;            // 16-byte code loads in flight per lane (per gate/up half)
+
+__device__ __forceinline__ uint32_t gv_pack2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kTcThreads) gemv_q4_tc_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) uint8_t gv_smem[];
+  const int K = p.K, lds = K + kTcPad;
+  __nv_bfloat16* sx = reinterpret_cast<__nv_bfloat16*>(gv_smem);
+  float* red = reinterpret_cast<float*>(gv_smem + static_cast<size_t>(16) * lds * 2);
+  __shared__ float s_rstd[16];
+  __shared__ float lut[16];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane & 3, col = lane >> 2;
+  const int n_tiles = (p.N + 7) / 8;
+  const int rounds = (K + 1023) / 1024;          // 128-wide k chunks per warp
+  if (threadIdx.x < 16) lut[threadIdx.x] = p.fp4 ? kGvFp4[threadIdx.x] : kGvNf4[threadIdx.x];
+
+  auto load_batch = [&](int tile, int r0, uint4 q[kQ4KU], float am[kQ4KU], uint4 q2[SWIGLU ? kQ4KU : 1],
+                        float am2[SWIGLU ? kQ4KU : 1]) {
+    const long long n = min(tile * 8 + col, p.N - 1);
+#pragma unroll
+    for (int u = 0; u < kQ4KU; ++u) {
+      const int k = ((r0 + u) * kTcWarps + warp) * 128 + g * 32;
+      const bool ok = r0 + u < rounds && k < K;
+      const long long e0 = n * K + k, e1 = (n + p.N) * K + k;
+      q[u] = ok ? __ldg(reinterpret_cast<const uint4*>(p.qdata + e0 / 2)) : make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);
+      am[u] = !ok ? 0.f : (p.absmax ? __ldg(p.absmax + e0 / p.qblock)
+                                    : static_cast<float>(__ldg(p.absmax_q + e0 / p.qblock)) * p.am_scale + p.am_offset);
+      if (SWIGLU) {
+        q2[u] = ok ? __ldg(reinterpret_cast<const uint4*>(p.qdata + e1 / 2)) : make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);
+        am2[u] = !ok ? 0.f : (p.absmax ? __ldg(p.absmax + e1 / p.qblock)
+                                       : static_cast<float>(__ldg(p.absmax_q + e1 / p.qblock)) * p.am_scale + p.am_offset);
+      }
+    }
+  };
+  uint4 q[kQ4KU], q2[SWIGLU ? kQ4KU : 1];
+  float am[kQ4KU], am2[SWIGLU ? kQ4KU : 1];
+  int tile = blockIdx.x;
+  if (tile < n_tiles) load_batch(tile, 0, q, am, q2, am2);
+  gv_stage16(p, sx, lds, s_rstd);
+
+  // expand one 32-bit word (8 codes, first element in the high nibble of the first byte) and run its two MMAs
+  auto word_mma = [&](float c[4], uint32_t w, float scale, const uint4& xa, const uint4& xb) {
+    float e[8];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const uint32_t byte = (w >> (8 * b)) & 0xffu;
+      e[2 * b] = lut[byte >> 4] * scale;
+      e[2 * b + 1] = lut[byte & 0xfu] * scale;
+    }
+    mma_16816(c, xa.x, xb.x, xa.y, xb.y, gv_pack2(e[0], e[1]), gv_pack2(e[2], e[3]));
+    mma_16816(c, xa.z, xb.z, xa.w, xb.w, gv_pack2(e[4], e[5]), gv_pack2(e[6], e[7]));
+  };
+
+  for (; tile < n_tiles; tile += gridDim.x) {
+    float c[4] = {0.f, 0.f, 0.f, 0.f}, c2[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r0 = 0; r0 < rounds; r0 += kQ4KU) {
+      if (r0 > 0) load_batch(tile, r0, q, am, q2, am2);
+#pragma unroll
+      for (int u = 0; u < kQ4KU; ++u) {
+        if (r0 + u >= rounds) break;
+        const int k = ((r0 + u) * kTcWarps + warp) * 128 + g * 32;
+        const uint32_t words[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+        const uint32_t words2[4] = {SWIGLU ? q2[u].x : 0u, SWIGLU ? q2[u].y : 0u, SWIGLU ? q2[u].z : 0u, SWIGLU ? q2[u].w : 0u};
+#pragma unroll
+        for (int sidx = 0; sidx < 4; ++sidx) {
+          const int kk = k + sidx * 8;
+          const bool in = kk < K;
+          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+          const uint4 xa = in ? *reinterpret_cast<const uint4*>(sx + col * lds + kk) : zero;
+          const uint4 xb = in ? *reinterpret_cast<const uint4*>(sx + (col + 8) * lds + kk) : zero;
+          word_mma(c, words[sidx], am[u], xa, xb);
+          if (SWIGLU) word_mma(c2, words2[sidx], am2[u], xa, xb);
+        }
+      }
+    }
+    const int next = tile + gridDim.x;
+    if (next < n_tiles) load_batch(next, 0, q, am, q2, am2);
+    float* my = red + (warp * 2) * 128;
+    *reinterpret_cast<float4*>(my + lane * 4) = make_float4(c[0], c[1], c[2], c[3]);
+    if (SWIGLU) *reinterpret_cast<float4*>(my + 128 + lane * 4) = make_float4(c2[0], c2[1], c2[2], c2[3]);
+    __syncthreads();
+    gv_tile_epilogue<SWIGLU>(p, red, tile);
+    __syncthreads();
+  }
+}
+
+template <bool SWIGLU>
+static int launch_gemv_q4(const GemvParams& p, cudaStream_t st) {
+  const size_t smem = static_cast<size_t>(16) * (p.K + kTcPad) * 2 + kTcWarps * 2 * 128 * sizeof(float);
+  static size_t configured = 0;
+  if (smem > 40 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_q4_tc_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = 200 * 1024;
+  }
+  const int n_tiles = (p.N + 7) / 8;
+  const int grid = n_tiles < 148 * 8 ? n_tiles : 148 * 8;
+  return static_cast<int>(launch_pdl(gemv_q4_tc_kernel<SWIGLU>, dim3(grid), dim3(kTcThreads), smem, st, p));
 }
 
 template <bool SWIGLU>
@@ -436,7 +584,7 @@ extern "C" int pm_gemv(const void* x, int ldx, const void* w, int ldw, const voi
     const char* e = getenv("PMETAL_GEMV_TC");
     use_tc = e ? atoi(e) : 1;
   }
-  if (use_tc && !t && (K % 32) == 0 && static_cast<size_t>(16) * (K + kTcPad) * 2 + 8192 <= 200 * 1024)
+  if (use_tc && (K % 32) == 0 && static_cast<size_t>(16) * (K + kTcPad) * 2 + 8192 <= 200 * 1024)
     return swiglu ? launch_gemv_tc<true>(p, st) : launch_gemv_tc<false>(p, st);
   // wide outputs: several columns per warp; narrow outputs: one column per warp (so that every SM gets work) with a
   // deeper load pipeline instead
@@ -449,4 +597,28 @@ extern "C" int pm_gemv(const void* x, int ldx, const void* w, int ldw, const voi
   if (M <= 4) return wide ? launch_gemv<4, 4, 4, false>(p, st) : launch_gemv<4, 1, 8, false>(p, st);
   if (M <= 8) return wide ? launch_gemv<8, 2, 4, false>(p, st) : launch_gemv<8, 1, 8, false>(p, st);
   return wide ? launch_gemv<16, 2, 2, false>(p, st) : launch_gemv<16, 1, 4, false>(p, st);
+}
+
+// 4-bit weights: qdata holds N_w * K / 2 bytes (two codes per byte, first element in the high nibble), absmax one fp32
+// per qblock elements or absmax_q one byte per block with scale / offset (double quantisation). K % 32 == 0,
+// qblock % 32 == 0. Other arguments as pm_gemv.
+extern "C" int pm_gemv_q4(const void* x, int ldx, const void* qdata, const float* absmax, const void* absmax_q,
+                          float am_scale, float am_offset, int qblock, int fp4, const void* norm_w, float eps,
+                          const void* residual, int ldr, void* y, int ldy, int M, int N, int K, int swiglu, float alpha,
+                          const void* t, int ldt, const float* lora_b, int r, const int* seg_end, cudaStream_t st) {
+  if (M < 1 || M > 16 || N < 1 || K < 32 || (K % 32) || (ldx % 8) || qblock < 32 || (qblock % 32)) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(qdata)) & 15) return -2;
+  if (!absmax && !absmax_q) return -2;
+  if (static_cast<size_t>(16) * (K + kTcPad) * 2 + 8192 > 200 * 1024) return -3;
+  GemvParams p{};
+  p.x = static_cast<const __nv_bfloat16*>(x); p.ldx = ldx;
+  p.qdata = static_cast<const uint8_t*>(qdata); p.absmax = absmax; p.absmax_q = static_cast<const uint8_t*>(absmax_q);
+  p.am_scale = am_scale; p.am_offset = am_offset; p.qblock = qblock; p.fp4 = fp4;
+  p.norm_w = static_cast<const __nv_bfloat16*>(norm_w); p.eps = eps;
+  p.residual = static_cast<const __nv_bfloat16*>(residual); p.ldr = ldr;
+  p.y = static_cast<__nv_bfloat16*>(y); p.ldy = ldy;
+  p.M = M; p.N = N; p.K = K; p.swiglu = swiglu; p.alpha = alpha;
+  p.t = static_cast<const __nv_bfloat16*>(t); p.ldt = ldt; p.lora_b = lora_b; p.r = r;
+  for (int i = 0; i < 4; ++i) p.seg_end[i] = seg_end ? seg_end[i] : 0x7fffffff;
+  return swiglu ? launch_gemv_q4<true>(p, st) : launch_gemv_q4<false>(p, st);
 }

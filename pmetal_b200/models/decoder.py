@@ -125,9 +125,15 @@ class FusedLinear(nn.Module):
                                getattr(self, "qweight", None))
 
     def gemv_ok(self, m: int) -> bool:
-        """Decode fast path: a few rows, plain bf16 weight, no bias."""
-        return (m <= GEMV_MAX_ROWS and self.bias is None and getattr(self, "qweight", None) is None and self.weight.is_cuda
-                and self.weight.dtype == torch.bfloat16 and not self.weight.requires_grad and self.in_features % 8 == 0)
+        """Decode fast path: a few rows, no bias, and either a plain bf16 weight or a 4-bit (NF4 / FP4) packed weight
+        that the mat-vec kernel expands on the fly."""
+        if m > GEMV_MAX_ROWS or self.bias is not None:
+            return False
+        q = getattr(self, "qweight", None)
+        if q is not None:
+            return (q.scheme in ("nf4", "fp4") and q.data.is_cuda and q.block_size % 32 == 0 and self.in_features % 32 == 0)
+        return (self.weight.is_cuda and self.weight.dtype == torch.bfloat16 and not self.weight.requires_grad
+                and self.in_features % 8 == 0)
 
     def gemv_forward(self, x: torch.Tensor, norm_w=None, eps: float = 1e-6, residual=None, swiglu: bool = False):
         """y = norm(x) W^T (+ LoRA) (+ residual), optionally SwiGLU over the (gate, up) halves; one or two launches of
@@ -139,9 +145,11 @@ class FusedLinear(nn.Module):
             if a_c is None:
                 a_c = self.lora_a.detach().to(torch.bfloat16)
             t = nat.gemv(x, a_c, norm_w, eps, alpha=self.scale)
-            return nat.gemv(x, self.weight, norm_w, eps, residual, swiglu, t=t, lora_b=self.lora_b.detach(), r=self.r,
-                            seg_sizes=self.seg_sizes)
-        return nat.gemv(x, self.weight, norm_w, eps, residual, swiglu)
+        q = getattr(self, "qweight", None)
+        kw = dict(t=t, lora_b=self.lora_b.detach(), r=self.r, seg_sizes=self.seg_sizes) if t is not None else {}
+        if q is not None:
+            return nat.gemv_q4(x, q, norm_w, eps, residual, swiglu, **kw)
+        return nat.gemv(x, self.weight, norm_w, eps, residual, swiglu, **kw)
 
     def _lora_delta(self, x: torch.Tensor) -> torch.Tensor:
         outs, o = [], 0

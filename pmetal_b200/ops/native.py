@@ -670,6 +670,23 @@ def gemv(x, w, norm_w=None, eps: float = 1e-6, residual=None, swiglu: bool = Fal
     return y
 
 
+def gemv_q4(x, q, norm_w=None, eps: float = 1e-6, residual=None, swiglu: bool = False, alpha: float = 1.0, t=None,
+            lora_b=None, r: int = 0, seg_sizes: Sequence[int] = ()):
+    """As ``gemv`` with the weight given as a 4-bit ``QuantizedTensor`` (nf4 / fp4) of shape [N_w, K]: the codes are
+    expanded to bf16 inside the kernel, so a decode step streams a quarter of the bytes."""
+    M, K = x.shape
+    Nw = q.shape[0]
+    N = Nw // 2 if swiglu else Nw
+    y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    ends = _seg_ends(seg_sizes) if len(seg_sizes) > 1 else (c_int * 4)(*([0x7FFFFFFF] * 4))
+    _chk(lib().pm_gemv_q4(_p(x), c_int(x.stride(0)), _p(q.data), _p(q.absmax), _p(q.absmax_q), c_float(q.absmax_scale),
+                          c_float(q.absmax_offset), c_int(q.block_size), c_int(1 if q.scheme == "fp4" else 0), _p(norm_w),
+                          c_float(eps), _p(residual), c_int(residual.stride(0) if residual is not None else 0), _p(y),
+                          c_int(N), c_int(M), c_int(N), c_int(K), c_int(int(swiglu)), c_float(alpha), _p(t),
+                          c_int(t.stride(0) if t is not None else 0), _p(lora_b), c_int(r), ends, _stream()), "pm_gemv_q4")
+    return y
+
+
 # ------------------------------------------------------------------------------------------- whole-step decode kernel
 def decode_layers_supported(M: int, H: int, hq: int, hkv: int, I: int) -> bool:
     return bool(lib().pm_decode_layers_supported(c_int(M), c_int(H), c_int(hq), c_int(hkv), c_int(I)))

@@ -339,3 +339,39 @@ def test_gemv_tensor_core_swiglu(M, K, I):
     ref = torch.nn.functional.silu(full[:, :I]) * full[:, I:]
     assert y.shape == (M, I)
     assert (y.float() - ref).abs().max() <= 0.03 * ref.abs().max() + 2e-2
+
+
+@pytest.mark.parametrize("scheme,double_quant,M,N,K,swiglu", [("nf4", False, 1, 512, 1024, False), ("nf4", True, 7, 1000, 2560, False),
+                                                             ("fp4", False, 16, 384, 1024, True), ("nf4", True, 3, 768, 3072, True)])
+def test_gemv_4bit_weights_match_dequantised_reference(scheme, double_quant, M, N, K, swiglu):
+    """The fused 4-bit mat-vec (codes expanded in registers) against dequantise-then-multiply, with norm, residual and
+    a LoRA term."""
+    from pmetal_b200.lora.nf4 import dequantize, quantize
+    nat = _nat()
+    torch.manual_seed(N + K)
+    rows = 2 * N if swiglu else N
+    w = (torch.randn(rows, K, device="cuda") * K ** -0.5)
+    q = quantize(w, scheme, 64, double_quant)
+    wd = dequantize(q, torch.float32).bfloat16().float()
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    nw = (1 + 0.1 * torch.randn(K, device="cuda")).bfloat16()
+    r = 8
+    a = (torch.randn(r, K, device="cuda") * K ** -0.5).bfloat16()
+    b = torch.randn(rows, r, device="cuda") * 0.1
+    xn = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)
+    xn = (xn.bfloat16().float() * nw.float()).bfloat16()
+    t = nat.gemv(x, a, norm_w=nw, eps=1e-6, alpha=2.0)
+    full = xn.float() @ wd.t() + t.float() @ b.t()
+    if swiglu:
+        y = nat.gemv_q4(x, q, norm_w=nw, eps=1e-6, swiglu=True, t=t, lora_b=b, r=r)
+        ref = torch.nn.functional.silu(full[:, :N]) * full[:, N:]
+    else:
+        res = torch.randn(M, N, device="cuda").bfloat16()
+        y = nat.gemv_q4(x, q, norm_w=nw, eps=1e-6, residual=res, t=t, lora_b=b, r=r)
+        ref = full + res.float()
+    assert y.shape == (M, N)
+    assert (y.float() - ref).abs().max() <= 0.03 * ref.abs().max() + 2e-2
+    # the bf16 tensor-core path with a LoRA term agrees too
+    y2 = nat.gemv(x, wd.bfloat16(), norm_w=nw, eps=1e-6, swiglu=swiglu, t=t, lora_b=b, r=r)
+    ref2 = ref if swiglu else full
+    assert (y2.float() - ref2).abs().max() <= 0.03 * ref2.abs().max() + 2e-2

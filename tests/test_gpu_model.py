@@ -238,3 +238,44 @@ def test_whole_step_decode_kernel_matches_per_layer_path(batch, heads, kv_heads)
     err = (a - b).abs().max().item()
     assert err < 0.06 * a.abs().max().item() + 0.02, err
     assert (a.argmax(-1) == b.argmax(-1)).float().mean().item() > 0.9
+
+
+def test_decode_with_4bit_base_weights_uses_the_fused_kernel():
+    """A model whose projections are NF4-packed decodes through the fused dequantising mat-vec; the logits agree with
+    the same model holding the dequantised weights in bf16."""
+    import copy
+
+    from pmetal_b200.lora.nf4 import dequantize
+    from pmetal_b200.lora.qlora import quantize_base
+    from pmetal_b200.models.config import ModelArgs
+    from pmetal_b200.models.decoder import DecoderLM
+    from pmetal_b200.models.generation import Generator
+    from pmetal_b200.ops import native
+    dev = torch.device("cuda")
+    cfg = ModelArgs(vocab_size=512, hidden_size=256, intermediate_size=384, num_hidden_layers=2,
+                    num_attention_heads=2, num_key_value_heads=1, head_dim=128)
+    base = DecoderLM(cfg).init_weights(0.05, 4).to(dev).to(torch.bfloat16).eval()
+    for p in base.parameters():
+        p.requires_grad_(False)
+    packed = copy.deepcopy(base)
+    quantize_base(packed, "nf4", 64, True)
+    plain = copy.deepcopy(base)
+    for (_, _, fq), (_, _, fp) in zip(packed.fused_linears(), plain.fused_linears()):
+        fp.weight.data.copy_(dequantize(fq.qweight, torch.bfloat16))
+        assert fq.gemv_ok(1) and fq.weight.numel() == 0
+    prompts = [torch.randint(0, 512, (40,)).tolist(), torch.randint(0, 512, (75,)).tolist()]
+    outs = []
+    for m in (packed, plain):
+        gen = Generator(m, num_blocks=32, cuda_graphs=False)
+        seqs = [gen.new_seq() for _ in prompts]
+        ids = gen.prefill(seqs, prompts).argmax(-1)
+        steps = []
+        for _ in range(3):
+            logits = gen.decode_step(seqs, ids)
+            steps.append(logits.float())
+            ids = logits.argmax(-1)
+        outs.append(torch.stack(steps))
+        native.check_status()
+    a, b = outs
+    assert torch.isfinite(a).all()
+    assert (a[0] - b[0]).abs().max().item() < 0.08 * b[0].abs().max().item() + 0.03
