@@ -349,7 +349,9 @@ def _quantize_args(sp):
     p.add_argument("--kl-calibrate", action="store_true")
     p.add_argument("--target-bpw", type=float)
     p.add_argument("--threads", type=int, default=0)
-    p.add_argument("--format", default="gguf", choices=["gguf", "fp8"])
+    p.add_argument("--format", default="gguf", choices=["gguf", "fp8", "mlx"],
+                   help="mlx: affine group quantisation with quality-driven bit allocation (--target-bpw, default 4.5)")
+    p.add_argument("--group-size", type=int, default=64)
     return p
 
 
@@ -360,6 +362,10 @@ def cmd_quantize(a) -> int:
     if a.format == "fp8":
         from ..models.fp8 import export_fp8_checkpoint
         print(json.dumps(export_fp8_checkpoint(mdir, a.output)))
+        return 0
+    if a.format == "mlx":
+        from ..quant.mlx_affine import quantize_model as quantize_mlx
+        print(json.dumps(quantize_mlx(mdir, a.output, a.target_bpw or 4.5, a.group_size)))
         return 0
     from ..gguf.convert import quantize_model
     from ..gguf.recipe import DynamicConfig
