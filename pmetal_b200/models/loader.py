@@ -71,6 +71,11 @@ def load_pretrained(model: str, dtype: torch.dtype = torch.bfloat16, device="cpu
     m = DecoderLM(args)
     sd = read_state_dict(path)
     sd = {k: v for k, v in sd.items() if not k.endswith("rotary_emb.inv_freq")}
+    if any(k.endswith(".scales") for k in sd):          # affine group-quantised checkpoint (MLX layout): expand on load
+        from ..quant.mlx_affine import load_quantized_state_dict
+        with open(os.path.join(path, "config.json"), "r", encoding="utf-8") as fh:
+            qcfg = json.load(fh).get("quantization") or {"bits": 4, "group_size": 64}
+        sd = load_quantized_state_dict(sd, qcfg, torch.float32)
     m.load_hf_state_dict(sd, strict=strict)
     return _cast(m, dtype, device), args, path
 

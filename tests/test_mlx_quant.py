@@ -86,3 +86,9 @@ def test_checkpoint_round_trip(tmp_path):
     w, r = ref["model.layers.0.mlp.down_proj.weight"].float(), dense["model.layers.0.mlp.down_proj.weight"]
     assert float((w - r).norm() / w.norm()) < 0.2
     assert torch.equal(dense["model.layers.0.input_layernorm.weight"], ref["model.layers.0.input_layernorm.weight"])
+    # the model loader expands such a checkpoint on the fly
+    from pmetal_b200.models.loader import load_pretrained
+    m2, _, _ = load_pretrained(str(tmp_path / "q"), dtype=torch.float32)
+    ids = torch.randint(0, cfg.vocab_size, (1, 12))
+    a, b = m(ids[0]), m2(ids[0])
+    assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.9
