@@ -563,13 +563,21 @@ class GatedDeltaNet(nn.Module):
         qf, kf = q.float(), k.float()
         qf = qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
         kf = kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + 1e-6)
-        outs, states = [], []
-        for i in range(B):
-            S0 = st[1][i] if st is not None else None
-            fn = gdn_recurrent if T <= 4 else gdn_chunked
-            y, S = fn(qf[i], kf[i], v[i].float(), g[i], beta[i].float(), S0)
-            outs.append(y)
-            states.append(S)
+        use_kernel = False
+        if x.is_cuda and not torch.is_grad_enabled():
+            from ...ops import native
+            use_kernel = native.available() and native.gdn_scan_supported(dk, dv)
+        if use_kernel:            # recurrence kernel with the state in registers (csrc/gdn.cu)
+            y_all, S_all = native.gdn_scan(qf, kf, v, g, beta, st[1] if st is not None else None)
+            outs, states = list(y_all), list(S_all)
+        else:
+            outs, states = [], []
+            for i in range(B):
+                S0 = st[1][i] if st is not None else None
+                fn = gdn_recurrent if T <= 4 else gdn_chunked
+                y, S = fn(qf[i], kf[i], v[i].float(), g[i], beta[i].float(), S0)
+                outs.append(y)
+                states.append(S)
         if cache is not None:
             cache.state[self.idx] = (full[:, :, -(kw - 1):].detach(), torch.stack(states))
             cache.state["length"] = int(cache.state.get("length", 0)) if self.idx != self._first_linear() else \

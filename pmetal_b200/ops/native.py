@@ -687,6 +687,24 @@ def gemv_q4(x, q, norm_w=None, eps: float = 1e-6, residual=None, swiglu: bool = 
     return y
 
 
+def gdn_scan(q, k, v, g, beta, state=None):
+    """Gated delta rule over a token sequence (csrc/gdn.cu). q, k [B, T, H, dk], v [B, T, H, dv], g, beta [B, T, H], all
+    fp32; ``state`` [B, H, dk, dv] fp32 or None (zeros). Returns (y [B, T, H, dv], final state)."""
+    B, T, H, dk = q.shape
+    dv = v.shape[-1]
+    f = lambda t: t.float().contiguous()
+    q, k, v, g, beta = f(q), f(k), f(v), f(g), f(beta)
+    st = torch.zeros(B, H, dk, dv, dtype=torch.float32, device=q.device) if state is None else state.float().contiguous().clone()
+    y = torch.empty(B, T, H, dv, dtype=torch.float32, device=q.device)
+    _chk(lib().pm_gdn_scan(_p(q), _p(k), _p(v), _p(g), _p(beta), _p(st), _p(y), c_int(B), c_int(T), c_int(H), c_int(dk),
+                           c_int(dv), _stream()), "pm_gdn_scan")
+    return y, st
+
+
+def gdn_scan_supported(dk: int, dv: int) -> bool:
+    return dk in (64, 128) and dv in (64, 128)
+
+
 # ------------------------------------------------------------------------------------------- whole-step decode kernel
 def decode_layers_supported(M: int, H: int, hq: int, hkv: int, I: int) -> bool:
     return bool(lib().pm_decode_layers_supported(c_int(M), c_int(H), c_int(hq), c_int(hkv), c_int(I)))

@@ -375,3 +375,25 @@ def test_gemv_4bit_weights_match_dequantised_reference(scheme, double_quant, M, 
     y2 = nat.gemv(x, wd.bfloat16(), norm_w=nw, eps=1e-6, swiglu=swiglu, t=t, lora_b=b, r=r)
     ref2 = ref if swiglu else full
     assert (y2.float() - ref2).abs().max() <= 0.03 * ref2.abs().max() + 2e-2
+
+
+@pytest.mark.parametrize("dk,dv,T", [(128, 128, 1), (128, 128, 37), (64, 64, 20), (128, 64, 9), (64, 128, 5)])
+def test_gated_delta_rule_scan_kernel(dk, dv, T):
+    from pmetal_b200.models.gdn import gdn_recurrent
+    nat = _nat()
+    torch.manual_seed(dk + T)
+    B, H = 2, 3
+    q = torch.nn.functional.normalize(torch.randn(B, T, H, dk, device="cuda"), dim=-1) * dk ** -0.5
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, dk, device="cuda"), dim=-1)
+    v = torch.randn(B, T, H, dv, device="cuda")
+    g = torch.rand(B, T, H, device="cuda") * 0.3 + 0.7
+    beta = torch.rand(B, T, H, device="cuda")
+    S0 = torch.randn(B, H, dk, dv, device="cuda") * 0.1
+    y, S = nat.gdn_scan(q, k, v, g, beta, S0)
+    for b in range(B):
+        yr, Sr = gdn_recurrent(q[b], k[b], v[b], g[b], beta[b], S0[b])
+        assert torch.allclose(y[b], yr, atol=1e-4, rtol=1e-4), float((y[b] - yr).abs().max())
+        assert torch.allclose(S[b], Sr, atol=1e-4, rtol=1e-4)
+    y0, _ = nat.gdn_scan(q, k, v, g, beta)                     # zero initial state
+    yr0, _ = gdn_recurrent(q[0], k[0], v[0], g[0], beta[0])
+    assert torch.allclose(y0[0], yr0, atol=1e-4, rtol=1e-4)
