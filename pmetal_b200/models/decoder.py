@@ -444,18 +444,26 @@ class DecoderLM(nn.Module):
                                            cfg.intermediate_size)
 
     def _mega_table(self, cache) -> torch.Tensor:
-        t = self._mega_tables.get(id(cache))
-        if t is None:
-            rows = []
-            for li, layer in enumerate(self.layers):
-                at, mlp = layer.self_attn, layer.mlp
-                rows.append([layer.input_layernorm.data_ptr(), at.qkv_proj.weight.data_ptr(),
-                             at.q_norm.data_ptr() if at.q_norm is not None else 0,
-                             at.k_norm.data_ptr() if at.k_norm is not None else 0, at.o_proj.weight.data_ptr(),
-                             layer.post_attention_layernorm.data_ptr(), mlp.gate_up_proj.weight.data_ptr(),
-                             mlp.down_proj.weight.data_ptr(), cache.k[li].data_ptr(), cache.v[li].data_ptr()])
-            t = torch.tensor(rows, dtype=torch.int64, device=self.embed_tokens.device)
-            self._mega_tables[id(cache)] = t
+        """Per-layer pointer table of the whole-step kernel for this cache. Entries are tied to the cache object by a
+        weak reference, so a new cache that happens to reuse the id of a freed one gets a fresh table."""
+        import weakref
+        ent = self._mega_tables.get(id(cache))
+        sig = (self.layers[0].self_attn.qkv_proj.weight.data_ptr(), self.layers[-1].mlp.down_proj.weight.data_ptr(),
+               cache.k[0].data_ptr())
+        if ent is not None and ent[0]() is cache and ent[2] == sig:      # same cache object, weights not re-allocated
+            return ent[1]
+        for key in [k for k, e in self._mega_tables.items() if e[0]() is None]:
+            del self._mega_tables[key]
+        rows = []
+        for li, layer in enumerate(self.layers):
+            at, mlp = layer.self_attn, layer.mlp
+            rows.append([layer.input_layernorm.data_ptr(), at.qkv_proj.weight.data_ptr(),
+                         at.q_norm.data_ptr() if at.q_norm is not None else 0,
+                         at.k_norm.data_ptr() if at.k_norm is not None else 0, at.o_proj.weight.data_ptr(),
+                         layer.post_attention_layernorm.data_ptr(), mlp.gate_up_proj.weight.data_ptr(),
+                         mlp.down_proj.weight.data_ptr(), cache.k[li].data_ptr(), cache.v[li].data_ptr()])
+        t = torch.tensor(rows, dtype=torch.int64, device=self.embed_tokens.device)
+        self._mega_tables[id(cache)] = (weakref.ref(cache), t, sig)
         return t
 
     def _paged_attention_reference(self, qkv, at, rope, cache, meta, li):

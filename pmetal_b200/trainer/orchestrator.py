@@ -45,6 +45,7 @@ class TrainingJobConfig:
     gradient_checkpointing_layers: int = 0
     log_metrics: Optional[str] = None
     resume: bool = False
+    resume_bundle: Optional[str] = None
     adaptive_lr: bool = True
     dataset_format: str = "auto"
     custom_columns: Optional[object] = None
@@ -165,6 +166,12 @@ def run_training(job: TrainingJobConfig, phase_cb: Optional[Callable[[str], None
         if job.resume and ckpt is not None and ckpt.latest_path():
             loop.resume(ckpt.latest_path())
             log.info("resumed from %s at step %d", ckpt.latest_path(), loop.state.step)
+        if getattr(job, "resume_bundle", None):
+            from ..parallel.cloud_bridge import import_bundle
+            params, _opt, meta = import_bundle(job.resume_bundle)
+            loop.load_lora_tensors(params)
+            loop.state.step = int(meta.get("step", 0))
+            log.info("continued from bundle %s at step %d", job.resume_bundle, loop.state.step)
         phase("training")
         state = loop.run(loader, eval_loader)
         # ---- save
