@@ -421,21 +421,24 @@ class DecoderLM(nn.Module):
     def _mega_ok(self, T: int) -> bool:
         """The whole-step kernel covers dense layers with plain bf16 weights: no adapters, biases, sliding windows or
         soft-capping."""
-        ok = getattr(self, "_mega_ok_cached", None)
-        if ok is None:
-            cfg = self.cfg
-            ok = cfg.attn_logit_softcap <= 0 and cfg.head_dim == 128
+        if not hasattr(self, "_mega_scratch"):
+            self._mega_scratch = {}
+            self._mega_tables = {}
+        cfg = self.cfg
+        ok = cfg.attn_logit_softcap <= 0 and cfg.head_dim == 128
+        if ok:            # checked on every call: adapters or packed weights may have been attached since the last one
             for layer in self.layers:
                 at = layer.self_attn
                 if not isinstance(layer.mlp, MLP) or at.window:
                     ok = False
                     break
                 for lin in (at.qkv_proj, at.o_proj, layer.mlp.gate_up_proj, layer.mlp.down_proj):
-                    if not lin.gemv_ok(1) or lin.lora_a is not None or not lin.weight.is_contiguous():
+                    if (lin.lora_a is not None or getattr(lin, "qweight", None) is not None or not lin.gemv_ok(1)
+                            or not lin.weight.is_contiguous()):
                         ok = False
-            self._mega_ok_cached = ok
-            self._mega_scratch = {}
-            self._mega_tables = {}
+                        break
+                if not ok:
+                    break
         if not ok:
             return False
         from ..ops import native as nat
