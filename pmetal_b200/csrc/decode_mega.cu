@@ -35,6 +35,7 @@ constexpr int kDmThreads = 256;
 constexpr int kDmWarps = 8;
 constexpr int kDmPad = 32;            // row padding of staged activations (bank spread for the fragment loads)
 constexpr int kDmMaxNT = 4;           // output tiles a CTA works on at once
+constexpr int kDmPre = 24;            // weight loads a lane keeps in flight across a barrier
 constexpr int kStatusDecodeBarrier = 109;
 constexpr unsigned long long kDmBarrierLimitNs = 1000000000ull;   // 1 s
 
@@ -209,10 +210,10 @@ __device__ __forceinline__ void dm_prefetch_tiles(const __nv_bfloat16* w, int N,
 
 // First batch of weight loads of a mat-vec phase (tiles base .. of this CTA, chunks r0 = 0 ..): issued before the grid
 // barrier that precedes the phase, consumed by dm_matvec after it. pre holds NT x RB loads (two halves of NT x RB / 2
-// each for SwiGLU), sixteen per lane.
+// each for SwiGLU), up to kDmPre per lane.
 template <int NT, int RB, bool SWIGLU>
 __device__ __forceinline__ void dm_load_batch(const __nv_bfloat16* __restrict__ w, int N, int K, int base, int r0,
-                                              uint4 (&pre)[16]) {
+                                              uint4 (&pre)[kDmPre]) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane & 3, col = lane >> 2;
   const int n_tiles = (N + 7) / 8, rounds = (K + 255) / 256;
 #pragma unroll
@@ -226,7 +227,7 @@ __device__ __forceinline__ void dm_load_batch(const __nv_bfloat16* __restrict__ 
       const bool ok = tile < n_tiles && r0 + u < rounds && k < K;
       pre[j * RB + u] = ok ? __ldg(reinterpret_cast<const uint4*>(wr + k)) : make_uint4(0u, 0u, 0u, 0u);
       if (SWIGLU)
-        pre[8 + j * RB + u] = ok ? __ldg(reinterpret_cast<const uint4*>(wr + static_cast<long long>(N) * K + k))
+        pre[NT * RB + j * RB + u] = ok ? __ldg(reinterpret_cast<const uint4*>(wr + static_cast<long long>(N) * K + k))
                                  : make_uint4(0u, 0u, 0u, 0u);
     }
   }
@@ -238,7 +239,7 @@ __device__ __forceinline__ void dm_load_batch(const __nv_bfloat16* __restrict__ 
 // k = 8 g .. 8 g + 7 of a chunk for column lane / 4; MMA j of the chunk contracts k = 8 g + 4 j + {0, 1} and {2, 3}.
 template <int NT, int RB, bool SWIGLU, typename Epi>
 __device__ __forceinline__ void dm_matvec(const __nv_bfloat16* sx, int lds, const __nv_bfloat16* __restrict__ w, int N,
-                                          int K, int M, float* red, uint4 (&pre)[16], Epi epi) {
+                                          int K, int M, float* red, uint4 (&pre)[kDmPre], Epi epi) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane & 3, col = lane >> 2;
   const int n_tiles = (N + 7) / 8;
   const int rounds = (K + 255) / 256;
@@ -265,7 +266,7 @@ __device__ __forceinline__ void dm_matvec(const __nv_bfloat16* sx, int lds, cons
           dm_mma(c[j], xa.x, xb.x, xa.y, xb.y, wv.x, wv.y);
           dm_mma(c[j], xa.z, xb.z, xa.w, xb.w, wv.z, wv.w);
           if (SWIGLU) {
-            const uint4 wv2 = pre[8 + j * RB + u];
+            const uint4 wv2 = pre[NT * RB + j * RB + u];
             dm_mma(c2[j], xa.x, xb.x, xa.y, xb.y, wv2.x, wv2.y);
             dm_mma(c2[j], xa.z, xb.z, xa.w, xb.w, wv2.z, wv2.w);
           }
@@ -300,10 +301,10 @@ __device__ __forceinline__ void dm_matvec(const __nv_bfloat16* sx, int lds, cons
 // Runtime choice of how many tiles a CTA keeps in flight: as many as 16 weight loads per lane allow. The same choice
 // is made by the preload before the barrier and by the phase after it.
 template <bool SWIGLU>
-__device__ __forceinline__ void dm_preload(const __nv_bfloat16* w, int N, int K, uint4 (&pre)[16]) {
+__device__ __forceinline__ void dm_preload(const __nv_bfloat16* w, int N, int K, uint4 (&pre)[kDmPre]) {
   const int rounds = (K + 255) / 256;
   if (SWIGLU) {
-    if (rounds <= 4) dm_load_batch<2, 4, true>(w, N, K, blockIdx.x, 0, pre);
+    if (rounds <= 4) dm_load_batch<3, 4, true>(w, N, K, blockIdx.x, 0, pre);
     else dm_load_batch<1, 8, true>(w, N, K, blockIdx.x, 0, pre);
   } else {
     if (rounds <= 4) dm_load_batch<4, 4, false>(w, N, K, blockIdx.x, 0, pre);
@@ -313,10 +314,10 @@ __device__ __forceinline__ void dm_preload(const __nv_bfloat16* w, int N, int K,
 }
 template <bool SWIGLU, typename Epi>
 __device__ __forceinline__ void dm_matvec_auto(const __nv_bfloat16* sx, int lds, const __nv_bfloat16* w, int N, int K,
-                                               int M, float* red, uint4 (&pre)[16], Epi epi) {
+                                               int M, float* red, uint4 (&pre)[kDmPre], Epi epi) {
   const int rounds = (K + 255) / 256;
   if (SWIGLU) {
-    if (rounds <= 4) dm_matvec<2, 4, true>(sx, lds, w, N, K, M, red, pre, epi);
+    if (rounds <= 4) dm_matvec<3, 4, true>(sx, lds, w, N, K, M, red, pre, epi);
     else dm_matvec<1, 8, true>(sx, lds, w, N, K, M, red, pre, epi);
   } else {
     if (rounds <= 4) dm_matvec<4, 4, false>(sx, lds, w, N, K, M, red, pre, epi);
@@ -360,8 +361,9 @@ __device__ __forceinline__ uint2 dm_pack4(const float x[4]) {
 // take interleaved groups of eight keys (all sixteen loads of a group are issued before the arithmetic), merge their
 // running (max, sum, output) through shared memory, and REP query heads of the kv head are processed together.
 // `sm` is scratch of at least 8 * REP * 132 floats.
-// Splits actually used for a row: one per 128 cached keys, so that short contexts skip the cross-CTA merge.
-__device__ __forceinline__ int dm_eff_splits(int cached, int ns) { return max(1, min(ns, (cached + 127) / 128)); }
+// Splits actually used for a row: one per 64 cached keys (eight warps x one group of eight keys, all requested before
+// the barrier), so that short contexts need no second round of key loads and few partial results to merge.
+__device__ __forceinline__ int dm_eff_splits(int cached, int ns) { return max(1, min(ns, (cached + 63) / 64)); }
 
 // First group of eight keys / values of this CTA's first attention item, requested before the barrier that precedes
 // the attention phase (cached keys do not depend on the projections of the current step).
@@ -587,7 +589,7 @@ __global__ void __launch_bounds__(kDmThreads, 1) decode_layers_kernel(const DmPa
   };
   const int qkv_n = (p.hq + 2 * p.hkv) * 128, qd = p.hq * 128;
   const int rep = p.hq / p.hkv;
-  uint4 pre[16];
+  uint4 pre[kDmPre];
   uint2 pk[8], pv[8];
   dm_preload<false>(p.layers[0].wqkv, qkv_n, p.H, pre);
   for (int i = threadIdx.x; i < (16 - p.M) * (lds / 8); i += kDmThreads)      // rows >= M stay zero for the whole step
