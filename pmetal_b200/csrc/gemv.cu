@@ -271,8 +271,10 @@ __device__ __forceinline__ float gv_lora(const GemvParams& p, int m, int row) {
   return s;
 }
 
-// Stage x (optionally RMS-normalised) as [16][lds] bf16; rows >= M are zero. Shared by the tensor-core kernels.
+// Stage x (optionally RMS-normalised) as [rows][lds] bf16 (rows = 8 when M <= 8, else 16); rows >= M are zero. Shared by
+// the tensor-core kernels; with M <= 8 the upper half of the MMA's A operand is passed as zero registers instead.
 __device__ __forceinline__ void gv_stage16(const GemvParams& p, __nv_bfloat16* sx, int lds, float* s_rstd) {
+  const int rows = p.M > 8 ? 16 : 8;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, K = p.K;
   if (p.norm_w) {
     for (int m = warp; m < p.M; m += kTcWarps) {
@@ -291,7 +293,7 @@ __device__ __forceinline__ void gv_stage16(const GemvParams& p, __nv_bfloat16* s
     }
     __syncthreads();
   }
-  for (int i = threadIdx.x; i < 16 * (K / 8); i += kTcThreads) {
+  for (int i = threadIdx.x; i < rows * (K / 8); i += kTcThreads) {
     const int m = i / (K / 8), k = (i - m * (K / 8)) * 8;
     uint4 raw = make_uint4(0u, 0u, 0u, 0u);
     if (m < p.M) {
@@ -385,7 +387,7 @@ __global__ void __launch_bounds__(kTcThreads) gemv_tc_kernel(const GemvParams p)
         const int k = ((r0 + u) * kTcWarps + warp) * 32 + g * 8;
         if (r0 + u >= rounds || k >= K) break;
         const uint4 xa = *reinterpret_cast<const uint4*>(sx + col * lds + k);
-        const uint4 xb = *reinterpret_cast<const uint4*>(sx + (col + 8) * lds + k);
+        const uint4 xb = p.M > 8 ? *reinterpret_cast<const uint4*>(sx + (col + 8) * lds + k) : make_uint4(0u, 0u, 0u, 0u);
         mma_16816(c, xa.x, xb.x, xa.y, xb.y, wv[u].x, wv[u].y);
         mma_16816(c, xa.z, xb.z, xa.w, xb.w, wv[u].z, wv[u].w);
         if (SWIGLU) {
@@ -489,7 +491,7 @@ __global__ void __launch_bounds__(kTcThreads) gemv_q4_tc_kernel(const GemvParams
           const bool in = kk < K;
           const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
           const uint4 xa = in ? *reinterpret_cast<const uint4*>(sx + col * lds + kk) : zero;
-          const uint4 xb = in ? *reinterpret_cast<const uint4*>(sx + (col + 8) * lds + kk) : zero;
+          const uint4 xb = (in && p.M > 8) ? *reinterpret_cast<const uint4*>(sx + (col + 8) * lds + kk) : zero;
           word_mma(c, words[sidx], am[u], xa, xb);
           if (SWIGLU) word_mma(c2, words2[sidx], am2[u], xa, xb);
         }
@@ -516,7 +518,7 @@ static int launch_gemv_q4(const GemvParams& p, cudaStream_t st) {
     configured = 200 * 1024;
   }
   const int n_tiles = (p.N + 7) / 8;
-  const int grid = n_tiles < 148 * 8 ? n_tiles : 148 * 8;
+  const int grid = n_tiles < 148 * 2 ? n_tiles : 148 * 2;
   return static_cast<int>(launch_pdl(gemv_q4_tc_kernel<SWIGLU>, dim3(grid), dim3(kTcThreads), smem, st, p));
 }
 
@@ -530,7 +532,7 @@ static int launch_gemv_tc(const GemvParams& p, cudaStream_t st) {
     configured = 200 * 1024;
   }
   const int n_tiles = (p.N + 7) / 8;
-  const int grid = n_tiles < 148 * 8 ? n_tiles : 148 * 8;
+  const int grid = n_tiles < 148 * 2 ? n_tiles : 148 * 2;      // each CTA stages x once and loops over its tiles
   return static_cast<int>(launch_pdl(gemv_tc_kernel<SWIGLU>, dim3(grid), dim3(kTcThreads), smem, st, p));
 }
 
