@@ -870,54 +870,114 @@ def cmd_dflash(a) -> int:
 
 # ------------------------------------------------------------------------------------------- pack-experts
 def _pack_args(sp):
-    p = sp.add_parser("pack-experts", help="split a mixture-of-experts checkpoint into one file per (layer, expert)")
+    p = sp.add_parser("pack-experts", help="pack the routed experts of a mixture-of-experts checkpoint into per-layer files")
     p.add_argument("-m", "--model", required=True)
     p.add_argument("-o", "--output", required=True)
+    p.add_argument("--bits", type=int, default=4, choices=[2, 4])
+    p.add_argument("--group-size", type=int, default=64)
     return p
 
 
-def pack_experts(sd, out_dir: str) -> dict:
-    """Write ``experts/layer_{L:03d}_expert_{E:03d}.safetensors`` (gate_up / down of one expert) and ``dense.safetensors``
-    (everything else) plus ``expert_index.json``; stacked ``...mlp.experts.gate_up_proj`` tensors and per-expert
-    ``...experts.E.{gate,up,down}_proj.weight`` layouts are both understood
-    (reference: crates/pmetal/src/pack_experts.rs, expert files for streaming from disk)."""
+def _expert_record(hidden: int, inter: int, group: int, bits: int) -> dict:
+    """Byte layout of one expert inside ``layer_XX.bin``: gate, up, down, each as packed uint32 weights, bf16 scales and
+    bf16 biases (crates/pmetal-models/src/expert_layout.rs:62-140)."""
+    pf = 32 // bits
+    comps, off = {}, 0
+    for name, rows, cols in (("gate", inter, hidden), ("up", inter, hidden), ("down", hidden, inter)):
+        for field, size, shape in ((f"{name}_weight", rows * (cols // pf) * 4, [rows, cols // pf]),
+                                   (f"{name}_scales", rows * (cols // group) * 2, [rows, cols // group]),
+                                   (f"{name}_biases", rows * (cols // group) * 2, [rows, cols // group])):
+            comps[field] = {"offset": off, "size": size, "shape": shape}
+            off += size
+    return comps
+
+
+def pack_experts(sd, out_dir: str, bits: int = 4, group_size: int = 64, model_name: str = "") -> dict:
+    """Write ``layer_XX.bin`` (expert E starts at byte ``E * expert_size``) and ``layout.json`` for every layer with routed
+    experts; weights are affine group-quantised on the fly (quant/mlx_affine.py). Both the stacked
+    (``...experts.gate_up_proj`` [E, 2I, H]) and the per-expert (``...experts.E.{gate,up,down}_proj.weight``) checkpoint
+    layouts are understood (crates/pmetal/src/pack_experts.rs)."""
     import re
 
     import torch
 
-    from ..utils.safetensors_io import save_file
-    os.makedirs(os.path.join(out_dir, "experts"), exist_ok=True)
-    dense, experts = {}, {}
-    per = re.compile(r"^(?:model\.)?layers\.(\d+)\.(?:mlp|block_sparse_moe)\.experts\.(\d+)\.(\w+)\.weight$")
+    from ..quant.mlx_affine import quantize_affine
+    os.makedirs(out_dir, exist_ok=True)
+    per = re.compile(r"^(?:model\.)?layers\.(\d+)\.(?:mlp|block_sparse_moe)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj|w1|w2|w3)\.weight$")
     stacked = re.compile(r"^(?:model\.)?layers\.(\d+)\.(?:mlp|block_sparse_moe)\.experts\.(gate_up_proj|down_proj)$")
+    role = {"gate_proj": "gate", "w1": "gate", "up_proj": "up", "w3": "up", "down_proj": "down", "w2": "down"}
+    layers = {}
     for k, v in sd.items():
         m = per.match(k)
         if m:
-            experts.setdefault((int(m.group(1)), int(m.group(2))), {})[m.group(3)] = v
+            layers.setdefault(int(m.group(1)), {}).setdefault(int(m.group(2)), {})[role[m.group(3)]] = v
             continue
         m = stacked.match(k)
         if m:
+            ex = layers.setdefault(int(m.group(1)), {})
             for e in range(v.shape[0]):
-                experts.setdefault((int(m.group(1)), e), {})[m.group(2)] = v[e].contiguous()
-            continue
-        dense[k] = v
-    index = {"experts": {}, "dense": "dense.safetensors"}
-    for (layer, e), tensors in sorted(experts.items()):
-        name = f"experts/layer_{layer:03d}_expert_{e:03d}.safetensors"
-        save_file({n: t.contiguous() for n, t in tensors.items()}, os.path.join(out_dir, name))
-        index["experts"][f"{layer}.{e}"] = {"file": name, "bytes": sum(t.numel() * t.element_size() for t in tensors.values())}
-    save_file({k: v.contiguous() if isinstance(v, torch.Tensor) else v for k, v in dense.items()},
-              os.path.join(out_dir, "dense.safetensors"))
-    with open(os.path.join(out_dir, "expert_index.json"), "w", encoding="utf-8") as fh:
-        json.dump(index, fh, indent=1)
-    return index
+                if m.group(2) == "gate_up_proj":
+                    half = v.shape[1] // 2
+                    ex.setdefault(e, {})["gate"], ex[e]["up"] = v[e, :half], v[e, half:]
+                else:
+                    ex.setdefault(e, {})["down"] = v[e]
+    if not layers:
+        raise ValueError("no routed experts found in the checkpoint")
+    first = next(iter(next(iter(layers.values())).values()))
+    inter, hidden = first["gate"].shape
+    record = _expert_record(hidden, inter, group_size, bits)
+    expert_size = record["down_biases"]["offset"] + record["down_biases"]["size"]
+    num_experts = max(len(ex) for ex in layers.values())
+    for layer, ex in sorted(layers.items()):
+        with open(os.path.join(out_dir, f"layer_{layer:02d}.bin"), "wb") as fh:
+            for e in range(num_experts):
+                buf = bytearray(expert_size)
+                for name in ("gate", "up", "down"):
+                    w, sc, bi = quantize_affine(ex[e][name].float(), bits, group_size)
+                    for field, t in ((f"{name}_weight", w), (f"{name}_scales", sc.to(torch.bfloat16)),
+                                     (f"{name}_biases", bi.to(torch.bfloat16))):
+                        raw = t.contiguous().view(torch.uint8).numpy().tobytes()
+                        c = record[field]
+                        assert len(raw) == c["size"], (field, len(raw), c["size"])
+                        buf[c["offset"]:c["offset"] + c["size"]] = raw
+                fh.write(buf)
+    layout = {"model_name": model_name, "num_layers": len(layers), "num_experts": num_experts, "hidden_dim": hidden,
+              "intermediate_dim": inter, "group_size": group_size, "bits": "Four" if bits == 4 else "Two",
+              "expert_size": expert_size, "moe_layer_indices": sorted(layers), "record": record}
+    with open(os.path.join(out_dir, "layout.json"), "w", encoding="utf-8") as fh:
+        json.dump(layout, fh, indent=1)
+    return layout
+
+
+def read_packed_expert(pack_dir: str, layer: int, expert: int):
+    """One expert's {gate, up, down} matrices (fp32, dequantised) from a packed directory."""
+    import numpy as np
+    import torch
+
+    from ..quant.mlx_affine import dequantize_affine
+    with open(os.path.join(pack_dir, "layout.json"), "r", encoding="utf-8") as fh:
+        lay = json.load(fh)
+    bits = 4 if lay["bits"] == "Four" else 2
+    with open(os.path.join(pack_dir, f"layer_{layer:02d}.bin"), "rb") as fh:
+        fh.seek(expert * lay["expert_size"])
+        raw = fh.read(lay["expert_size"])
+    out = {}
+    for name in ("gate", "up", "down"):
+        parts = {}
+        for field, dt in (("weight", torch.int32), ("scales", torch.bfloat16), ("biases", torch.bfloat16)):
+            c = lay["record"][f"{name}_{field}"]
+            arr = np.frombuffer(raw, dtype=np.uint8, count=c["size"], offset=c["offset"]).copy()
+            parts[field] = torch.from_numpy(arr).view(dt).reshape(c["shape"])
+        out[name] = dequantize_affine(parts["weight"], parts["scales"], parts["biases"], bits, lay["group_size"])
+    return out
 
 
 @_command(_pack_args)
 def cmd_pack_experts(a) -> int:
     from ..models.loader import read_state_dict
-    idx = pack_experts(read_state_dict(a.model), a.output)
-    print(json.dumps({"output": a.output, "expert_files": len(idx["experts"])}))
+    lay = pack_experts(read_state_dict(a.model), a.output, a.bits, a.group_size, os.path.basename(os.path.normpath(a.model)))
+    print(json.dumps({"output": a.output, "layers": lay["num_layers"], "experts": lay["num_experts"],
+                      "expert_size": lay["expert_size"]}))
     return 0
 
 

@@ -92,7 +92,6 @@ def test_new_subcommands(tmp_path, capsys):
 
     from pmetal_b200.cli import commands
     from pmetal_b200.cli.main import main
-    from pmetal_b200.utils.safetensors_io import load_file
     # dashboard folds an event file
     ev = tmp_path / "events.jsonl"
     ev.write_text("\n".join(json.dumps(e) for e in [
@@ -102,15 +101,26 @@ def test_new_subcommands(tmp_path, capsys):
     assert main(["dashboard", str(ev), "--once"]) == 0
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert out == {"job": "j1", "state": "finished", "kind": "train", "step": 3, "loss": 1.5, "tokens_per_s": 10.0}
-    # pack-experts understands both expert layouts
-    sd = {"model.embed_tokens.weight": torch.randn(8, 4),
-          "model.layers.0.mlp.experts.gate_up_proj": torch.randn(3, 6, 4), "model.layers.0.mlp.experts.down_proj": torch.randn(3, 4, 3),
-          "model.layers.1.mlp.experts.0.gate_proj.weight": torch.randn(3, 4), "model.layers.1.mlp.experts.0.down_proj.weight": torch.randn(4, 3)}
-    idx = commands.pack_experts(sd, str(tmp_path / "packed"))
-    assert set(idx["experts"]) == {"0.0", "0.1", "0.2", "1.0"}
-    one = load_file(str(tmp_path / "packed" / idx["experts"]["0.2"]["file"]))
-    assert torch.equal(one["gate_up_proj"], sd["model.layers.0.mlp.experts.gate_up_proj"][2])
-    assert "model.embed_tokens.weight" in load_file(str(tmp_path / "packed" / "dense.safetensors"))
+    # pack-experts: per-layer binary files with fixed-size expert records, both checkpoint layouts
+    torch.manual_seed(0)
+    sd = {"model.embed_tokens.weight": torch.randn(8, 64),
+          "model.layers.0.mlp.experts.gate_up_proj": torch.randn(3, 256, 64), "model.layers.0.mlp.experts.down_proj": torch.randn(3, 64, 128)}
+    for e in range(3):
+        sd[f"model.layers.2.mlp.experts.{e}.gate_proj.weight"] = torch.randn(128, 64)
+        sd[f"model.layers.2.mlp.experts.{e}.up_proj.weight"] = torch.randn(128, 64)
+        sd[f"model.layers.2.mlp.experts.{e}.down_proj.weight"] = torch.randn(64, 128)
+    lay = commands.pack_experts(sd, str(tmp_path / "packed"), bits=4, group_size=64, model_name="toy")
+    assert lay["moe_layer_indices"] == [0, 2] and lay["num_experts"] == 3 and lay["bits"] == "Four"
+    rec = lay["record"]
+    assert rec["gate_weight"] == {"offset": 0, "size": 128 * 8 * 4, "shape": [128, 8]} and rec["gate_scales"]["shape"] == [128, 1]
+    assert lay["expert_size"] == rec["down_biases"]["offset"] + rec["down_biases"]["size"]
+    assert (tmp_path / "packed" / "layer_02.bin").stat().st_size == 3 * lay["expert_size"]
+    one = commands.read_packed_expert(str(tmp_path / "packed"), 0, 2)
+    ref = sd["model.layers.0.mlp.experts.gate_up_proj"][2, 128:]
+    assert one["up"].shape == (128, 64) and float((one["up"] - ref).norm() / ref.norm()) < 0.15
+    two = commands.read_packed_expert(str(tmp_path / "packed"), 2, 1)
+    ref = sd["model.layers.2.mlp.experts.1.down_proj.weight"]
+    assert float((two["down"] - ref).norm() / ref.norm()) < 0.15
     # offline search, native call overhead, delta-rule micro-benchmark, DFlash on a random target
     assert main(["search", "nothing-matches-this"]) == 0 and json.loads(capsys.readouterr().out)["results"] == []
     assert main(["bench-ffi", "--calls", "2000"]) == 0 and json.loads(capsys.readouterr().out)["ns_per_call"] > 0
