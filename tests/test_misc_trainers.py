@@ -119,3 +119,77 @@ def test_python_api_generate(tmp_path):
     text = m.generate("hello", max_tokens=4, temperature=0)
     assert isinstance(text, str)
     assert "".join(m.stream("hello", max_tokens=4, temperature=0)) == text
+
+
+def test_masked_diffusion_lm_training_and_sampling():
+    import math
+
+    import torch
+
+    from pmetal_b200.models.architectures.generic import GenericDecoderLM
+    from pmetal_b200.trainer.diffusion import (BidirectionalLM, DiffusionConfig, DiffusionSampler, DiffusionTrainer,
+                                               diffusion_loss, forward_process, noise_alpha)
+    assert noise_alpha("linear", 0.25) == 0.75 and abs(noise_alpha("cosine", 1.0)) < 1e-6 and noise_alpha("polynomial2", 0.5) == 0.25
+    g = torch.Generator().manual_seed(0)
+    x0 = torch.randint(0, 50, (4, 200))
+    xt, mask = forward_process(x0, 0.3, 63, g)
+    assert 0.2 < mask.float().mean() < 0.4 and (xt[mask] == 63).all() and torch.equal(xt[~mask], x0[~mask])
+    elig = torch.zeros_like(mask)
+    elig[:, 100:] = True
+    _, m2 = forward_process(x0, 0.9, 63, g, elig)
+    assert not m2[:, :100].any() and m2[:, 100:].float().mean() > 0.8
+    logits = torch.zeros(1, 3, 5)
+    logits[0, 1, 2] = 10.0
+    tg = torch.tensor([[0, 2, -100]])
+    mk = torch.tensor([[True, True, True]])
+    plain = diffusion_loss(logits, tg, mk, 0.5, use_elbo=False)
+    assert abs(float(plain) - (math.log(5) + 0.0002) / 2) < 1e-2          # position 0 uniform, position 1 certain, 2 ignored
+    assert abs(float(diffusion_loss(logits, tg, mk, 0.5, True)) - 2 * float(plain)) < 1e-5
+    assert float(diffusion_loss(logits, tg, torch.zeros_like(mk), 0.5)) == 0.0
+    torch.manual_seed(0)
+    lm = GenericDecoderLM.from_hf_config(dict(model_type="llama", vocab_size=64, hidden_size=64, intermediate_size=96,
+                                              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2)).init_weights(0.05, 0)
+    model = BidirectionalLM(lm)
+    ids = torch.randint(0, 60, (1, 12))
+    a = model(ids)
+    ids2 = ids.clone()
+    ids2[0, -1] = (ids2[0, -1] + 1) % 60
+    assert not torch.allclose(a[0, 0], model(ids2)[0, 0])                 # position 0 sees the last token: no causal mask
+    assert torch.allclose(lm(ids)[0, 0], lm(ids2)[0, 0])                   # and the wrapper leaves the causal model intact
+    cfg = DiffusionConfig(mask_token_id=63, num_inference_steps=6, use_elbo_loss=False)
+    tr = DiffusionTrainer(model, cfg, lr=3e-3)
+    data = torch.arange(16)[None].repeat(8, 1) % 60                         # one memorisable pattern
+    losses = [tr.train_step(data)["loss"] for _ in range(60)]
+    assert sum(losses[-5:]) / 5 < 0.6 * sum(losses[:5]) / 5
+    ev = tr.evaluate([data])
+    assert ev["perplexity"] < 30
+    for strategy in ("low_confidence", "random", "semi_autoregressive"):
+        cfg.remasking, cfg.block_size = strategy, 2
+        out = DiffusionSampler(cfg).sample(model, list(range(6)), 8)
+        assert len(out) == 8 and all(0 <= t < 64 for t in out) and 63 not in out
+    cfg.remasking = "low_confidence"
+    out = DiffusionSampler(cfg).sample(model, list(range(6)), 8)
+    assert sum(int(t == 6 + i) for i, t in enumerate(out)) >= 4              # it continues the memorised pattern
+
+
+def test_dflash_draft_training_step_learns():
+    import torch
+
+    from pmetal_b200.models.architectures.generic import GenericDecoderLM
+    from pmetal_b200.models.dflash import DFlashConfig, DFlashDraftModel
+    from pmetal_b200.trainer.diffusion import DFlashDraftTrainer, dflash_train_step
+    torch.manual_seed(0)
+    target = GenericDecoderLM.from_hf_config(dict(model_type="qwen3", vocab_size=64, hidden_size=64, intermediate_size=96,
+                                                  num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                                                  head_dim=16)).init_weights(0.05, 1).eval()
+    dc = DFlashConfig.from_dict(dict(hidden_size=64, num_hidden_layers=1, intermediate_size=96, num_attention_heads=4,
+                                     num_key_value_heads=2, head_dim=16, vocab_size=64, block_size=4,
+                                     dflash_config=dict(target_layer_ids=[0, 2], mask_token_id=63)))
+    draft = DFlashDraftModel(dc)
+    toks = (torch.arange(24)[None] * 3) % 60
+    out = dflash_train_step(target, draft, toks, 10)
+    assert out["block"] == (10, 4) and out["loss"].requires_grad and 3.0 < float(out["loss"].detach()) < 6.0
+    assert all(p.grad is None for p in target.parameters())
+    tr = DFlashDraftTrainer(target, draft, lr=3e-3)
+    losses = [tr.train_step(toks)["loss"] for _ in range(120)]
+    assert sum(losses[-10:]) < 0.8 * sum(losses[:10])
