@@ -77,6 +77,35 @@ class ProgressCallback(TrainingCallback):
         self.stream.write("\n")
 
 
+class TensorBoardCallback(TrainingCallback):
+    """Scalars per step (loss, learning rate, tokens/s, gradient norm) and per evaluation into a TensorBoard event
+    directory (crates/pmetal-trainer/src/callbacks.rs, the ``tensorboard`` feature). Needs the ``tensorboard`` package;
+    construction raises ImportError without it."""
+
+    def __init__(self, log_dir: str):
+        from torch.utils.tensorboard import SummaryWriter
+        self.writer = SummaryWriter(log_dir)
+
+    def on_step_end_with_metrics(self, m: StepMetrics) -> None:
+        w = self.writer
+        w.add_scalar("train/loss", m.loss, m.step)
+        w.add_scalar("train/lr", m.lr, m.step)
+        w.add_scalar("train/tokens_per_sec", m.tok_sec, m.step)
+        if m.grad_norm is not None:
+            w.add_scalar("train/grad_norm", m.grad_norm, m.step)
+
+    def on_eval(self, metrics) -> None:
+        step = getattr(metrics, "step", 0)
+        for k in ("loss", "perplexity", "accuracy"):
+            v = getattr(metrics, k, None) if not isinstance(metrics, dict) else metrics.get(k)
+            if v is not None:
+                self.writer.add_scalar(f"eval/{k}", float(v), step)
+
+    def on_train_end(self) -> None:
+        self.writer.flush()
+        self.writer.close()
+
+
 class MetricsJsonCallback(TrainingCallback):
     """JSON-lines metrics file with the reference's keys and flush cadence
     (callbacks.rs:217-316: every step for the first 20, then every fifth)."""

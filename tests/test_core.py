@@ -57,3 +57,19 @@ def test_job_events(tmp_path):
     st = JobStatus.fold(lines)
     assert st.state == "completed" and st.phase == "training" and st.last_metric["loss"] == 2.0
     assert JobStatus.fold([JobEvent.started("j", "train"), JobEvent.failed("j", "boom")]).error == "boom"
+
+
+def test_tensorboard_callback_writes_event_file(tmp_path):
+    import os
+
+    import pytest
+    pytest.importorskip("tensorboard")
+    from pmetal_b200.core.callbacks import StepMetrics, TensorBoardCallback
+    cb = TensorBoardCallback(str(tmp_path / "tb"))
+    for i in range(3):
+        cb.on_step_end_with_metrics(StepMetrics(step=i + 1, total_steps=3, loss=2.0 - i * 0.1, lr=1e-4, tok_sec=100.0, grad_norm=0.5))
+    cb.on_eval({"loss": 1.5, "perplexity": 4.48})
+    cb.on_train_end()
+    files = os.listdir(tmp_path / "tb")
+    assert any(f.startswith("events.out.tfevents") for f in files)
+    assert os.path.getsize(os.path.join(tmp_path / "tb", files[0])) > 100
