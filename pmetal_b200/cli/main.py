@@ -37,6 +37,7 @@ def _add_train(sp):
     p.add_argument("--gradient-accumulation-steps", type=int, default=4)
     p.add_argument("--max-grad-norm", type=float, default=1.0)
     p.add_argument("--resume", action="store_true")
+    p.add_argument("--tensorboard", help="write TensorBoard scalars to this directory")
     p.add_argument("--resume-bundle", help="continue from a run bundle (parallel/cloud_bridge.py: model + optimiser + RNG)")
     p.add_argument("--quantization", default="none", choices=["none", "nf4", "fp4", "int8"])
     p.add_argument("--quant-block-size", type=int, default=64)
@@ -115,6 +116,7 @@ def cmd_train(a) -> int:
     job.gradient_checkpointing_layers = 0 if a.no_gradient_checkpointing else a.gradient_checkpointing_layers
     job.log_metrics, job.resume, job.adaptive_lr = a.log_metrics, a.resume, not a.no_adaptive_lr
     job.resume_bundle = a.resume_bundle
+    job.tensorboard_dir = a.tensorboard
     job.max_samples, job.device, job.dtype, job.dp_impl = a.max_samples, a.device, a.dtype, a.dp_impl
     job.distributed = bool(a.distributed_peers or a.distributed_auto)
     if a.text_column or a.text_columns or a.prompt_column:

@@ -44,6 +44,7 @@ class TrainingJobConfig:
     use_cuda_graph: bool = True
     gradient_checkpointing_layers: int = 0
     log_metrics: Optional[str] = None
+    tensorboard_dir: Optional[str] = None
     resume: bool = False
     resume_bundle: Optional[str] = None
     adaptive_lr: bool = True
@@ -140,6 +141,9 @@ def run_training(job: TrainingJobConfig, phase_cb: Optional[Callable[[str], None
             model.gradient_checkpointing = job.gradient_checkpointing_layers
         model.prepare_for_training()
         cbs = list(callbacks or []) + [LoggingCallback(tcfg.logging_steps)]
+        if getattr(job, "tensorboard_dir", None) and rank == 0:
+            from ..core.callbacks import TensorBoardCallback
+            cbs.append(TensorBoardCallback(job.tensorboard_dir))
         if job.log_metrics and rank == 0:
             cbs.append(MetricsJsonCallback(job.log_metrics, config={"lora": dataclasses.asdict(job.lora),
                                                                     "training": dataclasses.asdict(tcfg)}))
