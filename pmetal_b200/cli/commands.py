@@ -599,18 +599,52 @@ def cmd_cluster(a) -> int:
 
 
 def _dl_args(sp):
-    p = sp.add_parser("download", help="resolve a model from the local Hugging Face cache (this machine is offline)")
+    p = sp.add_parser("download", help="resolve a model from the local Hugging Face cache, or fetch it from the hub")
     p.add_argument("model")
+    p.add_argument("--revision", default="main")
+    p.add_argument("--token", default=os.environ.get("HF_TOKEN"))
+    p.add_argument("--offline", action="store_true", help="never contact the hub")
     return p
 
 
 @_command(_dl_args)
 def cmd_download(a) -> int:
-    from ..models.loader import resolve_model_path
+    from ..models.loader import is_hf_id, resolve_model_path
     try:
         print(resolve_model_path(a.model))
         return 0
     except FileNotFoundError as e:
+        if a.offline or not is_hf_id(a.model):
+            print(f"error: {e}", file=sys.stderr)
+            return 1
+    from .. import hub
+    try:
+        print(hub.download_model(a.model, a.revision, a.token))
+        return 0
+    except hub.HubError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
+
+
+def _upload_args(sp):
+    p = sp.add_parser("upload", help="upload a model directory to the Hugging Face Hub")
+    p.add_argument("path")
+    p.add_argument("repo", help="owner/name")
+    p.add_argument("--token", default=os.environ.get("HF_TOKEN"))
+    p.add_argument("--private", action="store_true")
+    return p
+
+
+@_command(_upload_args)
+def cmd_upload(a) -> int:
+    from .. import hub
+    if not a.token:
+        print("error: a token is required (--token or HF_TOKEN)", file=sys.stderr)
+        return 2
+    try:
+        print(json.dumps(hub.upload_model(a.path, a.repo, a.token, a.private)))
+        return 0
+    except (hub.HubError, ValueError) as e:
         print(f"error: {e}", file=sys.stderr)
         return 1
 
@@ -759,9 +793,11 @@ def cmd_rlkd(a) -> int:
 
 # ------------------------------------------------------------------------------------------- search (offline)
 def _search_args(sp):
-    p = sp.add_parser("search", help="search models in the local Hugging Face cache (this machine is offline)")
+    p = sp.add_parser("search", help="search models in the local Hugging Face cache, or on the hub with --online")
     p.add_argument("query", nargs="?", default="")
     p.add_argument("--limit", type=int, default=20)
+    p.add_argument("--online", action="store_true")
+    p.add_argument("--tag")
     return p
 
 
@@ -792,6 +828,17 @@ def local_model_index():
 @_command(_search_args)
 def cmd_search(a) -> int:
     from ..utils.sysinfo import estimate_fit
+    if getattr(a, "online", False):
+        from .. import hub
+        try:
+            res = hub.search_models(a.query, a.limit, a.tag, os.environ.get("HF_TOKEN"))
+        except hub.HubError as e:
+            print(f"error: {e}", file=sys.stderr)
+            return 1
+        print(json.dumps({"query": a.query, "source": hub.endpoint(), "results": [
+            {"id": r.id, "downloads": hub.format_downloads(r.downloads), "likes": r.likes, "pipeline_tag": r.pipeline_tag}
+            for r in res]}, indent=2))
+        return 0
     q = a.query.lower()
     rows = []
     for repo, snap, size in local_model_index():
