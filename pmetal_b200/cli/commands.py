@@ -863,6 +863,7 @@ def _dflash_args(sp):
     p.add_argument("--prompt", default="Hello")
     p.add_argument("--max-tokens", type=int, default=64)
     p.add_argument("--block-size", type=int, default=0)
+    p.add_argument("--tree-budget", type=int, default=0, help="> 0: tree verification with this many candidate nodes")
     p.add_argument("--device")
     return p
 
@@ -905,7 +906,10 @@ def cmd_dflash(a) -> int:
     prompt = tok.encode(a.prompt) if tok is not None else [min(ord(ch), c.vocab_size - 2) for ch in a.prompt]
     dec = DFlashDecoder(target, draft)
     t0 = time.time()
-    out = dec.generate(prompt, a.max_tokens, a.block_size or None)
+    if a.tree_budget > 0:
+        out = dec.generate_tree(prompt, a.max_tokens, a.tree_budget, a.block_size or None)
+    else:
+        out = dec.generate(prompt, a.max_tokens, a.block_size or None)
     dt = time.time() - t0
     dec.close()
     print(json.dumps({"tokens": out, "text": tok.decode(out) if tok is not None else None,

@@ -509,7 +509,8 @@ class Attention(nn.Module):
             q = (q * t[:, None, :, None]).to(q.dtype)
         if cache is not None:
             k, v = cache.append(self.idx, k, v)
-        mask = build_mask(self.kind, positions, k_positions, c.sliding_window, c.chunk_size)
+        mask = rope["mask"] if rope.get("mask") is not None else \
+            build_mask(self.kind, positions, k_positions, c.sliding_window, c.chunk_size)
         scale = (c.attn_scale or d ** -0.5) * rope.get("attention_factor", 1.0) ** 2
         o = attend(q, k, v, mask, scale, c.attn_softcap, self.sinks if c.sinks else None)
         o = o.transpose(1, 2).reshape(B, T, c.n_heads * d)
@@ -627,7 +628,7 @@ class LatentAttention(nn.Module):
         v = kv[..., nd:]
         if cache is not None:
             k, v = cache.append(self.idx, k, v)
-        mask = build_mask("full", positions, k_positions, 0, 0)
+        mask = rope["mask"] if rope.get("mask") is not None else build_mask("full", positions, k_positions, 0, 0)
         scale = (nd + rd) ** -0.5 * rope.get("attention_factor", 1.0) ** 2
         o = attend(q, k, v, mask, scale)
         return self.o_proj(o.transpose(1, 2).reshape(B, T, h * vd))
@@ -895,7 +896,9 @@ class GenericDecoderLM(nn.Module):
         return 1.0
 
     def forward_hidden(self, input_ids: torch.Tensor, cache: Optional[KVCache] = None,
-                       positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       positions: Optional[torch.Tensor] = None, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``attn_mask`` (bool [B, 1, Tq, Tk], True = attend) replaces the position-derived causal mask in every layer
+        (tree-structured verification); full-attention models only."""
         c = self.c
         if input_ids.dim() == 1:
             input_ids = input_ids[None]
@@ -909,6 +912,7 @@ class GenericDecoderLM(nn.Module):
         if c.embed_scale != 1.0:
             x = x * torch.tensor(c.embed_scale, dtype=x.dtype)
         rope = self._rope(positions)
+        rope["mask"] = attn_mask
         for layer in self.model.layers:
             x = layer(x, rope, positions, cache, k_positions)
         return getattr(self.model, c.final_norm_name)(x)
@@ -924,8 +928,8 @@ class GenericDecoderLM(nn.Module):
             z = torch.tanh(z / c.final_softcap) * c.final_softcap
         return z
 
-    def forward(self, input_ids, cache: Optional[KVCache] = None, positions=None) -> torch.Tensor:
-        return self.logits(self.forward_hidden(input_ids, cache, positions))
+    def forward(self, input_ids, cache: Optional[KVCache] = None, positions=None, attn_mask=None) -> torch.Tensor:
+        return self.logits(self.forward_hidden(input_ids, cache, positions, attn_mask))
 
     def new_cache(self) -> KVCache:
         return KVCache(self.c.num_layers)

@@ -123,6 +123,74 @@ class DFlashDraftModel(nn.Module):
         return self.load_state_dict(sd, strict=strict)
 
 
+# ------------------------------------------------------------------------------------------------ draft tree
+@dataclass
+class DraftTree:
+    """Budget-bounded tree of candidate continuations below the seed token (node 0 = root). ``tokens[i]`` / ``depths[i]``
+    / ``parents[i]`` describe node i + 1; ``children[i]`` maps token id -> node index for node i."""
+    tokens: List[int]
+    depths: List[int]
+    parents: List[int]
+    children: List[Dict[int, int]]
+
+    def visibility(self) -> torch.Tensor:
+        """[N + 1, N + 1] bool: row i sees column j iff j is i or an ancestor of i."""
+        n = len(self.tokens) + 1
+        vis = torch.zeros(n, n, dtype=torch.bool)
+        vis[0, 0] = True
+        for i in range(1, n):
+            vis[i] = vis[self.parents[i]]
+            vis[i, i] = True
+        return vis
+
+
+def build_tree(draft_logits: torch.Tensor, budget: int) -> DraftTree:
+    """Best-first expansion over the per-depth draft distributions ([horizon, vocab]): the state with the highest
+    cumulative log-probability is materialised next; it spawns its sibling (next rank at the same depth, same parent)
+    and its first child (rank 0 at the next depth). Ties pop in insertion order, so the tree is deterministic
+    (crates/pmetal-models/src/ddtree.rs:164-280)."""
+    import heapq
+    tree = DraftTree([], [], [-1], [{}])
+    horizon = draft_logits.shape[0]
+    if budget <= 0 or horizon == 0:
+        return tree
+    k = max(1, min(budget, draft_logits.shape[1]))
+    logp, ids = torch.log_softmax(draft_logits.float(), -1).topk(k, -1)
+    logp, ids = logp.tolist(), ids.tolist()
+    heap = [(-logp[0][0], 0, 1, 0, 0, logp[0][0])]          # (-logw, order, depth, rank, parent, logw)
+    order = 1
+    while heap and len(tree.tokens) < budget:
+        _, _, depth, rank, parent, logw = heapq.heappop(heap)
+        tok = ids[depth - 1][rank]
+        index = len(tree.tokens) + 1
+        tree.tokens.append(tok)
+        tree.depths.append(depth)
+        tree.parents.append(parent)
+        tree.children.append({})
+        tree.children[parent][tok] = index
+        if rank + 1 < k:
+            w = logw - logp[depth - 1][rank] + logp[depth - 1][rank + 1]
+            heapq.heappush(heap, (-w, order, depth, rank + 1, parent, w))
+            order += 1
+        if depth < horizon:
+            w = logw + logp[depth][0]
+            heapq.heappush(heap, (-w, order, depth + 1, 0, index, w))
+            order += 1
+    return tree
+
+
+def follow_verified_tree(tree: DraftTree, verifier_tokens: Sequence[int]) -> List[int]:
+    """Walk from the root following the target's argmax at every visited node (``verifier_tokens[i]`` = argmax at node
+    i). Returns the visited node indices, root first; the bonus token is the argmax at the last one."""
+    path, node = [0], 0
+    while True:
+        nxt = tree.children[node].get(int(verifier_tokens[node]))
+        if nxt is None:
+            return path
+        path.append(nxt)
+        node = nxt
+
+
 @dataclass
 class DFlashStats:
     acceptance_lengths: List[int] = field(default_factory=list)
@@ -167,6 +235,55 @@ class DFlashDecoder:
         for i in range(len(cache.k)):
             if cache.k[i] is not None:
                 cache.k[i], cache.v[i] = cache.k[i][:, :, :-n], cache.v[i][:, :, :-n]
+
+    @torch.no_grad()
+    def generate_tree(self, prompt: Sequence[int], max_new_tokens: int, tree_budget: int = 12,
+                      block_size: Optional[int] = None, stop_tokens: Sequence[int] = ()) -> List[int]:
+        """Tree verification: the draft's per-position distributions become a tree of ``tree_budget`` candidates, the
+        target scores all nodes in one forward pass under a tree attention mask (a node sees the context and its
+        ancestors; its position is context length + depth), and the walk along the target's own argmax accepts a path
+        through the tree. Keys / values of rejected nodes are dropped from the cache
+        (crates/pmetal-models/src/dflash_decoder.rs:537-790). Greedy output equals plain greedy decoding."""
+        c = self.draft.c
+        bs = max(2, min(block_size or c.block_size, c.block_size))
+        if tree_budget <= 0:
+            return self.generate(prompt, max_new_tokens, block_size, stop_tokens)
+        dev = self.target.model.embed_tokens.weight.device
+        cache = self.target.new_cache()
+        logits, hidden = self._forward(torch.tensor([list(prompt)], device=dev), cache)
+        out = [int(logits[0, -1].argmax())]
+        while len(out) < max_new_tokens and out[-1] not in stop_tokens:
+            block = [out[-1]] + [c.mask_token_id] * (bs - 1)
+            noise = self.target.model.embed_tokens(torch.tensor([block], device=dev))
+            if self.target.c.embed_scale != 1.0:
+                noise = noise * self.target.c.embed_scale
+            dlogits = self.target.logits(self.draft(noise, hidden)[:, 1:])[0]
+            tree = build_tree(dlogits, tree_budget)
+            n = len(tree.tokens) + 1
+            past = cache.length()
+            ids = torch.tensor([[out[-1]] + tree.tokens], device=dev)
+            pos = torch.tensor([[past] + [past + d for d in tree.depths]], device=dev)
+            mask = torch.ones(1, 1, n, past + n, dtype=torch.bool, device=dev)
+            mask[0, 0, :, past:] = tree.visibility().to(dev)
+            self._taps.clear()
+            vlogits = self.target(ids, cache, positions=pos, attn_mask=mask)
+            vhidden = torch.cat([self._taps[i] for i in c.target_layer_ids], -1)
+            verifier = vlogits[0].argmax(-1).tolist()
+            path = follow_verified_tree(tree, verifier)
+            keep = torch.tensor(list(range(past)) + [past + i for i in path], device=dev)
+            for li in range(len(cache.k)):
+                if cache.k[li] is not None:
+                    cache.k[li], cache.v[li] = cache.k[li].index_select(2, keep), cache.v[li].index_select(2, keep)
+            self.stats.acceptance_lengths.append(len(path))
+            self.stats.total_drafted += len(tree.tokens)
+            self.stats.total_accepted += len(path) - 1
+            new = [tree.tokens[i - 1] for i in path[1:]] + [verifier[path[-1]]]
+            for t in new:
+                out.append(t)
+                if t in stop_tokens or len(out) >= max_new_tokens:
+                    break
+            hidden = vhidden[:, torch.tensor(path, device=dev)]
+        return out[:max_new_tokens]
 
     @torch.no_grad()
     def generate(self, prompt: Sequence[int], max_new_tokens: int, block_size: Optional[int] = None,

@@ -370,3 +370,30 @@ def test_flux_transformer_and_autoencoder():
         rec = vae.decode(lat)
     assert lat.shape == (2, 4, 8, 8) and rec.shape == img.shape
     assert vae.encoder.conv_out.out_channels == 8                                 # mean and log-variance
+
+
+def test_dflash_tree_verification():
+    from pmetal_b200.models.dflash import (DFlashConfig, DFlashDecoder, DFlashDraftModel, build_tree, follow_verified_tree)
+    # hand-checked tree: depth-1 candidates a (p .6), b (.3); depth-2 candidates c (.9), d (.1)
+    lg = torch.log(torch.tensor([[0.6, 0.3, 0.05, 0.05], [0.02, 0.04, 0.9, 0.04]]))
+    t = build_tree(lg, 4)
+    # pop order: a (.6); then its child c under a (.54) beats sibling b (.3); then b; then c under b (.27) beats d under a (.024)
+    assert t.tokens == [0, 2, 1, 2] and t.depths == [1, 2, 1, 2] and t.parents == [-1, 0, 1, 0, 3]
+    assert t.children[0] == {0: 1, 1: 3} and t.children[1] == {2: 2} and t.children[3] == {2: 4}
+    vis = t.visibility()
+    assert vis[2].tolist() == [True, True, True, False, False] and vis[4].tolist() == [True, False, False, True, True]
+    assert follow_verified_tree(t, [1, 9, 9, 2, 7]) == [0, 3, 4] and follow_verified_tree(t, [3, 0, 0, 0, 0]) == [0]
+    assert build_tree(lg, 0).tokens == []
+    torch.manual_seed(0)
+    target = GenericDecoderLM.from_hf_config(dict(BASE, model_type="qwen3", head_dim=16)).init_weights(0.05, 1).eval()
+    dc = DFlashConfig.from_dict(dict(hidden_size=64, num_hidden_layers=2, intermediate_size=96, num_attention_heads=4,
+                                     num_key_value_heads=2, head_dim=16, vocab_size=128, block_size=5,
+                                     dflash_config=dict(target_layer_ids=[1, 3], mask_token_id=127)))
+    draft = DFlashDraftModel(dc).eval()
+    prompt = torch.randint(0, 120, (9,)).tolist()
+    greedy = target.generate(prompt, max_new_tokens=20)
+    dec = DFlashDecoder(target, draft)
+    out = dec.generate_tree(prompt, 20, tree_budget=8)
+    dec.close()
+    assert out == greedy
+    assert all(1 <= a <= 5 for a in dec.stats.acceptance_lengths) and dec.stats.total_drafted > 0
