@@ -17,12 +17,15 @@ GENERIC_DECODER = {"mixtral", "gemma", "gemma2", "gemma3", "gemma3_text", "phi",
                    "qwen3.5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text"}
 OTHER = {"nemotron_h": "nemotron_h", "nemotronh": "nemotron_h", "nemotron-h": "nemotron_h", "bert": "bert", "roberta": "bert",
          "distilbert": "bert", "xlm-roberta": "bert", "xlm_roberta": "bert", "t5": "t5", "clip": "clip", "whisper": "whisper",
-         "flux": "flux", "flux-1": "flux", "flux.1": "flux", "pixtral": "pixtral", "qwen2_vl": "qwen2_vl", "mllama": "mllama"}
+         "flux": "flux", "flux-1": "flux", "flux.1": "flux", "pixtral": "pixtral", "qwen2_vl": "qwen2_vl", "mllama": "mllama",
+         "gemma4": "gemma4", "gemma4_text": "gemma4"}
 
 
 def family_of(config: dict) -> Optional[str]:
     """``fast`` | ``generic`` | one of the names in ``OTHER`` | None for an unknown architecture."""
     mt = str(config.get("model_type", "")).lower()
+    if mt in ("gemma4", "gemma4_text"):
+        return "gemma4"
     if "text_config" in config and mt not in OTHER:
         mt = str(config["text_config"].get("model_type", mt)).lower()
     if mt in FAST_DECODER:
@@ -35,7 +38,7 @@ def family_of(config: dict) -> Optional[str]:
         a = arch.lower()
         for key, fam in (("llama4", "generic"), ("llama", "fast"), ("qwen3moe", "fast"), ("qwen3next", "generic"),
                          ("qwen3", "fast"), ("qwen2", "fast"), ("mistral", "fast"), ("mixtral", "generic"),
-                         ("gemma", "generic"), ("phi", "generic"), ("cohere", "generic"), ("granite", "generic"),
+                         ("gemma4", "gemma4"), ("gemma", "generic"), ("phi", "generic"), ("cohere", "generic"), ("granite", "generic"),
                          ("deepseek", "generic"), ("gptoss", "generic"), ("nemotronh", "nemotron_h"), ("bert", "bert"),
                          ("t5", "t5"), ("clip", "clip"), ("whisper", "whisper")):
             if key in a:
@@ -56,6 +59,9 @@ def build_model(config: dict, dtype=None, device=None):
     if fam == "generic":
         from .generic import GenericDecoderLM
         m = GenericDecoderLM.from_hf_config(config)
+    elif fam == "gemma4":
+        from .gemma4 import Gemma4LM
+        m = Gemma4LM.from_hf_config(config)
     elif fam == "nemotron_h":
         from .hybrid import NemotronHLM
         m = NemotronHLM(config)

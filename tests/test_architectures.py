@@ -397,3 +397,54 @@ def test_dflash_tree_verification():
     dec.close()
     assert out == greedy
     assert all(1 <= a <= 5 for a in dec.stats.acceptance_lengths) and dec.stats.total_drafted > 0
+
+
+# ---------------------------------------------------------------------------------------------- Gemma 4
+GEMMA4 = {
+    "dense": dict(),
+    "k_eq_v": dict(attention_k_eq_v=True, num_global_key_value_heads=1),
+    "shared_kv_wide": dict(num_kv_shared_layers=2, use_double_wide_mlp=True),
+    "experts": dict(enable_moe_block=True, num_experts=4, top_k_experts=2, moe_intermediate_size=32,
+                    hidden_size_per_layer_input=0),
+}
+
+
+def _gemma4_pair(name):
+    from pmetal_b200.models.architectures.gemma4 import Gemma4LM
+    kw = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=6, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=8, max_position_embeddings=256,
+              vocab_size_per_layer_input=128, hidden_size_per_layer_input=8, final_logit_softcapping=30.0,
+              layer_types=["sliding_attention", "sliding_attention", "full_attention"] * 2)
+    kw.update(GEMMA4[name])
+    torch.manual_seed(0)
+    cfg = tf.Gemma4TextConfig(**kw, attn_implementation="eager")
+    hf = tf.Gemma4ForCausalLM(cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() < 2:
+                p.add_(torch.randn_like(p) * 0.1)
+        for n, b in hf.named_buffers():
+            if n.endswith("layer_scalar"):
+                b.copy_(1.0 + 0.2 * torch.randn_like(b))
+    ours = Gemma4LM.from_hf_config(cfg.to_dict()).eval()
+    missing, unexpected = ours.load_hf_state_dict(hf.state_dict(), strict=False)
+    assert not [m for m in missing if "inv_" not in m] and not [u for u in unexpected if "inv_freq" not in u], (missing, unexpected)
+    return hf, ours
+
+
+@pytest.mark.parametrize("name", sorted(GEMMA4))
+def test_gemma4_matches_hugging_face_and_cache(name):
+    from pmetal_b200.models.architectures import build_model, family_of
+    hf, ours = _gemma4_pair(name)
+    ids = torch.randint(0, 128, (2, 24), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(input_ids=ids, use_cache=True).logits.float()
+        got = ours(ids).float()
+        assert torch.allclose(got, ref, atol=2e-4, rtol=2e-3), float((got - ref).abs().max())
+        cache = ours.new_cache()
+        inc = torch.cat([ours(ids[:1, :13], cache)] + [ours(ids[:1, t:t + 1], cache) for t in range(13, 24)], 1)
+    assert torch.allclose(inc, got[:1], atol=2e-4, rtol=2e-3), float((inc - got[:1]).abs().max())
+    assert len(ours.generate(ids[0, :5].tolist(), max_new_tokens=3)) == 3
+    d = hf.config.to_dict()
+    assert family_of(d) == "gemma4" and family_of({"model_type": "gemma4", "text_config": d}) == "gemma4"
+    assert type(build_model({"model_type": "gemma4", "text_config": d})).__name__ == "Gemma4LM"
