@@ -254,7 +254,8 @@ class _LlavaProjector(nn.Module):
 
 
 def build_vision_language(config: dict) -> VisionLanguageModel:
-    """Pixtral / Llava-style (``vision_config`` + ``text_config`` + MLP projector) and Qwen2-VL (tower with merger)."""
+    """Pixtral / Llava-style (``vision_config`` + ``text_config`` + MLP projector), Qwen2-VL (tower with merger) and
+    mllama (tiled tower + cross-attention decoder, its own class)."""
     from .generic import GenericDecoderLM
     mt = config.get("model_type", "")
     text = config.get("text_config") or {k: v for k, v in config.items() if k != "vision_config"}
@@ -263,7 +264,8 @@ def build_vision_language(config: dict) -> VisionLanguageModel:
         tower = Qwen2VLVision(config["vision_config"])
         return VisionLanguageModel(GenericDecoderLM.from_hf_config(text), tower, None, config.get("image_token_id", 151655))
     if mt == "mllama":
-        raise NotImplementedError("mllama's tiled vision encoder and cross-attention layers are not implemented")
+        from .mllama import MllamaForConditionalGeneration
+        return MllamaForConditionalGeneration(config)
     vis = config["vision_config"]
     tower = PixtralVision(vis)
     proj = _LlavaProjector(vis["hidden_size"], text["hidden_size"], config.get("projector_hidden_act", "gelu"),

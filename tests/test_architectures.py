@@ -448,3 +448,55 @@ def test_gemma4_matches_hugging_face_and_cache(name):
     d = hf.config.to_dict()
     assert family_of(d) == "gemma4" and family_of({"model_type": "gemma4", "text_config": d}) == "gemma4"
     assert type(build_model({"model_type": "gemma4", "text_config": d})).__name__ == "Gemma4LM"
+
+
+# ---------------------------------------------------------------------------------------------- mllama
+def test_mllama_matches_hugging_face_and_decodes_with_cached_image_keys():
+    from pmetal_b200.models.architectures import build_model
+    torch.manual_seed(0)
+    vis = dict(hidden_size=32, attention_heads=4, intermediate_size=64, num_hidden_layers=4, num_global_layers=2,
+               intermediate_layers_indices=[1, 3], image_size=28, patch_size=14, max_num_tiles=4, vision_output_dim=96,
+               supported_aspect_ratios=[[1, 1], [1, 2], [2, 1], [2, 2]], num_channels=3)
+    txt = dict(vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=5, num_attention_heads=4,
+               num_key_value_heads=2, cross_attention_layers=[1, 3], max_position_embeddings=256, pad_token_id=0,
+               rope_parameters=dict(rope_type="llama3", rope_theta=10000.0, factor=8.0, low_freq_factor=1.0,
+                                    high_freq_factor=4.0, original_max_position_embeddings=32))
+    cfg = tf.MllamaConfig(vision_config=vis, text_config=txt, attn_implementation="eager")
+    hf = tf.MllamaForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() < 2:
+                p.add_(torch.randn_like(p) * 0.3)          # opens the tanh gates, moves the norm weights
+    ours = build_model(cfg.to_dict()).eval()
+    assert type(ours).__name__ == "MllamaForConditionalGeneration"
+    _load(ours, hf, allow_unexpected=("inv_freq",))
+
+    g = torch.Generator().manual_seed(1)
+    B, T = 2, 12
+    ids = torch.randint(0, 128, (B, T), generator=g)
+    pix = torch.randn(B, 1, 4, 3, 28, 28, generator=g)
+    ar_ids = torch.tensor([[4], [2]])
+    ar_mask = torch.tensor([[[1, 1, 1, 1]], [[1, 1, 0, 0]]])
+    cam = torch.zeros(B, T, 1, 4)
+    cam[0, 3:, 0, :] = 1                                         # tokens after the image token see its tiles
+    cam[1, 5:, 0, :2] = 1
+    with torch.no_grad():
+        ref = hf(input_ids=ids, pixel_values=pix, aspect_ratio_ids=ar_ids, aspect_ratio_mask=ar_mask,
+                 cross_attention_mask=cam).logits.float()
+        vref = hf.model.vision_model(pix, ar_ids, ar_mask).last_hidden_state
+        vgot = ours.model.vision_model(pix, ar_ids, ar_mask)
+        assert torch.allclose(vgot, vref, atol=2e-4, rtol=2e-3), float((vgot - vref).abs().max())
+        got = ours(ids, pix, ar_ids, ar_mask, cam).float()
+        assert torch.allclose(got, ref, atol=3e-4, rtol=2e-3), float((got - ref).abs().max())
+        # incremental: image keys computed once with the prompt, then reused from the cache
+        cache = ours.new_cache()
+        a = ours(ids[:, :8], pix, ar_ids, ar_mask, cam[:, :8], cache)
+        rest = [ours(ids[:, t:t + 1], cross_attention_mask=cam[:, :t + 1], cache=cache) for t in range(8, T)]
+        inc = torch.cat([a] + rest, 1)
+        assert torch.allclose(inc, got, atol=3e-4, rtol=2e-3), float((inc - got).abs().max())
+        # text-only use skips the cross-attention layers, as the checkpoint's own code does
+        t_ref = hf(input_ids=ids).logits
+        assert torch.allclose(ours(ids), t_ref, atol=3e-4, rtol=2e-3)
+    out = ours.generate(ids[0, :6].tolist(), 3, pixel_values=pix[:1], aspect_ratio_ids=ar_ids[:1],
+                        aspect_ratio_mask=ar_mask[:1], cross_attention_mask=cam[:1, :6])
+    assert len(out) == 3
