@@ -1,43 +1,29 @@
-"""ctypes binding of the host C++ block codecs (``csrc/host/gguf_quant.cpp``).
-
-The library is built on first use when it is missing or older than its source (g++, about two seconds)."""
+"""ctypes binding of the host C++ block codecs (``csrc/host/gguf_quant.cpp``)."""
 from __future__ import annotations
 
 import ctypes
-import os
-import subprocess
 import threading
 
 import numpy as np
 
 from .types import BLOCK_GEOMETRY, GgmlType, tensor_nbytes
 
-_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-_SRC = os.path.join(_ROOT, "csrc", "host", "gguf_quant.cpp")
-_SO = os.path.join(_ROOT, "lib", "libpmetal_host.so")
+from ..utils import hostlib
+
 _LOCK = threading.Lock()
 _LIB = None
-# -ffp-contract=off: a fused multiply-add would change results in the last bit and break byte compatibility
-CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-ffp-contract=off", "-pthread"]
+CXX_FLAGS = hostlib.CXX_FLAGS
 
 
 def build(force: bool = False) -> str:
-    os.makedirs(os.path.dirname(_SO), exist_ok=True)
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(_SRC):
-        tmp = _SO + f".{os.getpid()}.tmp"
-        r = subprocess.run(["g++"] + CXX_FLAGS + ["-shared", "-o", tmp, _SRC], stdout=subprocess.PIPE,
-                           stderr=subprocess.STDOUT, text=True)
-        if r.returncode != 0:
-            raise RuntimeError("host library build failed:\n" + r.stdout)
-        os.replace(tmp, _SO)
-    return _SO
+    return hostlib.build(force)
 
 
 def lib():
     global _LIB
     with _LOCK:
         if _LIB is None:
-            L = ctypes.CDLL(build())
+            L = hostlib.load()
             L.pm_gguf_quantize.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
             L.pm_gguf_dequantize.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
             L.pm_gguf_row_bytes.restype = ctypes.c_int64

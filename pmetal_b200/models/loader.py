@@ -49,8 +49,10 @@ def read_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
     if not files:
         raise FileNotFoundError(f"no safetensors weights in {model_dir}")
     sd: Dict[str, torch.Tensor] = {}
-    for f in files:
-        sd.update(st.load_file(os.path.join(model_dir, f)))
+    for f in files:        # shards above 64 MiB go through the threaded positional reader
+        path = os.path.join(model_dir, f)
+        big = os.path.getsize(path) >= (64 << 20) and os.environ.get("PMETAL_PY_LOADER") != "1"
+        sd.update(st.load_file_parallel(path) if big else st.load_file(path))
     return sd
 
 

@@ -153,8 +153,14 @@ def run_training(job: TrainingJobConfig, phase_cb: Optional[Callable[[str], None
         use_pack = job.use_packing and tcfg.use_packing
         if use_pack:
             pack_len = job.pack_max_seq_len or compute_pack_seq_len([len(s) for s in ds.samples], max_seq)
-            loader = PackedDataLoader(ds.samples, pack_len, job.packs_per_batch or tcfg.batch_size, True, tcfg.seed,
-                                      rank, world, tok.pad_token_id or 0)
+            if os.environ.get("PMETAL_PY_LOADER") == "1":     # pure-Python packer and collation (same batches)
+                loader = PackedDataLoader(ds.samples, pack_len, job.packs_per_batch or tcfg.batch_size, True, tcfg.seed,
+                                          rank, world, tok.pad_token_id or 0)
+            else:                                              # native packer, collation into pinned buffers
+                from ..data.fastpack import FastPackedLoader, TokenStore
+                loader = FastPackedLoader(TokenStore.from_samples(ds.samples), pack_len,
+                                          job.packs_per_batch or tcfg.batch_size, True, tcfg.seed, rank, world,
+                                          tok.pad_token_id or 0)
             log.info("packing: %s", loader.stats.summary())
             if loader.stats.max_sequences_per_batch <= 1:     # nothing gained: fall back (run_packed.rs:99-105)
                 use_pack = False

@@ -39,7 +39,7 @@ _SIZE = {"F32": 4, "F16": 2, "BF16": 2, "F64": 8, "I64": 8, "I32": 4, "I16": 2, 
 
 def _raw_bytes(t: torch.Tensor) -> bytes:
     t = t.detach().contiguous().cpu()
-    return t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+    return t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
 
 
 def save_file(tensors: Dict[str, torch.Tensor], path: str, metadata: Optional[Dict[str, str]] = None,
@@ -126,3 +126,43 @@ def load_file(path: str) -> Dict[str, torch.Tensor]:
 def load_metadata(path: str) -> Dict[str, str]:
     header, _ = read_header(path)
     return header.get("__metadata__", {}) or {}
+
+
+def load_file_parallel(path: str, names: Optional[Iterable[str]] = None, threads: int = 8,
+                       pin: bool = False) -> Dict[str, torch.Tensor]:
+    """Read tensors with several positional reads in flight (``csrc/host/runtime.cpp: pm_read_ranges``): each tensor gets
+    its own (optionally pinned) buffer and worker threads fill them directly, large tensors split into 64 MiB pieces.
+    ``names`` restricts the load to some tensors (a shard of a tensor-parallel or pipeline rank)."""
+    import ctypes
+    from . import hostlib
+    header, base = read_header(path)
+    header.pop("__metadata__", None)
+    size = os.path.getsize(path)
+    want = list(names) if names is not None else list(header)
+    out: Dict[str, torch.Tensor] = {}
+    offs, sizes, ptrs = [], [], []
+    for k in want:
+        e = header[k]
+        b, en = e["data_offsets"]
+        n = int(np.prod(e["shape"])) if e["shape"] else 1
+        if en < b or base + en > size or (en - b) != n * _SIZE[e["dtype"]]:
+            raise ValueError(f"corrupt safetensors entry {k!r}")
+        t = torch.empty(e["shape"], dtype=_RDT[e["dtype"]], pin_memory=pin and en > b)
+        out[k] = t
+        if en > b:
+            offs.append(base + b)
+            sizes.append(en - b)
+            ptrs.append(t.data_ptr())
+    if offs:
+        L = hostlib.load()
+        L.pm_read_ranges.restype = ctypes.c_int
+        L.pm_read_ranges.argtypes = [ctypes.c_char_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                     ctypes.c_int]
+        n = len(offs)
+        a_off = (ctypes.c_int64 * n)(*offs)
+        a_size = (ctypes.c_int64 * n)(*sizes)
+        a_ptr = (ctypes.c_void_p * n)(*ptrs)
+        rc = L.pm_read_ranges(os.fsencode(path), n, a_off, a_size, a_ptr, int(threads))
+        if rc != 0:
+            raise OSError(-rc, f"reading {path}: {os.strerror(-rc)}")
+    return out
