@@ -2,7 +2,7 @@
 //
 //   mode 0  all-gather -> GEMM (column-parallel):  Y[M, N_loc] = concat_r(X_r)[M, K] * W_loc[N_loc, K]^T
 //           X is sharded by rows across ranks (sequence-parallel activations, M_r = M / world rows each, in
-//           symmetric memory). The kernel starts on the tiles of its own shard at once; meanwhile the four epilogue
+//           symmetric memory). The kernel starts on the tiles of its own shard at once; meanwhile four dedicated
 //           warps of every CTA pull the remote shards, 128-row block by block, over NVLink into a local buffer with
 //           16-byte peer loads and publish a per-block flag; the TMA producer reaches the remote row blocks last and
 //           waits on those flags. Each remote byte crosses NVLink once (reading remote tiles directly would re-fetch
@@ -10,17 +10,18 @@
 //           overlaps the MMAs of the local tiles.
 //   mode 1  GEMM -> reduce-scatter (row-parallel): Y_r[M_r, N] = sum_q ( X_q[M, K_loc] * W_q[N, K_loc]^T )[rows of r]
 //           Each rank computes all M rows of its partial product; the epilogue pushes every finished tile as bf16
-//           straight into the owner's staging slot [parity][source rank] with 16-byte peer stores (remote owners
-//           first, own rows last); once every rank has signalled, each rank sums the `world` slots of its rows in
-//           fixed rank order (deterministic) and writes Y_r.
+//           straight into the owner's staging slot [parity][source rank] as 256-byte row segments (transposed through
+//           shared memory so that a warp's peer stores are contiguous; remote owners first, own rows last); once
+//           every rank has signalled, each rank sums the `world` slots of its rows in fixed rank order
+//           (deterministic) and writes Y_r.
 //
 // This replaces the reference's all_to_sharded_forward / sharded_to_all_forward (an all_sum around a local matmul,
 // crates/pmetal-distributed/src/tensor_parallel/sharded_linear.rs:41-106).
 //
 // GEMM core: persistent 128x256x64 tiles, warp 0 = TMA producer, warp 1 = tcgen05.mma issuer (accumulators
-// double-buffered in TMEM), warps 2-5 = epilogue. Cross-rank ordering uses epoch-valued flags in each rank's signal
-// pad (system-scope release/acquire); every wait is bounded and reports through the status word. Plain peer
-// loads/stores only: no multimem and no multicast loads.
+// double-buffered in TMEM), warps 2-5 = epilogue, warps 6-9 = stage-in of remote rows (mode 0). Cross-rank ordering
+// uses epoch-valued flags in each rank's signal pad (system-scope release/acquire); every wait is bounded and reports
+// through the status word. Plain peer loads/stores only: no multimem and no multicast loads.
 #include "gemm_common.cuh"
 
 namespace pm {
@@ -28,6 +29,7 @@ namespace pm {
 constexpr int kTpMaxRanks = 8;
 constexpr int kTpBN = 256;
 constexpr int kTpStages = 4;
+constexpr int kTpThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 stage-in (mode 0)
 constexpr int kStatusTpPeer = 106;
 
 // signal pad words
@@ -105,7 +107,7 @@ __device__ __forceinline__ void tp_tile(const TpParams& p, int w, int n_tiles, i
   *owner = (p.mode == 0) ? (p.rank + s) % p.world : (p.rank + 1 + s) % p.world;
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kTpThreads, 1)
 tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -221,11 +223,12 @@ tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
         if (ok) umma_commit(&tfull_bar[buf]);
       }
     }
-  } else {
-    const int q = warp & 3;
+  } else if (warp >= 6) {
     if (p.mode == 0 && p.world > 1) {
-      // ---- stage-in: this CTA's share of the remote row blocks, pulled over NVLink by its 128 epilogue threads
-      const int t128 = threadIdx.x - 64;
+      // ---- stage-in: this CTA's share of the remote row blocks, pulled over NVLink by four dedicated warps while
+      // the other warps run the tiles that are already local. Eight 16-byte loads per thread are in flight
+      // (16 KB per CTA), enough to cover the link's round trip at full bandwidth.
+      const int t128 = threadIdx.x - 192;
       const int vec_per_row = p.K / 8;
       bool copy_ok = true;
       for (int s = 1; s < p.world && copy_ok; ++s) {
@@ -238,10 +241,10 @@ tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
           const __nv_bfloat16* from = p.x_peer[src] + static_cast<long long>(b) * kBM * p.ldx;
           __nv_bfloat16* to = p.gathered + (static_cast<long long>(src) * p.rows_per_rank + b * kBM) * p.K;
           const int n_vec = kBM * vec_per_row;
-          for (int i0 = t128; i0 < n_vec; i0 += 128 * 4) {
-            uint4 v[4];
+          for (int i0 = t128; i0 < n_vec; i0 += 128 * 8) {
+            uint4 v[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
               const int i = i0 + u * 128;
               if (i < n_vec) {
                 const int r = i / vec_per_row, c = i - r * vec_per_row;
@@ -249,7 +252,7 @@ tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
               }
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < 8; ++u) {
               const int i = i0 + u * 128;
               if (i < n_vec) *reinterpret_cast<uint4*>(to + static_cast<long long>(i) * 8) = v[u];
             }
@@ -260,6 +263,8 @@ tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
         }
       }
     }
+  } else {
+    const int q = warp & 3;
     uint32_t acc_it = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++acc_it) {
       int owner, mb, nb;
@@ -268,13 +273,44 @@ tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
       if (!mbar_wait(&tfull_bar[buf], (acc_it >> 1) & 1, abort_flag, p.status, kTimeoutEpilogue)) break;
       tc_fence_after();
       const int lrow = mb * kBM + q * 32 + lane;     // row within the owner's shard
-      __nv_bfloat16* drow;
-      if (p.mode == 0) {
-        drow = p.D + (static_cast<long long>(owner) * p.rows_per_rank + lrow) * p.ldd;
+      if (p.mode == 1) {
+        // Peer stores leave as full 256-byte row segments: each warp transposes its 32 x 128 half tile through a
+        // swizzled shared-memory buffer (16-byte chunk index xor row, conflict-free both ways) and then writes two
+        // rows per instruction, 16 lanes x 16 bytes each. Lane-per-row stores would reach NVLink as 16-byte pieces.
+        uint4* stg = reinterpret_cast<uint4*>(smem + kTpStages * stage_bytes + 256) + q * (32 * 16);
+        const long long slot0 =
+            (static_cast<long long>(epoch & 1) * p.world + p.rank) * p.rows_per_rank + mb * kBM + q * 32;
+        __nv_bfloat16* dbase = p.stage[owner] + slot0 * p.N + nb * kTpBN;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_base + buf * kTpBN + (half * 4 + c4) * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v * 8]), __uint_as_float(r[v * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              stg[lane * 16 + ((c4 * 4 + v) ^ (lane & 15))] = o;
+            }
+          }
+          __syncwarp();
+          const int ch = lane & 15;
+          const int col = nb * kTpBN + half * 128 + ch * 8;
+#pragma unroll 4
+          for (int rr = 0; rr < 16; ++rr) {
+            const int row = rr * 2 + (lane >> 4);
+            const uint4 val = stg[row * 16 + (ch ^ (row & 15))];
+            if (col + 8 <= p.N) *reinterpret_cast<uint4*>(dbase + static_cast<long long>(row) * p.N + half * 128 + ch * 8) = val;
+          }
+          __syncwarp();
+        }
       } else {
-        const long long slot = (static_cast<long long>(epoch & 1) * p.world + p.rank) * p.rows_per_rank + lrow;
-        drow = p.stage[owner] + slot * p.N;
-      }
+      __nv_bfloat16* drow = p.D + (static_cast<long long>(owner) * p.rows_per_rank + lrow) * p.ldd;
 #pragma unroll 1
       for (int c = 0; c < kTpBN / 32; ++c) {
         uint32_t r[32];
@@ -293,6 +329,7 @@ tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
             *reinterpret_cast<uint4*>(drow + col) = o;
           }
         }
+      }
       }
       tc_fence_before();
       __syncwarp();
@@ -429,7 +466,8 @@ extern "C" int pm_tp_gemm(int mode, const unsigned long long* x_ptrs, int ldx, c
   maps.a[1] = maps.a[0];
   if (mode == 0 && world > 1 && (rc = operand_map(&maps.a[1], gathered, 0, M, K, K, kBM))) return rc * 10 - 5;
   if ((rc = operand_map(&maps.b, w, 0, N, K, ldw, kTpBN))) return rc * 10 - 6;
-  const size_t smem = static_cast<size_t>(kTpStages) * (kBM * kBK * 2 + kTpBN * kBK * 2) + 1024 + 256;
+  // operand stages, 256 bytes of barriers, 32 KB epilogue transpose buffer (4 warps x 32 rows x 256 B), alignment slack
+  const size_t smem = static_cast<size_t>(kTpStages) * (kBM * kBK * 2 + kTpBN * kBK * 2) + 256 + 4 * 32 * 256 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -440,6 +478,6 @@ extern "C" int pm_tp_gemm(int mode, const unsigned long long* x_ptrs, int ldx, c
   int grid = total;
   const int cap = max_ctas > 0 ? max_ctas : num_sms();
   if (grid > cap) grid = cap;
-  tp_gemm_kernel<<<grid, kThreads, smem, stream>>>(maps, p);
+  tp_gemm_kernel<<<grid, kTpThreads, smem, stream>>>(maps, p);
   return static_cast<int>(cudaGetLastError());
 }
