@@ -8,16 +8,16 @@
 //                       it by all ranks are concatenated (own rows first) and cut into 128-row tiles, so a tile may
 //                       hold rows of several source ranks ("runs"). With few tokens per expert (decode, or many
 //                       ranks) this streams each expert's weights through the SMs once instead of once per source.
-//   moe_gemm_kernel #1  gate/up projection with the dispatch all-to-all inside: at kernel start the four epilogue warps
-//                       of every CTA pull their share of the tiles' token rows out of the *source ranks'* sorted
-//                       buffers (16-byte peer loads over NVLink) into a local staging buffer and publish a flag per
+//   moe_gemm_kernel #1  gate/up projection with the dispatch all-to-all inside: four dedicated warps of every CTA pull
+//                       their share of the tiles' token rows out of the *source ranks'* sorted buffers (16-byte
+//                       peer loads over NVLink, eight in flight per thread) into a local staging buffer and publish a flag per
 //                       tile; the TMA producer waits on a tile's flag before loading it. Every token row crosses
 //                       NVLink once (peer memory is not cached in the local L2, so reading remote rows in place would
 //                       re-fetch them once per column block). The epilogue applies SwiGLU, writing h locally.
 //   moe_gemm_kernel #2  down projection on h; the epilogue stores every output row straight into the *source rank's*
-//                       result buffer at the row's sorted position (16-byte peer stores, destination looked up in
-//                       the tile's runs) -- this is the combine
-//                       all-to-all. The launch ends only after every peer has signalled that its pushes are complete,
+//                       result buffer at the row's sorted position (256-byte row segments, transposed through shared
+//                       memory so that a warp's peer stores are contiguous; destination looked up in the tile's
+//                       runs) -- this is the combine all-to-all. The launch ends only after every peer has signalled that its pushes are complete,
 //                       so the local weighted combine that follows on the stream sees all rows.
 //
 // With world = 1 the same kernels are the local grouped GEMM. This replaces the reference's per-destination
@@ -25,7 +25,7 @@
 // kernels (crates/pmetal-metal/src/kernels/metal/grouped_gemm.metal:125-465, fused_moe.metal).
 //
 // GEMM core: persistent 128x256x64 tcgen05 tiles over a device-side tile list (warp 0 TMA, warp 1 MMA, warps 2-5
-// epilogue, TMEM double-buffered). Gate/up weights are stored per expert in blocks of 256 rows: 128 gate rows followed
+// epilogue, warps 6-9 dispatch stage-in, TMEM double-buffered). Gate/up weights are stored per expert in blocks of 256 rows: 128 gate rows followed
 // by the matching 128 up rows, so one accumulator tile holds both halves of 128 outputs.
 // All cross-rank waits are bounded and report through the status word; plain peer loads/stores only.
 #include "gemm_common.cuh"
@@ -35,6 +35,7 @@ namespace pm {
 constexpr int kEpMaxRanks = 8;
 constexpr int kEpBN = 256;
 constexpr int kEpStages = 4;
+constexpr int kEpThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-9 dispatch stage-in
 constexpr int kStatusEpPeer = 107;
 
 constexpr int kEpReady = 0;     // [8] rank r's sorted tokens + offsets of this epoch are published
@@ -215,7 +216,7 @@ __global__ void ep_prepare_kernel(const EpPtrs ptrs, int rank, int world, int e_
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kEpThreads, 1)
 moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -323,11 +324,11 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
         if (ok) umma_commit(&tfull_bar[buf]);
       }
     }
-  } else {
-    const int q = warp & 3;
+  } else if (warp >= 6) {
     if (p.stage_in) {
-      // ---- dispatch: copy this CTA's share of the tiles' rows from their source ranks into the staging buffer
-      const int t128 = threadIdx.x - 64;
+      // ---- dispatch: four dedicated warps copy this CTA's share of the tiles' rows from their source ranks into the
+      // staging buffer while the other warps work on tiles that have landed; eight 16-byte loads per thread in flight
+      const int t128 = threadIdx.x - 192;
       const int vec_per_row = p.K / 8;
       const int n_t = *p.n_tiles;
       for (int ti = blockIdx.x; ti < n_t; ti += gridDim.x) {
@@ -337,13 +338,13 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
           const __nv_bfloat16* from = p.x_peer[rn.src] + static_cast<long long>(rn.src_row0) * p.K;
           __nv_bfloat16* to = p.xin + static_cast<long long>(t.a_row0 + rn.tile_row0) * p.K;
           const int n_vec = rn.rows * vec_per_row;
-          for (int i0 = t128; i0 < n_vec; i0 += 128 * 4) {
-            uint4 v[4];
+          for (int i0 = t128; i0 < n_vec; i0 += 128 * 8) {
+            uint4 v[8];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < 8; ++u)
               if (i0 + u * 128 < n_vec) v[u] = reinterpret_cast<const uint4*>(from)[i0 + u * 128];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+            for (int u = 0; u < 8; ++u)
               if (i0 + u * 128 < n_vec) reinterpret_cast<uint4*>(to)[i0 + u * 128] = v[u];
           }
         }
@@ -352,6 +353,8 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
         if (t128 == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.tile_ready + ti), "r"(epoch) : "memory");
       }
     }
+  } else {
+    const int q = warp & 3;
     uint32_t acc_it = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++acc_it) {
       const MoeTile t = p.tiles[w / n_blocks];
@@ -398,6 +401,41 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
             o.w = pack_bf16x2(f[6], f[7]);
             *reinterpret_cast<uint4*>(drow + col) = o;
           }
+        }
+      } else if (p.push) {
+        // Rows leave for their source ranks as 256-byte segments: the warp transposes its 32 x 128 half tile through a
+        // swizzled shared-memory buffer and writes two rows per instruction (16 lanes x 16 bytes each); each row's
+        // destination comes from the lane that owns the row.
+        uint4* stg = reinterpret_cast<uint4*>(smem + kEpStages * stage_bytes + 256) + q * (32 * 16);
+        const unsigned long long dptr = row_ok ? reinterpret_cast<unsigned long long>(drow) : 0ull;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tbase + (half * 4 + c4) * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v * 8]), __uint_as_float(r[v * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              stg[lane * 16 + ((c4 * 4 + v) ^ (lane & 15))] = o;
+            }
+          }
+          __syncwarp();
+          const int ch = lane & 15;
+          const int col = nb * kEpBN + half * 128 + ch * 8;
+#pragma unroll 4
+          for (int rr = 0; rr < 16; ++rr) {
+            const int row = rr * 2 + (lane >> 4);
+            const unsigned long long dp = __shfl_sync(0xffffffffu, dptr, row);
+            const uint4 val = stg[row * 16 + (ch ^ (row & 15))];
+            if (dp != 0ull && col + 8 <= p.N) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dp) + col) = val;
+          }
+          __syncwarp();
         }
       } else {
 #pragma unroll 1
@@ -511,7 +549,8 @@ extern "C" int pm_moe_gemm(const void* a, int a_rows, int lda, const void* w, in
   }
   p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
   p.status = status;
-  const size_t smem = static_cast<size_t>(kEpStages) * (kBM * kBK * 2 + kEpBN * kBK * 2) + 1024 + 256;
+  // operand stages, 256 bytes of barriers, 32 KB epilogue transpose buffer (4 warps x 32 rows x 256 B), alignment slack
+  const size_t smem = static_cast<size_t>(kEpStages) * (kBM * kBK * 2 + kEpBN * kBK * 2) + 256 + 4 * 32 * 256 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(moe_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -521,6 +560,6 @@ extern "C" int pm_moe_gemm(const void* a, int a_rows, int lda, const void* w, in
   const long long work = static_cast<long long>(max_tiles) * ((N + kEpBN - 1) / kEpBN);
   int grid = num_sms();
   if (work < grid) grid = static_cast<int>(work < 1 ? 1 : work);
-  moe_gemm_kernel<<<grid, kThreads, smem, st>>>(maps, p);
+  moe_gemm_kernel<<<grid, kEpThreads, smem, st>>>(maps, p);
   return static_cast<int>(cudaGetLastError());
 }
