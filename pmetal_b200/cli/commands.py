@@ -175,27 +175,42 @@ def _load_for_inference(a):
         tpl = ChatTemplate.from_model_dir(mdir)
     else:
         tok, tpl = ByteTokenizer(), ChatTemplate("chatml")
-    eos = [i for i in (tok.eos_token_id,) if i is not None]
+    if mdir:
+        from ..data.inference_config import collect_all_stop_tokens
+        eos = collect_all_stop_tokens(mdir, tok, tpl.eos())
+    else:
+        eos = [i for i in (tok.eos_token_id,) if i is not None]
     return model, tok, tpl, eos, mdir
 
 
-def _sampling_from_args(a):
+def _sampling_from_args(a, model_dir=None, template_type=None, thinking=False):
+    """Explicit flags win over the ``--mode`` preset of the model family, which wins over the model's
+    ``generation_config.json``, which wins over the global fallback (temperature 0.7, top-k 20, top-p 0.8)."""
+    from ..data.inference_config import load_sampling_defaults
     from ..models.sampling import SamplingParams
-    if getattr(a, "greedy", False) or a.temperature <= 0:
+    d = load_sampling_defaults(model_dir, template_type, getattr(a, "mode", "auto") or "auto", thinking,
+                               use_preset=model_dir is not None)
+
+    def pick(name):
+        v = getattr(a, name, None)
+        return getattr(d, name) if v is None else v
+    temperature = pick("temperature")
+    if getattr(a, "greedy", False) or temperature <= 0:
         return SamplingParams.greedy(a.max_tokens)
-    return SamplingParams(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p, min_p=a.min_p,
-                          repetition_penalty=a.repetition_penalty, frequency_penalty=a.frequency_penalty,
-                          presence_penalty=a.presence_penalty, max_tokens=a.max_tokens, seed=a.seed)
+    return SamplingParams(temperature=temperature, top_k=pick("top_k"), top_p=pick("top_p"), min_p=pick("min_p"),
+                          repetition_penalty=pick("repetition_penalty"), frequency_penalty=pick("frequency_penalty"),
+                          presence_penalty=pick("presence_penalty"), max_tokens=a.max_tokens, seed=a.seed)
 
 
-def _add_sampling_flags(p):
-    p.add_argument("--temperature", type=float, default=0.7)
-    p.add_argument("--top-k", type=int, default=40)
-    p.add_argument("--top-p", type=float, default=0.95)
-    p.add_argument("--min-p", type=float, default=0.05)
-    p.add_argument("--repetition-penalty", type=float, default=1.1)
-    p.add_argument("--frequency-penalty", type=float, default=0.0)
-    p.add_argument("--presence-penalty", type=float, default=0.0)
+def _add_sampling_flags(p, defaults=None):
+    d = defaults or {}
+    p.add_argument("--temperature", type=float, default=d.get("temperature"))
+    p.add_argument("--top-k", type=int, default=d.get("top_k"))
+    p.add_argument("--top-p", type=float, default=d.get("top_p"))
+    p.add_argument("--min-p", type=float, default=d.get("min_p"))
+    p.add_argument("--repetition-penalty", type=float, default=d.get("repetition_penalty"))
+    p.add_argument("--frequency-penalty", type=float, default=d.get("frequency_penalty"))
+    p.add_argument("--presence-penalty", type=float, default=d.get("presence_penalty"))
     p.add_argument("--max-tokens", type=int, default=256)
     p.add_argument("--seed", type=int, default=None)
     p.add_argument("--greedy", action="store_true")
@@ -210,6 +225,9 @@ def _infer_args(sp):
     p.add_argument("--system")
     p.add_argument("--chat", action="store_true", help="apply the chat template")
     p.add_argument("--no-thinking", action="store_true")
+    p.add_argument("--hide-thinking", action="store_true", help="with --stream: do not print the reasoning channel")
+    p.add_argument("--mode", default="auto", help="sampling preset of the model family: auto, thinking-general, "
+                   "thinking-coding, instruct-general, instruct-reasoning")
     p.add_argument("--stream", action="store_true")
     p.add_argument("--draft-model", help="two-model speculative decoding with this draft")
     p.add_argument("--speculative-k", type=int, default=5)
@@ -224,15 +242,15 @@ def _infer_args(sp):
 @_command(_infer_args)
 def cmd_infer(a) -> int:
     from ..data.chat_templates import Message
-    from ..data.tokenizer import StreamDecoder
+    from ..data.stream_format import StreamFormatter
     from ..models.generation import Generator
-    model, tok, tpl, eos, _ = _load_for_inference(a)
+    model, tok, tpl, eos, mdir = _load_for_inference(a)
     if a.chat or a.system:
         msgs = ([Message("system", a.system)] if a.system else []) + [Message("user", a.prompt)]
         ids = tok.encode_with_special_tokens(tpl.apply_inference(msgs, a.no_thinking))
     else:
         ids = tok.encode(a.prompt)
-    sp_ = _sampling_from_args(a)
+    sp_ = _sampling_from_args(a, mdir, tpl.template_type, thinking=bool(a.chat or a.system) and not a.no_thinking)
     if a.draft_model:
         from ..models.loader import load_pretrained
         from ..models.speculative import SpeculativeConfig, SpeculativeDecoder
@@ -249,7 +267,7 @@ def cmd_infer(a) -> int:
         return 0
     gen = Generator(model, num_blocks=a.kv_blocks)
     if a.stream and not a.json:
-        dec = StreamDecoder(tok)
+        dec = StreamFormatter(tok, show_thinking=not a.hide_thinking)
         for t in gen.stream(ids, sp_, eos):
             if t not in eos:
                 sys.stdout.write(dec.push(t))
@@ -656,7 +674,7 @@ def _ollama_args(sp):
     p.add_argument("--template", default="chatml")
     p.add_argument("--system")
     p.add_argument("-o", "--output", default="Modelfile")
-    _add_sampling_flags(p)
+    _add_sampling_flags(p, {"temperature": 0.7, "top_k": 40, "top_p": 0.95, "repetition_penalty": 1.1})
     return p
 
 
