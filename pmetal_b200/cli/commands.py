@@ -669,9 +669,12 @@ def cmd_upload(a) -> int:
 
 def _ollama_args(sp):
     p = sp.add_parser("ollama", help="write an Ollama Modelfile for a GGUF export")
-    p.add_argument("action", choices=["modelfile", "templates"])
-    p.add_argument("--gguf")
-    p.add_argument("--template", default="chatml")
+    p.add_argument("action", choices=["modelfile", "create", "templates"])
+    p.add_argument("--gguf", "--base", dest="gguf", help="GGUF file (or model directory) the Modelfile starts FROM")
+    p.add_argument("--name", help="create: the Ollama model name to register")
+    p.add_argument("--lora", help="adapter directory or file added as ADAPTER")
+    p.add_argument("--num-ctx", type=int)
+    p.add_argument("--template", default=None, help="default: detected from the model name")
     p.add_argument("--system")
     p.add_argument("-o", "--output", default="Modelfile")
     _add_sampling_flags(p, {"temperature": 0.7, "top_k": 40, "top_p": 0.95, "repetition_penalty": 1.1})
@@ -687,8 +690,21 @@ def cmd_ollama(a) -> int:
     if not a.gguf:
         print("error: --gguf is required", file=sys.stderr)
         return 2
-    print(write_modelfile(a.gguf, a.output, a.template, a.system, temperature=a.temperature, top_k=a.top_k, top_p=a.top_p,
-                          repeat_penalty=a.repetition_penalty))
+    from ..utils.ollama import detect_template, validate_model_name
+    if a.action == "create":
+        if not a.name:
+            print("error: --name is required", file=sys.stderr)
+            return 2
+        try:
+            validate_model_name(a.name)
+        except ValueError as e:
+            print(f"error: {e}", file=sys.stderr)
+            return 2
+    print(write_modelfile(a.gguf, a.output, a.template or detect_template(a.gguf), a.system, a.lora,
+                          temperature=a.temperature, top_k=a.top_k, top_p=a.top_p, repeat_penalty=a.repetition_penalty,
+                          num_ctx=a.num_ctx))
+    if a.action == "create":
+        print(f"To register the model, run:\n  ollama create {a.name} -f {a.output}")
     return 0
 
 

@@ -1,4 +1,5 @@
-"""Ollama Modelfile generation (crates/pmetal-models/src/ollama.rs; CLI ``ollama modelfile|templates``)."""
+"""Ollama Modelfile generation (crates/pmetal-models/src/ollama.rs, crates/pmetal/src/commands/ollama.rs:35-310; CLI
+``ollama modelfile|create|templates``)."""
 from __future__ import annotations
 
 import os
@@ -21,10 +22,40 @@ STOPS = {"chatml": ["<|im_end|>", "<|im_start|>"], "llama3": ["<|eot_id|>", "<|s
          "gemma": ["<end_of_turn>"], "phi3": ["<|end|>", "<|user|>"], "alpaca": ["### Instruction:"]}
 
 
-def modelfile_text(gguf_path: str, template: str = "chatml", system: Optional[str] = None, **params) -> str:
+TEMPLATES["qwen3"] = TEMPLATES["chatml"]
+TEMPLATES["deepseek"] = ("{{ if .System }}{{ .System }}\n\n{{ end }}{{ if .Prompt }}User: {{ .Prompt }}\n\n{{ end }}"
+                         "Assistant: {{ .Response }}<｜end▁of▁sentence｜>")
+STOPS["qwen3"] = STOPS["chatml"]
+STOPS["deepseek"] = ["<｜end▁of▁sentence｜>", "User:"]
+
+
+def detect_template(model_name: str) -> str:
+    """Template by model name (llama / qwen / gemma / mistral / phi / deepseek), ChatML otherwise."""
+    n = model_name.lower()
+    for key, tpl in (("llama", "llama3"), ("qwen", "qwen3"), ("gemma", "gemma"), ("mistral", "mistral"),
+                     ("mixtral", "mistral"), ("phi", "phi3"), ("deepseek", "deepseek")):
+        if key in n:
+            return tpl
+    return "chatml"
+
+
+def validate_model_name(name: str) -> str:
+    """Ollama model names: ``[namespace/]model[:tag]`` of letters, digits, ``._-``; anything else is refused so the
+    printed ``ollama create`` command cannot be turned into another command."""
+    import re
+    if not name or len(name) > 128 or not re.fullmatch(r"[A-Za-z0-9][A-Za-z0-9._-]*(/[A-Za-z0-9][A-Za-z0-9._-]*)?(:[A-Za-z0-9._-]+)?", name):
+        raise ValueError(f"invalid Ollama model name {name!r}")
+    return name
+
+
+def modelfile_text(gguf_path: str, template: str = "chatml", system: Optional[str] = None, adapter: Optional[str] = None,
+                   **params) -> str:
     if template not in TEMPLATES:
         raise ValueError(f"unknown template {template!r}; choose from {sorted(TEMPLATES)}")
-    lines = [f"FROM {gguf_path}", f'TEMPLATE """{TEMPLATES[template]}"""']
+    lines = [f"FROM {gguf_path}"]
+    if adapter:
+        lines.append(f"ADAPTER {adapter}")
+    lines.append(f'TEMPLATE """{TEMPLATES[template]}"""')
     if system:
         lines.append(f'SYSTEM """{system}"""')
     for k, v in params.items():
@@ -35,7 +66,8 @@ def modelfile_text(gguf_path: str, template: str = "chatml", system: Optional[st
 
 
 def write_modelfile(gguf_path: str, out_path: str = "Modelfile", template: str = "chatml", system: Optional[str] = None,
-                    **params) -> str:
+                    adapter: Optional[str] = None, **params) -> str:
     with open(out_path, "w", encoding="utf-8") as fh:
-        fh.write(modelfile_text(os.path.abspath(gguf_path), template, system, **params))
+        fh.write(modelfile_text(os.path.abspath(gguf_path), template, system,
+                                os.path.abspath(adapter) if adapter else None, **params))
     return out_path

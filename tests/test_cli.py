@@ -65,6 +65,9 @@ def test_quantize_merge_fuse_ollama(model_dir, capsys, tmp_path):
     assert (back[k] - a[k].float()).abs().max() < 0.07 * a[k].float().abs().max()
     mf = str(tmp_path / "Modelfile")
     assert main(["ollama", "modelfile", "--gguf", gg, "-o", mf, "--template", "chatml", "--system", "be nice"]) == 0
+    assert main(["ollama", "create", "--name", "me/tiny:v1", "--base", gg, "-o", mf + "2", "--num-ctx", "4096"]) == 0
+    assert "ollama create me/tiny:v1" in capsys.readouterr().out and "num_ctx 4096" in open(mf + "2").read()
+    assert main(["ollama", "create", "--name", "x; rm -rf /", "--base", gg, "-o", mf + "3"]) == 2
     text = open(mf).read()
     assert text.startswith("FROM ") and 'SYSTEM """be nice"""' in text and "PARAMETER stop" in text
     assert main(["download", "/nonexistent/x"]) == 1
