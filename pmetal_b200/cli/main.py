@@ -66,6 +66,12 @@ def _add_train(sp):
     p.add_argument("--distributed-auto", action="store_true")
     p.add_argument("--compression-strategy", default="none")
     p.add_argument("--dp-impl", default="fused", choices=["fused", "nccl"])
+    # accepted for command-line compatibility with the reference (crates/pmetal/src/cli/train.rs:10-186)
+    p.add_argument("--no-flash-attention", action="store_true", help="same effect as --no-fused: PyTorch reference attention")
+    p.add_argument("--no-metal-fused-optimizer", action="store_true",
+                   help="same effect as --dp-impl nccl: separate all-reduce, clip and AdamW kernels instead of the fused step")
+    p.add_argument("--loss-scale", type=float, default=None, help="ignored: bf16 training needs no loss scaling")
+    p.add_argument("--ane", action="store_true", help="ignored: Apple Neural Engine path of the reference")
     p.add_argument("--device", default=None)
     p.add_argument("--dtype", default="bfloat16")
     p.set_defaults(func=cmd_train)
@@ -123,8 +129,13 @@ def cmd_train(a) -> int:
         job.dataset_format = "custom"
         job.custom_columns = CustomColumns(a.text_column or "text", a.text_columns.split(",") if a.text_columns else None,
                                            a.column_separator, a.prompt_column, a.response_column)
-    if a.no_fused:
+    if a.no_fused or a.no_flash_attention:
         os.environ["PMETAL_FORCE_REFERENCE"] = "1"
+    if a.no_metal_fused_optimizer:
+        job.dp_impl = "nccl"
+    for flag in ("ane", "loss_scale"):
+        if getattr(a, flag):
+            print(f"note: --{flag.replace('_', '-')} has no effect on this hardware", file=sys.stderr)
     sink = JsonlSink(a.log_events) if getattr(a, "log_events", None) else None
     summary = run_training(job, sink=sink)
     print(json.dumps(summary))
