@@ -62,7 +62,7 @@ def test_mel_features_and_losses():
     assert mel.shape == (1, 20, 800 // 8)
     peak = int(mel[0, :, 20].argmax())
     centre = V.mel_to_hz(V.hz_to_mel(0) + (V.hz_to_mel(4000) - V.hz_to_mel(0)) * (peak + 1) / 21)
-    assert abs(centre - 1000) < 250                                    # the tone lands in the band around 1 kHz
+    assert abs(centre - 1000) < 250                                    # the tone lands in the band near 1 kHz
     ones = [(torch.ones(2, 3), [torch.ones(2, 3)])]
     zeros = [(torch.zeros(2, 3), [torch.zeros(2, 3)])]
     assert float(V.generator_adversarial_loss(ones)) == 0 and float(V.generator_adversarial_loss(zeros)) == 1
