@@ -97,39 +97,135 @@ def cmd_tokenize(a) -> int:
 
 # ------------------------------------------------------------------------------------------- dataset
 def _dataset_args(sp):
-    p = sp.add_parser("dataset", help="dataset tools")
+    p = sp.add_parser("dataset", help="dataset tools: analyze, validate, preview, convert, filter, split, merge, sample, "
+                                      "template, prepare, formats, download")
     s = p.add_subparsers(dest="dataset_cmd")
+
+    def io(q, out=True):
+        q.add_argument("-i", "--input", required=True)
+        if out:
+            q.add_argument("-o", "--output", required=True)
     an = s.add_parser("analyze")
-    an.add_argument("path")
+    an.add_argument("path", nargs="?")
+    an.add_argument("-p", "--path", dest="path_flag")
     an.add_argument("-m", "--model", default=None)
     an.add_argument("--max-seq-len", type=int, default=8192)
+    va = s.add_parser("validate")
+    va.add_argument("path", nargs="?")
+    va.add_argument("-p", "--path", dest="path_flag")
+    va.add_argument("-m", "--model", default=None)
+    va.add_argument("--max-seq-len", type=int, default=2048)
+    pv = s.add_parser("preview")
+    pv.add_argument("dataset_id")
+    pv.add_argument("--split", default="train")
+    pv.add_argument("-n", "--num", type=int, default=5)
     cv = s.add_parser("convert")
-    cv.add_argument("path")
+    cv.add_argument("path", nargs="?")
+    cv.add_argument("-i", "--input", dest="path_flag")
     cv.add_argument("-o", "--output", required=True)
     cv.add_argument("--to", default="openai", choices=["openai", "simple"])
+    cv.add_argument("--columns", help='column mapping, e.g. "instruction=problem,output=solution"')
+    cv.add_argument("--shuffle", action="store_true")
+    cv.add_argument("--seed", type=int, default=42)
+    fl = s.add_parser("filter")
+    io(fl)
+    fl.add_argument("-m", "--model")
+    fl.add_argument("--min-tokens", type=int)
+    fl.add_argument("--max-tokens", type=int)
+    fl.add_argument("--dedup", action="store_true")
+    fl.add_argument("--pattern")
+    fl.add_argument("--invert", action="store_true")
+    fl.add_argument("--complete-only", action="store_true")
+    sl = s.add_parser("split")
+    io(sl, out=False)
+    sl.add_argument("-o", "--output-dir", required=True)
+    sl.add_argument("--val-ratio", type=float, default=0.1)
+    sl.add_argument("--test-ratio", type=float, default=0.0)
+    sl.add_argument("--seed", type=int, default=42)
+    sl.add_argument("--stratify")
+    mg = s.add_parser("merge")
+    mg.add_argument("-i", "--inputs", nargs="+", required=True)
+    mg.add_argument("-o", "--output", required=True)
+    mg.add_argument("--shuffle", action="store_true")
+    mg.add_argument("--seed", type=int, default=42)
+    mg.add_argument("--interleave", action="store_true")
+    mg.add_argument("--weights", help="comma-separated, one per input")
+    sm = s.add_parser("sample")
+    io(sm)
+    sm.add_argument("-n", "--num", type=int, required=True)
+    sm.add_argument("--seed", type=int, default=42)
+    tp = s.add_parser("template")
+    io(tp)
+    tp.add_argument("--template", default="chatml")
+    tp.add_argument("--system")
+    tp.add_argument("-m", "--model")
+    tp.add_argument("--add-generation-prompt", action="store_true")
+    tp.add_argument("--mask-prompt", action="store_true")
+    pr = s.add_parser("prepare")
+    pr.add_argument("dataset")
+    pr.add_argument("-o", "--output-dir", required=True)
+    pr.add_argument("-m", "--model", required=True)
+    pr.add_argument("--template", default="chatml")
+    pr.add_argument("--max-seq-len", type=int, default=2048)
+    pr.add_argument("--val-ratio", type=float, default=0.05)
+    pr.add_argument("--seed", type=int, default=42)
+    pr.add_argument("--no-dedup", action="store_true")
+    pr.add_argument("--columns")
+    s.add_parser("formats")
     dl = s.add_parser("download")
     dl.add_argument("dataset_id")
+    dl.add_argument("--split", default="train")
+    dl.add_argument("-o", "--output")
+    dl.add_argument("--revision")
     return p
+
+
+def _dataset_tokenizer(model):
+    """(tokenizer, model directory) for ``--model``; the byte tokenizer for ``random:`` presets."""
+    from ..data.tokenizer import ByteTokenizer, Tokenizer
+    from ..models.loader import resolve_model_path
+    if not model:
+        return None, None
+    path = resolve_model_path(model)
+    if path.startswith("random:") or not os.path.exists(os.path.join(path, "tokenizer.json")):
+        return ByteTokenizer(), None
+    return Tokenizer.from_model_dir(path), path
 
 
 @_command(_dataset_args)
 def cmd_dataset(a) -> int:
     from ..data import dataset as ds
-    from ..data.tokenizer import ByteTokenizer, Tokenizer
-    if a.dataset_cmd == "analyze":
-        tok = ByteTokenizer()
-        if a.model:
-            from ..models.loader import resolve_model_path
-            tok = Tokenizer.from_model_dir(resolve_model_path(a.model))
-        d = ds.TrainingDataset.from_file_tokenized(a.path, tok, a.max_seq_len)
+    from ..data import tools as dt
+    from ..data.tokenizer import ByteTokenizer
+    cmd = a.dataset_cmd
+    path = getattr(a, "path", None) or getattr(a, "path_flag", None)
+    if cmd in ("analyze", "validate", "convert") and not path:
+        print("error: a dataset path is required", file=sys.stderr)
+        return 2
+    if cmd == "analyze":
+        tok = _dataset_tokenizer(a.model)[0] or ByteTokenizer()
+        d = ds.TrainingDataset.from_file_tokenized(path, tok, a.max_seq_len)
         st = d.stats()
         st["format"] = d.format
         from ..data.packing import compute_pack_seq_len
         st["suggested_pack_len"] = compute_pack_seq_len([len(s) for s in d.samples], a.max_seq_len)
         print(json.dumps(st, indent=2))
         return 0
-    if a.dataset_cmd == "convert":
-        recs = ds.read_records(a.path)
+    if cmd == "validate":
+        rep = dt.validate(path, _dataset_tokenizer(a.model)[0], a.max_seq_len)
+        print(json.dumps(rep, indent=2))
+        return 0 if rep["ok"] else 1
+    if cmd == "preview":
+        if not os.path.exists(a.dataset_id):
+            print("dataset preview of a hub id needs network access; pass a local file", file=sys.stderr)
+            return 2
+        print(json.dumps(dt.preview(a.dataset_id, a.num), indent=2, ensure_ascii=False))
+        return 0
+    if cmd == "convert":
+        recs = dt.remap_columns(ds.read_records(path), a.columns)
+        if a.shuffle:
+            import random
+            random.Random(a.seed).shuffle(recs)
         fmt = ds.detect_format(recs[0])
         with open(a.output, "w", encoding="utf-8") as fh:
             for r in recs:
@@ -141,6 +237,49 @@ def cmd_dataset(a) -> int:
                     fh.write(json.dumps({"messages": [{"role": "user", "content": p},
                                                       {"role": "assistant", "content": ts.text[len(p):]}]}) + "\n")
         print(json.dumps({"converted": len(recs), "from": fmt, "to": a.to}))
+        return 0
+    if cmd == "filter":
+        try:
+            kept, rep = dt.filter_records(ds.read_records(a.input), _dataset_tokenizer(a.model)[0], a.min_tokens, a.max_tokens,
+                                          a.dedup, a.pattern, a.invert, a.complete_only)
+        except ValueError as e:
+            print(f"error: {e}", file=sys.stderr)
+            return 2
+        dt.write_jsonl(kept, a.output)
+        print(json.dumps(rep))
+        return 0
+    if cmd == "split":
+        parts = dt.split_records(ds.read_records(a.input), a.val_ratio, a.test_ratio, a.seed, a.stratify)
+        rep = {}
+        for name, rows in parts.items():
+            if rows or name == "train":
+                rep[name] = dt.write_jsonl(rows, os.path.join(a.output_dir, f"{name}.jsonl"))
+        print(json.dumps(rep))
+        return 0
+    if cmd == "merge":
+        w = [float(x) for x in a.weights.split(",")] if a.weights else None
+        out = dt.merge_records([ds.read_records(p) for p in a.inputs], a.shuffle, a.seed, a.interleave, w)
+        print(json.dumps({"merged": dt.write_jsonl(out, a.output), "inputs": len(a.inputs)}))
+        return 0
+    if cmd == "sample":
+        print(json.dumps({"sampled": dt.write_jsonl(dt.sample_records(ds.read_records(a.input), a.num, a.seed), a.output)}))
+        return 0
+    if cmd == "template":
+        out, rep = dt.apply_template(ds.read_records(a.input), a.template, a.system, _dataset_tokenizer(a.model)[1],
+                                     a.add_generation_prompt, a.mask_prompt)
+        dt.write_jsonl(out, a.output)
+        print(json.dumps(rep))
+        return 0
+    if cmd == "prepare":
+        if not os.path.exists(a.dataset):
+            print("dataset prepare of a hub id needs network access; pass a local file", file=sys.stderr)
+            return 2
+        tok, mdir = _dataset_tokenizer(a.model)
+        print(json.dumps(dt.prepare(a.dataset, a.output_dir, tok, mdir, a.template, a.max_seq_len, a.val_ratio, a.seed,
+                                    not a.no_dedup, a.columns), indent=2))
+        return 0
+    if cmd == "formats":
+        print(json.dumps(dt.formats(), indent=2))
         return 0
     print("dataset download needs network access, which this machine does not have", file=sys.stderr)
     return 2

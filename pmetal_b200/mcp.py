@@ -85,11 +85,13 @@ class McpServer:
                            stderr=subprocess.PIPE, text=True)
         if r.returncode != 0:
             raise RuntimeError(r.stderr[-2000:] or f"exit code {r.returncode}")
-        last = r.stdout.strip().splitlines()[-1] if r.stdout.strip() else ""
-        try:
-            return json.loads(last)
-        except json.JSONDecodeError:
-            return {"output": r.stdout[-4000:]}
+        text = r.stdout.strip()
+        for cand in (text, text.splitlines()[-1] if text else ""):      # one (possibly indented) document, or a last line
+            try:
+                return json.loads(cand)
+            except json.JSONDecodeError:
+                continue
+        return {"output": r.stdout[-4000:]}
 
     def _register(self):
         s = {"type": "string"}
@@ -135,6 +137,120 @@ class McpServer:
         self.tool("reset_learning_rate", "return to the schedule", od, ["output_dir"], lr_cmd("reset_lr"))
         self.tool("save_checkpoint_now", "ask a running job to checkpoint", od, ["output_dir"], lr_cmd("save_checkpoint"))
         self.tool("graceful_stop", "ask a running job to stop after the current step", od, ["output_dir"], lr_cmd("graceful_stop"))
+
+        self._register_more()
+
+    def _register_more(self):
+        """The rest of the reference server's tool list (crates/pmetal-mcp/src/lib.rs:187-1400): model discovery,
+        further job kinds, the dataset actions, benchmarks, packaging helpers and generic CLI access, under the
+        reference's tool names; a few earlier tools are also reachable by the name the reference gives them."""
+        s, i, b = {"type": "string"}, {"type": "integer"}, {"type": "boolean"}
+        extra = {"extra": {"type": "object", "description": "additional CLI flags"}}
+
+        def cli(name, description, argv_prefix, props, required, positional=()):
+            def fn(a):
+                flags = {k: v for k, v in a.items() if k not in positional and k != "extra"}
+                flags.update(a.get("extra") or {})
+                return self._cli_inline(list(argv_prefix) + [str(a[k]) for k in positional if k in a] + _args_to_argv(flags))
+            self.tool(name, description, {**props, **extra}, required, fn)
+
+        for alias, target in (("device_info", "system_info"), ("memory", "estimate_memory"), ("generate", "infer"),
+                              ("stop_job", "job_cancel"), ("eval_perplexity", "evaluate"), ("quantize", "start_quantize"),
+                              ("fuse_lora", "start_fuse"), ("merge_models", "start_merge"), ("train", "start_train"),
+                              ("distill", "start_distill"), ("grpo", "start_grpo"), ("job_set_lr", "set_learning_rate"),
+                              ("job_reduce_lr", "reduce_learning_rate"), ("job_reset_lr", "reset_learning_rate"),
+                              ("job_save_checkpoint", "save_checkpoint_now"), ("job_graceful_stop", "graceful_stop")):
+            self.tools[alias] = self.tools[target]
+        self._job_tool("pretrain", "full-parameter pre-training job on token shards", ["model", "dataset"])
+        self._job_tool("rlkd", "GRPO with a distillation term from a teacher", ["model", "teacher", "dataset"])
+        self._job_tool("embed-train", "embedding fine-tuning job (InfoNCE / triplet / CoSENT)", ["model", "dataset"])
+        for kind in ("pretrain", "rlkd"):
+            self.tools[kind] = self.tools[f"start_{kind}"]
+        self.tools["embed_train"] = self.tools["start_embed-train"]
+
+        def start_cli_job(a):
+            argv = [str(x) for x in a["argv"]]
+            job = Job(argv[0] if argv else "cli", argv)
+            self.jobs[job.id] = job
+            return job.status()
+        arr = {"type": "array", "items": s}
+        self.tool("run_cli", "run any pmetal subcommand and return its output", {"argv": arr}, ["argv"],
+                  lambda a: self._cli_inline([str(x) for x in a["argv"]]))
+        self.tool("start_cli_job", "start any pmetal subcommand as a background job", {"argv": arr}, ["argv"], start_cli_job)
+        cli("search_models", "search the local model cache (online: the hub)", ["search"], {"query": s, "limit": i, "online": b},
+            [], ("query",))
+        cli("list_local_models", "models in the local cache", ["search"], {"limit": i}, [])
+        cli("download_model", "download a model from the hub", ["download"], {"model": s}, ["model"], ("model",))
+        cli("model_fit", "does a model fit this device, and at what speed", ["memory"], {"model": s, "seq_len": i,
+                                                                                      "batch_size": i, "quantization": s}, ["model"])
+
+        def model_info(a):
+            from .models.loader import resolve_model_path
+            path = resolve_model_path(a["model"])
+            cfg_path = os.path.join(path, "config.json")
+            if not os.path.exists(cfg_path):
+                return {"model": a["model"], "path": path, "config": None}
+            with open(cfg_path, "r", encoding="utf-8") as fh:
+                cfg = json.load(fh)
+            from .models.architectures import family_of
+            files = sorted(f for f in os.listdir(path) if f.endswith((".safetensors", ".gguf")))
+            keys = ("model_type", "architectures", "hidden_size", "num_hidden_layers", "num_attention_heads",
+                    "num_key_value_heads", "intermediate_size", "vocab_size", "max_position_embeddings", "num_experts",
+                    "num_local_experts", "torch_dtype")
+            return {"model": a["model"], "path": path, "family": family_of(cfg), "weight_files": files,
+                    "bytes": sum(os.path.getsize(os.path.join(path, f)) for f in files),
+                    "config": {k: cfg[k] for k in keys if k in cfg}}
+        self.tool("model_info", "architecture, sizes and weight files of a local model", {"model": s}, ["model"], model_info)
+
+        def chat(a):
+            argv = ["infer", "--json", "--chat", "-m", a["model"], "-p", a["message"]]
+            if a.get("system"):
+                argv += ["--system", a["system"]]
+            rest = {k: v for k, v in a.items() if k not in ("model", "message", "system")}
+            return self._cli_inline(argv + _args_to_argv(rest))
+        self.tool("chat", "one chat turn through the model's chat template",
+                  {"model": s, "message": s, "system": s, "max_tokens": i, "lora": s}, ["model", "message"], chat)
+        # ---- dataset actions
+        io = {"input": s, "output": s}
+        cli("dataset_preview", "first samples of a dataset file", ["dataset", "preview"], {"dataset_id": s, "num": i},
+            ["dataset_id"], ("dataset_id",))
+        cli("dataset_validate", "check a JSONL dataset for training", ["dataset", "validate"],
+            {"path": s, "model": s, "max_seq_len": i}, ["path"], ("path",))
+        cli("dataset_download", "download a dataset from the hub", ["dataset", "download"], {"dataset_id": s, "split": s,
+                                                                                            "output": s}, ["dataset_id"], ("dataset_id",))
+        cli("dataset_convert", "convert a dataset to training JSONL", ["dataset", "convert"],
+            {"path": s, "output": s, "to": s, "columns": s, "shuffle": b}, ["path", "output"], ("path",))
+        cli("dataset_filter", "filter by token count, pattern, duplicates, completeness", ["dataset", "filter"],
+            {**io, "model": s, "min_tokens": i, "max_tokens": i, "dedup": b, "pattern": s, "invert": b, "complete_only": b},
+            ["input", "output"])
+        cli("dataset_split", "train / validation / test split", ["dataset", "split"],
+            {"input": s, "output_dir": s, "val_ratio": {"type": "number"}, "test_ratio": {"type": "number"}, "seed": i,
+             "stratify": s}, ["input", "output_dir"])
+
+        def dataset_merge(a):
+            argv = ["dataset", "merge", "-i"] + [str(x) for x in a["inputs"]]
+            return self._cli_inline(argv + _args_to_argv({k: v for k, v in a.items() if k != "inputs"}))
+        self.tool("dataset_merge", "merge several datasets", {"inputs": arr, "output": s, "shuffle": b, "interleave": b,
+                                                             "weights": s, "seed": i}, ["inputs", "output"], dataset_merge)
+        cli("dataset_sample", "random sample of a dataset", ["dataset", "sample"], {**io, "num": i, "seed": i},
+            ["input", "output", "num"])
+        cli("dataset_template", "apply a chat template", ["dataset", "template"],
+            {**io, "template": s, "system": s, "model": s, "add_generation_prompt": b, "mask_prompt": b}, ["input", "output"])
+        cli("dataset_prepare", "template + de-duplicate + length filter + split", ["dataset", "prepare"],
+            {"dataset": s, "output_dir": s, "model": s, "template": s, "max_seq_len": i, "val_ratio": {"type": "number"},
+             "columns": s}, ["dataset", "output_dir", "model"], ("dataset",))
+        # ---- benchmarks, packaging
+        cli("benchmark", "kernel corpus benchmark", ["bench", "corpus"], {"iters": i, "device": s}, [])
+        cli("bench_corpus", "kernel corpus benchmark", ["bench", "corpus"], {"iters": i, "device": s}, [])
+        cli("bench_train", "training-step workload benchmark", ["bench", "workload"], {"model": s, "iters": i}, [])
+        cli("bench_gen", "generation benchmark", ["bench", "gen"], {"model": s, "iters": i}, [])
+        cli("pack_experts", "write one file per MoE expert layer", ["pack-experts"], {"model": s, "output": s}, ["model", "output"])
+        cli("dflash", "speculative decoding with a block-diffusion draft", ["dflash"], {"model": s, "draft": s, "prompt": s},
+            ["model", "draft", "prompt"])
+        cli("ollama_modelfile", "write an Ollama Modelfile", ["ollama", "modelfile"], {"gguf": s, "output": s, "template": s,
+                                                                                   "system": s}, ["gguf"])
+        cli("ollama_create", "write a Modelfile and print the ollama create command", ["ollama", "create"],
+            {"name": s, "gguf": s, "output": s, "template": s, "system": s, "lora": s}, ["name", "gguf"])
 
     # ---------------------------------------------------------------- JSON-RPC
     def handle(self, msg: dict) -> Optional[dict]:

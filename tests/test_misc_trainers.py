@@ -108,6 +108,24 @@ def test_mcp_protocol(tmp_path):
     assert json.load(open(tmp_path / ".lr_control.json")) == {"command": "set_lr", "lr": 1e-5}
     assert by_id[4]["result"]["isError"] is True and by_id[5]["result"]["isError"] is True
     assert by_id[6]["error"]["code"] == -32601 and by_id[None]["error"]["code"] == -32700
+    # the reference server's tool names are all present, and the dataset tools run through the command line
+    reference_names = {"device_info", "search_models", "download_model", "list_local_models", "model_fit", "memory",
+                       "generate", "train", "pretrain", "distill", "grpo", "rlkd", "embed_train", "list_jobs", "job_status",
+                       "job_logs", "stop_job", "run_cli", "start_cli_job", "dataset_analyze", "dataset_preview",
+                       "dataset_validate", "dataset_download", "dataset_convert", "dataset_filter", "dataset_split",
+                       "dataset_merge", "dataset_sample", "dataset_template", "dataset_prepare", "quantize", "fuse_lora",
+                       "merge_models", "pack_experts", "eval_perplexity", "benchmark", "bench_train", "bench_gen",
+                       "bench_corpus", "start_serve", "tokenize", "dflash", "ollama_create", "ollama_modelfile",
+                       "job_set_lr", "job_reduce_lr", "job_reset_lr", "job_save_checkpoint", "job_graceful_stop",
+                       "model_info", "chat"}
+    assert reference_names <= names
+    src = tmp_path / "d.jsonl"
+    src.write_text("".join(json.dumps({"text": f"t{i}"}) + "\n" for i in range(10)))
+    call = lambda name, args: srv.tools[name]["fn"](args)
+    assert call("dataset_sample", {"input": str(src), "output": str(tmp_path / "o.jsonl"), "num": 3}) == {"sampled": 3}
+    assert call("dataset_validate", {"path": str(src)})["valid"] == 10
+    assert call("dataset_merge", {"inputs": [str(src), str(src)], "output": str(tmp_path / "m.jsonl")})["merged"] == 20
+    assert "chatml" in call("run_cli", {"argv": ["dataset", "formats"]})["templates"]
 
 
 def test_python_api_generate(tmp_path):
