@@ -374,8 +374,114 @@ def _infer_args(sp):
     p.add_argument("--kv-blocks", type=int, default=4096)
     p.add_argument("--device")
     p.add_argument("--json", action="store_true")
+    p.add_argument("--tools", help="JSON file with tool (function) definitions passed to the chat template")
+    p.add_argument("--benchmark", action="store_true", help="time prefill and decode on a synthetic prompt")
+    p.add_argument("--benchmark-iters", type=int, default=3)
+    p.add_argument("--benchmark-prompt-tokens", type=int, default=512)
+    p.add_argument("--backend", default="auto", choices=["auto", "standard", "compiled", "minimal", "dflash", "metal-sampler", "ane"],
+                   help="auto / compiled: CUDA-graph decode; standard / minimal: eager launches")
+    p.add_argument("--compiled", action="store_true", help="same as --backend compiled")
+    p.add_argument("--detect-repetition", action="store_true", help="cut the output where it starts to loop")
+    p.add_argument("--profile-layers", action="store_true", help="per-layer device timing of one forward pass")
+    p.add_argument("--profile-output", help="write the --profile-layers table to this JSON file")
+    _add_kv_quant_flags(p)
     _add_sampling_flags(p)
     return p
+
+
+def _add_kv_quant_flags(p):
+    """The reference compresses the KV cache to fit unified memory (crates/pmetal/src/cli/infer.rs); the paged cache here
+    stays bf16 (the attention kernels read bf16 blocks), so the flags are accepted and reported as not applied.
+    Quantised caches exist for the portable models (``GenericDecoderLM.new_cache(kv_bits=...)``) and as a library
+    (``models/turboquant.py``)."""
+    p.add_argument("--kv-quant", action="store_true")
+    p.add_argument("--no-kv-quant", action="store_true")
+    p.add_argument("--kv-group-size", type=int, default=64)
+    p.add_argument("--kv-k-bits", type=int)
+    p.add_argument("--kv-v-bits", type=int)
+    p.add_argument("--kv-qjl", action="store_true")
+    p.add_argument("--kv-turboquant", action="store_true")
+    p.add_argument("--kv-turboquant-preset")
+    p.add_argument("--kv-quant-preset")
+
+
+def _note_kv_flags(a) -> None:
+    if any(getattr(a, k, None) for k in ("kv_quant", "kv_turboquant", "kv_k_bits", "kv_v_bits", "kv_qjl",
+                                         "kv_turboquant_preset", "kv_quant_preset")):
+        print("note: KV-cache quantisation flags are not applied: the paged cache stays bf16", file=sys.stderr)
+
+
+def cut_repetition(tokens, min_period: int = 1, max_period: int = 64, min_repeats: int = 4, min_span: int = 24):
+    """Index at which ``tokens`` starts to loop, or None: the tail consists of one block of ``period`` tokens repeated
+    at least ``min_repeats`` times over at least ``min_span`` tokens. The first copy of the block is kept."""
+    n = len(tokens)
+    for period in range(min_period, min(max_period, n // min_repeats) + 1):
+        reps = 1
+        while (reps + 1) * period <= n and tokens[n - (reps + 1) * period:n - reps * period] == tokens[n - period:]:
+            reps += 1
+        if reps >= min_repeats and reps * period >= min_span:
+            return n - (reps - 1) * period
+    return None
+
+
+def _infer_benchmark(a, model, gen, sp_, eos) -> int:
+    import torch
+    g = torch.Generator().manual_seed(0)
+    vocab = model.cfg.vocab_size
+    rows = []
+    for it in range(a.benchmark_iters + 1):                      # the first pass warms up (graph capture, caches)
+        prompt = torch.randint(0, vocab, (a.benchmark_prompt_tokens,), generator=g).tolist()
+        res = gen.generate([prompt], sp_, ())                     # no stop tokens: always max_tokens new tokens
+        if it:
+            rows.append((res.prefill_tok_per_s, res.decode_tok_per_s))
+    pre = sorted(r[0] for r in rows)[len(rows) // 2]
+    dec = sorted(r[1] for r in rows)[len(rows) // 2]
+    print(json.dumps({"benchmark": "infer", "prompt_tokens": a.benchmark_prompt_tokens, "new_tokens": a.max_tokens,
+                      "iters": a.benchmark_iters, "prefill_tok_per_s": round(pre, 1), "decode_tok_per_s": round(dec, 1),
+                      "decode_ms_per_token": round(1e3 / dec, 3) if dec else None, "backend": a.backend}))
+    return 0
+
+
+def _infer_profile_layers(a, model, ids) -> int:
+    """Device time of every decoder layer for one forward pass over the prompt (CUDA events; wall clock on CPU)."""
+    import time
+
+    import torch
+    dev = next(model.parameters()).device
+    cuda = dev.type == "cuda"
+    marks = []
+
+    def stamp():
+        if cuda:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            return e
+        return time.perf_counter()
+    hooks = []
+    for i, layer in enumerate(model.layers):
+        hooks.append(layer.register_forward_pre_hook(lambda m, x, i=i: marks.append((i, "start", stamp()))))
+        hooks.append(layer.register_forward_hook(lambda m, x, y, i=i: marks.append((i, "end", stamp()))))
+    t = torch.tensor(ids, dtype=torch.int64, device=dev)
+    with torch.no_grad():
+        for rep in range(2):                                       # the second pass is the measured one
+            marks.clear()
+            model(t)
+    if cuda:
+        torch.cuda.synchronize()
+    for h in hooks:
+        h.remove()
+    start = {i: m for i, k, m in marks if k == "start"}
+    table = []
+    for i, k, m in marks:
+        if k == "end":
+            ms = start[i].elapsed_time(m) if cuda else (m - start[i]) * 1e3
+            table.append({"layer": i, "ms": round(ms, 4)})
+    rep = {"tokens": len(ids), "total_ms": round(sum(r["ms"] for r in table), 4), "layers": table}
+    if a.profile_output:
+        with open(a.profile_output, "w", encoding="utf-8") as fh:
+            json.dump(rep, fh, indent=2)
+    print(json.dumps(rep if a.json else {k: rep[k] for k in ("tokens", "total_ms")}))
+    return 0
 
 
 @_command(_infer_args)
@@ -384,12 +490,19 @@ def cmd_infer(a) -> int:
     from ..data.stream_format import StreamFormatter
     from ..models.generation import Generator
     model, tok, tpl, eos, mdir = _load_for_inference(a)
-    if a.chat or a.system:
+    _note_kv_flags(a)
+    tools = None
+    if a.tools:
+        with open(a.tools, "r", encoding="utf-8") as fh:
+            tools = json.load(fh)
+    if a.chat or a.system or tools:
         msgs = ([Message("system", a.system)] if a.system else []) + [Message("user", a.prompt)]
-        ids = tok.encode_with_special_tokens(tpl.apply_inference(msgs, a.no_thinking))
+        ids = tok.encode_with_special_tokens(tpl.apply_inference(msgs, a.no_thinking, tools))
     else:
         ids = tok.encode(a.prompt)
     sp_ = _sampling_from_args(a, mdir, tpl.template_type, thinking=bool(a.chat or a.system) and not a.no_thinking)
+    if a.profile_layers:
+        return _infer_profile_layers(a, model, ids)
     if a.draft_model:
         from ..models.loader import load_pretrained
         from ..models.speculative import SpeculativeConfig, SpeculativeDecoder
@@ -404,7 +517,10 @@ def cmd_infer(a) -> int:
                 "tokens_per_round": sg.stats.tokens_per_round}
         print(json.dumps(info) if a.json else text)
         return 0
-    gen = Generator(model, num_blocks=a.kv_blocks)
+    graphs = None if a.backend == "auto" and not a.compiled else (a.compiled or a.backend == "compiled")
+    gen = Generator(model, num_blocks=a.kv_blocks, cuda_graphs=graphs)
+    if a.benchmark:
+        return _infer_benchmark(a, model, gen, sp_, eos)
     if a.stream and not a.json:
         dec = StreamFormatter(tok, show_thinking=not a.hide_thinking)
         for t in gen.stream(ids, sp_, eos):
@@ -414,6 +530,11 @@ def cmd_infer(a) -> int:
         sys.stdout.write("\n")
         return 0
     res = gen.generate([ids], sp_, eos)
+    if a.detect_repetition:
+        cut = cut_repetition(res.tokens[0])
+        if cut is not None:
+            res.tokens[0] = res.tokens[0][:cut]
+            res.finish_reasons[0] = "repetition"
     text = tok.decode([t for t in res.tokens[0] if t not in eos])
     if a.json:
         print(json.dumps({"text": text, "prompt_tokens": res.prompt_tokens, "generated_tokens": res.generated_tokens,
@@ -431,18 +552,31 @@ def _serve_args(sp):
     p.add_argument("-l", "--lora")
     p.add_argument("--host", default="127.0.0.1")
     p.add_argument("--port", type=int, default=8080)
-    p.add_argument("--max-slots", type=int, default=64)
-    p.add_argument("--kv-blocks", type=int, default=8192)
+    p.add_argument("--max-slots", "--cb-max-slots", dest="max_slots", type=int, default=64)
+    p.add_argument("--kv-blocks", "--cb-max-blocks", dest="kv_blocks", type=int, default=8192)
+    p.add_argument("--cb-block-size", type=int, default=64, help="KV block size; the attention kernels use 64")
+    p.add_argument("--cb-max-queue-depth", type=int, default=1024, help="requests waiting for a slot before new ones are refused")
+    p.add_argument("--continuous-batch", action="store_true", help="always on (accepted for compatibility)")
+    p.add_argument("--max-seq-len", type=int, default=None, help="sizes the KV pool: slots x ceil(len / 64) blocks")
     p.add_argument("--fp8", action="store_true")
     p.add_argument("--device")
+    _add_kv_quant_flags(p)
     return p
 
 
 @_command(_serve_args)
 def cmd_serve(a) -> int:
     from ..serve.server import serve
+    if a.cb_block_size != 64:
+        print("error: the paged attention kernels use 64-token blocks (--cb-block-size 64)", file=sys.stderr)
+        return 2
     model, tok, tpl, eos, mdir = _load_for_inference(a)
-    serve(model, tok, tpl, a.host, a.port, eos, os.path.basename(os.path.normpath(mdir or a.model)), a.max_slots, a.kv_blocks)
+    _note_kv_flags(a)
+    blocks = a.kv_blocks
+    if a.max_seq_len:
+        blocks = max(blocks, a.max_slots * (-(-a.max_seq_len // 64) + 1))
+    serve(model, tok, tpl, a.host, a.port, eos, os.path.basename(os.path.normpath(mdir or a.model)), a.max_slots, blocks,
+          a.cb_max_queue_depth)
     return 0
 
 
@@ -509,6 +643,10 @@ def _quantize_args(sp):
     p.add_argument("--format", default="gguf", choices=["gguf", "fp8", "mlx"],
                    help="mlx: affine group quantisation with quality-driven bit allocation (--target-bpw, default 4.5)")
     p.add_argument("--group-size", type=int, default=64)
+    p.add_argument("--bits", type=int, choices=[3, 4, 5, 6, 8], help="--format mlx: default bit width (sets the "
+                   "bits-per-weight target when --target-bpw is not given)")
+    p.add_argument("--kl-threshold", type=float, default=0.01, help="dynamic: quality-loss budget of the calibration")
+    p.add_argument("--lora", help="fuse this LoRA adapter into the model before quantising")
     return p
 
 
@@ -516,17 +654,36 @@ def _quantize_args(sp):
 def cmd_quantize(a) -> int:
     from ..models.loader import resolve_model_path
     mdir = resolve_model_path(a.model)
+    fused_tmp = None
+    if a.lora:
+        import tempfile
+
+        from ..merge.merge import merge_lora_into_base
+        fused_tmp = tempfile.TemporaryDirectory(prefix="pmetal-fused-")
+        merge_lora_into_base(mdir, a.lora, fused_tmp.name, "bfloat16")
+        mdir = fused_tmp.name
+    try:
+        return _quantize_dir(a, mdir)
+    finally:
+        if fused_tmp is not None:
+            fused_tmp.cleanup()
+
+
+def _quantize_dir(a, mdir: str) -> int:
     if a.format == "fp8":
         from ..models.fp8 import export_fp8_checkpoint
         print(json.dumps(export_fp8_checkpoint(mdir, a.output)))
         return 0
     if a.format == "mlx":
         from ..quant.mlx_affine import quantize_model as quantize_mlx
-        print(json.dumps(quantize_mlx(mdir, a.output, a.target_bpw or 4.5, a.group_size)))
+        # per-weight cost of b-bit groups: b bits + one fp16 scale and bias per group
+        bpw = a.target_bpw or ((a.bits + 32.0 / a.group_size) if a.bits else 4.5)
+        print(json.dumps(quantize_mlx(mdir, a.output, bpw, a.group_size)))
         return 0
     from ..gguf.convert import quantize_model
     from ..gguf.recipe import DynamicConfig
-    dyn = DynamicConfig(kl_calibrate=a.kl_calibrate, target_bpw=a.target_bpw) if a.method == "dynamic" else None
+    dyn = DynamicConfig(kl_calibrate=a.kl_calibrate, target_bpw=a.target_bpw, error_budget=a.kl_threshold) \
+        if a.method == "dynamic" else None
     print(json.dumps(quantize_model(mdir, a.output, a.method, a.imatrix, dyn, a.threads)))
     return 0
 

@@ -132,3 +132,49 @@ def test_new_subcommands(tmp_path, capsys):
     assert main(["dflash", "-m", "random:tiny-qwen3", "--draft", "random", "--max-tokens", "12", "--device", "cpu"]) == 0
     res = json.loads(capsys.readouterr().out)
     assert len(res["tokens"]) == 12 and res["avg_acceptance_length"] >= 1
+
+
+def test_infer_benchmark_profile_tools_and_repetition(model_dir, capsys, tmp_path):
+    from pmetal_b200.cli.commands import cut_repetition
+    assert cut_repetition(list(range(30))) is None
+    assert cut_repetition([1, 2, 3] + [7] * 30) == 4                               # one copy of the repeated token stays
+    assert cut_repetition([9, 9] + [4, 5, 6] * 10) == 5 and cut_repetition([4, 5, 6] * 3) is None
+    assert main(["infer", "-m", model_dir, "-p", "x", "--max-tokens", "4", "--greedy", "--benchmark", "--benchmark-iters", "1",
+                 "--benchmark-prompt-tokens", "16", "--device", "cpu"]) == 0
+    b = _json_out(capsys)
+    assert b["prompt_tokens"] == 16 and b["new_tokens"] == 4 and b["decode_tok_per_s"] > 0 and b["prefill_tok_per_s"] > 0
+    prof = tmp_path / "layers.json"
+    assert main(["infer", "-m", model_dir, "-p", "hello world", "--profile-layers", "--profile-output", str(prof),
+                 "--device", "cpu"]) == 0
+    rep = json.load(open(prof))
+    assert [r["layer"] for r in rep["layers"]] == [0, 1] and rep["total_ms"] > 0
+    tools = tmp_path / "tools.json"
+    tools.write_text(json.dumps([{"type": "function", "function": {"name": "get_time", "description": "now", "parameters": {}}}]))
+    assert main(["infer", "-m", model_dir, "-p", "time?", "--tools", str(tools), "--max-tokens", "2", "--greedy", "--json",
+                 "--backend", "standard", "--kv-quant", "--detect-repetition", "--device", "cpu"]) == 0
+    out = capsys.readouterr()
+    assert "not applied" in out.err and json.loads(out.out.strip().splitlines()[-1])["prompt_tokens"] > 20   # the tool block is in the prompt
+
+
+def test_quantize_with_adapter_and_bits(model_dir, capsys, tmp_path):
+    from pmetal_b200.lora import apply_lora
+    from pmetal_b200.core.config import LoraConfig
+    from pmetal_b200.lora.adapter import save_adapter
+    from pmetal_b200.models.loader import load_pretrained
+    m, _, _ = load_pretrained(model_dir, dtype=torch.float32)
+    cfg = LoraConfig(r=4, alpha=8.0)
+    apply_lora(m, cfg)
+    for n, p in m.named_parameters():
+        if "lora_b" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    ad = str(tmp_path / "adapter")
+    save_adapter(m, ad, cfg)
+    assert main(["quantize", "-m", model_dir, "-o", str(tmp_path / "q.gguf"), "--method", "q8_0", "--lora", ad]) == 0
+    a = _json_out(capsys)
+    assert main(["quantize", "-m", model_dir, "-o", str(tmp_path / "p.gguf"), "--method", "q8_0"]) == 0
+    b = _json_out(capsys)
+    assert a["tensors"] == b["tensors"]
+    assert open(tmp_path / "q.gguf", "rb").read() != open(tmp_path / "p.gguf", "rb").read()      # the adapter changed the weights
+    assert main(["quantize", "-m", model_dir, "-o", str(tmp_path / "mlx"), "--format", "mlx", "--bits", "6"]) == 0
+    r = _json_out(capsys)
+    assert 5.0 < r["effective_bpw"] < 8.5
