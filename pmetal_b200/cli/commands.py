@@ -721,8 +721,22 @@ def _distill_args(sp):
     p.add_argument("--learning-rate", type=float, default=2e-5)
     p.add_argument("--max-steps", type=int, default=100)
     p.add_argument("--max-seq-len", type=int, default=1024)
-    p.add_argument("--cache-dir")
+    p.add_argument("--cache-dir", "--offline-cache", dest="cache_dir")
+    p.add_argument("--offline", action="store_true", help="same as --method offline: train against cached teacher logits")
+    p.add_argument("--offline-generate", action="store_true", help="build the teacher logit cache and stop")
+    p.add_argument("--offline-compression", default="topk", choices=["full", "topk", "int8", "int4", "int8_per_token"])
+    p.add_argument("--offline-top-k", type=int, default=64)
+    p.add_argument("--rationale", action="store_true", help="entropy-weighted KL that stresses reasoning tokens")
+    p.add_argument("--rationale-weight", type=float, default=1.0)
+    p.add_argument("--epochs", type=int, default=None, help="passes over the dataset (overrides --max-steps)")
+    p.add_argument("--batch-size", type=int, default=1, help="sequences per optimiser step are packed one at a time")
+    p.add_argument("--eval-dataset", help="report the distillation loss on this dataset at the end")
+    p.add_argument("--checkpoint-every", type=int, default=0)
+    p.add_argument("--resume", action="store_true", help="continue a LoRA run from the newest checkpoint in the output directory")
+    p.add_argument("--log-metrics")
+    p.add_argument("--seed", type=int, default=42)
     p.add_argument("--lora-r", type=int, default=0, help="train a LoRA adapter on the student instead of all weights")
+    p.add_argument("--lora-alpha", type=float, default=None)
     p.add_argument("--device")
     return p
 
@@ -743,33 +757,90 @@ def cmd_distill(a) -> int:
     if a.lora_r > 0:
         from ..core.config import LoraConfig
         from ..lora import apply_lora
-        apply_lora(student, LoraConfig(r=a.lora_r, alpha=2.0 * a.lora_r))
+        apply_lora(student, LoraConfig(r=a.lora_r, alpha=a.lora_alpha or 2.0 * a.lora_r))
         student.to(dev)
     else:
         for p in student.parameters():
             p.requires_grad_(True)
     student.train()
     seqs = [s[: a.max_seq_len] for s in _read_prompts(a.dataset, tok) if len(s) > 1]
-    cfg = DistillConfig(method=a.method, loss_type=a.loss_type, alpha=a.alpha, temperature=a.temperature,
-                        learning_rate=a.learning_rate, total_steps=a.max_steps, cache_dir=a.cache_dir)
+    if not seqs:
+        print("error: no usable sequences in dataset", file=sys.stderr)
+        return 2
+    method = "offline" if (a.offline or a.offline_generate) else a.method
+    steps = a.epochs * len(seqs) if a.epochs else a.max_steps
+    markers = None
+    if a.rationale:
+        ids = [tok.token_to_id(t) for t in ("<think>", "</think>")]
+        markers = tuple(ids) if all(i is not None for i in ids) else None
+    cache_ready = bool(a.cache_dir) and os.path.exists(os.path.join(a.cache_dir, "metadata.json"))
+    cfg = DistillConfig(method=method, loss_type=a.loss_type, alpha=a.alpha, temperature=a.temperature,
+                        learning_rate=a.learning_rate, total_steps=steps, cache_dir=a.cache_dir if cache_ready else None,
+                        rationale=a.rationale, rationale_weight=a.rationale_weight, reasoning_markers=markers)
     tr = DistillTrainer(student, teacher, cfg)
-    if a.method == "offline" and a.cache_dir and not os.path.exists(os.path.join(a.cache_dir, "metadata.json")):
-        tr.cache = tr.build_cache(seqs, a.cache_dir)
-    last = {}
-    for step in range(a.max_steps):
-        i = step % len(seqs)
-        ids = torch.tensor(seqs[i], dtype=torch.int64)
-        last = tr.step(ids, ids.clone(), seq_id=i)
-        if step % 10 == 0:
-            print(json.dumps({"step": step, **{k: round(v, 5) for k, v in last.items()}}), file=sys.stderr)
-    os.makedirs(a.output, exist_ok=True)
+    if method == "offline":
+        if not a.cache_dir:
+            print("error: offline distillation needs --offline-cache", file=sys.stderr)
+            return 2
+        if not cache_ready:
+            tr.cache = tr.build_cache(seqs, a.cache_dir, a.offline_compression, a.offline_top_k)
+        if a.offline_generate:
+            print(json.dumps({"cache": a.cache_dir, "sequences": len(seqs), "compression": a.offline_compression}))
+            return 0
+    lcfg = None
     if a.lora_r > 0:
         from ..core.config import LoraConfig
+        lcfg = LoraConfig(r=a.lora_r, alpha=a.lora_alpha or 2.0 * a.lora_r)
+    ckpt_dir = os.path.join(a.output, "checkpoints")
+    first = 0
+    if a.resume and lcfg is not None and os.path.isdir(ckpt_dir):
+        from ..lora.adapter import load_adapter
+        done = sorted(int(d.split("_")[1]) for d in os.listdir(ckpt_dir) if d.startswith("step_") and d.split("_")[1].isdigit())
+        if done:
+            load_adapter(student, os.path.join(ckpt_dir, f"step_{done[-1]}"))
+            first = tr.step_count = done[-1]
+    import random
+    order = list(range(len(seqs)))
+    random.Random(a.seed).shuffle(order)
+    log = open(a.log_metrics, "a", encoding="utf-8") if a.log_metrics else None
+    last = {}
+    try:
+        for step in range(first, steps):
+            i = order[step % len(seqs)]
+            ids = torch.tensor(seqs[i], dtype=torch.int64)
+            last = tr.step(ids, ids.clone(), seq_id=i)
+            line = json.dumps({"step": step + 1, **{k: round(v, 5) for k, v in last.items()}})
+            if log:
+                log.write(line + "\n")
+                log.flush()
+            if step % 10 == 0:
+                print(line, file=sys.stderr)
+            if a.checkpoint_every and lcfg is not None and (step + 1) % a.checkpoint_every == 0:
+                from ..lora.adapter import save_adapter
+                save_adapter(student, os.path.join(ckpt_dir, f"step_{step + 1}"), lcfg, a.student)
+    finally:
+        if log:
+            log.close()
+    extra = {}
+    if a.eval_dataset:
+        ev = [s[: a.max_seq_len] for s in _read_prompts(a.eval_dataset, tok) if len(s) > 1]
+        tr.cache = None
+        tot = []
+        with torch.no_grad():
+            for s_ in ev:
+                ids = torch.tensor(s_, dtype=torch.int64)
+                with torch.enable_grad():
+                    loss, _ = tr.loss(ids.to(tr.device), ids.clone().to(tr.device))
+                tot.append(float(loss.detach()))
+        extra["eval_loss"] = round(sum(tot) / max(len(tot), 1), 5)
+        extra["eval_samples"] = len(ev)
+    os.makedirs(a.output, exist_ok=True)
+    if lcfg is not None:
         from ..lora.adapter import save_adapter
-        save_adapter(student, a.output, LoraConfig(r=a.lora_r, alpha=2.0 * a.lora_r), a.student)
+        save_adapter(student, a.output, lcfg, a.student)
     else:
         save_pretrained(student, a.output, copy_from=sdir)
-    print(json.dumps({"output": a.output, "steps": a.max_steps, **last}))
+    print(json.dumps({"output": a.output, "steps": steps, "resumed_from": first, **last, **extra}))
     return 0
 
 
@@ -784,10 +855,24 @@ def _grpo_args(sp):
     p.add_argument("--max-completion-length", type=int, default=512)
     p.add_argument("--max-prompt-length", type=int, default=512)
     p.add_argument("--learning-rate", type=float, default=1e-6)
-    p.add_argument("--max-steps", type=int, default=100)
+    p.add_argument("--max-steps", type=int, default=None, help="default: --epochs passes over the prompts")
+    p.add_argument("--epochs", type=int, default=1)
     p.add_argument("--prompts-per-step", type=int, default=1)
     p.add_argument("--lora-r", type=int, default=16)
+    p.add_argument("--lora-alpha", type=float, default=None)
+    p.add_argument("--seed", type=int, default=42)
+    p.add_argument("--prompt-column", help="dataset field that holds the prompt")
     p.add_argument("--reward", default="format", choices=["format", "length", "accuracy"])
+    p.add_argument("--reasoning-rewards", action="store_true", help="XML format reward + answer accuracy reward")
+    p.add_argument("--reward-model", help="add the score of this reward model (decoder + scalar head)")
+    p.add_argument("--reward-model-weight", type=float, default=1.0)
+    p.add_argument("--async-rewards", action="store_true", help="score completions on worker threads")
+    p.add_argument("--checkpoint-every", type=int, default=0, help="save the adapter every N steps under checkpoints/")
+    p.add_argument("--resume", action="store_true", help="continue from the newest checkpoint in the output directory")
+    p.add_argument("--log-metrics", help="append one JSON line per step to this file")
+    p.add_argument("--speculative", action="store_true",
+                   help="accepted for compatibility: rollouts are generated as one paged batch, which replaces per-stream drafting")
+    p.add_argument("--speculative-draft-tokens", type=int, default=4)
     p.add_argument("--teacher", help="with --rlkd-alpha: add a KD term against this teacher (RLKD)")
     p.add_argument("--rlkd-alpha", type=float, default=0.0)
     p.add_argument("--device")
@@ -803,13 +888,27 @@ def cmd_grpo(a) -> int:
     from ..trainer.rewards import make_reward
     model, tok, _, eos, _ = _load_for_inference(a)
     dev = str(model.embed_tokens.device)
-    lcfg = LoraConfig(r=a.lora_r, alpha=2.0 * a.lora_r)
+    lcfg = LoraConfig(r=a.lora_r, alpha=a.lora_alpha if getattr(a, 'lora_alpha', None) else 2.0 * a.lora_r)
     apply_lora(model, lcfg)
     model.to(dev).train()
     kw = dict(num_generations=a.num_generations, beta=a.beta, max_completion_length=a.max_completion_length,
               max_prompt_length=a.max_prompt_length, learning_rate=a.learning_rate)
     cfg = GrpoConfig.dapo(**kw) if a.dapo else GrpoConfig(**kw)
     reward = make_reward(a.reward, tok)
+    if a.reasoning_rewards:
+        from ..trainer.rewards import combined_reward
+        reward = combined_reward([make_reward("format", tok), make_reward("accuracy", tok, _read_targets(a.dataset))], [1.0, 1.0])
+    if a.reward_model:
+        from ..models.loader import load_pretrained, read_state_dict, resolve_model_path
+        from ..trainer.rewards import ModelReward, combined_reward
+        rm, _, rdir = load_pretrained(a.reward_model, dtype=next(model.parameters()).dtype, device=dev)
+        head = None
+        if rdir:
+            sd = read_state_dict(rdir)
+            head = next((sd[k].reshape(-1).to(dev) for k in ("score.weight", "v_head.weight", "reward_head.weight") if k in sd), None)
+        reward = combined_reward([reward, ModelReward(rm.eval(), head)], [1.0, a.reward_model_weight])
+    if a.async_rewards:
+        reward = _threaded_reward(reward)
     if a.teacher and a.rlkd_alpha > 0:
         from ..models.loader import load_pretrained
         from ..trainer.gspo import RlkdTrainer
@@ -817,19 +916,76 @@ def cmd_grpo(a) -> int:
         tr = RlkdTrainer(model, cfg, reward, teacher.eval(), a.rlkd_alpha, eos_ids=eos)
     else:
         tr = GrpoTrainer(model, cfg, reward, eos_ids=eos)
-    prompts = _read_prompts(a.dataset, tok)
+    keys = ((a.prompt_column,) if a.prompt_column else ()) + ("prompt", "question", "text", "instruction")
+    prompts = _read_prompts(a.dataset, tok, key_order=keys)
     if not prompts:
         print("error: no prompts in dataset", file=sys.stderr)
         return 2
-    for step in range(a.max_steps):
-        batch = [prompts[(step * a.prompts_per_step + j) % len(prompts)] for j in range(a.prompts_per_step)]
-        st = tr.step(batch)
-        d = st if isinstance(st, dict) else st.__dict__
-        print(json.dumps({"step": step, **{k: (round(v, 5) if isinstance(v, float) else v) for k, v in d.items()}}),
-              file=sys.stderr)
+    import random
+    random.Random(a.seed).shuffle(prompts)
+    steps = a.max_steps if a.max_steps is not None else a.epochs * (-(-len(prompts) // a.prompts_per_step))
+    ckpt_dir = os.path.join(a.output, "checkpoints")
+    first = 0
+    if a.resume and os.path.isdir(ckpt_dir):
+        from ..lora.adapter import load_adapter
+        done = sorted(int(d.split("_")[1]) for d in os.listdir(ckpt_dir) if d.startswith("step_") and d.split("_")[1].isdigit())
+        if done:
+            load_adapter(model, os.path.join(ckpt_dir, f"step_{done[-1]}"))
+            first = done[-1]
+    log = open(a.log_metrics, "a", encoding="utf-8") if a.log_metrics else None
+    try:
+        for step in range(first, steps):
+            batch = [prompts[(step * a.prompts_per_step + j) % len(prompts)] for j in range(a.prompts_per_step)]
+            st = tr.step(batch)
+            d = st if isinstance(st, dict) else st.__dict__
+            line = json.dumps({"step": step + 1, **{k: (round(v, 5) if isinstance(v, float) else v) for k, v in d.items()
+                                                    if isinstance(v, (int, float, str, bool))}})
+            print(line, file=sys.stderr)
+            if log:
+                log.write(line + "\n")
+                log.flush()
+            if a.checkpoint_every and (step + 1) % a.checkpoint_every == 0:
+                save_adapter(model, os.path.join(ckpt_dir, f"step_{step + 1}"), lcfg, a.model)
+    finally:
+        if log:
+            log.close()
     save_adapter(model, a.output, lcfg, a.model)
-    print(json.dumps({"output": a.output, "steps": a.max_steps}))
+    print(json.dumps({"output": a.output, "steps": steps, "resumed_from": first}))
     return 0
+
+
+def _read_targets(path: str):
+    """prompt text -> reference answer, from records that carry ``answer`` / ``target`` / ``solution``."""
+    out = {}
+    with open(path, "r", encoding="utf-8") as fh:
+        for line in fh:
+            try:
+                d = json.loads(line)
+            except ValueError:
+                continue
+            if not isinstance(d, dict):
+                continue
+            p = next((d[k] for k in ("prompt", "question", "text", "instruction") if isinstance(d.get(k), str)), None)
+            t = next((d[k] for k in ("answer", "target", "solution") if d.get(k) is not None), None)
+            if p is not None and t is not None:
+                out[p] = str(t)
+    return out
+
+
+def _threaded_reward(fn, workers: int = 4):
+    """Score slices of the completions on worker threads (reward functions that call tools or models spend their time
+    outside the interpreter lock)."""
+    from concurrent.futures import ThreadPoolExecutor
+    pool = ThreadPoolExecutor(max_workers=workers)
+
+    def wrapped(prompts, completions):
+        n = len(completions)
+        if n < 2 * workers:
+            return fn(prompts, completions)
+        cuts = [n * i // workers for i in range(workers + 1)]
+        parts = pool.map(lambda i: fn(prompts[cuts[i]:cuts[i + 1]], completions[cuts[i]:cuts[i + 1]]), range(workers))
+        return [x for part in parts for x in part]
+    return wrapped
 
 
 # ------------------------------------------------------------------------------------------- eval / bench / cluster
@@ -1107,10 +1263,24 @@ def _rlkd_args(sp):
     p.add_argument("--max-completion-length", type=int, default=512)
     p.add_argument("--max-prompt-length", type=int, default=512)
     p.add_argument("--learning-rate", type=float, default=1e-6)
-    p.add_argument("--max-steps", type=int, default=100)
+    p.add_argument("--max-steps", type=int, default=None, help="default: --epochs passes over the prompts")
+    p.add_argument("--epochs", type=int, default=1)
     p.add_argument("--prompts-per-step", type=int, default=1)
     p.add_argument("--lora-r", type=int, default=16)
+    p.add_argument("--lora-alpha", type=float, default=None)
+    p.add_argument("--seed", type=int, default=42)
+    p.add_argument("--prompt-column", help="dataset field that holds the prompt")
     p.add_argument("--reward", default="format", choices=["format", "length", "accuracy"])
+    p.add_argument("--reasoning-rewards", action="store_true", help="XML format reward + answer accuracy reward")
+    p.add_argument("--reward-model", help="add the score of this reward model (decoder + scalar head)")
+    p.add_argument("--reward-model-weight", type=float, default=1.0)
+    p.add_argument("--async-rewards", action="store_true", help="score completions on worker threads")
+    p.add_argument("--checkpoint-every", type=int, default=0, help="save the adapter every N steps under checkpoints/")
+    p.add_argument("--resume", action="store_true", help="continue from the newest checkpoint in the output directory")
+    p.add_argument("--log-metrics", help="append one JSON line per step to this file")
+    p.add_argument("--speculative", action="store_true",
+                   help="accepted for compatibility: rollouts are generated as one paged batch, which replaces per-stream drafting")
+    p.add_argument("--speculative-draft-tokens", type=int, default=4)
     p.add_argument("--device")
     return p
 

@@ -145,7 +145,33 @@ def attention_transfer(student_attn, teacher_attn):
     return ((student_attn.float().mean(1) - teacher_attn.float().mean(1)) ** 2).mean()
 
 
-LOSSES = {"kl": kl_divergence, "forward_kl": kl_divergence,
+def reasoning_mask(tokens: torch.Tensor, start_token: int, end_token: int) -> torch.Tensor:
+    """1.0 for tokens strictly inside a ``start_token … end_token`` span (the markers themselves count as outside the
+    span start and as its last position respectively: inclusive running counts of both markers are subtracted and
+    clamped, crates/pmetal-distill/src/reasoning.rs:235-256)."""
+    inside = (tokens == start_token).cumsum(-1) - (tokens == end_token).cumsum(-1)
+    return inside.clamp(0, 1).float()
+
+
+def rationale_kl(student, teacher, T: float = 2.0, mask=None, reasoning_weight: float = 1.0,
+                 token_weights: Optional[torch.Tensor] = None):
+    """Entropy-weighted forward KL (rationale-based distillation, crates/pmetal-distill/src/reasoning.rs:178-226): token i
+    gets weight ``1 + reasoning_weight * H_i / max_j H_j`` with H the teacher's entropy at temperature T, times optional
+    external weights (a reasoning-span mask, or a per-sample correctness signal for outcome supervision); the loss is
+    the weighted mean of the per-token KL. No T^2 factor, as in the reference."""
+    ls, lt = _lsm(student, T), _lsm(teacher, T)
+    pt = lt.exp()
+    kl = (pt * (lt - ls)).sum(-1)
+    ent = -(pt * lt).sum(-1)
+    w = 1.0 + reasoning_weight * ent / ent.max().clamp(min=1e-6)
+    if token_weights is not None:
+        w = w * token_weights.to(w.dtype)
+    if mask is not None:
+        w = w * mask.to(w.dtype)
+    return (kl * w).sum() / w.sum().clamp(min=1e-6)
+
+
+LOSSES = {"kl": kl_divergence, "forward_kl": kl_divergence, "rationale": rationale_kl,
           "reverse_kl": lambda s, t, T=2.0, mask=None: kl_divergence(s, t, T, mask, reverse=True),
           "js": jensen_shannon, "jsd": jensen_shannon, "skewed_jsd": skewed_jsd, "soft_ce": soft_cross_entropy,
           "tvd": total_variation, "hinge_ranking": hinge_ranking, "logistic_ranking": logistic_ranking, "gkd": gkd,

@@ -32,6 +32,9 @@ class DistillConfig:
     total_steps: int = 1000
     chunk: int = 2048
     cache_dir: Optional[str] = None
+    rationale: bool = False           # entropy-weighted KL that stresses the reasoning tokens
+    rationale_weight: float = 1.0
+    reasoning_markers: Optional[tuple] = None   # (start token id, end token id): only tokens inside the span count
 
 
 class DistillTrainer:
@@ -78,7 +81,13 @@ class DistillTrainer:
         else:
             ht = self._hidden(self.teacher, input_ids, False)[:-1]
             wt = self.teacher.head_weight()
-            if self.taid is not None:
+            if c.rationale:
+                tw = None
+                if c.reasoning_markers is not None:
+                    span = L.reasoning_mask(input_ids.reshape(-1), *c.reasoning_markers)[1:]
+                    tw = span if bool(span.any()) else None
+                soft = L.rationale_kl(hs.float() @ ws.float().t(), ht.float() @ wt.float().t(), T, mask, c.rationale_weight, tw)
+            elif self.taid is not None:
                 s_logits = (hs.float() @ ws.float().t()).unsqueeze(0)
                 t_logits = (ht.float() @ wt.float().t()).unsqueeze(0)
                 soft, a = self.taid.loss(t_logits, s_logits, self.step_count, c.total_steps, mask=mask.unsqueeze(0))

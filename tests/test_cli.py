@@ -178,3 +178,56 @@ def test_quantize_with_adapter_and_bits(model_dir, capsys, tmp_path):
     assert main(["quantize", "-m", model_dir, "-o", str(tmp_path / "mlx"), "--format", "mlx", "--bits", "6"]) == 0
     r = _json_out(capsys)
     assert 5.0 < r["effective_bpw"] < 8.5
+
+
+def test_grpo_epochs_checkpoints_resume_and_metrics(model_dir, capsys, tmp_path):
+    data = tmp_path / "p.jsonl"
+    data.write_text("".join(json.dumps({"question": f"what is {i}+1?", "answer": str(i + 1)}) + "\n" for i in range(3)))
+    out = str(tmp_path / "g")
+    common = ["grpo", "-m", model_dir, "-d", str(data), "-o", out, "--num-generations", "2", "--max-completion-length", "4",
+              "--prompt-column", "question", "--reasoning-rewards", "--async-rewards", "--device", "cpu"]
+    assert main(common + ["--epochs", "1", "--checkpoint-every", "2", "--log-metrics", str(tmp_path / "m.jsonl")]) == 0
+    j = _json_out(capsys)
+    assert j["steps"] == 3 and j["resumed_from"] == 0
+    assert os.path.isdir(os.path.join(out, "checkpoints", "step_2")) and not os.path.isdir(os.path.join(out, "checkpoints", "step_3"))
+    lines = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
+    assert [l["step"] for l in lines] == [1, 2, 3]
+    assert main(common + ["--max-steps", "4", "--resume"]) == 0
+    j = _json_out(capsys)
+    assert j["resumed_from"] == 2 and j["steps"] == 4
+
+
+def test_distill_offline_rationale_and_checkpoints(model_dir, capsys, tmp_path):
+    data = tmp_path / "d.jsonl"
+    data.write_text("".join(json.dumps({"prompt": f"question {i} about several things"}) + "\n" for i in range(3)))
+    cache = str(tmp_path / "cache")
+    base = ["distill", "--teacher", model_dir, "--student", model_dir, "-d", str(data), "--device", "cpu"]
+    assert main(base + ["--offline-generate", "--offline-cache", cache, "--offline-top-k", "16"]) == 0
+    assert _json_out(capsys)["sequences"] == 3 and os.path.exists(os.path.join(cache, "metadata.json"))
+    out = str(tmp_path / "o")
+    assert main(base + ["--offline", "--offline-cache", cache, "-o", out, "--epochs", "1", "--lora-r", "4",
+                        "--checkpoint-every", "2", "--log-metrics", str(tmp_path / "m.jsonl"), "--eval-dataset", str(data)]) == 0
+    j = _json_out(capsys)
+    assert j["steps"] == 3 and j["eval_samples"] == 3 and os.path.isdir(os.path.join(out, "checkpoints", "step_2"))
+    assert len(open(tmp_path / "m.jsonl").read().splitlines()) == 3
+    assert main(base + ["-o", out, "--max-steps", "4", "--lora-r", "4", "--resume", "--rationale", "--rationale-weight", "2.0"]) == 0
+    assert _json_out(capsys)["resumed_from"] == 2
+    assert main(base + ["--offline", "-o", out]) == 2                       # offline needs a cache directory
+
+
+def test_rationale_loss_weights_uncertain_tokens():
+    from pmetal_b200.distill import losses as L
+    torch.manual_seed(0)
+    s, t = torch.randn(6, 50), torch.randn(6, 50)
+    t[:3] *= 8                                                              # confident teacher rows: low entropy
+    plain = L.kl_divergence(s, t, 1.0) 
+    lt, ls = torch.log_softmax(t, -1), torch.log_softmax(s, -1)
+    kl = (lt.exp() * (lt - ls)).sum(-1)
+    ent = -(lt.exp() * lt).sum(-1)
+    w = 1 + 2.0 * ent / ent.max()
+    assert torch.allclose(L.rationale_kl(s, t, 1.0, None, 2.0), (kl * w).sum() / w.sum(), atol=1e-6)
+    assert torch.allclose(L.rationale_kl(s, t, 1.0, None, 0.0), plain, atol=1e-6)        # weight 0: the plain mean KL
+    toks = torch.tensor([5, 1, 7, 8, 2, 9])
+    assert L.reasoning_mask(toks, 1, 2).tolist() == [0, 1, 1, 1, 0, 0]
+    only = L.rationale_kl(s, t, 1.0, None, 0.0, L.reasoning_mask(toks, 1, 2))
+    assert torch.allclose(only, kl[1:4].mean(), atol=1e-6)
