@@ -74,22 +74,65 @@ def cmd_init(a) -> int:
 
 # ------------------------------------------------------------------------------------------- tokenize
 def _tokenize_args(sp):
-    p = sp.add_parser("tokenize", help="tokenise text with a model's tokenizer")
-    p.add_argument("-m", "--model", required=True)
+    p = sp.add_parser("tokenize", help="tokenise text, or turn a JSONL / text corpus into pre-training token shards")
+    p.add_argument("-m", "--model", "--tokenizer", dest="model", required=True)
     p.add_argument("text", nargs="?")
+    p.add_argument("--text", dest="text_flag")
     p.add_argument("--decode", default=None, help="comma separated ids to decode")
+    p.add_argument("-i", "--input", help="corpus file: JSONL (one document per line) or plain text (one document per line)")
+    p.add_argument("-o", "--output", help="directory for shard_NNNNN.bin / .idx files")
+    p.add_argument("--text-column", default="text")
+    p.add_argument("--docs-per-shard", type=int, default=10000)
     return p
 
 
 @_command(_tokenize_args)
 def cmd_tokenize(a) -> int:
-    from ..data.tokenizer import Tokenizer
+    from ..data.tokenizer import ByteTokenizer, Tokenizer
     from ..models.loader import resolve_model_path
-    tok = Tokenizer.from_model_dir(resolve_model_path(a.model))
+    path = resolve_model_path(a.model)
+    tok = ByteTokenizer() if path.startswith("random:") else Tokenizer.from_model_dir(path)
+    if a.input:
+        if not a.output:
+            print("error: --output is required with --input", file=sys.stderr)
+            return 2
+        from ..data.streaming import ShardWriter
+        os.makedirs(a.output, exist_ok=True)
+        shard = docs = tokens = in_shard = 0
+        writer = None
+        with open(a.input, "r", encoding="utf-8", errors="replace") as fh:
+            for line in fh:
+                line = line.rstrip("\n")
+                if not line.strip():
+                    continue
+                text = line
+                if line.lstrip().startswith("{"):
+                    try:
+                        rec = json.loads(line)
+                        text = rec.get(a.text_column) if isinstance(rec, dict) else None
+                    except ValueError:
+                        text = line
+                if not isinstance(text, str) or not text:
+                    continue
+                ids = tok.encode(text)
+                if tok.eos_token_id is not None:
+                    ids = list(ids) + [tok.eos_token_id]          # documents are separated by the end-of-sequence token
+                if writer is None:
+                    writer = ShardWriter(os.path.join(a.output, f"shard_{shard:05d}.bin"))
+                writer.add_document(ids)
+                docs, tokens, in_shard = docs + 1, tokens + len(ids), in_shard + 1
+                if in_shard >= a.docs_per_shard:
+                    writer.close()
+                    writer, shard, in_shard = None, shard + 1, 0
+        if writer is not None:
+            writer.close()
+            shard += 1
+        print(json.dumps({"shards": shard, "documents": docs, "tokens": tokens, "output": a.output}))
+        return 0
     if a.decode:
         print(tok.decode([int(x) for x in a.decode.split(",")]))
     else:
-        text = a.text if a.text is not None else sys.stdin.read()
+        text = a.text if a.text is not None else (a.text_flag if a.text_flag is not None else sys.stdin.read())
         ids = tok.encode_with_special_tokens(text)
         print(json.dumps({"ids": ids, "count": len(ids)}))
     return 0
@@ -1173,16 +1216,30 @@ def cmd_mcp(a) -> int:
 
 def _pretrain_args(sp):
     p = sp.add_parser("pretrain", help="full-parameter pre-training on token shards")
-    p.add_argument("-m", "--model", required=True, help="model directory or random:<preset> for a fresh model")
+    p.add_argument("-m", "--model", help="model directory or random:<preset> for a fresh model")
+    p.add_argument("--arch", help="preset name of a fresh model (same as --model random:<name>)")
+    p.add_argument("--model-config", help="config.json of a fresh model with random weights")
     p.add_argument("--shards", required=True, help="glob of *.bin token shards")
+    p.add_argument("--eval-shards", help="glob of held-out shards")
+    p.add_argument("--eval-every", type=int, default=0)
+    p.add_argument("--eval-batches", type=int, default=20)
     p.add_argument("-o", "--output", default="./pretrain-output")
     p.add_argument("--seq-len", type=int, default=2048)
-    p.add_argument("--micro-batch", type=int, default=4)
-    p.add_argument("--max-steps", type=int, default=100)
+    p.add_argument("--micro-batch", "--batch-size", dest="micro_batch", type=int, default=4)
+    p.add_argument("--gradient-accumulation-steps", type=int, default=1)
+    p.add_argument("--max-steps", "--steps", dest="max_steps", type=int, default=100)
     p.add_argument("--learning-rate", type=float, default=3e-4)
+    p.add_argument("--min-lr", type=float, default=3e-5)
+    p.add_argument("--lr-schedule", default="cosine")
     p.add_argument("--warmup-steps", type=int, default=10)
+    p.add_argument("--weight-decay", type=float, default=0.1)
+    p.add_argument("--max-grad-norm", type=float, default=1.0)
     p.add_argument("--z-loss", type=float, default=1e-4)
-    p.add_argument("--resume")
+    p.add_argument("--checkpoint-every", type=int, default=0)
+    p.add_argument("--log-every", type=int, default=1)
+    p.add_argument("--eos-token-id", type=int, default=None, help="recorded in the saved config of a fresh model")
+    p.add_argument("--seed", type=int, default=42)
+    p.add_argument("--resume", nargs="?", const="auto", help="checkpoint directory, or no value for the newest one under --output")
     p.add_argument("--device")
     return p
 
@@ -1195,16 +1252,45 @@ def cmd_pretrain(a) -> int:
     from ..models.loader import load_pretrained
     from ..trainer.pretrain import PretrainConfig, PretrainTrainer
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
-    model, _, _ = load_pretrained(a.model, dtype=torch.float32, device=dev)
-    cfg = PretrainConfig(learning_rate=a.learning_rate, warmup_steps=a.warmup_steps, max_steps=a.max_steps,
-                         z_loss_coef=a.z_loss, seq_len=a.seq_len, micro_batch=a.micro_batch, output=a.output)
+    torch.manual_seed(a.seed)
+    if a.model_config:
+        from ..models.config import ModelArgs
+        from ..models.decoder import DecoderLM
+        with open(a.model_config, "r", encoding="utf-8") as fh:
+            margs = ModelArgs.from_dict(json.load(fh))
+        model = DecoderLM(margs, dtype=torch.float32, device=dev).init_weights(0.02, a.seed)
+    else:
+        name = a.model or (f"random:{a.arch}" if a.arch else None)
+        if not name:
+            print("error: one of --model, --arch or --model-config is required", file=sys.stderr)
+            return 2
+        model, _, _ = load_pretrained(name, dtype=torch.float32, device=dev, seed=a.seed)
+    if a.eos_token_id is not None and hasattr(model.cfg, "eos_token_id"):
+        model.cfg.eos_token_id = a.eos_token_id
+    cfg = PretrainConfig(learning_rate=a.learning_rate, min_lr=a.min_lr, warmup_steps=a.warmup_steps, max_steps=a.max_steps,
+                         weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm, z_loss_coef=a.z_loss, seq_len=a.seq_len,
+                         micro_batch=a.micro_batch, gradient_accumulation_steps=a.gradient_accumulation_steps,
+                         lr_scheduler=a.lr_schedule, checkpoint_every=a.checkpoint_every, output=a.output)
     tr = PretrainTrainer(model.train(), cfg)
-    if a.resume:
-        tr.load_checkpoint(a.resume)
-    ds = TokenShardDataset(a.shards, a.seq_len, int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)))
-    last = tr.run(ds, on_step=lambda s: print(json.dumps(s), file=sys.stderr))
+    resume = a.resume
+    if resume == "auto":
+        done = sorted((int(d.split("_")[1]), d) for d in (os.listdir(a.output) if os.path.isdir(a.output) else [])
+                      if d.startswith("step_") and d.split("_")[1].isdigit())
+        resume = os.path.join(a.output, done[-1][1]) if done else None
+    if resume:
+        tr.load_checkpoint(resume)
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    ds = TokenShardDataset(a.shards, a.seq_len, rank, world)
+    ev = TokenShardDataset(a.eval_shards, a.seq_len, rank, world) if a.eval_shards else None
+
+    def on_step(st):
+        if st.get("step", 0) % max(a.log_every, 1) == 0 or "eval_loss" in st:
+            print(json.dumps(st), file=sys.stderr)
+    last = tr.run(ds, on_step=on_step, eval_dataset=ev, eval_every=a.eval_every, eval_batches=a.eval_batches)
+    if ev is not None and "eval_loss" not in last:
+        last = {**last, **tr.evaluate(ev, a.eval_batches)}
     tr.save_checkpoint(os.path.join(a.output, "final"))
-    print(json.dumps({"output": a.output, **last}))
+    print(json.dumps({"output": a.output, "resumed_from": resume, **last}))
     return 0
 
 

@@ -6,6 +6,7 @@ and a checkpoint holds model, optimiser state, step and data position so a run r
 from __future__ import annotations
 
 import json
+import math
 import os
 from dataclasses import asdict, dataclass
 from typing import Iterable, Optional
@@ -64,8 +65,63 @@ class PretrainTrainer:
         ids = torch.as_tensor(np.asarray(windows), dtype=torch.int64, device=self.device)
         return ids if ids.dim() == 2 else ids[None]
 
+    def _loss(self, ids):
+        """(cross entropy, z-loss or None) of a [B, L] batch; next-token targets inside each window."""
+        from ..ops import functional as ops
+        import contextlib
+        tgt = torch.full_like(ids, -100)
+        tgt[:, :-1] = ids[:, 1:]
+        amp = torch.autocast("cuda", dtype=torch.bfloat16) if self.device.type == "cuda" else contextlib.nullcontext()
+        with ops.force_reference(), amp:
+            h = self.model.forward_hidden(ids)
+            ce = ops.causal_lm_loss(h, self.model.head_weight(), tgt.reshape(-1), -100, None)
+            zl = z_loss(h, self.model.head_weight()) if self.cfg.z_loss_coef > 0 else None
+        return ce, zl
+
+    @torch.no_grad()
+    def evaluate(self, dataset: Iterable, max_batches: int = 20) -> dict:
+        """Mean cross entropy and perplexity over up to ``max_batches`` micro-batches of held-out windows."""
+        was_training = self.model.training
+        self.model.eval()
+        batch, losses = [], []
+        for window in dataset:
+            batch.append(window)
+            if len(batch) < self.cfg.micro_batch:
+                continue
+            losses.append(float(self._loss(self._batch(batch))[0]))
+            batch = []
+            if len(losses) >= max_batches:
+                break
+        if was_training:
+            self.model.train()
+        mean = sum(losses) / max(len(losses), 1)
+        return {"eval_loss": mean, "eval_perplexity": math.exp(min(mean, 50.0)), "eval_batches": len(losses)}
+
     def train_step(self, windows) -> dict:
+        """One optimiser step. ``windows`` holds ``micro_batch x gradient_accumulation_steps`` windows; every micro-batch
+        contributes ``1 / accumulation`` of the gradient."""
         c = self.cfg
+        acc = max(c.gradient_accumulation_steps, 1)
+        if acc > 1 and len(windows) > c.micro_batch:
+            self.opt.set_lr(self.sched.get_lr(self.step_count))
+            self.opt.zero_grad()
+            ce_sum, zl_sum, n_tok, parts = 0.0, 0.0, 0, [windows[i:i + c.micro_batch] for i in range(0, len(windows), c.micro_batch)]
+            for part in parts:
+                ids = self._batch(part)
+                ce, zl = self._loss(ids)
+                loss = ce + (c.z_loss_coef * zl if zl is not None else 0.0)
+                (loss / len(parts)).backward()
+                ce_sum += float(ce.detach()) / len(parts)
+                zl_sum += (float(zl.detach()) if zl is not None else 0.0) / len(parts)
+                n_tok += ids.numel()
+            if self.dist is not None and self.dist.world_size > 1:
+                gn = self.dist.reduce_and_step(self.opt, 1.0)
+            else:
+                gn = self.opt.step(1.0)
+            self.step_count += 1
+            self.tokens_seen += n_tok
+            return {"step": self.step_count, "loss": ce_sum, "z_loss": zl_sum, "grad_norm": float(gn), "lr": self.opt.lr,
+                    "tokens": self.tokens_seen}
         self.opt.set_lr(self.sched.get_lr(self.step_count))
         self.opt.zero_grad()
         ids = self._batch(windows)
@@ -95,15 +151,18 @@ class PretrainTrainer:
         return {"step": self.step_count, "loss": float(ce.detach()), "z_loss": float(zl.detach()) if zl is not None else 0.0,
                 "grad_norm": float(gn), "lr": self.opt.lr, "tokens": self.tokens_seen}
 
-    def run(self, dataset: Iterable, on_step=None) -> dict:
+    def run(self, dataset: Iterable, on_step=None, eval_dataset=None, eval_every: int = 0, eval_batches: int = 20) -> dict:
         c = self.cfg
         batch, last = [], {}
+        per_step = c.micro_batch * max(c.gradient_accumulation_steps, 1)
         for window in dataset:
             batch.append(window)
-            if len(batch) < c.micro_batch:
+            if len(batch) < per_step:
                 continue
             last = self.train_step(batch)
             batch = []
+            if eval_dataset is not None and eval_every and self.step_count % eval_every == 0:
+                last = {**last, **self.evaluate(eval_dataset, eval_batches)}
             if on_step:
                 on_step(last)
             if c.checkpoint_every and self.step_count % c.checkpoint_every == 0:

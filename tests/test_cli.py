@@ -231,3 +231,24 @@ def test_rationale_loss_weights_uncertain_tokens():
     assert L.reasoning_mask(toks, 1, 2).tolist() == [0, 1, 1, 1, 0, 0]
     only = L.rationale_kl(s, t, 1.0, None, 0.0, L.reasoning_mask(toks, 1, 2))
     assert torch.allclose(only, kl[1:4].mean(), atol=1e-6)
+
+
+def test_tokenize_shards_then_pretrain_with_eval_and_resume(tmp_path, capsys):
+    corpus = tmp_path / "c.jsonl"
+    corpus.write_text("".join(json.dumps({"body": "the quick brown fox jumps over the lazy dog " * 6}) + "\n" for _ in range(25)))
+    shards = str(tmp_path / "shards")
+    assert main(["tokenize", "--tokenizer", "random:tiny-qwen3", "-i", str(corpus), "-o", shards, "--text-column", "body",
+                 "--docs-per-shard", "10"]) == 0
+    j = _json_out(capsys)
+    assert j["shards"] == 3 and j["documents"] == 25 and sorted(os.listdir(shards))[0] == "shard_00000.bin"
+    assert main(["tokenize", "-m", "random:tiny-qwen3", "--text", "hi"]) == 0 and _json_out(capsys)["count"] == 2
+    out = str(tmp_path / "pt")
+    base = ["pretrain", "--arch", "tiny-qwen3", "--shards", shards + "/shard_0000[01].bin", "--eval-shards",
+            shards + "/shard_00002.bin", "-o", out, "--seq-len", "32", "--batch-size", "2", "--gradient-accumulation-steps", "2",
+            "--learning-rate", "1e-3", "--warmup-steps", "1", "--eval-batches", "2", "--log-every", "2", "--device", "cpu"]
+    assert main(base + ["--steps", "4", "--checkpoint-every", "2", "--eval-every", "2"]) == 0
+    a = _json_out(capsys)
+    assert a["step"] == 4 and a["eval_batches"] == 2 and a["tokens"] == 4 * 2 * 2 * 32 and os.path.isdir(os.path.join(out, "step_4"))
+    assert main(base + ["--steps", "6", "--resume"]) == 0
+    b = _json_out(capsys)
+    assert b["resumed_from"].endswith("step_4") and b["step"] == 6
