@@ -630,6 +630,11 @@ def _fuse_args(sp):
     p.add_argument("-l", "--lora", required=True)
     p.add_argument("-o", "--output", required=True)
     p.add_argument("--dtype", default="bfloat16")
+    p.add_argument("--alpha", type=float, help="LoRA alpha (default: from adapter_config.json)")
+    p.add_argument("--rank", type=int, help="LoRA rank (default: from adapter_config.json)")
+    p.add_argument("--accurate", action="store_true", help="float64 accumulation (the default)")
+    p.add_argument("--fast", action="store_true", help="float32 accumulation")
+    p.add_argument("--low-memory", action="store_true", help="merge 1024 output rows at a time")
     return p
 
 
@@ -637,7 +642,8 @@ def _fuse_args(sp):
 def cmd_fuse(a) -> int:
     from ..merge.merge import merge_lora_into_base
     from ..models.loader import resolve_model_path
-    print(json.dumps(merge_lora_into_base(resolve_model_path(a.model), a.lora, a.output, a.dtype)))
+    print(json.dumps(merge_lora_into_base(resolve_model_path(a.model), a.lora, a.output, a.dtype, a.alpha, a.rank,
+                                          not a.fast, a.low_memory)))
     return 0
 
 
@@ -645,6 +651,11 @@ def _merge_args(sp):
     p = sp.add_parser("merge", help="merge models (linear, slerp, ties, dare, della, ...) from a YAML recipe or flags")
     p.add_argument("-c", "--config")
     p.add_argument("--models", nargs="*")
+    p.add_argument("--model-a")
+    p.add_argument("--model-b")
+    p.add_argument("--t", type=float, default=None, help="slerp interpolation: 0 = model a, 1 = model b")
+    p.add_argument("--weight-a", type=float, default=None)
+    p.add_argument("--weight-b", type=float, default=None)
     p.add_argument("--base")
     p.add_argument("--method", default="linear")
     p.add_argument("--weights", nargs="*", type=float)
@@ -661,13 +672,19 @@ def cmd_merge(a) -> int:
     if a.config:
         cfg = MergeConfig.from_yaml(a.config)
     else:
+        if a.model_a and a.model_b and not a.models:          # two-model form: --model-a / --model-b [--t | --weight-a/-b]
+            a.models = [a.model_a, a.model_b]
+            if a.weights is None and (a.weight_a is not None or a.weight_b is not None):
+                a.weights = [a.weight_a if a.weight_a is not None else 0.5, a.weight_b if a.weight_b is not None else 0.5]
         if not a.models:
-            print("error: --config or --models is required", file=sys.stderr)
+            print("error: --config, --models or --model-a/--model-b is required", file=sys.stderr)
             return 2
         ws = a.weights or [1.0 / len(a.models)] * len(a.models)
-        cfg = MergeConfig.from_dict({"merge_method": a.method, "base_model": a.base, "dtype": a.dtype,
-                                     "models": [{"model": m, "parameters": {"weight": w, "density": a.density}}
-                                                for m, w in zip(a.models, ws)]})
+        d = {"merge_method": a.method, "base_model": a.base, "dtype": a.dtype,
+             "models": [{"model": m, "parameters": {"weight": w, "density": a.density}} for m, w in zip(a.models, ws)]}
+        if a.t is not None:
+            d["parameters"] = {"t": a.t}
+        cfg = MergeConfig.from_dict(d)
     cfg.output_path = a.output
     print(json.dumps(run_merge(cfg, a.device)))
     return 0
@@ -1037,8 +1054,9 @@ def _eval_args(sp):
     p.add_argument("-m", "--model", required=True)
     p.add_argument("-l", "--lora")
     p.add_argument("-d", "--dataset", required=True)
-    p.add_argument("--max-samples", type=int, default=200)
+    p.add_argument("--max-samples", "--num-samples", dest="max_samples", type=int, default=200)
     p.add_argument("--max-seq-len", type=int, default=2048)
+    p.add_argument("--json", action="store_true", help="the result is always one JSON line (accepted for compatibility)")
     p.add_argument("--device")
     return p
 
@@ -1301,8 +1319,17 @@ def _embed_args(sp):
     p.add_argument("-o", "--output", default="./embed-output")
     p.add_argument("--loss", default="infonce", choices=["infonce", "triplet", "cosent"])
     p.add_argument("--batch-size", type=int, default=8)
-    p.add_argument("--max-steps", type=int, default=100)
+    p.add_argument("--max-steps", type=int, default=None, help="default: --epochs passes over the dataset")
+    p.add_argument("--epochs", type=int, default=1)
     p.add_argument("--learning-rate", type=float, default=2e-5)
+    p.add_argument("--weight-decay", type=float, default=0.0)
+    p.add_argument("--temperature", type=float, default=0.05, help="InfoNCE temperature")
+    p.add_argument("--margin", type=float, default=0.5, help="triplet margin")
+    p.add_argument("--pooling", default="mean", choices=["mean", "last", "cls", "first"])
+    p.add_argument("--no-normalize", action="store_true", help="do not scale embeddings to unit length")
+    p.add_argument("--max-seq-len", type=int, default=512)
+    p.add_argument("--log-every", type=int, default=10)
+    p.add_argument("--seed", type=int, default=42)
     p.add_argument("--lora-r", type=int, default=16)
     p.add_argument("--device")
     return p
@@ -1324,15 +1351,23 @@ def cmd_embed_train(a) -> int:
         for line in fh:
             if line.strip():
                 rows.append(json.loads(line))
-    tr = EmbeddingTrainer(model, EmbeddingConfig(loss=a.loss, learning_rate=a.learning_rate))
+    import random
+    random.Random(a.seed).shuffle(rows)
+    pooling = {"cls": "first"}.get(a.pooling, a.pooling)
+    tr = EmbeddingTrainer(model, EmbeddingConfig(loss=a.loss, pooling=pooling, temperature=a.temperature, margin=a.margin,
+                                                 learning_rate=a.learning_rate, max_length=a.max_seq_len,
+                                                 weight_decay=a.weight_decay, normalize=not a.no_normalize))
+    steps = a.max_steps if a.max_steps is not None else a.epochs * (-(-len(rows) // a.batch_size))
     last = {}
-    for step in range(a.max_steps):
+    for step in range(steps):
         b = [rows[(step * a.batch_size + j) % len(rows)] for j in range(a.batch_size)]
         enc = lambda k: [tok.encode(r[k]) for r in b]        # noqa: E731
         last = tr.step(enc("anchor"), enc("positive"), enc("negative") if "negative" in b[0] else None,
                        [r.get("label", 1.0) for r in b] if a.loss == "cosent" else None)
+        if a.log_every and (step + 1) % a.log_every == 0:
+            print(json.dumps({"step": step + 1, **{k: round(v, 5) for k, v in last.items()}}), file=sys.stderr)
     save_adapter(model, a.output, lcfg, a.model)
-    print(json.dumps({"output": a.output, **last}))
+    print(json.dumps({"output": a.output, "steps": steps, **last}))
     return 0
 
 

@@ -226,13 +226,23 @@ def _write(cfg: MergeConfig, tensors: Dict[str, torch.Tensor], copy_from: Option
                     shutil.copy2(src, os.path.join(cfg.output_path, f))
 
 
-def merge_lora_into_base(base_dir: str, adapter_path: str, out_dir: str, dtype: str = "bfloat16") -> dict:
-    """W <- W + (alpha/r or alpha/sqrt(r)) * B A in float64, tensor by tensor (commands/fuse.rs:67-204).
+def merge_lora_into_base(base_dir: str, adapter_path: str, out_dir: str, dtype: str = "bfloat16",
+                         alpha: Optional[float] = None, rank: Optional[int] = None, accurate: bool = True,
+                         low_memory: bool = False) -> dict:
+    """W <- W + (alpha/r or alpha/sqrt(r)) * B A, tensor by tensor (commands/fuse.rs:67-204). ``accurate`` accumulates in
+    float64 (float32 otherwise); ``low_memory`` forms the product 1024 output rows at a time so the wide intermediate
+    never exists for the whole matrix. ``alpha`` / ``rank`` override the adapter's own values.
     Adapter key ``layers.N.<scope>.<proj>.lora_a`` maps to ``model.layers.N.<scope>.<proj>.weight``."""
+    import dataclasses
+
     from ..lora.adapter import load_adapter_config, resolve_adapter_file
     lcfg = load_adapter_config(adapter_path if os.path.isdir(adapter_path) else os.path.dirname(adapter_path))
+    if alpha is not None or rank is not None:
+        lcfg = dataclasses.replace(lcfg, alpha=lcfg.alpha if alpha is None else float(alpha),
+                                   r=lcfg.r if rank is None else int(rank))
     ad = st.load_file(resolve_adapter_file(adapter_path))
     scale = lcfg.scaling()
+    acc = torch.float64 if accurate else torch.float32
     ck = LazyCheckpoint(base_dir)
     out: Dict[str, torch.Tensor] = {}
     fused = 0
@@ -243,7 +253,14 @@ def merge_lora_into_base(base_dir: str, adapter_path: str, out_dir: str, dtype: 
             a, b = ad.get(key + ".lora_a"), ad.get(key + ".lora_b")
             if a is not None and b is not None and a.shape[0] == lcfg.r and a.shape[0] > 0 and b.shape[1] == a.shape[0] \
                     and not (a.shape[0] == 1 and lcfg.r != 1):
-                w = (w.double() + scale * (b.double() @ a.double())).to(w.dtype)
+                if low_memory:
+                    new = torch.empty_like(w)
+                    for r0 in range(0, w.shape[0], 1024):
+                        r1 = min(r0 + 1024, w.shape[0])
+                        new[r0:r1] = (w[r0:r1].to(acc) + scale * (b[r0:r1].to(acc) @ a.to(acc))).to(w.dtype)
+                    w = new
+                else:
+                    w = (w.to(acc) + scale * (b.to(acc) @ a.to(acc))).to(w.dtype)
                 fused += 1
         out[n] = w.to(_dtype(dtype)) if w.is_floating_point() else w
     cfg = MergeConfig(output_path=out_dir, dtype=dtype)

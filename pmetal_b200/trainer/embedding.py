@@ -54,6 +54,8 @@ class EmbeddingConfig:
     learning_rate: float = 2e-5
     max_grad_norm: float = 1.0
     max_length: int = 512
+    weight_decay: float = 0.0
+    normalize: bool = True           # unit-length embeddings (cosine similarities in the losses)
 
 
 class EmbeddingTrainer:
@@ -62,7 +64,7 @@ class EmbeddingTrainer:
         self.model, self.cfg = model, cfg
         self.device = model.embed_tokens.device
         shadow = torch.bfloat16 if self.device.type == "cuda" else None
-        self.opt = optimizer or FlatAdamW(model.named_parameters(), lr=cfg.learning_rate, weight_decay=0.0,
+        self.opt = optimizer or FlatAdamW(model.named_parameters(), lr=cfg.learning_rate, weight_decay=cfg.weight_decay,
                                           max_grad_norm=cfg.max_grad_norm, shadow_dtype=shadow)
         if shadow is not None:
             attach_shadows(model, self.opt)
@@ -82,7 +84,7 @@ class EmbeddingTrainer:
         with (torch.enable_grad() if grad else torch.no_grad()):
             h = self.model.forward_hidden(torch.tensor(ids, dtype=torch.int64, device=dev),
                                           torch.tensor(pos, dtype=torch.int32, device=dev), cu_t, ss)
-            return pool(h, cu, self.cfg.pooling)
+            return pool(h, cu, self.cfg.pooling, self.cfg.normalize)
 
     def step(self, anchors, positives, negatives=None, labels=None) -> dict:
         c = self.cfg

@@ -252,3 +252,47 @@ def test_tokenize_shards_then_pretrain_with_eval_and_resume(tmp_path, capsys):
     assert main(base + ["--steps", "6", "--resume"]) == 0
     b = _json_out(capsys)
     assert b["resumed_from"].endswith("step_4") and b["step"] == 6
+
+
+def test_fuse_merge_eval_embed_flag_forms(model_dir, capsys, tmp_path):
+    from pmetal_b200.core.config import LoraConfig
+    from pmetal_b200.lora import apply_lora
+    from pmetal_b200.lora.adapter import save_adapter
+    from pmetal_b200.models.loader import load_pretrained
+    from pmetal_b200.utils.safetensors_io import load_file
+    m, _, _ = load_pretrained(model_dir, dtype=torch.float32)
+    cfg = LoraConfig(r=4, alpha=8.0)
+    apply_lora(m, cfg)
+    for n, p in m.named_parameters():
+        if "lora_b" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    ad = str(tmp_path / "ad")
+    save_adapter(m, ad, cfg)
+    outs = {}
+    for name, extra in (("a", []), ("b", ["--low-memory"]), ("c", ["--fast"]), ("d", ["--alpha", "16"])):
+        assert main(["fuse", "-m", model_dir, "-l", ad, "-o", str(tmp_path / name), "--dtype", "float32"] + extra) == 0
+        outs[name] = load_file(str(tmp_path / name / "model.safetensors"))["model.layers.0.self_attn.q_proj.weight"]
+    assert _json_out(capsys)["scale"] == 4.0                                       # alpha 16 / r 4
+    base = load_file(os.path.join(model_dir, "model.safetensors"))["model.layers.0.self_attn.q_proj.weight"]
+    assert torch.equal(outs["a"], outs["b"]) and torch.allclose(outs["a"], outs["c"], atol=1e-5)
+    assert torch.allclose(outs["d"] - base, 2 * (outs["a"] - base), atol=1e-5)
+    assert main(["merge", "--model-a", model_dir, "--model-b", str(tmp_path / "a"), "--method", "slerp", "--t", "0.0",
+                 "-o", str(tmp_path / "s0"), "--dtype", "float32"]) == 0
+    s0 = load_file(str(tmp_path / "s0" / "model.safetensors"))["model.layers.0.self_attn.q_proj.weight"]
+    assert torch.allclose(s0, base, atol=1e-5)                                     # t = 0 returns model a
+    assert main(["merge", "--model-a", model_dir, "--model-b", str(tmp_path / "a"), "--weight-a", "0.25", "--weight-b", "0.75",
+                 "-o", str(tmp_path / "lin"), "--dtype", "float32"]) == 0
+    lin = load_file(str(tmp_path / "lin" / "model.safetensors"))["model.layers.0.self_attn.q_proj.weight"]
+    assert torch.allclose(lin, 0.25 * base + 0.75 * outs["a"], atol=1e-5)
+    capsys.readouterr()
+    data = tmp_path / "e.jsonl"
+    data.write_text("".join(json.dumps({"text": "some words to score " * 4}) + "\n" for _ in range(5)))
+    assert main(["eval", "-m", model_dir, "-d", str(data), "--num-samples", "2", "--json", "--device", "cpu"]) == 0
+    assert _json_out(capsys)["samples"] == 2
+    pairs = tmp_path / "pairs.jsonl"
+    pairs.write_text("".join(json.dumps({"anchor": f"query {i}", "positive": f"answer {i}", "negative": f"other {i}"}) + "\n"
+                             for i in range(6)))
+    assert main(["embed-train", "-m", model_dir, "-d", str(pairs), "-o", str(tmp_path / "emb"), "--loss", "triplet", "--margin", "0.3",
+                 "--epochs", "1", "--batch-size", "3", "--pooling", "last", "--no-normalize", "--weight-decay", "0.01",
+                 "--log-every", "1", "--lora-r", "4", "--device", "cpu"]) == 0
+    assert _json_out(capsys)["steps"] == 2
