@@ -70,10 +70,13 @@ def main(a) -> int:
     for p in model.parameters():
         p.requires_grad_(False)
     g = torch.Generator().manual_seed(0)
-    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in (128, 256, 512, 1024)]
+    bs, sl = getattr(a, "batch_size", None), getattr(a, "seq_len", None)
+    lens = [sl or 512] * bs if bs else ((sl,) * 4 if sl else (128, 256, 512, 1024))
+    prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in lens]
     out = {"model": a.model, "device": dev, "generation": bench_generation(model, prompts)}
     if a.what == "workload":
-        out["training"] = bench_training(model, args.vocab_size, seq_len=2048 if dev.startswith("cuda") else 256)
+        out["training"] = bench_training(model, args.vocab_size, samples=bs or 4,
+                                         seq_len=sl or (2048 if dev.startswith("cuda") else 256))
     print(json.dumps(out))
     if a.json:
         with open(a.json, "w", encoding="utf-8") as fh:

@@ -996,6 +996,8 @@ def cmd_grpo(a) -> int:
     try:
         for step in range(first, steps):
             batch = [prompts[(step * a.prompts_per_step + j) % len(prompts)] for j in range(a.prompts_per_step)]
+            if getattr(a, "anneal_alpha", False) and hasattr(tr, "alpha"):
+                tr.alpha = a.rlkd_alpha + (a.final_alpha - a.rlkd_alpha) * step / max(steps - 1, 1)
             st = tr.step(batch)
             d = st if isinstance(st, dict) else st.__dict__
             line = json.dumps({"step": step + 1, **{k: (round(v, 5) if isinstance(v, float) else v) for k, v in d.items()
@@ -1093,6 +1095,8 @@ def _bench_args(sp):
     p.add_argument("--case", nargs="*")
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("-m", "--model", default="random:qwen3-0.6b")
+    p.add_argument("--batch-size", type=int, default=None, help="workload: packs per step; gen: concurrent sequences")
+    p.add_argument("--seq-len", type=int, default=None, help="workload: tokens per pack; gen: prompt length")
     p.add_argument("--json")
     p.add_argument("--device")
     return p
@@ -1114,6 +1118,11 @@ def _cluster_args(sp):
     p.add_argument("--gpus", type=int, default=0)
     p.add_argument("--mb", type=int, default=64)
     p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--hidden-dim", type=int, default=0, help="pipeline-bench: width of the activation message")
+    p.add_argument("--tokens", type=int, default=0, help="pipeline-bench: tokens per activation message")
+    p.add_argument("--layers", type=int, default=0, help="accepted for compatibility (the stages exchange activations only)")
+    p.add_argument("--vocab", type=int, default=0, help="accepted for compatibility")
+    p.add_argument("--timeout", type=float, default=0, help="process-group timeout in seconds")
     p.add_argument("rest", nargs=argparse_remainder())
     return p
 
@@ -1375,10 +1384,14 @@ def cmd_embed_train(a) -> int:
 def _rlkd_args(sp):
     p = sp.add_parser("rlkd", help="GRPO with an added distillation term against a teacher (RLKD)")
     p.add_argument("-m", "--model", required=True)
-    p.add_argument("-t", "--teacher", required=True)
+    p.add_argument("-t", "--teacher", "--teacher-model", dest="teacher", required=True)
     p.add_argument("-d", "--dataset", required=True)
     p.add_argument("-o", "--output", default="./rlkd-output")
-    p.add_argument("--alpha", type=float, default=0.5, help="weight of the KD term")
+    p.add_argument("--alpha", "--distill-alpha", dest="alpha", type=float, default=0.5, help="weight of the KD term")
+    p.add_argument("--anneal-alpha", action="store_true", help="move the KD weight linearly to --final-alpha over the run")
+    p.add_argument("--final-alpha", type=float, default=0.0)
+    p.add_argument("--distill-temperature", type=float, default=1.0,
+                   help="accepted for compatibility: the KD term uses the log-probabilities of the sampled tokens")
     p.add_argument("--num-generations", type=int, default=8)
     p.add_argument("--beta", type=float, default=0.001)
     p.add_argument("--max-completion-length", type=int, default=512)
@@ -1479,11 +1492,15 @@ def cmd_search(a) -> int:
 # ------------------------------------------------------------------------------------------- dflash
 def _dflash_args(sp):
     p = sp.add_parser("dflash", help="speculative decoding with a DFlash block-diffusion draft model")
-    p.add_argument("-m", "--model", required=True, help="target model directory or random:<preset>")
+    p.add_argument("-m", "--model", "--target", dest="model", required=True, help="target model directory or random:<preset>")
     p.add_argument("--draft", required=True, help="draft directory (config.json + safetensors) or 'random'")
-    p.add_argument("--prompt", default="Hello")
-    p.add_argument("--max-tokens", type=int, default=64)
-    p.add_argument("--block-size", type=int, default=0)
+    p.add_argument("-p", "--prompt", default="Hello")
+    p.add_argument("--max-tokens", "--max-new-tokens", dest="max_tokens", type=int, default=64)
+    p.add_argument("--block-size", "--speculative-tokens", dest="block_size", type=int, default=0)
+    p.add_argument("--temperature", type=float, default=0.0, help="verification is greedy; values above 0 are refused")
+    p.add_argument("--no-chat", action="store_true", help="the prompt is used as it is (always the case here)")
+    p.add_argument("--json", action="store_true", help="the result is always one JSON line")
+    p.add_argument("--draft-fp8", action="store_true", help="accepted for compatibility: the draft runs in the model dtype")
     p.add_argument("--tree-budget", type=int, default=0, help="> 0: tree verification with this many candidate nodes")
     p.add_argument("--device")
     return p
@@ -1499,6 +1516,9 @@ def cmd_dflash(a) -> int:
     from ..models.dflash import DFlashConfig, DFlashDecoder, DFlashDraftModel
     from ..models.loader import read_state_dict
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    if a.temperature > 0:
+        print("error: block-diffusion drafting verifies greedily; use --temperature 0", file=sys.stderr)
+        return 2
     if a.model.startswith("random:"):
         from ..models.config import preset
         cfg = preset(a.model.split(":", 1)[1]).to_hf_dict()

@@ -47,7 +47,8 @@ def run(a) -> int:
     if a.action == "bench":
         return _torchrun(n, [here, "bench", str(a.mb), str(a.iters)])
     if a.action == "pipeline-bench":
-        return _torchrun(n, [here, "pipeline", str(a.mb), str(a.iters)])
+        return _torchrun(n, [here, "pipeline", str(a.mb), str(a.iters), str(getattr(a, "hidden_dim", 0) or 0),
+                             str(getattr(a, "tokens", 0) or 0), str(getattr(a, "timeout", 0) or 0)])
     if a.action in ("train", "serve"):
         rest = [x for x in a.rest if x != "--"]
         return _torchrun(n, ["-m", "pmetal_b200.cli.main", a.action] + rest)
@@ -55,13 +56,16 @@ def run(a) -> int:
 
 
 # ------------------------------------------------------------------------------------------- workers
-def _worker_setup():
+def _worker_setup(timeout_s: float = 0.0):
+    import datetime
+
     import torch
     import torch.distributed as dist
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    kw = {"timeout": datetime.timedelta(seconds=timeout_s)} if timeout_s > 0 else {}
+    dist.init_process_group("nccl", device_id=dev, **kw)
     return dist, dev, dist.get_rank(), dist.get_world_size()
 
 
@@ -125,12 +129,13 @@ def _bench_worker(mb: int, iters: int) -> None:
     os._exit(0)
 
 
-def _pipeline_worker(mb: int, iters: int) -> None:
+def _pipeline_worker(mb: int, iters: int, hidden: int = 0, tokens: int = 0, timeout_s: float = 0.0) -> None:
+    """Activation message [1, tokens, hidden] bf16 around the stage ring; ``tokens`` defaults to what ``mb`` MiB hold."""
     import torch
-    dist, dev, rank, world = _worker_setup()
+    dist, dev, rank, world = _worker_setup(timeout_s)
     from .pipeline import ActivationMessage, pipeline_ring_step
-    hidden = 4096
-    tokens = max(mb * 1024 * 1024 // (hidden * 2), 1)
+    hidden = hidden or 4096
+    tokens = tokens or max(mb * 1024 * 1024 // (hidden * 2), 1)
     x = torch.randn(1, tokens, hidden, device=dev).bfloat16()
     msg = ActivationMessage(nonce=1, layer_id=rank, tensor=x)
     ms = _time_max(dist, dev, lambda: pipeline_ring_step(msg, rank, world), iters) if world > 1 else 0.0
@@ -150,4 +155,5 @@ if __name__ == "__main__":
     if kind == "bench":
         _bench_worker(mb, iters)
     else:
-        _pipeline_worker(mb, iters)
+        extra = [float(x) for x in sys.argv[4:7]] + [0.0] * 3
+        _pipeline_worker(mb, iters, int(extra[0]), int(extra[1]), extra[2])
