@@ -453,6 +453,70 @@ class KVCache:
         return int(self.state.get("length", 0))
 
 
+class QuantKVCache(KVCache):
+    """KV cache that stores keys and values quantised and expands them on read: ``bits`` 8 or 4 with one fp16 scale per
+    ``group`` channels (symmetric, absmax), or ``turbo=True`` for the rotation + Lloyd-Max codebook scheme (2, 4 or 8 bits) of
+    ``models/turboquant.py`` (optionally with the QJL residual sign sketch). The reference selects between fp16, q8 and
+    TurboQuant caches to fit unified memory (crates/pmetal-mlx/src/kv_cache/quantized.rs, crates/pmetal-serve/src/engine.rs
+    KV-mode selection); here the portable models can trade accuracy for cache size the same way."""
+
+    def __init__(self, num_layers: int, bits: int = 8, group: int = 64, turbo: bool = False, qjl: bool = False):
+        super().__init__(num_layers)
+        if bits not in (2, 4, 8):
+            raise ValueError("bits must be 2, 4 or 8")
+        if not turbo and bits not in (4, 8):
+            raise ValueError("group quantisation supports 4 or 8 bits")
+        self.bits, self.group, self.turbo, self.qjl = bits, group, turbo, qjl
+        self._store: List[List] = [[] for _ in range(num_layers)]        # per layer: list of (k blob, v blob, shape, dtype)
+        self._tq: Dict[int, object] = {}
+        self._len = [0] * num_layers
+
+    # ---- codecs
+    def _enc(self, x: torch.Tensor):
+        d = x.shape[-1]
+        if self.turbo:
+            from ..turboquant import TurboQuant
+            tq = self._tq.get(d)
+            if tq is None:
+                tq = self._tq[d] = TurboQuant(d, self.bits, self.qjl, device=x.device)
+            return tq.encode(x.reshape(-1, d).float())
+        g = self.group if d % self.group == 0 else d
+        xf = x.float().reshape(*x.shape[:-1], d // g, g)
+        qmax = 127.0 if self.bits == 8 else 7.0
+        scale = xf.abs().amax(-1, keepdim=True).clamp(min=1e-8) / qmax
+        q = torch.round(xf / scale).clamp(-qmax, qmax).to(torch.int8)
+        if self.bits == 4:                                              # two codes per byte
+            u = (q + 8).to(torch.uint8).reshape(*q.shape[:-1], g // 2, 2)
+            q = u[..., 0] | (u[..., 1] << 4)
+        return q, scale.to(torch.float16)
+
+    def _dec(self, blob, shape, dtype):
+        if self.turbo:
+            return self._tq[shape[-1]].decode(blob).reshape(shape).to(dtype)
+        q, scale = blob
+        if self.bits == 4:
+            q = torch.stack(((q & 15).to(torch.int8) - 8, (q >> 4).to(torch.int8) - 8), -1).flatten(-2)
+        return (q.float() * scale.float()).reshape(shape).to(dtype)
+
+    def append(self, layer: int, k: torch.Tensor, v: torch.Tensor):
+        self._store[layer].append((self._enc(k), self._enc(v), k.shape, v.shape, k.dtype))
+        self._len[layer] += k.shape[2]
+        ks = [self._dec(kb, ksh, dt) for kb, _, ksh, _, dt in self._store[layer]]
+        vs = [self._dec(vb, vsh, dt) for _, vb, _, vsh, dt in self._store[layer]]
+        return torch.cat(ks, 2), torch.cat(vs, 2)
+
+    def length(self) -> int:
+        return max(self._len) if any(self._len) else int(self.state.get("length", 0))
+
+    def nbytes(self) -> int:
+        """Bytes held by the compressed keys and values."""
+        def size(blob):
+            if self.turbo:
+                return blob.nbytes()
+            return sum(t.numel() * t.element_size() for t in blob)
+        return sum(size(kb) + size(vb) for layer in self._store for kb, vb, *_ in layer)
+
+
 class Attention(nn.Module):
     def __init__(self, c: ArchConfig, idx: int):
         super().__init__()
@@ -931,14 +995,19 @@ class GenericDecoderLM(nn.Module):
     def forward(self, input_ids, cache: Optional[KVCache] = None, positions=None, attn_mask=None) -> torch.Tensor:
         return self.logits(self.forward_hidden(input_ids, cache, positions, attn_mask))
 
-    def new_cache(self) -> KVCache:
-        return KVCache(self.c.num_layers)
+    def new_cache(self, kv_bits: Optional[int] = None, kv_group: int = 64, turbo: bool = False, qjl: bool = False) -> KVCache:
+        """``kv_bits`` None: keys and values in the model dtype; 8 / 4: group-quantised; with ``turbo`` 2 / 4 / 8 bit
+        rotation + codebook compression."""
+        if kv_bits is None:
+            return KVCache(self.c.num_layers)
+        return QuantKVCache(self.c.num_layers, kv_bits, kv_group, turbo, qjl)
 
     @torch.no_grad()
-    def generate(self, prompt: List[int], max_new_tokens: int = 32, eos_token_id: Optional[int] = None) -> List[int]:
+    def generate(self, prompt: List[int], max_new_tokens: int = 32, eos_token_id: Optional[int] = None,
+                 kv_bits: Optional[int] = None) -> List[int]:
         """Greedy decoding with the contiguous cache."""
         dev = self.model.embed_tokens.weight.device
-        cache = self.new_cache()
+        cache = self.new_cache(kv_bits)
         ids = torch.tensor([prompt], device=dev)
         out: List[int] = []
         for _ in range(max_new_tokens):

@@ -500,3 +500,24 @@ def test_mllama_matches_hugging_face_and_decodes_with_cached_image_keys():
     out = ours.generate(ids[0, :6].tolist(), 3, pixel_values=pix[:1], aspect_ratio_ids=ar_ids[:1],
                         aspect_ratio_mask=ar_mask[:1], cross_attention_mask=cam[:1, :6])
     assert len(out) == 3
+
+
+def test_quantised_kv_cache_tracks_the_exact_cache():
+    from pmetal_b200.models.architectures.generic import QuantKVCache
+    _, ours = _pair("llama")
+    ids = torch.randint(0, 128, (1, 24), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        full = ours(ids)
+        errs = {}
+        for name, kw in (("q8", dict(kv_bits=8, kv_group=16)), ("q4", dict(kv_bits=4, kv_group=16)),
+                         ("tq4", dict(kv_bits=4, turbo=True)), ("tq2_qjl", dict(kv_bits=2, turbo=True, qjl=True))):
+            cache = ours.new_cache(**kw)
+            assert isinstance(cache, QuantKVCache)
+            out = torch.cat([ours(ids[:, :16], cache)] + [ours(ids[:, t:t + 1], cache) for t in range(16, 24)], 1)
+            errs[name] = float((out - full).abs().max() / full.abs().max())
+            assert cache.length() == 24 and cache.nbytes() > 0
+            if name == "q8":
+                exact = sum(2 * 24 * 2 * 16 * 4 for _ in range(4))        # layers x (k,v) x tokens x kv heads x head dim x fp32
+                assert cache.nbytes() < 0.45 * exact
+    assert errs["q8"] < 0.02 and errs["q4"] < 0.2 and errs["tq4"] < 0.3 and errs["q8"] < errs["q4"], errs
+    assert len(ours.generate(ids[0, :6].tolist(), 4, kv_bits=8)) == 4
