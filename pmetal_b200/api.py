@@ -86,3 +86,105 @@ class Model:
 
 def infer(model: str, prompt: str, lora: Optional[str] = None, **kw) -> str:
     return Model.load(model, lora).generate(prompt, **kw)
+
+
+class Trainer:
+    """Object form of :func:`finetune` (crates/pmetal-py/src/trainer.rs:69-360): configure, attach callbacks, ``train()``.
+
+    Callbacks are ``core.callbacks.TrainingCallback`` objects, or any object with some of the methods ``on_train_start``,
+    ``on_step_end(metrics)``, ``on_eval(metrics)``, ``on_train_end`` (duck-typed, as the reference accepts plain Python
+    objects)."""
+
+    def __init__(self, model_id: str, lora_config=None, training_config=None, dataset_path: str = "",
+                 eval_dataset_path: Optional[str] = None, output: Optional[str] = None):
+        from .core.config import LoraConfig, TrainingConfig
+        from .trainer.orchestrator import TrainingJobConfig
+        self.job = TrainingJobConfig()
+        self.job.model, self.job.dataset, self.job.eval_dataset = model_id, dataset_path, eval_dataset_path
+        self.job.lora = lora_config or LoraConfig()
+        self.job.training = training_config or TrainingConfig()
+        out = output or getattr(self.job.training, "output_dir", None)
+        if out:
+            self.job.output = out
+        self.callbacks: list = []
+
+    def add_callback(self, callback) -> None:
+        self.callbacks.append(callback)
+
+    def set_sequence_packing(self, enabled: bool) -> None:
+        self.job.use_packing = bool(enabled)
+
+    def set_gradient_checkpointing(self, enabled: bool, layers: int = 4) -> None:
+        self.job.gradient_checkpointing_layers = layers if enabled else 0
+
+    def set_fused_optimizer(self, enabled: bool) -> None:
+        """Fused reduce + clip + AdamW step across GPUs (on) or NCCL all-reduce followed by separate kernels (off)."""
+        self.job.dp_impl = "fused" if enabled else "nccl"
+
+    set_metal_fused_optimizer = set_fused_optimizer          # the reference's name for the same switch
+
+    def set_embedding_lr(self, lr: float) -> None:
+        self.job.training.embedding_learning_rate = float(lr)
+
+    def set_quantization(self, kind: str, block_size: int = 64, double_quant: bool = False) -> None:
+        self.job.quantization, self.job.quant_block_size, self.job.double_quant = kind, block_size, double_quant
+
+    def train(self) -> dict:
+        from .core.callbacks import TrainingCallback
+        from .trainer.orchestrator import run_training
+
+        class _Duck(TrainingCallback):
+            def __init__(self, obj):
+                self.obj = obj
+
+            def __getattribute__(self, name):
+                if name.startswith("on_") or name == "should_stop":
+                    obj = object.__getattribute__(self, "obj")
+                    if hasattr(obj, name):
+                        return getattr(obj, name)
+                return object.__getattribute__(self, name)
+        cbs = [c if isinstance(c, TrainingCallback) else _Duck(c) for c in self.callbacks]
+        return run_training(self.job, callbacks=cbs)
+
+    def __repr__(self) -> str:
+        return f"Trainer(model={self.job.model!r}, dataset={self.job.dataset!r}, lora_r={self.job.lora.r})"
+
+
+class GenerationConfig:
+    """Sampling options of ``Model.generate`` (a thin, keyword-checked view of ``models.sampling.SamplingParams``)."""
+
+    def __init__(self, **kw):
+        from .models.sampling import SamplingParams
+        self.params = SamplingParams(**kw)
+
+    def __getattr__(self, name):
+        return getattr(object.__getattribute__(self, "params"), name)
+
+
+class DataLoaderConfig:
+    def __init__(self, batch_size: int = 1, max_seq_len: int = 2048, shuffle: bool = True, seed: int = 42,
+                 pad_token_id: int = 0, drop_last: bool = False):
+        self.batch_size, self.max_seq_len, self.shuffle, self.seed = batch_size, max_seq_len, shuffle, seed
+        self.pad_token_id, self.drop_last = pad_token_id, drop_last
+
+
+def download_model(model_id: str, revision: str = "main", token: Optional[str] = None, cache_dir: Optional[str] = None) -> str:
+    """Local path of a hub model: an existing directory or cached snapshot if there is one, else a (resumable,
+    checksum-verified) download."""
+    import os
+
+    from . import hub
+    from .models.loader import resolve_model_path
+    try:
+        path = resolve_model_path(model_id)
+        if os.path.isdir(path):
+            return path
+    except Exception:
+        pass
+    return hub.download_model(model_id, revision=revision, token=token, dest_dir=cache_dir)
+
+
+def download_file(model_id: str, filename: str, revision: str = "main", token: Optional[str] = None,
+                  cache_dir: Optional[str] = None) -> str:
+    from . import hub
+    return hub.download_file(model_id, filename, dest_dir=cache_dir, revision=revision, token=token)

@@ -211,3 +211,30 @@ def test_dflash_draft_training_step_learns():
     tr = DFlashDraftTrainer(target, draft, lr=3e-3)
     losses = [tr.train_step(toks)["loss"] for _ in range(120)]
     assert sum(losses[-10:]) < 0.8 * sum(losses[:10])
+
+
+def test_python_api_exports_and_trainer_object(tmp_path):
+    import pmetal_b200 as pm
+    for name in ("LoraConfig", "TrainingConfig", "GenerationConfig", "DataLoaderConfig", "Dtype", "Quantization", "LoraBias",
+                 "LrSchedulerType", "OptimizerType", "DatasetFormat", "ModelArchitecture", "download_model", "download_file",
+                 "Model", "Tokenizer", "Trainer", "ProgressCallback", "LoggingCallback", "MetricsJsonCallback", "finetune", "infer"):
+        assert getattr(pm, name) is not None and name in pm.__all__
+    assert pm.LrSchedulerType.COSINE == "cosine" and str(pm.Quantization.NF4) == "nf4"
+    assert pm.ModelArchitecture.from_config({"model_type": "qwen3_moe"}) is pm.ModelArchitecture.QWEN3_MOE
+    assert pm.GenerationConfig(temperature=0.3, max_tokens=5).temperature == 0.3
+    data = tmp_path / "d.jsonl"
+    data.write_text("".join(json.dumps({"text": "the cat sat on the mat " * 4}) + "\n" for _ in range(8)))
+    seen = []
+
+    class Watch:                                                     # a plain object: only the methods it has are called
+        def on_step_end_with_metrics(self, m):
+            seen.append(m.step)
+    tcfg = pm.TrainingConfig(learning_rate=1e-3, max_steps=2, gradient_accumulation_steps=1, warmup_steps=0)
+    tr = pm.Trainer("random:tiny-qwen3", pm.LoraConfig(r=4, alpha=8.0), tcfg, str(data), output=str(tmp_path / "out"))
+    tr.add_callback(Watch())
+    tr.set_sequence_packing(True)
+    tr.set_metal_fused_optimizer(False)
+    tr.job.device, tr.job.dtype, tr.job.adaptive_lr = "cpu", "float32", False
+    res = tr.train()
+    assert seen == [1, 2] and os.path.exists(tmp_path / "out" / "lora_weights.safetensors") and "Trainer(" in repr(tr)
+    assert isinstance(res, dict)
