@@ -1135,6 +1135,20 @@ def argparse_remainder():
 @_command(_cluster_args)
 def cmd_cluster(a) -> int:
     from ..parallel import cluster_cli
+    if a.rest:
+        # the trailing remainder also swallows this command's own flags when they follow the action
+        # (``cluster bench --gpus 2``): pick them out, leave the rest for the launched sub-command
+        import argparse
+        own = argparse.ArgumentParser(add_help=False)
+        for flag, typ in (("--gpus", int), ("--mb", int), ("--iters", int), ("--hidden-dim", int), ("--tokens", int),
+                          ("--layers", int), ("--vocab", int), ("--timeout", float)):
+            own.add_argument(flag, type=typ, default=None)
+        known, rest = own.parse_known_args([x for x in a.rest if x != "--"] if a.action not in ("train", "serve") else [])
+        for k, v in vars(known).items():
+            if v is not None:
+                setattr(a, k, v)
+        if a.action not in ("train", "serve"):
+            a.rest = rest
     return cluster_cli.run(a) or 0
 
 

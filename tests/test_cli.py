@@ -296,3 +296,15 @@ def test_fuse_merge_eval_embed_flag_forms(model_dir, capsys, tmp_path):
                  "--epochs", "1", "--batch-size", "3", "--pooling", "last", "--no-normalize", "--weight-decay", "0.01",
                  "--log-every", "1", "--lora-r", "4", "--device", "cpu"]) == 0
     assert _json_out(capsys)["steps"] == 2
+
+
+def test_cluster_flags_after_the_action_are_applied(monkeypatch):
+    from pmetal_b200.parallel import cluster_cli
+    seen = {}
+    monkeypatch.setattr(cluster_cli, "run", lambda a: seen.update(vars(a)) or 0)
+    assert main(["cluster", "pipeline-bench", "--gpus", "2", "--hidden-dim", "2048", "--tokens", "4096", "--mb", "8"]) == 0
+    assert (seen["gpus"], seen["hidden_dim"], seen["tokens"], seen["mb"], seen["rest"]) == (2, 2048, 4096, 8, [])
+    assert main(["cluster", "--gpus", "4", "bench", "--iters", "5"]) == 0
+    assert (seen["gpus"], seen["iters"]) == (4, 5)
+    assert main(["cluster", "train", "--", "-m", "x", "--gpus", "2"]) == 0           # flags of the launched command stay
+    assert seen["rest"] == ["--", "-m", "x", "--gpus", "2"] or seen["rest"] == ["-m", "x", "--gpus", "2"]
