@@ -153,11 +153,44 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
+def setup_logging(verbose: bool = False, log_file: Optional[str] = None) -> Optional[str]:
+    """Log to stderr and to a file with one rotation: ``PMETAL_LOG_FILE`` or ``~/.cache/pmetal/logs/cli.log``; a file
+    above 8 MiB is moved to ``.1`` first (crates/pmetal/src/main.rs:1318-1397). ``PMETAL_LOG_FILE=off`` disables the
+    file; an unwritable location is skipped silently. Returns the file path in use."""
+    level = logging.DEBUG if verbose else getattr(logging, os.environ.get("PMETAL_LOG", "INFO").upper(), logging.INFO)
+    fmt = logging.Formatter("%(asctime)s %(levelname)s %(message)s")
+    root = logging.getLogger()
+    root.setLevel(level)
+    for h in list(root.handlers):
+        if getattr(h, "_pmetal", False):
+            root.removeHandler(h)
+            h.close()
+    err = logging.StreamHandler(sys.stderr)
+    err.setFormatter(fmt)
+    err._pmetal = True
+    root.addHandler(err)
+    path = log_file or os.environ.get("PMETAL_LOG_FILE") or os.path.join(os.path.expanduser("~"), ".cache", "pmetal", "logs",
+                                                                         "cli.log")
+    if path.lower() in ("off", "none", "0"):
+        return None
+    try:
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        if os.path.exists(path) and os.path.getsize(path) > 8 << 20:
+            os.replace(path, path + ".1")
+        fh = logging.FileHandler(path, encoding="utf-8")
+    except OSError:
+        return None
+    fh.setFormatter(fmt)
+    fh._pmetal = True
+    root.addHandler(fh)
+    return path
+
+
 def main(argv: Optional[List[str]] = None) -> int:
     ap = build_parser()
     a = ap.parse_args(argv)
-    logging.basicConfig(level=logging.DEBUG if a.verbose else logging.INFO,
-                        format="%(asctime)s %(levelname)s %(message)s", stream=sys.stderr)
+    setup_logging(a.verbose)
+    logging.getLogger("pmetal").debug("command line: %s", " ".join(argv if argv is not None else sys.argv[1:]))
     if not getattr(a, "func", None):
         ap.print_help()
         return 1

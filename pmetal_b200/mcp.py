@@ -69,12 +69,25 @@ class McpServer:
                             "schema": {"type": "object", "properties": properties, "required": required}}
 
     def _job_tool(self, kind: str, description: str, required: List[str]):
-        props = {r: {"type": "string"} for r in required}
+        # the tool's input schema is the command's job specification (every flag with its type, default and help)
+        from .core.jobs import job_specs
+        if not hasattr(self, "_specs"):
+            self._specs = job_specs()
+        spec = self._specs.get(kind)
+        props = dict(spec.json_schema()["properties"]) if spec else {}
+        for r in required:
+            props.setdefault(r, {"type": "string"})
         props["extra"] = {"type": "object", "description": "additional CLI flags, e.g. {\"max_steps\": 10}"}
 
         def start(args):
             flags = {k: v for k, v in args.items() if k != "extra"}
             flags.update(args.get("extra") or {})
+            if spec is not None:
+                try:
+                    spec.validate(flags)
+                except ValueError as e:
+                    if "unknown field" not in str(e):      # unknown flags go through as they are; bad values are refused
+                        raise
             job = Job(kind, [kind] + _args_to_argv(flags))
             self.jobs[job.id] = job
             return job.status()

@@ -4,6 +4,7 @@ import sys
 import pytest
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+os.environ.setdefault("PMETAL_LOG_FILE", "off")          # command-line runs inside tests write no log file in the home directory
 
 
 def pytest_configure(config):

@@ -73,3 +73,54 @@ def test_tensorboard_callback_writes_event_file(tmp_path):
     files = os.listdir(tmp_path / "tb")
     assert any(f.startswith("events.out.tfevents") for f in files)
     assert os.path.getsize(os.path.join(tmp_path / "tb", files[0])) > 100
+
+
+def test_job_specs_describe_every_command_and_round_trip():
+    from pmetal_b200.cli.main import build_parser
+    from pmetal_b200.core.jobs import job_spec, job_specs
+    specs = job_specs()
+    for cmd in ("train", "infer", "serve", "grpo", "distill", "quantize", "merge", "fuse", "pretrain", "embed-train", "eval",
+                "tokenize", "dflash", "rlkd", "pack-experts", "bench", "dataset filter", "dataset prepare"):
+        assert cmd in specs and specs[cmd].fields, cmd
+    t = job_spec("train")
+    f = t.field("lora_r")
+    assert (f.kind, f.default, f.flags) == ("integer", 16, ["--lora-r"]) and t.field("use_dora").kind == "boolean"
+    assert t.json_schema()["properties"]["quantization"]["enum"] == ["none", "nf4", "fp4", "int8"]
+    vals = {"model": "m", "dataset": "d.jsonl", "lora_r": 8, "use_dora": True, "learning_rate": 1e-4, "max_steps": 3}
+    ns = build_parser().parse_args(t.to_argv(vals))
+    for k, v in vals.items():
+        assert getattr(ns, k) == v
+    g = job_spec("dataset merge")
+    ns = build_parser().parse_args(g.to_argv({"inputs": ["a", "b"], "output": "o", "shuffle": True}))
+    assert ns.inputs == ["a", "b"] and ns.output == "o" and ns.shuffle
+    for bad in ({"model": "m", "dataset": "d", "lora_r": "eight"}, {"model": "m", "dataset": "d", "quantization": "q3"},
+                {"model": "m", "dataset": "d", "bogus": 1}, {"model": "m", "dataset": "d", "use_dora": "yes"}):
+        with pytest.raises(ValueError):
+            t.validate(bad)
+    with pytest.raises(ValueError):
+        job_spec("fuse").validate({"model": "m"})                       # --lora and --output are required
+    with pytest.raises(KeyError):
+        job_spec("nope")
+
+
+def test_cli_log_file_with_rotation(tmp_path, monkeypatch):
+    import logging
+
+    from pmetal_b200.cli.main import setup_logging
+    log = tmp_path / "logs" / "cli.log"
+    monkeypatch.setenv("PMETAL_LOG_FILE", str(log))
+    assert setup_logging() == str(log)
+    logging.getLogger("pmetal").info("first run")
+    log_size = os.path.getsize(log)
+    assert log_size > 0
+    with open(log, "ab") as fh:
+        fh.write(b"x" * (9 << 20))
+    assert setup_logging() == str(log)                                    # re-initialising rotates the oversized file
+    logging.getLogger("pmetal").info("second run")
+    assert os.path.getsize(str(log) + ".1") > 9 << 20 and b"second run" in open(log, "rb").read()
+    monkeypatch.setenv("PMETAL_LOG_FILE", "off")
+    assert setup_logging() is None
+    monkeypatch.setenv("PMETAL_LOG_FILE", "/proc/definitely/not/writable/cli.log")
+    assert setup_logging() is None
+    monkeypatch.setenv("PMETAL_LOG_FILE", "off")
+    setup_logging()
