@@ -213,6 +213,11 @@ class Generator:
     @torch.no_grad()
     def decode_step(self, seq_ids: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
         """One new token per sequence → next-token logits [n, V]."""
+        from ..utils import nvtx
+        with nvtx.range("decode_step"):
+            return self._decode_step(seq_ids, tokens)
+
+    def _decode_step(self, seq_ids: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
         if self.cuda_graphs:
             from ..ops import functional as ops
             if ops.native_enabled(self.model.embed_tokens) and self.model.cfg.head_dim == 128:

@@ -102,9 +102,12 @@ class TrainingLoop:
         return gnorm
 
     def train_step(self, batch) -> (torch.Tensor, Optional[torch.Tensor]):
-        loss = self.micro_step(batch)
+        from ..utils import nvtx
+        with nvtx.range("forward_backward"):
+            loss = self.micro_step(batch)
         if self._accum >= self.cfg.gradient_accumulation_steps:
-            return loss, self.optimizer_step()
+            with nvtx.range("optimizer_step"):
+                return loss, self.optimizer_step()
         return loss, None
 
     # ------------------------------------------------------------------ CUDA-graph step
@@ -141,15 +144,18 @@ class TrainingLoop:
         self._g_loss, self._g_gnorm = loss, gn
 
     def train_step_graphed(self, batch: PackedTensors):
+        from ..utils import nvtx
         gi = self._g_in
-        gi.input_ids.copy_(batch.input_ids, non_blocking=True)
-        gi.labels.copy_(batch.labels, non_blocking=True)
-        gi.position_ids.copy_(batch.position_ids, non_blocking=True)
-        gi.seq_start.copy_(batch.seq_start, non_blocking=True)
-        self.opt.set_lr(self.current_lr())
-        self.opt.step_count += 1
-        self.opt.push_hparams(self.opt.step_count)
-        self._graph.replay()
+        with nvtx.range("stage_batch"):
+            gi.input_ids.copy_(batch.input_ids, non_blocking=True)
+            gi.labels.copy_(batch.labels, non_blocking=True)
+            gi.position_ids.copy_(batch.position_ids, non_blocking=True)
+            gi.seq_start.copy_(batch.seq_start, non_blocking=True)
+            self.opt.set_lr(self.current_lr())
+            self.opt.step_count += 1
+            self.opt.push_hparams(self.opt.step_count)
+        with nvtx.range("train_step_graph"):
+            self._graph.replay()
         self.state.step += 1
         return self._g_loss, self._g_gnorm
 

@@ -124,3 +124,11 @@ def test_cli_log_file_with_rotation(tmp_path, monkeypatch):
     assert setup_logging() is None
     monkeypatch.setenv("PMETAL_LOG_FILE", "off")
     setup_logging()
+
+
+def test_nvtx_ranges_are_inert_without_a_device():
+    from pmetal_b200.utils import nvtx
+    nvtx.set_enabled(False)
+    with nvtx.range("phase"):
+        nvtx.mark("point")
+    assert not nvtx.enabled()
