@@ -1321,7 +1321,7 @@ def cmd_pretrain(a) -> int:
     if resume:
         tr.load_checkpoint(resume)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    ds = TokenShardDataset(a.shards, a.seq_len, rank, world)
+    ds = TokenShardDataset(a.shards, a.seq_len, rank, world, seed=a.seed, loop=True)      # epochs roll over until --steps
     ev = TokenShardDataset(a.eval_shards, a.seq_len, rank, world) if a.eval_shards else None
 
     def on_step(st):

@@ -36,7 +36,7 @@ class ShardWriter:
 
 class TokenShardDataset:
     def __init__(self, pattern_or_paths, seq_len: int, rank: int = 0, world: int = 1, seed: int = 42,
-                 shuffle: bool = True, drop_last: bool = True):
+                 shuffle: bool = True, drop_last: bool = True, loop: bool = False):
         paths = sorted(glob.glob(pattern_or_paths)) if isinstance(pattern_or_paths, str) else list(pattern_or_paths)
         if not paths:
             raise FileNotFoundError(f"no token shards match {pattern_or_paths!r}")
@@ -47,6 +47,18 @@ class TokenShardDataset:
             n = sh.size // seq_len if drop_last else -(-sh.size // seq_len)
             self.index.extend((si, i * seq_len) for i in range(n))
         self.epoch = 0
+        self.cursor = 0                    # windows of the current epoch already handed out (this rank)
+        self.loop = loop                   # keep going into the next epoch (new shuffle) instead of stopping
+
+    def state_dict(self) -> dict:
+        """Exact position in the stream: resuming from it yields the windows an uninterrupted run would have seen next
+        (the reference's ``StreamPosition``, crates/pmetal-data/src/streaming.rs:66-80,333)."""
+        return {"epoch": int(self.epoch), "cursor": int(self.cursor), "seed": int(self.seed), "windows": len(self.index)}
+
+    def load_state_dict(self, d: dict) -> None:
+        if d.get("windows") not in (None, len(self.index)) or d.get("seed", self.seed) != self.seed:
+            raise ValueError("stream position belongs to a different shard set, window length or seed")
+        self.epoch, self.cursor = int(d["epoch"]), int(d["cursor"])
 
     def __len__(self) -> int:
         return len(self.index[self.rank::self.world])
@@ -58,12 +70,19 @@ class TokenShardDataset:
         self.epoch = epoch
 
     def __iter__(self) -> Iterator[np.ndarray]:
-        order = np.arange(len(self.index))
-        if self.shuffle:
-            np.random.default_rng(self.seed + self.epoch).shuffle(order)
-        for j in order[self.rank::self.world]:
-            si, start = self.index[j]
-            yield np.asarray(self.shards[si][start:start + self.seq_len], dtype=np.int64)
+        while True:
+            order = np.arange(len(self.index))
+            if self.shuffle:
+                np.random.default_rng(self.seed + self.epoch).shuffle(order)
+            mine = order[self.rank::self.world]
+            for k in range(self.cursor, len(mine)):
+                si, start = self.index[mine[k]]
+                self.cursor = k + 1
+                yield np.asarray(self.shards[si][start:start + self.seq_len], dtype=np.int64)
+            self.cursor = 0
+            if not self.loop or len(mine) == 0:
+                return
+            self.epoch += 1
 
     def documents(self, shard: int) -> Optional[np.ndarray]:
         idx = os.path.splitext(self.shards[shard].filename)[0] + ".idx"

@@ -59,6 +59,7 @@ class PretrainTrainer:
                                            min_lr=cfg.min_lr)
         self.step_count = 0
         self.tokens_seen = 0
+        self.data_state: Optional[dict] = None      # position of the training stream, saved with every checkpoint
 
     def _batch(self, windows):
         import numpy as np
@@ -155,12 +156,18 @@ class PretrainTrainer:
         c = self.cfg
         batch, last = [], {}
         per_step = c.micro_batch * max(c.gradient_accumulation_steps, 1)
+        if self.data_state is not None and hasattr(dataset, "load_state_dict"):
+            dataset.load_state_dict(self.data_state)            # resume exactly where the checkpointed run stopped reading
+        if self.step_count >= c.max_steps:
+            return last
         for window in dataset:
             batch.append(window)
             if len(batch) < per_step:
                 continue
             last = self.train_step(batch)
             batch = []
+            if hasattr(dataset, "state_dict"):
+                self.data_state = dataset.state_dict()
             if eval_dataset is not None and eval_every and self.step_count % eval_every == 0:
                 last = {**last, **self.evaluate(eval_dataset, eval_batches)}
             if on_step:
@@ -181,6 +188,7 @@ class PretrainTrainer:
                      os.path.join(path, "optimizer.safetensors"))
         with open(os.path.join(path, "trainer_state.json"), "w", encoding="utf-8") as fh:
             json.dump({"step": self.step_count, "tokens_seen": self.tokens_seen, "config": asdict(self.cfg),
+                       "data_state": self.data_state,
                        "optimizer_scalars": {k: v for k, v in o.items() if not isinstance(v, torch.Tensor)}}, fh, indent=2)
 
     def load_checkpoint(self, path: str) -> None:
@@ -194,3 +202,4 @@ class PretrainTrainer:
         self.opt.load_state_dict(o)
         self.opt.sync_shadow()
         self.step_count, self.tokens_seen = state["step"], state["tokens_seen"]
+        self.data_state = state.get("data_state")

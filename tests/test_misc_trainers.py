@@ -238,3 +238,22 @@ def test_python_api_exports_and_trainer_object(tmp_path):
     res = tr.train()
     assert seen == [1, 2] and os.path.exists(tmp_path / "out" / "lora_weights.safetensors") and "Trainer(" in repr(tr)
     assert isinstance(res, dict)
+
+
+def test_token_stream_position_resumes_exactly(tmp_path):
+    with ShardWriter(str(tmp_path / "s.bin")) as w:
+        w.add_document(list(range(1000)))
+    full = TokenShardDataset(str(tmp_path / "s.bin"), 10, seed=3, loop=True)
+    it = iter(full)
+    seq = [next(it)[0] for _ in range(250)]                              # 100 windows per epoch: runs into the third epoch
+    assert full.state_dict()["epoch"] == 2 and sorted(seq[:100]) == sorted(seq[100:200]) and seq[:100] != seq[100:200]
+    a = TokenShardDataset(str(tmp_path / "s.bin"), 10, seed=3, loop=True)
+    ia = iter(a)
+    head = [next(ia)[0] for _ in range(130)]
+    b = TokenShardDataset(str(tmp_path / "s.bin"), 10, seed=3, loop=True)
+    b.load_state_dict(a.state_dict())
+    ib = iter(b)
+    assert head + [next(ib)[0] for _ in range(120)] == seq
+    with pytest.raises(ValueError):
+        TokenShardDataset(str(tmp_path / "s.bin"), 20, seed=3).load_state_dict(a.state_dict())
+    assert len(list(TokenShardDataset(str(tmp_path / "s.bin"), 10))) == 100       # single pass without loop
