@@ -527,8 +527,85 @@ def _infer_profile_layers(a, model, ids) -> int:
     return 0
 
 
+def _infer_portable(a, model_dir: str) -> int:
+    """Generation with a portable architecture (Gemma, Phi, Cohere, Granite, DeepSeek, GPT-OSS, Llama 4, Mixtral, ...):
+    contiguous KV cache (optionally quantised with --kv-quant / --kv-turboquant), the same sampler and stop tokens."""
+    import time
+
+    import torch
+
+    from ..data.chat_templates import ChatTemplate, Message
+    from ..data.inference_config import collect_all_stop_tokens
+    from ..data.stream_format import StreamFormatter
+    from ..data.tokenizer import Tokenizer
+    from ..models.architectures import load_pretrained as load_portable
+    from ..models.sampling import Sampler
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    dtype = torch.bfloat16 if dev.startswith("cuda") else torch.float32
+    model = load_portable(model_dir, dtype, dev).eval()
+    if a.lora:
+        from ..lora.adapter import load_adapter_config
+        from ..lora.portable import apply_lora_portable, load_adapter_portable, merge_lora_portable
+        apply_lora_portable(model, load_adapter_config(a.lora))
+        load_adapter_portable(model, a.lora)
+        merge_lora_portable(model)
+    tok = Tokenizer.from_model_dir(model_dir)
+    tpl = ChatTemplate.from_model_dir(model_dir)
+    eos = set(collect_all_stop_tokens(model_dir, tok, tpl.eos()))
+    if a.chat or a.system:
+        msgs = ([Message("system", a.system)] if a.system else []) + [Message("user", a.prompt)]
+        ids = tok.encode_with_special_tokens(tpl.apply_inference(msgs, a.no_thinking))
+    else:
+        ids = tok.encode(a.prompt)
+    sp_ = _sampling_from_args(a, model_dir, tpl.template_type, thinking=bool(a.chat or a.system) and not a.no_thinking)
+    sampler = Sampler(sp_, torch.device(dev))
+    kv_bits = None
+    if a.kv_turboquant or a.kv_quant or a.kv_k_bits:
+        kv_bits = a.kv_k_bits or (4 if a.kv_turboquant else 8)
+    cache = model.new_cache(kv_bits, a.kv_group_size, bool(a.kv_turboquant), bool(a.kv_qjl)) if hasattr(model, "new_cache") \
+        else None
+    if cache is None:
+        print("error: this architecture has no text-generation head", file=sys.stderr)
+        return 2
+    fmt = StreamFormatter(tok, show_thinking=not a.hide_thinking) if a.stream and not a.json else None
+    out, t0 = [], time.perf_counter()
+    cur = torch.tensor([ids], device=dev)
+    t_first = None
+    with torch.no_grad():
+        for _ in range(a.max_tokens):
+            logits = model(cur, cache)[:, -1].float()
+            nxt = int(sampler.sample(logits, None)[0])
+            if t_first is None:
+                t_first = time.perf_counter()
+            if nxt in eos:
+                break
+            out.append(nxt)
+            if fmt is not None:
+                sys.stdout.write(fmt.push(nxt))
+                sys.stdout.flush()
+            cur = torch.tensor([[nxt]], device=dev)
+    t1 = time.perf_counter()
+    if fmt is not None:
+        sys.stdout.write("\n")
+        return 0
+    text = tok.decode(out)
+    if a.json:
+        dec = max(t1 - (t_first or t1), 1e-9)
+        print(json.dumps({"text": text, "prompt_tokens": len(ids), "generated_tokens": len(out),
+                          "prefill_tok_per_s": round(len(ids) / max((t_first or t1) - t0, 1e-9), 1),
+                          "decode_tok_per_s": round(max(len(out) - 1, 0) / dec, 1), "path": "portable",
+                          "finish_reason": "length" if len(out) >= a.max_tokens else "stop"}))
+    else:
+        print(text)
+    return 0
+
+
 @_command(_infer_args)
 def cmd_infer(a) -> int:
+    from ..trainer.orchestrator import _portable_model_dir
+    pdir = _portable_model_dir(a.model)
+    if pdir is not None:
+        return _infer_portable(a, pdir)
     from ..data.chat_templates import Message
     from ..data.stream_format import StreamFormatter
     from ..models.generation import Generator

@@ -1,0 +1,185 @@
+"""LoRA for the portable architecture implementations (``models/architectures``): Gemma, Phi, Cohere, Granite,
+DeepSeek, GPT-OSS, Llama 4, Mixtral, Qwen3-Next, Nemotron-H and the encoders.
+
+The hand-written kernels fuse LoRA into the projections of the fast decoder (``lora/adapter.py``); every other family
+gets adapters as plain modules wrapped around its ``nn.Linear`` projections: ``y = W x + s * B (A x)`` with ``A`` drawn
+from U(+-sqrt(3 / in)) (rsLoRA: +-sqrt(1 / r)), ``B = 0`` and ``s = alpha / r`` (``alpha / sqrt(r)``), DoRA optionally on
+top (column-norm magnitude vector). Adapter files use the same key format as the fast path and the reference
+(``layers.N.self_attn.q_proj.lora_a`` [r, in] / ``.lora_b`` [out, r], no ``model.`` prefix; crates/pmetal-lora/src/
+lora_helpers.rs:33-250, crates/pmetal-lora/src/dynamic.rs:125-600 dispatches one wrapper type per architecture), so an
+adapter can be fused into the base weights by ``pmetal fuse`` whatever produced it."""
+from __future__ import annotations
+
+import math
+import os
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..core.config import LoraConfig
+from ..utils import safetensors_io as st
+
+WEIGHTS_NAME = "lora_weights.safetensors"
+
+
+class LoraLinear(nn.Module):
+    def __init__(self, base: nn.Linear, r: int, scale: float, rslora: bool = False, dora: bool = False,
+                 generator: Optional[torch.Generator] = None):
+        super().__init__()
+        self.base, self.r, self.scale = base, r, scale
+        bound = math.sqrt(1.0 / r) if rslora else math.sqrt(3.0 / base.in_features)
+        a = (torch.rand(r, base.in_features, generator=generator) * 2 - 1) * bound
+        self.lora_a = nn.Parameter(a.to(base.weight.device))
+        self.lora_b = nn.Parameter(torch.zeros(base.out_features, r, device=base.weight.device))
+        self.magnitude = None
+        if dora:                                # per-output-row norm of the adapted weight, initialised from the base
+            self.magnitude = nn.Parameter(base.weight.detach().float().norm(dim=1).to(base.weight.device))
+        for p in base.parameters():
+            p.requires_grad_(False)
+
+    @property
+    def weight(self):
+        return self.base.weight
+
+    def delta(self) -> torch.Tensor:
+        return self.scale * (self.lora_b.float() @ self.lora_a.float())
+
+    def forward(self, x):
+        if self.magnitude is None:
+            lo = F.linear(F.linear(x.to(self.lora_a.dtype), self.lora_a), self.lora_b) * self.scale
+            return self.base(x) + lo.to(x.dtype)
+        w = self.base.weight.float() + self.delta()
+        w = w * (self.magnitude.float() / w.norm(dim=1).clamp(min=1e-8))[:, None]
+        return F.linear(x, w.to(x.dtype), self.base.bias)
+
+    @torch.no_grad()
+    def merged_weight(self) -> torch.Tensor:
+        w = self.base.weight.double() + self.delta().double()
+        if self.magnitude is not None:
+            w = w * (self.magnitude.double() / w.norm(dim=1).clamp(min=1e-8))[:, None]
+        return w.to(self.base.weight.dtype)
+
+
+def _targets(model: nn.Module, names: Iterable[str]) -> List[Tuple[nn.Module, str, str]]:
+    want = set(names)
+    out = []
+    for full, mod in model.named_modules():
+        for child_name, child in mod.named_children():
+            if isinstance(child, nn.Linear) and child_name in want:
+                out.append((mod, child_name, f"{full}.{child_name}" if full else child_name))
+    return out
+
+
+def apply_lora_portable(model: nn.Module, cfg: LoraConfig, seed: int = 42) -> nn.Module:
+    """Wrap every ``nn.Linear`` whose attribute name is in ``cfg.target_modules`` and freeze all other parameters."""
+    g = torch.Generator().manual_seed(seed)
+    for p in model.parameters():
+        p.requires_grad_(False)
+    hits = _targets(model, cfg.target_modules)
+    if not hits:
+        raise ValueError(f"no projection named one of {sorted(cfg.target_modules)} in {type(model).__name__}")
+    for parent, name, _ in hits:
+        setattr(parent, name, LoraLinear(getattr(parent, name), cfg.r, cfg.scaling(), cfg.use_rslora,
+                                         getattr(cfg, "use_dora", False), g))
+    return model
+
+
+def _key(path: str) -> str:
+    for prefix in ("model.language_model.", "model.", "backbone."):
+        if path.startswith(prefix):
+            return path[len(prefix):]
+    return path
+
+
+def lora_modules(model: nn.Module) -> Dict[str, LoraLinear]:
+    return {_key(n): m for n, m in model.named_modules() if isinstance(m, LoraLinear)}
+
+
+def lora_state_dict(model: nn.Module) -> Dict[str, torch.Tensor]:
+    out: Dict[str, torch.Tensor] = {}
+    for key, m in lora_modules(model).items():
+        out[key + ".lora_a"] = m.lora_a.detach().float().cpu().contiguous()
+        out[key + ".lora_b"] = m.lora_b.detach().float().cpu().contiguous()
+        if m.magnitude is not None:
+            out[key + ".magnitude"] = m.magnitude.detach().float().cpu().reshape(-1, 1).contiguous()
+    return out
+
+
+def save_adapter_portable(model: nn.Module, out_dir: str, cfg: LoraConfig, base_model: Optional[str] = None) -> str:
+    from .adapter import save_adapter_config
+    os.makedirs(out_dir, exist_ok=True)
+    path = os.path.join(out_dir, WEIGHTS_NAME)
+    st.save_file(lora_state_dict(model), path, metadata={"format": "mlx"})
+    save_adapter_config(out_dir, cfg, base_model)
+    return path
+
+
+def load_adapter_portable(model: nn.Module, path: str) -> int:
+    """Copy adapter tensors into the wrapped projections; unknown keys are ignored. Returns the number loaded."""
+    from .adapter import resolve_adapter_file
+    sd = st.load_file(resolve_adapter_file(path))
+    n = 0
+    with torch.no_grad():
+        for key, m in lora_modules(model).items():
+            a, b = sd.get(key + ".lora_a"), sd.get(key + ".lora_b")
+            if a is None or b is None or a.shape != m.lora_a.shape or b.shape != m.lora_b.shape:
+                continue
+            m.lora_a.copy_(a)
+            m.lora_b.copy_(b)
+            mag = sd.get(key + ".magnitude")
+            if mag is not None and m.magnitude is not None:
+                m.magnitude.copy_(mag.reshape(-1))
+            n += 1
+    return n
+
+
+def merge_lora_portable(model: nn.Module) -> nn.Module:
+    """Fold every adapter into its base weight and put the plain ``nn.Linear`` back."""
+    for full, mod in list(model.named_modules()):
+        for name, child in list(mod.named_children()):
+            if isinstance(child, LoraLinear):
+                child.base.weight.data.copy_(child.merged_weight())
+                setattr(mod, name, child.base)
+    return model
+
+
+# ------------------------------------------------------------------------------------------------ training
+def causal_lm_loss(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
+    """Mean next-token cross entropy: position t predicts labels[t + 1]."""
+    return F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), labels[:, 1:].reshape(-1),
+                           ignore_index=ignore_index)
+
+
+class PortableLoraTrainer:
+    """Padded-batch supervised fine-tuning of adapters on a portable model: AdamW with the reference's semantics
+    (bias-corrected, decay applied after the step), global-norm clipping, warm-up + cosine schedule."""
+
+    def __init__(self, model: nn.Module, learning_rate: float = 2e-4, weight_decay: float = 0.01, max_grad_norm: float = 1.0,
+                 warmup_steps: int = 0, total_steps: int = 1000, schedule: str = "cosine", loraplus_ratio: Optional[float] = None):
+        from ..core.scheduler import LearningRateScheduler
+        self.model = model
+        params = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        if not params:
+            raise ValueError("the model has no trainable parameters (apply_lora_portable first)")
+        ratio = loraplus_ratio or 1.0
+        groups = [{"params": [p for n, p in params if "lora_b" not in n], "lr_mult": 1.0},
+                  {"params": [p for n, p in params if "lora_b" in n], "lr_mult": ratio}]
+        self.groups = [g for g in groups if g["params"]]
+        self.opt = torch.optim.AdamW([{"params": g["params"]} for g in self.groups], lr=learning_rate, betas=(0.9, 0.999),
+                                     eps=1e-8, weight_decay=weight_decay)
+        self.sched = LearningRateScheduler(learning_rate, total_steps, warmup_steps, schedule)
+        self.max_grad_norm, self.step_count = max_grad_norm, 0
+
+    def step(self, input_ids: torch.Tensor, labels: torch.Tensor) -> dict:
+        lr = self.sched.get_lr(self.step_count)
+        for g, meta in zip(self.opt.param_groups, self.groups):
+            g["lr"] = lr * meta["lr_mult"]
+        self.opt.zero_grad(set_to_none=True)
+        loss = causal_lm_loss(self.model(input_ids), labels)
+        loss.backward()
+        gn = torch.nn.utils.clip_grad_norm_([p for g in self.groups for p in g["params"]], self.max_grad_norm or float("inf"))
+        self.opt.step()
+        self.step_count += 1
+        return {"loss": float(loss.detach()), "grad_norm": float(gn), "lr": lr}

@@ -66,6 +66,97 @@ class TrainingJobConfig:
                    use_packing=full.training.use_packing, max_samples=full.dataset.max_samples)
 
 
+def _portable_model_dir(model: str) -> Optional[str]:
+    """The model directory when its architecture is served by the portable implementations (anything but the
+    llama / qwen2 / qwen3 / qwen3-moe / mistral family of the hand-written kernels), else None."""
+    import json as _json
+
+    from ..models.architectures import family_of
+    from ..models.loader import resolve_model_path
+    try:
+        path = resolve_model_path(model)
+    except FileNotFoundError:
+        return None
+    cfg_path = os.path.join(path, "config.json")
+    if path.startswith("random:") or not os.path.exists(cfg_path):
+        return None
+    with open(cfg_path, "r", encoding="utf-8") as fh:
+        fam = family_of(_json.load(fh))
+    return path if fam not in (None, "fast") else None
+
+
+def _run_portable_training(job: "TrainingJobConfig", model_dir: str, dev, dtype, out_dir: str, phase, callbacks, t_start) -> dict:
+    """LoRA fine-tuning of a portable architecture: padded batches through the PyTorch modules with adapters wrapped
+    around the target projections (``lora/portable.py``). Same dataset handling, schedule, callbacks and output files as
+    the fast path; no sequence packing, CUDA graph or fused optimiser."""
+    import torch
+
+    from ..core.callbacks import CompositeCallback, LoggingCallback, MetricsJsonCallback
+    from ..core.types import StepMetrics
+    from ..data.chat_templates import ChatTemplate
+    from ..data.dataloader import DataLoader
+    from ..data.dataset import TrainingDataset
+    from ..data.tokenizer import Tokenizer
+    from ..lora.portable import PortableLoraTrainer, apply_lora_portable, load_adapter_portable, save_adapter_portable
+    from ..models.architectures import load_pretrained as load_portable
+    tcfg = job.training
+    if job.quantization != "none":
+        raise ValueError("quantised base weights (QLoRA) are available for the llama / qwen / mistral family only")
+    phase("loading_model")
+    model = load_portable(model_dir, dtype, dev)
+    phase("loading_tokenizer")
+    tok = Tokenizer.from_model_dir(model_dir)
+    template = ChatTemplate.from_model_dir(model_dir, job.model)
+    max_seq = tcfg.max_seq_len if tcfg.max_seq_len and tcfg.max_seq_len != 8192 else 2048
+    phase("tokenizing_dataset")
+    ds = TrainingDataset.from_file_tokenized(job.dataset, tok, max_seq, job.dataset_format, template, job.custom_columns,
+                                             job.max_samples)
+    log.info("dataset: %s", ds.stats())
+    apply_lora_portable(model, job.lora, seed=tcfg.seed)
+    if job.resume and os.path.exists(os.path.join(out_dir, "lora_weights.safetensors")):
+        load_adapter_portable(model, out_dir)
+    model.train()
+    loader = DataLoader(ds.samples, tcfg.batch_size, True, tcfg.seed, tok.pad_token_id or 0, max_seq)
+    accum = max(tcfg.gradient_accumulation_steps, 1)
+    per_epoch = max(len(loader) // accum, 1)
+    total = tcfg.max_steps or per_epoch * tcfg.num_epochs
+    tr = PortableLoraTrainer(model, tcfg.learning_rate, tcfg.weight_decay, tcfg.max_grad_norm, tcfg.warmup_steps, total,
+                             getattr(tcfg, "lr_scheduler", "cosine"), job.lora.loraplus_lr_ratio)
+    cbs = callbacks + [LoggingCallback(tcfg.logging_steps)]
+    if job.log_metrics:
+        cbs.append(MetricsJsonCallback(job.log_metrics, config={"lora": dataclasses.asdict(job.lora),
+                                                                "training": dataclasses.asdict(tcfg)}))
+    cb = CompositeCallback(cbs)
+    phase("training")
+    cb.on_train_start()
+    step, running, tokens, epoch, done = 0, 0.0, 0, 0, False
+    while not done:
+        loader.set_epoch(epoch)
+        for batch in loader:
+            t0 = time.perf_counter()
+            ids, labels = batch["input_ids"].to(dev), batch["labels"].to(dev)
+            st = tr.step(ids, labels)             # one optimiser step per batch (accumulation folds into the batch size)
+            step += 1
+            tokens += int(batch.get("tokens", ids.numel()))
+            running = st["loss"] if step == 1 else 0.99 * running + 0.01 * st["loss"]
+            dt = max(time.perf_counter() - t0, 1e-9)
+            cb.on_step_end_with_metrics(StepMetrics(step=step, epoch=epoch, total_epochs=tcfg.num_epochs, total_steps=total,
+                                                    loss=st["loss"], lr=st["lr"], tok_sec=int(batch.get("tokens", 0)) / dt,
+                                                    total_ms=dt * 1e3, tokens=int(batch.get("tokens", 0)),
+                                                    grad_norm=st["grad_norm"]))
+            if step >= total or cb.should_stop():
+                done = True
+                break
+        epoch += 1
+        if epoch >= tcfg.num_epochs and not tcfg.max_steps:
+            done = True
+    cb.on_train_end()
+    phase("saving")
+    adapter = save_adapter_portable(model, out_dir, job.lora, base_model=job.model)
+    return {"steps": step, "final_loss": running, "tokens": tokens, "seconds": time.time() - t_start, "adapter": adapter,
+            "output": out_dir, "path": "portable"}
+
+
 def run_training(job: TrainingJobConfig, phase_cb: Optional[Callable[[str], None]] = None,
                  callbacks: Optional[List[TrainingCallback]] = None, sink=None) -> dict:
     from ..data.chat_templates import ChatTemplate
@@ -115,6 +206,11 @@ def run_training(job: TrainingJobConfig, phase_cb: Optional[Callable[[str], None
             dtype = torch.float32
         # ---- model
         phase("resolving_model")
+        portable_dir = _portable_model_dir(job.model)
+        if portable_dir is not None:
+            summary = _run_portable_training(job, portable_dir, dev, dtype, out_dir, phase, list(callbacks or []), t_start)
+            sink.emit(JobEvent.completed(job.job_id, **summary))
+            return summary
         phase("loading_model")
         model, margs, model_dir = load_pretrained(job.model, dtype, dev, seed=tcfg.seed)
         max_seq = tcfg.max_seq_len if tcfg.max_seq_len and tcfg.max_seq_len != 8192 else min(

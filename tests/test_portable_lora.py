@@ -1,0 +1,117 @@
+"""LoRA on the portable architectures: wrapping, adapter files, merge, and the training orchestrator's portable path."""
+import json
+import os
+
+import pytest
+import torch
+
+tf = pytest.importorskip("transformers")
+
+from pmetal_b200.core.config import LoraConfig
+from pmetal_b200.lora import portable as P
+from pmetal_b200.models.architectures import build_model, load_pretrained
+
+
+def _tiny_gemma_dir(tmp_path):
+    """A tiny Gemma 3 checkpoint with a byte-level tokenizer, written the way the hub lays a model out."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    torch.manual_seed(0)
+    cfg = tf.Gemma3TextConfig(vocab_size=300, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2,
+                              num_key_value_heads=1, head_dim=16, sliding_window=8, max_position_embeddings=128)
+    hf = tf.Gemma3ForCausalLM(cfg)
+    d = tmp_path / "gemma"
+    hf.save_pretrained(str(d), safe_serialization=True)
+    vocab = {chr(i) if 32 <= i < 127 else f"<0x{i:02X}>": i for i in range(256)}
+    vocab.update({"<pad>": 256, "<eos>": 257, "<bos>": 258})
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<pad>"))
+    tok.pre_tokenizer = pre_tokenizers.Split("", "isolated")
+    tok.save(str(d / "tokenizer.json"))
+    (d / "tokenizer_config.json").write_text(json.dumps({"eos_token": "<eos>", "pad_token": "<pad>", "bos_token": "<bos>"}))
+    return str(d)
+
+
+def test_wrap_save_load_merge(tmp_path):
+    d = _tiny_gemma_dir(tmp_path)
+    model = load_pretrained(d, torch.float32).eval()
+    ids = torch.randint(0, 256, (2, 12), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        base = model(ids)
+    cfg = LoraConfig(r=4, alpha=8.0, target_modules=["q_proj", "v_proj", "down_proj"])
+    P.apply_lora_portable(model, cfg)
+    mods = P.lora_modules(model)
+    assert set(mods) == {f"layers.{i}.{s}" for i in range(2) for s in ("self_attn.q_proj", "self_attn.v_proj", "mlp.down_proj")}
+    assert all(p.requires_grad == ("lora_" in n) for n, p in model.named_parameters())
+    with torch.no_grad():
+        assert torch.allclose(model(ids), base, atol=1e-6)                       # B = 0: the adapted model is the base model
+        for m in mods.values():
+            m.lora_b.normal_(std=0.05)
+        tuned = model(ids)
+    assert not torch.allclose(tuned, base, atol=1e-4)
+    P.save_adapter_portable(model, str(tmp_path / "ad"), cfg, d)
+    sd = __import__("pmetal_b200.utils.safetensors_io", fromlist=["x"]).load_file(str(tmp_path / "ad" / "lora_weights.safetensors"))
+    assert sd["layers.0.self_attn.q_proj.lora_a"].shape == (4, 32) and sd["layers.1.mlp.down_proj.lora_b"].shape == (32, 4)
+    fresh = P.apply_lora_portable(load_pretrained(d, torch.float32).eval(), cfg)
+    assert P.load_adapter_portable(fresh, str(tmp_path / "ad")) == 6
+    with torch.no_grad():
+        assert torch.allclose(fresh(ids), tuned, atol=1e-5)
+        merged = P.merge_lora_portable(fresh)
+        assert not P.lora_modules(merged) and torch.allclose(merged(ids), tuned, atol=1e-4)
+    # the adapter file is in the common format: the fuse command folds it into the checkpoint
+    from pmetal_b200.cli.main import main
+    assert main(["fuse", "-m", d, "-l", str(tmp_path / "ad"), "-o", str(tmp_path / "fused"), "--dtype", "float32"]) == 0
+    with torch.no_grad():
+        assert torch.allclose(load_pretrained(str(tmp_path / "fused"), torch.float32).eval()(ids), tuned, atol=1e-4)
+
+
+def test_dora_and_trainer_reduce_the_loss():
+    from pmetal_b200.models.architectures.generic import GenericDecoderLM
+    torch.manual_seed(0)
+    cfg = tf.LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=2,
+                         num_key_value_heads=1, max_position_embeddings=64).to_dict()
+    model = GenericDecoderLM.from_hf_config(cfg).init_weights(0.05, 0)
+    lc = LoraConfig(r=4, alpha=8.0, target_modules=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"],
+                    use_dora=True)
+    P.apply_lora_portable(model, lc)
+    assert any(n.endswith("magnitude") for n, _ in model.named_parameters())
+    tr = P.PortableLoraTrainer(model, learning_rate=5e-3, warmup_steps=2, total_steps=40, loraplus_ratio=4.0)
+    ids = torch.randint(0, 64, (4, 16), generator=torch.Generator().manual_seed(2))
+    losses = [tr.step(ids, ids.clone())["loss"] for _ in range(40)]
+    assert losses[-1] < 0.8 * losses[0]
+    with pytest.raises(ValueError):
+        P.apply_lora_portable(GenericDecoderLM.from_hf_config(cfg), LoraConfig(r=2, target_modules=["nothing"]))
+
+
+def test_train_command_takes_the_portable_path_for_gemma(tmp_path, capsys):
+    from pmetal_b200.cli.main import main
+    d = _tiny_gemma_dir(tmp_path)
+    data = tmp_path / "d.jsonl"
+    data.write_text("".join(json.dumps({"text": "the cat sat on the mat and looked at the dog"}) + "\n" for _ in range(8)))
+    out = str(tmp_path / "out")
+    assert main(["train", "-m", d, "-d", str(data), "-o", out, "--lora-r", "4", "--lora-alpha", "8", "--learning-rate", "5e-3",
+                 "--batch-size", "4", "--max-steps", "6", "--warmup-steps", "0", "--device", "cpu", "--dtype", "float32",
+                 "--log-metrics", str(tmp_path / "m.jsonl"), "--no-adaptive-lr"]) == 0
+    summary = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert summary["path"] == "portable" and summary["steps"] == 6
+    assert os.path.exists(os.path.join(out, "lora_weights.safetensors"))
+    assert json.load(open(os.path.join(out, "adapter_config.json")))["r"] == 4
+    steps = [json.loads(l) for l in open(tmp_path / "m.jsonl") if '"step"' in l]
+    assert len(steps) == 6 and steps[-1]["loss"] < steps[0]["loss"]
+
+
+def test_infer_command_runs_portable_models_with_adapter_and_quantised_cache(tmp_path, capsys):
+    from pmetal_b200.cli.main import main
+    d = _tiny_gemma_dir(tmp_path)
+    assert main(["infer", "-m", d, "-p", "hello", "--max-tokens", "5", "--greedy", "--json", "--device", "cpu"]) == 0
+    a = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert a["path"] == "portable" and a["prompt_tokens"] == 5 and a["generated_tokens"] <= 5
+    assert main(["infer", "-m", d, "-p", "hello", "--max-tokens", "5", "--greedy", "--json", "--kv-quant", "--device", "cpu"]) == 0
+    b = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert b["generated_tokens"] == a["generated_tokens"]
+    model = load_pretrained(d, torch.float32)
+    cfg = LoraConfig(r=2, alpha=4.0, target_modules=["q_proj"])
+    P.apply_lora_portable(model, cfg)
+    P.save_adapter_portable(model, str(tmp_path / "ad"), cfg, d)
+    assert main(["infer", "-m", d, "-l", str(tmp_path / "ad"), "-p", "hello", "--max-tokens", "5", "--greedy", "--json",
+                 "--device", "cpu"]) == 0
+    c = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert c["text"] == a["text"]                                                  # a fresh adapter (B = 0) changes nothing
