@@ -1145,6 +1145,34 @@ def cmd_eval(a) -> int:
     import math
 
     import torch
+
+    from ..trainer.orchestrator import _portable_model_dir
+    pdir = _portable_model_dir(a.model)
+    if pdir is not None:                      # portable architecture: logits straight from the module
+        from ..data.tokenizer import Tokenizer
+        from ..models.architectures import load_pretrained as load_portable
+        dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+        model = load_portable(pdir, torch.bfloat16 if dev.startswith("cuda") else torch.float32, dev).eval()
+        if a.lora:
+            from ..lora.adapter import load_adapter_config
+            from ..lora.portable import apply_lora_portable, load_adapter_portable
+            apply_lora_portable(model, load_adapter_config(a.lora))
+            load_adapter_portable(model, a.lora)
+        tok = Tokenizer.from_model_dir(pdir)
+        seqs = [s[: a.max_seq_len] for s in _read_prompts(a.dataset, tok, a.max_samples) if len(s) > 1]
+        tot, n, correct = 0.0, 0, 0
+        with torch.no_grad():
+            for s in seqs:
+                ids = torch.tensor([s], dtype=torch.int64, device=dev)
+                logits = model(ids)[0, :-1].float()
+                tot += float(torch.nn.functional.cross_entropy(logits, ids[0, 1:], reduction="sum"))
+                correct += int((logits.argmax(-1) == ids[0, 1:]).sum())
+                n += ids.shape[1] - 1
+        loss = tot / max(n, 1)
+        print(json.dumps({"samples": len(seqs), "tokens": n, "loss": round(loss, 5),
+                          "perplexity": round(math.exp(min(loss, 50)), 4), "token_accuracy": round(correct / max(n, 1), 5),
+                          "path": "portable"}))
+        return 0
     model, tok, _, _, _ = _load_for_inference(a)
     seqs = [s[: a.max_seq_len] for s in _read_prompts(a.dataset, tok, a.max_samples) if len(s) > 1]
     tot, n, correct = 0.0, 0, 0

@@ -115,3 +115,19 @@ def test_infer_command_runs_portable_models_with_adapter_and_quantised_cache(tmp
                  "--device", "cpu"]) == 0
     c = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert c["text"] == a["text"]                                                  # a fresh adapter (B = 0) changes nothing
+
+
+def test_eval_command_on_a_portable_model_sees_the_adapter(tmp_path, capsys):
+    from pmetal_b200.cli.main import main
+    d = _tiny_gemma_dir(tmp_path)
+    data = tmp_path / "d.jsonl"
+    data.write_text("".join(json.dumps({"text": "the cat sat on the mat and looked at the dog"}) + "\n" for _ in range(8)))
+    out = str(tmp_path / "out")
+    assert main(["train", "-m", d, "-d", str(data), "-o", out, "--lora-r", "4", "--learning-rate", "1e-2", "--batch-size", "4",
+                 "--max-steps", "12", "--warmup-steps", "0", "--device", "cpu", "--dtype", "float32", "--no-adaptive-lr"]) == 0
+    capsys.readouterr()
+    assert main(["eval", "-m", d, "-d", str(data), "--device", "cpu"]) == 0
+    base = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert main(["eval", "-m", d, "-l", out, "-d", str(data), "--device", "cpu"]) == 0
+    tuned = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert base["path"] == "portable" and tuned["loss"] < base["loss"]
