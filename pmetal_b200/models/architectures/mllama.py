@@ -18,7 +18,7 @@ Parameter names match the published checkpoints (``model.vision_model.…``, ``m
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 import torch.nn as nn
