@@ -46,6 +46,7 @@ class MergeConfig:
     allow_mixed_dtype: bool = False
     dry_run: bool = False
     aux_paths: List[str] = field(default_factory=list)     # fisher / gram files for fisher and regmean
+    align_moe_experts: bool = False                        # permute each model's experts onto the first model's before merging
 
     @staticmethod
     def _params(d: Optional[dict], base: Optional[MergeParameters] = None) -> MergeParameters:
@@ -77,7 +78,7 @@ class MergeConfig:
         tok = d.get("tokenizer") or {}
         return cls(mm, models, d.get("base_model"), d.get("output_path"), d.get("dtype", "bfloat16"), g,
                    tok.get("source") if isinstance(tok, dict) else tok, slices, bool(d.get("allow_mixed_dtype")),
-                   bool(d.get("dry_run")), aux)
+                   bool(d.get("dry_run")), aux, bool(d.get("align_moe_experts") or d.get("align_experts")))
 
     @classmethod
     def from_yaml(cls, path: str) -> "MergeConfig":
@@ -134,13 +135,19 @@ def run_merge(cfg: MergeConfig, device: Optional[str] = None) -> dict:
         raise ValueError(f"tensor {missing[0]} is missing from one of the models")
     plan = {"method": cfg.merge_method, "tensors": len(names), "models": [m.model for m in cfg.models],
             "base": cfg.base_model, "dtype": cfg.dtype}
+    alignment = None
+    if cfg.align_moe_experts and len(cks) > 1:
+        from .moe_align import align_experts
+        alignment = align_experts(cks)
+        if alignment is not None:
+            plan["expert_alignment"] = {"layers": len(alignment.layers), "identity": alignment.is_identity()}
     if cfg.dry_run:
         return plan
     out: Dict[str, torch.Tensor] = {}
     odt = _dtype(cfg.dtype)
     params = [m.parameters for m in cfg.models]
     for n in names:
-        ts = [c.get(n).to(dev) for c in cks]
+        ts = [(alignment.fetch(c, i, n) if alignment is not None else c.get(n)).to(dev) for i, c in enumerate(cks)]
         if not cfg.allow_mixed_dtype and len({t.dtype for t in ts}) > 1:
             raise ValueError(f"mixed dtypes for {n}; set allow_mixed_dtype")
         if any(t.shape != ts[0].shape for t in ts):
