@@ -731,6 +731,8 @@ def _merge_args(sp):
     p.add_argument("--model-a")
     p.add_argument("--model-b")
     p.add_argument("--t", type=float, default=None, help="slerp interpolation: 0 = model a, 1 = model b")
+    p.add_argument("--sanity", choices=["off", "quick", "full"], default=None,
+                   help="checks on every merged tensor: NaN / infinity counts (quick, the default) plus statistics (full)")
     p.add_argument("--align-experts", action="store_true",
                    help="mixture-of-experts models: match every model's experts to the first model's before merging")
     p.add_argument("--weight-a", type=float, default=None)
@@ -766,6 +768,8 @@ def cmd_merge(a) -> int:
         cfg = MergeConfig.from_dict(d)
     if a.align_experts:
         cfg.align_moe_experts = True
+    if a.sanity:
+        cfg.sanity = a.sanity
     cfg.output_path = a.output
     print(json.dumps(run_merge(cfg, a.device)))
     return 0

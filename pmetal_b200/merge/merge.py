@@ -47,6 +47,7 @@ class MergeConfig:
     dry_run: bool = False
     aux_paths: List[str] = field(default_factory=list)     # fisher / gram files for fisher and regmean
     align_moe_experts: bool = False                        # permute each model's experts onto the first model's before merging
+    sanity: str = "quick"                                  # off | quick | full (merge/sanity.py)
 
     @staticmethod
     def _params(d: Optional[dict], base: Optional[MergeParameters] = None) -> MergeParameters:
@@ -78,7 +79,8 @@ class MergeConfig:
         tok = d.get("tokenizer") or {}
         return cls(mm, models, d.get("base_model"), d.get("output_path"), d.get("dtype", "bfloat16"), g,
                    tok.get("source") if isinstance(tok, dict) else tok, slices, bool(d.get("allow_mixed_dtype")),
-                   bool(d.get("dry_run")), aux, bool(d.get("align_moe_experts") or d.get("align_experts")))
+                   bool(d.get("dry_run")), aux, bool(d.get("align_moe_experts") or d.get("align_experts")),
+                   str(d.get("sanity", "quick")))
 
     @classmethod
     def from_yaml(cls, path: str) -> "MergeConfig":
@@ -164,8 +166,16 @@ def run_merge(cfg: MergeConfig, device: Optional[str] = None) -> dict:
             merged = merge_tensor("linear", ts, b, params, cfg.parameters)      # fallback_to_mean
         else:
             merged = merge_tensor(cfg.merge_method, ts, b, params, cfg.parameters, a)
-        if not torch.isfinite(merged).all():
-            raise ValueError(f"merge produced non-finite values in {n}")
+        from .sanity import check_tensor
+        if cfg.sanity == "off":
+            if not torch.isfinite(merged).all():
+                raise ValueError(f"merge produced non-finite values in {n}")
+        else:
+            rep = check_tensor(n, merged, cfg.sanity)
+            if rep.is_outlier():
+                plan.setdefault("outliers", []).append({"name": n, "mean": rep.mean, "std": rep.std, "abs_max": rep.abs_max})
+            if cfg.sanity == "full":
+                plan.setdefault("tensor_reports", []).append(rep.to_dict())
         out[n] = merged.to(odt).cpu()
     _write(cfg, out, cfg.tokenizer_source or cfg.base_model or cfg.models[0].model)
     for c in cks:

@@ -89,3 +89,25 @@ def test_dense_models_need_no_alignment(tmp_path):
     os.makedirs(tmp_path / "d")
     save_file({"model.layers.0.mlp.gate_proj.weight": torch.randn(4, 4)}, str(tmp_path / "d" / "model.safetensors"))
     assert align_experts([LazyCheckpoint(str(tmp_path / "d"))]) is None
+
+
+def test_merge_sanity_levels(tmp_path):
+    from pmetal_b200.merge.sanity import check_tensor
+    assert check_tensor("x", torch.ones(3), "off") is None
+    q = check_tensor("x", torch.tensor([0.0, 1.0, -3.0, 0.0]), "quick")
+    assert (q.n_elements, q.n_nan, q.n_inf, q.mean) == (4, 0, 0, None)
+    f = check_tensor("x", torch.tensor([0.0, 1.0, -3.0, 0.0]), "full")
+    assert f.abs_max == 3.0 and f.sparsity == 0.5 and abs(f.mean + 0.5) < 1e-6 and not f.is_outlier()
+    assert check_tensor("big", torch.full((4,), 50.0), "full").is_outlier()
+    for bad in (float("nan"), float("inf")):
+        with pytest.raises(ValueError):
+            check_tensor("x", torch.tensor([1.0, bad]), "quick")
+    for name, scale in (("a", 1.0), ("b", 200.0)):
+        os.makedirs(tmp_path / name)
+        save_file({"model.layers.0.mlp.down_proj.weight": torch.full((4, 4), scale)}, str(tmp_path / name / "model.safetensors"))
+        (tmp_path / name / "config.json").write_text("{}")
+    cfg = MergeConfig.from_dict({"merge_method": "linear", "dtype": "float32", "sanity": "full",
+                                 "models": [{"model": str(tmp_path / n), "parameters": {"weight": 0.5}} for n in "ab"]})
+    cfg.output_path = str(tmp_path / "o")
+    rep = run_merge(cfg, "cpu")
+    assert rep["outliers"][0]["name"].endswith("down_proj.weight") and len(rep["tensor_reports"]) == 1
