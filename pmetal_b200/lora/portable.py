@@ -153,8 +153,8 @@ def causal_lm_loss(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int
 
 
 class PortableLoraTrainer:
-    """Padded-batch supervised fine-tuning of adapters on a portable model: AdamW with the reference's semantics
-    (bias-corrected, decay applied after the step), global-norm clipping, warm-up + cosine schedule."""
+    """Padded-batch supervised fine-tuning of adapters on a portable model: ``torch.optim.AdamW`` (bias-corrected,
+    decoupled decay), global-norm clipping, warm-up + cosine schedule, optional LoRA+ learning-rate ratio for ``B``."""
 
     def __init__(self, model: nn.Module, learning_rate: float = 2e-4, weight_decay: float = 0.01, max_grad_norm: float = 1.0,
                  warmup_steps: int = 0, total_steps: int = 1000, schedule: str = "cosine", loraplus_ratio: Optional[float] = None):
@@ -183,3 +183,62 @@ class PortableLoraTrainer:
         self.opt.step()
         self.step_count += 1
         return {"loss": float(loss.detach()), "grad_norm": float(gn), "lr": lr}
+
+
+# ------------------------------------------------------------------------------------------------ Q-BLoRA
+class QBLoraLinear(nn.Module):
+    """Balanced adapter for quantised bases (Q-BLoRA; crates/pmetal-lora/src/qblora.rs:63-480):
+
+        y = W x + s * (((x P_in) A^T) B^T) P_out
+
+    The adapter sees a simplified input (``P_in`` [in, d_in]) and writes through a simplified output (``P_out``
+    [d_out, out]); in exchange its rank is ``rank_multiplier`` times the usual one. Projections are learnable or fixed
+    random maps scaled to preserve norms; ``B`` starts at zero, so the adapted layer starts equal to the base layer.
+    ``gradient_scale`` multiplies the adapter branch's gradient without changing its forward value."""
+
+    def __init__(self, base: nn.Module, in_features: int, out_features: int, r: int, scale: float,
+                 input_proj_dim: Optional[int] = None, output_proj_dim: Optional[int] = None, rank_multiplier: float = 2.0,
+                 learnable_projections: bool = True, gradient_scale: float = 1.0, generator: Optional[torch.Generator] = None):
+        super().__init__()
+        self.base, self.scale, self.gradient_scale = base, scale, gradient_scale
+        self.r = max(int(round(r * rank_multiplier)), 1)
+        d_in, d_out = input_proj_dim or in_features, output_proj_dim or out_features
+        g = generator
+
+        def rnd(*shape, std):
+            return torch.randn(*shape, generator=g) * std
+        self.lora_a = nn.Parameter((torch.rand(self.r, d_in, generator=g) * 2 - 1) * math.sqrt(3.0 / d_in))
+        self.lora_b = nn.Parameter(torch.zeros(d_out, self.r))
+        self.p_in = self.p_out = None
+        if input_proj_dim:
+            p = rnd(in_features, d_in, std=d_in ** -0.5)
+            self.p_in = nn.Parameter(p) if learnable_projections else None
+            if not learnable_projections:
+                self.register_buffer("p_in_fixed", p)
+        if output_proj_dim:
+            p = rnd(d_out, out_features, std=d_out ** -0.5)
+            self.p_out = nn.Parameter(p) if learnable_projections else None
+            if not learnable_projections:
+                self.register_buffer("p_out_fixed", p)
+        for q in base.parameters():
+            q.requires_grad_(False)
+
+    def adapter(self, x: torch.Tensor) -> torch.Tensor:
+        p_in = self.p_in if self.p_in is not None else getattr(self, "p_in_fixed", None)
+        p_out = self.p_out if self.p_out is not None else getattr(self, "p_out_fixed", None)
+        h = x.to(self.lora_a.dtype)
+        if p_in is not None:
+            h = h @ p_in
+        h = F.linear(F.linear(h, self.lora_a), self.lora_b)
+        if p_out is not None:
+            h = h @ p_out
+        return h * self.scale
+
+    def forward(self, x):
+        lo = self.adapter(x)
+        if self.gradient_scale != 1.0:                         # same value, scaled gradient
+            lo = lo.detach() + self.gradient_scale * (lo - lo.detach())
+        return self.base(x) + lo.to(x.dtype)
+
+    def trainable_parameters(self) -> List[nn.Parameter]:
+        return [p for p in (self.lora_a, self.lora_b, self.p_in, self.p_out) if p is not None]

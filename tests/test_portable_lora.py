@@ -131,3 +131,27 @@ def test_eval_command_on_a_portable_model_sees_the_adapter(tmp_path, capsys):
     assert main(["eval", "-m", d, "-l", out, "-d", str(data), "--device", "cpu"]) == 0
     tuned = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert base["path"] == "portable" and tuned["loss"] < base["loss"]
+
+
+def test_qblora_starts_at_the_base_and_balances_gradients():
+    torch.manual_seed(0)
+    base = torch.nn.Linear(32, 24, bias=False)
+    x = torch.randn(5, 32)
+    g = torch.Generator().manual_seed(1)
+    ad = P.QBLoraLinear(base, 32, 24, r=4, scale=2.0, input_proj_dim=16, output_proj_dim=12, rank_multiplier=2.0, generator=g)
+    assert ad.r == 8 and ad.lora_a.shape == (8, 16) and ad.lora_b.shape == (12, 8) and len(ad.trainable_parameters()) == 4
+    assert torch.allclose(ad(x), base(x)) and not base.weight.requires_grad
+    with torch.no_grad():
+        ad.lora_b.normal_(std=0.1)
+    want = base(x) + 2.0 * ((((x @ ad.p_in) @ ad.lora_a.t()) @ ad.lora_b.t()) @ ad.p_out)
+    assert torch.allclose(ad(x), want, atol=1e-5)
+    ad(x).sum().backward()
+    g1 = ad.lora_a.grad.clone()
+    ad.zero_grad()
+    ad.gradient_scale = 0.5
+    y = ad(x)
+    assert torch.allclose(y, want, atol=1e-5)                                  # the forward value does not change
+    y.sum().backward()
+    assert torch.allclose(ad.lora_a.grad, 0.5 * g1, atol=1e-6)
+    fixed = P.QBLoraLinear(torch.nn.Linear(32, 24), 32, 24, 4, 1.0, 16, None, learnable_projections=False)
+    assert len(fixed.trainable_parameters()) == 2 and fixed.p_in_fixed.shape == (32, 16)
