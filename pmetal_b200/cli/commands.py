@@ -1559,6 +1559,9 @@ def _search_args(sp):
     p.add_argument("--limit", type=int, default=20)
     p.add_argument("--online", action="store_true")
     p.add_argument("--tag")
+    p.add_argument("--detailed", action="store_true", help="full fit analysis (memory breakdown, training estimate) per result")
+    p.add_argument("--download", action="store_true", help="with --online: download the first result that fits this device")
+    p.add_argument("--json", action="store_true", help="the result is always JSON (accepted for compatibility)")
     return p
 
 
@@ -1596,9 +1599,22 @@ def cmd_search(a) -> int:
         except hub.HubError as e:
             print(f"error: {e}", file=sys.stderr)
             return 1
-        print(json.dumps({"query": a.query, "source": hub.endpoint(), "results": [
+        out = {"query": a.query, "source": hub.endpoint(), "results": [
             {"id": r.id, "downloads": hub.format_downloads(r.downloads), "likes": r.likes, "pipeline_tag": r.pipeline_tag}
-            for r in res]}, indent=2))
+            for r in res]}
+        if a.download and res:
+            # sizes are only known after a download, so take the results in order and keep the first that fits
+            for r in res:
+                try:
+                    path = hub.download_model(r.id, token=os.environ.get("HF_TOKEN"))
+                    fit = estimate_fit(path, 4096, 1, 16, "none")
+                except Exception as e:      # noqa: BLE001 - a failed candidate must not end the search
+                    out.setdefault("skipped", []).append({"id": r.id, "reason": str(e)[:200]})
+                    continue
+                if fit.get("fits", True):
+                    out["downloaded"] = {"id": r.id, "path": path, "fit": fit if a.detailed else fit.get("fits")}
+                    break
+        print(json.dumps(out, indent=2))
         return 0
     q = a.query.lower()
     rows = []
@@ -1609,6 +1625,8 @@ def cmd_search(a) -> int:
         try:
             fit = estimate_fit(snap, 4096, 1, 16, "none")
             row["fits"] = fit.get("fits")
+            if a.detailed:
+                row["fit"] = fit
         except Exception:
             pass
         rows.append(row)
