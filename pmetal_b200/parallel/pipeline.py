@@ -246,3 +246,54 @@ def run_local_pipeline(stage_fns: Sequence, micro_batches: Sequence):
     if errors:
         raise errors[0]
     return out
+
+
+class StreamMultiplexer:
+    """Routes activation / result messages of concurrent requests by their nonce.
+
+    The last pipeline stage answers on one channel for every request in flight; each request registers its nonce and
+    waits on its own queue, a reader thread (or the caller) hands every incoming message to :meth:`dispatch`. Messages
+    for a nonce nobody waits for are counted and dropped, so a cancelled request cannot block the channel
+    (crates/pmetal-distributed/src/pipeline.rs: the request router of the pipeline harness)."""
+
+    def __init__(self, max_pending: int = 1024):
+        import threading
+        self._lock = threading.Lock()
+        self._queues: dict = {}
+        self.max_pending = max_pending
+        self.dropped = 0
+
+    def register(self, nonce: int):
+        """Queue on which the messages of ``nonce`` will arrive; raises when the nonce is in use or the table is full."""
+        import queue
+        with self._lock:
+            if nonce in self._queues:
+                raise KeyError(f"nonce {nonce} is already registered")
+            if len(self._queues) >= self.max_pending:
+                raise RuntimeError("too many requests in flight")
+            q = self._queues[nonce] = queue.Queue()
+            return q
+
+    def dispatch(self, msg) -> bool:
+        """Deliver ``msg`` (anything with a ``nonce``) to its request; False when nobody is waiting for it."""
+        with self._lock:
+            q = self._queues.get(msg.nonce)
+            if q is None:
+                self.dropped += 1
+                return False
+        q.put(msg)
+        return True
+
+    def wait(self, nonce: int, timeout: Optional[float] = None):
+        """Next message of ``nonce`` (raises ``queue.Empty`` after ``timeout`` seconds)."""
+        with self._lock:
+            q = self._queues[nonce]
+        return q.get(timeout=timeout)
+
+    def close(self, nonce: int) -> None:
+        with self._lock:
+            self._queues.pop(nonce, None)
+
+    def pending(self) -> int:
+        with self._lock:
+            return len(self._queues)

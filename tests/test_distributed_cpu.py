@@ -337,3 +337,29 @@ def test_identity_fabric_discovery_and_bundle(tmp_path):
     import pytest
     with pytest.raises(RuntimeError):
         run_local_pipeline([lambda x: x, boom], range(3))
+
+
+def test_stream_multiplexer_routes_by_nonce():
+    import queue
+    import threading
+
+    import torch
+
+    from pmetal_b200.parallel.pipeline import ActivationMessage, StreamMultiplexer
+    mux = StreamMultiplexer(max_pending=3)
+    for n in (7, 8, 9):
+        mux.register(n)
+    with pytest.raises(KeyError):
+        mux.register(7)
+    with pytest.raises(RuntimeError):
+        mux.register(10)
+    msgs = [ActivationMessage(nonce=n, layer_id=i, tensor=torch.full((1, 1, 2), float(n))) for i, n in enumerate((9, 7, 8, 7))]
+    t = threading.Thread(target=lambda: [mux.dispatch(m) for m in msgs])
+    t.start()
+    got7 = [mux.wait(7, timeout=5).layer_id for _ in range(2)]
+    assert got7 == [1, 3] and mux.wait(8, timeout=5).nonce == 8 and float(mux.wait(9, timeout=5).tensor[0, 0, 0]) == 9.0
+    t.join()
+    mux.close(8)
+    assert not mux.dispatch(msgs[2]) and mux.dropped == 1 and mux.pending() == 2        # late message of a closed request
+    with pytest.raises(queue.Empty):
+        mux.wait(7, timeout=0.05)
