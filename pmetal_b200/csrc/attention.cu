@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "host_util.cuh"
 
 #include "pdl.cuh"
 
@@ -586,8 +587,8 @@ extern "C" int pm_attn_fwd(const void* q, long long q_stride, const void* k, lon
   p.q_stride = q_stride; p.k_stride = k_stride; p.v_stride = v_stride; p.o_stride = o_stride;
   p.seq_start = seq_start; p.lse = lse; p.T = T; p.hq = hq; p.hkv = hkv; p.scale = scale; p.window = window;
   const int smem = 5 * kTileBytes + 256;
-  static bool once = false;
-  if (!once) { int e = set_smem(reinterpret_cast<const void*>(attn_fwd_kernel), smem); if (e) return e; once = true; }
+  static DeviceOnce once;
+  if (once.pending()) { int e = set_smem(reinterpret_cast<const void*>(attn_fwd_kernel), smem); if (e) return e; once.mark(); }
   dim3 grid((T + kTile - 1) / kTile, hq);
   attn_fwd_kernel<<<grid, kAttnThreads, smem, st>>>(p);
   return static_cast<int>(cudaGetLastError());
@@ -610,13 +611,13 @@ extern "C" int pm_attn_bwd(const void* dout, const void* q, long long q_stride, 
   p.T = T; p.hq = hq; p.hkv = hkv; p.scale = scale; p.window = window;
   const int smem_dq = 6 * kTileBytes + 256;
   const int smem_dkv = 6 * kTileBytes + 6 * kTile * 4;
-  static bool once = false;
-  if (!once) {
+  static DeviceOnce once;
+  if (once.pending()) {
     int e = set_smem(reinterpret_cast<const void*>(attn_bwd_dq_kernel), smem_dq);
     if (e) return e;
     e = set_smem(reinterpret_cast<const void*>(attn_bwd_dkv_kernel), smem_dkv);
     if (e) return e;
-    once = true;
+    once.mark();
   }
   dim3 gq((T + kTile - 1) / kTile, hq);
   attn_bwd_dq_kernel<<<gq, kAttnThreads, smem_dq, st>>>(p);
@@ -906,11 +907,11 @@ extern "C" int pm_paged_attn(const void* q, const void* k_cache, const void* v_c
   p.q_tiles = (max_q * (hq / hkv) + kTile - 1) / kTile;
   if (p.q_tiles < 1) p.q_tiles = 1;
   const int smem = 5 * kTileBytes;
-  static bool once = false;
-  if (!once) {
+  static DeviceOnce once;
+  if (once.pending()) {
     int e = set_smem(reinterpret_cast<const void*>(paged_attn_kernel), smem);
     if (e) return e;
-    once = true;
+    once.mark();
   }
   dim3 grid(num_seqs * p.q_tiles, hkv, n_split);
   int e = static_cast<int>(launch_pdl(paged_attn_kernel, grid, dim3(kAttnThreads), static_cast<size_t>(smem), st, p));
@@ -926,7 +927,7 @@ extern "C" int pm_kv_append(const void* k, long long k_stride, const void* v, lo
   if (n_tokens <= 0) return 0;
   const long long work = static_cast<long long>(n_tokens) * hkv * 16;
   int grid = static_cast<int>((work + 255) / 256);
-  if (grid > 148 * 8) grid = 148 * 8;
+  if (grid > num_sms() * 8) grid = num_sms() * 8;
   kv_append_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k), k_stride,
                                          static_cast<const __nv_bfloat16*>(v), v_stride,
                                          static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), slots,

@@ -5,6 +5,7 @@
 namespace pm {
 
 constexpr int kFaThreads = 192;
+constexpr int kFaThreads2 = 320;              // TMA warp, MMA warp, two compute warp groups
 constexpr int kFaTile = 128;                 // queries per CTA and keys per tile
 constexpr int kFaBox = kFaTile * 64 * 2;     // one [128 rows][64 cols] bf16 box: 16 KB
 constexpr int kFaTileBytes = 2 * kFaBox;     // [128][128] bf16: 32 KB

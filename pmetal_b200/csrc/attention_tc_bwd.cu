@@ -11,6 +11,10 @@
 // A [128][128] bf16 tile in shared memory (two 128B-swizzled [128][64] boxes) is read by tcgen05.mma either
 // as a K-major operand (its rows are the M/N index) or as an MN-major operand (its rows are the reduction
 // index), which is how the same Q, dO, K tiles serve both products of each kernel without a transpose.
+//
+// Both kernels run 320 threads: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..9 = two compute warp groups.
+// The element-wise work has no row reductions (log-sum-exp and delta are inputs), so the two groups split the 128
+// columns of every row: group g handles the 32-column chunks 2g and 2g+1 of S / dP and of the output tiles.
 #include "attention_tc.cuh"
 
 namespace pm {
@@ -24,9 +28,10 @@ enum {
 // S is at taddr, dP at taddr + 128.
 template <bool kMask>
 __device__ __forceinline__ void dq_ds_rows(uint32_t taddr, uint32_t tile_addr, int r, float a, float b, float delta,
-                                           float scale, int lo, int span) {
+                                           float scale, int lo, int span, int c0) {
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int cc = 0; cc < 2; ++cc) {
+    const int c = c0 + cc;
     uint32_t sv[32], dv[32];
     tmem_ld_32x32b_x32(taddr + c * 32, sv);
     tmem_ld_32x32b_x32(taddr + 128 + c * 32, dv);
@@ -48,7 +53,7 @@ __device__ __forceinline__ void dq_ds_rows(uint32_t taddr, uint32_t tile_addr, i
 }
 
 // TMEM columns: [0,128) S   [128,256) dP   [256,384) dQ accumulator
-__global__ void __launch_bounds__(kFaThreads, 1)
+__global__ void __launch_bounds__(kFaThreads2, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                       const FaParams p) {
@@ -76,8 +81,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       mbar_init(&bar[kDqBarKvFree + i], 1);
     }
     mbar_init(&bar[kDqBarSpFull], 1);
-    mbar_init(&bar[kDqBarSpFree], 4);
-    mbar_init(&bar[kDqBarDsReady], 4);
+    mbar_init(&bar[kDqBarSpFree], 8);
+    mbar_init(&bar[kDqBarDsReady], 8);
     mbar_init(&bar[kDqBarDsFree], 1);
     mbar_init(&bar[kDqBarDqFull], 1);
     *abort_flag = 0;
@@ -158,6 +163,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
   } else {
     const int qd = warp & 3;
+    const int c0 = (warp >= 6) ? 2 : 0;        // first of the two 32-column chunks this warp group owns
     const int r = qd * 32 + lane;
     const int i = q0 + r;
     const int ic = min(i, p.T - 1);
@@ -182,8 +188,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int lo = max(st - j0, 0);
         const int span = (i < p.T) ? (min(i - j0, kFaTile - 1) - lo) : -1;
         const bool need_mask = (j0 + kFaTile - 1 > q0) || (j0 < st_max) || (q0 + kFaTile > p.T);
-        if (need_mask) dq_ds_rows<true>(tmem_base + lane_off, ds_addr, r, sl2, -lse2, dl, p.scale, lo, span);
-        else dq_ds_rows<false>(tmem_base + lane_off, ds_addr, r, sl2, -lse2, dl, p.scale, 0, 0);
+        if (need_mask) dq_ds_rows<true>(tmem_base + lane_off, ds_addr, r, sl2, -lse2, dl, p.scale, lo, span, c0);
+        else dq_ds_rows<false>(tmem_base + lane_off, ds_addr, r, sl2, -lse2, dl, p.scale, 0, 0, c0);
       }
       fence_async_smem();
       tc_fence_before();
@@ -197,7 +203,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tc_fence_after();
       __nv_bfloat16* drow = p.out + static_cast<long long>(ic) * p.o_stride + static_cast<long long>(h) * 128;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = c0 + cc;
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + 256 + c * 32 + lane_off, v);
         tmem_ld_wait();
@@ -238,9 +245,10 @@ enum {
 
 // P row for the dK/dV kernel: p = exp2(s*a + b) (masked), packed bf16 into pk[64].
 template <bool kMask>
-__device__ __forceinline__ void kv_p_row(uint32_t taddr, float a, float b, int lo, int span, uint32_t (&pk)[64]) {
+__device__ __forceinline__ void kv_p_row(uint32_t taddr, float a, float b, int lo, int span, int c0, uint32_t (&pk)[32]) {
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
+  for (int cc = 0; cc < 2; ++cc) {
+    const int c = c0 + cc;
     uint32_t sv[32];
     tmem_ld_32x32b_x32(taddr + c * 32, sv);
     tmem_ld_wait();
@@ -253,7 +261,7 @@ __device__ __forceinline__ void kv_p_row(uint32_t taddr, float a, float b, int l
         if (kMask) pv = (span >= 0 && static_cast<unsigned>(c * 32 + e + u - lo) <= static_cast<unsigned>(span)) ? pv : 0.f;
         p2[u] = pv;
       }
-      pk[c * 16 + (e >> 1)] = pack_bf16x2(p2[0], p2[1]);
+      pk[cc * 16 + (e >> 1)] = pack_bf16x2(p2[0], p2[1]);
     }
   }
 }
@@ -263,7 +271,7 @@ __device__ __forceinline__ void kv_p_row(uint32_t taddr, float a, float b, int l
 // the same [query][key] smem tile is then read as an MN-major A operand: dV += P^T dO, dK += dS^T Q.
 // S and dP have separate full/free barriers so that S of the next pair is computed while dS of this one is formed.
 // TMEM columns: [0,128) S   [128,256) dP   [256,384) dV accumulator   [384,512) dK accumulator
-__global__ void __launch_bounds__(kFaThreads, 1)
+__global__ void __launch_bounds__(kFaThreads2, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                        const FaParams p) {
@@ -291,12 +299,12 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&bar[kKvBarQdoFree + i], 1);
     }
     mbar_init(&bar[kKvBarSFull], 1);
-    mbar_init(&bar[kKvBarSFree], 4);
+    mbar_init(&bar[kKvBarSFree], 8);
     mbar_init(&bar[kKvBarDpFull], 1);
-    mbar_init(&bar[kKvBarDpFree], 4);
-    mbar_init(&bar[kKvBarPReady], 4);
+    mbar_init(&bar[kKvBarDpFree], 8);
+    mbar_init(&bar[kKvBarPReady], 8);
     mbar_init(&bar[kKvBarPFree], 1);
-    mbar_init(&bar[kKvBarDsReady], 4);
+    mbar_init(&bar[kKvBarDsReady], 8);
     mbar_init(&bar[kKvBarDsFree], 1);
     mbar_init(&bar[kKvBarAccFull], 1);
     *abort_flag = 0;
@@ -402,6 +410,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
   } else {
     const int qd = warp & 3;
+    const int grp = (warp >= 6) ? 1 : 0;   // warp group: owns column chunks 2*grp, 2*grp+1; writes dV (0) or dK (1)
+    const int c0 = 2 * grp;
     const int r = qd * 32 + lane;          // query row within the tile; key row in the epilogue
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     const float sl2 = p.scale * kFaLog2e;
@@ -422,9 +432,9 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
       if (!mbar_wait(&bar[kKvBarSFull], w & 1, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after();
-      uint32_t pk[64];
-      if (need_mask) kv_p_row<true>(tmem_base + lane_off, sl2, -lse2, lo, span, pk);
-      else kv_p_row<false>(tmem_base + lane_off, sl2, -lse2, 0, 0, pk);
+      uint32_t pk[32];
+      if (need_mask) kv_p_row<true>(tmem_base + lane_off, sl2, -lse2, lo, span, c0, pk);
+      else kv_p_row<false>(tmem_base + lane_off, sl2, -lse2, 0, 0, c0, pk);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar[kKvBarSFree]);
@@ -434,11 +444,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         break;
       }
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t ck[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) ck[e] = pk[c * 16 + e];
-        store_row_chunk_sw128(x_addr, r, c, ck);
+        for (int e = 0; e < 16; ++e) ck[e] = pk[cc * 16 + e];
+        store_row_chunk_sw128(x_addr, r, c0 + cc, ck);
       }
       fence_async_smem();
       __syncwarp();
@@ -447,15 +457,15 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (!mbar_wait(&bar[kKvBarDpFull], w & 1, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {        // dS = P * (dP - delta) * scale, in place over the packed P row
+      for (int cc = 0; cc < 2; ++cc) {     // dS = P * (dP - delta) * scale, in place over the packed P row
         uint32_t dv[32];
-        tmem_ld_32x32b_x32(tmem_base + 128 + c * 32 + lane_off, dv);
+        tmem_ld_32x32b_x32(tmem_base + 128 + (c0 + cc) * 32 + lane_off, dv);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const uint32_t pp = pk[c * 16 + e];
+          const uint32_t pp = pk[cc * 16 + e];
           const float p0 = __uint_as_float(pp << 16), p1 = __uint_as_float(pp & 0xffff0000u);
-          pk[c * 16 + e] = pack_bf16x2(p0 * (__uint_as_float(dv[2 * e]) - dl) * p.scale,
+          pk[cc * 16 + e] = pack_bf16x2(p0 * (__uint_as_float(dv[2 * e]) - dl) * p.scale,
                                        p1 * (__uint_as_float(dv[2 * e + 1]) - dl) * p.scale);
         }
       }
@@ -464,11 +474,11 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (lane == 0) mbar_arrive(&bar[kKvBarDpFree]);
       if (!mbar_wait(&bar[kKvBarPFree], w & 1, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t ck[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) ck[e] = pk[c * 16 + e];
-        store_row_chunk_sw128(x_addr, r, c, ck);
+        for (int e = 0; e < 16; ++e) ck[e] = pk[cc * 16 + e];
+        store_row_chunk_sw128(x_addr, r, c0 + cc, ck);
       }
       fence_async_smem();
       __syncwarp();
@@ -480,8 +490,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int jc = min(jrow, p.T - 1);
       __nv_bfloat16* krow = p.out + static_cast<long long>(jc) * p.o_stride + static_cast<long long>(hk) * 128;
       __nv_bfloat16* vrow = p.out2 + static_cast<long long>(jc) * p.o2_stride + static_cast<long long>(hk) * 128;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
+        const int half = grp;              // group 0 drains the dV accumulator, group 1 the dK accumulator
         __nv_bfloat16* dst = half ? krow : vrow;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -544,24 +554,24 @@ extern "C" int pm_attn_bwd_tc(const void* dout, long long do_stride, const void*
   p.lse = const_cast<float*>(lse); p.delta = delta; p.seq_start = seq_start;
   p.T = T; p.hq = hq; p.hkv = hkv; p.scale = scale; p.status = status;
   const int smem = 227 * 1024;
-  static bool once = false;
-  if (!once) {
+  static DeviceOnce once;
+  if (once.pending()) {
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     e = cudaFuncSetAttribute(attn_bwd_dkv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    once = true;
+    once.mark();
   }
   const int tiles = (T + kFaTile - 1) / kFaTile;
   p.out = static_cast<__nv_bfloat16*>(dq);
   p.o_stride = dq_stride;
-  attn_bwd_dq_tc_kernel<<<dim3(tiles, hq), kFaThreads, smem, st>>>(mq, mk, mv, mdo, p);
+  attn_bwd_dq_tc_kernel<<<dim3(tiles, hq), kFaThreads2, smem, st>>>(mq, mk, mv, mdo, p);
   int e = static_cast<int>(cudaGetLastError());
   if (e) return e;
   p.out = static_cast<__nv_bfloat16*>(dk);
   p.o_stride = dk_stride;
   p.out2 = static_cast<__nv_bfloat16*>(dv);
   p.o2_stride = dv_stride;
-  attn_bwd_dkv_tc_kernel<<<dim3(tiles, hkv), kFaThreads, smem, st>>>(mq, mk, mv, mdo, p);
+  attn_bwd_dkv_tc_kernel<<<dim3(tiles, hkv), kFaThreads2, smem, st>>>(mq, mk, mv, mdo, p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "host_util.cuh"
 #include <stdlib.h>
 
 #include "pdl.cuh"
@@ -695,11 +696,11 @@ extern "C" int pm_decode_layers(const void* layers, int n_layers, int M, int H, 
   p.bar = bar; p.status = status; p.trace = trace;
   const size_t smem = dm_smem_bytes(H, hq, I);
   const void* fn = reinterpret_cast<const void*>(decode_layers_kernel);
-  static size_t configured = 0;
-  if (smem > 40 * 1024 && smem > configured) {
+  static DeviceMax configured;
+  if (smem > 40 * 1024 && smem > configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = 200 * 1024;
+    configured.set(200 * 1024);
   }
   int dev = 0, sms = 0, per_sm = 0;
   cudaGetDevice(&dev);

@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "host_util.cuh"
 
 #include "pdl.cuh"
 
@@ -581,7 +582,8 @@ __global__ void dequant_4bit_kernel(const uint8_t* __restrict__ data, const floa
 
 using namespace pm;
 
-static inline int grid_for(long long work, int per_block, int cap = 148 * 16) {
+static inline int grid_for(long long work, int per_block, int cap = 0) {
+  if (cap <= 0) cap = num_sms() * 16;
   long long g = (work + per_block - 1) / per_block;
   if (g < 1) g = 1;
   return static_cast<int>(g > cap ? cap : g);
@@ -667,7 +669,7 @@ extern "C" int pm_ce_fwd_bwd(void* logits, long long ldl, const long long* label
 extern "C" int pm_sumsq(const float* x, long long n, float* out, cudaStream_t st) {
   cudaError_t e = cudaMemsetAsync(out, 0, sizeof(float), st);
   if (e != cudaSuccess) return static_cast<int>(e);
-  sumsq_kernel<<<grid_for(n / 4 + 1, 256, 148 * 4), 256, 0, st>>>(x, n, out);
+  sumsq_kernel<<<grid_for(n / 4 + 1, 256, num_sms() * 4), 256, 0, st>>>(x, n, out);
   return PM_LAUNCH_CHECK();
 }
 extern "C" int pm_adamw_flat(float* p, const float* g, float* m, float* v, void* shadow, const float* lr_mult,
@@ -680,7 +682,7 @@ extern "C" int pm_adamw_flat(float* p, const float* g, float* m, float* v, void*
   a.bc1 = 1.f - powf(beta1, static_cast<float>(step));
   a.bc2 = 1.f - powf(beta2, static_cast<float>(step));
   a.grad_scale = grad_scale; a.max_norm = max_norm;
-  adamw_flat_kernel<<<grid_for(n / 4, 256, 148 * 8), 256, 0, st>>>(p, g, m, v, static_cast<__nv_bfloat16*>(shadow),
+  adamw_flat_kernel<<<grid_for(n / 4, 256, num_sms() * 8), 256, 0, st>>>(p, g, m, v, static_cast<__nv_bfloat16*>(shadow),
                                                                   lr_mult, wd, gnorm_sq, hp, n, a);
   return PM_LAUNCH_CHECK();
 }

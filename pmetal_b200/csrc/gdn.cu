@@ -14,6 +14,7 @@
 // crates/pmetal-mlx/src/kernels/gated_delta.rs.
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "host_util.cuh"
 
 namespace pm {
 

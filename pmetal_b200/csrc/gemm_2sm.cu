@@ -317,7 +317,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             const uint64_t db = make_smem_desc(sb, bmn ? 8192u : 16u, 1024u);
             const uint32_t astep = amn ? 128u : 2u;
             const uint32_t bstep = bmn ? 128u : 2u;
-            for (int j = 0; j < ((p.debug & 2) ? 0 : nmma); ++j) {
+            for (int j = 0; j < nmma; ++j) {
               umma_f16_pair(d_tmem, da + static_cast<uint64_t>(astep * j), db + static_cast<uint64_t>(bstep * j),
                             idesc, accumulate);
               accumulate = 1;
@@ -363,7 +363,7 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         tmem_ld_32x32b_x32(tmem_base + buf * kPairBN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
         tmem_ld_wait();
         const int col0 = nb * kPairBN + c * 32;
-        if (!row_ok || col0 >= p.n_store || (p.debug & 1)) continue;
+        if (!row_ok || col0 >= p.n_store) continue;
         epilogue_store_chunk(p, r, row, col0);
       }
       tc_fence_before();
@@ -397,7 +397,7 @@ extern "C" int pm_gemm_bf16_2sm(const void* A, int a_mn, int lda, int a_rows, co
                                 int b_rows, const void* A2, int a2_mn, int lda2, int a2_k, const void* B2, int b2_mn,
                                 int ldb2, int b2_rows, void* D, int out_mode, int ldd, const void* R, int ldr, int M,
                                 int N, int K, int K2, int n_store, float alpha, int splits, int seg_mode,
-                                const int* seg_end, int seg_r, int max_ctas, int debug, int* status,
+                                const int* seg_end, int seg_r, int max_ctas, int* status,
                                 cudaStream_t stream) {
   if (splits < 1 || (splits > 1 && out_mode < 2)) return -12;
   if (M <= 0 || N <= 0 || K <= 0) return -13;
@@ -414,13 +414,11 @@ extern "C" int pm_gemm_bf16_2sm(const void* A, int a_mn, int lda, int a_rows, co
   p.seg_mode = seg_mode; p.seg_r = seg_r;
   for (int i = 0; i < 4; ++i) p.seg_end[i] = (seg_mode && seg_end) ? seg_end[i] : 0x7fffffff;
   p.status = status;
-  p.debug = debug & 3;
-  p.kps = (debug & 4) ? 1 : 2;
+  p.kps = 2;
   p.commit_both = 0;
-  p.fwd_full = (debug & 8) ? 1 : 0;
+  p.fwd_full = 0;
   int stages = (227 * 1024 - 2048) / (p.kps * kPairStageBytes);
   if (stages > kMaxStages) stages = kMaxStages;
-  if ((debug >> 4) > 0 && (debug >> 4) < stages) stages = debug >> 4;
   p.stages = stages;
   p.tmem_cols = 512;
 
@@ -435,11 +433,11 @@ extern "C" int pm_gemm_bf16_2sm(const void* A, int a_mn, int lda, int a_rows, co
     ma2 = ma; mb2 = mb;
   }
   const size_t smem = static_cast<size_t>(stages) * p.kps * kPairStageBytes + 1024 + 512;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured.mark();
   }
   const int m_tiles = (M + 2 * kBM - 1) / (2 * kBM), n_tiles = (N + kPairBN - 1) / kPairBN;
   int pairs = m_tiles * n_tiles * splits;

@@ -23,14 +23,13 @@ struct GemmParams {
   float alpha;
   void* D;
   const void* R;
-  int seg_mode;    // 0 none; 1: A2 K-offset = seg(n0)*seg_r; 2: B mn-offset = seg(m0)*seg_r
+  int seg_mode;    // 0 none; 1: A2 K-offset = seg(n0)*seg_r; 2: B mn-offset = seg(m0)*seg_r; 3: B mn-offset = -seg(k)*seg_r
   int seg_end[4];
   int seg_r;
   int tmem_cols;
   int kps;         // K blocks per pipeline stage (CTA-pair kernel)
   int fwd_full;    // CTA-pair kernel: each CTA counts its own TMA bytes; the partner forwards one arrive per stage
   int commit_both; // CTA-pair kernel: signal both CTAs' barriers with one commit
-  int debug;       // bit 0: skip epilogue stores, bit 1: skip MMA issue (timing experiments only)
   int* status;
 };
 
@@ -137,15 +136,5 @@ static inline int operand_map(CUtensorMap* map, const void* ptr, int mn_major, i
 }
 
 
-
-static inline int num_sms() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
-}
 
 }  // namespace pm

@@ -103,7 +103,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           mbar_expect_tx(&full_bar[s], a_bytes + b_bytes);
           if (kb < p.nk1) {
             load_operand(sa, &map_a, &full_bar[s], p.a_mn, kBM, m0, kb * kBK);
-            load_operand(sb, &map_b, &full_bar[s], p.b_mn, p.bn, n0 + b_off, kb * kBK);
+            // seg_mode 3: B is [K, seg_r] (MN-major, one narrow block of columns shared by every segment of K); the
+            // tile is fetched seg * seg_r columns to the left of its origin, so the rows of segment `seg` land in
+            // output columns [seg * seg_r, (seg + 1) * seg_r) and everything else reads as zero (out-of-range fill)
+            const int b_k_off = (p.seg_mode == 3) ? -seg_of(p, kb * kBK) * p.seg_r : 0;
+            load_operand(sb, &map_b, &full_bar[s], p.b_mn, p.bn, n0 + b_off + b_k_off, kb * kBK);
           } else {
             const int k0 = (kb - p.nk1) * kBK;
             load_operand(sa, &map_a2, &full_bar[s], p.a2_mn, kBM, m0, k0 + a2_off);
@@ -147,7 +151,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           const uint64_t db = make_smem_desc(sb, bmn ? 8192u : 16u, 1024u);
           const uint32_t astep = amn ? 128u : 2u;   // 16 K elements: 2048 B (MN-major) or 32 B (K-major), >> 4
           const uint32_t bstep = bmn ? 128u : 2u;
-          for (int j = 0; j < ((p.debug & 2) ? 0 : nmma); ++j) {
+          for (int j = 0; j < nmma; ++j) {
             umma_f16(d_tmem, da + static_cast<uint64_t>(astep * j), db + static_cast<uint64_t>(bstep * j), idesc,
                      accumulate);
             accumulate = 1;
@@ -179,7 +183,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         tmem_ld_32x32b_x32(tmem_base + buf * p.bn + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
         tmem_ld_wait();
         const int col0 = nb * p.bn + c * 32;
-        if (!row_ok || col0 >= p.n_store || (p.debug & 1)) continue;
+        if (!row_ok || col0 >= p.n_store) continue;
         epilogue_store_chunk(p, r, row, col0);
       }
       tc_fence_before();
@@ -214,13 +218,15 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
                             const void* A2, int a2_mn, int lda2, int a2_k, const void* B2, int b2_mn, int ldb2,
                             int b2_rows, void* D, int out_mode, int ldd, const void* R, int ldr, int M, int N, int K,
                             int K2, int n_store, float alpha, int bn, int splits, int seg_mode, const int* seg_end,
-                            int seg_r, int max_ctas, int debug, int* status, cudaStream_t stream) {
+                            int seg_r, int max_ctas, int* status, cudaStream_t stream) {
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return -10;
   if ((b_mn || (K2 > 0 && b2_mn)) && (bn % 64)) return -11;
   if (splits < 1 || (splits > 1 && out_mode < 2)) return -12;
   if (M <= 0 || N <= 0 || K <= 0) return -13;
   if (out_mode == 0 && ((ldd % 8) || (reinterpret_cast<uintptr_t>(D) & 15))) return -14;
   if (R && ((ldr % 8) || (reinterpret_cast<uintptr_t>(R) & 15))) return -15;
+  // seg_mode 3 shifts a TMA load by seg * seg_r elements: the shift must keep the 16-byte alignment of the copy
+  if (seg_mode == 3 && (!b_mn || (seg_r % 8) || N > bn || splits != 1)) return -16;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.K2 = K2; p.bn = bn;
   p.a_mn = a_mn; p.b_mn = b_mn; p.a2_mn = a2_mn; p.b2_mn = b2_mn;
@@ -232,11 +238,9 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
   p.seg_mode = seg_mode; p.seg_r = seg_r;
   for (int i = 0; i < 4; ++i) p.seg_end[i] = (seg_mode && seg_end) ? seg_end[i] : 0x7fffffff;
   p.status = status;
-  p.debug = debug & 3;
   const int stage_bytes = kBM * kBK * 2 + bn * kBK * 2;
   int stages = (227 * 1024 - 2048) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
-  if ((debug >> 4) > 0 && (debug >> 4) < stages) stages = debug >> 4;   // stage-count experiments
   p.stages = stages;
   int cols = 32;
   while (cols < 2 * bn) cols *= 2;
@@ -253,12 +257,12 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
     ma2 = ma; mb2 = mb;
   }
   const size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024 /*align*/ + 256 /*barriers*/;
-  static size_t configured = 0;
-  if (smem > configured) {
+  static DeviceOnce configured;
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(227 * 1024));
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = 227 * 1024;
+    configured.mark();
   }
   const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + bn - 1) / bn;
   int grid = m_tiles * n_tiles * splits;

@@ -15,6 +15,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "host_util.cuh"
 
 #include "pdl.cuh"
 
@@ -511,44 +512,44 @@ __global__ void __launch_bounds__(kTcThreads) gemv_q4_tc_kernel(const GemvParams
 template <bool SWIGLU>
 static int launch_gemv_q4(const GemvParams& p, cudaStream_t st) {
   const size_t smem = static_cast<size_t>(16) * (p.K + kTcPad) * 2 + kTcWarps * 2 * 128 * sizeof(float);
-  static size_t configured = 0;
-  if (smem > 40 * 1024 && smem > configured) {
+  static DeviceMax configured;
+  if (smem > 40 * 1024 && smem > configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(gemv_q4_tc_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = 200 * 1024;
+    configured.set(200 * 1024);
   }
   const int n_tiles = (p.N + 7) / 8;
-  const int grid = n_tiles < 148 * 2 ? n_tiles : 148 * 2;
+  const int grid = n_tiles < num_sms() * 2 ? n_tiles : num_sms() * 2;
   return static_cast<int>(launch_pdl(gemv_q4_tc_kernel<SWIGLU>, dim3(grid), dim3(kTcThreads), smem, st, p));
 }
 
 template <bool SWIGLU>
 static int launch_gemv_tc(const GemvParams& p, cudaStream_t st) {
   const size_t smem = static_cast<size_t>(16) * (p.K + kTcPad) * 2 + kTcWarps * 2 * 128 * sizeof(float);
-  static size_t configured = 0;
-  if (smem > 40 * 1024 && smem > configured) {
+  static DeviceMax configured;
+  if (smem > 40 * 1024 && smem > configured.get()) {
     cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = 200 * 1024;
+    configured.set(200 * 1024);
   }
   const int n_tiles = (p.N + 7) / 8;
-  const int grid = n_tiles < 148 * 2 ? n_tiles : 148 * 2;      // each CTA stages x once and loops over its tiles
+  const int grid = n_tiles < num_sms() * 2 ? n_tiles : num_sms() * 2;      // each CTA stages x once and loops over its tiles
   return static_cast<int>(launch_pdl(gemv_tc_kernel<SWIGLU>, dim3(grid), dim3(kTcThreads), smem, st, p));
 }
 
 template <int MR, int C, int KU, bool SWIGLU>
 static int launch_gemv(const GemvParams& p, cudaStream_t st) {
   const size_t smem = static_cast<size_t>(MR) * p.K * 2;
-  static size_t configured = 0;
-  if (smem > 40 * 1024 && smem > configured) {   // static shared memory counts against the 48 KB default too
+  static DeviceMax configured;
+  if (smem > 40 * 1024 && smem > configured.get()) {   // static shared memory counts against the 48 KB default too
     cudaError_t e = cudaFuncSetAttribute(gemv_kernel<MR, C, KU, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          200 * 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = 200 * 1024;
+    configured.set(200 * 1024);
   }
   const int groups = (p.N + C - 1) / C;
   int grid = (groups + kGvWarps - 1) / kGvWarps;
-  const int cap = 148 * 4;
+  const int cap = num_sms() * 4;
   if (grid > cap) grid = cap;
   return static_cast<int>(launch_pdl(gemv_kernel<MR, C, KU, SWIGLU>, dim3(grid), dim3(kGvThreads), smem, st, p));
 }
@@ -590,7 +591,7 @@ extern "C" int pm_gemv(const void* x, int ldx, const void* w, int ldw, const voi
     return swiglu ? launch_gemv_tc<true>(p, st) : launch_gemv_tc<false>(p, st);
   // wide outputs: several columns per warp; narrow outputs: one column per warp (so that every SM gets work) with a
   // deeper load pipeline instead
-  const bool wide = N >= 148 * kGvWarps * 2;
+  const bool wide = N >= num_sms() * kGvWarps * 2;
   if (swiglu) {
     if (M <= 4) return launch_gemv<4, 2, 4, true>(p, st);
     if (M <= 8) return launch_gemv<8, 1, 4, true>(p, st);

@@ -551,11 +551,11 @@ extern "C" int pm_moe_gemm(const void* a, int a_rows, int lda, const void* w, in
   p.status = status;
   // operand stages, 256 bytes of barriers, 32 KB epilogue transpose buffer (4 warps x 32 rows x 256 B), alignment slack
   const size_t smem = static_cast<size_t>(kEpStages) * (kBM * kBK * 2 + kEpBN * kBK * 2) + 256 + 4 * 32 * 256 + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(moe_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured.mark();
   }
   const long long work = static_cast<long long>(max_tiles) * ((N + kEpBN - 1) / kEpBN);
   int grid = num_sms();

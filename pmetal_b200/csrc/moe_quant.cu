@@ -18,6 +18,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include "host_util.cuh"
 
 namespace pm {
 
@@ -341,7 +342,8 @@ __global__ void fp8_dequant_kernel(const uint8_t* __restrict__ q, const float* _
   reinterpret_cast<uint2*>(y + b * 128)[lane] = o;
 }
 
-static inline int grid_cap(long long work, int per_block, int cap = 148 * 16) {
+static inline int grid_cap(long long work, int per_block, int cap = 0) {
+  if (cap <= 0) cap = num_sms() * 16;
   long long g = (work + per_block - 1) / per_block;
   return static_cast<int>(g < 1 ? 1 : (g > cap ? cap : g));
 }

@@ -22,6 +22,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include "host_util.cuh"
 
 namespace pm {
 

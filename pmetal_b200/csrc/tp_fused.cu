@@ -468,11 +468,11 @@ extern "C" int pm_tp_gemm(int mode, const unsigned long long* x_ptrs, int ldx, c
   if ((rc = operand_map(&maps.b, w, 0, N, K, ldw, kTpBN))) return rc * 10 - 6;
   // operand stages, 256 bytes of barriers, 32 KB epilogue transpose buffer (4 warps x 32 rows x 256 B), alignment slack
   const size_t smem = static_cast<size_t>(kTpStages) * (kBM * kBK * 2 + kTpBN * kBK * 2) + 256 + 4 * 32 * 256 + 1024;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured.mark();
   }
   const int total = (M / kBM) * ((N + kTpBN - 1) / kTpBN);
   int grid = total;

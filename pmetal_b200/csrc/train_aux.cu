@@ -19,6 +19,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include "host_util.cuh"
 
 namespace pm {
 
@@ -243,7 +244,7 @@ extern "C" int pm_merge_fused(const void* const* models, const void* base, const
   a.base = base; a.n_models = n_models; a.in_bf16 = in_bf16; a.out_bf16 = out_bf16; a.consensus = consensus;
   a.rescale = rescale; a.lam = lam; a.seed = seed; a.out = out; a.n = n;
   long long g = (n + 255) / 256;
-  if (g > 148 * 16) g = 148 * 16;
+  if (g > num_sms() * 16) g = num_sms() * 16;
   merge_fused_kernel<<<static_cast<unsigned>(g), 256, 0, st>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
@@ -253,7 +254,7 @@ extern "C" int pm_dot_norms(const void* a, const void* b, int bf16, long long n,
   cudaError_t e = cudaMemsetAsync(out3, 0, 3 * sizeof(float), st);
   if (e != cudaSuccess) return static_cast<int>(e);
   long long g = (n + 255) / 256;
-  if (g > 148 * 8) g = 148 * 8;
+  if (g > num_sms() * 8) g = num_sms() * 8;
   dot_norms_kernel<<<static_cast<unsigned>(g), 256, 0, st>>>(a, b, bf16, n, out3);
   return static_cast<int>(cudaGetLastError());
 }

@@ -49,6 +49,17 @@ def cache_dir(repo_id: str, revision: str = "main") -> str:
     return os.path.join(base, "models--" + repo_id.replace("/", "--"), "snapshots", revision)
 
 
+def _safe_join(dest_dir: str, name: str) -> str:
+    """``dest_dir/name`` for a server-supplied relative file name; raises when the result would escape ``dest_dir``."""
+    if not name or os.path.isabs(name) or name.startswith(("/", "\\")):
+        raise HubError(f"refusing file name {name!r}: not a relative path")
+    root = os.path.abspath(dest_dir)
+    path = os.path.abspath(os.path.join(root, os.path.normpath(name)))
+    if os.path.commonpath([root, path]) != root or path == root:
+        raise HubError(f"refusing file name {name!r}: it leaves the download directory")
+    return path
+
+
 def sha256_file(path: str) -> str:
     h = hashlib.sha256()
     with open(path, "rb") as fh:
@@ -59,11 +70,13 @@ def sha256_file(path: str) -> str:
 
 # ------------------------------------------------------------------------------------------------ download
 def download_file(repo_id: str, filename: str, dest_dir: Optional[str] = None, revision: str = "main",
-                  token: Optional[str] = None, expected_sha256: Optional[str] = None, timeout: float = 30.0) -> str:
+                  token: Optional[str] = None, expected_sha256: Optional[str] = None, timeout: float = 30.0,
+                  expected_size: Optional[int] = None) -> str:
     """Fetch one file. A partial ``.incomplete`` file is continued with a Range request; when the server (or the caller)
-    names a SHA-256, the finished file is verified and deleted on mismatch."""
+    names a SHA-256, the finished file is verified and deleted on mismatch. ``filename`` is a path inside the
+    repository: names that would leave ``dest_dir`` (absolute paths, ``..`` components) are rejected."""
     dest_dir = dest_dir or cache_dir(repo_id, revision)
-    path = os.path.join(dest_dir, filename)
+    path = _safe_join(dest_dir, filename)
     if os.path.exists(path) and (expected_sha256 is None or sha256_file(path) == expected_sha256):
         return path
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
@@ -76,8 +89,12 @@ def download_file(repo_id: str, filename: str, dest_dir: Optional[str] = None, r
         resp = s.get(url, headers=headers, stream=True, timeout=timeout)
     except Exception as e:
         raise HubError(f"download {url}: {e}") from e
-    if resp.status_code == 416:                      # nothing left to fetch
+    if resp.status_code == 416:                      # the server says nothing is left to fetch
         resp.close()
+        if expected_sha256 is None and not (expected_size is not None and have == expected_size):
+            # no checksum and no matching size to vouch for the partial file: fetch it again from the start
+            os.remove(tmp)
+            return download_file(repo_id, filename, dest_dir, revision, token, None, timeout, expected_size)
     else:
         _check(resp, f"download {filename}")
         mode = "ab" if (have and resp.status_code == 206) else "wb"
@@ -114,7 +131,9 @@ def download_model(repo_id: str, revision: str = "main", token: Optional[str] = 
     for sib in meta.get("siblings", []):
         name = sib.get("rfilename", "")
         if name.endswith(pats):
-            download_file(repo_id, name, dest, revision, token, (sib.get("lfs") or {}).get("sha256"))
+            size = sib.get("size") if sib.get("size") is not None else (sib.get("lfs") or {}).get("size")
+            download_file(repo_id, name, dest, revision, token, (sib.get("lfs") or {}).get("sha256"),
+                          expected_size=int(size) if size is not None else None)
     return dest
 
 

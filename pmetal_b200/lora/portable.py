@@ -172,17 +172,36 @@ class PortableLoraTrainer:
         self.sched = LearningRateScheduler(learning_rate, total_steps, warmup_steps, schedule)
         self.max_grad_norm, self.step_count = max_grad_norm, 0
 
-    def step(self, input_ids: torch.Tensor, labels: torch.Tensor) -> dict:
+    def micro_step(self, input_ids: torch.Tensor, labels: torch.Tensor, scale: float = 1.0) -> float:
+        """Forward + backward of one micro-batch; ``scale`` (1 / accumulation steps) multiplies its loss so that the
+        accumulated gradient is the mean over the micro-batches. Gradients add up until ``optimizer_step``."""
+        loss = causal_lm_loss(self.model(input_ids), labels)
+        (loss * scale if scale != 1.0 else loss).backward()
+        return float(loss.detach())
+
+    def optimizer_step(self) -> dict:
         lr = self.sched.get_lr(self.step_count)
         for g, meta in zip(self.opt.param_groups, self.groups):
             g["lr"] = lr * meta["lr_mult"]
-        self.opt.zero_grad(set_to_none=True)
-        loss = causal_lm_loss(self.model(input_ids), labels)
-        loss.backward()
         gn = torch.nn.utils.clip_grad_norm_([p for g in self.groups for p in g["params"]], self.max_grad_norm or float("inf"))
         self.opt.step()
+        self.opt.zero_grad(set_to_none=True)
         self.step_count += 1
-        return {"loss": float(loss.detach()), "grad_norm": float(gn), "lr": lr}
+        return {"grad_norm": float(gn), "lr": lr}
+
+    def step(self, input_ids: torch.Tensor, labels: torch.Tensor) -> dict:
+        """One optimiser step on one batch (no accumulation)."""
+        self.opt.zero_grad(set_to_none=True)
+        loss = self.micro_step(input_ids, labels)
+        return {"loss": loss, **self.optimizer_step()}
+
+    # -- resume: step counter (drives the schedule) and the optimiser moments
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "optimizer": self.opt.state_dict()}
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.step_count = int(sd["step"])
+        self.opt.load_state_dict(sd["optimizer"])
 
 
 # ------------------------------------------------------------------------------------------------ Q-BLoRA

@@ -212,9 +212,11 @@ class DecoderLayer(nn.Module):
         """x -> x + attn(norm(x)) -> (+ mlp(norm(.))). The residual adds run in the epilogue of the
         o_proj / down_proj GEMMs."""
         eps = self.cfg.rms_norm_eps
-        n1 = ops.rms_norm(x, self.input_layernorm, eps)
+        # the norm hands back the stream it read: using that alias for the residual branch lets its gradient be
+        # summed inside the norm's backward kernel
+        n1, x = ops.add_rms_norm(x, None, self.input_layernorm, eps)
         h = self.self_attn(n1, x, rope, cu_seqlens, seq_start)
-        n2 = ops.rms_norm(h, self.post_attention_layernorm, eps)
+        n2, h = ops.add_rms_norm(h, None, self.post_attention_layernorm, eps)
         return self.mlp(n2, h)
 
 

@@ -63,18 +63,24 @@ class _RmsNormFn(torch.autograd.Function):
         ctx.has_res = residual is not None
         ctx.w_grad = weight.requires_grad
         ctx.mark_non_differentiable(rstd)
+        ctx.set_materialize_grads(False)     # an unused output must not cost a zero-filled [T, H] gradient
         return y, h
 
     @staticmethod
     def backward(ctx, dy, dh):
         h, weight, rstd = ctx.saved_tensors
         nat = _native()
+        if dy is None:                       # only the pass-through output was used
+            return dh, None, None, (dh if ctx.has_res else None)
         dx, dw = nat.rmsnorm_bwd(dy.contiguous(), h, weight, rstd, dh, ctx.w_grad)
         return dx, dw, None, (dx if ctx.has_res else None)
 
 
 def add_rms_norm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, eps: float):
-    """h = x + residual (or x); returns (rms_norm(h)·w, h)."""
+    """h = x + residual (or x); returns (rms_norm(h)·w, h).
+
+    Callers that also feed the un-normalised stream onward (the residual branch of a pre-norm block) should use the
+    returned ``h`` for it: both gradients then meet inside the norm's backward kernel instead of in a separate add."""
     if use_native(x):
         y, h = _RmsNormFn.apply(x, weight, eps, residual)
         return y, h

@@ -22,8 +22,8 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__
 # PMETAL_MN_MAJOR=0 routes them through explicit transposes instead.
 MN_MAJOR = os.environ.get("PMETAL_MN_MAJOR", "1") == "1"
 ATTN_TC = os.environ.get("PMETAL_ATTN_TC", "1") == "1"      # tcgen05 attention kernels
+ATTN_FWD_V1 = os.environ.get("PMETAL_ATTN_FWD_V1", "0") == "1"   # single-softmax-group forward (comparison runs)
 USE_2SM = os.environ.get("PMETAL_GEMM_2SM", "1") == "1"   # CTA-pair kernel for 256-wide tiles
-GEMM_DEBUG = int(os.environ.get("PMETAL_GEMM_DEBUG", "0"))   # timing experiments only (see gemm_tcgen05.cu)
 LAUNCHES = 0   # number of kernels launched through this module (bench reporting)
 
 c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
@@ -47,7 +47,8 @@ def _load():
                "pm_qknorm_rope_bwd", "pm_swiglu_fwd", "pm_swiglu_bwd", "pm_ce_fwd_bwd", "pm_sumsq", "pm_adamw_flat",
                "pm_attn_delta", "pm_attn_fwd", "pm_attn_bwd", "pm_f32_to_bf16", "pm_paged_attn", "pm_kv_append", "pm_attn_fwd_tc", "pm_attn_bwd_tc", "pm_dequant_4bit", "pm_sample", "pm_spec_verify", "pm_count_tokens",
                "pm_moe_route", "pm_moe_gather", "pm_moe_combine", "pm_gguf_dequant_bf16", "pm_fp8_quant", "pm_fp8_dequant",
-               "pm_kd_fwd_bwd", "pm_merge_fused", "pm_dot_norms", "pm_attn_fwd_tc_rect", "pm_gemv", "pm_qknorm_rope_cache"):
+               "pm_kd_fwd_bwd", "pm_merge_fused", "pm_dot_norms", "pm_attn_fwd_tc_rect", "pm_attn_fwd_tc_rect_v1", "pm_gemv",
+               "pm_qknorm_rope_cache"):
         getattr(_LIB, fn).restype = c_int
 
 
@@ -74,6 +75,19 @@ def _stream() -> c_void_p:
 
 def _p(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
+
+
+_SM_COUNT = {}
+
+
+def sm_count(device=None) -> int:
+    """Number of SMs of the device (grid sizing); 148 when no GPU is present (CPU-side planning and tests)."""
+    if not torch.cuda.is_available():
+        return 148
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _SM_COUNT[idx]
 
 
 def _chk(rc: int, what: str) -> None:
@@ -107,7 +121,7 @@ def _pick_bn(n: int, seg_sizes: Sequence[int] = (), m: int = 1 << 30) -> int:
     segs = seg_sizes[:-1] if len(seg_sizes) > 1 else ()
     widths = (256, 128, 64, 32)
     if m <= 128:
-        widths = tuple(b for b in (32, 64, 128, 256) if -(-n // b) <= 4 * 148) or (256,)
+        widths = tuple(b for b in (32, 64, 128, 256) if -(-n // b) <= 4 * sm_count()) or (256,)
         for bn in widths:
             if all(s % bn == 0 for s in segs):
                 return bn
@@ -137,7 +151,7 @@ def raw_gemm(A, a_mn, lda, a_rows, B, b_mn, ldb, b_rows, D, out_mode, ldd, M, N,
                                     c_int(b2_mn), c_int(ldb2), c_int(b2_rows), _p(D), c_int(out_mode), c_int(ldd),
                                     _p(R), c_int(ldr), c_int(M), c_int(N), c_int(K), c_int(K2), c_int(n_store),
                                     c_float(alpha), c_int(splits), c_int(seg_mode), segs, c_int(seg_r),
-                                    c_int(max_ctas), c_int(GEMM_DEBUG), _p(status_word(D.device)), _stream())
+                                    c_int(max_ctas), _p(status_word(D.device)), _stream())
         _chk(rc, "pm_gemm_bf16_2sm")
         return
     rc = lib().pm_gemm_bf16(_p(A), c_int(a_mn), c_int(lda), c_int(a_rows), _p(B), c_int(b_mn), c_int(ldb),
@@ -145,7 +159,7 @@ def raw_gemm(A, a_mn, lda, a_rows, B, b_mn, ldb, b_rows, D, out_mode, ldd, M, N,
                             c_int(ldb2), c_int(b2_rows), _p(D), c_int(out_mode), c_int(ldd), _p(R), c_int(ldr),
                             c_int(M), c_int(N), c_int(K), c_int(K2), c_int(n_store), c_float(alpha), c_int(bn),
                             c_int(splits), c_int(seg_mode), segs, c_int(seg_r),
-                            c_int(max_ctas), c_int(GEMM_DEBUG), _p(status_word(D.device)), _stream())
+                            c_int(max_ctas), _p(status_word(D.device)), _stream())
     _chk(rc, "pm_gemm_bf16")
 
 
@@ -192,6 +206,13 @@ def lora_dt(dy, b, seg_sizes, r, scale) -> torch.Tensor:
     M, N = dy.shape
     nseg = len(seg_sizes)
     dt = torch.empty(M, _t_width(nseg * r), dtype=torch.bfloat16, device=dy.device)
+    if (MN_MAJOR and nseg * r <= 64 and r % 8 == 0 and all(s % 64 == 0 for s in seg_sizes) and b.is_contiguous()
+            and b.shape[1] == r):
+        # one launch: b [N, r] is read in place as an MN-major operand; segment s of the reduction lands in output
+        # columns [s r, (s + 1) r) because its tile is fetched s r columns left of the origin (zero fill elsewhere)
+        raw_gemm(dy, 0, dy.stride(0), M, b, 1, r, r, dt, 0, dt.stride(0), M, 64, N, alpha=scale, bn=64,
+                 seg_mode=3, seg_sizes=seg_sizes, seg_r=r)
+        return dt
     b_t = b.t().contiguous()                      # [r, N], K-major over N
     n0 = 0
     for i, sz in enumerate(seg_sizes):
@@ -227,7 +248,7 @@ def gemm_lora_dx(dy, w, w_t, dt, a) -> torch.Tensor:
 
 
 def _splits_for(m_tiles: int, nk: int) -> int:
-    return max(1, min(nk, -(-148 // max(m_tiles, 1))))
+    return max(1, min(nk, -(-sm_count() // max(m_tiles, 1))))
 
 
 def lora_da(dt, x, nr: int, out: torch.Tensor) -> None:
@@ -338,9 +359,10 @@ def attn_fwd(q, k, v, seq_start, scale: float, window: int = 0):
     out = torch.empty(T, hq, d, dtype=q.dtype, device=q.device)
     lse = torch.empty(hq, T, dtype=torch.float32, device=q.device)
     if ATTN_TC and window == 0 and q.stride(1) == d and k.stride(1) == d and v.stride(1) == d:
-        _chk(lib().pm_attn_fwd_tc(_p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)),
-                                  _p(out), c_ll(out.stride(0)), _p(lse), _p(seq_start), c_int(T), c_int(hq),
-                                  c_int(hkv), c_float(scale), _p(status_word(q.device)), _stream()), "pm_attn_fwd_tc")
+        fn = lib().pm_attn_fwd_tc_rect_v1 if ATTN_FWD_V1 else lib().pm_attn_fwd_tc_rect
+        _chk(fn(_p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)), _p(out),
+                c_ll(out.stride(0)), _p(lse), _p(seq_start), c_int(T), c_int(T), c_int(0), c_int(hq), c_int(hkv),
+                c_float(scale), _p(status_word(q.device)), _stream()), "pm_attn_fwd_tc")
         return out, lse
     _chk(lib().pm_attn_fwd(_p(q), c_ll(q.stride(0)), _p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)), _p(out),
                            c_ll(out.stride(0)), _p(lse), _p(seq_start), c_int(T), c_int(hq), c_int(hkv),
@@ -453,7 +475,7 @@ def paged_attn(q, k_cache, v_cache, meta, scale: float, window: int = 0, n_split
     if n_split <= 0:
         ctas = n_seq * hkv
         n_blocks = -(-meta.max_kv // 64)
-        n_split = max(1, min(n_blocks // 4, 296 // max(ctas, 1), 32)) if ctas < 148 else 1
+        n_split = max(1, min(n_blocks // 4, 2 * sm_count() // max(ctas, 1), 32)) if ctas < sm_count() else 1
     out = torch.empty_like(q)
     po = pml = None
     if n_split > 1:
@@ -729,7 +751,7 @@ def decode_layers(table, n_layers: int, x, scratch: dict, cos, sin, meta, hq: in
 
 def decode_splits(M: int, hkv: int, max_kv: int) -> int:
     """CTAs per (row, kv head) in the attention phase: fill the grid, at least 64 keys per CTA, at most 16."""
-    return max(1, min(148 // max(M * hkv, 1), 16, max(max_kv // 64, 1)))
+    return max(1, min(sm_count() // max(M * hkv, 1), 16, max(max_kv // 64, 1)))
 
 
 def decode_scratch(M: int, H: int, hq: int, hkv: int, I: int, n_split: int, device) -> dict:

@@ -59,8 +59,21 @@ class DistContext:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
         return float(t.item())
 
+    def broadcast_object(self, obj, src: int = 0):
+        """``obj`` of rank ``src`` on every rank (a small picklable value: a path, a step number)."""
+        if self.world_size == 1:
+            return obj
+        box = [obj if self.rank == src else None]
+        dist.broadcast_object_list(box, src=src, group=self.group)
+        return box[0]
+
     def bind_optimizer(self, opt) -> None:
         pass
+
+    def gather_optimizer_state(self, opt) -> None:
+        """Collective hook called by every rank before rank 0 writes ``optimizer.pt``. The all-reduce path keeps
+        identical full moments on every rank, so there is nothing to collect."""
+        return None
 
     @torch.no_grad()
     def reduce_and_step(self, opt, grad_scale: float, clip_after_reduce: bool = False) -> torch.Tensor:

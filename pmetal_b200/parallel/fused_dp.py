@@ -25,6 +25,25 @@ import torch.distributed as dist
 from .dp import DistContext
 
 
+def shard_range(total: int, rank: int, world: int, chunk: int = 1024) -> tuple:
+    """[lo, hi) of the flat buffer that ``rank`` owns in the fused step: whole 1024-element chunks, split evenly with
+    the remainder on the last ranks' side left empty (the same arithmetic as ``pm_dp_reduce_adamw``)."""
+    chunks = total // chunk
+    per = -(-chunks // world)
+    return min(per * rank, chunks) * chunk, min(per * (rank + 1), chunks) * chunk
+
+
+@torch.no_grad()
+def gather_sharded_(t: torch.Tensor, lo: int, hi: int, group=None) -> torch.Tensor:
+    """In place: every rank contributes ``t[lo:hi]`` (its own shard, disjoint across ranks) and ends up with the whole
+    vector. Entries outside a rank's shard are ignored, whatever they hold."""
+    full = torch.zeros_like(t)
+    full[lo:hi] = t[lo:hi]
+    dist.all_reduce(full, group=group)
+    t.copy_(full)
+    return t
+
+
 class FusedDataParallel(DistContext):
     fused = True
 
@@ -66,6 +85,16 @@ class FusedDataParallel(DistContext):
         self._bound = opt
         torch.cuda.synchronize()
         dist.barrier(self.group)
+
+    def gather_optimizer_state(self, opt) -> None:
+        """Collective. The fused step updates the Adam moments of the owned shard only, so ``flat_m`` / ``flat_v`` of a
+        rank are current on [lo, hi) and stale elsewhere; before a checkpoint every rank collects the other shards, so
+        that the file rank 0 writes holds the moments of every parameter and any rank can resume from it."""
+        if self.world_size == 1 or self._bound is not opt:
+            return
+        lo, hi = shard_range(opt.total, self.rank, self.world_size)
+        gather_sharded_(opt.flat_m, lo, hi, self.group)
+        gather_sharded_(opt.flat_v, lo, hi, self.group)
 
     def reset_flags(self) -> None:
         """Collective: clear the signal pads after a timed-out step."""

@@ -141,5 +141,6 @@ class CheckpointManager:
         for name in ("optimizer.pt", "rng.pt"):
             p = os.path.join(path, name)
             if os.path.exists(p):
-                extra[name] = torch.load(p, map_location="cpu", weights_only=False)
+                # tensors, lists, numbers and strings only: a checkpoint directory must not be able to run code
+                extra[name] = torch.load(p, map_location="cpu", weights_only=True)
         return tensors, meta, extra

@@ -224,8 +224,11 @@ class TrainingLoop:
                     self.cb.on_eval(em)
                     if st.best_val_loss is None or em.loss < st.best_val_loss:
                         st.best_val_loss = em.loss
-                if self.ckpt is not None and is_master and cfg.save_steps and st.step % cfg.save_steps == 0:
-                    self.save_checkpoint()
+                if cfg.save_steps and st.step % cfg.save_steps == 0:
+                    if self.dist is not None:                 # every rank: sharded optimizer state is collected first
+                        self.dist.gather_optimizer_state(self.opt)
+                    if self.ckpt is not None and is_master:
+                        self.save_checkpoint()
                 if (cfg.max_steps and st.step >= cfg.max_steps) or self.cb.should_stop() or self.should_stop:
                     done = True
                     break

@@ -118,10 +118,21 @@ def _run_portable_training(job: "TrainingJobConfig", model_dir: str, dev, dtype,
     model.train()
     loader = DataLoader(ds.samples, tcfg.batch_size, True, tcfg.seed, tok.pad_token_id or 0, max_seq)
     accum = max(tcfg.gradient_accumulation_steps, 1)
-    per_epoch = max(len(loader) // accum, 1)
+    per_epoch = max(len(loader) // accum, 1)        # optimiser steps per epoch: ``accum`` micro-batches each
     total = tcfg.max_steps or per_epoch * tcfg.num_epochs
     tr = PortableLoraTrainer(model, tcfg.learning_rate, tcfg.weight_decay, tcfg.max_grad_norm, tcfg.warmup_steps, total,
                              getattr(tcfg, "lr_scheduler", "cosine"), job.lora.loraplus_lr_ratio)
+    state_path = os.path.join(out_dir, "portable_trainer_state.pt")
+    step, running, tokens, epoch = 0, 0.0, 0, 0
+    if job.resume and os.path.exists(state_path):
+        sd = torch.load(state_path, map_location="cpu", weights_only=True)
+        tr.load_state_dict(sd["trainer"])
+        step, running, tokens, epoch = int(sd["step"]), float(sd["running"]), int(sd["tokens"]), int(sd["epoch"])
+        log.info("resumed the portable trainer at step %d (epoch %d)", step, epoch)
+
+    def save_state():
+        torch.save({"trainer": tr.state_dict(), "step": step, "running": running, "tokens": tokens, "epoch": epoch},
+                   state_path)
     cbs = callbacks + [LoggingCallback(tcfg.logging_steps)]
     if job.log_metrics:
         cbs.append(MetricsJsonCallback(job.log_metrics, config={"lora": dataclasses.asdict(job.lora),
@@ -129,21 +140,31 @@ def _run_portable_training(job: "TrainingJobConfig", model_dir: str, dev, dtype,
     cb = CompositeCallback(cbs)
     phase("training")
     cb.on_train_start()
-    step, running, tokens, epoch, done = 0, 0.0, 0, 0, False
+    done = step >= total
+    micro, acc_loss, acc_tok = 0, 0.0, 0
+    t0 = time.perf_counter()
     while not done:
         loader.set_epoch(epoch)
         for batch in loader:
-            t0 = time.perf_counter()
             ids, labels = batch["input_ids"].to(dev), batch["labels"].to(dev)
-            st = tr.step(ids, labels)             # one optimiser step per batch (accumulation folds into the batch size)
+            acc_loss += tr.micro_step(ids, labels, 1.0 / accum)
+            acc_tok += int(batch.get("tokens", ids.numel()))
+            micro += 1
+            if micro < accum:
+                continue
+            st = tr.optimizer_step()
+            st["loss"] = acc_loss / accum
             step += 1
-            tokens += int(batch.get("tokens", ids.numel()))
+            tokens += acc_tok
             running = st["loss"] if step == 1 else 0.99 * running + 0.01 * st["loss"]
             dt = max(time.perf_counter() - t0, 1e-9)
             cb.on_step_end_with_metrics(StepMetrics(step=step, epoch=epoch, total_epochs=tcfg.num_epochs, total_steps=total,
-                                                    loss=st["loss"], lr=st["lr"], tok_sec=int(batch.get("tokens", 0)) / dt,
-                                                    total_ms=dt * 1e3, tokens=int(batch.get("tokens", 0)),
-                                                    grad_norm=st["grad_norm"]))
+                                                    loss=st["loss"], lr=st["lr"], tok_sec=acc_tok / dt,
+                                                    total_ms=dt * 1e3, tokens=acc_tok, grad_norm=st["grad_norm"]))
+            micro, acc_loss, acc_tok, t0 = 0, 0.0, 0, time.perf_counter()
+            if tcfg.save_steps and step % tcfg.save_steps == 0:
+                save_adapter_portable(model, out_dir, job.lora, base_model=job.model)
+                save_state()
             if step >= total or cb.should_stop():
                 done = True
                 break
@@ -153,6 +174,7 @@ def _run_portable_training(job: "TrainingJobConfig", model_dir: str, dev, dtype,
     cb.on_train_end()
     phase("saving")
     adapter = save_adapter_portable(model, out_dir, job.lora, base_model=job.model)
+    save_state()
     return {"steps": step, "final_loss": running, "tokens": tokens, "seconds": time.time() - t_start, "adapter": adapter,
             "output": out_dir, "path": "portable"}
 
@@ -269,9 +291,15 @@ def run_training(job: TrainingJobConfig, phase_cb: Optional[Callable[[str], None
         total_steps = tcfg.max_steps or per_epoch * tcfg.num_epochs
         loop = TrainingLoop(model, tcfg, cbs, dctx, job.lora.loraplus_lr_ratio, checkpoint_manager=ckpt,
                             adaptive_lr=adaptive, total_steps=total_steps)
-        if job.resume and ckpt is not None and ckpt.latest_path():
-            loop.resume(ckpt.latest_path())
-            log.info("resumed from %s at step %d", ckpt.latest_path(), loop.state.step)
+        if job.resume:
+            # every rank restores the same checkpoint (parameters, step, epoch, optimizer moments): rank 0 names it,
+            # the others read the same directory; only the writes stay on rank 0
+            latest = ckpt.latest_path() if ckpt is not None else None
+            if dctx is not None:
+                latest = dctx.broadcast_object(latest, src=0)
+            if latest:
+                loop.resume(latest)
+                log.info("rank %d resumed from %s at step %d", rank, latest, loop.state.step)
         if getattr(job, "resume_bundle", None):
             from ..parallel.cloud_bridge import import_bundle
             params, _opt, meta = import_bundle(job.resume_bundle)

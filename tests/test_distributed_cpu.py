@@ -275,6 +275,17 @@ def test_ring_attention_pipeline_and_1f1b_over_gloo():
         assert r.returncode == 0 and "CP_PP_WORKER_OK" in r.stdout, r.stdout[-3000:]
 
 
+def test_every_rank_resumes_and_sharded_moments_are_collected(tmp_path):
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29741", os.path.join(root, "tests", "workers", "dp_resume_worker.py")]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=180,
+                       env=dict(os.environ, PMETAL_TEST_DIR=str(tmp_path)))
+    assert r.returncode == 0 and r.stdout.count("DP_RESUME_WORKER_OK") == 2, r.stdout[-3000:]
+
+
 def test_activation_message_wire_format():
     import struct
 

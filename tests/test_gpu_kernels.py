@@ -200,6 +200,64 @@ def test_attention_fwd_bwd(T, lens, hq, hkv, window):
     _close(dv, vf.grad, rtol=3e-2, atol=3e-2, what="attn dv")
 
 
+def _packed_lens(T, lo, hi, seed):
+    g = torch.Generator().manual_seed(seed)
+    lens, tot = [], 0
+    while tot < T:
+        n = int(torch.randint(lo, hi + 1, (1,), generator=g))
+        lens.append(min(n, T - tot))
+        tot += lens[-1]
+    return lens
+
+
+def test_attention_training_shape():
+    """The benchmark's shape: 4 packs x 4096 tokens of documents U[64, 2048], 16 query / 8 kv heads."""
+    nat = _nat()
+    from pmetal_b200.ops import reference as ref
+    torch.manual_seed(17)
+    T, hq, hkv, d = 16384, 16, 8, 128
+    cu = _doc_bounds(T, _packed_lens(T, 64, 2048, 3))
+    ss = ref.seq_starts_from_cu(cu, T)
+    q, k, v = _rand(T, hq, d), _rand(T, hkv, d), _rand(T, hkv, d)
+    scale = d ** -0.5
+    o, lse = nat.attn_fwd(q, k, v, ss, scale, 0)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    orf = ref.varlen_attention(qf, kf, vf, cu, scale, True, 0)
+    _close(o, orf, what="attn fwd (training shape)")
+    do = _rand(T, hq, d)
+    orf.backward(do.float())
+    dq, dk, dv = nat.attn_bwd(do, q, k, v, o, lse, ss, scale, 0)
+    nat.check_status()
+    _close(dq, qf.grad, rtol=3e-2, atol=3e-2, what="attn dq (training shape)")
+    _close(dk, kf.grad, rtol=3e-2, atol=3e-2, what="attn dk (training shape)")
+    _close(dv, vf.grad, rtol=3e-2, atol=3e-2, what="attn dv (training shape)")
+
+
+def test_attention_fwd_growing_logits():
+    """Keys whose scores grow along the sequence force the running maximum up tile after tile, so the forward
+    kernel has to rescale the output accumulator it keeps in tensor memory."""
+    nat = _nat()
+    from pmetal_b200.ops import reference as ref
+    torch.manual_seed(19)
+    T, hq, hkv, d = 1536, 2, 1, 128
+    cu = _doc_bounds(T, [T])
+    ss = ref.seq_starts_from_cu(cu, T)
+    base = torch.randn(d, device="cuda")
+    base = base / base.norm()
+    ramp = torch.linspace(0.0, 40.0, T, device="cuda")[:, None, None]          # up to e^40 between first and last key
+    q = (base[None, None, :] * math.sqrt(d) + 0.1 * torch.randn(T, hq, d, device="cuda")).to(torch.bfloat16)
+    k = (base[None, None, :] * ramp + 0.1 * torch.randn(T, hkv, d, device="cuda")).to(torch.bfloat16)
+    v = _rand(T, hkv, d)
+    scale = d ** -0.5
+    o, lse = nat.attn_fwd(q, k, v, ss, scale, 0)
+    nat.check_status()
+    orf = ref.varlen_attention(q.float(), k.float(), v.float(), cu, scale, True, 0)
+    _close(o, orf, what="attn fwd (growing logits)")
+    s = torch.einsum("qhd,khd->hqk", q.float(), k.float().repeat_interleave(hq // hkv, 1)) * scale
+    s = s.masked_fill(~torch.tril(torch.ones(T, T, dtype=torch.bool, device="cuda")), float("-inf"))
+    _close(lse, torch.logsumexp(s, -1), rtol=1e-3, atol=2e-2, what="attn lse (growing logits)")
+
+
 def test_linear_ce():
     nat = _nat()
     torch.manual_seed(8)

@@ -50,6 +50,11 @@ class Fake(BaseHTTPRequestHandler):
         rng = self.headers.get("Range")
         if rng:
             start = int(rng.split("=")[1].split("-")[0])
+            if start >= len(raw):
+                self.send_response(416)
+                self.send_header("Content-Length", "0")
+                self.end_headers()
+                return
             self.send_response(206)
         else:
             self.send_response(200)
@@ -123,6 +128,33 @@ def test_search_download_resume_and_checksum(server, tmp_path):
     assert not (dest / "bad.bin").exists() and not (dest / "bad.bin.incomplete").exists()
     with pytest.raises(hub.HubError, match="404"):
         hub.download_file("org/tiny", "missing.json", str(dest))
+
+
+def test_download_rejects_names_that_leave_the_directory(server, tmp_path):
+    dest = tmp_path / "snap"
+    dest.mkdir()
+    for bad in ("../escape.json", "/etc/passwd", "a/../../b.json", ""):
+        with pytest.raises(hub.HubError, match="refusing"):
+            hub.download_file("org/tiny", bad, str(dest))
+    assert not (tmp_path / "escape.json").exists()
+    assert not any(e[0] == "GET" for e in Fake.log)           # nothing was requested for a refused name
+    p = hub.download_file("org/tiny", "config.json", str(dest))
+    assert p == str(dest / "config.json")
+
+
+def test_range_not_satisfiable_without_checksum_is_not_trusted(server, tmp_path):
+    dest = tmp_path / "r416"
+    dest.mkdir()
+    # a stale partial file that is as long as the real one but holds other bytes; no checksum is known
+    (dest / "config.json.incomplete").write_bytes(b"X" * len(b'{"model_type": "llama"}'))
+    p = hub.download_file("org/tiny", "config.json", str(dest))
+    assert json.load(open(p))["model_type"] == "llama"
+    # with a matching size on record the finished partial file is accepted as is
+    (dest / "again.incomplete").write_bytes(b"x")
+    (dest / "config.json").unlink()
+    (dest / "config.json.incomplete").write_bytes(b'{"model_type": "llama"}')
+    p = hub.download_file("org/tiny", "config.json", str(dest), expected_size=len(b'{"model_type": "llama"}'))
+    assert json.load(open(p))["model_type"] == "llama"
 
 
 def test_upload_splits_inline_and_lfs_files(server, tmp_path):

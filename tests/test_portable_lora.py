@@ -98,6 +98,35 @@ def test_train_command_takes_the_portable_path_for_gemma(tmp_path, capsys):
     assert len(steps) == 6 and steps[-1]["loss"] < steps[0]["loss"]
 
 
+def test_portable_path_accumulates_micro_batches_and_resumes(tmp_path, capsys):
+    """16 samples, batch 2, accumulation 4, one epoch: two optimiser steps that together see every token of the data;
+    a second run with --resume continues the step count and the optimiser instead of starting over."""
+    from pmetal_b200.cli.main import main
+    d = _tiny_gemma_dir(tmp_path)
+    data = tmp_path / "d.jsonl"
+    rows = ["the cat sat on the mat " * (1 + i % 3) for i in range(16)]
+    data.write_text("".join(json.dumps({"text": r}) + "\n" for r in rows))
+    out = str(tmp_path / "out")
+    args = ["train", "-m", d, "-d", str(data), "-o", out, "--lora-r", "4", "--lora-alpha", "8", "--batch-size", "2",
+            "--gradient-accumulation-steps", "4", "--epochs", "1", "--warmup-steps", "0", "--device", "cpu", "--dtype",
+            "float32", "--log-metrics", str(tmp_path / "m.jsonl"), "--no-adaptive-lr"]
+    assert main(args) == 0
+    summary = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    steps = [json.loads(l) for l in open(tmp_path / "m.jsonl") if '"step"' in l]
+    assert summary["steps"] == 2 and len(steps) == 2
+    from pmetal_b200.data.dataset import TrainingDataset
+    from pmetal_b200.data.tokenizer import Tokenizer
+    ds = TrainingDataset.from_file_tokenized(str(data), Tokenizer.from_model_dir(d), 2048, "auto", None, None, None)
+    assert summary["tokens"] == sum(len(x) for x in ds.samples)        # nothing skipped, nothing seen twice
+    state = torch.load(os.path.join(out, "portable_trainer_state.pt"), weights_only=True)
+    assert state["step"] == 2 and state["trainer"]["step"] == 2
+    assert main(args + ["--resume", "--max-steps", "3"]) == 0
+    summary = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert summary["steps"] == 3
+    state = torch.load(os.path.join(out, "portable_trainer_state.pt"), weights_only=True)
+    assert state["trainer"]["step"] == 3 and state["trainer"]["optimizer"]["state"]
+
+
 def test_infer_command_runs_portable_models_with_adapter_and_quantised_cache(tmp_path, capsys):
     from pmetal_b200.cli.main import main
     d = _tiny_gemma_dir(tmp_path)
