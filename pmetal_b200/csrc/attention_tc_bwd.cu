@@ -12,9 +12,11 @@
 // as a K-major operand (its rows are the M/N index) or as an MN-major operand (its rows are the reduction
 // index), which is how the same Q, dO, K tiles serve both products of each kernel without a transpose.
 //
-// Both kernels run 320 threads: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..9 = two compute warp groups.
-// The element-wise work has no row reductions (log-sum-exp and delta are inputs), so the two groups split the 128
-// columns of every row: group g handles the 32-column chunks 2g and 2g+1 of S / dP and of the output tiles.
+// Both kernels run 320 threads: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 and 6..9 = two compute groups.
+// The element-wise work has no row reductions (log-sum-exp and delta are inputs), so the two groups split the 128 columns of every
+// row: group g handles the 32-column chunks 2g and 2g+1 of S / dP and of the output tiles. A group reads its 64
+// columns of S (and dP) with back-to-back tcgen05.ld instructions and one wait, and releases the TMEM buffer as soon
+// as the values are in registers, so the tensor cores start on the next tile while this one is still being formed.
 #include "attention_tc.cuh"
 
 namespace pm {
@@ -24,32 +26,28 @@ enum {
   kDqBarDsFree = 8, kDqBarDqFull = 9, kDqBarCount = 10
 };
 
-// dS row for the dQ kernel: p = exp2(s*a + b); ds = p * (dp - delta) * scale, written as bf16 into the swizzled tile.
-// S is at taddr, dP at taddr + 128.
+// dS for this group's 64 columns of one query row (dQ kernel): p = exp2(s*a + b); ds = p * (dp - delta) * scale, packed
+// as bf16 into pk[32]. sv / dv hold the row's S and dP values (chunks c0 and c0 + 1).
 template <bool kMask>
-__device__ __forceinline__ void dq_ds_rows(uint32_t taddr, uint32_t tile_addr, int r, float a, float b, float delta,
-                                           float scale, int lo, int span, int c0) {
+__device__ __forceinline__ void dq_ds_pack(const uint32_t (&sv)[64], const uint32_t (&dv)[64], float a, float b,
+                                           float delta, float scale, int lo, int span, int c0, uint32_t (&pk)[32]) {
 #pragma unroll
-  for (int cc = 0; cc < 2; ++cc) {
-    const int c = c0 + cc;
-    uint32_t sv[32], dv[32];
-    tmem_ld_32x32b_x32(taddr + c * 32, sv);
-    tmem_ld_32x32b_x32(taddr + 128 + c * 32, dv);
-    tmem_ld_wait();
-    uint32_t pk[16];
+  for (int e = 0; e < 64; e += 2) {
+    float d2[2];
 #pragma unroll
-    for (int e = 0; e < 32; e += 2) {
-      float d2[2];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), a, b));
-        if (kMask) pv = (span >= 0 && static_cast<unsigned>(c * 32 + e + u - lo) <= static_cast<unsigned>(span)) ? pv : 0.f;
-        d2[u] = pv * (__uint_as_float(dv[e + u]) - delta) * scale;
-      }
-      pk[e >> 1] = pack_bf16x2(d2[0], d2[1]);
+    for (int u = 0; u < 2; ++u) {
+      float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), a, b));
+      if (kMask) pv = (span >= 0 && static_cast<unsigned>(c0 * 32 + e + u - lo) <= static_cast<unsigned>(span)) ? pv : 0.f;
+      d2[u] = pv * (__uint_as_float(dv[e + u]) - delta) * scale;
     }
-    store_row_chunk_sw128(tile_addr, r, c, pk);
+    pk[e >> 1] = pack_bf16x2(d2[0], d2[1]);
   }
+}
+
+// two back-to-back 32-column TMEM loads into one 64-entry array (no wait)
+__device__ __forceinline__ void tmem_ld_64(uint32_t taddr, uint32_t (&v)[64]) {
+  tmem_ld_32x32b_x32(taddr, *reinterpret_cast<uint32_t (*)[32]>(&v[0]));
+  tmem_ld_32x32b_x32(taddr + 32, *reinterpret_cast<uint32_t (*)[32]>(&v[32]));
 }
 
 // TMEM columns: [0,128) S   [128,256) dP   [256,384) dQ accumulator
@@ -179,25 +177,36 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const int j0 = kv_lo + j * kFaTile;
       if (!mbar_wait(&bar[kDqBarSpFull], j & 1, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after();
+      uint32_t pk[32];
+      {
+        uint32_t sv[64], dv[64];
+        tmem_ld_64(tmem_base + lane_off + c0 * 32, sv);
+        tmem_ld_64(tmem_base + lane_off + 128 + c0 * 32, dv);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar[kDqBarSpFree]);    // S and dP are in registers: the next pair of MMAs may start
+        const int lo = max(st - j0, 0);
+        const int span = (i < p.T) ? (min(i - j0, kFaTile - 1) - lo) : -1;
+        const bool need_mask = (j0 + kFaTile - 1 > q0) || (j0 < st_max) || (q0 + kFaTile > p.T);
+        if (need_mask) dq_ds_pack<true>(sv, dv, sl2, -lse2, dl, p.scale, lo, span, c0, pk);
+        else dq_ds_pack<false>(sv, dv, sl2, -lse2, dl, p.scale, 0, 0, c0, pk);
+      }
       // the previous tile's dS must have been consumed by its MMA before it is overwritten
       if (j > 0 && !mbar_wait(&bar[kDqBarDsFree], (j - 1) & 1, abort_flag, p.status, kTimeoutEpilogue)) {
         ok = false;
         break;
       }
-      {
-        const int lo = max(st - j0, 0);
-        const int span = (i < p.T) ? (min(i - j0, kFaTile - 1) - lo) : -1;
-        const bool need_mask = (j0 + kFaTile - 1 > q0) || (j0 < st_max) || (q0 + kFaTile > p.T);
-        if (need_mask) dq_ds_rows<true>(tmem_base + lane_off, ds_addr, r, sl2, -lse2, dl, p.scale, lo, span, c0);
-        else dq_ds_rows<false>(tmem_base + lane_off, ds_addr, r, sl2, -lse2, dl, p.scale, 0, 0, c0);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t ck[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) ck[e] = pk[cc * 16 + e];
+        store_row_chunk_sw128(ds_addr, r, c0 + cc, ck);
       }
       fence_async_smem();
-      tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bar[kDqBarDsReady]);
-        mbar_arrive(&bar[kDqBarSpFree]);
-      }
+      if (lane == 0) mbar_arrive(&bar[kDqBarDsReady]);
     }
     if (ok && n_tiles > 0 && mbar_wait(&bar[kDqBarDqFull], 0, abort_flag, p.status, kTimeoutEpilogue)) {
       tc_fence_after();
@@ -243,26 +252,22 @@ enum {
   kKvBarCount = 14
 };
 
-// P row for the dK/dV kernel: p = exp2(s*a + b) (masked), packed bf16 into pk[64].
+// P for this group's 64 columns of one query row (dK/dV kernel): p = exp2(s*a + b) (masked), packed bf16 into pk[32].
 template <bool kMask>
 __device__ __forceinline__ void kv_p_row(uint32_t taddr, float a, float b, int lo, int span, int c0, uint32_t (&pk)[32]) {
+  uint32_t sv[64];
+  tmem_ld_64(taddr + c0 * 32, sv);
+  tmem_ld_wait();
 #pragma unroll
-  for (int cc = 0; cc < 2; ++cc) {
-    const int c = c0 + cc;
-    uint32_t sv[32];
-    tmem_ld_32x32b_x32(taddr + c * 32, sv);
-    tmem_ld_wait();
+  for (int e = 0; e < 64; e += 2) {
+    float p2[2];
 #pragma unroll
-    for (int e = 0; e < 32; e += 2) {
-      float p2[2];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), a, b));
-        if (kMask) pv = (span >= 0 && static_cast<unsigned>(c * 32 + e + u - lo) <= static_cast<unsigned>(span)) ? pv : 0.f;
-        p2[u] = pv;
-      }
-      pk[cc * 16 + (e >> 1)] = pack_bf16x2(p2[0], p2[1]);
+    for (int u = 0; u < 2; ++u) {
+      float pv = fast_exp2(fmaf(__uint_as_float(sv[e + u]), a, b));
+      if (kMask) pv = (span >= 0 && static_cast<unsigned>(c0 * 32 + e + u - lo) <= static_cast<unsigned>(span)) ? pv : 0.f;
+      p2[u] = pv;
     }
+    pk[e >> 1] = pack_bf16x2(p2[0], p2[1]);
   }
 }
 
@@ -456,22 +461,21 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
       if (!mbar_wait(&bar[kKvBarDpFull], w & 1, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {     // dS = P * (dP - delta) * scale, in place over the packed P row
-        uint32_t dv[32];
-        tmem_ld_32x32b_x32(tmem_base + 128 + (c0 + cc) * 32 + lane_off, dv);
+      {                                    // dS = P * (dP - delta) * scale, in place over the packed P row
+        uint32_t dv[64];
+        tmem_ld_64(tmem_base + 128 + c0 * 32 + lane_off, dv);
         tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar[kKvBarDpFree]);
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const uint32_t pp = pk[cc * 16 + e];
+        for (int e = 0; e < 32; ++e) {
+          const uint32_t pp = pk[e];
           const float p0 = __uint_as_float(pp << 16), p1 = __uint_as_float(pp & 0xffff0000u);
-          pk[cc * 16 + e] = pack_bf16x2(p0 * (__uint_as_float(dv[2 * e]) - dl) * p.scale,
-                                       p1 * (__uint_as_float(dv[2 * e + 1]) - dl) * p.scale);
+          pk[e] = pack_bf16x2(p0 * (__uint_as_float(dv[2 * e]) - dl) * p.scale,
+                              p1 * (__uint_as_float(dv[2 * e + 1]) - dl) * p.scale);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar[kKvBarDpFree]);
       if (!mbar_wait(&bar[kKvBarPFree], w & 1, abort_flag, p.status, kTimeoutEpilogue)) { ok = false; break; }
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {

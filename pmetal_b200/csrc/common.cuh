@@ -61,17 +61,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait. Returns false when the wait was abandoned (limit hit here or abort
-// raised by another thread of the CTA).
+// Bounded wait. Returns false when the wait was abandoned (limit hit here or abort raised by another thread of the
+// CTA). The global timer is a slow register to read (its latency is of the order of a whole pipeline hop), so it stays
+// off the path of a wait that completes normally: the clock is first looked at after 2048 failed polls, and only every
+// 256 polls after that.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* g_status,
                                           int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  unsigned long long t0 = 0;
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 255u) == 0u) {
+    if ((++spins & 255u) == 0u && spins >= 2048u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
         *abort_flag = 1;
         if (g_status) atomicCAS(g_status, 0, code);
         return false;

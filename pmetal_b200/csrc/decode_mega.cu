@@ -111,13 +111,19 @@ __device__ __forceinline__ bool dm_grid_barrier(const DmParams& p, unsigned& epo
     const unsigned target = epoch * gridDim.x;
     __threadfence();
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.bar) : "memory");
-    const unsigned long long t0 = dm_now();
+    unsigned long long t0 = 0;     // the global timer is slow to read: first looked at after 1024 failed polls
     unsigned spins = 0;
     int ok = 1;
     while (static_cast<int>(dm_ld_acquire(p.bar) - target) < 0) {
       if ((++spins & 63u) == 0u) {
         if (dm_ld_acquire(p.bar + 1) != 0u) { ok = 0; break; }
-        if (dm_now() - t0 > kDmBarrierLimitNs) {
+        bool late = false;
+        if (spins >= 1024u) {
+          const unsigned long long now = dm_now();
+          if (t0 == 0) t0 = now;
+          late = now - t0 > kDmBarrierLimitNs;
+        }
+        if (late) {
           atomicCAS(p.status, 0, kStatusDecodeBarrier);
           atomicExch(p.bar + 1, 1u);
           ok = 0;

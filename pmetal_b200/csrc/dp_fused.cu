@@ -73,13 +73,18 @@ __device__ __forceinline__ bool wait_all(const uint32_t* pad, int off, int world
                                          unsigned long long timeout_ns, int* status, int* s_fail) {
   if (threadIdx.x < world) {
     const uint32_t* f = pad + off + threadIdx.x;
-    const unsigned long long t0 = now_ns();
+    unsigned long long t0 = 0;     // the global timer is slow to read: first looked at after 1024 failed polls
     uint32_t spins = 0;
     while (static_cast<int32_t>(ld_acquire_sys(f) - epoch) < 0) {
-      if ((++spins & 63u) == 0u && now_ns() - t0 > timeout_ns) {
-        atomicCAS(status, 0, kStatusPeerTimeout);
-        *s_fail = 1;
-        break;
+      if ((++spins & 63u) == 0u && spins >= 1024u) {
+        const unsigned long long now = now_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > timeout_ns) {
+          atomicCAS(status, 0, kStatusPeerTimeout);
+          *s_fail = 1;
+          break;
+        }
       }
     }
   }

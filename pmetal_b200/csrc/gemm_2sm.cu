@@ -99,12 +99,15 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   int* g_status, int code) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
+  unsigned long long t0 = 0;     // the global timer is read only after many failed polls (see mbar_wait)
   uint32_t spins = 0;
   while (!mbar_try_wait_cluster(bar, parity)) {
-    if ((++spins & 255u) == 0u) {
+    if ((++spins & 255u) == 0u && spins >= 2048u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
         *abort_flag = 1;
         if (g_status) atomicCAS(g_status, 0, code);
         return false;

@@ -95,13 +95,18 @@ __device__ __forceinline__ void ep_st_release(uint32_t* p, uint32_t v) {
 }
 __device__ __forceinline__ bool ep_wait_flag(const uint32_t* flag, uint32_t epoch, unsigned long long timeout_ns,
                                              int* status) {
-  const unsigned long long t0 = globaltimer_ns();
+  unsigned long long t0 = 0;     // the global timer is slow to read: first looked at after 1024 failed polls
   uint32_t spins = 0;
   while (static_cast<int32_t>(ep_ld_acquire(flag) - epoch) < 0) {
     if ((++spins & 31u) == 0u) {
-      if (globaltimer_ns() - t0 > timeout_ns) {
-        atomicCAS(status, 0, kStatusEpPeer);
-        return false;
+      if (spins >= 1024u) {
+        const unsigned long long now = globaltimer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > timeout_ns) {
+          atomicCAS(status, 0, kStatusEpPeer);
+          return false;
+        }
       }
       __nanosleep(64);
     }
@@ -269,13 +274,19 @@ moe_gemm_kernel(const __grid_constant__ MoeMaps maps, const MoeGemmParams p) {
         const int b_row = t.expert * p.N + nb * kEpBN;
         if (p.stage_in) {   // the tile's rows must have landed in the staging buffer
           const uint32_t* flag = p.tile_ready + w / n_blocks;
-          const unsigned long long t0 = globaltimer_ns();
+          unsigned long long t0 = 0;     // timer first read after 1024 failed polls (it is slow to read)
           uint32_t spins = 0, v;
           do {
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
             if (static_cast<int32_t>(v - epoch) >= 0) break;
             if ((++spins & 31u) == 0u) {
-              if (*abort_flag || globaltimer_ns() - t0 > p.timeout_ns) {
+              bool late = false;
+              if (spins >= 1024u) {
+                const unsigned long long now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                late = now - t0 > p.timeout_ns;
+              }
+              if (*abort_flag || late) {
                 atomicCAS(p.status, 0, kStatusEpPeer);
                 *abort_flag = 1;
                 ok = false;

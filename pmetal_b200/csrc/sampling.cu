@@ -33,7 +33,8 @@ struct SampleParams {
   int is_bf16;
   long long ld;
   int vocab;
-  const int* counts;         // [rows, vocab] occurrences of each token so far (may be null)
+  const int* counts;         // [*, vocab] occurrences of each token so far (may be null)
+  const int* count_rows;     // [rows] row of `counts` that belongs to each logits row (null: the same row index)
   const float* temperature;  // per row
   const int* top_k;          // per row, <= 0 disables
   const float* top_p;        // per row, >= 1 disables
@@ -184,7 +185,7 @@ __global__ void __launch_bounds__(kSampThreads) sample_kernel(const SampleParams
   RowView row;
   row.base = static_cast<const char*>(p.logits) + static_cast<long long>(r) * p.ld * (p.is_bf16 ? 2 : 4);
   row.is_bf16 = p.is_bf16;
-  row.counts = p.counts ? p.counts + static_cast<long long>(r) * p.vocab : nullptr;
+  row.counts = p.counts ? p.counts + static_cast<long long>(p.count_rows ? p.count_rows[r] : r) * p.vocab : nullptr;
   const float temp = p.temperature[r];
   const bool greedy = !(temp > 0.f);
   row.inv_t = greedy ? 1.f : 1.f / temp;
@@ -339,11 +340,13 @@ __global__ void __launch_bounds__(kSampThreads) spec_verify_kernel(const VerifyP
 }
 
 // counts[row, token] += 1 for each newly sampled token (keeps the penalty table current without a host round trip)
-__global__ void count_tokens_kernel(int* __restrict__ counts, const int* __restrict__ tokens, int rows, int vocab) {
+__global__ void count_tokens_kernel(int* __restrict__ counts, const int* __restrict__ count_rows,
+                                    const int* __restrict__ tokens, int rows, int vocab) {
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   const int t = tokens[r];
-  if (t >= 0 && t < vocab) counts[static_cast<long long>(r) * vocab + t] += 1;
+  const long long cr = count_rows ? count_rows[r] : r;
+  if (t >= 0 && t < vocab) counts[cr * vocab + t] += 1;
 }
 
 }  // namespace pm
@@ -351,12 +354,12 @@ __global__ void count_tokens_kernel(int* __restrict__ counts, const int* __restr
 using namespace pm;
 
 extern "C" int pm_sample(const void* logits, int is_bf16, long long ld, int rows, int vocab, const int* counts,
-                         const float* temperature, const int* top_k, const float* top_p, const float* min_p,
+                         const int* count_rows, const float* temperature, const int* top_k, const float* top_p, const float* min_p,
                          const float* rep_pen, const float* freq_pen, const float* pres_pen,
                          const unsigned long long* seeds, unsigned long long step, int* out_token, float* out_logprob,
                          cudaStream_t st) {
   if (rows <= 0 || vocab <= 0 || !temperature) return -1;
-  SampleParams p{logits, is_bf16, ld, vocab, counts, temperature, top_k, top_p, min_p, rep_pen, freq_pen, pres_pen,
+  SampleParams p{logits, is_bf16, ld, vocab, counts, count_rows, temperature, top_k, top_p, min_p, rep_pen, freq_pen, pres_pen,
                  seeds, step, out_token, out_logprob};
   sample_kernel<<<rows, kSampThreads, 0, st>>>(p);
   return static_cast<int>(cudaGetLastError());
@@ -372,8 +375,9 @@ extern "C" int pm_spec_verify(const float* target, const float* draft, const int
   return static_cast<int>(cudaGetLastError());
 }
 
-extern "C" int pm_count_tokens(int* counts, const int* tokens, int rows, int vocab, cudaStream_t st) {
+extern "C" int pm_count_tokens(int* counts, const int* count_rows, const int* tokens, int rows, int vocab,
+                               cudaStream_t st) {
   if (rows <= 0) return 0;
-  count_tokens_kernel<<<(rows + 127) / 128, 128, 0, st>>>(counts, tokens, rows, vocab);
+  count_tokens_kernel<<<(rows + 127) / 128, 128, 0, st>>>(counts, count_rows, tokens, rows, vocab);
   return static_cast<int>(cudaGetLastError());
 }

@@ -83,13 +83,18 @@ __device__ __forceinline__ void tp_st_release(uint32_t* p, uint32_t v) {
 // bounded wait for *flag >= epoch (wrap-safe); false on expiry
 __device__ __forceinline__ bool tp_wait_flag(const uint32_t* flag, uint32_t epoch, unsigned long long timeout_ns,
                                              int* status) {
-  const unsigned long long t0 = globaltimer_ns();
+  unsigned long long t0 = 0;     // the global timer is slow to read: first looked at after 1024 failed polls
   uint32_t spins = 0;
   while (static_cast<int32_t>(tp_ld_acquire(flag) - epoch) < 0) {
     if ((++spins & 31u) == 0u) {
-      if (globaltimer_ns() - t0 > timeout_ns) {
-        atomicCAS(status, 0, kStatusTpPeer);
-        return false;
+      if (spins >= 1024u) {
+        const unsigned long long now = globaltimer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > timeout_ns) {
+          atomicCAS(status, 0, kStatusTpPeer);
+          return false;
+        }
       }
       __nanosleep(64);
     }
@@ -168,11 +173,17 @@ tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
         const int m0 = (p.mode == 0) ? (remote ? owner * p.rows_per_rank + mb * kBM : mb * kBM) : (owner * tpr + mb) * kBM;
         if (remote) {   // the row block must have been copied into the gathered buffer (by some CTA's copy warps)
           const uint32_t* flag = p.blk_ready + owner * tpr + mb;
-          const unsigned long long t0 = globaltimer_ns();
+          unsigned long long t0 = 0;     // timer first read after 1024 failed polls (it is slow to read)
           uint32_t spins = 0;
           while (static_cast<int32_t>(tp_ld_acquire_gpu(flag) - epoch) < 0 && ok) {
             if ((++spins & 31u) == 0u) {
-              if (*abort_flag || globaltimer_ns() - t0 > p.timeout_ns) {
+              bool late = false;
+              if (spins >= 1024u) {
+                const unsigned long long now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                late = now - t0 > p.timeout_ns;
+              }
+              if (*abort_flag || late) {
                 atomicCAS(p.status, 0, kStatusTpPeer);
                 *abort_flag = 1;
                 ok = false;

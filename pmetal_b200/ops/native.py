@@ -16,7 +16,8 @@ import torch
 _LIB = None
 _ERR: Optional[str] = None
 _STATUS = {}
-LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libpmetal_b200.so")
+LIB_PATH = os.environ.get("PMETAL_NATIVE_LIB") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libpmetal_b200.so")
 
 # The transposed LoRA products read token-major tensors through MN-major tcgen05 descriptors.
 # PMETAL_MN_MAJOR=0 routes them through explicit transposes instead.
@@ -538,15 +539,16 @@ c_ull = ctypes.c_ulonglong
 
 
 def sample(logits, temperature, top_k=None, top_p=None, min_p=None, counts=None, rep_pen=None, freq_pen=None,
-           pres_pen=None, seeds=None, step: int = 0, want_logprob: bool = True):
+           pres_pen=None, seeds=None, step: int = 0, want_logprob: bool = True, count_rows=None):
     """logits [rows, V] fp32 or bf16 (row stride arbitrary); per-row parameter tensors on the device.
+    ``counts`` [*, V] int32 holds token occurrences; logits row r uses counts row ``count_rows[r]`` (int32, default r).
     Returns (tokens int32 [rows], logprobs fp32 [rows] or None)."""
     rows, V = logits.shape
     assert logits.stride(1) == 1 and logits.dtype in (torch.float32, torch.bfloat16)
     tok = torch.empty(rows, dtype=torch.int32, device=logits.device)
     lp = torch.empty(rows, dtype=torch.float32, device=logits.device) if want_logprob else None
     _chk(lib().pm_sample(_p(logits), c_int(int(logits.dtype == torch.bfloat16)), c_ll(logits.stride(0)), c_int(rows),
-                         c_int(V), _p(counts), _p(temperature), _p(top_k), _p(top_p), _p(min_p), _p(rep_pen),
+                         c_int(V), _p(counts), _p(count_rows), _p(temperature), _p(top_k), _p(top_p), _p(min_p), _p(rep_pen),
                          _p(freq_pen), _p(pres_pen), _p(seeds), c_ull(step), _p(tok), _p(lp), _stream()), "pm_sample")
     return tok, lp
 
@@ -567,9 +569,10 @@ def spec_verify(target_logits, draft_logits, draft_tokens, temperature: float = 
     return acc, nxt
 
 
-def count_tokens(counts, tokens) -> None:
-    _chk(lib().pm_count_tokens(_p(counts), _p(tokens), c_int(tokens.numel()), c_int(counts.shape[1]), _stream()),
-         "pm_count_tokens")
+def count_tokens(counts, tokens, count_rows=None) -> None:
+    """counts[count_rows[r] (default r), tokens[r]] += 1 for every row r."""
+    _chk(lib().pm_count_tokens(_p(counts), _p(count_rows), _p(tokens), c_int(tokens.numel()), c_int(counts.shape[1]),
+                               _stream()), "pm_count_tokens")
 
 
 # ------------------------------------------------------------------------------------------- MoE routing

@@ -5,7 +5,12 @@ a fixed pool of slots, a FIFO queue with block-budget admission, serial chunked 
 token sampled right after its last chunk, prompt parked in the prefix cache), and one batched decode step per tick for
 all active slots with per-slot sampling parameters, stop sequences, log-probabilities and retirement. Where the
 reference keeps a dense [slots, heads, max_seq, D] cache and slices it, this engine decodes straight from the paged
-cache with the block-table attention kernel, and samples every slot in one fused kernel launch."""
+cache with the block-table attention kernel, and samples every slot in one fused kernel launch.
+
+Sampling state per slot: repetition / frequency / presence penalties see the tokens generated so far (a device table
+of per-token counts, one row per slot, updated by a kernel after every step; crates/pmetal-models/src/generation.rs:
+813-838). Stop strings are matched on the decoded text after every token and the tokens that spell the match are cut
+from the output (crates/pmetal-serve/src/engine.rs:225-250)."""
 from __future__ import annotations
 
 import threading
@@ -22,12 +27,36 @@ from ..models.sampling import Sampler, SamplingParams
 from .prefix_cache import PrefixCache
 
 
+def detect_stop_suffix(decode: Callable[[List[int]], str], generated: Sequence[int], stops: Sequence[str]) -> int:
+    """Number of trailing tokens of ``generated`` whose decoding is exactly the longest stop string that the decoded
+    output ends with; 0 when no stop string ends the text or the match does not start on a token boundary."""
+    stops = [s for s in stops if s]
+    if not generated or not stops:
+        return 0
+    longest = max(len(s) for s in stops)
+    # a token decodes to at least one character in practice; a generous window keeps the check O(stop length)
+    window = list(generated[-(2 * longest + 8):])
+    text = decode(window)
+    hit = [s for s in stops if text.endswith(s)]
+    if not hit:
+        return 0
+    match = max(hit, key=len)
+    for n in range(1, len(window) + 1):
+        if decode(window[-n:]) == match:
+            return n
+    return 0
+
+
 @dataclass
 class Request:
     prompt: List[int]
     params: SamplingParams = field(default_factory=SamplingParams)
     stop_sequences: List[List[int]] = field(default_factory=list)
     want_logprobs: bool = False
+    stop_strings: List[str] = field(default_factory=list)                   # matched on decoded text (needs ``decode``)
+    decode: Optional[Callable[[List[int]], str]] = None
+    top_logprobs: int = 0                                                   # alternatives recorded per generated token
+    top_entries: List[List[tuple]] = field(default_factory=list)            # per token: [(token id, logprob), ...]
     on_token: Optional[Callable[[int, Optional[float]], None]] = None       # called from the engine thread
     on_done: Optional[Callable[["Request"], None]] = None
     # filled by the engine
@@ -49,6 +78,7 @@ class _Slot:
     prefill_pos: int = 0
     last_token: int = -1
     state: str = "prefill"       # prefill | decode
+    row: int = -1                # row of the penalty count table (-1: the request uses no penalty)
 
 
 @dataclass
@@ -87,6 +117,8 @@ class ContinuousBatchEngine:
         self._thread: Optional[threading.Thread] = None
         self._next_req = 0
         self._step = 0
+        self._counts: Optional[torch.Tensor] = None      # [max_slots, vocab] int32, allocated on first use
+        self._free_rows = list(range(max_slots))
 
     # ------------------------------------------------------------------ submission
     def submit(self, req: Request) -> Request:
@@ -141,6 +173,14 @@ class ContinuousBatchEngine:
                     req.cached_tokens = n
                     self.stats.prefix_hits += 1
             self.stats.prompt_tokens += len(req.prompt)
+            p = req.params
+            if p.repetition_penalty != 1.0 or p.frequency_penalty != 0.0 or p.presence_penalty != 0.0:
+                slot.row = self._free_rows.pop()
+                if self._counts is None:
+                    self._counts = torch.zeros(self.max_slots, self.model.cfg.vocab_size, dtype=torch.int32,
+                                               device=self.device)
+                else:
+                    self._counts[slot.row].zero_()
             self.slots.append(slot)
 
     def _finish(self, req: Request, reason: str) -> None:
@@ -167,21 +207,43 @@ class ContinuousBatchEngine:
         for ss in req.stop_sequences:
             if ss and len(req.output) >= len(ss) and req.output[-len(ss):] == ss:
                 return self._retire(slot, "stop")
+        if req.stop_strings and req.decode is not None:
+            cut = detect_stop_suffix(req.decode, req.output, req.stop_strings)
+            if cut:                                  # the tokens that spell the stop string are not part of the answer
+                del req.output[-cut:]
+                del req.logprobs[len(req.output):]
+                del req.top_entries[len(req.output):]
+                return self._retire(slot, "stop")
         if len(req.output) >= req.params.max_tokens:
             return self._retire(slot, "length")
         slot.last_token = tok
         return False
 
     def _retire(self, slot: _Slot, reason: str) -> bool:
+        if slot.row >= 0:
+            self._free_rows.append(slot.row)
+            slot.row = -1
         self.cache.free_sequence(slot.seq)
         self.slots.remove(slot)
         self._finish(slot.req, reason)
         return True
 
     def _sample(self, logits: torch.Tensor, slots: List[_Slot]):
-        """One fused launch for all rows on the GPU; per-request Sampler objects otherwise."""
+        """One fused launch for all rows on the GPU; per-request Sampler objects otherwise. Returns (token ids,
+        log-probabilities or None); alternatives for requests that asked for ``top_logprobs`` are stored on the request."""
         from ..ops import functional as ops
         want_lp = any(s.req.want_logprobs for s in slots)
+        pen = any(s.row >= 0 for s in slots)
+        top_n = max((s.req.top_logprobs for s in slots), default=0)
+        if top_n > 0:
+            # alternatives come from the unfiltered distribution, as the chosen token's reported log-probability does
+            lsm = torch.log_softmax(logits.float(), -1)
+            tv, ti = lsm.topk(min(top_n, lsm.shape[-1]), -1)
+            tv, ti = tv.tolist(), ti.tolist()
+            for j, s in enumerate(slots):
+                n = s.req.top_logprobs
+                if n > 0:
+                    s.req.top_entries.append(list(zip(ti[j][:n], tv[j][:n])))
         if ops.native_enabled(logits):
             from ..ops import native
             dev = logits.device
@@ -194,20 +256,39 @@ class ContinuousBatchEngine:
             lg = logits if logits.stride(-1) == 1 else logits.contiguous()
             if lg.dtype not in (torch.float32, torch.bfloat16):
                 lg = lg.float()
+            counts = rows = rep_t = freq_t = pres_t = None
+            if pen:
+                # rows without a penalty point at row 0 with neutral factors, which leaves their logits untouched
+                counts = self._counts
+                rows = torch.tensor([max(s.row, 0) for s in slots], dtype=torch.int32, device=dev)
+                on = [s.row >= 0 for s in slots]
+                rep_t = f([p.repetition_penalty if o else 1.0 for p, o in zip(ps, on)])
+                freq_t = f([p.frequency_penalty if o else 0.0 for p, o in zip(ps, on)])
+                pres_t = f([p.presence_penalty if o else 0.0 for p, o in zip(ps, on)])
             ids, lp = native.sample(lg, temp, torch.tensor([p.top_k for p in ps], dtype=torch.int32, device=dev),
-                                    f([p.top_p for p in ps]), f([p.min_p for p in ps]), None, None, None, None, seeds,
-                                    self._step, want_lp)
+                                    f([p.top_p for p in ps]), f([p.min_p for p in ps]), counts, rep_t, freq_t, pres_t,
+                                    seeds, self._step, want_lp, count_rows=rows)
+            if pen:
+                sel = [j for j, s in enumerate(slots) if s.row >= 0]
+                if len(sel) == len(slots):
+                    native.count_tokens(counts, ids, rows)
+                else:
+                    ix = torch.tensor(sel, dtype=torch.int64, device=dev)
+                    native.count_tokens(counts, ids[ix].contiguous(), rows[ix].contiguous())
             return ids.tolist(), (lp.tolist() if want_lp else None)
         ids, lps = [], []
         for j, s in enumerate(slots):
             smp = getattr(s, "_sampler", None)
             if smp is None:
                 smp = s._sampler = Sampler(s.req.params, logits.device)
+            cnt = self._counts[s.row:s.row + 1] if s.row >= 0 else None
             if want_lp:
-                i, l = smp.sample(logits[j:j + 1], None, True)
+                i, l = smp.sample(logits[j:j + 1], cnt, True)
                 lps.append(float(l[0]))
             else:
-                i = smp.sample(logits[j:j + 1])
+                i = smp.sample(logits[j:j + 1], cnt)
+            if s.row >= 0:
+                self._counts[s.row, int(i[0])] += 1
             ids.append(int(i[0]))
         return ids, (lps if want_lp else None)
 

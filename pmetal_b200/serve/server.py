@@ -1,7 +1,9 @@
 """OpenAI- and Anthropic-compatible HTTP server on top of the continuous-batching engine.
 
 Routes (crates/pmetal-serve/src/server.rs:41-100, routes.rs:30-1060, anthropic.rs, sse.rs):
-``POST /v1/chat/completions`` (streaming SSE and non-streaming, tools passed to the chat template, logprobs),
+``POST /v1/chat/completions`` (streaming SSE and non-streaming, tools passed to the chat template and tool calls parsed
+back out of the answer, ``logprobs`` / ``top_logprobs``, stop strings matched on the decoded text with the last tokens
+held back from a stream until they can no longer be part of a stop string: routes.rs:162,235-335,558-605),
 ``POST /v1/completions``, ``POST /v1/embeddings`` (mean-pooled, L2-normalised final hidden states),
 ``POST /v1/messages`` (Anthropic), ``GET /v1/models``, ``GET /v1/metrics``, ``GET /health``.
 A semaphore bounds in-flight requests and bodies larger than 2 MiB are rejected, as in the reference."""
@@ -38,6 +40,41 @@ def _params(body: Dict[str, Any], default_max: int = 256) -> SamplingParams:
                           do_sample=temp > 0, seed=body.get("seed"), stop_token_ids=stop_ids)
 
 
+def try_parse_tool_calls(text: str) -> Optional[List[dict]]:
+    """Tool calls in a model answer (crates/pmetal-serve/src/types.rs:474-519): the whole answer must be one JSON
+    value, either ``{"tool_calls": [{"function": {"name", "arguments"}, ...}]}`` or a bare ``{"name", "arguments"}``.
+    Returns OpenAI-style tool-call objects or None when the text is ordinary prose."""
+    t = text.strip()
+    if not t.startswith(("{", "[")):
+        return None
+    try:
+        v = json.loads(t)
+    except json.JSONDecodeError:
+        return None
+    if not isinstance(v, dict):
+        return None
+
+    def call(name, arguments, cid=None, kind="function"):
+        args = arguments if isinstance(arguments, str) else json.dumps(arguments)
+        return {"id": cid or "call_" + uuid.uuid4().hex[:24], "type": kind, "function": {"name": name, "arguments": args}}
+    if isinstance(v.get("tool_calls"), list):
+        out = []
+        for tc in v["tool_calls"]:
+            fn = tc.get("function") if isinstance(tc, dict) else None
+            if isinstance(fn, dict) and isinstance(fn.get("name"), str):
+                out.append(call(fn["name"], fn.get("arguments"), tc.get("id"), tc.get("type") or "function"))
+        return out or None
+    if isinstance(v.get("name"), str):
+        return [call(v["name"], v.get("arguments"))]
+    return None
+
+
+def _stop_list(stop) -> List[str]:
+    if not stop:
+        return []
+    return [s for s in ([stop] if isinstance(stop, str) else list(stop)) if isinstance(s, str) and s]
+
+
 def _content_text(content) -> str:
     if isinstance(content, str):
         return content
@@ -58,40 +95,50 @@ class ServerState:
                         m.get("name")) for m in messages]
         return self.tok.encode_with_special_tokens(self.template.apply_inference(msgs, no_thinking, tools))
 
-    def stop_sequences(self, stop) -> List[List[int]]:
-        if not stop:
-            return []
-        if isinstance(stop, str):
-            stop = [stop]
-        return [self.tok.encode(s) for s in stop if s]
-
-    async def run(self, prompt: List[int], params: SamplingParams, stop=None, want_logprobs=False) -> Request:
+    async def run(self, prompt: List[int], params: SamplingParams, stop=None, want_logprobs=False,
+                  top_logprobs: int = 0) -> Request:
         loop = asyncio.get_running_loop()
         fut = loop.create_future()
-        req = Request(prompt, params, self.stop_sequences(stop), want_logprobs,
+        req = Request(prompt, params, [], want_logprobs or top_logprobs > 0, stop_strings=_stop_list(stop),
+                      decode=self.tok.decode, top_logprobs=top_logprobs,
                       on_done=lambda r: loop.call_soon_threadsafe(fut.set_result, r))
         self.engine.submit(req)
         return await fut
 
     async def stream(self, prompt: List[int], params: SamplingParams, stop=None) -> AsyncIterator[tuple]:
-        """Yields (text piece, finish_reason or None)."""
+        """Yields (text piece, finish_reason or None). With stop strings the newest tokens are held back (as many
+        tokens as the longest stop string has characters) so that text which turns out to be the beginning of a stop
+        string is never sent; when the request ends, only the tokens the engine kept are flushed."""
         loop = asyncio.get_running_loop()
         q: asyncio.Queue = asyncio.Queue()
-        req = Request(prompt, params, self.stop_sequences(stop), False,
+        stops = _stop_list(stop)
+        hold = max((len(x) for x in stops), default=0)
+        req = Request(prompt, params, [], False, stop_strings=stops, decode=self.tok.decode,
                       on_token=lambda t, lp: loop.call_soon_threadsafe(q.put_nowait, ("tok", t)),
-                      on_done=lambda r: loop.call_soon_threadsafe(q.put_nowait, ("done", r.finish_reason)))
+                      on_done=lambda r: loop.call_soon_threadsafe(q.put_nowait, ("done", (r.finish_reason, len(r.output)))))
         self.engine.submit(req)
         dec = StreamDecoder(self.tok)
+        pending: List[int] = []
+        sent = 0
+
+        def release(tok: int) -> str:
+            return "" if tok in self.engine.eos else (dec.push(tok) or "")
         while True:
             kind, val = await q.get()
             if kind == "done":
-                yield "", val
+                reason, kept = val
+                for tok in pending[:max(kept - sent, 0)]:
+                    piece = release(tok)
+                    if piece:
+                        yield piece, None
+                yield "", reason
                 return
-            if val in self.engine.eos:
-                continue
-            piece = dec.push(val)
-            if piece:
-                yield piece, None
+            pending.append(val)
+            while len(pending) > hold:
+                piece = release(pending.pop(0))
+                sent += 1
+                if piece:
+                    yield piece, None
 
     def text_of(self, req: Request) -> str:
         ids = [t for t in req.output if t not in self.engine.eos]
@@ -149,19 +196,41 @@ def create_app(state: ServerState):
                     base = {"id": rid, "object": "chat.completion.chunk", "created": created, "model": state.model_name}
                     yield sse({**base, "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""},
                                                     "finish_reason": None}]})
+                    whole = []
                     async for piece, fin in state.stream(prompt, params, body.get("stop")):
                         if fin is None:
+                            whole.append(piece)
                             yield sse({**base, "choices": [{"index": 0, "delta": {"content": piece}, "finish_reason": None}]})
                         else:
-                            yield sse({**base, "choices": [{"index": 0, "delta": {}, "finish_reason": state.finish(fin)}]})
+                            calls = try_parse_tool_calls("".join(whole)) if body.get("tools") else None
+                            if calls:               # tool-aware clients get the structured call in the closing chunk
+                                yield sse({**base, "choices": [{"index": 0, "delta": {"tool_calls": [
+                                    {"index": i, **c} for i, c in enumerate(calls)]}, "finish_reason": "tool_calls"}]})
+                            else:
+                                yield sse({**base, "choices": [{"index": 0, "delta": {}, "finish_reason": state.finish(fin)}]})
                     yield sse(b"[DONE]")
                 return StreamingResponse(gen(), media_type="text/event-stream")
-            req = await state.run(prompt, params, body.get("stop"), bool(body.get("logprobs")))
-        choice = {"index": 0, "message": {"role": "assistant", "content": state.text_of(req)},
-                  "finish_reason": state.finish(req.finish_reason)}
+            top_n = min(int(body.get("top_logprobs") or 0), 20) if body.get("logprobs") else 0
+            req = await state.run(prompt, params, body.get("stop"), bool(body.get("logprobs")), top_n)
+        text = state.text_of(req)
+        calls = try_parse_tool_calls(text) if body.get("tools") else None
+        if calls:                                   # a structured call replaces the text (routes.rs:304-309)
+            choice = {"index": 0, "message": {"role": "assistant", "content": None, "tool_calls": calls},
+                      "finish_reason": "tool_calls"}
+        else:
+            choice = {"index": 0, "message": {"role": "assistant", "content": text},
+                      "finish_reason": state.finish(req.finish_reason)}
         if body.get("logprobs"):
-            choice["logprobs"] = {"content": [{"token": state.tok.decode([t]), "logprob": lp}
-                                              for t, lp in zip(req.output, req.logprobs)]}
+            content = []
+            for i, (t, lp) in enumerate(zip(req.output, req.logprobs)):
+                piece = state.tok.decode([t])
+                entry = {"token": piece, "logprob": lp, "bytes": list(piece.encode("utf-8"))}
+                if top_n:
+                    alts = req.top_entries[i] if i < len(req.top_entries) else []
+                    entry["top_logprobs"] = [{"token": state.tok.decode([a]), "logprob": alp,
+                                              "bytes": list(state.tok.decode([a]).encode("utf-8"))} for a, alp in alts]
+                content.append(entry)
+            choice["logprobs"] = {"content": content}
         return {"id": rid, "object": "chat.completion", "created": created, "model": state.model_name, "choices": [choice],
                 "usage": {"prompt_tokens": len(prompt), "completion_tokens": len(req.output),
                           "total_tokens": len(prompt) + len(req.output),
@@ -187,9 +256,17 @@ def create_app(state: ServerState):
                                                         "finish_reason": None if fin is None else state.finish(fin)}]})
                     yield sse(b"[DONE]")
                 return StreamingResponse(gen(), media_type="text/event-stream")
-            req = await state.run(prompt, params, body.get("stop"), bool(body.get("logprobs")))
+            n_lp = body.get("logprobs")
+            top_n = min(int(n_lp), 20) if isinstance(n_lp, int) and not isinstance(n_lp, bool) else 0
+            req = await state.run(prompt, params, body.get("stop"), bool(n_lp), top_n)
+        choice = {"index": 0, "text": state.text_of(req), "finish_reason": state.finish(req.finish_reason)}
+        if n_lp:                                    # legacy completions layout (routes.rs:446-471)
+            toks = [state.tok.decode([t]) for t in req.output]
+            choice["logprobs"] = {"tokens": toks, "token_logprobs": list(req.logprobs),
+                                  "top_logprobs": [{state.tok.decode([a]): alp for a, alp in alts}
+                                                   for alts in req.top_entries] if top_n else None}
         return {"id": rid, "object": "text_completion", "created": created, "model": state.model_name,
-                "choices": [{"index": 0, "text": state.text_of(req), "finish_reason": state.finish(req.finish_reason)}],
+                "choices": [choice],
                 "usage": {"prompt_tokens": len(prompt), "completion_tokens": len(req.output),
                           "total_tokens": len(prompt) + len(req.output)}}
 

@@ -120,3 +120,89 @@ def test_http_routes():
             assert c.get("/v1/metrics").json()["requests_done"] >= 4
     finally:
         eng.shutdown()
+
+
+def test_stop_suffix_detection_follows_token_boundaries():
+    from pmetal_b200.serve.engine import detect_stop_suffix
+    words = {1: "alpha", 2: " beta", 3: " gamma", 4: " be", 5: "ta"}
+    dec = lambda ids: "".join(words[i] for i in ids)      # noqa: E731
+    assert detect_stop_suffix(dec, [1, 2, 3], ["beta gamma"]) == 0          # " beta gamma" != "beta gamma": no boundary
+    assert detect_stop_suffix(dec, [1, 2, 3], [" beta gamma"]) == 2
+    assert detect_stop_suffix(dec, [1, 2, 3], [" gamma", " beta gamma"]) == 2   # the longest match wins
+    assert detect_stop_suffix(dec, [1, 4, 5], [" beta"]) == 2               # a stop string spread over two tokens
+    assert detect_stop_suffix(dec, [1, 2], ["delta"]) == 0 and detect_stop_suffix(dec, [], ["x"]) == 0
+
+
+def test_stop_strings_cut_the_output_and_penalties_change_sampling():
+    from pmetal_b200.data.tokenizer import ByteTokenizer
+    m = tiny()
+    tok = ByteTokenizer()
+    eng = ContinuousBatchEngine(m, max_slots=4, num_blocks=64)
+    base = eng.generate([1, 2, 3, 4, 5], SamplingParams.greedy(24))
+    text = tok.decode(base.output)
+    # pick a stop string from the middle of the greedy answer (byte tokenizer: one token per byte)
+    i = max(3, len(base.output) // 2)
+    stop = tok.decode(base.output[i:i + 2])
+    r = eng.generate([1, 2, 3, 4, 5], SamplingParams.greedy(24), stop_strings=[stop], decode=tok.decode,
+                     want_logprobs=True)
+    first = text.find(stop)
+    assert r.finish_reason == "stop" and tok.decode(r.output) == text[:first]
+    assert len(r.logprobs) == len(r.output)
+    # a greedy answer of a tiny random model repeats itself; penalties over the generated tokens change that
+    greedy = SamplingParams.greedy(24)
+    pen = SamplingParams.greedy(24)
+    pen.repetition_penalty, pen.frequency_penalty, pen.presence_penalty = 1.8, 0.6, 0.4
+    a = eng.generate([9, 9, 9], greedy).output
+    b = eng.generate([9, 9, 9], pen).output
+    assert a != b and len(set(b)) > len(set(a))
+    assert sorted(eng._free_rows) == list(range(4))          # count-table rows go back to the pool
+    # the penalised request does not disturb an unpenalised one decoded in the same batch
+    r1 = eng.submit(Request([9, 9, 9], greedy))
+    r2 = eng.submit(Request([9, 9, 9], pen))
+    while not (r1.done.is_set() and r2.done.is_set()):
+        eng.tick()
+    assert r1.output == a and r2.output == b
+    eng.shutdown()
+
+
+def test_http_logprob_alternatives_stop_holdback_and_tool_calls():
+    fastapi = pytest.importorskip("fastapi")
+    from fastapi.testclient import TestClient
+    from pmetal_b200.data.tokenizer import ByteTokenizer
+    from pmetal_b200.serve.server import ServerState, create_app, try_parse_tool_calls
+    calls = try_parse_tool_calls(' {"name": "get_weather", "arguments": {"city": "Oslo"}} ')
+    assert calls and calls[0]["function"]["name"] == "get_weather" and json.loads(calls[0]["function"]["arguments"]) == {"city": "Oslo"}
+    calls = try_parse_tool_calls('{"tool_calls": [{"id": "c1", "function": {"name": "f", "arguments": "{}"}}, {"nofunction": 1}]}')
+    assert len(calls) == 1 and calls[0]["id"] == "c1" and calls[0]["type"] == "function"
+    assert try_parse_tool_calls("sure, here you go") is None and try_parse_tool_calls("{broken") is None
+    assert try_parse_tool_calls('{"answer": 42}') is None
+    m = tiny()
+    eng = ContinuousBatchEngine(m, max_slots=4, num_blocks=128)
+    eng.start()
+    try:
+        tok = ByteTokenizer()
+        app = create_app(ServerState(eng, tok, model_name="tiny"))
+        with TestClient(app) as c:
+            msg = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 12, "temperature": 0}
+            j = c.post("/v1/chat/completions", json={**msg, "logprobs": True, "top_logprobs": 3}).json()
+            content = j["choices"][0]["logprobs"]["content"]
+            assert len(content) == j["usage"]["completion_tokens"]
+            for e in content:
+                assert len(e["top_logprobs"]) == 3 and e["top_logprobs"][0]["logprob"] >= e["top_logprobs"][1]["logprob"]
+                assert abs(e["top_logprobs"][0]["logprob"] - e["logprob"]) < 1e-3      # greedy: the choice is the top entry
+            full = j["choices"][0]["message"]["content"]
+            # stop string taken from the answer: non-streaming and streaming both end right before it
+            stop = full[4:6]
+            cut = full[:full.find(stop)]
+            j2 = c.post("/v1/chat/completions", json={**msg, "stop": [stop]}).json()
+            assert j2["choices"][0]["message"]["content"] == cut and j2["choices"][0]["finish_reason"] == "stop"
+            with c.stream("POST", "/v1/chat/completions", json={**msg, "stop": stop, "stream": True}) as s:
+                lines = [l for l in s.iter_lines() if l.startswith("data: ") and l != "data: [DONE]"]
+            pieces = "".join(json.loads(l[6:])["choices"][0]["delta"].get("content") or "" for l in lines)
+            assert pieces == cut                                                         # nothing of the stop string leaked
+            j3 = c.post("/v1/completions", json={"prompt": "abc", "max_tokens": 4, "temperature": 0, "logprobs": 2}).json()
+            lp = j3["choices"][0]["logprobs"]
+            # (alternatives are keyed by their text: two byte tokens that decode to the same replacement character share a key)
+            assert len(lp["tokens"]) == len(lp["token_logprobs"]) == len(lp["top_logprobs"]) and 1 <= len(lp["top_logprobs"][0]) <= 2
+    finally:
+        eng.shutdown()
