@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import json
+import logging
 import os
 import sys
 
@@ -433,11 +434,13 @@ def _infer_args(sp):
 
 
 def _add_kv_quant_flags(p):
-    """The reference compresses the KV cache to fit unified memory (crates/pmetal/src/cli/infer.rs); the paged cache here
-    stays bf16 (the attention kernels read bf16 blocks), so the flags are accepted and reported as not applied.
-    Quantised caches exist for the portable models (``GenericDecoderLM.new_cache(kv_bits=...)``) and as a library
-    (``models/turboquant.py``)."""
-    p.add_argument("--kv-quant", action="store_true")
+    """KV-cache flags (crates/pmetal/src/cli/infer.rs:150-180). On the fast path the paged cache holds bf16 or int8
+    blocks (the attention kernel expands int8 blocks as it loads them); without flags int8 is chosen by itself when
+    weights plus a 16-bit cache would not fit comfortably (``models.kv_cache.select_cache_mode``). Narrower widths and
+    TurboQuant run on the portable models' cache (``GenericDecoderLM.new_cache(kv_bits=...)``). ``--kv-window`` /
+    ``--kv-keep`` turn the cache into a rotating one: only the last N tokens (plus the first ``keep``) stay resident."""
+    p.add_argument("--kv-quant", nargs="?", const=8, type=int, default=None, metavar="BITS",
+                   help="quantise the KV cache (8 when no width is given; 0 = off)")
     p.add_argument("--no-kv-quant", action="store_true")
     p.add_argument("--kv-group-size", type=int, default=64)
     p.add_argument("--kv-k-bits", type=int)
@@ -446,12 +449,34 @@ def _add_kv_quant_flags(p):
     p.add_argument("--kv-turboquant", action="store_true")
     p.add_argument("--kv-turboquant-preset")
     p.add_argument("--kv-quant-preset")
+    p.add_argument("--kv-window", type=int, default=0, help="rotating cache: keep only the last N tokens")
+    p.add_argument("--kv-keep", type=int, default=0, help="rotating cache: leading tokens that are never dropped")
 
 
-def _note_kv_flags(a) -> None:
-    if any(getattr(a, k, None) for k in ("kv_quant", "kv_turboquant", "kv_k_bits", "kv_v_bits", "kv_qjl",
-                                         "kv_turboquant_preset", "kv_quant_preset")):
-        print("note: KV-cache quantisation flags are not applied: the paged cache stays bf16", file=sys.stderr)
+def _paged_cache_options(a, model, num_blocks: int) -> dict:
+    """Keyword arguments for ``DecoderLM.new_cache`` from the ``--kv-*`` flags and the memory estimate."""
+    import torch
+    from ..models.kv_cache import BLOCK, select_cache_mode
+    cfg = model.cfg
+    weight_bytes = sum(p.numel() * p.element_size() for p in model.parameters())
+    kv16 = 2 * cfg.num_hidden_layers * num_blocks * BLOCK * cfg.num_key_value_heads * cfg.head_dim * 2
+    dev = model.embed_tokens.device
+    total = torch.cuda.get_device_properties(dev).total_memory if dev.type == "cuda" else None
+    turbo = bool(a.kv_turboquant or a.kv_turboquant_preset or a.kv_quant_preset)
+    mode = select_cache_mode(weight_bytes, kv16, total, a.kv_quant, a.no_kv_quant, a.kv_k_bits, a.kv_v_bits, turbo,
+                             a.kv_group_size)
+    quant = None
+    if mode.kind != "standard":
+        quant = "int8"
+        if mode.kind != "quantized" or mode.bits != 8 or a.kv_group_size != 64 or a.kv_qjl:
+            print(f"note: the paged cache stores bf16 or int8 (group 64); using int8 instead of {mode.kind} "
+                  f"k{mode.k_bits}/v{mode.v_bits} (narrower caches run on the portable models)", file=sys.stderr)
+        if cfg.head_dim % 64:
+            quant = None
+    if quant or a.kv_window:
+        logging.getLogger("pmetal").info("kv cache: %s (%s)%s", quant or "bf16", mode.source,
+                                         f", window {a.kv_window} keep {a.kv_keep}" if a.kv_window else "")
+    return dict(quant=quant, window=int(a.kv_window or 0), sink=int(a.kv_keep or 0))
 
 
 def cut_repetition(tokens, min_period: int = 1, max_period: int = 64, min_repeats: int = 4, min_span: int = 24):
@@ -561,7 +586,7 @@ def _infer_portable(a, model_dir: str) -> int:
     sampler = Sampler(sp_, torch.device(dev))
     kv_bits = None
     if a.kv_turboquant or a.kv_quant or a.kv_k_bits:
-        kv_bits = a.kv_k_bits or (4 if a.kv_turboquant else 8)
+        kv_bits = a.kv_k_bits or (4 if a.kv_turboquant else (a.kv_quant if isinstance(a.kv_quant, int) and a.kv_quant > 0 else 8))
     cache = model.new_cache(kv_bits, a.kv_group_size, bool(a.kv_turboquant), bool(a.kv_qjl)) if hasattr(model, "new_cache") \
         else None
     if cache is None:
@@ -610,7 +635,6 @@ def cmd_infer(a) -> int:
     from ..data.stream_format import StreamFormatter
     from ..models.generation import Generator
     model, tok, tpl, eos, mdir = _load_for_inference(a)
-    _note_kv_flags(a)
     tools = None
     if a.tools:
         with open(a.tools, "r", encoding="utf-8") as fh:
@@ -638,7 +662,8 @@ def cmd_infer(a) -> int:
         print(json.dumps(info) if a.json else text)
         return 0
     graphs = None if a.backend == "auto" and not a.compiled else (a.compiled or a.backend == "compiled")
-    gen = Generator(model, num_blocks=a.kv_blocks, cuda_graphs=graphs)
+    gen = Generator(model, cache=model.new_cache(a.kv_blocks, **_paged_cache_options(a, model, a.kv_blocks)),
+                    cuda_graphs=graphs)
     if a.benchmark:
         return _infer_benchmark(a, model, gen, sp_, eos)
     if a.stream and not a.json:
@@ -691,12 +716,11 @@ def cmd_serve(a) -> int:
         print("error: the paged attention kernels use 64-token blocks (--cb-block-size 64)", file=sys.stderr)
         return 2
     model, tok, tpl, eos, mdir = _load_for_inference(a)
-    _note_kv_flags(a)
     blocks = a.kv_blocks
     if a.max_seq_len:
         blocks = max(blocks, a.max_slots * (-(-a.max_seq_len // 64) + 1))
     serve(model, tok, tpl, a.host, a.port, eos, os.path.basename(os.path.normpath(mdir or a.model)), a.max_slots, blocks,
-          a.cb_max_queue_depth)
+          a.cb_max_queue_depth, cache_options=_paged_cache_options(a, model, blocks))
     return 0
 
 

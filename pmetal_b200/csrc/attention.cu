@@ -653,8 +653,57 @@ struct PagedParams {
   int max_blocks, hq, hkv, n_split, total_q, q_tiles;
   float scale;
   int window;
+  int sink;                      // with a window: the first `sink` keys stay visible (attention-sink cache)
+  // int8 cache (kQ8): k_cache / v_cache hold int8 [num_blocks, 64, hkv, 128] and these hold one fp32 scale per group
+  // of 64 channels, [num_blocks, 64, hkv, 2]
+  const float* k_scale;
+  const float* v_scale;
 };
 
+// One thread's share of a [64][128] int8 key or value block in flight: four 16-byte pieces and their scales.
+struct Q8Regs {
+  uint4 d[4];
+  float s[4];
+};
+__device__ __forceinline__ void q8_fetch(Q8Regs& r, const int8_t* base, const float* sbase, long long row_stride,
+                                         long long srow_stride) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = threadIdx.x + i * kAttnThreads;   // 0..511
+    const int row = idx >> 3, c = idx & 7;            // 16 channels [16c, 16c+16)
+    r.d[i] = __ldg(reinterpret_cast<const uint4*>(base + row * row_stride + c * 16));
+    r.s[i] = __ldg(sbase + row * srow_stride + (c >> 2));
+  }
+}
+// expand to bf16 and store into the swizzled [64][128] tile that the MMA fragments read
+__device__ __forceinline__ void q8_store(const Q8Regs& r, uint8_t* smem_tile) {
+  const uint32_t sbase = smem_addr(smem_tile);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = threadIdx.x + i * kAttnThreads;
+    const int row = idx >> 3, c = idx & 7;
+    const uint32_t w[4] = {r.d[i].x, r.d[i].y, r.d[i].z, r.d[i].w};
+    uint32_t o[8];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float f0 = static_cast<float>(static_cast<int8_t>(w[q] & 0xff)) * r.s[i];
+      const float f1 = static_cast<float>(static_cast<int8_t>((w[q] >> 8) & 0xff)) * r.s[i];
+      const float f2 = static_cast<float>(static_cast<int8_t>((w[q] >> 16) & 0xff)) * r.s[i];
+      const float f3 = static_cast<float>(static_cast<int8_t>(w[q] >> 24)) * r.s[i];
+      o[2 * q] = pack2(f0, f1);
+      o[2 * q + 1] = pack2(f2, f3);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t dst = sbase + row * 256 + (((2 * c + h) ^ (row & 7)) << 4);
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(o[4 * h]), "r"(o[4 * h + 1]),
+                   "r"(o[4 * h + 2]), "r"(o[4 * h + 3])
+                   : "memory");
+    }
+  }
+}
+
+template <bool kQ8>
 __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedParams p) {
   pdl_launch_dependents();
   pdl_wait();
@@ -699,9 +748,35 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
   auto kv_base = [&](const __nv_bfloat16* cache, int blk) {
     return cache + (static_cast<long long>(bt[blk]) * kTile * p.hkv + hk) * kD;
   };
-  if (b0 < b1) {
-    load_tile(sK, kv_base(p.k_cache, b0), row_stride, 0, kTile);
-    load_tile(sV, kv_base(p.v_cache, b0), row_stride, 0, kTile);
+  // with a sliding window, key blocks that no row of this tile can see are skipped (their table entries may be stale:
+  // the cache manager recycles such blocks): a block is dead when it ends before the window of the tile's first row
+  // and starts after the sink
+  const int lim_first = kv_len - q_len + row_base / rep;
+  auto dead = [&](int blk) {
+    return p.window > 0 && blk * kTile + kTile - 1 < lim_first - p.window + 1 && blk * kTile >= p.sink;
+  };
+  auto next_live = [&](int blk) {
+    while (blk < b1 && dead(blk)) ++blk;
+    return blk;
+  };
+  Q8Regs rk, rv;
+  auto fetch_q8 = [&](int blk) {
+    const long long off = (static_cast<long long>(bt[blk]) * kTile * p.hkv + hk);
+    q8_fetch(rk, reinterpret_cast<const int8_t*>(p.k_cache) + off * kD, p.k_scale + off * 2, row_stride,
+             static_cast<long long>(p.hkv) * 2);
+    q8_fetch(rv, reinterpret_cast<const int8_t*>(p.v_cache) + off * kD, p.v_scale + off * 2, row_stride,
+             static_cast<long long>(p.hkv) * 2);
+  };
+  int b_cur = next_live(b0);
+  if (b_cur < b1) {
+    if (kQ8) {
+      fetch_q8(b_cur);
+      q8_store(rk, sK);
+      q8_store(rv, sV);
+    } else {
+      load_tile(sK, kv_base(p.k_cache, b_cur), row_stride, 0, kTile);
+      load_tile(sV, kv_base(p.v_cache, b_cur), row_stride, 0, kTile);
+    }
   }
   cp_async_commit();
 
@@ -718,11 +793,16 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
   // visible-key limit (inclusive) for the two rows this thread owns
   const int lim_lo = kv_len - q_len + ((row_base + r_lo) / rep), lim_hi = kv_len - q_len + ((row_base + r_lo + 8) / rep);
 
-  for (int b = b0; b < b1; ++b) {
-    const int buf = (b - b0) & 1;
-    if (b + 1 < b1) {
-      load_tile(sK + (buf ^ 1) * kTileBytes, kv_base(p.k_cache, b + 1), row_stride, 0, kTile);
-      load_tile(sV + (buf ^ 1) * kTileBytes, kv_base(p.v_cache, b + 1), row_stride, 0, kTile);
+  int it = 0;
+  for (int b = b_cur; b < b1; ++it) {
+    const int buf = it & 1;
+    const int b_next = next_live(b + 1);
+    if (kQ8) {
+      if (b_next < b1) fetch_q8(b_next);          // global loads stay in flight while this block is processed
+      cp_async_wait<0>();                         // the query tile (first iteration)
+    } else if (b_next < b1) {
+      load_tile(sK + (buf ^ 1) * kTileBytes, kv_base(p.k_cache, b_next), row_stride, 0, kTile);
+      load_tile(sV + (buf ^ 1) * kTileBytes, kv_base(p.v_cache, b_next), row_stride, 0, kTile);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -758,7 +838,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
           const int j = j0 + nt * 8 + 2 * t4 + (e & 1);
           const int lim = (e < 2) ? lim_lo : lim_hi;
           bool ok = j <= lim;
-          if (p.window > 0) ok = ok && (lim - j < p.window);
+          if (p.window > 0) ok = ok && (lim - j < p.window || j < p.sink);
           const float v = ok ? s[nt][e] * sl2 : -INFINITY;
           s[nt][e] = v;
           mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -806,7 +886,12 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
         }
       }
     }
+    if (kQ8 && b_next < b1) {     // the other buffer was last read one iteration ago (barrier at the end of it)
+      q8_store(rk, sK + (buf ^ 1) * kTileBytes);
+      q8_store(rv, sV + (buf ^ 1) * kTileBytes);
+    }
     __syncthreads();
+    b = b_next;
   }
   if (!warp_active) return;
 #pragma unroll
@@ -889,13 +974,18 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, long long 
 
 // Scratch (part_o / part_ml) is needed only when n_split > 1:
 //   part_o  : n_split * total_q * hq * 128 floats,  part_ml : n_split * total_q * hq * 2 floats
-extern "C" int pm_paged_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
-                             const int* seq_lens, const int* q_start, const int* q_lens, float* part_o, float* part_ml,
-                             int num_seqs, int max_blocks, int total_q, int max_q, int hq, int hkv, int n_split,
-                             float scale, int window, cudaStream_t st) {
+// k_scale / v_scale non-null: the caches hold int8 with one fp32 scale per (token, kv head, 64-channel group).
+// sink: with window > 0, the first `sink` keys of a sequence stay visible.
+extern "C" int pm_paged_attn_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                const int* block_table, const int* seq_lens, const int* q_start, const int* q_lens,
+                                float* part_o, float* part_ml, int num_seqs, int max_blocks, int total_q, int max_q,
+                                int hq, int hkv, int n_split, float scale, int window, int sink, const float* k_scale,
+                                const float* v_scale, cudaStream_t st) {
   if (hq % hkv || num_seqs <= 0) return -1;
   if (n_split < 1 || (n_split > 1 && (!part_o || !part_ml))) return -2;
+  if ((k_scale == nullptr) != (v_scale == nullptr)) return -4;
   PagedParams p{};
+  p.sink = sink; p.k_scale = k_scale; p.v_scale = v_scale;
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
   p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
@@ -909,17 +999,83 @@ extern "C" int pm_paged_attn(const void* q, const void* k_cache, const void* v_c
   const int smem = 5 * kTileBytes;
   static DeviceOnce once;
   if (once.pending()) {
-    int e = set_smem(reinterpret_cast<const void*>(paged_attn_kernel), smem);
+    int e = set_smem(reinterpret_cast<const void*>(paged_attn_kernel<false>), smem);
+    if (e) return e;
+    e = set_smem(reinterpret_cast<const void*>(paged_attn_kernel<true>), smem);
     if (e) return e;
     once.mark();
   }
   dim3 grid(num_seqs * p.q_tiles, hkv, n_split);
-  int e = static_cast<int>(launch_pdl(paged_attn_kernel, grid, dim3(kAttnThreads), static_cast<size_t>(smem), st, p));
+  int e = k_scale ? static_cast<int>(launch_pdl(paged_attn_kernel<true>, grid, dim3(kAttnThreads),
+                                                static_cast<size_t>(smem), st, p))
+                  : static_cast<int>(launch_pdl(paged_attn_kernel<false>, grid, dim3(kAttnThreads),
+                                                static_cast<size_t>(smem), st, p));
   if (e || n_split == 1) return e;
   const int rows = total_q * hq;
   return static_cast<int>(launch_pdl(paged_attn_combine_kernel, dim3((rows + 7) / 8), dim3(256), 0, st,
                                      static_cast<const float*>(part_o), static_cast<const float*>(part_ml),
                                      static_cast<__nv_bfloat16*>(out), rows, n_split));
+}
+
+extern "C" int pm_paged_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                             const int* seq_lens, const int* q_start, const int* q_lens, float* part_o, float* part_ml,
+                             int num_seqs, int max_blocks, int total_q, int max_q, int hq, int hkv, int n_split,
+                             float scale, int window, cudaStream_t st) {
+  return pm_paged_attn_ex(q, k_cache, v_cache, out, block_table, seq_lens, q_start, q_lens, part_o, part_ml, num_seqs,
+                          max_blocks, total_q, max_q, hq, hkv, n_split, scale, window, 0, nullptr, nullptr, st);
+}
+
+// int8 cache append: one warp per (token, kv head) row of 128 channels; each half (64 channels) gets its own scale
+// absmax / 127 (symmetric), stored next to the codes.
+__global__ void kv_append_q8_kernel(const __nv_bfloat16* __restrict__ k, long long k_stride,
+                                    const __nv_bfloat16* __restrict__ v, long long v_stride, int8_t* __restrict__ k_cache,
+                                    int8_t* __restrict__ v_cache, float* __restrict__ k_scale,
+                                    float* __restrict__ v_scale, const long long* __restrict__ slots, int n_tokens,
+                                    int hkv) {
+  const int lane = threadIdx.x & 31;
+  const long long rows = static_cast<long long>(n_tokens) * hkv * 2;      // K rows then V rows per (token, head)
+  for (long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; w < rows;
+       w += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    const int is_v = static_cast<int>(w & 1);
+    const long long th = w >> 1;
+    const int t = static_cast<int>(th / hkv), h = static_cast<int>(th - static_cast<long long>(t) * hkv);
+    const long long slot = slots[t];
+    if (slot < 0) continue;
+    const __nv_bfloat16* src = (is_v ? v + t * v_stride : k + t * k_stride) + h * pm::kD + lane * 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    float f[4];
+    f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);
+    f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xffff0000u);
+    float mx = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));   // within each half-warp
+    const float sc = mx > 0.f ? mx / 127.f : 1.f;
+    const float inv = 1.f / sc;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      int q = __float2int_rn(f[e] * inv);
+      q = max(-127, min(127, q));
+      packed |= (static_cast<uint32_t>(q) & 0xffu) << (8 * e);
+    }
+    const long long row = slot * hkv + h;
+    *reinterpret_cast<uint32_t*>((is_v ? v_cache : k_cache) + row * pm::kD + lane * 4) = packed;
+    if ((lane & 15) == 0) (is_v ? v_scale : k_scale)[row * 2 + (lane >> 4)] = sc;
+  }
+}
+
+extern "C" int pm_kv_append_q8(const void* k, long long k_stride, const void* v, long long v_stride, void* k_cache,
+                               void* v_cache, float* k_scale, float* v_scale, const long long* slots, int n_tokens,
+                               int hkv, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  const long long warps = static_cast<long long>(n_tokens) * hkv * 2;
+  int grid = static_cast<int>((warps + 7) / 8);
+  if (grid > num_sms() * 8) grid = num_sms() * 8;
+  kv_append_q8_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k), k_stride,
+                                            static_cast<const __nv_bfloat16*>(v), v_stride,
+                                            static_cast<int8_t*>(k_cache), static_cast<int8_t*>(v_cache), k_scale,
+                                            v_scale, slots, n_tokens, hkv);
+  return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int pm_kv_append(const void* k, long long k_stride, const void* v, long long v_stride, void* k_cache,

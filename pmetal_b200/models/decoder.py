@@ -366,7 +366,9 @@ class DecoderLM(nn.Module):
         T = x.shape[0]
         skinny = native and T <= GEMV_MAX_ROWS
         layers = self.layers
-        if skinny and DECODE_MEGA and meta.max_q == 1 and T == meta.block_table.shape[0] and self._mega_ok(T):
+        plain_cache = cache.quant is None and cache.window == 0      # bf16 blocks, nothing recycled
+        if (skinny and DECODE_MEGA and plain_cache and meta.max_q == 1 and T == meta.block_table.shape[0]
+                and self._mega_ok(T)):
             # every layer of the step in one cooperative launch (csrc/decode_mega.cu)
             from ..ops import native as nat
             table = self._mega_table(cache)
@@ -386,9 +388,13 @@ class DecoderLM(nn.Module):
                 from ..ops import native as nat
                 eps = cfg.rms_norm_eps
                 qkv = at.qkv_proj.gemv_forward(x, layer.input_layernorm, eps)
-                q = nat.qknorm_rope_cache(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps, cache.k[li],
-                                          cache.v[li], meta.slots)
-                o = nat.paged_attn(q, cache.k[li], cache.v[li], meta, d ** -0.5, at.window).view(T, hq * d)
+                if cache.quant is None:
+                    q = nat.qknorm_rope_cache(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps, cache.k[li],
+                                              cache.v[li], meta.slots)
+                else:
+                    q, k = nat.qknorm_rope_fwd(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps)
+                    cache.append(li, k, qkv[:, (hq + hkv) * d:].view(T, hkv, d), meta.slots)
+                o = cache.attention(li, q, meta, d ** -0.5, at.window).view(T, hq * d)
                 h = at.o_proj.gemv_forward(o, residual=x)
                 if isinstance(layer.mlp, MLP) and layer.mlp.gate_up_proj.gemv_ok(T):
                     act = layer.mlp.gate_up_proj.gemv_forward(h, layer.post_attention_layernorm, eps, swiglu=True)
@@ -402,8 +408,8 @@ class DecoderLM(nn.Module):
                 from ..ops import native as nat
                 q, k = nat.qknorm_rope_fwd(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, cfg.rms_norm_eps)
                 v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
-                nat.kv_append(k, v, cache.k[li], cache.v[li], meta.slots)
-                o = nat.paged_attn(q, cache.k[li], cache.v[li], meta, d ** -0.5, at.window).view(T, hq * d)
+                cache.append(li, k, v, meta.slots)
+                o = cache.attention(li, q, meta, d ** -0.5, at.window).view(T, hq * d)
             else:
                 o = self._paged_attention_reference(qkv, at, rope, cache, meta, li)
             h = at.o_proj(o, x)
@@ -482,9 +488,9 @@ class DecoderLM(nn.Module):
         if at.q_norm is not None:
             q, k = ref.rms_norm(q, at.q_norm, cfg.rms_norm_eps), ref.rms_norm(k, at.k_norm, cfg.rms_norm_eps)
         q, k = ref.apply_rope(q, rope[0], rope[1]), ref.apply_rope(k, rope[0], rope[1])
-        kc, vc = cache.k[li].view(-1, hkv, d), cache.v[li].view(-1, hkv, d)
-        kc[meta.slots] = k.to(kc.dtype)
-        vc[meta.slots] = v.to(vc.dtype)
+        cache.write_reference(li, k, v, meta.slots)
+        win = min(w for w in (at.window, cache.window) if w > 0) if (at.window > 0 or cache.window > 0) else 0
+        sink = cache.sink if cache.window > 0 else 0
         out = torch.empty(T, hq, d, dtype=qkv.dtype, device=qkv.device)
         qs, ql = meta.q_start.tolist(), meta.q_lens.tolist()
         rep = hq // hkv
@@ -498,17 +504,17 @@ class DecoderLM(nn.Module):
             qpos = torch.arange(L - n, L, device=qkv.device)[:, None]
             kpos = torch.arange(L, device=qkv.device)[None, :]
             mask = kpos <= qpos
-            if at.window > 0:
-                mask &= kpos > qpos - at.window
+            if win > 0:
+                mask &= (kpos > qpos - win) | (kpos < sink)
             sc = sc.masked_fill(~mask, float("-inf"))
             out[qs[i]:qs[i] + n] = torch.matmul(sc.softmax(-1), vv).transpose(0, 1).to(out.dtype)
         return out.view(T, hq * d)
 
-    def new_cache(self, num_blocks: int, dtype=None, device=None):
+    def new_cache(self, num_blocks: int, dtype=None, device=None, quant=None, window: int = 0, sink: int = 0):
         from .kv_cache import PagedKVCache
         p = self.embed_tokens
         return PagedKVCache(self.cfg.num_hidden_layers, self.cfg.num_key_value_heads, self.cfg.head_dim, num_blocks,
-                            dtype or p.dtype, device or p.device)
+                            dtype or p.dtype, device or p.device, quant=quant, window=window, sink=sink)
 
     # ------------------------------------------------------------------ checkpoint name mapping
     def hf_state_dict(self, merged: bool = False) -> Dict[str, torch.Tensor]:

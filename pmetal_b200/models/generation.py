@@ -125,7 +125,7 @@ class GraphedDecoder:
         rows = st["rows"]
         for i in range(nb):
             bl = tables[i] if i < n else None
-            sig = None if bl is None else (bl[0], len(bl), bl[-1])
+            sig = None if bl is None else (bl[0], len(bl), bl[-1], sum(1 for b in bl if b < 0) if self.cache.window > 0 else 0)
             if rows[i] == sig:
                 continue
             rows[i] = sig
@@ -134,6 +134,9 @@ class GraphedDecoder:
             else:
                 tab[i, :len(bl)] = bl
                 tab[i, len(bl):] = self.pad_block
+                if self.cache.window > 0:          # blocks given back by the rotating window are never visited
+                    row = tab[i, :len(bl)]
+                    row[row < 0] = self.pad_block
 
     def _copy(self, st):
         st["d64"].copy_(st["h64"], non_blocking=True)
@@ -147,6 +150,8 @@ class GraphedDecoder:
         for sid in seq_ids:
             start = cache.seqs[sid].length
             slots.extend(cache.reserve(sid, 1))
+            if cache.window > 0:
+                cache._evict_outside_window(sid, start)
             pos.append(start)
             lens.append(start + 1)
             tables.append(cache.seqs[sid].blocks)

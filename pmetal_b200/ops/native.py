@@ -468,8 +468,19 @@ def kv_append(k, v, k_cache, v_cache, slots) -> None:
                             c_int(n), c_int(hkv), _stream()), "pm_kv_append")
 
 
-def paged_attn(q, k_cache, v_cache, meta, scale: float, window: int = 0, n_split: int = 0):
-    """q: [total_q, hq, 128]; ``meta`` is a ``BatchMeta``. Long single sequences are split over key blocks."""
+def kv_append_q8(k, v, k_cache, v_cache, k_scale, v_scale, slots) -> None:
+    """bf16 k, v [n, hkv, 128] -> int8 cache [num_blocks, 64, hkv, 128] with fp32 scales [num_blocks, 64, hkv, 2]."""
+    n, hkv, d = k.shape
+    assert d == 128 and k.dtype == torch.bfloat16 and k.stride(2) == 1 and v.stride(2) == 1 and k.stride(1) == d
+    lib().pm_kv_append_q8.restype = c_int
+    _chk(lib().pm_kv_append_q8(_p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)), _p(k_cache), _p(v_cache), _p(k_scale),
+                               _p(v_scale), _p(slots), c_int(n), c_int(hkv), _stream()), "pm_kv_append_q8")
+
+
+def paged_attn(q, k_cache, v_cache, meta, scale: float, window: int = 0, n_split: int = 0, sink: int = 0,
+               k_scale=None, v_scale=None):
+    """q: [total_q, hq, 128]; ``meta`` is a ``BatchMeta``. Long single sequences are split over key blocks.
+    With ``k_scale`` / ``v_scale`` the caches are int8; ``sink`` keys stay visible in front of a sliding window."""
     total_q, hq, _ = q.shape
     hkv = k_cache.shape[2]
     n_seq = meta.block_table.shape[0]
@@ -482,10 +493,12 @@ def paged_attn(q, k_cache, v_cache, meta, scale: float, window: int = 0, n_split
     if n_split > 1:
         po = torch.empty(n_split, total_q, hq, 128, dtype=torch.float32, device=q.device)
         pml = torch.empty(n_split, total_q, hq, 2, dtype=torch.float32, device=q.device)
-    _chk(lib().pm_paged_attn(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(meta.block_table), _p(meta.seq_lens),
-                             _p(meta.q_start), _p(meta.q_lens), _p(po), _p(pml), c_int(n_seq),
-                             c_int(meta.block_table.shape[1]), c_int(total_q), c_int(meta.max_q), c_int(hq), c_int(hkv), c_int(n_split),
-                             c_float(scale), c_int(window), _stream()), "pm_paged_attn")
+    lib().pm_paged_attn_ex.restype = c_int
+    _chk(lib().pm_paged_attn_ex(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(meta.block_table), _p(meta.seq_lens),
+                                _p(meta.q_start), _p(meta.q_lens), _p(po), _p(pml), c_int(n_seq),
+                                c_int(meta.block_table.shape[1]), c_int(total_q), c_int(meta.max_q), c_int(hq),
+                                c_int(hkv), c_int(n_split), c_float(scale), c_int(window), c_int(sink), _p(k_scale),
+                                _p(v_scale), _stream()), "pm_paged_attn")
     return out
 
 

@@ -100,9 +100,13 @@ class EngineStats:
 
 class ContinuousBatchEngine:
     def __init__(self, model, eos_ids: Sequence[int] = (), max_slots: int = 64, num_blocks: int = 8192,
-                 prefill_chunk: int = PREFILL_CHUNK, prefix_cache: bool = True, max_queue: int = 1024):
+                 prefill_chunk: int = PREFILL_CHUNK, prefix_cache: bool = True, max_queue: int = 1024,
+                 cache_options: Optional[dict] = None):
         self.model = model
-        self.gen = Generator(model, num_blocks=num_blocks)
+        opts = dict(cache_options or {})
+        self.gen = Generator(model, cache=model.new_cache(num_blocks, **opts)) if opts else Generator(model, num_blocks=num_blocks)
+        if opts.get("window"):
+            prefix_cache = False      # a rotating cache recycles prompt blocks: there is no stable prefix to share
         self.cache = self.gen.cache
         self.device = self.gen.device
         self.eos = set(eos_ids)

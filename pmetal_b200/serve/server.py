@@ -345,10 +345,12 @@ def create_app(state: ServerState):
 
 
 def serve(model, tokenizer, template=None, host: str = "127.0.0.1", port: int = 8080, eos_ids=(), model_name="pmetal-b200",
-          max_slots: int = 64, num_blocks: int = 8192, max_queue: int = 1024):
-    """Blocking: starts the engine thread and the HTTP server."""
+          max_slots: int = 64, num_blocks: int = 8192, max_queue: int = 1024, cache_options: Optional[dict] = None):
+    """Blocking: starts the engine thread and the HTTP server. ``cache_options`` (quant / window / sink) go to
+    ``DecoderLM.new_cache``."""
     import uvicorn
-    engine = ContinuousBatchEngine(model, eos_ids, max_slots=max_slots, num_blocks=num_blocks, max_queue=max_queue)
+    engine = ContinuousBatchEngine(model, eos_ids, max_slots=max_slots, num_blocks=num_blocks, max_queue=max_queue,
+                                   cache_options=cache_options)
     engine.start()
     try:
         uvicorn.run(create_app(ServerState(engine, tokenizer, template, model_name)), host=host, port=port, log_level="info")

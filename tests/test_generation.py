@@ -118,3 +118,59 @@ def test_layer_split_self_speculation():
     ref = Generator(tgt, num_blocks=16).generate(prompts, SamplingParams.greedy(10)).tokens
     out = SpeculativeDecoder(tgt, draft, SpeculativeConfig(num_draft_tokens=2), 16, 16).generate(prompts, 10)
     assert out == ref
+
+
+def test_cache_mode_rule_and_paged_cache_variants_on_cpu():
+    """The cache choice rule, and the int8 / rotating variants of the paged cache against the plain one (CPU path)."""
+    import torch
+    from pmetal_b200.models.config import ModelArgs
+    from pmetal_b200.models.decoder import DecoderLM
+    from pmetal_b200.models.generation import Generator
+    from pmetal_b200.models.kv_cache import select_cache_mode
+    from pmetal_b200.models.sampling import SamplingParams
+    GB = 1 << 30
+    assert select_cache_mode(10 * GB, 10 * GB, 180 * GB).source == "auto_fp16"
+    m = select_cache_mode(100 * GB, 40 * GB, 180 * GB)
+    assert (m.kind, m.bits, m.source) == ("quantized", 8, "auto_q8")
+    assert select_cache_mode(100 * GB, 40 * GB, 180 * GB, no_kv_quant=True).source == "forced_fp16"
+    assert select_cache_mode(100 * GB, 40 * GB, 180 * GB, kv_quant=0).kind == "standard"
+    m = select_cache_mode(1, 1, 180 * GB, kv_quant=4)
+    assert (m.kind, m.bits, m.source) == ("quantized", 4, "explicit")
+    m = select_cache_mode(1, 1, 180 * GB, k_bits=8, v_bits=4)
+    assert (m.kind, m.k_bits, m.v_bits) == ("asymmetric", 8, 4)
+    m = select_cache_mode(1, 1, 180 * GB, k_bits=4)
+    assert (m.kind, m.k_bits, m.v_bits) == ("asymmetric", 4, 8)
+    assert select_cache_mode(1, 1, None, turboquant=True, kv_quant=3).kind == "turboquant"
+
+    cfg = ModelArgs(vocab_size=300, hidden_size=128, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
+                    num_key_value_heads=1, head_dim=64)
+    model = DecoderLM(cfg).init_weights(0.08, 0).eval()
+    for p in model.parameters():
+        p.requires_grad_(False)
+    prompt = list(range(3, 150))
+    plain = Generator(model, cache=model.new_cache(32)).generate([prompt], SamplingParams.greedy(20))
+    q8 = Generator(model, cache=model.new_cache(32, quant="int8"))
+    lg_a = Generator(model, cache=model.new_cache(32)).prefill([0], [prompt]) if False else None
+    out8 = q8.generate([prompt], SamplingParams.greedy(20))
+    same = sum(a == b for a, b in zip(plain.tokens[0], out8.tokens[0]))
+    assert same >= 15, (plain.tokens[0], out8.tokens[0])          # int8 keys and values barely move the logits
+    # logits with the int8 cache stay close to the 16-bit ones
+    g1, g2 = Generator(model, cache=model.new_cache(32)), Generator(model, cache=model.new_cache(32, quant="int8"))
+    s1, s2 = g1.new_seq(), g2.new_seq()
+    l1, l2 = g1.prefill([s1], [prompt]), g2.prefill([s2], [prompt])
+    assert (l1 - l2).abs().max() < 0.05 * l1.abs().max()
+    # rotating cache: a window as long as the whole text changes nothing, and blocks behind the window are recycled
+    win = Generator(model, cache=model.new_cache(32, window=4096, sink=4)).generate([prompt], SamplingParams.greedy(20))
+    assert win.tokens[0] == plain.tokens[0]
+    small = model.new_cache(32, window=64, sink=8)
+    gs = Generator(model, cache=small)
+    sid = gs.new_seq()
+    gs.prefill([sid], [prompt])
+    for _ in range(70):
+        gs.decode_step([sid], torch.tensor([5]))
+    assert small.length(sid) == len(prompt) + 70
+    assert small.live_blocks(sid) <= 3 and small.seqs[sid].blocks[0] >= 0        # sink block + the window's blocks
+    assert small.num_free() >= 32 - 3
+    # the windowed result equals dense attention restricted to sink + window (the CPU path applies the same mask)
+    small.free_sequence(sid)
+    assert small.num_free() == 32

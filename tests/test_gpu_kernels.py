@@ -343,6 +343,111 @@ def test_paged_attention_and_append(hq, hkv, lens, qlens):
             _close(o[qs[i]:qs[i] + n], ref, what=f"paged attn seq {i}")
 
 
+@pytest.mark.parametrize("hq,hkv,lens,qlens,window,sink", [(4, 2, [70, 1, 300], [1, 1, 1], 0, 0),
+                                                           (8, 2, [2000, 130], [1, 3], 0, 0),
+                                                           (4, 2, [900, 333], [1, 2], 256, 16),
+                                                           (2, 2, [5000], [1], 512, 64)])
+def test_paged_attention_int8_cache_and_sink_window(hq, hkv, lens, qlens, window, sink):
+    """int8 blocks (quantised by the append kernel, expanded by the attention kernel) against the same attention over
+    the de-quantised values, and the sink + window mask with recycled blocks against dense masked attention."""
+    nat = _nat()
+    from pmetal_b200.models.kv_cache import PagedKVCache
+    torch.manual_seed(13)
+    d = 128
+    cache = PagedKVCache(1, hkv, d, 256, torch.bfloat16, "cuda", quant="int8", window=window, sink=sink)
+    ks, vs = [], []
+    for i, (L, n) in enumerate(zip(lens, qlens)):
+        cache.add_sequence(i)
+        k, v = _rand(L, hkv, d), _rand(L, hkv, d)
+        ks.append(k); vs.append(v)
+        if L - n > 0:
+            slots = torch.tensor(cache.reserve(i, L - n), device="cuda")
+            cache.append(0, k[:L - n], v[:L - n], slots)
+    meta = cache.prepare(list(range(len(lens))), qlens)      # recycles the blocks behind the window
+    knew = torch.cat([k[L - n:] for k, L, n in zip(ks, lens, qlens)])
+    vnew = torch.cat([v[L - n:] for v, L, n in zip(vs, lens, qlens)])
+    cache.append(0, knew, vnew, meta.slots)
+    # the append kernel's codes and scales equal the PyTorch quantiser's
+    qk, sk = cache.quantize_rows(knew)
+    flat = cache.k[0].view(-1, hkv, d)[meta.slots]
+    assert (flat.int() - qk.int()).abs().max() <= 1
+    assert torch.allclose(cache.k_scale[0].view(-1, hkv, 2)[meta.slots], sk, rtol=1e-6)
+    if window:
+        assert cache.live_blocks(0) < -(-lens[0] // 64)            # blocks behind the window went back to the pool
+        assert cache.live_blocks(0) <= -(-window // 64) + 2 + -(-sink // 64)
+    q = _rand(meta.total_q, hq, d)
+    scale = d ** -0.5
+    outs = [cache.attention(0, q, meta, scale)] + [nat.paged_attn(q, cache.k[0], cache.v[0], meta, scale, window, n_split=3,
+                                                                  sink=sink, k_scale=cache.k_scale[0],
+                                                                  v_scale=cache.v_scale[0])]
+    rep = hq // hkv
+    qs = meta.q_start.tolist()
+    for i, (L, n) in enumerate(zip(lens, qlens)):
+        qq = q[qs[i]:qs[i] + n].float().transpose(0, 1)
+
+        def dq(x):
+            c, sc = cache.quantize_rows(x)
+            return (c.float().reshape(L, hkv, 2, 64) * sc[..., None]).reshape(L, hkv, d)
+        kk = dq(ks[i]).transpose(0, 1).repeat_interleave(rep, 0)
+        vv = dq(vs[i]).transpose(0, 1).repeat_interleave(rep, 0)
+        sc = qq @ kk.transpose(1, 2) * scale
+        qpos = torch.arange(L - n, L, device="cuda")[:, None]
+        kpos = torch.arange(L, device="cuda")[None, :]
+        mask = kpos <= qpos
+        if window:
+            mask &= (kpos > qpos - window) | (kpos < sink)
+        sc = sc.masked_fill(~mask, float("-inf"))
+        ref = (sc.softmax(-1) @ vv).transpose(0, 1)
+        for o in outs:
+            _close(o[qs[i]:qs[i] + n], ref, what=f"int8 paged attn seq {i}")
+        # and the quantisation error itself is small against the unquantised attention
+        kk0 = ks[i].float().transpose(0, 1).repeat_interleave(rep, 0)
+        vv0 = vs[i].float().transpose(0, 1).repeat_interleave(rep, 0)
+        sc0 = (qq @ kk0.transpose(1, 2) * scale).masked_fill(~mask, float("-inf"))
+        _close(outs[0][qs[i]:qs[i] + n], (sc0.softmax(-1) @ vv0).transpose(0, 1), rtol=5e-2, atol=5e-2,
+               what=f"int8 vs bf16 attention seq {i}")
+    nat.check_status()
+
+
+def test_generation_with_int8_and_rotating_cache_on_gpu():
+    _nat()
+    from pmetal_b200.models.config import ModelArgs
+    from pmetal_b200.models.decoder import DecoderLM
+    from pmetal_b200.models.generation import Generator
+    from pmetal_b200.models.sampling import SamplingParams
+    cfg = ModelArgs(vocab_size=2048, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                    num_attention_heads=4, num_key_value_heads=2, head_dim=128)
+    m = DecoderLM(cfg).init_weights(0.05, 0).to("cuda").to(torch.bfloat16).eval()
+    for p in m.parameters():
+        p.requires_grad_(False)
+    prompt = torch.randint(0, 2048, (300,), generator=torch.Generator().manual_seed(3)).tolist()
+    plain = Generator(m, num_blocks=64).generate([prompt], SamplingParams.greedy(24)).tokens[0]
+    # logits of a prefill and of decode steps over the int8 cache stay close to the 16-bit ones (token-for-token
+    # equality is too strict for a random model whose logits are nearly flat)
+    ga, gb = Generator(m, num_blocks=64), Generator(m, cache=m.new_cache(64, quant="int8"))
+    sa, sb = ga.new_seq(), gb.new_seq()
+    la, lb = ga.prefill([sa], [prompt]).float(), gb.prefill([sb], [prompt]).float()
+    assert (la - lb).abs().max() < 0.05 * la.abs().max(), ((la - lb).abs().max(), la.abs().max())
+    for t in plain[:6]:
+        tok = torch.tensor([t], device="cuda")
+        la, lb = ga.decode_step([sa], tok).float(), gb.decode_step([sb], tok).float()
+        assert (la - lb).abs().max() < 0.05 * la.abs().max(), ((la - lb).abs().max(), la.abs().max())
+    # a window wider than the text must not change the result (other kernels run: compare logits, not tokens)
+    gc = Generator(m, cache=m.new_cache(64, window=4096, sink=4))
+    sc = gc.new_seq()
+    la, lc = Generator(m, num_blocks=64), None
+    sa2 = la.new_seq()
+    l0, l1 = la.prefill([sa2], [prompt]).float(), gc.prefill([sc], [prompt]).float()
+    assert (l0 - l1).abs().max() < 0.03 * l0.abs().max()
+    tok = torch.tensor([plain[0]], device="cuda")
+    l0, l1 = la.decode_step([sa2], tok).float(), gc.decode_step([sc], tok).float()
+    assert (l0 - l1).abs().max() < 0.03 * l0.abs().max()
+    rot = m.new_cache(64, quant="int8", window=128, sink=64)
+    g = Generator(m, cache=rot)
+    out = g.generate([prompt], SamplingParams.greedy(24))
+    assert len(out.tokens[0]) == 24
+
+
 def test_generation_native_matches_reference_path():
     _nat()
     from pmetal_b200.models.config import ModelArgs
