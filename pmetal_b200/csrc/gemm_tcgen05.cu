@@ -16,18 +16,6 @@
 
 namespace pm {
 
-// Issue the TMA copies that bring one operand tile (rows x 64 K) into shared memory.
-//   K-major : one box [rows][64 k], coordinates (k0, row0)
-//   MN-major: rows/64 boxes [64 k][64 mn], coordinates (mn0 + 64 j, k0), 8 KB apart
-__device__ __forceinline__ void load_operand(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int mn_major,
-                                             int rows, int row0, int k0) {
-  if (!mn_major) {
-    tma_load_2d(dst, map, bar, k0, row0);
-  } else {
-    for (int j = 0; j < rows / 64; ++j) tma_load_2d(dst + j * 8192, map, bar, row0 + 64 * j, k0);
-  }
-}
-
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,

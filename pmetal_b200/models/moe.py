@@ -66,15 +66,7 @@ class SparseMoeBlock(nn.Module):
 
     def experts_forward(self, x: torch.Tensor, w: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
         from ..ops import functional as ops
-        T, k = idx.shape
-        order, counts, offsets = sort_by_expert(idx, self.cfg.num_experts)
-        tok = order // k
-        xs = x[tok]                                           # [T·k, H] grouped by expert
-        ys = ops.grouped_mlp(xs, self.gate_up, self.down, offsets)
-        ys = ys * w.reshape(-1)[order].to(ys.dtype)[:, None]
-        out = torch.zeros_like(x)
-        out.index_add_(0, tok, ys)
-        return out
+        return ops.moe_experts(x, w, idx, self.gate_up, self.down)
 
     def hf_state_dict(self) -> Dict[str, torch.Tensor]:
         I = self.cfg.moe_intermediate_size

@@ -282,16 +282,100 @@ def causal_lm_loss(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Ten
 
 
 # --------------------------------------------------------------------------- grouped expert MLP
+GROUP_ALIGN = 128      # row alignment of every expert's slab in the padded sorted layout (one GEMM tile)
+
+
+def padded_expert_layout(idx: torch.Tensor, num_experts: int, align: int = GROUP_ALIGN):
+    """Where each (token, slot) assignment goes when rows are sorted by expert with every expert's slab padded to a
+    multiple of ``align`` rows. Returns (dest [T*k] int64: row of assignment i in the padded buffer, off int32 [E+1],
+    rows_cap: static capacity of the buffer). Everything stays on the device; ``rows_cap`` depends on shapes only."""
+    flat = idx.reshape(-1)
+    n = flat.numel()
+    counts = torch.bincount(flat, minlength=num_experts)
+    padded = (counts + (align - 1)) // align * align
+    off = torch.zeros(num_experts + 1, dtype=torch.int64, device=idx.device)
+    off[1:] = torch.cumsum(padded, 0)
+    start = torch.zeros(num_experts + 1, dtype=torch.int64, device=idx.device)
+    start[1:] = torch.cumsum(counts, 0)
+    order = torch.argsort(flat, stable=True)
+    rank = torch.empty_like(order)
+    rank[order] = torch.arange(n, device=idx.device) - start[flat[order]]
+    dest = off[flat] + rank
+    rows_cap = -(-(n + num_experts * (align - 1)) // align) * align
+    return dest, off.to(torch.int32), rows_cap
+
+
+class _GroupedLinearFn(torch.autograd.Function):
+    """y[r] = x[r] W_e(r)^T over rows grouped by expert in the padded layout; tcgen05 grouped GEMMs forward and backward."""
+
+    @staticmethod
+    def forward(ctx, x, w, off):
+        nat = _native()
+        E, N, K = w.shape
+        ctx.save_for_backward(x, w, off)
+        return nat.grouped_gemm(0, x, w, off, N, K)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, off = ctx.saved_tensors
+        nat = _native()
+        E, N, K = w.shape
+        dy = dy.contiguous()
+        dx = nat.grouped_gemm(1, dy, w, off, N, K) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = nat.grouped_gemm(2, dy, x, off, N, K).to(w.dtype)
+        return dx, dw, None
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, off: torch.Tensor) -> torch.Tensor:
+    """x [R, K] rows grouped by expert (padded layout, ``off`` int32 [E+1]); w [E, N, K]. Returns [R, N]."""
+    if use_native(x) and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.shape[2] % 8 == 0:
+        return _GroupedLinearFn.apply(x, w.contiguous() if not w.is_contiguous() else w, off)
+    out = torch.zeros(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
+    o = off.tolist()
+    for e in range(w.shape[0]):
+        if o[e + 1] > o[e]:
+            out[o[e]:o[e + 1]] = F.linear(x[o[e]:o[e + 1]], w[e])
+    return out
+
+
 def grouped_mlp(xs: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
-    """Rows of ``xs`` are grouped by expert (``offsets`` [E+1]); returns down_e(swiglu(gate_up_e(x))) per row."""
-    # Library path (training and the oracle). Inference goes through parallel.ep.FusedExpertMoE, whose grouped tcgen05
-    # GEMMs also do the routing sort, SwiGLU and the weighted combine.
+    """Rows of ``xs`` are grouped by expert (``offsets`` [E+1], unpadded); returns down_e(swiglu(gate_up_e(x))) per row.
+    Plain per-expert loop: the oracle of the grouped kernels and the CPU path."""
     out = torch.empty(xs.shape[0], down.shape[1], dtype=xs.dtype, device=xs.device)
     off = offsets.tolist()
     for e in range(gate_up.shape[0]):
         s, t = off[e], off[e + 1]
         if t > s:
             out[s:t] = F.linear(ref.swiglu(F.linear(xs[s:t], gate_up[e])), down[e])
+    return out
+
+
+def moe_experts(x: torch.Tensor, w: torch.Tensor, idx: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
+    """Mixture-of-experts feed-forward for routed tokens: x [T, H], routing weights w [T, k] and expert ids idx [T, k].
+    On the native path tokens are scattered into the padded expert-sorted layout and both projections (and their
+    gradients) run as grouped tcgen05 GEMMs with no host synchronisation; elsewhere a per-expert loop."""
+    T, k = idx.shape
+    E = gate_up.shape[0]
+    if use_native(x) and gate_up.dtype == torch.bfloat16:
+        dest, off, cap = padded_expert_layout(idx, E)
+        tok = torch.arange(T, device=x.device).repeat_interleave(k)
+        xs = torch.zeros(cap, x.shape[1], dtype=x.dtype, device=x.device).index_copy(0, dest, x[tok])
+        act = swiglu(grouped_linear(xs, gate_up, off))
+        ys = grouped_linear(act, down, off)[dest]
+        ys = ys * w.reshape(-1).to(ys.dtype)[:, None]
+        return torch.zeros_like(x).index_add(0, tok, ys)
+    flat = idx.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=E)
+    offsets = torch.zeros(E + 1, dtype=torch.int64, device=idx.device)
+    offsets[1:] = torch.cumsum(counts, 0)
+    tok = order // k
+    ys = grouped_mlp(x[tok], gate_up, down, offsets)
+    ys = ys * w.reshape(-1)[order].to(ys.dtype)[:, None]
+    out = torch.zeros_like(x)
+    out.index_add_(0, tok, ys)
     return out
 
 

@@ -279,6 +279,36 @@ def lora_db(dy, t, seg_sizes, r: int, out: torch.Tensor) -> None:
              seg_r=r)
 
 
+# ------------------------------------------------------------------------------------------- grouped (expert) GEMM
+def grouped_gemm(mode: int, a: torch.Tensor, b: torch.Tensor, off: torch.Tensor, n: int, k: int,
+                 out: Optional[torch.Tensor] = None, accumulate: bool = False, alpha: float = 1.0) -> torch.Tensor:
+    """Grouped GEMM over expert-sorted rows in the padded layout (``off`` int32 [E+1], multiples of 128; csrc/grouped_gemm.cu).
+
+    mode 0: a = X [R, K], b = W [E, N, K]      -> Y  [R, N] bf16
+    mode 1: a = dY [R, N], b = W [E, N, K]     -> dX [R, K] bf16
+    mode 2: a = dY [R, N], b = X [R, K]        -> dW [E, N, K] fp32 (experts without rows keep ``out``'s contents)"""
+    E = off.numel() - 1
+    R = a.shape[0]
+    assert R % 128 == 0 and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and off.dtype == torch.int32
+    assert a.stride(1) == 1 and b.stride(-1) == 1
+    if mode == 0:
+        out = out if out is not None else torch.empty(R, n, dtype=torch.bfloat16, device=a.device)
+        ldb = b.stride(1)
+    elif mode == 1:
+        out = out if out is not None else torch.empty(R, k, dtype=torch.bfloat16, device=a.device)
+        ldb = b.stride(1)
+    else:
+        if out is None:
+            out = torch.zeros(E, n, k, dtype=torch.float32, device=a.device)
+        ldb = b.stride(0)
+    lib().pm_grouped_gemm.restype = c_int
+    rc = lib().pm_grouped_gemm(c_int(mode), _p(a), c_int(a.stride(0)), _p(b), c_int(ldb), _p(out), c_int(out.stride(-2)),
+                               _p(off), c_int(E), c_int(R), c_int(n), c_int(k), c_float(alpha), c_int(int(accumulate)),
+                               _p(status_word(a.device)), _stream())
+    _chk(rc, "pm_grouped_gemm")
+    return out
+
+
 # ------------------------------------------------------------------------------------------- norms etc.
 def rmsnorm_fwd(x, w, eps: float, residual=None):
     T, H = x.shape

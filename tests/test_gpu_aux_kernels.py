@@ -16,6 +16,13 @@ def _nat():
     return native
 
 
+def _close(a, b, rtol=2e-2, atol=2e-2, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert err <= atol + rtol * ref, f"{what}: max err {err} vs ref max {ref}"
+
+
 def _f(dev, *vals, dtype=torch.float32):
     return torch.tensor(vals, dtype=dtype, device=dev)
 
@@ -397,3 +404,46 @@ def test_gated_delta_rule_scan_kernel(dk, dv, T):
     y0, _ = nat.gdn_scan(q, k, v, g, beta)                     # zero initial state
     yr0, _ = gdn_recurrent(q[0], k[0], v[0], g[0], beta[0])
     assert torch.allclose(y0[0], yr0, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("E,N,K,counts", [(4, 256, 128, [130, 0, 257, 64]), (8, 1536, 2048, [300, 5, 0, 129, 1000, 64, 128, 1]),
+                                          (3, 200, 136, [10, 20, 30])])
+def test_grouped_gemm_forward_dx_dw(E, N, K, counts):
+    """Expert-grouped GEMMs in the padded sorted layout against a per-expert fp32 loop: forward, input gradient,
+    weight gradient (an expert without rows keeps a zero gradient)."""
+    nat = _nat()
+    from pmetal_b200.ops import functional as F
+    torch.manual_seed(21)
+    idx = torch.cat([torch.full((c,), e, dtype=torch.int64) for e, c in enumerate(counts)])
+    idx = idx[torch.randperm(idx.numel())].cuda().reshape(-1, 1)
+    dest, off, cap = F.padded_expert_layout(idx, E)
+    o = off.tolist()
+    assert all(x % 128 == 0 for x in o) and o[-1] <= cap and [b - a >= c for a, b, c in zip(o, o[1:], counts)]
+    assert dest.unique().numel() == idx.numel()
+    n = idx.numel()
+    x = (torch.randn(n, K, device="cuda")).to(torch.bfloat16)
+    w = (torch.randn(E, N, K, device="cuda") * K ** -0.5).to(torch.bfloat16)
+    xs = torch.zeros(cap, K, dtype=torch.bfloat16, device="cuda").index_copy(0, dest, x)
+    y = nat.grouped_gemm(0, xs, w, off, N, K)
+    nat.check_status()
+    e_of = idx.reshape(-1)
+    ref_y = torch.einsum("rk,rnk->rn", x.float(), w.float()[e_of])
+    _close(y[dest], ref_y, what="grouped fwd")
+    pad = torch.ones(cap, dtype=torch.bool, device="cuda")
+    pad[dest] = False
+    assert float(y[pad].float().abs().max()) == 0.0                                # padding rows stay zero
+    dy = (torch.randn(n, N, device="cuda")).to(torch.bfloat16)
+    dys = torch.zeros(cap, N, dtype=torch.bfloat16, device="cuda").index_copy(0, dest, dy)
+    dx = nat.grouped_gemm(1, dys, w, off, N, K)
+    _close(dx[dest], torch.einsum("rn,rnk->rk", dy.float(), w.float()[e_of]), what="grouped dx")
+    dw = nat.grouped_gemm(2, dys, xs, off, N, K)
+    nat.check_status()
+    ref_dw = torch.zeros(E, N, K, device="cuda")
+    for e in range(E):
+        sel = e_of == e
+        if bool(sel.any()):
+            ref_dw[e] = dy[sel].float().t() @ x[sel].float()
+    _close(dw, ref_dw, rtol=2e-2, atol=2e-2 * max(1.0, float(ref_dw.abs().max())), what="grouped dw")
+    for e, c in enumerate(counts):
+        if c == 0:
+            assert float(dw[e].abs().max()) == 0.0
