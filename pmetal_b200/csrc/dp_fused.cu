@@ -114,7 +114,19 @@ __global__ void __launch_bounds__(256) dp_reduce_adamw_kernel(const DpArgs a) {
     st_release_sys(peer + kReadyOff + a.rank, epoch);
   }
   // ---- wait for every rank's gradients
-  if (!wait_all(my_pad, kReadyOff, a.world, epoch, a.timeout_ns, a.status, &s_fail)) return;
+  if (!wait_all(my_pad, kReadyOff, a.world, epoch, a.timeout_ns, a.status, &s_fail)) {
+    // abandoned step: still count this CTA in, and let the last one close the epoch, so that the pad is in a
+    // defined state for the next launch (flags of the failed epoch are then simply too old to match)
+    if (threadIdx.x == 0) {
+      const uint32_t prev = atomicAdd(my_pad + kArriveOff, 1u);
+      if (prev == gridDim.x - 1) {
+        my_pad[kArriveOff] = 0u;
+        my_pad[kEpochOff] = epoch;
+        __threadfence_system();
+      }
+    }
+    return;
+  }
   if (threadIdx.x < a.world) s_coef[threadIdx.x] = __uint_as_float(my_pad[kCoefOff + threadIdx.x]);
   __syncthreads();
 
@@ -177,7 +189,8 @@ __global__ void __launch_bounds__(256) dp_reduce_adamw_kernel(const DpArgs a) {
   const bool ok = wait_all(my_pad, kDoneOff, a.world, epoch, a.timeout_ns, a.status, &s_fail);
   if (threadIdx.x == 0) {
     my_pad[kArriveOff] = 0u;
-    if (ok) my_pad[kEpochOff] = epoch;
+    my_pad[kEpochOff] = epoch;     // also after a timed-out wait: every rank moves on to the same next epoch
+    (void)ok;
     __threadfence_system();
   }
 }

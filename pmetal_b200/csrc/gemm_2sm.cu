@@ -402,7 +402,7 @@ extern "C" int pm_gemm_bf16_2sm(const void* A, int a_mn, int lda, int a_rows, co
                                 int N, int K, int K2, int n_store, float alpha, int splits, int seg_mode,
                                 const int* seg_end, int seg_r, int max_ctas, int* status,
                                 cudaStream_t stream) {
-  if (splits < 1 || (splits > 1 && out_mode < 2)) return -12;
+  if (splits < 1 || (splits > 1 && (out_mode < 2 || out_mode > 3))) return -12;   // split-K needs the atomic modes
   if (M <= 0 || N <= 0 || K <= 0) return -13;
   if (out_mode == 0 && ((ldd % 8) || (reinterpret_cast<uintptr_t>(D) & 15))) return -14;
   if (R && ((ldr % 8) || (reinterpret_cast<uintptr_t>(R) & 15))) return -15;

@@ -17,7 +17,9 @@ struct GemmParams {
   int nk1, nk2;    // number of 64-wide K blocks in the first / second product
   int splits;      // split-K factor (out_mode must be atomic when > 1)
   int stages;
-  int out_mode;    // 0: bf16 store, 1: f32 store, 2: f32 atomic add, 3: f32 atomic add, transposed
+  int out_mode;    // 0: bf16 store, 1: f32 store, 2: f32 atomic add, 3: f32 atomic add, transposed,
+                   // 4 / 5: as 2 / 3 with a plain read-add-write (one CTA owns each output tile: needs splits == 1;
+                   // the sum is then formed in a fixed order, bit for bit the same on every run)
   int ldd, ldr;
   int n_store;     // columns >= n_store are computed but not written
   float alpha;
@@ -87,12 +89,22 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
 #pragma unroll
       for (int e = 0; e < 32; ++e)
         if (col0 + e < p.n_store) atomicAdd(drow + col0 + e, __uint_as_float(r[e]) * p.alpha);
-    } else {
+    } else if (p.out_mode == 3) {
       float* d = static_cast<float*>(p.D);
 #pragma unroll
       for (int e = 0; e < 32; ++e)
         if (col0 + e < p.n_store)
           atomicAdd(d + static_cast<size_t>(col0 + e) * p.ldd + row, __uint_as_float(r[e]) * p.alpha);
+    } else if (p.out_mode == 4) {
+      float* drow = static_cast<float*>(p.D) + static_cast<size_t>(row) * p.ldd;
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        if (col0 + e < p.n_store) drow[col0 + e] += __uint_as_float(r[e]) * p.alpha;
+    } else {
+      float* d = static_cast<float*>(p.D);
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        if (col0 + e < p.n_store) d[static_cast<size_t>(col0 + e) * p.ldd + row] += __uint_as_float(r[e]) * p.alpha;
     }
 }
 

@@ -209,7 +209,7 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
                             int seg_r, int max_ctas, int* status, cudaStream_t stream) {
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return -10;
   if ((b_mn || (K2 > 0 && b2_mn)) && (bn % 64)) return -11;
-  if (splits < 1 || (splits > 1 && out_mode < 2)) return -12;
+  if (splits < 1 || (splits > 1 && (out_mode < 2 || out_mode > 3))) return -12;   // split-K needs the atomic modes
   if (M <= 0 || N <= 0 || K <= 0) return -13;
   if (out_mode == 0 && ((ldd % 8) || (reinterpret_cast<uintptr_t>(D) & 15))) return -14;
   if (R && ((ldr % 8) || (reinterpret_cast<uintptr_t>(R) & 15))) return -15;

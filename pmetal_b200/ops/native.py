@@ -25,6 +25,10 @@ MN_MAJOR = os.environ.get("PMETAL_MN_MAJOR", "1") == "1"
 ATTN_TC = os.environ.get("PMETAL_ATTN_TC", "1") == "1"      # tcgen05 attention kernels
 ATTN_FWD_V1 = os.environ.get("PMETAL_ATTN_FWD_V1", "0") == "1"   # single-softmax-group forward (comparison runs)
 USE_2SM = os.environ.get("PMETAL_GEMM_2SM", "1") == "1"   # CTA-pair kernel for 256-wide tiles
+# Reductions over tokens (LoRA dA / dB, weight gradients) are split across CTAs and summed with fp32 atomics, whose
+# order varies from run to run. With PMETAL_DETERMINISTIC=1 every output tile is owned by one CTA and accumulated in a
+# fixed order instead (slower for the skinny LoRA products, bitwise reproducible).
+DETERMINISTIC = os.environ.get("PMETAL_DETERMINISTIC", "0") == "1"
 LAUNCHES = 0   # number of kernels launched through this module (bench reporting)
 
 c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
@@ -260,8 +264,9 @@ def lora_da(dt, x, nr: int, out: torch.Tensor) -> None:
         return
     tw = dt.shape[1]
     nk = -(-M // 64)
-    raw_gemm(x, 1, x.stride(0), kin, dt, 1, dt.stride(0), tw, out, 3, out.stride(0), kin, tw, M, n_store=nr, bn=64,
-             splits=_splits_for(-(-kin // 128), nk))
+    det = DETERMINISTIC
+    raw_gemm(x, 1, x.stride(0), kin, dt, 1, dt.stride(0), tw, out, 5 if det else 3, out.stride(0), kin, tw, M, n_store=nr,
+             bn=64, splits=1 if det else _splits_for(-(-kin // 128), nk))
 
 
 def lora_db(dy, t, seg_sizes, r: int, out: torch.Tensor) -> None:
@@ -274,9 +279,10 @@ def lora_db(dy, t, seg_sizes, r: int, out: torch.Tensor) -> None:
             n0 += sz
         return
     nk = -(-M // 64)
-    raw_gemm(dy, 1, dy.stride(0), N, t, 1, t.stride(0), t.shape[1], out, 2, out.stride(0), N, 64, M, n_store=r, bn=64,
-             splits=_splits_for(-(-N // 128), nk), seg_mode=2 if len(seg_sizes) > 1 else 0, seg_sizes=seg_sizes,
-             seg_r=r)
+    det = DETERMINISTIC
+    raw_gemm(dy, 1, dy.stride(0), N, t, 1, t.stride(0), t.shape[1], out, 4 if det else 2, out.stride(0), N, 64, M,
+             n_store=r, bn=64, splits=1 if det else _splits_for(-(-N // 128), nk),
+             seg_mode=2 if len(seg_sizes) > 1 else 0, seg_sizes=seg_sizes, seg_r=r)
 
 
 # ------------------------------------------------------------------------------------------- grouped (expert) GEMM

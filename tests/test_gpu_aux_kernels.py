@@ -447,3 +447,51 @@ def test_grouped_gemm_forward_dx_dw(E, N, K, counts):
     for e, c in enumerate(counts):
         if c == 0:
             assert float(dw[e].abs().max()) == 0.0
+
+
+def test_fused_dp_step_gives_up_on_a_silent_peer_and_recovers():
+    """The fused data-parallel kernel is launched as rank 0 of a world of two whose second rank never shows up (its
+    signal pad is a local buffer that nothing writes). The bounded wait must run out after the 20 ms limit, the status
+    word must carry the peer-timeout code, the process must stay usable, and the next, ordinary step on the same signal
+    pad must give the AdamW result."""
+    import ctypes
+    nat = _nat()
+    from pmetal_b200.ops import reference as ref
+    lib = nat.lib()
+    lib.pm_dp_reduce_adamw.restype = ctypes.c_int
+    dev = "cuda"
+    n = 8 * 1024
+    torch.manual_seed(5)
+    g0, g1 = torch.randn(n, device=dev), torch.zeros(n, device=dev)
+    p0, p1 = torch.randn(n, device=dev), torch.zeros(n, device=dev)
+    s0, s1 = torch.zeros(n, device=dev, dtype=torch.bfloat16), torch.zeros(n, device=dev, dtype=torch.bfloat16)
+    pad0, pad1 = torch.zeros(32, dtype=torch.int32, device=dev), torch.zeros(32, dtype=torch.int32, device=dev)
+    m, v = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    lr_mult, wd = torch.ones(n // 1024, device=dev), torch.zeros(n // 1024, device=dev)
+    gn = torch.zeros(1, device=dev)
+    nat.sumsq(g0, gn)
+    arr = ctypes.c_ulonglong * 2
+
+    def launch(world, timeout_s, step):
+        ptr = lambda a, b: arr(a.data_ptr(), b.data_ptr())       # noqa: E731
+        return lib.pm_dp_reduce_adamw(ptr(g0, g1), ptr(p0, p1), ptr(s0, s1), ptr(pad0, pad1), nat._p(m), nat._p(v),
+                                      nat._p(lr_mult), nat._p(wd), nat._p(gn), nat._p(None), ctypes.c_longlong(n),
+                                      ctypes.c_int(0), ctypes.c_int(world), ctypes.c_float(1e-2), ctypes.c_float(0.9),
+                                      ctypes.c_float(0.999), ctypes.c_float(1e-8), ctypes.c_int(step), ctypes.c_float(1.0),
+                                      ctypes.c_float(0.0), ctypes.c_double(timeout_s), ctypes.c_int(16),
+                                      nat._p(nat.status_word()), nat._stream())
+    before = p0.clone()
+    assert launch(2, 0.02, 1) == 0
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="104"):
+        nat.check_status()
+    assert torch.equal(p0, before)                       # nothing was updated by the abandoned step
+    assert int(pad0[25]) == 0 and int(pad0[24]) == 1     # arrival counter cleared, epoch closed
+    # the same pad, now as a world of one: an ordinary step
+    assert launch(1, 5.0, 1) == 0
+    torch.cuda.synchronize()
+    nat.check_status()
+    pr, mr, vr = before.clone(), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+    ref.adamw_step(pr, g0.clone(), mr, vr, 1, 1e-2, 0.9, 0.999, 1e-8, 0.0)
+    assert torch.allclose(p0, pr, rtol=1e-5, atol=1e-6) and int(pad0[24]) == 2
+    assert torch.allclose(s0.float(), pr, rtol=1e-2, atol=1e-2)

@@ -108,6 +108,66 @@ def test_lora_backward_pieces(mn):
         nat.MN_MAJOR = old
 
 
+def test_lora_gradients_are_bitwise_reproducible_in_deterministic_mode():
+    """dA and dB are reductions over all tokens. The default path sums CTA partials with fp32 atomics (order varies);
+    the deterministic mode gives one CTA each output tile, so two runs must agree bit for bit."""
+    nat = _nat()
+    old = nat.DETERMINISTIC
+    try:
+        torch.manual_seed(4)
+        segs, r = (512, 256, 256), 16
+        M, K, N = 8192, 1024, sum(segs)
+        x, dy = _rand(M, K), _rand(M, N)
+        a, b = _rand(len(segs) * r, K, scale=K ** -0.5), _rand(N, r, scale=0.2)
+        t = nat.lora_t(x, a, 2.0)
+        dt = nat.lora_dt(dy, b, segs, r, 2.0)
+        outs = {}
+        for det in (True, True, False):
+            nat.DETERMINISTIC = det
+            da = torch.zeros(len(segs) * r, K, device="cuda")
+            db = torch.zeros(N, r, device="cuda")
+            nat.lora_da(dt, x, len(segs) * r, da)
+            nat.lora_db(dy, t, segs, r, db)
+            nat.lora_da(dt, x, len(segs) * r, da)          # accumulation over micro-batches goes the same way
+            outs.setdefault(det, []).append((da, db))
+        nat.check_status()
+        (da1, db1), (da2, db2) = outs[True]
+        assert torch.equal(da1, da2) and torch.equal(db1, db2)
+        _close(da1, outs[False][0][0], rtol=1e-3, atol=1e-2, what="deterministic vs atomic dA")
+        _close(db1, outs[False][0][1], rtol=1e-3, atol=1e-2, what="deterministic vs atomic dB")
+        _close(da1, 2 * (dt[:, :len(segs) * r].float().t() @ x.float()), rtol=2e-2, atol=1.0, what="dA")
+    finally:
+        nat.DETERMINISTIC = old
+
+
+def test_cta_pair_gemm_with_lora_segments_at_the_training_shape():
+    """The 256 x 256 CTA-pair kernel on the benchmark's QKV projection (16384 tokens, 3 LoRA segments) and its input
+    gradient, against fp32."""
+    nat = _nat()
+    torch.manual_seed(6)
+    M, K, segs, r = 16384, 1024, (2048, 1024, 1024), 16
+    N = sum(segs)
+    x, w = _rand(M, K), _rand(N, K, scale=K ** -0.5)
+    a, b = _rand(len(segs) * r, K, scale=K ** -0.5), _rand(N, r, scale=0.2)
+    res = None
+    t = nat.lora_t(x, a, 2.0)
+    y = nat.gemm_lora(x, w, t, b, segs, r, res)
+    nat.check_status()
+    ref = x.float() @ w.float().t()
+    n0 = 0
+    for i, sz in enumerate(segs):
+        ref[:, n0:n0 + sz] += t[:, i * r:(i + 1) * r].float() @ b[n0:n0 + sz].float().t()
+        n0 += sz
+    _close(y, ref, what="2-SM gemm + lora (training shape)")
+    dy = _rand(M, N)
+    dt = nat.lora_dt(dy, b, segs, r, 2.0)
+    for wt in (w.t().contiguous(), None):
+        dx = nat.gemm_lora_dx(dy, w, wt, dt, a)
+        _close(dx, dy.float() @ w.float() + dt[:, :len(segs) * r].float() @ a.float(), rtol=2e-2, atol=5e-2,
+               what="2-SM dX + lora (training shape)")
+    nat.check_status()
+
+
 def test_rmsnorm():
     nat = _nat()
     from pmetal_b200.ops import reference as ref
