@@ -318,11 +318,17 @@ def main() -> None:
         print(json.dumps(out))
     sys.stdout.flush()
     if world > 1:
-        # leave without the collective teardown: destroying a communicator whose collectives were captured in a
-        # CUDA graph can block for minutes, and nothing after this point needs it
+        # orderly teardown: captured graphs hold the streams (and, on the NCCL path, the communicator's work) they were
+        # recorded on, so they go first; then symmetric-memory handles, then the process group. A watchdog ends the
+        # process if the communicator still fails to shut down within 30 s, so a stuck teardown cannot hold the node.
         dist.barrier()
         torch.cuda.synchronize()
-        os._exit(0)
+        for name in ("_graph", "_g_in", "_g_loss", "_g_gnorm"):
+            if hasattr(loop, name):
+                delattr(loop, name)
+        del loop, model, dctx
+        from pmetal_b200.parallel.dp import shutdown_process_group
+        shutdown_process_group(30.0)
 
 
 if __name__ == "__main__":

@@ -121,7 +121,8 @@ def main(argv=None) -> int:
         print(json.dumps(out), flush=True)
     dist.barrier()
     torch.cuda.synchronize()
-    os._exit(0)
+    from pmetal_b200.parallel.dp import shutdown_process_group
+    shutdown_process_group()
 
 
 if __name__ == "__main__":

@@ -10,8 +10,6 @@ import argparse
 import json
 import os
 
-os.environ.setdefault("PMETAL_DECODE_GRAPHS", "0")
-
 PHASES = ["P1 stage", "P1 qkv mat-vec", "P1 barrier", "P2 attention", "P2 barrier", "P3 stage", "P3 o-proj mat-vec",
           "P3 barrier", "P4 stage", "P4 gate/up mat-vec", "P4 barrier", "P5 stage", "P5 down mat-vec", "P5 barrier"]
 
@@ -56,18 +54,26 @@ def phase_trace(model, batch: int, prompt_len: int = 128) -> dict:
     return out
 
 
-def main() -> int:
+def add_arguments(ap) -> None:
+    ap.add_argument("--tokens", type=int, default=6)
+    ap.add_argument("--model", default="random:qwen3-0.6b")
+    ap.add_argument("--phases", action="store_true")
+    ap.add_argument("--batch", type=int, default=1)
+
+
+def main(argv=None, args=None) -> int:
+    """Also reachable as ``pmetal bench-decode`` (which passes its parsed arguments as ``args``)."""
+    os.environ.setdefault("PMETAL_DECODE_GRAPHS", "0")      # eager launches: one kernel per launch under a profiler
     import torch
 
     from ..models.generation import Generator
     from ..models.loader import load_pretrained
     from ..models.sampling import SamplingParams
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--tokens", type=int, default=6)
-    ap.add_argument("--model", default="random:qwen3-0.6b")
-    ap.add_argument("--phases", action="store_true")
-    ap.add_argument("--batch", type=int, default=1)
-    a = ap.parse_args()
+    a = args
+    if a is None:
+        ap = argparse.ArgumentParser()
+        add_arguments(ap)
+        a = ap.parse_args(argv)
     m, _, _ = load_pretrained(a.model, dtype=torch.bfloat16, device="cuda")
     m.eval()
     for p in m.parameters():

@@ -87,7 +87,8 @@ def main(argv=None) -> int:
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()
-        os._exit(0)
+        from pmetal_b200.parallel.dp import shutdown_process_group
+        shutdown_process_group()
     return 0
 
 

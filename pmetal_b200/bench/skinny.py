@@ -9,7 +9,8 @@ before every timed call so that nothing is served from L2."""
 import json
 
 
-def main() -> int:
+def main(argv=None, args=None) -> int:
+    """Also reachable as ``pmetal bench-skinny``."""
     import torch
 
     from ..ops import native

@@ -1920,6 +1920,13 @@ def _bench_alias_args(sp):
     p = sp.add_parser("bench-ffi", help="cost of one call into the native host library")
     p.add_argument("--calls", type=int, default=200000)
     p.set_defaults(func=cmd_bench_ffi)
+    p = sp.add_parser("bench-skinny", help="few-row linear layers: mat-vec and narrow-tile GEMM kernels against cuBLAS")
+    p.set_defaults(func=lambda a: __import__("pmetal_b200.bench.skinny", fromlist=["main"]).main(args=a))
+    p = sp.add_parser("bench-decode", help="short decode runs for profiling; --phases prints per-phase device times of "
+                                           "the whole-step decode kernel")
+    from ..bench.decode_trace import add_arguments as _decode_trace_args
+    _decode_trace_args(p)
+    p.set_defaults(func=lambda a: __import__("pmetal_b200.bench.decode_trace", fromlist=["main"]).main(args=a))
     return p
 
 

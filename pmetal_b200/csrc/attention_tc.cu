@@ -13,6 +13,7 @@
 // exp pipeline overlap. Same masking rule as attention.cu: key j is visible to query i iff
 // seq_start[i] <= j <= i.
 #include "attention_tc.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

@@ -18,6 +18,7 @@
 // columns of S (and dP) with back-to-back tcgen05.ld instructions and one wait, and releases the TMEM buffer as soon
 // as the values are in registers, so the tensor cores start on the next tile while this one is still being formed.
 #include "attention_tc.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

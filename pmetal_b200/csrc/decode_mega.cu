@@ -29,6 +29,7 @@
 #include <stdlib.h>
 
 #include "pdl.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

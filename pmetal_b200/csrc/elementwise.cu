@@ -12,6 +12,7 @@
 #include "host_util.cuh"
 
 #include "pdl.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "host_util.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

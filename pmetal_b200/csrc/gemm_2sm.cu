@@ -18,6 +18,7 @@
 // All waits are bounded (see common.cuh); the pair leaves through a cluster barrier so neither CTA
 // exits while its partner can still touch its shared memory.
 #include "gemm_common.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

@@ -13,6 +13,7 @@
 // owner, warps 2..5 = epilogue (TMEM -> registers -> global). Two accumulator buffers
 // in TMEM let the epilogue of tile i overlap the MMAs of tile i+1.
 #include "gemm_common.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

@@ -14,6 +14,7 @@
 // Same CTA layout as gemm_tcgen05.cu: warp 0 TMA producer, warp 1 MMA issuer (TMEM double-buffered), warps 2..5
 // epilogue; persistent over the tile list; every wait is bounded.
 #include "gemm_common.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

@@ -29,6 +29,7 @@
 // by the matching 128 up rows, so one accumulator tile holds both halves of 128 outputs.
 // All cross-rank waits are bounded and report through the status word; plain peer loads/stores only.
 #include "gemm_common.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

@@ -19,6 +19,7 @@
 #include <math.h>
 #include <stdint.h>
 #include "host_util.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

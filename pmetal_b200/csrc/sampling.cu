@@ -23,6 +23,7 @@
 #include <math.h>
 #include <stdint.h>
 #include "host_util.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

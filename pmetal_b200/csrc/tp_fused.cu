@@ -23,6 +23,7 @@
 // uses epoch-valued flags in each rank's signal pad (system-scope release/acquire); every wait is bounded and reports
 // through the status word. Plain peer loads/stores only: no multimem and no multicast loads.
 #include "gemm_common.cuh"
+#include "pmetal_b200.h"
 
 namespace pm {
 

@@ -14,9 +14,40 @@ import torch.nn as nn
 
 
 def row_norms(fl) -> torch.Tensor:
-    """||W + s B A|| per output row, fp32, no graph."""
+    """||W + s B A|| per output row, fp32, no graph.
+
+    The merged weight is never formed. Per row, with G = A A^T (r x r):
+        ||W + s B A||^2 = ||W||^2 + 2 s (W A^T) . B + s^2 B G B^T
+    ``||W||^2`` is computed once (the base is frozen); ``W A^T`` is one skinny product per segment that reads W once
+    in its stored precision. The result is cached until a factor changes (``_version`` of the two parameters), so
+    gradient-accumulation micro-steps and evaluation passes reuse it."""
     with torch.no_grad():
-        return fl.merged_weight().float().norm(dim=1).clamp(min=1e-8)
+        a, b = fl.lora_a, fl.lora_b
+        key = (a._version, b._version, a.data_ptr(), b.data_ptr())
+        hit = getattr(fl, "_dora_norm_cache", None)
+        if hit is not None and hit[0] == key:
+            return hit[1]
+        if getattr(fl, "qweight", None) is not None:              # packed base: expand once for this computation
+            from .nf4 import dequantize
+            w = dequantize(fl.qweight, torch.float32)
+            w_sq = (w * w).sum(1)
+        else:
+            w = fl.weight.detach()
+            w_sq = getattr(fl, "_dora_w_sq", None)
+            if w_sq is None or w_sq.device != w.device:
+                w_sq = fl._dora_w_sq = (w.float() ** 2).sum(1)
+        out = w_sq.clone()
+        o = 0
+        for i, sz in enumerate(fl.seg_sizes):
+            ai = a[i * fl.r:(i + 1) * fl.r].detach()
+            bi = b[o:o + sz].detach().float()
+            wa = (w[o:o + sz] @ ai.to(w.dtype).t()).float()                     # [sz, r]
+            g = ai.float() @ ai.float().t()                                     # [r, r]
+            out[o:o + sz] += 2.0 * fl.scale * (wa * bi).sum(1) + fl.scale ** 2 * ((bi @ g) * bi).sum(1)
+            o += sz
+        n = out.clamp(min=0).sqrt().clamp(min=1e-8)
+        fl._dora_norm_cache = (key, n)
+        return n
 
 
 def attach_dora(model) -> int:

@@ -105,7 +105,7 @@ class FusedLinear(nn.Module):
             from ..lora.nf4 import dequantize
             w = dequantize(q, torch.float32)
         else:
-            w = self.weight.detach().float()
+            w = self.weight.detach().to(torch.float32, copy=True)     # never alias the stored weight (fp32 models)
         if self.lora_a is not None:
             o = 0
             for i, sz in enumerate(self.seg_sizes):

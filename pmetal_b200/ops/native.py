@@ -29,6 +29,9 @@ USE_2SM = os.environ.get("PMETAL_GEMM_2SM", "1") == "1"   # CTA-pair kernel for 
 # order varies from run to run. With PMETAL_DETERMINISTIC=1 every output tile is owned by one CTA and accumulated in a
 # fixed order instead (slower for the skinny LoRA products, bitwise reproducible).
 DETERMINISTIC = os.environ.get("PMETAL_DETERMINISTIC", "0") == "1"
+# PMETAL_TUNA=1: the tile width of plain GEMMs comes from the tuner's cache (utils/tuna.py); a shape seen for the first
+# time is timed over the candidate widths once (never during CUDA-graph capture) and the winner is remembered on disk.
+TUNA = os.environ.get("PMETAL_TUNA", "0") == "1"
 LAUNCHES = 0   # number of kernels launched through this module (bench reporting)
 
 c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
@@ -136,6 +139,19 @@ def _pick_bn(n: int, seg_sizes: Sequence[int] = (), m: int = 1 << 30) -> int:
     return 32
 
 
+def tuned_choice(op: str, shape, candidates, default, run):
+    """Best of ``candidates`` for ``op`` at ``shape`` according to the tuner's cache; times them on a cache miss."""
+    from ..utils.tuna import Tuner, global_tuner
+    t = global_tuner()
+    key = Tuner.make_key(op, *shape)
+    hit = t.lookup(key)
+    if hit is not None and hit in list(candidates):
+        return hit
+    if torch.cuda.is_available() and torch.cuda.is_current_stream_capturing():
+        return default                      # timing needs synchronisation: not inside a capture
+    return t.tune(key, list(candidates), run)
+
+
 def _seg_ends(seg_sizes: Sequence[int]):
     ends, c = [], 0
     for s in seg_sizes:
@@ -180,9 +196,15 @@ def gemm(x: torch.Tensor, w: torch.Tensor, alpha: float = 1.0, residual: Optiona
     Nw = max(N, pad_n_to)
     if out is None:
         out = torch.empty(M, Nw, dtype=torch.bfloat16, device=x.device)
-    bn = bn or _pick_bn(Nw, (), M)
-    raw_gemm(x, 0, x.stride(0), M, w, 0, w.stride(0), N, out, 0, out.stride(0), M, Nw, K, R=residual,
-             ldr=residual.stride(0) if residual is not None else 0, alpha=alpha, bn=bn)
+
+    def run(b):
+        raw_gemm(x, 0, x.stride(0), M, w, 0, w.stride(0), N, out, 0, out.stride(0), M, Nw, K, R=residual,
+                 ldr=residual.stride(0) if residual is not None else 0, alpha=alpha, bn=b)
+    if not bn:
+        bn = _pick_bn(Nw, (), M)
+        if TUNA:
+            bn = tuned_choice("gemm_bn", (M, Nw, K), [b for b in (32, 64, 128, 256) if b <= max(Nw, 32)], bn, run)
+    run(bn)
     return out
 
 

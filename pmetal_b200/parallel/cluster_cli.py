@@ -126,7 +126,8 @@ def _bench_worker(mb: int, iters: int) -> None:
         print(json.dumps(out), flush=True)
     dist.barrier()
     torch.cuda.synchronize()
-    os._exit(0)
+    from pmetal_b200.parallel.dp import shutdown_process_group
+    shutdown_process_group()
 
 
 def _pipeline_worker(mb: int, iters: int, hidden: int = 0, tokens: int = 0, timeout_s: float = 0.0) -> None:
@@ -145,7 +146,8 @@ def _pipeline_worker(mb: int, iters: int, hidden: int = 0, tokens: int = 0, time
                           "gbs_per_hop": round(gbs, 1), "frac_of_nvlink_copy": round(gbs / NVLINK_COPY_GBS, 3)}), flush=True)
     dist.barrier()
     torch.cuda.synchronize()
-    os._exit(0)
+    from pmetal_b200.parallel.dp import shutdown_process_group
+    shutdown_process_group()
 
 
 if __name__ == "__main__":

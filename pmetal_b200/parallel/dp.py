@@ -16,6 +16,34 @@ import torch
 import torch.distributed as dist
 
 
+def shutdown_process_group(timeout_s: float = 30.0) -> None:
+    """Orderly end of a multi-rank job: barrier, drain the device, drop unreachable objects (captured CUDA graphs keep
+    the streams, and on the NCCL path the communicator's work, they were recorded on; symmetric-memory handles keep
+    peer mappings), then destroy the process group. The caller should already have released its graphs and models.
+    A watchdog thread ends the process if the communicator has not shut down after ``timeout_s`` seconds, so that a
+    stuck teardown cannot hold the node's GPUs."""
+    import gc
+    import threading
+    if not dist.is_initialized():
+        return
+    try:
+        dist.barrier()
+    except Exception:
+        pass
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    watchdog = threading.Timer(timeout_s, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
+    try:
+        dist.destroy_process_group()
+    finally:
+        watchdog.cancel()
+
+
 class DistContext:
     """Rank bookkeeping + the collectives the training loop needs."""
 

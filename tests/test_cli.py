@@ -153,7 +153,8 @@ def test_infer_benchmark_profile_tools_and_repetition(model_dir, capsys, tmp_pat
     assert main(["infer", "-m", model_dir, "-p", "time?", "--tools", str(tools), "--max-tokens", "2", "--greedy", "--json",
                  "--backend", "standard", "--kv-quant", "--detect-repetition", "--device", "cpu"]) == 0
     out = capsys.readouterr()
-    assert "not applied" in out.err and json.loads(out.out.strip().splitlines()[-1])["prompt_tokens"] > 20   # the tool block is in the prompt
+    # --kv-quant selects the int8 paged cache; the tool block is in the prompt
+    assert "kv cache: int8 (explicit)" in out.err and json.loads(out.out.strip().splitlines()[-1])["prompt_tokens"] > 20
 
 
 def test_quantize_with_adapter_and_bits(model_dir, capsys, tmp_path):

@@ -36,6 +36,27 @@ def test_gemm_kmajor(M, N, K, bn):
     _close(y, x.float() @ w.float().t(), what="gemm")
 
 
+def test_gemm_tile_width_from_the_tuner(tmp_path, monkeypatch):
+    """With the tuner on, the first call of a shape times the candidate tile widths and records the winner; later
+    calls read it from the cache file and give the same result."""
+    nat = _nat()
+    from pmetal_b200.utils import tuna
+    monkeypatch.setenv("PMETAL_TUNA_CACHE", str(tmp_path))
+    monkeypatch.setattr(tuna, "_GLOBAL", None)
+    monkeypatch.setattr(nat, "TUNA", True)
+    torch.manual_seed(0)
+    x, w = _rand(512, 256), _rand(384, 256, scale=1 / 16)
+    y = nat.gemm(x, w)
+    nat.check_status()
+    _close(y, x.float() @ w.float().t(), what="tuned gemm")
+    key = tuna.Tuner.make_key("gemm_bn", 512, 384, 256)
+    table = tuna.Tuner(str(tmp_path / "tuna.json")).table
+    assert key in table and table[key]["best"] in (32, 64, 128, 256) and len(table[key]["ms"]) >= 3
+    n0 = nat.LAUNCHES
+    y2 = nat.gemm(x, w)
+    assert nat.LAUNCHES - n0 == 1 and torch.equal(y, y2)          # cache hit: one launch, no timing runs
+
+
 def test_gemm_alpha_residual_pad():
     nat = _nat()
     torch.manual_seed(1)

@@ -160,3 +160,28 @@ def test_config1_tiny_sft_loss_decreases_and_checkpoint(tmp_path):
     a, b = lora_state_dict(m), lora_state_dict(m2)
     assert all(torch.equal(a[k], b[k]) for k in a)
     save_adapter(m, str(tmp_path / "final"), cfg)
+
+
+def test_dora_row_norms_without_the_merged_weight_and_their_cache():
+    from pmetal_b200.lora.dora import attach_dora, merged_dora_weight, row_norms
+    m = _tiny()
+    apply_lora(m, LoraConfig(r=8, alpha=16, target_modules=["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj",
+                                                            "up_proj", "down_proj"]))
+    g = torch.Generator().manual_seed(3)
+    with torch.no_grad():
+        for _, _, fl in m.fused_linears():
+            fl.lora_b.copy_(torch.randn(fl.lora_b.shape, generator=g) * 0.1)
+    assert attach_dora(m) == 8
+    for _, _, fl in m.fused_linears():
+        want = fl.merged_weight().float().norm(dim=1)
+        got = row_norms(fl)
+        assert torch.allclose(got, want, rtol=1e-4, atol=1e-5)
+        assert row_norms(fl) is got                      # unchanged factors: the cached tensor comes back
+        with torch.no_grad():
+            fl.lora_b.mul_(1.5)                          # an optimizer step bumps the version
+        again = row_norms(fl)
+        assert again is not got and torch.allclose(again, fl.merged_weight().float().norm(dim=1), rtol=1e-4, atol=1e-5)
+    # forward of the decomposed form equals a plain linear with the merged DoRA weight
+    fl = m.layers[0].self_attn.qkv_proj
+    x = torch.randn(5, fl.in_features, generator=g)
+    assert torch.allclose(fl.forward(x), x @ merged_dora_weight(fl).t(), rtol=1e-4, atol=1e-4)

@@ -51,7 +51,8 @@ def main():
     if rank == 0:
         print("TP_WORKER_OK", flush=True)
     sys.stdout.flush()
-    os._exit(0)
+    from pmetal_b200.parallel.dp import shutdown_process_group
+    shutdown_process_group()
 
 
 if __name__ == "__main__":
