@@ -73,6 +73,143 @@ def build_tp_plan(arch: str, config: dict, world: int) -> Dict[str, ShardingDire
     return plan
 
 
+# --------------------------------------------------------------------------- per-architecture tensor plans
+# Block planners: suffix -> directive tables for one block of a layer; ``build_plan`` walks the layers of a checkpoint
+# and applies the table that fits each block (crates/pmetal-distributed/src/tensor_parallel/plan.rs:50-748). Weights
+# are named as in Hugging Face checkpoints; "col" splits output rows (axis 0) and expects a replicated input, "row"
+# splits input columns (axis 1) and produces partial sums that are reduced.
+_COLW, _ROWW, _REP = ShardingDirective("all_to_sharded", 0), ShardingDirective("sharded_to_all", 1), ShardingDirective("replicated")
+
+
+def _apply(prefix: str, table: Dict[str, ShardingDirective]) -> Dict[str, ShardingDirective]:
+    return {f"{prefix}.{k}": v for k, v in table.items()}
+
+
+def plan_attention(prefix: str) -> Dict[str, ShardingDirective]:
+    """Multi-head / grouped-query attention: q, k, v by head (weights and biases), o by input columns; the o bias is
+    added once after the reduction, so it stays whole."""
+    t = {f"{p}_proj.{k}": _COLW for p in "qkv" for k in ("weight", "bias")}
+    t.update({"o_proj.weight": _ROWW, "o_proj.bias": _REP, "q_norm.weight": _REP, "k_norm.weight": _REP})
+    return _apply(prefix, t)
+
+
+def plan_mla(prefix: str, q_lora_rank: Optional[int]) -> Dict[str, ShardingDirective]:
+    """Multi-head latent attention (DeepSeek V2/V3): the down-projections to the latent and their norms are shared by
+    all heads and stay whole; the up-projections carry the head dimension and are split by head."""
+    t = {"kv_a_proj_with_mqa.weight": _REP, "kv_a_layernorm.weight": _REP, "kv_b_proj.weight": _COLW, "o_proj.weight": _ROWW}
+    if q_lora_rank:
+        t.update({"q_a_proj.weight": _REP, "q_a_layernorm.weight": _REP, "q_b_proj.weight": _COLW})
+    else:
+        t["q_proj.weight"] = _COLW
+    return _apply(prefix, t)
+
+
+def plan_ffn(prefix: str) -> Dict[str, ShardingDirective]:
+    return _apply(prefix, {"gate_proj.weight": _COLW, "up_proj.weight": _COLW, "down_proj.weight": _ROWW})
+
+
+def plan_gdn(prefix: str) -> Dict[str, ShardingDirective]:
+    """Gated delta-net mixer (Qwen3-Next): every input projection, the depth-wise convolution and the per-head decay
+    parameters are split over heads; the output projection is split by input columns like attention's."""
+    t = {f"in_proj_{n}.weight": _COLW for n in ("qkv", "z", "b", "a")}
+    t.update({"conv1d.weight": _COLW, "dt_bias": _COLW, "A_log": _COLW, "norm.weight": _REP, "o_proj.weight": _ROWW})
+    return _apply(prefix, t)
+
+
+def _stacked_experts(prefix: str, total: int, projs=("gate_proj", "up_proj", "down_proj"), kinds=("weight",)):
+    d = ShardingDirective("expert_sharded", 0, total)
+    return {f"{prefix}.{p}.{k}": d for p in projs for k in kinds}
+
+
+def plan_deepseek_moe(prefix: str, total_experts: int, has_shared: bool) -> Dict[str, ShardingDirective]:
+    t = {f"{prefix}.gate.weight": _REP, f"{prefix}.gate.e_score_correction_bias": _REP}
+    if has_shared:
+        t.update(plan_ffn(f"{prefix}.shared_experts"))
+    t.update(_stacked_experts(f"{prefix}.switch_mlp", total_experts))
+    return t
+
+
+def plan_qwen_moe(prefix: str, total_experts: int) -> Dict[str, ShardingDirective]:
+    t = {f"{prefix}.gate.weight": _REP, f"{prefix}.shared_expert_gate.weight": _REP}
+    t.update(plan_ffn(f"{prefix}.shared_expert"))
+    t.update(_stacked_experts(f"{prefix}.switch_mlp", total_experts))
+    return t
+
+
+def plan_llama4_moe(prefix: str, total_experts: int) -> Dict[str, ShardingDirective]:
+    t = {f"{prefix}.router.weight": _REP}
+    t.update(plan_ffn(f"{prefix}.shared_expert"))
+    t.update(_stacked_experts(f"{prefix}.experts", total_experts))
+    return t
+
+
+def plan_gpt_oss_moe(prefix: str, total_experts: int) -> Dict[str, ShardingDirective]:
+    """GPT-OSS experts carry a bias per expert ([E, out]): axis 0 is the expert axis for weights and biases alike."""
+    t = {f"{prefix}.router.weight": _REP, f"{prefix}.router.bias": _REP}
+    t.update(_stacked_experts(f"{prefix}.experts", total_experts, kinds=("weight", "bias")))
+    return t
+
+
+def build_plan(arch: str, config: dict, world: int) -> Dict[str, ShardingDirective]:
+    """Full tensor name -> directive for a checkpoint of family ``arch`` (a Hugging Face ``architectures`` entry or
+    ``model_type``). ``world <= 1`` gives an empty plan. Layer kinds follow the configuration: DeepSeek's dense prefix and
+    MoE frequency, Llama-4's interleave step, Qwen's sparse step, Qwen3-Next's ``layer_types`` (or its attention
+    interval when the list is missing or has the wrong length)."""
+    if world <= 1:
+        return {}
+    g = config.get
+    n_layers = int(g("num_hidden_layers", 32))
+    heads = int(g("num_attention_heads", 32))
+    if heads % world:
+        raise ValueError(f"{heads} attention heads do not divide over {world} ranks")
+    experts = int(g("num_experts") or g("num_local_experts") or g("n_routed_experts") or 0)
+    mt = str(g("model_type", "") or "")
+    low = arch.lower()
+    hybrid = g("gdn_heads") is not None or g("mixer_pattern") is not None or "qwen3next" in low.replace("_", "")
+    deepseek = "deepseek" in low or mt in ("deepseek_v2", "deepseek_v3")
+    llama4 = "llama4" in low or mt == "llama4"
+    gpt_oss = "gptoss" in low.replace("_", "") or mt == "gpt_oss"
+    qwen_moe = any(k in low.replace("_", "") for k in ("qwen2moe", "qwen3moe")) or hybrid
+    layer_types = g("layer_types")
+    if not (isinstance(layer_types, list) and len(layer_types) == n_layers):
+        layer_types = None
+    attn_every = int(g("full_attention_interval") or g("attention_interval") or g("attn_layer_period") or 4)
+    plan: Dict[str, ShardingDirective] = {"model.embed_tokens.weight": _REP}
+    for i in range(n_layers):
+        lp = f"model.layers.{i}"
+        # ---- token mixer
+        if hybrid:
+            full = layer_types[i] == "full_attention" if layer_types else (i + 1) % attn_every == 0
+            plan.update(plan_attention(f"{lp}.self_attn") if full else plan_gdn(f"{lp}.linear_attn"))
+        elif deepseek:
+            plan.update(plan_mla(f"{lp}.self_attn", g("q_lora_rank")))
+        else:
+            plan.update(plan_attention(f"{lp}.self_attn"))
+        # ---- channel mixer
+        if deepseek:
+            moe = experts > 0 and i >= int(g("first_k_dense_replace", 0) or 0) and i % max(int(g("moe_layer_freq", 1) or 1), 1) == 0
+            plan.update(plan_deepseek_moe(f"{lp}.mlp", experts, bool(g("n_shared_experts"))) if moe else plan_ffn(f"{lp}.mlp"))
+        elif llama4 and experts > 0:
+            moe = i % max(int(g("interleave_moe_layer_step", 1) or 1), 1) == 0
+            plan.update(plan_llama4_moe(f"{lp}.feed_forward", experts) if moe else plan_ffn(f"{lp}.mlp"))
+        elif gpt_oss and experts > 0:
+            plan.update(plan_gpt_oss_moe(f"{lp}.mlp", experts))
+        elif qwen_moe and experts > 0:
+            moe = (i + 1) % max(int(g("decoder_sparse_step", 1) or 1), 1) == 0
+            plan.update(plan_qwen_moe(f"{lp}.mlp", experts) if moe else plan_ffn(f"{lp}.mlp"))
+        else:
+            plan.update(plan_ffn(f"{lp}.mlp"))
+        plan[f"{lp}.input_layernorm.weight"] = _REP
+        plan[f"{lp}.post_attention_layernorm.weight"] = _REP
+    plan["model.norm.weight"] = _REP
+    plan["lm_head.weight"] = _REP
+    return plan
+
+
+def num_sharded(plan: Dict[str, ShardingDirective]) -> int:
+    return sum(1 for d in plan.values() if d.kind != "replicated")
+
+
 def directive_for(plan: Dict[str, ShardingDirective], name: str) -> ShardingDirective:
     if "experts" in plan and "experts" in name:     # expert weights are split by expert, never inside one
         return plan["experts"]

@@ -374,3 +374,60 @@ def test_stream_multiplexer_routes_by_nonce():
     assert not mux.dispatch(msgs[2]) and mux.dropped == 1 and mux.pending() == 2        # late message of a closed request
     with pytest.raises(queue.Empty):
         mux.wait(7, timeout=0.05)
+
+
+def test_per_architecture_tensor_plans():
+    import pytest
+    import torch
+    from pmetal_b200.parallel import plans as P
+    assert P.build_plan("LlamaForCausalLM", {"num_hidden_layers": 2, "num_attention_heads": 8}, 1) == {}
+    with pytest.raises(ValueError):
+        P.build_plan("LlamaForCausalLM", {"num_hidden_layers": 2, "num_attention_heads": 6}, 4)
+    # dense llama: column / row split of attention and feed-forward, norms and embeddings whole
+    p = P.build_plan("LlamaForCausalLM", {"num_hidden_layers": 2, "num_attention_heads": 8, "num_key_value_heads": 2}, 2)
+    assert p["model.layers.0.self_attn.q_proj.weight"] == P.ShardingDirective("all_to_sharded", 0)
+    assert p["model.layers.1.self_attn.o_proj.weight"] == P.ShardingDirective("sharded_to_all", 1)
+    assert p["model.layers.1.self_attn.o_proj.bias"].kind == "replicated"
+    assert p["model.layers.0.mlp.down_proj.weight"].kind == "sharded_to_all" and p["lm_head.weight"].kind == "replicated"
+    assert p["model.layers.0.input_layernorm.weight"].kind == "replicated" and P.num_sharded(p) == 2 * (6 + 1 + 3)
+    # deepseek: latent attention, dense prefix, shared experts, stacked routed experts
+    cfg = {"num_hidden_layers": 4, "num_attention_heads": 16, "n_routed_experts": 64, "n_shared_experts": 2,
+           "first_k_dense_replace": 1, "moe_layer_freq": 1, "q_lora_rank": 1536, "model_type": "deepseek_v3"}
+    p = P.build_plan("DeepseekV3ForCausalLM", cfg, 4)
+    assert p["model.layers.0.self_attn.q_a_proj.weight"].kind == "replicated"
+    assert p["model.layers.0.self_attn.q_b_proj.weight"].kind == "all_to_sharded"
+    assert p["model.layers.0.self_attn.kv_a_proj_with_mqa.weight"].kind == "replicated"
+    assert p["model.layers.0.self_attn.kv_b_proj.weight"].kind == "all_to_sharded"
+    assert "model.layers.0.mlp.gate_proj.weight" in p and "model.layers.0.mlp.switch_mlp.gate_proj.weight" not in p
+    assert p["model.layers.1.mlp.switch_mlp.down_proj.weight"] == P.ShardingDirective("expert_sharded", 0, 64)
+    assert p["model.layers.1.mlp.shared_experts.up_proj.weight"].kind == "all_to_sharded"
+    assert p["model.layers.1.mlp.gate.weight"].kind == "replicated"
+    cfg2 = dict(cfg, q_lora_rank=None)
+    assert "model.layers.0.self_attn.q_proj.weight" in P.build_plan("DeepseekV2ForCausalLM", cfg2, 4)
+    # qwen3-moe with a sparse step of 2: odd layers are sparse
+    p = P.build_plan("Qwen3MoeForCausalLM", {"num_hidden_layers": 4, "num_attention_heads": 8, "num_experts": 16,
+                                             "decoder_sparse_step": 2}, 2)
+    assert "model.layers.0.mlp.gate_proj.weight" in p and "model.layers.1.mlp.switch_mlp.up_proj.weight" in p
+    assert p["model.layers.1.mlp.shared_expert_gate.weight"].kind == "replicated"
+    # llama-4 interleave, gpt-oss biases
+    p = P.build_plan("Llama4ForCausalLM", {"num_hidden_layers": 4, "num_attention_heads": 8, "num_local_experts": 16,
+                                           "interleave_moe_layer_step": 2, "model_type": "llama4"}, 2)
+    assert p["model.layers.0.feed_forward.experts.gate_proj.weight"].total == 16 and "model.layers.1.mlp.up_proj.weight" in p
+    assert p["model.layers.0.feed_forward.shared_expert.down_proj.weight"].kind == "sharded_to_all"
+    p = P.build_plan("GptOssForCausalLM", {"num_hidden_layers": 2, "num_attention_heads": 8, "num_local_experts": 32}, 2)
+    assert p["model.layers.1.mlp.experts.down_proj.bias"] == P.ShardingDirective("expert_sharded", 0, 32)
+    # qwen3-next: layer_types decides between attention and the delta-net mixer; a wrong-length list falls back to
+    # the attention interval
+    cfg = {"num_hidden_layers": 4, "num_attention_heads": 8, "num_experts": 8, "gdn_heads": 4,
+           "layer_types": ["linear_attention", "linear_attention", "linear_attention", "full_attention"]}
+    p = P.build_plan("Qwen3NextForCausalLM", cfg, 2)
+    assert p["model.layers.0.linear_attn.in_proj_qkv.weight"].kind == "all_to_sharded"
+    assert p["model.layers.0.linear_attn.A_log"].kind == "all_to_sharded" and p["model.layers.0.linear_attn.o_proj.weight"].axis == 1
+    assert "model.layers.3.self_attn.q_proj.weight" in p and "model.layers.3.linear_attn.conv1d.weight" not in p
+    p = P.build_plan("Qwen3NextForCausalLM", dict(cfg, layer_types=["full_attention"], full_attention_interval=2), 2)
+    assert "model.layers.1.self_attn.q_proj.weight" in p and "model.layers.0.linear_attn.dt_bias" in p
+    # shards of a stacked expert tensor and of a row-split weight
+    w = torch.arange(8 * 3 * 2, dtype=torch.float32).reshape(8, 3, 2)
+    assert P.shard_weight(w, P.ShardingDirective("expert_sharded", 0, 8), 1, 4).shape == (2, 3, 2)
+    m = torch.arange(12.0).reshape(3, 4)
+    assert torch.equal(P.shard_weight(m, P.ShardingDirective("sharded_to_all", 1), 1, 2), m[:, 2:])
