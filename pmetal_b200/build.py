@@ -45,9 +45,62 @@ def _run(cmd, log):
         raise RuntimeError("build failed:\n" + " ".join(cmd) + "\n" + r.stdout)
 
 
+ABI_HEADER_TOP = '''// C interface of libpmetal_b200.so: every launcher of the sm_100a kernel library.
+//
+// All functions take raw device pointers and a CUDA stream, allocate nothing unless their comment says so, and return
+// 0 on success, a negative value for an argument or descriptor error, or the CUDA error code of the launch. `status`
+// arguments point at a device int that a kernel sets when one of its bounded waits runs out (codes 101-109); the
+// caller reads it after synchronising the stream. Pointers and the stream must belong to the current device.
+// The no-allocation paged-attention entry point is declared in paged_attn_static.h.
+//
+// This file is written by pmetal_b200/build.py from the definitions in csrc/*.cu; every source includes it, so a
+// declaration that drifts from its definition fails to compile.
+#pragma once
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+'''
+
+
+def write_abi_header() -> str:
+    """Collect every ``extern "C" ... pm_*`` definition (with the comment block above it) into csrc/pmetal_b200.h."""
+    import re
+    decls = []
+    for src in sorted(glob.glob(os.path.join(CSRC, "*.cu"))):
+        with open(src, "r", encoding="utf-8") as fh:
+            text = fh.read()
+        for m in re.finditer(r'((?:^//[^\n]*\n)*)^extern "C" ([\w \*]+?)\b(pm_\w+)\(([^{;]*?)\)\s*\{', text, re.M | re.S):
+            decls.append((os.path.basename(src), m.group(1), m.group(2).strip(), m.group(3), " ".join(m.group(4).split())))
+    out, cur = ABI_HEADER_TOP, None
+    for fname, comment, ret, name, args in decls:
+        if name == "pm_paged_attn_static":
+            continue
+        if fname != cur:
+            out += f"\n// ---------------------------------------------------------------- {fname}\n"
+            cur = fname
+        out += comment
+        line, piece = "", ""
+        for tok in f"{ret} {name}({args});".split(" "):
+            if len(piece) + len(tok) + 1 > 116:
+                line += piece.rstrip() + "\n"
+                piece = "    "
+            piece += tok + " "
+        out += line + piece.rstrip() + "\n"
+    out += "\n#ifdef __cplusplus\n}\n#endif\n"
+    path = os.path.join(CSRC, "pmetal_b200.h")
+    old = open(path, "r", encoding="utf-8").read() if os.path.exists(path) else None
+    if old != out:
+        with open(path, "w", encoding="utf-8") as fh:
+            fh.write(out)
+    return path
+
+
 def build_native(force: bool = False, verbose: bool = False) -> dict:
     os.makedirs(OBJDIR, exist_ok=True)
     log = []
+    write_abi_header()
     headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + \
         glob.glob(os.path.join(CSRC, "host", "*.h"))
     out = {}

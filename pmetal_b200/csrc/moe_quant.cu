@@ -129,6 +129,111 @@ __global__ void __launch_bounds__(1024) moe_route_small_kernel(const __nv_bfloat
   }
 }
 
+// Replicated-token expert parallelism (every rank sees every token, each rank applies its own experts and the partial
+// outputs are summed across ranks): routing for all E experts, then the padded expert-sorted layout of the assignments
+// that fall on this rank's experts [e0, e0 + e_loc). One CTA; T * k <= 4096.
+//   off[e_loc + 1]  row offsets of the local experts' slabs, each padded to a multiple of `align`
+//   dest[T * k]     row of assignment i in the padded buffer, -1 when its expert lives on another rank
+//   src[cap]        assignment index of every row of the padded buffer, -1 for padding (rows >= off[e_loc] untouched)
+constexpr int kRouteLocalMax = 4096;
+__global__ void __launch_bounds__(1024) moe_route_local_kernel(const __nv_bfloat16* __restrict__ logits_bf16,
+                                                               const float* __restrict__ logits_f32, int T, int E, int k,
+                                                               int renorm, int e0, int e_loc, int align,
+                                                               int* __restrict__ topk_idx, float* __restrict__ topk_w,
+                                                               int* __restrict__ off, int* __restrict__ dest,
+                                                               int* __restrict__ src) {
+  __shared__ int s_idx[kRouteLocalMax];
+  __shared__ int s_off[1024 + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = T * k;
+  for (int t = warp; t < T; t += 32) moe_route_token(logits_bf16, logits_f32, t, E, k, renorm, topk_idx, topk_w, lane);
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s_idx[i] = topk_idx[i];
+  __syncthreads();
+  const int e = threadIdx.x;          // local expert index
+  int c = 0;
+  if (e < e_loc)
+    for (int i = 0; i < n; ++i) c += (s_idx[i] == e0 + e);
+  if (e < e_loc) s_off[e + 1] = (c + align - 1) / align * align;
+  if (e == 0) s_off[0] = 0;
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int j = 1; j <= e_loc; ++j) s_off[j] += s_off[j - 1];
+  __syncthreads();
+  if (e <= e_loc) off[e] = s_off[e];
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int x = s_idx[i];
+    if (x < e0 || x >= e0 + e_loc) dest[i] = -1;
+  }
+  if (e < e_loc) {
+    int pos = s_off[e];
+    for (int i = 0; i < n; ++i)
+      if (s_idx[i] == e0 + e) {
+        dest[i] = pos;
+        src[pos] = i;
+        ++pos;
+      }
+    for (; pos < s_off[e + 1]; ++pos) src[pos] = -1;
+  }
+}
+
+// xs[row] = x[src[row] / k] for the rows of the local experts' slabs (zeros for padding rows)
+__global__ void moe_gather_padded_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src,
+                                         const int* __restrict__ off_end, int k, __nv_bfloat16* __restrict__ xs, int H) {
+  const int rows = *off_end;
+  const int per = H / 8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < static_cast<long long>(rows) * per;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(i / per), c = static_cast<int>(i - static_cast<long long>(row) * per);
+    const int a = src[row];
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (a >= 0) v = *reinterpret_cast<const uint4*>(x + static_cast<long long>(a / k) * H + c * 8);
+    *reinterpret_cast<uint4*>(xs + static_cast<long long>(row) * H + c * 8) = v;
+  }
+}
+
+// y[t] = (residual[t]) + sum over the token's local assignments of w[t, slot] * z[dest[t * k + slot]]
+__global__ void moe_combine_local_kernel(const __nv_bfloat16* __restrict__ z, const int* __restrict__ dest,
+                                         const float* __restrict__ w, int k, const __nv_bfloat16* __restrict__ residual,
+                                         __nv_bfloat16* __restrict__ y, long long T, int H) {
+  const int per = H / 8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < T * per;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / per;
+    const int c = static_cast<int>(i - t * per) * 8;
+    float acc[8];
+    if (residual) {
+      const uint4 rv = *reinterpret_cast<const uint4*>(residual + t * H + c);
+      const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] = __uint_as_float(rw[e] << 16);
+        acc[2 * e + 1] = __uint_as_float(rw[e] & 0xffff0000u);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    }
+    for (int s = 0; s < k; ++s) {
+      const int d = dest[t * k + s];
+      if (d < 0) continue;
+      const float ws = w[t * k + s];
+      const uint4 zv = *reinterpret_cast<const uint4*>(z + static_cast<long long>(d) * H + c);
+      const uint32_t zw[4] = {zv.x, zv.y, zv.z, zv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] += ws * __uint_as_float(zw[e] << 16);
+        acc[2 * e + 1] += ws * __uint_as_float(zw[e] & 0xffff0000u);
+      }
+    }
+    uint4 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(acc[0], acc[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(acc[2], acc[3]);
+    *reinterpret_cast<__nv_bfloat162*>(&o.z) = __floats2bfloat162_rn(acc[4], acc[5]);
+    *reinterpret_cast<__nv_bfloat162*>(&o.w) = __floats2bfloat162_rn(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(y + t * H + c) = o;
+  }
+}
+
 __global__ void moe_count_kernel(const int* __restrict__ topk_idx, long long n, int* __restrict__ counts) {
   const int e = blockIdx.x;
   int c = 0;
@@ -381,6 +486,40 @@ extern "C" int pm_moe_route2(const void* logits, int is_f32, int T, int E, int k
 extern "C" int pm_moe_route(const void* logits, int is_f32, int T, int E, int k, int renorm, int* topk_idx,
                             float* topk_w, int* counts, int* offsets, int* perm, int* inv, cudaStream_t st) {
   return pm_moe_route2(logits, is_f32, T, E, k, renorm, topk_idx, topk_w, counts, offsets, nullptr, perm, inv, st);
+}
+
+// Routing plus the padded layout of the assignments that belong to experts [e0, e0 + e_loc) (see the kernel).
+extern "C" int pm_moe_route_local(const void* logits, int is_f32, int T, int E, int k, int renorm, int e0, int e_loc,
+                                  int align, int* topk_idx, float* topk_w, int* off, int* dest, int* src,
+                                  cudaStream_t st) {
+  if (T <= 0 || E <= 0 || E > 1024 || k <= 0 || k > 16 || k > E || e_loc < 1 || e_loc > 1024 || e0 < 0 ||
+      e0 + e_loc > E || align < 1)
+    return -1;
+  if (static_cast<long long>(T) * k > kRouteLocalMax) return -2;
+  moe_route_local_kernel<<<1, 1024, 0, st>>>(is_f32 ? nullptr : static_cast<const __nv_bfloat16*>(logits),
+                                             is_f32 ? static_cast<const float*>(logits) : nullptr, T, E, k, renorm, e0,
+                                             e_loc, align, topk_idx, topk_w, off, dest, src);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// off_end points at the device int holding the number of rows in use (off[e_loc]); cap bounds the launch.
+extern "C" int pm_moe_gather_padded(const void* x, const int* src, const int* off_end, int k, void* xs, int cap, int H,
+                                    cudaStream_t st) {
+  if (H % 8) return -1;
+  if (cap <= 0) return 0;
+  moe_gather_padded_kernel<<<grid_cap(static_cast<long long>(cap) * (H / 8), 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), src, off_end, k, static_cast<__nv_bfloat16*>(xs), H);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int pm_moe_combine_local(const void* z, const int* dest, const float* w, int k, const void* residual, void* y,
+                                    long long T, int H, cudaStream_t st) {
+  if (H % 8) return -1;
+  if (T <= 0) return 0;
+  moe_combine_local_kernel<<<grid_cap(T * (H / 8), 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(z), dest, w, k, static_cast<const __nv_bfloat16*>(residual),
+      static_cast<__nv_bfloat16*>(y), T, H);
+  return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int pm_moe_gather(const void* x, const int* perm, int k, void* out, long long n, int H, cudaStream_t st) {

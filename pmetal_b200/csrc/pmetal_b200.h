@@ -5,6 +5,9 @@
 // arguments point at a device int that a kernel sets when one of its bounded waits runs out (codes 101-109); the
 // caller reads it after synchronising the stream. Pointers and the stream must belong to the current device.
 // The no-allocation paged-attention entry point is declared in paged_attn_static.h.
+//
+// This file is written by pmetal_b200/build.py from the definitions in csrc/*.cu; every source includes it, so a
+// declaration that drifts from its definition fails to compile.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -167,6 +170,14 @@ int pm_moe_route2(const void* logits, int is_f32, int T, int E, int k, int renor
     int* counts, int* offsets, int* offsets2, int* perm, int* inv, cudaStream_t st);
 int pm_moe_route(const void* logits, int is_f32, int T, int E, int k, int renorm, int* topk_idx, float* topk_w,
     int* counts, int* offsets, int* perm, int* inv, cudaStream_t st);
+// Routing plus the padded layout of the assignments that belong to experts [e0, e0 + e_loc) (see the kernel).
+int pm_moe_route_local(const void* logits, int is_f32, int T, int E, int k, int renorm, int e0, int e_loc, int
+    align, int* topk_idx, float* topk_w, int* off, int* dest, int* src, cudaStream_t st);
+// off_end points at the device int holding the number of rows in use (off[e_loc]); cap bounds the launch.
+int pm_moe_gather_padded(const void* x, const int* src, const int* off_end, int k, void* xs, int cap, int H,
+    cudaStream_t st);
+int pm_moe_combine_local(const void* z, const int* dest, const float* w, int k, const void* residual, void* y, long
+    long T, int H, cudaStream_t st);
 int pm_moe_gather(const void* x, const int* perm, int k, void* out, long long n, int H, cudaStream_t st);
 int pm_moe_combine2(const void* z, const int* inv, const float* w, int k, const void* residual, void* y, long long
     T, int H, cudaStream_t st);
@@ -195,6 +206,10 @@ int pm_count_tokens(int* counts, const int* count_rows, const int* tokens, int r
 int pm_tp_gemm(int mode, const unsigned long long* x_ptrs, int ldx, const void* w, int ldw, void* out, int ldd,
     const unsigned long long* stage_ptrs, const unsigned long long* pad_ptrs, int rank, int world, int M, int N,
     int K, void* gathered, void* blk_ready, double timeout_s, int max_ctas, int* status, cudaStream_t stream);
+// x: bf16 [n] (n a multiple of 8, at most slot_elems), summed in place over the ranks. bufs[r] / pads[r]: rank r's
+// exchange buffer (2 * world * slot_elems bf16) and signal pad (64 uint32, zero-initialised once), peer-mapped.
+int pm_peer_allreduce(void* x, long long n, const unsigned long long* bufs, const unsigned long long* pads, long
+    long slot_elems, int rank, int world, double timeout_s, int* status, cudaStream_t st);
 
 // ---------------------------------------------------------------- train_aux.cu
 int pm_kd_fwd_bwd(void* student, long long ld, const void* teacher, long long ldt, int rows, int V, float

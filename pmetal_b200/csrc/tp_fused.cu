@@ -438,6 +438,97 @@ tp_gemm_kernel(const __grid_constant__ TpMaps maps, const TpParams p) {
   }
 }
 
+
+// ------------------------------------------------------------------------------------------ small all-reduce
+// Sum of a bf16 vector over the ranks in one launch per rank, over peer memory: every rank stores its vector into slot
+// `rank` of every peer's exchange buffer, the last of its CTAs to finish storing raises a flag on every peer, every CTA
+// then waits (bounded) until all ranks' flags for this epoch have arrived in its own pad and sums the `world` slots
+// of its share of the vector in fp32. The exchange buffer has two halves used by alternate epochs, so a rank that has
+// moved on to the next call cannot overwrite slots a slower peer still reads; the epoch lives in the pad (advanced
+// by the last CTA to finish), which keeps the launch replayable from a CUDA graph.
+constexpr int kArFlag = 0;       // [2][8] epoch of the data in slot [half][src]
+constexpr int kArEpoch = 16;     // local epoch counter
+constexpr int kArStored = 17;    // CTAs of this launch that have finished their stores
+constexpr int kArDone = 18;      // CTAs of this launch that have finished
+constexpr int kStatusArPeer = 108;
+
+struct ArParams {
+  __nv_bfloat16* x;
+  long long n;
+  __nv_bfloat16* bufs[kTpMaxRanks];
+  uint32_t* pads[kTpMaxRanks];
+  long long slot_elems;
+  int rank, world;
+  unsigned long long timeout_ns;
+  int* status;
+};
+
+__global__ void __launch_bounds__(256) peer_allreduce_kernel(const ArParams p) {
+  __shared__ int s_fail;
+  uint32_t* my_pad = p.pads[p.rank];
+  const uint32_t epoch = my_pad[kArEpoch] + 1u;
+  const int half = static_cast<int>(epoch & 1u);
+  if (threadIdx.x == 0) s_fail = 0;
+  const long long n8 = p.n / 8;
+  const long long per = (n8 + gridDim.x - 1) / gridDim.x;
+  const long long lo = blockIdx.x * per, hi = min(n8, lo + per);
+  // ---- scatter this CTA's share of the local vector into slot `rank` of every rank's buffer
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p.x + i * 8);
+    for (int r = 0; r < p.world; ++r) {
+      const int dst = (p.rank + r) % p.world;      // start with the own buffer, then walk the ring
+      __nv_bfloat16* slot = p.bufs[dst] + (static_cast<long long>(half) * p.world + p.rank) * p.slot_elems;
+      *reinterpret_cast<uint4*>(slot + i * 8) = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(my_pad + kArStored, 1u);
+    if (prev == gridDim.x - 1) {           // all of this rank's stores are out: tell every rank
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r) tp_st_release(p.pads[r] + kArFlag + half * 8 + p.rank, epoch);
+    }
+  }
+  // ---- wait for every rank's slot of this epoch
+  if (threadIdx.x < p.world) {
+    if (!tp_wait_flag(my_pad + kArFlag + half * 8 + threadIdx.x, epoch, p.timeout_ns, p.status)) s_fail = 1;
+  }
+  __syncthreads();
+  if (!s_fail) {
+    const __nv_bfloat16* mine = p.bufs[p.rank] + static_cast<long long>(half) * p.world * p.slot_elems;
+    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < p.world; ++r) {
+        const uint4 v = *reinterpret_cast<const uint4*>(mine + r * p.slot_elems + i * 8);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[2 * e] += __uint_as_float(w[e] << 16);
+          acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+        }
+      }
+      uint4 o;
+      *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(acc[0], acc[1]);
+      *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(acc[2], acc[3]);
+      *reinterpret_cast<__nv_bfloat162*>(&o.z) = __floats2bfloat162_rn(acc[4], acc[5]);
+      *reinterpret_cast<__nv_bfloat162*>(&o.w) = __floats2bfloat162_rn(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(p.x + i * 8) = o;
+    }
+  }
+  // ---- the last CTA to finish closes the epoch (also after an abandoned wait, so the pad stays consistent)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(my_pad + kArDone, 1u);
+    if (prev == gridDim.x - 1) {
+      my_pad[kArStored] = 0u;
+      my_pad[kArDone] = 0u;
+      my_pad[kArEpoch] = epoch;
+      __threadfence_system();
+    }
+  }
+}
+
 }  // namespace pm
 
 using namespace pm;
@@ -491,5 +582,30 @@ extern "C" int pm_tp_gemm(int mode, const unsigned long long* x_ptrs, int ldx, c
   const int cap = max_ctas > 0 ? max_ctas : num_sms();
   if (grid > cap) grid = cap;
   tp_gemm_kernel<<<grid, kTpThreads, smem, stream>>>(maps, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// x: bf16 [n] (n a multiple of 8, at most slot_elems), summed in place over the ranks. bufs[r] / pads[r]: rank r's
+// exchange buffer (2 * world * slot_elems bf16) and signal pad (64 uint32, zero-initialised once), peer-mapped.
+extern "C" int pm_peer_allreduce(void* x, long long n, const unsigned long long* bufs, const unsigned long long* pads,
+                                 long long slot_elems, int rank, int world, double timeout_s, int* status,
+                                 cudaStream_t st) {
+  if (world < 1 || world > kTpMaxRanks || rank < 0 || rank >= world) return -1;
+  if (n <= 0 || (n % 8) || n > slot_elems || (slot_elems % 8)) return -2;
+  ArParams p{};
+  p.x = static_cast<__nv_bfloat16*>(x);
+  p.n = n;
+  for (int r = 0; r < kTpMaxRanks; ++r) {
+    const int rr = r < world ? r : rank;
+    p.bufs[r] = reinterpret_cast<__nv_bfloat16*>(bufs[rr]);
+    p.pads[r] = reinterpret_cast<uint32_t*>(pads[rr]);
+  }
+  p.slot_elems = slot_elems; p.rank = rank; p.world = world;
+  p.timeout_ns = static_cast<unsigned long long>(timeout_s * 1e9);
+  p.status = status;
+  int grid = static_cast<int>((n / 8 + 2047) / 2048);     // about 8 x 16 bytes per thread
+  if (grid < 1) grid = 1;
+  if (grid > 32) grid = 32;                               // every CTA must be resident: they wait on each other's flag
+  peer_allreduce_kernel<<<grid, 256, 0, st>>>(p);
   return static_cast<int>(cudaGetLastError());
 }

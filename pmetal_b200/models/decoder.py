@@ -382,6 +382,9 @@ class DecoderLM(nn.Module):
             layers = ()
         for li, layer in enumerate(layers):
             at = layer.self_attn
+            if getattr(self, "tp_world", 1) > 1:
+                x = self._layer_paged_sharded(li, layer, x, rope, cache, meta, native)
+                continue
             if skinny and at.qkv_proj.gemv_ok(T) and at.o_proj.gemv_ok(T):
                 # decode: six launches per dense layer (norm+qkv, qk-norm+rope+cache append, attention, o+residual,
                 # norm+gate/up+SwiGLU, down+residual); mixture-of-experts layers share the attention half
@@ -426,6 +429,31 @@ class DecoderLM(nn.Module):
         x = ops.rms_norm(x, self.norm, cfg.rms_norm_eps)
         return x if return_hidden else self.logits(x)
 
+    def _layer_paged_sharded(self, li, layer, x, rope, cache, meta, native: bool):
+        """One layer of the cached forward on a model cut by ``parallel.tp_model.shard_for_serving``: this rank's
+        heads and experts (or feed-forward channels) on replicated activations; the two partial results are summed over
+        the ranks. The residual enters each sum once, through the epilogue of rank 0's projection."""
+        cfg = self.cfg
+        at = layer.self_attn
+        hq, hkv, d, eps = at.hq_local, at.hkv_local, cfg.head_dim, cfg.rms_norm_eps
+        T = x.shape[0]
+        first = self.tp_rank == 0
+        qkv = at.qkv_proj(ops.rms_norm(x, layer.input_layernorm, eps))
+        if native:
+            from ..ops import native as nat
+            q, k = nat.qknorm_rope_fwd(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps)
+            cache.append(li, k, qkv[:, (hq + hkv) * d:].view(T, hkv, d), meta.slots)
+            o = cache.attention(li, q, meta, d ** -0.5, at.window).view(T, hq * d)
+        else:
+            o = self._paged_attention_reference(qkv, at, rope, cache, meta, li, hq, hkv)
+        h = at.tp_reduce(at.o_proj(o, x if first else None))
+        n2 = ops.rms_norm(h, layer.post_attention_layernorm, eps)
+        if isinstance(layer.mlp, MLP):
+            y = layer.mlp.down_proj(ops.swiglu(layer.mlp.gate_up_proj(n2)), h if first else None)
+            return layer.mlp.tp_reduce(y)
+        from ..parallel.tp_model import moe_local_forward
+        return moe_local_forward(layer.mlp, n2, h)
+
     def _mega_ok(self, T: int) -> bool:
         """The whole-step kernel covers dense layers with plain bf16 weights: no adapters, biases, sliding windows or
         soft-capping."""
@@ -433,7 +461,7 @@ class DecoderLM(nn.Module):
             self._mega_scratch = {}
             self._mega_tables = {}
         cfg = self.cfg
-        ok = cfg.attn_logit_softcap <= 0 and cfg.head_dim == 128
+        ok = cfg.attn_logit_softcap <= 0 and cfg.head_dim == 128 and getattr(self, "tp_world", 1) == 1
         if ok:            # checked on every call: adapters or packed weights may have been attached since the last one
             for layer in self.layers:
                 at = layer.self_attn
@@ -477,10 +505,12 @@ class DecoderLM(nn.Module):
         self._mega_tables[id(cache)] = (weakref.ref(cache), t, sig)
         return t
 
-    def _paged_attention_reference(self, qkv, at, rope, cache, meta, li):
+    def _paged_attention_reference(self, qkv, at, rope, cache, meta, li, hq=None, hkv=None):
         from ..ops import reference as ref
         cfg = self.cfg
-        hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        d = cfg.head_dim
+        hq = hq if hq is not None else cfg.num_attention_heads
+        hkv = hkv if hkv is not None else cfg.num_key_value_heads
         T = qkv.shape[0]
         q = qkv[:, :hq * d].view(T, hq, d)
         k = qkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d)
@@ -513,8 +543,9 @@ class DecoderLM(nn.Module):
     def new_cache(self, num_blocks: int, dtype=None, device=None, quant=None, window: int = 0, sink: int = 0):
         from .kv_cache import PagedKVCache
         p = self.embed_tokens
-        return PagedKVCache(self.cfg.num_hidden_layers, self.cfg.num_key_value_heads, self.cfg.head_dim, num_blocks,
-                            dtype or p.dtype, device or p.device, quant=quant, window=window, sink=sink)
+        return PagedKVCache(self.cfg.num_hidden_layers, getattr(self, "kv_heads_local", self.cfg.num_key_value_heads),
+                            self.cfg.head_dim, num_blocks, dtype or p.dtype, device or p.device, quant=quant,
+                            window=window, sink=sink)
 
     # ------------------------------------------------------------------ checkpoint name mapping
     def hf_state_dict(self, merged: bool = False) -> Dict[str, torch.Tensor]:

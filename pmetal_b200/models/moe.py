@@ -48,6 +48,9 @@ class SparseMoeBlock(nn.Module):
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         cfg = self.cfg
+        if getattr(self, "tp_reduce", None) is not None and self.local_experts is not None:
+            from ..parallel.tp_model import moe_local_forward
+            return moe_local_forward(self, x, residual)      # replicated tokens, this rank's experts, summed over ranks
         logits = F.linear(x, self.router)
         eng = getattr(self, "ep_engine", None)
         if eng is not None and x.is_cuda and not torch.is_grad_enabled() and x.shape[0] * eng.k <= eng.max_rows:

@@ -100,10 +100,10 @@ class SpeculativeDecoder:
     """Two-model speculative decoding over a batch of sequences (greedy or sampling verification)."""
 
     def __init__(self, target, draft, cfg: Optional[SpeculativeConfig] = None, target_blocks: int = 4096,
-                 draft_blocks: int = 4096):
+                 draft_blocks: int = 4096, cuda_graphs: Optional[bool] = None):
         self.cfg = cfg or SpeculativeConfig()
-        self.t = Generator(target, num_blocks=target_blocks)
-        self.d = Generator(draft, num_blocks=draft_blocks)
+        self.t = Generator(target, num_blocks=target_blocks, cuda_graphs=cuda_graphs)
+        self.d = Generator(draft, num_blocks=draft_blocks, cuda_graphs=cuda_graphs)
         self.stats = SpecStats()
 
     @torch.no_grad()
@@ -141,7 +141,12 @@ class SpeculativeDecoder:
             meta = self.t.cache.prepare([ts[i] for i in live], [k + 1] * len(live))
             tl = self.t.model.forward_paged(ver_in, self.t.cache, meta, all_logits=True).view(len(live), k + 1, -1)
             if greedy:
-                n_acc, new = verify_greedy(tl, draft)
+                from ..ops import functional as _ops
+                if _ops.native_enabled(tl):          # accept / correct / bonus decided on the device (csrc/sampling.cu)
+                    from ..ops import native as _nat
+                    n_acc, new = _nat.spec_verify(tl.float().contiguous(), None, draft.to(torch.int32), 0.0)
+                else:
+                    n_acc, new = verify_greedy(tl, draft)
             else:
                 n_acc, new = verify_sampling(tl, draft, torch.stack(dprobs, 1), cfg.temperature)
             n_l, new_l, dr_l = n_acc.tolist(), new.tolist(), draft.tolist()

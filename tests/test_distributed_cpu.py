@@ -286,6 +286,16 @@ def test_every_rank_resumes_and_sharded_moments_are_collected(tmp_path):
     assert r.returncode == 0 and r.stdout.count("DP_RESUME_WORKER_OK") == 2, r.stdout[-3000:]
 
 
+def test_tensor_and_expert_parallel_serving_slices_over_gloo():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29743", os.path.join(root, "tests", "workers", "tp_serve_worker.py")]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=240)
+    assert r.returncode == 0 and r.stdout.count("TP_SERVE_WORKER_OK") == 2, r.stdout[-3000:]
+
+
 def test_activation_message_wire_format():
     import struct
 

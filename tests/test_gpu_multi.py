@@ -43,3 +43,10 @@ def test_fused_ring_attention():
     n = 4 if torch.cuda.device_count() >= 4 else 2
     r = _run("cp_worker.py", n, port=29547)
     assert r.returncode == 0 and "CP_WORKER_OK" in r.stdout, r.stdout[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_tensor_and_expert_parallel_serving_slices():
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    r = _run("tp_serve_gpu_worker.py", n, port=29549)
+    assert r.returncode == 0 and "TP_SERVE_GPU_WORKER_OK" in r.stdout, r.stdout[-4000:]
