@@ -705,6 +705,10 @@ def _serve_args(sp):
     p.add_argument("--max-seq-len", type=int, default=None, help="sizes the KV pool: slots x ceil(len / 64) blocks")
     p.add_argument("--fp8", action="store_true")
     p.add_argument("--device")
+    p.add_argument("--tp", type=int, default=1, help="cut attention heads (and dense feed-forward channels) over N GPUs")
+    p.add_argument("--ep", type=int, default=0, help="cut experts over N GPUs (the same ranks as --tp; default: = --tp)")
+    p.add_argument("--reduce", choices=["peer", "nccl"], default="peer",
+                   help="sum of the partial layer outputs: one kernel over symmetric memory, or NCCL")
     _add_kv_quant_flags(p)
     return p
 
@@ -715,12 +719,54 @@ def cmd_serve(a) -> int:
     if a.cb_block_size != 64:
         print("error: the paged attention kernels use 64-token blocks (--cb-block-size 64)", file=sys.stderr)
         return 2
+    ways = max(a.tp, a.ep or a.tp)
+    if a.ep and a.tp > 1 and a.ep != a.tp:
+        print("error: heads and experts are cut over the same ranks (--ep must equal --tp)", file=sys.stderr)
+        return 2
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if ways > 1 and world == 1:
+        # one process per GPU: start this same command under the launcher
+        from ..parallel.cluster_cli import _torchrun
+        return _torchrun(ways, ["-m", "pmetal_b200.cli.main"] + sys.argv[1:])
+    channel = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        if torch.cuda.is_available():
+            torch.cuda.set_device(local)
+            a.device = f"cuda:{local}"
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group("gloo")
     model, tok, tpl, eos, mdir = _load_for_inference(a)
     blocks = a.kv_blocks
     if a.max_seq_len:
         blocks = max(blocks, a.max_slots * (-(-a.max_seq_len // 64) + 1))
-    serve(model, tok, tpl, a.host, a.port, eos, os.path.basename(os.path.normpath(mdir or a.model)), a.max_slots, blocks,
-          a.cb_max_queue_depth, cache_options=_paged_cache_options(a, model, blocks))
+    opts = _paged_cache_options(a, model, blocks)
+    if world > 1:
+        from ..parallel.dp import shutdown_process_group
+        from ..parallel.tp_model import AllReduce, PeerAllReduce, shard_for_serving
+        from ..serve.replica import StepChannel, follow
+        red = PeerAllReduce(None) if (a.reduce == "peer" and a.device.startswith("cuda")) else AllReduce(None)
+        shard_for_serving(model, None, red)
+        channel = model.step_channel = StepChannel(StepChannel.control_group())
+        if not channel.leader:
+            cache = model.new_cache(blocks, **(opts or {}))
+            try:
+                steps = follow(model, cache, channel)
+                logging.getLogger("pmetal").info("rank %d replayed %d steps", dist.get_rank(), steps)
+            except KeyboardInterrupt:          # an interrupt of the whole process group ends the followers too
+                return 0
+            shutdown_process_group()
+            return 0
+    try:
+        serve(model, tok, tpl, a.host, a.port, eos, os.path.basename(os.path.normpath(mdir or a.model)), a.max_slots,
+              blocks, a.cb_max_queue_depth, cache_options=opts, channel=channel)
+    finally:
+        if world > 1:
+            from ..parallel.dp import shutdown_process_group
+            shutdown_process_group()
     return 0
 
 

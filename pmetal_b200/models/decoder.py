@@ -359,6 +359,9 @@ class DecoderLM(nn.Module):
         attention reads the block table directly. Returns logits for the last new token of every sequence
         ([n_seq, V]) or for every new token ([total_q, V], speculative verification)."""
         cfg = self.cfg
+        ch = getattr(self, "step_channel", None)
+        if ch is not None and ch.leader and not ch.muted:
+            ch.publish_paged(input_ids, meta, all_logits, return_hidden)      # the other ranks repeat this call
         hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         x = F.embedding(input_ids, self.embed_tokens)
         native = ops.use_native(x) and d == 128
@@ -438,15 +441,31 @@ class DecoderLM(nn.Module):
         hq, hkv, d, eps = at.hq_local, at.hkv_local, cfg.head_dim, cfg.rms_norm_eps
         T = x.shape[0]
         first = self.tp_rank == 0
-        qkv = at.qkv_proj(ops.rms_norm(x, layer.input_layernorm, eps))
-        if native:
+        if native and T <= GEMV_MAX_ROWS and at.qkv_proj.gemv_ok(T) and at.o_proj.gemv_ok(T):
+            # a handful of rows: the mat-vec kernels with the norm, the cache append and the residual fused in
             from ..ops import native as nat
-            q, k = nat.qknorm_rope_fwd(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps)
-            cache.append(li, k, qkv[:, (hq + hkv) * d:].view(T, hkv, d), meta.slots)
+            qkv = at.qkv_proj.gemv_forward(x, layer.input_layernorm, eps)
+            if cache.quant is None:
+                q = nat.qknorm_rope_cache(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps, cache.k[li],
+                                          cache.v[li], meta.slots)
+            else:
+                q, k = nat.qknorm_rope_fwd(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps)
+                cache.append(li, k, qkv[:, (hq + hkv) * d:].view(T, hkv, d), meta.slots)
             o = cache.attention(li, q, meta, d ** -0.5, at.window).view(T, hq * d)
+            h = at.tp_reduce(at.o_proj.gemv_forward(o, residual=x if first else None))
+            if isinstance(layer.mlp, MLP) and layer.mlp.gate_up_proj.gemv_ok(T) and layer.mlp.down_proj.gemv_ok(T):
+                act = layer.mlp.gate_up_proj.gemv_forward(h, layer.post_attention_layernorm, eps, swiglu=True)
+                return layer.mlp.tp_reduce(layer.mlp.down_proj.gemv_forward(act, residual=h if first else None))
         else:
-            o = self._paged_attention_reference(qkv, at, rope, cache, meta, li, hq, hkv)
-        h = at.tp_reduce(at.o_proj(o, x if first else None))
+            qkv = at.qkv_proj(ops.rms_norm(x, layer.input_layernorm, eps))
+            if native:
+                from ..ops import native as nat
+                q, k = nat.qknorm_rope_fwd(qkv, at.q_norm, at.k_norm, rope[0], rope[1], hq, hkv, eps)
+                cache.append(li, k, qkv[:, (hq + hkv) * d:].view(T, hkv, d), meta.slots)
+                o = cache.attention(li, q, meta, d ** -0.5, at.window).view(T, hq * d)
+            else:
+                o = self._paged_attention_reference(qkv, at, rope, cache, meta, li, hq, hkv)
+            h = at.tp_reduce(at.o_proj(o, x if first else None))
         n2 = ops.rms_norm(h, layer.post_attention_layernorm, eps)
         if isinstance(layer.mlp, MLP):
             y = layer.mlp.down_proj(ops.swiglu(layer.mlp.gate_up_proj(n2)), h if first else None)
@@ -522,10 +541,11 @@ class DecoderLM(nn.Module):
         win = min(w for w in (at.window, cache.window) if w > 0) if (at.window > 0 or cache.window > 0) else 0
         sink = cache.sink if cache.window > 0 else 0
         out = torch.empty(T, hq, d, dtype=qkv.dtype, device=qkv.device)
-        qs, ql = meta.q_start.tolist(), meta.q_lens.tolist()
+        qs, ql, sl = meta.q_start.tolist(), meta.q_lens.tolist(), meta.seq_lens.tolist()
         rep = hq // hkv
-        for i, sid in enumerate(meta.seq_ids):
-            K, V = cache.gather(li, sid)
+        for i in range(len(ql)):
+            K, V = cache.gather_blocks(li, meta.block_table[i], sl[i])      # from the metadata alone: ranks that follow
+            # another rank's scheduler hold no per-sequence state
             L, n = K.shape[0], ql[i]
             qq = q[qs[i]:qs[i] + n].transpose(0, 1).float()
             kk = K.transpose(0, 1).float().repeat_interleave(rep, 0)

@@ -63,9 +63,13 @@ class GraphedDecoder:
 
     PAD_SEQ = -(1 << 40)
 
-    def __init__(self, model, cache: PagedKVCache):
+    def __init__(self, model, cache: PagedKVCache, pad_block: Optional[int] = None):
         self.model, self.cache, self.device = model, cache, cache.device
         self.graphs = {}
+        self.channel = getattr(model, "step_channel", None)
+        if pad_block is not None:           # a rank that follows another rank's scheduler uses that rank's scratch block
+            self.pad_block = pad_block
+            return
         if self.PAD_SEQ not in cache.seqs:
             cache.add_sequence(self.PAD_SEQ)
             cache.reserve(self.PAD_SEQ, 1)
@@ -76,6 +80,19 @@ class GraphedDecoder:
         st = self.graphs.get(key)
         if st is not None:
             return st
+        ch = self.channel
+        if ch is not None:
+            if ch.leader:           # the other ranks warm up and capture the same graph now: its collectives pair up
+                from ..serve.replica import KIND_CAPTURE
+                ch.publish(KIND_CAPTURE, [nb, mb, 0, self.pad_block])
+            ch.muted += 1
+        try:
+            return self._capture(key, nb, mb)
+        finally:
+            if ch is not None:
+                ch.muted -= 1
+
+    def _capture(self, key, nb: int, mb: int):
         dev = self.device
         st = {
             "h64": torch.zeros(2 * nb, dtype=torch.int64).pin_memory(),              # slots | tokens
@@ -159,6 +176,8 @@ class GraphedDecoder:
         st = self._state(nb, mb)
         toks = tokens.tolist() if isinstance(tokens, torch.Tensor) else list(tokens)
         self._fill(st, nb, mb, slots, pos, lens, tables, toks)
+        if self.channel is not None and self.channel.leader:
+            self.channel.publish_graph(nb, mb, n, self.pad_block, st["h64"], st["h32"])
         self._copy(st)
         st["graph"].replay()
         return st["logits"][:n].clone()      # the static buffer is overwritten by the next replay

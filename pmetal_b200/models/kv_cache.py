@@ -44,6 +44,7 @@ class BatchMeta:
     total_q: int = 0
     max_q: int = 1
     max_kv: int = 0
+    host: Optional[tuple] = None    # host copies (slots, positions, seq_lens, q_start, q_lens, block table) when known
 
 
 GROUP = 64      # channels per quantisation scale of the int8 cache
@@ -218,7 +219,7 @@ class PagedKVCache:
             return torch.tensor(x, dtype=dt).to(dev, non_blocking=True)
         return BatchMeta(list(seq_ids), bt.to(dev, non_blocking=True), t(seq_lens, torch.int32), t(q_start, torch.int32),
                          t(q_lens, torch.int32), t(slots, torch.int64), t(pos, torch.int32), len(slots),
-                         max(q_lens), max(seq_lens))
+                         max(q_lens), max(seq_lens), host=(slots, pos, seq_lens, q_start, q_lens, bt))
 
     def _evict_outside_window(self, seq_id: int, first_query_pos: int) -> None:
         """Give back the blocks that no query at or after ``first_query_pos`` can see: blocks that end before
@@ -274,11 +275,16 @@ class PagedKVCache:
         """Dense [length, hkv, d] keys and values of a sequence (recycled blocks read as zeros; they are masked)."""
         st = self.seqs[seq_id]
         idx = torch.tensor([max(b, 0) for b in st.blocks], dtype=torch.int64, device=self.device)
+        return self.gather_blocks(layer, idx, st.length)
+
+    def gather_blocks(self, layer: int, idx: torch.Tensor, length: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Dense [length, hkv, d] keys and values behind a row of a block table (``idx`` int64, one entry per block)."""
+        idx = idx[:(length + BLOCK - 1) // BLOCK].long()
         out = []
         for cache, scales in ((self.k[layer], self.k_scale), (self.v[layer], self.v_scale)):
             x = cache[idx]
             if self.quant == "int8":
                 sc = scales[layer][idx]
                 x = (x.float().reshape(*x.shape[:-1], -1, GROUP) * sc[..., None]).reshape(x.shape).to(self.compute_dtype)
-            out.append(x.reshape(-1, self.hkv, self.d)[:st.length])
+            out.append(x.reshape(-1, self.hkv, self.d)[:length])
         return out[0], out[1]

@@ -21,7 +21,10 @@ NVLINK_COPY_GBS = 770.0        # measured peer copy bandwidth per direction per 
 def _torchrun(n: int, module_args, port: int = 29611) -> int:
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(port)] + module_args
-    return subprocess.call(cmd)
+    try:
+        return subprocess.call(cmd)
+    except KeyboardInterrupt:                  # the interrupt reached the workers as well; they wind down by themselves
+        return 130
 
 
 def run(a) -> int:

@@ -345,9 +345,11 @@ def create_app(state: ServerState):
 
 
 def serve(model, tokenizer, template=None, host: str = "127.0.0.1", port: int = 8080, eos_ids=(), model_name="pmetal-b200",
-          max_slots: int = 64, num_blocks: int = 8192, max_queue: int = 1024, cache_options: Optional[dict] = None):
+          max_slots: int = 64, num_blocks: int = 8192, max_queue: int = 1024, cache_options: Optional[dict] = None,
+          channel=None):
     """Blocking: starts the engine thread and the HTTP server. ``cache_options`` (quant / window / sink) go to
-    ``DecoderLM.new_cache``."""
+    ``DecoderLM.new_cache``. With a model cut over several ranks, ``channel`` (serve/replica.py) is the leader's end of
+    the step channel: the ranks that follow are released when the server stops."""
     import uvicorn
     engine = ContinuousBatchEngine(model, eos_ids, max_slots=max_slots, num_blocks=num_blocks, max_queue=max_queue,
                                    cache_options=cache_options)
@@ -356,3 +358,5 @@ def serve(model, tokenizer, template=None, host: str = "127.0.0.1", port: int = 
         uvicorn.run(create_app(ServerState(engine, tokenizer, template, model_name)), host=host, port=port, log_level="info")
     finally:
         engine.shutdown()
+        if channel is not None:
+            channel.stop()

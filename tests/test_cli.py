@@ -309,3 +309,45 @@ def test_cluster_flags_after_the_action_are_applied(monkeypatch):
     assert (seen["gpus"], seen["iters"]) == (4, 5)
     assert main(["cluster", "train", "--", "-m", "x", "--gpus", "2"]) == 0           # flags of the launched command stay
     assert seen["rest"] == ["--", "-m", "x", "--gpus", "2"] or seen["rest"] == ["-m", "x", "--gpus", "2"]
+
+
+def test_serve_over_two_ranks_answers_http(tmp_path):
+    """``serve --tp 2`` starts one process per rank; rank 0 answers HTTP while rank 1 repeats its model calls."""
+    import json
+    import signal
+    import subprocess
+    import sys
+    import time
+    import urllib.request
+    port = 18431
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.Popen([sys.executable, "-m", "pmetal_b200.cli.main", "serve", "-m", "random:tiny-qwen3-moe", "--tp", "2",
+                          "--device", "cpu", "--port", str(port), "--kv-blocks", "64", "--max-slots", "4"], cwd=root,
+                         start_new_session=True, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        up = False
+        for _ in range(240):
+            try:
+                urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1).read()
+                up = True
+                break
+            except Exception:
+                if p.poll() is not None:
+                    break
+                time.sleep(0.5)
+        assert up, "server did not come up"
+        outs = []
+        for _ in range(2):
+            req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions",
+                                         data=json.dumps({"prompt": "hello world", "max_tokens": 8, "temperature": 0}).encode(),
+                                         headers={"Content-Type": "application/json"})
+            outs.append(json.loads(urllib.request.urlopen(req, timeout=120).read()))
+        assert outs[0]["usage"]["completion_tokens"] == 8
+        assert outs[0]["choices"][0]["text"] == outs[1]["choices"][0]["text"]
+    finally:
+        os.killpg(p.pid, signal.SIGINT)
+        try:
+            p.communicate(timeout=60)
+        except subprocess.TimeoutExpired:
+            os.killpg(p.pid, signal.SIGKILL)
+            p.communicate()

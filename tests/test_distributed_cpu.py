@@ -296,6 +296,16 @@ def test_tensor_and_expert_parallel_serving_slices_over_gloo():
     assert r.returncode == 0 and r.stdout.count("TP_SERVE_WORKER_OK") == 2, r.stdout[-3000:]
 
 
+def test_sharded_engine_with_follower_ranks_over_gloo():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29747", os.path.join(root, "tests", "workers", "serve_replica_worker.py")]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=240)
+    assert r.returncode == 0 and r.stdout.count("SERVE_REPLICA_WORKER_OK") == 2, r.stdout[-3000:]
+
+
 def test_activation_message_wire_format():
     import struct
 

@@ -73,6 +73,32 @@ def main():
             print(f"block T={T}: median {rows.median().item():.4f} max {rows.max().item():.3f} rows over 2 %: {bad:.3f}",
                   flush=True)
         assert rows.median().item() < 0.01 and bad < 0.05, f"block T={T}"
+    # continuous batching over the cut model, decode steps replayed from graphs: every rank running its own scheduler in
+    # lock-step against rank 0 scheduling alone while the others repeat its steps from the published descriptors
+    from pmetal_b200.models.sampling import SamplingParams
+    from pmetal_b200.serve.engine import ContinuousBatchEngine, Request
+    from pmetal_b200.serve.replica import StepChannel, follow
+
+    def run_requests(engine):
+        reqs = [engine.submit(Request(list(p), SamplingParams.greedy(8 + i))) for i, p in enumerate(prompts[:5])]
+        for _ in range(4):
+            engine.tick()
+        reqs += [engine.submit(Request(list(p), SamplingParams.greedy(6))) for p in prompts[5:9]]
+        while not all(r.done.is_set() for r in reqs):
+            engine.tick()
+        return [r.output for r in reqs]
+    want = run_requests(ContinuousBatchEngine(cut, num_blocks=128, max_slots=8))
+    ch = cut.step_channel = StepChannel(StepChannel.control_group())
+    if ch.leader:
+        got = run_requests(ContinuousBatchEngine(cut, num_blocks=128, max_slots=8))
+        ch.stop()
+        assert got == want, (got, want)
+        print(f"engine with follower ranks: {len(got)} requests, {ch.published} step descriptors", flush=True)
+    else:
+        assert follow(cut, cut.new_cache(128), ch) > 10
+    cut.step_channel = None
+    torch.cuda.synchronize()
+    native.check_status()
     # the peer all-reduce by itself: sizes up to the slot size, many calls back to back (both buffer halves, epochs)
     for it in range(12):
         n = [8, 4096, 1 << 16, 520 * 8][it % 4]
