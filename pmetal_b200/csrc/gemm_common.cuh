@@ -20,6 +20,8 @@ struct GemmParams {
   int out_mode;    // 0: bf16 store, 1: f32 store, 2: f32 atomic add, 3: f32 atomic add, transposed,
                    // 4 / 5: as 2 / 3 with a plain read-add-write (one CTA owns each output tile: needs splits == 1;
                    // the sum is then formed in a fixed order, bit for bit the same on every run)
+                   // 6: bf16 store with split-K reduced inside the kernel (1-SM kernel): every split parks its fp32
+                   // partial tile in `ws`; the last one to arrive adds them in split order and runs the bf16 epilogue
   int ldd, ldr;
   int n_store;     // columns >= n_store are computed but not written
   float alpha;
@@ -33,6 +35,8 @@ struct GemmParams {
   int fwd_full;    // CTA-pair kernel: each CTA counts its own TMA bytes; the partner forwards one arrive per stage
   int commit_both; // CTA-pair kernel: signal both CTAs' barriers with one commit
   int* status;
+  float* ws;             // out_mode 6: [tiles][splits][128][bn] fp32 partial tiles
+  unsigned* ws_cnt;      // out_mode 6: [tiles][4] arrival counters, zero between launches
 };
 
 __device__ __forceinline__ int seg_of(const GemmParams& p, int x) {
@@ -45,7 +49,7 @@ __device__ __forceinline__ int seg_of(const GemmParams& p, int x) {
 
 // Write 32 consecutive accumulator columns of one output row (fp32 bits in r) according to out_mode.
 __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&r)[32], int row, int col0) {
-    if (p.out_mode == 0) {
+    if (p.out_mode == 0 || p.out_mode == 6) {
       __nv_bfloat16* drow = static_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.ldd;
       const __nv_bfloat16* rrow =
           p.R ? static_cast<const __nv_bfloat16*>(p.R) + static_cast<size_t>(row) * p.ldr : nullptr;

@@ -167,6 +167,59 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tc_fence_after();
       const int row = mb * kBM + q * 32 + lane;
       const bool row_ok = row < p.M;
+      if (p.out_mode == 6) {
+        // park this split's partial rows, then count the arrival of this warp's quarter of the tile; the warp that
+        // completes the count owns the reduction of that quarter
+        float* mine = p.ws + ((static_cast<size_t>(tile) * p.splits + split) * kBM + q * 32 + lane) * p.bn;
+        for (int c = 0; c < p.bn / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + buf * p.bn + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
+          tmem_ld_wait();
+          if (row_ok && nb * p.bn + c * 32 < p.n_store) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              __stcg(reinterpret_cast<float4*>(mine + c * 32) + v,
+                     make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]),
+                                 __uint_as_float(r[4 * v + 3])));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        ++acc_it;
+        __threadfence();
+        __syncwarp();
+        unsigned seen = 0;
+        if (lane == 0) seen = atomicAdd(p.ws_cnt + tile * 4 + q, 1u);
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+        if (seen != static_cast<unsigned>(p.splits - 1)) continue;
+        __threadfence();
+        if (row_ok) {
+          const float* base = p.ws + (static_cast<size_t>(tile) * p.splits * kBM + q * 32 + lane) * p.bn;
+          for (int c = 0; c < p.bn / 32; ++c) {
+            const int col0 = nb * p.bn + c * 32;
+            if (col0 >= p.n_store) break;
+            float acc[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+            for (int s2 = 0; s2 < p.splits; ++s2) {        // fixed order: the result does not depend on who came last
+              const float4* src = reinterpret_cast<const float4*>(base + static_cast<size_t>(s2) * kBM * p.bn + c * 32);
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                const float4 x = __ldcg(src + v);
+                acc[4 * v] += x.x; acc[4 * v + 1] += x.y; acc[4 * v + 2] += x.z; acc[4 * v + 3] += x.w;
+              }
+            }
+            uint32_t r[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(acc[e]);
+            epilogue_store_chunk(p, r, row, col0);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) p.ws_cnt[tile * 4 + q] = 0u;       // ready for the next launch on this stream
+        continue;
+      }
       for (int c = 0; c < p.bn / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_base + buf * p.bn + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
@@ -207,12 +260,21 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
                             const void* A2, int a2_mn, int lda2, int a2_k, const void* B2, int b2_mn, int ldb2,
                             int b2_rows, void* D, int out_mode, int ldd, const void* R, int ldr, int M, int N, int K,
                             int K2, int n_store, float alpha, int bn, int splits, int seg_mode, const int* seg_end,
-                            int seg_r, int max_ctas, int* status, cudaStream_t stream) {
+                            int seg_r, int max_ctas, float* ws, long long ws_floats, unsigned* ws_cnt,
+                            long long ws_cnt_len, int* status, cudaStream_t stream) {
   if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return -10;
   if ((b_mn || (K2 > 0 && b2_mn)) && (bn % 64)) return -11;
-  if (splits < 1 || (splits > 1 && (out_mode < 2 || out_mode > 3))) return -12;   // split-K needs the atomic modes
+  // split-K needs the atomic modes, or mode 6 with its workspace (every split must own at least one K block)
+  if (splits < 1 || (splits > 1 && out_mode != 2 && out_mode != 3 && out_mode != 6)) return -12;
+  if (out_mode == 6) {
+    const long long tiles = static_cast<long long>((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+    const int nk_all = (K + kBK - 1) / kBK + (K2 > 0 ? (K2 + kBK - 1) / kBK : 0);
+    const int per = (nk_all + splits - 1) / splits;
+    if (!ws || !ws_cnt || tiles * splits * kBM * bn > ws_floats || tiles * 4 > ws_cnt_len) return -17;
+    if (static_cast<long long>(splits - 1) * per >= nk_all) return -18;
+  }
   if (M <= 0 || N <= 0 || K <= 0) return -13;
-  if (out_mode == 0 && ((ldd % 8) || (reinterpret_cast<uintptr_t>(D) & 15))) return -14;
+  if ((out_mode == 0 || out_mode == 6) && ((ldd % 8) || (reinterpret_cast<uintptr_t>(D) & 15))) return -14;
   if (R && ((ldr % 8) || (reinterpret_cast<uintptr_t>(R) & 15))) return -15;
   // seg_mode 3 shifts a TMA load by seg * seg_r elements: the shift must keep the 16-byte alignment of the copy
   if (seg_mode == 3 && (!b_mn || (seg_r % 8) || N > bn || splits != 1)) return -16;
@@ -227,6 +289,7 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
   p.seg_mode = seg_mode; p.seg_r = seg_r;
   for (int i = 0; i < 4; ++i) p.seg_end[i] = (seg_mode && seg_end) ? seg_end[i] : 0x7fffffff;
   p.status = status;
+  p.ws = ws; p.ws_cnt = ws_cnt;
   const int stage_bytes = kBM * kBK * 2 + bn * kBK * 2;
   int stages = (227 * 1024 - 2048) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;

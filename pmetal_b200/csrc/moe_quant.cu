@@ -24,14 +24,15 @@
 namespace pm {
 
 // ------------------------------------------------------------------------------------------------ MoE routing
-// One warp per token. E <= 1024 experts (32 per lane), k <= 16.
-__device__ __forceinline__ void moe_route_token(const __nv_bfloat16* __restrict__ logits_bf16,
-                                                const float* __restrict__ logits_f32, int t, int E, int k, int renorm,
-                                                int* __restrict__ topk_idx, float* __restrict__ topk_w, int lane) {
-  float v[32];
+// One warp per token. E <= 1024 experts (NV = ceil(E / 32) per lane, kept in registers), k <= 16.
+template <int NV>
+__device__ __forceinline__ void moe_route_token_nv(const __nv_bfloat16* __restrict__ logits_bf16,
+                                                   const float* __restrict__ logits_f32, int t, int E, int k, int renorm,
+                                                   int* __restrict__ topk_idx, float* __restrict__ topk_w, int lane) {
+  float v[NV];
   float mx = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
+  for (int i = 0; i < NV; ++i) {
     const int e = i * 32 + lane;
     float x = -INFINITY;
     if (e < E) x = logits_f32 ? logits_f32[static_cast<long long>(t) * E + e]
@@ -42,7 +43,7 @@ __device__ __forceinline__ void moe_route_token(const __nv_bfloat16* __restrict_
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   float z = 0.f;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
+  for (int i = 0; i < NV; ++i) {
     v[i] = (i * 32 + lane < E) ? __expf(v[i] - mx) : -1.f;
     if (v[i] > 0.f) z += v[i];
   }
@@ -54,7 +55,7 @@ __device__ __forceinline__ void moe_route_token(const __nv_bfloat16* __restrict_
     float bv = -1.f;
     int bi = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
+    for (int i = 0; i < NV; ++i) {
       const int e = i * 32 + lane;
       if (v[i] > bv) { bv = v[i]; bi = e; }     // ascending e within a lane: first maximum wins
     }
@@ -65,7 +66,7 @@ __device__ __forceinline__ void moe_route_token(const __nv_bfloat16* __restrict_
     }
     if ((bi & 31) == lane) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
+      for (int i = 0; i < NV; ++i)
         if (i == (bi >> 5)) v[i] = -1.f;
     }
     const float w = bv * inv_z;
@@ -76,6 +77,15 @@ __device__ __forceinline__ void moe_route_token(const __nv_bfloat16* __restrict_
     topk_idx[static_cast<long long>(t) * k + lane] = my_idx;
     topk_w[static_cast<long long>(t) * k + lane] = renorm ? my_w / wsum : my_w;
   }
+}
+
+__device__ __forceinline__ void moe_route_token(const __nv_bfloat16* __restrict__ logits_bf16,
+                                                const float* __restrict__ logits_f32, int t, int E, int k, int renorm,
+                                                int* __restrict__ topk_idx, float* __restrict__ topk_w, int lane) {
+  if (E <= 64) moe_route_token_nv<2>(logits_bf16, logits_f32, t, E, k, renorm, topk_idx, topk_w, lane);
+  else if (E <= 128) moe_route_token_nv<4>(logits_bf16, logits_f32, t, E, k, renorm, topk_idx, topk_w, lane);
+  else if (E <= 256) moe_route_token_nv<8>(logits_bf16, logits_f32, t, E, k, renorm, topk_idx, topk_w, lane);
+  else moe_route_token_nv<32>(logits_bf16, logits_f32, t, E, k, renorm, topk_idx, topk_w, lane);
 }
 
 __global__ void moe_router_kernel(const __nv_bfloat16* __restrict__ logits_bf16, const float* __restrict__ logits_f32,
@@ -147,32 +157,54 @@ __global__ void __launch_bounds__(1024) moe_route_local_kernel(const __nv_bfloat
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = T * k;
   for (int t = warp; t < T; t += 32) moe_route_token(logits_bf16, logits_f32, t, E, k, renorm, topk_idx, topk_w, lane);
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) s_idx[i] = topk_idx[i];
-  __syncthreads();
-  const int e = threadIdx.x;          // local expert index
-  int c = 0;
-  if (e < e_loc)
-    for (int i = 0; i < n; ++i) c += (s_idx[i] == e0 + e);
-  if (e < e_loc) s_off[e + 1] = (c + align - 1) / align * align;
-  if (e == 0) s_off[0] = 0;
-  __syncthreads();
-  if (threadIdx.x == 0)
-    for (int j = 1; j <= e_loc; ++j) s_off[j] += s_off[j - 1];
-  __syncthreads();
-  if (e <= e_loc) off[e] = s_off[e];
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int x = s_idx[i];
+    const int x = topk_idx[i];
+    s_idx[i] = x;
     if (x < e0 || x >= e0 + e_loc) dest[i] = -1;
   }
-  if (e < e_loc) {
-    int pos = s_off[e];
-    for (int i = 0; i < n; ++i)
-      if (s_idx[i] == e0 + e) {
-        dest[i] = pos;
-        src[pos] = i;
-        ++pos;
+  if (threadIdx.x == 0) s_off[0] = 0;
+  __syncthreads();
+  // one warp per local expert: count its assignments 32 at a time
+  for (int e = warp; e < e_loc; e += 32) {
+    int c = 0;
+    for (int i0 = 0; i0 < n; i0 += 32) {
+      const int i = i0 + lane;
+      c += __popc(__ballot_sync(0xffffffffu, i < n && s_idx[i] == e0 + e));
+    }
+    if (lane == 0) s_off[e + 1] = (c + align - 1) / align * align;
+  }
+  __syncthreads();
+  if (warp == 0) {            // inclusive scan of the padded counts, 32 experts per round
+    int carry = 0;
+    for (int j0 = 1; j0 <= e_loc; j0 += 32) {
+      const int j = j0 + lane;
+      int v = j <= e_loc ? s_off[j] : 0;
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
       }
-    for (; pos < s_off[e + 1]; ++pos) src[pos] = -1;
+      v += carry;
+      if (j <= e_loc) s_off[j] = v;
+      carry = __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= e_loc; e += blockDim.x) off[e] = s_off[e];
+  // placement: rows of one expert keep the order of their assignment index
+  for (int e = warp; e < e_loc; e += 32) {
+    int pos = s_off[e];
+    for (int i0 = 0; i0 < n; i0 += 32) {
+      const int i = i0 + lane;
+      const bool hit = i < n && s_idx[i] == e0 + e;
+      const unsigned m = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int r = pos + __popc(m & ((1u << lane) - 1u));
+        dest[i] = r;
+        src[r] = i;
+      }
+      pos += __popc(m);
+    }
+    for (int r = pos + lane; r < s_off[e + 1]; r += 32) src[r] = -1;
   }
 }
 

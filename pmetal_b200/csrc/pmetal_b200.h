@@ -128,7 +128,8 @@ int pm_gemm_bf16_2sm(const void* A, int a_mn, int lda, int a_rows, const void* B
 int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const void* B, int b_mn, int ldb, int b_rows, const
     void* A2, int a2_mn, int lda2, int a2_k, const void* B2, int b2_mn, int ldb2, int b2_rows, void* D, int
     out_mode, int ldd, const void* R, int ldr, int M, int N, int K, int K2, int n_store, float alpha, int bn, int
-    splits, int seg_mode, const int* seg_end, int seg_r, int max_ctas, int* status, cudaStream_t stream);
+    splits, int seg_mode, const int* seg_end, int seg_r, int max_ctas, float* ws, long long ws_floats, unsigned*
+    ws_cnt, long long ws_cnt_len, int* status, cudaStream_t stream);
 
 // ---------------------------------------------------------------- gemv.cu
 // Returns 0, a negative argument error, or a CUDA error code. K % 8 == 0, row strides % 8 == 0, M <= 16,
@@ -150,6 +151,11 @@ int pm_gemv_q4(const void* x, int ldx, const void* qdata, const float* absmax, c
 // [E, N, ldd] (mode 2; experts without rows are left untouched, so clear D first unless accumulating).
 int pm_grouped_gemm(int mode, const void* a, int lda, const void* b, int ldb, void* D, int ldd, const int* off, int
     E, int rows_cap, int N, int K, float alpha, int accumulate, int* status, cudaStream_t stream);
+// Few rows per expert (see the kernel): x [rows, K] expert-sorted with offsets off [E + 1] (any alignment), w stacked
+// [E * N, K] (swiglu 0) or [E * 2N, K] with gate rows above up rows per expert (swiglu 1); y [rows, N] bf16.
+// bn (32, 64, 128) is the token tile: experts with more rows take several passes over their weights.
+int pm_grouped_gemm_skinny(const void* x, int ldx, int rows, const void* w, int ldw, void* y, int ldy, const int*
+    off, int E, int N, int K, int bn, int swiglu, float alpha, int* status, cudaStream_t stream);
 
 // ---------------------------------------------------------------- moe_gemm.cu
 int pm_ep_prepare(const unsigned long long* offset_ptrs, const unsigned long long* pad_ptrs, int rank, int world,

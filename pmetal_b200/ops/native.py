@@ -175,13 +175,52 @@ def raw_gemm(A, a_mn, lda, a_rows, B, b_mn, ldb, b_rows, D, out_mode, ldd, M, N,
                                     c_int(max_ctas), _p(status_word(D.device)), _stream())
         _chk(rc, "pm_gemm_bf16_2sm")
         return
+    ws = cnt = None
+    if out_mode == 0 and splits == 1 and SPLIT_K and M <= 128 and seg_mode in (0, 1):
+        # one row block: the few column tiles leave most SMs idle and each walks all of K by itself; cut K so that the
+        # launch covers the machine, partial tiles meeting in a workspace (reduced inside the kernel)
+        tiles = -(-N // bn)
+        nk = -(-K // 64) + (-(-K2 // 64) if K2 > 0 else 0)
+        want = min(nk // 4, sm_count() // tiles)
+        if want >= 2:
+            per = -(-nk // want)
+            want = -(-nk // per)
+            got = _splitk_workspace(D.device, tiles * want * 128 * bn, tiles * 4)
+            if got is not None and want >= 2:
+                ws, cnt = got
+                out_mode, splits = 6, want
     rc = lib().pm_gemm_bf16(_p(A), c_int(a_mn), c_int(lda), c_int(a_rows), _p(B), c_int(b_mn), c_int(ldb),
                             c_int(b_rows), _p(A2), c_int(a2_mn), c_int(lda2), c_int(a2_k), _p(B2), c_int(b2_mn),
                             c_int(ldb2), c_int(b2_rows), _p(D), c_int(out_mode), c_int(ldd), _p(R), c_int(ldr),
                             c_int(M), c_int(N), c_int(K), c_int(K2), c_int(n_store), c_float(alpha), c_int(bn),
-                            c_int(splits), c_int(seg_mode), segs, c_int(seg_r),
-                            c_int(max_ctas), _p(status_word(D.device)), _stream())
+                            c_int(splits), c_int(seg_mode), segs, c_int(seg_r), c_int(max_ctas), _p(ws),
+                            ctypes.c_longlong(ws.numel() if ws is not None else 0), _p(cnt),
+                            ctypes.c_longlong(cnt.numel() if cnt is not None else 0), _p(status_word(D.device)), _stream())
     _chk(rc, "pm_gemm_bf16")
+
+
+SPLIT_K = os.environ.get("PMETAL_GEMM_SPLITK", "1") == "1"
+_SPLITK_WS = {}
+
+
+def _splitk_workspace(device, floats: int, counters: int):
+    """(fp32 partial-tile buffer, zeroed arrival counters) for split-K launches on the current stream of ``device``.
+    Launches on one stream run in order and may share a buffer; every stream has its own. Captured launches use a
+    buffer of their own that is created ahead of the capture (by the first eager call); a capture that would have to
+    create or grow it gets None and runs without the split."""
+    capturing = torch.cuda.is_current_stream_capturing()
+    dev = device.index if device.index is not None else torch.cuda.current_device()
+    keys = [(dev, 0)] if capturing else [(dev, torch.cuda.current_stream(device).cuda_stream), (dev, 0)]
+    out = None
+    for key in reversed(keys):           # the capture buffer first, so that it always exists before a capture starts
+        ent = _SPLITK_WS.get(key)
+        if ent is None or ent[0].numel() < floats or ent[1].numel() < counters:
+            if capturing:
+                return None
+            ent = _SPLITK_WS[key] = (torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device),
+                                     torch.zeros(max(counters, 4096), dtype=torch.int32, device=device))
+        out = ent
+    return out
 
 
 def _t_width(nr: int) -> int:
@@ -335,6 +374,27 @@ def grouped_gemm(mode: int, a: torch.Tensor, b: torch.Tensor, off: torch.Tensor,
                                _p(status_word(a.device)), _stream())
     _chk(rc, "pm_grouped_gemm")
     return out
+
+
+def grouped_gemm_skinny(x: torch.Tensor, w: torch.Tensor, off: torch.Tensor, swiglu: bool = False,
+                        max_rows_per_expert: int = 128) -> torch.Tensor:
+    """Expert GEMM for steps that give each expert few rows (csrc/grouped_gemm.cu, swapped operands): ``x`` [R, K]
+    expert-sorted with row offsets ``off`` (int32 [E + 1], no alignment), ``w`` [E, N, K], or [E, 2 N, K] with
+    ``swiglu`` (gate rows above up rows), in which case the result is silu(x G^T) * (x U^T). Returns [R, N] bf16; rows
+    that belong to no expert are left unwritten."""
+    E = off.numel() - 1
+    R, K = x.shape
+    N = w.shape[1] // 2 if swiglu else w.shape[1]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and off.dtype == torch.int32
+    assert x.stride(1) == 1 and w.is_contiguous() and w.shape[0] == E and w.shape[2] == K
+    bn = 32 if max_rows_per_expert <= 32 else (64 if max_rows_per_expert <= 64 else 128)
+    y = torch.empty(R, N, dtype=torch.bfloat16, device=x.device)
+    lib().pm_grouped_gemm_skinny.restype = c_int
+    rc = lib().pm_grouped_gemm_skinny(_p(x), c_int(x.stride(0)), c_int(R), _p(w), c_int(w.stride(1)), _p(y), c_int(N),
+                                      _p(off), c_int(E), c_int(N), c_int(K), c_int(bn), c_int(int(swiglu)),
+                                      c_float(1.0), _p(status_word(x.device)), _stream())
+    _chk(rc, "pm_grouped_gemm_skinny")
+    return y
 
 
 # ------------------------------------------------------------------------------------------- norms etc.

@@ -112,12 +112,16 @@ def _slice_rows(w: torch.Tensor, pieces) -> torch.Tensor:
 
 
 @torch.no_grad()
-def shard_for_serving(model, group=None, reduce: Optional[AllReduce] = None) -> AllReduce:
+def shard_for_serving(model, group=None, reduce: Optional[AllReduce] = None, rank: Optional[int] = None,
+                      world: Optional[int] = None) -> AllReduce:
     """Cut ``model`` (a frozen ``DecoderLM`` without adapters) down to this rank's slice; see the module docstring.
-    Returns the all-reduce object the layers use."""
+    Returns the all-reduce object the layers use. ``rank`` / ``world`` override the process group's (cutting a slice
+    offline, or timing one rank's share of the work on a single device with a ``reduce`` that does nothing)."""
     from ..models.decoder import MLP, FusedLinear
-    world = dist.get_world_size(group) if dist.is_initialized() else 1
-    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    if world is None:
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if rank is None:
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
     reduce = reduce or AllReduce(group)
     cfg = model.cfg
     hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
@@ -193,6 +197,7 @@ class _Scratch:
 
 
 _SCRATCH = _Scratch()
+SKINNY_MAX_TOKENS = int(__import__("os").environ.get("PMETAL_MOE_SKINNY_TOKENS", "128"))
 
 
 def moe_local_forward(block, x: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
@@ -224,15 +229,22 @@ def moe_local_forward(block, x: torch.Tensor, residual: Optional[torch.Tensor]) 
             n = min(step, T - t0)
             b = _SCRATCH.get(n, k, e1 - e0, H, I, x.device)
             xs_in, lg_in = x[t0:t0 + n], lg[t0:t0 + n]
+            # a decode or verification step gives an expert at most n rows (one per token): the swapped-operand
+            # kernels stream the weights once, need no slab padding and fuse SwiGLU; larger batches use 128-row tiles
+            few = n <= SKINNY_MAX_TOKENS
             nat._chk(lib.pm_moe_route_local(nat._p(lg_in), ci(is_f32), ci(n), ci(cfg.num_experts), ci(k),
-                                            ci(int(cfg.norm_topk_prob)), ci(e0), ci(e1 - e0), ci(128), nat._p(b["idx"]),
-                                            nat._p(b["w"]), nat._p(b["off"]), nat._p(b["dest"]), nat._p(b["src"]),
-                                            nat._stream()), "pm_moe_route_local")
+                                            ci(int(cfg.norm_topk_prob)), ci(e0), ci(e1 - e0), ci(1 if few else 128),
+                                            nat._p(b["idx"]), nat._p(b["w"]), nat._p(b["off"]), nat._p(b["dest"]),
+                                            nat._p(b["src"]), nat._stream()), "pm_moe_route_local")
             nat._chk(lib.pm_moe_gather_padded(nat._p(xs_in), nat._p(b["src"]), nat._p(b["off"][e1 - e0:]), ci(k),
                                               nat._p(b["xs"]), ci(b["cap"]), ci(H), nat._stream()), "pm_moe_gather_padded")
-            gu = nat.grouped_gemm(0, b["xs"], block.gate_up, b["off"], 2 * I, H)
-            act = nat.swiglu_fwd(gu)
-            z = nat.grouped_gemm(0, act, block.down, b["off"], H, I)
+            if few:
+                act = nat.grouped_gemm_skinny(b["xs"], block.gate_up, b["off"], swiglu=True, max_rows_per_expert=n)
+                z = nat.grouped_gemm_skinny(act, block.down, b["off"], max_rows_per_expert=n)
+            else:
+                gu = nat.grouped_gemm(0, b["xs"], block.gate_up, b["off"], 2 * I, H)
+                act = nat.swiglu_fwd(gu)
+                z = nat.grouped_gemm(0, act, block.down, b["off"], H, I)
             nat._chk(lib.pm_moe_combine_local(nat._p(z), nat._p(b["dest"]), nat._p(b["w"]), ci(k),
                                               nat._p(res[t0:t0 + n] if res is not None else None), nat._p(y[t0:t0 + n]),
                                               ctypes.c_longlong(n), ci(H), nat._stream()), "pm_moe_combine_local")

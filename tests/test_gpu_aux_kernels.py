@@ -406,6 +406,35 @@ def test_gated_delta_rule_scan_kernel(dk, dv, T):
     assert torch.allclose(y0[0], yr0, atol=1e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("E,N,K,counts,cap", [(4, 256, 128, [3, 0, 40, 1], 32), (16, 768, 2048, [5, 0, 1, 9, 64, 2, 3, 0, 7, 1, 1, 4, 8, 6, 2, 30], 64),
+                                              (3, 200, 136, [10, 70, 33], 32), (16, 2048, 768, [4] * 16, 128)])
+def test_grouped_gemm_few_rows_per_expert(E, N, K, counts, cap):
+    """Swapped-operand expert GEMM (weights in the 128-row operand, a few token rows in the narrow one) against a
+    per-row fp32 product: unpadded slabs, experts without rows, experts with more rows than one token tile, widths that
+    are not a multiple of the tile; then the gate / up variant with SwiGLU in the epilogue. Garbage in the rows that
+    belong to no expert must not leak into the result."""
+    nat = _nat()
+    torch.manual_seed(5)
+    off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device="cuda")
+    n = int(off[-1])
+    e_of = torch.cat([torch.full((c,), e, dtype=torch.int64) for e, c in enumerate(counts)]).cuda()
+    rows = n + 37
+    x = torch.full((rows, K), float("nan"), dtype=torch.bfloat16, device="cuda")
+    x[:n] = torch.randn(n, K, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(E, N, K, device="cuda") * K ** -0.5).to(torch.bfloat16)
+    for _ in range(2):              # twice: barriers and accumulator buffers start over cleanly
+        y = nat.grouped_gemm_skinny(x, w, off, max_rows_per_expert=cap)
+    nat.check_status()
+    ref = torch.einsum("rk,rnk->rn", x[:n].float(), w.float()[e_of])
+    _close(y[:n], ref, what="few-rows grouped")
+    w2 = (torch.randn(E, 2 * N, K, device="cuda") * K ** -0.5).to(torch.bfloat16)
+    act = nat.grouped_gemm_skinny(x, w2, off, swiglu=True, max_rows_per_expert=cap)
+    nat.check_status()
+    gu = torch.einsum("rk,rnk->rn", x[:n].float(), w2.float()[e_of])
+    ref_act = torch.nn.functional.silu(gu[:, :N]) * gu[:, N:]
+    _close(act[:n], ref_act, what="few-rows grouped swiglu")
+
+
 @pytest.mark.parametrize("E,N,K,counts", [(4, 256, 128, [130, 0, 257, 64]), (8, 1536, 2048, [300, 5, 0, 129, 1000, 64, 128, 1]),
                                           (3, 200, 136, [10, 20, 30])])
 def test_grouped_gemm_forward_dx_dw(E, N, K, counts):

@@ -36,6 +36,25 @@ def test_gemm_kmajor(M, N, K, bn):
     _close(y, x.float() @ w.float().t(), what="gemm")
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 768, 2048), (17, 2048, 512), (128, 96, 1000), (100, 2560, 2048), (33, 40, 4096)])
+def test_gemm_single_row_block_splits_k_inside_the_kernel(M, N, K, monkeypatch):
+    """At most 128 rows and few column tiles: the reduction is cut over several CTAs whose partial tiles meet in a
+    workspace; the last arrival of each tile adds them in a fixed order. Same result as the unsplit launch up to the
+    rounding of the sum order, bit-identical from call to call, residual and scale applied once."""
+    nat = _nat()
+    torch.manual_seed(2)
+    x, w, r = _rand(M, K), _rand(N, K, scale=K ** -0.5), _rand(M, N)
+    n0 = nat.LAUNCHES
+    ys = [nat.gemm(x, w, alpha=0.5, residual=r) for _ in range(3)]
+    assert nat.LAUNCHES - n0 == 3                     # no separate reduction launch
+    nat.check_status()
+    ref = 0.5 * (x.float() @ w.float().t()) + r.float()
+    _close(ys[0], ref, what="split-k gemm")
+    assert torch.equal(ys[0], ys[1]) and torch.equal(ys[0], ys[2])
+    monkeypatch.setattr(nat, "SPLIT_K", False)
+    _close(nat.gemm(x, w, alpha=0.5, residual=r), ys[0], rtol=1e-2, atol=1e-2, what="split vs unsplit")
+
+
 def test_gemm_tile_width_from_the_tuner(tmp_path, monkeypatch):
     """With the tuner on, the first call of a shape times the candidate tile widths and records the winner; later
     calls read it from the cache file and give the same result."""
