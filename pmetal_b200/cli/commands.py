@@ -1465,6 +1465,8 @@ def _pretrain_args(sp):
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--resume", nargs="?", const="auto", help="checkpoint directory, or no value for the newest one under --output")
     p.add_argument("--device")
+    p.add_argument("--dp-impl", choices=["fused", "nccl"], default="fused",
+                   help="gradient exchange on several GPUs: the fused reduce + AdamW kernel over peer memory, or an all-reduce")
     return p
 
 
@@ -1475,7 +1477,19 @@ def cmd_pretrain(a) -> int:
     from ..data.streaming import TokenShardDataset
     from ..models.loader import load_pretrained
     from ..trainer.pretrain import PretrainConfig, PretrainTrainer
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    dctx = None
+    if world > 1:
+        # every rank reads its own shard of the data: the gradients have to meet before the update, or the replicas
+        # drift apart. The process group comes first so that each rank builds its model on its own GPU
+        from ..parallel.dp import DistContext
+        dctx = DistContext.from_env()
+        if torch.cuda.is_available() and not a.device:
+            a.device = f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}"
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    if dctx is not None and dev.startswith("cuda") and a.dp_impl == "fused":
+        from ..parallel.fused_dp import FusedDataParallel
+        dctx = FusedDataParallel()
     torch.manual_seed(a.seed)
     if a.model_config:
         from ..models.config import ModelArgs
@@ -1495,7 +1509,7 @@ def cmd_pretrain(a) -> int:
                          weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm, z_loss_coef=a.z_loss, seq_len=a.seq_len,
                          micro_batch=a.micro_batch, gradient_accumulation_steps=a.gradient_accumulation_steps,
                          lr_scheduler=a.lr_schedule, checkpoint_every=a.checkpoint_every, output=a.output)
-    tr = PretrainTrainer(model.train(), cfg)
+    tr = PretrainTrainer(model.train(), cfg, dist=dctx)
     resume = a.resume
     if resume == "auto":
         done = sorted((int(d.split("_")[1]), d) for d in (os.listdir(a.output) if os.path.isdir(a.output) else [])
@@ -1503,7 +1517,6 @@ def cmd_pretrain(a) -> int:
         resume = os.path.join(a.output, done[-1][1]) if done else None
     if resume:
         tr.load_checkpoint(resume)
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     ds = TokenShardDataset(a.shards, a.seq_len, rank, world, seed=a.seed, loop=True)      # epochs roll over until --steps
     ev = TokenShardDataset(a.eval_shards, a.seq_len, rank, world) if a.eval_shards else None
 
@@ -1513,8 +1526,15 @@ def cmd_pretrain(a) -> int:
     last = tr.run(ds, on_step=on_step, eval_dataset=ev, eval_every=a.eval_every, eval_batches=a.eval_batches)
     if ev is not None and "eval_loss" not in last:
         last = {**last, **tr.evaluate(ev, a.eval_batches)}
-    tr.save_checkpoint(os.path.join(a.output, "final"))
-    print(json.dumps({"output": a.output, "resumed_from": resume, **last}))
+    if dctx is not None:
+        dctx.gather_optimizer_state(tr.opt)          # sharded moments (fused path) back to full size before writing
+    if rank == 0:
+        tr.save_checkpoint(os.path.join(a.output, "final"))
+        print(json.dumps({"output": a.output, "resumed_from": resume, **last}))
+    if dctx is not None:
+        from ..parallel.dp import shutdown_process_group
+        dctx.barrier()
+        shutdown_process_group()
     return 0
 
 

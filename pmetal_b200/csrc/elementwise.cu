@@ -91,6 +91,56 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __
   }
 }
 
+// Few rows (decode, verification): one 256-thread CTA per row, so that 64 rows occupy 64 SMs instead of 8. Each thread
+// keeps its (up to two) 8-element chunks in registers between the reduction and the scaling. H <= 4096, H % 8 == 0.
+__global__ void __launch_bounds__(256) rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x,
+                                                              const __nv_bfloat16* __restrict__ res,
+                                                              const __nv_bfloat16* __restrict__ w,
+                                                              __nv_bfloat16* __restrict__ y,
+                                                              __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd,
+                                                              int H, float eps) {
+  __shared__ float red[8];
+  const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t base = static_cast<size_t>(row) * H;
+  float f[2][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int c = (u * 256 + threadIdx.x) * 8;
+    if (c < H) {
+      load8(x + base + c, f[u]);
+      if (res) {
+        float g[8];
+        load8(res + base + c, g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[u][i] = __bfloat162float(__float2bfloat16(f[u][i] + g[i]));
+        store8(h_out + base + c, f[u]);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[u][i] * f[u][i];
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rs = rsqrtf(tot / H + eps);
+  if (threadIdx.x == 0) rstd[row] = rs;
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int c = (u * 256 + threadIdx.x) * 8;
+    if (c < H) {
+      float g[8];
+      load8(w + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[u][i] = f[u][i] * rs * g[i];
+      store8(y + base + c, f[u]);
+    }
+  }
+}
+
 // dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dh_add);  optional dw += sum_rows dy * xhat
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
                                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
@@ -362,7 +412,7 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const 
 __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ labels,
                                   float* __restrict__ loss_sum, const float* __restrict__ inv_n,
                                   float* __restrict__ row_loss, const float* __restrict__ row_scale, int V,
-                                  long long ignore_index, int write_grad) {
+                                  long long ignore_index, int write_grad, float z_coef, float* __restrict__ z_sum) {
   __shared__ float red[32];
   __shared__ float bcast[2];
   const int row = blockIdx.x;
@@ -417,21 +467,24 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
     const float rl = lse - __bfloat162float(lr[label]);
     if (row_loss) row_loss[row] = rl;
     if (loss_sum) atomicAdd(loss_sum, rl);
+    if (z_sum) atomicAdd(z_sum, lse * lse);
   }
   __syncthreads();
   if (!write_grad) return;
   const float lse = bcast[0];
   const float gs = row_scale ? row_scale[row] : *inv_n;
+  // with the z term  z_coef * lse^2  the gradient is  (1 + 2 z_coef lse) softmax - onehot
+  const float pz = 1.f + 2.f * z_coef * lse;
   for (int c = tid * 8; c < V8; c += nthr * 8) {
     float f[8];
     load8(lr + c, f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = (__expf(f[i] - lse) - ((c + i) == label ? 1.f : 0.f)) * gs;
+    for (int i = 0; i < 8; ++i) f[i] = (pz * __expf(f[i] - lse) - ((c + i) == label ? 1.f : 0.f)) * gs;
     store8(lr + c, f);
   }
   for (int c = V8 + tid; c < V; c += nthr) {
     const float f = __bfloat162float(lr[c]);
-    lr[c] = __float2bfloat16((__expf(f - lse) - (c == label ? 1.f : 0.f)) * gs);
+    lr[c] = __float2bfloat16((pz * __expf(f - lse) - (c == label ? 1.f : 0.f)) * gs);
   }
 }
 
@@ -594,6 +647,13 @@ static inline int grid_for(long long work, int per_block, int cap = 0) {
 extern "C" int pm_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd, int T,
                               int H, float eps, cudaStream_t st) {
   if (H % 8) return -1;
+  if (T <= 592 && H <= 4096) {        // fewer row groups than SMs: spread the rows instead
+    rmsnorm_fwd_row_kernel<<<T, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
+        static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(h_out), rstd, H,
+        eps);
+    return PM_LAUNCH_CHECK();
+  }
   rmsnorm_fwd_kernel<<<(T + 7) / 8, 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
       static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(h_out), rstd, T,
@@ -664,7 +724,17 @@ extern "C" int pm_ce_fwd_bwd(void* logits, long long ldl, const long long* label
                              int write_grad, cudaStream_t st) {
   if (ldl % 8) return -1;
   ce_fwd_bwd_kernel<<<n_rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ldl, labels, loss_sum, inv_n, row_loss,
-                                             row_scale, V, ignore_index, write_grad);
+                                             row_scale, V, ignore_index, write_grad, 0.f, nullptr);
+  return PM_LAUNCH_CHECK();
+}
+// Cross entropy plus the z term z_coef * logsumexp(logits)^2 per valid row: z_sum receives the sum of the squared
+// normalisers, and the gradient written over the logits is that of (cross entropy + z_coef * z) summed over rows.
+extern "C" int pm_ce_z_fwd_bwd(void* logits, long long ldl, const long long* labels, float* loss_sum, float* z_sum,
+                               const float* inv_n, int n_rows, int V, long long ignore_index, int write_grad, float z_coef,
+                               cudaStream_t st) {
+  if (ldl % 8) return -1;
+  ce_fwd_bwd_kernel<<<n_rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ldl, labels, loss_sum, inv_n, nullptr,
+                                             nullptr, V, ignore_index, write_grad, z_coef, z_sum);
   return PM_LAUNCH_CHECK();
 }
 extern "C" int pm_sumsq(const float* x, long long n, float* out, cudaStream_t st) {

@@ -101,6 +101,10 @@ int pm_swiglu_bwd(const void* dout, const void* gu, void* dgu, long long T, int 
 // row_loss (optional): per-row loss out. row_scale (optional): per-row gradient scale replacing *inv_n.
 int pm_ce_fwd_bwd(void* logits, long long ldl, const long long* labels, float* loss_sum, const float* inv_n, float*
     row_loss, const float* row_scale, int n_rows, int V, long long ignore_index, int write_grad, cudaStream_t st);
+// Cross entropy plus the z term z_coef * logsumexp(logits)^2 per valid row: z_sum receives the sum of the squared
+// normalisers, and the gradient written over the logits is that of (cross entropy + z_coef * z) summed over rows.
+int pm_ce_z_fwd_bwd(void* logits, long long ldl, const long long* labels, float* loss_sum, float* z_sum, const
+    float* inv_n, int n_rows, int V, long long ignore_index, int write_grad, float z_coef, cudaStream_t st);
 int pm_sumsq(const float* x, long long n, float* out, cudaStream_t st);
 int pm_adamw_flat(float* p, const float* g, float* m, float* v, void* shadow, const float* lr_mult, const float*
     wd, const float* gnorm_sq, const float* hp, long long n, float lr, float beta1, float beta2, float eps, int

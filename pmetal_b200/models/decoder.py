@@ -115,6 +115,10 @@ class FusedLinear(nn.Module):
         return w
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.weight.requires_grad and self.bias is None and self.lora_a is None:
+            sh = getattr(self.weight, "shadow", None)           # full-parameter training: bf16 shadow of the fp32 master
+            if sh is not None and ops.use_native(x) and self.in_features % 8 == 0 and self.out_features % 8 == 0:
+                return ops.dense_linear(x, self.weight, sh, residual)
         if self.bias is not None or self.weight.requires_grad:
             y = F.linear(x, self.weight, self.bias)
             if self.lora_a is not None:
@@ -178,7 +182,8 @@ class Attention(nn.Module):
     def forward(self, x_normed, residual, rope, cu_seqlens, seq_start):
         cfg = self.cfg
         qkv = self.qkv_proj(x_normed)
-        o = ops.attention_block(qkv, self.q_norm, self.k_norm, rope[0], rope[1], cu_seqlens, seq_start,
+        qn, kn = (ops.live(self.q_norm), ops.live(self.k_norm)) if self.q_norm is not None else (None, None)
+        o = ops.attention_block(qkv, qn, kn, rope[0], rope[1], cu_seqlens, seq_start,
                                 cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps,
                                 None, self.window, cfg.attn_logit_softcap)
         return self.o_proj(o, residual)
@@ -214,9 +219,9 @@ class DecoderLayer(nn.Module):
         eps = self.cfg.rms_norm_eps
         # the norm hands back the stream it read: using that alias for the residual branch lets its gradient be
         # summed inside the norm's backward kernel
-        n1, x = ops.add_rms_norm(x, None, self.input_layernorm, eps)
+        n1, x = ops.add_rms_norm(x, None, ops.live(self.input_layernorm), eps)
         h = self.self_attn(n1, x, rope, cu_seqlens, seq_start)
-        n2, h = ops.add_rms_norm(h, None, self.post_attention_layernorm, eps)
+        n2, h = ops.add_rms_norm(h, None, ops.live(self.post_attention_layernorm), eps)
         return self.mlp(n2, h)
 
 
@@ -309,7 +314,7 @@ class DecoderLM(nn.Module):
             ss = seq_start if seq_start is not None else seq_starts_from_cu(cu_seqlens, T)
             positions = torch.arange(T, device=input_ids.device, dtype=torch.int32) - ss
         lo, hi = layer_range if layer_range is not None else (0, len(self.layers))
-        x = hidden_in if hidden_in is not None else F.embedding(input_ids, self.embed_tokens)
+        x = hidden_in if hidden_in is not None else F.embedding(input_ids, ops.live(self.embed_tokens))
         rope = ops.rope_table(positions, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scale)
         for i in range(lo, hi):
             layer = self.layers[i]
@@ -320,7 +325,7 @@ class DecoderLM(nn.Module):
                 x = layer(x, rope, cu_seqlens, seq_start)
         if hi < len(self.layers):
             return x
-        return ops.rms_norm(x, self.norm, self.cfg.rms_norm_eps)
+        return ops.rms_norm(x, ops.live(self.norm), self.cfg.rms_norm_eps)
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         out = F.linear(hidden, self.head_weight())

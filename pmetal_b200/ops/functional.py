@@ -148,7 +148,17 @@ class _AttnBlockFn(torch.autograd.Function):
         dv = dqkv[:, (hq + hkv) * d:].view(T, hkv, d)
         dq, dk = nat.attn_bwd(do.contiguous().view(T, hq, d), q, k, v, o, lse, seq_start, scale, window, dv)
         nat.qknorm_rope_bwd(dq, dk, qkv, qw, kw, cos, sin, hq, hkv, eps, dqkv)
-        return (dqkv,) + (None,) * 11
+        dqw = dkw = None
+        if qw is not None and (ctx.needs_input_grad[1] or ctx.needs_input_grad[2]):
+            # gradient of the per-head norm weights: un-rotate the gradient, multiply by the normalised activations
+            def norm_weight_grad(g, raw):
+                g = ref.apply_rope(g, cos, -sin).float()
+                x = raw.float()
+                xhat = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+                return (g * xhat).sum((0, 1))
+            dqw = norm_weight_grad(dq, qkv[:, :hq * d].view(T, hq, d)).to(qw.dtype)
+            dkw = norm_weight_grad(dk, qkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d)).to(kw.dtype)
+        return (dqkv, dqw, dkw) + (None,) * 9
 
 
 def attention_block(qkv: torch.Tensor, q_weight, k_weight, cos: torch.Tensor, sin: torch.Tensor,
@@ -168,6 +178,61 @@ def attention_block(qkv: torch.Tensor, q_weight, k_weight, cos: torch.Tensor, si
         q, k = ref.rms_norm(q, q_weight, eps), ref.rms_norm(k, k_weight, eps)
     q, k = ref.apply_rope(q, cos, sin), ref.apply_rope(k, cos, sin)
     return ref.varlen_attention(q, k, v, cu_seqlens, scale, True, window, softcap).reshape(T, hq * d)
+
+
+# --------------------------------------------------------------------------- trainable parameters with bf16 shadows
+class _ShadowFn(torch.autograd.Function):
+    """The bf16 shadow of an fp32 master parameter as a differentiable stand-in: kernels read the shadow, the gradient
+    flows to the master."""
+
+    @staticmethod
+    def forward(ctx, master, shadow):
+        return shadow.view_as(shadow)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g.to(torch.float32), None
+
+
+def live(p: torch.Tensor) -> torch.Tensor:
+    """What the native kernels should read for parameter ``p``: its bf16 shadow (kept in step by the optimiser) when it
+    trains in fp32 on the GPU, else ``p`` itself."""
+    sh = getattr(p, "shadow", None)
+    if sh is None or not p.requires_grad or not native_enabled(sh):
+        return p
+    return _ShadowFn.apply(p, sh)
+
+
+class _DenseLinearFn(torch.autograd.Function):
+    """y = x W^T (+ residual) with a trainable W: forward and input gradient read the bf16 shadow on the tcgen05 GEMM, the
+    weight gradient dY^T X is accumulated straight into the master's fp32 ``.grad`` (fixed summation order)."""
+
+    @staticmethod
+    def forward(ctx, x, master, shadow, residual):
+        nat = _native()
+        x2 = x.reshape(-1, x.shape[-1])
+        y = nat.gemm(x2, shadow, residual=residual.reshape(-1, shadow.shape[0]) if residual is not None else None)
+        ctx.save_for_backward(x2, shadow)
+        ctx.master = master
+        ctx.has_res = residual is not None
+        ctx.shape = x.shape
+        return y.view(*x.shape[:-1], shadow.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, shadow = ctx.saved_tensors
+        nat = _native()
+        dy2 = dy.reshape(-1, shadow.shape[0]).contiguous()
+        dx = nat.gemm_lora_dx(dy2, shadow, None, None, None).view(ctx.shape) if ctx.needs_input_grad[0] else None
+        m = ctx.master
+        if m.grad is None:
+            m.grad = torch.zeros_like(m, dtype=torch.float32)
+        nat.gemm_dw(dy2, x2, m.grad)
+        return dx, None, None, (dy if ctx.has_res else None)
+
+
+def dense_linear(x: torch.Tensor, master: torch.Tensor, shadow: torch.Tensor, residual: Optional[torch.Tensor] = None):
+    return _DenseLinearFn.apply(x, master, shadow, residual)
 
 
 # --------------------------------------------------------------------------- fused base + LoRA linear
@@ -251,27 +316,77 @@ def lora_linear(x: torch.Tensor, w: torch.Tensor, w_t: Optional[torch.Tensor], a
 
 # --------------------------------------------------------------------------- linear + cross-entropy
 class _LinearCeFn(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, hidden, weight, weight_t, labels, ignore_index, chunk):
-        loss_sum, n_valid, dh = _native().linear_ce(hidden, weight, weight_t, labels, ignore_index, chunk,
-                                                    hidden.requires_grad)
-        ctx.save_for_backward(dh)
-        ctx.mark_non_differentiable(n_valid)
-        return loss_sum, n_valid
+    """Σ over valid rows of (cross entropy + z_coef · logsumexp²), with the gradients formed in the forward pass: the
+    one for the hidden states is saved, the one for a trainable head weight is accumulated chunk by chunk into an fp32
+    buffer and added to the master's ``.grad`` in backward (scaled by the incoming gradient)."""
 
     @staticmethod
-    def backward(ctx, dloss, _dn):
-        (dh,) = ctx.saved_tensors
-        return (dh * dloss.to(dh.dtype)) if dh is not None else None, None, None, None, None, None
+    def forward(ctx, hidden, weight, weight_t, labels, ignore_index, chunk, z_coef, master):
+        w_grad = None
+        if master is not None:
+            w_grad = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+        ce, z, n_valid, dh = _native().linear_ce(hidden, weight, weight_t, labels, ignore_index, chunk,
+                                                 hidden.requires_grad, z_coef, w_grad)
+        ctx.save_for_backward(dh, w_grad)
+        ctx.master = master
+        ctx.mark_non_differentiable(n_valid)
+        total = ce + z_coef * z if z_coef else ce.clone()
+        ce_out, z_out = ce.detach().clone(), z.detach().clone()
+        ctx.mark_non_differentiable(ce_out, z_out)
+        return total, n_valid, ce_out, z_out
+
+    @staticmethod
+    def backward(ctx, dloss, _dn, _dce, _dz):
+        dh, w_grad = ctx.saved_tensors
+        if w_grad is not None:
+            m = ctx.master
+            if m.grad is None:
+                m.grad = torch.zeros_like(m, dtype=torch.float32)
+            m.grad.addcmul_(w_grad, dloss.to(torch.float32))
+        return (dh * dloss.to(dh.dtype)) if dh is not None else None, None, None, None, None, None, None, None
+
+
+def _head_pair(weight: torch.Tensor):
+    """(tensor the kernels read, fp32 master that receives the gradient or None) for a head weight that may be a
+    trainable fp32 master with a bf16 shadow."""
+    sh = getattr(weight, "shadow", None)
+    if weight.requires_grad and sh is not None and native_enabled(sh):
+        return sh, weight
+    return weight, None
 
 
 def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
                          chunk: int = 4096, weight_t: Optional[torch.Tensor] = None, softcap: float = 0.0):
-    """Returns (Σ loss over valid tokens, number of valid tokens). The head weight is treated as frozen on
-    the native path (LoRA fine-tuning); full fine-tuning of the head uses the reference path."""
-    if use_native(hidden) and softcap == 0.0 and not weight.requires_grad:
-        return _LinearCeFn.apply(hidden, weight, weight_t, labels, ignore_index, chunk)
+    """Returns (Σ loss over valid tokens, number of valid tokens). A frozen head, or a trainable fp32 head with a bf16
+    shadow (full-parameter training), runs the chunked kernels; anything else the reference path."""
+    w, master = _head_pair(weight)
+    if use_native(hidden) and softcap == 0.0 and (master is not None or not weight.requires_grad):
+        return _LinearCeFn.apply(hidden, w, weight_t if master is None else None, labels, ignore_index, chunk, 0.0, master)[:2]
     return ref.linear_cross_entropy(hidden, weight, labels, ignore_index, chunk, softcap)
+
+
+def linear_cross_entropy_z(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, z_coef: float,
+                           ignore_index: int = -100, chunk: int = 4096):
+    """Cross entropy with the z regulariser of pre-training: returns (mean over valid tokens of ce + z_coef·lse²,
+    mean ce, mean lse²); the last two are for logging only."""
+    w, master = _head_pair(weight)
+    if use_native(hidden) and (master is not None or not weight.requires_grad):
+        total, n, ce, z = _LinearCeFn.apply(hidden, w, None, labels, ignore_index, chunk, float(z_coef), master)
+        d = n.clamp(min=1).to(total.dtype)
+        return total / d, ce / d, z / d
+    V = weight.shape[0]
+    valid = labels != ignore_index
+    ce_sum = hidden.new_zeros((), dtype=torch.float32)
+    z_sum = hidden.new_zeros((), dtype=torch.float32)
+    for a in range(0, hidden.shape[0], chunk):
+        lg = (hidden[a:a + chunk] @ weight.t().to(hidden.dtype)).float()
+        m = valid[a:a + chunk]
+        lse = torch.logsumexp(lg, -1)
+        tgt = labels[a:a + chunk].clamp(0, V - 1)
+        ce_sum = ce_sum + ((lse - lg.gather(-1, tgt[:, None]).squeeze(-1)) * m).sum()
+        z_sum = z_sum + ((lse ** 2) * m).sum()
+    d = valid.sum().clamp(min=1).to(torch.float32)
+    return (ce_sum + z_coef * z_sum) / d, (ce_sum / d).detach(), (z_sum / d).detach()
 
 
 def causal_lm_loss(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,

@@ -529,27 +529,45 @@ def attn_bwd(dout, q, k, v, o, lse, seq_start, scale: float, window: int = 0, dv
 
 
 # ------------------------------------------------------------------------------------------- loss / optimizer
-def linear_ce(hidden, weight, weight_t, labels, ignore_index: int, chunk: int, need_grad: bool):
+def gemm_dw(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None) -> None:
+    """out [N, K] (fp32) += dy[:, :N]^T x  — the weight gradient of y = x W^T, reduction over the token rows. Both
+    operands are read in place (token index as the reduction dimension); every output tile belongs to one CTA, which
+    adds into ``out`` with a plain read-add-write, so the sum is formed in a fixed order."""
+    T, K = x.shape
+    N = out.shape[0] if rows is None else rows
+    assert out.dtype == torch.float32 and out.stride(1) == 1 and dy.stride(1) == 1 and x.stride(1) == 1
+    if not MN_MAJOR:
+        out[:N].add_(dy[:, :N].t().float() @ x.float())
+        return
+    bn = 128 if K >= 128 else 64
+    raw_gemm(dy, 1, dy.stride(0), N, x, 1, x.stride(0), K, out, 4, out.stride(0), N, K, T, bn=bn)
+
+
+def linear_ce(hidden, weight, weight_t, labels, ignore_index: int, chunk: int, need_grad: bool, z_coef: float = 0.0,
+              w_grad: Optional[torch.Tensor] = None):
     """Chunked linear + cross-entropy. Logits of one token chunk live in a bf16 scratch buffer, are turned
-    into their gradient in place, and feed the input-gradient GEMM; the [T, V] matrix never exists."""
+    into their gradient in place, and feed the input-gradient GEMM; the [T, V] matrix never exists.
+    ``z_coef`` adds ``z_coef * logsumexp(logits)^2`` per valid row to the differentiated sum (the second return value
+    is the sum of the squared normalisers); ``w_grad`` (fp32 [V, H]) receives the gradient of the head weight."""
     T, H = hidden.shape
     V = weight.shape[0]
     labels = labels.contiguous()
     n_valid = (labels != ignore_index).sum()
     inv_n = torch.ones(1, dtype=torch.float32, device=hidden.device)   # gradient is of the *sum*; caller divides
-    loss = torch.zeros(1, dtype=torch.float32, device=hidden.device)
+    loss = torch.zeros(2, dtype=torch.float32, device=hidden.device)  # [cross entropy, squared normalisers]
     dh = torch.empty_like(hidden) if need_grad else None
     chunk = min(chunk, T)
     ldl = -(-V // 8) * 8
     scratch = torch.empty(chunk, ldl, dtype=torch.bfloat16, device=hidden.device)
     bn = _pick_bn(V)
+    grads = need_grad or w_grad is not None
     for s in range(0, T, chunk):
         n = min(chunk, T - s)
         h = hidden[s:s + n]
         raw_gemm(h, 0, h.stride(0), n, weight, 0, weight.stride(0), V, scratch, 0, ldl, n, V, H, bn=bn)
-        _chk(lib().pm_ce_fwd_bwd(_p(scratch), c_ll(ldl), _p(labels[s:s + n]), _p(loss), _p(inv_n), _p(None), _p(None),
-                                 c_int(n), c_int(V), c_ll(ignore_index), c_int(1 if need_grad else 0), _stream()),
-             "pm_ce_fwd_bwd")
+        _chk(lib().pm_ce_z_fwd_bwd(_p(scratch), c_ll(ldl), _p(labels[s:s + n]), _p(loss), _p(loss[1:]), _p(inv_n),
+                                   c_int(n), c_int(V), c_ll(ignore_index), c_int(1 if grads else 0), c_float(z_coef),
+                                   _stream()), "pm_ce_z_fwd_bwd")
         if need_grad:
             d = dh[s:s + n]
             if weight_t is not None:
@@ -561,7 +579,9 @@ def linear_ce(hidden, weight, weight_t, labels, ignore_index: int, chunk: int, n
             else:
                 wt = weight.t().contiguous()
                 raw_gemm(scratch, 0, ldl, n, wt, 0, V, H, d, 0, d.stride(0), n, H, V, bn=_pick_bn(H))
-    return loss.reshape(()), n_valid, dh
+        if w_grad is not None:
+            gemm_dw(scratch[:n], h, w_grad, rows=V)
+    return loss[0], loss[1], n_valid, dh
 
 
 def sumsq(x: torch.Tensor, out: torch.Tensor) -> None:

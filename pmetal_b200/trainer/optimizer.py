@@ -185,3 +185,11 @@ def attach_shadows(model, opt: FlatAdamW) -> None:
         if fl.lora_a is not None:
             fl.lora_a_c = opt.shadows.get(ids[id(fl.lora_a)])
             fl.lora_b_c = opt.shadows.get(ids[id(fl.lora_b)])
+    # full-parameter training: every fp32 master that trains carries its bf16 shadow, which the kernels read
+    # (ops.functional.live / dense_linear); adapter factors keep their own route above
+    for n, p in byname.items():
+        if "lora_" in n or not p.requires_grad or p.dtype != torch.float32:
+            continue
+        sh = opt.shadows.get(n)
+        if sh is not None:
+            p.shadow = sh

@@ -1,7 +1,8 @@
 """Full-parameter pre-training loop over token shards (crates/pmetal-trainer/src/pretrain/*).
 
 Every parameter trains (bf16 compute shadows of fp32 masters in the flat AdamW buffer), the loss is next-token
-cross-entropy plus an optional z-loss ``z_coef * mean(logsumexp(logits)^2)`` that keeps the softmax normaliser near one,
+cross-entropy plus an optional z-loss ``z_coef * mean(logsumexp(logits)^2)`` (over the positions that have a target) that
+keeps the softmax normaliser near one,
 and a checkpoint holds model, optimiser state, step and data position so a run resumes exactly."""
 from __future__ import annotations
 
@@ -33,14 +34,6 @@ class PretrainConfig:
     output: str = "./pretrain-output"
 
 
-def z_loss(hidden: torch.Tensor, head: torch.Tensor, chunk: int = 4096) -> torch.Tensor:
-    tot = hidden.new_zeros((), dtype=torch.float32)
-    for a in range(0, hidden.shape[0], chunk):
-        lse = torch.logsumexp(hidden[a:a + chunk].float() @ head.float().t(), -1)
-        tot = tot + (lse ** 2).sum()
-    return tot / hidden.shape[0]
-
-
 class PretrainTrainer:
     def __init__(self, model, cfg: PretrainConfig, dist=None):
         from .optimizer import FlatAdamW, attach_shadows
@@ -66,18 +59,36 @@ class PretrainTrainer:
         ids = torch.as_tensor(np.asarray(windows), dtype=torch.int64, device=self.device)
         return ids if ids.dim() == 2 else ids[None]
 
+    def _native_path(self) -> bool:
+        """Dense decoder without biases on a GPU with the kernels loaded: embedding, norms, projections, attention and
+        the loss all read the bf16 shadows and write fp32 gradients into the flat buffer. Anything else (mixture-of-
+        experts layers, biases, CPU) takes the PyTorch operators under autocast."""
+        if not hasattr(self, "_native_ok"):
+            from ..models.decoder import MLP
+            from ..ops import functional as ops
+            m = self.model
+            self._native_ok = bool(
+                self.device.type == "cuda" and getattr(m.embed_tokens, "shadow", None) is not None
+                and ops.native_enabled(m.embed_tokens.shadow) and m.cfg.final_logit_softcap <= 0
+                and all(isinstance(layer.mlp, MLP) for layer in m.layers)
+                and all(fl.bias is None for _, _, fl in m.fused_linears()))
+        return self._native_ok
+
     def _loss(self, ids):
-        """(cross entropy, z-loss or None) of a [B, L] batch; next-token targets inside each window."""
+        """(loss to differentiate, cross entropy, z term) of a [B, L] batch; next-token targets inside each window. The z
+        term is the mean of logsumexp(logits)^2 over the positions that have a target."""
         from ..ops import functional as ops
         import contextlib
         tgt = torch.full_like(ids, -100)
         tgt[:, :-1] = ids[:, 1:]
+        head = self.model.head_weight()
+        if self._native_path():
+            h = self.model.forward_hidden(ids)
+            return ops.linear_cross_entropy_z(h, head, tgt.reshape(-1), self.cfg.z_loss_coef)
         amp = torch.autocast("cuda", dtype=torch.bfloat16) if self.device.type == "cuda" else contextlib.nullcontext()
         with ops.force_reference(), amp:
             h = self.model.forward_hidden(ids)
-            ce = ops.causal_lm_loss(h, self.model.head_weight(), tgt.reshape(-1), -100, None)
-            zl = z_loss(h, self.model.head_weight()) if self.cfg.z_loss_coef > 0 else None
-        return ce, zl
+            return ops.linear_cross_entropy_z(h, head, tgt.reshape(-1), self.cfg.z_loss_coef)
 
     @torch.no_grad()
     def evaluate(self, dataset: Iterable, max_batches: int = 20) -> dict:
@@ -89,7 +100,7 @@ class PretrainTrainer:
             batch.append(window)
             if len(batch) < self.cfg.micro_batch:
                 continue
-            losses.append(float(self._loss(self._batch(batch))[0]))
+            losses.append(float(self._loss(self._batch(batch))[1]))
             batch = []
             if len(losses) >= max_batches:
                 break
@@ -109,11 +120,10 @@ class PretrainTrainer:
             ce_sum, zl_sum, n_tok, parts = 0.0, 0.0, 0, [windows[i:i + c.micro_batch] for i in range(0, len(windows), c.micro_batch)]
             for part in parts:
                 ids = self._batch(part)
-                ce, zl = self._loss(ids)
-                loss = ce + (c.z_loss_coef * zl if zl is not None else 0.0)
+                loss, ce, zl = self._loss(ids)
                 (loss / len(parts)).backward()
                 ce_sum += float(ce.detach()) / len(parts)
-                zl_sum += (float(zl.detach()) if zl is not None else 0.0) / len(parts)
+                zl_sum += float(zl.detach()) / len(parts)
                 n_tok += ids.numel()
             if self.dist is not None and self.dist.world_size > 1:
                 gn = self.dist.reduce_and_step(self.opt, 1.0)
@@ -127,21 +137,7 @@ class PretrainTrainer:
         self.opt.zero_grad()
         ids = self._batch(windows)
         B, L = ids.shape
-        tgt = torch.full_like(ids, -100)
-        tgt[:, :-1] = ids[:, 1:]
-        from ..ops import functional as ops
-        import contextlib
-        # every weight trains, so the masters are the fp32 views of the flat optimiser buffer: run the PyTorch operator
-        # path, under bf16 autocast on the GPU
-        amp = torch.autocast("cuda", dtype=torch.bfloat16) if self.device.type == "cuda" else contextlib.nullcontext()
-        with ops.force_reference(), amp:
-            h = self.model.forward_hidden(ids)
-            ce = ops.causal_lm_loss(h, self.model.head_weight(), tgt.reshape(-1), -100, None)
-            loss = ce
-            zl = None
-            if c.z_loss_coef > 0:
-                zl = z_loss(h, self.model.head_weight())
-                loss = loss + c.z_loss_coef * zl
+        loss, ce, zl = self._loss(ids)
         loss.backward()
         if self.dist is not None and self.dist.world_size > 1:
             gn = self.dist.reduce_and_step(self.opt, 1.0)
@@ -149,7 +145,7 @@ class PretrainTrainer:
             gn = self.opt.step(1.0)
         self.step_count += 1
         self.tokens_seen += B * L
-        return {"step": self.step_count, "loss": float(ce.detach()), "z_loss": float(zl.detach()) if zl is not None else 0.0,
+        return {"step": self.step_count, "loss": float(ce.detach()), "z_loss": float(zl.detach()),
                 "grad_norm": float(gn), "lr": self.opt.lr, "tokens": self.tokens_seen}
 
     def run(self, dataset: Iterable, on_step=None, eval_dataset=None, eval_every: int = 0, eval_batches: int = 20) -> dict:

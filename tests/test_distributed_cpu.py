@@ -306,6 +306,17 @@ def test_sharded_engine_with_follower_ranks_over_gloo():
     assert r.returncode == 0 and r.stdout.count("SERVE_REPLICA_WORKER_OK") == 2, r.stdout[-3000:]
 
 
+def test_pretrain_replicas_stay_identical_over_gloo():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29751", os.path.join(root, "tests", "workers", "pretrain_dp_worker.py")]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=240,
+                       env=dict(os.environ, PMETAL_TEST_CPU="1"))
+    assert r.returncode == 0 and r.stdout.count("PRETRAIN_DP_WORKER_OK") == 2, r.stdout[-3000:]
+
+
 def test_activation_message_wire_format():
     import struct
 

@@ -227,6 +227,22 @@ def test_rmsnorm():
     _close(dw, wf.grad, rtol=3e-2, atol=0.5, what="rmsnorm dw")
 
 
+@pytest.mark.parametrize("T,H", [(64, 2048), (5, 1024), (300, 4096), (17, 2560)])
+def test_rmsnorm_few_rows(T, H):
+    """The one-CTA-per-row variant used for decode-sized inputs, with and without the residual add."""
+    nat = _nat()
+    from pmetal_b200.ops import reference as ref
+    torch.manual_seed(5)
+    x, res, w = _rand(T, H), _rand(T, H), (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    h, y, rstd = nat.rmsnorm_fwd(x, w, 1e-6, res)
+    hr = (x.float() + res.float()).bfloat16()
+    assert torch.equal(h, hr)
+    _close(y, ref.rms_norm(hr.float(), w.float(), 1e-6), what="rmsnorm fwd (rows)")
+    _, y2, rstd2 = nat.rmsnorm_fwd(x, w, 1e-6)
+    _close(y2, ref.rms_norm(x.float(), w.float(), 1e-6), what="rmsnorm fwd (rows, no residual)")
+    _close(rstd2, (x.float().pow(2).mean(-1) + 1e-6).rsqrt(), rtol=1e-3, atol=1e-3, what="rstd")
+
+
 def test_qknorm_rope():
     nat = _nat()
     from pmetal_b200.ops import reference as ref
@@ -366,13 +382,58 @@ def test_linear_ce():
     lab = torch.randint(0, V, (T,), device="cuda")
     lab[::7] = -100
     for wt in (w.t().contiguous(), None):
-        loss, n, dh = nat.linear_ce(h, w, wt, lab, -100, 256, True)
+        loss, _, n, dh = nat.linear_ce(h, w, wt, lab, -100, 256, True)
         hf = h.float().requires_grad_(True)
         ref = torch.nn.functional.cross_entropy(hf @ w.float().t(), lab, ignore_index=-100, reduction="sum")
         ref.backward()
         assert int(n) == int((lab != -100).sum())
         assert abs(loss.item() - ref.item()) / ref.item() < 5e-3
         _close(dh, hf.grad, rtol=3e-2, atol=2e-3, what="linear_ce dh")
+    nat.check_status()
+
+
+def test_trainable_dense_linear_and_head_with_z_loss():
+    """Full-parameter training pieces against fp32 autograd: y = x W^T (+ residual) with the weight gradient accumulated
+    into the fp32 master's .grad, and the chunked cross entropy with the z term and a trainable head."""
+    nat = _nat()
+    from pmetal_b200.ops import functional as F
+    torch.manual_seed(12)
+    T, K, N, V = 1500, 256, 384, 3000
+    x = _rand(T, K).requires_grad_(True)
+    res = _rand(T, N)
+    w = (torch.randn(N, K, device="cuda") * K ** -0.5).requires_grad_(True)
+    w.shadow = w.detach().bfloat16()
+    w.grad = torch.full_like(w, 0.25)                 # accumulation: what is there stays
+    y = F.dense_linear(x, w, w.shadow, res)
+    dy = _rand(T, N)
+    y.backward(dy)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.shadow.float().requires_grad_(True)
+    (xr @ wr.t() + res.float()).backward(dy.float())
+    _close(y, xr @ wr.t() + res.float(), what="dense fwd")
+    _close(x.grad, xr.grad, what="dense dx")
+    _close(w.grad - 0.25, wr.grad, rtol=2e-2, atol=2e-2 * float(wr.grad.abs().max()), what="dense dw")
+    # head: cross entropy + z term, gradients for hidden states and head weight
+    h = _rand(T, K).requires_grad_(True)
+    hw = (torch.randn(V, K, device="cuda") * K ** -0.5).requires_grad_(True)
+    hw.shadow = hw.detach().bfloat16()
+    lab = torch.randint(0, V, (T,), device="cuda")
+    lab[::5] = -100
+    z_coef = 0.05
+    total, ce, z = F.linear_cross_entropy_z(h, hw, lab, z_coef, chunk=512)
+    (total * 3.0).backward()
+    hf = h.detach().float().requires_grad_(True)
+    wf = hw.shadow.float().requires_grad_(True)
+    lg = hf @ wf.t()
+    m = lab != -100
+    lse = torch.logsumexp(lg, -1)
+    ce_ref = torch.nn.functional.cross_entropy(lg, lab, ignore_index=-100, reduction="sum") / m.sum()
+    z_ref = ((lse ** 2) * m).sum() / m.sum()
+    ((ce_ref + z_coef * z_ref) * 3.0).backward()
+    assert abs(float(ce) - float(ce_ref)) < 5e-3 * float(ce_ref) and abs(float(z) - float(z_ref)) < 1e-2 * float(z_ref)
+    assert abs(float(total) - float(ce_ref + z_coef * z_ref)) < 5e-3 * float(total)
+    _close(h.grad, hf.grad, rtol=3e-2, atol=3e-2 * float(hf.grad.abs().max()), what="ce+z dh")
+    _close(hw.grad, wf.grad, rtol=3e-2, atol=3e-2 * float(wf.grad.abs().max()), what="ce+z dW head")
     nat.check_status()
 
 

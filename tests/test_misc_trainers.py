@@ -66,7 +66,8 @@ def test_token_shards(tmp_path):
 
 
 def test_pretrain_loss_falls_and_checkpoint_resumes(tmp_path):
-    from pmetal_b200.trainer.pretrain import PretrainConfig, PretrainTrainer, z_loss
+    from pmetal_b200.ops.functional import linear_cross_entropy_z
+    from pmetal_b200.trainer.pretrain import PretrainConfig, PretrainTrainer
     torch.manual_seed(0)
     cfg = PretrainConfig(learning_rate=5e-3, min_lr=5e-3, warmup_steps=0, max_steps=6, micro_batch=2, seq_len=16,
                          z_loss_coef=1e-3, lr_scheduler="constant")
@@ -75,7 +76,9 @@ def test_pretrain_loss_falls_and_checkpoint_resumes(tmp_path):
     first = tr.train_step(data[:2])
     last = tr.run(iter(data))
     assert last["loss"] < first["loss"] and last["z_loss"] > 0 and tr.step_count == 6
-    assert float(z_loss(torch.zeros(3, 4), torch.zeros(5, 4))) == pytest.approx(math.log(5) ** 2)
+    tot, ce, z = linear_cross_entropy_z(torch.zeros(3, 4), torch.zeros(5, 4), torch.tensor([1, -100, 2]), 0.5)
+    assert float(z) == pytest.approx(math.log(5) ** 2) and float(ce) == pytest.approx(math.log(5))
+    assert float(tot) == pytest.approx(math.log(5) + 0.5 * math.log(5) ** 2)
     ck = str(tmp_path / "ck")
     tr.save_checkpoint(ck)
     tr2 = PretrainTrainer(tiny(3), cfg)
