@@ -705,6 +705,9 @@ def _serve_args(sp):
     p.add_argument("--max-seq-len", type=int, default=None, help="sizes the KV pool: slots x ceil(len / 64) blocks")
     p.add_argument("--fp8", action="store_true")
     p.add_argument("--device")
+    p.add_argument("--adapter", action="append", default=[], metavar="NAME=DIR",
+                   help="serve this LoRA adapter beside the base model (repeatable); a request selects it with "
+                        "\"adapter\": NAME or \"model\": NAME, and requests with different adapters share a batch")
     p.add_argument("--tp", type=int, default=1, help="cut attention heads (and dense feed-forward channels) over N GPUs")
     p.add_argument("--ep", type=int, default=0, help="cut experts over N GPUs (the same ranks as --tp; default: = --tp)")
     p.add_argument("--reduce", choices=["peer", "nccl"], default="peer",
@@ -760,9 +763,20 @@ def cmd_serve(a) -> int:
                 return 0
             shutdown_process_group()
             return 0
+    adapters = None
+    if a.adapter:
+        if world > 1:
+            print("error: --adapter is not available together with --tp", file=sys.stderr)
+            return 2
+        from ..lora.adapter import load_adapter_config
+        from ..lora.batched import AdapterSet
+        pairs = [x.split("=", 1) if "=" in x else (os.path.basename(os.path.normpath(x)), x) for x in a.adapter]
+        adapters = AdapterSet(model, len(pairs), load_adapter_config(pairs[0][1]).r)
+        for name, path in pairs:
+            adapters.load(name, path)
     try:
         serve(model, tok, tpl, a.host, a.port, eos, os.path.basename(os.path.normpath(mdir or a.model)), a.max_slots,
-              blocks, a.cb_max_queue_depth, cache_options=opts, channel=channel)
+              blocks, a.cb_max_queue_depth, cache_options=opts, channel=channel, adapters=adapters)
     finally:
         if world > 1:
             from ..parallel.dp import shutdown_process_group

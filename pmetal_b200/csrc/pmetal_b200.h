@@ -126,6 +126,18 @@ int pm_gemm_bf16_2sm(const void* A, int a_mn, int lda, int a_rows, const void* B
     out_mode, int ldd, const void* R, int ldr, int M, int N, int K, int K2, int n_store, float alpha, int splits,
     int seg_mode, const int* seg_end, int seg_r, int max_ctas, int* status, cudaStream_t stream);
 
+// ---------------------------------------------------------------- gemm_q4_2sm.cu
+// A [M, K] bf16 (K-major). codes: packed weight [w_rows, w_cols / 2] bytes, first element of a pair in the high nibble;
+// absmax (fp32) or absmax_q (+ am_scale / am_offset) hold one scale per 64 consecutive weights of a row.
+//   trans 0: D[M, w_rows] (K = w_cols);  trans 1: D[M, w_cols] (K = w_rows).
+// A2 / B2 (bf16, optional) add the low-rank product as in pm_gemm_bf16_2sm; seg_mode 0 or 1. D bf16 (+ R).
+// w_cols % 128 == 0 and w_rows % 64 == 0. Returns 0, a negative argument error or a CUDA error code.
+int pm_gemm_q4_2sm(const void* A, int lda, int a_rows, const void* codes, const float* absmax, const void*
+    absmax_q, float am_scale, float am_offset, int fp4, int w_rows, int w_cols, int trans, const void* A2, int
+    a2_mn, int lda2, int a2_k, const void* B2, int b2_mn, int ldb2, int b2_rows, void* D, int ldd, const void* R,
+    int ldr, int M, int K2, int n_store, float alpha, int seg_mode, const int* seg_end, int seg_r, int max_ctas,
+    int* status, cudaStream_t stream);
+
 // ---------------------------------------------------------------- gemm_tcgen05.cu
 // Returns 0 on success, negative on argument / descriptor errors, or the CUDA error code.
 //   a_rows/b_rows: extent of the operand along M / N as seen by the tensor map (rows beyond it read as zero).

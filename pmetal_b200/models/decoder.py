@@ -59,6 +59,8 @@ class FusedLinear(nn.Module):
         self.r = 0
         self.scale = 0.0
         self.active: Tuple[bool, ...] = tuple(False for _ in self.seg_sizes)
+        self.batched = None             # lora.batched.BatchedLoraAdapters: several adapters, one index per input row
+        self.adapter_rows: Optional[torch.Tensor] = None
 
     # -- LoRA management
     def add_lora(self, r: int, scale: float, active: Sequence[bool], use_rslora: bool = False,
@@ -115,6 +117,9 @@ class FusedLinear(nn.Module):
         return w
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.batched is not None and self.adapter_rows is not None and self.bias is None:
+            from ..lora.batched import batched_lora_linear
+            return batched_lora_linear(x, self.weight, self.batched, self.adapter_rows, residual)
         if self.weight.requires_grad and self.bias is None and self.lora_a is None:
             sh = getattr(self.weight, "shadow", None)           # full-parameter training: bf16 shadow of the fp32 master
             if sh is not None and ops.use_native(x) and self.in_features % 8 == 0 and self.out_features % 8 == 0:
@@ -131,7 +136,7 @@ class FusedLinear(nn.Module):
     def gemv_ok(self, m: int) -> bool:
         """Decode fast path: a few rows, no bias, and either a plain bf16 weight or a 4-bit (NF4 / FP4) packed weight
         that the mat-vec kernel expands on the fly."""
-        if m > GEMV_MAX_ROWS or self.bias is not None:
+        if m > GEMV_MAX_ROWS or self.bias is not None or (self.batched is not None and self.adapter_rows is not None):
             return False
         q = getattr(self, "qweight", None)
         if q is not None:

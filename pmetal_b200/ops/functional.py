@@ -247,11 +247,17 @@ class _LoraLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, w_t, a32, b32, a, b, seg_sizes, r, scale, residual, qweight=None):
         nat = _native()
-        if qweight is not None:      # QLoRA: dequantise into a transient buffer; only the packed weight is kept
+        fused_q = qweight is not None and nat.q4_gemm_ok(qweight, x.shape[0], seg_sizes)
+        if qweight is not None and not fused_q:
+            # QLoRA off the fused shapes: dequantise into a transient buffer; only the packed weight is kept
             from ..lora.qlora import dequantize_weight
             w, w_t = dequantize_weight(qweight), None
         t = nat.lora_t(x, a, scale) if a is not None else None    # [M, 64-padded] = s x A^T
-        y = nat.gemm_lora(x, w, t, b, seg_sizes, r, residual)
+        if fused_q:       # the GEMM expands the 4-bit codes on their way into the tensor cores
+            y = nat.gemm_q4_lora(x, qweight, t, b, seg_sizes, r, residual)
+        else:
+            y = nat.gemm_lora(x, w, t, b, seg_sizes, r, residual)
+        ctx.fused_q = fused_q
         ctx.save_for_backward(x, None if qweight is not None else w, w_t, a, b, t)
         ctx.params = (a32, b32)
         ctx.qweight = qweight
@@ -264,7 +270,8 @@ class _LoraLinearFn(torch.autograd.Function):
         a32, b32 = ctx.params
         seg_sizes, r, scale, has_res = ctx.cfg
         nat = _native()
-        if ctx.qweight is not None:
+        fused_q = ctx.fused_q and _native().MN_MAJOR
+        if ctx.qweight is not None and not fused_q:
             from ..lora.qlora import dequantize_weight
             w = dequantize_weight(ctx.qweight)
         dy = dy.contiguous()
@@ -272,7 +279,7 @@ class _LoraLinearFn(torch.autograd.Function):
         if a is not None:
             dt = nat.lora_dt(dy, b, seg_sizes, r, scale)          # [M, 64-padded] = s dY_seg B_seg
             if ctx.needs_input_grad[0]:
-                dx = nat.gemm_lora_dx(dy, w, w_t, dt, a)
+                dx = nat.gemm_q4_lora_dx(dy, ctx.qweight, dt, a) if fused_q else nat.gemm_lora_dx(dy, w, w_t, dt, a)
 
             def target(p32):
                 g = p32.grad
@@ -285,7 +292,7 @@ class _LoraLinearFn(torch.autograd.Function):
             nat.lora_da(dt, x, a.shape[0], ga)
             nat.lora_db(dy, t, seg_sizes, r, gb)
         elif ctx.needs_input_grad[0]:
-            dx = nat.gemm_lora_dx(dy, w, w_t, None, None)
+            dx = nat.gemm_q4_lora_dx(dy, ctx.qweight, None, None) if fused_q else nat.gemm_lora_dx(dy, w, w_t, None, None)
         return dx, None, None, da, db, None, None, None, None, None, (dy if has_res else None), None
 
 

@@ -200,6 +200,7 @@ def raw_gemm(A, a_mn, lda, a_rows, B, b_mn, ldb, b_rows, D, out_mode, ldd, M, N,
 
 
 SPLIT_K = os.environ.get("PMETAL_GEMM_SPLITK", "1") == "1"
+FUSED_Q4 = os.environ.get("PMETAL_FUSED_Q4", "1") == "1"
 _SPLITK_WS = {}
 
 
@@ -310,6 +311,58 @@ def gemm_lora_dx(dy, w, w_t, dt, a) -> torch.Tensor:
     else:
         wt = w.t().contiguous()
         raw_gemm(dy, 0, dy.stride(0), M, wt, 0, N, kin, out, 0, kin, M, kin, N, bn=bn, **kw)
+    return out
+
+
+def q4_gemm_ok(q, M: int, seg_sizes: Sequence[int] = ()) -> bool:
+    """Whether the GEMMs against packed weight ``q`` can expand it on the fly (csrc/gemm_q4_2sm.cu): 4-bit codes in blocks
+    of 64 that line up with the rows, enough token rows for 256-row tiles, LoRA segments on tile boundaries."""
+    if not FUSED_Q4 or q is None or q.scheme not in ("nf4", "fp4") or q.block_size != 64 or len(q.shape) != 2:
+        return False
+    n, k = q.shape
+    return (M >= 256 and k % 128 == 0 and n % 64 == 0 and q.data.is_cuda
+            and all(s % 256 == 0 for s in tuple(seg_sizes)[:-1]))
+
+
+def _q4_call(x, q, trans: int, out, residual, kw) -> None:
+    n, k = q.shape
+    segs = _seg_ends(kw.get("seg_sizes", ())) if kw.get("seg_mode", 0) else None
+    A2, B2 = kw.get("A2"), kw.get("B2")
+    lib().pm_gemm_q4_2sm.restype = c_int
+    rc = lib().pm_gemm_q4_2sm(_p(x), c_int(x.stride(0)), c_int(x.shape[0]), _p(q.data), _p(q.absmax), _p(q.absmax_q),
+                              c_float(q.absmax_scale), c_float(q.absmax_offset), c_int(int(q.scheme == "fp4")), c_int(n),
+                              c_int(k), c_int(trans), _p(A2), c_int(kw.get("a2_mn", 0)), c_int(kw.get("lda2", 0)),
+                              c_int(kw.get("a2_k", 0)), _p(B2), c_int(kw.get("b2_mn", 0)), c_int(kw.get("ldb2", 0)),
+                              c_int(kw.get("b2_rows", 0)), _p(out), c_int(out.stride(0)), _p(residual),
+                              c_int(residual.stride(0) if residual is not None else 0), c_int(x.shape[0]),
+                              c_int(kw.get("K2", 0)), c_int(0), c_float(1.0), c_int(kw.get("seg_mode", 0)), segs,
+                              c_int(kw.get("seg_r", 0)), c_int(0), _p(status_word(x.device)), _stream())
+    _chk(rc, "pm_gemm_q4_2sm")
+
+
+def gemm_q4_lora(x, q, t, b, seg_sizes, r, residual=None) -> torch.Tensor:
+    """y = x W^T + sum_seg t[:, seg] b_seg^T (+ residual) with W given as packed 4-bit codes (expanded inside the GEMM)."""
+    M = x.shape[0]
+    N = q.shape[0]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    kw = {}
+    if t is not None:
+        kw = dict(A2=t, a2_mn=0, lda2=t.stride(0), a2_k=t.shape[1], B2=b, b2_mn=0, ldb2=b.stride(0), b2_rows=N, K2=r,
+                  seg_mode=1 if len(seg_sizes) > 1 else 0, seg_sizes=seg_sizes, seg_r=r)
+    _q4_call(x, q, 0, out, residual, kw)
+    return out
+
+
+def gemm_q4_lora_dx(dy, q, dt, a) -> torch.Tensor:
+    """dx = dy W (+ dt[:, :nr] a) with W given as packed 4-bit codes."""
+    M = dy.shape[0]
+    kin = q.shape[1]
+    out = torch.empty(M, kin, dtype=torch.bfloat16, device=dy.device)
+    kw = {}
+    if dt is not None:
+        nr = a.shape[0]
+        kw = dict(A2=dt, a2_mn=0, lda2=dt.stride(0), a2_k=dt.shape[1], B2=a, b2_mn=1, ldb2=a.stride(0), b2_rows=kin, K2=nr)
+    _q4_call(dy, q, 1, out, None, kw)
     return out
 
 

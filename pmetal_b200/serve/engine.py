@@ -57,6 +57,7 @@ class Request:
     decode: Optional[Callable[[List[int]], str]] = None
     top_logprobs: int = 0                                                   # alternatives recorded per generated token
     top_entries: List[List[tuple]] = field(default_factory=list)            # per token: [(token id, logprob), ...]
+    adapter: Optional[str] = None                                           # LoRA adapter of this request (multi-adapter serving)
     on_token: Optional[Callable[[int, Optional[float]], None]] = None       # called from the engine thread
     on_done: Optional[Callable[["Request"], None]] = None
     # filled by the engine
@@ -101,12 +102,16 @@ class EngineStats:
 class ContinuousBatchEngine:
     def __init__(self, model, eos_ids: Sequence[int] = (), max_slots: int = 64, num_blocks: int = 8192,
                  prefill_chunk: int = PREFILL_CHUNK, prefix_cache: bool = True, max_queue: int = 1024,
-                 cache_options: Optional[dict] = None):
+                 cache_options: Optional[dict] = None, adapters=None):
         self.model = model
+        self.adapters = adapters        # lora.batched.AdapterSet: every request picks an adapter (or none) by name
         opts = dict(cache_options or {})
         self.gen = Generator(model, cache=model.new_cache(num_blocks, **opts)) if opts else Generator(model, num_blocks=num_blocks)
         if opts.get("window"):
             prefix_cache = False      # a rotating cache recycles prompt blocks: there is no stable prefix to share
+        if adapters is not None:
+            self.gen.cuda_graphs = False      # the adapter of every row changes from step to step
+            prefix_cache = False              # cached keys/values depend on the adapter that produced them
         self.cache = self.gen.cache
         self.device = self.gen.device
         self.eos = set(eos_ids)
@@ -126,6 +131,10 @@ class ContinuousBatchEngine:
 
     # ------------------------------------------------------------------ submission
     def submit(self, req: Request) -> Request:
+        if req.adapter:
+            if self.adapters is None:
+                raise KeyError(f"no adapters are loaded (request asked for {req.adapter!r})")
+            self.adapters.index(req.adapter)         # raises KeyError for an unknown name
         with self._lock:
             if len(self.queue) >= self.max_queue:
                 raise RuntimeError("queue full")
@@ -311,6 +320,8 @@ class ContinuousBatchEngine:
             take = min(self.prefill_chunk, len(req.prompt) - pre.prefill_pos)
             meta = self.cache.prepare([pre.seq], [take])
             ids = torch.tensor(req.prompt[pre.prefill_pos:pre.prefill_pos + take], dtype=torch.int64, device=self.device)
+            if self.adapters is not None:
+                self.adapters.set_rows([self.adapters.index(req.adapter)] * take)
             logits = self.model.forward_paged(ids, self.cache, meta)
             pre.prefill_pos += take
             if pre.prefill_pos == len(req.prompt):
@@ -324,6 +335,8 @@ class ContinuousBatchEngine:
         if dec:
             t0 = time.perf_counter()
             toks = torch.tensor([s.last_token for s in dec], dtype=torch.int64, device=self.device)
+            if self.adapters is not None:
+                self.adapters.set_rows([self.adapters.index(s.req.adapter) for s in dec])
             logits = self.gen.decode_step([s.seq for s in dec], toks)
             ids, lps = self._sample(logits, dec)
             for j, s in enumerate(list(dec)):

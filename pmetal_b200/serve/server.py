@@ -95,17 +95,29 @@ class ServerState:
                         m.get("name")) for m in messages]
         return self.tok.encode_with_special_tokens(self.template.apply_inference(msgs, no_thinking, tools))
 
+    def adapter_of(self, body: Dict[str, Any]) -> Optional[str]:
+        """Adapter a request asks for: the ``adapter`` field, or a ``model`` that names a loaded adapter."""
+        ad = self.engine.adapters
+        name = body.get("adapter")
+        if name:
+            return str(name)
+        m = body.get("model")
+        if ad is not None and isinstance(m, str) and m in ad.names:
+            return m
+        return None
+
     async def run(self, prompt: List[int], params: SamplingParams, stop=None, want_logprobs=False,
-                  top_logprobs: int = 0) -> Request:
+                  top_logprobs: int = 0, adapter: Optional[str] = None) -> Request:
         loop = asyncio.get_running_loop()
         fut = loop.create_future()
         req = Request(prompt, params, [], want_logprobs or top_logprobs > 0, stop_strings=_stop_list(stop),
-                      decode=self.tok.decode, top_logprobs=top_logprobs,
+                      decode=self.tok.decode, top_logprobs=top_logprobs, adapter=adapter,
                       on_done=lambda r: loop.call_soon_threadsafe(fut.set_result, r))
         self.engine.submit(req)
         return await fut
 
-    async def stream(self, prompt: List[int], params: SamplingParams, stop=None) -> AsyncIterator[tuple]:
+    async def stream(self, prompt: List[int], params: SamplingParams, stop=None,
+                     adapter: Optional[str] = None) -> AsyncIterator[tuple]:
         """Yields (text piece, finish_reason or None). With stop strings the newest tokens are held back (as many
         tokens as the longest stop string has characters) so that text which turns out to be the beginning of a stop
         string is never sent; when the request ends, only the tokens the engine kept are flushed."""
@@ -113,7 +125,7 @@ class ServerState:
         q: asyncio.Queue = asyncio.Queue()
         stops = _stop_list(stop)
         hold = max((len(x) for x in stops), default=0)
-        req = Request(prompt, params, [], False, stop_strings=stops, decode=self.tok.decode,
+        req = Request(prompt, params, [], False, stop_strings=stops, decode=self.tok.decode, adapter=adapter,
                       on_token=lambda t, lp: loop.call_soon_threadsafe(q.put_nowait, ("tok", t)),
                       on_done=lambda r: loop.call_soon_threadsafe(q.put_nowait, ("done", (r.finish_reason, len(r.output)))))
         self.engine.submit(req)
@@ -172,8 +184,13 @@ def create_app(state: ServerState):
 
     @app.get("/v1/models")
     async def models():
-        return {"object": "list", "data": [{"id": state.model_name, "object": "model", "created": int(state.started),
-                                            "owned_by": "pmetal"}]}
+        data = [{"id": state.model_name, "object": "model", "created": int(state.started), "owned_by": "pmetal"}]
+        ad = state.engine.adapters
+        for name in (ad.names if ad is not None else []):         # every loaded adapter is addressable as a model
+            if name:
+                data.append({"id": name, "object": "model", "created": int(state.started), "owned_by": "pmetal",
+                             "parent": state.model_name})
+        return {"object": "list", "data": data}
 
     @app.get("/v1/metrics")
     async def metrics():
@@ -197,7 +214,7 @@ def create_app(state: ServerState):
                     yield sse({**base, "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""},
                                                     "finish_reason": None}]})
                     whole = []
-                    async for piece, fin in state.stream(prompt, params, body.get("stop")):
+                    async for piece, fin in state.stream(prompt, params, body.get("stop"), adapter=state.adapter_of(body)):
                         if fin is None:
                             whole.append(piece)
                             yield sse({**base, "choices": [{"index": 0, "delta": {"content": piece}, "finish_reason": None}]})
@@ -211,7 +228,7 @@ def create_app(state: ServerState):
                     yield sse(b"[DONE]")
                 return StreamingResponse(gen(), media_type="text/event-stream")
             top_n = min(int(body.get("top_logprobs") or 0), 20) if body.get("logprobs") else 0
-            req = await state.run(prompt, params, body.get("stop"), bool(body.get("logprobs")), top_n)
+            req = await state.run(prompt, params, body.get("stop"), bool(body.get("logprobs")), top_n, adapter=state.adapter_of(body))
         text = state.text_of(req)
         calls = try_parse_tool_calls(text) if body.get("tools") else None
         if calls:                                   # a structured call replaces the text (routes.rs:304-309)
@@ -251,14 +268,14 @@ def create_app(state: ServerState):
             if body.get("stream"):
                 async def gen():
                     base = {"id": rid, "object": "text_completion", "created": created, "model": state.model_name}
-                    async for piece, fin in state.stream(prompt, params, body.get("stop")):
+                    async for piece, fin in state.stream(prompt, params, body.get("stop"), adapter=state.adapter_of(body)):
                         yield sse({**base, "choices": [{"index": 0, "text": piece,
                                                         "finish_reason": None if fin is None else state.finish(fin)}]})
                     yield sse(b"[DONE]")
                 return StreamingResponse(gen(), media_type="text/event-stream")
             n_lp = body.get("logprobs")
             top_n = min(int(n_lp), 20) if isinstance(n_lp, int) and not isinstance(n_lp, bool) else 0
-            req = await state.run(prompt, params, body.get("stop"), bool(n_lp), top_n)
+            req = await state.run(prompt, params, body.get("stop"), bool(n_lp), top_n, adapter=state.adapter_of(body))
         choice = {"index": 0, "text": state.text_of(req), "finish_reason": state.finish(req.finish_reason)}
         if n_lp:                                    # legacy completions layout (routes.rs:446-471)
             toks = [state.tok.decode([t]) for t in req.output]
@@ -319,7 +336,7 @@ def create_app(state: ServerState):
                     yield ev("content_block_start", {"type": "content_block_start", "index": 0,
                                                      "content_block": {"type": "text", "text": ""}})
                     n = 0
-                    async for piece, fin in state.stream(prompt, params, stop):
+                    async for piece, fin in state.stream(prompt, params, stop, adapter=state.adapter_of(body)):
                         if fin is None:
                             n += 1
                             yield ev("content_block_delta", {"type": "content_block_delta", "index": 0,
@@ -331,11 +348,16 @@ def create_app(state: ServerState):
                                 "usage": {"output_tokens": n}})
                     yield ev("message_stop", {"type": "message_stop"})
                 return StreamingResponse(gen(), media_type="text/event-stream")
-            req = await state.run(prompt, params, stop)
+            req = await state.run(prompt, params, stop, adapter=state.adapter_of(body))
         return {"id": mid, "type": "message", "role": "assistant", "model": state.model_name,
                 "content": [{"type": "text", "text": state.text_of(req)}],
                 "stop_reason": "max_tokens" if req.finish_reason == "length" else "end_turn", "stop_sequence": None,
                 "usage": {"input_tokens": len(prompt), "output_tokens": len(req.output)}}
+
+    @app.exception_handler(KeyError)
+    async def unknown_adapter(_, exc):
+        return JSONResponse(status_code=404, content={"error": {"message": str(exc.args[0] if exc.args else exc),
+                                                                "type": "invalid_request_error"}})
 
     @app.exception_handler(RuntimeError)
     async def runtime_error(_, exc):
@@ -346,13 +368,13 @@ def create_app(state: ServerState):
 
 def serve(model, tokenizer, template=None, host: str = "127.0.0.1", port: int = 8080, eos_ids=(), model_name="pmetal-b200",
           max_slots: int = 64, num_blocks: int = 8192, max_queue: int = 1024, cache_options: Optional[dict] = None,
-          channel=None):
+          channel=None, adapters=None):
     """Blocking: starts the engine thread and the HTTP server. ``cache_options`` (quant / window / sink) go to
     ``DecoderLM.new_cache``. With a model cut over several ranks, ``channel`` (serve/replica.py) is the leader's end of
     the step channel: the ranks that follow are released when the server stops."""
     import uvicorn
     engine = ContinuousBatchEngine(model, eos_ids, max_slots=max_slots, num_blocks=num_blocks, max_queue=max_queue,
-                                   cache_options=cache_options)
+                                   cache_options=cache_options, adapters=adapters)
     engine.start()
     try:
         uvicorn.run(create_app(ServerState(engine, tokenizer, template, model_name)), host=host, port=port, log_level="info")

@@ -524,3 +524,34 @@ def test_fused_dp_step_gives_up_on_a_silent_peer_and_recovers():
     ref.adamw_step(pr, g0.clone(), mr, vr, 1, 1e-2, 0.9, 0.999, 1e-8, 0.0)
     assert torch.allclose(p0, pr, rtol=1e-5, atol=1e-6) and int(pad0[24]) == 2
     assert torch.allclose(s0.float(), pr, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("T", [40, 700])
+def test_batched_lora_rows_pick_their_adapter(T):
+    """Multi-adapter LoRA on the grouped kernels (few rows: swapped operands; many rows: 128-row tiles) against the
+    per-adapter loop in fp32."""
+    _nat()
+    from pmetal_b200.lora.batched import NO_ADAPTER, BatchedLoraAdapters, batched_lora_linear
+    torch.manual_seed(31)
+    K, segs, r, n = 256, (256, 128, 128), 16, 5
+    st = BatchedLoraAdapters(n, K, segs, r, torch.bfloat16, "cuda")
+    facs = []
+    for i in range(n - 1):                      # the last slot stays empty
+        a = (torch.randn(len(segs) * r, K, device="cuda") * 0.1).bfloat16()
+        b = (torch.randn(sum(segs), r, device="cuda") * 0.1).bfloat16()
+        st.load_adapter(i, a, b, 1.0 + 0.5 * i)
+        facs.append((a, b, 1.0 + 0.5 * i))
+    x = (torch.randn(T, K, device="cuda")).bfloat16()
+    w = (torch.randn(sum(segs), K, device="cuda") * K ** -0.5).bfloat16()
+    ids = torch.randint(-1, n - 1, (T,), device="cuda")
+    y = batched_lora_linear(x, w, st, ids)
+    ref = x.float() @ w.float().t()
+    for i, (a, b, sc) in enumerate(facs):
+        rows = (ids == i).nonzero().flatten()
+        t = (x[rows].float() @ a.float().t()).bfloat16().float()
+        o = 0
+        for s, sz in enumerate(segs):
+            ref[rows, o:o + sz] += sc * (t[:, s * r:(s + 1) * r] @ b[o:o + sz].float().t())
+            o += sz
+    _close(y, ref, what=f"batched lora T={T}")
+    assert bool((ids == NO_ADAPTER).any())

@@ -437,6 +437,49 @@ def test_trainable_dense_linear_and_head_with_z_loss():
     nat.check_status()
 
 
+@pytest.mark.parametrize("scheme,dq", [("nf4", True), ("nf4", False), ("fp4", False)])
+def test_gemm_expands_4bit_weight_in_flight(scheme, dq):
+    """Forward and input-gradient GEMMs that read the packed 4-bit weight directly, with and without the low-rank
+    second product, against fp32 products with the dequantised weight (which is what the unfused path feeds the GEMM)."""
+    nat = _nat()
+    from pmetal_b200.lora import nf4
+    torch.manual_seed(13)
+    M, K, segs, r = 700, 384, (512, 256, 256), 16
+    N = sum(segs)
+    w = torch.randn(N, K, device="cuda") * K ** -0.5
+    q = nf4.quantize(w, scheme, 64, double_quant=dq).to("cuda")
+    wd = nf4.dequantize(q, torch.float32).bfloat16().float()
+    assert nat.q4_gemm_ok(q, M, segs)
+    x, res = _rand(M, K), _rand(M, N)
+    a = _rand(len(segs) * r, K, scale=K ** -0.5)
+    b = _rand(N, r, scale=0.2)
+    t = nat.lora_t(x, a, 2.0)
+    y = nat.gemm_q4_lora(x, q, t, b, segs, r, res)
+    nat.check_status()
+    ref = x.float() @ wd.t() + res.float()
+    o = 0
+    for i, sz in enumerate(segs):
+        ref[:, o:o + sz] += t[:, i * r:(i + 1) * r].float() @ b[o:o + sz].float().t()
+        o += sz
+    _close(y, ref, what=f"{scheme} fused forward + lora")
+    _close(nat.gemm_q4_lora(x, q, None, None, segs, r), x.float() @ wd.t(), what=f"{scheme} fused forward")
+    dy = _rand(M, N)
+    dt = nat.lora_dt(dy, b, segs, r, 2.0)
+    dx = nat.gemm_q4_lora_dx(dy, q, dt, a)
+    nat.check_status()
+    _close(dx, dy.float() @ wd + dt[:, :len(segs) * r].float() @ a.float(), rtol=2e-2, atol=5e-2, what=f"{scheme} fused dx + lora")
+    _close(nat.gemm_q4_lora_dx(dy, q, None, None), dy.float() @ wd, rtol=2e-2, atol=5e-2, what=f"{scheme} fused dx")
+    # a shape with several tiles per pair and a ragged last column tile
+    M2, K2, N2 = 1100, 1152, 2560 + 128
+    w2 = torch.randn(N2, K2, device="cuda") * K2 ** -0.5
+    q2 = nf4.quantize(w2, scheme, 64, double_quant=dq).to("cuda")
+    wd2 = nf4.dequantize(q2, torch.float32).bfloat16().float()
+    x2, dy2 = _rand(M2, K2), _rand(M2, N2)
+    _close(nat.gemm_q4_lora(x2, q2, None, None, (N2,), 0), x2.float() @ wd2.t(), what=f"{scheme} fused forward (large)")
+    _close(nat.gemm_q4_lora_dx(dy2, q2, None, None), dy2.float() @ wd2, rtol=2e-2, atol=8e-2, what=f"{scheme} fused dx (large)")
+    nat.check_status()
+
+
 def test_adamw_and_sumsq():
     nat = _nat()
     from pmetal_b200.ops import reference as ref
