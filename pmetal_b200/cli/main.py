@@ -48,6 +48,10 @@ def _add_train(sp):
     p.add_argument("--no-jit-compilation", action="store_true", help="do not capture the step in a CUDA graph")
     p.add_argument("--no-gradient-checkpointing", action="store_true")
     p.add_argument("--gradient-checkpointing-layers", type=int, default=0)
+    p.add_argument("--activation-policy", choices=["save", "recompute", "offload-cpu", "offload-disk", "smart"], default=None,
+                   help="what every decoder block does with the activations it needs for backward: keep them, recompute "
+                        "them, park them in pinned host memory / on disk, or decide from the memory in use")
+    p.add_argument("--offload-dir", default=None, help="directory for --activation-policy offload-disk")
     p.add_argument("--log-metrics")
     p.add_argument("--embedding-lr", type=float, default=None)
     p.add_argument("--warmup-steps", type=int, default=0)
@@ -120,6 +124,7 @@ def cmd_train(a) -> int:
     job.pack_max_seq_len = a.pack_max_seq_len
     job.use_cuda_graph = not a.no_jit_compilation
     job.gradient_checkpointing_layers = 0 if a.no_gradient_checkpointing else a.gradient_checkpointing_layers
+    job.activation_policy, job.offload_dir = a.activation_policy, a.offload_dir
     job.log_metrics, job.resume, job.adaptive_lr = a.log_metrics, a.resume, not a.no_adaptive_lr
     job.resume_bundle = a.resume_bundle
     job.tensorboard_dir = a.tensorboard

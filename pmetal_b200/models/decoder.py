@@ -321,11 +321,17 @@ class DecoderLM(nn.Module):
         lo, hi = layer_range if layer_range is not None else (0, len(self.layers))
         x = hidden_in if hidden_in is not None else F.embedding(input_ids, ops.live(self.embed_tokens))
         rope = ops.rope_table(positions, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scale)
+        policies = getattr(self, "layer_policies", None) if self.training else None      # utils/offload.py plan
         for i in range(lo, hi):
             layer = self.layers[i]
-            if self.gradient_checkpointing and self.training and (i % self.gradient_checkpointing == 0):
+            pol = policies[i] if policies is not None else None
+            if pol == "recompute" or (pol is None and self.gradient_checkpointing and self.training
+                                      and (i % self.gradient_checkpointing == 0)):
                 from torch.utils.checkpoint import checkpoint
                 x = checkpoint(layer, x, rope, cu_seqlens, seq_start, use_reentrant=False)
+            elif pol in ("offload_cpu", "offload_disk") and getattr(self, "activation_offloader", None) is not None:
+                with self.activation_offloader:       # what this block saves for backward waits in host memory
+                    x = layer(x, rope, cu_seqlens, seq_start)
             else:
                 x = layer(x, rope, cu_seqlens, seq_start)
         if hi < len(self.layers):

@@ -43,6 +43,8 @@ class TrainingJobConfig:
     packs_per_batch: Optional[int] = None
     use_cuda_graph: bool = True
     gradient_checkpointing_layers: int = 0
+    activation_policy: Optional[str] = None      # save | recompute | offload-cpu | offload-disk | smart (utils/offload.py)
+    offload_dir: Optional[str] = None
     log_metrics: Optional[str] = None
     tensorboard_dir: Optional[str] = None
     resume: bool = False
@@ -257,6 +259,20 @@ def run_training(job: TrainingJobConfig, phase_cb: Optional[Callable[[str], None
         apply_lora(model, job.lora, seed=tcfg.seed)
         if job.gradient_checkpointing_layers:
             model.gradient_checkpointing = job.gradient_checkpointing_layers
+        if job.activation_policy:
+            from ..utils import offload as off
+            n_layers = len(model.layers)
+            if job.activation_policy == "smart":
+                used = 0.0
+                if torch.cuda.is_available() and model.embed_tokens.is_cuda:
+                    free, total = torch.cuda.mem_get_info(model.embed_tokens.device)
+                    used = (total - free) / total
+                sc = off.SmartCheckpointConfig().with_cpu_offload()
+                plan = off.plan_decoder_layers(sc, n_layers, bool(getattr(model.cfg, "num_experts", 0)), used)
+            else:
+                plan = [job.activation_policy.replace("-", "_")] * n_layers
+            off.apply_to_model(model, plan, off.OffloadConfig(offload_dir=job.offload_dir))
+            job.use_cuda_graph = False           # host copies and recomputation do not replay from a captured step
         model.prepare_for_training()
         cbs = list(callbacks or []) + [LoggingCallback(tcfg.logging_steps)]
         if getattr(job, "tensorboard_dir", None) and rank == 0:
