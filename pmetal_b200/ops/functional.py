@@ -41,6 +41,9 @@ def native_enabled(t: torch.Tensor) -> bool:
     return (not _FORCE_REF) and t.is_cuda and _native().available()
 
 
+PAD_SMALL_HEADS = os.environ.get("PMETAL_PAD_SMALL_HEADS", "1") == "1"
+
+
 def use_native(t: torch.Tensor) -> bool:
     if _FORCE_REF or not t.is_cuda:
         return False
@@ -161,6 +164,41 @@ class _AttnBlockFn(torch.autograd.Function):
         return (dqkv, dqw, dkw) + (None,) * 9
 
 
+class _AttnCoreFn(torch.autograd.Function):
+    """Varlen causal attention on already normalised / rotated q, k and v [T, h, 128] (the tcgen05 kernels)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, seq_start, scale, window):
+        nat = _native()
+        o, lse = nat.attn_fwd(q, k, v, seq_start, scale, window)
+        ctx.save_for_backward(q, k, v, o, lse, seq_start)
+        ctx.cfg = (scale, window)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, seq_start = ctx.saved_tensors
+        scale, window = ctx.cfg
+        dq, dk, dv = _native().attn_bwd(do.contiguous(), q, k, v, o, lse, seq_start, scale, window)
+        return dq, dk, dv, None, None, None
+
+
+def _attention_padded_heads(qkv, q_weight, k_weight, cos, sin, seq_start, hq, hkv, d, eps, scale, window):
+    """Head sizes below 128 (64, 80, 96, ...) on the 128-wide kernels: QK-norm and RoPE at the true width, then q, k and
+    v are zero-padded to 128 channels (zeros add nothing to q.k, and the padded output channels are dropped)."""
+    T = qkv.shape[0]
+    q = qkv[:, :hq * d].view(T, hq, d)
+    k = qkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+    if q_weight is not None:
+        q, k = ref.rms_norm(q, q_weight, eps), ref.rms_norm(k, k_weight, eps)
+    q, k = ref.apply_rope(q, cos, sin), ref.apply_rope(k, cos, sin)
+    pad = (0, 128 - d)
+    qp, kp, vp = (F.pad(t, pad).contiguous() for t in (q, k, v))
+    o = _AttnCoreFn.apply(qp, kp, vp, seq_start, scale, window)
+    return o[..., :d].reshape(T, hq * d)
+
+
 def attention_block(qkv: torch.Tensor, q_weight, k_weight, cos: torch.Tensor, sin: torch.Tensor,
                     cu_seqlens: torch.Tensor, seq_start: Optional[torch.Tensor], hq: int, hkv: int, d: int,
                     eps: float, scale: Optional[float] = None, window: int = 0, softcap: float = 0.0) -> torch.Tensor:
@@ -171,6 +209,10 @@ def attention_block(qkv: torch.Tensor, q_weight, k_weight, cos: torch.Tensor, si
         if seq_start is None:
             seq_start = ref.seq_starts_from_cu(cu_seqlens, T)
         return _AttnBlockFn.apply(qkv, q_weight, k_weight, cos, sin, seq_start, hq, hkv, d, eps, scale, window)
+    if use_native(qkv) and d < 128 and d % 8 == 0 and softcap == 0.0 and PAD_SMALL_HEADS:
+        if seq_start is None:
+            seq_start = ref.seq_starts_from_cu(cu_seqlens, T)
+        return _attention_padded_heads(qkv, q_weight, k_weight, cos, sin, seq_start, hq, hkv, d, eps, scale, window)
     q = qkv[:, :hq * d].view(T, hq, d)
     k = qkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d)
     v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)

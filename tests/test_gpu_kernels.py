@@ -480,6 +480,40 @@ def test_gemm_expands_4bit_weight_in_flight(scheme, dq):
     nat.check_status()
 
 
+@pytest.mark.parametrize("d,qk_norm", [(64, False), (96, True), (80, False)])
+def test_attention_block_small_heads_run_on_the_128_wide_kernels(d, qk_norm):
+    """Head sizes below 128 go through the tensor-core attention kernels zero-padded to 128 channels; forward and the
+    gradient of the fused projection match the fp32 per-document reference."""
+    nat = _nat()
+    from pmetal_b200.ops import functional as F
+    from pmetal_b200.ops import reference as ref
+    torch.manual_seed(3)
+    hq, hkv = 4, 2
+    lens = [300, 17, 511, 200]
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    pos = torch.cat([torch.arange(n) for n in lens]).to(torch.int32).cuda()
+    cos, sin = ref.rope_cos_sin(pos, d, 10000.0)
+    qkv = (_rand(T, (hq + 2 * hkv) * d, scale=0.7)).requires_grad_(True)
+    qw = kw = None
+    if qk_norm:
+        qw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+        kw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    n0 = nat.LAUNCHES
+    o = F.attention_block(qkv, qw, kw, cos, sin, cu, None, hq, hkv, d, 1e-6)
+    assert nat.LAUNCHES > n0                                   # the native kernels ran
+    do = _rand(T, hq * d)
+    o.backward(do)
+    with F.force_reference():
+        q32 = qkv.detach().float().requires_grad_(True)
+        o_ref = F.attention_block(q32, None if qw is None else qw.float(), None if kw is None else kw.float(), cos, sin, cu,
+                                  None, hq, hkv, d, 1e-6)
+        o_ref.backward(do.float())
+    _close(o, o_ref, rtol=3e-2, atol=3e-2, what=f"attention d={d}")
+    _close(qkv.grad, q32.grad, rtol=5e-2, atol=5e-2 * float(q32.grad.abs().max()), what=f"attention d={d} grad")
+    nat.check_status()
+
+
 def test_adamw_and_sumsq():
     nat = _nat()
     from pmetal_b200.ops import reference as ref
