@@ -173,6 +173,25 @@ int pm_grouped_gemm(int mode, const void* a, int lda, const void* b, int ldb, vo
 int pm_grouped_gemm_skinny(const void* x, int ldx, int rows, const void* w, int ldw, void* y, int ldy, const int*
     off, int E, int N, int K, int bn, int swiglu, float alpha, int* status, cudaStream_t stream);
 
+// ---------------------------------------------------------------- mhc.cu
+// x [T, n, C] bf16; either phi [n C, n^2 + 2n] fp32 (dot products formed here) or raw [T, ld_raw] fp32 = x . phi computed by
+// the caller; bias [n^2 + 2n], alpha [3]; n in {2, 4, 8}, C % 8 == 0, iters <= 32.
+int pm_mhc_mappings(const void* x, const float* phi, const float* raw, int ld_raw, const float* bias, const float*
+    alpha, int T, int n, int C, int iters, float* h_tilde, float* rms_inv, float* h_pre, float* h_post, float*
+    h_res, cudaStream_t st);
+int pm_mhc_pre(const void* x, const float* h_pre, int T, int n, int C, void* h_in, cudaStream_t st);
+int pm_mhc_post_res(const void* x, const void* h_out, const float* h_res, const float* h_post, int T, int n, int C,
+    void* x_out, cudaStream_t st);
+int pm_mhc_mix_bwd(const void* x, const void* h_out, const void* dh_in, const void* dx_out, const float* h_pre,
+    const float* h_post, const float* h_res, int T, int n, int C, void* dx, void* dh_out, float* d_pre, float*
+    d_post, float* d_res, cudaStream_t st);
+int pm_mhc_constraints_bwd(const float* h_tilde, const float* d_pre, const float* d_post, const float* d_res, int
+    T, int n, int iters, float* d_tilde, cudaStream_t st);
+// gains [2] fp32, cleared here: largest absolute row sum and column sum of H_res over all tokens
+int pm_mhc_amax_gain(const float* h_res, int T, int n, float* gains, cudaStream_t st);
+int pm_mhc_expand(const void* x, int T, int n, int C, void* xs, cudaStream_t st);
+int pm_mhc_collapse(const void* xs, int T, int n, int C, void* x, cudaStream_t st);
+
 // ---------------------------------------------------------------- moe_gemm.cu
 int pm_ep_prepare(const unsigned long long* offset_ptrs, const unsigned long long* pad_ptrs, int rank, int world,
     int e_loc, void* tiles, void* runs, int max_tiles, int max_runs, int* counts_out, double timeout_s, int*

@@ -450,6 +450,98 @@ def grouped_gemm_skinny(x: torch.Tensor, w: torch.Tensor, off: torch.Tensor, swi
     return y
 
 
+# ------------------------------------------------------------------------------------------- hyper-connections
+def gemm_f32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """[M, K] x [N, K]^T -> [M, N padded to a multiple of 32] fp32 (extra columns are zero)."""
+    M, K = x.shape
+    N = w.shape[0]
+    bn = 32 if N <= 32 else (64 if N <= 64 else 128)
+    Np = -(-N // bn) * bn
+    out = torch.zeros(M, Np, dtype=torch.float32, device=x.device)
+    raw_gemm(x, 0, x.stride(0), M, w, 0, w.stride(0), N, out, 1, Np, M, Np, K, bn=bn)
+    return out
+
+
+def mhc_mappings(x, raw, bias, alpha, iters: int):
+    """x [T, n, C] bf16, raw [T, ld] fp32 = flatten(x) . phi -> (H~ [T, n^2+2n], 1/rms [T], H_pre, H_post, H_res)."""
+    T, n, C = x.shape
+    out = n * n + 2 * n
+    f = lambda *s: torch.empty(*s, dtype=torch.float32, device=x.device)      # noqa: E731
+    ht, ri, pre, post, res = f(T, out), f(T), f(T, n), f(T, n), f(T, n, n)
+    lib().pm_mhc_mappings.restype = c_int
+    _chk(lib().pm_mhc_mappings(_p(x), _p(None), _p(raw), c_int(raw.stride(0)), _p(bias), _p(alpha), c_int(T), c_int(n),
+                               c_int(C), c_int(iters), _p(ht), _p(ri), _p(pre), _p(post), _p(res), _stream()),
+         "pm_mhc_mappings")
+    return ht, ri, pre, post, res
+
+
+def mhc_pre(x, h_pre):
+    T, n, C = x.shape
+    out = torch.empty(T, C, dtype=x.dtype, device=x.device)
+    lib().pm_mhc_pre.restype = c_int
+    _chk(lib().pm_mhc_pre(_p(x), _p(h_pre), c_int(T), c_int(n), c_int(C), _p(out), _stream()), "pm_mhc_pre")
+    return out
+
+
+def mhc_post_res(x, h_out, h_res, h_post):
+    T, n, C = x.shape
+    out = torch.empty_like(x)
+    lib().pm_mhc_post_res.restype = c_int
+    _chk(lib().pm_mhc_post_res(_p(x), _p(h_out), _p(h_res), _p(h_post), c_int(T), c_int(n), c_int(C), _p(out), _stream()),
+         "pm_mhc_post_res")
+    return out
+
+
+def mhc_mix_bwd(x, h_out, dh_in, dx_out, h_pre, h_post, h_res):
+    """Gradients of the two stream applications; either half may be None. Returns (dx, dh_out, dH_pre, dH_post, dH_res)."""
+    T, n, C = x.shape
+    f = lambda *s: torch.empty(*s, dtype=torch.float32, device=x.device)      # noqa: E731
+    dx = torch.empty_like(x)
+    dh_out = torch.empty(T, C, dtype=x.dtype, device=x.device) if dx_out is not None else None
+    d_pre = f(T, n) if dh_in is not None else None
+    d_post, d_res = (f(T, n), f(T, n, n)) if dx_out is not None else (None, None)
+    dummy = torch.zeros(n * n, dtype=torch.float32, device=x.device)          # unused halves still need readable gains
+    lib().pm_mhc_mix_bwd.restype = c_int
+    _chk(lib().pm_mhc_mix_bwd(_p(x), _p(h_out), _p(dh_in), _p(dx_out), _p(h_pre if h_pre is not None else dummy),
+                              _p(h_post if h_post is not None else dummy), _p(h_res if h_res is not None else dummy),
+                              c_int(T), c_int(n), c_int(C), _p(dx), _p(dh_out), _p(d_pre), _p(d_post), _p(d_res),
+                              _stream()), "pm_mhc_mix_bwd")
+    return dx, dh_out, d_pre, d_post, d_res
+
+
+def mhc_constraints_bwd(h_tilde, d_pre, d_post, d_res, n: int, iters: int):
+    T = h_tilde.shape[0]
+    out = torch.empty_like(h_tilde)
+    lib().pm_mhc_constraints_bwd.restype = c_int
+    _chk(lib().pm_mhc_constraints_bwd(_p(h_tilde), _p(d_pre), _p(d_post), _p(d_res), c_int(T), c_int(n), c_int(iters),
+                                      _p(out), _stream()), "pm_mhc_constraints_bwd")
+    return out
+
+
+def mhc_amax_gain(h_res):
+    T, n = h_res.shape[0], h_res.shape[-1]
+    g = torch.empty(2, dtype=torch.float32, device=h_res.device)
+    lib().pm_mhc_amax_gain.restype = c_int
+    _chk(lib().pm_mhc_amax_gain(_p(h_res), c_int(T), c_int(n), _p(g), _stream()), "pm_mhc_amax_gain")
+    return g
+
+
+def mhc_expand(x, n: int):
+    T, C = x.shape
+    out = torch.empty(T, n, C, dtype=x.dtype, device=x.device)
+    lib().pm_mhc_expand.restype = c_int
+    _chk(lib().pm_mhc_expand(_p(x), c_int(T), c_int(n), c_int(C), _p(out), _stream()), "pm_mhc_expand")
+    return out
+
+
+def mhc_collapse(xs):
+    T, n, C = xs.shape
+    out = torch.empty(T, C, dtype=xs.dtype, device=xs.device)
+    lib().pm_mhc_collapse.restype = c_int
+    _chk(lib().pm_mhc_collapse(_p(xs), c_int(T), c_int(n), c_int(C), _p(out), _stream()), "pm_mhc_collapse")
+    return out
+
+
 # ------------------------------------------------------------------------------------------- norms etc.
 def rmsnorm_fwd(x, w, eps: float, residual=None):
     T, H = x.shape

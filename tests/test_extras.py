@@ -84,6 +84,30 @@ def test_mhc_sinkhorn_and_layer():
     assert dyn.dynamic.weight.grad is not None and o.shape == xs.shape
 
 
+def test_mhc_per_token_mappings():
+    torch.manual_seed(1)
+    n, C, T = 4, 16, 9
+    layer = mhc.MhcDynamicLayer(n, C, sinkhorn_iters=30)
+    x = torch.randn(T, C)
+    xs = mhc.expand_streams(x, n)
+    out = layer(xs, lambda h: torch.zeros_like(h))
+    assert torch.allclose(mhc.collapse_streams(out), x, atol=1e-4)            # fresh layer: mean-preserving mixing
+    out = layer(xs, lambda h: 3 * h)
+    assert torch.allclose(mhc.collapse_streams(out), x + 3 * x, atol=1e-3)    # reads the mean stream, writes with gain 1
+    with torch.no_grad():
+        layer.phi.normal_(0, 0.3)
+        layer.alpha.fill_(1.0)
+    pre, post, res = mhc.compute_mappings(xs + torch.randn(T, n, C), layer.phi, layer.bias, layer.alpha, 30)
+    assert pre.shape == (T, n) and float(pre.min()) > 0 and float(post.max()) < 2
+    assert torch.allclose(res.sum(-1), torch.ones(T, n), atol=1e-3) and torch.allclose(res.sum(-2), torch.ones(T, n), atol=1e-3)
+    assert not torch.allclose(res[0], res[1])                                  # the mixing depends on the token
+    fr, fc = mhc.amax_gain(res)
+    assert abs(float(fr) - 1) < 1e-3 and abs(float(fc) - 1) < 1e-3
+    o = layer(xs.requires_grad_(True), lambda h: torch.tanh(h))
+    o.square().mean().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in layer.parameters()) and xs.grad is not None
+
+
 def test_gdn_chunked_equals_recurrent():
     torch.manual_seed(0)
     T, H, dk, dv = 150, 3, 16, 24

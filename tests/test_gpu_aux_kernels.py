@@ -555,3 +555,46 @@ def test_batched_lora_rows_pick_their_adapter(T):
             o += sz
     _close(y, ref, what=f"batched lora T={T}")
     assert bool((ids == NO_ADAPTER).any())
+
+
+@pytest.mark.parametrize("n,C", [(4, 256), (2, 1024), (8, 64)])
+def test_hyper_connection_kernels(n, C):
+    """Per-token hyper-connection mappings, the two stream applications and all their gradients (including the one
+    through the Sinkhorn iterations) against the PyTorch formulation in fp32."""
+    _nat()
+    from pmetal_b200.models import mhc
+    torch.manual_seed(17)
+    T, iters = 300, 12
+    out_dim = n * n + 2 * n
+    x = (torch.randn(T, n, C, device="cuda")).bfloat16()
+    phi = (torch.randn(n * C, out_dim, device="cuda") * (n * C) ** -0.5).bfloat16().float()
+    bias = torch.randn(out_dim, device="cuda") * 0.5
+    alpha = torch.tensor([0.7, 1.3, 0.9], device="cuda")
+    w = (torch.randn(C, C, device="cuda") * C ** -0.5)
+
+    def run(native):
+        xs = x.clone().requires_grad_(True) if native else x.float().requires_grad_(True)
+        p, b, a = (t.clone().requires_grad_(True) for t in (phi, bias, alpha))
+        if native:
+            pre, post, res = mhc.compute_mappings(xs, p, b, a, iters)
+            h_in = mhc.apply_pre(xs, pre)
+            h_out = torch.tanh(h_in.float() @ w).to(h_in.dtype)
+            y = mhc.apply_post_res(xs, h_out, res, post)
+        else:
+            pre, post, res = mhc.mappings_reference(xs, p, b, a, iters)
+            h_in = torch.einsum("tn,tnc->tc", pre, xs)
+            h_out = torch.tanh(h_in @ w)
+            y = torch.einsum("tmn,tnc->tmc", res, xs) + post[:, :, None] * h_out[:, None, :]
+        g = torch.Generator(device="cuda").manual_seed(5)
+        dy = torch.randn(T, n, C, device="cuda", generator=g)
+        (y.float() * dy).sum().backward()
+        return y.float(), pre, post, res, xs.grad.float(), p.grad, b.grad, a.grad
+    got, want = run(True), run(False)
+    names = ["y", "H_pre", "H_post", "H_res", "dx", "dphi", "dbias", "dalpha"]
+    for name, a, b in zip(names, got, want):
+        _close(a, b, rtol=4e-2, atol=4e-2 * max(1.0, float(b.abs().max())) if name.startswith("d") else 3e-2, what=name)
+    fr, fc = mhc.amax_gain(got[3])
+    assert abs(float(fr) - float(want[3].abs().sum(-1).max())) < 1e-3
+    xe = (torch.randn(50, C, device="cuda")).bfloat16()
+    assert torch.equal(mhc.expand_streams(xe, n)[:, n - 1], xe)
+    _close(mhc.collapse_streams(x), x.float().mean(1), what="collapse")
