@@ -317,6 +317,18 @@ def test_pretrain_replicas_stay_identical_over_gloo():
     assert r.returncode == 0 and r.stdout.count("PRETRAIN_DP_WORKER_OK") == 2, r.stdout[-3000:]
 
 
+@pytest.mark.parametrize("world", [2, 3])
+def test_context_parallel_attention_trains_over_gloo(world):
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29753 + world), os.path.join(root, "tests", "workers", "cp_train_worker.py")]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=240,
+                       env=dict(os.environ, PMETAL_TEST_CPU="1"))
+    assert r.returncode == 0 and r.stdout.count("CP_TRAIN_WORKER_OK") == world, r.stdout[-3000:]
+
+
 def test_activation_message_wire_format():
     import struct
 

@@ -56,3 +56,10 @@ def test_tensor_and_expert_parallel_serving_slices():
 def test_pretrain_native_kernels_and_identical_replicas():
     r = _run("pretrain_dp_worker.py", 2, port=29551)
     assert r.returncode == 0 and r.stdout.count("PRETRAIN_DP_WORKER_OK") == 2, r.stdout[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_context_parallel_attention_forward_and_backward():
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    r = _run("cp_train_worker.py", n, port=29553)
+    assert r.returncode == 0 and r.stdout.count("CP_TRAIN_WORKER_OK") == n, r.stdout[-4000:]
