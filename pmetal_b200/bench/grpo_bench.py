@@ -23,6 +23,8 @@ def main(argv=None) -> int:
     ap.add_argument("--prompt-len", type=int, default=256)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--model", default="qwen3-0.6b")
+    ap.add_argument("--no-merged-rollout", action="store_true",
+                    help="generate through the adapter-aware decode path instead of folded bf16 weights")
     a = ap.parse_args(argv)
     import torch.distributed as dist
 
@@ -55,7 +57,8 @@ def main(argv=None) -> int:
         return m
     policy, ref = build(True), build(False).eval()
     gc = GrpoConfig(num_generations=a.group, max_prompt_length=a.prompt_len, max_completion_length=a.new_tokens, beta=0.04,
-                    temperature=1.0, top_p=1.0, top_k=0, epsilon_low=0.2, epsilon_high=0.2, learning_rate=1e-6)
+                    temperature=1.0, top_p=1.0, top_k=0, epsilon_low=0.2, epsilon_high=0.2, learning_rate=1e-6,
+                    rollout_merged=not a.no_merged_rollout)
     blocks = a.prompts * a.group * ((a.prompt_len + a.new_tokens) // 64 + 2) + 64
     tr = GrpoTrainer(policy, gc, mod7_length_reward, reference=ref, kv_blocks=blocks, dist=dctx)
     g = torch.Generator().manual_seed(100 + rank)

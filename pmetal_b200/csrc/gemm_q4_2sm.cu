@@ -8,8 +8,8 @@
 //
 // Same CTA-pair structure as gemm_2sm.cu (256 x 256 tile per pair, tcgen05.mma.cta_group::2, accumulators in TMEM),
 // with the B operand produced inside the CTA: the TMA producer brings the packed codes of this CTA's half of the B
-// tile (4 KB per 64-wide K block) into a staging ring, eight dequant warps look the codes up two at a time, scale them
-// by the block's absmax (fp32, or 8-bit double-quantised), round to bf16 and store them in the 128-byte-swizzled
+// tile (4 KB per 64-wide K block) into a staging ring, eight dequant warps look the codes up in a register-resident code
+// book with byte permutes, scale them by the block's absmax (fp32, or 8-bit double-quantised) and store them in the 128-byte-swizzled
 // layout the MMA descriptors expect (K-major for the forward pass, MN-major for the input gradient, where the packed
 // rows run along the reduction). A generic-to-async proxy fence orders those stores before the MMA reads them.
 // The low-rank second product arrives as bf16 through TMA exactly as in the dense kernel.
@@ -47,6 +47,39 @@ __constant__ float kQ4Fp4[16] = {0.0f, 0.0052083333f, 0.6666667f, 1.0f, 0.333333
 
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
+// Eight 4-bit codes (one 32-bit word of the packed weight; byte b holds element 2b in its high nibble and element 2b+1 in
+// its low nibble) -> eight bf16 values times the block scale, as one 16-byte chunk. The 16-entry code book lives in eight
+// registers (th: the high bytes of its bf16 values, tl: the low bytes, four entries per register), and a value is looked
+// up with byte permutes: one permute per half of the table with the low three bits of the code as selector, a third
+// permute in sign-replicating mode that turns bit 3 of every code into a byte mask, and a bitwise select. No shared-
+// memory traffic, which this kernel has none to spare of. Table entries and scale are rounded to bf16 and multiplied in
+// bf16, so a value can differ from the fp32-multiplied reference by two units in the last place.
+__device__ __forceinline__ void q4_expand8(uint32_t w, const uint32_t (&th)[4], const uint32_t (&tl)[4],
+                                           __nv_bfloat162 sc2, uint32_t (&out)[4]) {
+  const uint32_t ws = w << 4;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {                       // nibbles 0..3, then 4..7
+    const uint32_t sel = (half ? (w >> 16) : w) & 0x7777u;
+    const uint32_t mask = prmt(ws, w, half ? 0xFBEAu : 0xD9C8u);
+    const uint32_t ha = prmt(th[0], th[1], sel), hb = prmt(th[2], th[3], sel);
+    const uint32_t la = prmt(tl[0], tl[1], sel), lb = prmt(tl[2], tl[3], sel);
+    const uint32_t hw = (ha & ~mask) | (hb & mask);
+    const uint32_t lw = (la & ~mask) | (lb & mask);
+    // nibble i is element i ^ 1: (element 0, element 1) = (nibble 1, nibble 0), low byte first
+    uint32_t p0 = prmt(lw, hw, 0x4051u), p1 = prmt(lw, hw, 0x6273u);
+    __nv_bfloat162 v0 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&p0), sc2);
+    __nv_bfloat162 v1 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&p1), sc2);
+    out[half * 2] = *reinterpret_cast<uint32_t*>(&v0);
+    out[half * 2 + 1] = *reinterpret_cast<uint32_t*>(&v1);
+  }
+}
+
 __global__ void __launch_bounds__(kQ4Threads, 1)
 gemm_q4_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_c,
                    const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
@@ -63,7 +96,6 @@ gemm_q4_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   uint64_t* tempty_bar = tfull_bar + 2;           // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float2* lut2 = reinterpret_cast<float2*>(smem + p.stages * kQ4StageBytes + 512);      // [256] values of a code pair
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -89,11 +121,6 @@ gemm_q4_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       tma_prefetch_desc(&map_a2);
       tma_prefetch_desc(&map_b2);
     }
-  }
-  if (threadIdx.x >= kThreads) {        // the dequant warps fill the pair table: byte -> (first code, second code)
-    const int b = threadIdx.x - kThreads;
-    const float* t = q.fp4 ? kQ4Fp4 : kQ4Nf4;
-    lut2[b] = make_float2(t[b >> 4], t[b & 15]);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, 512);
@@ -237,33 +264,49 @@ gemm_q4_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     // (32 weights, four 16-byte chunks of bf16) per thread and K block
     const int t = threadIdx.x - kThreads;            // 0..255
     const int blocks_per_row = q.w_cols / 64;
+    // where this thread's 16 bytes of codes sit in the staging tile, where its 32 values go in the B tile, and which
+    // scale they use: fixed per thread up to the tile / K-block origin
+    int row, dst_off;
+    if (!q.trans) {          // staging [128 rows][32 B]; B tile row = weight row, 64 k = 128 B
+      row = t >> 1;
+      dst_off = row * 128 + (t & 1) * 64;
+    } else {                 // staging [64 rows][64 B]; two boxes of [64 k][64 mn]
+      row = t >> 2;
+      dst_off = ((t >> 1) & 1) * 8192 + row * 128 + (t & 1) * 64;
+    }
+    const int code_off = t * 16;
+    uint32_t th[4], tl[4];                           // the code book as bf16, split into high and low bytes
+    {
+      const float* tab = q.fp4 ? kQ4Fp4 : kQ4Nf4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        th[j] = tl[j] = 0u;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t bits = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(tab[4 * j + e])));
+          th[j] |= (bits >> 8) << (8 * e);
+          tl[j] |= (bits & 0xFFu) << (8 * e);
+        }
+      }
+    }
+    auto scale_of = [&](int w, int kb) -> float {
+      if (w >= total || kb >= p.nk1) return 0.f;
+      const int n0 = (w % n_tiles) * kPairBN + static_cast<int>(rank) * kHalfBN;
+      long long blk;
+      if (!q.trans) blk = static_cast<long long>(min(n0 + row, q.w_rows - 1)) * blocks_per_row + kb;
+      else blk = static_cast<long long>(min(kb * 64 + row, q.w_rows - 1)) * blocks_per_row +
+                 min(n0 / 64 + ((t >> 1) & 1), blocks_per_row - 1);
+      return q.absmax ? __ldg(q.absmax + blk) : static_cast<float>(__ldg(q.absmax_q + blk)) * q.am_scale + q.am_offset;
+    };
     uint32_t it = 0;
     bool ok = true;
+    float scale = scale_of(first, 0);          // the scale of the next K block is always requested one block ahead
     for (int w = first; w < total && ok; w += stride) {
-      const int nb = w % n_tiles;
-      const int n0 = nb * kPairBN + static_cast<int>(rank) * kHalfBN;
       for (int kb = 0; kb < nk; ++kb, ++it) {
         const int s = it % p.stages;
         const uint32_t ph = (it / p.stages) & 1;
         const bool expand = kb < p.nk1;
-        int row, code_off, dst_off;
-        long long blk;
-        if (!q.trans) {          // staging [128 rows][32 B]; B tile row = weight row, 64 k = 128 B
-          row = t >> 1;
-          const int half = t & 1;
-          code_off = t * 16;
-          dst_off = row * 128 + half * 64;            // chunk index half*4 + i is applied below
-          blk = static_cast<long long>(min(n0 + row, q.w_rows - 1)) * blocks_per_row + kb;
-        } else {                 // staging [64 rows][64 B]; two boxes of [64 k][64 mn]
-          row = t >> 2;
-          const int box = (t >> 1) & 1, half = t & 1;
-          code_off = t * 16;
-          dst_off = box * 8192 + row * 128 + half * 64;
-          blk = static_cast<long long>(min(kb * 64 + row, q.w_rows - 1)) * blocks_per_row +
-                min(n0 / 64 + box, blocks_per_row - 1);
-        }
-        float scale = 0.f;
-        if (expand) scale = q.absmax ? __ldg(q.absmax + blk) : static_cast<float>(__ldg(q.absmax_q + blk)) * q.am_scale + q.am_offset;
+        const float next_scale = (kb + 1 < nk) ? scale_of(w, kb + 1) : scale_of(w + stride, 0);
         if (!mbar_wait(&cfull_bar[s], ph, abort_flag, p.status, kTimeoutMma)) { ok = false; break; }
         if (expand) {
           uint8_t* sb = smem + s * kQ4StageBytes + a_bytes;
@@ -271,15 +314,11 @@ gemm_q4_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const uint32_t words[4] = {cw.x, cw.y, cw.z, cw.w};
           const int c0 = (dst_off >> 4) & 7;           // first chunk index within the 128-byte row
           uint8_t* rowp = sb + (dst_off & ~127);
+          const __nv_bfloat162 sc2 = __float2bfloat162_rn(scale);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const uint32_t wd = words[i];
             uint32_t o[4];
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              const float2 v = lut2[(wd >> (8 * b)) & 0xFFu];
-              o[b] = pack_bf16x2(v.x * scale, v.y * scale);
-            }
+            q4_expand8(words[i], th, tl, sc2, o);
             const int chunk = (c0 + i) ^ (row & 7);
             *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
           }
@@ -287,6 +326,7 @@ gemm_q4_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&full_bar[s]);
+        scale = next_scale;
       }
     }
   }
@@ -354,7 +394,7 @@ extern "C" int pm_gemm_q4_2sm(const void* A, int lda, int a_rows, const void* co
   for (int i = 0; i < 4; ++i) p.seg_end[i] = (seg_mode && seg_end) ? seg_end[i] : 0x7fffffff;
   p.status = status;
   p.kps = 1; p.fwd_full = 1; p.commit_both = 0;
-  int stages = (227 * 1024 - 4096) / kQ4StageBytes;
+  int stages = (227 * 1024 - 2048) / kQ4StageBytes;
   if (stages > kMaxStages) stages = kMaxStages;
   p.stages = stages;
   p.tmem_cols = 512;
@@ -374,7 +414,7 @@ extern "C" int pm_gemm_q4_2sm(const void* A, int lda, int a_rows, const void* co
   } else {
     ma2 = ma; mb2 = ma;
   }
-  const size_t smem = static_cast<size_t>(stages) * kQ4StageBytes + 1024 + 512 + 2048;
+  const size_t smem = static_cast<size_t>(stages) * kQ4StageBytes + 1024 + 512;
   static DeviceOnce configured;
   if (configured.pending()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_q4_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);

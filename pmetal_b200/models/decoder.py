@@ -138,6 +138,9 @@ class FusedLinear(nn.Module):
         that the mat-vec kernel expands on the fly."""
         if m > GEMV_MAX_ROWS or self.bias is not None or (self.batched is not None and self.adapter_rows is not None):
             return False
+        rows = 4 if m <= 4 else (8 if m <= 8 else 16)
+        if rows * self.in_features * 2 > 200 * 1024:        # the kernel stages the token rows in shared memory
+            return False
         q = getattr(self, "qweight", None)
         if q is not None:
             return (q.scheme in ("nf4", "fp4") and q.data.is_cuda and q.block_size % 32 == 0 and self.in_features % 32 == 0)
@@ -418,7 +421,7 @@ class DecoderLM(nn.Module):
                     cache.append(li, k, qkv[:, (hq + hkv) * d:].view(T, hkv, d), meta.slots)
                 o = cache.attention(li, q, meta, d ** -0.5, at.window).view(T, hq * d)
                 h = at.o_proj.gemv_forward(o, residual=x)
-                if isinstance(layer.mlp, MLP) and layer.mlp.gate_up_proj.gemv_ok(T):
+                if isinstance(layer.mlp, MLP) and layer.mlp.gate_up_proj.gemv_ok(T) and layer.mlp.down_proj.gemv_ok(T):
                     act = layer.mlp.gate_up_proj.gemv_forward(h, layer.post_attention_layernorm, eps, swiglu=True)
                     x = layer.mlp.down_proj.gemv_forward(act, residual=h)
                 else:

@@ -200,7 +200,7 @@ def raw_gemm(A, a_mn, lda, a_rows, B, b_mn, ldb, b_rows, D, out_mode, ldd, M, N,
 
 
 SPLIT_K = os.environ.get("PMETAL_GEMM_SPLITK", "1") == "1"
-FUSED_Q4 = os.environ.get("PMETAL_FUSED_Q4", "1") == "1"
+FUSED_Q4 = os.environ.get("PMETAL_FUSED_Q4", "0") == "1"      # opt-in: saves the transient bf16 weight, not time
 _SPLITK_WS = {}
 
 

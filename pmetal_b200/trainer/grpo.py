@@ -50,6 +50,7 @@ class GrpoConfig:
     dapo_accuracy_reward_threshold: float = 0.5
     dapo_dynamic_sampling_min_accuracy: float = 0.01
     logprob_chunk: int = 4096
+    rollout_merged: bool = True          # generate from W + s B A folded into one bf16 weight (adapter-free decode path)
 
     @classmethod
     def dapo(cls, **kw) -> "GrpoConfig":
@@ -121,6 +122,48 @@ class GrpoStepStats:
         return self.completion_tokens / self.generation_seconds if self.generation_seconds > 0 else 0.0
 
 
+class RolloutWeights:
+    """Context manager for the generation phase: every adapted projection is replaced by one bf16 weight
+    W + s B A (refreshed from the current factors on entry, in buffers that keep their address from step to step), and
+    the factors are hidden, so that rollouts run on the adapter-free decode path (the whole-step kernel, the tensor-core
+    mat-vec and the CUDA graphs captured over them) instead of the slower adapter-aware one. The training forward is
+    untouched: on exit the base weights and the factors are back. Packed (quantised) bases are left alone."""
+
+    def __init__(self, model):
+        self.items = []
+        for _, _, fl in model.fused_linears():
+            if fl.lora_a is None or getattr(fl, "qweight", None) is not None or fl.weight.dtype != torch.bfloat16:
+                continue
+            self.items.append((fl, torch.empty_like(fl.weight.data)))
+        self.saved = []
+
+    @torch.no_grad()
+    def __enter__(self):
+        self.saved = []
+        for fl, buf in self.items:
+            buf.copy_(fl.weight.data)
+            o = 0
+            for i, sz in enumerate(fl.seg_sizes):
+                if fl.active[i]:
+                    a = fl.lora_a.detach()[i * fl.r:(i + 1) * fl.r].to(torch.bfloat16)
+                    b = fl.lora_b.detach()[o:o + sz].to(torch.bfloat16)
+                    buf[o:o + sz].addmm_(b, a, alpha=fl.scale)
+                o += sz
+            self.saved.append((fl.weight.data, fl.lora_a, fl.lora_b, getattr(fl, "lora_a_c", None), getattr(fl, "lora_b_c", None)))
+            fl.weight.data = buf
+            fl.lora_a = fl.lora_b = None
+            fl.lora_a_c = fl.lora_b_c = None
+        return self
+
+    def __exit__(self, *exc):
+        for (fl, _), (w, a, b, ac, bc) in zip(self.items, self.saved):
+            fl.weight.data = w
+            fl.lora_a, fl.lora_b = a, b
+            fl.lora_a_c, fl.lora_b_c = ac, bc
+        self.saved = []
+        return False
+
+
 class GrpoTrainer:
     def __init__(self, policy, cfg: GrpoConfig, reward_fn: RewardFn, reference=None, eos_ids: Sequence[int] = (),
                  kv_blocks: int = 8192, dist=None, optimizer=None):
@@ -136,6 +179,8 @@ class GrpoTrainer:
         if shadow is not None:
             attach_shadows(policy, self.opt)
         self.gen = Generator(policy, num_blocks=kv_blocks)
+        self.rollout_weights = (RolloutWeights(policy) if self.device.type == "cuda" and getattr(cfg, "rollout_merged", True)
+                                else None)
         self.step_count = 0
 
     # ------------------------------------------------------------------ rollout phase
@@ -146,8 +191,11 @@ class GrpoTrainer:
                             repetition_penalty=1.0, max_tokens=c.max_completion_length, do_sample=True)
         was = self.policy.training
         self.policy.eval()
-        res = self.gen.generate([p[-c.max_prompt_length:] for p in prompts], sp, self.eos_ids,
-                                num_return_sequences=c.num_generations, track_history=False)
+        import contextlib
+        with (self.rollout_weights if self.rollout_weights is not None and self.rollout_weights.items
+              else contextlib.nullcontext()):
+            res = self.gen.generate([p[-c.max_prompt_length:] for p in prompts], sp, self.eos_ids,
+                                    num_return_sequences=c.num_generations, track_history=False)
         self.policy.train(was)
         return res
 

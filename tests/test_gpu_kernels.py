@@ -438,11 +438,12 @@ def test_trainable_dense_linear_and_head_with_z_loss():
 
 
 @pytest.mark.parametrize("scheme,dq", [("nf4", True), ("nf4", False), ("fp4", False)])
-def test_gemm_expands_4bit_weight_in_flight(scheme, dq):
+def test_gemm_expands_4bit_weight_in_flight(scheme, dq, monkeypatch):
     """Forward and input-gradient GEMMs that read the packed 4-bit weight directly, with and without the low-rank
     second product, against fp32 products with the dequantised weight (which is what the unfused path feeds the GEMM)."""
     nat = _nat()
     from pmetal_b200.lora import nf4
+    monkeypatch.setattr(nat, "FUSED_Q4", True)
     torch.manual_seed(13)
     M, K, segs, r = 700, 384, (512, 256, 256), 16
     N = sum(segs)
