@@ -36,6 +36,10 @@ def main(argv=None) -> int:
     ap.add_argument("--draft", default=None, help="draft architecture for speculative decoding (e.g. qwen3-0.6b)")
     ap.add_argument("--spec-k", type=int, default=4)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--emulate-world", type=int, default=0,
+                    help="with --tp on one GPU: run rank 0's slice of a W-rank layout without the cross-rank sums "
+                         "(one rank's share of the work per step)")
+    ap.add_argument("--profile", action="store_true", help="print per-kernel device times of a few decode steps")
     a = ap.parse_args(argv)
     if a.tp:
         return main_tp(a)
@@ -148,6 +152,13 @@ def main_tp(a) -> int:
     if world > 1:
         red = PeerAllReduce(None, max_elems=1 << 20) if a.reduce == "peer" else AllReduce(None)
         shard_for_serving(model, None, red)
+    elif a.emulate_world > 1:
+        class _NoSum:
+            world = a.emulate_world
+
+            def __call__(self, x):
+                return x
+        shard_for_serving(model, None, _NoSum(), rank=0, world=a.emulate_world)
     build_s = time.time() - t0
     n_req = a.requests
     blocks = n_req * ((a.prompt_len + a.new_tokens + 8) // 64 + 2) + 64
@@ -195,10 +206,26 @@ def main_tp(a) -> int:
     run(8)
     pre_ms, dec_ms = run(a.new_tokens)
     native.check_status()
+    if a.profile and rank == 0:
+        from torch.profiler import ProfilerActivity, profile
+        seqs = [gen.new_seq() for _ in prompts]
+        ids = gen.prefill(seqs, prompts, 4096).argmax(-1)
+        for _ in range(3):
+            ids = gen.decode_step(seqs, ids).argmax(-1)
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(5):
+                ids = gen.decode_step(seqs, ids).argmax(-1)
+            torch.cuda.synchronize()
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=24, max_name_column_width=56), flush=True)
+        for s_ in seqs:
+            gen.cache.free_sequence(s_)
     pre_ms, dec_ms = mx(pre_ms), mx(dec_ms)
     out = {"bench": "moe_serve", "model": a.model, "layers": cfg.num_hidden_layers, "n_gpus": world, "requests": n_req,
            "prompt_len": a.prompt_len, "new_tokens": a.new_tokens,
-           "parallelism": f"tp{world} attention x ep{world} experts (replicated requests, {a.reduce} all-reduce)",
+           "parallelism": (f"tp{world} attention x ep{world} experts (replicated requests, {a.reduce} all-reduce)" if world > 1
+                           else f"rank 0 of an emulated tp{a.emulate_world} x ep{a.emulate_world} layout, no cross-rank sums"
+                           if a.emulate_world > 1 else "one GPU"),
            "build_s": round(build_s, 1), "prefill_tok_s": round(n_req * a.prompt_len / (pre_ms / 1e3), 1),
            "decode_tok_s": round(n_req * (a.new_tokens - 1) / (dec_ms / 1e3), 1),
            "decode_ms_per_step": round(dec_ms / (a.new_tokens - 1), 3),

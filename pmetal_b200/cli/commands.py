@@ -468,9 +468,12 @@ def _paged_cache_options(a, model, num_blocks: int) -> dict:
     quant = None
     if mode.kind != "standard":
         quant = "int8"
-        if mode.kind != "quantized" or mode.bits != 8 or a.kv_group_size != 64 or a.kv_qjl:
-            print(f"note: the paged cache stores bf16 or int8 (group 64); using int8 instead of {mode.kind} "
-                  f"k{mode.k_bits}/v{mode.v_bits} (narrower caches run on the portable models)", file=sys.stderr)
+        if (mode.kind == "turboquant" or (mode.kind == "quantized" and mode.bits == 4)) and cfg.head_dim == 128 \
+                and not a.kv_qjl:
+            quant = "tq4"         # rotated 4-bit code-book cache (TurboQuant without the residual sketch)
+        elif mode.kind != "quantized" or mode.bits != 8 or a.kv_group_size != 64 or a.kv_qjl:
+            print(f"note: the paged cache stores bf16, int8 (group 64) or rotated 4-bit codes; using int8 instead of "
+                  f"{mode.kind} k{mode.k_bits}/v{mode.v_bits} (other layouts run on the portable models)", file=sys.stderr)
         if cfg.head_dim % 64:
             quant = None
     if quant or a.kv_window:
@@ -710,8 +713,9 @@ def _serve_args(sp):
                         "\"adapter\": NAME or \"model\": NAME, and requests with different adapters share a batch")
     p.add_argument("--tp", type=int, default=1, help="cut attention heads (and dense feed-forward channels) over N GPUs")
     p.add_argument("--ep", type=int, default=0, help="cut experts over N GPUs (the same ranks as --tp; default: = --tp)")
-    p.add_argument("--reduce", choices=["peer", "nccl"], default="peer",
-                   help="sum of the partial layer outputs: one kernel over symmetric memory, or NCCL")
+    p.add_argument("--reduce", choices=["peer", "nccl"], default="nccl",
+                   help="sum of the partial layer outputs: NCCL (in-switch reduction; measured faster at 8 ranks), or one "
+                        "kernel over symmetric memory")
     _add_kv_quant_flags(p)
     return p
 

@@ -659,6 +659,9 @@ struct PagedParams {
   // of 64 channels, [num_blocks, 64, hkv, 2]
   const float* k_scale;
   const float* v_scale;
+  // 4-bit code-book cache (kQ == 2): k_cache / v_cache hold two codes per byte (first channel in the low nibble),
+  // [num_blocks, 64, hkv, 64] bytes; a value is lut[code] * scale with the scales laid out as for the int8 cache
+  float lut[16];
 };
 
 // One thread's share of a [64][128] int8 key or value block in flight: four 16-byte pieces and their scales.
@@ -704,7 +707,44 @@ __device__ __forceinline__ void q8_store(const Q8Regs& r, uint8_t* smem_tile) {
   }
 }
 
-template <bool kQ8>
+// One thread's share of a [64][128] block of 4-bit codes (64 bytes per row): two 16-byte pieces of 32 codes each.
+struct Q4Regs {
+  uint4 d[2];
+  float s[2];
+};
+__device__ __forceinline__ void q4_fetch(Q4Regs& r, const uint8_t* base, const float* sbase, long long row_stride_bytes,
+                                         long long srow_stride) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int idx = threadIdx.x + i * kAttnThreads;   // 0..255
+    const int row = idx >> 2, c = idx & 3;            // 32 channels [32c, 32c+32)
+    r.d[i] = __ldg(reinterpret_cast<const uint4*>(base + row * row_stride_bytes + c * 16));
+    r.s[i] = __ldg(sbase + row * srow_stride + (c >> 1));
+  }
+}
+__device__ __forceinline__ void q4_store(const Q4Regs& r, uint8_t* smem_tile, const float* lut) {
+  const uint32_t sbase = smem_addr(smem_tile);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int idx = threadIdx.x + i * kAttnThreads;
+    const int row = idx >> 2, c = idx & 3;
+    const uint32_t w[4] = {r.d[i].x, r.d[i].y, r.d[i].z, r.d[i].w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {                     // one word = 8 codes = one 16-byte chunk of bf16
+      uint32_t o[4];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const uint32_t byte = (w[q] >> (8 * b)) & 0xffu;
+        o[b] = pack2(lut[byte & 15u] * r.s[i], lut[byte >> 4] * r.s[i]);
+      }
+      const uint32_t dst = sbase + row * 256 + (((4 * c + q) ^ (row & 7)) << 4);
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                   : "memory");
+    }
+  }
+}
+
+template <int kQ>
 __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedParams p) {
   pdl_launch_dependents();
   pdl_wait();
@@ -761,19 +801,40 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
     return blk;
   };
   Q8Regs rk, rv;
+  Q4Regs rk4, rv4;
+  __shared__ float s_lut[16];
+  if (kQ == 2) {
+    if (threadIdx.x < 16) s_lut[threadIdx.x] = p.lut[threadIdx.x];
+    __syncthreads();
+  }
   auto fetch_q8 = [&](int blk) {
     const long long off = (static_cast<long long>(bt[blk]) * kTile * p.hkv + hk);
+    if (kQ == 2) {
+      q4_fetch(rk4, reinterpret_cast<const uint8_t*>(p.k_cache) + off * (kD / 2), p.k_scale + off * 2,
+               static_cast<long long>(p.hkv) * (kD / 2), static_cast<long long>(p.hkv) * 2);
+      q4_fetch(rv4, reinterpret_cast<const uint8_t*>(p.v_cache) + off * (kD / 2), p.v_scale + off * 2,
+               static_cast<long long>(p.hkv) * (kD / 2), static_cast<long long>(p.hkv) * 2);
+      return;
+    }
     q8_fetch(rk, reinterpret_cast<const int8_t*>(p.k_cache) + off * kD, p.k_scale + off * 2, row_stride,
              static_cast<long long>(p.hkv) * 2);
     q8_fetch(rv, reinterpret_cast<const int8_t*>(p.v_cache) + off * kD, p.v_scale + off * 2, row_stride,
              static_cast<long long>(p.hkv) * 2);
   };
+  auto store_q8 = [&](uint8_t* dk, uint8_t* dv) {
+    if (kQ == 2) {
+      q4_store(rk4, dk, s_lut);
+      q4_store(rv4, dv, s_lut);
+    } else {
+      q8_store(rk, dk);
+      q8_store(rv, dv);
+    }
+  };
   int b_cur = next_live(b0);
   if (b_cur < b1) {
-    if (kQ8) {
+    if (kQ) {
       fetch_q8(b_cur);
-      q8_store(rk, sK);
-      q8_store(rv, sV);
+      store_q8(sK, sV);
     } else {
       load_tile(sK, kv_base(p.k_cache, b_cur), row_stride, 0, kTile);
       load_tile(sV, kv_base(p.v_cache, b_cur), row_stride, 0, kTile);
@@ -798,7 +859,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
   for (int b = b_cur; b < b1; ++it) {
     const int buf = it & 1;
     const int b_next = next_live(b + 1);
-    if (kQ8) {
+    if (kQ) {
       if (b_next < b1) fetch_q8(b_next);          // global loads stay in flight while this block is processed
       cp_async_wait<0>();                         // the query tile (first iteration)
     } else if (b_next < b1) {
@@ -887,9 +948,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_attn_kernel(const PagedPar
         }
       }
     }
-    if (kQ8 && b_next < b1) {     // the other buffer was last read one iteration ago (barrier at the end of it)
-      q8_store(rk, sK + (buf ^ 1) * kTileBytes);
-      q8_store(rv, sV + (buf ^ 1) * kTileBytes);
+    if (kQ && b_next < b1) {      // the other buffer was last read one iteration ago (barrier at the end of it)
+      store_q8(sK + (buf ^ 1) * kTileBytes, sV + (buf ^ 1) * kTileBytes);
     }
     __syncthreads();
     b = b_next;
@@ -977,16 +1037,19 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, long long 
 //   part_o  : n_split * total_q * hq * 128 floats,  part_ml : n_split * total_q * hq * 2 floats
 // k_scale / v_scale non-null: the caches hold int8 with one fp32 scale per (token, kv head, 64-channel group).
 // sink: with window > 0, the first `sink` keys of a sequence stay visible.
-extern "C" int pm_paged_attn_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                const int* block_table, const int* seq_lens, const int* q_start, const int* q_lens,
-                                float* part_o, float* part_ml, int num_seqs, int max_blocks, int total_q, int max_q,
-                                int hq, int hkv, int n_split, float scale, int window, int sink, const float* k_scale,
-                                const float* v_scale, cudaStream_t st) {
+static int paged_attn_launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                             const int* seq_lens, const int* q_start, const int* q_lens, float* part_o, float* part_ml,
+                             int num_seqs, int max_blocks, int total_q, int max_q, int hq, int hkv, int n_split,
+                             float scale, int window, int sink, const float* k_scale, const float* v_scale,
+                             const float* lut16, cudaStream_t st) {
   if (hq % hkv || num_seqs <= 0) return -1;
   if (n_split < 1 || (n_split > 1 && (!part_o || !part_ml))) return -2;
   if ((k_scale == nullptr) != (v_scale == nullptr)) return -4;
+  if (lut16 && !k_scale) return -5;
   PagedParams p{};
   p.sink = sink; p.k_scale = k_scale; p.v_scale = v_scale;
+  if (lut16)
+    for (int i = 0; i < 16; ++i) p.lut[i] = lut16[i];
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
   p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
@@ -1000,22 +1063,46 @@ extern "C" int pm_paged_attn_ex(const void* q, const void* k_cache, const void* 
   const int smem = 5 * kTileBytes;
   static DeviceOnce once;
   if (once.pending()) {
-    int e = set_smem(reinterpret_cast<const void*>(paged_attn_kernel<false>), smem);
+    int e = set_smem(reinterpret_cast<const void*>(paged_attn_kernel<0>), smem);
     if (e) return e;
-    e = set_smem(reinterpret_cast<const void*>(paged_attn_kernel<true>), smem);
+    e = set_smem(reinterpret_cast<const void*>(paged_attn_kernel<1>), smem);
+    if (e) return e;
+    e = set_smem(reinterpret_cast<const void*>(paged_attn_kernel<2>), smem);
     if (e) return e;
     once.mark();
   }
   dim3 grid(num_seqs * p.q_tiles, hkv, n_split);
-  int e = k_scale ? static_cast<int>(launch_pdl(paged_attn_kernel<true>, grid, dim3(kAttnThreads),
-                                                static_cast<size_t>(smem), st, p))
-                  : static_cast<int>(launch_pdl(paged_attn_kernel<false>, grid, dim3(kAttnThreads),
-                                                static_cast<size_t>(smem), st, p));
+  int e;
+  if (lut16) e = static_cast<int>(launch_pdl(paged_attn_kernel<2>, grid, dim3(kAttnThreads), static_cast<size_t>(smem), st, p));
+  else if (k_scale) e = static_cast<int>(launch_pdl(paged_attn_kernel<1>, grid, dim3(kAttnThreads), static_cast<size_t>(smem), st, p));
+  else e = static_cast<int>(launch_pdl(paged_attn_kernel<0>, grid, dim3(kAttnThreads), static_cast<size_t>(smem), st, p));
   if (e || n_split == 1) return e;
   const int rows = total_q * hq;
   return static_cast<int>(launch_pdl(paged_attn_combine_kernel, dim3((rows + 7) / 8), dim3(256), 0, st,
                                      static_cast<const float*>(part_o), static_cast<const float*>(part_ml),
                                      static_cast<__nv_bfloat16*>(out), rows, n_split));
+}
+
+extern "C" int pm_paged_attn_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                const int* block_table, const int* seq_lens, const int* q_start, const int* q_lens,
+                                float* part_o, float* part_ml, int num_seqs, int max_blocks, int total_q, int max_q,
+                                int hq, int hkv, int n_split, float scale, int window, int sink, const float* k_scale,
+                                const float* v_scale, cudaStream_t st) {
+  return paged_attn_launch(q, k_cache, v_cache, out, block_table, seq_lens, q_start, q_lens, part_o, part_ml, num_seqs,
+                           max_blocks, total_q, max_q, hq, hkv, n_split, scale, window, sink, k_scale, v_scale, nullptr, st);
+}
+
+// 4-bit code-book cache: k_cache / v_cache hold two codes per byte [num_blocks, 64, hkv, 64]; a cached value is
+// lut16[code] * scale (scales as for the int8 cache). lut16: 16 floats on the host. The query and the output live in
+// whatever basis the cached vectors were quantised in (the caller rotates the query and un-rotates the output).
+extern "C" int pm_paged_attn_q4(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                const int* block_table, const int* seq_lens, const int* q_start, const int* q_lens,
+                                float* part_o, float* part_ml, int num_seqs, int max_blocks, int total_q, int max_q,
+                                int hq, int hkv, int n_split, float scale, int window, int sink, const float* k_scale,
+                                const float* v_scale, const float* lut16, cudaStream_t st) {
+  if (!lut16) return -5;
+  return paged_attn_launch(q, k_cache, v_cache, out, block_table, seq_lens, q_start, q_lens, part_o, part_ml, num_seqs,
+                           max_blocks, total_q, max_q, hq, hkv, n_split, scale, window, sink, k_scale, v_scale, lut16, st);
 }
 
 extern "C" int pm_paged_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
@@ -1076,6 +1163,121 @@ extern "C" int pm_kv_append_q8(const void* k, long long k_stride, const void* v,
                                             static_cast<const __nv_bfloat16*>(v), v_stride,
                                             static_cast<int8_t*>(k_cache), static_cast<int8_t*>(v_cache), k_scale,
                                             v_scale, slots, n_tokens, hkv);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------------- rotated 4-bit cache
+// Signed Walsh-Hadamard transform of a 128-vector held four consecutive elements per lane (natural order):
+// two butterfly stages inside the thread, five across lanes.
+__device__ __forceinline__ void fwht128(float (&f)[4], int lane) {
+  float a = f[0] + f[1], b = f[0] - f[1], c = f[2] + f[3], d = f[2] - f[3];
+  f[0] = a + c; f[1] = b + d; f[2] = a - c; f[3] = b - d;
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+    const bool upper = (lane & m) != 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float o = __shfl_xor_sync(0xffffffffu, f[e], m);
+      f[e] = upper ? o - f[e] : f[e] + o;
+    }
+  }
+}
+
+// y = H (x * sign) / sqrt(128) (forward) or (H y) / sqrt(128) * sign (inverse); rows of 128, one warp per row.
+__global__ void tq_rotate_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride, const float* __restrict__ sign,
+                                 __nv_bfloat16* __restrict__ y, long long y_stride, long long rows, int heads, int inverse) {
+  const int lane = threadIdx.x & 31;
+  const float s0 = sign[lane * 4], s1 = sign[lane * 4 + 1], s2 = sign[lane * 4 + 2], s3 = sign[lane * 4 + 3];
+  for (long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; w < rows;
+       w += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    const long long t = w / heads;
+    const int h = static_cast<int>(w - t * heads);
+    const uint2 raw = *reinterpret_cast<const uint2*>(x + t * x_stride + h * pm::kD + lane * 4);
+    float f[4] = {__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u), __uint_as_float(raw.y << 16),
+                  __uint_as_float(raw.y & 0xffff0000u)};
+    if (!inverse) { f[0] *= s0; f[1] *= s1; f[2] *= s2; f[3] *= s3; }
+    fwht128(f, lane);
+    const float r = 0.08838834764831845f;       // 1 / sqrt(128)
+    f[0] *= r; f[1] *= r; f[2] *= r; f[3] *= r;
+    if (inverse) { f[0] *= s0; f[1] *= s1; f[2] *= s2; f[3] *= s3; }
+    uint2 o;
+    o.x = pack2(f[0], f[1]);
+    o.y = pack2(f[2], f[3]);
+    *reinterpret_cast<uint2*>(y + t * y_stride + h * pm::kD + lane * 4) = o;
+  }
+}
+
+// Append to the rotated 4-bit cache: one warp per (token, kv head, K or V) row. The row is rotated, its norm taken, every
+// coordinate of the unit-variance vector  H(x sign) / |x|  is mapped to the cell of a 16-level scalar quantiser
+// (thr: its 15 decision thresholds), codes are packed two per byte, and |x| / sqrt(128) is stored as the row's scale.
+__global__ void kv_append_tq4_kernel(const __nv_bfloat16* __restrict__ k, long long k_stride,
+                                     const __nv_bfloat16* __restrict__ v, long long v_stride, uint8_t* __restrict__ k_cache,
+                                     uint8_t* __restrict__ v_cache, float* __restrict__ k_scale,
+                                     float* __restrict__ v_scale, const long long* __restrict__ slots,
+                                     const float* __restrict__ sign, const float* __restrict__ thr, int n_tokens, int hkv) {
+  __shared__ float s_thr[15];
+  if (threadIdx.x < 15) s_thr[threadIdx.x] = thr[threadIdx.x];
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const float s0 = sign[lane * 4], s1 = sign[lane * 4 + 1], s2 = sign[lane * 4 + 2], s3 = sign[lane * 4 + 3];
+  const long long rows = static_cast<long long>(n_tokens) * hkv * 2;
+  for (long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; w < rows;
+       w += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    const int is_v = static_cast<int>(w & 1);
+    const long long th = w >> 1;
+    const int t = static_cast<int>(th / hkv), h = static_cast<int>(th - static_cast<long long>(t) * hkv);
+    const long long slot = slots[t];
+    if (slot < 0) continue;
+    const __nv_bfloat16* src = (is_v ? v + t * v_stride : k + t * k_stride) + h * pm::kD + lane * 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    float f[4] = {__uint_as_float(raw.x << 16) * s0, __uint_as_float(raw.x & 0xffff0000u) * s1,
+                  __uint_as_float(raw.y << 16) * s2, __uint_as_float(raw.y & 0xffff0000u) * s3};
+    float ss = f[0] * f[0] + f[1] * f[1] + f[2] * f[2] + f[3] * f[3];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float norm = sqrtf(ss);
+    fwht128(f, lane);                      // |H x|^2 = 128 |x|^2: H x / |x| has unit-variance coordinates
+    const float inv = norm > 1e-12f ? 1.f / norm : 0.f;
+    uint32_t codes = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float y = f[e] * inv;
+      int c = 0;
+#pragma unroll
+      for (int j = 0; j < 15; ++j) c += (s_thr[j] < y) ? 1 : 0;
+      codes |= static_cast<uint32_t>(c) << (4 * e);
+    }
+    const long long row = slot * hkv + h;
+    *reinterpret_cast<uint16_t*>((is_v ? v_cache : k_cache) + row * (pm::kD / 2) + lane * 2) = static_cast<uint16_t>(codes);
+    if ((lane & 15) == 0) (is_v ? v_scale : k_scale)[row * 2 + (lane >> 4)] = norm * 0.08838834764831845f;
+  }
+}
+
+// sign: 128 floats (+-1) on the device; thr: 15 ascending thresholds on the device.
+extern "C" int pm_kv_append_tq4(const void* k, long long k_stride, const void* v, long long v_stride, void* k_cache,
+                                void* v_cache, float* k_scale, float* v_scale, const long long* slots, const float* sign,
+                                const float* thr, int n_tokens, int hkv, cudaStream_t st) {
+  if (n_tokens <= 0) return 0;
+  const long long warps = static_cast<long long>(n_tokens) * hkv * 2;
+  int grid = static_cast<int>((warps + 7) / 8);
+  if (grid > num_sms() * 8) grid = num_sms() * 8;
+  kv_append_tq4_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(k), k_stride,
+                                             static_cast<const __nv_bfloat16*>(v), v_stride,
+                                             static_cast<uint8_t*>(k_cache), static_cast<uint8_t*>(v_cache), k_scale,
+                                             v_scale, slots, sign, thr, n_tokens, hkv);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// x, y: [rows / heads, heads, 128] bf16 with token strides x_stride / y_stride (elements); inverse 0: y = H (x sign) / sqrt(d),
+// inverse 1: y = (H x) / sqrt(d) * sign.
+extern "C" int pm_tq_rotate(const void* x, long long x_stride, const float* sign, void* y, long long y_stride,
+                            long long tokens, int heads, int inverse, cudaStream_t st) {
+  if (tokens <= 0) return 0;
+  const long long rows = tokens * heads;
+  int grid = static_cast<int>((rows + 7) / 8);
+  if (grid > num_sms() * 8) grid = num_sms() * 8;
+  tq_rotate_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_stride, sign,
+                                         static_cast<__nv_bfloat16*>(y), y_stride, rows, heads, inverse);
   return static_cast<int>(cudaGetLastError());
 }
 

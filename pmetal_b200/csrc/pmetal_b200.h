@@ -25,19 +25,30 @@ int pm_attn_bwd(const void* dout, const void* q, long long q_stride, const void*
     v, long long v_stride, long long o_stride, const float* lse, const float* delta, void* dq, long long dq_stride,
     void* dk, long long dk_stride, void* dv, long long dv_stride, const int* seq_start, int T, int hq, int hkv,
     float scale, int window, cudaStream_t st);
-// Scratch (part_o / part_ml) is needed only when n_split > 1:
-//   part_o  : n_split * total_q * hq * 128 floats,  part_ml : n_split * total_q * hq * 2 floats
-// k_scale / v_scale non-null: the caches hold int8 with one fp32 scale per (token, kv head, 64-channel group).
-// sink: with window > 0, the first `sink` keys of a sequence stay visible.
 int pm_paged_attn_ex(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
     const int* seq_lens, const int* q_start, const int* q_lens, float* part_o, float* part_ml, int num_seqs, int
     max_blocks, int total_q, int max_q, int hq, int hkv, int n_split, float scale, int window, int sink, const
     float* k_scale, const float* v_scale, cudaStream_t st);
+// 4-bit code-book cache: k_cache / v_cache hold two codes per byte [num_blocks, 64, hkv, 64]; a cached value is
+// lut16[code] * scale (scales as for the int8 cache). lut16: 16 floats on the host. The query and the output live in
+// whatever basis the cached vectors were quantised in (the caller rotates the query and un-rotates the output).
+int pm_paged_attn_q4(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+    const int* seq_lens, const int* q_start, const int* q_lens, float* part_o, float* part_ml, int num_seqs, int
+    max_blocks, int total_q, int max_q, int hq, int hkv, int n_split, float scale, int window, int sink, const
+    float* k_scale, const float* v_scale, const float* lut16, cudaStream_t st);
 int pm_paged_attn(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table, const
     int* seq_lens, const int* q_start, const int* q_lens, float* part_o, float* part_ml, int num_seqs, int
     max_blocks, int total_q, int max_q, int hq, int hkv, int n_split, float scale, int window, cudaStream_t st);
 int pm_kv_append_q8(const void* k, long long k_stride, const void* v, long long v_stride, void* k_cache, void*
     v_cache, float* k_scale, float* v_scale, const long long* slots, int n_tokens, int hkv, cudaStream_t st);
+// sign: 128 floats (+-1) on the device; thr: 15 ascending thresholds on the device.
+int pm_kv_append_tq4(const void* k, long long k_stride, const void* v, long long v_stride, void* k_cache, void*
+    v_cache, float* k_scale, float* v_scale, const long long* slots, const float* sign, const float* thr, int
+    n_tokens, int hkv, cudaStream_t st);
+// x, y: [rows / heads, heads, 128] bf16 with token strides x_stride / y_stride (elements); inverse 0: y = H (x sign) / sqrt(d),
+// inverse 1: y = (H x) / sqrt(d) * sign.
+int pm_tq_rotate(const void* x, long long x_stride, const float* sign, void* y, long long y_stride, long long
+    tokens, int heads, int inverse, cudaStream_t st);
 int pm_kv_append(const void* k, long long k_stride, const void* v, long long v_stride, void* k_cache, void*
     v_cache, const long long* slots, int n_tokens, int hkv, cudaStream_t st);
 int pm_paged_attn_static_max_rows(void);

@@ -10,6 +10,9 @@ Variants on the same block table (the reference keeps separate cache classes, cr
 quantized.rs and rotating.rs; ``select_cache_mode`` restates its choice rule,
 crates/pmetal/src/inference_runner.rs:1187-1258,1335-1405):
 
+* ``quant="tq4"``: keys and values are rotated by a random signed Hadamard transform, normalised and stored as 4-bit
+  Lloyd-Max codes plus one scale per vector (the TurboQuant scheme, 3.6x smaller than bf16); queries are rotated once,
+  attention runs in the rotated basis on the same kernel with a code-book lookup, and the output is rotated back.
 * ``quant="int8"``: keys and values are stored as int8 with one fp32 scale per (token, kv head, 64 channels); the
   append kernel quantises, the attention kernel expands a block to bf16 in shared memory while it loads it.
 * ``window > 0`` (with ``sink`` leading tokens kept): a rotating cache. Blocks that lie wholly before the window of
@@ -89,18 +92,27 @@ class PagedKVCache:
                  device="cuda", quant: Optional[str] = None, window: int = 0, sink: int = 0):
         self.num_layers, self.hkv, self.d, self.num_blocks = num_layers, num_kv_heads, head_dim, num_blocks
         self.device = torch.device(device)
-        if quant not in (None, "int8"):
-            raise ValueError("the paged cache stores bf16 or int8; other widths use the portable QuantKVCache")
+        if quant not in (None, "int8", "tq4"):
+            raise ValueError("the paged cache stores bf16, int8 or rotated 4-bit codes; other widths use the portable "
+                             "QuantKVCache")
         if quant == "int8" and head_dim % GROUP:
             raise ValueError(f"int8 cache needs head_dim to be a multiple of {GROUP}")
+        if quant == "tq4" and head_dim != 128:
+            raise ValueError("the rotated 4-bit cache is built for head_dim 128")
         self.quant, self.window, self.sink = quant, int(window), int(sink)
-        shape = (num_blocks, BLOCK, num_kv_heads, head_dim)
-        store = torch.int8 if quant == "int8" else dtype
+        shape = (num_blocks, BLOCK, num_kv_heads, head_dim // 2 if quant == "tq4" else head_dim)
+        store = torch.int8 if quant == "int8" else (torch.uint8 if quant == "tq4" else dtype)
+        self.tq = None
+        if quant == "tq4":
+            # random signed Hadamard rotation + 16-level Lloyd-Max code book of the unit normal (models/turboquant.py)
+            from .turboquant import TurboQuant
+            self.tq = TurboQuant(head_dim, 4, qjl=False, seed=0, device=device)
+            self.tq_lut = [float(x) for x in self.tq.centroids.tolist()]
         self.compute_dtype = dtype
         self.k = [torch.zeros(shape, dtype=store, device=device) for _ in range(num_layers)]
         self.v = [torch.zeros(shape, dtype=store, device=device) for _ in range(num_layers)]
         self.k_scale = self.v_scale = None
-        if quant == "int8":
+        if quant in ("int8", "tq4"):
             sshape = (num_blocks, BLOCK, num_kv_heads, head_dim // GROUP)
             self.k_scale = [torch.ones(sshape, dtype=torch.float32, device=device) for _ in range(num_layers)]
             self.v_scale = [torch.ones(sshape, dtype=torch.float32, device=device) for _ in range(num_layers)]
@@ -239,6 +251,9 @@ class PagedKVCache:
         from ..ops import native as nat
         if self.quant == "int8":
             nat.kv_append_q8(k, v, self.k[layer], self.v[layer], self.k_scale[layer], self.v_scale[layer], slots)
+        elif self.quant == "tq4":
+            nat.kv_append_tq4(k, v, self.k[layer], self.v[layer], self.k_scale[layer], self.v_scale[layer], slots,
+                              self.tq.sign, self.tq.thresholds)
         else:
             nat.kv_append(k, v, self.k[layer], self.v[layer], slots)
 
@@ -247,6 +262,12 @@ class PagedKVCache:
         cache's own rotating window combine to the smaller of the two; the sink applies to the cache's window."""
         from ..ops import native as nat
         win = min(w for w in (window, self.window) if w > 0) if (window > 0 or self.window > 0) else 0
+        if self.quant == "tq4":
+            # keys and values are stored in the rotated basis: rotate the queries once, attend there, rotate the result back
+            o = nat.paged_attn(nat.tq_rotate(q.contiguous(), self.tq.sign), self.k[layer], self.v[layer], meta, scale, win,
+                               sink=self.sink if self.window > 0 else 0, k_scale=self.k_scale[layer],
+                               v_scale=self.v_scale[layer], lut=self.tq_lut)
+            return nat.tq_rotate(o, self.tq.sign, inverse=True)
         return nat.paged_attn(q, self.k[layer], self.v[layer], meta, scale, win, sink=self.sink if self.window > 0 else 0,
                               k_scale=self.k_scale[layer] if self.quant else None,
                               v_scale=self.v_scale[layer] if self.quant else None)
@@ -268,6 +289,11 @@ class PagedKVCache:
                 q, sc = self.quantize_rows(x)
                 flat[slots] = q
                 scales[layer].view(-1, self.hkv, self.d // GROUP)[slots] = sc
+            elif self.quant == "tq4":
+                c = self.tq.encode(x.float())
+                cache.view(-1, self.hkv, self.d // 2)[slots] = c.codes
+                sc = (x.float().norm(dim=-1) / self.d ** 0.5)[..., None].expand(-1, -1, self.d // GROUP)
+                scales[layer].view(-1, self.hkv, self.d // GROUP)[slots] = sc
             else:
                 flat[slots] = x.to(flat.dtype)
 
@@ -286,5 +312,10 @@ class PagedKVCache:
             if self.quant == "int8":
                 sc = scales[layer][idx]
                 x = (x.float().reshape(*x.shape[:-1], -1, GROUP) * sc[..., None]).reshape(x.shape).to(self.compute_dtype)
+            elif self.quant == "tq4":
+                from .turboquant import unpack_bits
+                sc = scales[layer][idx][..., 0]                                     # |x| / sqrt(d) per (token, head)
+                y = self.tq.centroids[unpack_bits(x, 4, self.d).long()] * sc[..., None]
+                x = self.tq.unrotate(y).to(self.compute_dtype)                      # back in the original basis
             out.append(x.reshape(-1, self.hkv, self.d)[:length])
         return out[0], out[1]

@@ -761,9 +761,10 @@ def kv_append_q8(k, v, k_cache, v_cache, k_scale, v_scale, slots) -> None:
 
 
 def paged_attn(q, k_cache, v_cache, meta, scale: float, window: int = 0, n_split: int = 0, sink: int = 0,
-               k_scale=None, v_scale=None):
+               k_scale=None, v_scale=None, lut=None):
     """q: [total_q, hq, 128]; ``meta`` is a ``BatchMeta``. Long single sequences are split over key blocks.
-    With ``k_scale`` / ``v_scale`` the caches are int8; ``sink`` keys stay visible in front of a sliding window."""
+    With ``k_scale`` / ``v_scale`` the caches are int8, or, with ``lut`` (16 floats), 4-bit codes into that code book;
+    ``sink`` keys stay visible in front of a sliding window."""
     total_q, hq, _ = q.shape
     hkv = k_cache.shape[2]
     n_seq = meta.block_table.shape[0]
@@ -776,12 +777,44 @@ def paged_attn(q, k_cache, v_cache, meta, scale: float, window: int = 0, n_split
     if n_split > 1:
         po = torch.empty(n_split, total_q, hq, 128, dtype=torch.float32, device=q.device)
         pml = torch.empty(n_split, total_q, hq, 2, dtype=torch.float32, device=q.device)
+    if lut is not None:
+        lib().pm_paged_attn_q4.restype = c_int
+        arr = (c_float * 16)(*[float(x) for x in lut])
+        _chk(lib().pm_paged_attn_q4(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(meta.block_table), _p(meta.seq_lens),
+                                    _p(meta.q_start), _p(meta.q_lens), _p(po), _p(pml), c_int(n_seq),
+                                    c_int(meta.block_table.shape[1]), c_int(total_q), c_int(meta.max_q), c_int(hq),
+                                    c_int(hkv), c_int(n_split), c_float(scale), c_int(window), c_int(sink), _p(k_scale),
+                                    _p(v_scale), arr, _stream()), "pm_paged_attn_q4")
+        return out
     lib().pm_paged_attn_ex.restype = c_int
     _chk(lib().pm_paged_attn_ex(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(meta.block_table), _p(meta.seq_lens),
                                 _p(meta.q_start), _p(meta.q_lens), _p(po), _p(pml), c_int(n_seq),
                                 c_int(meta.block_table.shape[1]), c_int(total_q), c_int(meta.max_q), c_int(hq),
                                 c_int(hkv), c_int(n_split), c_float(scale), c_int(window), c_int(sink), _p(k_scale),
                                 _p(v_scale), _stream()), "pm_paged_attn")
+    return out
+
+
+def kv_append_tq4(k, v, k_cache, v_cache, k_scale, v_scale, slots, sign, thresholds) -> None:
+    """bf16 k, v [n, hkv, 128] -> rotated 4-bit cache [num_blocks, 64, hkv, 64] bytes with fp32 scales
+    [num_blocks, 64, hkv, 2]; ``sign`` [128] (+-1) and ``thresholds`` [15] are device fp32 tensors."""
+    n, hkv, d = k.shape
+    assert d == 128 and k.dtype == torch.bfloat16 and k.stride(2) == 1 and v.stride(2) == 1 and k.stride(1) == d
+    lib().pm_kv_append_tq4.restype = c_int
+    _chk(lib().pm_kv_append_tq4(_p(k), c_ll(k.stride(0)), _p(v), c_ll(v.stride(0)), _p(k_cache), _p(v_cache),
+                                _p(k_scale), _p(v_scale), _p(slots), _p(sign), _p(thresholds), c_int(n), c_int(hkv),
+                                _stream()), "pm_kv_append_tq4")
+
+
+def tq_rotate(x, sign, inverse: bool = False):
+    """Signed Walsh-Hadamard rotation of every 128-vector of x [T, h, 128] (bf16): forward H(x sign)/sqrt(d), inverse
+    (H x)/sqrt(d) sign."""
+    T, h, d = x.shape
+    assert d == 128 and x.stride(2) == 1 and x.stride(1) == d
+    out = torch.empty(T, h, d, dtype=x.dtype, device=x.device)
+    lib().pm_tq_rotate.restype = c_int
+    _chk(lib().pm_tq_rotate(_p(x), c_ll(x.stride(0)), _p(sign), _p(out), c_ll(out.stride(0)), c_ll(T), c_int(h),
+                            c_int(int(inverse)), _stream()), "pm_tq_rotate")
     return out
 
 

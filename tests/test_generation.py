@@ -174,3 +174,29 @@ def test_cache_mode_rule_and_paged_cache_variants_on_cpu():
     # the windowed result equals dense attention restricted to sink + window (the CPU path applies the same mask)
     small.free_sequence(sid)
     assert small.num_free() == 32
+
+
+def test_rotated_4bit_cache_reference_path():
+    """The rotated 4-bit code-book cache on the CPU path: written with the PyTorch quantiser, read back de-rotated; the
+    logits stay close to the 16-bit cache and most greedy tokens agree."""
+    from pmetal_b200.models.config import ModelArgs
+    from pmetal_b200.models.decoder import DecoderLM
+    from pmetal_b200.models.generation import Generator
+    from pmetal_b200.models.sampling import SamplingParams
+    cfg = ModelArgs(vocab_size=300, hidden_size=256, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                    num_key_value_heads=1, head_dim=128)
+    model = DecoderLM(cfg).init_weights(0.05, 0).eval()
+    for p in model.parameters():
+        p.requires_grad_(False)
+    prompt = list(range(3, 150))
+    g1, g2 = Generator(model, cache=model.new_cache(32)), Generator(model, cache=model.new_cache(32, quant="tq4"))
+    assert g2.cache.k[0].dtype == torch.uint8 and g2.cache.k[0].shape[-1] == 64
+    s1, s2 = g1.new_seq(), g2.new_seq()
+    l1, l2 = g1.prefill([s1], [prompt]), g2.prefill([s2], [prompt])
+    assert (l1 - l2).norm() < 0.25 * l1.norm()           # a randomly initialised model amplifies the 10 % key error
+    k16, _ = g1.cache.gather(0, s1)
+    k4, _ = g2.cache.gather(0, s2)
+    rel = (k16.float() - k4.float()).norm() / k16.float().norm()
+    assert rel < 0.12, rel                          # 4-bit Lloyd-Max on unit-variance coordinates: about 10 % error
+    with pytest.raises(ValueError):
+        model.new_cache(8, quant="q2")

@@ -648,6 +648,60 @@ def test_paged_attention_int8_cache_and_sink_window(hq, hkv, lens, qlens, window
     nat.check_status()
 
 
+@pytest.mark.parametrize("hq,hkv,lens,qlens", [(4, 2, [700, 64, 1], [1, 1, 1]), (8, 2, [2000, 130], [1, 3])])
+def test_paged_attention_rotated_4bit_cache(hq, hkv, lens, qlens):
+    """Rotated 4-bit code-book cache: the append kernel (rotation, norm, 16-level quantiser) against the PyTorch
+    quantiser, and attention in the rotated basis (query rotated in, output rotated back) against dense attention over
+    the de-quantised, de-rotated keys and values."""
+    nat = _nat()
+    from pmetal_b200.models.kv_cache import PagedKVCache
+    from pmetal_b200.models.turboquant import unpack_bits
+    torch.manual_seed(14)
+    d = 128
+    cache = PagedKVCache(1, hkv, d, 128, torch.bfloat16, "cuda", quant="tq4")
+    tq = cache.tq
+    ks, vs = [], []
+    for i, (L, n) in enumerate(zip(lens, qlens)):
+        cache.add_sequence(i)
+        k, v = _rand(L, hkv, d), _rand(L, hkv, d)
+        ks.append(k); vs.append(v)
+        if L - n > 0:
+            cache.append(0, k[:L - n], v[:L - n], torch.tensor(cache.reserve(i, L - n), device="cuda"))
+    meta = cache.prepare(list(range(len(lens))), qlens)
+    knew = torch.cat([k[L - n:] for k, L, n in zip(ks, lens, qlens)])
+    vnew = torch.cat([v[L - n:] for v, L, n in zip(vs, lens, qlens)])
+    cache.append(0, knew, vnew, meta.slots)
+    # rotation kernel against the PyTorch transform, and its inverse
+    x = _rand(50, 3, d)
+    _close(nat.tq_rotate(x, tq.sign), tq.rotate(x.float()), what="rotate")
+    _close(nat.tq_rotate(nat.tq_rotate(x, tq.sign), tq.sign, inverse=True), x, what="rotate and back")
+    # codes: the kernel and the PyTorch quantiser agree except where a coordinate sits on a threshold
+    want = tq.encode(knew.float())
+    got = cache.k[0].view(-1, hkv, d // 2)[meta.slots]
+    cw, cg = unpack_bits(want.codes, 4, d).int(), unpack_bits(got, 4, d).int()
+    assert float((cw != cg).float().mean()) < 0.01 and int((cw - cg).abs().max()) <= 1
+    sc = cache.k_scale[0].view(-1, hkv, 2)[meta.slots]
+    assert torch.allclose(sc[..., 0], knew.float().norm(dim=-1) / d ** 0.5, rtol=1e-3) and torch.equal(sc[..., 0], sc[..., 1])
+    q = _rand(meta.total_q, hq, d)
+    scale = d ** -0.5
+    out = cache.attention(0, q, meta, scale)
+    rep = hq // hkv
+    qs = meta.q_start.tolist()
+    for i, (L, n) in enumerate(zip(lens, qlens)):
+        kd, vd = cache.gather(0, i)                               # de-quantised, back in the original basis
+        qq = q[qs[i]:qs[i] + n].float().transpose(0, 1)
+        kk = kd.float().transpose(0, 1).repeat_interleave(rep, 0)
+        vv = vd.float().transpose(0, 1).repeat_interleave(rep, 0)
+        s_ = qq @ kk.transpose(1, 2) * scale
+        qpos = torch.arange(L - n, L, device="cuda")[:, None]
+        kpos = torch.arange(L, device="cuda")[None, :]
+        s_ = s_.masked_fill(~(kpos <= qpos), float("-inf"))
+        _close(out[qs[i]:qs[i] + n], (s_.softmax(-1) @ vv).transpose(0, 1), rtol=4e-2, atol=4e-2, what=f"4-bit paged attn seq {i}")
+        rel = (kd.float() - ks[i].float()).norm() / ks[i].float().norm()
+        assert float(rel) < 0.12
+    nat.check_status()
+
+
 def test_generation_with_int8_and_rotating_cache_on_gpu():
     _nat()
     from pmetal_b200.models.config import ModelArgs
