@@ -1,3 +1,4 @@
+import pytest
 import torch
 
 from pmetal_b200.models.config import preset
