@@ -16,6 +16,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .fast import Linear
+
 
 # ------------------------------------------------------------------------------------------------ embeddings
 def timestep_embedding(t: torch.Tensor, dim: int = 256, max_period: float = 10000.0) -> torch.Tensor:
@@ -29,7 +31,7 @@ def timestep_embedding(t: torch.Tensor, dim: int = 256, max_period: float = 1000
 class _MlpEmbedder(nn.Module):
     def __init__(self, din, dout):
         super().__init__()
-        self.linear_1, self.linear_2 = nn.Linear(din, dout), nn.Linear(dout, dout)
+        self.linear_1, self.linear_2 = Linear(din, dout), Linear(dout, dout)
 
     def forward(self, x):
         return self.linear_2(F.silu(self.linear_1(x)))
@@ -83,7 +85,7 @@ class _AdaNorm(nn.Module):
 
     def __init__(self, dim, n):
         super().__init__()
-        self.linear = nn.Linear(dim, n * dim)
+        self.linear = Linear(dim, n * dim)
         self.n = n
 
     def forward(self, x, emb):
@@ -95,8 +97,8 @@ class _FeedForward(nn.Module):
     def __init__(self, dim):
         super().__init__()
         proj = nn.Module()
-        proj.proj = nn.Linear(dim, 4 * dim)
-        self.net = nn.ModuleList([proj, nn.Identity(), nn.Linear(4 * dim, dim)])
+        proj.proj = Linear(dim, 4 * dim)
+        self.net = nn.ModuleList([proj, nn.Identity(), Linear(4 * dim, dim)])
 
     def forward(self, x):
         return self.net[2](F.gelu(self.net[0].proj(x), approximate="tanh"))
@@ -107,13 +109,13 @@ class _JointAttention(nn.Module):
         super().__init__()
         self.h, self.joint = heads, joint
         d = dim // heads
-        self.to_q, self.to_k, self.to_v = nn.Linear(dim, dim), nn.Linear(dim, dim), nn.Linear(dim, dim)
+        self.to_q, self.to_k, self.to_v = Linear(dim, dim), Linear(dim, dim), Linear(dim, dim)
         self.norm_q, self.norm_k = _RmsNorm(d), _RmsNorm(d)
         if joint:
-            self.add_q_proj, self.add_k_proj, self.add_v_proj = nn.Linear(dim, dim), nn.Linear(dim, dim), nn.Linear(dim, dim)
+            self.add_q_proj, self.add_k_proj, self.add_v_proj = Linear(dim, dim), Linear(dim, dim), Linear(dim, dim)
             self.norm_added_q, self.norm_added_k = _RmsNorm(d), _RmsNorm(d)
-            self.to_out = nn.ModuleList([nn.Linear(dim, dim), nn.Identity()])
-            self.to_add_out = nn.Linear(dim, dim)
+            self.to_out = nn.ModuleList([Linear(dim, dim), nn.Identity()])
+            self.to_add_out = Linear(dim, dim)
 
     def _split(self, x):
         B, T, D = x.shape
@@ -156,8 +158,8 @@ class _SingleBlock(nn.Module):
     def __init__(self, dim, heads):
         super().__init__()
         self.norm = _AdaNorm(dim, 3)
-        self.proj_mlp = nn.Linear(dim, 4 * dim)
-        self.proj_out = nn.Linear(5 * dim, dim)
+        self.proj_mlp = Linear(dim, 4 * dim)
+        self.proj_out = Linear(5 * dim, dim)
         self.attn = _JointAttention(dim, heads, False)
 
     def forward(self, x, emb, cos, sin):
@@ -169,7 +171,7 @@ class _SingleBlock(nn.Module):
 class _AdaNormOut(nn.Module):
     def __init__(self, dim):
         super().__init__()
-        self.linear = nn.Linear(dim, 2 * dim)
+        self.linear = Linear(dim, 2 * dim)
 
     def forward(self, x, emb):
         scale, shift = self.linear(F.silu(emb))[:, None].chunk(2, -1)
@@ -185,13 +187,13 @@ class FluxTransformer(nn.Module):
         self.axes_dim = list(cfg.get("axes_dims_rope", (16, 56, 56)))
         assert sum(self.axes_dim) == hd
         cin = cfg.get("in_channels", 64)
-        self.x_embedder = nn.Linear(cin, dim)
-        self.context_embedder = nn.Linear(cfg.get("joint_attention_dim", 4096), dim)
+        self.x_embedder = Linear(cin, dim)
+        self.context_embedder = Linear(cfg.get("joint_attention_dim", 4096), dim)
         self.time_text_embed = _TimeTextEmbed(dim, cfg.get("pooled_projection_dim", 768), bool(cfg.get("guidance_embeds", False)))
         self.transformer_blocks = nn.ModuleList([_DoubleBlock(dim, heads) for _ in range(cfg.get("num_layers", 19))])
         self.single_transformer_blocks = nn.ModuleList([_SingleBlock(dim, heads) for _ in range(cfg.get("num_single_layers", 38))])
         self.norm_out = _AdaNormOut(dim)
-        self.proj_out = nn.Linear(dim, cfg.get("out_channels") or cin)
+        self.proj_out = Linear(dim, cfg.get("out_channels") or cin)
 
     def forward(self, latents, text, pooled, timestep, img_ids, txt_ids, guidance: Optional[torch.Tensor] = None):
         """latents [B, T_img, C_in] (packed patches), text [B, T_txt, D_txt], pooled [B, D_pool], timestep [B] in [0, 1],
@@ -266,8 +268,8 @@ class _VaeAttention(nn.Module):
     def __init__(self, c, groups=32):
         super().__init__()
         self.group_norm = nn.GroupNorm(groups, c, eps=1e-6)
-        self.to_q, self.to_k, self.to_v = nn.Linear(c, c), nn.Linear(c, c), nn.Linear(c, c)
-        self.to_out = nn.ModuleList([nn.Linear(c, c), nn.Identity()])
+        self.to_q, self.to_k, self.to_v = Linear(c, c), Linear(c, c), Linear(c, c)
+        self.to_out = nn.ModuleList([Linear(c, c), nn.Identity()])
 
     def forward(self, x):
         B, C, H, W = x.shape

@@ -13,6 +13,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .fast import Linear
+
 
 def _act(name: str):
     return {"gelu": F.gelu, "relu": F.relu, "silu": F.silu, "gelu_new": lambda x: F.gelu(x, approximate="tanh"),
@@ -34,7 +36,7 @@ class _BertSelf(nn.Module):
     def __init__(self, H, h):
         super().__init__()
         self.h = h
-        self.query, self.key, self.value = nn.Linear(H, H), nn.Linear(H, H), nn.Linear(H, H)
+        self.query, self.key, self.value = Linear(H, H), Linear(H, H), Linear(H, H)
 
     def forward(self, x, mask):
         q, k, v = (_heads(f(x), self.h) for f in (self.query, self.key, self.value))
@@ -44,7 +46,7 @@ class _BertSelf(nn.Module):
 class _BertOut(nn.Module):
     def __init__(self, inp, H, eps):
         super().__init__()
-        self.dense = nn.Linear(inp, H)
+        self.dense = Linear(inp, H)
         self.LayerNorm = nn.LayerNorm(H, eps=eps)
 
     def forward(self, x, residual):
@@ -64,7 +66,7 @@ class _BertAttention(nn.Module):
 class _BertIntermediate(nn.Module):
     def __init__(self, H, I):
         super().__init__()
-        self.dense = nn.Linear(H, I)
+        self.dense = Linear(H, I)
 
 
 class _BertLayer(nn.Module):
@@ -108,7 +110,7 @@ class _BertEncoder(nn.Module):
 class _BertPooler(nn.Module):
     def __init__(self, H):
         super().__init__()
-        self.dense = nn.Linear(H, H)
+        self.dense = Linear(H, H)
 
 
 class BertModel(nn.Module):
@@ -185,8 +187,8 @@ class _T5Attention(nn.Module):
         inner = c["num_heads"] * c["d_kv"]
         self.h, self.bidirectional = c["num_heads"], bidirectional
         self.buckets, self.max_dist = c.get("relative_attention_num_buckets", 32), c.get("relative_attention_max_distance", 128)
-        self.q, self.k, self.v = (nn.Linear(c["d_model"], inner, bias=False) for _ in range(3))
-        self.o = nn.Linear(inner, c["d_model"], bias=False)
+        self.q, self.k, self.v = (Linear(c["d_model"], inner, bias=False) for _ in range(3))
+        self.o = Linear(inner, c["d_model"], bias=False)
         if has_bias:
             self.relative_attention_bias = nn.Embedding(self.buckets, self.h)
 
@@ -225,10 +227,10 @@ class _T5Dense(nn.Module):
         self.gated = proj.startswith("gated-")
         self.fn = _act({"gelu": "gelu_new"}.get(proj.replace("gated-", ""), proj.replace("gated-", "")))
         if self.gated:
-            self.wi_0, self.wi_1 = nn.Linear(c["d_model"], c["d_ff"], bias=False), nn.Linear(c["d_model"], c["d_ff"], bias=False)
+            self.wi_0, self.wi_1 = Linear(c["d_model"], c["d_ff"], bias=False), Linear(c["d_model"], c["d_ff"], bias=False)
         else:
-            self.wi = nn.Linear(c["d_model"], c["d_ff"], bias=False)
-        self.wo = nn.Linear(c["d_ff"], c["d_model"], bias=False)
+            self.wi = Linear(c["d_model"], c["d_ff"], bias=False)
+        self.wo = Linear(c["d_ff"], c["d_model"], bias=False)
 
     def forward(self, x):
         return self.wo(self.fn(self.wi_0(x)) * self.wi_1(x)) if self.gated else self.wo(self.fn(self.wi(x)))
@@ -294,7 +296,7 @@ class T5Model(nn.Module):
         self.decoder.embed_tokens = self.shared
         self.tied = bool(cfg.get("tie_word_embeddings", True))
         if not self.tied:
-            self.lm_head = nn.Linear(cfg["d_model"], cfg["vocab_size"], bias=False)
+            self.lm_head = Linear(cfg["d_model"], cfg["vocab_size"], bias=False)
 
     def encode(self, input_ids, attention_mask=None):
         return self.encoder(input_ids, mask=attention_mask)
@@ -314,8 +316,8 @@ class _PreLnAttention(nn.Module):
     def __init__(self, H, h, k_bias: bool = True):
         super().__init__()
         self.h = h
-        self.q_proj, self.v_proj, self.out_proj = nn.Linear(H, H), nn.Linear(H, H), nn.Linear(H, H)
-        self.k_proj = nn.Linear(H, H, bias=k_bias)
+        self.q_proj, self.v_proj, self.out_proj = Linear(H, H), Linear(H, H), Linear(H, H)
+        self.k_proj = Linear(H, H, bias=k_bias)
 
     def forward(self, x, kv=None, causal: bool = False):
         kv = x if kv is None else kv
@@ -326,7 +328,7 @@ class _PreLnAttention(nn.Module):
 class _ClipMlp(nn.Module):
     def __init__(self, H, I, act):
         super().__init__()
-        self.fc1, self.fc2, self.fn = nn.Linear(H, I), nn.Linear(I, H), _act(act)
+        self.fc1, self.fc2, self.fn = Linear(H, I), Linear(I, H), _act(act)
 
     def forward(self, x):
         return self.fc2(self.fn(self.fc1(x)))
@@ -411,8 +413,8 @@ class ClipModel(nn.Module):
         t, v = cfg["text_config"], cfg["vision_config"]
         dim = cfg.get("projection_dim", 512)
         self.text_model, self.vision_model = _ClipText(t), _ClipVision(v)
-        self.visual_projection = nn.Linear(v["hidden_size"], dim, bias=False)
-        self.text_projection = nn.Linear(t["hidden_size"], dim, bias=False)
+        self.visual_projection = Linear(v["hidden_size"], dim, bias=False)
+        self.text_projection = Linear(t["hidden_size"], dim, bias=False)
         self.logit_scale = nn.Parameter(torch.tensor(cfg.get("logit_scale_init_value", 2.6592)))
 
     def text_embeds(self, ids):
@@ -436,7 +438,7 @@ class _WhisperLayer(nn.Module):
         if cross:
             self.encoder_attn = _PreLnAttention(D, h, k_bias=False)
             self.encoder_attn_layer_norm = nn.LayerNorm(D)
-        self.fc1, self.fc2, self.final_layer_norm, self.fn = nn.Linear(D, ffn), nn.Linear(ffn, D), nn.LayerNorm(D), _act(act)
+        self.fc1, self.fc2, self.final_layer_norm, self.fn = Linear(D, ffn), Linear(ffn, D), nn.LayerNorm(D), _act(act)
 
     def forward(self, x, enc=None):
         x = x + self.self_attn(self.self_attn_layer_norm(x), causal=enc is not None)

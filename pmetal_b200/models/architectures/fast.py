@@ -1,0 +1,85 @@
+"""Native-kernel routes for the config-driven architectures: the building blocks of ``generic.py`` and its siblings are
+ordinary ``torch.nn`` modules (they are checked against Hugging Face on CPU in fp32); on a GPU in bf16 their hot operators
+are sent to the same sm_100a kernels as the fast decoder:
+
+* ``Linear``      frozen bf16 projections run on the tcgen05 GEMM forward and for the input gradient (split-K inside the
+                  kernel for a handful of rows), bias added on top; trainable or fp32 weights keep ``F.linear``;
+* ``rms_norm``    plain RMS norms over the last dimension run on the fused norm kernel;
+* ``causal_attention``  full-sequence causal (optionally sliding-window) self-attention without soft-capping, sinks or an
+                  explicit mask runs on the varlen flash-attention kernels, every batch row as one document, head sizes
+                  below 128 zero-padded.
+
+Everything else (soft-capped logits, attention sinks, chunked masks, cached decode steps, layer norms) stays on the
+PyTorch operators. The reference has stand-alone native engines per family
+(crates/pmetal-bridge/src/{qwen3,deepseek,gpt_oss,llama4}_native/, gemma4_native.rs); here one set of kernels serves
+every family through these three entry points."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+import os
+
+# comma-separated routes that are switched on: linear, norm, attention (all by default)
+ROUTES = set(os.environ.get("PMETAL_PORTABLE_FAST", "linear,norm,attention").split(","))
+
+
+def _native(x: torch.Tensor) -> bool:
+    if not x.is_cuda or x.dtype != torch.bfloat16:
+        return False
+    from ...ops import functional as ops
+    return ops.use_native(x)
+
+
+class Linear(nn.Linear):
+    """``nn.Linear`` whose forward takes the tensor-core GEMM when the weight is a frozen bf16 matrix."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w = self.weight
+        if ("linear" in ROUTES and w.dtype == torch.bfloat16 and not w.requires_grad and self.in_features % 8 == 0 and self.out_features % 8 == 0
+                and x.numel() > 0 and _native(x)):
+            from ...ops import functional as ops
+            x2 = x.reshape(-1, self.in_features)
+            if x2.stride(-1) != 1 or (x2.stride(0) % 8):
+                x2 = x2.contiguous()
+            y = ops.lora_linear(x2, w, None, None, None, (self.out_features,), 0, 0.0, None)
+            if self.bias is not None:
+                y = y + self.bias
+            return y.view(*x.shape[:-1], self.out_features)
+        return F.linear(x, w, self.bias)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> Optional[torch.Tensor]:
+    """weight * x / rms(x) over the last dimension on the fused kernel, or None when the shapes / types do not fit."""
+    if "norm" not in ROUTES or weight.dim() != 1 or x.shape[-1] != weight.shape[0] or x.shape[-1] % 8 or weight.dtype != torch.bfloat16 \
+            or not _native(x):
+        return None
+    from ...ops import functional as ops
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    return ops.rms_norm(x2, weight, eps).view(x.shape)
+
+
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int = 0) -> Optional[torch.Tensor]:
+    """q [B, h, T, d], k / v [B, hkv, T, d] (same T: no cache) -> [B, h, T, d] with a causal (sliding-window) mask, on the
+    varlen kernels; None when the case is not covered."""
+    B, h, T, d = q.shape
+    if "attention" not in ROUTES or k.shape[2] != T or v.shape[-1] != d or d > 128 or d % 8 or h % k.shape[1] or not _native(q):
+        return None
+    from ...ops import functional as ops
+    hkv = k.shape[1]
+    qf = q.transpose(1, 2).reshape(B * T, h, d)
+    kf = k.transpose(1, 2).reshape(B * T, hkv, d)
+    vf = v.transpose(1, 2).reshape(B * T, hkv, d)
+    if d < 128:
+        pad = (0, 128 - d)
+        qf, kf, vf = F.pad(qf, pad), F.pad(kf, pad), F.pad(vf, pad)
+    qf, kf, vf = qf.contiguous(), kf.contiguous(), vf.contiguous()
+    seq_start = (torch.arange(B, device=q.device, dtype=torch.int32) * T).repeat_interleave(T)
+    o = ops._AttnCoreFn.apply(qf, kf, vf, seq_start, scale, int(window))
+    return o[..., :d].reshape(B, T, h, d).transpose(1, 2)

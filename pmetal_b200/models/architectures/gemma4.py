@@ -28,6 +28,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .fast import Linear
+
 from .generic import KVCache, _act, apply_rope, attend, build_mask
 
 
@@ -163,10 +165,10 @@ class Gemma4Attention(nn.Module):
         self.hkv = c.layer_kv_heads(idx)
         self.source = c.kv_source(idx)
         H, b = c.hidden_size, c.attention_bias
-        self.q_proj = nn.Linear(H, c.num_heads * self.d, bias=b)
-        self.k_proj = nn.Linear(H, self.hkv * self.d, bias=b)
-        self.v_proj = None if c.layer_k_eq_v(idx) else nn.Linear(H, self.hkv * self.d, bias=b)
-        self.o_proj = nn.Linear(c.num_heads * self.d, H, bias=b)
+        self.q_proj = Linear(H, c.num_heads * self.d, bias=b)
+        self.k_proj = Linear(H, self.hkv * self.d, bias=b)
+        self.v_proj = None if c.layer_k_eq_v(idx) else Linear(H, self.hkv * self.d, bias=b)
+        self.o_proj = Linear(c.num_heads * self.d, H, bias=b)
         self.q_norm = RMSNorm(self.d, c.eps)
         self.k_norm = RMSNorm(self.d, c.eps)
         self.v_norm = RMSNorm(self.d, c.eps, with_scale=False)
@@ -197,9 +199,9 @@ class Gemma4MLP(nn.Module):
         super().__init__()
         wide = c.double_wide_mlp and c.kv_source(idx) is not None
         inter = c.intermediate_size * (2 if wide else 1)
-        self.gate_proj = nn.Linear(c.hidden_size, inter, bias=False)
-        self.up_proj = nn.Linear(c.hidden_size, inter, bias=False)
-        self.down_proj = nn.Linear(inter, c.hidden_size, bias=False)
+        self.gate_proj = Linear(c.hidden_size, inter, bias=False)
+        self.up_proj = Linear(c.hidden_size, inter, bias=False)
+        self.down_proj = Linear(inter, c.hidden_size, bias=False)
         self.act = _act(c.activation)
 
     def forward(self, x):
@@ -214,7 +216,7 @@ class Gemma4Router(nn.Module):
         super().__init__()
         self.c = c
         self.norm = RMSNorm(c.hidden_size, c.eps, with_scale=False)
-        self.proj = nn.Linear(c.hidden_size, c.num_experts, bias=False)
+        self.proj = Linear(c.hidden_size, c.num_experts, bias=False)
         self.scale = nn.Parameter(torch.ones(c.hidden_size))
         self.per_expert_scale = nn.Parameter(torch.ones(c.num_experts))
 
@@ -268,8 +270,8 @@ class Gemma4Layer(nn.Module):
         self.post_feedforward_layernorm = RMSNorm(H, c.eps)
         self.register_buffer("layer_scalar", torch.ones(1))
         if c.per_layer_dim:
-            self.per_layer_input_gate = nn.Linear(H, c.per_layer_dim, bias=False)
-            self.per_layer_projection = nn.Linear(c.per_layer_dim, H, bias=False)
+            self.per_layer_input_gate = Linear(H, c.per_layer_dim, bias=False)
+            self.per_layer_projection = Linear(c.per_layer_dim, H, bias=False)
             self.post_per_layer_input_norm = RMSNorm(H, c.eps)
             self.act = _act(c.activation)
         if c.moe:
@@ -303,7 +305,7 @@ class _Backbone(nn.Module):
         self.norm = RMSNorm(c.hidden_size, c.eps)
         if c.per_layer_dim:
             self.embed_tokens_per_layer = nn.Embedding(c.vocab_size_per_layer, c.num_layers * c.per_layer_dim)
-            self.per_layer_model_projection = nn.Linear(c.hidden_size, c.num_layers * c.per_layer_dim, bias=False)
+            self.per_layer_model_projection = Linear(c.hidden_size, c.num_layers * c.per_layer_dim, bias=False)
             self.per_layer_projection_norm = RMSNorm(c.per_layer_dim, c.eps)
 
 
@@ -313,7 +315,7 @@ class Gemma4LM(nn.Module):
         self.c = c
         self.model = _Backbone(c)
         if not c.tie_embeddings:
-            self.lm_head = nn.Linear(c.hidden_size, c.vocab_size, bias=False)
+            self.lm_head = Linear(c.hidden_size, c.vocab_size, bias=False)
         self.register_buffer("inv_local", rope_table(c.rope_local, c.head_dim), persistent=False)
         self.register_buffer("inv_global", rope_table(c.rope_global, c.global_head_dim or c.head_dim), persistent=False)
 

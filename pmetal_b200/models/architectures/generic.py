@@ -20,6 +20,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .fast import Linear
+
 
 # ------------------------------------------------------------------------------------------------ configuration
 @dataclass
@@ -319,6 +321,11 @@ class Norm(nn.Module):
             self.bias = nn.Parameter(torch.zeros(dim))
 
     def forward(self, x):
+        if self.kind == "rms":
+            from .fast import rms_norm
+            y = rms_norm(x, self.weight, self.eps)
+            if y is not None:
+                return y
         xf = x.float()
         if self.kind.startswith("rms"):
             y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)
@@ -525,12 +532,12 @@ class Attention(nn.Module):
         self.kind = c.layer_type(idx)
         self.rotary = idx not in c.nope_layers
         if c.fused_qkv:
-            self.qkv_proj = nn.Linear(H, (c.n_heads + 2 * c.n_kv_heads) * d, bias=c.attn_bias)
+            self.qkv_proj = Linear(H, (c.n_heads + 2 * c.n_kv_heads) * d, bias=c.attn_bias)
         else:
-            self.q_proj = nn.Linear(H, c.n_heads * d * (2 if c.attn_output_gate else 1), bias=c.attn_bias)
-            self.k_proj = nn.Linear(H, c.n_kv_heads * d, bias=c.attn_bias)
-            self.v_proj = nn.Linear(H, c.n_kv_heads * d, bias=c.attn_bias)
-        setattr(self, c.attn_out_name, nn.Linear(c.n_heads * d, H, bias=c.o_bias))
+            self.q_proj = Linear(H, c.n_heads * d * (2 if c.attn_output_gate else 1), bias=c.attn_bias)
+            self.k_proj = Linear(H, c.n_kv_heads * d, bias=c.attn_bias)
+            self.v_proj = Linear(H, c.n_kv_heads * d, bias=c.attn_bias)
+        setattr(self, c.attn_out_name, Linear(c.n_heads * d, H, bias=c.o_bias))
         qn = c.qk_norm if (self.rotary or not c.qk_norm_rope_only) else ""
         self.qn_kind = qn
         if qn == "head":
@@ -573,10 +580,17 @@ class Attention(nn.Module):
             q = (q * t[:, None, :, None]).to(q.dtype)
         if cache is not None:
             k, v = cache.append(self.idx, k, v)
-        mask = rope["mask"] if rope.get("mask") is not None else \
-            build_mask(self.kind, positions, k_positions, c.sliding_window, c.chunk_size)
         scale = (c.attn_scale or d ** -0.5) * rope.get("attention_factor", 1.0) ** 2
-        o = attend(q, k, v, mask, scale, c.attn_softcap, self.sinks if c.sinks else None)
+        o = None
+        if (cache is None and rope.get("mask") is None and c.attn_softcap <= 0 and not c.sinks
+                and self.kind in ("full", "sliding") and q.is_cuda and rope.get("contiguous", False)):
+            # whole sequences from position 0 with a causal (or sliding-window) mask: the varlen flash-attention kernels
+            from .fast import causal_attention
+            o = causal_attention(q, k, v, scale, c.sliding_window if self.kind == "sliding" else 0)
+        if o is None:
+            mask = rope["mask"] if rope.get("mask") is not None else \
+                build_mask(self.kind, positions, k_positions, c.sliding_window, c.chunk_size)
+            o = attend(q, k, v, mask, scale, c.attn_softcap, self.sinks if c.sinks else None)
         o = o.transpose(1, 2).reshape(B, T, c.n_heads * d)
         if gate is not None:
             o = o * torch.sigmoid(gate)
@@ -594,12 +608,12 @@ class GatedDeltaNet(nn.Module):
         self.key_dim, self.value_dim = c.lin_k_dim * c.lin_k_heads, c.lin_v_dim * c.lin_v_heads
         conv_dim = 2 * self.key_dim + self.value_dim
         self.conv1d = nn.Conv1d(conv_dim, conv_dim, c.lin_conv, groups=conv_dim, padding=c.lin_conv - 1, bias=False)
-        self.in_proj_qkvz = nn.Linear(c.hidden_size, 2 * self.key_dim + 2 * self.value_dim, bias=False)
-        self.in_proj_ba = nn.Linear(c.hidden_size, 2 * c.lin_v_heads, bias=False)
+        self.in_proj_qkvz = Linear(c.hidden_size, 2 * self.key_dim + 2 * self.value_dim, bias=False)
+        self.in_proj_ba = Linear(c.hidden_size, 2 * c.lin_v_heads, bias=False)
         self.dt_bias = nn.Parameter(torch.ones(c.lin_v_heads))
         self.A_log = nn.Parameter(torch.log(torch.empty(c.lin_v_heads).uniform_(0, 16)))
         self.norm = Norm(c.lin_v_dim, "rms", c.norm_eps)
-        self.out_proj = nn.Linear(self.value_dim, c.hidden_size, bias=False)
+        self.out_proj = Linear(self.value_dim, c.hidden_size, bias=False)
 
     def forward(self, x, rope, positions, cache: Optional[KVCache], k_positions):
         from ..gdn import gdn_chunked, gdn_recurrent
@@ -665,15 +679,15 @@ class LatentAttention(nn.Module):
         H, h = c.hidden_size, c.n_heads
         qd = c.qk_nope_dim + c.qk_rope_dim
         if c.q_lora_rank:
-            self.q_a_proj = nn.Linear(H, c.q_lora_rank, bias=c.attn_bias)
+            self.q_a_proj = Linear(H, c.q_lora_rank, bias=c.attn_bias)
             self.q_a_layernorm = Norm(c.q_lora_rank, "rms", c.norm_eps)
-            self.q_b_proj = nn.Linear(c.q_lora_rank, h * qd, bias=False)
+            self.q_b_proj = Linear(c.q_lora_rank, h * qd, bias=False)
         else:
-            self.q_proj = nn.Linear(H, h * qd, bias=False)
-        self.kv_a_proj_with_mqa = nn.Linear(H, c.kv_lora_rank + c.qk_rope_dim, bias=c.attn_bias)
+            self.q_proj = Linear(H, h * qd, bias=False)
+        self.kv_a_proj_with_mqa = Linear(H, c.kv_lora_rank + c.qk_rope_dim, bias=c.attn_bias)
         self.kv_a_layernorm = Norm(c.kv_lora_rank, "rms", c.norm_eps)
-        self.kv_b_proj = nn.Linear(c.kv_lora_rank, h * (c.qk_nope_dim + c.v_head_dim), bias=False)
-        self.o_proj = nn.Linear(h * c.v_head_dim, H, bias=c.attn_bias)
+        self.kv_b_proj = Linear(c.kv_lora_rank, h * (c.qk_nope_dim + c.v_head_dim), bias=False)
+        self.o_proj = Linear(h * c.v_head_dim, H, bias=c.attn_bias)
 
     def forward(self, x, rope, positions, cache, k_positions):
         c = self.c
@@ -704,12 +718,12 @@ class MLP(nn.Module):
         self.c = c
         H = c.hidden_size
         if not c.gated_mlp:
-            self.fc1, self.fc2 = nn.Linear(H, inter, bias=c.mlp_bias), nn.Linear(inter, H, bias=c.mlp_bias)
+            self.fc1, self.fc2 = Linear(H, inter, bias=c.mlp_bias), Linear(inter, H, bias=c.mlp_bias)
         elif c.fused_qkv:
-            self.gate_up_proj, self.down_proj = nn.Linear(H, 2 * inter, bias=c.mlp_bias), nn.Linear(inter, H, bias=c.mlp_bias)
+            self.gate_up_proj, self.down_proj = Linear(H, 2 * inter, bias=c.mlp_bias), Linear(inter, H, bias=c.mlp_bias)
         else:
-            self.gate_proj, self.up_proj = nn.Linear(H, inter, bias=c.mlp_bias), nn.Linear(H, inter, bias=c.mlp_bias)
-            self.down_proj = nn.Linear(inter, H, bias=c.mlp_bias)
+            self.gate_proj, self.up_proj = Linear(H, inter, bias=c.mlp_bias), Linear(H, inter, bias=c.mlp_bias)
+            self.down_proj = Linear(inter, H, bias=c.mlp_bias)
         self.fn = _act(c.act)
 
     def forward(self, x):
@@ -825,7 +839,7 @@ class MoE(nn.Module):
             shared = MLP(_dense_view(c), c.shared_intermediate or c.moe_intermediate * c.n_shared_experts)
             setattr(self, c.shared_name, shared)
             if c.shared_gate:
-                self.shared_expert_gate = nn.Linear(c.hidden_size, 1, bias=False)
+                self.shared_expert_gate = Linear(c.hidden_size, 1, bias=False)
 
     def _expert(self, e: int, x: torch.Tensor) -> torch.Tensor:
         if self.c.moe_name == "block_sparse_moe":
@@ -922,7 +936,7 @@ class GenericDecoderLM(nn.Module):
         self.c = c
         self.model = _Backbone(c)
         if not c.tie_embeddings:
-            self.lm_head = nn.Linear(c.hidden_size, c.vocab_size, bias=c.lm_head_bias)
+            self.lm_head = Linear(c.hidden_size, c.vocab_size, bias=c.lm_head_bias)
         rd = c.rope_dim or c.head_dim
         inv, att = rope_inv_freq(rd, c.rope_theta, c.rope_scaling, c.max_position)
         self.register_buffer("inv_freq", inv, persistent=False)
@@ -968,6 +982,7 @@ class GenericDecoderLM(nn.Module):
             input_ids = input_ids[None]
         B, T = input_ids.shape
         past = cache.length() if cache is not None else 0
+        default_positions = positions is None
         if positions is None:
             positions = torch.arange(past, past + T, device=input_ids.device)[None].expand(B, T)
         k_positions = torch.arange(0, past + T, device=input_ids.device)[None].expand(B, past + T) if cache is not None \
@@ -977,6 +992,7 @@ class GenericDecoderLM(nn.Module):
             x = x * torch.tensor(c.embed_scale, dtype=x.dtype)
         rope = self._rope(positions)
         rope["mask"] = attn_mask
+        rope["contiguous"] = default_positions and past == 0       # every row is a whole sequence starting at position 0
         for layer in self.model.layers:
             x = layer(x, rope, positions, cache, k_positions)
         return getattr(self.model, c.final_norm_name)(x)

@@ -14,6 +14,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .fast import Linear
+
 from .generic import ArchConfig, KVCache, Norm, attend, build_mask, route
 
 
@@ -28,14 +30,14 @@ class Mamba2Mixer(nn.Module):
         self.dt_min = c.get("time_step_min", 0.001)
         self.conv1d = nn.Conv1d(self.conv_dim, self.conv_dim, self.kw, groups=self.conv_dim, padding=self.kw - 1,
                                 bias=c.get("use_conv_bias", True))
-        self.in_proj = nn.Linear(c["hidden_size"], self.inner + self.conv_dim + self.heads, bias=c.get("use_bias", False))
+        self.in_proj = Linear(c["hidden_size"], self.inner + self.conv_dim + self.heads, bias=c.get("use_bias", False))
         self.dt_bias = nn.Parameter(torch.ones(self.heads))
         self.A_log = nn.Parameter(torch.log(torch.arange(1, self.heads + 1).float()))
         self.D = nn.Parameter(torch.ones(self.heads))
         self.norm = nn.Module()
         self.norm.weight = nn.Parameter(torch.ones(self.inner))
         self.eps = c.get("layer_norm_epsilon", 1e-5)
-        self.out_proj = nn.Linear(self.inner, c["hidden_size"], bias=c.get("use_bias", False))
+        self.out_proj = Linear(self.inner, c["hidden_size"], bias=c.get("use_bias", False))
 
     def forward(self, x, cache: Optional[KVCache]):
         B, T, _ = x.shape
@@ -73,8 +75,8 @@ class _Attention(nn.Module):
         H, self.h, self.hkv = c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"]
         self.d = c.get("head_dim") or H // self.h
         bias = c.get("attention_bias", False)
-        self.q_proj, self.k_proj = nn.Linear(H, self.h * self.d, bias=bias), nn.Linear(H, self.hkv * self.d, bias=bias)
-        self.v_proj, self.o_proj = nn.Linear(H, self.hkv * self.d, bias=bias), nn.Linear(self.h * self.d, H, bias=bias)
+        self.q_proj, self.k_proj = Linear(H, self.h * self.d, bias=bias), Linear(H, self.hkv * self.d, bias=bias)
+        self.v_proj, self.o_proj = Linear(H, self.hkv * self.d, bias=bias), Linear(self.h * self.d, H, bias=bias)
 
     def forward(self, x, cache, positions, k_positions):
         B, T, _ = x.shape
@@ -91,8 +93,8 @@ class _Mlp(nn.Module):
     def __init__(self, c: dict):
         super().__init__()
         bias = c.get("mlp_bias", False)
-        self.up_proj = nn.Linear(c["hidden_size"], c["intermediate_size"], bias=bias)
-        self.down_proj = nn.Linear(c["intermediate_size"], c["hidden_size"], bias=bias)
+        self.up_proj = Linear(c["hidden_size"], c["intermediate_size"], bias=bias)
+        self.down_proj = Linear(c["intermediate_size"], c["hidden_size"], bias=bias)
 
     def forward(self, x):
         return self.down_proj(F.relu(self.up_proj(x)).square())
@@ -129,7 +131,7 @@ class _Moe(nn.Module):
         self.shared_experts = _Mlp(dict(c, intermediate_size=c["moe_shared_expert_intermediate_size"]))
         if latent:
             bias = c.get("mlp_bias", False)
-            self.fc1_latent_proj, self.fc2_latent_proj = nn.Linear(H, latent, bias=bias), nn.Linear(latent, H, bias=bias)
+            self.fc1_latent_proj, self.fc2_latent_proj = Linear(H, latent, bias=bias), Linear(latent, H, bias=bias)
         self.latent = bool(latent)
 
     def forward(self, x):
@@ -196,7 +198,7 @@ class NemotronHLM(nn.Module):
         self.cfg = cfg
         self.kinds = block_types(cfg)
         self.backbone = _Backbone(cfg, self.kinds)
-        self.lm_head = nn.Linear(cfg["hidden_size"], cfg["vocab_size"], bias=False)
+        self.lm_head = Linear(cfg["hidden_size"], cfg["vocab_size"], bias=False)
 
     def new_cache(self) -> KVCache:
         return KVCache(len(self.kinds))

@@ -24,6 +24,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .fast import Linear
+
 from .generic import KVCache, apply_rope, attend, rope_inv_freq
 
 
@@ -67,8 +69,8 @@ class _VisionAttention(nn.Module):
     def __init__(self, v: dict):
         super().__init__()
         D, self.h = v["hidden_size"], v["attention_heads"]
-        self.q_proj, self.k_proj = nn.Linear(D, D, bias=False), nn.Linear(D, D, bias=False)
-        self.v_proj, self.o_proj = nn.Linear(D, D, bias=False), nn.Linear(D, D, bias=False)
+        self.q_proj, self.k_proj = Linear(D, D, bias=False), Linear(D, D, bias=False)
+        self.v_proj, self.o_proj = Linear(D, D, bias=False), Linear(D, D, bias=False)
 
     def forward(self, x, bias):
         B, N, D = x.shape
@@ -80,8 +82,8 @@ class _VisionAttention(nn.Module):
 class _VisionMLP(nn.Module):
     def __init__(self, v: dict):
         super().__init__()
-        self.fc1 = nn.Linear(v["hidden_size"], v["intermediate_size"])
-        self.fc2 = nn.Linear(v["intermediate_size"], v["hidden_size"])
+        self.fc1 = Linear(v["hidden_size"], v["intermediate_size"])
+        self.fc2 = Linear(v["intermediate_size"], v["hidden_size"])
         self.tanh_approx = v.get("hidden_act", "gelu") in ("gelu_pytorch_tanh", "gelu_new")
 
     def forward(self, x):
@@ -186,8 +188,8 @@ class _TextMLP(nn.Module):
     def __init__(self, t: dict):
         super().__init__()
         H, I = t["hidden_size"], t["intermediate_size"]
-        self.gate_proj, self.up_proj = nn.Linear(H, I, bias=False), nn.Linear(H, I, bias=False)
-        self.down_proj = nn.Linear(I, H, bias=False)
+        self.gate_proj, self.up_proj = Linear(H, I, bias=False), Linear(H, I, bias=False)
+        self.down_proj = Linear(I, H, bias=False)
 
     def forward(self, x):
         return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
@@ -198,10 +200,10 @@ class _Proj(nn.Module):
         super().__init__()
         H, self.h, self.hkv = t["hidden_size"], t["num_attention_heads"], t.get("num_key_value_heads") or t["num_attention_heads"]
         self.d = H // self.h
-        self.q_proj = nn.Linear(H, self.h * self.d, bias=False)
-        self.k_proj = nn.Linear(H, self.hkv * self.d, bias=False)
-        self.v_proj = nn.Linear(H, self.hkv * self.d, bias=False)
-        self.o_proj = nn.Linear(self.h * self.d, H, bias=False)
+        self.q_proj = Linear(H, self.h * self.d, bias=False)
+        self.k_proj = Linear(H, self.hkv * self.d, bias=False)
+        self.v_proj = Linear(H, self.hkv * self.d, bias=False)
+        self.o_proj = Linear(self.h * self.d, H, bias=False)
 
 
 class _SelfAttention(_Proj):
@@ -315,7 +317,7 @@ class _MllamaBody(nn.Module):
         v, t = config["vision_config"], config["text_config"]
         self.vision_model = MllamaVision(v)
         self.language_model = MllamaText(t)
-        self.multi_modal_projector = nn.Linear(v["vision_output_dim"], t["hidden_size"])
+        self.multi_modal_projector = Linear(v["vision_output_dim"], t["hidden_size"])
 
 
 def prepare_cross_mask(cross_attention_mask: torch.Tensor, vision_tokens: int, dtype) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -336,7 +338,7 @@ class MllamaForConditionalGeneration(nn.Module):
         self.config = config
         self.model = _MllamaBody(config)
         t = config["text_config"]
-        self.lm_head = nn.Linear(t["hidden_size"], t["vocab_size"], bias=False)
+        self.lm_head = Linear(t["hidden_size"], t["vocab_size"], bias=False)
 
     def encode_images(self, pixel_values, aspect_ratio_ids, aspect_ratio_mask) -> torch.Tensor:
         """Projected vision states [B, images*tiles*patches, hidden] for the cross-attention layers."""

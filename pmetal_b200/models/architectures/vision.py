@@ -11,6 +11,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .fast import Linear
+
 from .generic import Norm
 
 
@@ -32,8 +34,8 @@ class _PixAttention(nn.Module):
     def __init__(self, H, h, d):
         super().__init__()
         self.h, self.d = h, d
-        self.q_proj, self.k_proj, self.v_proj = (nn.Linear(H, h * d, bias=False) for _ in range(3))
-        self.o_proj = nn.Linear(h * d, H, bias=False)
+        self.q_proj, self.k_proj, self.v_proj = (Linear(H, h * d, bias=False) for _ in range(3))
+        self.o_proj = Linear(h * d, H, bias=False)
 
     def forward(self, x, cos, sin, mask):
         B, T, _ = x.shape
@@ -47,7 +49,7 @@ class _PixAttention(nn.Module):
 class _PixMlp(nn.Module):
     def __init__(self, H, I, act):
         super().__init__()
-        self.gate_proj, self.up_proj, self.down_proj = nn.Linear(H, I, bias=False), nn.Linear(H, I, bias=False), nn.Linear(I, H, bias=False)
+        self.gate_proj, self.up_proj, self.down_proj = Linear(H, I, bias=False), Linear(H, I, bias=False), Linear(I, H, bias=False)
         self.fn = {"gelu": F.gelu, "silu": F.silu}[act]
 
     def forward(self, x):
@@ -119,7 +121,7 @@ class _QvAttention(nn.Module):
     def __init__(self, D, h):
         super().__init__()
         self.h = h
-        self.qkv, self.proj = nn.Linear(D, 3 * D), nn.Linear(D, D)
+        self.qkv, self.proj = Linear(D, 3 * D), Linear(D, D)
 
     def forward(self, x, cos, sin, mask):
         T, D = x.shape
@@ -134,7 +136,7 @@ class _QvAttention(nn.Module):
 class _QvMlp(nn.Module):
     def __init__(self, D, I, act):
         super().__init__()
-        self.fc1, self.fc2 = nn.Linear(D, I), nn.Linear(I, D)
+        self.fc1, self.fc2 = Linear(D, I), Linear(I, D)
         self.fn = {"quick_gelu": lambda x: x * torch.sigmoid(1.702 * x), "gelu": F.gelu, "silu": F.silu}[act]
 
     def forward(self, x):
@@ -167,7 +169,7 @@ class _QvMerger(nn.Module):
         super().__init__()
         self.width = D * merge * merge
         self.ln_q = nn.LayerNorm(D, eps=1e-6)
-        self.mlp = nn.Sequential(nn.Linear(self.width, self.width), nn.GELU(), nn.Linear(self.width, out_dim))
+        self.mlp = nn.Sequential(Linear(self.width, self.width), nn.GELU(), Linear(self.width, out_dim))
 
     def forward(self, x):
         return self.mlp(self.ln_q(x).view(-1, self.width))
@@ -246,7 +248,7 @@ class VisionLanguageModel(nn.Module):
 class _LlavaProjector(nn.Module):
     def __init__(self, vin, vout, act="gelu", bias=True):
         super().__init__()
-        self.linear_1, self.linear_2 = nn.Linear(vin, vout, bias=bias), nn.Linear(vout, vout, bias=bias)
+        self.linear_1, self.linear_2 = Linear(vin, vout, bias=bias), Linear(vout, vout, bias=bias)
         self.fn = {"gelu": F.gelu, "silu": F.silu}[act]
 
     def forward(self, x):
