@@ -145,6 +145,9 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--dp", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-decode", action="store_true", help="skip the decode tok/s measurement appended to the report")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="after the warm-up, run one extra (untimed) step under the profiler and print per-kernel device "
+                         "times to stderr")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -230,6 +233,16 @@ def main() -> None:
         step_fn(batches[bi]); bi += 1
     barrier()
     native.check_status()
+    if args.profile_step:
+        import contextlib
+        from torch.profiler import ProfilerActivity, profile
+        with (profile(activities=[ProfilerActivity.CUDA]) if rank == 0 else contextlib.nullcontext()) as prof:
+            step_fn(batches[bi])
+            torch.cuda.synchronize()
+        if rank == 0:
+            print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40, max_name_column_width=64),
+                  file=sys.stderr, flush=True)
+        barrier()
 
     # ---- region A: device-timed steps, inputs already resident on the device
     dev_batches = [batches[bi + i].to(dev) for i in range(args.steps)]
