@@ -71,6 +71,26 @@ def make_cases(T: int = 16384):
     cases["gemm_lm_head_chunk"] = lambda: gemm_case(4096, 151936, 1024)
     cases["gemm_square_8192"] = lambda: gemm_case(8192, 8192, 8192)
 
+    def lora_side(which):
+        """The narrow products of the LoRA path at the q|k|v projection shape (K_in 1024, N 4096, r 16 x 3 segments)."""
+        segs, r, K, N = (2048, 1024, 1024), 16, 1024, 4096
+        x, dy = _r(T, K), _r(T, N)
+        a, b = _r(len(segs) * r, K, scale=K ** -0.5), _r(N, r, scale=0.1)
+        t = nat.lora_t(x, a, 2.0)
+        dt = nat.lora_dt(dy, b, segs, r, 2.0)
+        ga = torch.zeros(len(segs) * r, K, device="cuda")
+        gb = torch.zeros(N, r, device="cuda")
+        if which == "t":
+            return (lambda: nat.lora_t(x, a, 2.0)), 0.0, 2.0 * (T * K + T * 64)
+        if which == "dt":
+            return (lambda: nat.lora_dt(dy, b, segs, r, 2.0)), 0.0, 2.0 * (T * N + T * 64)
+        if which == "da":
+            return (lambda: nat.lora_da(dt, x, len(segs) * r, ga)), 0.0, 2.0 * (T * K + T * 64)
+        return (lambda: nat.lora_db(dy, t, segs, r, gb)), 0.0, 2.0 * (T * N + T * 64)
+
+    for w_ in ("t", "dt", "da", "db"):
+        cases["lora_" + w_] = (lambda w_=w_: lora_side(w_))
+
     def attn(which, one_doc=False):
         hq, hkv, d = 16, 8, 128
         g = torch.Generator().manual_seed(0)

@@ -293,10 +293,27 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
   const int stage_bytes = kBM * kBK * 2 + bn * kBK * 2;
   int stages = (227 * 1024 - 2048) / stage_bytes;
   if (stages > kMaxStages) stages = kMaxStages;
-  p.stages = stages;
   int cols = 32;
   while (cols < 2 * bn) cols *= 2;
   p.tmem_cols = cols;
+  // Narrow tiles stream one big operand and do little arithmetic: two CTAs per SM (half the ring each) keep two
+  // independent TMA pipelines busy per SM. PMETAL_GEMM_OCC=1 switches it off; PMETAL_GEMM_STAGES caps the ring depth.
+  static int env_occ = -1, env_stages = -1;
+  if (env_occ < 0) {
+    const char* e = getenv("PMETAL_GEMM_OCC");
+    env_occ = e ? atoi(e) : 2;
+    const char* s2 = getenv("PMETAL_GEMM_STAGES");
+    env_stages = s2 ? atoi(s2) : 0;
+  }
+  int occ = 1;
+  if (env_occ >= 2 && bn <= 64 && cols <= 256) {
+    occ = 2;
+    const int half = (113 * 1024 - 2048) / stage_bytes;
+    if (stages > half) stages = half;
+  }
+  if (env_stages > 0 && stages > env_stages) stages = env_stages;
+  if (stages < 2) return -19;
+  p.stages = stages;
 
   CUtensorMap ma, mb, ma2, mb2;
   int rc;
@@ -318,7 +335,7 @@ extern "C" int pm_gemm_bf16(const void* A, int a_mn, int lda, int a_rows, const 
   }
   const int m_tiles = (M + kBM - 1) / kBM, n_tiles = (N + bn - 1) / bn;
   int grid = m_tiles * n_tiles * splits;
-  int cap = max_ctas > 0 ? max_ctas : num_sms();
+  int cap = max_ctas > 0 ? max_ctas : num_sms() * occ;
   if (grid > cap) grid = cap;
   gemm_bf16_tcgen05_kernel<<<grid, kThreads, smem, stream>>>(ma, mb, ma2, mb2, p);
   return static_cast<int>(cudaGetLastError());
