@@ -195,6 +195,19 @@ __global__ void rope_table_kernel(const int* __restrict__ pos, float* __restrict
   sn[i] = s;
 }
 
+// Same table from a precomputed frequency vector (llama3 / yarn / NTK / longrope schedules are built once on the host);
+// `mscale` is the schedule's attention factor, applied to both cos and sin.
+__global__ void rope_table_freqs_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
+                                        float* __restrict__ cs, float* __restrict__ sn, int T, int half, float mscale) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * half) return;
+  const int t = i / half, j = i - t * half;
+  float s, c;
+  sincosf(static_cast<float>(pos[t]) * inv_freq[j], &s, &c);
+  cs[i] = c * mscale;
+  sn[i] = s * mscale;
+}
+
 // ------------------------------------------------------------------------------------ QK-norm + RoPE (D = 128)
 // One warp per (token, head). Lane l owns elements {4l..4l+3} of the vector: the first 16 lanes hold
 // the first half (j < 64), the last 16 the second half; rotation partners are exchanged by shuffle.
@@ -673,6 +686,12 @@ extern "C" int pm_rope_table(const int* pos, float* cs, float* sn, int T, int ha
                              cudaStream_t st) {
   const long long n = static_cast<long long>(T) * half;
   rope_table_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, st>>>(pos, cs, sn, T, half, theta, 1.f / rope_scale);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_rope_table_freqs(const int* pos, const float* inv_freq, float* cs, float* sn, int T, int half,
+                                   float mscale, cudaStream_t st) {
+  const long long n = static_cast<long long>(T) * half;
+  rope_table_freqs_kernel<<<static_cast<int>((n + 255) / 256), 256, 0, st>>>(pos, inv_freq, cs, sn, T, half, mscale);
   return PM_LAUNCH_CHECK();
 }
 extern "C" int pm_qknorm_rope_fwd(const void* qkv, int ld, const void* qw, const void* kw, const float* cs,

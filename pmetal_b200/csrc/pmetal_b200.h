@@ -100,6 +100,8 @@ int pm_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rs
     float* dw, int T, int H, cudaStream_t st);
 int pm_rope_table(const int* pos, float* cs, float* sn, int T, int half, float theta, float rope_scale,
     cudaStream_t st);
+int pm_rope_table_freqs(const int* pos, const float* inv_freq, float* cs, float* sn, int T, int half, float mscale,
+    cudaStream_t st);
 int pm_qknorm_rope_fwd(const void* qkv, int ld, const void* qw, const void* kw, const float* cs, const float* sn,
     void* q_out, void* k_out, int T, int hq, int hkv, float eps, cudaStream_t st);
 int pm_qknorm_rope_cache(const void* qkv, int ld, const void* qw, const void* kw, const float* cs, const float* sn,

@@ -32,6 +32,12 @@ def config_from_metadata(meta: Dict[str, object]) -> dict:
            "intermediate_size": g("feed_forward_length"), "max_position_embeddings": g("context_length"),
            "vocab_size": g("vocab_size"), "head_dim": g("attention.key_length", g("attention.head_dim")),
            "rope_theta": g("rope.freq_base", 10000.0), "rms_norm_eps": g("attention.layer_norm_rms_epsilon", 1e-6)}
+    kind = g("rope.scaling.type")
+    if kind and kind != "none":
+        rs = {"rope_type": kind, "factor": float(g("rope.scaling.factor", 1.0))}
+        if g("rope.scaling.original_context_length"):
+            rs["original_max_position_embeddings"] = int(g("rope.scaling.original_context_length"))
+        cfg["rope_scaling"] = rs
     if g("expert_count"):
         cfg["num_experts"] = g("expert_count")
         cfg["num_experts_per_tok"] = g("expert_used_count")

@@ -27,6 +27,7 @@ class ModelArgs:
     rms_norm_eps: float = 1e-6
     rope_theta: float = 1e6
     rope_scale: float = 1.0
+    rope_scaling: Optional[dict] = None  # llama3 / yarn / dynamic / longrope schedule (linear folds into rope_scale)
     max_position_embeddings: int = 40960
     tie_word_embeddings: bool = True
     qk_norm: bool = True
@@ -91,8 +92,14 @@ class ModelArgs:
         if "rope_theta" not in d:
             out["rope_theta"] = 10000.0
         rs = d.get("rope_scaling") or {}
-        if rs.get("type", rs.get("rope_type")) == "linear":
+        kind = rs.get("rope_type", rs.get("type"))
+        if kind == "linear":
             out["rope_scale"] = float(rs.get("factor", 1.0))
+            out["rope_scaling"] = None
+        elif kind in (None, "default"):
+            out["rope_scaling"] = None
+        else:
+            out["rope_scaling"] = dict(rs, rope_type=kind)
         if not d.get("use_sliding_window", True):
             out["sliding_window"] = 0
         if isinstance(out.get("eos_token_id"), list):
@@ -106,6 +113,8 @@ class ModelArgs:
 
     def to_hf_dict(self) -> dict:
         d = dataclasses.asdict(self)
+        if d.get("rope_scaling") is None and self.rope_scale != 1.0:
+            d["rope_scaling"] = {"rope_type": "linear", "factor": self.rope_scale}
         d["architectures"] = [{"qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
                                "qwen2": "Qwen2ForCausalLM", "llama": "LlamaForCausalLM",
                                "mistral": "MistralForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]

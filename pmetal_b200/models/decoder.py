@@ -244,6 +244,20 @@ class DecoderLM(nn.Module):
             torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
         self.head_t: Optional[torch.Tensor] = None
         self.gradient_checkpointing = 0
+        self._rope_schedule = None      # (inv_freq on the device, attention factor) for non-linear rope_scaling
+
+    def rope(self, positions: torch.Tensor):
+        """cos/sin tables of this batch: plain or linearly scaled RoPE straight from theta, every other
+        schedule (llama3, yarn, dynamic NTK, longrope) from its frequency vector built once per device."""
+        cfg = self.cfg
+        if not cfg.rope_scaling:
+            return ops.rope_table(positions, cfg.head_dim, cfg.rope_theta, cfg.rope_scale)
+        sched = self._rope_schedule
+        if sched is None or sched[0].device != positions.device:
+            from .rope import rope_inv_freq
+            inv, att = rope_inv_freq(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling, cfg.max_position_embeddings)
+            sched = self._rope_schedule = (inv.to(positions.device).contiguous(), float(att))
+        return ops.rope_table_scheduled(positions, sched[0], sched[1])
 
     # ------------------------------------------------------------------ init / freeze
     @torch.no_grad()
@@ -323,7 +337,7 @@ class DecoderLM(nn.Module):
             positions = torch.arange(T, device=input_ids.device, dtype=torch.int32) - ss
         lo, hi = layer_range if layer_range is not None else (0, len(self.layers))
         x = hidden_in if hidden_in is not None else F.embedding(input_ids, ops.live(self.embed_tokens))
-        rope = ops.rope_table(positions, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scale)
+        rope = self.rope(positions)
         policies = getattr(self, "layer_policies", None) if self.training else None      # utils/offload.py plan
         for i in range(lo, hi):
             layer = self.layers[i]
@@ -384,7 +398,7 @@ class DecoderLM(nn.Module):
         hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         x = F.embedding(input_ids, self.embed_tokens)
         native = ops.use_native(x) and d == 128
-        rope = ops.rope_table(meta.positions, d, cfg.rope_theta, cfg.rope_scale)
+        rope = self.rope(meta.positions)
         T = x.shape[0]
         skinny = native and T <= GEMV_MAX_ROWS
         layers = self.layers

@@ -193,6 +193,7 @@ class LayerSplitDraft(torch.nn.Module):
         self.norm = target.norm
         self.lm_head = target.lm_head
         self._target = [target]
+        self._rope_schedule = None
 
     def head_weight(self):
         return self._target[0].head_weight()
@@ -213,6 +214,7 @@ def _bind_layer_split():
     from .decoder import DecoderLM
     LayerSplitDraft.forward_paged = DecoderLM.forward_paged
     LayerSplitDraft._paged_attention_reference = DecoderLM._paged_attention_reference
+    LayerSplitDraft.rope = DecoderLM.rope
 
 
 _bind_layer_split()

@@ -122,6 +122,14 @@ def rope_table(positions: torch.Tensor, head_dim: int, theta: float, rope_scale:
     return ref.rope_cos_sin(positions, head_dim, theta, rope_scale)
 
 
+def rope_table_scheduled(positions: torch.Tensor, inv_freq: torch.Tensor, mscale: float = 1.0):
+    """cos/sin [T, half] for a precomputed frequency schedule (llama3, yarn, NTK, longrope) and its attention factor."""
+    if positions.is_cuda and not _FORCE_REF and _native().available():
+        return _native().rope_table_freqs(positions, inv_freq, mscale)
+    ang = positions.float()[:, None] * inv_freq.to(positions.device)[None, :]
+    return ang.cos() * mscale, ang.sin() * mscale
+
+
 class _AttnBlockFn(torch.autograd.Function):
     """fused projection [T,(hq+2hkv)*d] -> per-head RMSNorm(q,k) -> RoPE -> varlen causal attention -> [T,hq*d].
 

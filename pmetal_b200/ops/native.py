@@ -573,6 +573,17 @@ def rope_table(positions: torch.Tensor, head_dim: int, theta: float, rope_scale:
     return cs, sn
 
 
+def rope_table_freqs(positions: torch.Tensor, inv_freq: torch.Tensor, mscale: float = 1.0):
+    """cos/sin [T, half] from a host-built frequency vector [half] (fp32, on the device) times `mscale`."""
+    T, half = positions.shape[0], inv_freq.shape[0]
+    pos = positions if positions.dtype == torch.int32 else positions.to(torch.int32)
+    cs = torch.empty(T, half, dtype=torch.float32, device=positions.device)
+    sn = torch.empty_like(cs)
+    _chk(lib().pm_rope_table_freqs(_p(pos), _p(inv_freq), _p(cs), _p(sn), c_int(T), c_int(half), c_float(mscale),
+                                   _stream()), "pm_rope_table_freqs")
+    return cs, sn
+
+
 def qknorm_rope_fwd(qkv, qw, kw, cos, sin, hq: int, hkv: int, eps: float):
     T = qkv.shape[0]
     q = torch.empty(T, hq, 128, dtype=qkv.dtype, device=qkv.device)

@@ -243,6 +243,20 @@ def test_rmsnorm_few_rows(T, H):
     _close(rstd2, (x.float().pow(2).mean(-1) + 1e-6).rsqrt(), rtol=1e-3, atol=1e-3, what="rstd")
 
 
+def test_rope_table_from_frequency_schedule():
+    """llama3 / yarn tables from the host-built frequency vector equal the fp32 reference, attention factor included."""
+    nat = _nat()
+    from pmetal_b200.models.rope import rope_inv_freq
+    pos = torch.randint(0, 30000, (257,), device="cuda", dtype=torch.int32)
+    for sc in ({"rope_type": "llama3", "factor": 8.0, "original_max_position_embeddings": 8192},
+               {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 8192}):
+        inv, att = rope_inv_freq(128, 5e5, sc, 32768)
+        cs, sn = nat.rope_table_freqs(pos, inv.cuda(), att)
+        ang = pos.double()[:, None] * inv.double().cuda()[None, :]
+        _close(cs, (ang.cos() * att).float(), rtol=0, atol=2e-3, what="cos " + sc["rope_type"])
+        _close(sn, (ang.sin() * att).float(), rtol=0, atol=2e-3, what="sin " + sc["rope_type"])
+
+
 def test_qknorm_rope():
     nat = _nat()
     from pmetal_b200.ops import reference as ref
