@@ -1926,15 +1926,35 @@ def cmd_pack_experts(a) -> int:
     return 0
 
 
-# ------------------------------------------------------------------------------------------- dashboard / tui (headless)
+# ------------------------------------------------------------------------------------------- dashboard / tui
 def _dash_args(sp):
-    for name in ("dashboard", "tui"):
-        p = sp.add_parser(name, help="follow a job-event file (--log-events output) and print progress lines")
-        p.add_argument("events", help="JSON-lines event file")
-        p.add_argument("--once", action="store_true", help="print the summary of what is there and exit")
-        p.add_argument("--interval", type=float, default=1.0)
-        p.set_defaults(func=cmd_dashboard)
+    p = sp.add_parser("dashboard", help="follow a job-event file (--log-events output) and print progress lines")
+    p.add_argument("events", help="JSON-lines event file")
+    p.add_argument("--once", action="store_true", help="print the summary of what is there and exit")
+    p.add_argument("--interval", type=float, default=1.0)
+    p.set_defaults(func=cmd_dashboard)
+    p = sp.add_parser("tui", help="terminal application: forms for every job kind, job runner, live monitor; with an "
+                                  "event file it follows that file like `dashboard`")
+    p.add_argument("events", nargs="?", help="JSON-lines event file to follow instead of opening the application")
+    p.add_argument("--once", action="store_true")
+    p.add_argument("--interval", type=float, default=1.0)
+    p.add_argument("--keys", default=None,
+                   help="scripted keys separated by commas (names: tab, enter, up, down, esc ... or single characters); "
+                        "the application applies them, waits for the jobs it started and prints the last frame")
+    p.add_argument("--workdir", default=None, help="where job logs and event files go (default: a temporary directory)")
+    p.set_defaults(func=cmd_tui)
     return p
+
+
+def cmd_tui(a) -> int:
+    if a.events:
+        return cmd_dashboard(a)
+    from ..tui import JobRunner, TuiApp, run
+    app = TuiApp(runner=JobRunner(workdir=a.workdir))
+    keys = None
+    if a.keys is not None:
+        keys = [k if k != "comma" else "," for k in a.keys.split(",") if k != ""]
+    return run(app, keys=keys)
 
 
 def summarise_events(lines) -> dict:

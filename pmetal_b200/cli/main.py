@@ -4,7 +4,8 @@ Sub-commands and flag names follow the reference CLI (crates/pmetal/src/main.rs:
 crates/pmetal/src/cli/*.rs): train, infer, fuse, merge, quantize, distill, grpo, serve, cluster,
 bench, bench-corpus, eval, info, memory, dataset, tokenize, init, search/download (offline: local
 cache only). ``--log-events PATH`` writes the job-event JSONL stream for any command.
-Window/terminal UIs of the reference (``tui``, ``dashboard``, GUI) are replaced by the JSONL streams.
+``tui`` opens the terminal application (``pmetal_b200/tui``); ``dashboard`` follows a JSONL event stream headlessly;
+the reference's desktop GUI has no counterpart.
 """
 from __future__ import annotations
 

@@ -164,5 +164,5 @@ class EventSinkCallback(TrainingCallback):
 
     def on_step_end_with_metrics(self, m: StepMetrics) -> None:
         from .events import JobEvent
-        self.sink.emit(JobEvent.metric(self.job_id, "step", step=m.step, loss=m.loss, lr=m.lr, tok_sec=m.tok_sec,
-                                       grad_norm=m.grad_norm))
+        self.sink.emit(JobEvent.metric(self.job_id, "step", step=m.step, total_steps=m.total_steps, loss=m.loss, lr=m.lr,
+                                       tok_sec=m.tok_sec, tokens_per_s=m.tok_sec, grad_norm=m.grad_norm))

@@ -275,6 +275,9 @@ def run_training(job: TrainingJobConfig, phase_cb: Optional[Callable[[str], None
             job.use_cuda_graph = False           # host copies and recomputation do not replay from a captured step
         model.prepare_for_training()
         cbs = list(callbacks or []) + [LoggingCallback(tcfg.logging_steps)]
+        if not isinstance(sink, NullSink) and rank == 0:
+            from ..core.callbacks import EventSinkCallback
+            cbs.append(EventSinkCallback(sink, job.job_id))      # per-step metric events for the front ends
         if getattr(job, "tensorboard_dir", None) and rank == 0:
             from ..core.callbacks import TensorBoardCallback
             cbs.append(TensorBoardCallback(job.tensorboard_dir))
