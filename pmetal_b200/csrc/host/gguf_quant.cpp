@@ -869,6 +869,124 @@ inline uint16_t f32_to_bf16(float f) {
   return static_cast<uint16_t>((x + 0x7fffu + ((x >> 16) & 1)) >> 16);
 }
 
+
+// ---------------------------------------------------------------------------------------------- integer dot products
+// Dot product of a K-quant row with a Q8_K-quantised activation row without going through floats
+// (role of crates/pmetal-gguf/src/vec_dot.rs:53-880). One routine serves every type: a block is unpacked
+// into 256 integer levels, sixteen integer sub-block scales and sixteen integer sub-block minima, so that
+//   x_i = d * sc[i/16] * q_i - dmin * mn[i/16],   y_i = yd * yq_i
+//   dot = yd * ( d * sum_j sc_j * sum_{i in j} q_i yq_i  -  dmin * sum_j mn_j * bsum_j )
+// with all inner sums exact in int32 (|q| <= 128, |yq| <= 128, 16 terms, |sc| <= 255).
+struct Levels {
+  int8_t q[256];
+  int sc[16];
+  int mn[16];
+  float d, dmin;
+};
+
+bool unpack_levels(int type, const uint8_t* b, Levels* L) {
+  for (int j = 0; j < 16; ++j) L->mn[j] = 0;
+  L->dmin = 0.f;
+  switch (type) {
+    case T_Q2K: {
+      const uint8_t *scales = b, *qs = b + 16;
+      L->d = f16_to_f32(get16(b + 80));
+      L->dmin = f16_to_f32(get16(b + 82));
+      for (int j = 0; j < 16; ++j) { L->sc[j] = scales[j] & 15; L->mn[j] = scales[j] >> 4; }
+      for (int i = 0; i < 256; ++i) {
+        const int h = i >> 7, r = i & 127;
+        L->q[i] = static_cast<int8_t>((qs[32 * h + (r & 31)] >> (2 * (r >> 5))) & 3);
+      }
+      return true;
+    }
+    case T_Q3K: {
+      const uint8_t *hmask = b, *qs = b + 32, *scales = b + 96;
+      L->d = f16_to_f32(get16(b + 108));
+      for (int j = 0; j < 16; ++j) L->sc[j] = q3k_scale(scales, j);
+      for (int i = 0; i < 256; ++i) {
+        const int h = i >> 7, r = i & 127;
+        const int lo = (qs[32 * h + (r & 31)] >> (2 * (r >> 5))) & 3;
+        const int hi = (hmask[i & 31] >> (i >> 5)) & 1;
+        L->q[i] = static_cast<int8_t>(lo - (hi ? 0 : 4));
+      }
+      return true;
+    }
+    case T_Q4K:
+    case T_Q5K: {
+      L->d = f16_to_f32(get16(b));
+      L->dmin = f16_to_f32(get16(b + 2));
+      const uint8_t* qh = b + 16;
+      const uint8_t* qs = type == T_Q4K ? b + 16 : b + 48;
+      for (int j = 0; j < 8; ++j) {
+        int sv, mv;
+        unpack_scale_min(j, b + 4, &sv, &mv);
+        L->sc[2 * j] = L->sc[2 * j + 1] = sv;
+        L->mn[2 * j] = L->mn[2 * j + 1] = mv;
+      }
+      for (int g = 0; g < 4; ++g)
+        for (int i = 0; i < 32; ++i) {
+          int lo = qs[g * 32 + i] & 15, hi = qs[g * 32 + i] >> 4;
+          if (type == T_Q5K) {
+            lo += ((qh[i] >> (2 * g)) & 1) << 4;
+            hi += ((qh[i] >> (2 * g + 1)) & 1) << 4;
+          }
+          L->q[g * 64 + i] = static_cast<int8_t>(lo);
+          L->q[g * 64 + 32 + i] = static_cast<int8_t>(hi);
+        }
+      return true;
+    }
+    case T_Q6K: {
+      const uint8_t *ql = b, *qh = b + 128;
+      const int8_t* sc = reinterpret_cast<const int8_t*>(b + 192);
+      L->d = f16_to_f32(get16(b + 208));
+      for (int j = 0; j < 16; ++j) L->sc[j] = sc[j];
+      for (int h = 0; h < 2; ++h)
+        for (int i = 0; i < 32; ++i) {
+          const uint8_t hb = qh[32 * h + i];
+          int8_t* o = L->q + 128 * h + i;
+          o[0] = static_cast<int8_t>(((ql[64 * h + i] & 15) | (((hb >> 0) & 3) << 4)) - 32);
+          o[32] = static_cast<int8_t>(((ql[64 * h + i + 32] & 15) | (((hb >> 2) & 3) << 4)) - 32);
+          o[64] = static_cast<int8_t>(((ql[64 * h + i] >> 4) | (((hb >> 4) & 3) << 4)) - 32);
+          o[96] = static_cast<int8_t>(((ql[64 * h + i + 32] >> 4) | (((hb >> 6) & 3) << 4)) - 32);
+        }
+      return true;
+    }
+    case T_Q8K: {
+      std::memcpy(&L->d, b, 4);
+      for (int j = 0; j < 16; ++j) L->sc[j] = 1;
+      std::memcpy(L->q, b + 4, 256);
+      return true;
+    }
+    default:
+      return false;
+  }
+}
+
+// one 256-element block of `type` against one Q8_K block
+inline float block_dot_q8k(const Levels& L, const uint8_t* yb) {
+  float yd;
+  std::memcpy(&yd, yb, 4);
+  const int8_t* yq = reinterpret_cast<const int8_t*>(yb + 4);
+  int64_t acc = 0, macc = 0;
+  for (int j = 0; j < 16; ++j) {
+    int s = 0;
+    for (int i = 0; i < 16; ++i) s += static_cast<int>(L.q[16 * j + i]) * static_cast<int>(yq[16 * j + i]);
+    acc += static_cast<int64_t>(L.sc[j]) * s;
+    macc += static_cast<int64_t>(L.mn[j]) * static_cast<int16_t>(get16(yb + 260 + 2 * j));
+  }
+  return yd * (L.d * static_cast<float>(acc) - L.dmin * static_cast<float>(macc));
+}
+
+double row_dot_q8k(int type, int bytes, const uint8_t* x, const uint8_t* y, int64_t nb) {
+  Levels L;
+  double sum = 0.0;
+  for (int64_t i = 0; i < nb; ++i) {
+    unpack_levels(type, x + i * bytes, &L);
+    sum += block_dot_q8k(L, y + i * 292);
+  }
+  return sum;
+}
+
 }  // namespace
 
 extern "C" {
@@ -929,6 +1047,33 @@ int pm_gguf_dequantize(int type, const void* src, float* dst, int64_t n, int thr
       if (left >= f->elems) { dec(in + i * f->bytes, dst + i * f->elems); }
       else { dec(in + i * f->bytes, tmp); std::memcpy(dst + i * f->elems, tmp, static_cast<size_t>(left) * 4); }
     }
+  });
+  return 0;
+}
+
+// x: n elements of a K-quant type (Q2_K..Q6_K, Q8_K); y: the same n elements quantised as Q8_K. n must be a
+// multiple of 256. Returns 0 and the dot product in *out; -1 unknown type, -2 type without an integer path, -3 bad n.
+int pm_gguf_vec_dot_q8k(int type, const void* x, const void* y_q8k, int64_t n, float* out) {
+  const Fmt* f = find_fmt(type);
+  if (!f) return -1;
+  if (!(type >= T_Q2K && type <= T_Q8K)) return -2;
+  if (n <= 0 || n % 256) return -3;
+  *out = static_cast<float>(row_dot_q8k(type, f->bytes, static_cast<const uint8_t*>(x),
+                                        static_cast<const uint8_t*>(y_q8k), n / 256));
+  return 0;
+}
+
+// out[r] = dot(W[r, :], y) for a row-major quantised matrix W [rows, n] (rows split over threads).
+int pm_gguf_matvec_q8k(int type, const void* w, int64_t rows, int64_t n, const void* y_q8k, float* out, int threads) {
+  const Fmt* f = find_fmt(type);
+  if (!f) return -1;
+  if (!(type >= T_Q2K && type <= T_Q8K)) return -2;
+  if (n <= 0 || n % 256 || rows < 0) return -3;
+  const int64_t nb = n / 256, row_bytes = nb * f->bytes;
+  const uint8_t* W = static_cast<const uint8_t*>(w);
+  const uint8_t* y = static_cast<const uint8_t*>(y_q8k);
+  parallel_blocks(rows, threads, [&](int64_t a, int64_t b) {
+    for (int64_t r = a; r < b; ++r) out[r] = static_cast<float>(row_dot_q8k(type, f->bytes, W + r * row_bytes, y, nb));
   });
   return 0;
 }

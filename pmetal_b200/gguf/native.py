@@ -28,6 +28,10 @@ def lib():
             L.pm_gguf_dequantize.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int]
             L.pm_gguf_row_bytes.restype = ctypes.c_int64
             L.pm_gguf_row_bytes.argtypes = [ctypes.c_int, ctypes.c_int64]
+            L.pm_gguf_vec_dot_q8k.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                              ctypes.POINTER(ctypes.c_float)]
+            L.pm_gguf_matvec_q8k.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p,
+                                             ctypes.c_void_p, ctypes.c_int]
             _LIB = L
     return _LIB
 
@@ -75,4 +79,45 @@ def dequantize(buf, t: GgmlType, n_elements: int, threads: int = 0) -> np.ndarra
     return out
 
 
-__all__ = ["build", "lib", "quantize", "dequantize", "can_quantize", "can_dequantize", "BLOCK_GEOMETRY"]
+VEC_DOT_TYPES = (GgmlType.Q2K, GgmlType.Q3K, GgmlType.Q4K, GgmlType.Q5K, GgmlType.Q6K, GgmlType.Q8K)
+
+
+def vec_dot_q8k(x_blocks: np.ndarray, t: GgmlType, y_q8k: np.ndarray, n: int) -> float:
+    """Integer dot product of ``n`` elements stored as K-quant blocks of type ``t`` with the same ``n`` elements of an
+    activation row stored as Q8_K blocks (crates/pmetal-gguf/src/vec_dot.rs)."""
+    t = GgmlType(t)
+    if t not in VEC_DOT_TYPES:
+        raise NotImplementedError(f"no integer dot product for {t.name}")
+    if n <= 0 or n % 256:
+        raise ValueError("n must be a positive multiple of 256")
+    x = np.ascontiguousarray(x_blocks).reshape(-1).view(np.uint8)
+    y = np.ascontiguousarray(y_q8k).reshape(-1).view(np.uint8)
+    if x.size < tensor_nbytes(t, n) or y.size < tensor_nbytes(GgmlType.Q8K, n):
+        raise ValueError("block buffers are shorter than n elements")
+    out = ctypes.c_float(0.0)
+    rc = lib().pm_gguf_vec_dot_q8k(int(t), x.ctypes.data, y.ctypes.data, n, ctypes.byref(out))
+    if rc != 0:
+        raise ValueError(f"pm_gguf_vec_dot_q8k failed with {rc}")
+    return float(out.value)
+
+
+def matvec_q8k(w_blocks: np.ndarray, t: GgmlType, rows: int, n: int, y: np.ndarray, threads: int = 0) -> np.ndarray:
+    """``W @ y`` for a quantised row-major matrix ``W`` [rows, n] and a float32 vector ``y`` [n]: ``y`` is quantised to
+    Q8_K once and every row is an integer dot product (the CPU inference path for quantised weights)."""
+    t = GgmlType(t)
+    if t not in VEC_DOT_TYPES:
+        raise NotImplementedError(f"no integer dot product for {t.name}")
+    if n <= 0 or n % 256:
+        raise ValueError("n must be a positive multiple of 256")
+    w = np.ascontiguousarray(w_blocks).reshape(-1).view(np.uint8)
+    if w.size < rows * tensor_nbytes(t, n):
+        raise ValueError("weight buffer is shorter than rows x n elements")
+    yq = quantize(np.asarray(y, dtype=np.float32).reshape(-1)[:n], GgmlType.Q8K)
+    out = np.empty(rows, dtype=np.float32)
+    rc = lib().pm_gguf_matvec_q8k(int(t), w.ctypes.data, rows, n, yq.ctypes.data, out.ctypes.data, threads)
+    if rc != 0:
+        raise ValueError(f"pm_gguf_matvec_q8k failed with {rc}")
+    return out
+
+
+__all__ = ["vec_dot_q8k", "matvec_q8k", "VEC_DOT_TYPES", "build", "lib", "quantize", "dequantize", "can_quantize", "can_dequantize", "BLOCK_GEOMETRY"]

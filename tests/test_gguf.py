@@ -270,3 +270,39 @@ def test_quantize_model_and_load_back(tmp_path):
     assert abs(float(a) - float(b)) < 0.05
     info2 = quantize_model(src, str(tmp_path / "k.gguf"), "q4_k_m")
     assert info2["types"].get("Q6K", 0) >= 1 and info2["compression"] > 3
+
+
+@pytest.mark.parametrize("t", ["Q2K", "Q3K", "Q4K", "Q5K", "Q6K", "Q8K"])
+def test_integer_vec_dot_equals_dequantised_dot(t):
+    """The integer dot product with a Q8_K activation row equals the float dot product of the two dequantised rows."""
+    from pmetal_b200.gguf import native
+    from pmetal_b200.gguf.types import GgmlType
+    ty = GgmlType[t]
+    rng = np.random.default_rng(3)
+    n = 1024
+    x = rng.standard_normal(n).astype(np.float32)
+    y = rng.standard_normal(n).astype(np.float32) * 2.0
+    xb, yb = native.quantize(x, ty), native.quantize(y, GgmlType.Q8K)
+    got = native.vec_dot_q8k(xb, ty, yb, n)
+    want = float(np.dot(native.dequantize(xb, ty, n).astype(np.float64), native.dequantize(yb, GgmlType.Q8K, n).astype(np.float64)))
+    assert abs(got - want) <= 1e-4 * max(1.0, abs(want)) + 1e-3
+    with pytest.raises(ValueError):
+        native.vec_dot_q8k(xb, ty, yb, 100)
+    with pytest.raises(NotImplementedError):
+        native.vec_dot_q8k(xb, GgmlType.Q4_0, yb, n)
+
+
+def test_quantised_matvec_close_to_float():
+    from pmetal_b200.gguf import native
+    from pmetal_b200.gguf.types import GgmlType
+    rng = np.random.default_rng(4)
+    rows, n = 37, 512
+    w = rng.standard_normal((rows, n)).astype(np.float32)
+    y = rng.standard_normal(n).astype(np.float32)
+    wb = native.quantize(w, GgmlType.Q6K)
+    out = native.matvec_q8k(wb, GgmlType.Q6K, rows, n, y, threads=3)
+    ref = w @ y
+    assert np.abs(out - ref).max() / np.abs(ref).max() < 0.03
+    wd = native.dequantize(wb, GgmlType.Q6K, rows * n).reshape(rows, n)
+    yd = native.dequantize(native.quantize(y, GgmlType.Q8K), GgmlType.Q8K, n)
+    np.testing.assert_allclose(out, wd @ yd, rtol=1e-4, atol=1e-3)
