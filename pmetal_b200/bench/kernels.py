@@ -144,7 +144,25 @@ def make_cases(T: int = 16384):
         gn = torch.ones(1, device="cuda")
         return (lambda: nat.adamw_flat(p, g, m, v, sh, lm, wd, gn, 1e-4, .9, .999, 1e-8, 3, 1.0, 1.0)), 0.0, n * (7 * 4 + 2)
 
+    def rms_bwd():
+        dy, h, w, dh = _r(T, 1024), _r(T, 1024), _r(1024), _r(T, 1024)
+        rstd = torch.rand(T, device="cuda") + 0.5
+        return (lambda: nat.rmsnorm_bwd(dy, h, w, rstd, dh, False)), 0.0, 2.0 * T * 1024 * 4
+
+    def qk(which):
+        hq, hkv = 16, 8
+        qkv, qw, kw = _r(T, (hq + 2 * hkv) * 128), _r(128), _r(128)
+        cs, sn = nat.rope_table(torch.arange(T, device="cuda", dtype=torch.int32), 128, 1e6, 1.0)
+        if which == "fwd":
+            return (lambda: nat.qknorm_rope_fwd(qkv, qw, kw, cs, sn, hq, hkv, 1e-6)), 0.0, 2.0 * T * 128 * (hq + hkv) * 2
+        dq, dk, dqkv = _r(T, hq, 128), _r(T, hkv, 128), torch.zeros_like(qkv)
+        return (lambda: nat.qknorm_rope_bwd(dq, dk, qkv, qw, kw, cs, sn, hq, hkv, 1e-6, dqkv)), 0.0, \
+            2.0 * T * 128 * (hq + hkv) * 3
+
     cases["rmsnorm_add_fwd"] = rms
+    cases["rmsnorm_bwd"] = rms_bwd
+    cases["qknorm_rope_fwd"] = lambda: qk("fwd")
+    cases["qknorm_rope_bwd"] = lambda: qk("bwd")
     cases["swiglu_fwd"] = swi
     cases["ce_fwd_bwd"] = ce
     cases["adamw_flat_10M"] = adam

@@ -182,6 +182,55 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const _
   }
 }
 
+// Same, for H = NC * 256 with the row held in registers: every lane issues its 2 NC (3 NC with dh_add) 16-byte loads
+// before the first use, and nothing is read twice.
+template <int NC>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                              const __nv_bfloat16* __restrict__ h,
+                                                              const __nv_bfloat16* __restrict__ w,
+                                                              const float* __restrict__ rstd,
+                                                              const __nv_bfloat16* __restrict__ dh_add,
+                                                              __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
+                                                              int T) {
+  constexpr int H = NC * 256;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= T) return;
+  const size_t off = static_cast<size_t>(row) * H;
+  float a[NC][8], b[NC][8], e[NC][8];
+#pragma unroll
+  for (int u = 0; u < NC; ++u) {
+    load8(dy + off + u * 256 + lane * 8, a[u]);
+    load8(h + off + u * 256 + lane * 8, b[u]);
+  }
+  if (dh_add) {
+#pragma unroll
+    for (int u = 0; u < NC; ++u) load8(dh_add + off + u * 256 + lane * 8, e[u]);
+  }
+  const float rs = rstd[row];
+  float dot = 0.f;
+#pragma unroll
+  for (int u = 0; u < NC; ++u) {
+    float g[8];
+    load8(w + u * 256 + lane * 8, g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      b[u][i] *= rs;                       // xhat
+      if (dw) atomicAdd(dw + u * 256 + lane * 8 + i, a[u][i] * b[u][i]);
+      a[u][i] *= g[i];                     // dy * w
+      dot += a[u][i] * b[u][i];
+    }
+  }
+  dot = warp_sum(dot) / H;
+#pragma unroll
+  for (int u = 0; u < NC; ++u) {
+    float o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = rs * (a[u][i] - b[u][i] * dot) + (dh_add ? e[u][i] : 0.f);
+    store8(dx + off + u * 256 + lane * 8, o);
+  }
+}
+
 // ------------------------------------------------------------------------------------ RoPE table
 __global__ void rope_table_kernel(const int* __restrict__ pos, float* __restrict__ cs, float* __restrict__ sn, int T,
                                   int half, float theta, float inv_scale) {
@@ -257,6 +306,175 @@ __global__ void qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, in
   *reinterpret_cast<__nv_bfloat162*>(&ov.x) = __floats2bfloat162_rn(o[0], o[1]);
   *reinterpret_cast<__nv_bfloat162*>(&ov.y) = __floats2bfloat162_rn(o[2], o[3]);
   *reinterpret_cast<uint2*>(dst) = ov;
+}
+
+// Wide variants for whole batches: sixteen lanes per (token, head) and two consecutive heads per half-warp. Lane l owns
+// the four rotation pairs j = 4l .. 4l+3, i.e. elements {j} of the first half and {64 + j} of the second (two 8-byte
+// loads), so the rotation needs no exchange between lanes; the only shuffles are the four steps of the sum of squares.
+// Both heads of a half-warp usually belong to one token and share its cos / sin registers.
+__device__ __forceinline__ float half16_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ void unpack4(const uint2& r, float (&f)[4]) {
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ uint2 pack4(const float (&f)[4]) {
+  uint2 r;
+  *reinterpret_cast<__nv_bfloat162*>(&r.x) = __floats2bfloat162_rn(f[0], f[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&r.y) = __floats2bfloat162_rn(f[2], f[3]);
+  return r;
+}
+__device__ __forceinline__ void load4f(const float* __restrict__ p, float (&c)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w;
+}
+
+constexpr int kQkU = 2;   // heads per half-warp
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }   // null counts as aligned
+
+__global__ void __launch_bounds__(256) qknorm_rope_fwd_wide_kernel(
+    const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfloat16* __restrict__ qw,
+    const __nv_bfloat16* __restrict__ kw, const float* __restrict__ cs, const float* __restrict__ sn,
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out, int T, int hq, int hkv, float eps) {
+  const long long warp_g = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, l16 = lane & 15, sub = lane >> 4;
+  const int heads = hq + hkv;
+  const long long total = static_cast<long long>(T) * heads;
+  uint2 lo[kQkU], hi[kQkU];
+  int tt[kQkU], hh[kQkU];
+  bool ok[kQkU];
+#pragma unroll
+  for (int u = 0; u < kQkU; ++u) {
+    const long long g = (warp_g * 2 + sub) * kQkU + u;
+    ok[u] = g < total;
+    const long long gc = ok[u] ? g : 0;
+    tt[u] = static_cast<int>(gc / heads);
+    hh[u] = static_cast<int>(gc - static_cast<long long>(tt[u]) * heads);
+    const __nv_bfloat16* src = qkv + static_cast<size_t>(tt[u]) * ld + hh[u] * 128 + l16 * 4;
+    lo[u] = ok[u] ? *reinterpret_cast<const uint2*>(src) : make_uint2(0, 0);
+    hi[u] = ok[u] ? *reinterpret_cast<const uint2*>(src + 64) : make_uint2(0, 0);
+  }
+  float c[4], s4[4];
+#pragma unroll
+  for (int u = 0; u < kQkU; ++u) {
+    if (u == 0 || tt[u] != tt[u - 1]) {
+      load4f(cs + static_cast<size_t>(tt[u]) * 64 + l16 * 4, c);
+      load4f(sn + static_cast<size_t>(tt[u]) * 64 + l16 * 4, s4);
+    }
+    const bool is_q = hh[u] < hq;
+    const __nv_bfloat16* wv = is_q ? qw : kw;
+    float x1[4], x2[4];
+    unpack4(lo[u], x1);
+    unpack4(hi[u], x2);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ss += x1[i] * x1[i] + x2[i] * x2[i];
+    ss = half16_sum(ss);           // every lane takes part; heads without a norm weight keep x
+    if (wv) {
+      const float rs = rsqrtf(ss / 128.f + eps);
+      float w1[4], w2[4];
+      unpack4(*reinterpret_cast<const uint2*>(wv + l16 * 4), w1);
+      unpack4(*reinterpret_cast<const uint2*>(wv + 64 + l16 * 4), w2);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        x1[i] *= rs * w1[i];
+        x2[i] *= rs * w2[i];
+      }
+    }
+    float o1[4], o2[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o1[i] = x1[i] * c[i] - x2[i] * s4[i];
+      o2[i] = x2[i] * c[i] + x1[i] * s4[i];
+    }
+    if (ok[u]) {
+      __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(tt[u]) * hq + hh[u]) * 128 + l16 * 4
+                                : k_out + (static_cast<size_t>(tt[u]) * hkv + (hh[u] - hq)) * 128 + l16 * 4;
+      *reinterpret_cast<uint2*>(dst) = pack4(o1);
+      *reinterpret_cast<uint2*>(dst + 64) = pack4(o2);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) qknorm_rope_bwd_wide_kernel(
+    const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk, const __nv_bfloat16* __restrict__ qkv,
+    int ld, const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw, const float* __restrict__ cs,
+    const float* __restrict__ sn, __nv_bfloat16* __restrict__ dqkv, int T, int hq, int hkv, float eps) {
+  const long long warp_g = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31, l16 = lane & 15, sub = lane >> 4;
+  const int heads = hq + hkv;
+  const long long total = static_cast<long long>(T) * heads;
+  const bool norm = qw != nullptr || kw != nullptr;
+  uint2 glo[kQkU], ghi[kQkU], xlo[kQkU], xhi[kQkU];
+  int tt[kQkU], hh[kQkU];
+  bool ok[kQkU];
+#pragma unroll
+  for (int u = 0; u < kQkU; ++u) {
+    const long long g = (warp_g * 2 + sub) * kQkU + u;
+    ok[u] = g < total;
+    const long long gc = ok[u] ? g : 0;
+    tt[u] = static_cast<int>(gc / heads);
+    hh[u] = static_cast<int>(gc - static_cast<long long>(tt[u]) * heads);
+    const bool is_q = hh[u] < hq;
+    const __nv_bfloat16* gsrc = is_q ? dq + (static_cast<size_t>(tt[u]) * hq + hh[u]) * 128 + l16 * 4
+                                     : dk + (static_cast<size_t>(tt[u]) * hkv + (hh[u] - hq)) * 128 + l16 * 4;
+    const __nv_bfloat16* xsrc = qkv + static_cast<size_t>(tt[u]) * ld + hh[u] * 128 + l16 * 4;
+    glo[u] = ok[u] ? *reinterpret_cast<const uint2*>(gsrc) : make_uint2(0, 0);
+    ghi[u] = ok[u] ? *reinterpret_cast<const uint2*>(gsrc + 64) : make_uint2(0, 0);
+    xlo[u] = (ok[u] && norm) ? *reinterpret_cast<const uint2*>(xsrc) : make_uint2(0, 0);
+    xhi[u] = (ok[u] && norm) ? *reinterpret_cast<const uint2*>(xsrc + 64) : make_uint2(0, 0);
+  }
+  float c[4], s4[4];
+#pragma unroll
+  for (int u = 0; u < kQkU; ++u) {
+    if (u == 0 || tt[u] != tt[u - 1]) {
+      load4f(cs + static_cast<size_t>(tt[u]) * 64 + l16 * 4, c);
+      load4f(sn + static_cast<size_t>(tt[u]) * 64 + l16 * 4, s4);
+    }
+    const bool is_q = hh[u] < hq;
+    const __nv_bfloat16* wv = is_q ? qw : kw;
+    float g1[4], g2[4], d1[4], d2[4];
+    unpack4(glo[u], g1);
+    unpack4(ghi[u], g2);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {      // transpose of the rotation
+      d1[i] = g1[i] * c[i] + g2[i] * s4[i];
+      d2[i] = g2[i] * c[i] - g1[i] * s4[i];
+    }
+    float x1[4], x2[4], w1[4] = {0.f, 0.f, 0.f, 0.f}, w2[4] = {0.f, 0.f, 0.f, 0.f};
+    unpack4(xlo[u], x1);
+    unpack4(xhi[u], x2);
+    if (wv) {
+      unpack4(*reinterpret_cast<const uint2*>(wv + l16 * 4), w1);
+      unpack4(*reinterpret_cast<const uint2*>(wv + 64 + l16 * 4), w2);
+    }
+    // both sums are reduced by every lane (the two half-warps may hold heads of different kinds)
+    float ss = 0.f, dwx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      ss += x1[i] * x1[i] + x2[i] * x2[i];
+      dwx += d1[i] * w1[i] * x1[i] + d2[i] * w2[i] * x2[i];
+    }
+    ss = half16_sum(ss);
+    dwx = half16_sum(dwx);
+    const float rs = rsqrtf(ss / 128.f + eps);
+    const float dot = dwx * rs / 128.f;
+    float o1[4], o2[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o1[i] = wv ? rs * (d1[i] * w1[i] - x1[i] * rs * dot) : d1[i];
+      o2[i] = wv ? rs * (d2[i] * w2[i] - x2[i] * rs * dot) : d2[i];
+    }
+    if (ok[u]) {
+      __nv_bfloat16* dst = dqkv + static_cast<size_t>(tt[u]) * ld + hh[u] * 128 + l16 * 4;
+      *reinterpret_cast<uint2*>(dst) = pack4(o1);
+      *reinterpret_cast<uint2*>(dst + 64) = pack4(o2);
+    }
+  }
 }
 
 // Decode variant: q heads go to q_out; k heads are normalised, rotated and written straight into the paged key cache
@@ -676,6 +894,23 @@ extern "C" int pm_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
 extern "C" int pm_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dh_add,
                               void* dx, float* dw, int T, int H, cudaStream_t st) {
   if (H % 8) return -1;
+  if (H % 256 == 0 && H <= 2048) {
+    const dim3 grid((T + 7) / 8);
+    const __nv_bfloat16 *a = static_cast<const __nv_bfloat16*>(dy), *b = static_cast<const __nv_bfloat16*>(h),
+                        *g = static_cast<const __nv_bfloat16*>(w), *e = static_cast<const __nv_bfloat16*>(dh_add);
+    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(dx);
+    switch (H / 256) {
+      case 1: rmsnorm_bwd_reg_kernel<1><<<grid, 256, 0, st>>>(a, b, g, rstd, e, o, dw, T); break;
+      case 2: rmsnorm_bwd_reg_kernel<2><<<grid, 256, 0, st>>>(a, b, g, rstd, e, o, dw, T); break;
+      case 3: rmsnorm_bwd_reg_kernel<3><<<grid, 256, 0, st>>>(a, b, g, rstd, e, o, dw, T); break;
+      case 4: rmsnorm_bwd_reg_kernel<4><<<grid, 256, 0, st>>>(a, b, g, rstd, e, o, dw, T); break;
+      case 5: rmsnorm_bwd_reg_kernel<5><<<grid, 256, 0, st>>>(a, b, g, rstd, e, o, dw, T); break;
+      case 6: rmsnorm_bwd_reg_kernel<6><<<grid, 256, 0, st>>>(a, b, g, rstd, e, o, dw, T); break;
+      case 7: rmsnorm_bwd_reg_kernel<7><<<grid, 256, 0, st>>>(a, b, g, rstd, e, o, dw, T); break;
+      default: rmsnorm_bwd_reg_kernel<8><<<grid, 256, 0, st>>>(a, b, g, rstd, e, o, dw, T); break;
+    }
+    return PM_LAUNCH_CHECK();
+  }
   rmsnorm_bwd_kernel<<<(T + 7) / 8, 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(h),
       static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dh_add),
@@ -698,6 +933,15 @@ extern "C" int pm_qknorm_rope_fwd(const void* qkv, int ld, const void* qw, const
                                   const float* sn, void* q_out, void* k_out, int T, int hq, int hkv, float eps,
                                   cudaStream_t st) {
   const long long warps = static_cast<long long>(T) * (hq + hkv);
+  if (warps >= 4096 && ld % 8 == 0 && aligned16(qkv) && aligned16(q_out) && aligned16(k_out) && aligned16(qw) &&
+      aligned16(kw) && aligned16(cs) && aligned16(sn)) {
+    const long long wide = (warps + 2 * kQkU - 1) / (2 * kQkU);
+    qknorm_rope_fwd_wide_kernel<<<static_cast<int>((wide + 7) / 8), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(qkv), ld, static_cast<const __nv_bfloat16*>(qw),
+        static_cast<const __nv_bfloat16*>(kw), cs, sn, static_cast<__nv_bfloat16*>(q_out),
+        static_cast<__nv_bfloat16*>(k_out), T, hq, hkv, eps);
+    return PM_LAUNCH_CHECK();
+  }
   qknorm_rope_fwd_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(qkv), ld, static_cast<const __nv_bfloat16*>(qw),
       static_cast<const __nv_bfloat16*>(kw), cs, sn, static_cast<__nv_bfloat16*>(q_out),
@@ -718,6 +962,15 @@ extern "C" int pm_qknorm_rope_bwd(const void* dq, const void* dk, const void* qk
                                   const void* kw, const float* cs, const float* sn, void* dqkv, int T, int hq, int hkv,
                                   float eps, cudaStream_t st) {
   const long long warps = static_cast<long long>(T) * (hq + hkv);
+  if (warps >= 4096 && ld % 8 == 0 && aligned16(qkv) && aligned16(dq) && aligned16(dk) && aligned16(dqkv) &&
+      aligned16(qw) && aligned16(kw) && aligned16(cs) && aligned16(sn)) {
+    const long long wide = (warps + 2 * kQkU - 1) / (2 * kQkU);
+    qknorm_rope_bwd_wide_kernel<<<static_cast<int>((wide + 7) / 8), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(dq), static_cast<const __nv_bfloat16*>(dk),
+        static_cast<const __nv_bfloat16*>(qkv), ld, static_cast<const __nv_bfloat16*>(qw),
+        static_cast<const __nv_bfloat16*>(kw), cs, sn, static_cast<__nv_bfloat16*>(dqkv), T, hq, hkv, eps);
+    return PM_LAUNCH_CHECK();
+  }
   qknorm_rope_bwd_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(dq), static_cast<const __nv_bfloat16*>(dk),
       static_cast<const __nv_bfloat16*>(qkv), ld, static_cast<const __nv_bfloat16*>(qw),

@@ -208,11 +208,12 @@ def test_cta_pair_gemm_with_lora_segments_at_the_training_shape():
     nat.check_status()
 
 
-def test_rmsnorm():
+@pytest.mark.parametrize("T,H", [(777, 1024), (130, 2048), (99, 768), (61, 2560)])
+def test_rmsnorm(T, H):
+    """H = 768 ... 2048 take the register-resident backward, 2560 the looping one."""
     nat = _nat()
     from pmetal_b200.ops import reference as ref
     torch.manual_seed(4)
-    T, H = 777, 1024
     x, res, w = _rand(T, H), _rand(T, H), (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
     h, y, rstd = nat.rmsnorm_fwd(x, w, 1e-6, res)
     hr = (x.float() + res.float()).bfloat16()
@@ -257,11 +258,14 @@ def test_rope_table_from_frequency_schedule():
         _close(sn, (ang.sin() * att).float(), rtol=0, atol=2e-3, what="sin " + sc["rope_type"])
 
 
-def test_qknorm_rope():
+@pytest.mark.parametrize("T,hq,hkv", [(300, 4, 2), (1101, 4, 2), (2050, 3, 1)])
+def test_qknorm_rope(T, hq, hkv):
+    """300 tokens run one warp per head; the larger cases run the 16-lanes-per-head kernels, with a ragged last warp
+    and with q and k heads sharing a warp."""
     nat = _nat()
     from pmetal_b200.ops import reference as ref
     torch.manual_seed(5)
-    T, hq, hkv, d = 300, 4, 2, 128
+    d = 128
     qkv = _rand(T, (hq + 2 * hkv) * d)
     qw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
     kw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
@@ -281,6 +285,26 @@ def test_qknorm_rope():
     nat.qknorm_rope_bwd(dq, dk, qkv, qw, kw, cs, sn, hq, hkv, 1e-6, dqkv)
     (qr * dq.float()).sum().add((kr * dk.float()).sum()).backward()
     _close(dqkv[:, :(hq + hkv) * d], x.grad[:, :(hq + hkv) * d], what="qknorm_rope bwd")
+
+
+@pytest.mark.parametrize("T", [200, 1500])
+def test_rope_without_qk_norm(T):
+    """Architectures without QK-norm pass no weights: the kernels only rotate (and un-rotate in backward)."""
+    nat = _nat()
+    from pmetal_b200.ops import reference as ref
+    torch.manual_seed(15)
+    hq, hkv, d = 4, 2, 128
+    qkv = _rand(T, (hq + 2 * hkv) * d)
+    pos = torch.arange(T, device="cuda", dtype=torch.int32)
+    cs, sn = nat.rope_table(pos, d, 1e4, 1.0)
+    q, k = nat.qknorm_rope_fwd(qkv, None, None, cs, sn, hq, hkv, 1e-6)
+    _close(q, ref.apply_rope(qkv[:, :hq * d].float().view(T, hq, d), cs, sn), what="q rope only")
+    _close(k, ref.apply_rope(qkv[:, hq * d:(hq + hkv) * d].float().view(T, hkv, d), cs, sn), what="k rope only")
+    dq, dk = _rand(T, hq, d), _rand(T, hkv, d)
+    dqkv = torch.zeros_like(qkv)
+    nat.qknorm_rope_bwd(dq, dk, qkv, None, None, cs, sn, hq, hkv, 1e-6, dqkv)
+    _close(dqkv[:, :hq * d].view(T, hq, d), ref.apply_rope(dq.float(), cs, -sn), what="dq un-rotated")
+    _close(dqkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d), ref.apply_rope(dk.float(), cs, -sn), what="dk un-rotated")
 
 
 def test_swiglu():
