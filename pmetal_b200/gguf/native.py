@@ -42,8 +42,12 @@ def can_quantize(t: GgmlType) -> bool:
                  GgmlType.Q8K, GgmlType.MXFP4, GgmlType.NVFP4, GgmlType.TQ1_0, GgmlType.TQ2_0, GgmlType.Q1_0)
 
 
+GRID_IQ_TYPES = (GgmlType.IQ2_XXS, GgmlType.IQ2_XS, GgmlType.IQ2_S, GgmlType.IQ3_XXS, GgmlType.IQ3_S, GgmlType.IQ1_S,
+                 GgmlType.IQ1_M)
+
+
 def can_dequantize(t: GgmlType) -> bool:
-    return can_quantize(t) or t in (GgmlType.IQ4_NL, GgmlType.IQ4_XS)
+    return can_quantize(t) or t in (GgmlType.IQ4_NL, GgmlType.IQ4_XS) or t in GRID_IQ_TYPES
 
 
 def quantize(x: np.ndarray, t: GgmlType, threads: int = 0) -> np.ndarray:
@@ -66,6 +70,9 @@ def dequantize(buf, t: GgmlType, n_elements: int, threads: int = 0) -> np.ndarra
     if not can_dequantize(t):
         raise NotImplementedError(f"dequantisation of {t.name} is not implemented")
     raw = np.frombuffer(buf, dtype=np.uint8) if not isinstance(buf, np.ndarray) else buf.reshape(-1).view(np.uint8)
+    if t in GRID_IQ_TYPES:                      # grid-coded i-quants: vectorised numpy decoders (gguf/iq_quants.py)
+        from . import iq_quants
+        return iq_quants.dequantize(raw, t, n_elements)
     need = tensor_nbytes(t, n_elements)
     if raw.size < need:
         raise ValueError(f"{t.name}: need {need} bytes for {n_elements} elements, got {raw.size}")

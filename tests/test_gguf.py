@@ -98,7 +98,63 @@ def test_iq4_and_unknown_types():
     with pytest.raises(NotImplementedError):
         native.quantize(_data(256), T.IQ4_XS)
     with pytest.raises(NotImplementedError):
-        native.dequantize(np.zeros(66, np.uint8), T.IQ2_XXS, 256)
+        native.quantize(_data(256), T.IQ2_XXS)
+
+
+IQ_GRID_TYPES = ["IQ2_XXS", "IQ2_XS", "IQ2_S", "IQ3_XXS", "IQ3_S", "IQ1_S", "IQ1_M"]
+
+
+def _random_iq_blocks(name, nb, seed):
+    from pmetal_b200.gguf.types import BLOCK_GEOMETRY
+    nbytes = BLOCK_GEOMETRY[T[name]][1]
+    blocks = np.random.default_rng(seed).integers(0, 256, size=(nb, nbytes), dtype=np.uint8)
+    if name == "IQ1_M":                          # the f16 scale is spread over the top nibbles of four words
+        sc = blocks[:, 48:56].view("<u2")
+        sc[:, 3] = (sc[:, 3] & 0x0FFF) | 0x2000
+    else:
+        blocks[:, 0:2] = np.array([0.01 * (i + 1) for i in range(nb)], dtype="<f2").view(np.uint8).reshape(nb, 2)
+    return blocks
+
+
+@pytest.mark.parametrize("name", IQ_GRID_TYPES)
+def test_grid_iquant_decoders_match_gguf_py(name):
+    """Random block bytes decode to exactly what the gguf Python package gives."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    blocks = _random_iq_blocks(name, 9, seed=len(name))
+    want = quants.dequantize(blocks, getattr(gguf.GGMLQuantizationType, name)).reshape(-1)
+    got = native.dequantize(blocks.reshape(-1), T[name], 9 * 256)
+    np.testing.assert_array_equal(got, want.astype(np.float32))
+    assert native.can_dequantize(T[name]) and not native.can_quantize(T[name])
+    with pytest.raises(ValueError):
+        native.dequantize(blocks.reshape(-1)[:-1], T[name], 9 * 256)
+
+
+def test_grid_iquant_structure_without_the_oracle():
+    """Format facts that hold for any block: IQ2_XXS magnitudes come from the grid, signs have even parity, the scale
+    nibble multiplies a whole group of 32, and IQ1_S values are scale * ({-1, 0, 1} +- 1/8)."""
+    from pmetal_b200.gguf import iq_quants
+    from pmetal_b200.gguf.iq_grids import KSIGNS, grid
+    assert all(bin(int(v)).count("1") % 2 == 0 for v in KSIGNS) and [int(v) & 127 for v in KSIGNS] == list(range(128))
+    assert grid("IQ2XXS").shape == (256, 8) and grid("IQ2XS").shape == (512, 8) and grid("IQ2S").shape == (1024, 8)
+    assert grid("IQ3XXS").shape == (256, 4) and grid("IQ3S").shape == (512, 4) and grid("IQ1S").shape == (2048, 8)
+    assert set(np.unique(grid("IQ2XXS"))) <= {8, 25, 43} and set(np.unique(grid("IQ1S"))) == {-1, 0, 1}
+    blk = np.zeros(66, np.uint8)
+    blk[0:2] = np.frombuffer(np.float16(1.0).tobytes(), np.uint8)
+    blk[2:6] = [5, 0, 0, 0]                                  # grid entries of the first four groups
+    blk[6:10] = np.frombuffer(np.uint32((3 << 28) | 1).tobytes(), np.uint8)   # scale 3; first group: sign index 1
+    y = iq_quants.dequantize(blk, T.IQ2_XXS, 256)
+    db = (0.5 + 3) * 0.25
+    sign = 1.0 - 2.0 * ((int(KSIGNS[1]) >> np.arange(8)) & 1)
+    np.testing.assert_allclose(y[:8], db * grid("IQ2XXS")[5] * sign)
+    np.testing.assert_allclose(y[8:16], db * grid("IQ2XXS")[0])
+    np.testing.assert_allclose(y[32:40], 0.5 * 0.25 * grid("IQ2XXS")[0])     # next group of 32: scale nibble 0
+    b1 = np.zeros(50, np.uint8)
+    b1[0:2] = np.frombuffer(np.float16(2.0).tobytes(), np.uint8)
+    b1[34:36] = np.frombuffer(np.uint16((2 << 12) | 0x8000).tobytes(), np.uint8)      # scale 2*2+1 = 5, negative offset
+    y1 = iq_quants.dequantize(b1, T.IQ1_S, 256)
+    np.testing.assert_allclose(y1[:8], 2.0 * 5 * (grid("IQ1S")[0] - 0.125))
+    np.testing.assert_allclose(y1[32:40], 2.0 * 1 * (grid("IQ1S")[0] + 0.125))
 
 
 def test_ternary_one_bit_and_nvfp4_codecs():
@@ -306,3 +362,19 @@ def test_quantised_matvec_close_to_float():
     wd = native.dequantize(wb, GgmlType.Q6K, rows * n).reshape(rows, n)
     yd = native.dequantize(native.quantize(y, GgmlType.Q8K), GgmlType.Q8K, n)
     np.testing.assert_allclose(out, wd @ yd, rtol=1e-4, atol=1e-3)
+
+
+def test_gguf_file_with_iquant_tensor_reads_back(tmp_path):
+    """A tensor stored in an i-quant type comes out of the reader as float32 through the same decoders."""
+    from pmetal_b200.gguf.reader import GgufFile
+    from pmetal_b200.gguf.writer import GgufWriter
+    blocks = _random_iq_blocks("IQ3_S", 8, seed=2)           # 8 blocks = a [4, 512] matrix
+    w = GgufWriter()
+    w.add_string("general.architecture", "llama")
+    w.add_tensor_bytes("blk.0.ffn_up.weight", [4, 512], T.IQ3_S, blocks.tobytes())
+    path = tmp_path / "iq.gguf"
+    w.write_to(str(path))
+    with GgufFile(str(path)) as f:
+        arr = f.tensor_f32("blk.0.ffn_up.weight")
+    assert arr.shape == (4, 512)
+    np.testing.assert_array_equal(arr.reshape(-1), native.dequantize(blocks.reshape(-1), T.IQ3_S, 8 * 256))
