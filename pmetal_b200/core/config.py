@@ -35,9 +35,14 @@ class ModelConfig:
     use_flash_attention: bool = True
     trust_remote_code: bool = False
     revision: Optional[str] = None
-    hf_token: Optional[str] = None
+    hf_token: Optional["SecretString"] = None      # never serialised, never printed (core/secrets.py)
 
     from_dict = classmethod(_from_dict)
+
+    def __post_init__(self):
+        from .secrets import SecretString
+        if self.hf_token is not None and not isinstance(self.hf_token, SecretString):
+            self.hf_token = SecretString(self.hf_token)
 
 
 @dataclass
