@@ -367,7 +367,21 @@ def gemm_q4_lora_dx(dy, q, dt, a) -> torch.Tensor:
 
 
 def _splits_for(m_tiles: int, nk: int) -> int:
-    return max(1, min(nk, -(-sm_count() // max(m_tiles, 1))))
+    """How many ways to cut the reduction of a token-reduction GEMM with ``m_tiles`` output tiles and ``nk`` k-blocks.
+
+    Every (tile, split) pair is one CTA and an SM streams its operands at a fixed rate, so the launch takes
+    waves * (k-blocks per split + a fixed cost per CTA) with waves = ceil(pairs / SMs). One pair more than there are SMs
+    doubles the time, so the count is chosen by that makespan, not by rounding SMs / tiles up."""
+    sms, m_tiles = sm_count(), max(m_tiles, 1)
+    best, best_cost = 1, None
+    for s in range(1, min(nk, 64) + 1):
+        per = -(-nk // s)
+        if (s - 1) * per >= nk:              # an empty last split is rejected by the launcher
+            continue
+        cost = -(-(m_tiles * s) // sms) * (per + 6)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def lora_da(dt, x, nr: int, out: torch.Tensor) -> None:
