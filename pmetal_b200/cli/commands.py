@@ -1483,8 +1483,12 @@ def _pretrain_args(sp):
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--resume", nargs="?", const="auto", help="checkpoint directory, or no value for the newest one under --output")
     p.add_argument("--device")
-    p.add_argument("--dp-impl", choices=["fused", "nccl"], default="fused",
-                   help="gradient exchange on several GPUs: the fused reduce + AdamW kernel over peer memory, or an all-reduce")
+    p.add_argument("--dp-impl", choices=["fused", "nccl", "overlap"], default="fused",
+                   help="gradient exchange on several GPUs: the fused reduce + AdamW kernel over peer memory, one all-reduce "
+                        "after backward, or bucketed all-reduces that run while backward continues")
+    p.add_argument("--reduce-dtype", choices=["float32", "bfloat16"], default="float32",
+                   help="--dp-impl overlap: number format of the gradients on the wire")
+    p.add_argument("--bucket-mb", type=float, default=32.0, help="--dp-impl overlap: smallest bucket")
     return p
 
 
@@ -1527,7 +1531,8 @@ def cmd_pretrain(a) -> int:
                          weight_decay=a.weight_decay, max_grad_norm=a.max_grad_norm, z_loss_coef=a.z_loss, seq_len=a.seq_len,
                          micro_batch=a.micro_batch, gradient_accumulation_steps=a.gradient_accumulation_steps,
                          lr_scheduler=a.lr_schedule, checkpoint_every=a.checkpoint_every, output=a.output)
-    tr = PretrainTrainer(model.train(), cfg, dist=dctx)
+    tr = PretrainTrainer(model.train(), cfg, dist=dctx, overlap_reduce=a.dp_impl == "overlap",
+                         reduce_dtype=torch.bfloat16 if a.reduce_dtype == "bfloat16" else None, bucket_mb=a.bucket_mb)
     resume = a.resume
     if resume == "auto":
         done = sorted((int(d.split("_")[1]), d) for d in (os.listdir(a.output) if os.path.isdir(a.output) else [])

@@ -339,8 +339,11 @@ class DecoderLM(nn.Module):
         x = hidden_in if hidden_in is not None else F.embedding(input_ids, ops.live(self.embed_tokens))
         rope = self.rope(positions)
         policies = getattr(self, "layer_policies", None) if self.training else None      # utils/offload.py plan
+        ready = getattr(self, "grad_ready_hook", None) if torch.is_grad_enabled() else None   # parallel/overlap.py
         for i in range(lo, hi):
             layer = self.layers[i]
+            if ready is not None and x.requires_grad:     # fires once the gradient w.r.t. this layer's input exists
+                x.register_hook(lambda g, i=i: ready(i))
             pol = policies[i] if policies is not None else None
             if pol == "recompute" or (pol is None and self.gradient_checkpointing and self.training
                                       and (i % self.gradient_checkpointing == 0)):

@@ -44,6 +44,28 @@ def shutdown_process_group(timeout_s: float = 30.0) -> None:
         watchdog.cancel()
 
 
+@torch.no_grad()
+def step_on_summed_gradient(opt, grad_scale: float, world: int, group=None) -> torch.Tensor:
+    """Optimiser step on a gradient buffer that holds the sum over ``world`` ranks, clipping by the norm of the mean.
+
+    Every rank holds the same numbers, but the norm is a parallel sum whose order (and last bit) can differ from rank to
+    rank; replicas that clip with their own value drift apart by an ulp per step. The largest norm is agreed on first,
+    so that all ranks scale by the same coefficient."""
+    if not opt.max_grad_norm:
+        return opt.step(grad_scale / world)
+    norm = opt.compute_grad_norm().reshape(1) * (grad_scale / world)
+    if world > 1:
+        dist.all_reduce(norm, op=dist.ReduceOp.MAX, group=group)
+    coef = torch.clamp(opt.max_grad_norm / (norm + 1e-6), max=1.0) * (grad_scale / world)
+    opt.flat_g.mul_(coef)
+    saved, opt.max_grad_norm = opt.max_grad_norm, 0.0
+    try:
+        opt.step(1.0)
+    finally:
+        opt.max_grad_norm = saved
+    return norm
+
+
 class DistContext:
     """Rank bookkeeping + the collectives the training loop needs."""
 
@@ -109,7 +131,7 @@ class DistContext:
         n = self.world_size
         if clip_after_reduce or not opt.max_grad_norm:
             dist.all_reduce(opt.flat_g, group=self.group)
-            return opt.step(grad_scale / n)
+            return step_on_summed_gradient(opt, grad_scale, n, self.group)
         # clip-before-reduce: scale the local gradient by its own clip coefficient, then average
         norm = opt.compute_grad_norm() * grad_scale
         coef = torch.clamp(opt.max_grad_norm / (norm + 1e-6), max=1.0) * grad_scale / n

@@ -35,7 +35,10 @@ class PretrainConfig:
 
 
 class PretrainTrainer:
-    def __init__(self, model, cfg: PretrainConfig, dist=None):
+    def __init__(self, model, cfg: PretrainConfig, dist=None, overlap_reduce: bool = False,
+                 reduce_dtype: Optional[torch.dtype] = None, bucket_mb: float = 32.0):
+        """``overlap_reduce``: all-reduce the gradient bucket by bucket while backward is still running
+        (parallel/overlap.py) instead of after it; ``reduce_dtype=torch.bfloat16`` halves the bytes on the wire."""
         from .optimizer import FlatAdamW, attach_shadows
         self.model, self.cfg, self.dist = model, cfg, dist
         self.device = model.embed_tokens.device
@@ -48,6 +51,11 @@ class PretrainTrainer:
             dist.bind_optimizer(self.opt)
         if shadow is not None:
             attach_shadows(model, self.opt)
+        self.reducer = None
+        if overlap_reduce and dist is not None and dist.world_size > 1 and not getattr(dist, "fused", False):
+            from ..parallel.overlap import OverlappedGradReducer
+            self.reducer = OverlappedGradReducer(self.opt, model, group=dist.group, bucket_mb=bucket_mb,
+                                                 reduce_dtype=reduce_dtype)
         self.sched = LearningRateScheduler(cfg.learning_rate, cfg.max_steps, cfg.warmup_steps, cfg.lr_scheduler,
                                            min_lr=cfg.min_lr)
         self.step_count = 0
@@ -118,14 +126,18 @@ class PretrainTrainer:
             self.opt.set_lr(self.sched.get_lr(self.step_count))
             self.opt.zero_grad()
             ce_sum, zl_sum, n_tok, parts = 0.0, 0.0, 0, [windows[i:i + c.micro_batch] for i in range(0, len(windows), c.micro_batch)]
-            for part in parts:
+            for j, part in enumerate(parts):
                 ids = self._batch(part)
                 loss, ce, zl = self._loss(ids)
+                if self.reducer is not None and j == len(parts) - 1:
+                    self.reducer.arm()                       # only the last micro-batch leaves final gradients
                 (loss / len(parts)).backward()
                 ce_sum += float(ce.detach()) / len(parts)
                 zl_sum += float(zl.detach()) / len(parts)
                 n_tok += ids.numel()
-            if self.dist is not None and self.dist.world_size > 1:
+            if self.reducer is not None:
+                gn = self.reducer.finish_and_step(1.0)
+            elif self.dist is not None and self.dist.world_size > 1:
                 gn = self.dist.reduce_and_step(self.opt, 1.0)
             else:
                 gn = self.opt.step(1.0)
@@ -138,8 +150,12 @@ class PretrainTrainer:
         ids = self._batch(windows)
         B, L = ids.shape
         loss, ce, zl = self._loss(ids)
+        if self.reducer is not None:
+            self.reducer.arm()
         loss.backward()
-        if self.dist is not None and self.dist.world_size > 1:
+        if self.reducer is not None:
+            gn = self.reducer.finish_and_step(1.0)
+        elif self.dist is not None and self.dist.world_size > 1:
             gn = self.dist.reduce_and_step(self.opt, 1.0)
         else:
             gn = self.opt.step(1.0)

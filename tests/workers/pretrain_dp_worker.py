@@ -37,12 +37,19 @@ def main():
                          z_loss_coef=1e-3, lr_scheduler="constant")
     rng = np.random.default_rng(100 + rank)               # different data on every rank
     data = [rng.integers(0, V, L) for _ in range(8)]
-    variants = [("allreduce", ctx)]
+    class ClipAfter(DistContext):                          # one all-reduce after backward, clip on the averaged gradient
+        def reduce_and_step(self, opt, grad_scale, clip_after_reduce=False):
+            return DistContext.reduce_and_step(self, opt, grad_scale, clip_after_reduce=True)
+
+    variants = [("allreduce", ctx, {}), ("clip-after", ClipAfter(), {}),
+                ("overlap", ctx, dict(overlap_reduce=True, bucket_mb=0.001)),
+                ("overlap-bf16", ctx, dict(overlap_reduce=True, bucket_mb=0.001, reduce_dtype=torch.bfloat16))]
     if gpu:
         from pmetal_b200.parallel.fused_dp import FusedDataParallel
-        variants.append(("fused", FusedDataParallel()))
-    for name, dctx in variants:
-        tr = PretrainTrainer(build(dev, gpu).train(), cfg, dist=dctx)
+        variants.append(("fused", FusedDataParallel(), {}))
+    finals = {}
+    for name, dctx, extra in variants:
+        tr = PretrainTrainer(build(dev, gpu).train(), cfg, dist=dctx, **extra)
         if gpu:
             assert tr._native_path(), "the GPU run must take the native kernels"
             from pmetal_b200.ops import functional as ops
@@ -55,7 +62,11 @@ def main():
             assert abs(nat_loss - ref_loss) < 2e-2 * abs(ref_loss), (nat_loss, ref_loss)
         logs = [tr.train_step(data[2 * i:2 * i + 2]) for i in range(4)]
         assert all(np.isfinite(x["loss"]) and np.isfinite(x["grad_norm"]) for x in logs), logs
+        if name.startswith("overlap"):
+            assert len(tr.reducer.buckets) == 2 and tr.reducer.launched_early == 2, \
+                (tr.reducer.buckets, tr.reducer.launched_early)      # both layers left while backward was still running
         flat = tr.opt.flat_p.detach().clone()
+        finals[name] = flat
         got = [torch.empty_like(flat) for _ in range(world)]
         dist.all_gather(got, flat)
         for r, other in enumerate(got):
@@ -68,6 +79,18 @@ def main():
             torch.cuda.synchronize()
             native.check_status()
         del tr
+    # bucket by bucket during backward = one all-reduce after it (same sums, same clip); bf16 on the wire stays close
+    d = (finals["overlap"] - finals["clip-after"]).abs()
+    if gpu:
+        # a few norm-weight gradients are sums of atomics (last bits vary from run to run) and Adam turns a sign flip of a
+        # near-zero gradient into a step of size lr, so single elements may move; a bucket sent too early would move all
+        # of its elements
+        moved = (d > 1e-5).float().mean().item()
+        assert moved < 0.01 and d.max().item() < 5e-3, f"overlapped reduce: {moved:.4f} of the parameters differ, max {d.max().item()}"
+    else:
+        assert d.max().item() == 0.0, f"overlapped reduce differs from the plain one by {d.max().item()}"
+    drift = (finals["overlap-bf16"] - finals["clip-after"]).abs().max().item()
+    assert 0.0 < drift < 5e-3, f"bf16 gradient exchange drifted by {drift}"
     dist.barrier()
     print("PRETRAIN_DP_WORKER_OK", flush=True)
     shutdown_process_group()
