@@ -18,7 +18,9 @@ import statistics
 import torch
 import torch.distributed as dist
 
-NVLINK_GBS = 770.0
+from ..parallel.linkbw import FALLBACK_GBS, measure_link_gbs
+
+NVLINK_GBS = FALLBACK_GBS     # replaced by the ring-exchange measurement of this run in main()
 
 
 def _peak_tflops() -> float:
@@ -68,9 +70,12 @@ def main(argv=None) -> int:
     from ..parallel.ep import FusedExpertMoE, expert_range
     from ..parallel.tp import ColumnParallelLinear, RowParallelLinear
     peak = _peak_tflops()
+    global NVLINK_GBS
+    NVLINK_GBS, link_src = measure_link_gbs(dist, dev)
     H, T = a.hidden, a.tokens
     rows = T - T % 128
-    out = {"world_size": world, "tokens_per_rank": rows, "hidden": H, "peak_tflops": peak, "nvlink_gbs": NVLINK_GBS}
+    out = {"world_size": world, "tokens_per_rank": rows, "hidden": H, "peak_tflops": peak,
+           "nvlink_gbs": round(NVLINK_GBS, 1), "nvlink_gbs_source": link_src}
     g = torch.Generator(device=dev).manual_seed(1 + rank)
 
     # ---- TP column-parallel: qkv-like projection, N_loc = 3H / world ... use 4H / world

@@ -15,7 +15,6 @@ import os
 import subprocess
 import sys
 
-NVLINK_COPY_GBS = 770.0        # measured peer copy bandwidth per direction per GPU on this class of node
 
 
 def _torchrun(n: int, module_args, port: int = 29611) -> int:
@@ -122,9 +121,12 @@ def _bench_worker(mb: int, iters: int) -> None:
                                      "note": "reduce-scatter + clip + AdamW + all-gather in one kernel"}
     except Exception as e:          # the collective bench must still report the library number
         out["fused_reduce_adamw"] = {"error": f"{type(e).__name__}: {e}"}
+    from .linkbw import measure_link_gbs
+    link, src = measure_link_gbs(dist, dev)
+    out["link_gbs_per_direction"] = {"value": round(link, 1), "source": src}
     for k in ("nccl", "fused_reduce_adamw"):
         if "busbw_gbs" in out[k]:
-            out[k]["frac_of_nvlink_copy"] = round(out[k]["busbw_gbs"] / NVLINK_COPY_GBS, 3)
+            out[k]["frac_of_nvlink_copy"] = round(out[k]["busbw_gbs"] / link, 3)
     if rank == 0:
         print(json.dumps(out), flush=True)
     dist.barrier()
@@ -143,10 +145,13 @@ def _pipeline_worker(mb: int, iters: int, hidden: int = 0, tokens: int = 0, time
     x = torch.randn(1, tokens, hidden, device=dev).bfloat16()
     msg = ActivationMessage(nonce=1, layer_id=rank, tensor=x)
     ms = _time_max(dist, dev, lambda: pipeline_ring_step(msg, rank, world), iters) if world > 1 else 0.0
+    from .linkbw import measure_link_gbs
+    link, src = measure_link_gbs(dist, dev)
     if rank == 0:
         gbs = x.numel() * 2 / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
         print(json.dumps({"world_size": world, "message_mb": round(x.numel() * 2 / 2 ** 20, 2), "ms": round(ms, 4),
-                          "gbs_per_hop": round(gbs, 1), "frac_of_nvlink_copy": round(gbs / NVLINK_COPY_GBS, 3)}), flush=True)
+                          "gbs_per_hop": round(gbs, 1), "link_gbs_per_direction": round(link, 1), "link_source": src,
+                          "frac_of_nvlink_copy": round(gbs / link, 3)}), flush=True)
     dist.barrier()
     torch.cuda.synchronize()
     from pmetal_b200.parallel.dp import shutdown_process_group
