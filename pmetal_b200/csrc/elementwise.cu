@@ -638,12 +638,23 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const 
 
 // ------------------------------------------------------------------------------------ cross-entropy on a logits chunk
 // One block per row. logits (bf16, [n, ldl]) are replaced in place by d(loss_sum)/dlogits * grad_scale,
-// where grad_scale = *inv_n (1 / number of valid tokens of the whole batch). Adds the row's
-// loss (lse - logit[label]) to loss_sum. Rows whose label is ignore_index get a zero gradient.
+// where grad_scale = *inv_n (1 / number of valid tokens of the whole batch). Adds the row's loss to loss_sum.
+// Rows whose label is ignore_index get a zero gradient. Options (compile-time kOpt for the two that touch every element):
+//   softcap c > 0:  the logits are c * tanh(x / c) before the softmax (gradient times 1 - tanh^2)
+//   smoothing e:    loss = lse - (1 - e) x[label] - e * mean(x)   (gradient  softmax - (1 - e) onehot - e / V)
+//   z_coef:         adds z_coef * lse^2 (gradient factor 1 + 2 z_coef lse on the softmax term)
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool kOpt>
 __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ labels,
                                   float* __restrict__ loss_sum, const float* __restrict__ inv_n,
                                   float* __restrict__ row_loss, const float* __restrict__ row_scale, int V,
-                                  long long ignore_index, int write_grad, float z_coef, float* __restrict__ z_sum) {
+                                  long long ignore_index, int write_grad, float z_coef, float* __restrict__ z_sum,
+                                  float smooth, float cap) {
   __shared__ float red[32];
   __shared__ float bcast[2];
   const int row = blockIdx.x;
@@ -660,11 +671,20 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
     }
     return;
   }
-  // pass 1: online max / sum-exp
-  float m = -INFINITY, s = 0.f;
+  const bool capped = kOpt && cap > 0.f;
+  const float inv_cap = capped ? 1.f / cap : 0.f;
+  // pass 1: online max / sum-exp (and the plain sum of the logits for the smoothing term)
+  float m = -INFINITY, s = 0.f, sx = 0.f;
   for (int c = tid * 8; c < V8; c += nthr * 8) {
     float f[8];
     load8(lr + c, f);
+    if (kOpt) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (capped) f[i] = cap * tanh_fast(f[i] * inv_cap);
+        sx += f[i];
+      }
+    }
     float lm = f[0];
 #pragma unroll
     for (int i = 1; i < 8; ++i) lm = fmaxf(lm, f[i]);
@@ -673,7 +693,11 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
     for (int i = 0; i < 8; ++i) s += __expf(f[i] - m);
   }
   for (int c = V8 + tid; c < V; c += nthr) {
-    const float f = __bfloat162float(lr[c]);
+    float f = __bfloat162float(lr[c]);
+    if (kOpt) {
+      if (capped) f = cap * tanh_fast(f * inv_cap);
+      sx += f;
+    }
     if (f > m) { s *= __expf(m - f); m = f; }
     s += __expf(f - m);
   }
@@ -690,12 +714,25 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
   s = (wm == -INFINITY) ? 0.f : s * __expf(wm - bm);
   if ((tid & 31) == 0) red[tid >> 5] = s;
   __syncthreads();
-  if (tid == 0) {
-    float tot = 0.f;
+  float tot = 0.f;
+  if (tid == 0)
     for (int i = 0; i < nw; ++i) tot += red[i];
+  float sx_tot = 0.f;
+  if (kOpt) {                       // second use of the scratch array: the sum of the logits
+    __syncthreads();
+    sx = warp_sum(sx);
+    if ((tid & 31) == 0) red[tid >> 5] = sx;
+    __syncthreads();
+    if (tid == 0)
+      for (int i = 0; i < nw; ++i) sx_tot += red[i];
+  }
+  if (tid == 0) {
     const float lse = bm + logf(tot);
     bcast[0] = lse;
-    const float rl = lse - __bfloat162float(lr[label]);
+    float xl = __bfloat162float(lr[label]);
+    if (capped) xl = cap * tanh_fast(xl * inv_cap);
+    float rl = lse - xl;
+    if (kOpt && smooth > 0.f) rl = lse - (1.f - smooth) * xl - smooth * sx_tot / static_cast<float>(V);
     if (row_loss) row_loss[row] = rl;
     if (loss_sum) atomicAdd(loss_sum, rl);
     if (z_sum) atomicAdd(z_sum, lse * lse);
@@ -706,16 +743,31 @@ __global__ void ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long 
   const float gs = row_scale ? row_scale[row] : *inv_n;
   // with the z term  z_coef * lse^2  the gradient is  (1 + 2 z_coef lse) softmax - onehot
   const float pz = 1.f + 2.f * z_coef * lse;
+  const float hot = kOpt ? 1.f - smooth : 1.f;
+  const float uni = kOpt ? smooth / static_cast<float>(V) : 0.f;
   for (int c = tid * 8; c < V8; c += nthr * 8) {
     float f[8];
     load8(lr + c, f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = (pz * __expf(f[i] - lse) - ((c + i) == label ? 1.f : 0.f)) * gs;
+    for (int i = 0; i < 8; ++i) {
+      float x = f[i], dcap = 1.f;
+      if (capped) {
+        const float t = tanh_fast(x * inv_cap);
+        x = cap * t;
+        dcap = 1.f - t * t;
+      }
+      f[i] = (pz * __expf(x - lse) - ((c + i) == label ? hot : 0.f) - uni) * gs * dcap;
+    }
     store8(lr + c, f);
   }
   for (int c = V8 + tid; c < V; c += nthr) {
-    const float f = __bfloat162float(lr[c]);
-    lr[c] = __float2bfloat16((pz * __expf(f - lse) - (c == label ? 1.f : 0.f)) * gs);
+    float x = __bfloat162float(lr[c]), dcap = 1.f;
+    if (capped) {
+      const float t = tanh_fast(x * inv_cap);
+      x = cap * t;
+      dcap = 1.f - t * t;
+    }
+    lr[c] = __float2bfloat16((pz * __expf(x - lse) - (c == label ? hot : 0.f) - uni) * gs * dcap);
   }
 }
 
@@ -995,8 +1047,8 @@ extern "C" int pm_ce_fwd_bwd(void* logits, long long ldl, const long long* label
                              float* row_loss, const float* row_scale, int n_rows, int V, long long ignore_index,
                              int write_grad, cudaStream_t st) {
   if (ldl % 8) return -1;
-  ce_fwd_bwd_kernel<<<n_rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ldl, labels, loss_sum, inv_n, row_loss,
-                                             row_scale, V, ignore_index, write_grad, 0.f, nullptr);
+  ce_fwd_bwd_kernel<false><<<n_rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ldl, labels, loss_sum, inv_n,
+                                                    row_loss, row_scale, V, ignore_index, write_grad, 0.f, nullptr, 0.f, 0.f);
   return PM_LAUNCH_CHECK();
 }
 // Cross entropy plus the z term z_coef * logsumexp(logits)^2 per valid row: z_sum receives the sum of the squared
@@ -1005,8 +1057,19 @@ extern "C" int pm_ce_z_fwd_bwd(void* logits, long long ldl, const long long* lab
                                const float* inv_n, int n_rows, int V, long long ignore_index, int write_grad, float z_coef,
                                cudaStream_t st) {
   if (ldl % 8) return -1;
-  ce_fwd_bwd_kernel<<<n_rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ldl, labels, loss_sum, inv_n, nullptr,
-                                             nullptr, V, ignore_index, write_grad, z_coef, z_sum);
+  ce_fwd_bwd_kernel<false><<<n_rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ldl, labels, loss_sum, inv_n,
+                                                    nullptr, nullptr, V, ignore_index, write_grad, z_coef, z_sum, 0.f, 0.f);
+  return PM_LAUNCH_CHECK();
+}
+// The same with label smoothing (0 <= smooth < 1) and soft-capped logits (softcap > 0: cap * tanh(x / cap)).
+extern "C" int pm_ce_opt_fwd_bwd(void* logits, long long ldl, const long long* labels, float* loss_sum, float* z_sum,
+                                 const float* inv_n, int n_rows, int V, long long ignore_index, int write_grad,
+                                 float z_coef, float smooth, float softcap, cudaStream_t st) {
+  if (ldl % 8) return -1;
+  if (smooth < 0.f || smooth >= 1.f || softcap < 0.f) return -2;
+  ce_fwd_bwd_kernel<true><<<n_rows, 1024, 0, st>>>(static_cast<__nv_bfloat16*>(logits), ldl, labels, loss_sum, inv_n,
+                                                   nullptr, nullptr, V, ignore_index, write_grad, z_coef, z_sum, smooth,
+                                                   softcap);
   return PM_LAUNCH_CHECK();
 }
 extern "C" int pm_sumsq(const float* x, long long n, float* out, cudaStream_t st) {

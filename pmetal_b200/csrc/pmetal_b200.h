@@ -118,6 +118,10 @@ int pm_ce_fwd_bwd(void* logits, long long ldl, const long long* labels, float* l
 // normalisers, and the gradient written over the logits is that of (cross entropy + z_coef * z) summed over rows.
 int pm_ce_z_fwd_bwd(void* logits, long long ldl, const long long* labels, float* loss_sum, float* z_sum, const
     float* inv_n, int n_rows, int V, long long ignore_index, int write_grad, float z_coef, cudaStream_t st);
+// The same with label smoothing (0 <= smooth < 1) and soft-capped logits (softcap > 0: cap * tanh(x / cap)).
+int pm_ce_opt_fwd_bwd(void* logits, long long ldl, const long long* labels, float* loss_sum, float* z_sum, const
+    float* inv_n, int n_rows, int V, long long ignore_index, int write_grad, float z_coef, float smooth, float
+    softcap, cudaStream_t st);
 int pm_sumsq(const float* x, long long n, float* out, cudaStream_t st);
 int pm_adamw_flat(float* p, const float* g, float* m, float* v, void* shadow, const float* lr_mult, const float*
     wd, const float* gnorm_sq, const float* hp, long long n, float lr, float beta1, float beta2, float eps, int

@@ -105,8 +105,10 @@ def varlen_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
 
 
 def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
-                         chunk: int = 4096, softcap: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Σ over valid tokens of (logsumexp(h Wᵀ) − (h Wᵀ)[label]) and the valid-token count.
+                         chunk: int = 4096, softcap: float = 0.0,
+                         label_smoothing: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Σ over valid tokens of (logsumexp(h Wᵀ) − (h Wᵀ)[label]) and the valid-token count; with ``label_smoothing`` e
+    the target is (1 − e) one-hot + e / V.
 
     ``labels`` are already aligned with ``hidden`` (the caller did the causal shift).
     Token-chunked so the [T, V] logits never exist at once.
@@ -119,7 +121,8 @@ def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: tor
         logits = F.linear(h, weight).float()
         if softcap > 0:
             logits = softcap * torch.tanh(logits / softcap)
-        total = total + F.cross_entropy(logits, lab, ignore_index=ignore_index, reduction="sum")
+        total = total + F.cross_entropy(logits, lab, ignore_index=ignore_index, reduction="sum",
+                                        label_smoothing=label_smoothing)
     return total, valid.sum()
 
 
