@@ -636,6 +636,73 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const 
   }
 }
 
+// ------------------------------------------------------------------------------------ gated activations (GLU family)
+// out = act(gate) * up with gate and up as separate row-strided matrices (two projections, or the two halves of a fused
+// one). kAct: 0 SiLU (SwiGLU), 1 GELU with the tanh approximation (GeGLU of Gemma), 2 exact GELU (erf).
+template <int kAct>
+__device__ __forceinline__ void glu_act(float g, float* a, float* da) {
+  if (kAct == 0) {
+    const float sg = 1.f / (1.f + __expf(-g));
+    *a = g * sg;
+    *da = sg * (1.f + g * (1.f - sg));
+  } else if (kAct == 1) {
+    const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+    const float u = k0 * (g + k1 * g * g * g);
+    const float t = tanhf(u);
+    *a = 0.5f * g * (1.f + t);
+    *da = 0.5f * (1.f + t) + 0.5f * g * (1.f - t * t) * k0 * (1.f + 3.f * k1 * g * g);
+  } else {
+    const float cdf = 0.5f * (1.f + erff(g * 0.7071067811865476f));
+    *a = g * cdf;
+    *da = cdf + g * 0.3989422804014327f * __expf(-0.5f * g * g);
+  }
+}
+template <int kAct>
+__global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up, long long ldg,
+                               long long ldu, __nv_bfloat16* __restrict__ out, long long T, int I) {
+  const long long n8 = T * (I / 8);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / (I / 8);
+    const int c = static_cast<int>(i - t * (I / 8)) * 8;
+    float g[8], u[8], o[8];
+    load8(gate + t * ldg + c, g);
+    load8(up + t * ldu + c, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float a, da;
+      glu_act<kAct>(g[k], &a, &da);
+      o[k] = a * u[k];
+    }
+    store8(out + t * I + c, o);
+  }
+}
+template <int kAct>
+__global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ gate,
+                               const __nv_bfloat16* __restrict__ up, long long ldg, long long ldu,
+                               __nv_bfloat16* __restrict__ dgate, __nv_bfloat16* __restrict__ dup, long long lddg,
+                               long long lddu, long long T, int I) {
+  const long long n8 = T * (I / 8);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / (I / 8);
+    const int c = static_cast<int>(i - t * (I / 8)) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gate + t * ldg + c, g);
+    load8(up + t * ldu + c, u);
+    load8(dout + t * I + c, d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float a, da;
+      glu_act<kAct>(g[k], &a, &da);
+      dg[k] = d[k] * u[k] * da;
+      du[k] = d[k] * a;
+    }
+    store8(dgate + t * lddg + c, dg);
+    store8(dup + t * lddu + c, du);
+  }
+}
+
 // ------------------------------------------------------------------------------------ cross-entropy on a logits chunk
 // One block per row. logits (bf16, [n, ldl]) are replaced in place by d(loss_sum)/dlogits * grad_scale,
 // where grad_scale = *inv_n (1 / number of valid tokens of the whole batch). Adds the row's loss to loss_sum.
@@ -1042,6 +1109,30 @@ extern "C" int pm_swiglu_bwd(const void* dout, const void* gu, void* dgu, long l
       T, I);
   return PM_LAUNCH_CHECK();
 }
+// act(gate) * up for separate gate / up matrices (row strides in elements, multiples of 8); act: 0 SiLU, 1 GELU-tanh, 2 GELU.
+extern "C" int pm_glu_fwd(const void* gate, const void* up, long long ldg, long long ldu, void* out, long long T, int I,
+                          int act, cudaStream_t st) {
+  if ((I % 8) || (ldg % 8) || (ldu % 8) || act < 0 || act > 2) return -1;
+  const __nv_bfloat16 *g = static_cast<const __nv_bfloat16*>(gate), *u = static_cast<const __nv_bfloat16*>(up);
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  const int grid = grid_for(T * (I / 8), 256);
+  if (act == 0) glu_fwd_kernel<0><<<grid, 256, 0, st>>>(g, u, ldg, ldu, o, T, I);
+  else if (act == 1) glu_fwd_kernel<1><<<grid, 256, 0, st>>>(g, u, ldg, ldu, o, T, I);
+  else glu_fwd_kernel<2><<<grid, 256, 0, st>>>(g, u, ldg, ldu, o, T, I);
+  return PM_LAUNCH_CHECK();
+}
+extern "C" int pm_glu_bwd(const void* dout, const void* gate, const void* up, long long ldg, long long ldu, void* dgate,
+                          void* dup, long long lddg, long long lddu, long long T, int I, int act, cudaStream_t st) {
+  if ((I % 8) || (ldg % 8) || (ldu % 8) || (lddg % 8) || (lddu % 8) || act < 0 || act > 2) return -1;
+  const __nv_bfloat16 *d = static_cast<const __nv_bfloat16*>(dout), *g = static_cast<const __nv_bfloat16*>(gate),
+                      *u = static_cast<const __nv_bfloat16*>(up);
+  __nv_bfloat16 *dg = static_cast<__nv_bfloat16*>(dgate), *du = static_cast<__nv_bfloat16*>(dup);
+  const int grid = grid_for(T * (I / 8), 256);
+  if (act == 0) glu_bwd_kernel<0><<<grid, 256, 0, st>>>(d, g, u, ldg, ldu, dg, du, lddg, lddu, T, I);
+  else if (act == 1) glu_bwd_kernel<1><<<grid, 256, 0, st>>>(d, g, u, ldg, ldu, dg, du, lddg, lddu, T, I);
+  else glu_bwd_kernel<2><<<grid, 256, 0, st>>>(d, g, u, ldg, ldu, dg, du, lddg, lddu, T, I);
+  return PM_LAUNCH_CHECK();
+}
 // row_loss (optional): per-row loss out. row_scale (optional): per-row gradient scale replacing *inv_n.
 extern "C" int pm_ce_fwd_bwd(void* logits, long long ldl, const long long* labels, float* loss_sum, const float* inv_n,
                              float* row_loss, const float* row_scale, int n_rows, int V, long long ignore_index,
@@ -1085,8 +1176,9 @@ extern "C" int pm_adamw_flat(float* p, const float* g, float* m, float* v, void*
   if (n % 1024) return -1;
   AdamwArgs a;
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps;
-  a.bc1 = 1.f - powf(beta1, static_cast<float>(step));
-  a.bc2 = 1.f - powf(beta2, static_cast<float>(step));
+  // step <= 0 selects the variant without bias correction (moments used as they are)
+  a.bc1 = step > 0 ? 1.f - powf(beta1, static_cast<float>(step)) : 1.f;
+  a.bc2 = step > 0 ? 1.f - powf(beta2, static_cast<float>(step)) : 1.f;
   a.grad_scale = grad_scale; a.max_norm = max_norm;
   adamw_flat_kernel<<<grid_for(n / 4, 256, num_sms() * 8), 256, 0, st>>>(p, g, m, v, static_cast<__nv_bfloat16*>(shadow),
                                                                   lr_mult, wd, gnorm_sq, hp, n, a);

@@ -111,6 +111,11 @@ int pm_qknorm_rope_bwd(const void* dq, const void* dk, const void* qkv, int ld, 
     const float* cs, const float* sn, void* dqkv, int T, int hq, int hkv, float eps, cudaStream_t st);
 int pm_swiglu_fwd(const void* gu, void* out, long long T, int I, cudaStream_t st);
 int pm_swiglu_bwd(const void* dout, const void* gu, void* dgu, long long T, int I, cudaStream_t st);
+// act(gate) * up for separate gate / up matrices (row strides in elements, multiples of 8); act: 0 SiLU, 1 GELU-tanh, 2 GELU.
+int pm_glu_fwd(const void* gate, const void* up, long long ldg, long long ldu, void* out, long long T, int I, int
+    act, cudaStream_t st);
+int pm_glu_bwd(const void* dout, const void* gate, const void* up, long long ldg, long long ldu, void* dgate, void*
+    dup, long long lddg, long long lddu, long long T, int I, int act, cudaStream_t st);
 // row_loss (optional): per-row loss out. row_scale (optional): per-row gradient scale replacing *inv_n.
 int pm_ce_fwd_bwd(void* logits, long long ldl, const long long* labels, float* loss_sum, const float* inv_n, float*
     row_loss, const float* row_scale, int n_rows, int V, long long ignore_index, int write_grad, cudaStream_t st);

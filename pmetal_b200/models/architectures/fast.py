@@ -5,6 +5,8 @@ are sent to the same sm_100a kernels as the fast decoder:
 * ``Linear``      frozen bf16 projections run on the tcgen05 GEMM forward and for the input gradient (split-K inside the
                   kernel for a handful of rows), bias added on top; trainable or fp32 weights keep ``F.linear``;
 * ``rms_norm``    plain RMS norms over the last dimension run on the fused norm kernel;
+* ``glu``         gated activations act(gate) * up (SiLU, tanh-GELU, GELU) run as one kernel forward and one backward,
+                  reading gate and up in place when they are the two halves of a fused projection;
 * ``causal_attention``  full-sequence causal (optionally sliding-window) self-attention without soft-capping, sinks or an
                   explicit mask runs on the varlen flash-attention kernels, every batch row as one document, head sizes
                   below 128 zero-padded.
@@ -12,7 +14,7 @@ are sent to the same sm_100a kernels as the fast decoder:
 Everything else (soft-capped logits, attention sinks, chunked masks, cached decode steps, layer norms) stays on the
 PyTorch operators. The reference has stand-alone native engines per family
 (crates/pmetal-bridge/src/{qwen3,deepseek,gpt_oss,llama4}_native/, gemma4_native.rs); here one set of kernels serves
-every family through these three entry points."""
+every family through these entry points."""
 from __future__ import annotations
 
 from typing import Optional
@@ -24,8 +26,10 @@ import torch.nn.functional as F
 
 import os
 
-# comma-separated routes that are switched on: linear, norm, attention (all by default)
-ROUTES = set(os.environ.get("PMETAL_PORTABLE_FAST", "linear,norm,attention").split(","))
+# comma-separated routes that are switched on: linear, norm, attention, glu (all by default)
+ROUTES = set(os.environ.get("PMETAL_PORTABLE_FAST", "linear,norm,attention,glu").split(","))
+GLU_NAMES = {"silu": "silu", "swish": "silu", "gelu_tanh": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "gelu_new": "gelu_tanh",
+             "gelu": "gelu"}
 
 
 def _native(x: torch.Tensor) -> bool:
@@ -51,6 +55,15 @@ class Linear(nn.Linear):
                 y = y + self.bias
             return y.view(*x.shape[:-1], self.out_features)
         return F.linear(x, w, self.bias)
+
+
+def glu(gate: torch.Tensor, up: torch.Tensor, act_name: str, act_fn) -> torch.Tensor:
+    """act(gate) * up; the fused kernel pair when the route is on and the activation is one it knows."""
+    name = GLU_NAMES.get(act_name)
+    if "glu" in ROUTES and name is not None and _native(gate) and up.dtype == gate.dtype:
+        from ...ops import functional as ops
+        return ops.glu(gate, up, name)
+    return act_fn(gate) * up
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> Optional[torch.Tensor]:

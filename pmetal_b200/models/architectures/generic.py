@@ -21,7 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..rope import rope_inv_freq  # noqa: F401  (re-exported for the architecture files)
-from .fast import Linear
+from .fast import Linear, glu as _glu
 
 
 # ------------------------------------------------------------------------------------------------ configuration
@@ -686,8 +686,8 @@ class MLP(nn.Module):
             return self.fc2(self.fn(self.fc1(x)))
         if self.c.fused_qkv:
             g, u = self.gate_up_proj(x).chunk(2, -1)
-            return self.down_proj(self.fn(g) * u)
-        return self.down_proj(self.fn(self.gate_proj(x)) * self.up_proj(x))
+            return self.down_proj(_glu(g, u, self.c.act, self.fn))
+        return self.down_proj(_glu(self.gate_proj(x), self.up_proj(x), self.c.act, self.fn))
 
 
 class Experts(nn.Module):

@@ -114,6 +114,39 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return ref.swiglu(gate_up)
 
 
+class _GluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up, act):
+        ctx.save_for_backward(gate, up)
+        ctx.act = act
+        return _native().glu_fwd(gate, up, act)
+
+    @staticmethod
+    def backward(ctx, dout):
+        gate, up = ctx.saved_tensors
+        dg, du = _native().glu_bwd(dout.contiguous(), gate, up, ctx.act)
+        return dg, du, None
+
+
+def glu(gate: torch.Tensor, up: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """``act(gate) * up`` for separate gate / up activations [..., I]: SwiGLU (``silu``), GeGLU (``gelu_tanh``) or exact
+    GELU gating. One kernel forward and one backward on a GPU (crates/pmetal-bridge/cpp/bridge_compiled.cpp:35-118:
+    fused_swiglu / fused_geglu_tanh); the PyTorch operators elsewhere."""
+    code = _native().GLU_ACTS.get(act) if gate.is_cuda else None
+    if (code is not None and use_native(gate) and up.dtype == gate.dtype and gate.shape == up.shape and gate.shape[-1] % 8 == 0
+            and gate.stride(-1) == 1 and up.stride(-1) == 1):
+        g2, u2 = gate.reshape(-1, gate.shape[-1]), up.reshape(-1, up.shape[-1])
+        if g2.stride(0) % 8 == 0 and u2.stride(0) % 8 == 0:
+            return _GluFn.apply(g2, u2, code).view(gate.shape)
+    if act in ("silu", "swish"):
+        return F.silu(gate) * up
+    if act in ("gelu_tanh", "gelu_pytorch_tanh", "gelu_new"):
+        return F.gelu(gate, approximate="tanh") * up
+    if act == "gelu":
+        return F.gelu(gate) * up
+    raise ValueError(f"unknown gated activation {act!r}")
+
+
 # --------------------------------------------------------------------------- attention block
 def rope_table(positions: torch.Tensor, head_dim: int, theta: float, rope_scale: float = 1.0):
     """cos/sin [T, head_dim/2] in fp32 for the positions of this batch (shared by every layer)."""

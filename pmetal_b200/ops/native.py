@@ -638,6 +638,26 @@ def swiglu_bwd(dout, gate_up):
     return dgu
 
 
+GLU_ACTS = {"silu": 0, "swish": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "gelu_new": 1, "gelu": 2}
+
+
+def glu_fwd(gate, up, act: int):
+    """act(gate) * up for two [T, I] bf16 matrices whose rows may be strided (views into a fused projection)."""
+    T, I = gate.shape
+    out = torch.empty(T, I, dtype=gate.dtype, device=gate.device)
+    _chk(lib().pm_glu_fwd(_p(gate), _p(up), c_ll(gate.stride(0)), c_ll(up.stride(0)), _p(out), c_ll(T), c_int(I), c_int(act),
+                          _stream()), "pm_glu_fwd")
+    return out
+
+
+def glu_bwd(dout, gate, up, act: int):
+    T, I = gate.shape
+    dg, du = torch.empty(T, I, dtype=gate.dtype, device=gate.device), torch.empty(T, I, dtype=gate.dtype, device=gate.device)
+    _chk(lib().pm_glu_bwd(_p(dout), _p(gate), _p(up), c_ll(gate.stride(0)), c_ll(up.stride(0)), _p(dg), _p(du), c_ll(I),
+                          c_ll(I), c_ll(T), c_int(I), c_int(act), _stream()), "pm_glu_bwd")
+    return dg, du
+
+
 # ------------------------------------------------------------------------------------------- attention
 def attn_fwd(q, k, v, seq_start, scale: float, window: int = 0):
     """Varlen causal attention forward. The tcgen05 kernel handles the common case; sliding windows use the

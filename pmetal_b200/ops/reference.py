@@ -133,8 +133,8 @@ def adamw_step(p: torch.Tensor, g: torch.Tensor, m: torch.Tensor, v: torch.Tenso
     g = g.float()
     m.mul_(beta1).add_(g, alpha=1 - beta1)
     v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
-    mh = m / (1 - beta1 ** step)
-    vh = v / (1 - beta2 ** step)
+    mh = m / (1 - beta1 ** step) if step > 0 else m          # step <= 0: no bias correction
+    vh = v / (1 - beta2 ** step) if step > 0 else v
     p.sub_(lr * mh / (vh.sqrt() + eps))
     if weight_decay != 0.0:
         p.sub_(weight_decay * lr * p)

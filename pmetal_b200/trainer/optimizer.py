@@ -40,7 +40,10 @@ class FlatAdamW:
     def __init__(self, named_params: Iterable[Tuple[str, torch.nn.Parameter]], lr: float = 2e-4,
                  betas: Tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
                  embedding_lr: Optional[float] = 5e-5, loraplus_ratio: Optional[float] = None,
-                 max_grad_norm: float = 0.0, shadow_dtype: Optional[torch.dtype] = None):
+                 max_grad_norm: float = 0.0, shadow_dtype: Optional[torch.dtype] = None, bias_correction: bool = True):
+        """``bias_correction=False`` uses the running moments as they are (the plain variant of the reference's fused
+        update, fused_training.metal: ``fused_adamw_update`` next to ``fused_adamw_update_bias_corrected``)."""
+        self.bias_correction = bias_correction
         self.named = [(n, p) for n, p in named_params if p.requires_grad]
         if not self.named:
             raise ValueError("no trainable parameters")
@@ -136,7 +139,8 @@ class FlatAdamW:
             from ..ops import native
             native.sumsq(self.flat_g, self.grad_norm)
             native.adamw_flat(self.flat_p, self.flat_g, self.flat_m, self.flat_v, self.flat_shadow, self.lr_mult,
-                              self.wd_tab, self.grad_norm, self.lr, b1, b2, self.eps, self.step_count, grad_scale,
+                              self.wd_tab, self.grad_norm, self.lr, b1, b2, self.eps,
+                              self.step_count if self.bias_correction else 0, grad_scale,
                               self.max_grad_norm, self._hp if self.device_hparams else None)
             return self.grad_norm.sqrt() * grad_scale
         if grad_scale != 1.0:
@@ -149,7 +153,8 @@ class FlatAdamW:
             k = p.numel()
             c = o // CHUNK
             ref.adamw_step(self.flat_p[o:o + k], self.flat_g[o:o + k], self.flat_m[o:o + k], self.flat_v[o:o + k],
-                           self.step_count, self.lr * float(self.lr_mult[c]), b1, b2, self.eps, float(self.wd_tab[c]))
+                           self.step_count if self.bias_correction else 0, self.lr * float(self.lr_mult[c]), b1, b2,
+                           self.eps, float(self.wd_tab[c]))
         if self.flat_shadow is not None:
             self.flat_shadow.copy_(self.flat_p)
         return norm.reshape(1)
@@ -157,7 +162,10 @@ class FlatAdamW:
     def push_hparams(self, step: int) -> None:
         """Stage lr and the bias corrections of ``step`` on the device (call before replaying a captured step)."""
         b1, b2 = self.betas
-        self._hp_host[0], self._hp_host[1], self._hp_host[2] = self.lr, 1 - b1 ** step, 1 - b2 ** step
+        if not self.bias_correction:
+            step = 0
+        self._hp_host[0] = self.lr
+        self._hp_host[1], self._hp_host[2] = (1 - b1 ** step, 1 - b2 ** step) if step > 0 else (1.0, 1.0)
         self._hp.copy_(self._hp_host, non_blocking=True)
 
     # ---------------------------------------------------------------- state

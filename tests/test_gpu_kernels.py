@@ -287,6 +287,39 @@ def test_qknorm_rope(T, hq, hkv):
     _close(dqkv[:, :(hq + hkv) * d], x.grad[:, :(hq + hkv) * d], what="qknorm_rope bwd")
 
 
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh", "gelu"])
+def test_gated_activations(act):
+    """act(gate) * up forward and backward, with separate matrices and with the two halves of one fused projection."""
+    from pmetal_b200.ops import functional as F
+    torch.manual_seed(21)
+    T, I = 333, 768
+    fn = {"silu": torch.nn.functional.silu, "gelu_tanh": lambda x: torch.nn.functional.gelu(x, approximate="tanh"),
+          "gelu": torch.nn.functional.gelu}[act]
+    fused = _rand(T, 2 * I, scale=2.0).requires_grad_(True)
+    for halves in (True, False):
+        if halves:
+            g, u = fused.chunk(2, -1)
+        else:
+            g, u = _rand(T, I, scale=2.0).requires_grad_(True), _rand(T, I).requires_grad_(True)
+        n0 = _nat().LAUNCHES if hasattr(_nat(), "LAUNCHES") else 0
+        y = F.glu(g, u, act)
+        dy = _rand(T, I)
+        grads = torch.autograd.grad(y, (fused,) if halves else (g, u), dy)
+        gr = (fused if halves else g).detach().float().requires_grad_(True)
+        if halves:
+            g32, u32 = gr.chunk(2, -1)
+            want = fn(g32) * u32
+            wg = torch.autograd.grad(want, gr, dy.float())
+        else:
+            ur = u.detach().float().requires_grad_(True)
+            want = fn(gr) * ur
+            wg = torch.autograd.grad(want, (gr, ur), dy.float())
+        _close(y, want, what=f"{act} forward")
+        for a, b in zip(grads, wg):
+            _close(a, b, what=f"{act} backward")
+    _nat().check_status()
+
+
 @pytest.mark.parametrize("T", [200, 1500])
 def test_rope_without_qk_norm(T):
     """Architectures without QK-norm pass no weights: the kernels only rotate (and un-rotate in backward)."""
@@ -603,6 +636,14 @@ def test_adamw_and_sumsq():
                            wd[c].item())
     _close(p, pr, rtol=1e-5, atol=1e-6, what="adamw p")
     _close(sh, pr, rtol=1e-2, atol=1e-2, what="adamw shadow")
+    # step 0 = the variant without bias correction
+    p2, m2, v2 = torch.randn(1024, device="cuda"), torch.zeros(1024, device="cuda"), torch.zeros(1024, device="cuda")
+    g2 = torch.randn(1024, device="cuda")
+    p2r, m2r, v2r = p2.clone(), m2.clone(), v2.clone()
+    one, zero = torch.ones(1, device="cuda"), torch.zeros(1, device="cuda")
+    nat.adamw_flat(p2, g2, m2, v2, None, one, zero, gn, 1e-3, 0.9, 0.999, 1e-8, 0, 1.0, 0.0)
+    ref.adamw_step(p2r, g2, m2r, v2r, 0, 1e-3, 0.9, 0.999, 1e-8, 0.0)
+    _close(p2, p2r, rtol=1e-5, atol=1e-6, what="adamw without bias correction")
 
 
 @pytest.mark.parametrize("hq,hkv,lens,qlens", [(4, 2, [70, 1, 300], [1, 1, 1]), (8, 1, [200, 64], [5, 3]),

@@ -124,6 +124,23 @@ def test_flat_adamw_matches_per_tensor(tmp_path):
         assert torch.allclose(p.detach(), c, atol=1e-6)
 
 
+def test_flat_adamw_without_bias_correction():
+    """The plain variant uses the running moments as they are: after one step m = (1 - b1) g and v = (1 - b2) g^2."""
+    torch.manual_seed(1)
+    p = torch.nn.Parameter(torch.randn(6, 5))
+    start = p.detach().clone()
+    opt = FlatAdamW([("x.lora_a", p)], lr=1e-2, weight_decay=0.0, max_grad_norm=0.0, bias_correction=False)
+    g = torch.randn(6, 5)
+    p.grad.copy_(g)
+    opt.step()
+    want = start - 1e-2 * (0.1 * g) / ((0.001 * g * g).sqrt() + 1e-8)
+    assert torch.allclose(p.detach(), want, atol=1e-6)
+    m, v = torch.zeros(2), torch.zeros(2)
+    q = torch.tensor([1.0, -1.0])
+    ref.adamw_step(q, torch.tensor([0.5, 0.5]), m, v, 0, 0.1, 0.9, 0.999, 1e-8, 0.0)
+    assert torch.allclose(q, torch.tensor([1.0, -1.0]) - 0.1 * 0.05 / (0.00025 ** 0.5 + 1e-8), atol=1e-6)
+
+
 def test_grad_clip_and_accumulation():
     m = _tiny(); apply_lora(m, LoraConfig(r=4, alpha=8))
     loop = TrainingLoop(m, TrainingConfig(gradient_accumulation_steps=2, warmup_steps=0, max_grad_norm=1e-3,
