@@ -175,9 +175,24 @@ class PortableLoraTrainer:
     def micro_step(self, input_ids: torch.Tensor, labels: torch.Tensor, scale: float = 1.0) -> float:
         """Forward + backward of one micro-batch; ``scale`` (1 / accumulation steps) multiplies its loss so that the
         accumulated gradient is the mean over the micro-batches. Gradients add up until ``optimizer_step``."""
-        loss = causal_lm_loss(self.model(input_ids), labels)
+        loss = self.loss(input_ids, labels)
         (loss * scale if scale != 1.0 else loss).backward()
         return float(loss.detach())
+
+    def loss(self, input_ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """Mean next-token cross entropy. Models that expose their read-out matrix (``loss_head``) get the chunked
+        linear + cross-entropy (logit scale and soft cap inside it), so the [batch, tokens, vocabulary] logits are never
+        formed; the others go through their own ``forward``."""
+        spec = getattr(self.model, "loss_head", None)
+        spec = spec() if callable(spec) else None
+        if spec is None or input_ids.dim() != 2:
+            return causal_lm_loss(self.model(input_ids), labels)
+        from ..ops import functional as ops
+        w, factor, cap = spec
+        h = self.model.forward_hidden(input_ids)
+        hs = h[:, :-1].reshape(-1, h.shape[-1])
+        s, n = ops.linear_cross_entropy(hs, w, labels[:, 1:].reshape(-1), softcap=cap, logit_scale=factor)
+        return s / n.clamp(min=1).to(s.dtype)
 
     def optimizer_step(self) -> dict:
         lr = self.sched.get_lr(self.step_count)

@@ -963,6 +963,19 @@ class GenericDecoderLM(nn.Module):
             z = torch.tanh(z / c.final_softcap) * c.final_softcap
         return z
 
+    def loss_head(self):
+        """(head matrix [V, H], factor on the logits, soft cap) when the read-out is one bias-free matrix, so that a trainer
+        can fuse it with the cross entropy instead of materialising [tokens, V] logits; None otherwise."""
+        c = self.c
+        if c.tie_embeddings:
+            w = self.model.embed_tokens.weight
+        else:
+            head = self.lm_head
+            if type(head).__name__ not in ("Linear",) or getattr(head, "bias", None) is not None:
+                return None
+            w = head.weight
+        return w, c.logit_scale / c.logits_divisor, c.final_softcap
+
     def forward(self, input_ids, cache: Optional[KVCache] = None, positions=None, attn_mask=None) -> torch.Tensor:
         return self.logits(self.forward_hidden(input_ids, cache, positions, attn_mask))
 

@@ -411,12 +411,13 @@ class _LinearCeFn(torch.autograd.Function):
     buffer and added to the master's ``.grad`` in backward (scaled by the incoming gradient)."""
 
     @staticmethod
-    def forward(ctx, hidden, weight, weight_t, labels, ignore_index, chunk, z_coef, master, smoothing=0.0, softcap=0.0):
+    def forward(ctx, hidden, weight, weight_t, labels, ignore_index, chunk, z_coef, master, smoothing=0.0, softcap=0.0,
+                logit_scale=1.0):
         w_grad = None
         if master is not None:
             w_grad = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
         ce, z, n_valid, dh = _native().linear_ce(hidden, weight, weight_t, labels, ignore_index, chunk,
-                                                 hidden.requires_grad, z_coef, w_grad, smoothing, softcap)
+                                                 hidden.requires_grad, z_coef, w_grad, smoothing, softcap, logit_scale)
         ctx.save_for_backward(dh, w_grad)
         ctx.master = master
         ctx.mark_non_differentiable(n_valid)
@@ -433,7 +434,7 @@ class _LinearCeFn(torch.autograd.Function):
             if m.grad is None:
                 m.grad = torch.zeros_like(m, dtype=torch.float32)
             m.grad.addcmul_(w_grad, dloss.to(torch.float32))
-        return (dh * dloss.to(dh.dtype)) if dh is not None else None, None, None, None, None, None, None, None, None, None
+        return ((dh * dloss.to(dh.dtype)) if dh is not None else None,) + (None,) * 10
 
 
 def _head_pair(weight: torch.Tensor):
@@ -447,15 +448,16 @@ def _head_pair(weight: torch.Tensor):
 
 def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
                          chunk: int = 4096, weight_t: Optional[torch.Tensor] = None, softcap: float = 0.0,
-                         label_smoothing: float = 0.0):
+                         label_smoothing: float = 0.0, logit_scale: float = 1.0):
     """Returns (Σ loss over valid tokens, number of valid tokens). A frozen head, or a trainable fp32 head with a bf16
     shadow (full-parameter training), runs the chunked kernels; anything else the reference path. ``softcap`` c replaces
-    the logits by c tanh(x / c); ``label_smoothing`` e mixes the one-hot target with e / V."""
+    the logits by c tanh(x / c); ``label_smoothing`` e mixes the one-hot target with e / V; ``logit_scale`` multiplies the
+    logits before either."""
     w, master = _head_pair(weight)
     if use_native(hidden) and (master is not None or not weight.requires_grad):
         return _LinearCeFn.apply(hidden, w, weight_t if master is None else None, labels, ignore_index, chunk, 0.0, master,
-                                 float(label_smoothing), float(softcap))[:2]
-    return ref.linear_cross_entropy(hidden, weight, labels, ignore_index, chunk, softcap, label_smoothing)
+                                 float(label_smoothing), float(softcap), float(logit_scale))[:2]
+    return ref.linear_cross_entropy(hidden, weight, labels, ignore_index, chunk, softcap, label_smoothing, logit_scale)
 
 
 def linear_cross_entropy_z(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, z_coef: float,

@@ -734,17 +734,20 @@ def gemm_dw(dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor, rows: Optional
 
 
 def linear_ce(hidden, weight, weight_t, labels, ignore_index: int, chunk: int, need_grad: bool, z_coef: float = 0.0,
-              w_grad: Optional[torch.Tensor] = None, label_smoothing: float = 0.0, softcap: float = 0.0):
+              w_grad: Optional[torch.Tensor] = None, label_smoothing: float = 0.0, softcap: float = 0.0,
+              logit_scale: float = 1.0):
     """Chunked linear + cross-entropy. Logits of one token chunk live in a bf16 scratch buffer, are turned
     into their gradient in place, and feed the input-gradient GEMM; the [T, V] matrix never exists.
     ``z_coef`` adds ``z_coef * logsumexp(logits)^2`` per valid row to the differentiated sum (the second return value
     is the sum of the squared normalisers); ``w_grad`` (fp32 [V, H]) receives the gradient of the head weight;
-    ``label_smoothing`` mixes the target with the uniform distribution; ``softcap`` c turns logits into c tanh(x / c)."""
+    ``label_smoothing`` mixes the target with the uniform distribution; ``softcap`` c turns logits into c tanh(x / c);
+    ``logit_scale`` multiplies the logits first (inside the GEMM; the gradient picks the factor up on its way back)."""
     T, H = hidden.shape
     V = weight.shape[0]
     labels = labels.contiguous()
     n_valid = (labels != ignore_index).sum()
-    inv_n = torch.ones(1, dtype=torch.float32, device=hidden.device)   # gradient is of the *sum*; caller divides
+    # gradient is of the *sum* (the caller divides); d/d(h W^T) = logit_scale * d/d(logits)
+    inv_n = torch.full((1,), float(logit_scale), dtype=torch.float32, device=hidden.device)
     loss = torch.zeros(2, dtype=torch.float32, device=hidden.device)  # [cross entropy, squared normalisers]
     dh = torch.empty_like(hidden) if need_grad else None
     chunk = min(chunk, T)
@@ -755,7 +758,7 @@ def linear_ce(hidden, weight, weight_t, labels, ignore_index: int, chunk: int, n
     for s in range(0, T, chunk):
         n = min(chunk, T - s)
         h = hidden[s:s + n]
-        raw_gemm(h, 0, h.stride(0), n, weight, 0, weight.stride(0), V, scratch, 0, ldl, n, V, H, bn=bn)
+        raw_gemm(h, 0, h.stride(0), n, weight, 0, weight.stride(0), V, scratch, 0, ldl, n, V, H, bn=bn, alpha=logit_scale)
         if label_smoothing > 0.0 or softcap > 0.0:
             _chk(lib().pm_ce_opt_fwd_bwd(_p(scratch), c_ll(ldl), _p(labels[s:s + n]), _p(loss), _p(loss[1:]), _p(inv_n),
                                          c_int(n), c_int(V), c_ll(ignore_index), c_int(1 if grads else 0), c_float(z_coef),

@@ -106,7 +106,7 @@ def varlen_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
 
 def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
                          chunk: int = 4096, softcap: float = 0.0,
-                         label_smoothing: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
+                         label_smoothing: float = 0.0, logit_scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
     """Σ over valid tokens of (logsumexp(h Wᵀ) − (h Wᵀ)[label]) and the valid-token count; with ``label_smoothing`` e
     the target is (1 − e) one-hot + e / V.
 
@@ -118,7 +118,9 @@ def linear_cross_entropy(hidden: torch.Tensor, weight: torch.Tensor, labels: tor
     for s in range(0, hidden.shape[0], chunk):
         h = hidden[s:s + chunk]
         lab = labels[s:s + chunk]
-        logits = F.linear(h, weight).float()
+        logits = F.linear(h, weight.to(h.dtype)).float()
+        if logit_scale != 1.0:
+            logits = logits * logit_scale
         if softcap > 0:
             logits = softcap * torch.tanh(logits / softcap)
         total = total + F.cross_entropy(logits, lab, ignore_index=ignore_index, reduction="sum",

@@ -463,18 +463,19 @@ def test_linear_ce():
     nat.check_status()
 
 
-@pytest.mark.parametrize("smooth,cap", [(0.1, 0.0), (0.0, 30.0), (0.05, 20.0)])
-def test_linear_ce_label_smoothing_and_softcap(smooth, cap):
-    """The chunked loss with a smoothed target and with c tanh(x / c) logits against fp32 autograd (V not a multiple of 8)."""
+@pytest.mark.parametrize("smooth,cap,mul", [(0.1, 0.0, 1.0), (0.0, 30.0, 1.0), (0.05, 20.0, 1.0), (0.0, 0.0, 0.25), (0.0, 10.0, 0.5)])
+def test_linear_ce_label_smoothing_and_softcap(smooth, cap, mul):
+    """The chunked loss with a smoothed target, c tanh(x / c) logits and a factor on the logits against fp32 autograd
+    (V not a multiple of 8)."""
     nat = _nat()
     torch.manual_seed(18)
     T, H, V = 520, 256, 4003
     h, w = _rand(T, H, scale=3.0), _rand(V, H, scale=H ** -0.5)
     lab = torch.randint(0, V, (T,), device="cuda")
     lab[::5] = -100
-    loss, _, n, dh = nat.linear_ce(h, w, None, lab, -100, 256, True, 0.0, None, smooth, cap)
+    loss, _, n, dh = nat.linear_ce(h, w, None, lab, -100, 256, True, 0.0, None, smooth, cap, mul)
     hf = h.float().requires_grad_(True)
-    lg = hf @ w.float().t()
+    lg = (hf @ w.float().t()) * mul
     lg = lg + (lg.bfloat16().float() - lg).detach()          # the kernel reads bf16 logits
     if cap > 0:
         lg = cap * torch.tanh(lg / cap)
@@ -483,7 +484,7 @@ def test_linear_ce_label_smoothing_and_softcap(smooth, cap):
     assert abs(loss.item() - ref.item()) / ref.item() < 5e-3, (loss.item(), ref.item())
     _close(dh, hf.grad, rtol=3e-2, atol=3e-3, what="smoothed / capped linear_ce dh")
     from pmetal_b200.ops import functional as F
-    s2, n2 = F.linear_cross_entropy(h, w, lab, softcap=cap, label_smoothing=smooth)
+    s2, n2 = F.linear_cross_entropy(h, w, lab, softcap=cap, label_smoothing=smooth, logit_scale=mul)
     assert abs(s2.item() - ref.item()) / ref.item() < 5e-3 and int(n2) == int(n)
     nat.check_status()
 

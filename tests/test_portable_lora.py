@@ -184,3 +184,31 @@ def test_qblora_starts_at_the_base_and_balances_gradients():
     assert torch.allclose(ad.lora_a.grad, 0.5 * g1, atol=1e-6)
     fixed = P.QBLoraLinear(torch.nn.Linear(32, 24), 32, 24, 4, 1.0, 16, None, learnable_projections=False)
     assert len(fixed.trainable_parameters()) == 2 and fixed.p_in_fixed.shape == (32, 16)
+
+
+@pytest.mark.parametrize("family,extra", [("cohere", dict(logit_scale=0.25)), ("gemma2", dict(final_logit_softcapping=20.0)),
+                                          ("granite", dict(logits_scaling=4.0)), ("llama", {})])
+def test_trainer_loss_without_materialised_logits_matches_forward(family, extra):
+    """The fused read-out + cross entropy (logit scale, soft cap) equals the loss on the model's own logits, value and gradient."""
+    import torch
+    from pmetal_b200.lora import portable as P
+    from pmetal_b200.models.architectures.generic import GenericDecoderLM, arch_config_from_hf
+    cfg = dict(model_type=family, vocab_size=96, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=8, max_position_embeddings=64)
+    cfg.update(extra)
+    torch.manual_seed(0)
+    m = GenericDecoderLM(arch_config_from_hf(cfg)).init_weights(0.2, 0)
+    P.apply_lora_portable(m, LoraConfig(r=4, alpha=8.0, target_modules=["q_proj", "v_proj", "down_proj"]))
+    tr = P.PortableLoraTrainer(m, total_steps=4)
+    assert m.loss_head() is not None
+    ids = torch.randint(0, 96, (3, 17))
+    labels = ids.clone()
+    labels[:, :4] = -100
+    a = tr.loss(ids, labels)
+    ga = torch.autograd.grad(a, [p for p in m.parameters() if p.requires_grad], allow_unused=True)
+    b = P.causal_lm_loss(m(ids), labels)
+    gb = torch.autograd.grad(b, [p for p in m.parameters() if p.requires_grad], allow_unused=True)
+    assert abs(float(a) - float(b)) < 1e-5 * max(1.0, abs(float(b)))
+    for x, y in zip(ga, gb):
+        if x is not None:
+            assert torch.allclose(x, y, atol=1e-6, rtol=1e-4)
