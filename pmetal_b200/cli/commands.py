@@ -735,6 +735,10 @@ def cmd_serve(a) -> int:
         # one process per GPU: start this same command under the launcher
         from ..parallel.cluster_cli import _torchrun
         return _torchrun(ways, ["-m", "pmetal_b200.cli.main"] + sys.argv[1:])
+    from ..trainer.orchestrator import _portable_model_dir
+    pdir = _portable_model_dir(a.model) if world == 1 else None
+    if pdir is not None:
+        return _serve_portable(a, pdir)
     channel = None
     if world > 1:
         import torch
@@ -785,6 +789,43 @@ def cmd_serve(a) -> int:
         if world > 1:
             from ..parallel.dp import shutdown_process_group
             shutdown_process_group()
+    return 0
+
+
+def _serve_portable(a, model_dir: str) -> int:
+    """``serve`` for the config-driven architectures: same HTTP routes, requests interleaved token by token on the models'
+    own contiguous caches (serve/portable_engine.py)."""
+    import torch
+
+    from ..data.chat_templates import ChatTemplate
+    from ..data.inference_config import collect_all_stop_tokens
+    from ..data.tokenizer import Tokenizer
+    from ..models.architectures import load_pretrained as load_portable
+    from ..serve.portable_engine import PortableEngine
+    from ..serve.server import serve
+    if a.tp > 1 or a.ep or a.adapter:
+        print("error: --tp / --ep / --adapter serve the llama / qwen family only", file=sys.stderr)
+        return 2
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    model = load_portable(model_dir, torch.bfloat16 if dev.startswith("cuda") else torch.float32, dev).eval()
+    for p in model.parameters():
+        p.requires_grad_(False)
+    lora = getattr(a, "lora", None)
+    if lora:
+        from ..lora.adapter import load_adapter_config
+        from ..lora.portable import apply_lora_portable, load_adapter_portable, merge_lora_portable
+        apply_lora_portable(model, load_adapter_config(lora))
+        load_adapter_portable(model, lora)
+        merge_lora_portable(model)
+    tok = Tokenizer.from_model_dir(model_dir)
+    tpl = ChatTemplate.from_model_dir(model_dir)
+    eos = collect_all_stop_tokens(model_dir, tok, tpl.eos())
+    opts = {}
+    if getattr(a, "kv_turboquant", False) or getattr(a, "kv_quant", None):
+        bits = 4 if getattr(a, "kv_turboquant", False) else (a.kv_quant if isinstance(a.kv_quant, int) and a.kv_quant > 0 else 8)
+        opts = dict(kv_bits=bits, turbo=bool(getattr(a, "kv_turboquant", False)))
+    engine = PortableEngine(model, eos, max_slots=min(a.max_slots, 16), max_queue=a.cb_max_queue_depth, cache_options=opts)
+    serve(model, tok, tpl, a.host, a.port, eos, os.path.basename(os.path.normpath(model_dir)), engine=engine)
     return 0
 
 

@@ -304,9 +304,12 @@ def create_app(state: ServerState):
             x = torch.tensor(ids, dtype=torch.int64, device=state.engine.device)
             T = x.numel()
             with torch.no_grad():
-                h = model.forward_hidden(x, torch.arange(T, dtype=torch.int32, device=x.device),
-                                         torch.tensor([0, T], dtype=torch.int32, device=x.device),
-                                         torch.zeros(T, dtype=torch.int32, device=x.device))
+                if hasattr(state.engine, "gen"):       # fast decoder: flat token batch with positions and document starts
+                    h = model.forward_hidden(x, torch.arange(T, dtype=torch.int32, device=x.device),
+                                             torch.tensor([0, T], dtype=torch.int32, device=x.device),
+                                             torch.zeros(T, dtype=torch.int32, device=x.device))
+                else:                                  # config-driven architectures take [batch, tokens]
+                    h = model.forward_hidden(x[None])[0]
             e = torch.nn.functional.normalize(h.float().mean(0), dim=0)
             out.append({"object": "embedding", "index": i, "embedding": e.tolist()})
         return {"object": "list", "data": out, "model": state.model_name, "usage": {"prompt_tokens": total, "total_tokens": total}}
@@ -368,13 +371,15 @@ def create_app(state: ServerState):
 
 def serve(model, tokenizer, template=None, host: str = "127.0.0.1", port: int = 8080, eos_ids=(), model_name="pmetal-b200",
           max_slots: int = 64, num_blocks: int = 8192, max_queue: int = 1024, cache_options: Optional[dict] = None,
-          channel=None, adapters=None):
+          channel=None, adapters=None, engine=None):
     """Blocking: starts the engine thread and the HTTP server. ``cache_options`` (quant / window / sink) go to
     ``DecoderLM.new_cache``. With a model cut over several ranks, ``channel`` (serve/replica.py) is the leader's end of
-    the step channel: the ranks that follow are released when the server stops."""
+    the step channel: the ranks that follow are released when the server stops. ``engine`` replaces the paged
+    continuous-batching engine (``serve/portable_engine.py`` for the config-driven architectures)."""
     import uvicorn
-    engine = ContinuousBatchEngine(model, eos_ids, max_slots=max_slots, num_blocks=num_blocks, max_queue=max_queue,
-                                   cache_options=cache_options, adapters=adapters)
+    if engine is None:
+        engine = ContinuousBatchEngine(model, eos_ids, max_slots=max_slots, num_blocks=num_blocks, max_queue=max_queue,
+                                       cache_options=cache_options, adapters=adapters)
     engine.start()
     try:
         uvicorn.run(create_app(ServerState(engine, tokenizer, template, model_name)), host=host, port=port, log_level="info")

@@ -212,3 +212,47 @@ def test_trainer_loss_without_materialised_logits_matches_forward(family, extra)
     for x, y in zip(ga, gb):
         if x is not None:
             assert torch.allclose(x, y, atol=1e-6, rtol=1e-4)
+
+
+def test_serve_command_answers_http_for_a_portable_family(tmp_path):
+    """``serve -m <gemma directory>`` picks the sequential engine and answers the OpenAI routes."""
+    import signal
+    import subprocess
+    import sys
+    import time
+    import urllib.request
+    d = _tiny_gemma_dir(tmp_path)
+    port = 18437
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.Popen([sys.executable, "-m", "pmetal_b200.cli.main", "serve", "-m", d, "--device", "cpu", "--port", str(port),
+                          "--max-slots", "4"], cwd=root, start_new_session=True, stdout=subprocess.PIPE,
+                         stderr=subprocess.STDOUT, text=True)
+    try:
+        up = False
+        for _ in range(240):
+            try:
+                urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1).read()
+                up = True
+                break
+            except Exception:
+                if p.poll() is not None:
+                    break
+                time.sleep(0.5)
+        assert up, "server did not come up: " + (p.stdout.read()[-2000:] if p.poll() is not None else "")
+        outs = []
+        for _ in range(2):
+            req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions",
+                                         data=json.dumps({"prompt": "hello", "max_tokens": 6, "temperature": 0}).encode(),
+                                         headers={"Content-Type": "application/json"})
+            outs.append(json.loads(urllib.request.urlopen(req, timeout=120).read()))
+        assert outs[0]["usage"]["completion_tokens"] <= 6 and outs[0]["usage"]["prompt_tokens"] >= 5
+        assert outs[0]["choices"][0]["text"] == outs[1]["choices"][0]["text"]
+        models = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=10).read())
+        assert models["data"][0]["id"] == "gemma"
+    finally:
+        os.killpg(p.pid, signal.SIGINT)
+        try:
+            p.communicate(timeout=60)
+        except subprocess.TimeoutExpired:
+            os.killpg(p.pid, signal.SIGKILL)
+            p.communicate()
