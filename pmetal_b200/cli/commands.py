@@ -1153,16 +1153,80 @@ def _grpo_args(sp):
     return p
 
 
+def _grpo_portable(a, model_dir: str, lcfg) -> int:
+    """``grpo`` on a config-driven architecture: portable LoRA adapters, rollouts on the model's own cache
+    (trainer/grpo_portable.py). Reward models, teachers and --resume belong to the llama / qwen path."""
+    import random
+
+    import torch
+
+    from ..data.chat_templates import ChatTemplate
+    from ..data.inference_config import collect_all_stop_tokens
+    from ..data.tokenizer import Tokenizer
+    from ..lora.portable import apply_lora_portable, save_adapter_portable
+    from ..models.architectures import load_pretrained as load_portable
+    from ..trainer.grpo import GrpoConfig
+    from ..trainer.grpo_portable import PortableGrpoTrainer
+    from ..trainer.rewards import make_reward
+    if a.reward_model or (a.teacher and a.rlkd_alpha > 0):
+        print("error: --reward-model / --teacher are available for the llama / qwen family only", file=sys.stderr)
+        return 2
+    dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    model = load_portable(model_dir, torch.bfloat16 if dev.startswith("cuda") else torch.float32, dev)
+    apply_lora_portable(model, lcfg)
+    model.train()
+    tok = Tokenizer.from_model_dir(model_dir)
+    eos = collect_all_stop_tokens(model_dir, tok, ChatTemplate.from_model_dir(model_dir).eos())
+    kw = dict(num_generations=a.num_generations, beta=a.beta, max_completion_length=a.max_completion_length,
+              max_prompt_length=a.max_prompt_length, learning_rate=a.learning_rate)
+    cfg = GrpoConfig.dapo(**kw) if a.dapo else GrpoConfig(**kw)
+    reward = make_reward(a.reward, tok)
+    if a.reasoning_rewards:
+        from ..trainer.rewards import combined_reward
+        reward = combined_reward([make_reward("format", tok), make_reward("accuracy", tok, _read_targets(a.dataset))], [1.0, 1.0])
+    tr = PortableGrpoTrainer(model, cfg, reward, eos_ids=eos, pad_id=tok.pad_token_id or 0)
+    keys = ((a.prompt_column,) if a.prompt_column else ()) + ("prompt", "question", "text", "instruction")
+    prompts = _read_prompts(a.dataset, tok, key_order=keys)
+    if not prompts:
+        print("error: no prompts in dataset", file=sys.stderr)
+        return 2
+    random.Random(a.seed).shuffle(prompts)
+    steps = a.max_steps if a.max_steps is not None else a.epochs * (-(-len(prompts) // a.prompts_per_step))
+    log = open(a.log_metrics, "a", encoding="utf-8") if a.log_metrics else None
+    try:
+        for step in range(steps):
+            batch = [prompts[(step * a.prompts_per_step + j) % len(prompts)] for j in range(a.prompts_per_step)]
+            d = tr.step(batch).__dict__
+            line = json.dumps({"step": step + 1, **{k: (round(v, 5) if isinstance(v, float) else v) for k, v in d.items()
+                                                    if isinstance(v, (int, float, str, bool))}})
+            print(line, file=sys.stderr)
+            if log:
+                log.write(line + "\n")
+                log.flush()
+            if a.checkpoint_every and (step + 1) % a.checkpoint_every == 0:
+                save_adapter_portable(model, os.path.join(a.output, "checkpoints", f"step_{step + 1}"), lcfg, a.model)
+    finally:
+        if log:
+            log.close()
+    save_adapter_portable(model, a.output, lcfg, a.model)
+    print(json.dumps({"output": a.output, "steps": steps, "path": "portable"}))
+    return 0
+
+
 @_command(_grpo_args)
 def cmd_grpo(a) -> int:
     from ..core.config import LoraConfig
     from ..lora import apply_lora
     from ..lora.adapter import save_adapter
     from ..trainer.grpo import GrpoConfig, GrpoTrainer
+    from ..trainer.orchestrator import _portable_model_dir
     from ..trainer.rewards import make_reward
+    lcfg = LoraConfig(r=a.lora_r, alpha=a.lora_alpha if getattr(a, 'lora_alpha', None) else 2.0 * a.lora_r)
+    pdir = _portable_model_dir(a.model)
+    if pdir is not None:
+        return _grpo_portable(a, pdir, lcfg)
     model, tok, _, eos, _ = _load_for_inference(a)
     dev = str(model.embed_tokens.device)
-    lcfg = LoraConfig(r=a.lora_r, alpha=a.lora_alpha if getattr(a, 'lora_alpha', None) else 2.0 * a.lora_r)
     apply_lora(model, lcfg)
     model.to(dev).train()
     kw = dict(num_generations=a.num_generations, beta=a.beta, max_completion_length=a.max_completion_length,

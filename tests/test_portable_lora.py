@@ -256,3 +256,44 @@ def test_serve_command_answers_http_for_a_portable_family(tmp_path):
         except subprocess.TimeoutExpired:
             os.killpg(p.pid, signal.SIGKILL)
             p.communicate()
+
+
+def test_grpo_on_a_portable_family_updates_the_adapters_and_keeps_the_reference(tmp_path, capsys):
+    import math
+    from pmetal_b200.lora.portable import lora_modules
+    from pmetal_b200.trainer.grpo import GrpoConfig, mod7_length_reward
+    from pmetal_b200.trainer.grpo_portable import PortableGrpoTrainer
+    d = _tiny_gemma_dir(tmp_path)
+    model = load_pretrained(d, torch.float32)
+    P.apply_lora_portable(model, LoraConfig(r=4, alpha=8.0, target_modules=["q_proj", "v_proj", "down_proj"]))
+    with torch.no_grad():
+        for m in lora_modules(model).values():
+            m.lora_b.normal_(0, 0.05)
+    cfg = GrpoConfig(num_generations=4, max_completion_length=6, beta=0.05, learning_rate=1e-2, top_k=0, top_p=1.0)
+    tr = PortableGrpoTrainer(model, cfg, mod7_length_reward, eos_ids=[257], pad_id=256, logprob_batch=5)
+    prompts = [torch.randint(0, 256, (7,)).tolist() for _ in range(3)]
+    before = {k: m.lora_b.detach().clone() for k, m in lora_modules(model).items()}
+    base_w = {k: m.base.weight.detach().clone() for k, m in lora_modules(model).items()}
+    st = tr.step(prompts)
+    assert math.isfinite(st.loss) and 0 < st.completion_tokens <= 3 * 4 * 6 and st.kl >= 0.0
+    assert any(not torch.equal(before[k], m.lora_b) for k, m in lora_modules(model).items())
+    assert all(torch.equal(base_w[k], m.base.weight) for k, m in lora_modules(model).items())
+    # reference log-probabilities are those of the base model: the adapters are switched off and back on
+    seqs, plens = [prompts[0] + [5, 6, 7]], [len(prompts[0])]
+    ref_lp, _ = tr._completion_logps(tr.ref, seqs, plens, grad=False)
+    scales = [m.scale for m in lora_modules(model).values()]
+    assert all(s != 0.0 for s in scales)
+    plain = load_pretrained(d, torch.float32).eval()
+    with torch.no_grad():
+        lg = plain(torch.tensor(seqs))[0]
+    want = torch.log_softmax(lg[len(prompts[0]) - 1:-1].float(), -1).gather(-1, torch.tensor([5, 6, 7])[:, None])[:, 0]
+    assert torch.allclose(ref_lp, want, atol=1e-5)
+    # the command takes the same path for a portable model directory
+    from pmetal_b200.cli.main import main
+    data = tmp_path / "p.jsonl"
+    data.write_text("\\n".join(json.dumps({"prompt": f"question {i}"}) for i in range(3)))
+    out = str(tmp_path / "grpo")
+    assert main(["grpo", "-m", d, "-d", str(data), "-o", out, "--max-steps", "1", "--num-generations", "2",
+                 "--max-completion-length", "4", "--lora-r", "4", "--device", "cpu", "--reward", "length"]) == 0
+    assert os.path.exists(os.path.join(out, "adapter_config.json"))
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["path"] == "portable"
