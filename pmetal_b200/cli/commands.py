@@ -1021,14 +1021,32 @@ def cmd_distill(a) -> int:
 
     from ..distill.trainer import DistillConfig, DistillTrainer
     from ..models.loader import load_pretrained, save_pretrained
+    from ..trainer.orchestrator import _portable_model_dir
     a.model = a.student
-    student, tok, _, _, sdir = _load_for_inference(a)
-    dev = str(student.embed_tokens.device)
-    teacher, _, _ = load_pretrained(a.teacher, dtype=next(student.parameters()).dtype, device=dev)
+    s_pdir, t_pdir = _portable_model_dir(a.student), _portable_model_dir(a.teacher)
+    if s_pdir is not None:
+        # student from the config-driven architectures: portable adapters (or all weights), its own tokenizer
+        from ..data.tokenizer import Tokenizer
+        from ..models.architectures import load_pretrained as load_portable
+        dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+        student = load_portable(s_pdir, torch.bfloat16 if dev.startswith("cuda") else torch.float32, dev)
+        tok, sdir = Tokenizer.from_model_dir(s_pdir), s_pdir
+    else:
+        student, tok, _, _, sdir = _load_for_inference(a)
+        dev = str(student.embed_tokens.device)
+    if t_pdir is not None:
+        from ..models.architectures import load_pretrained as load_portable
+        teacher = load_portable(t_pdir, next(student.parameters()).dtype, dev)
+    else:
+        teacher, _, _ = load_pretrained(a.teacher, dtype=next(student.parameters()).dtype, device=dev)
     teacher.eval()
     for p in teacher.parameters():
         p.requires_grad_(False)
-    if a.lora_r > 0:
+    if a.lora_r > 0 and s_pdir is not None:
+        from ..core.config import LoraConfig
+        from ..lora.portable import apply_lora_portable
+        apply_lora_portable(student, LoraConfig(r=a.lora_r, alpha=a.lora_alpha or 2.0 * a.lora_r))
+    elif a.lora_r > 0:
         from ..core.config import LoraConfig
         from ..lora import apply_lora
         apply_lora(student, LoraConfig(r=a.lora_r, alpha=a.lora_alpha or 2.0 * a.lora_r))
@@ -1067,8 +1085,11 @@ def cmd_distill(a) -> int:
         lcfg = LoraConfig(r=a.lora_r, alpha=a.lora_alpha or 2.0 * a.lora_r)
     ckpt_dir = os.path.join(a.output, "checkpoints")
     first = 0
+    if s_pdir is not None:
+        from ..lora.portable import load_adapter_portable as load_adapter, save_adapter_portable as save_adapter
+    else:
+        from ..lora.adapter import load_adapter, save_adapter
     if a.resume and lcfg is not None and os.path.isdir(ckpt_dir):
-        from ..lora.adapter import load_adapter
         done = sorted(int(d.split("_")[1]) for d in os.listdir(ckpt_dir) if d.startswith("step_") and d.split("_")[1].isdigit())
         if done:
             load_adapter(student, os.path.join(ckpt_dir, f"step_{done[-1]}"))
@@ -1090,7 +1111,6 @@ def cmd_distill(a) -> int:
             if step % 10 == 0:
                 print(line, file=sys.stderr)
             if a.checkpoint_every and lcfg is not None and (step + 1) % a.checkpoint_every == 0:
-                from ..lora.adapter import save_adapter
                 save_adapter(student, os.path.join(ckpt_dir, f"step_{step + 1}"), lcfg, a.student)
     finally:
         if log:
@@ -1110,8 +1130,10 @@ def cmd_distill(a) -> int:
         extra["eval_samples"] = len(ev)
     os.makedirs(a.output, exist_ok=True)
     if lcfg is not None:
-        from ..lora.adapter import save_adapter
         save_adapter(student, a.output, lcfg, a.student)
+    elif s_pdir is not None:
+        from ..models.architectures import save_pretrained as save_portable
+        save_portable(student, a.output, copy_from=sdir)
     else:
         save_pretrained(student, a.output, copy_from=sdir)
     print(json.dumps({"output": a.output, "steps": steps, "resumed_from": first, **last, **extra}))

@@ -41,8 +41,8 @@ class DistillTrainer:
     def __init__(self, student, teacher, cfg: DistillConfig, optimizer=None, taid: Optional[TaidConfig] = None):
         from ..trainer.optimizer import FlatAdamW, attach_shadows
         self.student, self.teacher, self.cfg = student, teacher, cfg
-        self.device = student.embed_tokens.device
-        shadow = torch.bfloat16 if self.device.type == "cuda" else None
+        self.device = next(student.parameters()).device
+        shadow = torch.bfloat16 if (self.device.type == "cuda" and self._fast(student)) else None
         self.opt = optimizer or FlatAdamW(student.named_parameters(), lr=cfg.learning_rate, weight_decay=0.0,
                                           max_grad_norm=cfg.max_grad_norm, shadow_dtype=shadow)
         if shadow is not None:
@@ -58,12 +58,25 @@ class DistillTrainer:
         p = min(self.step_count / max(c.total_steps, 1), 1.0)
         return c.temperature + (c.final_temperature - c.temperature) * p
 
+    @staticmethod
+    def _fast(model) -> bool:
+        """The hand-written decoder (flat token batches, ``head_weight``); everything else is a config-driven architecture
+        that takes [batch, tokens] and applies its own read-out (logit scale, soft cap) in ``logits``."""
+        return hasattr(model, "head_weight") and hasattr(model, "fused_linears")
+
     def _hidden(self, model, ids, grad):
         T = ids.numel()
-        pos = torch.arange(T, dtype=torch.int32, device=ids.device)
-        cu = torch.tensor([0, T], dtype=torch.int32, device=ids.device)
         with (torch.enable_grad() if grad else torch.no_grad()):
+            if not self._fast(model):
+                return model.forward_hidden(ids.reshape(1, -1))[0]
+            pos = torch.arange(T, dtype=torch.int32, device=ids.device)
+            cu = torch.tensor([0, T], dtype=torch.int32, device=ids.device)
             return model.forward_hidden(ids.reshape(-1), pos, cu, torch.zeros(T, dtype=torch.int32, device=ids.device))
+
+    def _logits(self, model, h):
+        if self._fast(model):
+            return h.float() @ model.head_weight().float().t()
+        return model.logits(h).float()
 
     def loss(self, input_ids: torch.Tensor, labels: torch.Tensor, seq_id: Optional[int] = None):
         """One sequence [T] (callers pack or loop). Labels -100 are ignored; position t predicts labels[t+1]."""
@@ -72,34 +85,39 @@ class DistillTrainer:
         hs = self._hidden(self.student, input_ids, True)[:-1]
         tgt = labels.reshape(-1)[1:]
         mask = tgt != -100
-        ws = self.student.head_weight()
+        both_fast = self._fast(self.student) and self._fast(self.teacher)
+        ws = self.student.head_weight() if self._fast(self.student) else None
         stats = {}
         if self.cache is not None and seq_id is not None and self.cache.has_sequence(seq_id):
             t_logits = self.cache.load_sequence(seq_id).to(self.device)[:-1]
-            s_logits = hs.float() @ ws.float().t()
-            soft = L.LOSSES[c.loss_type](s_logits, t_logits, T, mask)
+            soft = L.LOSSES[c.loss_type](self._logits(self.student, hs), t_logits, T, mask)
         else:
             ht = self._hidden(self.teacher, input_ids, False)[:-1]
-            wt = self.teacher.head_weight()
             if c.rationale:
                 tw = None
                 if c.reasoning_markers is not None:
                     span = L.reasoning_mask(input_ids.reshape(-1), *c.reasoning_markers)[1:]
                     tw = span if bool(span.any()) else None
-                soft = L.rationale_kl(hs.float() @ ws.float().t(), ht.float() @ wt.float().t(), T, mask, c.rationale_weight, tw)
+                soft = L.rationale_kl(self._logits(self.student, hs), self._logits(self.teacher, ht), T, mask,
+                                      c.rationale_weight, tw)
             elif self.taid is not None:
-                s_logits = (hs.float() @ ws.float().t()).unsqueeze(0)
-                t_logits = (ht.float() @ wt.float().t()).unsqueeze(0)
+                s_logits = self._logits(self.student, hs).unsqueeze(0)
+                t_logits = self._logits(self.teacher, ht).unsqueeze(0)
                 soft, a = self.taid.loss(t_logits, s_logits, self.step_count, c.total_steps, mask=mask.unsqueeze(0))
                 stats["taid_alpha"] = a
-            elif c.loss_type in ("kl", "forward_kl", "reverse_kl", "js", "jsd", "soft_ce", "tvd"):
-                soft = L.fused_kd_loss(hs, ws, ht, wt, mask, T, c.loss_type, 0.5, c.chunk)
+            elif both_fast and c.loss_type in ("kl", "forward_kl", "reverse_kl", "js", "jsd", "soft_ce", "tvd"):
+                soft = L.fused_kd_loss(hs, ws, ht, self.teacher.head_weight(), mask, T, c.loss_type, 0.5, c.chunk)
             else:
-                soft = L.LOSSES[c.loss_type](hs.float() @ ws.float().t(), ht.float() @ wt.float().t(), T, mask)
+                soft = L.LOSSES[c.loss_type](self._logits(self.student, hs), self._logits(self.teacher, ht), T, mask)
             if c.hidden_loss_weight > 0 and hs.shape[-1] == ht.shape[-1]:
                 soft = soft + c.hidden_loss_weight * L.hidden_state_loss(hs, ht, c.hidden_loss_kind, mask=mask)
         from ..ops import functional as ops
-        hard = ops.causal_lm_loss(hs, ws, tgt) if mask.any() else hs.sum() * 0
+        if not mask.any():
+            hard = hs.sum() * 0
+        elif ws is not None:
+            hard = ops.causal_lm_loss(hs, ws, tgt)
+        else:
+            hard = torch.nn.functional.cross_entropy(self._logits(self.student, hs), tgt, ignore_index=-100)
         total = c.alpha * soft + (1 - c.alpha) * hard
         stats.update(soft=float(soft.detach()), hard=float(hard.detach()), temperature=T)
         return total, stats
@@ -119,6 +137,6 @@ class DistillTrainer:
         for i, ids in enumerate(sequences):
             ids = torch.as_tensor(ids, dtype=torch.int64, device=self.device)
             h = self._hidden(self.teacher, ids, False)
-            cache.cache_sequence(i, h.float() @ self.teacher.head_weight().float().t())
+            cache.cache_sequence(i, self._logits(self.teacher, h))
         cache.save_metadata()
         return cache

@@ -97,3 +97,28 @@ def load_pretrained(model_dir: str, dtype=None, device=None):
     else:
         model.load_state_dict(sd, strict=False)
     return model
+
+
+def save_pretrained(model, out_dir: str, copy_from: str) -> None:
+    """Write the weights of a config-driven model next to the configuration and tokenizer files of ``copy_from`` (the
+    directory it was loaded from): parameter names are the checkpoint's own, so the result loads with ``load_pretrained``
+    here and with the Hugging Face classes. Tied read-outs are stored once."""
+    import shutil
+
+    from safetensors.torch import save_file
+    os.makedirs(out_dir, exist_ok=True)
+    sd, seen = {}, {}
+    for k, v in model.state_dict().items():
+        t = v.detach()
+        key = (t.data_ptr(), tuple(t.shape))
+        if key in seen:                                    # shared storage (tied embeddings): keep the first name
+            continue
+        seen[key] = k
+        sd[k] = t.cpu().contiguous()
+    save_file(sd, os.path.join(out_dir, "model.safetensors"), metadata={"format": "pt"})
+    for f in os.listdir(copy_from):
+        if f.endswith(".safetensors") or f.endswith(".safetensors.index.json") or f.endswith(".bin"):
+            continue
+        src = os.path.join(copy_from, f)
+        if os.path.isfile(src):
+            shutil.copy2(src, os.path.join(out_dir, f))

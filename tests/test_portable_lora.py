@@ -297,3 +297,28 @@ def test_grpo_on_a_portable_family_updates_the_adapters_and_keeps_the_reference(
                  "--max-completion-length", "4", "--lora-r", "4", "--device", "cpu", "--reward", "length"]) == 0
     assert os.path.exists(os.path.join(out, "adapter_config.json"))
     assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["path"] == "portable"
+
+
+def test_distill_command_with_portable_student_and_teacher(tmp_path, capsys):
+    """``distill`` between config-driven models: LoRA student (adapter written in the portable format) and full-parameter
+    student (a loadable model directory)."""
+    from pmetal_b200.cli.main import main
+    d = _tiny_gemma_dir(tmp_path)
+    data = tmp_path / "p.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"question {i} about things"}) for i in range(4)))
+    out = str(tmp_path / "kd")
+    assert main(["distill", "--teacher", d, "--student", d, "-d", str(data), "-o", out, "--max-steps", "2", "--lora-r", "4",
+                 "--device", "cpu"]) == 0
+    j = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert j["steps"] == 2 and os.path.exists(os.path.join(out, "lora_weights.safetensors"))
+    m = load_pretrained(d, torch.float32)
+    P.apply_lora_portable(m, P.load_adapter_config(out) if hasattr(P, "load_adapter_config") else LoraConfig(r=4, alpha=8.0))
+    assert P.load_adapter_portable(m, out) > 0
+    out2 = str(tmp_path / "kd_full")
+    assert main(["distill", "--teacher", d, "--student", d, "-d", str(data), "-o", out2, "--max-steps", "2", "--lora-r", "0",
+                 "--device", "cpu", "--loss-type", "reverse_kl", "--learning-rate", "1e-3"]) == 0
+    tuned = load_pretrained(out2, torch.float32).eval()
+    base = load_pretrained(d, torch.float32).eval()
+    ids = torch.randint(0, 256, (1, 9))
+    with torch.no_grad():
+        assert not torch.allclose(tuned(ids), base(ids))          # the weights moved and the directory loads
