@@ -62,12 +62,59 @@ class LoraLinear(nn.Module):
         return w.to(self.base.weight.dtype)
 
 
+class QuantLinear(nn.Module):
+    """A frozen projection whose weight is stored as 4-bit (NF4 / FP4) or int8 blocks and expanded into a transient
+    matrix of the activation's type at every use: the QLoRA base for the config-driven architectures
+    (crates/pmetal-lora/src/qlora.rs:33-480). It offers what ``LoraLinear`` asks of its base: ``weight`` (dequantised on
+    access), ``bias``, ``in_features`` / ``out_features`` and a forward."""
+
+    def __init__(self, linear: nn.Linear, scheme: str = "nf4", block_size: int = 64, double_quant: bool = False):
+        super().__init__()
+        from .nf4 import quantize
+        self.in_features, self.out_features = linear.in_features, linear.out_features
+        self.dtype = linear.weight.dtype
+        q = quantize(linear.weight.detach(), scheme, block_size, double_quant)
+        self.qweight = q.to(linear.weight.device) if q.data.device != linear.weight.device else q
+        self.bias = None if linear.bias is None else nn.Parameter(linear.bias.detach().clone(), requires_grad=False)
+
+    @property
+    def weight(self) -> torch.Tensor:
+        from .qlora import dequantize_weight
+        return dequantize_weight(self.qweight, self.dtype)
+
+    def forward(self, x):
+        return F.linear(x, self.weight.to(x.dtype), self.bias)
+
+    def _apply(self, fn, recurse=True):            # .to(device) / .cuda() move the packed blocks too
+        super()._apply(fn, recurse)
+        probe = fn(torch.empty(0, device=self.qweight.data.device))
+        if probe.device != self.qweight.data.device:
+            self.qweight = self.qweight.to(probe.device)
+        return self
+
+
+@torch.no_grad()
+def quantize_base_portable(model: nn.Module, scheme: str = "nf4", block_size: int = 64, double_quant: bool = False,
+                           skip: Iterable[str] = ("lm_head", "embed_tokens", "router", "gate")) -> int:
+    """Replace every ``nn.Linear`` of the decoder blocks by a :class:`QuantLinear`; read-out, embeddings and routers keep
+    their precision. Call before ``apply_lora_portable``. Returns the bytes saved."""
+    skip = set(skip)
+    saved = 0
+    for full, mod in list(model.named_modules()):
+        for name, child in list(mod.named_children()):
+            if type(child).__name__ in ("Linear",) and isinstance(child, nn.Linear) and name not in skip:
+                q = QuantLinear(child, scheme, block_size, double_quant)
+                saved += child.weight.numel() * child.weight.element_size() - q.qweight.nbytes()
+                setattr(mod, name, q)
+    return saved
+
+
 def _targets(model: nn.Module, names: Iterable[str]) -> List[Tuple[nn.Module, str, str]]:
     want = set(names)
     out = []
     for full, mod in model.named_modules():
         for child_name, child in mod.named_children():
-            if isinstance(child, nn.Linear) and child_name in want:
+            if isinstance(child, (nn.Linear, QuantLinear)) and child_name in want:
                 out.append((mod, child_name, f"{full}.{child_name}" if full else child_name))
     return out
 
@@ -140,8 +187,16 @@ def merge_lora_portable(model: nn.Module) -> nn.Module:
     for full, mod in list(model.named_modules()):
         for name, child in list(mod.named_children()):
             if isinstance(child, LoraLinear):
-                child.base.weight.data.copy_(child.merged_weight())
-                setattr(mod, name, child.base)
+                w = child.merged_weight()
+                base = child.base
+                if isinstance(base, QuantLinear):          # a packed base comes back as a plain matrix of its original type
+                    lin = nn.Linear(base.in_features, base.out_features, bias=base.bias is not None, device=w.device, dtype=w.dtype)
+                    if base.bias is not None:
+                        lin.bias.data.copy_(base.bias)
+                    lin.requires_grad_(False)
+                    base = lin
+                base.weight.data.copy_(w)
+                setattr(mod, name, base)
     return model
 
 

@@ -102,10 +102,12 @@ def _run_portable_training(job: "TrainingJobConfig", model_dir: str, dev, dtype,
     from ..lora.portable import PortableLoraTrainer, apply_lora_portable, load_adapter_portable, save_adapter_portable
     from ..models.architectures import load_pretrained as load_portable
     tcfg = job.training
-    if job.quantization != "none":
-        raise ValueError("quantised base weights (QLoRA) are available for the llama / qwen / mistral family only")
     phase("loading_model")
     model = load_portable(model_dir, dtype, dev)
+    if job.quantization != "none":                  # QLoRA: the block projections are stored packed, adapters stay in full precision
+        from ..lora.portable import quantize_base_portable
+        saved = quantize_base_portable(model, job.quantization, job.quant_block_size, job.double_quant)
+        log.info("base projections stored as %s: %.1f MiB saved", job.quantization, saved / 2 ** 20)
     phase("loading_tokenizer")
     tok = Tokenizer.from_model_dir(model_dir)
     template = ChatTemplate.from_model_dir(model_dir, job.model)

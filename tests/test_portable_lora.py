@@ -291,7 +291,7 @@ def test_grpo_on_a_portable_family_updates_the_adapters_and_keeps_the_reference(
     # the command takes the same path for a portable model directory
     from pmetal_b200.cli.main import main
     data = tmp_path / "p.jsonl"
-    data.write_text("\\n".join(json.dumps({"prompt": f"question {i}"}) for i in range(3)))
+    data.write_text("\n".join(json.dumps({"prompt": f"question {i}"}) for i in range(3)))
     out = str(tmp_path / "grpo")
     assert main(["grpo", "-m", d, "-d", str(data), "-o", out, "--max-steps", "1", "--num-generations", "2",
                  "--max-completion-length", "4", "--lora-r", "4", "--device", "cpu", "--reward", "length"]) == 0
@@ -322,3 +322,37 @@ def test_distill_command_with_portable_student_and_teacher(tmp_path, capsys):
     ids = torch.randint(0, 256, (1, 9))
     with torch.no_grad():
         assert not torch.allclose(tuned(ids), base(ids))          # the weights moved and the directory loads
+
+
+def test_qlora_on_a_portable_family(tmp_path, capsys):
+    """Packed base projections: close to the full-precision model, adapters train, merging gives plain matrices back, and
+    ``train --quantization nf4`` runs the whole path for a Gemma directory."""
+    from pmetal_b200.lora.portable import QuantLinear, quantize_base_portable
+    d = _tiny_gemma_dir(tmp_path)
+    full = load_pretrained(d, torch.float32).eval()
+    model = load_pretrained(d, torch.float32)
+    saved = quantize_base_portable(model, "nf4", 64, double_quant=True)
+    packed = [m for m in model.modules() if isinstance(m, QuantLinear)]
+    assert saved > 0 and len(packed) == 2 * 7 and not isinstance(model.lm_head if hasattr(model, "lm_head") else None, QuantLinear)
+    ids = torch.randint(0, 256, (2, 11), generator=torch.Generator().manual_seed(3))
+    with torch.no_grad():
+        a, b = full(ids), model.eval()(ids)
+    assert (a - b).norm() / a.norm() < 0.35                      # 4-bit weights of a random tiny model: close, not equal
+    P.apply_lora_portable(model, LoraConfig(r=4, alpha=8.0, target_modules=["q_proj", "v_proj", "down_proj"]))
+    assert all(isinstance(m.base, QuantLinear) for m in P.lora_modules(model).values())
+    tr = P.PortableLoraTrainer(model.train(), learning_rate=2e-2, total_steps=30)
+    losses = [tr.step(ids, ids.clone())["loss"] for _ in range(30)]
+    assert losses[-1] < 0.97 * losses[0]
+    with torch.no_grad():
+        tuned = model.eval()(ids)
+    P.merge_lora_portable(model)
+    assert not P.lora_modules(model)
+    with torch.no_grad():
+        assert torch.allclose(model(ids), tuned, atol=1e-4)
+    from pmetal_b200.cli.main import main
+    data = tmp_path / "t.jsonl"
+    data.write_text("".join(json.dumps({"text": "hello world " * 6}) + "\n" for _ in range(8)))
+    out = str(tmp_path / "qlora")
+    assert main(["train", "--model", d, "--dataset", str(data), "--output", out, "--max-steps", "2", "--lora-r", "4",
+                 "--quantization", "nf4", "--device", "cpu", "--dtype", "float32"]) == 0
+    assert os.path.exists(os.path.join(out, "lora_weights.safetensors"))
