@@ -188,3 +188,53 @@ def test_training_job_through_the_real_command_line(tmp_path):
     assert job.metrics["step"] == 3 and job.metrics["total_steps"] == 3 and len(job.history["loss"]) == 3
     txt = _text(app)
     assert "3/3" in txt and "grad_norm" in txt and os.path.exists(tmp_path / "out" / "lora_weights.safetensors")
+
+
+def test_interactive_loop_on_a_pseudo_terminal(tmp_path):
+    """The real loop: raw-mode key reading and full-screen drawing on a pty; tab twice, open and close the help, quit."""
+    import pty
+    import select
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    master, slave = pty.openpty()
+    env = dict(os.environ, TERM="xterm-256color", COLUMNS="140", LINES="40")
+    p = subprocess.Popen([sys.executable, "-m", "pmetal_b200.cli.main", "tui", "--workdir", str(tmp_path)], cwd=root,
+                         stdin=slave, stdout=slave, stderr=subprocess.PIPE, env=env, start_new_session=True)
+    os.close(slave)
+    seen = b""
+
+    def pump(seconds):
+        nonlocal seen
+        end = time.time() + seconds
+        while time.time() < end:
+            r, _, _ = select.select([master], [], [], 0.2)
+            if r:
+                try:
+                    chunk = os.read(master, 65536)
+                except OSError:
+                    return
+                if not chunk:
+                    return
+                seen += chunk
+
+    try:
+        deadline = time.time() + 90
+        while b"System" not in seen and time.time() < deadline and p.poll() is None:
+            pump(0.5)
+        assert b"System" in seen and b"Training" in seen, (seen[-500:], p.stderr.read()[-2000:] if p.poll() is not None else b"")
+        for key in (b"\t", b"\t", b"?"):
+            os.write(master, key)
+            pump(0.8)
+        assert b"cancel the selected job" in seen              # the help page was drawn
+        os.write(master, b"x")                                  # any key closes it
+        pump(0.5)
+        os.write(master, b"q")
+        end = time.time() + 30
+        while p.poll() is None and time.time() < end:
+            pump(0.3)
+        assert p.poll() == 0, p.stderr.read()[-2000:]
+    finally:
+        if p.poll() is None:
+            p.kill()
+            p.wait()
+        os.close(master)
