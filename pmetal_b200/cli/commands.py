@@ -2075,7 +2075,17 @@ def _dash_args(sp):
                         "the application applies them, waits for the jobs it started and prints the last frame")
     p.add_argument("--workdir", default=None, help="where job logs and event files go (default: a temporary directory)")
     p.set_defaults(func=cmd_tui)
+    p = sp.add_parser("gui", help="browser front end: job forms, runner and live monitor served over HTTP")
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=8090)
+    p.add_argument("--workdir", default=None, help="where job logs and event files go (default: a temporary directory)")
+    p.set_defaults(func=cmd_gui)
     return p
+
+
+def cmd_gui(a) -> int:
+    from ..gui import serve_gui
+    return serve_gui(a.host, a.port, a.workdir)
 
 
 def cmd_tui(a) -> int:
