@@ -38,9 +38,21 @@ def build(force: bool = False) -> str:
     return SO
 
 
+def build_instrumented(out_path: str, sanitizers: str = "address,undefined") -> str:
+    """The same sources with compiler sanitisers, for test runs (``PMETAL_HOST_LIB`` then points the package at it and
+    the interpreter is started with the sanitiser runtime preloaded)."""
+    r = subprocess.run(["g++", "-O1", "-g", "-std=c++17", "-fPIC", "-ffp-contract=off", "-pthread", f"-fsanitize={sanitizers}",
+                        "-fno-omit-frame-pointer", "-fno-sanitize-recover=all", "-shared", "-o", out_path] + sources(),
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("instrumented host library build failed:\n" + r.stdout)
+    return out_path
+
+
 def load() -> ctypes.CDLL:
     global _LIB
     with _LOCK:
         if _LIB is None:
-            _LIB = ctypes.CDLL(build())
+            override = os.environ.get("PMETAL_HOST_LIB")        # an alternative build (sanitisers) for test runs
+            _LIB = ctypes.CDLL(override if override else build())
     return _LIB
