@@ -37,3 +37,47 @@ def test_host_library_is_clean_under_asan_and_ubsan(tmp_path):
     probe = subprocess.run([sys.executable, "-c", "from pmetal_b200.utils import hostlib; print(hostlib.load()._name)"], cwd=ROOT,
                            env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=120)
     assert so in probe.stdout, probe.stdout[-1000:]
+
+
+THREADED_DRIVER = r"""
+import numpy as np, os, tempfile, torch
+from pmetal_b200.gguf import native
+from pmetal_b200.gguf.types import GgmlType as T
+rng = np.random.default_rng(0)
+x = rng.standard_normal(64 * 1024).astype(np.float32)
+for t in (T.Q4_0, T.Q8_0, T.Q4K, T.Q6K):
+    q = native.quantize(x, t, threads=4)
+    y = native.dequantize(q, t, x.size, threads=4)
+    assert np.isfinite(y).all()
+w = rng.standard_normal((64, 1024)).astype(np.float32)
+out = native.matvec_q8k(native.quantize(w, T.Q5K, threads=3), T.Q5K, 64, 1024, x[:1024], threads=4)
+assert out.shape == (64,)
+from safetensors.torch import save_file
+from pmetal_b200.utils import safetensors_io as sio
+d = tempfile.mkdtemp()
+for i in range(3):
+    save_file({f"w{i}_{j}": torch.randn(256, 300) for j in range(4)}, os.path.join(d, f"s{i}.safetensors"))
+names = [n for n in dir(sio) if "thread" in n.lower() or "parallel" in n.lower()]
+from pmetal_b200.models.loader import read_state_dict
+import json
+json.dump({"weight_map": {f"w{i}_{j}": f"s{i}.safetensors" for i in range(3) for j in range(4)}}, open(os.path.join(d, "model.safetensors.index.json"), "w"))
+sd = read_state_dict(d)
+assert len(sd) == 12
+print("THREADED_OK")
+"""
+
+
+@pytest.mark.timeout(900)
+def test_threaded_host_paths_are_race_free_under_tsan(tmp_path):
+    """Block codecs split over threads, the row-parallel quantised mat-vec and the multi-threaded shard reader under
+    ThreadSanitizer."""
+    tsan = _runtime("libtsan.so")
+    if not tsan:
+        pytest.skip("the thread sanitiser runtime is not installed with this compiler")
+    from pmetal_b200.utils import hostlib
+    so = hostlib.build_instrumented(str(tmp_path / "libpmetal_host_tsan.so"), sanitizers="thread")
+    env = dict(os.environ, LD_PRELOAD=tsan, PMETAL_HOST_LIB=so, PMETAL_READ_THREADS="4",
+               TSAN_OPTIONS="halt_on_error=1:report_signal_unsafe=0:exitcode=66")
+    r = subprocess.run([sys.executable, "-c", THREADED_DRIVER], cwd=ROOT, env=env, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT, text=True, timeout=850)
+    assert r.returncode == 0 and "THREADED_OK" in r.stdout and "ThreadSanitizer" not in r.stdout, r.stdout[-4000:]
