@@ -52,17 +52,12 @@ for t in (T.Q4_0, T.Q8_0, T.Q4K, T.Q6K):
 w = rng.standard_normal((64, 1024)).astype(np.float32)
 out = native.matvec_q8k(native.quantize(w, T.Q5K, threads=3), T.Q5K, 64, 1024, x[:1024], threads=4)
 assert out.shape == (64,)
-from safetensors.torch import save_file
-from pmetal_b200.utils import safetensors_io as sio
-d = tempfile.mkdtemp()
-for i in range(3):
-    save_file({f"w{i}_{j}": torch.randn(256, 300) for j in range(4)}, os.path.join(d, f"s{i}.safetensors"))
-names = [n for n in dir(sio) if "thread" in n.lower() or "parallel" in n.lower()]
-from pmetal_b200.models.loader import read_state_dict
-import json
-json.dump({"weight_map": {f"w{i}_{j}": f"s{i}.safetensors" for i in range(3) for j in range(4)}}, open(os.path.join(d, "model.safetensors.index.json"), "w"))
-sd = read_state_dict(d)
-assert len(sd) == 12
+from pmetal_b200.utils.safetensors_io import load_file, load_file_parallel, save_file
+path = os.path.join(tempfile.mkdtemp(), "m.safetensors")
+tensors = {f"w{j}": torch.randn(256, 300 + j) for j in range(12)}
+save_file(tensors, path)
+a, b = load_file(path), load_file_parallel(path, threads=4)
+assert all(torch.equal(a[k], b[k]) for k in tensors)
 print("THREADED_OK")
 """
 
