@@ -71,6 +71,9 @@ def _add_train(sp):
     p.add_argument("--distributed-auto", action="store_true")
     p.add_argument("--compression-strategy", default="none")
     p.add_argument("--dp-impl", default="fused", choices=["fused", "nccl"])
+    p.add_argument("--expert-parallel", action="store_true",
+                   help="mixture-of-experts models on several GPUs: every rank keeps its share of each layer's experts and "
+                        "tokens travel to their expert's rank and back (differentiable all-to-all)")
     # accepted for command-line compatibility with the reference (crates/pmetal/src/cli/train.rs:10-186)
     p.add_argument("--no-flash-attention", action="store_true", help="same effect as --no-fused: PyTorch reference attention")
     p.add_argument("--no-metal-fused-optimizer", action="store_true",
@@ -130,6 +133,7 @@ def cmd_train(a) -> int:
     job.resume_bundle = a.resume_bundle
     job.tensorboard_dir = a.tensorboard
     job.max_samples, job.device, job.dtype, job.dp_impl = a.max_samples, a.device, a.dtype, a.dp_impl
+    job.expert_parallel = a.expert_parallel
     job.distributed = bool(a.distributed_peers or a.distributed_auto)
     if a.text_column or a.text_columns or a.prompt_column:
         job.dataset_format = "custom"

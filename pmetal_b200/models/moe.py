@@ -60,7 +60,10 @@ class SparseMoeBlock(nn.Module):
             out = eng.forward(x.to(torch.bfloat16), logits).to(x.dtype)
             return out if residual is None else out + residual
         w, idx = route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
-        if self.ep_group is not None:
+        if self.ep_group is not None and getattr(self, "ep_train", False):
+            from ..parallel.ep_train import ep_moe_train_forward
+            out = ep_moe_train_forward(self, x, w, idx)          # sharded expert parameters, differentiable exchange
+        elif self.ep_group is not None:
             from ..parallel.ep import ep_moe_forward_nccl
             out = ep_moe_forward_nccl(self, x, w, idx)
         else:

@@ -57,6 +57,7 @@ class TrainingJobConfig:
     dtype: str = "bfloat16"
     distributed: bool = False
     dp_impl: str = "fused"
+    expert_parallel: bool = False        # mixture-of-experts models: every rank keeps 1 / world of each layer's experts
     cut_cross_entropy: bool = True
     job_id: str = "train"
 
@@ -254,6 +255,14 @@ def run_training(job: TrainingJobConfig, phase_cb: Optional[Callable[[str], None
         if job.eval_dataset:
             eval_ds = TrainingDataset.from_file_tokenized(job.eval_dataset, tok, max_seq, job.dataset_format, template,
                                                           job.custom_columns)
+        # ---- expert parallelism: the (frozen) expert stacks are cut over the ranks before anything else looks at them;
+        # adapters on the replicated projections keep going through the data-parallel exchange
+        if job.expert_parallel and world > 1 and getattr(model.cfg, "num_experts", 0):
+            from ..parallel.ep_train import shard_experts_for_training
+            n_ep = shard_experts_for_training(model)
+            log.info("expert parallelism: %d layers, %d of %d experts on this rank", n_ep,
+                     model.cfg.num_experts // world, model.cfg.num_experts)
+            job.use_cuda_graph = False           # the token exchange sizes its messages on the host every step
         # ---- adapters
         if job.quantization != "none":
             from ..lora.qlora import quantize_base

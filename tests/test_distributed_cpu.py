@@ -474,3 +474,15 @@ def test_per_architecture_tensor_plans():
     assert P.shard_weight(w, P.ShardingDirective("expert_sharded", 0, 8), 1, 4).shape == (2, 3, 2)
     m = torch.arange(12.0).reshape(3, 4)
     assert torch.equal(P.shard_weight(m, P.ShardingDirective("sharded_to_all", 1), 1, 2), m[:, 2:])
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_training_matches_the_unsharded_model_over_gloo(world):
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29760 + world), os.path.join(root, "tests", "workers", "ep_train_worker.py")]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300,
+                       env=dict(os.environ, PMETAL_TEST_CPU="1"))
+    assert r.returncode == 0 and r.stdout.count("EP_TRAIN_WORKER_OK") == world, r.stdout[-3000:]

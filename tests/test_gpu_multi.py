@@ -63,3 +63,11 @@ def test_context_parallel_attention_forward_and_backward():
     n = 4 if torch.cuda.device_count() >= 4 else 2
     r = _run("cp_train_worker.py", n, port=29553)
     assert r.returncode == 0 and r.stdout.count("CP_TRAIN_WORKER_OK") == n, r.stdout[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_expert_parallel_training_matches_the_unsharded_model():
+    """Sharded expert stacks, differentiable all-to-all, grouped tcgen05 GEMMs for the local experts and their gradients."""
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    r = _run("ep_train_worker.py", n, port=29555)
+    assert r.returncode == 0 and r.stdout.count("EP_TRAIN_WORKER_OK") == n, r.stdout[-4000:]
