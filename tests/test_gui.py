@@ -9,7 +9,18 @@ from fastapi.testclient import TestClient  # noqa: E402
 
 from pmetal_b200.gui import create_app  # noqa: E402
 from pmetal_b200.tui.runner import JobRunner  # noqa: E402
-from tests.test_tui import FAKE_CLI  # noqa: E402
+
+def _fake_cli() -> str:
+    """The stand-in command line of the terminal-application tests (same directory), loaded by path."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("_tui_tests", os.path.join(os.path.dirname(os.path.abspath(__file__)), "test_tui.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.FAKE_CLI
+
+
+FAKE_CLI = _fake_cli()
 
 
 @pytest.fixture
