@@ -227,24 +227,29 @@ class PortableLoraTrainer:
         self.sched = LearningRateScheduler(learning_rate, total_steps, warmup_steps, schedule)
         self.max_grad_norm, self.step_count = max_grad_norm, 0
 
-    def micro_step(self, input_ids: torch.Tensor, labels: torch.Tensor, scale: float = 1.0) -> float:
+    def micro_step(self, input_ids: torch.Tensor, labels: torch.Tensor, scale: float = 1.0,
+                   positions: Optional[torch.Tensor] = None, doc_ids: Optional[torch.Tensor] = None) -> float:
         """Forward + backward of one micro-batch; ``scale`` (1 / accumulation steps) multiplies its loss so that the
-        accumulated gradient is the mean over the micro-batches. Gradients add up until ``optimizer_step``."""
-        loss = self.loss(input_ids, labels)
+        accumulated gradient is the mean over the micro-batches. Gradients add up until ``optimizer_step``.
+        ``positions`` / ``doc_ids`` [B, T] describe packed rows (several documents per row)."""
+        loss = self.loss(input_ids, labels, positions, doc_ids)
         (loss * scale if scale != 1.0 else loss).backward()
         return float(loss.detach())
 
-    def loss(self, input_ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    def loss(self, input_ids: torch.Tensor, labels: torch.Tensor, positions: Optional[torch.Tensor] = None,
+             doc_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Mean next-token cross entropy. Models that expose their read-out matrix (``loss_head``) get the chunked
         linear + cross-entropy (logit scale and soft cap inside it), so the [batch, tokens, vocabulary] logits are never
-        formed; the others go through their own ``forward``."""
+        formed; the others go through their own ``forward``. Packed rows pass their per-document positions and document
+        ids; their labels are expected to be masked at every document start."""
+        packed = {} if doc_ids is None else {"positions": positions, "doc_ids": doc_ids}
         spec = getattr(self.model, "loss_head", None)
         spec = spec() if callable(spec) else None
         if spec is None or input_ids.dim() != 2:
-            return causal_lm_loss(self.model(input_ids), labels)
+            return causal_lm_loss(self.model(input_ids, **packed), labels)
         from ..ops import functional as ops
         w, factor, cap = spec
-        h = self.model.forward_hidden(input_ids)
+        h = self.model.forward_hidden(input_ids, **packed)
         hs = h[:, :-1].reshape(-1, h.shape[-1])
         s, n = ops.linear_cross_entropy(hs, w, labels[:, 1:].reshape(-1), softcap=cap, logit_scale=factor)
         return s / n.clamp(min=1).to(s.dtype)

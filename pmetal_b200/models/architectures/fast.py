@@ -78,9 +78,11 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> Optional[torc
     return ops.rms_norm(x2, weight, eps).view(x.shape)
 
 
-def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int = 0) -> Optional[torch.Tensor]:
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int = 0,
+                     doc_ids: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """q [B, h, T, d], k / v [B, hkv, T, d] (same T: no cache) -> [B, h, T, d] with a causal (sliding-window) mask, on the
-    varlen kernels; None when the case is not covered."""
+    varlen kernels; None when the case is not covered. ``doc_ids`` [B, T] (non-decreasing along a row) cuts every row
+    into documents that do not see each other."""
     B, h, T, d = q.shape
     if "attention" not in ROUTES or k.shape[2] != T or v.shape[-1] != d or d > 128 or d % 8 or h % k.shape[1] or not _native(q):
         return None
@@ -93,6 +95,14 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
         pad = (0, 128 - d)
         qf, kf, vf = F.pad(qf, pad), F.pad(kf, pad), F.pad(vf, pad)
     qf, kf, vf = qf.contiguous(), kf.contiguous(), vf.contiguous()
-    seq_start = (torch.arange(B, device=q.device, dtype=torch.int32) * T).repeat_interleave(T)
+    if doc_ids is None:
+        seq_start = (torch.arange(B, device=q.device, dtype=torch.int32) * T).repeat_interleave(T)
+    else:
+        # flat index of the first token of each token's document: a new document starts where the id changes or a row begins
+        flat = doc_ids.reshape(-1)
+        idx = torch.arange(B * T, device=q.device)
+        new = torch.ones(B * T, dtype=torch.bool, device=q.device)
+        new[1:] = (flat[1:] != flat[:-1]) | (idx[1:] % T == 0)
+        seq_start = torch.cummax(torch.where(new, idx, torch.zeros_like(idx)), 0).values.to(torch.int32)
     o = ops._AttnCoreFn.apply(qf, kf, vf, seq_start, scale, int(window))
     return o[..., :d].reshape(B, T, h, d).transpose(1, 2)

@@ -372,6 +372,13 @@ def build_mask(kind: str, q_pos: torch.Tensor, k_pos: torch.Tensor, window: int,
     return m[:, None]
 
 
+def with_documents(mask: torch.Tensor, doc_ids: Optional[torch.Tensor]) -> torch.Tensor:
+    """Restrict a [B, 1, T, T] mask to pairs of the same document (packed rows); ``doc_ids`` [B, T] or None."""
+    if doc_ids is None:
+        return mask
+    return mask & (doc_ids[:, None, :, None] == doc_ids[:, None, None, :])
+
+
 def attend(q, k, v, mask, scale: float, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None):
     """q [B, h, Tq, d], k/v [B, hkv, Tk, d*]. Softmax in fp32; optional tanh soft-cap and per-head sink logits."""
     B, h, Tq, _ = q.shape
@@ -537,14 +544,16 @@ class Attention(nn.Module):
             k, v = cache.append(self.idx, k, v)
         scale = (c.attn_scale or d ** -0.5) * rope.get("attention_factor", 1.0) ** 2
         o = None
+        docs = rope.get("doc_ids")
         if (cache is None and rope.get("mask") is None and c.attn_softcap <= 0 and not c.sinks
-                and self.kind in ("full", "sliding") and q.is_cuda and rope.get("contiguous", False)):
-            # whole sequences from position 0 with a causal (or sliding-window) mask: the varlen flash-attention kernels
+                and self.kind in ("full", "sliding") and q.is_cuda and (rope.get("contiguous", False) or docs is not None)):
+            # whole sequences from position 0 (or packed documents whose positions restart) with a causal or
+            # sliding-window mask: the varlen flash-attention kernels
             from .fast import causal_attention
-            o = causal_attention(q, k, v, scale, c.sliding_window if self.kind == "sliding" else 0)
+            o = causal_attention(q, k, v, scale, c.sliding_window if self.kind == "sliding" else 0, docs)
         if o is None:
             mask = rope["mask"] if rope.get("mask") is not None else \
-                build_mask(self.kind, positions, k_positions, c.sliding_window, c.chunk_size)
+                with_documents(build_mask(self.kind, positions, k_positions, c.sliding_window, c.chunk_size), docs)
             o = attend(q, k, v, mask, scale, c.attn_softcap, self.sinks if c.sinks else None)
         o = o.transpose(1, 2).reshape(B, T, c.n_heads * d)
         if gate is not None:
@@ -661,7 +670,8 @@ class LatentAttention(nn.Module):
         v = kv[..., nd:]
         if cache is not None:
             k, v = cache.append(self.idx, k, v)
-        mask = rope["mask"] if rope.get("mask") is not None else build_mask("full", positions, k_positions, 0, 0)
+        mask = rope["mask"] if rope.get("mask") is not None else \
+            with_documents(build_mask("full", positions, k_positions, 0, 0), rope.get("doc_ids"))
         scale = (nd + rd) ** -0.5 * rope.get("attention_factor", 1.0) ** 2
         o = attend(q, k, v, mask, scale)
         return self.o_proj(o.transpose(1, 2).reshape(B, T, h * vd))
@@ -929,9 +939,12 @@ class GenericDecoderLM(nn.Module):
         return 1.0
 
     def forward_hidden(self, input_ids: torch.Tensor, cache: Optional[KVCache] = None,
-                       positions: Optional[torch.Tensor] = None, attn_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       positions: Optional[torch.Tensor] = None, attn_mask: Optional[torch.Tensor] = None,
+                       doc_ids: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``attn_mask`` (bool [B, 1, Tq, Tk], True = attend) replaces the position-derived causal mask in every layer
-        (tree-structured verification); full-attention models only."""
+        (tree-structured verification); full-attention models only. ``doc_ids`` [B, T] marks packed rows: tokens attend
+        inside their own document only (on top of the causal / sliding / chunked rule of each layer) and ``positions``
+        should restart at every document; recurrent layers (Mamba, gated delta net) are not reset at the boundaries."""
         c = self.c
         if input_ids.dim() == 1:
             input_ids = input_ids[None]
@@ -947,6 +960,7 @@ class GenericDecoderLM(nn.Module):
             x = x * torch.tensor(c.embed_scale, dtype=x.dtype)
         rope = self._rope(positions)
         rope["mask"] = attn_mask
+        rope["doc_ids"] = doc_ids if cache is None else None
         rope["contiguous"] = default_positions and past == 0       # every row is a whole sequence starting at position 0
         for layer in self.model.layers:
             x = layer(x, rope, positions, cache, k_positions)
@@ -976,8 +990,8 @@ class GenericDecoderLM(nn.Module):
             w = head.weight
         return w, c.logit_scale / c.logits_divisor, c.final_softcap
 
-    def forward(self, input_ids, cache: Optional[KVCache] = None, positions=None, attn_mask=None) -> torch.Tensor:
-        return self.logits(self.forward_hidden(input_ids, cache, positions, attn_mask))
+    def forward(self, input_ids, cache: Optional[KVCache] = None, positions=None, attn_mask=None, doc_ids=None) -> torch.Tensor:
+        return self.logits(self.forward_hidden(input_ids, cache, positions, attn_mask, doc_ids))
 
     def new_cache(self, kv_bits: Optional[int] = None, kv_group: int = 64, turbo: bool = False, qjl: bool = False) -> KVCache:
         """``kv_bits`` None: keys and values in the model dtype; 8 / 4: group-quantised; with ``turbo`` 2 / 4 / 8 bit

@@ -89,9 +89,10 @@ def _portable_model_dir(model: str) -> Optional[str]:
 
 
 def _run_portable_training(job: "TrainingJobConfig", model_dir: str, dev, dtype, out_dir: str, phase, callbacks, t_start) -> dict:
-    """LoRA fine-tuning of a portable architecture: padded batches through the PyTorch modules with adapters wrapped
-    around the target projections (``lora/portable.py``). Same dataset handling, schedule, callbacks and output files as
-    the fast path; no sequence packing, CUDA graph or fused optimiser."""
+    """LoRA fine-tuning of a portable architecture: packed rows (documents side by side, attention kept inside each
+    document) or padded batches through the modules with adapters wrapped around the target projections
+    (``lora/portable.py``). Same dataset handling, schedule, callbacks and output files as the fast path; no CUDA graph or
+    fused optimiser."""
     import torch
 
     from ..core.callbacks import CompositeCallback, LoggingCallback, MetricsJsonCallback
@@ -121,7 +122,19 @@ def _run_portable_training(job: "TrainingJobConfig", model_dir: str, dev, dtype,
     if job.resume and os.path.exists(os.path.join(out_dir, "lora_weights.safetensors")):
         load_adapter_portable(model, out_dir)
     model.train()
-    loader = DataLoader(ds.samples, tcfg.batch_size, True, tcfg.seed, tok.pad_token_id or 0, max_seq)
+    import inspect
+    packing = (job.use_packing and tcfg.use_packing and hasattr(model, "forward_hidden")
+               and "doc_ids" in inspect.signature(model.forward_hidden).parameters)
+    if packing:
+        # several documents per row: positions restart and attention stays inside each document (models/architectures/
+        # generic.py: doc_ids); on a GPU the rows run on the varlen flash-attention kernels
+        from ..data.dataloader import PackedDataLoader
+        from ..data.packing import compute_pack_seq_len
+        pack_len = job.pack_max_seq_len or compute_pack_seq_len([len(s) for s in ds.samples], max_seq)
+        loader = PackedDataLoader(ds.samples, pack_len, tcfg.batch_size, True, tcfg.seed, 0, 1, tok.pad_token_id or 0)
+        log.info("packing: %s", loader.stats.summary())
+    else:
+        loader = DataLoader(ds.samples, tcfg.batch_size, True, tcfg.seed, tok.pad_token_id or 0, max_seq)
     accum = max(tcfg.gradient_accumulation_steps, 1)
     per_epoch = max(len(loader) // accum, 1)        # optimiser steps per epoch: ``accum`` micro-batches each
     total = tcfg.max_steps or per_epoch * tcfg.num_epochs
@@ -151,9 +164,17 @@ def _run_portable_training(job: "TrainingJobConfig", model_dir: str, dev, dtype,
     while not done:
         loader.set_epoch(epoch)
         for batch in loader:
-            ids, labels = batch["input_ids"].to(dev), batch["labels"].to(dev)
-            acc_loss += tr.micro_step(ids, labels, 1.0 / accum)
-            acc_tok += int(batch.get("tokens", ids.numel()))
+            if packing:
+                rows = batch.input_ids.numel() // pack_len
+                ids = batch.input_ids.view(rows, pack_len).to(dev)
+                labels = batch.labels.view(rows, pack_len).to(dev)
+                acc_loss += tr.micro_step(ids, labels, 1.0 / accum, batch.position_ids.view(rows, pack_len).to(dev).long(),
+                                          batch.seq_start.view(rows, pack_len).to(dev).long())
+                acc_tok += int(batch.total_tokens)
+            else:
+                ids, labels = batch["input_ids"].to(dev), batch["labels"].to(dev)
+                acc_loss += tr.micro_step(ids, labels, 1.0 / accum)
+                acc_tok += int(batch.get("tokens", ids.numel()))
             micro += 1
             if micro < accum:
                 continue

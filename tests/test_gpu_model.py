@@ -364,3 +364,32 @@ def test_portable_architectures_run_on_the_native_kernels(family, extra):
     gerr = (g_nat.float() - g_ref.float()).norm() / g_ref.float().norm()
     assert float(gerr) < 0.05, float(gerr)
     nat.check_status()
+
+
+def test_portable_packed_rows_run_on_the_varlen_kernels():
+    """Rows that hold several documents (doc_ids, positions restarting): the native route cuts the attention at the
+    document boundaries exactly like the masked PyTorch path."""
+    from pmetal_b200.models.architectures.generic import GenericDecoderLM, arch_config_from_hf
+    from pmetal_b200.ops import functional as F
+    from pmetal_b200.ops import native as nat
+    cfg = dict(model_type="mistral", vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=64, sliding_window=48, max_position_embeddings=2048,
+               rms_norm_eps=1e-6)
+    torch.manual_seed(0)
+    m = GenericDecoderLM(arch_config_from_hf(cfg)).init_weights(0.05, 0).cuda().to(torch.bfloat16).eval()
+    lens = [[70, 130, 56], [200, 56]]
+    ids = torch.randint(0, 512, (2, 256), device="cuda")
+    pos = torch.stack([torch.cat([torch.arange(n) for n in row]) for row in lens]).cuda()
+    docs = torch.stack([torch.cat([torch.full((n,), i) for i, n in enumerate(row)]) for row in lens]).cuda()
+    n0 = nat.LAUNCHES
+    with torch.no_grad():
+        h = m.forward_hidden(ids, positions=pos, doc_ids=docs)
+        assert nat.LAUNCHES > n0
+        with F.force_reference():
+            h_ref = m.forward_hidden(ids, positions=pos, doc_ids=docs)
+        alone = m.forward_hidden(ids[:1, 70:200])                      # the middle document of the first row by itself
+    err = (h.float() - h_ref.float()).norm() / h_ref.float().norm()
+    assert float(err) < 0.03, float(err)
+    e2 = (h[0, 70:200].float() - alone[0].float()).norm() / alone.float().norm()
+    assert float(e2) < 0.03, float(e2)
+    nat.check_status()

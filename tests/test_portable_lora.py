@@ -356,3 +356,39 @@ def test_qlora_on_a_portable_family(tmp_path, capsys):
     assert main(["train", "--model", d, "--dataset", str(data), "--output", out, "--max-steps", "2", "--lora-r", "4",
                  "--quantization", "nf4", "--device", "cpu", "--dtype", "float32"]) == 0
     assert os.path.exists(os.path.join(out, "lora_weights.safetensors"))
+
+
+def test_packed_rows_equal_separate_documents_and_train_command_packs(tmp_path, capsys):
+    """Documents packed into one row (positions restart, attention inside each document) give the loss of the documents run
+    one by one; the train command packs by default for a Gemma directory."""
+    from pmetal_b200.data.dataloader import PackedDataLoader
+    from pmetal_b200.data.packing import Sample
+    d = _tiny_gemma_dir(tmp_path)
+    model = load_pretrained(d, torch.float32)
+    P.apply_lora_portable(model, LoraConfig(r=4, alpha=8.0, target_modules=["q_proj", "v_proj"]))
+    with torch.no_grad():
+        for m in P.lora_modules(model).values():
+            m.lora_b.normal_(0, 0.05)
+    tr = P.PortableLoraTrainer(model, total_steps=2)
+    g = torch.Generator().manual_seed(5)
+    docs = [torch.randint(0, 256, (n,), generator=g).tolist() for n in (9, 14, 6, 11)]
+    loader = PackedDataLoader([Sample(x, list(x)) for x in docs], 24, packs_per_batch=2, shuffle=False)
+    assert len(loader.packs) == 2                                  # two rows of 24 hold the 40 tokens
+    batch = next(iter(loader))
+    ids, labels = batch.input_ids.view(2, 24), batch.labels.view(2, 24)
+    packed = tr.loss(ids, labels, batch.position_ids.view(2, 24).long(), batch.seq_start.view(2, 24).long())
+    tot, cnt = 0.0, 0
+    for x in docs:
+        t = torch.tensor([x])
+        n = len(x) - 1
+        tot += float(tr.loss(t, t.clone())) * n
+        cnt += n
+    assert abs(float(packed) - tot / cnt) < 1e-4
+    from pmetal_b200.cli.main import main
+    data = tmp_path / "t.jsonl"
+    data.write_text("".join(json.dumps({"text": "hello world " * (2 + i % 3)}) + "\n" for i in range(12)))
+    out = str(tmp_path / "packed")
+    assert main(["train", "--model", d, "--dataset", str(data), "--output", out, "--max-steps", "2", "--lora-r", "4",
+                 "--device", "cpu", "--dtype", "float32", "--batch-size", "2", "--gradient-accumulation-steps", "1"]) == 0
+    j = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert j["path"] == "portable" and j["steps"] == 2 and os.path.exists(os.path.join(out, "lora_weights.safetensors"))
