@@ -109,7 +109,7 @@ def test_portable_path_accumulates_micro_batches_and_resumes(tmp_path, capsys):
     out = str(tmp_path / "out")
     args = ["train", "-m", d, "-d", str(data), "-o", out, "--lora-r", "4", "--lora-alpha", "8", "--batch-size", "2",
             "--gradient-accumulation-steps", "4", "--epochs", "1", "--warmup-steps", "0", "--device", "cpu", "--dtype",
-            "float32", "--log-metrics", str(tmp_path / "m.jsonl"), "--no-adaptive-lr"]
+            "float32", "--log-metrics", str(tmp_path / "m.jsonl"), "--no-adaptive-lr", "--no-sequence-packing"]
     assert main(args) == 0
     summary = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     steps = [json.loads(l) for l in open(tmp_path / "m.jsonl") if '"step"' in l]
