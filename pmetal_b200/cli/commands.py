@@ -595,6 +595,30 @@ def _infer_portable(a, model_dir: str) -> int:
     if cache is None:
         print("error: this architecture has no text-generation head", file=sys.stderr)
         return 2
+    if getattr(a, "draft_model", None):
+        # two-model speculative decoding on the contiguous caches (models/architectures/speculative.py)
+        from ..models.architectures.speculative import speculative_generate
+        from ..trainer.orchestrator import _portable_model_dir
+        ddir = _portable_model_dir(a.draft_model)
+        if ddir is None:
+            print("error: --draft-model must be a directory of a config-driven architecture for this target", file=sys.stderr)
+            return 2
+        if kv_bits is not None:
+            print("error: speculative decoding keeps plain caches (no --kv-quant / --kv-turboquant)", file=sys.stderr)
+            return 2
+        draft = load_portable(ddir, dtype, dev).eval()
+        t0 = time.perf_counter()
+        st = speculative_generate(model, draft, ids, a.max_tokens, k=a.speculative_k, eos_ids=eos,
+                                  temperature=0.0 if sp_.is_greedy else sp_.temperature)
+        out = [t for t in st.tokens if t not in eos]
+        dt = max(time.perf_counter() - t0, 1e-9)
+        if a.json:
+            print(json.dumps({"text": tok.decode(out), "prompt_tokens": len(ids), "generated_tokens": len(out),
+                              "tok_per_s": round(len(out) / dt, 1), "path": "portable", "speculative": True,
+                              "rounds": st.rounds, "acceptance_rate": round(st.acceptance_rate, 3)}))
+        else:
+            print(tok.decode(out))
+        return 0
     fmt = StreamFormatter(tok, show_thinking=not a.hide_thinking) if a.stream and not a.json else None
     out, t0 = [], time.perf_counter()
     cur = torch.tensor([ids], device=dev)

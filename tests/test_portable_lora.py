@@ -392,3 +392,14 @@ def test_packed_rows_equal_separate_documents_and_train_command_packs(tmp_path, 
                  "--device", "cpu", "--dtype", "float32", "--batch-size", "2", "--gradient-accumulation-steps", "1"]) == 0
     j = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert j["path"] == "portable" and j["steps"] == 2 and os.path.exists(os.path.join(out, "lora_weights.safetensors"))
+
+
+def test_infer_command_with_a_draft_for_a_portable_target(tmp_path, capsys):
+    from pmetal_b200.cli.main import main
+    d = _tiny_gemma_dir(tmp_path)
+    assert main(["infer", "-m", d, "-p", "hello", "--max-tokens", "8", "--greedy", "--json", "--device", "cpu"]) == 0
+    plain = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert main(["infer", "-m", d, "-p", "hello", "--max-tokens", "8", "--greedy", "--json", "--device", "cpu",
+                 "--draft-model", d]) == 0
+    spec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert spec["speculative"] and spec["text"] == plain["text"] and spec["acceptance_rate"] == 1.0
