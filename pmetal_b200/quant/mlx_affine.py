@@ -90,6 +90,27 @@ def quantized_matmul(x: torch.Tensor, packed, scales, biases, bits: int, group_s
     return torch.cat(outs, -1)
 
 
+def gather_qmm(x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, indices: torch.Tensor,
+               bits: int, group_size: int) -> torch.Tensor:
+    """Quantised gather-matmul for mixture-of-experts layers: row ``i`` of ``x`` [R, K] is multiplied by the quantised
+    matrix of expert ``indices[i]`` out of a stack ``packed`` [E, N, K * bits / 32] (``scales`` / ``biases`` [E, N, K /
+    group]); returns [R, N]. Rows are grouped by expert so that each expert's matrix is expanded once and only while it
+    is used (bridge_inference.cpp ``gather_qmm``, crates/pmetal-bridge/cpp/bridge_inference.cpp)."""
+    R = x.shape[0]
+    N = scales.shape[1]
+    out = x.new_empty(R, N)
+    order = torch.argsort(indices, stable=True)
+    counts = torch.bincount(indices, minlength=packed.shape[0]).tolist()
+    pos = 0
+    for e, n in enumerate(counts):
+        if n == 0:
+            continue
+        rows = order[pos:pos + n]
+        out[rows] = quantized_matmul(x[rows], packed[e], scales[e], biases[e], bits, group_size)
+        pos += n
+    return out
+
+
 # ------------------------------------------------------------------------------------------------ allocation
 def is_critical_tensor(name: str) -> bool:
     n = name.lower()

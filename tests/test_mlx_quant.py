@@ -96,3 +96,19 @@ def test_checkpoint_round_trip(tmp_path):
         a, b, c = m(ids[0]), m2(ids[0]), m3(ids[0])
     assert torch.allclose(b, c, atol=1e-5)
     assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.8
+
+
+def test_gather_qmm_matches_per_row_dense_products():
+    import torch
+    from pmetal_b200.quant.mlx_affine import dequantize_affine, gather_qmm, quantize_affine
+    torch.manual_seed(0)
+    E, N, K, R = 5, 24, 128, 17
+    w = torch.randn(E, N, K)
+    packed, scales, biases = quantize_affine(w, 4, 64)
+    x = torch.randn(R, K)
+    idx = torch.tensor([4, 0, 0, 3, 1, 4, 4, 2, 0, 1, 3, 3, 2, 0, 4, 1, 2])
+    got = gather_qmm(x, packed, scales, biases, idx, 4, 64)
+    dense = dequantize_affine(packed, scales, biases, 4, 64)
+    want = torch.stack([x[i] @ dense[idx[i]].t() for i in range(R)])
+    assert got.shape == (R, N) and torch.allclose(got, want, atol=1e-4)
+    assert (dense - w).abs().max() < 0.6                          # 4-bit groups of 64 on N(0,1) data
