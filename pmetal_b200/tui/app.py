@@ -14,7 +14,7 @@ from typing import Any, Dict, List, Optional, Tuple
 
 from .runner import Job, JobRunner
 
-# (tab title, sub-command) in display order; None marks the tabs that are not forms.
+# (tab title, sub-command) of the form tabs, in display order
 FORM_TABS: List[Tuple[str, str]] = [
     ("Tokenize", "tokenize"), ("Training", "train"), ("EmbedTrain", "embed-train"), ("Pretrain", "pretrain"),
     ("Distill", "distill"), ("RLKD", "rlkd"), ("GRPO", "grpo"), ("Inference", "infer"), ("DFlash", "dflash"),
@@ -42,8 +42,8 @@ def sparkline(values: List[float], width: int = 60) -> str:
         return ""
     if len(vals) > width:
         step = len(vals) / width
-        vals = [sum(vals[int(i * step):max(int(i * step) + 1, int((i + 1) * step))]) /
-                max(1, len(vals[int(i * step):max(int(i * step) + 1, int((i + 1) * step))])) for i in range(width)]
+        buckets = [vals[int(i * step):max(int(i * step) + 1, int((i + 1) * step))] for i in range(width)]
+        vals = [sum(b) / len(b) for b in buckets]
     lo, hi = min(vals), max(vals)
     span = (hi - lo) or 1.0
     return "".join(SPARK[min(len(SPARK) - 1, int((v - lo) / span * (len(SPARK) - 1) + 0.5))] for v in vals)
