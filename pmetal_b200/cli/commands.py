@@ -1199,6 +1199,28 @@ def _grpo_args(sp):
     return p
 
 
+def _load_reward_model(path: str, dtype, dev):
+    """A frozen scorer for ``--reward-model``: any supported architecture; the scalar head is read from the checkpoint
+    (``score.weight`` / ``v_head.weight`` / ``reward_head.weight``), without one the mean read-out logit is the score."""
+    from ..models.loader import load_pretrained, read_state_dict
+    from ..trainer.orchestrator import _portable_model_dir
+    from ..trainer.rewards import ModelReward
+    pdir = _portable_model_dir(path)
+    if pdir is not None:
+        from ..models.architectures import load_pretrained as load_portable
+        rm, rdir = load_portable(pdir, dtype, dev), pdir
+    else:
+        rm, _, rdir = load_pretrained(path, dtype=dtype, device=dev)
+    head = None
+    if rdir:
+        sd = read_state_dict(rdir)
+        head = next((sd[k].reshape(-1).to(dev) for k in ("score.weight", "v_head.weight", "reward_head.weight") if k in sd), None)
+    rm.eval()
+    for p in rm.parameters():
+        p.requires_grad_(False)
+    return ModelReward(rm, head)
+
+
 def _grpo_portable(a, model_dir: str, lcfg) -> int:
     """``grpo`` on a config-driven architecture: portable LoRA adapters, rollouts on the model's own cache
     (trainer/grpo_portable.py). Reward models, teachers and --resume belong to the llama / qwen path."""
@@ -1214,8 +1236,8 @@ def _grpo_portable(a, model_dir: str, lcfg) -> int:
     from ..trainer.grpo import GrpoConfig
     from ..trainer.grpo_portable import PortableGrpoTrainer
     from ..trainer.rewards import make_reward
-    if a.reward_model or (a.teacher and a.rlkd_alpha > 0):
-        print("error: --reward-model / --teacher are available for the llama / qwen family only", file=sys.stderr)
+    if a.teacher and a.rlkd_alpha > 0:
+        print("error: --teacher (RLKD) is available for the llama / qwen family only", file=sys.stderr)
         return 2
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
     model = load_portable(model_dir, torch.bfloat16 if dev.startswith("cuda") else torch.float32, dev)
@@ -1230,6 +1252,10 @@ def _grpo_portable(a, model_dir: str, lcfg) -> int:
     if a.reasoning_rewards:
         from ..trainer.rewards import combined_reward
         reward = combined_reward([make_reward("format", tok), make_reward("accuracy", tok, _read_targets(a.dataset))], [1.0, 1.0])
+    if a.reward_model:
+        from ..trainer.rewards import combined_reward
+        reward = combined_reward([reward, _load_reward_model(a.reward_model, next(model.parameters()).dtype, dev)],
+                                 [1.0, a.reward_model_weight])
     tr = PortableGrpoTrainer(model, cfg, reward, eos_ids=eos, pad_id=tok.pad_token_id or 0)
     keys = ((a.prompt_column,) if a.prompt_column else ()) + ("prompt", "question", "text", "instruction")
     prompts = _read_prompts(a.dataset, tok, key_order=keys)
@@ -1283,14 +1309,9 @@ def cmd_grpo(a) -> int:
         from ..trainer.rewards import combined_reward
         reward = combined_reward([make_reward("format", tok), make_reward("accuracy", tok, _read_targets(a.dataset))], [1.0, 1.0])
     if a.reward_model:
-        from ..models.loader import load_pretrained, read_state_dict, resolve_model_path
-        from ..trainer.rewards import ModelReward, combined_reward
-        rm, _, rdir = load_pretrained(a.reward_model, dtype=next(model.parameters()).dtype, device=dev)
-        head = None
-        if rdir:
-            sd = read_state_dict(rdir)
-            head = next((sd[k].reshape(-1).to(dev) for k in ("score.weight", "v_head.weight", "reward_head.weight") if k in sd), None)
-        reward = combined_reward([reward, ModelReward(rm.eval(), head)], [1.0, a.reward_model_weight])
+        from ..trainer.rewards import combined_reward
+        reward = combined_reward([reward, _load_reward_model(a.reward_model, next(model.parameters()).dtype, dev)],
+                                 [1.0, a.reward_model_weight])
     if a.async_rewards:
         reward = _threaded_reward(reward)
     if a.teacher and a.rlkd_alpha > 0:

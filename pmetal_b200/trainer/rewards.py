@@ -4,6 +4,7 @@ reward that scores completions with a sequence-classification head."""
 from __future__ import annotations
 
 import re
+from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional, Sequence
 
 RewardFn = Callable[[List[List[int]], List[List[int]]], List[float]]
@@ -68,25 +69,74 @@ def combined_reward(fns: Sequence[RewardFn], weights: Sequence[float]) -> Reward
     return fn
 
 
-class ModelReward:
-    """Scores prompt+completion with a decoder whose last hidden state feeds a scalar head (reward model)."""
+@dataclass
+class RewardModelConfig:
+    """How a reward model reads a prompt + completion (crates/pmetal-trainer/src/reward_model.rs:47-120)."""
+    max_length: int = 2048             # longer inputs are cut from the right
+    use_last_token: bool = True        # False: mean over all positions
+    batch_size: int = 16               # sequences per packed forward
+    template: Optional[str] = None     # "... {prompt} ... {completion} ..." applied on text (needs a tokenizer)
 
-    def __init__(self, model, head_weight=None):
+
+class ModelReward:
+    """Scores prompt + completion with a frozen decoder. Strategies of the reference's ``MLRewardModel``: a scalar head
+    on the pooled hidden state (``score.weight`` of sequence-classification checkpoints) or, without a head, the mean of
+    the read-out logits at the pooled position. Sequences are scored several at a time: the fast decoder takes them as one
+    packed token stream (documents do not see each other), the config-driven architectures one row each."""
+
+    def __init__(self, model, head_weight=None, config: Optional[RewardModelConfig] = None, tokenizer=None):
+        self.model, self.head = model, head_weight
+        self.cfg = config or RewardModelConfig()
+        self.tok = tokenizer
+        if self.cfg.template and tokenizer is None:
+            raise ValueError("a reward template works on text and needs the tokenizer")
+        self.strategy = "score_head" if head_weight is not None else "mean_logits"
+
+    def _sequences(self, prompts, completions) -> List[List[int]]:
+        out = []
+        for p, c in zip(prompts, completions):
+            if self.cfg.template:
+                text = self.cfg.template.replace("{prompt}", self.tok.decode(list(p))).replace("{completion}", self.tok.decode(list(c)))
+                ids = self.tok.encode(text)
+            else:
+                ids = list(p) + list(c)
+            out.append((ids or [0])[: self.cfg.max_length])
+        return out
+
+    def _score(self, pooled):
         import torch
-        self.model = model
-        dev = model.embed_tokens.device
-        self.head = head_weight if head_weight is not None else torch.zeros(model.cfg.hidden_size, device=dev)
+        if self.head is not None:
+            return pooled.float() @ self.head.float().reshape(-1)
+        m = self.model
+        logits = m.logits(pooled) if hasattr(m, "logits") else torch.nn.functional.linear(pooled, m.head_weight())
+        return logits.float().mean(-1)
 
     def __call__(self, prompts, completions):
         import torch
-        out = []
-        dev = self.model.embed_tokens.device
+        seqs = self._sequences(prompts, completions)
+        dev = next(self.model.parameters()).device
+        fast = hasattr(self.model, "fused_linears")
+        out: List[float] = []
         with torch.no_grad():
-            for p, c in zip(prompts, completions):
-                ids = torch.tensor(list(p) + list(c), dtype=torch.int64, device=dev)
-                T = ids.numel()
-                h = self.model.forward_hidden(ids, torch.arange(T, dtype=torch.int32, device=dev),
-                                              torch.tensor([0, T], dtype=torch.int32, device=dev),
-                                              torch.zeros(T, dtype=torch.int32, device=dev))
-                out.append(float(h[-1].float() @ self.head.float()))
+            for b0 in range(0, len(seqs), max(self.cfg.batch_size, 1)):
+                part = seqs[b0:b0 + self.cfg.batch_size]
+                if fast:
+                    lens = [len(s) for s in part]
+                    ids = torch.tensor([t for s in part for t in s], dtype=torch.int64, device=dev)
+                    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+                    pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).to(dev)
+                    start = torch.repeat_interleave(cu[:-1], torch.tensor(lens, device=dev)).to(torch.int32)
+                    h = self.model.forward_hidden(ids, pos, cu, start)
+                    ends = (cu[1:] - 1).long()
+                    if self.cfg.use_last_token:
+                        pooled = h[ends]
+                    else:
+                        pooled = torch.stack([h[int(cu[i]):int(cu[i + 1])].float().mean(0) for i in range(len(part))]).to(h.dtype)
+                else:
+                    rows = []
+                    for s_ in part:
+                        h = self.model.forward_hidden(torch.tensor([s_], device=dev))[0]
+                        rows.append(h[-1] if self.cfg.use_last_token else h.float().mean(0).to(h.dtype))
+                    pooled = torch.stack(rows)
+                out.extend(float(x) for x in self._score(pooled))
         return out

@@ -1,5 +1,7 @@
 import math
 
+import pytest
+
 import torch
 
 from pmetal_b200.core.config import LoraConfig
@@ -56,3 +58,32 @@ def test_grpo_step_runs_and_updates_policy():
     st2 = GrpoTrainer(m, GrpoConfig.dapo(num_generations=4, max_completion_length=6), mod7_length_reward,
                       kv_blocks=64, optimizer=tr.opt).step(prompts)
     assert st2.skipped_groups >= 0
+
+
+def test_model_reward_strategies_batching_and_families():
+    """Packed scoring of several sequences equals scoring them one by one; score head and mean-logit strategies, last
+    token and mean pooling, truncation, and a config-driven scorer."""
+    from pmetal_b200.trainer.rewards import ModelReward, RewardModelConfig
+    torch.manual_seed(0)
+    m = DecoderLM(preset("tiny-qwen3")).init_weights(0.05, 0).eval()
+    head = torch.randn(m.cfg.hidden_size)
+    prompts = [torch.randint(0, 1024, (n,)).tolist() for n in (5, 9, 3, 7)]
+    comps = [torch.randint(0, 1024, (n,)).tolist() for n in (4, 2, 6, 1)]
+    for cfg in (RewardModelConfig(batch_size=3), RewardModelConfig(use_last_token=False, batch_size=2)):
+        packed = ModelReward(m, head, cfg)(prompts, comps)
+        single = [ModelReward(m, head, RewardModelConfig(use_last_token=cfg.use_last_token, batch_size=1))([p], [c])[0]
+                  for p, c in zip(prompts, comps)]
+        assert all(abs(a - b) < 1e-4 for a, b in zip(packed, single))
+    r = ModelReward(m)
+    assert r.strategy == "mean_logits" and len(r(prompts, comps)) == 4
+    cut = ModelReward(m, head, RewardModelConfig(max_length=6))(prompts[:1], comps[:1])[0]
+    want = ModelReward(m, head)([prompts[0][:5]], [comps[0][:1]])[0]
+    assert abs(cut - want) < 1e-4
+    from pmetal_b200.models.architectures.generic import GenericDecoderLM, arch_config_from_hf
+    g = GenericDecoderLM(arch_config_from_hf(dict(model_type="gemma2", vocab_size=1024, hidden_size=32, intermediate_size=64,
+                                                  num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2, head_dim=8,
+                                                  max_position_embeddings=64))).init_weights(0.1, 0).eval()
+    vals = ModelReward(g, torch.randn(32))(prompts, comps)
+    assert len(vals) == 4 and all(math.isfinite(v) for v in vals)
+    with pytest.raises(ValueError):
+        ModelReward(m, head, RewardModelConfig(template="{prompt} => {completion}"))
