@@ -44,13 +44,46 @@ class Model:
         from types import SimpleNamespace
 
         from .cli.commands import _load_for_inference
+        from .trainer.orchestrator import _portable_model_dir
+        pdir = _portable_model_dir(path)
+        if pdir is not None:                       # a config-driven architecture (Gemma, Phi, Cohere, ...)
+            return cls._load_portable(pdir, lora, device)
         m, tok, tpl, eos, mdir = _load_for_inference(SimpleNamespace(model=path, lora=lora, device=device, fp8=fp8, seed=0))
         return cls(m, tok, tpl, eos, mdir)
 
+    @classmethod
+    def _load_portable(cls, model_dir: str, lora: Optional[str], device: Optional[str]) -> "Model":
+        import torch
+
+        from .data.chat_templates import ChatTemplate
+        from .data.inference_config import collect_all_stop_tokens
+        from .data.tokenizer import Tokenizer
+        from .models.architectures import load_pretrained as load_portable
+        dev = device or ("cuda" if torch.cuda.is_available() else "cpu")
+        m = load_portable(model_dir, torch.bfloat16 if dev.startswith("cuda") else torch.float32, dev).eval()
+        if lora:
+            from .lora.adapter import load_adapter_config
+            from .lora.portable import apply_lora_portable, load_adapter_portable, merge_lora_portable
+            apply_lora_portable(m, load_adapter_config(lora))
+            load_adapter_portable(m, lora)
+            merge_lora_portable(m)
+        for p in m.parameters():
+            p.requires_grad_(False)
+        tok, tpl = Tokenizer.from_model_dir(model_dir), ChatTemplate.from_model_dir(model_dir)
+        return cls(m, tok, tpl, collect_all_stop_tokens(model_dir, tok, tpl.eos()), model_dir)
+
+    @property
+    def portable(self) -> bool:
+        return not hasattr(self.model, "fused_linears")
+
     def _generator(self):
         if self._gen is None:
-            from .models.generation import Generator
-            self._gen = Generator(self.model)
+            if self.portable:
+                from .serve.portable_engine import PortableEngine
+                self._gen = PortableEngine(self.model, self.eos_ids)
+            else:
+                from .models.generation import Generator
+                self._gen = Generator(self.model)
         return self._gen
 
     def _encode(self, prompt, system=None, chat=False) -> List[int]:
@@ -65,6 +98,9 @@ class Model:
         from .models.sampling import SamplingParams
         sp = SamplingParams.greedy(max_tokens) if temperature <= 0 else SamplingParams(temperature=temperature,
                                                                                         max_tokens=max_tokens, **sampling)
+        if self.portable:
+            req = self._generator().generate(self._encode(prompt, system, chat), sp)
+            return self.tokenizer.decode([t for t in req.output if t not in self.eos_ids])
         res = self._generator().generate([self._encode(prompt, system, chat)], sp, self.eos_ids)
         return self.tokenizer.decode([t for t in res.tokens[0] if t not in self.eos_ids])
 
@@ -73,6 +109,22 @@ class Model:
         from .models.sampling import SamplingParams
         sp = SamplingParams.greedy(max_tokens) if temperature <= 0 else SamplingParams(temperature=temperature, max_tokens=max_tokens)
         dec = StreamDecoder(self.tokenizer)
+        if self.portable:
+            from .serve.engine import Request
+            eng = self._generator()
+            req = eng.submit(Request(self._encode(prompt, kw.get("system"), kw.get("chat", False)), sp))
+            sent = 0
+            while not req.done.is_set() or sent < len(req.output):
+                if not req.done.is_set():
+                    eng.tick()
+                while sent < len(req.output):
+                    t = req.output[sent]
+                    sent += 1
+                    if t not in self.eos_ids:
+                        piece = dec.push(t)
+                        if piece:
+                            yield piece
+            return
         for t in self._generator().stream(self._encode(prompt, kw.get("system"), kw.get("chat", False)), sp, self.eos_ids):
             if t not in self.eos_ids:
                 piece = dec.push(t)
@@ -80,6 +132,9 @@ class Model:
                     yield piece
 
     def save(self, out_dir: str, merged: bool = True) -> None:
+        if self.portable:
+            from .models.architectures import save_pretrained as save_portable
+            return save_portable(self.model, out_dir, copy_from=self.model_dir)
         from .models.loader import save_pretrained
         save_pretrained(self.model, out_dir, merged=merged, copy_from=self.model_dir)
 

@@ -403,3 +403,18 @@ def test_infer_command_with_a_draft_for_a_portable_target(tmp_path, capsys):
                  "--draft-model", d]) == 0
     spec = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert spec["speculative"] and spec["text"] == plain["text"] and spec["acceptance_rate"] == 1.0
+
+
+def test_python_api_loads_generates_streams_and_saves_a_portable_model(tmp_path):
+    import pmetal_b200 as pm
+    d = _tiny_gemma_dir(tmp_path)
+    m = pm.Model.load(d, device="cpu")
+    assert m.portable
+    text = m.generate("hello", max_tokens=6, temperature=0)
+    assert isinstance(text, str)
+    assert "".join(m.stream("hello", max_tokens=6, temperature=0)) == text
+    out = str(tmp_path / "copy")
+    m.save(out)
+    again = pm.Model.load(out, device="cpu")
+    assert again.generate("hello", max_tokens=6, temperature=0) == text
+    assert pm.infer(d, "hello", max_tokens=3, temperature=0) == m.generate("hello", max_tokens=3, temperature=0)
