@@ -91,6 +91,20 @@ def main():
         assert d.max().item() == 0.0, f"overlapped reduce differs from the plain one by {d.max().item()}"
     drift = (finals["overlap-bf16"] - finals["clip-after"]).abs().max().item()
     assert 0.0 < drift < 5e-3, f"bf16 gradient exchange drifted by {drift}"
+    # gradient accumulation: buckets leave during the last micro-batch only, earlier ones just add into the buffer
+    import dataclasses
+    acc_cfg = dataclasses.replace(cfg, gradient_accumulation_steps=2, max_steps=2)
+    acc = {}
+    for name, dctx, extra in (("clip-after", ClipAfter(), {}), ("overlap", ctx, dict(overlap_reduce=True, bucket_mb=0.001))):
+        tr = PretrainTrainer(build(dev, gpu).train(), acc_cfg, dist=dctx, **extra)
+        for i in range(2):
+            tr.train_step(data[4 * i:4 * i + 4])
+        if name == "overlap":
+            assert tr.reducer.launched_early == 2
+        acc[name] = tr.opt.flat_p.detach().clone()
+        del tr
+    d2 = (acc["overlap"] - acc["clip-after"]).abs()
+    assert (d2.max().item() == 0.0) if not gpu else ((d2 > 1e-5).float().mean().item() < 0.01), d2.max().item()
     dist.barrier()
     print("PRETRAIN_DP_WORKER_OK", flush=True)
     shutdown_process_group()
