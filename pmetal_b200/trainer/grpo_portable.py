@@ -56,6 +56,10 @@ class _AdaptersOff:
             m.scale = s
 
 
+class _ReferenceHandle:
+    """Stands for "the policy without its adapters" where ``GrpoTrainer.step`` passes a reference model around."""
+
+
 class PortableGrpoTrainer(GrpoTrainer):
     def __init__(self, policy, cfg: GrpoConfig, reward_fn: RewardFn, eos_ids: Sequence[int] = (), pad_id: int = 0,
                  logprob_batch: int = 8):
@@ -66,7 +70,8 @@ class PortableGrpoTrainer(GrpoTrainer):
         if not train:
             raise ValueError("the policy has no trainable parameters (apply_lora_portable first)")
         self.opt = _TorchOpt(train, cfg.learning_rate, cfg.max_grad_norm)
-        self.ref = policy if cfg.beta > 0 else None         # same network, adapters off (see _completion_logps)
+        # the reference policy is this network with its adapters off: a handle that _completion_logps recognises
+        self.ref = _ReferenceHandle() if cfg.beta > 0 else None
         self.pad_id, self.logprob_batch = pad_id, logprob_batch
         self.rollout_weights = None
         self.step_count = 0
@@ -109,30 +114,11 @@ class PortableGrpoTrainer(GrpoTrainer):
     # ------------------------------------------------------------------ log-probabilities of the completion tokens
     def _completion_logps(self, model, seqs: List[List[int]], prompt_lens: List[int], grad: bool):
         """Flat log-probabilities of every completion token (position t predicts token t + 1) and the index of its
-        sequence. ``model is self.ref`` evaluates the policy with its adapters off."""
+        sequence. The reference handle evaluates the policy with its adapters off."""
         import contextlib
-        off = _AdaptersOff(self.policy) if (model is self.ref and not grad) else contextlib.nullcontext()
-        lps, idx = [], []
-        ctx = torch.enable_grad() if grad else torch.no_grad()
-        with off, ctx:
-            for b0 in range(0, len(seqs), self.logprob_batch):
-                part = seqs[b0:b0 + self.logprob_batch]
-                L = max(len(s) for s in part)
-                ids = torch.full((len(part), L), self.pad_id, dtype=torch.int64, device=self.device)
-                rows, cols, tgt = [], [], []
-                for i, s in enumerate(part):
-                    ids[i, :len(s)] = torch.tensor(s, device=self.device)
-                    for t in range(max(prompt_lens[b0 + i], 1), len(s)):
-                        rows.append(i)
-                        cols.append(t - 1)
-                        tgt.append(s[t])
-                        idx.append(b0 + i)
-                if not rows:
-                    continue
-                h = self.policy.forward_hidden(ids)
-                sel = h[torch.tensor(rows, device=self.device), torch.tensor(cols, device=self.device)]
-                lg = self.policy.logits(sel).float()
-                lp = torch.log_softmax(lg, -1).gather(-1, torch.tensor(tgt, device=self.device)[:, None])[:, 0]
-                lps.append(lp)
-        flat = torch.cat(lps) if lps else torch.zeros(0, device=self.device)
-        return flat, torch.tensor(idx, dtype=torch.int64, device=self.device)
+
+        from .logprob_utils import padded_completion_logps
+        is_ref = isinstance(model, _ReferenceHandle)
+        with (_AdaptersOff(self.policy) if is_ref else contextlib.nullcontext()):
+            return padded_completion_logps(self.policy if is_ref else model, seqs, prompt_lens, grad and not is_ref,
+                                           self.logprob_batch, self.pad_id)

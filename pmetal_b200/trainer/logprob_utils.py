@@ -13,9 +13,49 @@ import torch
 from ..ops import functional as ops
 
 
+def is_fast_decoder(model) -> bool:
+    """The hand-written decoder (flat packed token streams) as opposed to a config-driven architecture ([batch, tokens])."""
+    return hasattr(model, "fused_linears") and hasattr(model, "head_weight")
+
+
+def padded_completion_logps(model, seqs: Sequence[Sequence[int]], prompt_lens: Sequence[int], grad: bool,
+                            batch: int = 8, pad_id: int = 0, return_hidden: bool = False):
+    """The same contract for a config-driven architecture: right-padded batches through ``forward_hidden`` and the model's
+    own read-out (logit scale, soft cap) on the completion positions only."""
+    dev = next(model.parameters()).device
+    lps, idx, hid = [], [], []
+    with (torch.enable_grad() if grad else torch.no_grad()):
+        for b0 in range(0, len(seqs), batch):
+            part = seqs[b0:b0 + batch]
+            L = max(len(s) for s in part)
+            ids = torch.full((len(part), L), pad_id, dtype=torch.int64, device=dev)
+            rows, cols, tgt = [], [], []
+            for i, s in enumerate(part):
+                ids[i, :len(s)] = torch.tensor(list(s), device=dev)
+                for t in range(max(prompt_lens[b0 + i], 1), len(s)):
+                    rows.append(i)
+                    cols.append(t - 1)
+                    tgt.append(s[t])
+                    idx.append(b0 + i)
+            if not rows:
+                continue
+            h = model.forward_hidden(ids)
+            sel = h[torch.tensor(rows, device=dev), torch.tensor(cols, device=dev)]
+            lg = model.logits(sel).float()
+            lps.append(torch.log_softmax(lg, -1).gather(-1, torch.tensor(tgt, device=dev)[:, None])[:, 0])
+            hid.append(sel)
+    lp = torch.cat(lps) if lps else torch.zeros(0, device=dev)
+    idx_t = torch.tensor(idx, dtype=torch.int64, device=dev)
+    if return_hidden:
+        return lp, idx_t, (torch.cat(hid) if hid else torch.zeros(0, device=dev))
+    return lp, idx_t
+
+
 def packed_completion_logps(model, seqs: Sequence[Sequence[int]], prompt_lens: Sequence[int], grad: bool,
                             chunk: int = 4096, return_hidden: bool = False):
     """Returns (logps [n_completion_tokens], seq_idx [n_completion_tokens][, hidden of the selected positions])."""
+    if not is_fast_decoder(model):
+        return padded_completion_logps(model, seqs, prompt_lens, grad, return_hidden=return_hidden)
     dev = model.embed_tokens.device
     ids: List[int] = []
     pos: List[int] = []

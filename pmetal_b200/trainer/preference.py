@@ -106,8 +106,9 @@ class PreferenceTrainer:
     def __init__(self, policy, cfg: PreferenceConfig, reference=None, optimizer=None, dist=None):
         from .optimizer import FlatAdamW, attach_shadows
         self.policy, self.ref, self.cfg, self.dist = policy, reference, cfg, dist
-        self.device = policy.embed_tokens.device
-        shadow = torch.bfloat16 if self.device.type == "cuda" else None
+        from .logprob_utils import is_fast_decoder
+        self.device = next(policy.parameters()).device
+        shadow = torch.bfloat16 if (self.device.type == "cuda" and is_fast_decoder(policy)) else None
         self.opt = optimizer or FlatAdamW(policy.named_parameters(), lr=cfg.learning_rate, weight_decay=0.0,
                                           max_grad_norm=cfg.max_grad_norm, shadow_dtype=shadow)
         if dist is not None and getattr(dist, "fused", False):

@@ -281,6 +281,8 @@ def test_grpo_on_a_portable_family_updates_the_adapters_and_keeps_the_reference(
     # reference log-probabilities are those of the base model: the adapters are switched off and back on
     seqs, plens = [prompts[0] + [5, 6, 7]], [len(prompts[0])]
     ref_lp, _ = tr._completion_logps(tr.ref, seqs, plens, grad=False)
+    pol_lp, _ = tr._completion_logps(tr.policy, seqs, plens, grad=False)
+    assert not torch.allclose(pol_lp, ref_lp)                     # the policy itself is scored with its adapters on
     scales = [m.scale for m in lora_modules(model).values()]
     assert all(s != 0.0 for s in scales)
     plain = load_pretrained(d, torch.float32).eval()

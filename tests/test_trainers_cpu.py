@@ -221,3 +221,39 @@ def test_distill_trainer_online_offline_progressive(tmp_path):
     assert temps[0] == 4.0 and temps[-1] == 1.0
     td = DistillTrainer(tiny(14), teacher, DistillConfig(loss_type="taid", total_steps=10))
     assert "taid_alpha" in td.step(ids, ids.clone())
+
+
+def test_preference_trainers_on_a_config_driven_architecture():
+    """DPO with a frozen reference copy, SimPO and KTO drive a Gemma-style model through the padded log-probability path."""
+    from pmetal_b200.models.architectures.generic import GenericDecoderLM, arch_config_from_hf
+
+    def gemma(seed):
+        cfg = dict(model_type="gemma2", vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                   num_attention_heads=4, num_key_value_heads=2, head_dim=8, max_position_embeddings=64,
+                   final_logit_softcapping=30.0)
+        torch.manual_seed(seed)
+        m = GenericDecoderLM(arch_config_from_hf(cfg)).init_weights(0.2, seed)
+        for p in m.parameters():
+            p.requires_grad_(True)
+        return m
+
+    policy, ref = gemma(1), gemma(1)
+    for p in ref.parameters():
+        p.requires_grad_(False)
+    pairs = [PR.PreferencePair([1, 2, 3], [10, 11, 12, 13], [20, 21]), PR.PreferencePair([4, 5], [30, 31], [40, 41, 42])]
+    tr = PR.PreferenceTrainer(policy, PR.PreferenceConfig(beta=0.5, learning_rate=5e-3), ref)
+    first = tr.step(pairs)
+    for _ in range(15):
+        last = tr.step(pairs)
+    assert abs(first["loss"] - math.log(2)) < 1e-4 and last["loss"] < first["loss"] and last["reward_accuracy"] == 1.0
+    t2 = PR.PreferenceTrainer(gemma(2), PR.PreferenceConfig.simpo(learning_rate=5e-3))
+    a = t2.step(pairs)["loss"]
+    for _ in range(10):
+        b = t2.step(pairs)["loss"]
+    assert b < a
+    kt = PR.KtoTrainer(gemma(3), PR.KtoConfig(beta=0.5, learning_rate=5e-3), gemma(3))
+    ex = [PR.KtoExample([1, 2], [5, 6, 7], True), PR.KtoExample([1, 2], [8, 9], False)]
+    a = kt.step(ex)["loss"]
+    for _ in range(10):
+        b = kt.step(ex)["loss"]
+    assert b < a
