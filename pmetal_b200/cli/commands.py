@@ -1236,9 +1236,6 @@ def _grpo_portable(a, model_dir: str, lcfg) -> int:
     from ..trainer.grpo import GrpoConfig
     from ..trainer.grpo_portable import PortableGrpoTrainer
     from ..trainer.rewards import make_reward
-    if a.teacher and a.rlkd_alpha > 0:
-        print("error: --teacher (RLKD) is available for the llama / qwen family only", file=sys.stderr)
-        return 2
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
     model = load_portable(model_dir, torch.bfloat16 if dev.startswith("cuda") else torch.float32, dev)
     apply_lora_portable(model, lcfg)
@@ -1256,7 +1253,20 @@ def _grpo_portable(a, model_dir: str, lcfg) -> int:
         from ..trainer.rewards import combined_reward
         reward = combined_reward([reward, _load_reward_model(a.reward_model, next(model.parameters()).dtype, dev)],
                                  [1.0, a.reward_model_weight])
-    tr = PortableGrpoTrainer(model, cfg, reward, eos_ids=eos, pad_id=tok.pad_token_id or 0)
+    if a.teacher and a.rlkd_alpha > 0:
+        from ..trainer.gspo import portable_rlkd_trainer
+        from ..trainer.orchestrator import _portable_model_dir
+        tdir = _portable_model_dir(a.teacher)
+        if tdir is not None:
+            teacher = load_portable(tdir, next(model.parameters()).dtype, dev).eval()
+        else:
+            from ..models.loader import load_pretrained
+            teacher = load_pretrained(a.teacher, dtype=next(model.parameters()).dtype, device=dev)[0].eval()
+        for p in teacher.parameters():
+            p.requires_grad_(False)
+        tr = portable_rlkd_trainer(model, cfg, reward, teacher, a.rlkd_alpha, eos_ids=eos, pad_id=tok.pad_token_id or 0)
+    else:
+        tr = PortableGrpoTrainer(model, cfg, reward, eos_ids=eos, pad_id=tok.pad_token_id or 0)
     keys = ((a.prompt_column,) if a.prompt_column else ()) + ("prompt", "question", "text", "instruction")
     prompts = _read_prompts(a.dataset, tok, key_order=keys)
     if not prompts:
@@ -1268,7 +1278,8 @@ def _grpo_portable(a, model_dir: str, lcfg) -> int:
     try:
         for step in range(steps):
             batch = [prompts[(step * a.prompts_per_step + j) % len(prompts)] for j in range(a.prompts_per_step)]
-            d = tr.step(batch).__dict__
+            st = tr.step(batch)
+            d = st if isinstance(st, dict) else st.__dict__
             line = json.dumps({"step": step + 1, **{k: (round(v, 5) if isinstance(v, float) else v) for k, v in d.items()
                                                     if isinstance(v, (int, float, str, bool))}})
             print(line, file=sys.stderr)

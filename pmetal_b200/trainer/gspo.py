@@ -143,10 +143,10 @@ class RlkdTrainer(GrpoTrainer):
         keep = [i for i, t in enumerate(res.tokens) if len(t) > 0]
         seqs = [rep[i] + res.tokens[i] for i in keep]
         plens = [len(rep[i]) for i in keep]
-        old_lp, idx = packed_completion_logps(self.policy, seqs, plens, False, c.logprob_chunk)
-        t_lp, _ = packed_completion_logps(self.teacher, seqs, plens, False, c.logprob_chunk)
+        old_lp, idx = self._completion_logps(self.policy, seqs, plens, False)
+        t_lp, _ = packed_completion_logps(self.teacher, seqs, plens, False, c.logprob_chunk)      # either model kind
         self.opt.zero_grad()
-        lp, _ = packed_completion_logps(self.policy, seqs, plens, True, c.logprob_chunk)
+        lp, _ = self._completion_logps(self.policy, seqs, plens, True)
         adv_t = torch.tensor([adv[i] for i in keep], dtype=torch.float32, device=self.device)[idx]
         rl, kl, pol = grpo_loss(lp.float(), old_lp.float().detach(), None, adv_t, torch.ones_like(lp), idx, len(seqs), c)
         # on-policy samples x ~ student: KL(student || teacher) ~ E[log p_s - log p_t]; the teacher-forcing direction
@@ -159,3 +159,16 @@ class RlkdTrainer(GrpoTrainer):
         self.step_count += 1
         return {"loss": float(loss.detach()), "rl_loss": float(rl.detach()), "kd_loss": float(kd.detach()),
                 "mean_reward": sum(rewards) / max(len(rewards), 1)}
+
+
+def portable_rlkd_trainer(policy, cfg: GrpoConfig, reward_fn, teacher, alpha: float = 0.5, **kw):
+    """RLKD for a config-driven policy (adapters from ``lora/portable.py``): the step above on top of the rollouts and
+    log-probabilities of ``PortableGrpoTrainer``; the teacher may be of either kind."""
+    from .grpo_portable import PortableGrpoTrainer
+
+    class PortableRlkdTrainer(PortableGrpoTrainer):
+        step = RlkdTrainer.step
+
+    tr = PortableRlkdTrainer(policy, cfg, reward_fn, **kw)
+    tr.teacher, tr.alpha = teacher, alpha
+    return tr

@@ -420,3 +420,17 @@ def test_python_api_loads_generates_streams_and_saves_a_portable_model(tmp_path)
     again = pm.Model.load(out, device="cpu")
     assert again.generate("hello", max_tokens=6, temperature=0) == text
     assert pm.infer(d, "hello", max_tokens=3, temperature=0) == m.generate("hello", max_tokens=3, temperature=0)
+
+
+def test_rlkd_command_on_a_portable_policy_with_a_portable_teacher(tmp_path, capsys):
+    from pmetal_b200.cli.main import main
+    d = _tiny_gemma_dir(tmp_path)
+    data = tmp_path / "p.jsonl"
+    data.write_text("\n".join(json.dumps({"prompt": f"question {i}"}) for i in range(3)))
+    out = str(tmp_path / "rlkd")
+    assert main(["rlkd", "-m", d, "--teacher", d, "-d", str(data), "-o", out, "--max-steps", "1", "--num-generations", "2",
+                 "--max-completion-length", "4", "--lora-r", "4", "--device", "cpu", "--reward", "length", "--alpha", "0.5",
+                 "--log-metrics", str(tmp_path / "m.jsonl")]) == 0
+    assert os.path.exists(os.path.join(out, "adapter_config.json"))
+    line = json.loads(open(tmp_path / "m.jsonl").read().strip().splitlines()[-1])
+    assert "kd_loss" in line and "rl_loss" in line and line["kd_loss"] >= 0.0
