@@ -1773,11 +1773,40 @@ def cmd_embed_train(a) -> int:
     from ..lora import apply_lora
     from ..lora.adapter import save_adapter
     from ..trainer.embedding import EmbeddingConfig, EmbeddingTrainer
-    model, tok, _, _, _ = _load_for_inference(a)
-    dev = str(model.embed_tokens.device)
+    from ..trainer.orchestrator import _portable_model_dir
     lcfg = LoraConfig(r=a.lora_r, alpha=2.0 * a.lora_r)
-    apply_lora(model, lcfg)
-    model.to(dev).train()
+    pdir = _portable_model_dir(a.model)
+    if pdir is not None:
+        # encoders (BERT / RoBERTa) and config-driven decoders: adapters on their projections, or every weight with --lora-r 0
+        import torch
+
+        from ..data.tokenizer import Tokenizer
+        from ..lora.portable import apply_lora_portable, save_adapter_portable
+        from ..models.architectures import load_pretrained as load_portable, save_pretrained as save_portable
+        dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+        model = load_portable(pdir, torch.float32 if a.lora_r == 0 or not dev.startswith("cuda") else torch.bfloat16, dev)
+        tok = Tokenizer.from_model_dir(pdir)
+        if a.lora_r > 0:
+            lcfg.target_modules = ["q_proj", "k_proj", "v_proj", "o_proj", "query", "key", "value", "dense"]
+            apply_lora_portable(model, lcfg)
+        else:
+            for p_ in model.parameters():
+                p_.requires_grad_(True)
+        model.train()
+
+        def save():
+            if a.lora_r > 0:
+                save_adapter_portable(model, a.output, lcfg, a.model)
+            else:
+                save_portable(model, a.output, copy_from=pdir)
+    else:
+        model, tok, _, _, _ = _load_for_inference(a)
+        dev = str(model.embed_tokens.device)
+        apply_lora(model, lcfg)
+        model.to(dev).train()
+
+        def save():
+            save_adapter(model, a.output, lcfg, a.model)
     rows = []
     with open(a.dataset, "r", encoding="utf-8") as fh:
         for line in fh:
@@ -1798,7 +1827,7 @@ def cmd_embed_train(a) -> int:
                        [r.get("label", 1.0) for r in b] if a.loss == "cosent" else None)
         if a.log_every and (step + 1) % a.log_every == 0:
             print(json.dumps({"step": step + 1, **{k: round(v, 5) for k, v in last.items()}}), file=sys.stderr)
-    save_adapter(model, a.output, lcfg, a.model)
+    save()
     print(json.dumps({"output": a.output, "steps": steps, **last}))
     return 0
 

@@ -60,16 +60,45 @@ class EmbeddingConfig:
 
 class EmbeddingTrainer:
     def __init__(self, model, cfg: EmbeddingConfig = EmbeddingConfig(), optimizer=None):
+        from .logprob_utils import is_fast_decoder
         from .optimizer import FlatAdamW, attach_shadows
         self.model, self.cfg = model, cfg
-        self.device = model.embed_tokens.device
-        shadow = torch.bfloat16 if self.device.type == "cuda" else None
+        self.device = next(model.parameters()).device
+        self.fast = is_fast_decoder(model)
+        shadow = torch.bfloat16 if (self.device.type == "cuda" and self.fast) else None
         self.opt = optimizer or FlatAdamW(model.named_parameters(), lr=cfg.learning_rate, weight_decay=cfg.weight_decay,
                                           max_grad_norm=cfg.max_grad_norm, shadow_dtype=shadow)
         if shadow is not None:
             attach_shadows(model, self.opt)
 
+    def _encode_padded(self, seqs: Sequence[Sequence[int]], grad: bool) -> torch.Tensor:
+        """Encoders (BERT family: ``forward(ids, attention_mask)`` + ``pool``) and config-driven decoders (``forward_hidden``
+        on right-padded rows; causal attention keeps the padding out of the real positions): masked pooling."""
+        rows = [list(s)[: self.cfg.max_length] or [0] for s in seqs]
+        L = max(len(r) for r in rows)
+        ids = torch.zeros(len(rows), L, dtype=torch.int64, device=self.device)
+        mask = torch.zeros(len(rows), L, dtype=torch.int64, device=self.device)
+        for i, r in enumerate(rows):
+            ids[i, :len(r)] = torch.tensor(r, device=self.device)
+            mask[i, :len(r)] = 1
+        mode = self.cfg.pooling
+        with (torch.enable_grad() if grad else torch.no_grad()):
+            if hasattr(self.model, "pool") and not hasattr(self.model, "forward_hidden"):
+                h = self.model(ids, mask)
+                return self.model.pool(h, mask, {"first": "cls"}.get(mode, mode), self.cfg.normalize)
+            h = self.model.forward_hidden(ids).float()
+            m = mask[..., None].float()
+            if mode == "last":
+                e = h[torch.arange(len(rows), device=self.device), mask.sum(1) - 1]
+            elif mode in ("first", "cls"):
+                e = h[:, 0]
+            else:
+                e = (h * m).sum(1) / m.sum(1).clamp(min=1.0)
+            return F.normalize(e, dim=-1) if self.cfg.normalize else e
+
     def encode(self, seqs: Sequence[Sequence[int]], grad: bool = False) -> torch.Tensor:
+        if not self.fast:
+            return self._encode_padded(seqs, grad)
         ids: List[int] = []
         pos: List[int] = []
         cu = [0]

@@ -434,3 +434,60 @@ def test_rlkd_command_on_a_portable_policy_with_a_portable_teacher(tmp_path, cap
     assert os.path.exists(os.path.join(out, "adapter_config.json"))
     line = json.loads(open(tmp_path / "m.jsonl").read().strip().splitlines()[-1])
     assert "kd_loss" in line and "rl_loss" in line and line["kd_loss"] >= 0.0
+
+
+def _tiny_bert_dir(tmp_path):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    torch.manual_seed(0)
+    cfg = tf.BertConfig(vocab_size=300, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                        max_position_embeddings=64)
+    d = tmp_path / "bert"
+    tf.BertModel(cfg).save_pretrained(str(d), safe_serialization=True)
+    vocab = {chr(i) if 32 <= i < 127 else f"<0x{i:02X}>": i for i in range(256)}
+    vocab.update({"[PAD]": 256, "[SEP]": 257, "[CLS]": 258})
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="[PAD]"))
+    tok.pre_tokenizer = pre_tokenizers.Split("", "isolated")
+    tok.save(str(d / "tokenizer.json"))
+    (d / "tokenizer_config.json").write_text(json.dumps({"pad_token": "[PAD]", "sep_token": "[SEP]", "cls_token": "[CLS]"}))
+    return str(d)
+
+
+def test_embedding_training_on_an_encoder_and_a_portable_decoder(tmp_path, capsys):
+    """InfoNCE on a BERT encoder (all weights, then adapters) and on a Gemma decoder: the loss falls, the command writes
+    a model directory or an adapter."""
+    from pmetal_b200.cli.main import main
+    from pmetal_b200.trainer.embedding import EmbeddingConfig, EmbeddingTrainer
+    bert = _tiny_bert_dir(tmp_path)
+    enc = load_pretrained(bert, torch.float32)
+    for p in enc.parameters():
+        p.requires_grad_(True)
+    tr = EmbeddingTrainer(enc.train(), EmbeddingConfig(learning_rate=2e-3, pooling="cls"))
+    g = torch.Generator().manual_seed(1)
+    anchors = [torch.randint(0, 256, (n,), generator=g).tolist() for n in (6, 9, 4, 7)]
+    positives = [a[::-1] for a in anchors]
+    first = tr.step(anchors, positives)["loss"]
+    for _ in range(20):
+        last = tr.step(anchors, positives)["loss"]
+    assert last < 0.7 * first
+    e = tr.encode(anchors)
+    assert e.shape == (4, 32) and torch.allclose(e.norm(dim=-1), torch.ones(4), atol=1e-5)
+    gem = load_pretrained(_tiny_gemma_dir(tmp_path), torch.float32)
+    P.apply_lora_portable(gem, LoraConfig(r=4, alpha=8.0, target_modules=["q_proj", "v_proj", "o_proj"]))
+    t2 = EmbeddingTrainer(gem.train(), EmbeddingConfig(learning_rate=2e-2, pooling="last"))
+    a0 = t2.step(anchors, positives)["loss"]
+    for _ in range(25):
+        b0 = t2.step(anchors, positives)["loss"]
+    assert b0 < a0
+    data = tmp_path / "pairs.jsonl"
+    data.write_text("".join(json.dumps({"anchor": f"query {i}", "positive": f"answer {i}"}) + "\n" for i in range(8)))
+    out = str(tmp_path / "emb_full")
+    assert main(["embed-train", "-m", bert, "-d", str(data), "-o", out, "--max-steps", "3", "--batch-size", "4", "--lora-r", "0",
+                 "--device", "cpu", "--pooling", "mean", "--learning-rate", "1e-3"]) == 0
+    assert os.path.exists(os.path.join(out, "model.safetensors")) and os.path.exists(os.path.join(out, "config.json"))
+    tuned = load_pretrained(out, torch.float32)
+    assert not torch.equal(tuned.encoder.layer[0].attention.self.query.weight,
+                           load_pretrained(bert, torch.float32).encoder.layer[0].attention.self.query.weight)
+    out2 = str(tmp_path / "emb_lora")
+    assert main(["embed-train", "-m", bert, "-d", str(data), "-o", out2, "--max-steps", "2", "--batch-size", "4", "--lora-r", "4",
+                 "--device", "cpu"]) == 0
+    assert os.path.exists(os.path.join(out2, "lora_weights.safetensors"))
