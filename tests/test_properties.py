@@ -110,6 +110,7 @@ def test_stop_suffix_detector_agrees_with_string_search(prefix, stop):
     decode = lambda ids: "".join(chr(i) for i in ids)                      # noqa: E731
     gen = prefix + stop
     cut = detect_stop_suffix(decode, gen, [decode(stop)])
-    assert cut >= 1 and decode(stop) not in decode(gen[:len(gen) - cut])[-len(stop):] or cut == len(stop)
-    assert decode(gen[:len(gen) - cut]) + decode(gen[len(gen) - cut:]) == decode(gen)
-    assert detect_stop_suffix(decode, prefix, ["~~"]) == 0
+    assert cut == len(stop) and decode(gen[len(gen) - cut:]) == decode(stop)      # one character per token here
+    longer = decode(prefix[-1:] + stop) if prefix else decode(stop)
+    assert detect_stop_suffix(decode, gen, [decode(stop), longer]) == len(longer)    # the longest stop that ends the text
+    assert detect_stop_suffix(decode, prefix, ["~~"]) == 0 and detect_stop_suffix(decode, [], [decode(stop)]) == 0
