@@ -163,16 +163,16 @@ class PagedKVCache:
         return need <= len(self.free)
 
     def reserve(self, seq_id: int, n: int) -> List[int]:
-        """Make room for ``n`` more tokens; returns their slots (block*64+offset) and advances the length."""
+        """Make room for ``n`` more tokens; returns their slots (block*64+offset) and advances the length. Work is per
+        block, not per token: only the block that holds the current tail can be shared (copy-on-write), every later
+        block is new."""
         st = self.seqs[seq_id]
-        slots = []
-        for i in range(n):
-            pos = st.length + i
+        slots: List[int] = []
+        pos, end = st.length, st.length + n
+        while pos < end:
             bi = pos // BLOCK
             if bi == len(st.blocks):
                 st.blocks.append(self._take())
-            elif pos % BLOCK == 0 and False:
-                pass
             b = st.blocks[bi]
             if self.ref[b] > 1:          # copy-on-write of a shared, partially filled block
                 nb = self._take()
@@ -184,8 +184,11 @@ class PagedKVCache:
                         self.v_scale[l][nb].copy_(self.v_scale[l][b])
                 self._release(b)
                 st.blocks[bi] = b = nb
-            slots.append(b * BLOCK + pos % BLOCK)
-        st.length += n
+            stop = min(end, (bi + 1) * BLOCK)
+            base = b * BLOCK - bi * BLOCK
+            slots.extend(range(base + pos, base + stop))
+            pos = stop
+        st.length = end
         return slots
 
     def truncate(self, seq_id: int, new_len: int) -> None:
