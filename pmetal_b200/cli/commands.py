@@ -987,7 +987,48 @@ def _quantize_dir(a, mdir: str) -> int:
 
 
 # ------------------------------------------------------------------------------------------- distill / grpo / rlkd
-def _read_prompts(path: str, tok, limit=None, key_order=("prompt", "question", "text", "instruction")):
+def _column_args(p, prompt_column: bool = True) -> None:
+    """Dataset column options shared by ``train``, ``distill``, ``grpo`` and ``rlkd``."""
+    p.add_argument("--text-column", help="dataset field that holds the text")
+    p.add_argument("--text-columns", help="comma-separated fields joined into the text")
+    p.add_argument("--column-separator", default="\n\n", help="what joins --text-columns (and prompt / response)")
+    if prompt_column:
+        p.add_argument("--prompt-column", help="dataset field that holds the prompt")
+    p.add_argument("--response-column", help="dataset field that holds the response")
+
+
+DEFAULT_TEXT_KEYS = ("prompt", "question", "text", "instruction")
+
+
+def record_text(rec, columns=None, key_order=DEFAULT_TEXT_KEYS, with_response: bool = False):
+    """The text of one dataset record under the column options. ``with_response`` appends the response column to the
+    prompt (full sequences for distillation); without it only the prompt side is read (rollout prompts)."""
+    if not isinstance(rec, dict):
+        return str(rec)
+    sep = getattr(columns, "column_separator", None) or "\n\n"
+    names = getattr(columns, "text_columns", None)
+    if names:
+        parts = [str(rec[k]) for k in (n.strip() for n in names.split(",")) if isinstance(rec.get(k), (str, int, float))]
+        if parts:
+            return sep.join(parts)
+    pc, rc = getattr(columns, "prompt_column", None), getattr(columns, "response_column", None)
+    if pc and isinstance(rec.get(pc), str):
+        if with_response and rc and isinstance(rec.get(rc), str):
+            return rec[pc] + sep + rec[rc]
+        return rec[pc]
+    tc = getattr(columns, "text_column", None)
+    if tc and isinstance(rec.get(tc), str):
+        return rec[tc]
+    text = next((rec[k] for k in key_order if isinstance(rec.get(k), str)), None)
+    if text is not None and with_response:
+        resp = next((rec[k] for k in ((rc,) if rc else ()) + ("response", "answer", "output", "completion")
+                     if k and isinstance(rec.get(k), str)), None)
+        if resp is not None and "text" not in rec:
+            return text + sep + resp
+    return text
+
+
+def _read_prompts(path: str, tok, limit=None, key_order=DEFAULT_TEXT_KEYS, columns=None, with_response: bool = False):
     out = []
     with open(path, "r", encoding="utf-8") as fh:
         for line in fh:
@@ -995,8 +1036,7 @@ def _read_prompts(path: str, tok, limit=None, key_order=("prompt", "question", "
             if not line:
                 continue
             try:
-                d = json.loads(line)
-                text = next((d[k] for k in key_order if isinstance(d.get(k), str)), None) if isinstance(d, dict) else str(d)
+                text = record_text(json.loads(line), columns, key_order, with_response)
             except json.JSONDecodeError:
                 text = line
             if text:
@@ -1035,6 +1075,7 @@ def _distill_args(sp):
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--lora-r", type=int, default=0, help="train a LoRA adapter on the student instead of all weights")
     p.add_argument("--lora-alpha", type=float, default=None)
+    _column_args(p)
     p.add_argument("--device")
     return p
 
@@ -1079,7 +1120,7 @@ def cmd_distill(a) -> int:
         for p in student.parameters():
             p.requires_grad_(True)
     student.train()
-    seqs = [s[: a.max_seq_len] for s in _read_prompts(a.dataset, tok) if len(s) > 1]
+    seqs = [s[: a.max_seq_len] for s in _read_prompts(a.dataset, tok, columns=a, with_response=True) if len(s) > 1]
     if not seqs:
         print("error: no usable sequences in dataset", file=sys.stderr)
         return 2
@@ -1181,7 +1222,14 @@ def _grpo_args(sp):
     p.add_argument("--lora-r", type=int, default=16)
     p.add_argument("--lora-alpha", type=float, default=None)
     p.add_argument("--seed", type=int, default=42)
-    p.add_argument("--prompt-column", help="dataset field that holds the prompt")
+    _column_args(p)
+    p.add_argument("--max-seq-len", type=int, default=None,
+                   help="cap on prompt + completion tokens: prompts are cut from the left to leave room for the completion")
+    p.add_argument("--no-flash-attention", action="store_true", help="PyTorch reference attention instead of the kernels")
+    p.add_argument("--reward-model-max-length", type=int, default=2048, help="tokens the reward model reads (cut from the right)")
+    p.add_argument("--reward-model-template", help="text template with {prompt} and {completion} for the reward model")
+    p.add_argument("--grpo-kv-bits", type=int, choices=[4, 8], default=None,
+                   help="rollout key/value cache precision: 8 = int8 blocks, 4 = rotated 4-bit codes (default bf16)")
     p.add_argument("--reward", default="format", choices=["format", "length", "accuracy"])
     p.add_argument("--reasoning-rewards", action="store_true", help="XML format reward + answer accuracy reward")
     p.add_argument("--reward-model", help="add the score of this reward model (decoder + scalar head)")
@@ -1199,12 +1247,12 @@ def _grpo_args(sp):
     return p
 
 
-def _load_reward_model(path: str, dtype, dev):
+def _load_reward_model(path: str, dtype, dev, max_length: int = 2048, template=None, tokenizer=None):
     """A frozen scorer for ``--reward-model``: any supported architecture; the scalar head is read from the checkpoint
     (``score.weight`` / ``v_head.weight`` / ``reward_head.weight``), without one the mean read-out logit is the score."""
     from ..models.loader import load_pretrained, read_state_dict
     from ..trainer.orchestrator import _portable_model_dir
-    from ..trainer.rewards import ModelReward
+    from ..trainer.rewards import ModelReward, RewardModelConfig
     pdir = _portable_model_dir(path)
     if pdir is not None:
         from ..models.architectures import load_pretrained as load_portable
@@ -1218,7 +1266,20 @@ def _load_reward_model(path: str, dtype, dev):
     rm.eval()
     for p in rm.parameters():
         p.requires_grad_(False)
-    return ModelReward(rm, head)
+    if template and tokenizer is None:
+        from ..data.tokenizer import Tokenizer
+        tokenizer = Tokenizer.from_model_dir(rdir)
+    return ModelReward(rm, head, RewardModelConfig(max_length=max_length, template=template), tokenizer)
+
+
+def _grpo_prompt_cap(a) -> int:
+    """Prompt length limit: --max-prompt-length, tightened so that prompt + completion fits --max-seq-len."""
+    cap = a.max_prompt_length
+    if getattr(a, "max_seq_len", None):
+        if a.max_seq_len <= a.max_completion_length:
+            raise SystemExit("error: --max-seq-len must exceed --max-completion-length")
+        cap = min(cap, a.max_seq_len - a.max_completion_length)
+    return cap
 
 
 def _grpo_portable(a, model_dir: str, lcfg) -> int:
@@ -1237,13 +1298,19 @@ def _grpo_portable(a, model_dir: str, lcfg) -> int:
     from ..trainer.grpo_portable import PortableGrpoTrainer
     from ..trainer.rewards import make_reward
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    if getattr(a, "no_flash_attention", False):
+        from ..models.architectures import fast
+        fast.ROUTES.discard("attention")
+    if getattr(a, "grpo_kv_bits", None):
+        print("note: --grpo-kv-bits applies to the paged cache of the llama / qwen path; this architecture keeps bf16 "
+              "rollout caches", file=sys.stderr)
     model = load_portable(model_dir, torch.bfloat16 if dev.startswith("cuda") else torch.float32, dev)
     apply_lora_portable(model, lcfg)
     model.train()
     tok = Tokenizer.from_model_dir(model_dir)
     eos = collect_all_stop_tokens(model_dir, tok, ChatTemplate.from_model_dir(model_dir).eos())
     kw = dict(num_generations=a.num_generations, beta=a.beta, max_completion_length=a.max_completion_length,
-              max_prompt_length=a.max_prompt_length, learning_rate=a.learning_rate)
+              max_prompt_length=_grpo_prompt_cap(a), learning_rate=a.learning_rate)
     cfg = GrpoConfig.dapo(**kw) if a.dapo else GrpoConfig(**kw)
     reward = make_reward(a.reward, tok)
     if a.reasoning_rewards:
@@ -1251,7 +1318,8 @@ def _grpo_portable(a, model_dir: str, lcfg) -> int:
         reward = combined_reward([make_reward("format", tok), make_reward("accuracy", tok, _read_targets(a.dataset))], [1.0, 1.0])
     if a.reward_model:
         from ..trainer.rewards import combined_reward
-        reward = combined_reward([reward, _load_reward_model(a.reward_model, next(model.parameters()).dtype, dev)],
+        reward = combined_reward([reward, _load_reward_model(a.reward_model, next(model.parameters()).dtype, dev,
+                                                                 a.reward_model_max_length, a.reward_model_template)],
                                  [1.0, a.reward_model_weight])
     if a.teacher and a.rlkd_alpha > 0:
         from ..trainer.gspo import portable_rlkd_trainer
@@ -1268,7 +1336,7 @@ def _grpo_portable(a, model_dir: str, lcfg) -> int:
     else:
         tr = PortableGrpoTrainer(model, cfg, reward, eos_ids=eos, pad_id=tok.pad_token_id or 0)
     keys = ((a.prompt_column,) if a.prompt_column else ()) + ("prompt", "question", "text", "instruction")
-    prompts = _read_prompts(a.dataset, tok, key_order=keys)
+    prompts = _read_prompts(a.dataset, tok, key_order=keys, columns=a)
     if not prompts:
         print("error: no prompts in dataset", file=sys.stderr)
         return 2
@@ -1308,12 +1376,15 @@ def cmd_grpo(a) -> int:
     pdir = _portable_model_dir(a.model)
     if pdir is not None:
         return _grpo_portable(a, pdir, lcfg)
+    if getattr(a, "no_flash_attention", False):
+        from ..ops.functional import set_force_reference
+        set_force_reference(True)
     model, tok, _, eos, _ = _load_for_inference(a)
     dev = str(model.embed_tokens.device)
     apply_lora(model, lcfg)
     model.to(dev).train()
     kw = dict(num_generations=a.num_generations, beta=a.beta, max_completion_length=a.max_completion_length,
-              max_prompt_length=a.max_prompt_length, learning_rate=a.learning_rate)
+              max_prompt_length=_grpo_prompt_cap(a), learning_rate=a.learning_rate)
     cfg = GrpoConfig.dapo(**kw) if a.dapo else GrpoConfig(**kw)
     reward = make_reward(a.reward, tok)
     if a.reasoning_rewards:
@@ -1321,7 +1392,8 @@ def cmd_grpo(a) -> int:
         reward = combined_reward([make_reward("format", tok), make_reward("accuracy", tok, _read_targets(a.dataset))], [1.0, 1.0])
     if a.reward_model:
         from ..trainer.rewards import combined_reward
-        reward = combined_reward([reward, _load_reward_model(a.reward_model, next(model.parameters()).dtype, dev)],
+        reward = combined_reward([reward, _load_reward_model(a.reward_model, next(model.parameters()).dtype, dev,
+                                                                 a.reward_model_max_length, a.reward_model_template)],
                                  [1.0, a.reward_model_weight])
     if a.async_rewards:
         reward = _threaded_reward(reward)
@@ -1332,8 +1404,12 @@ def cmd_grpo(a) -> int:
         tr = RlkdTrainer(model, cfg, reward, teacher.eval(), a.rlkd_alpha, eos_ids=eos)
     else:
         tr = GrpoTrainer(model, cfg, reward, eos_ids=eos)
+    if getattr(a, "grpo_kv_bits", None):
+        # rollouts on a quantised paged cache; log-probabilities are recomputed in bf16, so only sampling sees the codes
+        from ..models.generation import Generator
+        tr.gen = Generator(model, cache=model.new_cache(8192, quant={8: "int8", 4: "tq4"}[a.grpo_kv_bits]))
     keys = ((a.prompt_column,) if a.prompt_column else ()) + ("prompt", "question", "text", "instruction")
-    prompts = _read_prompts(a.dataset, tok, key_order=keys)
+    prompts = _read_prompts(a.dataset, tok, key_order=keys, columns=a)
     if not prompts:
         print("error: no prompts in dataset", file=sys.stderr)
         return 2
@@ -1507,6 +1583,15 @@ def _cluster_args(sp):
     p.add_argument("--layers", type=int, default=0, help="accepted for compatibility (the stages exchange activations only)")
     p.add_argument("--vocab", type=int, default=0, help="accepted for compatibility")
     p.add_argument("--timeout", type=float, default=0, help="process-group timeout in seconds")
+    p.add_argument("--min-peers", type=int, default=0, help="fail unless this many GPUs besides the first are present")
+    p.add_argument("--wait", type=float, default=0, help="up: keep printing snapshots for this many seconds")
+    p.add_argument("--status-interval", type=float, default=10, help="up: seconds between snapshots")
+    p.add_argument("--json", action="store_true", help="status: one compact JSON line instead of the indented document")
+    p.add_argument("--no-discovery", action="store_true", help="status: skip the peer-access / NVLink probe")
+    p.add_argument("--gradient-port", type=int, default=0, help="bench: rendezvous port of the worker processes")
+    p.add_argument("--activation-port", type=int, default=0, help="pipeline-bench: rendezvous port of the worker processes")
+    p.add_argument("--discovery-port", type=int, default=0, help="reported in the status document")
+    p.add_argument("--result-port", type=int, default=0, help="reported in the status document")
     p.add_argument("rest", nargs=argparse_remainder())
     return p
 
@@ -1525,8 +1610,12 @@ def cmd_cluster(a) -> int:
         import argparse
         own = argparse.ArgumentParser(add_help=False)
         for flag, typ in (("--gpus", int), ("--mb", int), ("--iters", int), ("--hidden-dim", int), ("--tokens", int),
-                          ("--layers", int), ("--vocab", int), ("--timeout", float)):
+                          ("--layers", int), ("--vocab", int), ("--timeout", float), ("--min-peers", int),
+                          ("--wait", float), ("--status-interval", float), ("--gradient-port", int),
+                          ("--activation-port", int), ("--discovery-port", int), ("--result-port", int)):
             own.add_argument(flag, type=typ, default=None)
+        for flag in ("--json", "--no-discovery"):
+            own.add_argument(flag, action="store_true", default=None)
         known, rest = own.parse_known_args([x for x in a.rest if x != "--"] if a.action not in ("train", "serve") else [])
         for k, v in vars(known).items():
             if v is not None:
@@ -1855,7 +1944,14 @@ def _rlkd_args(sp):
     p.add_argument("--lora-r", type=int, default=16)
     p.add_argument("--lora-alpha", type=float, default=None)
     p.add_argument("--seed", type=int, default=42)
-    p.add_argument("--prompt-column", help="dataset field that holds the prompt")
+    _column_args(p)
+    p.add_argument("--max-seq-len", type=int, default=None,
+                   help="cap on prompt + completion tokens: prompts are cut from the left to leave room for the completion")
+    p.add_argument("--no-flash-attention", action="store_true", help="PyTorch reference attention instead of the kernels")
+    p.add_argument("--reward-model-max-length", type=int, default=2048, help="tokens the reward model reads (cut from the right)")
+    p.add_argument("--reward-model-template", help="text template with {prompt} and {completion} for the reward model")
+    p.add_argument("--grpo-kv-bits", type=int, choices=[4, 8], default=None,
+                   help="rollout key/value cache precision: 8 = int8 blocks, 4 = rotated 4-bit codes (default bf16)")
     p.add_argument("--reward", default="format", choices=["format", "length", "accuracy"])
     p.add_argument("--reasoning-rewards", action="store_true", help="XML format reward + answer accuracy reward")
     p.add_argument("--reward-model", help="add the score of this reward model (decoder + scalar head)")

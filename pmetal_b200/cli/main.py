@@ -140,7 +140,8 @@ def cmd_train(a) -> int:
         job.custom_columns = CustomColumns(a.text_column or "text", a.text_columns.split(",") if a.text_columns else None,
                                            a.column_separator, a.prompt_column, a.response_column)
     if a.no_fused or a.no_flash_attention:
-        os.environ["PMETAL_FORCE_REFERENCE"] = "1"
+        from ..ops.functional import set_force_reference
+        set_force_reference(True)
     if a.no_metal_fused_optimizer:
         job.dp_impl = "nccl"
     for flag in ("ane", "loss_scale"):

@@ -36,6 +36,14 @@ class force_reference:
         _FORCE_REF = self._old
 
 
+def set_force_reference(on: bool = True) -> None:
+    """Process-wide switch to the PyTorch reference operators (``--no-fused`` / ``--no-flash-attention``). The environment
+    variable is set as well so that child processes follow."""
+    global _FORCE_REF
+    _FORCE_REF = bool(on)
+    os.environ["PMETAL_FORCE_REFERENCE"] = "1" if on else "0"
+
+
 def native_enabled(t: torch.Tensor) -> bool:
     """CUDA tensor, native library loaded and the reference path not forced (any dtype)."""
     return (not _FORCE_REF) and t.is_cuda and _native().available()

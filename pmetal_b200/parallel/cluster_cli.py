@@ -26,31 +26,53 @@ def _torchrun(n: int, module_args, port: int = 29611) -> int:
         return 130
 
 
+def _snapshot(a, n: int) -> dict:
+    """The status document: devices, ring order, link classes and the ports in use."""
+    import torch
+
+    from ..utils.sysinfo import system_info
+    from . import discovery
+    info = system_info()
+    probe = torch.cuda.is_available() and not getattr(a, "no_discovery", False)
+    fabric = discovery.probe_fabric(n) if probe else []
+    peers = discovery.discover_local(num_devices=n)
+    info["cluster"] = {"world_size": n, "topology": "nvswitch-all-to-all" if n > 1 else "single",
+                       "ring_order": [p.device for p in discovery.ring_order(peers)],
+                       "links": [[link.name for link in row] for row in fabric],
+                       "ring_bandwidth_gbs": discovery.ring_bandwidth(fabric, list(range(n))) if fabric else 0.0,
+                       "ports": {"gradients": getattr(a, "gradient_port", 0) or discovery.GRADIENT_PORT,
+                                 "discovery": getattr(a, "discovery_port", 0) or discovery.DISCOVERY_PORT,
+                                 "activations": getattr(a, "activation_port", 0) or discovery.GRADIENT_PORT + 1,
+                                 "results": getattr(a, "result_port", 0) or discovery.GRADIENT_PORT + 2}}
+    return info
+
+
 def run(a) -> int:
     import torch
     n = a.gpus or (torch.cuda.device_count() if torch.cuda.is_available() else 0)
+    need = int(getattr(a, "min_peers", 0) or 0) + 1
+    if getattr(a, "min_peers", 0) and n < need:
+        print(f"error: {need} GPUs wanted (--min-peers {need - 1}), {n} present", file=sys.stderr)
+        return 1
     if a.action in ("status", "up"):
-        from ..utils.sysinfo import system_info
-        info = system_info()
-        from . import discovery
-        fabric = discovery.probe_fabric(n) if torch.cuda.is_available() else []
-        peers = discovery.discover_local(num_devices=n)
-        info["cluster"] = {"world_size": n, "topology": "nvswitch-all-to-all" if n > 1 else "single",
-                           "ring_order": [p.device for p in discovery.ring_order(peers)],
-                           "links": [[link.name for link in row] for row in fabric],
-                           "ring_bandwidth_gbs": discovery.ring_bandwidth(fabric, list(range(n))) if fabric else 0.0,
-                           "ports": {"gradients": discovery.GRADIENT_PORT, "discovery": discovery.DISCOVERY_PORT}}
-        print(json.dumps(info, indent=2))
-        return 0
+        import time
+        deadline = time.monotonic() + (float(getattr(a, "wait", 0) or 0) if a.action == "up" else 0.0)
+        while True:
+            print(json.dumps(_snapshot(a, n), indent=None if getattr(a, "json", False) else 2), flush=True)
+            left = deadline - time.monotonic()
+            if left <= 0:
+                return 0
+            time.sleep(min(max(float(getattr(a, "status_interval", 10) or 10), 0.05), left))
     if n < 1:
         print("error: no CUDA devices", file=sys.stderr)
         return 1
     here = os.path.abspath(__file__)
     if a.action == "bench":
-        return _torchrun(n, [here, "bench", str(a.mb), str(a.iters)])
+        return _torchrun(n, [here, "bench", str(a.mb), str(a.iters)], getattr(a, "gradient_port", 0) or 29611)
     if a.action == "pipeline-bench":
         return _torchrun(n, [here, "pipeline", str(a.mb), str(a.iters), str(getattr(a, "hidden_dim", 0) or 0),
-                             str(getattr(a, "tokens", 0) or 0), str(getattr(a, "timeout", 0) or 0)])
+                             str(getattr(a, "tokens", 0) or 0), str(getattr(a, "timeout", 0) or 0)],
+                        getattr(a, "activation_port", 0) or 29611)
     if a.action in ("train", "serve"):
         rest = [x for x in a.rest if x != "--"]
         return _torchrun(n, ["-m", "pmetal_b200.cli.main", a.action] + rest)

@@ -351,3 +351,43 @@ def test_serve_over_two_ranks_answers_http(tmp_path):
         except subprocess.TimeoutExpired:
             os.killpg(p.pid, signal.SIGKILL)
             p.communicate()
+
+
+def test_column_options_select_the_text_of_a_record():
+    from types import SimpleNamespace as NS
+    from pmetal_b200.cli.commands import record_text
+    rec = {"q": "why?", "ctx": "because", "a": "so", "text": "plain"}
+    assert record_text(rec) == "plain"
+    assert record_text(rec, NS(text_column="ctx")) == "because"
+    assert record_text(rec, NS(text_columns="q, ctx", column_separator=" | ")) == "why? | because"
+    assert record_text(rec, NS(prompt_column="q", response_column="a")) == "why?"                      # rollout prompt only
+    assert record_text(rec, NS(prompt_column="q", response_column="a", column_separator="\n"), with_response=True) == "why?\nso"
+    assert record_text({"question": "x", "answer": "y"}, with_response=True) == "x\n\ny"
+    assert record_text("bare") == "bare"
+
+
+def test_grpo_takes_the_reference_flags(model_dir, capsys, tmp_path):
+    data = tmp_path / "p.jsonl"
+    data.write_text("".join(json.dumps({"a": f"part {i}", "b": "and more words to make the prompt long enough"}) + "\n" for i in range(2)))
+    out = str(tmp_path / "g")
+    from pmetal_b200.ops.functional import set_force_reference
+    try:
+        assert main(["grpo", "-m", model_dir, "-d", str(data), "-o", out, "--num-generations", "2", "--max-completion-length", "4",
+                     "--text-columns", "a,b", "--column-separator", " ", "--max-seq-len", "8", "--no-flash-attention",
+                     "--reward-model", model_dir, "--reward-model-max-length", "16",
+                     "--reward-model-template", "Q: {prompt} A: {completion}", "--max-steps", "1", "--device", "cpu"]) == 0
+    finally:
+        set_force_reference(False)                     # the switch is process-wide
+    assert _json_out(capsys)["steps"] == 1
+    with pytest.raises(SystemExit):
+        main(["grpo", "-m", model_dir, "-d", str(data), "-o", out, "--max-completion-length", "4", "--max-seq-len", "4",
+              "--device", "cpu"])
+
+
+def test_cluster_status_flags(capsys):
+    assert main(["cluster", "status", "--json", "--no-discovery", "--result-port", "7"]) == 0
+    doc = json.loads(capsys.readouterr().out.strip())
+    assert doc["cluster"]["ports"]["results"] == 7
+    assert main(["cluster", "up", "--wait", "0.25", "--status-interval", "0.1", "--json"]) == 0
+    assert len(capsys.readouterr().out.strip().splitlines()) >= 2
+    assert main(["cluster", "status", "--min-peers", "64"]) == 1
