@@ -65,7 +65,8 @@ def main(a) -> int:
     from ..models.loader import load_pretrained
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
     dtype = torch.bfloat16 if dev.startswith("cuda") else torch.float32
-    model, args, _ = load_pretrained(a.model, dtype=dtype, device=dev)
+    experts_dir = getattr(a, "experts_dir", None)
+    model, args, _ = load_pretrained(a.model, dtype=dtype, device=dev, experts_dir=experts_dir)
     model.eval()
     for p in model.parameters():
         p.requires_grad_(False)
@@ -74,7 +75,12 @@ def main(a) -> int:
     lens = [sl or 512] * bs if bs else ((sl,) * 4 if sl else (128, 256, 512, 1024))
     prompts = [torch.randint(0, args.vocab_size, (n,), generator=g).tolist() for n in lens]
     out = {"model": a.model, "device": dev, "generation": bench_generation(model, prompts)}
-    if a.what == "workload":
+    store = getattr(model, "expert_store", None)
+    if store is not None:                      # experts streamed from a packed directory: what the reads cost
+        st = store.stats
+        out["expert_io"] = {"reads": st["reads"], "gib": round(st["bytes"] / 2 ** 30, 3),
+                            "read_seconds": round(st["read_seconds"], 3), "prefetch_hit_rate": round(store.hit_rate(), 3)}
+    if a.what == "workload" and store is None:
         out["training"] = bench_training(model, args.vocab_size, samples=bs or 4,
                                          seq_len=sl or (2048 if dev.startswith("cuda") else 256))
     print(json.dumps(out))

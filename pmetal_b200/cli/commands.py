@@ -339,7 +339,12 @@ def _load_for_inference(a):
     from ..models.loader import load_pretrained
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
     dtype = torch.bfloat16 if dev.startswith("cuda") else torch.float32
-    model, args, mdir = load_pretrained(a.model, dtype=dtype, device=dev, seed=getattr(a, "seed", 0) or 0)
+    model, args, mdir = load_pretrained(a.model, dtype=dtype, device=dev, seed=getattr(a, "seed", 0) or 0,
+                                        experts_dir=getattr(a, "experts_dir", None))
+    if getattr(a, "ane", False):
+        print("note: --ane has no effect on this hardware", file=sys.stderr)
+    if getattr(a, "minimal", False):
+        a.backend = "minimal"
     lora = getattr(a, "lora", None)
     if lora:
         from ..lora import apply_lora
@@ -399,6 +404,18 @@ def _add_sampling_flags(p, defaults=None):
     p.add_argument("--greedy", action="store_true")
 
 
+def _add_platform_flags(p, infer: bool = False) -> None:
+    """Expert streaming, and the reference's Apple-only switches (accepted so that its command lines run unchanged)."""
+    p.add_argument("--experts-dir", help="serve the routed experts of a mixture-of-experts model from this "
+                                         "`pack-experts` directory instead of holding them in memory")
+    p.add_argument("--ane", action="store_true", help="ignored: Apple Neural Engine path of the reference")
+    p.add_argument("--ane-max-seq-len", type=int, default=None, help="ignored with --ane")
+    p.add_argument("--ane-real-time", action="store_true", help="ignored with --ane")
+    if infer:
+        p.add_argument("--metal-sampler", action="store_true", help="ignored: sampling already runs on the device")
+        p.add_argument("--minimal", action="store_true", help="same as --backend minimal (eager launches)")
+
+
 # ------------------------------------------------------------------------------------------- infer
 def _infer_args(sp):
     p = sp.add_parser("infer", help="generate text (paged KV cache, optional LoRA, speculative draft)")
@@ -430,6 +447,7 @@ def _infer_args(sp):
     p.add_argument("--profile-output", help="write the --profile-layers table to this JSON file")
     _add_kv_quant_flags(p)
     _add_sampling_flags(p)
+    _add_platform_flags(p, infer=True)
     return p
 
 
@@ -735,6 +753,7 @@ def _serve_args(sp):
     p.add_argument("--adapter", action="append", default=[], metavar="NAME=DIR",
                    help="serve this LoRA adapter beside the base model (repeatable); a request selects it with "
                         "\"adapter\": NAME or \"model\": NAME, and requests with different adapters share a batch")
+    _add_platform_flags(p)
     p.add_argument("--tp", type=int, default=1, help="cut attention heads (and dense feed-forward channels) over N GPUs")
     p.add_argument("--ep", type=int, default=0, help="cut experts over N GPUs (the same ranks as --tp; default: = --tp)")
     p.add_argument("--reduce", choices=["peer", "nccl"], default="nccl",
@@ -2338,6 +2357,7 @@ def _bench_alias_args(sp):
         p.add_argument("-m", "--model", default="random:qwen3-0.6b")
         p.add_argument("--json")
         p.add_argument("--device")
+        p.add_argument("--experts-dir", help="stream the routed experts from this `pack-experts` directory")
         p.set_defaults(func=cmd_bench, what=what)
     p = sp.add_parser("bench-gdn", help="gated delta rule: chunked against token-by-token evaluation")
     p.add_argument("--tokens", type=int, default=512)

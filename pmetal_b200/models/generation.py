@@ -196,7 +196,9 @@ class Generator:
         if cuda_graphs is None:
             import os
             cuda_graphs = os.environ.get("PMETAL_DECODE_GRAPHS", "1") == "1"
-        self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda"
+        # experts streamed from disk are chosen on the host every step: nothing to capture
+        self.cuda_graphs = (bool(cuda_graphs) and self.device.type == "cuda"
+                            and getattr(model, "expert_store", None) is None)
 
     def new_seq(self) -> int:
         sid = self._next_id

@@ -57,8 +57,9 @@ def read_state_dict(model_dir: str) -> Dict[str, torch.Tensor]:
 
 
 def load_pretrained(model: str, dtype: torch.dtype = torch.bfloat16, device="cpu", seed: int = 0,
-                    strict: bool = False) -> Tuple[DecoderLM, ModelArgs, Optional[str]]:
-    """Returns (model, args, model_dir or None)."""
+                    strict: bool = False, experts_dir: Optional[str] = None) -> Tuple[DecoderLM, ModelArgs, Optional[str]]:
+    """Returns (model, args, model_dir or None). With ``experts_dir`` (written by ``pack-experts``) the routed experts are
+    not read from the checkpoint: they are served from that directory on demand (models/expert_store.py)."""
     path = resolve_model_path(model)
     if path.startswith("random:"):
         name = path.split(":", 1)[1]
@@ -78,6 +79,12 @@ def load_pretrained(model: str, dtype: torch.dtype = torch.bfloat16, device="cpu
         with open(os.path.join(path, "config.json"), "r", encoding="utf-8") as fh:
             qcfg = json.load(fh).get("quantization") or {"bits": 4, "group_size": 64}
         sd = load_quantized_state_dict(sd, qcfg, torch.float32)
+    if experts_dir:
+        from .expert_store import enable_expert_offloading
+        sd = {k: v for k, v in sd.items() if ".experts." not in k and ".switch_mlp." not in k}
+        m.load_hf_state_dict(sd, strict=False)
+        enable_expert_offloading(m, experts_dir)
+        return _cast(m, dtype, device), args, path
     m.load_hf_state_dict(sd, strict=strict)
     return _cast(m, dtype, device), args, path
 

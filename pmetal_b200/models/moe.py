@@ -60,7 +60,10 @@ class SparseMoeBlock(nn.Module):
             out = eng.forward(x.to(torch.bfloat16), logits).to(x.dtype)
             return out if residual is None else out + residual
         w, idx = route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
-        if self.ep_group is not None and getattr(self, "ep_train", False):
+        if getattr(self, "offload", None) is not None:
+            from .expert_store import offloaded_experts_forward
+            out = offloaded_experts_forward(self, x, w, idx)     # experts read from a packed directory on demand
+        elif self.ep_group is not None and getattr(self, "ep_train", False):
             from ..parallel.ep_train import ep_moe_train_forward
             out = ep_moe_train_forward(self, x, w, idx)          # sharded expert parameters, differentiable exchange
         elif self.ep_group is not None:
@@ -75,6 +78,8 @@ class SparseMoeBlock(nn.Module):
         return ops.moe_experts(x, w, idx, self.gate_up, self.down)
 
     def hf_state_dict(self) -> Dict[str, torch.Tensor]:
+        if getattr(self, "offload", None) is not None:
+            raise RuntimeError("the experts of this block live in a packed directory and cannot be exported from here")
         I = self.cfg.moe_intermediate_size
         sd = {"gate.weight": self.router.detach()}
         for e in range(self.cfg.num_experts):
