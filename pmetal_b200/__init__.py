@@ -7,7 +7,8 @@ normalisation/activation/loss/optimizer kernels and peer-memory collectives).
 __version__ = "0.1.0"
 
 
-_API = ("finetune", "infer", "Model", "Trainer", "GenerationConfig", "DataLoaderConfig", "download_model", "download_file")
+_API = ("finetune", "infer", "Model", "Trainer", "GenerationConfig", "DataLoaderConfig", "download_model", "download_file",
+        "DFlashGenerator")
 _LAZY = {"LoraConfig": "core.config", "TrainingConfig": "core.config", "ModelConfig": "core.config",
          "DatasetConfig": "core.config", "Dtype": "core.types", "Quantization": "core.types", "LoraBias": "core.types",
          "LrSchedulerType": "core.types", "OptimizerType": "core.types", "DatasetFormat": "core.types",

@@ -73,6 +73,18 @@ class Model:
         return cls(m, tok, tpl, collect_all_stop_tokens(model_dir, tok, tpl.eos()), model_dir)
 
     @property
+    def architecture(self) -> str:
+        """The ``model_type`` of the checkpoint (llama, qwen3, qwen3_moe, gemma3, ...)."""
+        for holder in (getattr(self.model, "cfg", None), getattr(self.model, "c", None)):
+            mt = getattr(holder, "model_type", None)
+            if mt:
+                return str(mt)
+        cfg = getattr(self.model, "config", None)
+        if isinstance(cfg, dict) and cfg.get("model_type"):
+            return str(cfg["model_type"])
+        return type(self.model).__name__
+
+    @property
     def portable(self) -> bool:
         return not hasattr(self.model, "fused_linears")
 
@@ -243,3 +255,45 @@ def download_file(model_id: str, filename: str, revision: str = "main", token: O
                   cache_dir: Optional[str] = None) -> str:
     from . import hub
     return hub.download_file(model_id, filename, dest_dir=cache_dir, revision=revision, token=token)
+
+
+class DFlashGenerator:
+    """Speculative generation with a DFlash block-diffusion draft (crates/pmetal-py/src/dflash.rs). ``generate`` takes
+    and returns token ids: (prompt + generated tokens, acceptance metrics). Verification is greedy, so the output equals
+    plain greedy decoding of the target."""
+
+    def __init__(self, target_model: str, draft_model: str, device: Optional[str] = None):
+        import torch
+
+        from .models.dflash import DFlashDecoder, load_dflash_pair
+        from .models.loader import is_hf_id, resolve_model_path
+        self.device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+        resolve = lambda m: m if m == "random" or m.startswith("random:") or not is_hf_id(m) else resolve_model_path(m)
+        self.target_model, self.draft_model = target_model, draft_model
+        self.target, self.draft, self.tokenizer = load_dflash_pair(resolve(target_model), resolve(draft_model), self.device)
+        self.decoder = DFlashDecoder(self.target, self.draft)
+
+    def generate(self, prompt_ids, max_new_tokens: int = 256, temperature: float = 0.0, stop_tokens=None,
+                 speculative_tokens: Optional[int] = None, tree_budget: int = 0):
+        if temperature > 0:
+            raise ValueError("block-diffusion drafting verifies greedily: temperature must be 0")
+        import time
+        from .models.dflash import DFlashStats
+        self.decoder.stats = DFlashStats()
+        stops = tuple(stop_tokens or ())
+        t0 = time.perf_counter()
+        if tree_budget > 0:
+            new = self.decoder.generate_tree(list(prompt_ids), max_new_tokens, tree_budget, speculative_tokens, stops)
+        else:
+            new = self.decoder.generate(list(prompt_ids), max_new_tokens, speculative_tokens, stops)
+        dt = time.perf_counter() - t0
+        st = self.decoder.stats
+        return list(prompt_ids) + new, {"generated_tokens": len(new), "steps": len(st.acceptance_lengths),
+                                         "avg_acceptance_length": st.avg_acceptance_length,
+                                         "acceptance_rate": st.acceptance_rate, "tokens_per_s": len(new) / max(dt, 1e-9)}
+
+    def close(self) -> None:
+        self.decoder.close()
+
+    def __repr__(self) -> str:
+        return f"DFlashGenerator(target={self.target_model!r}, draft={self.draft_model!r}, device={self.device!r})"

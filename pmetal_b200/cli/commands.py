@@ -1249,6 +1249,8 @@ def _grpo_args(sp):
     p.add_argument("--reward-model-template", help="text template with {prompt} and {completion} for the reward model")
     p.add_argument("--grpo-kv-bits", type=int, choices=[4, 8], default=None,
                    help="rollout key/value cache precision: 8 = int8 blocks, 4 = rotated 4-bit codes (default bf16)")
+    p.add_argument("--vlm", action="store_true", help="image-conditioned rollouts (not available: the command stops with a message)")
+    p.add_argument("--max-image-size", type=int, default=336, help="with --vlm")
     p.add_argument("--reward", default="format", choices=["format", "length", "accuracy"])
     p.add_argument("--reasoning-rewards", action="store_true", help="XML format reward + answer accuracy reward")
     p.add_argument("--reward-model", help="add the score of this reward model (decoder + scalar head)")
@@ -1392,6 +1394,10 @@ def cmd_grpo(a) -> int:
     from ..trainer.orchestrator import _portable_model_dir
     from ..trainer.rewards import make_reward
     lcfg = LoraConfig(r=a.lora_r, alpha=a.lora_alpha if getattr(a, 'lora_alpha', None) else 2.0 * a.lora_r)
+    if getattr(a, "vlm", False):
+        print("error: --vlm (rollouts conditioned on images) is not available; the vision towers load and run "
+              "(models/architectures/vision.py, mllama.py) but the GRPO trainers take text prompts only", file=sys.stderr)
+        return 2
     pdir = _portable_model_dir(a.model)
     if pdir is not None:
         return _grpo_portable(a, pdir, lcfg)
@@ -2097,38 +2103,13 @@ def cmd_dflash(a) -> int:
 
     import torch
 
-    from ..models.architectures.generic import GenericDecoderLM
-    from ..models.dflash import DFlashConfig, DFlashDecoder, DFlashDraftModel
-    from ..models.loader import read_state_dict
+    from ..models.dflash import DFlashDecoder, load_dflash_pair
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
     if a.temperature > 0:
         print("error: block-diffusion drafting verifies greedily; use --temperature 0", file=sys.stderr)
         return 2
-    if a.model.startswith("random:"):
-        from ..models.config import preset
-        cfg = preset(a.model.split(":", 1)[1]).to_hf_dict()
-        target = GenericDecoderLM.from_hf_config(cfg).init_weights(0.02, 0)
-        tok = None
-    else:
-        from ..data.tokenizer import load_tokenizer
-        with open(os.path.join(a.model, "config.json"), "r", encoding="utf-8") as fh:
-            cfg = json.load(fh)
-        target = GenericDecoderLM.from_hf_config(cfg)
-        target.load_state_dict(read_state_dict(a.model), strict=False)
-        tok = load_tokenizer(a.model)
-    target = target.to(dev).eval()
+    target, draft, tok = load_dflash_pair(a.model, a.draft, dev)
     c = target.c
-    if a.draft == "random":
-        n = c.num_layers
-        dc = DFlashConfig(c.hidden_size, 2, c.intermediate_size, c.n_heads, c.n_kv_heads, c.head_dim, c.vocab_size,
-                          sorted({n // 3, (2 * n) // 3, n - 1}), c.vocab_size - 1, c.norm_eps, c.rope_theta, 8)
-        draft = DFlashDraftModel(dc)
-    else:
-        with open(os.path.join(a.draft, "config.json"), "r", encoding="utf-8") as fh:
-            dc = DFlashConfig.from_dict(json.load(fh))
-        draft = DFlashDraftModel(dc)
-        draft.load_hf_state_dict(read_state_dict(a.draft), strict=False)
-    draft = draft.to(dev).eval()
     prompt = tok.encode(a.prompt) if tok is not None else [min(ord(ch), c.vocab_size - 2) for ch in a.prompt]
     dec = DFlashDecoder(target, draft)
     t0 = time.time()

@@ -53,6 +53,23 @@ class Tokenizer:
             bos = c.get("bos_token_id", bos)
         return cls(tok, bos, eos, pad, eos_s)
 
+    @classmethod
+    def from_pretrained(cls, model_id: str) -> "Tokenizer":
+        """From a model directory, a ``tokenizer.json`` path, or a hub id that is in the local cache (or can be fetched)."""
+        if os.path.isfile(model_id):
+            return cls.from_file(model_id)
+        if os.path.isdir(model_id):
+            return cls.from_model_dir(model_id)
+        from ..models.loader import resolve_model_path
+        return cls.from_model_dir(resolve_model_path(model_id))
+
+    @property
+    def unk_token_id(self) -> Optional[int]:
+        if self._tok is None:
+            return None
+        unk = getattr(getattr(self._tok, "model", None), "unk_token", None)
+        return self._tok.token_to_id(unk) if unk else None
+
     @property
     def vocab_size(self) -> int:
         return self._tok.get_vocab_size(with_added_tokens=True)

@@ -320,3 +320,35 @@ class DFlashDecoder:
                     break
             hidden = vhidden[:, :accepted_inputs]
         return out[:max_new_tokens]
+
+
+def load_dflash_pair(target_model: str, draft_model: str, device: str):
+    """(target, draft, tokenizer or None): the target is ``random:<preset>`` or a checkpoint directory, the draft a
+    DFlash checkpoint directory or ``random`` (a two-layer draft sized from the target, for smoke runs)."""
+    import json
+    import os
+
+    from .loader import read_state_dict
+    if target_model.startswith("random:"):
+        from .config import preset
+        target = GenericDecoderLM.from_hf_config(preset(target_model.split(":", 1)[1]).to_hf_dict()).init_weights(0.02, 0)
+        tok = None
+    else:
+        from ..data.tokenizer import load_tokenizer
+        with open(os.path.join(target_model, "config.json"), "r", encoding="utf-8") as fh:
+            target = GenericDecoderLM.from_hf_config(json.load(fh))
+        target.load_state_dict(read_state_dict(target_model), strict=False)
+        tok = load_tokenizer(target_model)
+    target = target.to(device).eval()
+    c = target.c
+    if draft_model == "random":
+        n = c.num_layers
+        dc = DFlashConfig(c.hidden_size, 2, c.intermediate_size, c.n_heads, c.n_kv_heads, c.head_dim, c.vocab_size,
+                          sorted({n // 3, (2 * n) // 3, n - 1}), c.vocab_size - 1, c.norm_eps, c.rope_theta, 8)
+        draft = DFlashDraftModel(dc)
+    else:
+        with open(os.path.join(draft_model, "config.json"), "r", encoding="utf-8") as fh:
+            dc = DFlashConfig.from_dict(json.load(fh))
+        draft = DFlashDraftModel(dc)
+        draft.load_hf_state_dict(read_state_dict(draft_model), strict=False)
+    return target, draft.to(device).eval(), tok
