@@ -44,7 +44,9 @@ async function draw(){nav();clearInterval(timer);const m=document.getElementById
  if(cur==='System'){m.append($('pre',{text:JSON.stringify(await j('/api/system'),null,1)}));return}
  if(cur==='Models'||cur==='Datasets'){const rows=await j('/api/'+cur.toLowerCase());const t=$('table');
   rows.forEach(r=>t.append($('tr',{},$('td',{text:r.source||r.bytes||''}),$('td',{text:r.id||r.path}),$('td',{},$('button',{text:'use',on:{click:()=>{
-   const keys=cur==='Models'?['model','student','base']:['dataset','data','input'];for(const c in specs)for(const f of specs[c].fields)if(keys.includes(f.name)&&f.kind==='string'){(values[c]=values[c]||{})[f.name]=r.id||r.path;break}}}})))));m.append(t);return}
+   const keys=cur==='Models'?['model','student','base']:['dataset','data','input'];for(const c in specs)for(const f of specs[c].fields)if(keys.includes(f.name)&&f.kind==='string'){(values[c]=values[c]||{})[f.name]=r.id||r.path;break}}}}),
+   $('button',{text:cur==='Models'?'info':'columns',on:{click:async()=>{const u=cur==='Models'?'/api/models/info?path='+encodeURIComponent(r.path||r.id):'/api/datasets/columns?path='+encodeURIComponent(r.path);
+    try{det.textContent=JSON.stringify(await j(u),null,1)}catch(e){det.textContent=String(e)}}}})))));const det=$('pre');m.append(t,det);return}
  if(cur==='Jobs'){const show=async()=>{const js=await j('/api/jobs');const t=$('table',{},$('tr',{},...['id','command','state','step','loss','elapsed',''].map(h=>$('th',{text:h}))));
    js.forEach(x=>t.append($('tr',{},$('td',{text:x.id}),$('td',{text:x.command}),$('td',{text:x.state}),$('td',{text:x.metrics.step??''}),$('td',{text:x.metrics.loss?.toFixed?.(4)??''}),$('td',{text:x.elapsed.toFixed(1)+' s'}),
     $('td',{},$('button',{text:'monitor',on:{click:()=>{watch=x.id;cur='Monitor';draw()}}}),$('button',{text:'cancel',on:{click:()=>j(`/api/jobs/${x.id}/cancel`,{method:'POST'}).then(show)}})))));m.innerHTML='';m.append(t)};await show();timer=setInterval(show,1500);return}
@@ -62,7 +64,7 @@ let tabs2cmd={};
 </script></body></html>"""
 
 
-def create_app(runner: Optional[JobRunner] = None, model_roots=None, dataset_roots=None):
+def create_app(runner: Optional[JobRunner] = None, model_roots=None, dataset_roots=None, settings_path: Optional[str] = None):
     from fastapi import FastAPI, HTTPException
     from fastapi.responses import HTMLResponse
 
@@ -156,10 +158,16 @@ def create_app(runner: Optional[JobRunner] = None, model_roots=None, dataset_roo
             runner.cancel(j)
             return job_view(j)
 
+    import os
+
+    from .library import Settings, register
+    register(app, runner, Settings(settings_path or os.path.join(runner.workdir, "settings.json")), model_roots, dataset_roots)
     return app
 
 
 def serve_gui(host: str = "127.0.0.1", port: int = 8090, workdir: Optional[str] = None) -> int:
     import uvicorn
-    uvicorn.run(create_app(JobRunner(workdir=workdir)), host=host, port=port, log_level="info")
+    import os
+    settings = os.path.join(os.path.expanduser(os.environ.get("PMETAL_CONFIG_DIR", "~/.config/pmetal")), "gui.json")
+    uvicorn.run(create_app(JobRunner(workdir=workdir), settings_path=settings), host=host, port=port, log_level="info")
     return 0

@@ -65,3 +65,70 @@ def test_jobs_start_follow_fail_and_cancel(client):
     assert client.get("/api/jobs/99").status_code == 404
     assert [j["id"] for j in client.get("/api/jobs").json()] == [jid]
     assert client.post(f"/api/jobs/{jid}/cancel").json()["state"] == "finished"          # nothing left to cancel
+
+
+def test_settings_directories_and_dashboard(client, tmp_path):
+    cfg = client.get("/api/config").json()
+    assert cfg["model_directories"] == [] and cfg["default_lora_r"] == 16
+    assert client.put("/api/config", json={"default_lora_r": 32, "default_learning_rate": 1}).json()["default_lora_r"] == 32
+    assert client.get("/api/config").json()["default_learning_rate"] == 1.0
+    assert client.put("/api/config", json={"nonsense": 1}).status_code == 422
+    assert client.put("/api/config", json={"default_lora_r": "many"}).status_code == 422
+    lib = tmp_path / "lib"
+    (lib / "m1").mkdir(parents=True)
+    (lib / "m1" / "config.json").write_text('{"model_type": "qwen3", "hidden_size": 64, "num_hidden_layers": 2, "vocab_size": 100}')
+    assert client.post("/api/model-directories", json={"path": str(lib / "absent")}).status_code == 404
+    assert client.post("/api/model-directories", json={"path": str(lib)}).json() == [str(lib)]
+    assert client.post("/api/model-directories", json={"path": str(lib)}).json() == [str(lib)]          # no duplicates
+    ids = [m["id"] for m in client.get("/api/library/models").json()]
+    assert str(lib / "m1") in ids
+    d = client.get("/api/dashboard").json()
+    assert d["models"] >= 1 and d["presets"] > 0 and d["datasets"] >= 1 and d["jobs_total"] == 0
+    info = client.get("/api/models/info", params={"path": str(lib / "m1")}).json()
+    assert info["model_type"] == "qwen3" and info["num_layers"] == 2 and info["parameters"] is None and info["bytes"] > 0
+    assert client.get("/api/models/info", params={"path": str(lib / "nothing")}).status_code == 404
+    assert client.get("/api/models/info", params={"path": "random:tiny-qwen3"}).json()["model_type"] == "qwen3"
+    dft = client.get("/api/models/defaults", params={"path": str(lib / "m1")}).json()
+    assert "temperature" in dft["sampling"] and dft["training"]["lora_r"] == 16
+    # deletion: only direct children of registered directories
+    assert client.delete("/api/models", params={"path": str(tmp_path / "jobs")}).status_code == 403
+    assert client.delete("/api/models", params={"path": str(lib)}).status_code == 403
+    gone = client.delete("/api/models", params={"path": str(lib / "m1")}).json()
+    assert gone["deleted"] == str(lib / "m1") and not (lib / "m1").exists()
+    assert client.delete("/api/model-directories", params={"path": str(lib)}).json() == []
+
+
+def test_parameter_count_comes_from_the_file_headers(tmp_path):
+    import torch
+
+    from pmetal_b200.gui.library import model_info
+    from pmetal_b200.utils import safetensors_io as st
+    (tmp_path / "config.json").write_text('{"model_type": "llama"}')
+    st.save_file({"a": torch.zeros(3, 5), "b": torch.zeros(7)}, str(tmp_path / "model.safetensors"))
+    assert model_info(str(tmp_path))["parameters"] == 22
+
+
+def test_dataset_columns_adapters_and_merge_methods(client, tmp_path):
+    (tmp_path / "qa.jsonl").write_text('{"question": "why", "answer": "so", "meta": {"k": 1}}\n{"question": "how", "extra": 3}\n')
+    c = client.get("/api/datasets/columns", params={"path": str(tmp_path / "qa.jsonl")}).json()
+    assert [x["name"] for x in c["columns"]] == ["question", "answer", "meta", "extra"] and c["rows_read"] == 2
+    assert c["suggested_text_column"] == "question"
+    (tmp_path / "t.csv").write_text("text,label\nhello,1\n")
+    c = client.get("/api/datasets/columns", params={"path": str(tmp_path / "t.csv")}).json()
+    assert c["suggested_text_column"] == "text" and c["columns"][1]["sample"] == "1"
+    assert client.get("/api/datasets/columns", params={"path": str(tmp_path / "none.jsonl")}).status_code == 404
+    run = tmp_path / "jobs" / "run1"
+    run.mkdir()
+    (run / "adapter_config.json").write_text('{"r": 8, "lora_alpha": 16, "base_model_name_or_path": "random:tiny-qwen3"}')
+    ad = client.get("/api/adapters").json()
+    assert ad and ad[0]["path"] == str(run) and ad[0]["r"] == 8
+    methods = client.get("/api/merge-strategies").json()
+    assert "ties" in methods and "slerp" in methods and len(methods) >= 16
+
+
+def test_hub_routes_answer_without_a_network(client, monkeypatch):
+    monkeypatch.setenv("HF_ENDPOINT", "http://127.0.0.1:9")            # nothing listens there
+    assert client.get("/api/hub/models", params={"query": "qwen"}).status_code == 503
+    r = client.post("/api/hub/download", json={"model": "org/name", "revision": "main"}).json()
+    assert r["command"] == "download" and r["argv"] == ["download", "org/name", "--revision", "main"]
+    assert client.post("/api/hub/download", json={}).status_code == 422
