@@ -1591,7 +1591,9 @@ def _bench_args(sp):
 def cmd_bench(a) -> int:
     if a.what == "corpus":
         from ..bench import kernels
-        argv = ["--iters", str(a.iters)] + (["--case"] + a.case if a.case else []) + (["--json", a.json] if a.json else [])
+        iters = a.iters if a.iters is not None else (3 if getattr(a, "quick", False) else 10)
+        path = getattr(a, "output", None) or (a.json if isinstance(a.json, str) else None)
+        argv = ["--iters", str(iters)] + (["--case"] + a.case if a.case else []) + (["--json", path] if path else [])
         return kernels.main(argv) or 0
     from ..bench import workload
     return workload.main(a) or 0
@@ -1710,6 +1712,7 @@ def _ollama_args(sp):
     p.add_argument("--num-ctx", type=int)
     p.add_argument("--template", default=None, help="default: detected from the model name")
     p.add_argument("--system")
+    p.add_argument("--license", help="license text written as the LICENSE block")
     p.add_argument("-o", "--output", default="Modelfile")
     _add_sampling_flags(p, {"temperature": 0.7, "top_k": 40, "top_p": 0.95, "repetition_penalty": 1.1})
     return p
@@ -1734,7 +1737,7 @@ def cmd_ollama(a) -> int:
         except ValueError as e:
             print(f"error: {e}", file=sys.stderr)
             return 2
-    print(write_modelfile(a.gguf, a.output, a.template or detect_template(a.gguf), a.system, a.lora,
+    print(write_modelfile(a.gguf, a.output, a.template or detect_template(a.gguf), a.system, a.lora, a.license,
                           temperature=a.temperature, top_k=a.top_k, top_p=a.top_p, repeat_penalty=a.repetition_penalty,
                           num_ctx=a.num_ctx))
     if a.action == "create":
@@ -2242,7 +2245,8 @@ def cmd_pack_experts(a) -> int:
 # ------------------------------------------------------------------------------------------- dashboard / tui
 def _dash_args(sp):
     p = sp.add_parser("dashboard", help="follow a job-event file (--log-events output) and print progress lines")
-    p.add_argument("events", help="JSON-lines event file")
+    p.add_argument("events", nargs="?", help="JSON-lines event file")
+    p.add_argument("-m", "--metrics-file", help="a --log-metrics file (one JSON object per step) instead of an event file")
     p.add_argument("--once", action="store_true", help="print the summary of what is there and exit")
     p.add_argument("--interval", type=float, default=1.0)
     p.set_defaults(func=cmd_dashboard)
@@ -2291,6 +2295,13 @@ def summarise_events(lines) -> dict:
             ev = json.loads(ln)
         except ValueError:
             continue
+        if isinstance(ev, dict) and "event" not in ev and "step" in ev:
+            # a plain metrics line (--log-metrics): the file is one job
+            j = jobs.setdefault("metrics", {"state": "running", "kind": "metrics"})
+            for k in ("step", "loss", "lr", "tokens_per_s", "tok_per_s", "grad_norm", "eval_loss", "reward", "kl"):
+                if k in ev:
+                    j[k] = ev[k]
+            continue
         j = jobs.setdefault(ev.get("job_id", "?"), {"state": "running"})
         kind = ev.get("event")
         if kind == "started":
@@ -2311,6 +2322,11 @@ def summarise_events(lines) -> dict:
 
 def cmd_dashboard(a) -> int:
     import time
+    if getattr(a, "metrics_file", None):
+        a.events = a.metrics_file
+    if not a.events:
+        print("error: an event file or --metrics-file is needed", file=sys.stderr)
+        return 2
     seen = 0
     lines = []
     while True:
@@ -2334,15 +2350,46 @@ def _bench_alias_args(sp):
     for name, what in (("bench-corpus", "corpus"), ("bench-workload", "workload"), ("bench-gen", "gen")):
         p = sp.add_parser(name, help=f"same as: bench {what}")
         p.add_argument("--case", nargs="*")
-        p.add_argument("--iters", type=int, default=10)
+        p.add_argument("--iters", type=int, default=None)
         p.add_argument("-m", "--model", default="random:qwen3-0.6b")
-        p.add_argument("--json")
+        p.add_argument("--json", nargs="?", const=True, default=None,
+                       help="the result is always printed as JSON; with a path it is also written there")
+        p.add_argument("-o", "--output", help="write the JSON report to this file")
         p.add_argument("--device")
         p.add_argument("--experts-dir", help="stream the routed experts from this `pack-experts` directory")
+        if what == "corpus":
+            p.add_argument("--quick", action="store_true", help="fewer iterations per kernel case")
+        else:
+            from ..bench.workload import PRESETS
+            p.add_argument("--preset", choices=sorted(PRESETS), help="named set of the shape options below")
+            p.add_argument("--dataset", help="JSON-lines file to take prompts and training documents from (default: synthetic tokens)")
+            p.add_argument("--prompt-samples", type=int, default=None, help="prompts in the inference part")
+            p.add_argument("--max-prompt-tokens", type=int, default=None, help="cut prompts to this length (0: 1024)")
+            p.add_argument("--inference-context", choices=["auto", "prompt", "text-prefix"], default="auto",
+                           help="with --dataset: prompts are the prompt column only, or a prefix of the whole record (auto)")
+            p.add_argument("--decode-steps", type=int, default=None)
+            p.add_argument("--inference-warmup-passes", type=int, default=None, help="untimed passes per session")
+            p.add_argument("--inference-session-repeats", type=int, default=None, help="independent sessions (fresh cache)")
+            p.add_argument("--inference-repeats", type=int, default=None, help="timed passes per session")
+            p.add_argument("--train-samples", type=int, default=None, help="sequences per training step")
+            p.add_argument("--train-steps", type=int, default=None)
+            p.add_argument("--batch-size", type=int, default=None)
+            p.add_argument("--max-seq-len", "--seq-len", dest="seq_len", type=int, default=None)
         p.set_defaults(func=cmd_bench, what=what)
-    p = sp.add_parser("bench-gdn", help="gated delta rule: chunked against token-by-token evaluation")
+    p = sp.add_parser("bench-gdn", help="gated delta rule layer: projections and the recurrent update, backend against backend")
+    p.add_argument("-m", "--model", help="Qwen3-Next style checkpoint directory to take the layer shapes from")
+    p.add_argument("--stage", choices=["input-proj", "out-proj", "prefill"], default="prefill",
+                   help="input-proj: the four input projections, one concatenated GEMM against four; out-proj: the output "
+                        "projection; prefill: the recurrent update, chunked against token by token")
+    p.add_argument("--layer", type=int, default=None, help="accepted for compatibility: all GDN layers share one shape")
+    p.add_argument("--batch-size", type=int, default=1)
+    p.add_argument("--seq-len", type=int, default=None, help="tokens (same as --tokens)")
     p.add_argument("--tokens", type=int, default=512)
     p.add_argument("--heads", type=int, default=8)
+    p.add_argument("--warmup-iterations", type=int, default=2)
+    p.add_argument("--benchmark-iterations", type=int, default=5)
+    p.add_argument("--json", action="store_true", help="the result is always JSON")
+    p.add_argument("-o", "--output", help="write the JSON report to this file")
     p.add_argument("--device")
     p.set_defaults(func=cmd_bench_gdn)
     p = sp.add_parser("bench-ffi", help="cost of one call into the native host library")
@@ -2365,24 +2412,79 @@ def cmd_bench_gdn(a) -> int:
 
     from ..models.gdn import gdn_chunked, gdn_recurrent
     dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
-    T, H, d = a.tokens, a.heads, 64
+    shape = {"hidden_size": 2048, "linear_num_key_heads": 16, "linear_num_value_heads": 32, "linear_key_head_dim": 128,
+             "linear_value_head_dim": 128}
+    if a.model and os.path.isfile(os.path.join(a.model, "config.json")):
+        with open(os.path.join(a.model, "config.json"), "r", encoding="utf-8") as fh:
+            cfg = json.load(fh)
+        cfg = cfg.get("text_config") or cfg
+        shape.update({k: cfg[k] for k in shape if cfg.get(k)})
+    T = (a.seq_len or a.tokens) * max(1, a.batch_size)
+
+    def timed(fn):
+        for _ in range(max(0, a.warmup_iterations)):
+            fn()
+        if dev.startswith("cuda"):
+            torch.cuda.synchronize()
+        ts = []
+        for _ in range(max(1, a.benchmark_iterations)):
+            t0 = time.perf_counter()
+            y = fn()
+            if dev.startswith("cuda"):
+                torch.cuda.synchronize()
+            ts.append(time.perf_counter() - t0)
+        ts.sort()
+        return {"ms": round(ts[len(ts) // 2] * 1e3, 3)}, y
+
     g = torch.Generator().manual_seed(0)
-    q, k = (torch.nn.functional.normalize(torch.randn(T, H, d, generator=g), dim=-1).to(dev) for _ in range(2))
-    v = torch.randn(T, H, d, generator=g).to(dev)
-    gate, beta = torch.rand(T, H, generator=g).mul(0.2).add(0.8).to(dev), torch.rand(T, H, generator=g).to(dev)
+    dt = torch.bfloat16 if dev.startswith("cuda") else torch.float32
     res = {}
-    for name, fn in (("recurrent", gdn_recurrent), ("chunked", gdn_chunked)):
-        fn(q[:8], k[:8], v[:8], gate[:8], beta[:8])
-        if dev == "cuda":
-            torch.cuda.synchronize()
-        t0 = time.time()
-        y, _ = fn(q, k, v, gate, beta)
-        if dev == "cuda":
-            torch.cuda.synchronize()
-        res[name] = {"ms": round((time.time() - t0) * 1e3, 3)}
-        res[name + "_out"] = y
-    err = float((res.pop("recurrent_out") - res.pop("chunked_out")).abs().max())
-    print(json.dumps({"tokens": T, "heads": H, "device": dev, **res, "max_abs_diff": err}))
+
+    def lin(x, w):
+        """The projection as the models run it: the tensor-core GEMM of this package on a GPU."""
+        from ..ops import functional as ops
+        if x.is_cuda and ops.use_native(x) and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0:
+            return ops.lora_linear(x, w, None, None, None, (w.shape[0],), 0, 0.0, None)
+        return torch.nn.functional.linear(x, w)
+
+    if a.stage == "prefill":
+        H, d = a.heads, 64
+        q, k = (torch.nn.functional.normalize(torch.randn(T, H, d, generator=g), dim=-1).to(dev) for _ in range(2))
+        v = torch.randn(T, H, d, generator=g).to(dev)
+        gate, beta = torch.rand(T, H, generator=g).mul(0.2).add(0.8).to(dev), torch.rand(T, H, generator=g).to(dev)
+        res["recurrent"], y0 = timed(lambda: gdn_recurrent(q, k, v, gate, beta)[0])
+        for chunk in (32, 64, 128):
+            res[f"chunked_{chunk}"], y = timed(lambda c=chunk: gdn_chunked(q, k, v, gate, beta, chunk=c)[0])
+            res[f"chunked_{chunk}"]["max_abs_diff"] = float((y - y0).abs().max())
+        res["chunked"] = res["chunked_64"]
+        out = {"stage": a.stage, "tokens": T, "heads": H, "device": dev, **res, "max_abs_diff": res["chunked_64"]["max_abs_diff"]}
+    else:
+        hid = shape["hidden_size"]
+        kd = shape["linear_num_key_heads"] * shape["linear_key_head_dim"]
+        vd = shape["linear_num_value_heads"] * shape["linear_value_head_dim"]
+        nv = shape["linear_num_value_heads"]
+        if a.stage == "input-proj":
+            dims = {"qkv": 2 * kd + vd, "z": vd, "b": nv, "a": nv}
+            x = torch.randn(T, hid, generator=g).to(dev, dt)
+            ws = {n: (torch.randn(o, hid, generator=g) * 0.02).to(dev, dt) for n, o in dims.items()}
+            cat = torch.cat(list(ws.values()), 0)
+            res["separate"], ys = timed(lambda: torch.cat([lin(x, w) for w in ws.values()], -1))
+            res["concatenated"], yc = timed(lambda: lin(x, cat))
+            res["max_abs_diff"] = float((ys.float() - yc.float()).abs().max())
+            flops = 2.0 * T * hid * sum(dims.values())
+        else:
+            x = torch.randn(T, vd, generator=g).to(dev, dt)
+            w = (torch.randn(hid, vd, generator=g) * 0.02).to(dev, dt)
+            res["linear"], _ = timed(lambda: lin(x, w))
+            flops = 2.0 * T * hid * vd
+        for r in res.values():
+            if isinstance(r, dict):
+                r["tflops"] = round(flops / (r["ms"] * 1e-3) / 1e12, 3)
+        out = {"stage": a.stage, "tokens": T, "device": dev, "shape": shape, **res}
+    print(json.dumps(out))
+    if a.output:
+        with open(a.output, "w", encoding="utf-8") as fh:
+            json.dump(out, fh, indent=2)
     return 0
 
 

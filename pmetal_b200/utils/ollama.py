@@ -49,7 +49,7 @@ def validate_model_name(name: str) -> str:
 
 
 def modelfile_text(gguf_path: str, template: str = "chatml", system: Optional[str] = None, adapter: Optional[str] = None,
-                   **params) -> str:
+                   license: Optional[str] = None, **params) -> str:
     if template not in TEMPLATES:
         raise ValueError(f"unknown template {template!r}; choose from {sorted(TEMPLATES)}")
     lines = [f"FROM {gguf_path}"]
@@ -62,12 +62,14 @@ def modelfile_text(gguf_path: str, template: str = "chatml", system: Optional[st
         if v is not None:
             lines.append(f"PARAMETER {k} {v}")
     lines.extend(f'PARAMETER stop "{s}"' for s in STOPS[template])
+    if license:
+        lines.append(f'LICENSE """{license}"""')
     return "\n".join(lines) + "\n"
 
 
 def write_modelfile(gguf_path: str, out_path: str = "Modelfile", template: str = "chatml", system: Optional[str] = None,
-                    adapter: Optional[str] = None, **params) -> str:
+                    adapter: Optional[str] = None, license: Optional[str] = None, **params) -> str:
     with open(out_path, "w", encoding="utf-8") as fh:
         fh.write(modelfile_text(os.path.abspath(gguf_path), template, system,
-                                os.path.abspath(adapter) if adapter else None, **params))
+                                os.path.abspath(adapter) if adapter else None, license, **params))
     return out_path

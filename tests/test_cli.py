@@ -391,3 +391,40 @@ def test_cluster_status_flags(capsys):
     assert main(["cluster", "up", "--wait", "0.25", "--status-interval", "0.1", "--json"]) == 0
     assert len(capsys.readouterr().out.strip().splitlines()) >= 2
     assert main(["cluster", "status", "--min-peers", "64"]) == 1
+
+
+def test_bench_commands_take_the_reference_options(tmp_path, capsys):
+    data = tmp_path / "d.jsonl"
+    data.write_text("".join(json.dumps({"prompt": f"question number {i} " * 3, "response": "an answer " * 4}) + "\n" for i in range(6)))
+    out = tmp_path / "w.json"
+    assert main(["bench-workload", "-m", "random:tiny-qwen3", "--device", "cpu", "--dataset", str(data), "--prompt-samples", "2",
+                 "--max-prompt-tokens", "24", "--decode-steps", "3", "--inference-warmup-passes", "1",
+                 "--inference-session-repeats", "2", "--inference-repeats", "2", "--inference-context", "prompt",
+                 "--train-samples", "2", "--train-steps", "1", "--max-seq-len", "64", "--json", "-o", str(out)]) == 0
+    doc = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    g = doc["generation"]
+    assert g["batch"] == 2 and g["decode_steps"] == 3 and g["sessions"] == 2 and g["warmup_passes"] == 1 and g["timed_passes"] == 4
+    assert max(g["prompt_tokens"]) <= 24 and doc["inference_context"] == "prompt"
+    assert doc["training"]["steps"] == 1 and doc["training"]["samples_per_step"] == 2
+    assert json.load(open(out))["generation"]["batch"] == 2
+    assert main(["bench-gen", "-m", "random:tiny-qwen3", "--device", "cpu", "--preset", "quick"]) == 0
+    doc = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert doc["preset"] == "quick" and doc["generation"]["decode_steps"] == 8 and "training" not in doc
+    for stage in ("prefill", "input-proj", "out-proj"):
+        assert main(["bench-gdn", "--stage", stage, "--seq-len", "16", "--heads", "2", "--device", "cpu", "--warmup-iterations", "0",
+                     "--benchmark-iterations", "1", "-o", str(tmp_path / "g.json")]) == 0
+        assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["stage"] == stage
+    assert json.load(open(tmp_path / "g.json"))["stage"] == "out-proj"
+
+
+def test_dashboard_follows_a_metrics_file_and_modelfile_carries_a_license(tmp_path, capsys):
+    m = tmp_path / "m.jsonl"
+    m.write_text('{"step": 1, "loss": 2.5}\n{"step": 2, "loss": 2.25, "reward": 0.5}\n')
+    assert main(["dashboard", "--metrics-file", str(m), "--once"]) == 0
+    row = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert row["job"] == "metrics" and row["step"] == 2 and row["loss"] == 2.25 and row["reward"] == 0.5
+    assert main(["dashboard", "--once"]) == 2
+    capsys.readouterr()
+    mf = tmp_path / "Modelfile"
+    assert main(["ollama", "modelfile", "--gguf", str(tmp_path / "x.gguf"), "--license", "Apache-2.0", "-o", str(mf)]) == 0
+    assert 'LICENSE """Apache-2.0"""' in mf.read_text()
